@@ -1,0 +1,378 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a: TMA -> shared memory -> tcgen05.mma with
+// fp32 accumulators in TMEM -> tcgen05.ld epilogue.
+//
+//   C[M,N] (+)= A[M,K] * B[N,K]^T  (+ R[M,N])
+//
+// Each operand may be stored with its contraction dimension contiguous ("K-major", e.g. activations
+// [M,K] and nn.Linear weights [N,K]) or with its M/N dimension contiguous ("MN-major", e.g. the weight
+// as the B operand of dX = dY * W, or dY / X as operands of dW = dY^T * X), so forward, grad-input and
+// grad-weight GEMMs all run without a transpose pass.
+//
+// CTA layout (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer (one elected lane) and TMEM
+// owner, warps 2..5 = epilogue (one TMEM lane quarter each).  Two TMEM accumulators of BN columns
+// let the epilogue of tile i overlap the main loop of tile i+1.  One CTA per SM (TMEM and shared
+// memory are sized for that), grid = min(#tiles, #SMs), static round-robin tile schedule with
+// M-grouped rasterisation for L2 reuse.
+#include "common.cuh"
+#include "host.h"
+
+namespace b2 {
+
+constexpr int GEMM_BM = 128;
+constexpr int GEMM_BK = 64;
+constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_GROUP_M = 16;
+
+// epilogue flags
+constexpr int GEMM_OUT_FP32 = 1;     // C is fp32 (else bf16)
+constexpr int GEMM_ACCUMULATE = 2;   // C += result
+constexpr int GEMM_RESIDUAL = 4;     // result += R (bf16, same ld as C)
+
+template <int BN>
+struct GemmCfg {
+  static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
+  static constexpr int B_BYTES = BN * GEMM_BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int TMEM_COLS = 2 * BN;  // 512 or 256: powers of two
+};
+
+struct GemmMnDesc {
+  uint32_t lbo, sbo, kstep;
+};
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 void* __restrict__ Cout, const __nv_bfloat16* __restrict__ R, int M, int N, int K,
+                 int ldc, int flags, GemmMnDesc mn, int* status) {
+  using Cfg = GemmCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + Cfg::STAGES;
+  uint64_t* tmem_full = bars + 2 * Cfg::STAGES;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int num_m = (M + GEMM_BM - 1) / GEMM_BM;
+  const int num_n = (N + BN - 1) / BN;
+  const int num_tiles = num_m * num_n;
+  const int num_kb = (K + GEMM_BK - 1) / GEMM_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_empty[a], 128);
+    }
+    mbar_fence_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+
+  auto tile_coords = [&](int t, int& m_blk, int& n_blk) {
+    const int per_group = GEMM_GROUP_M * num_n;
+    const int g = t / per_group;
+    const int first_m = g * GEMM_GROUP_M;
+    const int gsz = min(GEMM_GROUP_M, num_m - first_m);
+    const int r = t - g * per_group;
+    m_blk = first_m + (r % gsz);
+    n_blk = r / gsz;
+  };
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        int m_blk, n_blk;
+        tile_coords(t, m_blk, n_blk);
+        const int m0 = m_blk * GEMM_BM, n0 = n_blk * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, status, ERR_GEMM_PRODUCER_WAIT)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sA = smem + stage * Cfg::STAGE_BYTES;
+          uint8_t* sB = sA + Cfg::A_BYTES;
+          mbar_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
+          if (!A_MN) {
+            tma_load_2d(sA, &tmA, &full_bar[stage], kb * GEMM_BK, m0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < GEMM_BM / 64; ++c)
+              tma_load_2d(sA + c * 8192, &tmA, &full_bar[stage], m0 + c * 64, kb * GEMM_BK);
+          }
+          if (!B_MN) {
+            tma_load_2d(sB, &tmB, &full_bar[stage], kb * GEMM_BK, n0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(sB + c * 8192, &tmB, &full_bar[stage], n0 + c * 64, kb * GEMM_BK);
+          }
+          if (++stage == Cfg::STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_f16(1, GEMM_BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, status, ERR_GEMM_MMA_WAIT_TMEM)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, status, ERR_GEMM_MMA_WAIT_FULL)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_base = smem_u32(smem + stage * Cfg::STAGE_BYTES);
+          const uint32_t b_base = a_base + Cfg::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < GEMM_BK / 16; ++k) {
+            const uint64_t adesc = A_MN ? make_smem_desc_sw128(a_base + k * mn.kstep, mn.lbo, mn.sbo)
+                                        : make_smem_desc_sw128(a_base + k * 32, 16, 1024);
+            const uint64_t bdesc = B_MN ? make_smem_desc_sw128(b_base + k * mn.kstep, mn.lbo, mn.sbo)
+                                        : make_smem_desc_sw128(b_base + k * 32, 16, 1024);
+            umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == Cfg::STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        umma_commit(&tmem_full[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+      }
+    }
+  } else {
+    const int quarter = warp & 3;  // TMEM lane quarter this warp may read
+    uint32_t acc = 0, acc_phase = 0;
+    const bool out_fp32 = flags & GEMM_OUT_FP32;
+    const bool accumulate = flags & GEMM_ACCUMULATE;
+    const bool residual = flags & GEMM_RESIDUAL;
+    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+      int m_blk, n_blk;
+      tile_coords(t, m_blk, n_blk);
+      const int n0 = n_blk * BN;
+      const int row = m_blk * GEMM_BM + quarter * 32 + lane;
+      if (!mbar_wait(&tmem_full[acc], acc_phase, status, ERR_GEMM_EPI_WAIT)) break;
+      tc_fence_after();
+      const uint32_t t_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(t_base + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (row < M && col0 < N) {
+          const size_t off = static_cast<size_t>(row) * ldc + col0;
+          const bool full = (col0 + 32 <= N);
+          if (residual) {
+            const __nv_bfloat16* rp = R + off;
+            if (full) {
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                uint4 q = *reinterpret_cast<const uint4*>(rp + v * 8);
+                const uint32_t qq[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  float2 f = unpack_bf16x2(qq[j]);
+                  r[v * 8 + 2 * j] = __float_as_uint(__uint_as_float(r[v * 8 + 2 * j]) + f.x);
+                  r[v * 8 + 2 * j + 1] = __float_as_uint(__uint_as_float(r[v * 8 + 2 * j + 1]) + f.y);
+                }
+              }
+            } else {
+              for (int j = 0; j < 32 && col0 + j < N; ++j)
+                r[j] = __float_as_uint(__uint_as_float(r[j]) + __bfloat162float(rp[j]));
+            }
+          }
+          if (out_fp32) {
+            float* cp = reinterpret_cast<float*>(Cout) + off;
+            if (full) {
+#pragma unroll
+              for (int v = 0; v < 8; ++v) {
+                float4 o = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+                                       __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+                if (accumulate) {
+                  float4 p = *reinterpret_cast<float4*>(cp + 4 * v);
+                  o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
+                }
+                *reinterpret_cast<float4*>(cp + 4 * v) = o;
+              }
+            } else {
+              for (int j = 0; j < 32 && col0 + j < N; ++j)
+                cp[j] = __uint_as_float(r[j]) + (accumulate ? cp[j] : 0.f);
+            }
+          } else {
+            __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(Cout) + off;
+            if (full) {
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                float f[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[v * 8 + j]);
+                if (accumulate) {
+                  uint4 q = *reinterpret_cast<const uint4*>(cp + v * 8);
+                  const uint32_t qq[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    float2 p = unpack_bf16x2(qq[j]);
+                    f[2 * j] += p.x;
+                    f[2 * j + 1] += p.y;
+                  }
+                }
+                uint4 o;
+                o.x = pack_bf16x2(f[0], f[1]);
+                o.y = pack_bf16x2(f[2], f[3]);
+                o.z = pack_bf16x2(f[4], f[5]);
+                o.w = pack_bf16x2(f[6], f[7]);
+                *reinterpret_cast<uint4*>(cp + v * 8) = o;
+              }
+            } else {
+              for (int j = 0; j < 32 && col0 + j < N; ++j) {
+                float f = __uint_as_float(r[j]);
+                if (accumulate) f += __bfloat162float(cp[j]);
+                cp[j] = __float2bfloat16(f);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&tmem_empty[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1;
+    }
+  }
+
+  // Common tail: every thread arrives here, also after a wait that ran out.
+  if (*reinterpret_cast<volatile int*>(status) != 0) {
+    // give TMA copies and MMAs still in flight time to land before shared memory / TMEM go away
+    unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+static GemmMnDesc g_mn_desc = {8192u, 1024u, 2048u};
+
+template <int BN, bool A_MN, bool B_MN>
+static int launch_gemm(const void* A, const void* B, void* C, const void* R, int M, int N, int K,
+                       int lda, int ldb, int ldc, int flags, int max_ctas, cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!configured[dev]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES) !=
+        cudaSuccess) {
+      set_error("gemm: cudaFuncSetAttribute(smem=%d) failed", Cfg::SMEM_BYTES);
+      return 1;
+    }
+    configured[dev] = true;
+  }
+  const CUtensorMap* ta = A_MN ? tensor_map_2d_bf16(A, K, M, lda, 64, 64)
+                               : tensor_map_2d_bf16(A, M, K, lda, GEMM_BM, 64);
+  const CUtensorMap* tb = B_MN ? tensor_map_2d_bf16(B, K, N, ldb, 64, 64)
+                               : tensor_map_2d_bf16(B, N, K, ldb, BN, 64);
+  if (!ta || !tb) return 2;
+  int* status = status_ptr();
+  if (!status) return 3;
+  const int num_tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + BN - 1) / BN);
+  int grid = num_sms();
+  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
+  if (num_tiles < grid) grid = num_tiles;
+  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(
+      *ta, *tb, C, reinterpret_cast<const __nv_bfloat16*>(R), M, N, K, ldc, flags, g_mn_desc, status);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("gemm launch failed: %s", cudaGetErrorString(e));
+    return 4;
+  }
+  return 0;
+}
+
+}  // namespace b2
+
+// C[M,N] (+)= A * B^T (+ R).  a_mn / b_mn: 0 = operand stored [rows, K] (K contiguous),
+// 1 = operand stored [K, rows] (rows contiguous).  lda / ldb / ldc in elements.
+// flags: 1 fp32 output, 2 accumulate into C, 4 add bf16 residual R.  bn: 0 = auto, else 128 / 256.
+// max_ctas: 0 = all SMs; a smaller grid leaves SMs free for a concurrent kernel.
+B2_EXPORT int b2_gemm_bf16(const void* A, const void* B, void* C, const void* R, int M, int N, int K,
+                           int lda, int ldb, int ldc, int a_mn, int b_mn, int flags, int bn,
+                           int max_ctas, void* stream_) {
+  using namespace b2;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  const bool out_fp32 = flags & GEMM_OUT_FP32;
+  if ((lda % 8) || (ldb % 8) || (ldc % (out_fp32 ? 4 : 8)) ||
+      (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15) ||
+      (reinterpret_cast<uintptr_t>(C) & 15) || ((flags & GEMM_RESIDUAL) && (R == nullptr ||
+      (reinterpret_cast<uintptr_t>(R) & 15)))) {
+    set_error("gemm: operands need 16-byte aligned bases and leading dimensions (lda %d ldb %d ldc %d)",
+              lda, ldb, ldc);
+    return 10;
+  }
+  if (bn == 0) {
+    const int sms = num_sms();
+    const int tiles256 = ((M + 127) / 128) * ((N + 255) / 256);
+    bn = (tiles256 >= sms || N % 256 == 0) && tiles256 * 2 > sms ? 256 : 128;
+  }
+#define B2_GEMM_CASE(BN_, AMN_, BMN_)                                                              \
+  if (bn == BN_ && a_mn == AMN_ && b_mn == BMN_)                                                   \
+    return launch_gemm<BN_, AMN_ != 0, BMN_ != 0>(A, B, C, R, M, N, K, lda, ldb, ldc, flags, max_ctas, stream);
+  B2_GEMM_CASE(256, 0, 0)
+  B2_GEMM_CASE(256, 0, 1)
+  B2_GEMM_CASE(256, 1, 1)
+  B2_GEMM_CASE(256, 1, 0)
+  B2_GEMM_CASE(128, 0, 0)
+  B2_GEMM_CASE(128, 0, 1)
+  B2_GEMM_CASE(128, 1, 1)
+  B2_GEMM_CASE(128, 1, 0)
+#undef B2_GEMM_CASE
+  set_error("gemm: unsupported configuration bn=%d a_mn=%d b_mn=%d", bn, a_mn, b_mn);
+  return 11;
+}
+
+// Test hook: descriptor strides used for MN-major operands (bytes): distance between 64-element
+// chunks along M/N, distance between 8-row groups along K, and the start-address step per UMMA_K.
+B2_EXPORT void b2_gemm_set_mn_desc(unsigned lbo, unsigned sbo, unsigned kstep) {
+  b2::g_mn_desc.lbo = lbo;
+  b2::g_mn_desc.sbo = sbo;
+  b2::g_mn_desc.kstep = kstep;
+}
