@@ -6,7 +6,7 @@ never calls into it.
 """
 from __future__ import annotations
 
-import ctypes
+import ctypes  # noqa: F401  (re-exported: ops use nv.ctypes)
 import threading
 from typing import Optional
 
@@ -34,6 +34,8 @@ def lib() -> ctypes.CDLL:
             handle = ctypes.CDLL(str(path), mode=ctypes.RTLD_GLOBAL)
             handle.b2_last_error.restype = ctypes.c_char_p
             handle.b2_status_read_and_clear.restype = ctypes.c_int
+            if torch.cuda.is_available():
+                handle.b2_set_device(int(torch.cuda.current_device()))
             _lib = handle
     return _lib
 
@@ -78,3 +80,9 @@ launch_count = 0
 def count_launch(n: int = 1) -> None:
     global launch_count
     launch_count += n
+
+
+def set_device(index: int) -> None:
+    """Tell the kernel library which device this process drives (call after torch.cuda.set_device)."""
+    if torch.cuda.is_available():
+        lib().b2_set_device(int(index))

@@ -1,0 +1,218 @@
+"""LoRA on tensor-parallel linears.
+
+Same roles as the reference (src/distributed/lora.py:46-416): ``LoRAColumnParallel`` shards ``B`` with
+the base layer's output rows and replicates ``A``; ``LoRARowParallel`` shards ``A`` with the base
+layer's input columns, all-reduces the rank-r intermediate and replicates ``B``.  ``apply_lora`` freezes
+the base model and attaches adapters by HF target name; because q|k|v and gate|up are stored fused, a
+fused layer carries one adapter per targeted sub-projection, each writing its own column range.
+Adapter parameters are fp32; the low-rank products run in the activation dtype.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Iterable, List, Optional, Tuple
+
+import torch
+import torch.nn as nn
+
+from ..dist import comm
+from .qwen3 import ColumnParallelLinear, RowParallelLinear, ParallelAttention, ParallelMLP
+
+DEFAULT_TARGETS = ["q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"]
+
+
+class LoRALayer(nn.Module):
+    """Plain (unsharded) adapter: ``delta(x) = (x A^T) B^T * alpha/r``; A kaiming-uniform, B zero."""
+
+    def __init__(self, in_features, out_features, rank=16, alpha=32.0, device=None):
+        super().__init__()
+        self.rank, self.alpha, self.scaling = rank, alpha, alpha / rank
+        self.lora_A = nn.Parameter(torch.empty(rank, in_features, dtype=torch.float32, device=device))
+        self.lora_B = nn.Parameter(torch.zeros(out_features, rank, dtype=torch.float32, device=device))
+        nn.init.kaiming_uniform_(self.lora_A, a=math.sqrt(5))
+
+    def delta(self, x):
+        a = self.lora_A.to(x.dtype)
+        b = self.lora_B.to(x.dtype)
+        return (x @ a.t()) @ b.t() * self.scaling
+
+    def forward(self, x):
+        return self.delta(x)
+
+    def delta_weight(self) -> torch.Tensor:
+        return (self.lora_B @ self.lora_A) * self.scaling
+
+
+class LoRAColumnParallel(LoRALayer):
+    """A ``[r, in]`` replicated (its gradient is a partial sum over TP ranks), B ``[out/tp, r]`` sharded."""
+
+    def __init__(self, in_features, out_local, rank, alpha, tp_group=None, device=None):
+        super().__init__(in_features, out_local, rank, alpha, device)
+        self.tp_group = tp_group
+        self.lora_A.tp_partial_grad = tp_group is not None
+        self.lora_B.tp_sharded = tp_group is not None
+
+
+class LoRARowParallel(LoRALayer):
+    """A ``[r, in/tp]`` sharded, B ``[out, r]`` replicated; the rank-r intermediate is all-reduced."""
+
+    def __init__(self, in_local, out_features, rank, alpha, tp_group=None, device=None):
+        super().__init__(in_local, out_features, rank, alpha, device)
+        self.tp_group = tp_group
+        self.lora_A.tp_sharded = tp_group is not None
+        self.lora_B.tp_partial_grad = False  # every rank sees the full gradient after the all-reduce
+
+    def delta(self, x):
+        a = self.lora_A.to(x.dtype)
+        b = self.lora_B.to(x.dtype)
+        mid = x @ a.t()
+        mid = comm.reduce_from_parallel_region(mid, self.tp_group)
+        return mid @ b.t() * self.scaling
+
+
+class LinearWithLoRA(nn.Module):
+    """Wraps a (possibly fused) parallel linear; ``adapters`` maps a target name to
+    ``(adapter, col_start, col_end)`` in the wrapped layer's local output columns."""
+
+    def __init__(self, base: nn.Module, adapters: Dict[str, Tuple[LoRALayer, int, int]]):
+        super().__init__()
+        self.base = base
+        self.adapters = nn.ModuleDict({k: v[0] for k, v in adapters.items()})
+        self.ranges = {k: (v[1], v[2]) for k, v in adapters.items()}
+        self.merged = False
+
+    @property
+    def weight(self):
+        return self.base.weight
+
+    def forward(self, x, residual=None):
+        is_row = isinstance(self.base, RowParallelLinear)
+        y = self.base(x, residual) if is_row else self.base(x)
+        if self.merged or not self.adapters:
+            return y
+        x2 = x.reshape(-1, x.shape[-1])
+        if not is_row and self.base.tp_size > 1:
+            x2 = comm.gather_sequence(x2, self.base.tp_group) if self.base.sequence_parallel \
+                else comm.copy_to_parallel_region(x2, self.base.tp_group)
+        shape = y.shape
+        y2 = y.reshape(-1, shape[-1])
+        full = len(self.ranges) == 1 and next(iter(self.ranges.values())) == (0, y2.shape[-1])
+        if full:
+            name = next(iter(self.ranges))
+            d = self.adapters[name].delta(x2)
+            if is_row and self.base.sequence_parallel and self.base.tp_size > 1:
+                n = d.shape[0] // self.base.tp_size
+                d = d[self.base.tp_rank * n:(self.base.tp_rank + 1) * n]
+            return (y2 + d).reshape(shape)
+        pieces = []
+        cur = 0
+        for name, (s, e) in sorted(self.ranges.items(), key=lambda kv: kv[1][0]):
+            if s > cur:
+                pieces.append(y2[:, cur:s])
+            pieces.append(y2[:, s:e] + self.adapters[name].delta(x2))
+            cur = e
+        if cur < y2.shape[-1]:
+            pieces.append(y2[:, cur:])
+        return torch.cat(pieces, dim=-1).reshape(shape)
+
+
+def _sub_ranges(parent) -> Dict[str, Tuple[str, int, int]]:
+    """target name -> (attribute of the fused layer on ``parent``, local col start, local col end)."""
+    out = {}
+    if isinstance(parent, ParallelAttention):
+        D = parent.cfg.head_dim
+        hq, hk = parent.heads_local * D, parent.kv_heads_local * D
+        out["q_proj"] = ("qkv_proj", 0, hq)
+        out["k_proj"] = ("qkv_proj", hq, hq + hk)
+        out["v_proj"] = ("qkv_proj", hq + hk, hq + 2 * hk)
+        out["o_proj"] = ("o_proj", 0, parent.o_proj.out_features)
+    elif isinstance(parent, ParallelMLP):
+        base = parent.gate_up_proj.base if isinstance(parent.gate_up_proj, LinearWithLoRA) else parent.gate_up_proj
+        il = base.out_local // 2
+        out["gate_proj"] = ("gate_up_proj", 0, il)
+        out["up_proj"] = ("gate_up_proj", il, 2 * il)
+        out["down_proj"] = ("down_proj", 0, parent.down_proj.out_features)
+    return out
+
+
+def apply_lora(model: nn.Module, rank: int = 16, alpha: float = 32.0,
+               target_modules: Optional[Iterable[str]] = None) -> List[str]:
+    """Freeze every existing parameter and attach adapters to the targeted projections.
+    Returns the qualified names of the adapted sub-projections."""
+    targets = list(target_modules) if target_modules is not None else list(DEFAULT_TARGETS)
+    for p in model.parameters():
+        p.requires_grad_(False)
+    adapted: List[str] = []
+    for mod_name, parent in list(model.named_modules()):
+        table = _sub_ranges(parent)
+        if not table:
+            continue
+        per_attr: Dict[str, Dict[str, Tuple[LoRALayer, int, int]]] = {}
+        for tgt in targets:
+            if tgt not in table:
+                continue
+            attr, s, e = table[tgt]
+            base = getattr(parent, attr)
+            if isinstance(base, LinearWithLoRA):
+                continue
+            dev = base.weight.device
+            grp = base.tp_group if base.tp_size > 1 else None
+            if isinstance(base, RowParallelLinear):
+                ad = LoRARowParallel(base.in_local, base.out_features, rank, alpha, grp, dev)
+            else:
+                ad = LoRAColumnParallel(base.in_features, e - s, rank, alpha, grp, dev)
+            per_attr.setdefault(attr, {})[tgt] = (ad, s, e)
+            adapted.append(f"{mod_name}.{tgt}")
+        for attr, ads in per_attr.items():
+            setattr(parent, attr, LinearWithLoRA(getattr(parent, attr), ads))
+    return adapted
+
+
+def iter_lora(model: nn.Module):
+    for name, mod in model.named_modules():
+        if isinstance(mod, LinearWithLoRA):
+            for tgt, ad in mod.adapters.items():
+                yield name, tgt, mod, ad
+
+
+@torch.no_grad()
+def merge_lora_weights(model: nn.Module, unmerge: bool = False) -> int:
+    """``W += scaling * B A`` on the targeted row / column ranges (``unmerge`` subtracts).  Works
+    shard-locally under TP: column adapters hold the matching rows of B, row adapters the matching
+    columns of A."""
+    n = 0
+    sign = -1.0 if unmerge else 1.0
+    for _, tgt, mod, ad in iter_lora(model):
+        s, e = mod.ranges[tgt]
+        w = mod.base.weight
+        dw = ad.delta_weight().to(w.dtype)
+        if isinstance(mod.base, RowParallelLinear):
+            w.add_(dw, alpha=sign)
+        else:
+            w[s:e].add_(dw, alpha=sign)
+        n += 1
+    for m in model.modules():
+        if isinstance(m, LinearWithLoRA):
+            m.merged = not unmerge
+    return n
+
+
+def get_lora_state_dict(model: nn.Module) -> Dict[str, torch.Tensor]:
+    """``{qualified.target.lora_A|lora_B: tensor}`` of this rank's adapter shards."""
+    out = {}
+    for name, tgt, _, ad in iter_lora(model):
+        out[f"{name}.{tgt}.lora_A"] = ad.lora_A.detach()
+        out[f"{name}.{tgt}.lora_B"] = ad.lora_B.detach()
+    return out
+
+
+@torch.no_grad()
+def load_lora_state_dict(model: nn.Module, state: Dict[str, torch.Tensor]) -> int:
+    n = 0
+    for name, tgt, _, ad in iter_lora(model):
+        for leaf in ("lora_A", "lora_B"):
+            key = f"{name}.{tgt}.{leaf}"
+            if key in state:
+                getattr(ad, leaf).copy_(state[key].to(getattr(ad, leaf).dtype))
+                n += 1
+    return n

@@ -1,0 +1,72 @@
+"""Text evaluation helpers: normalisation, token-F1, smoothed BLEU-4, exact match and an aggregate
+(src/utils/eval_utils.py:22-178)."""
+from __future__ import annotations
+
+import math
+import re
+import string
+from collections import Counter
+from dataclasses import dataclass, field
+from typing import Dict, List
+
+
+def normalize_text(s: str) -> str:
+    s = s.lower()
+    s = "".join(ch for ch in s if ch not in set(string.punctuation))
+    s = re.sub(r"\b(a|an|the)\b", " ", s)
+    return " ".join(s.split())
+
+
+def compute_exact_match(pred: str, ref: str) -> float:
+    return float(normalize_text(pred) == normalize_text(ref))
+
+
+def compute_token_f1(pred: str, ref: str) -> float:
+    p, r = normalize_text(pred).split(), normalize_text(ref).split()
+    if not p or not r:
+        return float(p == r)
+    common = Counter(p) & Counter(r)
+    n = sum(common.values())
+    if n == 0:
+        return 0.0
+    prec, rec = n / len(p), n / len(r)
+    return 2 * prec * rec / (prec + rec)
+
+
+def compute_bleu4(pred: str, ref: str) -> float:
+    """Sentence BLEU-4 with add-one smoothing on the higher-order precisions and brevity penalty."""
+    p, r = normalize_text(pred).split(), normalize_text(ref).split()
+    if not p or not r:
+        return 0.0
+    logs = 0.0
+    for n in range(1, 5):
+        pn = Counter(tuple(p[i:i + n]) for i in range(len(p) - n + 1))
+        rn = Counter(tuple(r[i:i + n]) for i in range(len(r) - n + 1))
+        match = sum((pn & rn).values())
+        total = max(sum(pn.values()), 0)
+        if n == 1:
+            if match == 0:
+                return 0.0
+            prec = match / total
+        else:
+            prec = (match + 1) / (total + 1)
+        logs += 0.25 * math.log(prec)
+    bp = 1.0 if len(p) > len(r) else math.exp(1 - len(r) / len(p))
+    return bp * math.exp(logs)
+
+
+@dataclass
+class EvalMetrics:
+    exact_match: List[float] = field(default_factory=list)
+    f1: List[float] = field(default_factory=list)
+    bleu4: List[float] = field(default_factory=list)
+
+    def add(self, pred: str, ref: str):
+        self.exact_match.append(compute_exact_match(pred, ref))
+        self.f1.append(compute_token_f1(pred, ref))
+        self.bleu4.append(compute_bleu4(pred, ref))
+
+    def summary(self) -> Dict[str, float]:
+        n = max(1, len(self.f1))
+        return {"count": len(self.f1), "exact_match": sum(self.exact_match) / n, "token_f1": sum(self.f1) / n,
+                "bleu4": sum(self.bleu4) / n}

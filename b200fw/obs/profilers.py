@@ -1,0 +1,211 @@
+"""Communication and compute profilers.
+
+* :class:`CommProfiler` — CUDA-event timing per collective, bus-bandwidth formulas, P50/95/99,
+  communication ratio (src/profiling/comm_profiler.py:34-276); adds NVLink 5 peaks and a roofline
+  fraction for fused compute+collective paths.
+* :class:`ComputeProfiler` — FLOP estimator, MFU against a peak table, per-layer timing
+  (src/profiling/compute_profiler.py:53-388); adds the B200 peak (measured when available) and reports
+  both the reference-formula MFU (src/orchestrator/colocate_orchestrator.py:1197-1217) and an exact
+  count including attention and GQA projection sizes.
+"""
+from __future__ import annotations
+
+import contextlib
+import json
+import os
+import time
+from collections import defaultdict
+from typing import Dict, List, Optional
+
+import torch
+
+DEVICE_BANDWIDTH_GBS = {  # per direction per GPU
+    "B200": 900.0, "H100": 450.0, "H20": 450.0, "A100": 300.0, "V100": 150.0, "PCIe4": 32.0,
+}
+MEASURED_NVLINK_GBS = {"B200_peer_copy": 770.0, "B200_allreduce_bus_8x": 725.0}
+PEAK_TFLOPS_BF16 = {"B200": 2250.0, "H100": 989.0, "H20": 148.0, "A100": 312.0, "V100": 125.0, "L40S": 362.0}
+
+
+def measured_peaks(path: Optional[str] = None) -> Dict[str, float]:
+    """Measured roofline denominators for this machine if a ``MEASURED_PEAKS.json`` is present next to
+    the package (hbm_gbs, bf16_tflops, bf16_tflops_sustained); otherwise an earlier measurement on the
+    same kind of GPU, flagged ``source = fallback``."""
+    cand = [path] if path else []
+    here = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    cand.append(os.path.join(here, "MEASURED_PEAKS.json"))
+    for c in cand:
+        if c and os.path.exists(c):
+            with open(c) as f:
+                d = json.load(f)
+            d["source"] = "measured"
+            return d
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def _pct(v: List[float], q: float) -> float:
+    if not v:
+        return 0.0
+    s = sorted(v)
+    i = min(len(s) - 1, max(0, int(round(q * (len(s) - 1)))))
+    return s[i]
+
+
+class CommProfiler:
+    def __init__(self, device_name: str = "B200", enabled: bool = True):
+        self.enabled = enabled
+        self.device_name = device_name
+        self.records: Dict[str, List[Dict[str, float]]] = defaultdict(list)
+        self.total_step_ms = 0.0
+
+    @contextlib.contextmanager
+    def profile_op(self, op: str, nbytes: int, world_size: int):
+        if not self.enabled:
+            yield
+            return
+        cuda = torch.cuda.is_available()
+        if cuda:
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+        t0 = time.perf_counter()
+        yield
+        if cuda:
+            e.record()
+            e.synchronize()
+            ms = s.elapsed_time(e)
+        else:
+            ms = (time.perf_counter() - t0) * 1e3
+        self.add(op, nbytes, world_size, ms)
+
+    def add(self, op: str, nbytes: int, world_size: int, ms: float):
+        self.records[op].append({"bytes": nbytes, "world": world_size, "ms": ms,
+                                 "bus_gbs": self.bus_bandwidth(op, nbytes, world_size, ms)})
+
+    @staticmethod
+    def bus_bandwidth(op: str, nbytes: int, n: int, ms: float) -> float:
+        """Ring-equivalent bus bandwidth in GB/s: all_reduce 2(n-1)/n, all_gather / reduce_scatter
+        (n-1)/n of the full tensor, broadcast / p2p 1."""
+        if ms <= 0 or n <= 0:
+            return 0.0
+        factor = {"all_reduce": 2.0 * (n - 1) / n, "all_gather": (n - 1) / n, "reduce_scatter": (n - 1) / n}.get(op, 1.0)
+        return nbytes * factor / (ms * 1e-3) / 1e9
+
+    @staticmethod
+    def fused_roofline(flops: float, wire_bytes: float, ms: float, peak_tflops: float,
+                       link_gbs: float = MEASURED_NVLINK_GBS["B200_peer_copy"]) -> Dict[str, float]:
+        """Target time of a fused compute+collective kernel = max(compute at peak, bytes over the link);
+        returns the target, the bound and achieved/target."""
+        t_c = flops / (peak_tflops * 1e12) * 1e3
+        t_w = wire_bytes / (link_gbs * 1e9) * 1e3
+        tgt = max(t_c, t_w)
+        return {"t_compute_ms": t_c, "t_wire_ms": t_w, "target_ms": tgt,
+                "bound": "compute" if t_c >= t_w else "wire", "fraction": tgt / ms if ms > 0 else 0.0}
+
+    def set_step_time(self, ms: float):
+        self.total_step_ms += ms
+
+    def get_summary(self) -> Dict:
+        out: Dict = {"ops": {}}
+        total = 0.0
+        for op, recs in self.records.items():
+            ms = [r["ms"] for r in recs]
+            bw = [r["bus_gbs"] for r in recs]
+            total += sum(ms)
+            out["ops"][op] = {"count": len(recs), "total_ms": sum(ms), "mean_ms": sum(ms) / len(ms),
+                              "p50_ms": _pct(ms, 0.5), "p95_ms": _pct(ms, 0.95), "p99_ms": _pct(ms, 0.99),
+                              "mean_bus_gbs": sum(bw) / len(bw),
+                              "peak_fraction": (sum(bw) / len(bw)) / DEVICE_BANDWIDTH_GBS.get(self.device_name, 900.0)}
+        out["total_comm_ms"] = total
+        out["comm_ratio"] = total / self.total_step_ms if self.total_step_ms > 0 else 0.0
+        return out
+
+
+class ComputeProfiler:
+    def __init__(self, device_name: str = "B200", peak_tflops: Optional[float] = None, enabled: bool = True):
+        self.enabled = enabled
+        self.device_name = device_name
+        mp = measured_peaks()
+        self.peak_tflops = peak_tflops or (mp["bf16_tflops_sustained"] if device_name == "B200"
+                                           else PEAK_TFLOPS_BF16.get(device_name, 1000.0))
+        self.layer_ms: Dict[str, List[float]] = defaultdict(list)
+
+    # ---- FLOPs -----------------------------------------------------------------------------------
+    @staticmethod
+    def reference_formula_flops(L, B, S, H, I, V, full: bool = True) -> float:
+        """The reference's estimate: fwd = L*2*B*S*(4H^2+3HI) + 2*B*S*H*V; x3 full / x2 LoRA."""
+        fwd = L * 2.0 * B * S * (4 * H * H + 3 * H * I) + 2.0 * B * S * H * V
+        return fwd * (3 if full else 2)
+
+    @staticmethod
+    def exact_flops(cfg, B: int, S: int, full: bool = True, causal: bool = True,
+                    grad_checkpoint: bool = False) -> float:
+        """Matmul FLOPs of one training step's forward+backward: GQA-sized projections, SwiGLU FFN,
+        causal attention (S^2 terms halved), LM head."""
+        T = B * S
+        D = cfg.head_dim
+        proj = cfg.hidden_size * D * (2 * cfg.num_heads + 2 * cfg.num_kv_heads)
+        ffn = 3 * cfg.hidden_size * cfg.intermediate_size
+        attn = 2 * S * cfg.num_heads * D * (0.5 if causal else 1.0)  # per token: QK^T and PV, MACs
+        per_tok = cfg.num_layers * (proj + ffn + attn) + cfg.hidden_size * cfg.vocab_size
+        fwd = 2.0 * T * per_tok
+        mult = (3 if full else 2) + (1 if grad_checkpoint else 0)
+        return fwd * mult
+
+    def compute_mfu(self, flops: float, step_s: float, n_gpus: int = 1) -> float:
+        return flops / (step_s * n_gpus * self.peak_tflops * 1e12) if step_s > 0 else 0.0
+
+    # ---- per-layer timing --------------------------------------------------------------------------
+    @contextlib.contextmanager
+    def profile_layer(self, name: str):
+        if not self.enabled:
+            yield
+            return
+        cuda = torch.cuda.is_available()
+        if cuda:
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+        t0 = time.perf_counter()
+        yield
+        if cuda:
+            e.record()
+            e.synchronize()
+            self.layer_ms[name].append(s.elapsed_time(e))
+        else:
+            self.layer_ms[name].append((time.perf_counter() - t0) * 1e3)
+
+    def profile_model(self, model, run, warmup: int = 1, iters: int = 3) -> Dict[str, float]:
+        """Time every top-level layer of ``model`` with forward hooks while ``run()`` executes."""
+        starts: Dict[str, float] = {}
+        hooks = []
+        cuda = torch.cuda.is_available()
+
+        def pre(name):
+            def f(_m, _i):
+                if cuda:
+                    torch.cuda.synchronize()
+                starts[name] = time.perf_counter()
+            return f
+
+        def post(name):
+            def f(_m, _i, _o):
+                if cuda:
+                    torch.cuda.synchronize()
+                self.layer_ms[name].append((time.perf_counter() - starts[name]) * 1e3)
+            return f
+
+        for name, mod in model.named_modules():
+            if name and name.count(".") <= 1:
+                hooks.append(mod.register_forward_pre_hook(pre(name)))
+                hooks.append(mod.register_forward_hook(post(name)))
+        try:
+            for i in range(warmup + iters):
+                if i == warmup:
+                    self.layer_ms.clear()
+                run()
+        finally:
+            for h in hooks:
+                h.remove()
+        return {k: sum(v) / len(v) for k, v in self.layer_ms.items()}
+
+    def get_summary(self) -> Dict:
+        return {"peak_tflops": self.peak_tflops,
+                "layers": {k: {"count": len(v), "mean_ms": sum(v) / len(v)} for k, v in self.layer_ms.items() if v}}

@@ -1,0 +1,112 @@
+"""Schedule timeline: event tracking, ASCII Gantt chart, Chrome-trace JSON, utilisation statistics and
+a two-run comparison (src/profiling/schedule_visualizer.py:79-467)."""
+from __future__ import annotations
+
+import contextlib
+import json
+import time
+from dataclasses import dataclass, asdict
+from typing import Dict, List, Optional
+
+
+@dataclass
+class TimelineEvent:
+    name: str
+    category: str   # e.g. forward / backward / comm / optimizer / rollout / sync
+    lane: str       # row of the chart: "rank0/compute", "stage1", ...
+    start_ms: float
+    end_ms: float
+    meta: Optional[Dict] = None
+
+    @property
+    def duration_ms(self) -> float:
+        return self.end_ms - self.start_ms
+
+
+class ScheduleVisualizer:
+    SYMBOLS = {"forward": "F", "backward": "B", "comm": "c", "optimizer": "O", "rollout": "R", "sync": "s", "idle": "."}
+
+    def __init__(self):
+        self.events: List[TimelineEvent] = []
+        self._t0 = time.perf_counter()
+
+    def now_ms(self) -> float:
+        return (time.perf_counter() - self._t0) * 1e3
+
+    def add_event(self, name, category, lane, start_ms, end_ms, meta=None):
+        self.events.append(TimelineEvent(name, category, lane, start_ms, end_ms, meta))
+
+    @contextlib.contextmanager
+    def track(self, name: str, category: str, lane: str = "main", meta=None):
+        s = self.now_ms()
+        try:
+            yield
+        finally:
+            self.add_event(name, category, lane, s, self.now_ms(), meta)
+
+    def lanes(self) -> List[str]:
+        seen = []
+        for e in self.events:
+            if e.lane not in seen:
+                seen.append(e.lane)
+        return seen
+
+    def ascii_gantt(self, width: int = 100) -> str:
+        if not self.events:
+            return "(no events)"
+        t0 = min(e.start_ms for e in self.events)
+        t1 = max(e.end_ms for e in self.events)
+        span = max(t1 - t0, 1e-9)
+        rows = []
+        label_w = max(len(l) for l in self.lanes())
+        for lane in self.lanes():
+            row = [self.SYMBOLS["idle"]] * width
+            for e in (x for x in self.events if x.lane == lane):
+                a = int((e.start_ms - t0) / span * (width - 1))
+                b = max(a, int((e.end_ms - t0) / span * (width - 1)))
+                sym = self.SYMBOLS.get(e.category, e.category[:1].upper() or "?")
+                for i in range(a, b + 1):
+                    row[i] = sym
+            rows.append(f"{lane.ljust(label_w)} |{''.join(row)}|")
+        rows.append(f"{' ' * label_w}  0 ms{' ' * (width - 14)}{span:8.2f} ms")
+        return "\n".join(rows)
+
+    def chrome_trace(self) -> Dict:
+        lanes = {l: i for i, l in enumerate(self.lanes())}
+        ev = [{"name": e.name, "cat": e.category, "ph": "X", "ts": e.start_ms * 1e3, "dur": e.duration_ms * 1e3,
+               "pid": 0, "tid": lanes[e.lane], "args": e.meta or {}} for e in self.events]
+        ev += [{"name": "thread_name", "ph": "M", "pid": 0, "tid": i, "args": {"name": l}} for l, i in lanes.items()]
+        return {"traceEvents": ev, "displayTimeUnit": "ms"}
+
+    def save_chrome_trace(self, path: str):
+        with open(path, "w") as f:
+            json.dump(self.chrome_trace(), f)
+
+    def utilisation(self) -> Dict[str, Dict[str, float]]:
+        if not self.events:
+            return {}
+        t0 = min(e.start_ms for e in self.events)
+        t1 = max(e.end_ms for e in self.events)
+        span = max(t1 - t0, 1e-9)
+        out = {}
+        for lane in self.lanes():
+            by_cat: Dict[str, float] = {}
+            busy = 0.0
+            for e in (x for x in self.events if x.lane == lane):
+                by_cat[e.category] = by_cat.get(e.category, 0.0) + e.duration_ms
+                busy += e.duration_ms
+            out[lane] = {"busy_ms": busy, "span_ms": span, "utilisation": min(1.0, busy / span),
+                         "bubble_ratio": max(0.0, 1.0 - busy / span), **{f"{k}_ms": v for k, v in by_cat.items()}}
+        return out
+
+    @staticmethod
+    def compare(a: "ScheduleVisualizer", b: "ScheduleVisualizer", names=("a", "b")) -> Dict:
+        ua, ub = a.utilisation(), b.utilisation()
+        span = lambda u: max((v["span_ms"] for v in u.values()), default=0.0)
+        mean_u = lambda u: sum(v["utilisation"] for v in u.values()) / max(1, len(u))
+        return {names[0]: {"span_ms": span(ua), "mean_utilisation": mean_u(ua)},
+                names[1]: {"span_ms": span(ub), "mean_utilisation": mean_u(ub)},
+                "speedup": span(ua) / span(ub) if span(ub) > 0 else 0.0}
+
+    def to_rows(self) -> List[Dict]:
+        return [asdict(e) for e in self.events]

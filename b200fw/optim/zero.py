@@ -1,0 +1,460 @@
+"""Bucketed flat-buffer AdamW with ZeRO stage 0 / 1 / 2 / 3 sharding over the data-parallel group.
+
+What the stages shard (same contract as the reference's three optimizers,
+src/distributed/zero_optim.py:48-266, zero_optim_v2.py:46-362, zero_optim_v3.py:56-479):
+
+* stage 0 — nothing (plain fused AdamW on fp32 masters);
+* stage 1 — fp32 master weights and Adam moments; gradients are reduce-scattered at ``step``;
+* stage 2 — also gradients: every backward ends with a reduce-scatter into an fp32 shard accumulator
+  and the full-size gradient buffers are released;
+* stage 3 — also parameters: between steps each rank keeps only its shard; ``pre_forward`` gathers,
+  ``post_backward`` releases.
+
+Design differences from the reference: parameters live in *buckets* (tens of MB) instead of one
+whole-model buffer, each bucket is sharded over the DP ranks, and a bucket's reduce-scatter is
+launched as soon as its last gradient is written (overlapping the rest of the backward pass) rather
+than as one unbucketed call after the last hook.  Gradient scaling (1/world), the global-norm clip,
+the NaN/Inf guard, AdamW and the bf16 write-back are one kernel per bucket shard.  Weight gradients
+are written by the GEMM epilogues straight into the bucket buffers (``param.main_grad``), so there is
+no per-parameter copy in or out of flat buffers.
+
+Tensor-parallel awareness: parameters tagged ``tp_partial_grad`` (per-head q/k norms, and all norm
+weights under sequence parallelism) hold partial gradients and are summed over the TP group; the
+global norm counts TP-sharded parameters once per shard and replicated parameters once.  (The
+reference sums *every* replicated parameter's gradient over TP, which scales the norm weights',
+embedding's and LM head's gradients by ``tp`` — src/engines/train_engine.py:1478-1482.)
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+from ..dist.context import ParallelContext
+
+KIND_TP_PARTIAL, KIND_REPLICATED, KIND_TP_SHARDED = 0, 1, 2
+
+
+class _Bucket:
+    def __init__(self, params: List[torch.nn.Parameter], kind: int, world: int, rank: int, dtype, device,
+                 grad_dtype):
+        self.params, self.kind = params, kind
+        self.offsets, n = [], 0
+        for p in params:
+            self.offsets.append(n)
+            n += (p.numel() + 7) // 8 * 8  # keep every parameter 16-byte aligned (TMA operands)
+        align = world * 8
+        self.numel = (n + align - 1) // align * align
+        self.shard_numel = self.numel // world
+        self.shard_start = rank * self.shard_numel
+        self.dtype, self.grad_dtype, self.device = dtype, grad_dtype, device
+        self.param_buf: Optional[torch.Tensor] = torch.zeros(self.numel, dtype=dtype, device=device)
+        self.grad_buf: Optional[torch.Tensor] = None
+        self.pending = 0
+        self.reduced = False
+        self.work = None
+        with torch.no_grad():
+            for p, o in zip(params, self.offsets):
+                self.param_buf[o:o + p.numel()].copy_(p.data.reshape(-1))
+        self.bind_params()
+
+    def bind_params(self):
+        for p, o in zip(self.params, self.offsets):
+            p.data = self.param_buf[o:o + p.numel()].view(p.shape)
+
+    def unbind_params(self):
+        empty = torch.empty(0, dtype=self.dtype, device=self.device)
+        for p in self.params:
+            p.data = empty
+        self.param_buf = None
+
+    def ensure_grad_buf(self, use_main_grad: bool):
+        if self.grad_buf is None:
+            self.grad_buf = torch.zeros(self.numel, dtype=self.grad_dtype, device=self.device)
+            if use_main_grad:
+                for p, o in zip(self.params, self.offsets):
+                    p.main_grad = self.grad_buf[o:o + p.numel()].view(p.shape)
+                    p.grad_filled = False
+
+    def release_grad_buf(self):
+        self.grad_buf = None
+        for p in self.params:
+            if hasattr(p, "main_grad"):
+                p.main_grad = None
+                del p.main_grad
+            p.grad_filled = False
+
+    def param_shard(self) -> torch.Tensor:
+        return self.param_buf[self.shard_start:self.shard_start + self.shard_numel]
+
+
+class ZeROOptimizer:
+    """AdamW over bucketed flat buffers; ``stage`` selects what is sharded over ``dp_group``."""
+
+    def __init__(self, params, lr=1e-5, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, stage: int = 1,
+                 ctx: Optional[ParallelContext] = None, dp_group=None, bucket_mb: float = 64.0,
+                 max_grad_norm: float = 0.0, grad_dtype: Optional[torch.dtype] = None,
+                 overlap: bool = True):
+        params = [p for p in params if p.requires_grad]
+        assert params, "no trainable parameters"
+        self.ctx = ctx
+        self.dp_group = dp_group if dp_group is not None else (ctx.dp_group if ctx is not None else None)
+        self.world = dist.get_world_size(self.dp_group) if self.dp_group is not None else 1
+        self.rank = dist.get_rank(self.dp_group) if self.dp_group is not None else 0
+        self.stage = stage if self.world > 1 else min(stage, 1)
+        self.requested_stage = stage
+        self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
+        self.max_grad_norm = max_grad_norm
+        self.step_count = 0
+        self.accumulation_count = 0
+        self.device = params[0].device
+        self.dtype = params[0].dtype
+        self.on_cuda = self.device.type == "cuda"
+        # gradient-accumulation fusion (GEMM epilogues write into bucket buffers) needs the kernels
+        self.use_main_grad = self.on_cuda and self.dtype == torch.bfloat16
+        self.grad_dtype = grad_dtype or (torch.bfloat16 if self.dtype == torch.bfloat16 else torch.float32)
+        self.overlap = overlap and self.on_cuda
+        self.comm_stream = torch.cuda.Stream(device=self.device, priority=-1) if self.overlap else None
+        self.sync_this_backward = True
+        self.params_gathered = True
+
+        # ---- bucket assignment: by TP kind, big ones split by size in reverse (backward) order -----
+        by_kind: Dict[int, List[torch.nn.Parameter]] = {0: [], 1: [], 2: []}
+        for p in params:
+            kind = KIND_TP_PARTIAL if getattr(p, "tp_partial_grad", False) else (
+                KIND_TP_SHARDED if getattr(p, "tp_sharded", False) else KIND_REPLICATED)
+            by_kind[kind].append(p)
+        limit = int(bucket_mb * 1024 * 1024 / params[0].element_size())
+        self.buckets: List[_Bucket] = []
+        for kind in (KIND_TP_SHARDED, KIND_REPLICATED, KIND_TP_PARTIAL):
+            cur, cur_n = [], 0
+            for p in reversed(by_kind[kind]):
+                if cur and cur_n + p.numel() > limit:
+                    self.buckets.append(_Bucket(cur, kind, self.world, self.rank, self.dtype, self.device, self.grad_dtype))
+                    cur, cur_n = [], 0
+                cur.append(p)
+                cur_n += p.numel()
+            if cur:
+                self.buckets.append(_Bucket(cur, kind, self.world, self.rank, self.dtype, self.device, self.grad_dtype))
+        for b in self.buckets:
+            for p in b.params:
+                p._zero_bucket = b
+                if self.use_main_grad:
+                    p.grad_ready_hook = self._on_grad_ready
+        # ---- sharded optimizer state ---------------------------------------------------------------
+        sizes = [b.shard_numel if self.stage >= 1 else b.numel for b in self.buckets]
+        self.shard_offsets = [0]
+        for s in sizes:
+            self.shard_offsets.append(self.shard_offsets[-1] + s)
+        total = self.shard_offsets[-1]
+        self.master = torch.empty(total, dtype=torch.float32, device=self.device)
+        for i, b in enumerate(self.buckets):
+            src = b.param_shard() if self.stage >= 1 else b.param_buf
+            self._shard_view(self.master, i).copy_(src.float())
+        self.exp_avg = torch.zeros_like(self.master)
+        self.exp_avg_sq = torch.zeros_like(self.master)
+        self.grad_acc = torch.zeros_like(self.master) if self.stage >= 2 else None
+        self.grad_acc_filled = False
+        self.hyper = torch.zeros(8, dtype=torch.float32, device=self.device)
+        self._hyper_host = torch.zeros(8, dtype=torch.float32, pin_memory=self.on_cuda)
+        self.norm_sq = torch.zeros(1, dtype=torch.float32, device=self.device)
+        self._norm_parts = torch.zeros(2, dtype=torch.float32, device=self.device)
+        self._reduced_shards: Dict[int, torch.Tensor] = {}
+        self.param_groups = [{"lr": lr, "weight_decay": weight_decay, "betas": betas, "eps": eps}]
+        if self.stage >= 3:
+            self._release_params()
+        self._prepare_backward()
+
+    # ---- helpers -----------------------------------------------------------------------------
+    def _shard_view(self, flat: torch.Tensor, i: int) -> torch.Tensor:
+        return flat[self.shard_offsets[i]:self.shard_offsets[i + 1]]
+
+    def _prepare_backward(self):
+        for b in self.buckets:
+            b.reduced = False
+            b.work = None
+            b.pending = sum(int(getattr(p, "grad_contribs", 1)) for p in b.params)
+            if self.use_main_grad:
+                b.ensure_grad_buf(True)
+                for p in b.params:
+                    if self.accumulation_count == 0 or self.stage >= 2:
+                        p.grad_filled = False
+
+    def begin_backward(self, sync: bool = True):
+        """Declare whether the coming backward is the last of the accumulation window (stage 1 only
+        reduces then; stages 2/3 reduce after every backward)."""
+        self.sync_this_backward = sync or self.stage >= 2
+
+    # ---- gradient reduction ----------------------------------------------------------------------
+    def _on_grad_ready(self, p):
+        b = p._zero_bucket
+        b.pending -= 1
+        if b.pending == 0 and self.overlap and self.sync_this_backward and self.world > 1 and not b.reduced:
+            self._launch_reduce(b, async_op=True)
+
+    def _tp_group(self):
+        return self.ctx.tp_group if (self.ctx is not None and self.ctx.tp_size > 1) else None
+
+    def _launch_reduce(self, b: _Bucket, async_op: bool):
+        """TP sum for partial-grad buckets, then reduce-scatter (sum) over DP into this rank's shard."""
+        idx = self.buckets.index(b)
+        if async_op:
+            self.comm_stream.wait_stream(torch.cuda.current_stream())
+            stream_ctx = torch.cuda.stream(self.comm_stream)
+        else:
+            import contextlib
+            stream_ctx = contextlib.nullcontext()
+        with stream_ctx:
+            if b.kind == KIND_TP_PARTIAL and self._tp_group() is not None:
+                dist.all_reduce(b.grad_buf, group=self._tp_group())
+            if self.world > 1:
+                out = torch.empty(b.shard_numel, dtype=b.grad_buf.dtype, device=self.device)
+                dist.reduce_scatter_tensor(out, b.grad_buf, group=self.dp_group)
+            else:
+                out = b.grad_buf
+            if self.stage >= 2:
+                acc = self._shard_view(self.grad_acc, idx)
+                if self.grad_acc_filled:
+                    acc.add_(out.float())
+                else:
+                    acc.copy_(out.float())
+            else:
+                self._reduced_shards[idx] = out
+            if async_op:
+                b.work = torch.cuda.Event()
+                b.work.record(self.comm_stream)
+                b.grad_buf.record_stream(self.comm_stream)
+        b.reduced = True
+
+    def _pack_autograd_grads(self):
+        """CPU / non-fused path: copy ``p.grad`` into the bucket buffers."""
+        for b in self.buckets:
+            b.ensure_grad_buf(False)
+            for p, o in zip(b.params, b.offsets):
+                if p.grad is not None:
+                    b.grad_buf[o:o + p.numel()].copy_(p.grad.reshape(-1))
+                else:
+                    b.grad_buf[o:o + p.numel()].zero_()
+
+    def post_backward(self):
+        """Finish this backward's gradient reduction.  Stage 2/3: every call reduces and releases the
+        full gradients (and stage 3 the full parameters); stage 0/1: a no-op until ``step``."""
+        self.accumulation_count += 1
+        if self.stage >= 2:
+            self._reduce_all()
+            self.grad_acc_filled = True
+            for b in self.buckets:
+                if self.use_main_grad:
+                    b.release_grad_buf()
+                else:
+                    b.grad_buf = None
+                    for p in b.params:
+                        p.grad = None
+            if self.stage >= 3:
+                self._release_params()
+            self._prepare_backward()
+
+    def _reduce_all(self):
+        if not self.use_main_grad:
+            self._pack_autograd_grads()
+        for b in self.buckets:
+            if not b.reduced:
+                self._launch_reduce(b, async_op=False)
+        if self.overlap:
+            torch.cuda.current_stream().wait_stream(self.comm_stream)
+
+    # ---- ZeRO-3 parameter residency --------------------------------------------------------------
+    def _release_params(self):
+        if not self.params_gathered:
+            return
+        for b in self.buckets:
+            b.unbind_params()
+        self.params_gathered = False
+
+    def pre_forward(self):
+        """Stage 3: all-gather every bucket's parameters from the bf16 image of the fp32 shards."""
+        if self.stage < 3 or self.params_gathered:
+            return
+        for i, b in enumerate(self.buckets):
+            b.param_buf = torch.empty(b.numel, dtype=b.dtype, device=self.device)
+            shard = self._shard_view(self.master, i).to(b.dtype)
+            dist.all_gather_into_tensor(b.param_buf, shard, group=self.dp_group)
+            b.bind_params()
+        self.params_gathered = True
+
+    def pre_eval(self):
+        self.pre_forward()
+
+    def post_eval(self):
+        if self.stage >= 3:
+            self._release_params()
+
+    class _EvalCtx:
+        def __init__(self, opt):
+            self.opt = opt
+
+        def __enter__(self):
+            self.opt.pre_eval()
+
+        def __exit__(self, *a):
+            self.opt.post_eval()
+
+    def eval_mode(self):
+        return ZeROOptimizer._EvalCtx(self)
+
+    # ---- norm / step ---------------------------------------------------------------------------
+    def _grad_shard(self, i: int) -> torch.Tensor:
+        if self.stage >= 2:
+            return self._shard_view(self.grad_acc, i)
+        if self.stage == 0 or self.world == 1:
+            return self.buckets[i].grad_buf
+        return self._reduced_shards[i]
+
+    def clip_grad_norm(self, max_norm: Optional[float] = None) -> torch.Tensor:
+        """Reduce gradients if still pending, compute the global L2 norm of the *averaged* gradient
+        over DP, TP and PP, and arm the clip for ``step``.  Returns a 0-d tensor (``-1`` marks a
+        non-finite norm; ``step`` then leaves the weights untouched), without a host sync."""
+        if max_norm is not None:
+            self.max_grad_norm = max_norm
+        if self.stage < 2:
+            self._reduce_all()
+        inv = 1.0 / self.world
+        self._norm_parts.zero_()
+        for i, b in enumerate(self.buckets):
+            g = self._grad_shard(i)
+            ops.sumsq(g, self._norm_parts[1:2] if b.kind == KIND_TP_SHARDED else self._norm_parts[0:1])
+        parts = self._norm_parts * (inv * inv)
+        if self.world > 1 and self.stage >= 1:
+            dist.all_reduce(parts, group=self.dp_group)
+        if self._tp_group() is not None:
+            sharded = parts[1:2].clone()
+            dist.all_reduce(sharded, group=self._tp_group())
+            parts = torch.cat([parts[0:1], sharded])
+        total = parts.sum().reshape(1)
+        if self.ctx is not None and self.ctx.pp_size > 1:
+            dist.all_reduce(total, group=self.ctx.pp_group)
+        self.norm_sq.copy_(total)
+        norm = total.sqrt().squeeze(0)
+        return torch.where(torch.isfinite(norm), norm, torch.full_like(norm, -1.0))
+
+    def _write_hyper(self):
+        t = self.step_count + 1
+        b1, b2 = self.betas
+        lr = self.param_groups[0]["lr"]
+        self._hyper_host.copy_(torch.tensor([lr, b1, b2, self.eps, self.param_groups[0]["weight_decay"],
+                                             1 - b1 ** t, 1 - b2 ** t, self.max_grad_norm]))
+        self.hyper.copy_(self._hyper_host, non_blocking=True)
+
+    def step(self, use_norm: bool = True):
+        """AdamW on the owned shards (clipped by the norm armed in ``clip_grad_norm``; skipped on the
+        device when that norm is not finite), then publish the updated bf16 parameters."""
+        if self.stage < 2:
+            self._reduce_all()
+        self._write_hyper()
+        inv = 1.0 / self.world
+        for i, b in enumerate(self.buckets):
+            g = self._grad_shard(i)
+            gather = self.stage >= 1 and self.world > 1
+            if self.stage >= 3:
+                out = None
+            elif gather:
+                out = b.param_shard()
+            else:
+                out = b.param_buf
+            if out is not None and out.dtype != torch.bfloat16:
+                out_arg = None
+            else:
+                out_arg = out
+            ops.fused_adamw(self._shard_view(self.master, i), self._shard_view(self.exp_avg, i),
+                            self._shard_view(self.exp_avg_sq, i), g, self.hyper, param_out=out_arg,
+                            norm_sq=self.norm_sq if use_norm else None, grad_scale=inv)
+            if out is not None and out_arg is None:
+                out.copy_(self._shard_view(self.master, i).to(out.dtype))
+            if gather and self.stage < 3:
+                dist.all_gather_into_tensor(b.param_buf, b.param_shard().clone(), group=self.dp_group)
+        self.step_count += 1
+
+    def zero_grad(self, set_to_none: bool = True):
+        self.accumulation_count = 0
+        self.grad_acc_filled = False
+        self._reduced_shards.clear()
+        for b in self.buckets:
+            for p in b.params:
+                p.grad = None
+        self._prepare_backward()
+
+    # ---- state ---------------------------------------------------------------------------------
+    def state_dict(self) -> Dict:
+        return {
+            "type": f"zero{self.requested_stage}", "stage": self.stage, "world": self.world, "rank": self.rank,
+            "step_count": self.step_count, "accumulation_count": self.accumulation_count,
+            "local_shard": self.master.detach().cpu(), "exp_avg": self.exp_avg.detach().cpu(),
+            "exp_avg_sq": self.exp_avg_sq.detach().cpu(), "shard_offsets": list(self.shard_offsets),
+            "lr": self.param_groups[0]["lr"],
+        }
+
+    def load_state_dict(self, sd: Dict) -> bool:
+        if sd.get("world") != self.world or tuple(sd["local_shard"].shape) != tuple(self.master.shape):
+            return False
+        self.master.copy_(sd["local_shard"])
+        self.exp_avg.copy_(sd["exp_avg"])
+        self.exp_avg_sq.copy_(sd["exp_avg_sq"])
+        self.step_count = int(sd["step_count"])
+        self.accumulation_count = 0
+        self.resync_params()
+        return True
+
+    @torch.no_grad()
+    def resync_params(self):
+        """Re-publish the parameters from the fp32 masters (after loading a checkpoint)."""
+        if self.stage >= 3:
+            self._release_params()
+            return
+        for i, b in enumerate(self.buckets):
+            src = self._shard_view(self.master, i).to(b.dtype)
+            if self.stage >= 1 and self.world > 1:
+                dist.all_gather_into_tensor(b.param_buf, src, group=self.dp_group)
+            else:
+                b.param_buf.copy_(src)
+
+    @torch.no_grad()
+    def refresh_masters_from_params(self):
+        """Re-derive the fp32 masters from the current parameters (after loading weights)."""
+        for i, b in enumerate(self.buckets):
+            assert b.param_buf is not None, "gather parameters first"
+            src = b.param_shard() if self.stage >= 1 else b.param_buf
+            self._shard_view(self.master, i).copy_(src.float())
+
+    def memory_bytes(self) -> Dict[str, int]:
+        es = torch.tensor([], dtype=self.dtype).element_size()
+        return {
+            "params": sum(b.numel for b in self.buckets) * es if self.params_gathered else 0,
+            "master+moments": self.master.numel() * 12,
+            "grad_acc": 0 if self.grad_acc is None else self.grad_acc.numel() * 4,
+            "grad_bufs": sum(0 if b.grad_buf is None else b.grad_buf.numel() * b.grad_buf.element_size()
+                             for b in self.buckets),
+        }
+
+
+class ZeROStage2Optimizer(ZeROOptimizer):
+    def __init__(self, params, **kw):
+        kw["stage"] = 2
+        super().__init__(params, **kw)
+
+
+class ZeROStage3Optimizer(ZeROOptimizer):
+    def __init__(self, params, **kw):
+        kw["stage"] = 3
+        super().__init__(params, **kw)
+
+
+def build_optimizer(params, zero_stage: int, **kw) -> ZeROOptimizer:
+    """Stage -> class, as the reference's engine does (src/engines/train_engine.py:378-422)."""
+    if zero_stage >= 3:
+        return ZeROStage3Optimizer(params, **kw)
+    if zero_stage == 2:
+        return ZeROStage2Optimizer(params, **kw)
+    return ZeROOptimizer(params, stage=max(0, zero_stage), **kw)

@@ -1,0 +1,133 @@
+"""1F1B pipeline schedule.
+
+Semantics of the reference scheduler (src/distributed/pipeline_scheduler.py:68-320): ``pp-1-rank``
+warm-up forwards, steady one-forward-one-backward with combined send/recv pairs (which cannot
+deadlock), cool-down backwards; each micro-batch's loss is scaled by ``1/num_micro``; a one-time
+``int64[3]`` shape handshake travels stage to stage; received activations become autograd leaves.
+Gradients accumulate into the optimizer's bucket buffers across micro-batches.
+"""
+from __future__ import annotations
+
+from collections import deque
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..dist import comm
+
+
+class PipelineScheduler:
+    def __init__(self, model, pp_context, num_micro_batches: int):
+        assert num_micro_batches >= pp_context.pp_size, "need num_micro_batches >= pp_size to fill the pipe"
+        self.model, self.pp, self.num_micro = model, pp_context, num_micro_batches
+        self._act_shape: Optional[Tuple[int, ...]] = None
+        self.timeline = None  # optional ScheduleVisualizer
+
+    # ---- shape handshake ---------------------------------------------------------------------------
+    def _handshake(self, mb_tokens: int, device, dtype):
+        if self._act_shape is not None and self._act_shape[0] * (self.model.tp_size if self.model.sequence_parallel else 1) == mb_tokens:
+            return
+        H = self.model.cfg.hidden_size
+        if self.pp.is_first_stage:
+            rows = mb_tokens // self.model.tp_size if self.model.sequence_parallel else mb_tokens
+            shape = torch.tensor([rows, H, 0], dtype=torch.int64, device=device)
+        else:
+            shape = comm.recv_forward((3,), torch.int64, device, self.pp.prev_rank, self.pp.group)
+        if not self.pp.is_last_stage:
+            comm.send_forward(shape, self.pp.next_rank, self.pp.group)
+        self._act_shape = (int(shape[0]), int(shape[1]))
+
+    # ---- one micro-batch ---------------------------------------------------------------------------
+    def _forward(self, ids_mb, labels_mb, recv):
+        B, S = labels_mb.shape
+        if self.pp.is_first_stage:
+            inp = None
+            out = self.model.forward_hidden(ids_mb, B, S)
+        else:
+            inp = recv.requires_grad_(True)
+            out = self.model.forward_hidden(inp, B, S)
+        if self.pp.is_last_stage:
+            loss = self.model.loss(None, labels_mb, loss_scale=1.0 / self.num_micro, hidden=out)
+            return inp, loss, loss.detach() / self.num_micro
+        return inp, out, None
+
+    @staticmethod
+    def _backward(inp, out, grad):
+        if grad is None:
+            out.backward()         # last stage: `out` is the loss (gradients already carry 1/num_micro)
+        else:
+            out.backward(grad)
+        return None if inp is None else inp.grad
+
+    def _track(self, name, cat):
+        import contextlib
+        if self.timeline is None:
+            return contextlib.nullcontext()
+        return self.timeline.track(name, cat, lane=f"stage{self.pp.pp_rank}")
+
+    # ---- schedule ------------------------------------------------------------------------------------
+    def run_1f1b_schedule(self, input_ids: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
+        """Run all micro-batches of ``[B,S]`` (split along B).  Returns the mean loss on the last stage
+        and zeros elsewhere; use :meth:`broadcast_loss` to share it."""
+        pp = self.pp
+        dev = labels.device
+        dtype = next(self.model.parameters()).dtype
+        ids_mbs = input_ids.chunk(self.num_micro, dim=0)
+        lab_mbs = labels.chunk(self.num_micro, dim=0)
+        self._handshake(lab_mbs[0].numel(), dev, dtype)
+        shape = self._act_shape
+        prev, nxt, grp = pp.prev_rank, pp.next_rank, pp.group
+        warm = min(pp.pp_size - 1 - pp.pp_rank, self.num_micro)
+        steady = self.num_micro - warm
+        fifo = deque()
+        total = torch.zeros((), device=dev, dtype=torch.float32)
+        f = 0
+
+        def fwd(recv):
+            nonlocal f, total
+            with self._track(f"F{f}", "forward"):
+                inp, out, l = self._forward(ids_mbs[f], lab_mbs[f], recv)
+            if l is not None:
+                total = total + l
+            fifo.append((inp, out))
+            f += 1
+            return out
+
+        recv = None
+        for _ in range(warm):
+            recv = comm.recv_forward(shape, dtype, dev, prev, grp)
+            out = fwd(recv)
+            comm.send_forward(out.detach(), nxt, grp)
+        if steady > 0:
+            recv = comm.recv_forward(shape, dtype, dev, prev, grp)
+        for i in range(steady):
+            out = fwd(recv)
+            if pp.is_last_stage:
+                grad = None
+            else:
+                grad = comm.send_forward_recv_backward(out.detach(), shape, dtype, dev, nxt, grp)
+            inp, o = fifo.popleft()
+            with self._track(f"B{i}", "backward"):
+                gin = self._backward(inp, o, grad)
+            last_steady = i == steady - 1
+            if last_steady:
+                comm.send_backward(gin, prev, grp) if gin is not None else None
+            else:
+                recv = comm.send_backward_recv_forward(gin, shape, dtype, dev, prev, grp) if gin is not None \
+                    else comm.recv_forward(shape, dtype, dev, prev, grp)
+        for _ in range(warm):
+            grad = comm.recv_backward(shape, dtype, dev, nxt, grp)
+            inp, o = fifo.popleft()
+            with self._track("Bc", "backward"):
+                gin = self._backward(inp, o, grad)
+            if gin is not None:
+                comm.send_backward(gin, prev, grp)
+        return total
+
+    def broadcast_loss(self, loss: torch.Tensor) -> torch.Tensor:
+        """Share the last stage's loss with every stage of this pipeline."""
+        if self.pp.pp_size > 1 and self.pp.group is not None:
+            loss = loss.clone()
+            dist.broadcast(loss, src=self.pp.ctx.pp_ranks[-1], group=self.pp.group)
+        return loss

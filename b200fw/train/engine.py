@@ -1,0 +1,559 @@
+"""TrainEngine: SFT and GRPO steps over the parallel Qwen3 model.
+
+Public surface of the reference engine (src/engines/train_engine.py:53-1768): ``TrainConfig`` /
+``TrainMetrics`` with the same fields, ``initialize``, ``sft_step``, ``grpo_step``, ``generate``,
+``eval_sft_loss``, ``export_weights``, ``export_lora_delta``, ``save_checkpoint``, ``load_checkpoint``,
+``generate_memory_report``.  Differences by design: losses never materialise ``[B,S,V]`` logits,
+gradient norm / clip / NaN guard / AdamW run on the device inside the optimizer, batches reach the
+GPU from pinned host buffers, and full-SFT checkpoints include the base weights.
+"""
+from __future__ import annotations
+
+import copy
+import json
+import os
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from ..dist.context import ParallelContext
+from ..model import (ModelConfig, PRESETS, ParallelTransformerModel, apply_lora, get_lora_state_dict,
+                     load_from_hf_checkpoint, merge_lora_weights, read_hf_config, save_hf_checkpoint)
+from ..model.lora import LinearWithLoRA, load_lora_state_dict
+from ..obs.logging import get_logger
+from ..obs.memory import MemoryBreakdown, MemoryProfiler, MemoryReport
+from ..obs.metrics import MetricsCollector
+from ..ops import grpo_token_loss
+from ..optim import LRSchedule, ZeROOptimizer, build_optimizer
+from ..pipeline import PipelineParallelContext, PipelineScheduler
+from .icepop import IcePopConfig, IcePopFilter
+
+logger = get_logger("train.engine")
+
+
+@dataclass
+class TrainConfig:
+    model_path: str = ""
+    tp_size: int = 1
+    dp_size: int = 1
+    pp_size: int = 1
+    num_micro_batches: int = 1
+    max_seq_len: int = 2048
+    use_flash_attn: bool = False          # accepted for config compatibility; attention is always the
+    attention_backend: str = "sdpa"       # native flash kernel on GPU
+    use_gradient_checkpoint: bool = False
+    lora_rank: int = 16
+    lora_alpha: float = 32.0
+    lora_target_modules: List[str] = field(default_factory=lambda: [
+        "q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"])
+    learning_rate: float = 1e-5
+    weight_decay: float = 0.01
+    max_grad_norm: float = 1.0
+    use_amp: bool = True
+    amp_dtype: str = "bf16"
+    gradient_accumulation_steps: int = 4
+    grpo_num_samples: int = 4
+    grpo_beta: float = 0.1
+    grpo_clip_eps: float = 0.2
+    pad_token_id: int = 0
+    zero_stage: int = 1
+    enable_comm_overlap: bool = False
+    min_prompt_len: int = 16
+    lr_scheduler_type: str = "cosine"
+    warmup_steps: int = 100
+    min_lr_ratio: float = 0.1
+    total_training_steps: int = 0
+    icepop_enabled: bool = False
+    icepop_divergence_threshold: float = 0.5
+    icepop_max_mask_ratio: float = 0.5
+    # ---- additions -------------------------------------------------------------------------------
+    model_preset: Optional[str] = None          # random-init architecture from model.PRESETS
+    model_config: Optional[ModelConfig] = None  # or an explicit architecture
+    sequence_parallel: bool = False
+    seed: int = 0
+    adam_beta1: float = 0.9
+    adam_beta2: float = 0.999
+    adam_eps: float = 1e-8
+    bucket_mb: float = 64.0
+    build_ref_model: Optional[bool] = None      # default: grpo_beta > 0, as in the reference
+    backend: Optional[str] = None               # nccl / gloo (default by device)
+
+
+@dataclass
+class TrainMetrics:
+    loss: float
+    policy_loss: float
+    kl_divergence: float
+    grad_norm: float
+    learning_rate: float
+    step: int
+    extras: Dict[str, float] = field(default_factory=dict)
+
+
+class TrainEngine:
+    def __init__(self, config: TrainConfig):
+        self.config = config
+        self.parallel_ctx: Optional[ParallelContext] = None
+        self.model: Optional[ParallelTransformerModel] = None
+        self.ref_model: Optional[ParallelTransformerModel] = None
+        self.optimizer: Optional[ZeROOptimizer] = None
+        self.lr_scheduler: Optional[LRSchedule] = None
+        self.model_config: Optional[ModelConfig] = None
+        self.step_count = 0
+        self._accumulation_count = 0
+        self.metrics_collector: Optional[MetricsCollector] = None
+        self._old_log_probs_buffer: Optional[torch.Tensor] = None
+        self.pp_context: Optional[PipelineParallelContext] = None
+        self.pipeline_scheduler: Optional[PipelineScheduler] = None
+        self.icepop: Optional[IcePopFilter] = None
+        self._prev_lora_snapshot: Optional[Dict[str, torch.Tensor]] = None
+        self.memory_profiler = MemoryProfiler()
+        self.device = torch.device("cpu")
+        self.dtype = torch.float32
+        self._pinned: Dict[str, torch.Tensor] = {}
+        self.last_icepop_info: Dict[str, float] = {}
+        self.last_grpo_info: Dict[str, float] = {}
+
+    # =============================================================================================
+    def initialize(self, parallel_context: Optional[ParallelContext] = None):
+        cfg = self.config
+        if parallel_context is not None:
+            ctx = parallel_context
+        elif int(os.environ.get("WORLD_SIZE", "1")) > 1 or cfg.tp_size * cfg.dp_size * cfg.pp_size > 1:
+            ctx = ParallelContext.init_distributed(cfg.tp_size, cfg.dp_size, cfg.pp_size, cfg.backend)
+        else:
+            ctx = ParallelContext.init_single_process()
+        self.parallel_ctx = ctx
+        self.device = ctx.device
+        if self.device.type == "cuda":
+            from .. import _native
+            _native.set_device(self.device.index or 0)
+        if cfg.pp_size > 1:
+            if cfg.zero_stage > 1:
+                raise ValueError("pipeline parallelism supports zero_stage <= 1")
+            if cfg.num_micro_batches < cfg.pp_size:
+                raise ValueError("num_micro_batches must be >= pp_size")
+        amp = cfg.amp_dtype if cfg.use_amp else "fp32"
+        self.dtype = {"bf16": torch.bfloat16, "fp16": torch.bfloat16, "fp32": torch.float32}[amp]
+        if self.device.type == "cpu":
+            self.dtype = torch.float32 if amp == "fp32" or not cfg.use_amp else self.dtype
+        # ---- architecture ----------------------------------------------------------------------
+        if cfg.model_config is not None:
+            mc = cfg.model_config
+        elif cfg.model_preset is not None:
+            mc = copy.deepcopy(PRESETS[cfg.model_preset])
+        else:
+            mc = read_hf_config(cfg.model_path)
+        self.model_config = mc
+        layer_range, first, last = None, True, True
+        if cfg.pp_size > 1:
+            self.pp_context = PipelineParallelContext(mc.num_layers, ctx)
+            layer_range = (self.pp_context.layer_start, self.pp_context.layer_end)
+            first, last = self.pp_context.is_first_stage, self.pp_context.is_last_stage
+            if mc.tie_word_embeddings:
+                mc = copy.deepcopy(mc)
+                mc.tie_word_embeddings = False  # the two ends live on different stages
+                self.model_config = mc
+        self.model = ParallelTransformerModel(
+            mc, ctx, layer_range, first, last, sequence_parallel=cfg.sequence_parallel,
+            gradient_checkpointing=cfg.use_gradient_checkpoint, dtype=self.dtype, device=self.device)
+        self.model.init_weights(cfg.seed)
+        if cfg.model_path and os.path.isdir(cfg.model_path):
+            loaded, missing = load_from_hf_checkpoint(self.model, cfg.model_path)
+            logger.info("loaded %d tensors from %s (%d missing)", loaded, cfg.model_path, missing)
+        # ---- frozen reference policy ---------------------------------------------------------------
+        want_ref = cfg.build_ref_model if cfg.build_ref_model is not None else cfg.grpo_beta > 0
+        if want_ref and cfg.lora_rank <= 0 and cfg.pp_size == 1:
+            self.ref_model = copy.deepcopy(self.model)
+            for p in self.ref_model.parameters():
+                p.requires_grad_(False)
+            self.ref_model.eval()
+        self._ref_is_base = bool(want_ref and cfg.lora_rank > 0)  # LoRA: reference = adapters off
+        # ---- LoRA -------------------------------------------------------------------------------
+        if cfg.lora_rank > 0:
+            names = apply_lora(self.model, cfg.lora_rank, cfg.lora_alpha, cfg.lora_target_modules)
+            logger.info("LoRA r=%d on %d projections", cfg.lora_rank, len(names))
+        # ---- optimizer + schedule -------------------------------------------------------------------
+        trainable = [p for p in self.model.parameters() if p.requires_grad]
+        self.optimizer = build_optimizer(
+            trainable, cfg.zero_stage if (cfg.dp_size > 1 or cfg.tp_size > 1 or cfg.zero_stage == 0) else 1,
+            lr=cfg.learning_rate, betas=(cfg.adam_beta1, cfg.adam_beta2), eps=cfg.adam_eps,
+            weight_decay=cfg.weight_decay, ctx=ctx, bucket_mb=cfg.bucket_mb, max_grad_norm=cfg.max_grad_norm,
+            overlap=True)
+        self.lr_scheduler = LRSchedule(cfg.learning_rate, cfg.lr_scheduler_type, cfg.warmup_steps,
+                                       cfg.total_training_steps, cfg.min_lr_ratio)
+        self.optimizer.param_groups[0]["lr"] = self.lr_scheduler.lr_at(0)
+        if cfg.pp_size > 1:
+            self.pipeline_scheduler = PipelineScheduler(self.model, self.pp_context, cfg.num_micro_batches)
+        if cfg.icepop_enabled:
+            self.icepop = IcePopFilter(IcePopConfig(True, cfg.icepop_divergence_threshold, cfg.icepop_max_mask_ratio))
+        self.memory_profiler.snapshot("after_init")
+        return self
+
+    # ---- batching ------------------------------------------------------------------------------
+    def _truncate_prompt_response(self, prompt: List[int], response: List[int]) -> Tuple[List[int], List[int]]:
+        """Fit ``prompt + response`` into ``max_seq_len``: keep the response if possible (it is the
+        training target) and trim the prompt's tail; if the response alone is too long, cut it and keep
+        ``min_prompt_len`` prompt tokens."""
+        L = self.config.max_seq_len
+        keep = min(self.config.min_prompt_len, len(prompt))
+        if len(prompt) + len(response) <= L:
+            return prompt, response
+        if len(response) >= L - keep:
+            return prompt[:keep], response[:L - keep]
+        return prompt[:L - len(response)], response
+
+    def _to_device(self, name: str, rows: List[List[int]], fill: int) -> torch.Tensor:
+        """Pad ``rows`` to a rectangle in a reusable pinned host buffer and copy it to the device."""
+        n, m = len(rows), max(len(r) for r in rows)
+        if self.device.type != "cuda":
+            t = torch.full((n, m), fill, dtype=torch.long)
+            for i, r in enumerate(rows):
+                t[i, :len(r)] = torch.tensor(r, dtype=torch.long)
+            return t
+        buf = self._pinned.get(name)
+        if buf is None or buf.numel() < n * m:
+            buf = torch.empty(max(n * m, 1), dtype=torch.long, pin_memory=True)
+            self._pinned[name] = buf
+        view = buf[:n * m].view(n, m)
+        view.fill_(fill)
+        for i, r in enumerate(rows):
+            view[i, :len(r)] = torch.tensor(r, dtype=torch.long)
+        return view.to(self.device, non_blocking=True)
+
+    def _build_batch(self, prompts: List[List[int]], responses: List[List[int]]):
+        ids, labels = [], []
+        for p, r in zip(prompts, responses):
+            p, r = self._truncate_prompt_response(list(p), list(r))
+            ids.append(p + r)
+            labels.append([-100] * len(p) + r)
+        return self._to_device("ids", ids, self.config.pad_token_id), self._to_device("labels", labels, -100)
+
+    # ---- optimizer step --------------------------------------------------------------------------
+    def _maybe_step(self, skip: bool = False):
+        """After ``gradient_accumulation_steps`` backwards: clip (global norm), AdamW, schedule."""
+        cfg = self.config
+        if self._accumulation_count < cfg.gradient_accumulation_steps or skip:
+            return None
+        opt = self.optimizer
+        opt.param_groups[0]["lr"] = self.lr_scheduler.get_last_lr()[0]
+        gn = opt.clip_grad_norm(cfg.max_grad_norm)
+        opt.step()           # the kernel itself skips the update when the norm is not finite
+        opt.zero_grad()
+        self._accumulation_count = 0
+        return gn
+
+    def _finish_step(self, gn: Optional[torch.Tensor]) -> float:
+        """Host side of the NaN/Inf guard: a non-finite norm (reported as -1) means the device skipped
+        the update, so neither the step counter nor the schedule advance."""
+        if gn is None:
+            return 0.0
+        g = float(gn)
+        if g < 0:
+            logger.warning("non-finite gradient norm: optimizer step skipped")
+            self.optimizer.step_count -= 1
+            return g
+        self.lr_scheduler.step()
+        self.step_count += 1
+        if self.metrics_collector is not None:
+            self.metrics_collector.record("grad_norm", g)
+        return g
+
+    # =============================================================================================
+    def sft_step(self, prompts_tokens: List[List[int]], response_tokens: List[List[int]]) -> TrainMetrics:
+        """Teacher-forced SFT step; prompt positions are not supervised."""
+        ids, labels = self._build_batch(prompts_tokens, response_tokens)
+        return self.sft_step_tensors(ids, labels)
+
+    def sft_step_tensors(self, input_ids: torch.Tensor, labels: torch.Tensor, sync: bool = True):
+        """SFT step on ready ``[B,S]`` tensors (host tensors are copied to the device asynchronously).
+        ``sync=False`` returns ``(loss_tensor, grad_norm_tensor_or_None)`` without a host sync."""
+        if input_ids.device != self.device:
+            input_ids = input_ids.to(self.device, non_blocking=True)
+            labels = labels.to(self.device, non_blocking=True)
+        if self.pp_context is not None and self.pp_context.pp_size > 1:
+            loss, gn = self._pp_batch_step(input_ids, labels)
+        else:
+            loss, gn = self._single_batch_step(input_ids, labels)
+        if not sync:
+            if gn is not None:   # optimistic bookkeeping; call resolve_step(gn) to apply the NaN guard
+                self.lr_scheduler.step()
+                self.step_count += 1
+            return loss, gn
+        lr = self.lr_scheduler.get_last_lr()[0]
+        g = self._finish_step(gn)
+        lv = float(loss)
+        if self.metrics_collector is not None:
+            self.metrics_collector.record("learning_rate", lr)
+            self.metrics_collector.record("loss", lv)
+        return TrainMetrics(lv, lv, 0.0, g, lr, self.step_count)
+
+    def _single_batch_step(self, input_ids, labels):
+        cfg, opt = self.config, self.optimizer
+        opt.pre_forward()
+        opt.begin_backward(sync=self._accumulation_count + 1 >= cfg.gradient_accumulation_steps)
+        loss = self.model.loss(input_ids, labels, loss_scale=1.0 / cfg.gradient_accumulation_steps)
+        loss.backward()
+        opt.post_backward()
+        self._accumulation_count += 1
+        return loss.detach(), self._maybe_step()
+
+    def _pp_batch_step(self, input_ids, labels):
+        cfg, opt = self.config, self.optimizer
+        opt.begin_backward(sync=True)
+        loss = self.pipeline_scheduler.run_1f1b_schedule(input_ids, labels)
+        opt.post_backward()
+        self._accumulation_count = cfg.gradient_accumulation_steps
+        gn = self._maybe_step()
+        return self.pipeline_scheduler.broadcast_loss(loss), gn
+
+    @torch.no_grad()
+    def eval_sft_loss(self, prompts_tokens: List[List[int]], response_tokens: List[List[int]]) -> float:
+        ids, labels = self._build_batch(prompts_tokens, response_tokens)
+        with self.optimizer.eval_mode():
+            was = self.model.training
+            self.model.eval()
+            try:
+                return float(self.model.loss(ids, labels))
+            finally:
+                self.model.train(was)
+
+    # =============================================================================================
+    @staticmethod
+    def group_advantages(rewards: List[float]) -> List[float]:
+        """Group-normalised advantages; all-equal rewards carry no signal and give zeros."""
+        t = torch.tensor(rewards, dtype=torch.float32)
+        std = t.std(unbiased=False)
+        if std < 1e-8:
+            return [0.0] * len(rewards)
+        return ((t - t.mean()) / (std + 1e-8)).tolist()
+
+    def _lora_enabled(self, on: bool):
+        for m in self.model.modules():
+            if isinstance(m, LinearWithLoRA):
+                m.merged = not on   # `merged=True` bypasses the adapters in forward
+
+    @torch.no_grad()
+    def _ref_token_logprobs(self, ids, labels) -> Optional[torch.Tensor]:
+        if self.ref_model is not None:
+            return self.ref_model.token_logprobs(ids, labels=labels)
+        if self._ref_is_base:
+            self._lora_enabled(False)
+            try:
+                return self.model.token_logprobs(ids, labels=labels)
+            finally:
+                self._lora_enabled(True)
+        return None
+
+    def grpo_step(self, prompts_tokens: List[List[int]], responses_group: List[List[List[int]]],
+                  rewards_group: List[List[float]], infer_log_probs: Optional[torch.Tensor] = None,
+                  skip_optimizer_step: bool = False, reset_behavior_baseline: bool = True,
+                  precomputed_advantages: Optional[List[List[float]]] = None) -> TrainMetrics:
+        """One GRPO step over ``batch x K`` sequences: group-relative advantages, clipped token-level
+        surrogate against the behaviour log-probs, KL to the frozen reference, optional IcePop."""
+        assert self.pp_context is None or self.pp_context.pp_size == 1, "GRPO needs pp_size == 1"
+        cfg, opt = self.config, self.optimizer
+        if reset_behavior_baseline:
+            self._old_log_probs_buffer = None
+        P, R, A = [], [], []
+        for i, prompt in enumerate(prompts_tokens):
+            adv = precomputed_advantages[i] if precomputed_advantages is not None \
+                else self.group_advantages(rewards_group[i])
+            for k, resp in enumerate(responses_group[i]):
+                P.append(prompt)
+                R.append(resp)
+                A.append(adv[k])
+        ids, labels = self._build_batch(P, R)
+        adv_t = torch.tensor(A, dtype=torch.float32).to(self.device, non_blocking=True)
+        mask = (labels[:, 1:] != -100).float()
+        opt.pre_forward()
+        opt.begin_backward(sync=self._accumulation_count + 1 >= cfg.gradient_accumulation_steps)
+        lp = self.model.token_logprobs(ids, labels=labels)
+        self.last_icepop_info = {}
+        if self.icepop is not None and self.icepop.config.enabled:
+            seq_lp = (lp.detach() * mask).sum(-1) / (mask.sum(-1) + 1e-8)
+            if infer_log_probs is None:
+                infer_log_probs = self._inference_log_probs(ids, labels, mask)
+            adv_t, self.last_icepop_info = self.icepop.filter_divergent_responses(seq_lp, infer_log_probs, adv_t)
+        ref_lp = self._ref_token_logprobs(ids, labels) if cfg.grpo_beta > 0 else None
+        old_lp = lp.detach() if self._old_log_probs_buffer is None or \
+            self._old_log_probs_buffer.shape != lp.shape else self._old_log_probs_buffer
+        loss, info = grpo_token_loss(lp, old_lp, ref_lp, mask, adv_t, cfg.grpo_clip_eps, cfg.grpo_beta,
+                                     loss_scale=1.0 / cfg.gradient_accumulation_steps)
+        self._old_log_probs_buffer = lp.detach().clone()
+        loss.backward()
+        opt.post_backward()
+        self._accumulation_count += 1
+        gn = self._maybe_step(skip=skip_optimizer_step)
+        lr = self.lr_scheduler.get_last_lr()[0]
+        g = self._finish_step(gn)
+        self.last_grpo_info = {k: float(v) for k, v in info.items()}
+        if self.metrics_collector is not None:
+            self.metrics_collector.record("learning_rate", lr)
+        return TrainMetrics(float(loss.detach()), self.last_grpo_info["policy_loss"], self.last_grpo_info["kl_divergence"],
+                            g, lr, self.step_count, extras={**self.last_grpo_info, **self.last_icepop_info})
+
+    @torch.no_grad()
+    def _inference_log_probs(self, ids, labels, mask) -> torch.Tensor:
+        """Sequence log-probs from an inference-mode forward (the IcePop fallback when the rollout
+        engine did not report its own)."""
+        was = self.model.training
+        self.model.eval()
+        try:
+            lp = self.model.token_logprobs(ids, labels=labels)
+        finally:
+            self.model.train(was)
+        return (lp * mask).sum(-1) / (mask.sum(-1) + 1e-8)
+
+    @torch.no_grad()
+    def compute_sequence_log_probs(self, prompts_tokens, response_tokens) -> torch.Tensor:
+        ids, labels = self._build_batch(prompts_tokens, response_tokens)
+        mask = (labels[:, 1:] != -100).float()
+        with self.optimizer.eval_mode():
+            return self._inference_log_probs(ids, labels, mask)
+
+    # =============================================================================================
+    @staticmethod
+    def sample_next_token(logits: torch.Tensor, temperature: float, top_p: float,
+                          generator: Optional[torch.Generator] = None) -> torch.Tensor:
+        """Temperature + nucleus sampling on ``[B,V]`` logits (greedy when ``temperature <= 0``)."""
+        if temperature <= 0:
+            return logits.argmax(-1)
+        probs = torch.softmax(logits.float() / temperature, dim=-1)
+        if top_p < 1.0:
+            sp, si = probs.sort(dim=-1, descending=True)
+            keep = (sp.cumsum(-1) - sp) < top_p      # keep the token that crosses the threshold
+            sp = sp * keep
+            probs = torch.zeros_like(probs).scatter_(-1, si, sp)
+            probs = probs / probs.sum(-1, keepdim=True)
+        return torch.multinomial(probs, 1, generator=generator).squeeze(-1)
+
+    @torch.no_grad()
+    def generate(self, prompt_tokens: List[int], max_new_tokens: int = 128, temperature: float = 0.7,
+                 top_p: float = 0.95, eos_token_id: Optional[int] = None) -> List[int]:
+        """Reference-compatible local generation: full re-forward per token, no KV cache
+        (src/engines/train_engine.py:907-1008).  Kept for previews and tests; rollouts use
+        :class:`b200fw.infer.InferenceEngine`.  Under TP, rank 0 of the TP group samples and broadcasts."""
+        import torch.distributed as dist
+        ctx = self.parallel_ctx
+        seq = list(prompt_tokens)
+        out: List[int] = []
+        with self.optimizer.eval_mode():
+            was = self.model.training
+            self.model.eval()
+            try:
+                for _ in range(max_new_tokens):
+                    ids = torch.tensor([seq[-self.config.max_seq_len:]], dtype=torch.long, device=self.device)
+                    logits = self.model(ids)[:, -1, :]
+                    tok = self.sample_next_token(logits, temperature, top_p)
+                    if ctx.tp_size > 1:
+                        dist.broadcast(tok, src=ctx.tp_ranks[0], group=ctx.tp_group)
+                    t = int(tok)
+                    out.append(t)
+                    seq.append(t)
+                    if eos_token_id is not None and t == eos_token_id:
+                        break
+            finally:
+                self.model.train(was)
+        return out
+
+    # =============================================================================================
+    @torch.no_grad()
+    def export_weights(self, device: Optional[str] = None) -> Dict[str, torch.Tensor]:
+        """HF-named full weights with LoRA merged (TP shards gathered); stage-3 gathers first."""
+        from ..model.hf_io import hf_named_tensors
+        with self.optimizer.eval_mode():
+            has_lora = any(isinstance(m, LinearWithLoRA) for m in self.model.modules())
+            if has_lora:
+                merge_lora_weights(self.model)
+            try:
+                out = {k: (v.to(device) if device else v).clone() for k, v in hf_named_tensors(self.model)}
+            finally:
+                if has_lora:
+                    merge_lora_weights(self.model, unmerge=True)
+        return out
+
+    @torch.no_grad()
+    def export_lora_delta(self) -> Dict[str, torch.Tensor]:
+        """Current LoRA tensors minus the previous export's snapshot (the first call returns the full
+        state).  Feeds the SwiftSync delta path."""
+        cur = {k: v.clone() for k, v in get_lora_state_dict(self.model).items()}
+        if self._prev_lora_snapshot is None:
+            delta = {k: v.clone() for k, v in cur.items()}
+        else:
+            delta = {k: v - self._prev_lora_snapshot[k] for k, v in cur.items()}
+        self._prev_lora_snapshot = cur
+        return delta
+
+    # ---- checkpoints --------------------------------------------------------------------------------
+    def save_checkpoint(self, path: str, save_base_weights: Optional[bool] = None) -> None:
+        """``lora_weights.pt`` + ``optimizer_state_rank{r}.pt`` (every rank saves its own shard; rank 0
+        also writes the reference-compatible ``optimizer_state.pt``) + ``trainer_state.json`` (step
+        counters, LR schedule, RNG) + HF-format base weights for full fine-tuning."""
+        ctx = self.parallel_ctx
+        os.makedirs(path, exist_ok=True)
+        rank = ctx.global_rank
+        lora = get_lora_state_dict(self.model)
+        if lora and ctx.dp_rank == 0:
+            name = "lora_weights.pt" if ctx.tp_size == 1 else f"lora_weights_tp{ctx.tp_rank}.pt"
+            torch.save({k: v.cpu() for k, v in lora.items()}, os.path.join(path, name))
+        sd = self.optimizer.state_dict()
+        torch.save(sd, os.path.join(path, f"optimizer_state_rank{rank}.pt"))
+        if rank == 0:
+            torch.save(sd, os.path.join(path, "optimizer_state.pt"))
+            with open(os.path.join(path, "trainer_state.json"), "w") as f:
+                json.dump({"step_count": self.step_count, "accumulation_count": self._accumulation_count,
+                           "lr_scheduler": self.lr_scheduler.state_dict(), "world_size": ctx.world_size,
+                           "torch_rng_seed": int(torch.initial_seed())}, f)
+        full = save_base_weights if save_base_weights is not None else (self.config.lora_rank <= 0)
+        if full:
+            with self.optimizer.eval_mode():
+                shard = "model.safetensors" if ctx.pp_size == 1 else f"model-stage{ctx.pp_rank}.safetensors"
+                save_hf_checkpoint(self.model, path, write=(ctx.dp_rank == 0 and ctx.tp_rank == 0), shard_name=shard)
+        ctx.barrier()
+
+    def load_checkpoint(self, path: str) -> bool:
+        """Tolerant restore (returns False instead of raising when files are absent or do not match)."""
+        ctx = self.parallel_ctx
+        try:
+            ok = True
+            if any(f.endswith(".safetensors") for f in os.listdir(path)) and self.config.lora_rank <= 0:
+                with self.optimizer.eval_mode():
+                    load_from_hf_checkpoint(self.model, path)
+                    self.optimizer.refresh_masters_from_params()
+            lname = "lora_weights.pt" if ctx.tp_size == 1 else f"lora_weights_tp{ctx.tp_rank}.pt"
+            lpath = os.path.join(path, lname)
+            if os.path.exists(lpath):
+                load_lora_state_dict(self.model, torch.load(lpath, map_location="cpu", weights_only=True))
+                self.optimizer.refresh_masters_from_params()
+            opath = os.path.join(path, f"optimizer_state_rank{ctx.global_rank}.pt")
+            if not os.path.exists(opath):
+                opath = os.path.join(path, "optimizer_state.pt")
+            if os.path.exists(opath):
+                ok = self.optimizer.load_state_dict(torch.load(opath, map_location="cpu", weights_only=False)) and ok
+            else:
+                ok = False
+            spath = os.path.join(path, "trainer_state.json")
+            if os.path.exists(spath):
+                with open(spath) as f:
+                    st = json.load(f)
+                self.step_count = int(st.get("step_count", 0))
+                self.lr_scheduler.load_state_dict(st.get("lr_scheduler", {}))
+            return ok
+        except Exception as e:  # noqa: BLE001 - restore is best-effort by contract
+            logger.warning("load_checkpoint(%s) failed: %s", path, e)
+            return False
+
+    # ---- reports ------------------------------------------------------------------------------------
+    def generate_memory_report(self, batch_tokens: int = 0) -> MemoryReport:
+        cfg, mc = self.config, self.model_config
+        total = mc.num_params()
+        trainable = sum(p.numel() for p in self.model.parameters() if p.requires_grad) * cfg.tp_size * cfg.pp_size \
+            if cfg.lora_rank > 0 else total
+        bd = MemoryBreakdown.estimate(total, trainable, 2 if self.dtype == torch.bfloat16 else 4, cfg.tp_size,
+                                      cfg.pp_size, cfg.dp_size, cfg.zero_stage, batch_tokens, mc.hidden_size,
+                                      mc.num_layers, mc.vocab_size, mc.intermediate_size,
+                                      cfg.use_gradient_checkpoint)
+        self.memory_profiler.snapshot("report")
+        return MemoryReport.from_profiler(self.memory_profiler, bd, self.optimizer.memory_bytes())

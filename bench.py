@@ -1,0 +1,232 @@
+"""Headline benchmark: full-SFT training throughput (tokens/s) and MFU.
+
+Default workload (one named by the benchmark configs): Qwen3-0.6B-architecture full SFT in bf16, data
+parallel over N GPUs with ZeRO-1, sequence 1024, micro-batch 8 per GPU, gradient accumulation 2,
+seeded uniform synthetic tokens with the loss on the second half of every sequence, random-init
+weights.  ``--model qwen3-32b --tp 8`` runs the TP8 large-model configuration on 8 GPUs.
+
+One "step" is one optimizer step (all its micro-batches, gradient reduction, clip, AdamW).  Prints one
+JSON line on rank 0.  ``--impl reference`` runs the unmodified reference implementation installed under
+``baseline/_ref`` on the same workload through its own TrainEngine.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=8)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200fw", choices=["b200fw", "reference"])
+    ap.add_argument("--model", default="qwen3-0.6b")
+    ap.add_argument("--seq-len", type=int, default=1024)
+    ap.add_argument("--micro-batch", type=int, default=8)
+    ap.add_argument("--grad-accum", type=int, default=2)
+    ap.add_argument("--zero-stage", type=int, default=1)
+    ap.add_argument("--tp", type=int, default=1)
+    ap.add_argument("--pp", type=int, default=1)
+    ap.add_argument("--lora-rank", type=int, default=0)
+    ap.add_argument("--grad-ckpt", action="store_true")
+    ap.add_argument("--sequence-parallel", action="store_true")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.samples, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()   # the exact child started above
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            parts = [p.strip() for p in s.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx = float(parts[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def synthetic_batches(vocab, micro_batch, seq, count, seed, pinned):
+    g = torch.Generator().manual_seed(seed)
+    out = []
+    for _ in range(count):
+        ids = torch.randint(0, vocab, (micro_batch, seq), generator=g, dtype=torch.long)
+        labels = ids.clone()
+        labels[:, : seq // 2] = -100
+        if pinned:
+            ids, labels = ids.pin_memory(), labels.pin_memory()
+        out.append((ids, labels))
+    return out
+
+
+def max_over_ranks(x: float, world: int, device) -> float:
+    if world == 1:
+        return x
+    import torch.distributed as dist
+    t = torch.tensor([x], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t)
+
+
+def run_ours(a):
+    from b200fw import _native as nv
+    from b200fw.model import PRESETS
+    from b200fw.obs.profilers import ComputeProfiler, measured_peaks
+    from b200fw.train import TrainConfig, TrainEngine
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == a.gpus, f"--gpus {a.gpus} but WORLD_SIZE={world}"
+    torch.cuda.set_device(local)
+    dp = world // (a.tp * a.pp)
+    mc = PRESETS[a.model]
+    cfg = TrainConfig(model_preset=a.model, tp_size=a.tp, dp_size=dp, pp_size=a.pp,
+                      num_micro_batches=max(a.pp, a.grad_accum) if a.pp > 1 else 1, max_seq_len=a.seq_len,
+                      use_gradient_checkpoint=a.grad_ckpt, lora_rank=a.lora_rank, learning_rate=1e-5,
+                      gradient_accumulation_steps=a.grad_accum if a.pp == 1 else 1, grpo_beta=0.0,
+                      zero_stage=a.zero_stage, warmup_steps=2, total_training_steps=a.steps + a.warmup + 8,
+                      sequence_parallel=a.sequence_parallel, amp_dtype="bf16")
+    eng = TrainEngine(cfg).initialize()
+    dev = eng.device
+    accum = a.grad_accum
+    n_micro = (a.warmup + a.steps) * accum
+    host = synthetic_batches(mc.vocab_size, a.micro_batch, a.seq_len, accum * 2, 1234 + eng.parallel_ctx.dp_rank, True)
+    on_dev = [(i.to(dev), l.to(dev)) for i, l in host]
+
+    def micro_dev(k):
+        ids, labels = on_dev[k % len(on_dev)]
+        if a.pp > 1:
+            return eng.sft_step_tensors(ids, labels, sync=False)
+        return eng.sft_step_tensors(ids, labels, sync=False)
+
+    def barrier():
+        if world > 1:
+            import torch.distributed as dist
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    micro_per_step = accum if a.pp == 1 else 1
+    # ---- device-timed: inputs resident on the device, no host sync inside the region ----------------
+    for k in range(a.warmup * micro_per_step):
+        micro_dev(k)
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    launches0 = nv.launch_count
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for k in range(a.steps * micro_per_step):
+        micro_dev(k)
+    e.record()
+    barrier()
+    ms = max_over_ranks(s.elapsed_time(e), world, dev)
+    launches = nv.launch_count - launches0
+    status = nv.read_status()
+    # ---- end to end: pinned host -> device copy of every micro-batch, loss read back every step -------
+    barrier()
+    s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s2.record()
+    last_loss = 0.0
+    for k in range(a.steps * micro_per_step):
+        ids, labels = host[k % len(host)]
+        m = eng.sft_step_tensors(ids, labels, sync=True)   # H2D inside; float(loss) is the D2H read
+        last_loss = m.loss
+    e2.record()
+    barrier()
+    ms_e2e = max_over_ranks(s2.elapsed_time(e2), world, dev)
+    clocks = sampler.stop() if rank == 0 else None
+
+    tokens_per_step = a.micro_batch * a.seq_len * micro_per_step * dp * (a.grad_accum if a.pp > 1 and False else 1)
+    tps = tokens_per_step * a.steps / (ms * 1e-3)
+    tps_e2e = tokens_per_step * a.steps / (ms_e2e * 1e-3)
+    flops = ComputeProfiler.exact_flops(mc, a.micro_batch * micro_per_step * dp, a.seq_len, full=a.lora_rank <= 0,
+                                        grad_checkpoint=a.grad_ckpt)
+    peaks = measured_peaks()
+    step_s = ms * 1e-3 / a.steps
+    if rank == 0:
+        par = "+".join(p for p in [f"dp{dp}" if dp > 1 or (a.tp == 1 and a.pp == 1) else "", f"tp{a.tp}" if a.tp > 1 else "",
+                                   f"pp{a.pp}" if a.pp > 1 else ""] if p)
+        line = {
+            "metric": "sft_tokens_per_s", "value": tps, "unit": "tokens/s", "n_gpus": world, "steps": a.steps,
+            "warmup": a.warmup, "ms_per_step": ms / a.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded uniform tokens, random-init weights)",
+            "impl": "b200fw",
+            "config": {"model": f"{a.model}-arch full SFT" if a.lora_rank <= 0 else f"{a.model}-arch LoRA r{a.lora_rank}",
+                       "global_batch": a.micro_batch * micro_per_step * dp, "micro_batch_per_gpu": a.micro_batch,
+                       "grad_accum": a.grad_accum, "seq_len": a.seq_len, "parallelism": par,
+                       "zero_stage": a.zero_stage, "l2": "inputs larger than L2 (weights+activations >> 126 MB)",
+                       "step": "one optimizer step = grad_accum micro-batches + reduce + clip + AdamW"},
+            "mfu_exact_of_measured_sustained": flops / (step_s * world * peaks["bf16_tflops_sustained"] * 1e12),
+            "model_tflops_per_gpu": flops / step_s / world / 1e12,
+            "e2e": {"value": tps_e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / a.steps,
+                    "h2d_bytes_per_step": 2 * a.micro_batch * a.seq_len * 8 * micro_per_step,
+                    "d2h_bytes_per_step": 8, "final_loss": last_loss},
+            "gpu_launches": launches, "device_status": status, "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    eng.parallel_ctx.destroy()
+
+
+def main():
+    a = parse()
+    if a.impl == "reference":
+        from baseline.run_reference import run_reference
+        run_reference(a)
+        return
+    if not torch.cuda.is_available():
+        print(json.dumps({"impl": "b200fw", "unavailable": "no CUDA device"}))
+        return
+    run_ours(a)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,324 @@
+// Causal flash-attention forward for sm_100a (head_dim 128, GQA), tcgen05 MMAs with S and O in TMEM.
+//
+// One CTA handles one 128-row query tile of one (batch, q-head).  Warp 0 streams K/V tiles with TMA
+// (two stages each), warp 1 issues the MMAs, warps 2..5 (128 threads, one query row each) run the
+// online softmax: they read S from TMEM, write P (bf16) to shared memory in the 128-byte-swizzled
+// K-major layout the PV MMA consumes, and rescale the O accumulator in TMEM only when the running
+// row maximum grew by more than 2^8 (the final normalisation uses the same reference maximum for
+// P and for the row sum, so a stale maximum is exact as long as nothing overflows).
+// S is double-buffered so that Q*K^T of tile j+1 overlaps the softmax of tile j.
+//
+// Layouts: q [T, Hq*128], k [T, Hkv*128], v [T, ld_v] (a column slice of the fused projection output),
+// out [T, Hq*128], lse [Hq, T] (natural log, scaled scores).  T = B*S; sequence b owns rows b*S..b*S+S-1.
+#include "common.cuh"
+#include "host.h"
+
+namespace b2 {
+
+constexpr int AT_THREADS = 192;
+constexpr int AT_TILE_BYTES = 128 * 128 * 2;  // 32 KiB: two [128 x 64] swizzled halves
+constexpr int AT_HALF_BYTES = 128 * 64 * 2;
+
+struct AttnFwdSmem {
+  // offsets into the 1024-byte aligned dynamic shared memory
+  static constexpr int Q = 0;
+  static constexpr int K = Q + AT_TILE_BYTES;           // 2 stages
+  static constexpr int V = K + 2 * AT_TILE_BYTES;       // 2 stages
+  static constexpr int P = V + 2 * AT_TILE_BYTES;
+  static constexpr int BARS = P + AT_TILE_BYTES;        // 196608
+  static constexpr int TOTAL = BARS + 256 + 1024;
+};
+
+__global__ void __launch_bounds__(AT_THREADS, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, __nv_bfloat16* __restrict__ out,
+                float* __restrict__ lse_out, int S, int Hq, int Hkv, float scale, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + AttnFwdSmem::BARS);
+  uint64_t* q_full = bars + 0;
+  uint64_t* k_full = bars + 1;    // [2]
+  uint64_t* v_full = bars + 3;    // [2]
+  uint64_t* k_empty = bars + 5;   // [2]
+  uint64_t* v_empty = bars + 7;   // [2]
+  uint64_t* s_full = bars + 9;    // [2]
+  uint64_t* s_empty = bars + 11;  // [2]
+  uint64_t* p_full = bars + 13;
+  uint64_t* pv_done = bars + 14;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_q_tiles = (S + 127) / 128;
+  const int qt = num_q_tiles - 1 - blockIdx.x;  // heaviest tiles first
+  const int head = blockIdx.y, batch = blockIdx.z;
+  const int kvh = head / (Hq / Hkv);
+  const int n_kv = qt + 1;  // causal: kv tiles 0..qt
+  const int row0 = batch * S + qt * 128;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_empty[i], 128);
+    }
+    mbar_init(p_full, 128);
+    mbar_init(pv_done, 1);
+    mbar_fence_init();
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+  const uint32_t tmem_S = tmem_base;        // 2 x 128 columns
+  const uint32_t tmem_O = tmem_base + 256;  // 128 columns
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(q_full, AT_TILE_BYTES);
+      tma_load_2d(smem + AttnFwdSmem::Q, &tmQ, q_full, head * 128, row0);
+      tma_load_2d(smem + AttnFwdSmem::Q + AT_HALF_BYTES, &tmQ, q_full, head * 128 + 64, row0);
+      for (int j = 0; j < n_kv; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        const int krow = batch * S + j * 128;
+        if (!mbar_wait(&k_empty[st], ph ^ 1, status, ERR_ATTN_WAIT)) break;
+        uint8_t* sK = smem + AttnFwdSmem::K + st * AT_TILE_BYTES;
+        mbar_expect_tx(&k_full[st], AT_TILE_BYTES);
+        tma_load_2d(sK, &tmK, &k_full[st], kvh * 128, krow);
+        tma_load_2d(sK + AT_HALF_BYTES, &tmK, &k_full[st], kvh * 128 + 64, krow);
+        if (!mbar_wait(&v_empty[st], ph ^ 1, status, ERR_ATTN_WAIT)) break;
+        uint8_t* sV = smem + AttnFwdSmem::V + st * AT_TILE_BYTES;
+        mbar_expect_tx(&v_full[st], AT_TILE_BYTES);
+        tma_load_2d(sV, &tmV, &v_full[st], kvh * 128, krow);
+        tma_load_2d(sV + AT_HALF_BYTES, &tmV, &v_full[st], kvh * 128 + 64, krow);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_f16(1, 128, 128, 0, 0);
+      constexpr uint32_t idesc_pv = make_idesc_f16(1, 128, 128, 0, 1);
+      const uint32_t q_base = smem_u32(smem + AttnFwdSmem::Q);
+      const uint32_t p_base = smem_u32(smem + AttnFwdSmem::P);
+      auto issue_s = [&](int j) {
+        const uint32_t k_base = smem_u32(smem + AttnFwdSmem::K + (j & 1) * AT_TILE_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t o = (ks >> 2) * AT_HALF_BYTES + (ks & 3) * 32;
+          umma_f16_ss(tmem_S + (j & 1) * 128, make_smem_desc_sw128(q_base + o, 16, 1024),
+                      make_smem_desc_sw128(k_base + o, 16, 1024), idesc_s, ks != 0);
+        }
+        umma_commit(&k_empty[j & 1]);
+        umma_commit(&s_full[j & 1]);
+      };
+      bool ok = mbar_wait(q_full, 0, status, ERR_ATTN_WAIT) &&
+                mbar_wait(&k_full[0], 0, status, ERR_ATTN_WAIT);
+      if (ok) {
+        tc_fence_after();
+        issue_s(0);
+      }
+      for (int j = 0; j < n_kv && ok; ++j) {
+        if (j + 1 < n_kv) {
+          const int st = (j + 1) & 1;
+          const uint32_t ph = ((j + 1) >> 1) & 1;
+          if (!mbar_wait(&k_full[st], ph, status, ERR_ATTN_WAIT) ||
+              !mbar_wait(&s_empty[st], ph ^ 1, status, ERR_ATTN_WAIT)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          issue_s(j + 1);
+        }
+        if (!mbar_wait(p_full, j & 1, status, ERR_ATTN_WAIT) ||
+            !mbar_wait(&v_full[j & 1], (j >> 1) & 1, status, ERR_ATTN_WAIT)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t v_base = smem_u32(smem + AttnFwdSmem::V + (j & 1) * AT_TILE_BYTES);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint32_t o = (ks >> 2) * AT_HALF_BYTES + (ks & 3) * 32;
+          umma_f16_ss(tmem_O, make_smem_desc_sw128(p_base + o, 16, 1024),
+                      make_smem_desc_sw128(v_base + ks * 2048, AT_HALF_BYTES, 1024), idesc_pv,
+                      (j | ks) != 0);
+        }
+        umma_commit(&v_empty[j & 1]);
+        umma_commit(pv_done);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;        // query row inside the tile
+    const int q_pos = qt * 128 + r;           // position inside the sequence
+    const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
+    const float sl2 = scale * 1.4426950408889634f;
+    float m_used = -INFINITY, l = 0.f;
+    uint8_t* sP = smem + AttnFwdSmem::P;
+    bool ok = true;
+    for (int j = 0; j < n_kv; ++j) {
+      if (!mbar_wait(&s_full[j & 1], (j >> 1) & 1, status, ERR_ATTN_WAIT)) { ok = false; break; }
+      tc_fence_after();
+      float s[128];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t t[32];
+        tmem_ld_32x32b_x32(tmem_S + lane_off + (j & 1) * 128 + c * 32, t);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(t[i]);
+      }
+      tc_fence_before();
+      mbar_arrive(&s_empty[j & 1]);
+      const bool need_mask = (j == qt) || ((j + 1) * 128 > S);
+      if (need_mask) {
+        const int col0 = j * 128;
+#pragma unroll
+        for (int i = 0; i < 128; ++i)
+          if (col0 + i > q_pos || col0 + i >= S) s[i] = -INFINITY;
+      }
+      float mx = s[0];
+#pragma unroll
+      for (int i = 1; i < 128; ++i) mx = fmaxf(mx, s[i]);
+      const float m_new = fmaxf(m_used, mx);
+      if (j > 0) {
+        // previous PV must be complete before P is overwritten or O is rescaled
+        if (!mbar_wait(pv_done, (j - 1) & 1, status, ERR_ATTN_WAIT)) { ok = false; break; }
+        tc_fence_after();
+        const bool need = (m_new - m_used) * sl2 > 8.f;
+        if (__any_sync(0xffffffffu, need)) {
+          const float alpha = need ? exp2f((m_used - m_new) * sl2) : 1.f;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            uint32_t t[16];
+            tmem_ld_32x32b_x16(tmem_O + lane_off + c * 16, t);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) t[i] = __float_as_uint(__uint_as_float(t[i]) * alpha);
+            tmem_st_32x32b_x16(tmem_O + lane_off + c * 16, t);
+          }
+          tmem_st_wait();
+          if (need) {
+            l *= alpha;
+            m_used = m_new;
+          }
+        }
+      } else {
+        m_used = m_new;
+      }
+      const float mb = m_used * sl2;
+      float rs = 0.f;
+#pragma unroll
+      for (int c8 = 0; c8 < 16; ++c8) {
+        float p[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          p[i] = exp2f(s[c8 * 8 + i] * sl2 - mb);
+          rs += p[i];
+        }
+        uint4 o;
+        o.x = pack_bf16x2(p[0], p[1]);
+        o.y = pack_bf16x2(p[2], p[3]);
+        o.z = pack_bf16x2(p[4], p[5]);
+        o.w = pack_bf16x2(p[6], p[7]);
+        const int sub = c8 >> 3, cc = c8 & 7;
+        *reinterpret_cast<uint4*>(sP + sub * AT_HALF_BYTES + r * 128 + ((cc ^ (r & 7)) << 4)) = o;
+      }
+      l += rs;
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(p_full);
+    }
+    if (ok && mbar_wait(pv_done, (n_kv - 1) & 1, status, ERR_ATTN_WAIT)) {
+      tc_fence_after();
+      const float inv = 1.f / l;
+      const bool in_range = q_pos < S;
+      __nv_bfloat16* orow = out + (static_cast<size_t>(row0 + r) * Hq + head) * 128;
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t t[32];
+        tmem_ld_32x32b_x32(tmem_O + lane_off + c * 32, t);
+        tmem_ld_wait();
+        if (in_range) {
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(t[v * 8 + 0]) * inv, __uint_as_float(t[v * 8 + 1]) * inv);
+            o.y = pack_bf16x2(__uint_as_float(t[v * 8 + 2]) * inv, __uint_as_float(t[v * 8 + 3]) * inv);
+            o.z = pack_bf16x2(__uint_as_float(t[v * 8 + 4]) * inv, __uint_as_float(t[v * 8 + 5]) * inv);
+            o.w = pack_bf16x2(__uint_as_float(t[v * 8 + 6]) * inv, __uint_as_float(t[v * 8 + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) = o;
+          }
+        }
+      }
+      if (in_range && lse_out)
+        lse_out[static_cast<size_t>(head) * (gridDim.z * S) + row0 + r] = m_used * scale + __logf(l);
+    }
+  }
+
+  if (*reinterpret_cast<volatile int*>(status) != 0) {
+    unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace b2
+
+using namespace b2;
+
+// q [B*S, Hq*128], k [B*S, Hkv*128] contiguous; v rows have stride ld_v elements.
+B2_EXPORT int b2_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int S,
+                          int Hq, int Hkv, int head_dim, int ld_v, float scale, void* stream_) {
+  b2::ensure_thread_context();
+  if (head_dim != 128 || Hq % Hkv != 0 || (ld_v % 8) != 0) {
+    set_error("attn_fwd: head_dim must be 128, Hq %% Hkv == 0, ld_v %% 8 == 0");
+    return 10;
+  }
+  if (B <= 0 || S <= 0) return 0;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!configured[dev]) {
+    if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             AttnFwdSmem::TOTAL) != cudaSuccess) {
+      set_error("attn_fwd: cannot set shared memory size");
+      return 1;
+    }
+    configured[dev] = true;
+  }
+  const uint64_t T = static_cast<uint64_t>(B) * S;
+  const CUtensorMap* tq = tensor_map_2d_bf16(q, T, static_cast<uint64_t>(Hq) * 128, static_cast<uint64_t>(Hq) * 128, 128, 64);
+  const CUtensorMap* tk = tensor_map_2d_bf16(k, T, static_cast<uint64_t>(Hkv) * 128, static_cast<uint64_t>(Hkv) * 128, 128, 64);
+  const CUtensorMap* tv = tensor_map_2d_bf16(v, T, static_cast<uint64_t>(Hkv) * 128, ld_v, 128, 64);
+  if (!tq || !tk || !tv) return 2;
+  int* status = status_ptr();
+  if (!status) return 3;
+  dim3 grid((S + 127) / 128, Hq, B);
+  attn_fwd_kernel<<<grid, AT_THREADS, AttnFwdSmem::TOTAL, stream>>>(
+      *tq, *tk, *tv, static_cast<__nv_bfloat16*>(out), lse, S, Hq, Hkv, scale, status);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("attn_fwd launch failed: %s", cudaGetErrorString(e));
+    return 4;
+  }
+  return 0;
+}

@@ -336,6 +336,7 @@ static int launch_gemm(const void* A, const void* B, void* C, const void* R, int
 B2_EXPORT int b2_gemm_bf16(const void* A, const void* B, void* C, const void* R, int M, int N, int K,
                            int lda, int ldb, int ldc, int a_mn, int b_mn, int flags, int bn,
                            int max_ctas, void* stream_) {
+  b2::ensure_thread_context();
   using namespace b2;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   if (M <= 0 || N <= 0 || K <= 0) return 0;

@@ -15,6 +15,19 @@ __device__ int g_status_word[4];
 static char g_error_text[512] = {0};
 static std::mutex g_mu;
 
+static int g_device = -1;
+
+void ensure_thread_context() {
+  thread_local int bound = -2;
+  if (bound == g_device) return;
+  if (g_device >= 0) {
+    cudaSetDevice(g_device);
+  } else {
+    cudaFree(nullptr);  // binds the runtime's default device and creates / attaches its context
+  }
+  bound = g_device;
+}
+
 void set_error(const char* fmt, ...) {
   va_list ap;
   va_start(ap, fmt);
@@ -23,6 +36,7 @@ void set_error(const char* fmt, ...) {
 }
 
 int* status_ptr() {
+  ensure_thread_context();
   static int* ptrs[64] = {nullptr};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -78,6 +92,7 @@ static std::unordered_map<MapKey, CUtensorMap*, MapKeyHash> g_maps;
 const CUtensorMap* tensor_map_nd_bf16(const void* base, int rank, const uint64_t* dims,
                                       const uint64_t* strides_bytes, const uint32_t* box,
                                       int swizzle) {
+  ensure_thread_context();
   MapKey key;
   memset(&key, 0, sizeof(key));
   int dev = 0;
@@ -145,6 +160,9 @@ B2_EXPORT int b2_status_read_and_clear() {
   if (v != 0) cudaMemset(p, 0, sizeof(int));
   return v;
 }
+
+// One process drives one GPU: the Python side reports torch's current device once at start-up.
+B2_EXPORT void b2_set_device(int device) { b2::g_device = device; }
 
 B2_EXPORT const char* b2_last_error() { return b2::g_error_text; }
 

@@ -8,6 +8,11 @@
 
 namespace b2 {
 
+// Makes the process's device (b2_set_device) current on the calling thread.  Launchers call this
+// first: autograd runs backward passes on worker threads that this library's runtime has never
+// seen, and driver entry points such as the tensor-map encoder need a current context.
+void ensure_thread_context();
+
 // Device address of this device's status word (one int; 0 = no error).
 int* status_ptr();
 

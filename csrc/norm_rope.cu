@@ -1,0 +1,502 @@
+// RMSNorm forward/backward, fused per-head QK-RMSNorm + rotary embedding forward/backward, SwiGLU
+// forward/backward, embedding gather / scatter-add.  All HBM-bound: 16-byte vector accesses, fp32
+// math, bf16 storage.
+#include "common.cuh"
+#include "host.h"
+
+namespace b2 {
+
+struct alignas(16) bf16x8 {
+  __nv_bfloat162 v[4];
+};
+
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&f)[8]) {
+  bf16x8 r = *reinterpret_cast<const bf16x8*>(p);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = __bfloat1622float2(r.v[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const float (&f)[8]) {
+  bf16x8 r;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) r.v[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  *reinterpret_cast<bf16x8*>(p) = r;
+}
+
+template <int THREADS>
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = (lane < THREADS / 32) ? scratch[lane] : 0.f;
+  t = warp_sum(t);
+  return t;
+}
+
+// ---------------------------------------------------------------------------------------------
+// RMSNorm forward: one CTA per row, H % 8 == 0.  y = x * rstd * w ; rstd saved for backward.
+// ---------------------------------------------------------------------------------------------
+constexpr int RMS_THREADS = 256;
+constexpr int RMS_MAX_VEC = 4;  // up to 256*8*4 = 8192 columns kept in registers
+
+__global__ void __launch_bounds__(RMS_THREADS) rmsnorm_fwd_kernel(
+    const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+    __nv_bfloat16* __restrict__ y, float* __restrict__ rstd_out, int H, float eps) {
+  __shared__ float scratch[32];
+  const size_t row = blockIdx.x;
+  const __nv_bfloat16* xr = x + row * H;
+  __nv_bfloat16* yr = y + row * H;
+  float v[RMS_MAX_VEC][8];
+  float ss = 0.f;
+  const int nvec = H / 8;
+#pragma unroll
+  for (int i = 0; i < RMS_MAX_VEC; ++i) {
+    const int c = threadIdx.x + i * RMS_THREADS;
+    if (c < nvec) {
+      load8(xr + c * 8, v[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += v[i][j] * v[i][j];
+    }
+  }
+  // columns beyond the register window (H > 8192): accumulate only
+  for (int c = threadIdx.x + RMS_MAX_VEC * RMS_THREADS; c < nvec; c += RMS_THREADS) {
+    float t[8];
+    load8(xr + c * 8, t);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += t[j] * t[j];
+  }
+  ss = block_sum<RMS_THREADS>(ss, scratch);
+  const float rstd = rsqrtf(ss / H + eps);
+  if (threadIdx.x == 0 && rstd_out) rstd_out[row] = rstd;
+#pragma unroll
+  for (int i = 0; i < RMS_MAX_VEC; ++i) {
+    const int c = threadIdx.x + i * RMS_THREADS;
+    if (c < nvec) {
+      float wv[8], o[8];
+      load8(w + c * 8, wv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = v[i][j] * rstd * wv[j];
+      store8(yr + c * 8, o);
+    }
+  }
+  for (int c = threadIdx.x + RMS_MAX_VEC * RMS_THREADS; c < nvec; c += RMS_THREADS) {
+    float t[8], wv[8], o[8];
+    load8(xr + c * 8, t);
+    load8(w + c * 8, wv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = t[j] * rstd * wv[j];
+    store8(yr + c * 8, o);
+  }
+}
+
+// RMSNorm backward.  Persistent CTAs stride over rows; each keeps a partial dw in registers and
+// writes it to dw_partial[cta, H] (fp32); a second kernel reduces the partials.
+//   dx = rstd * (dy*w - xhat * mean(dy*w*xhat)),  dw = sum_rows dy * xhat,  xhat = x*rstd
+__global__ void __launch_bounds__(RMS_THREADS) rmsnorm_bwd_kernel(
+    const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd_in,
+    __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_partial, int M, int H, int add_to_dx) {
+  __shared__ float scratch[32];
+  const int nvec = H / 8;
+  float dwacc[RMS_MAX_VEC][8];
+  float wv[RMS_MAX_VEC][8];
+#pragma unroll
+  for (int i = 0; i < RMS_MAX_VEC; ++i) {
+    const int c = threadIdx.x + i * RMS_THREADS;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
+    if (c < nvec) load8(w + c * 8, wv[i]);
+  }
+  for (int row = blockIdx.x; row < M; row += gridDim.x) {
+    const __nv_bfloat16* xr = x + static_cast<size_t>(row) * H;
+    const __nv_bfloat16* dyr = dy + static_cast<size_t>(row) * H;
+    __nv_bfloat16* dxr = dx + static_cast<size_t>(row) * H;
+    const float rstd = rstd_in[row];
+    float xh[RMS_MAX_VEC][8], g[RMS_MAX_VEC][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < RMS_MAX_VEC; ++i) {
+      const int c = threadIdx.x + i * RMS_THREADS;
+      if (c < nvec) {
+        float xv[8], dv[8];
+        load8(xr + c * 8, xv);
+        load8(dyr + c * 8, dv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[i][j] = xv[j] * rstd;
+          dwacc[i][j] += dv[j] * xh[i][j];
+          g[i][j] = dv[j] * wv[i][j];
+          dot += g[i][j] * xh[i][j];
+        }
+      }
+    }
+    dot = block_sum<RMS_THREADS>(dot, scratch);
+    const float mean = dot / H;
+#pragma unroll
+    for (int i = 0; i < RMS_MAX_VEC; ++i) {
+      const int c = threadIdx.x + i * RMS_THREADS;
+      if (c < nvec) {
+        float o[8];
+        if (add_to_dx) load8(dxr + c * 8, o);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float d = rstd * (g[i][j] - xh[i][j] * mean);
+          o[j] = add_to_dx ? o[j] + d : d;
+        }
+        store8(dxr + c * 8, o);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < RMS_MAX_VEC; ++i) {
+    const int c = threadIdx.x + i * RMS_THREADS;
+    if (c < nvec) {
+      float* p = dw_partial + static_cast<size_t>(blockIdx.x) * H + c * 8;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) p[j] = dwacc[i][j];
+    }
+  }
+}
+
+// dw[h] (+)= sum_p partial[p, h]   (bf16 or fp32 destination)
+__global__ void reduce_partials_kernel(const float* __restrict__ partial, void* __restrict__ dw,
+                                       int P, int H, int accumulate, int out_fp32) {
+  const int h = blockIdx.x * blockDim.x + threadIdx.x;
+  if (h >= H) return;
+  float s = 0.f;
+  for (int p = 0; p < P; ++p) s += partial[static_cast<size_t>(p) * H + h];
+  if (out_fp32) {
+    float* o = reinterpret_cast<float*>(dw);
+    o[h] = accumulate ? o[h] + s : s;
+  } else {
+    __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(dw);
+    o[h] = __float2bfloat16(accumulate ? __bfloat162float(o[h]) + s : s);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Fused per-head RMSNorm (q_norm / k_norm) + half-rotation RoPE.  head_dim = 128, one warp per
+// (token, head); lane l holds elements 4l..4l+3, the rotation partner (i +- 64) lives in lane l^16.
+// qkv: [M, (Hq + 2*Hkv) * 128] (the fused projection output); q_out [M,Hq,128], k_out [M,Hkv,128].
+// cos/sin: fp32 tables [max_pos, 64].  rstd_out: [M, Hq+Hkv] fp32 for backward.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) qknorm_rope_fwd_kernel(
+    const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ qw,
+    const __nv_bfloat16* __restrict__ kw, const int* __restrict__ pos,
+    const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+    __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_out,
+    float* __restrict__ rstd_out, int M, int Hq, int Hkv, int ld_qkv, float eps) {
+  const int heads = Hq + Hkv;
+  const long long gw = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (gw >= static_cast<long long>(M) * heads) return;
+  const int tok = static_cast<int>(gw / heads);
+  const int head = static_cast<int>(gw % heads);
+  const bool is_q = head < Hq;
+  const __nv_bfloat16* src = qkv + static_cast<size_t>(tok) * ld_qkv + head * 128 + lane * 4;
+  const __nv_bfloat16* w = (is_q ? qw : kw) + lane * 4;
+  uint2 raw = *reinterpret_cast<const uint2*>(src);
+  float2 a = unpack_bf16x2(raw.x), b = unpack_bf16x2(raw.y);
+  float v[4] = {a.x, a.y, b.x, b.y};
+  float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+  ss = warp_sum(ss);
+  const float rstd = rsqrtf(ss * (1.f / 128.f) + eps);
+  uint2 wraw = *reinterpret_cast<const uint2*>(w);
+  float2 wa = unpack_bf16x2(wraw.x), wb = unpack_bf16x2(wraw.y);
+  const float wv[4] = {wa.x, wa.y, wb.x, wb.y};
+  const int p = pos[tok];
+  const int fi = (lane & 15) * 4;  // frequency index of this lane's first element
+  const float4 c4 = *reinterpret_cast<const float4*>(cos_t + static_cast<size_t>(p) * 64 + fi);
+  const float4 s4 = *reinterpret_cast<const float4*>(sin_t + static_cast<size_t>(p) * 64 + fi);
+  const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
+  float o[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float n = v[j] * rstd * wv[j];
+    const float partner = __shfl_xor_sync(0xffffffffu, n, 16);
+    // first half: y = x1*c - x2*s ; second half: y = x2*c + x1*s
+    o[j] = (lane < 16) ? n * cs[j] - partner * sn[j] : n * cs[j] + partner * sn[j];
+  }
+  __nv_bfloat16* dst = is_q ? q_out + (static_cast<size_t>(tok) * Hq + head) * 128 + lane * 4
+                            : k_out + (static_cast<size_t>(tok) * Hkv + (head - Hq)) * 128 + lane * 4;
+  uint2 ov;
+  ov.x = pack_bf16x2(o[0], o[1]);
+  ov.y = pack_bf16x2(o[2], o[3]);
+  *reinterpret_cast<uint2*>(dst) = ov;
+  if (lane == 0 && rstd_out) rstd_out[static_cast<size_t>(tok) * heads + head] = rstd;
+}
+
+// Backward: dq/dk (post-RoPE grads) -> grads w.r.t. the projection output (written into dqkv's q and
+// k column ranges) and partial weight grads accumulated with fp32 atomics into dqw/dkw [128].
+__global__ void __launch_bounds__(256) qknorm_rope_bwd_kernel(
+    const __nv_bfloat16* __restrict__ dq, const __nv_bfloat16* __restrict__ dk,
+    const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ qw,
+    const __nv_bfloat16* __restrict__ kw, const int* __restrict__ pos,
+    const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+    const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dqkv, float* __restrict__ dqw,
+    float* __restrict__ dkw, int M, int Hq, int Hkv, int ld_qkv) {
+  __shared__ float sdw[2][128];
+  for (int i = threadIdx.x; i < 256; i += blockDim.x) (&sdw[0][0])[i] = 0.f;
+  __syncthreads();
+  const int heads = Hq + Hkv;
+  const int lane = threadIdx.x & 31;
+  const long long total = static_cast<long long>(M) * heads;
+  const long long warps_per_grid = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  for (long long gw = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; gw < total;
+       gw += warps_per_grid) {
+    const int tok = static_cast<int>(gw / heads);
+    const int head = static_cast<int>(gw % heads);
+    const bool is_q = head < Hq;
+    const __nv_bfloat16* gsrc =
+        is_q ? dq + (static_cast<size_t>(tok) * Hq + head) * 128 + lane * 4
+             : dk + (static_cast<size_t>(tok) * Hkv + (head - Hq)) * 128 + lane * 4;
+    uint2 graw = *reinterpret_cast<const uint2*>(gsrc);
+    float2 ga = unpack_bf16x2(graw.x), gb = unpack_bf16x2(graw.y);
+    const float g[4] = {ga.x, ga.y, gb.x, gb.y};
+    const int p = pos[tok];
+    const int fi = (lane & 15) * 4;
+    const float4 c4 = *reinterpret_cast<const float4*>(cos_t + static_cast<size_t>(p) * 64 + fi);
+    const float4 s4 = *reinterpret_cast<const float4*>(sin_t + static_cast<size_t>(p) * 64 + fi);
+    const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
+    const size_t off = static_cast<size_t>(tok) * ld_qkv + head * 128 + lane * 4;
+    uint2 xraw = *reinterpret_cast<const uint2*>(qkv + off);
+    float2 xa = unpack_bf16x2(xraw.x), xb = unpack_bf16x2(xraw.y);
+    const float xv[4] = {xa.x, xa.y, xb.x, xb.y};
+    uint2 wraw = *reinterpret_cast<const uint2*>((is_q ? qw : kw) + lane * 4);
+    float2 wa = unpack_bf16x2(wraw.x), wb = unpack_bf16x2(wraw.y);
+    const float wv[4] = {wa.x, wa.y, wb.x, wb.y};
+    const float rstd = rstd_in[static_cast<size_t>(tok) * heads + head];
+    float dn[4], xh[4], gw_[4];
+    float dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float partner = __shfl_xor_sync(0xffffffffu, g[j], 16);
+      // inverse rotation: dx1 = dy1*c + dy2*s ; dx2 = dy2*c - dy1*s
+      dn[j] = (lane < 16) ? g[j] * cs[j] + partner * sn[j] : g[j] * cs[j] - partner * sn[j];
+      xh[j] = xv[j] * rstd;
+      gw_[j] = dn[j] * wv[j];
+      dot += gw_[j] * xh[j];
+      atomicAdd(&sdw[is_q ? 0 : 1][lane * 4 + j], dn[j] * xh[j]);
+    }
+    dot = warp_sum(dot) * (1.f / 128.f);
+    uint2 ov;
+    ov.x = pack_bf16x2(rstd * (gw_[0] - xh[0] * dot), rstd * (gw_[1] - xh[1] * dot));
+    ov.y = pack_bf16x2(rstd * (gw_[2] - xh[2] * dot), rstd * (gw_[3] - xh[3] * dot));
+    *reinterpret_cast<uint2*>(dqkv + off) = ov;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < 128; i += blockDim.x) {
+    atomicAdd(dqw + i, sdw[0][i]);
+    atomicAdd(dkw + i, sdw[1][i]);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// SwiGLU on the fused gate|up projection output gu [M, 2I]: out = silu(gate) * up.
+// ---------------------------------------------------------------------------------------------
+__global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out,
+                                  long long M, int I) {
+  const int nvec = I / 8;
+  const long long total = M * nvec;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long row = i / nvec;
+    const int c = static_cast<int>(i % nvec) * 8;
+    float g[8], u[8], o[8];
+    load8(gu + row * 2 * I + c, g);
+    load8(gu + row * 2 * I + I + c, u);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = g[j] / (1.f + __expf(-g[j])) * u[j];
+    store8(out + row * I + c, o);
+  }
+}
+__global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ dout,
+                                  const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ dgu,
+                                  long long M, int I) {
+  const int nvec = I / 8;
+  const long long total = M * nvec;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long row = i / nvec;
+    const int c = static_cast<int>(i % nvec) * 8;
+    float g[8], u[8], d[8], dg[8], du[8];
+    load8(gu + row * 2 * I + c, g);
+    load8(gu + row * 2 * I + I + c, u);
+    load8(dout + row * I + c, d);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float s = 1.f / (1.f + __expf(-g[j]));
+      const float silu = g[j] * s;
+      du[j] = d[j] * silu;
+      dg[j] = d[j] * u[j] * (s + silu * (1.f - s));
+    }
+    store8(dgu + row * 2 * I + c, dg);
+    store8(dgu + row * 2 * I + I + c, du);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Embedding gather and scatter-add (bf16 weights / grads; ids int64).
+// ---------------------------------------------------------------------------------------------
+__global__ void embedding_fwd_kernel(const long long* __restrict__ ids,
+                                     const __nv_bfloat16* __restrict__ table,
+                                     __nv_bfloat16* __restrict__ out, int M, int H) {
+  const int nvec = H / 8;
+  for (int row = blockIdx.x; row < M; row += gridDim.x) {
+    const long long id = ids[row];
+    const bf16x8* src = reinterpret_cast<const bf16x8*>(table + id * H);
+    bf16x8* dst = reinterpret_cast<bf16x8*>(out + static_cast<size_t>(row) * H);
+    for (int c = threadIdx.x; c < nvec; c += blockDim.x) dst[c] = src[c];
+  }
+}
+__global__ void embedding_bwd_kernel(const long long* __restrict__ ids,
+                                     const __nv_bfloat16* __restrict__ dout,
+                                     __nv_bfloat16* __restrict__ dtable, int M, int H) {
+  const int npair = H / 2;
+  for (int row = blockIdx.x; row < M; row += gridDim.x) {
+    const long long id = ids[row];
+    const __nv_bfloat162* src = reinterpret_cast<const __nv_bfloat162*>(dout + static_cast<size_t>(row) * H);
+    __nv_bfloat162* dst = reinterpret_cast<__nv_bfloat162*>(dtable + id * H);
+    for (int c = threadIdx.x; c < npair; c += blockDim.x) atomicAdd(dst + c, src[c]);
+  }
+}
+
+}  // namespace b2
+
+using namespace b2;
+
+#define B2_LAUNCH_CHECK(name)                                        \
+  do {                                                               \
+    cudaError_t e_ = cudaGetLastError();                             \
+    if (e_ != cudaSuccess) {                                         \
+      set_error(name " launch failed: %s", cudaGetErrorString(e_)); \
+      return 4;                                                      \
+    }                                                                \
+  } while (0)
+
+B2_EXPORT int b2_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, int M, int H, float eps,
+                             void* stream) {
+  b2::ensure_thread_context();
+  if (H % 8) { set_error("rmsnorm: H %% 8 != 0"); return 10; }
+  if (M <= 0) return 0;
+  rmsnorm_fwd_kernel<<<M, RMS_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
+      static_cast<__nv_bfloat16*>(y), rstd, H, eps);
+  B2_LAUNCH_CHECK("rmsnorm_fwd");
+  return 0;
+}
+
+// dw_partial: fp32 scratch of at least b2_rmsnorm_bwd_ctas() * H floats.
+B2_EXPORT int b2_rmsnorm_bwd_ctas() {
+  b2::ensure_thread_context(); return num_sms() * 2; }
+
+B2_EXPORT int b2_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx,
+                             void* dw, float* dw_partial, int M, int H, int add_to_dx,
+                             int accumulate_dw, int dw_fp32, void* stream_) {
+  b2::ensure_thread_context();
+  if (H % 8 || H > RMS_THREADS * 8 * RMS_MAX_VEC) { set_error("rmsnorm_bwd: H must be a multiple of 8 and <= 8192"); return 10; }
+  if (M <= 0) return 0;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  int ctas = num_sms() * 2;
+  if (ctas > M) ctas = M;
+  rmsnorm_bwd_kernel<<<ctas, RMS_THREADS, 0, stream>>>(
+      static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
+      static_cast<const __nv_bfloat16*>(w), rstd, static_cast<__nv_bfloat16*>(dx), dw_partial, M, H,
+      add_to_dx);
+  B2_LAUNCH_CHECK("rmsnorm_bwd");
+  reduce_partials_kernel<<<(H + 255) / 256, 256, 0, stream>>>(dw_partial, dw, ctas, H, accumulate_dw, dw_fp32);
+  B2_LAUNCH_CHECK("rmsnorm_bwd_reduce");
+  return 0;
+}
+
+B2_EXPORT int b2_qknorm_rope_fwd(const void* qkv, const void* qw, const void* kw, const int* pos,
+                                 const float* cos_t, const float* sin_t, void* q_out, void* k_out,
+                                 float* rstd, int M, int Hq, int Hkv, int head_dim, int ld_qkv, float eps,
+                                 void* stream) {
+  b2::ensure_thread_context();
+  if (head_dim != 128) { set_error("qknorm_rope: head_dim must be 128"); return 10; }
+  if (M <= 0) return 0;
+  const long long warps = static_cast<long long>(M) * (Hq + Hkv);
+  const int blocks = static_cast<int>((warps + 7) / 8);
+  qknorm_rope_fwd_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(qkv), static_cast<const __nv_bfloat16*>(qw),
+      static_cast<const __nv_bfloat16*>(kw), pos, cos_t, sin_t, static_cast<__nv_bfloat16*>(q_out),
+      static_cast<__nv_bfloat16*>(k_out), rstd, M, Hq, Hkv, ld_qkv, eps);
+  B2_LAUNCH_CHECK("qknorm_rope_fwd");
+  return 0;
+}
+
+// dqw / dkw: fp32 [128] accumulators (caller zeroes them or accumulates across micro-batches).
+B2_EXPORT int b2_qknorm_rope_bwd(const void* dq, const void* dk, const void* qkv, const void* qw,
+                                 const void* kw, const int* pos, const float* cos_t, const float* sin_t,
+                                 const float* rstd, void* dqkv, float* dqw, float* dkw, int M, int Hq,
+                                 int Hkv, int head_dim, int ld_qkv, void* stream) {
+  b2::ensure_thread_context();
+  if (head_dim != 128) { set_error("qknorm_rope: head_dim must be 128"); return 10; }
+  if (M <= 0) return 0;
+  const long long warps = static_cast<long long>(M) * (Hq + Hkv);
+  long long blocks = (warps + 7) / 8;
+  const long long cap = static_cast<long long>(num_sms()) * 8;
+  if (blocks > cap) blocks = cap;
+  qknorm_rope_bwd_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(dq), static_cast<const __nv_bfloat16*>(dk),
+      static_cast<const __nv_bfloat16*>(qkv), static_cast<const __nv_bfloat16*>(qw),
+      static_cast<const __nv_bfloat16*>(kw), pos, cos_t, sin_t, rstd, static_cast<__nv_bfloat16*>(dqkv),
+      dqw, dkw, M, Hq, Hkv, ld_qkv);
+  B2_LAUNCH_CHECK("qknorm_rope_bwd");
+  return 0;
+}
+
+B2_EXPORT int b2_swiglu_fwd(const void* gu, void* out, long long M, int I, void* stream) {
+  b2::ensure_thread_context();
+  if (I % 8) { set_error("swiglu: I %% 8 != 0"); return 10; }
+  if (M <= 0) return 0;
+  const long long total = M * (I / 8);
+  long long blocks = (total + 255) / 256;
+  const long long cap = static_cast<long long>(num_sms()) * 16;
+  if (blocks > cap) blocks = cap;
+  swiglu_fwd_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(gu), static_cast<__nv_bfloat16*>(out), M, I);
+  B2_LAUNCH_CHECK("swiglu_fwd");
+  return 0;
+}
+B2_EXPORT int b2_swiglu_bwd(const void* dout, const void* gu, void* dgu, long long M, int I, void* stream) {
+  b2::ensure_thread_context();
+  if (I % 8) { set_error("swiglu: I %% 8 != 0"); return 10; }
+  if (M <= 0) return 0;
+  const long long total = M * (I / 8);
+  long long blocks = (total + 255) / 256;
+  const long long cap = static_cast<long long>(num_sms()) * 16;
+  if (blocks > cap) blocks = cap;
+  swiglu_bwd_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(dout), static_cast<const __nv_bfloat16*>(gu),
+      static_cast<__nv_bfloat16*>(dgu), M, I);
+  B2_LAUNCH_CHECK("swiglu_bwd");
+  return 0;
+}
+
+B2_EXPORT int b2_embedding_fwd(const long long* ids, const void* table, void* out, int M, int H, void* stream) {
+  b2::ensure_thread_context();
+  if (H % 8) { set_error("embedding: H %% 8 != 0"); return 10; }
+  if (M <= 0) return 0;
+  int blocks = M < num_sms() * 8 ? M : num_sms() * 8;
+  embedding_fwd_kernel<<<blocks, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      ids, static_cast<const __nv_bfloat16*>(table), static_cast<__nv_bfloat16*>(out), M, H);
+  B2_LAUNCH_CHECK("embedding_fwd");
+  return 0;
+}
+B2_EXPORT int b2_embedding_bwd(const long long* ids, const void* dout, void* dtable, int M, int H, void* stream) {
+  b2::ensure_thread_context();
+  if (H % 8) { set_error("embedding: H %% 8 != 0"); return 10; }
+  if (M <= 0) return 0;
+  int blocks = M < num_sms() * 8 ? M : num_sms() * 8;
+  embedding_bwd_kernel<<<blocks, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      ids, static_cast<const __nv_bfloat16*>(dout), static_cast<__nv_bfloat16*>(dtable), M, H);
+  B2_LAUNCH_CHECK("embedding_bwd");
+  return 0;
+}

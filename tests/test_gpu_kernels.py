@@ -1,0 +1,241 @@
+"""Numerics of every sm_100a kernel against a plain PyTorch fp32 reference of the same op."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def relerr(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).abs().max() / (b.abs().max() + 1e-6)).item()
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (0, 1), (1, 1), (1, 0)])
+@pytest.mark.parametrize("shape", [(256, 256, 128), (1000, 776, 520), (136, 72, 2056)])
+@pytest.mark.parametrize("bn", [0, 128, 256])
+def test_gemm_layouts(a_mn, b_mn, shape, bn):
+    from b200fw.ops import gemm
+    torch.manual_seed(0)
+    M, N, K = shape
+    A = torch.randn((K, M) if a_mn else (M, K), device=DEV, dtype=torch.bfloat16)
+    B = torch.randn((K, N) if b_mn else (N, K), device=DEV, dtype=torch.bfloat16)
+    C = gemm(A, B, a_mn=bool(a_mn), b_mn=bool(b_mn), bn=bn)
+    ref = (A.float().t() if a_mn else A.float()) @ (B.float() if b_mn else B.float().t())
+    assert relerr(C, ref) < 1e-2
+
+
+def test_gemm_epilogues():
+    from b200fw.ops import gemm
+    torch.manual_seed(1)
+    M, N, K = 520, 776, 264
+    A = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    B = torch.randn(N, K, device=DEV, dtype=torch.bfloat16)
+    R = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    ref = A.float() @ B.float().t()
+    assert relerr(gemm(A, B, residual=R), ref + R.float()) < 1e-2
+    C32 = torch.randn(M, N, device=DEV)
+    want = C32 + ref
+    gemm(A, B, out=C32, accumulate=True)
+    assert relerr(C32, want) < 1e-4
+    Cb = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    want = Cb.float() + ref
+    gemm(A, B, out=Cb, accumulate=True)
+    assert relerr(Cb, want) < 1e-2
+    # strided output / operand rows
+    big = torch.zeros(M, N + 64, device=DEV, dtype=torch.bfloat16)
+    gemm(A, B, out=big[:, 32:32 + N] if False else big[:, :N])
+    assert relerr(big[:, :N], ref) < 1e-2 and big[:, N:].abs().max().item() == 0
+
+
+def test_linear_autograd():
+    from b200fw.ops import linear
+    torch.manual_seed(2)
+    x = torch.randn(384, 256, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = torch.randn(512, 256, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    r = torch.randn(384, 512, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    y = linear(x, w, r)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xf, wf, rf = [t.detach().float().requires_grad_() for t in (x, w, r)]
+    (xf @ wf.t() + rf).backward(g.float())
+    assert relerr(x.grad, xf.grad) < 1e-2 and relerr(w.grad, wf.grad) < 1e-2 and relerr(r.grad, rf.grad) < 1e-3
+
+
+@pytest.mark.parametrize("H", [1024, 5120, 264])
+def test_rmsnorm(H):
+    from b200fw.ops import rmsnorm
+    torch.manual_seed(3)
+    x = torch.randn(300, H, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(H, device=DEV)).to(torch.bfloat16).requires_grad_()
+    y = rmsnorm(x, w, 1e-6)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xf, wf = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    yr = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6) * wf
+    yr.backward(g.float())
+    assert relerr(y, yr) < 1e-2 and relerr(x.grad, xf.grad) < 1.5e-2 and relerr(w.grad, wf.grad) < 1.5e-2
+
+
+def test_qknorm_rope_fwd_bwd():
+    from b200fw.ops import qknorm_rope, rope_tables
+    torch.manual_seed(4)
+    M, Hq, Hkv, D = 200, 4, 2, 128
+    qkv = torch.randn(M, (Hq + 2 * Hkv) * D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    qw = (1 + 0.1 * torch.randn(D, device=DEV)).to(torch.bfloat16).requires_grad_()
+    kw = (1 + 0.1 * torch.randn(D, device=DEV)).to(torch.bfloat16).requires_grad_()
+    pos = torch.randint(0, 4096, (M,), device=DEV, dtype=torch.int32)
+    cos, sin = rope_tables(4096, D, 1e6, DEV)
+    q, k, v = qknorm_rope(qkv, qw, kw, pos, cos, sin, Hq, Hkv, D)
+    gq, gk, gv = torch.randn_like(q), torch.randn_like(k), torch.randn_like(v)
+    torch.autograd.backward([q, k, v], [gq, gk, gv])
+    c = [t.detach().float().cpu().requires_grad_() for t in (qkv, qw, kw)]
+    qr, kr, vr = qknorm_rope(c[0], c[1], c[2], pos.cpu(), cos.cpu(), sin.cpu(), Hq, Hkv, D)
+    torch.autograd.backward([qr, kr, vr], [gq.float().cpu(), gk.float().cpu(), gv.float().cpu()])
+    assert relerr(q.cpu(), qr) < 1e-2 and relerr(k.cpu(), kr) < 1e-2
+    assert relerr(qkv.grad.cpu(), c[0].grad) < 2e-2
+    assert relerr(qw.grad.cpu(), c[1].grad) < 2e-2 and relerr(kw.grad.cpu(), c[2].grad) < 2e-2
+
+
+def test_swiglu_embedding():
+    from b200fw.ops import swiglu, embedding
+    torch.manual_seed(5)
+    gu = torch.randn(100, 2 * 704, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    y = swiglu(gu)
+    g = torch.randn_like(y)
+    y.backward(g)
+    gf = gu.detach().float().requires_grad_()
+    a, b = gf.chunk(2, -1)
+    yr = torch.nn.functional.silu(a) * b
+    yr.backward(g.float())
+    assert relerr(y, yr) < 1e-2 and relerr(gu.grad, gf.grad) < 1e-2
+    table = torch.randn(1000, 256, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    ids = torch.randint(0, 1000, (64,), device=DEV)
+    e = embedding(ids, table)
+    ge = torch.randn_like(e)
+    e.backward(ge)
+    tf = table.detach().float().requires_grad_()
+    torch.nn.functional.embedding(ids, tf).backward(ge.float())
+    assert torch.equal(e, table.detach()[ids]) and relerr(table.grad, tf.grad) < 1e-2
+
+
+@pytest.mark.parametrize("B,S,Hq,Hkv", [(1, 128, 1, 1), (2, 256, 4, 2), (1, 1024, 8, 1), (2, 200, 2, 2), (1, 77, 2, 1)])
+def test_flash_attention(B, S, Hq, Hkv):
+    from b200fw.ops import flash_attention
+    from b200fw.ops.attention import _attn_ref
+    torch.manual_seed(6)
+    D = 128
+    T = B * S
+    q = torch.randn(T, Hq * D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(T, Hkv * D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(T, Hkv * D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    o = flash_attention(q, k, v, B, S, Hq, Hkv)
+    g = torch.randn_like(o)
+    o.backward(g)
+    qf, kf, vf = [t.detach().float().requires_grad_() for t in (q, k, v)]
+    orf = _attn_ref(qf, kf, vf, B, S, Hq, Hkv, 1 / math.sqrt(D))
+    orf.backward(g.float())
+    assert relerr(o, orf) < 2e-2
+    assert relerr(q.grad, qf.grad) < 3e-2 and relerr(k.grad, kf.grad) < 3e-2 and relerr(v.grad, vf.grad) < 3e-2
+
+
+def test_fused_qkv_attention():
+    from b200fw.ops.attention import fused_qkv_attention
+    from b200fw.ops import rope_tables
+    torch.manual_seed(7)
+    B, S, Hq, Hkv, D = 2, 256, 4, 2, 128
+    M = B * S
+    qkv = torch.randn(M, (Hq + 2 * Hkv) * D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    qw = (1 + 0.1 * torch.randn(D, device=DEV)).to(torch.bfloat16).requires_grad_()
+    kw = (1 + 0.1 * torch.randn(D, device=DEV)).to(torch.bfloat16).requires_grad_()
+    pos = torch.arange(S, device=DEV, dtype=torch.int32).repeat(B)
+    cos, sin = rope_tables(1024, D, 1e6, DEV)
+    o = fused_qkv_attention(qkv, qw, kw, pos, cos, sin, B, S, Hq, Hkv, D)
+    g = torch.randn_like(o)
+    o.backward(g)
+    c = [t.detach().float().cpu().requires_grad_() for t in (qkv, qw, kw)]
+    orf = fused_qkv_attention(c[0], c[1], c[2], pos.cpu(), cos.cpu(), sin.cpu(), B, S, Hq, Hkv, D)
+    orf.backward(g.float().cpu())
+    assert relerr(o.cpu(), orf) < 2e-2
+    assert relerr(qkv.grad.cpu(), c[0].grad) < 4e-2
+    assert relerr(qw.grad.cpu(), c[1].grad) < 4e-2 and relerr(kw.grad.cpu(), c[2].grad) < 4e-2
+
+
+def test_lm_head_ce_and_logprob():
+    from b200fw.ops import lm_head_cross_entropy, lm_head_logprob
+    torch.manual_seed(8)
+    M, H, V = 300, 256, 4096
+    h = (0.5 * torch.randn(M, H, device=DEV)).to(torch.bfloat16).requires_grad_()
+    w = (0.05 * torch.randn(V, H, device=DEV)).to(torch.bfloat16).requires_grad_()
+    labels = torch.randint(0, V, (M,), device=DEV)
+    labels[:50] = -100
+    loss = lm_head_cross_entropy(h, w, labels, loss_scale=0.5, chunk=128)
+    loss.backward()
+    hf, wf = h.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    lr = torch.nn.functional.cross_entropy(hf @ wf.t(), labels, ignore_index=-100)
+    (0.5 * lr).backward()
+    assert abs(loss.item() - lr.item()) < 2e-2
+    assert relerr(h.grad, hf.grad) < 3e-2 and relerr(w.grad, wf.grad) < 3e-2
+    h.grad = None
+    w.grad = None
+    lp = lm_head_logprob(h, w, labels, temperature=0.8, chunk=128)
+    gl = torch.randn_like(lp)
+    lp.backward(gl)
+    hf.grad = None
+    wf.grad = None
+    lpr = torch.log_softmax((hf @ wf.t()) / 0.8, -1).gather(-1, labels.clamp(min=0)[:, None]).squeeze(-1)
+    lpr = torch.where(labels == -100, torch.zeros_like(lpr), lpr)
+    lpr.backward(gl)
+    assert (lp - lpr).abs().max().item() < 3e-2
+    assert relerr(h.grad, hf.grad) < 3e-2 and relerr(w.grad, wf.grad) < 3e-2
+
+
+def test_grpo_loss():
+    from b200fw.ops import grpo_token_loss
+    from b200fw.ops.loss import _grpo_ref
+    torch.manual_seed(9)
+    R, C = 16, 200
+    lp = (-2 + 0.3 * torch.randn(R, C, device=DEV)).requires_grad_()
+    old = lp.detach() + 0.3 * torch.randn(R, C, device=DEV)
+    ref = lp.detach() - 0.05 + 0.1 * torch.randn(R, C, device=DEV)
+    mask = (torch.rand(R, C, device=DEV) > 0.3).float()
+    adv = torch.randn(R, device=DEV)
+    loss, info = grpo_token_loss(lp, old, ref, mask, adv, 0.2, 0.01)
+    loss.backward()
+    lpf = lp.detach().clone().requires_grad_()
+    lr, ir = _grpo_ref(lpf, old, ref, mask, adv, 0.2, 0.01)
+    lr.backward()
+    assert abs(loss.item() - lr.item()) < 1e-4
+    assert (lp.grad - lpf.grad).abs().max().item() < 1e-6
+    for key in ("ratio_mean", "ratio_max", "ratio_min", "clipped_fraction", "kl_divergence"):
+        assert abs(float(info[key]) - float(ir[key])) < 1e-3, key
+
+
+def test_sumsq_adamw():
+    from b200fw.ops import sumsq, fused_adamw
+    torch.manual_seed(10)
+    n = 100003
+    g = torch.randn(n, device=DEV).to(torch.bfloat16)
+    assert abs(sumsq(g).item() - g.float().pow(2).sum().item()) / n < 1e-3
+    bad = g.clone()
+    bad[5] = float("nan")
+    assert math.isnan(sumsq(bad).item())
+    master = torch.randn(n, device=DEV)
+    m, v = torch.zeros(n, device=DEV), torch.zeros(n, device=DEV)
+    p_out = torch.empty(n, device=DEV, dtype=torch.bfloat16)
+    ref = master.clone().requires_grad_()
+    opt = torch.optim.AdamW([ref], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    for step in range(1, 4):
+        hyper = torch.tensor([1e-2, 0.9, 0.95, 1e-8, 0.1, 1 - 0.9 ** step, 1 - 0.95 ** step, 0.0], device=DEV)
+        fused_adamw(master, m, v, g, hyper, param_out=p_out)
+        ref.grad = g.float()
+        opt.step()
+    assert (master - ref.detach()).abs().max().item() < 1e-5
+    assert relerr(p_out, master) < 1e-2
+    # skipped when the norm is not finite; clipped otherwise
+    before = master.clone()
+    fused_adamw(master, m, v, g, hyper, norm_sq=torch.tensor([float("inf")], device=DEV))
+    assert torch.equal(before, master)
