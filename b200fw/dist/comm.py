@@ -126,6 +126,47 @@ class _ScatterSeq(torch.autograd.Function):
         return all_gather(g.contiguous(), ctx.group), None
 
 
+class _ScatterToSeq(torch.autograd.Function):
+    """Keep this rank's dim-0 slice of a replicated tensor (forward) / all-gather the gradient slices
+    (backward), so that the producer of the replicated tensor sees its complete gradient."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        n, r = _size(group), dist.get_rank(group)
+        rows = x.shape[0] // n
+        return x[r * rows:(r + 1) * rows]
+
+    @staticmethod
+    def backward(ctx, g):
+        return all_gather(g.contiguous(), ctx.group), None
+
+
+class _GatherSeqReplicated(torch.autograd.Function):
+    """All-gather along dim 0 (forward) into a tensor that every rank then consumes identically;
+    each rank's gradient of the gathered tensor is already complete, so backward keeps the local
+    slice instead of reduce-scattering."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return all_gather(x, group)
+
+    @staticmethod
+    def backward(ctx, g):
+        n, r = _size(ctx.group), dist.get_rank(ctx.group)
+        rows = g.shape[0] // n
+        return g[r * rows:(r + 1) * rows].contiguous(), None
+
+
+def scatter_to_sequence_region(x, group=None):
+    return x if group is None else _ScatterToSeq.apply(x, group)
+
+
+def gather_sequence_replicated(x, group=None):
+    return x if group is None else _GatherSeqReplicated.apply(x, group)
+
+
 def copy_to_parallel_region(x, group=None):
     return x if group is None else _CopyToParallelRegion.apply(x, group)
 

@@ -84,8 +84,9 @@ class RowParallelLinear(nn.Module):
     """``y = sum_ranks x_local @ W_local^T`` with ``W_local = W[:, rank*in/tp : (rank+1)*in/tp]``.
 
     ``sequence_parallel``: the partial sums are reduce-scattered along tokens (the residual, already
-    a token shard, is added afterwards); otherwise they are all-reduced and the residual is fused in
-    the GEMM epilogue of rank-local work (added once: on TP rank 0's partial)."""
+    a token shard, is added afterwards); otherwise they are all-reduced and the residual is added on
+    every rank after the reduction (so each rank keeps the full gradient of the residual stream).
+    Without TP the residual add rides in the GEMM epilogue."""
 
     def __init__(self, in_features, out_features, ctx=None, sequence_parallel=False, init_std=0.02,
                  dtype=None, device=None):
@@ -108,8 +109,9 @@ class RowParallelLinear(nn.Module):
             if residual is not None:
                 y = y + residual
         else:
-            y = ops.linear(x, self.weight, residual if self.tp_rank == 0 else None)
-            y = comm.reduce_from_parallel_region(y, self.tp_group)
+            y = comm.reduce_from_parallel_region(ops.linear(x, self.weight), self.tp_group)
+            if residual is not None:
+                y = y + residual.reshape(y.shape)
         if not self.sequence_parallel:
             y = y.reshape(*shape[:-1], y.shape[-1])
         return y
@@ -243,6 +245,19 @@ class ParallelTransformerModel(nn.Module):
             g = torch.Generator(device=p.device).manual_seed(key % (2 ** 62))
             p.copy_(torch.empty(p.shape, dtype=torch.float32, device=p.device).normal_(0.0, std, generator=g).to(p.dtype))
 
+    def clone(self, requires_grad: bool = False) -> "ParallelTransformerModel":
+        """A second model with the same architecture, parallel layout and weights (process groups are
+        shared, not copied); used for the frozen reference policy."""
+        p0 = next(self.parameters())
+        other = ParallelTransformerModel(self.cfg, self.ctx, (self.layer_start, self.layer_end),
+                                         self.is_first_stage, self.is_last_stage, self.sequence_parallel,
+                                         self.gradient_checkpointing, dtype=p0.dtype, device=p0.device)
+        with torch.no_grad():
+            for a, b in zip(other.parameters(), self.parameters()):
+                a.copy_(b)
+                a.requires_grad_(requires_grad)
+        return other
+
     # ---- pieces ------------------------------------------------------------------------------
     @property
     def lm_head_weight(self) -> torch.Tensor:
@@ -256,8 +271,7 @@ class ParallelTransformerModel(nn.Module):
     def embed(self, input_ids: torch.Tensor) -> torch.Tensor:
         h = ops.embedding(input_ids.reshape(-1), self.embed_tokens)
         if self.sequence_parallel:
-            n = h.shape[0] // self.tp_size
-            h = h[self.tp_rank * n:(self.tp_rank + 1) * n]
+            h = comm.scatter_to_sequence_region(h, self.tp_group)
         return h
 
     def run_layers(self, h: torch.Tensor, positions: torch.Tensor, B: int, S: int) -> torch.Tensor:
@@ -272,7 +286,7 @@ class ParallelTransformerModel(nn.Module):
         """Final norm; under sequence parallelism the result is gathered to all tokens."""
         h = self.norm(h)
         if self.sequence_parallel:
-            h = comm.gather_sequence(h, self.tp_group)
+            h = comm.gather_sequence_replicated(h, self.tp_group)
         return h
 
     # ---- public entry points ---------------------------------------------------------------------

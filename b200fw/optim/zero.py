@@ -42,6 +42,7 @@ class _Bucket:
     def __init__(self, params: List[torch.nn.Parameter], kind: int, world: int, rank: int, dtype, device,
                  grad_dtype):
         self.params, self.kind = params, kind
+        self.shapes = [tuple(p.shape) for p in params]
         self.offsets, n = [], 0
         for p in params:
             self.offsets.append(n)
@@ -62,8 +63,11 @@ class _Bucket:
         self.bind_params()
 
     def bind_params(self):
-        for p, o in zip(self.params, self.offsets):
-            p.data = self.param_buf[o:o + p.numel()].view(p.shape)
+        for p, o, shp in zip(self.params, self.offsets, self.shapes):
+            n = 1
+            for d in shp:
+                n *= d
+            p.data = self.param_buf[o:o + n].view(shp)
 
     def unbind_params(self):
         empty = torch.empty(0, dtype=self.dtype, device=self.device)
@@ -210,7 +214,10 @@ class ZeROOptimizer:
         with stream_ctx:
             if b.kind == KIND_TP_PARTIAL and self._tp_group() is not None:
                 dist.all_reduce(b.grad_buf, group=self._tp_group())
-            if self.world > 1:
+            if self.world > 1 and self.stage == 0:
+                dist.all_reduce(b.grad_buf, group=self.dp_group)   # unsharded: every rank keeps it all
+                out = b.grad_buf
+            elif self.world > 1:
                 out = torch.empty(b.shard_numel, dtype=b.grad_buf.dtype, device=self.device)
                 dist.reduce_scatter_tensor(out, b.grad_buf, group=self.dp_group)
             else:
@@ -258,6 +265,8 @@ class ZeROOptimizer:
             self._prepare_backward()
 
     def _reduce_all(self):
+        if all(b.reduced for b in self.buckets):
+            return
         if not self.use_main_grad:
             self._pack_autograd_grads()
         for b in self.buckets:

@@ -165,9 +165,7 @@ class TrainEngine:
         # ---- frozen reference policy ---------------------------------------------------------------
         want_ref = cfg.build_ref_model if cfg.build_ref_model is not None else cfg.grpo_beta > 0
         if want_ref and cfg.lora_rank <= 0 and cfg.pp_size == 1:
-            self.ref_model = copy.deepcopy(self.model)
-            for p in self.ref_model.parameters():
-                p.requires_grad_(False)
+            self.ref_model = self.model.clone(requires_grad=False)
             self.ref_model.eval()
         self._ref_is_base = bool(want_ref and cfg.lora_rank > 0)  # LoRA: reference = adapters off
         # ---- LoRA -------------------------------------------------------------------------------

@@ -1,0 +1,116 @@
+"""3-D group layout, collectives, TP autograd regions and PP p2p over gloo on CPU."""
+import torch
+
+from _dist_util import run_ranks
+from b200fw.dist.context import ParallelContext
+
+
+def test_group_table_layout():
+    tp, pp, dp = ParallelContext.group_table(8, tp=2, dp=2, pp=2)
+    assert tp == [[0, 1], [2, 3], [4, 5], [6, 7]]
+    assert pp == [[0, 2], [1, 3], [4, 6], [5, 7]]
+    assert dp == [[0, 4], [1, 5], [2, 6], [3, 7]]
+    assert ParallelContext.coords(5, tp=2, pp=2) == (1, 0, 1)
+    tp, pp, dp = ParallelContext.group_table(8, tp=2, dp=4, pp=1)
+    assert dp == [[0, 2, 4, 6], [1, 3, 5, 7]] and pp == [[r] for r in [0, 1, 2, 3, 4, 5, 6, 7]]
+
+
+def _groups(rank, world):
+    ctx = ParallelContext.init_distributed(tp_size=2, dp_size=2, pp_size=1, backend="gloo")
+    return (ctx.tp_rank, ctx.dp_rank, ctx.tp_ranks, ctx.dp_ranks)
+
+
+def test_process_groups_gloo():
+    res = run_ranks(_groups, 4)
+    assert res[0] == (0, 0, [0, 1], [0, 2]) and res[3] == (1, 1, [2, 3], [1, 3])
+
+
+def _collectives(rank, world):
+    from b200fw.dist import comm
+    ctx = ParallelContext.init_distributed(tp_size=world, backend="gloo")
+    g = ctx.tp_group
+    x = torch.full((4, 3), float(rank + 1))
+    assert torch.equal(comm.all_reduce(x.clone(), g), torch.full((4, 3), 3.0))
+    ag = comm.all_gather(x, g)
+    assert ag.shape == (8, 3) and ag[0, 0] == 1 and ag[4, 0] == 2
+    assert comm.all_gather_last_dim(x, g).shape == (4, 6)
+    rs = comm.reduce_scatter(torch.arange(8.0).reshape(4, 2) + rank, g)
+    assert torch.equal(rs, (torch.arange(8.0).reshape(4, 2) * 2 + 1)[rank * 2:(rank + 1) * 2])
+    b = torch.full((2,), float(rank))
+    assert comm.broadcast(b, 1, g)[0] == 1
+    # autograd regions
+    a = torch.ones(2, 2, requires_grad=True)
+    comm.copy_to_parallel_region(a, g).sum().backward()
+    assert torch.equal(a.grad, torch.full((2, 2), 2.0))
+    a = torch.ones(2, 2, requires_grad=True)
+    y = comm.reduce_from_parallel_region(a * (rank + 1), g)
+    assert torch.equal(y, torch.full((2, 2), 3.0))
+    y.sum().backward()
+    assert torch.equal(a.grad, torch.full((2, 2), float(rank + 1)))
+    a = torch.ones(2, 2, requires_grad=True)
+    y = comm.gather_from_parallel_region(a, g)
+    (y * torch.arange(4.0)).sum().backward()
+    assert torch.equal(a.grad[0], torch.tensor([0.0, 1.0]) + 2 * rank)
+    # sequence-parallel pair
+    a = torch.ones(2, 3, requires_grad=True)
+    y = comm.gather_sequence(a * (rank + 1), g)
+    assert y.shape == (4, 3)
+    y.sum().backward()
+    assert torch.equal(a.grad, torch.full((2, 3), 2.0 * (rank + 1)))
+    # async all-reduce with bounded wait
+    h = comm.AsyncAllReduce().launch(x.clone(), g)
+    h.wait(timeout_sec=30)
+    assert h.is_completed()
+    return True
+
+
+def test_collectives_and_regions():
+    assert all(run_ranks(_collectives, 2))
+
+
+def _p2p(rank, world):
+    from b200fw.dist import comm
+    ctx = ParallelContext.init_distributed(pp_size=world, backend="gloo")
+    dev = torch.device("cpu")
+    if rank == 0:
+        comm.send_forward(torch.arange(6.0).reshape(2, 3), ctx.pp_next_rank, ctx.pp_group)
+        g = comm.recv_backward((2, 3), torch.float32, dev, ctx.pp_next_rank, ctx.pp_group)
+        assert torch.equal(g, torch.full((2, 3), 7.0))
+        g2 = comm.send_forward_recv_backward(torch.ones(2, 3), (2, 3), torch.float32, dev, ctx.pp_next_rank, ctx.pp_group)
+        assert torch.equal(g2, torch.full((2, 3), 9.0))
+    else:
+        x = comm.recv_forward((2, 3), torch.float32, dev, ctx.pp_prev_rank, ctx.pp_group)
+        assert torch.equal(x, torch.arange(6.0).reshape(2, 3))
+        comm.send_backward(torch.full((2, 3), 7.0), ctx.pp_prev_rank, ctx.pp_group)
+        x2 = comm.send_backward_recv_forward(torch.full((2, 3), 9.0), (2, 3), torch.float32, dev, ctx.pp_prev_rank, ctx.pp_group)
+        assert torch.equal(x2, torch.ones(2, 3))
+    assert ctx.is_first_pp_stage == (rank == 0) and ctx.is_last_pp_stage == (rank == 1)
+    return True
+
+
+def test_pp_p2p():
+    assert all(run_ranks(_p2p, 2))
+
+
+def test_async_handle_timeout():
+    from b200fw.dist.comm import AsyncHandle
+
+    class Never:
+        def is_completed(self):
+            return False
+
+        def wait(self):
+            raise AssertionError("must not block")
+
+    import pytest
+    with pytest.raises(RuntimeError):
+        AsyncHandle(work=Never()).wait(timeout_sec=0.05, poll_s=0.01)
+
+
+def test_stream_manager_cpu_noop():
+    from b200fw.dist.streams import StreamManager
+    sm = StreamManager()
+    with sm.comm_context():
+        pass
+    sm.sync_compute_to_comm()
+    assert sm.get_stats()["comm_ops"] == 1

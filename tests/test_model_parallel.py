@@ -1,0 +1,162 @@
+"""Tensor-parallel layers, sequence parallelism, LoRA x TP and HF shard IO against single-process
+references (gloo, CPU, fp32)."""
+import copy
+import tempfile
+
+import torch
+
+from _dist_util import run_ranks
+from b200fw.model import (PRESETS, ModelConfig, ParallelTransformerModel, apply_lora, get_lora_state_dict,
+                          load_from_hf_checkpoint, merge_lora_weights, save_hf_checkpoint)
+
+CFG = ModelConfig(vocab_size=512, hidden_size=64, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=16,
+                  intermediate_size=96, max_position_embeddings=256, tie_word_embeddings=False)
+
+
+def _full_model(path):
+    torch.manual_seed(0)
+    m = ParallelTransformerModel(CFG)
+    m.init_weights(3)
+    save_hf_checkpoint(m, path)
+    return m
+
+
+def _tp_worker(rank, world, path, seq_par):
+    from b200fw.dist.context import ParallelContext
+    ctx = ParallelContext.init_distributed(tp_size=world, backend="gloo")
+    ref = ParallelTransformerModel(CFG)
+    load_from_hf_checkpoint(ref, path, strict=True)
+    m = ParallelTransformerModel(CFG, ctx, sequence_parallel=seq_par)
+    loaded, missing = load_from_hf_checkpoint(m, path, strict=True)
+    assert missing == 0
+    g = torch.Generator().manual_seed(1)
+    ids = torch.randint(0, CFG.vocab_size, (2, 16), generator=g)
+    labels = ids.clone()
+    labels[:, :4] = -100
+    out = m(ids)
+    want = ref(ids)
+    assert (out - want).abs().max() < 1e-4
+    l, lr = m.loss(ids, labels), ref.loss(ids, labels)
+    assert abs(l.item() - lr.item()) < 1e-5
+    l.backward()
+    lr.backward()
+    # sharded weight grads equal the matching slice of the reference grads
+    gw = m.layers[0].mlp.down_proj.weight.grad
+    rw = ref.layers[0].mlp.down_proj.weight.grad
+    n = rw.shape[1] // world
+    assert (gw - rw[:, rank * n:(rank + 1) * n]).abs().max() < 1e-5, ((gw - rw[:, rank * n:(rank + 1) * n]).abs().max(), rw.abs().max())
+    gq = m.layers[1].self_attn.qkv_proj.weight.grad
+    rq = ref.layers[1].self_attn.qkv_proj.weight.grad
+    D, hq, hk = CFG.head_dim, CFG.num_heads // world, CFG.num_kv_heads // world
+    want_q = rq[rank * hq * D:(rank + 1) * hq * D]
+    assert (gq[:hq * D] - want_q).abs().max() < 1e-5
+    # partial-grad parameters need the TP sum; replicated ones are already complete
+    import torch.distributed as dist
+    qn = m.layers[0].self_attn.q_norm.weight
+    assert qn.tp_partial_grad
+    tot = qn.grad.clone()
+    dist.all_reduce(tot, group=ctx.tp_group)
+    assert (tot - ref.layers[0].self_attn.q_norm.weight.grad).abs().max() < 1e-5
+    ln = m.layers[0].input_layernorm.weight
+    if seq_par:
+        assert ln.tp_partial_grad
+        t2 = ln.grad.clone()
+        dist.all_reduce(t2, group=ctx.tp_group)
+        assert (t2 - ref.layers[0].input_layernorm.weight.grad).abs().max() < 1e-5
+    else:
+        assert not ln.tp_partial_grad
+        assert (ln.grad - ref.layers[0].input_layernorm.weight.grad).abs().max() < 1e-5
+    assert (m.embed_tokens.grad - ref.embed_tokens.grad).abs().max() < 1e-5
+    # gathered export equals the original full tensors
+    from b200fw.model.hf_io import hf_named_tensors
+    full = dict(hf_named_tensors(m))
+    refd = dict(hf_named_tensors(ref))
+    assert all((full[k] - refd[k]).abs().max() < 1e-7 for k in refd)
+    return True
+
+
+def test_tp2_matches_single():
+    with tempfile.TemporaryDirectory() as d:
+        _full_model(d)
+        assert all(run_ranks(_tp_worker, 2, d, False))
+
+
+def test_tp2_sequence_parallel_matches_single():
+    with tempfile.TemporaryDirectory() as d:
+        _full_model(d)
+        assert all(run_ranks(_tp_worker, 2, d, True))
+
+
+def test_hf_roundtrip_and_tied_presets():
+    with tempfile.TemporaryDirectory() as d:
+        m = _full_model(d)
+        m2 = ParallelTransformerModel(CFG)
+        loaded, missing = load_from_hf_checkpoint(m2, d, strict=True)
+        assert missing == 0 and loaded > 0
+        ids = torch.randint(0, CFG.vocab_size, (1, 8))
+        assert torch.equal(m(ids), m2(ids))
+    tiny = ParallelTransformerModel(PRESETS["tiny"])
+    assert tiny.tied and tiny.lm_head is None
+    assert sum(p.numel() for p in tiny.parameters()) == PRESETS["tiny"].num_params()
+    assert PRESETS["qwen3-0.6b"].num_params() == 596049920
+
+
+def test_gradient_checkpointing_same_grads():
+    torch.manual_seed(0)
+    a = ParallelTransformerModel(CFG)
+    a.init_weights(1)
+    b = copy.deepcopy(a)
+    b.gradient_checkpointing = True
+    ids = torch.randint(0, CFG.vocab_size, (2, 12))
+    a.loss(ids, ids).backward()
+    b.loss(ids, ids).backward()
+    for pa, pb in zip(a.parameters(), b.parameters()):
+        assert (pa.grad - pb.grad).abs().max() < 1e-6
+
+
+def test_lora_single_process_merge_and_freeze():
+    torch.manual_seed(0)
+    m = ParallelTransformerModel(CFG)
+    m.init_weights(2)
+    ids = torch.randint(0, CFG.vocab_size, (2, 10))
+    base = m(ids).detach()
+    names = apply_lora(m, rank=4, alpha=8.0)
+    assert len(names) == 7 * CFG.num_layers
+    assert all(("lora_" in n) == p.requires_grad for n, p in m.named_parameters())
+    assert torch.allclose(m(ids), base, atol=1e-6)          # B starts at zero
+    for _, p in m.named_parameters():
+        if p.requires_grad and p.shape[1] == 4:                # lora_B
+            torch.nn.init.normal_(p, std=0.05)
+    with_lora = m(ids).detach()
+    assert (with_lora - base).abs().max() > 1e-4
+    merge_lora_weights(m)
+    assert torch.allclose(m(ids), with_lora, atol=1e-4)
+    merge_lora_weights(m, unmerge=True)
+    assert torch.allclose(m(ids), with_lora, atol=1e-4)
+    assert len(get_lora_state_dict(m)) == 2 * 7 * CFG.num_layers
+
+
+def _lora_tp_worker(rank, world, path):
+    from b200fw.dist.context import ParallelContext
+    ctx = ParallelContext.init_distributed(tp_size=world, backend="gloo")
+    m = ParallelTransformerModel(CFG, ctx)
+    load_from_hf_checkpoint(m, path, strict=True)
+    apply_lora(m, rank=4, alpha=8.0)
+    g = torch.Generator().manual_seed(5)
+    for n, p in m.named_parameters():      # same replicated values on all ranks, distinct shards
+        if "lora_" in n:
+            with torch.no_grad():
+                p.copy_(torch.empty(p.shape).normal_(0, 0.05, generator=g))
+    ids = torch.randint(0, CFG.vocab_size, (2, 10), generator=torch.Generator().manual_seed(2))
+    out = m(ids).detach()
+    merge_lora_weights(m)
+    merged = m(ids).detach()
+    assert (out - merged).abs().max() < 1e-4
+    return out.tolist()
+
+
+def test_lora_tp2_merge_consistent_across_ranks():
+    with tempfile.TemporaryDirectory() as d:
+        _full_model(d)
+        outs = run_ranks(_lora_tp_worker, 2, d)
+        assert (torch.tensor(outs[0]) - torch.tensor(outs[1])).abs().max() < 1e-5
