@@ -1,0 +1,202 @@
+"""TrainEngine end to end on CPU: the tiny-Qwen3 DP2 + ZeRO-1 plumbing configuration, 1F1B pipeline
+equivalence, GRPO step against a plain PyTorch oracle, checkpoints, truncation."""
+import math
+import tempfile
+
+import torch
+
+from _dist_util import run_ranks
+from b200fw.model import PRESETS, ModelConfig, ParallelTransformerModel
+from b200fw.train import TrainConfig, TrainEngine
+
+SMALL = ModelConfig(vocab_size=256, hidden_size=32, num_layers=4, num_heads=2, num_kv_heads=2, head_dim=16,
+                    intermediate_size=48, max_position_embeddings=128, tie_word_embeddings=False)
+
+
+def _tiny_batch(step, rank, n, seq, vocab):
+    g = torch.Generator().manual_seed(step * 17 + rank)
+    ids = torch.randint(0, vocab, (n, seq), generator=g)
+    labels = ids.clone()
+    labels[:, : seq // 2] = -100
+    return ids, labels
+
+
+def _tiny_worker(rank, world, steps, seq):
+    cfg = TrainConfig(model_preset="tiny", dp_size=world, lora_rank=0, grpo_beta=0.0, learning_rate=1e-4,
+                      gradient_accumulation_steps=1, zero_stage=1, use_amp=False, amp_dtype="fp32",
+                      warmup_steps=max(1, steps // 20), total_training_steps=steps, lr_scheduler_type="cosine",
+                      max_seq_len=seq, backend="gloo", bucket_mb=4.0)
+    eng = TrainEngine(cfg).initialize()
+    assert eng.optimizer.stage == 1 and eng.optimizer.world == world
+    out = []
+    for s in range(steps):
+        ids, labels = _tiny_batch(s, rank, 4 // world, seq, 8192)
+        m = eng.sft_step_tensors(ids, labels)
+        out.append((m.loss, m.grad_norm, m.learning_rate))
+    return out
+
+
+def test_tiny_qwen3_sft_dp2_zero1_matches_single_process():
+    """4 layers / hidden 256 / 4q-2kv heads of 64 / FFN 704 / vocab 8192 / tied; batch 4 x seq 256 (seq
+    shortened to 64 here for CPU time), loss on the second half, AdamW 1e-4, 5 % warm-up, cosine."""
+    steps, seq = 20, 64
+    dp = run_ranks(_tiny_worker, 2, steps, seq, timeout=900)
+    # oracle: one process, plain torch AdamW, whole global batch
+    torch.manual_seed(0)
+    model = ParallelTransformerModel(PRESETS["tiny"])
+    model.init_weights(0)
+    opt = torch.optim.AdamW(model.parameters(), lr=1e-4, weight_decay=0.01)
+    from b200fw.optim import LRSchedule
+    sched = LRSchedule(1e-4, "cosine", 1, steps, 0.1)
+    for s in range(steps):
+        for g in opt.param_groups:
+            g["lr"] = sched.lr_at(s)
+        losses = []
+        for r in range(2):
+            ids, labels = _tiny_batch(s, r, 2, seq, 8192)
+            l = model.loss(ids, labels)
+            (l / 2).backward()
+            losses.append(l.item())
+        gn = torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
+        opt.step()
+        opt.zero_grad()
+        for r in range(2):
+            assert abs(dp[r][s][0] - losses[r]) < 2e-4, (s, r, dp[r][s][0], losses[r])
+            assert abs(dp[r][s][1] - float(gn)) / float(gn) < 1e-3
+            assert abs(dp[r][s][2] - sched.lr_at(s)) < 1e-12
+
+
+def _pp_worker(rank, world, path):
+    from b200fw.dist.context import ParallelContext
+    from b200fw.model import load_from_hf_checkpoint
+    cfg = TrainConfig(model_config=SMALL, pp_size=world, num_micro_batches=4, lora_rank=0, grpo_beta=0.0,
+                      learning_rate=1e-3, gradient_accumulation_steps=1, zero_stage=1, use_amp=False,
+                      amp_dtype="fp32", warmup_steps=0, max_seq_len=32, backend="gloo", max_grad_norm=0.0)
+    eng = TrainEngine(cfg).initialize()
+    load_from_hf_checkpoint(eng.model, path, strict=False)
+    eng.optimizer.refresh_masters_from_params()
+    m = eng.model
+    assert (m.embed_tokens is not None) == (rank == 0) and (m.lm_head is not None) == (rank == world - 1)
+    assert len(m.layers) == 2
+    ids, labels = _tiny_batch(0, 0, 8, 16, SMALL.vocab_size)
+    eng.optimizer.begin_backward(True)
+    loss = eng.pipeline_scheduler.run_1f1b_schedule(ids, labels)
+    loss = eng.pipeline_scheduler.broadcast_loss(loss)
+    grads = {f"{m.layer_start + i}": l.mlp.down_proj.weight.grad.clone() for i, l in enumerate(m.layers)}
+    met = eng.sft_step_tensors(ids, labels)     # a full step through the public API also works
+    return float(loss), {k: v.tolist() for k, v in grads.items()}, met.loss
+
+
+def test_pipeline_1f1b_matches_single_process():
+    from b200fw.model import save_hf_checkpoint
+    with tempfile.TemporaryDirectory() as d:
+        ref = ParallelTransformerModel(SMALL)
+        ref.init_weights(11)
+        save_hf_checkpoint(ref, d)
+        res = run_ranks(_pp_worker, 2, d, timeout=600)
+        ids, labels = _tiny_batch(0, 0, 8, 16, SMALL.vocab_size)
+        # mean of per-micro-batch means, as the schedule computes it
+        total = 0.0
+        for mb_ids, mb_labels in zip(ids.chunk(4), labels.chunk(4)):
+            l = ref.loss(mb_ids, mb_labels)
+            (l / 4).backward()
+            total += l.item() / 4
+        assert abs(res[0][0] - total) < 1e-5 and abs(res[1][0] - total) < 1e-5
+        for r in range(2):
+            for k, g in res[r][1].items():
+                want = ref.layers[int(k)].mlp.down_proj.weight.grad
+                assert (torch.tensor(g) - want).abs().max() < 1e-6
+        assert abs(res[0][2] - res[1][2]) < 1e-7
+
+
+def test_grpo_step_matches_oracle_and_icepop_masks():
+    torch.manual_seed(0)
+    cfg = TrainConfig(model_config=SMALL, lora_rank=0, grpo_beta=0.05, grpo_clip_eps=0.2, learning_rate=1e-3,
+                      gradient_accumulation_steps=1, use_amp=False, amp_dtype="fp32", warmup_steps=0,
+                      max_seq_len=64, icepop_enabled=True, icepop_divergence_threshold=1e9)
+    eng = TrainEngine(cfg).initialize()
+    assert eng.ref_model is not None
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, 256, (6,), generator=g).tolist() for _ in range(2)]
+    groups = [[torch.randint(0, 256, (5 + k,), generator=g).tolist() for k in range(3)] for _ in range(2)]
+    rewards = [[1.0, 0.0, 0.5], [0.2, 0.2, 0.2]]
+    # oracle on a clone of the initial weights
+    oracle = eng.model.clone(requires_grad=True)
+    m = eng.grpo_step(prompts, groups, rewards)
+    adv = TrainEngine.group_advantages(rewards[0]) + TrainEngine.group_advantages(rewards[1])
+    assert adv[3:] == [0.0, 0.0, 0.0] and abs(sum(adv[:3])) < 1e-5
+    seqs = [p + r for p, rs in zip(prompts, groups) for r in rs]
+    L = max(len(s) for s in seqs)
+    ids = torch.tensor([s + [0] * (L - len(s)) for s in seqs])
+    labels = torch.full_like(ids, -100)
+    i = 0
+    for p, rs in zip(prompts, groups):
+        for r in rs:
+            labels[i, len(p):len(p) + len(r)] = torch.tensor(r)
+            i += 1
+    lp = torch.log_softmax(oracle(ids)[:, :-1].float(), -1).gather(-1, labels[:, 1:].clamp(min=0)[..., None]).squeeze(-1)
+    mask = (labels[:, 1:] != -100).float()
+    lp = lp * mask
+    ratio = torch.exp(lp - lp.detach())
+    a = torch.tensor(adv)[:, None]
+    pol = (-torch.min(ratio * a, ratio.clamp(0.8, 1.2) * a) * mask).sum() / (mask.sum() + 1e-8)
+    assert abs(m.policy_loss - pol.item()) < 1e-5 and m.kl_divergence == 0.0     # ref == policy at step 0
+    assert abs(m.extras["ratio_mean"] - 1.0) < 1e-6 and m.grad_norm > 0
+    assert m.extras["icepop_num_masked"] == 0
+    # second step: behaviour baseline kept -> ratio != 1, KL >= 0
+    m2 = eng.grpo_step(prompts, groups, rewards, reset_behavior_baseline=False)
+    assert m2.extras["ratio_max"] != 1.0 and m2.kl_divergence >= 0.0
+    # IcePop: rollout log-probs far from the trainer's mask at most max_mask_ratio of the responses
+    eng.icepop.config.divergence_threshold = 0.1
+    fake = torch.full((6,), -100.0)
+    m3 = eng.grpo_step(prompts, groups, rewards, infer_log_probs=fake)
+    assert m3.extras["icepop_num_masked"] == 3 and m3.extras["icepop_masked_ratio"] == 0.5
+    # skip_optimizer_step leaves the weights alone and keeps accumulating
+    before = [p.detach().clone() for p in eng.model.parameters()]
+    step_before = eng.step_count
+    eng.grpo_step(prompts, groups, rewards, skip_optimizer_step=True)
+    assert all(torch.equal(a, b) for a, b in zip(before, eng.model.parameters())) and eng.step_count == step_before
+
+
+def test_checkpoint_roundtrip_full_and_lora():
+    for rank_ in (0, 4):
+        cfg = TrainConfig(model_config=SMALL, lora_rank=rank_, grpo_beta=0.0, learning_rate=1e-2,
+                          gradient_accumulation_steps=1, use_amp=False, amp_dtype="fp32", warmup_steps=0, max_seq_len=32)
+        eng = TrainEngine(cfg).initialize()
+        ids, labels = _tiny_batch(0, 0, 2, 16, 256)
+        for _ in range(2):
+            eng.sft_step_tensors(ids, labels)
+        with tempfile.TemporaryDirectory() as d:
+            eng.save_checkpoint(d)
+            import os
+            files = set(os.listdir(d))
+            assert {"optimizer_state.pt", "trainer_state.json"} <= files
+            assert ("lora_weights.pt" in files) == (rank_ > 0) and ("model.safetensors" in files) == (rank_ == 0)
+            eng2 = TrainEngine(cfg).initialize()
+            if rank_ > 0:
+                # base weights are not part of a LoRA checkpoint: start both from the same base
+                for a, b in zip(eng2.model.parameters(), eng.model.parameters()):
+                    if not a.requires_grad:
+                        a.data.copy_(b.data)
+            assert eng2.load_checkpoint(d)
+            assert eng2.step_count == 2 and eng2.optimizer.step_count == 2
+            a = eng.sft_step_tensors(ids, labels)
+            b = eng2.sft_step_tensors(ids, labels)
+            assert abs(a.loss - b.loss) < 1e-6 and abs(a.grad_norm - b.grad_norm) < 1e-5
+        assert not eng.load_checkpoint("/nonexistent/dir")
+
+
+def test_truncation_and_sampling_helpers():
+    eng = TrainEngine(TrainConfig(model_config=SMALL, max_seq_len=32, min_prompt_len=4))
+    p, r = eng._truncate_prompt_response(list(range(10)), list(range(10)))
+    assert (len(p), len(r)) == (10, 10)
+    p, r = eng._truncate_prompt_response(list(range(30)), list(range(10)))
+    assert (len(p), len(r)) == (22, 10)                         # prompt tail trimmed, response kept
+    p, r = eng._truncate_prompt_response(list(range(30)), list(range(40)))
+    assert (len(p), len(r)) == (4, 28)                          # response cut, min prompt kept
+    logits = torch.tensor([[0.0, 5.0, 1.0, -2.0]])
+    assert int(TrainEngine.sample_next_token(logits, 0.0, 1.0)) == 1
+    g = torch.Generator().manual_seed(0)
+    picks = {int(TrainEngine.sample_next_token(logits, 1.0, 0.5, g)) for _ in range(50)}
+    assert picks == {1}                                        # nucleus 0.5 keeps only the top token
+    assert math.isclose(sum(TrainEngine.group_advantages([1.0, 2.0, 3.0])), 0.0, abs_tol=1e-6)
