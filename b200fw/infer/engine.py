@@ -1,0 +1,505 @@
+"""InferenceEngine: continuous batching over the native paged model.
+
+Public surface of the reference engine (src/inference/engine.py:197-1693): ``initialize``,
+``add_request`` / ``step``, ``generate``, ``on_weights_updated``, ``has_pending``, ``get_stats``, with
+three modes — ``kv_cache`` (the product path: scheduler-driven chunked prefill + batched paged decode,
+prefix / radix block sharing, optional CUDA-graph decode, split-KV attention and speculative decoding),
+``eager`` (full re-forward per token, the oracle) and ``mock`` (scheduler + random tokens, no model).
+Per-request failures are isolated (the request is finished with what it has and its blocks are
+returned); a CUDA out-of-memory error clears caches and graphs and reports ``None`` for the batch.
+"""
+from __future__ import annotations
+
+import random
+import time
+from typing import Dict, List, Optional
+
+import torch
+
+from ..model import ModelConfig, ParallelTransformerModel, load_from_hf_checkpoint, read_hf_config
+from ..obs.logging import get_logger
+from .config import InferenceConfig
+from .graphs import CUDAGraphRunner
+from .kv_cache import BlockPool, KVCacheManager
+from .prefix_cache import PrefixCache
+from .radix_cache import RadixAttentionCache
+from .runner import ModelRunner
+from .scheduler import ContinuousBatchingScheduler, Request, SchedulerOutput
+from .spec import SpeculativeDecoder
+
+logger = get_logger("infer.engine")
+
+
+class InferenceEngine:
+    def __init__(self, config: InferenceConfig, model: Optional[ParallelTransformerModel] = None,
+                 draft_model: Optional[ParallelTransformerModel] = None):
+        self.config = config
+        self.model = model
+        self.draft_model = draft_model
+        self.scheduler: Optional[ContinuousBatchingScheduler] = None
+        self.pool: Optional[BlockPool] = None
+        self.kv: Optional[KVCacheManager] = None
+        self.runner: Optional[ModelRunner] = None
+        self.prefix_cache = None
+        self.graph_runner: Optional[CUDAGraphRunner] = None
+        self.spec: Optional[SpeculativeDecoder] = None
+        self.requests: Dict[str, Request] = {}
+        self.finished: Dict[str, Request] = {}
+        self.initialized = False
+        self.weights_version = 0
+        self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "cached_prefix_tokens": 0,
+                      "oom_recoveries": 0, "request_errors": 0, "graph_replays": 0, "spec_rounds": 0}
+        self._rng = random.Random(config.seed)
+        self._gen: Optional[torch.Generator] = None
+        self.device = torch.device("cpu")
+
+    # =================================================================================================
+    def initialize(self):
+        cfg = self.config
+        self.scheduler = ContinuousBatchingScheduler(cfg.max_num_batched_tokens, cfg.max_num_sequences,
+                                                     cfg.max_prefill_tokens, cfg.enable_chunked_prefill,
+                                                     cfg.chunk_size, cfg.adaptive_chunking)
+        if cfg.inference_mode == "mock":
+            self.pool = BlockPool(cfg.num_blocks, cfg.block_size, cfg.num_layers, cfg.num_kv_heads, cfg.head_dim,
+                                  allocate=False)
+            self.kv = KVCacheManager(self.pool, cfg.block_size)
+            self.initialized = True
+            return self
+        if self.model is None:
+            self.model = self._build_model()
+        p0 = next(self.model.parameters())
+        self.device = p0.device
+        if self.device.type == "cuda":
+            from .. import _native
+            _native.set_device(self.device.index or 0)
+        self._gen = torch.Generator(device=self.device).manual_seed(cfg.seed)
+        self.model.eval()
+        if cfg.inference_mode == "eager":
+            self.initialized = True
+            return self
+        mc = self.model.cfg
+        self.pool = BlockPool(cfg.num_blocks, cfg.block_size, mc.num_layers, mc.num_kv_heads, mc.head_dim,
+                              p0.dtype, self.device, cfg.kv_cache_dtype)
+        self.kv = KVCacheManager(self.pool, cfg.block_size)
+        self.runner = ModelRunner(self.model, self.pool, self.kv, cfg.attention_partition_size,
+                                  cfg.enable_partitioned_attention)
+        if cfg.enable_prefix_caching or cfg.use_radix_cache:
+            self.prefix_cache = RadixAttentionCache(cfg.block_size, cfg.radix_cache_max_nodes) if cfg.use_radix_cache \
+                else PrefixCache(cfg.block_size, cfg.max_cached_blocks)
+            self.prefix_cache.on_evict = lambda bid: self.pool.free(self.pool.get_block(bid))
+        if cfg.enable_cuda_graph and self.device.type == "cuda":
+            self.graph_runner = CUDAGraphRunner(cfg.max_num_sequences)
+        if cfg.speculative_enabled:
+            self._init_speculative()
+        self.initialized = True
+        return self
+
+    def _build_model(self) -> ParallelTransformerModel:
+        cfg = self.config
+        dev = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+        dtype = {"bfloat16": torch.bfloat16, "float32": torch.float32, "float16": torch.bfloat16}[cfg.dtype]
+        if dev.type == "cpu":
+            dtype = torch.float32
+        if cfg.model_path:
+            mc = read_hf_config(cfg.model_path)
+        else:
+            mc = ModelConfig(cfg.vocab_size, cfg.hidden_size, cfg.num_layers, cfg.num_heads, cfg.num_kv_heads,
+                             cfg.head_dim, cfg.intermediate_size or 3 * cfg.hidden_size)
+        model = ParallelTransformerModel(mc, dtype=dtype, device=dev)
+        model.init_weights(cfg.seed)
+        if cfg.model_path:
+            load_from_hf_checkpoint(model, cfg.model_path)
+        for p in model.parameters():
+            p.requires_grad_(False)
+        return model
+
+    def _init_speculative(self):
+        cfg, mc = self.config, self.model.cfg
+        if self.draft_model is None:
+            import copy
+            dc = copy.deepcopy(mc)
+            dc.num_layers = cfg.speculative_draft_layers
+            p0 = next(self.model.parameters())
+            self.draft_model = ParallelTransformerModel(dc, dtype=p0.dtype, device=p0.device)
+            self.draft_model.init_weights(cfg.seed + 1)
+            if cfg.speculative_draft_model_path:
+                load_from_hf_checkpoint(self.draft_model, cfg.speculative_draft_model_path)
+            for p in self.draft_model.parameters():
+                p.requires_grad_(False)
+        self.draft_model.eval()
+        dmc = self.draft_model.cfg
+        p0 = next(self.draft_model.parameters())
+        dpool = BlockPool(self.config.num_blocks, self.config.block_size, dmc.num_layers, dmc.num_kv_heads,
+                          dmc.head_dim, p0.dtype, self.device, "fp16")
+        dmgr = KVCacheManager(dpool, self.config.block_size)
+        self.draft_runner = ModelRunner(self.draft_model, dpool, dmgr)
+        self.spec = SpeculativeDecoder(self.runner, self.draft_runner, self.config.speculative_num_tokens)
+
+    # =================================================================================================
+    def add_request(self, request_id: str, prompt_tokens: List[int], max_tokens: int = 512,
+                    temperature: Optional[float] = None, top_p: Optional[float] = None) -> Request:
+        assert self.initialized, "call initialize() first"
+        r = Request(request_id, list(prompt_tokens), max_tokens,
+                    self.config.temperature if temperature is None else temperature,
+                    self.config.top_p if top_p is None else top_p, eos_token_id=self.config.eos_token_id)
+        self.requests[request_id] = r
+        self.scheduler.add_request(r)
+        return r
+
+    def has_pending(self) -> bool:
+        return self.scheduler.has_pending_requests()
+
+    # ---- one engine step ----------------------------------------------------------------------------------
+    def step(self) -> Dict[str, List[int]]:
+        """Schedule, run prefill chunks and one decode token for every running sequence.  Returns the
+        tokens produced in this step per request id."""
+        out = self.scheduler.schedule()
+        self.stats["steps"] += 1
+        for r in out.preempted_requests:
+            self._release(r, cache_prefix=False)
+        produced: Dict[str, List[int]] = {}
+        if out.is_empty:
+            return produced
+        try:
+            decode = [r for r in out.decode_requests if r.request_id not in out.prefill_tokens]
+            if out.prefill_requests:
+                self._execute_prefill(out, produced)
+            if decode:
+                self._execute_decode(decode, produced)
+        except torch.cuda.OutOfMemoryError:
+            self._recover_from_oom()
+            return produced
+        for rid in list(produced):
+            r = self.requests.get(rid)
+            if r is not None and r.is_finished:
+                self._finish(r)
+        return produced
+
+    # ---- prefill --------------------------------------------------------------------------------------------
+    def _admit(self, r: Request) -> bool:
+        """First chunk of a request: allocate its block table, sharing cached prefix blocks."""
+        shared: List[int] = []
+        if self.prefix_cache is not None and self.config.enable_prefix_reuse and r.num_computed_tokens == 0:
+            # never reuse the whole prompt: the last token must be computed to get logits
+            matched, ids = self.prefix_cache.match_prefix(r.prompt_tokens[:-1])
+            shared = ids
+            r.num_cached_tokens = matched
+        need = r.num_prompt_tokens
+        if not self.kv.can_allocate(need - len(shared) * self.config.block_size):
+            if self.prefix_cache is not None:
+                self.prefix_cache.evict_lru(self.kv.blocks_needed(need))
+        table = self.kv.allocate_for_sequence(r.request_id, need, shared)
+        if table is None:
+            if shared:
+                self.prefix_cache.release_blocks(shared)
+            return False
+        r.num_computed_tokens = r.num_cached_tokens
+        self.stats["cached_prefix_tokens"] += r.num_cached_tokens
+        return True
+
+    def _execute_prefill(self, out: SchedulerOutput, produced: Dict[str, List[int]]):
+        cfg = self.config
+        batch, starts, counts = [], [], []
+        for r in out.prefill_requests:
+            n = out.prefill_tokens[r.request_id]
+            if cfg.inference_mode == "mock":
+                r.num_computed_tokens += n
+                if r.is_prefill_complete:
+                    produced.setdefault(r.request_id, []).append(self._mock_token(r))
+                continue
+            try:
+                if r.request_id not in self.kv.tables and not self._admit(r):
+                    raise RuntimeError("KV cache exhausted")
+                n = min(n, r.num_prompt_tokens - r.num_computed_tokens)   # a cached prefix shortens the chunk
+                if n <= 0:
+                    n = 1
+                    r.num_computed_tokens = r.num_prompt_tokens - 1
+                batch.append(r)
+                starts.append(r.num_computed_tokens)
+                counts.append(n)
+            except Exception as e:  # noqa: BLE001 - isolate the failing request
+                self._fail(r, e)
+        if cfg.inference_mode == "mock" or not batch:
+            self.stats["prefill_tokens"] += out.num_prefill_tokens
+            return
+        ids = [t for r, s, n in zip(batch, starts, counts) for t in r.prompt_tokens[s:s + n]]
+        ctx = self.runner.prepare_prefill([r.request_id for r in batch], starts, counts)
+        tok = torch.tensor(ids, dtype=torch.long)
+        tok = tok.pin_memory().to(self.device, non_blocking=True) if self.device.type == "cuda" else tok
+        logits = self.runner.forward(tok, ctx)
+        self.stats["prefill_tokens"] += len(ids)
+        done = [i for i, (r, s, n) in enumerate(zip(batch, starts, counts)) if s + n >= r.num_prompt_tokens]
+        for r, n in zip(batch, counts):
+            r.num_computed_tokens += n
+            self.scheduler.promote_if_prefilled(r)
+        if done:
+            rows = torch.tensor(done, device=self.device)
+            new, lps = self._sample([batch[i] for i in done], logits.index_select(0, rows))
+            for i, t, lp in zip(done, new, lps):
+                r = batch[i]
+                r.output_tokens.append(t)
+                r.output_logprobs.append(lp)
+                produced.setdefault(r.request_id, []).append(t)
+                if self.spec is not None:
+                    self._draft_prefill(r)
+
+    def _draft_prefill(self, r: Request):
+        """Bring the draft model's cache level with the target's for a sequence that just finished
+        prefill (whole prompt in one go: the draft is tiny)."""
+        dm = self.draft_runner
+        if dm.mgr.allocate_for_sequence(r.request_id, r.num_prompt_tokens) is None:
+            raise RuntimeError("draft KV cache exhausted")
+        ctx = dm.prepare_prefill([r.request_id], [0], [r.num_prompt_tokens])
+        dm.forward(torch.tensor(r.prompt_tokens, dtype=torch.long, device=self.device), ctx)
+
+    # ---- decode ---------------------------------------------------------------------------------------------
+    def _execute_decode(self, reqs: List[Request], produced: Dict[str, List[int]]):
+        cfg = self.config
+        if cfg.inference_mode == "mock":
+            for r in reqs:
+                t = self._mock_token(r)
+                produced.setdefault(r.request_id, []).append(t)
+            self.stats["decode_tokens"] += len(reqs)
+            return
+        if self.spec is not None and self._use_speculation(reqs):
+            return self._execute_speculative(reqs, produced)
+        live = []
+        for r in reqs:
+            try:
+                if not self.kv.append_token(r.request_id):
+                    if self.prefix_cache is not None and self.prefix_cache.evict_lru(4) and \
+                            self.kv.append_token(r.request_id):
+                        pass
+                    else:
+                        raise RuntimeError("KV cache exhausted during decode")
+                live.append(r)
+            except Exception as e:  # noqa: BLE001
+                self._fail(r, e)
+        if not live:
+            return
+        last = torch.tensor([r.output_tokens[-1] for r in live], dtype=torch.long)
+        last = last.pin_memory().to(self.device, non_blocking=True) if self.device.type == "cuda" else last
+        logits = self._decode_forward(live, last)
+        new, lps = self._sample(live, logits[:len(live)])
+        for r, t, lp in zip(live, new, lps):
+            r.output_tokens.append(t)
+            r.output_logprobs.append(lp)
+            produced.setdefault(r.request_id, []).append(t)
+        self.stats["decode_tokens"] += len(live)
+
+    def _decode_forward(self, live: List[Request], last: torch.Tensor) -> torch.Tensor:
+        ids = [r.request_id for r in live]
+        gr = self.graph_runner
+        if gr is None:
+            return self.runner.forward(last, self.runner.prepare_decode(ids))
+        size = gr.padded_size(len(live))
+        width = self._graph_table_width()
+        ctx = self.runner.prepare_decode(ids, pad_to=size, max_blocks=width)
+        if ctx.block_tables.shape[1] > width or size is None:
+            return self.runner.forward(last, self.runner.prepare_decode(ids))   # longer than the graphs cover
+        plan = self._graph_split_plan(width)
+        if not gr.has(size):
+            def make(n):
+                return {"tokens": torch.zeros(n, dtype=torch.long, device=self.device),
+                        "positions": torch.zeros(n, dtype=torch.int32, device=self.device),
+                        "block_tables": torch.full((n, width), -1, dtype=torch.int32, device=self.device),
+                        "context_lens": torch.zeros(n, dtype=torch.int32, device=self.device),
+                        "segments": torch.tensor([[-1, 0, 0, 0]] * n, dtype=torch.int32, device=self.device)}
+
+            def fn(inp):
+                from .context import InferenceContext
+                c = InferenceContext(False, inp["tokens"].shape[0], inp["block_tables"], inp["context_lens"],
+                                     width * self.config.block_size, inp["segments"], positions=inp["positions"])
+                return self.runner.forward(inp["tokens"], c, split_plan=plan)
+            gr.capture(size, make, fn)
+        tokens = torch.zeros(size, dtype=torch.long, device=self.device)
+        tokens[:len(live)] = last
+        self.stats["graph_replays"] += 1
+        return gr.replay(size, {"tokens": tokens, "positions": ctx.positions, "block_tables": ctx.block_tables,
+                                "context_lens": ctx.context_lens, "segments": ctx.store_segments})
+
+    def _graph_table_width(self) -> int:
+        """Block-table width the graphs are captured for (grows in powers of two with the longest
+        sequence; growth invalidates the captured graphs)."""
+        longest = max((self.kv.get_seq_token_count(s) for s in self.kv.tables), default=1)
+        need = self.kv.blocks_needed(longest + 1)
+        w = getattr(self, "_graph_width", 0)
+        if need > w:
+            w = 64
+            while w < need:
+                w *= 2
+            if getattr(self, "_graph_width", 0) and self.graph_runner is not None:
+                self.graph_runner.invalidate()
+            self._graph_width = w
+        return self._graph_width
+
+    def _graph_split_plan(self, width: int):
+        if not self.config.enable_partitioned_attention:
+            return (0, 1)
+        part = max(64, self.config.attention_partition_size // 64 * 64)
+        cap = width * self.config.block_size
+        return (part, (cap + part - 1) // part) if cap > part else (0, 1)
+
+    # ---- speculative ------------------------------------------------------------------------------------------
+    def _use_speculation(self, reqs: List[Request]) -> bool:
+        temps = {r.temperature for r in reqs}
+        return len(temps) == 1 and all(r.request_id in self.draft_runner.mgr.tables for r in reqs) and \
+            (self.spec.steps < 4 or self.spec.acceptance_rate > 0.2)
+
+    def _execute_speculative(self, reqs: List[Request], produced: Dict[str, List[int]]):
+        ids = [r.request_id for r in reqs]
+        outs = self.spec.step(ids, [r.output_tokens[-1] for r in reqs], reqs[0].temperature, self._gen)
+        self.stats["spec_rounds"] += 1
+        for r, toks in zip(reqs, outs):
+            for t in toks:
+                if r.is_finished:
+                    break
+                r.output_tokens.append(t)
+                r.output_logprobs.append(0.0)
+                produced.setdefault(r.request_id, []).append(t)
+            self.stats["decode_tokens"] += len(toks)
+
+    # ---- sampling / mock ----------------------------------------------------------------------------------------
+    def _sample(self, reqs: List[Request], logits: torch.Tensor):
+        temp = torch.tensor([r.temperature for r in reqs], dtype=torch.float32, device=self.device)
+        topp = torch.tensor([r.top_p for r in reqs], dtype=torch.float32, device=self.device)
+        ids, lps = self.runner.sample(logits.contiguous(), temp, topp, self._gen, return_logprob=True)
+        return ids.tolist(), lps.tolist()
+
+    def _mock_token(self, r: Request) -> int:
+        lo = 3 if self.config.vocab_size > 4 else 0
+        t = self._rng.randrange(lo, self.config.vocab_size)
+        r.output_tokens.append(t)
+        return t
+
+    # ---- lifecycle ------------------------------------------------------------------------------------------------
+    def _release(self, r: Request, cache_prefix: bool = True):
+        if self.kv is None or r.request_id not in self.kv.tables:
+            return
+        table = self.kv.get_block_table(r.request_id)
+        if cache_prefix and self.prefix_cache is not None and r.is_prefill_complete:
+            for bid in self.prefix_cache.insert(r.prompt_tokens, table):
+                self.pool.share(bid)            # the cache holds its own reference
+        if self.prefix_cache is not None and r.num_cached_tokens:
+            self.prefix_cache.release_blocks(table[:r.num_cached_tokens // self.config.block_size])
+        self.kv.free_sequence(r.request_id)
+        if self.spec is not None:
+            self.draft_runner.mgr.free_sequence(r.request_id)
+
+    def _finish(self, r: Request):
+        self._release(r)
+        self.scheduler.finish_request(r.request_id)
+        self.finished[r.request_id] = r
+        self.requests.pop(r.request_id, None)
+
+    def _fail(self, r: Request, err: Exception):
+        logger.warning("request %s failed: %s", r.request_id, err)
+        self.stats["request_errors"] += 1
+        r.max_tokens = r.num_generated_tokens      # finished with what it has
+        self._finish(r)
+
+    def _recover_from_oom(self):
+        logger.warning("CUDA out of memory: clearing KV cache, prefix cache and graphs")
+        self.stats["oom_recoveries"] += 1
+        for r in self.scheduler.abort_all():
+            self.finished[r.request_id] = r
+            self.requests.pop(r.request_id, None)
+        if self.prefix_cache is not None:
+            self.prefix_cache.invalidate_all()
+        if self.kv is not None:
+            self.kv.reset()
+        if self.graph_runner is not None:
+            self.graph_runner.invalidate()
+        if torch.cuda.is_available():
+            torch.cuda.empty_cache()
+
+    # =================================================================================================
+    def generate(self, prompts_tokens: List[List[int]], max_tokens: int = 128, temperature: Optional[float] = None,
+                 top_p: Optional[float] = None, return_logprobs: bool = False):
+        """Generate for a batch of prompts; returns the output token lists in prompt order (``None`` for
+        a prompt whose request was dropped by an out-of-memory recovery)."""
+        assert self.initialized
+        if self.config.inference_mode == "eager":
+            return self._generate_eager(prompts_tokens, max_tokens, temperature, top_p)
+        base = f"gen{time.monotonic_ns()}"
+        rids = []
+        for i, p in enumerate(prompts_tokens):
+            rid = f"{base}-{i}"
+            self.add_request(rid, p, max_tokens, temperature, top_p)
+            rids.append(rid)
+        guard = 0
+        limit = (max_tokens + 8) * (len(prompts_tokens) + 8) + sum(len(p) for p in prompts_tokens)
+        while any(r in self.requests for r in rids):
+            self.step()
+            guard += 1
+            if guard > limit:
+                raise RuntimeError("generate() made no progress")
+        outs, lps = [], []
+        for rid in rids:
+            r = self.finished.pop(rid, None)
+            outs.append(None if r is None else list(r.output_tokens))
+            lps.append(None if r is None else list(r.output_logprobs))
+        return (outs, lps) if return_logprobs else outs
+
+    @torch.no_grad()
+    def _generate_eager(self, prompts_tokens, max_tokens, temperature, top_p):
+        """Full re-forward per token, no KV cache: slow, simple, and the oracle for the paged path."""
+        from ..ops import topp_sample
+        t = self.config.temperature if temperature is None else temperature
+        p = self.config.top_p if top_p is None else top_p
+        outs = []
+        for prompt in prompts_tokens:
+            seq, new = list(prompt), []
+            for _ in range(max_tokens):
+                ids = torch.tensor([seq], dtype=torch.long, device=self.device)
+                logits = self.model(ids)[:, -1, :].float().contiguous()
+                u = torch.rand(1, device=self.device, generator=self._gen)
+                tok = int(topp_sample(logits, torch.tensor([t], device=self.device),
+                                      torch.tensor([p], device=self.device), u))
+                new.append(tok)
+                seq.append(tok)
+                if self.config.eos_token_id is not None and tok == self.config.eos_token_id:
+                    break
+            outs.append(new)
+        return outs
+
+    # ---- weight updates --------------------------------------------------------------------------------------------
+    @torch.no_grad()
+    def load_weights(self, named_tensors) -> int:
+        """Copy HF-named tensors into the live model *in place* (captured graphs keep working)."""
+        from ..model.hf_io import hf_named_tensors
+        mine = dict(hf_named_tensors(self.model))
+        n = 0
+        for k, v in (named_tensors.items() if isinstance(named_tensors, dict) else named_tensors):
+            if k in mine:
+                mine[k].copy_(v.to(mine[k].dtype))
+                n += 1
+        self.on_weights_updated()
+        return n
+
+    def on_weights_updated(self):
+        """KV computed with the old weights is stale: drop the prefix cache and abort running requests.
+        Graphs are kept when weights were updated in place."""
+        self.weights_version += 1
+        if self.scheduler is not None:
+            for r in self.scheduler.abort_all():
+                self._release(r, cache_prefix=False)
+                self.finished[r.request_id] = r
+                self.requests.pop(r.request_id, None)
+        if self.prefix_cache is not None:
+            self.prefix_cache.invalidate_all()
+
+    def get_stats(self) -> dict:
+        s = dict(self.stats)
+        s["weights_version"] = self.weights_version
+        if self.scheduler is not None:
+            s["scheduler"] = self.scheduler.get_stats()
+        if self.kv is not None:
+            s["kv_cache"] = self.kv.get_stats()
+        if self.prefix_cache is not None:
+            s["prefix_cache"] = self.prefix_cache.get_stats()
+        if self.graph_runner is not None:
+            s["cuda_graphs"] = self.graph_runner.get_stats()
+        if self.spec is not None:
+            s["speculative"] = {"acceptance_rate": self.spec.acceptance_rate, "rounds": self.spec.steps}
+        return s

@@ -1,0 +1,141 @@
+"""ModelRunner: runs the framework's own Qwen3 weights over the paged KV cache.
+
+Where the reference wraps a Hugging Face model and moves KV between its ``DynamicCache`` and the pages
+with Python loops (src/inference/model_runner.py:192-433), this runner drives the native layers
+directly: fused QKV GEMM -> QK-norm + RoPE kernel -> KV-store kernel -> paged decode / variable-length
+prefill attention -> GEMMs with the residual in the epilogue.  It also builds the per-step metadata
+(store segments, block tables, cu_seqlens, gather slots) in pinned host memory.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from .. import ops
+from ..model.qwen3 import ParallelTransformerModel
+from .context import InferenceContext
+from .kv_cache import BlockPool, KVCacheManager
+
+
+class ModelRunner:
+    def __init__(self, model: ParallelTransformerModel, pool: BlockPool, manager: KVCacheManager,
+                 partition_size: int = 512, enable_partitioned: bool = False):
+        assert model.tp_size == 1, "the inference runner drives one GPU per engine instance"
+        self.model, self.pool, self.mgr = model, pool, manager
+        self.cfg = model.cfg
+        self.device = next(model.parameters()).device
+        self.dtype = next(model.parameters()).dtype
+        self.partition_size, self.enable_partitioned = partition_size, enable_partitioned
+        self.block_size = pool.block_size
+        self.forward_calls = 0
+
+    # ---- metadata ----------------------------------------------------------------------------------------
+    def _dev(self, data, dtype) -> torch.Tensor:
+        t = torch.tensor(data, dtype=dtype)
+        if self.device.type == "cuda":
+            return t.pin_memory().to(self.device, non_blocking=True)
+        return t
+
+    @staticmethod
+    def _segments(table: List[int], start: int, count: int, row0: int, bs: int) -> List[List[int]]:
+        """Split positions [start, start+count) of one sequence into per-block runs."""
+        segs, pos, row = [], start, row0
+        end = start + count
+        while pos < end:
+            off = pos % bs
+            n = min(bs - off, end - pos)
+            segs.append([table[pos // bs], row, n, off])
+            pos += n
+            row += n
+        return segs
+
+    def prepare_prefill(self, seq_ids: Sequence, starts: Sequence[int], counts: Sequence[int]) -> InferenceContext:
+        """Metadata for a batch of prefill chunks: sequence ``i`` computes positions
+        ``starts[i] .. starts[i]+counts[i]`` (its KV blocks must already cover them)."""
+        bs = self.block_size
+        cu_q, cu_k, segs, pos, slots, last = [0], [0], [], [], [], []
+        need_gather = any(s > 0 for s in starts)
+        for sid, st, n in zip(seq_ids, starts, counts):
+            table = self.mgr.get_block_table(sid)
+            segs += self._segments(table, st, n, cu_q[-1], bs)
+            pos += list(range(st, st + n))
+            if need_gather:
+                slots += [table[p // bs] * bs + p % bs for p in range(st + n)]
+            cu_q.append(cu_q[-1] + n)
+            cu_k.append(cu_k[-1] + (st + n if need_gather else n))
+            last.append(cu_q[-1] - 1)
+        return InferenceContext(
+            is_prefill=True, num_seqs=len(seq_ids), store_segments=self._dev(segs, torch.int32),
+            cu_seqlens_q=self._dev(cu_q, torch.int32), cu_seqlens_k=self._dev(cu_k, torch.int32),
+            max_seqlen_q=max(counts), total_q=cu_q[-1], total_k=cu_k[-1],
+            gather_slots=self._dev(slots, torch.int32) if need_gather else None,
+            positions=self._dev(pos, torch.int32), last_token_rows=self._dev(last, torch.long))
+
+    def prepare_decode(self, seq_ids: Sequence, pad_to: int = 0, max_blocks: int = 0) -> InferenceContext:
+        """Metadata for one decode step: every sequence's newest token sits at position ``len-1`` (its
+        slot must already be allocated with ``append_token``)."""
+        bs = self.block_size
+        n = len(seq_ids)
+        B = max(n, pad_to)
+        tables = [self.mgr.get_block_table(s) for s in seq_ids]
+        lens = [self.mgr.get_seq_token_count(s) for s in seq_ids]
+        width = max(max_blocks, max((len(t) for t in tables), default=1), 1)
+        bt = [t + [-1] * (width - len(t)) for t in tables] + [[-1] * width] * (B - n)
+        segs = [[t[(l - 1) // bs], i, 1, (l - 1) % bs] for i, (t, l) in enumerate(zip(tables, lens))]
+        segs += [[-1, 0, 0, 0]] * (B - n)
+        return InferenceContext(
+            is_prefill=False, num_seqs=B, block_tables=self._dev(bt, torch.int32),
+            context_lens=self._dev(lens + [0] * (B - n), torch.int32), max_context_len=max(lens, default=0),
+            store_segments=self._dev(segs, torch.int32),
+            positions=self._dev([l - 1 for l in lens] + [0] * (B - n), torch.int32))
+
+    # ---- forward -----------------------------------------------------------------------------------------
+    def _split_plan(self, ctx: InferenceContext) -> Tuple[int, int]:
+        if not self.enable_partitioned or ctx.max_context_len <= self.partition_size:
+            return 0, 1
+        part = max(64, self.partition_size // 64 * 64)
+        return part, (ctx.max_context_len + part - 1) // part
+
+    @torch.no_grad()
+    def forward(self, token_ids: torch.Tensor, ctx: InferenceContext, all_rows: bool = False,
+                split_plan: Optional[Tuple[int, int]] = None) -> torch.Tensor:
+        """Token ids ``[T]`` -> logits ``[num_seqs, V]`` of each sequence's last row (or of every row)."""
+        m, cfg = self.model, self.cfg
+        self.forward_calls += 1
+        Hq, Hkv, D = cfg.num_heads, cfg.num_kv_heads, cfg.head_dim
+        cos, sin = ops.rope_tables(cfg.max_position_embeddings, D, cfg.rope_theta, self.device)
+        part, nsplit = split_plan if split_plan is not None else (self._split_plan(ctx) if not ctx.is_prefill else (0, 1))
+        h = ops.embedding(token_ids, m.embed_tokens)
+        for li, layer in enumerate(m.layers):
+            att_mod = layer.self_attn
+            x = ops.rmsnorm(h, layer.input_layernorm.weight, cfg.rms_norm_eps)
+            qkv = ops.linear(x, att_mod.qkv_proj.weight)
+            q, k, v = ops.qknorm_rope(qkv, att_mod.q_norm.weight, att_mod.k_norm.weight, ctx.positions, cos, sin,
+                                      Hq, Hkv, D, cfg.rms_norm_eps)
+            kc, vc = self.pool.layer_kv(li)
+            ks, vs = self.pool.layer_scales(li)
+            ops.kv_store(k, v, kc, vc, ctx.store_segments, ks, vs)
+            if ctx.is_prefill:
+                if ctx.gather_slots is not None:
+                    K, V = ops.kv_gather(kc, vc, ctx.gather_slots, self.dtype, ks, vs)
+                else:
+                    K, V = k, v
+                att = ops.varlen_attention(q, K, V, ctx.cu_seqlens_q, ctx.cu_seqlens_k, ctx.max_seqlen_q, Hq, Hkv)
+            else:
+                att = ops.paged_decode_attention(q, kc, vc, ctx.block_tables, ctx.context_lens, Hq,
+                                                 k_scale=ks, v_scale=vs, partition=part, nsplit=nsplit)
+            h = ops.linear(att, att_mod.o_proj.weight, h)
+            x = ops.rmsnorm(h, layer.post_attention_layernorm.weight, cfg.rms_norm_eps)
+            gu = ops.linear(x, layer.mlp.gate_up_proj.weight)
+            h = ops.linear(ops.swiglu(gu), layer.mlp.down_proj.weight, h)
+        if ctx.is_prefill and not all_rows:
+            h = h.index_select(0, ctx.last_token_rows)
+        h = ops.rmsnorm(h.contiguous(), m.norm.weight, cfg.rms_norm_eps)
+        return ops.linear(h, m.lm_head_weight)
+
+    # ---- sampling ------------------------------------------------------------------------------------------
+    def sample(self, logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor,
+               generator: Optional[torch.Generator] = None, return_logprob: bool = False):
+        u = torch.rand(logits.shape[0], device=logits.device, generator=generator)
+        return ops.topp_sample(logits, temperature, top_p, u, return_logprob)

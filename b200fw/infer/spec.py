@@ -1,0 +1,136 @@
+"""Speculative decoding with a native draft model.
+
+Roles as in the reference (src/inference/speculative.py:44-533): the draft proposes ``K`` tokens, the
+target scores ``K+1`` positions in ONE forward, acceptance is either greedy (longest matching prefix
+plus the target's next token) or sampling-aware (accept with ``min(1, p_t/p_d)``, resample the first
+rejection from the normalised residual ``max(0, p_t - p_d)``), and a sliding window tracks the
+acceptance rate.  Both models run over paged KV caches; the verify pass is a variable-length prefill
+chunk of ``K+1`` tokens per sequence, and rejected positions are trimmed from both caches.
+"""
+from __future__ import annotations
+
+from collections import deque
+from typing import Deque, List, Optional, Tuple
+
+import torch
+
+
+class AcceptanceTracker:
+    def __init__(self, window: int = 100):
+        self.events: Deque[Tuple[int, int]] = deque(maxlen=window)
+
+    def record(self, accepted: int, proposed: int):
+        self.events.append((accepted, proposed))
+
+    @property
+    def rate(self) -> float:
+        p = sum(e[1] for e in self.events)
+        return sum(e[0] for e in self.events) / p if p else 1.0
+
+
+def verify_greedy(draft_tokens: torch.Tensor, target_logits: torch.Tensor) -> Tuple[int, int]:
+    """``draft_tokens [K]``, ``target_logits [K+1, V]`` -> (accepted count, next token)."""
+    pred = target_logits.argmax(-1)
+    K = draft_tokens.numel()
+    match = (pred[:K] == draft_tokens).long()
+    n = int(match.cumprod(0).sum())
+    return n, int(pred[n])
+
+
+def verify_sampling(draft_tokens: torch.Tensor, draft_probs: torch.Tensor, target_logits: torch.Tensor,
+                    temperature: float, generator: Optional[torch.Generator] = None) -> Tuple[int, int]:
+    """Sampling-aware acceptance that preserves the target distribution.  ``draft_probs [K, V]`` are the
+    distributions the draft sampled from; returns (accepted count, next token)."""
+    K = draft_tokens.numel()
+    pt = torch.softmax(target_logits.float() / max(temperature, 1e-6), -1)
+    u = torch.rand(K, device=pt.device, generator=generator)
+    for i in range(K):
+        tok = int(draft_tokens[i])
+        ratio = pt[i, tok] / draft_probs[i, tok].clamp(min=1e-20)
+        if float(u[i]) < float(ratio.clamp(max=1.0)):
+            continue
+        resid = (pt[i] - draft_probs[i]).clamp(min=0)
+        s = resid.sum()
+        resid = resid / s if float(s) > 0 else pt[i]
+        return i, int(torch.multinomial(resid, 1, generator=generator))
+    return K, int(torch.multinomial(pt[K], 1, generator=generator))
+
+
+class SpeculativeDecoder:
+    """Drives draft + target runners for a batch of sequences that already finished prefill in both
+    caches.  ``target`` / ``draft`` are :class:`ModelRunner` objects with their own block managers."""
+
+    def __init__(self, target, draft, num_tokens: int = 4, window: int = 100):
+        self.target, self.draft, self.K = target, draft, num_tokens
+        self.tracker = AcceptanceTracker(window)
+        self.steps = 0
+
+    @property
+    def acceptance_rate(self) -> float:
+        return self.tracker.rate
+
+    def _draft_propose(self, seq_ids: List, last_tokens: List[int], temperature: float,
+                       generator=None) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+        """K draft decode steps for all sequences.  Returns tokens ``[B, K]`` and, when sampling, the
+        draft distributions ``[B, K, V]``."""
+        dev = self.draft.device
+        B = len(seq_ids)
+        cur = torch.tensor(last_tokens, dtype=torch.long, device=dev)
+        toks, probs = [], []
+        for _ in range(self.K):
+            for s in seq_ids:
+                if not self.draft.mgr.append_token(s):
+                    raise RuntimeError("draft KV cache exhausted")
+            ctx = self.draft.prepare_decode(seq_ids)
+            logits = self.draft.forward(cur, ctx)
+            if temperature <= 0:
+                cur = logits.argmax(-1)
+            else:
+                p = torch.softmax(logits.float() / temperature, -1)
+                cur = torch.multinomial(p, 1, generator=generator).squeeze(-1)
+                probs.append(p)
+            toks.append(cur)
+        return torch.stack(toks, 1), (torch.stack(probs, 1) if probs else None)
+
+    def step(self, seq_ids: List, last_tokens: List[int], temperature: float = 0.0,
+             generator: Optional[torch.Generator] = None) -> List[List[int]]:
+        """One speculative round.  ``last_tokens[i]`` is the newest token of sequence ``i`` that is not
+        in either cache yet.  Returns the new tokens per sequence (1 .. K+1 each) and leaves both caches
+        holding exactly the accepted history (without the final returned token)."""
+        K = self.K
+        tgt, dr = self.target, self.draft
+        base = [tgt.mgr.get_seq_token_count(s) for s in seq_ids]
+        d_tokens, d_probs = self._draft_propose(seq_ids, last_tokens, temperature, generator)
+        # target verifies [last, d_0 .. d_{K-1}] in one variable-length chunk per sequence
+        for s, b in zip(seq_ids, base):
+            if not tgt.mgr.ensure_capacity(s, b + K + 1):
+                raise RuntimeError("target KV cache exhausted")
+            tgt.mgr.set_num_tokens(s, b + K + 1)
+        ctx = tgt.prepare_prefill(seq_ids, base, [K + 1] * len(seq_ids))
+        ids = torch.cat([torch.tensor(last_tokens, dtype=torch.long, device=tgt.device)[:, None], d_tokens], 1)
+        logits = tgt.forward(ids.reshape(-1), ctx, all_rows=True).reshape(len(seq_ids), K + 1, -1)
+        out: List[List[int]] = []
+        catch_up: List[int] = []
+        for i, s in enumerate(seq_ids):
+            if temperature <= 0:
+                n, nxt = verify_greedy(d_tokens[i], logits[i])
+            else:
+                n, nxt = verify_sampling(d_tokens[i], d_probs[i], logits[i], temperature, generator)
+            self.tracker.record(n, K)
+            out.append(d_tokens[i, :n].tolist() + [nxt])
+            # both caches must end up holding history + last + the n accepted drafts; the returned
+            # final token is the next round's `last` and is not stored yet
+            tgt.mgr.trim(s, base[i] + 1 + n)
+            if n < K:
+                dr.mgr.trim(s, base[i] + 1 + n)
+            else:
+                catch_up.append(i)      # the draft produced d_{K-1} but never consumed it
+        if catch_up:
+            ids_c = [seq_ids[i] for i in catch_up]
+            for s in ids_c:
+                if not dr.mgr.append_token(s):
+                    raise RuntimeError("draft KV cache exhausted")
+            ctx_c = dr.prepare_decode(ids_c)
+            dr.forward(d_tokens[catch_up, K - 1].contiguous(), ctx_c)
+        self.steps += 1
+        return out

@@ -32,7 +32,8 @@ struct AttnFwdSmem {
 __global__ void __launch_bounds__(AT_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, __nv_bfloat16* __restrict__ out,
-                float* __restrict__ lse_out, int S, int Hq, int Hkv, float scale, int* status) {
+                float* __restrict__ lse_out, int S, int Hq, int Hkv, float scale,
+                const int* __restrict__ cu_q, const int* __restrict__ cu_k, int total_q, int* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -49,12 +50,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int num_q_tiles = (S + 127) / 128;
-  const int qt = num_q_tiles - 1 - blockIdx.x;  // heaviest tiles first
+  // Fixed-length mode (cu_q == nullptr): every sequence has S query and S key tokens.  Variable
+  // length mode: sequence b owns query rows cu_q[b]..cu_q[b+1] and key rows cu_k[b]..cu_k[b+1]; its
+  // queries are the LAST q_len positions of its kv_len keys (chunked prefill / speculative verify), so
+  // query i sees keys 0..(kv_len - q_len + i).
   const int head = blockIdx.y, batch = blockIdx.z;
+  const int q_begin = cu_q ? cu_q[batch] : batch * S;
+  const int q_len = cu_q ? cu_q[batch + 1] - q_begin : S;
+  const int k_begin = cu_k ? cu_k[batch] : batch * S;
+  const int kv_len = cu_k ? cu_k[batch + 1] - k_begin : S;
+  const int kv_off = kv_len - q_len;
+  const int num_q_tiles = (q_len + 127) / 128;
+  const int qt = num_q_tiles - 1 - static_cast<int>(blockIdx.x);  // heaviest tiles first
+  const bool active = qt >= 0 && q_len > 0;
   const int kvh = head / (Hq / Hkv);
-  const int n_kv = qt + 1;  // causal: kv tiles 0..qt
-  const int row0 = batch * S + qt * 128;
+  const int last_key = min(kv_len, kv_off + (qt + 1) * 128);  // exclusive
+  const int n_kv = active ? (last_key + 127) / 128 : 0;
+  const int row0 = q_begin + qt * 128;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -85,14 +97,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const uint32_t tmem_O = tmem_base + 256;  // 128 columns
 
   if (warp == 0) {
-    if (lane == 0) {
+    if (lane == 0 && active) {
       mbar_expect_tx(q_full, AT_TILE_BYTES);
       tma_load_2d(smem + AttnFwdSmem::Q, &tmQ, q_full, head * 128, row0);
       tma_load_2d(smem + AttnFwdSmem::Q + AT_HALF_BYTES, &tmQ, q_full, head * 128 + 64, row0);
       for (int j = 0; j < n_kv; ++j) {
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        const int krow = batch * S + j * 128;
+        const int krow = k_begin + j * 128;
         if (!mbar_wait(&k_empty[st], ph ^ 1, status, ERR_ATTN_WAIT)) break;
         uint8_t* sK = smem + AttnFwdSmem::K + st * AT_TILE_BYTES;
         mbar_expect_tx(&k_full[st], AT_TILE_BYTES);
@@ -106,7 +118,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    if (lane == 0 && active) {
       constexpr uint32_t idesc_s = make_idesc_f16(1, 128, 128, 0, 0);
       constexpr uint32_t idesc_pv = make_idesc_f16(1, 128, 128, 0, 1);
       const uint32_t q_base = smem_u32(smem + AttnFwdSmem::Q);
@@ -161,7 +173,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   } else {
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;        // query row inside the tile
-    const int q_pos = qt * 128 + r;           // position inside the sequence
+    const int q_idx = qt * 128 + r;           // index among this sequence's queries
+    const int q_pos = kv_off + q_idx;         // last key this query may see
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     const float sl2 = scale * 1.4426950408889634f;
     float m_used = -INFINITY, l = 0.f;
@@ -181,12 +194,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
       tc_fence_before();
       mbar_arrive(&s_empty[j & 1]);
-      const bool need_mask = (j == qt) || ((j + 1) * 128 > S);
+      const bool need_mask = ((j + 1) * 128 > kv_off + qt * 128 + 1) || ((j + 1) * 128 > kv_len);
       if (need_mask) {
         const int col0 = j * 128;
 #pragma unroll
         for (int i = 0; i < 128; ++i)
-          if (col0 + i > q_pos || col0 + i >= S) s[i] = -INFINITY;
+          if (col0 + i > q_pos || col0 + i >= kv_len) s[i] = -INFINITY;
       }
       float mx = s[0];
 #pragma unroll
@@ -240,10 +253,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_before();
       mbar_arrive(p_full);
     }
-    if (ok && mbar_wait(pv_done, (n_kv - 1) & 1, status, ERR_ATTN_WAIT)) {
+    if (ok && active && mbar_wait(pv_done, (n_kv - 1) & 1, status, ERR_ATTN_WAIT)) {
       tc_fence_after();
       const float inv = 1.f / l;
-      const bool in_range = q_pos < S;
+      const bool in_range = q_idx < q_len;
       __nv_bfloat16* orow = out + (static_cast<size_t>(row0 + r) * Hq + head) * 128;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
@@ -263,7 +276,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
       }
       if (in_range && lse_out)
-        lse_out[static_cast<size_t>(head) * (gridDim.z * S) + row0 + r] = m_used * scale + __logf(l);
+        lse_out[static_cast<size_t>(head) * total_q + row0 + r] = m_used * scale + __logf(l);
     }
   }
 
@@ -284,15 +297,30 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
 using namespace b2;
 
-// q [B*S, Hq*128], k [B*S, Hkv*128] contiguous; v rows have stride ld_v elements.
+// q [Tq, Hq*128], out [Tq, Hq*128]; k rows have stride ld_k, v rows stride ld_v elements.
+// Fixed length: cu_q = cu_k = nullptr, Tq = Tk = B*S.  Variable length: cu_q / cu_k are int32 [B+1]
+// device arrays of row offsets, max_q = longest query run, total_q / total_k = row counts.
+B2_EXPORT int b2_attn_fwd_varlen(const void* q, const void* k, const void* v, void* out, float* lse, int B,
+                                 int S, int Hq, int Hkv, int head_dim, int ld_k, int ld_v, float scale,
+                                 const int* cu_q, const int* cu_k, int max_q, int total_q, int total_k,
+                                 void* stream_);
+
 B2_EXPORT int b2_attn_fwd(const void* q, const void* k, const void* v, void* out, float* lse, int B, int S,
                           int Hq, int Hkv, int head_dim, int ld_v, float scale, void* stream_) {
+  return b2_attn_fwd_varlen(q, k, v, out, lse, B, S, Hq, Hkv, head_dim, Hkv * 128, ld_v, scale, nullptr,
+                            nullptr, S, B * S, B * S, stream_);
+}
+
+B2_EXPORT int b2_attn_fwd_varlen(const void* q, const void* k, const void* v, void* out, float* lse, int B,
+                                 int S, int Hq, int Hkv, int head_dim, int ld_k, int ld_v, float scale,
+                                 const int* cu_q, const int* cu_k, int max_q, int total_q, int total_k,
+                                 void* stream_) {
   b2::ensure_thread_context();
-  if (head_dim != 128 || Hq % Hkv != 0 || (ld_v % 8) != 0) {
-    set_error("attn_fwd: head_dim must be 128, Hq %% Hkv == 0, ld_v %% 8 == 0");
+  if (head_dim != 128 || Hq % Hkv != 0 || (ld_v % 8) != 0 || (ld_k % 8) != 0) {
+    set_error("attn_fwd: head_dim must be 128, Hq %% Hkv == 0, ld_k / ld_v %% 8 == 0");
     return 10;
   }
-  if (B <= 0 || S <= 0) return 0;
+  if (B <= 0 || max_q <= 0 || total_q <= 0) return 0;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   static bool configured[64] = {false};
   int dev = 0;
@@ -305,16 +333,15 @@ B2_EXPORT int b2_attn_fwd(const void* q, const void* k, const void* v, void* out
     }
     configured[dev] = true;
   }
-  const uint64_t T = static_cast<uint64_t>(B) * S;
-  const CUtensorMap* tq = tensor_map_2d_bf16(q, T, static_cast<uint64_t>(Hq) * 128, static_cast<uint64_t>(Hq) * 128, 128, 64);
-  const CUtensorMap* tk = tensor_map_2d_bf16(k, T, static_cast<uint64_t>(Hkv) * 128, static_cast<uint64_t>(Hkv) * 128, 128, 64);
-  const CUtensorMap* tv = tensor_map_2d_bf16(v, T, static_cast<uint64_t>(Hkv) * 128, ld_v, 128, 64);
+  const CUtensorMap* tq = tensor_map_2d_bf16(q, total_q, static_cast<uint64_t>(Hq) * 128, static_cast<uint64_t>(Hq) * 128, 128, 64);
+  const CUtensorMap* tk = tensor_map_2d_bf16(k, total_k, static_cast<uint64_t>(Hkv) * 128, ld_k, 128, 64);
+  const CUtensorMap* tv = tensor_map_2d_bf16(v, total_k, static_cast<uint64_t>(Hkv) * 128, ld_v, 128, 64);
   if (!tq || !tk || !tv) return 2;
   int* status = status_ptr();
   if (!status) return 3;
-  dim3 grid((S + 127) / 128, Hq, B);
+  dim3 grid((max_q + 127) / 128, Hq, B);
   attn_fwd_kernel<<<grid, AT_THREADS, AttnFwdSmem::TOTAL, stream>>>(
-      *tq, *tk, *tv, static_cast<__nv_bfloat16*>(out), lse, S, Hq, Hkv, scale, status);
+      *tq, *tk, *tv, static_cast<__nv_bfloat16*>(out), lse, S, Hq, Hkv, scale, cu_q, cu_k, total_q, status);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_error("attn_fwd launch failed: %s", cudaGetErrorString(e));

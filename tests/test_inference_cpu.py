@@ -1,0 +1,181 @@
+"""Inference runtime on CPU: KV manager, prefix / radix caches, scheduler policy, mock engine, and the
+native paged engine against the eager (full re-forward) oracle for every feature switch."""
+import pytest
+import torch
+
+from b200fw.infer import (BlockPool, ContinuousBatchingScheduler, InferenceConfig, InferenceEngine, KVCacheManager,
+                          PrefixCache, RadixAttentionCache, Request, verify_greedy, verify_sampling)
+from b200fw.model import ModelConfig, ParallelTransformerModel
+
+MC = ModelConfig(vocab_size=128, hidden_size=32, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=8,
+                 intermediate_size=48, max_position_embeddings=256, tie_word_embeddings=True)
+PROMPTS = [list(range(5, 23)), [3, 4, 5], [9] * 40, list(range(5, 21)) + [77, 78]]
+
+
+@pytest.fixture(scope="module")
+def model():
+    torch.manual_seed(0)
+    m = ParallelTransformerModel(MC)
+    m.init_weights(0, std=0.3)
+    return m
+
+
+def _engine(model, **kw):
+    base = dict(num_blocks=64, inference_mode="kv_cache", temperature=0.0, chunk_size=16, max_prefill_tokens=32,
+                eos_token_id=None)
+    base.update(kw)
+    return InferenceEngine(InferenceConfig.from_model_config(MC, **base), model).initialize()
+
+
+@pytest.fixture(scope="module")
+def oracle(model):
+    cfg = InferenceConfig.from_model_config(MC, inference_mode="eager", temperature=0.0, eos_token_id=None)
+    return InferenceEngine(cfg, model).initialize().generate(PROMPTS, max_tokens=10)
+
+
+def test_kv_manager_allocation_rollback_and_double_free():
+    pool = BlockPool(8, 16, 1, 1, 8, torch.float32, "cpu")
+    mgr = KVCacheManager(pool, 16)
+    assert mgr.can_allocate(16 * 7) and not mgr.can_allocate(16 * 8)        # one spare block is kept
+    t = mgr.allocate_for_sequence("a", 40)
+    assert t.num_blocks == 3 and pool.num_free_blocks == 5
+    assert mgr.allocate_for_sequence("b", 16 * 6) is None                     # rolled back completely
+    assert pool.num_free_blocks == 5 and mgr.alloc_failures == 1
+    for _ in range(8):
+        assert mgr.append_token("a")
+    assert mgr.get_seq_token_count("a") == 48 and t.num_blocks == 3
+    assert mgr.append_token("a") and t.num_blocks == 4
+    mgr.trim("a", 17)
+    assert t.num_blocks == 2 and mgr.get_seq_token_count("a") == 17
+    blk = t.blocks[0]
+    mgr.free_sequence("a")
+    assert pool.num_free_blocks == 8
+    pool.free(blk)
+    assert pool.double_free_count == 1 and pool.num_free_blocks == 8
+    shared = mgr.allocate_for_sequence("c", 32)
+    ids = shared.get_physical_block_ids()
+    mgr.allocate_for_sequence("d", 48, shared_block_ids=ids)
+    assert pool.get_block(ids[0]).ref_count == 2
+    mgr.free_sequence("c")
+    assert pool.get_block(ids[0]).ref_count == 1 and ids[0] not in pool.free_list
+
+
+@pytest.mark.parametrize("cls", [PrefixCache, RadixAttentionCache])
+def test_prefix_caches(cls):
+    c = cls(block_size=4) if cls is RadixAttentionCache else cls(block_size=4, max_cached_blocks=3)
+    toks = list(range(1, 14))
+    assert c.match_prefix(toks) == (0, [])
+    assert c.insert(toks, [10, 11, 12]) == [10, 11, 12]
+    assert c.match_prefix(toks) == (12, [10, 11, 12])
+    assert c.match_prefix(toks[:8] + [99] * 5) == (8, [10, 11])
+    assert c.match_prefix([1, 2, 3, 5] + toks[4:]) == (0, [])
+    assert 0 < c.hit_rate < 1
+    evicted = []
+    c.on_evict = evicted.append
+    assert c.evict_lru(1) == []                    # everything is referenced by the matches above
+    c.release_blocks([10, 11, 12])
+    c.release_blocks([10, 11])
+    got = c.evict_lru(1)
+    assert len(got) == 1 and evicted == got
+    assert set(c.invalidate_all()) | set(got) == {10, 11, 12} and c.size == 0
+
+
+def test_scheduler_decode_first_chunking_and_preemption():
+    s = ContinuousBatchingScheduler(max_num_batched_tokens=64, max_num_sequences=3, max_prefill_tokens=48,
+                                    chunk_size=16, enable_adaptive_chunking=True)
+    for i, n in enumerate([40, 10, 30, 5]):
+        s.add_request(Request(f"r{i}", list(range(n)), arrival_time=float(i)))
+    out = s.schedule()
+    # idle: chunk doubles to 32; 32 + 10 fit the 48-token prefill budget, the third request does not fit
+    # the remaining 6 tokens and only the FIRST request of a step may take a partial chunk
+    assert out.chunk_size == 32 and [out.prefill_tokens[r.request_id] for r in out.prefill_requests] == [32, 10]
+    assert [r.request_id for r in s.running_queue] == ["r1"]
+    for r in out.prefill_requests:
+        r.num_computed_tokens += out.prefill_tokens[r.request_id]
+    out = s.schedule()
+    assert [r.request_id for r in out.decode_requests] == ["r1"]
+    assert out.prefill_tokens == {"r0": 8, "r2": 16}            # sequence slots: 3 - 1 running = 2 new
+    for r in out.prefill_requests:
+        r.num_computed_tokens += out.prefill_tokens[r.request_id]
+    assert [r.request_id for r in s.running_queue] == ["r1", "r0"]
+    # too many running sequences -> the latest arrival is preempted and returns to the queue head
+    s.max_num_sequences = 1
+    out = s.schedule()
+    assert [r.request_id for r in out.preempted_requests] == ["r1"] and s.waiting_queue[0].request_id == "r1"
+    assert s.waiting_queue[0].num_computed_tokens == 0 and s.total_preempted == 1
+    s.finish_request("r0")
+    assert s.total_finished == 1 and s.has_pending_requests()
+
+
+def test_mock_engine_lifecycle():
+    e = InferenceEngine(InferenceConfig(inference_mode="mock", vocab_size=1000, max_prefill_tokens=64)).initialize()
+    outs = e.generate([[1, 2, 3], [4] * 100], max_tokens=7)
+    assert [len(o) for o in outs] == [7, 7] and all(3 <= t < 1000 for o in outs for t in o)
+    e.add_request("x", [1] * 10, max_tokens=50)
+    e.step()
+    assert e.has_pending()
+    e.on_weights_updated()
+    assert not e.has_pending() and e.get_stats()["weights_version"] == 1
+    k = e.generate([[7, 8]] * 4, max_tokens=3)           # K samples of one prompt
+    assert len(k) == 4
+
+
+@pytest.mark.parametrize("kw", [
+    {}, {"enable_prefix_caching": True}, {"use_radix_cache": True},
+    {"enable_partitioned_attention": True, "attention_partition_size": 64},
+    {"enable_chunked_prefill": False, "max_prefill_tokens": 256},
+    {"speculative_enabled": True, "speculative_num_tokens": 3, "speculative_draft_layers": 1},
+    {"max_num_sequences": 2},
+])
+def test_paged_engine_matches_eager_oracle(model, oracle, kw):
+    e = _engine(model, **kw)
+    assert e.generate(PROMPTS, max_tokens=10) == oracle
+    assert e.generate(PROMPTS, max_tokens=10) == oracle                      # second pass hits the caches
+    st = e.get_stats()
+    if "prefix_cache" in st:
+        assert st["cached_prefix_tokens"] > 0 and st["prefix_cache"]["hits"] > 0
+    held = st.get("prefix_cache", {}).get("size", 0)
+    assert st["kv_cache"]["used_blocks"] == held and st["kv_cache"]["double_frees"] == 0
+
+
+def test_fp8_kv_cache_close_to_oracle(model, oracle):
+    out = _engine(model, kv_cache_dtype="fp8").generate(PROMPTS, max_tokens=10)
+    same = sum(a == b for x, y in zip(out, oracle) for a, b in zip(x, y))
+    assert same >= 0.6 * sum(len(o) for o in oracle)
+
+
+def test_kv_exhaustion_is_isolated_per_request(model):
+    e = _engine(model, num_blocks=4)
+    outs = e.generate([[1] * 30, [2] * 200], max_tokens=4)
+    assert len(outs[0]) == 4 and outs[1] == [] and e.get_stats()["request_errors"] == 1
+    assert e.get_stats()["kv_cache"]["used_blocks"] == 0
+
+
+def test_weight_update_in_place_changes_outputs(model, oracle):
+    import copy
+    m2 = ParallelTransformerModel(MC)
+    m2.load_state_dict(copy.deepcopy(model.state_dict()))
+    e = _engine(m2, enable_prefix_caching=True)
+    assert e.generate(PROMPTS, max_tokens=10) == oracle
+    from b200fw.model.hf_io import hf_named_tensors
+    new = {k: v + 0.05 * torch.randn_like(v) for k, v in hf_named_tensors(m2)}
+    assert e.load_weights(new) == len(new)
+    assert e.get_stats()["prefix_cache"]["size"] == 0 and e.weights_version == 1
+    assert e.generate(PROMPTS, max_tokens=10) != oracle
+
+
+def test_speculative_verification_rules():
+    logits = torch.full((4, 10), -5.0)
+    for i, t in enumerate([3, 4, 7, 1]):
+        logits[i, t] = 5.0
+    assert verify_greedy(torch.tensor([3, 4, 5]), logits) == (2, 7)
+    assert verify_greedy(torch.tensor([3, 4, 7]), logits) == (3, 1)
+    assert verify_greedy(torch.tensor([9, 4, 7]), logits) == (0, 3)
+    g = torch.Generator().manual_seed(0)
+    probs = torch.softmax(logits[:3], -1)
+    n, nxt = verify_sampling(torch.tensor([3, 4, 7]), probs, logits, 1.0, g)     # draft == target: all accepted
+    assert n == 3 and 0 <= nxt < 10
+    wrong = torch.zeros(3, 10)
+    wrong[:, 0] = 1.0
+    n, nxt = verify_sampling(torch.tensor([0, 0, 0]), wrong, logits, 1.0, g)     # p_t(0) ~ 0: reject at once
+    assert n == 0 and nxt == 3
