@@ -1,0 +1,531 @@
+"""Colocate orchestrator: SFT or GRPO iterations with rollout, reward, training and weight sync on the
+same set of GPUs.
+
+State machine and artefacts follow the reference (src/orchestrator/colocate_orchestrator.py:43-1848):
+``INIT -> [INFERRING -> REWARDING -> TRAINING -> SLEEPING -> SYNCING]* -> DONE`` (``ERROR`` on a failed
+iteration, after which the loop carries on), per-iteration JSONL rows, ``run_summary.json``,
+``config_snapshot.json``, ``loss_curve.csv``, memory timeline / report, optional TensorBoard scalars,
+``iter_N`` / ``latest`` / ``final`` checkpoints, MFU sampling.  Rollouts run in the native paged
+engine of this process (the reference's "custom" backend generates with the trainer model, one
+sequence at a time and without a KV cache); the vLLM server backend is kept behind the same interface.
+With ``async_pipeline`` the rollout for iteration N+1 overlaps the training of iteration N on a worker
+thread and a second CUDA stream, and rollouts older than ``max_staleness`` weight versions are dropped
+and regenerated — the reference declares that knob but never enforces it.
+"""
+from __future__ import annotations
+
+import asyncio
+import csv
+import enum
+import os
+import time
+from concurrent.futures import ThreadPoolExecutor
+from dataclasses import asdict, dataclass, field
+from typing import Dict, List, Optional
+
+import torch
+
+from ..config import ColocateConfig, config_snapshot
+from ..data import GRPOBatch, GSM8KDataPipeline, SyntheticTokenPipeline
+from ..infer import InferenceConfig, InferenceEngine
+from ..obs import ArtifactWriter, CommProfiler, ComputeProfiler, MemoryProfiler, MemoryReport, MetricsCollector, get_logger
+from ..reward import GSM8KRewardFunction, SyntheticTokenReward
+from ..sync import DeltaComputer, PeerWeightSync, SwiftSyncConfig, SwiftSyncTransfer
+from ..train import C3POConfig, C3POPlusScheduler, TrainConfig, TrainEngine, TrainMetrics
+
+logger = get_logger("orch.colocate")
+
+
+class OrchestratorState(enum.Enum):
+    INIT = "init"
+    TRAINING = "training"
+    SLEEPING = "sleeping"
+    SYNCING = "syncing"
+    INFERRING = "inferring"
+    REWARDING = "rewarding"
+    ERROR = "error"
+    DONE = "done"
+
+
+@dataclass
+class IterationMetrics:
+    iteration: int
+    state_durations: Dict[str, float] = field(default_factory=dict)
+    train_metrics: Optional[TrainMetrics] = None
+    avg_reward: float = 0.0
+    accuracy: float = 0.0
+    iteration_accuracy: float = 0.0
+    cumulative_accuracy: float = 0.0
+    total_time: float = 0.0
+    tokens_generated: int = 0
+    tokens_trained: int = 0
+    weights_version: int = 0
+    rollout_staleness: int = 0
+    error: Optional[str] = None
+
+
+@dataclass
+class _Rollout:
+    batch: GRPOBatch
+    responses: List[List[List[int]]]             # [B][K][tokens]
+    logprobs: Optional[List[List[float]]]        # mean per-token log-prob per response, flattened B*K
+    weights_version: int
+    seconds: float
+
+
+class ColocateOrchestrator:
+    def __init__(self, config: ColocateConfig, engine: Optional[TrainEngine] = None,
+                 inference_engine: Optional[InferenceEngine] = None, data=None, reward_fn=None, vllm_client=None):
+        self.config = config
+        self.state = OrchestratorState.INIT
+        self.train_engine = engine
+        self.infer_engine = inference_engine
+        self.data = data
+        self.reward_fn = reward_fn
+        self.vllm_client = vllm_client
+        self.metrics: List[IterationMetrics] = []
+        self.collector = MetricsCollector()
+        self.memory = MemoryProfiler()
+        self.comm_profiler: Optional[CommProfiler] = None
+        self.compute_profiler: Optional[ComputeProfiler] = None
+        self.artifacts: Optional[ArtifactWriter] = None
+        self.c3po: Optional[C3POPlusScheduler] = None
+        self.swift: Optional[SwiftSyncTransfer] = None
+        self.weight_sync: Optional[PeerWeightSync] = None
+        self.tb = None
+        self.state_log: List[str] = []
+        self.weights_version = 0
+        self._batches = None
+        self._pool = ThreadPoolExecutor(max_workers=1)
+        self._rollout_stream = None
+        self._start_time = 0.0
+
+    # ---- state --------------------------------------------------------------------------------------------
+    def _set_state(self, s: OrchestratorState):
+        self.state = s
+        self.state_log.append(s.value)
+
+    # =================================================================================================
+    async def initialize(self):
+        cfg = self.config
+        if self.train_engine is None:
+            total_steps = max(1, cfg.total_iterations * cfg.train_steps_per_iteration // max(1, cfg.gradient_accumulation_steps))
+            tc = TrainConfig(
+                model_path=cfg.model_path if cfg.model_preset is None else "", model_preset=cfg.model_preset,
+                tp_size=cfg.tp_size, dp_size=cfg.dp_size, pp_size=cfg.pp_size, num_micro_batches=cfg.num_micro_batches,
+                max_seq_len=cfg.max_seq_len, use_flash_attn=cfg.use_flash_attn, attention_backend=cfg.attention_backend,
+                use_gradient_checkpoint=cfg.use_gradient_checkpoint, lora_rank=cfg.lora_rank, lora_alpha=cfg.lora_alpha,
+                lora_target_modules=list(cfg.lora_target_modules), learning_rate=cfg.learning_rate,
+                weight_decay=cfg.weight_decay, max_grad_norm=cfg.max_grad_norm, use_amp=cfg.amp_dtype != "fp32",
+                amp_dtype=cfg.amp_dtype, gradient_accumulation_steps=cfg.gradient_accumulation_steps,
+                grpo_num_samples=cfg.num_samples_per_prompt, grpo_beta=cfg.grpo_beta if cfg.training_mode == "grpo" else 0.0,
+                grpo_clip_eps=cfg.grpo_clip_eps, zero_stage=cfg.zero_stage, enable_comm_overlap=cfg.enable_comm_overlap,
+                lr_scheduler_type=cfg.lr_scheduler_type, warmup_steps=cfg.warmup_steps, min_lr_ratio=cfg.min_lr_ratio,
+                total_training_steps=total_steps, icepop_enabled=cfg.icepop_enabled,
+                icepop_divergence_threshold=cfg.icepop_divergence_threshold,
+                icepop_max_mask_ratio=cfg.icepop_max_mask_ratio, sequence_parallel=cfg.sequence_parallel, seed=cfg.seed)
+            self.train_engine = TrainEngine(tc).initialize()
+        eng = self.train_engine
+        eng.metrics_collector = self.collector
+        ctx = eng.parallel_ctx
+        self.artifacts = ArtifactWriter(cfg.output_dir, ctx.global_rank, ctx.world_size)
+        self.artifacts.write_json("config_snapshot.json", config_snapshot(cfg))
+        if cfg.resume_from:
+            ok = eng.load_checkpoint(cfg.resume_from)
+            logger.info("resume from %s: %s", cfg.resume_from, "ok" if ok else "failed")
+        # ---- data + reward ----------------------------------------------------------------------------------
+        if self.data is None:
+            if cfg.synthetic_data:
+                self.data = SyntheticTokenPipeline(eng.model_config.vocab_size, cfg.max_data_samples,
+                                                   cfg.synthetic_prompt_len, cfg.seed, ctx.dp_rank, ctx.dp_size,
+                                                   response_len=cfg.max_tokens if cfg.training_mode == "sft" else 0)
+            else:
+                self.data = GSM8KDataPipeline(
+                    tokenizer_name=cfg.model_path, dataset_name=cfg.dataset_name, dataset_config=cfg.dataset_config,
+                    split=cfg.dataset_split, max_samples=cfg.max_data_samples, prompt_template=cfg.prompt_template,
+                    prompt_field=cfg.prompt_field, input_field=cfg.input_field or "input",
+                    response_field=cfg.response_field, answer_field=cfg.answer_field or "answer",
+                    dp_rank=ctx.dp_rank, dp_size=ctx.dp_size)
+        if self.reward_fn is None:
+            self.reward_fn = SyntheticTokenReward(eng.model_config.vocab_size, cfg.seed) if cfg.synthetic_data \
+                else GSM8KRewardFunction()
+        # ---- rollout backend ----------------------------------------------------------------------------------
+        if cfg.training_mode == "grpo" or cfg.inference_preview_enabled:
+            await self._init_inference()
+        if cfg.c3po_plus_enabled:
+            self.c3po = C3POPlusScheduler(C3POConfig(True, cfg.c3po_plus_token_budget,
+                                                     cfg.c3po_plus_target_batch_tokens, cfg.c3po_plus_packing_strategy))
+        if cfg.swift_sync_enabled and cfg.lora_rank > 0:
+            self.swift = SwiftSyncTransfer(_LoRAWorker(self), SwiftSyncConfig(True, cfg.swift_sync_fallback_full_every,
+                                                                              cfg.swift_sync_double_buffer))
+        if cfg.enable_profiling:
+            self.comm_profiler = CommProfiler()
+            self.compute_profiler = ComputeProfiler()
+        if cfg.tensorboard and ctx.is_main:
+            try:
+                from torch.utils.tensorboard import SummaryWriter
+                self.tb = SummaryWriter(os.path.join(cfg.output_dir, "tensorboard"))
+            except Exception:  # noqa: BLE001 - optional dependency
+                self.tb = None
+        self.memory.snapshot("init")
+        return self
+
+    async def _init_inference(self):
+        cfg, eng = self.config, self.train_engine
+        backend = cfg.inference_backend
+        if self.infer_engine is not None or backend == "vllm" and self.vllm_client is not None:
+            return
+        if backend == "vllm":
+            from ..sync import IPCWeightTransfer, VLLMClient
+            self.vllm_client = VLLMClient(cfg.vllm_url, max_retries=cfg.max_retries, backoff_s=cfg.retry_delay)
+            self.ipc = IPCWeightTransfer(self.vllm_client, cfg.ipc_chunk_size)
+            return
+        mc = eng.model_config
+        if backend == "mock" or eng.parallel_ctx.tp_size > 1 or eng.parallel_ctx.pp_size > 1:
+            ic = InferenceConfig.from_model_config(mc, inference_mode="mock", temperature=cfg.temperature, top_p=cfg.top_p)
+            self.infer_engine = InferenceEngine(ic).initialize()
+            return
+        kw = dict(inference_mode="kv_cache", temperature=cfg.temperature, top_p=cfg.top_p,
+                  kv_cache_dtype=cfg.kv_cache_dtype, enable_cuda_graph=cfg.enable_cuda_graph,
+                  use_radix_cache=cfg.use_radix_cache, enable_prefix_caching=cfg.use_radix_cache,
+                  max_num_batched_tokens=8192, max_prefill_tokens=4096, chunk_size=512, seed=cfg.seed,
+                  max_num_sequences=256)
+        if cfg.kv_num_blocks > 0:
+            ic = InferenceConfig.from_model_config(mc, num_blocks=cfg.kv_num_blocks, **kw)
+        else:
+            auto = InferenceConfig.auto_from_device(mc.num_layers, mc.num_kv_heads, mc.head_dim, gpu_memory_fraction=0.3,
+                                                    kv_cache_dtype=cfg.kv_cache_dtype)
+            ic = InferenceConfig.from_model_config(mc, num_blocks=auto.num_blocks, **kw)
+        rollout_model = eng.model.clone(requires_grad=False) if cfg.lora_rank <= 0 else self._merged_clone()
+        self.infer_engine = InferenceEngine(ic, rollout_model).initialize()
+        from ..model.hf_io import hf_named_tensors
+        layout = [(k, tuple(v.shape)) for k, v in hf_named_tensors(rollout_model)]
+        self.weight_sync = PeerWeightSync(layout, next(rollout_model.parameters()).dtype, eng.device)
+        if torch.cuda.is_available():
+            self._rollout_stream = torch.cuda.Stream()
+
+    def _merged_clone(self):
+        """Plain (adapter-free) copy of the policy with the LoRA branch merged in."""
+        from ..model import ParallelTransformerModel, merge_lora_weights
+        eng = self.train_engine
+        m = ParallelTransformerModel(eng.model_config, dtype=eng.dtype, device=eng.device)
+        from ..model.hf_io import hf_named_tensors
+        merge_lora_weights(eng.model)
+        try:
+            src = dict(hf_named_tensors(eng.model))
+            with torch.no_grad():
+                for k, v in hf_named_tensors(m):
+                    v.copy_(src[k])
+        finally:
+            merge_lora_weights(eng.model, unmerge=True)
+        for p in m.parameters():
+            p.requires_grad_(False)
+        return m
+
+    # =================================================================================================
+    def _next_batch(self) -> GRPOBatch:
+        if self._batches is None:
+            self._batches = self.data.get_batches(max(1, self.config.batch_size // max(1, self.train_engine.parallel_ctx.dp_size)))
+        try:
+            return next(self._batches)
+        except StopIteration:
+            self._batches = self.data.get_batches(max(1, self.config.batch_size // max(1, self.train_engine.parallel_ctx.dp_size)))
+            return next(self._batches)
+
+    def _rollout(self, batch: GRPOBatch) -> _Rollout:
+        """K sampled responses per prompt through the rollout backend."""
+        cfg = self.config
+        t0 = time.perf_counter()
+        K = cfg.num_samples_per_prompt
+        prompts = [p for p in batch.prompt_tokens for _ in range(K)]
+        version = self.weights_version
+        if self._rollout_stream is not None:
+            self._rollout_stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self._rollout_stream):
+                outs, lps = self.infer_engine.generate(prompts, cfg.max_tokens, cfg.temperature, cfg.top_p, return_logprobs=True)
+            self._rollout_stream.synchronize()
+        else:
+            outs, lps = self.infer_engine.generate(prompts, cfg.max_tokens, cfg.temperature, cfg.top_p, return_logprobs=True)
+        outs = [o if o else [0] for o in outs]
+        responses = [outs[i * K:(i + 1) * K] for i in range(len(batch.prompt_tokens))]
+        seq_lp = [sum(l) / max(1, len(l)) if l else 0.0 for l in lps] if lps and lps[0] is not None else None
+        return _Rollout(batch, responses, seq_lp, version, time.perf_counter() - t0)
+
+    def _rewards(self, ro: _Rollout) -> List[List[float]]:
+        if isinstance(self.reward_fn, SyntheticTokenReward):
+            return self.reward_fn(ro.responses, ro.batch.prompt_indices or list(range(len(ro.responses))))
+        tok = self.data.tokenizer
+        texts = [[tok.decode(r) for r in group] for group in ro.responses]
+        return self.reward_fn(texts, ro.batch.ground_truths)
+
+    def _train_grpo(self, ro: _Rollout, rewards: List[List[float]]) -> TrainMetrics:
+        cfg, eng = self.config, self.train_engine
+        prompts = ro.batch.prompt_tokens
+        infer_lp = torch.tensor(ro.logprobs) if (ro.logprobs is not None and cfg.icepop_enabled) else None
+        if self.c3po is not None:
+            adv = [TrainEngine.group_advantages(r) for r in rewards]
+            subs = self.c3po.split_and_pack(prompts, ro.responses, rewards, adv)
+            m = None
+            for i, sb in enumerate(subs):
+                m = eng.grpo_step(**sb, skip_optimizer_step=(i < len(subs) - 1),
+                                  reset_behavior_baseline=True)
+                eng._accumulation_count = cfg.gradient_accumulation_steps if i == len(subs) - 2 else eng._accumulation_count
+            return m
+        m = None
+        for s in range(cfg.train_steps_per_iteration):
+            m = eng.grpo_step(prompts, ro.responses, rewards, infer_log_probs=infer_lp,
+                              reset_behavior_baseline=(s == 0))
+        return m
+
+    def _train_sft(self, batch: GRPOBatch) -> TrainMetrics:
+        eng = self.train_engine
+        if isinstance(self.data, SyntheticTokenPipeline):
+            responses = [self.data.responses[i] or [3] for i in batch.prompt_indices]
+        else:
+            tok = self.data.tokenizer
+            responses = [tok.encode(r) + [getattr(tok, "eos_token_id", 2) or 2] for r in batch.reference_responses]
+        m = None
+        for _ in range(self.config.train_steps_per_iteration):
+            m = eng.sft_step(batch.prompt_tokens, responses)
+        return m
+
+    def _sync_weights(self, iteration: int) -> int:
+        """Publish the trainer's current weights to the rollout engine.  LoRA + SwiftSync: deltas (full
+        every N); otherwise the merged full weights through the peer-write path."""
+        eng = self.train_engine
+        if self.infer_engine is None or self.infer_engine.config.inference_mode == "mock":
+            if self.infer_engine is not None:
+                self.infer_engine.on_weights_updated()
+            self.weights_version += 1
+            return self.weights_version
+        if self.swift is not None:
+            from ..model import get_lora_state_dict
+            self.swift.sync(iteration, get_lora_state_dict(eng.model))
+        else:
+            state = eng.export_weights()
+            self.weight_sync.sync(True, state, self.infer_engine)
+        self.weights_version += 1
+        return self.weights_version
+
+    # =================================================================================================
+    async def run(self) -> List[IterationMetrics]:
+        cfg = self.config
+        self._start_time = time.time()
+        loop = asyncio.get_running_loop()
+        pending: Optional[asyncio.Future] = None
+        for it in range(cfg.total_iterations):
+            im = IterationMetrics(it)
+            t_iter = time.perf_counter()
+            try:
+                if cfg.training_mode == "sft":
+                    self._set_state(OrchestratorState.TRAINING)
+                    t0 = time.perf_counter()
+                    batch = self._next_batch()
+                    im.train_metrics = self._train_sft(batch)
+                    im.state_durations["training"] = time.perf_counter() - t0
+                    im.tokens_trained = sum(len(p) for p in batch.prompt_tokens)
+                else:
+                    # ---- rollout (possibly prefetched while the previous iteration trained) ----------------
+                    self._set_state(OrchestratorState.INFERRING)
+                    t0 = time.perf_counter()
+                    ro = None
+                    if pending is not None:
+                        ro = await pending
+                        pending = None
+                        stale = self.weights_version - ro.weights_version
+                        if stale > cfg.async_pipeline_max_staleness:
+                            logger.info("dropping a rollout that is %d versions stale", stale)
+                            ro = None
+                    if ro is None:
+                        ro = self._rollout(self._next_batch())
+                    im.rollout_staleness = self.weights_version - ro.weights_version
+                    im.state_durations["inferring"] = time.perf_counter() - t0
+                    im.tokens_generated = sum(len(r) for g in ro.responses for r in g)
+                    # ---- reward ------------------------------------------------------------------------------
+                    self._set_state(OrchestratorState.REWARDING)
+                    t0 = time.perf_counter()
+                    rewards = self._rewards(ro)
+                    flat = [x for g in rewards for x in g]
+                    im.avg_reward = sum(flat) / max(1, len(flat))
+                    im.iteration_accuracy = sum(1 for x in flat if x >= 1.0) / max(1, len(flat))
+                    im.state_durations["rewarding"] = time.perf_counter() - t0
+                    # ---- train (next rollout overlaps on the worker thread) ---------------------------------
+                    self._set_state(OrchestratorState.TRAINING)
+                    t0 = time.perf_counter()
+                    if cfg.async_pipeline_enabled and it + 1 < cfg.total_iterations:
+                        nxt = self._next_batch()
+                        pending = loop.run_in_executor(self._pool, self._rollout, nxt)
+                    im.train_metrics = self._train_grpo(ro, rewards)
+                    im.tokens_trained = sum(len(p) + len(r) for p, g in zip(ro.batch.prompt_tokens, ro.responses) for r in g)
+                    im.state_durations["training"] = time.perf_counter() - t0
+                    # ---- sleep / sync / wake -------------------------------------------------------------------
+                    self._set_state(OrchestratorState.SLEEPING)
+                    if self.vllm_client is not None:
+                        await self.vllm_client.sleep(cfg.sleep_level)
+                    self._set_state(OrchestratorState.SYNCING)
+                    t0 = time.perf_counter()
+                    if pending is not None and cfg.async_pipeline_max_staleness <= 0:
+                        ro_next = await pending      # staleness 0: finish the rollout before weights change
+                        pending = loop.create_future()
+                        pending.set_result(ro_next)
+                    await self._sync(it)
+                    im.state_durations["syncing"] = time.perf_counter() - t0
+                    if self.vllm_client is not None:
+                        await self._wake_with_retries()
+                im.weights_version = self.weights_version
+            except Exception as e:  # noqa: BLE001 - an iteration may fail; the loop continues
+                await self._handle_error(it, e, im)
+            im.total_time = time.perf_counter() - t_iter
+            self.metrics.append(im)
+            self._record(im)
+            if cfg.checkpoint_save_enabled and cfg.checkpoint_save_interval > 0 and (it + 1) % cfg.checkpoint_save_interval == 0:
+                self._save_checkpoint(f"iter_{it + 1}")
+            if cfg.memory_profile_interval > 0 and (it + 1) % cfg.memory_profile_interval == 0:
+                self.memory.snapshot(f"iter_{it + 1}")
+        if pending is not None:
+            try:
+                await pending
+            except Exception:  # noqa: BLE001
+                pass
+        if cfg.checkpoint_save_enabled:
+            self._save_checkpoint("final")
+        self._set_state(OrchestratorState.DONE)
+        self._write_final_artifacts()
+        return self.metrics
+
+    async def _sync(self, iteration: int):
+        if self.vllm_client is not None:
+            state = self.train_engine.export_weights("cuda" if torch.cuda.is_available() else None)
+            await self.ipc.push_weights(state, sleep_first=False)
+            self.weights_version += 1
+        else:
+            self._sync_weights(iteration)
+
+    async def _wake_with_retries(self):
+        cfg = self.config
+        for attempt in range(cfg.max_retries):
+            try:
+                await self.vllm_client.wake_up()
+                return
+            except Exception as e:  # noqa: BLE001
+                logger.warning("wake_up attempt %d failed: %s", attempt + 1, e)
+                await asyncio.sleep(cfg.retry_delay)
+        raise RuntimeError("inference server did not wake up")
+
+    async def _handle_error(self, it: int, e: Exception, im: IterationMetrics):
+        logger.error("iteration %d failed: %s: %s", it, type(e).__name__, e)
+        self._set_state(OrchestratorState.ERROR)
+        im.error = f"{type(e).__name__}: {e}"
+        if self.vllm_client is not None:
+            try:
+                await self._wake_with_retries()
+            except Exception:  # noqa: BLE001
+                pass
+
+    # ---- artefacts ------------------------------------------------------------------------------------------
+    def _record(self, im: IterationMetrics):
+        cum = [m.iteration_accuracy for m in self.metrics]
+        im.cumulative_accuracy = sum(cum) / max(1, len(cum))
+        im.accuracy = im.iteration_accuracy
+        tm = im.train_metrics
+        row = {"iteration": im.iteration, "total_time": im.total_time, "avg_reward": im.avg_reward,
+               "accuracy": im.iteration_accuracy, "cumulative_accuracy": im.cumulative_accuracy,
+               "tokens_generated": im.tokens_generated, "tokens_trained": im.tokens_trained,
+               "weights_version": im.weights_version, "rollout_staleness": im.rollout_staleness, "error": im.error,
+               **{f"t_{k}": v for k, v in im.state_durations.items()}}
+        if tm is not None:
+            row.update({"loss": tm.loss, "policy_loss": tm.policy_loss, "kl": tm.kl_divergence,
+                        "grad_norm": tm.grad_norm, "lr": tm.learning_rate, "step": tm.step})
+            row.update({k: v for k, v in (tm.extras or {}).items()})
+        self.artifacts.append_jsonl("metrics", row)
+        if self.tb is not None and tm is not None:
+            self.tb.add_scalar("train/loss", tm.loss, im.iteration)
+            self.tb.add_scalar("train/grad_norm", tm.grad_norm, im.iteration)
+            self.tb.add_scalar("train/lr", tm.learning_rate, im.iteration)
+            self.tb.add_scalar("rollout/avg_reward", im.avg_reward, im.iteration)
+            self.tb.add_scalar("time/iteration_s", im.total_time, im.iteration)
+        if self.compute_profiler is not None and tm is not None and (im.iteration + 1) % max(1, self.config.profile_interval) == 0:
+            self.collector.record("mfu", self._mfu(im))
+
+    def _mfu(self, im: IterationMetrics) -> float:
+        cfg, mc = self.config, self.train_engine.model_config
+        t = im.state_durations.get("training", 0.0)
+        if t <= 0:
+            return 0.0
+        fl = ComputeProfiler.reference_formula_flops(mc.num_layers, cfg.batch_size, cfg.max_seq_len, mc.hidden_size,
+                                                     mc.intermediate_size, mc.vocab_size, full=cfg.lora_rank <= 0)
+        return self.compute_profiler.compute_mfu(fl / (cfg.tp_size * cfg.pp_size), t)
+
+    def _save_checkpoint(self, tag: str):
+        base = self.config.checkpoint_save_dir
+        for name in (tag, "latest"):
+            self.train_engine.save_checkpoint(os.path.join(base, name))
+
+    def get_summary(self) -> Dict:
+        ok = [m for m in self.metrics if m.error is None]
+        losses = [m.train_metrics.loss for m in ok if m.train_metrics is not None]
+        stage: Dict[str, float] = {}
+        for m in ok:
+            for k, v in m.state_durations.items():
+                stage[k] = stage.get(k, 0.0) + v
+        n = max(1, len(ok))
+        summary = {
+            "config": config_snapshot(self.config),
+            "results": {"iterations": len(self.metrics), "failed_iterations": len(self.metrics) - len(ok),
+                        "final_loss": losses[-1] if losses else None, "initial_loss": losses[0] if losses else None,
+                        "avg_reward": sum(m.avg_reward for m in ok) / n,
+                        "avg_iteration_time": sum(m.total_time for m in ok) / n,
+                        "final_weights_version": self.weights_version},
+            "stage_averages": {k: v / n for k, v in stage.items()},
+            "system": {"world_size": self.train_engine.parallel_ctx.world_size if self.train_engine else 1,
+                       "device": torch.cuda.get_device_name(0) if torch.cuda.is_available() else "cpu",
+                       "wall_time_s": time.time() - self._start_time if self._start_time else 0.0},
+            "performance": {"tokens_trained": sum(m.tokens_trained for m in ok),
+                            "tokens_generated": sum(m.tokens_generated for m in ok),
+                            "mfu_samples": self.collector.series.get("mfu", [])},
+            "metrics": self.collector.summary(),
+            "state_log_tail": self.state_log[-16:],
+        }
+        if self.infer_engine is not None:
+            summary["inference"] = self.infer_engine.get_stats()
+        if self.swift is not None:
+            summary["swift_sync"] = self.swift.get_stats()
+        if self.weight_sync is not None:
+            summary["weight_sync"] = self.weight_sync.get_stats()
+        return summary
+
+    def _write_final_artifacts(self):
+        self.artifacts.write_json("run_summary.json", self.get_summary())
+        if self.artifacts.is_main:
+            with open(self.artifacts.path("loss_curve.csv"), "w", newline="") as f:
+                w = csv.writer(f)
+                w.writerow(["iteration", "loss", "grad_norm", "avg_reward"])
+                for m in self.metrics:
+                    if m.train_metrics is not None:
+                        w.writerow([m.iteration, m.train_metrics.loss, m.train_metrics.grad_norm, m.avg_reward])
+        self.artifacts.write_json("memory_timeline.json", self.memory.timeline(), all_ranks=True)
+        rep = self.train_engine.generate_memory_report(self.config.batch_size * self.config.max_seq_len)
+        self.artifacts.write_json("memory_report.json", rep.to_dict())
+        if self.tb is not None:
+            self.tb.flush()
+
+    async def shutdown(self):
+        self._pool.shutdown(wait=True)
+        if self.vllm_client is not None:
+            await self.vllm_client.close()
+        if self.tb is not None:
+            self.tb.close()
+
+
+class _LoRAWorker:
+    """SwiftSync's view of the in-process rollout engine: takes adapter states / deltas and re-merges
+    them into the engine's plain weights (in place)."""
+
+    def __init__(self, orch: ColocateOrchestrator):
+        self.orch = orch
+
+    def update_weights(self, state, mode: str = "full"):
+        orch = self.orch
+        merged = orch._merged_clone()
+        from ..model.hf_io import hf_named_tensors
+        orch.infer_engine.load_weights(dict(hf_named_tensors(merged)))

@@ -1,0 +1,210 @@
+"""Disaggregated orchestrator: trainer ranks and rollout ranks are two groups of ONE torchrun world
+(e.g. GPUs 0-3 train with ZeRO-2, GPUs 4-7 run the native engine), instead of the reference's Ray
+placement group with ``TrainWorker`` / ``InferWorker`` actors and object-store transfers
+(src/orchestrator/disagg_orchestrator.py:88-500).
+
+Per iteration: every rollout rank generates for its share of the prompts while the trainer ranks train
+on the previous iteration's samples (pipeline mode; ``sequential`` runs the two phases one after the
+other), the samples travel trainer-ward as token tensors, and the weights travel engine-ward through
+the weight-transfer manager (peer write over NVLink, or the NCCL broadcast baseline).  The overlap
+ratio reported is ``min(train, rollout) / max(train, rollout)`` of the concurrent phases.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..obs import get_logger
+
+logger = get_logger("orch.disagg")
+
+
+@dataclass
+class DisaggConfig:
+    model_path: str = ""
+    model_preset: Optional[str] = None
+    num_train_gpus: int = 4
+    num_infer_gpus: int = 4
+    train_zero_stage: int = 2
+    total_iterations: int = 10
+    batch_size: int = 64                 # prompts per iteration (global)
+    num_samples_per_prompt: int = 8
+    prompt_len: int = 256
+    max_tokens: int = 512
+    temperature: float = 0.8
+    top_p: float = 0.95
+    learning_rate: float = 1e-5
+    lora_rank: int = 0
+    grpo_beta: float = 0.01
+    grpo_clip_eps: float = 0.2
+    gradient_accumulation_steps: int = 1
+    mode: str = "pipeline"               # "pipeline" | "sequential"
+    transfer_backend: str = "nccl"       # "peer_write" | "nccl"
+    max_staleness: int = 1
+    kv_cache_dtype: str = "fp16"
+    kv_num_blocks: int = 4096
+    seed: int = 0
+    output_dir: str = "outputs_disagg"
+    backend: Optional[str] = None        # process-group backend (default by device)
+
+
+@dataclass
+class DisaggIterationMetrics:
+    iteration: int
+    train_time: float = 0.0
+    rollout_time: float = 0.0
+    sync_time: float = 0.0
+    total_time: float = 0.0
+    overlap_ratio: float = 0.0
+    loss: float = 0.0
+    avg_reward: float = 0.0
+    weights_version: int = 0
+
+
+class DisaggOrchestrator:
+    """Run the same object on every rank of the world; the rank decides its role."""
+
+    def __init__(self, config: DisaggConfig, train_engine_factory=None, infer_engine_factory=None, reward_fn=None):
+        self.config = config
+        self.rank = dist.get_rank() if dist.is_initialized() else 0
+        self.world = dist.get_world_size() if dist.is_initialized() else 1
+        self.is_trainer = self.rank < config.num_train_gpus
+        self.train_engine = None
+        self.infer_engine = None
+        self.train_group = self.infer_group = None
+        self.train_engine_factory, self.infer_engine_factory = train_engine_factory, infer_engine_factory
+        self.reward_fn = reward_fn
+        self.metrics: List[DisaggIterationMetrics] = []
+        self.weights_version = 0
+        self.transfer = None
+
+    # ---- set-up ----------------------------------------------------------------------------------------------
+    def initialize(self):
+        cfg = self.config
+        assert cfg.num_train_gpus + cfg.num_infer_gpus == self.world, "train + infer GPUs must equal WORLD_SIZE"
+        tr = list(range(cfg.num_train_gpus))
+        inf = list(range(cfg.num_train_gpus, self.world))
+        self.train_group = dist.new_group(tr)
+        self.infer_group = dist.new_group(inf)
+        # one sync group per trainer-leader -> all engines (leader = rank 0)
+        self.sync_group = dist.new_group([0] + inf)
+        if self.is_trainer:
+            self.train_engine = self.train_engine_factory(self.train_group, len(tr), self.rank)
+        else:
+            self.infer_engine = self.infer_engine_factory(self.rank - cfg.num_train_gpus)
+        from ..sync import WeightTransferManager
+        if self.rank == 0 or not self.is_trainer:
+            self.transfer = WeightTransferManager("nccl", self.sync_group, src_rank=0)
+        if self.reward_fn is None:
+            from ..reward import SyntheticTokenReward
+            vocab = (self.train_engine.model_config.vocab_size if self.is_trainer else self.infer_engine.config.vocab_size)
+            self.reward_fn = SyntheticTokenReward(vocab, cfg.seed)
+        return self
+
+    # ---- phases ------------------------------------------------------------------------------------------------
+    def _prompts(self, iteration: int) -> List[List[int]]:
+        """Seeded prompts, identical on every rank (no data transfer needed for them)."""
+        import random
+        rng = random.Random(self.config.seed * 7919 + iteration)
+        vocab = (self.train_engine.model_config.vocab_size if self.is_trainer else self.infer_engine.config.vocab_size)
+        return [[rng.randrange(3, vocab) for _ in range(self.config.prompt_len)] for _ in range(self.config.batch_size)]
+
+    def _rollout_share(self, prompts: List[List[int]]):
+        cfg = self.config
+        i = self.rank - cfg.num_train_gpus
+        mine = list(range(i, len(prompts), cfg.num_infer_gpus))
+        reqs = [prompts[j] for j in mine for _ in range(cfg.num_samples_per_prompt)]
+        outs = self.infer_engine.generate(reqs, cfg.max_tokens, cfg.temperature, cfg.top_p)
+        K = cfg.num_samples_per_prompt
+        return {j: [o or [0] for o in outs[n * K:(n + 1) * K]] for n, j in enumerate(mine)}
+
+    def _exchange_samples(self, local: Optional[Dict[int, List[List[int]]]]) -> Dict[int, List[List[int]]]:
+        """Rollout ranks publish their samples; everyone ends up with the full set (token id lists)."""
+        box = [None] * self.world
+        dist.all_gather_object(box, local or {})
+        merged: Dict[int, List[List[int]]] = {}
+        for d in box:
+            merged.update(d)
+        return merged
+
+    def _train(self, prompts, samples) -> float:
+        cfg = self.config
+        n_tr = cfg.num_train_gpus
+        mine = list(range(self.rank, len(prompts), n_tr))
+        P = [prompts[j] for j in mine]
+        R = [samples[j] for j in mine]
+        rewards = self.reward_fn(R, mine)
+        m = self.train_engine.grpo_step(P, R, rewards)
+        self._last_reward = sum(x for g in rewards for x in g) / max(1, sum(len(g) for g in rewards))
+        return m.loss
+
+    def _sync_weights(self):
+        t0 = time.perf_counter()
+        if self.is_trainer:
+            state = self.train_engine.export_weights()        # collective over the trainer group (ZeRO-3 gathers)
+            if self.rank == 0:
+                self.transfer.sync_weights(True, state)
+        else:
+            from ..model.hf_io import hf_named_tensors
+            templates = dict(hf_named_tensors(self.infer_engine.model))
+            self.transfer.sync_weights(False, engine=self.infer_engine, templates=templates)
+        self.weights_version += 1
+        return time.perf_counter() - t0
+
+    # ---- loop ----------------------------------------------------------------------------------------------------
+    def run(self) -> List[DisaggIterationMetrics]:
+        cfg = self.config
+        prev = None     # (prompts, samples) generated in the previous iteration, trained in this one
+        for it in range(cfg.total_iterations + (1 if cfg.mode == "pipeline" else 0)):
+            t_iter = time.perf_counter()
+            m = DisaggIterationMetrics(it)
+            prompts = self._prompts(it)
+            do_rollout = it < cfg.total_iterations
+            t0 = time.perf_counter()
+            local = self._rollout_share(prompts) if (not self.is_trainer and do_rollout) else None
+            if not self.is_trainer:
+                m.rollout_time = time.perf_counter() - t0
+            if cfg.mode == "pipeline":
+                if self.is_trainer and prev is not None:
+                    t1 = time.perf_counter()
+                    m.loss = self._train(*prev)
+                    m.train_time = time.perf_counter() - t1
+                samples = self._exchange_samples(local)
+                prev = (prompts, samples) if do_rollout else None
+            else:
+                samples = self._exchange_samples(local)
+                if self.is_trainer:
+                    t1 = time.perf_counter()
+                    m.loss = self._train(prompts, samples)
+                    m.train_time = time.perf_counter() - t1
+            m.sync_time = self._sync_weights()
+            m.total_time = time.perf_counter() - t_iter
+            times = torch.tensor([m.train_time, m.rollout_time], dtype=torch.float64)
+            if torch.cuda.is_available() and dist.get_backend() == "nccl":
+                times = times.cuda()
+            dist.all_reduce(times, op=dist.ReduceOp.MAX)
+            m.train_time, m.rollout_time = float(times[0]), float(times[1])
+            hi = max(m.train_time, m.rollout_time)
+            m.overlap_ratio = min(m.train_time, m.rollout_time) / hi if hi > 0 else 0.0
+            m.avg_reward = getattr(self, "_last_reward", 0.0)
+            m.weights_version = self.weights_version
+            self.metrics.append(m)
+        return self.metrics
+
+    def get_summary(self) -> Dict:
+        n = max(1, len(self.metrics))
+        return {"iterations": len(self.metrics), "role": "trainer" if self.is_trainer else "rollout",
+                "avg_iteration_s": sum(m.total_time for m in self.metrics) / n,
+                "avg_train_s": sum(m.train_time for m in self.metrics) / n,
+                "avg_rollout_s": sum(m.rollout_time for m in self.metrics) / n,
+                "avg_sync_s": sum(m.sync_time for m in self.metrics) / n,
+                "avg_overlap_ratio": sum(m.overlap_ratio for m in self.metrics) / n,
+                "final_loss": self.metrics[-1].loss if self.metrics else None,
+                "weights_version": self.weights_version}
+
+    def shutdown(self):
+        pass

@@ -1,0 +1,82 @@
+"""Rule-based GSM8K reward (behaviour of src/reward/gsm8k_reward.py:17-223).
+
+Answer extraction tries, in order: ``#### <number>``, ``\\boxed{...}``, "the answer is" / "答案是" phrases,
+then the last number in the text.  Reward: +1 for a correct answer, -0.5 for a well-formed but wrong one,
+-1 when no answer can be extracted.  Running accuracy statistics are kept.
+"""
+from __future__ import annotations
+
+import re
+from typing import Dict, List, Optional
+
+_NUM = r"-?\d[\d,]*(?:\.\d+)?(?:/\d+)?"
+_PATTERNS = [
+    re.compile(r"####\s*\$?\s*(" + _NUM + ")"),
+    re.compile(r"\\boxed\{\s*\$?\s*(" + _NUM + r")\s*\}"),
+    re.compile(r"(?:final answer|answer)\s*(?:is|:|=)\s*\$?\s*(" + _NUM + ")", re.IGNORECASE),
+    re.compile(r"(?:答案是|答案为|答案[:：])\s*\$?\s*(" + _NUM + ")"),
+]
+_LAST = re.compile(_NUM)
+
+
+def _to_float(s: str) -> Optional[float]:
+    s = s.replace(",", "").strip().rstrip(".")
+    try:
+        if "/" in s:
+            a, b = s.split("/", 1)
+            return float(a) / float(b)
+        return float(s)
+    except (ValueError, ZeroDivisionError):
+        return None
+
+
+def extract_answer(text: str) -> Optional[float]:
+    for pat in _PATTERNS:
+        m = pat.findall(text)
+        if m:
+            v = _to_float(m[-1])
+            if v is not None:
+                return v
+    nums = _LAST.findall(text)
+    return _to_float(nums[-1]) if nums else None
+
+
+def check_format(text: str) -> bool:
+    """True when the response states its answer explicitly (marker, box or answer phrase)."""
+    return any(p.search(text) for p in _PATTERNS)
+
+
+class GSM8KRewardFunction:
+    def __init__(self, correct: float = 1.0, wrong: float = -0.5, no_answer: float = -1.0, tol: float = 1e-4):
+        self.correct, self.wrong, self.no_answer, self.tol = correct, wrong, no_answer, tol
+        self.total = 0
+        self.num_correct = 0
+        self.num_formatted = 0
+
+    def score(self, response: str, ground_truth) -> float:
+        self.total += 1
+        pred = extract_answer(response)
+        gt = ground_truth if isinstance(ground_truth, (int, float)) else extract_answer(str(ground_truth))
+        if check_format(response):
+            self.num_formatted += 1
+        if pred is None or gt is None:
+            return self.no_answer
+        if abs(pred - gt) <= self.tol * max(1.0, abs(gt)):
+            self.num_correct += 1
+            return self.correct
+        return self.wrong
+
+    def __call__(self, responses: List[List[str]], ground_truths: List) -> List[List[float]]:
+        """``responses[b][k]`` -> rewards of the same shape."""
+        return [[self.score(r, gt) for r in group] for group, gt in zip(responses, ground_truths)]
+
+    @property
+    def accuracy(self) -> float:
+        return self.num_correct / self.total if self.total else 0.0
+
+    def get_stats(self) -> Dict[str, float]:
+        return {"total": self.total, "accuracy": self.accuracy,
+                "format_rate": self.num_formatted / self.total if self.total else 0.0}
+
+    def reset_stats(self):
+        self.total = self.num_correct = self.num_formatted = 0

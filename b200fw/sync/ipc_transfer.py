@@ -1,0 +1,211 @@
+"""vLLM-server compatibility layer: HTTP control client, CUDA-IPC handle transfer, and the weight update
+manager with rollback (src/transfer/ipc_transfer.py:53-667).
+
+Not on this framework's product path (rollouts run in the native engine and weights move by peer
+write), but kept so that a vLLM server can still be driven: the same endpoints, the same retry taxonomy
+(programming errors are never retried, a CUDA out-of-memory answer is retried once, everything else
+with linear back-off), chunked handle payloads keyed by GPU UUID, and ``push_weights`` always tries to
+wake the server up again when something fails.
+"""
+from __future__ import annotations
+
+import asyncio
+import base64
+import hashlib
+import pickle
+import time
+from dataclasses import dataclass, field
+from typing import Any, Callable, Dict, List, Optional
+
+import torch
+
+from ..obs.logging import get_logger
+from .nccl_transfer import TransferStats
+
+logger = get_logger("sync.ipc")
+
+
+class NonRetriableError(Exception):
+    pass
+
+
+def classify_error(e: BaseException) -> str:
+    """'fatal' (never retry), 'oom' (retry once), or 'retry'."""
+    if isinstance(e, (ValueError, KeyError, TypeError, NonRetriableError)):
+        return "fatal"
+    if "out of memory" in str(e).lower():
+        return "oom"
+    return "retry"
+
+
+class VLLMClient:
+    def __init__(self, base_url: str = "http://localhost:8000", timeout: float = 60.0, max_retries: int = 3,
+                 backoff_s: float = 1.0, client=None):
+        self.base_url = base_url.rstrip("/")
+        self.timeout, self.max_retries, self.backoff_s = timeout, max_retries, backoff_s
+        self._client = client
+        self.calls: List[str] = []
+
+    async def _get_client(self):
+        if self._client is None:
+            import httpx
+            self._client = httpx.AsyncClient(timeout=self.timeout)
+        return self._client
+
+    async def _request(self, method: str, path: str, **kw) -> Any:
+        client = await self._get_client()
+        attempt, oom_retried = 0, False
+        while True:
+            try:
+                self.calls.append(f"{method} {path}")
+                resp = await getattr(client, method.lower())(self.base_url + path, **kw)
+                if hasattr(resp, "raise_for_status"):
+                    resp.raise_for_status()
+                return resp
+            except Exception as e:  # noqa: BLE001
+                kind = classify_error(e)
+                attempt += 1
+                if kind == "fatal":
+                    raise
+                if kind == "oom":
+                    if oom_retried:
+                        raise
+                    oom_retried = True
+                elif attempt > self.max_retries:
+                    raise
+                await asyncio.sleep(self.backoff_s * attempt)
+
+    async def health(self) -> bool:
+        try:
+            await self._request("GET", "/health")
+            return True
+        except Exception:  # noqa: BLE001
+            return False
+
+    async def reset_prefix_cache(self):
+        return await self._request("POST", "/reset_prefix_cache")
+
+    async def sleep(self, level: int = 1):
+        await self.reset_prefix_cache()
+        return await self._request("POST", f"/sleep?level={level}")
+
+    async def wake_up(self, tags: Optional[str] = None):
+        return await self._request("POST", "/wake_up" + (f"?tags={tags}" if tags else ""))
+
+    async def init_weight_transfer(self, payload: Optional[Dict] = None):
+        return await self._request("POST", "/init_weight_transfer_engine", json=payload or {})
+
+    async def start_weight_update(self, payload: Optional[Dict] = None):
+        return await self._request("POST", "/start_weight_update", json=payload or {})
+
+    async def update_weights(self, payload: Dict):
+        return await self._request("POST", "/update_weights", json=payload)
+
+    async def finish_weight_update(self, payload: Optional[Dict] = None):
+        return await self._request("POST", "/finish_weight_update", json=payload or {})
+
+    async def close(self):
+        if self._client is not None and hasattr(self._client, "aclose"):
+            await self._client.aclose()
+
+
+def _gpu_uuid(device_index: int = 0) -> str:
+    try:
+        return str(torch.cuda.get_device_properties(device_index).uuid)
+    except Exception:  # noqa: BLE001
+        return f"cpu-{device_index}"
+
+
+class IPCWeightTransfer:
+    def __init__(self, client: VLLMClient, chunk_size: int = 16, device_index: int = 0):
+        self.client, self.chunk_size, self.device_index = client, chunk_size, device_index
+        self.stats = TransferStats()
+        self._keepalive: List[torch.Tensor] = []     # exported tensors must outlive the receiver's import
+
+    def build_ipc_handles(self, state: Dict[str, torch.Tensor]) -> List[Dict]:
+        handles = []
+        self._keepalive = []
+        for name, t in state.items():
+            t = t.detach().contiguous()
+            self._keepalive.append(t)
+            if t.is_cuda:
+                from torch.multiprocessing.reductions import reduce_tensor
+                fn, args = reduce_tensor(t)
+                handle = (fn.__name__, args)
+            else:
+                handle = ("cpu_tensor", t)        # CPU fallback keeps the protocol testable
+            handles.append({"name": name, "shape": tuple(t.shape), "dtype": str(t.dtype), "handle": handle})
+        return handles
+
+    def _chunk_handles(self, handles: List[Dict]) -> List[List[Dict]]:
+        return [handles[i:i + self.chunk_size] for i in range(0, len(handles), self.chunk_size)]
+
+    def _build_http_payload(self, chunk: List[Dict]) -> Dict:
+        blob = base64.b64encode(pickle.dumps([h["handle"] for h in chunk])).decode()
+        return {"names": [h["name"] for h in chunk], "shapes": [list(h["shape"]) for h in chunk],
+                "dtypes": [h["dtype"] for h in chunk], "ipc_handles": {_gpu_uuid(self.device_index): blob}}
+
+    @staticmethod
+    def checksum(state: Dict[str, torch.Tensor]) -> str:
+        m = hashlib.md5()
+        for k in sorted(state):
+            m.update(k.encode())
+            m.update(state[k].detach().to(torch.float32).cpu().contiguous().numpy().tobytes())
+        return m.hexdigest()
+
+    async def push_weights(self, state: Dict[str, torch.Tensor], sleep_first: bool = True) -> TransferStats:
+        t0 = time.perf_counter()
+        nbytes = sum(v.numel() * v.element_size() for v in state.values())
+        try:
+            if sleep_first:
+                await self.client.sleep()
+            handles = self.build_ipc_handles(state)
+            await self.client.init_weight_transfer()
+            await self.client.start_weight_update({"num_tensors": len(handles)})
+            for chunk in self._chunk_handles(handles):
+                await self.client.update_weights(self._build_http_payload(chunk))
+            await self.client.finish_weight_update()
+            await self.client.wake_up()
+            self.stats.record(nbytes, time.perf_counter() - t0, ok=True)
+        except Exception:
+            self.stats.record(nbytes, time.perf_counter() - t0, ok=False)
+            try:
+                await self.client.wake_up()      # never leave the server asleep
+            except Exception as e2:  # noqa: BLE001
+                logger.warning("wake_up after a failed push also failed: %s", e2)
+            raise
+        return self.stats
+
+
+class WeightUpdateManager:
+    """Apply a state dict to a model; on any failure restore the previous tensors
+    (src/transfer/ipc_transfer.py:566-667)."""
+
+    def __init__(self, model: torch.nn.Module, validate: Optional[Callable[[torch.nn.Module], bool]] = None):
+        self.model, self.validate = model, validate
+        self.version = 0
+        self.rollbacks = 0
+
+    @torch.no_grad()
+    def update_weights(self, state: Dict[str, torch.Tensor]) -> bool:
+        params = dict(self.model.named_parameters())
+        backup = {k: params[k].detach().clone() for k in state if k in params}
+        try:
+            for k, v in state.items():
+                if k not in params:
+                    continue
+                if tuple(params[k].shape) != tuple(v.shape):
+                    raise ValueError(f"shape mismatch for {k}: {tuple(v.shape)} vs {tuple(params[k].shape)}")
+                if not torch.isfinite(v).all():
+                    raise ValueError(f"non-finite values in {k}")
+                params[k].copy_(v.to(params[k].dtype))
+            if self.validate is not None and not self.validate(self.model):
+                raise RuntimeError("post-update validation failed")
+            self.version += 1
+            return True
+        except Exception as e:  # noqa: BLE001
+            for k, v in backup.items():
+                params[k].copy_(v)
+            self.rollbacks += 1
+            logger.warning("weight update rolled back: %s", e)
+            return False

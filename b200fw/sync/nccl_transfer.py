@@ -1,0 +1,177 @@
+"""Collective weight transfer baselines and the backend-agnostic manager.
+
+``NCCLWeightTransfer`` is the measured baseline for sync latency: names are agreed once, every tensor
+is broadcast from the trainer rank into template buffers, a checksum over a sample of each tensor is
+compared and a version number follows (src/transfer/nccl_transfer.py:76-223).  It runs over whatever
+backend the process group has (NCCL on GPUs, gloo in the CPU tests).  ``RayObjectStoreTransfer`` keeps
+the reference's interface; Ray is not part of this framework's runtime, so it reports unavailable
+unless ``ray`` can be imported.  ``WeightTransferManager`` selects a backend and keeps stats.
+"""
+from __future__ import annotations
+
+import hashlib
+import time
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass
+class TransferStats:
+    transfers: int = 0
+    total_bytes: int = 0
+    total_time_s: float = 0.0
+    failures: int = 0
+    last_gbps: float = 0.0
+    history: List[Dict] = field(default_factory=list)
+
+    def record(self, nbytes: int, dt: float, ok: bool = True):
+        self.transfers += 1
+        self.total_bytes += nbytes
+        self.total_time_s += dt
+        self.failures += 0 if ok else 1
+        self.last_gbps = nbytes / dt / 1e9 if dt > 0 else 0.0
+        self.history.append({"bytes": nbytes, "time_s": dt, "gbps": self.last_gbps, "ok": ok})
+
+    @property
+    def avg_gbps(self) -> float:
+        return self.total_bytes / self.total_time_s / 1e9 if self.total_time_s > 0 else 0.0
+
+
+def sample_checksum(t: torch.Tensor, n: int = 64) -> str:
+    """md5 of the first ``n`` elements (cheap integrity probe, as the reference does)."""
+    flat = t.detach().reshape(-1)[:n].to(torch.float32).cpu().contiguous()
+    return hashlib.md5(flat.numpy().tobytes()).hexdigest()
+
+
+class NCCLWeightTransfer:
+    def __init__(self, group=None, src_rank: int = 0):
+        self.group, self.src = group, src_rank
+        self.version = 0
+        self.stats = TransferStats()
+        self._names: Optional[List[str]] = None
+
+    def _bcast_obj(self, obj):
+        box = [obj]
+        dist.broadcast_object_list(box, src=self.src, group=self.group)
+        return box[0]
+
+    def broadcast_weights(self, state: Dict[str, torch.Tensor]) -> int:
+        """Trainer side.  Returns the new version."""
+        t0 = time.perf_counter()
+        names = list(state.keys())
+        meta = self._bcast_obj({"names": names, "shapes": [tuple(state[n].shape) for n in names],
+                                "checks": [sample_checksum(state[n]) for n in names]})
+        nbytes = 0
+        for n in meta["names"]:
+            t = state[n].contiguous()
+            dist.broadcast(t, src=self.src, group=self.group)
+            nbytes += t.numel() * t.element_size()
+        self.version = self._bcast_obj(self.version + 1)
+        self.stats.record(nbytes, time.perf_counter() - t0)
+        return self.version
+
+    def receive_weights(self, templates: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+        """Engine side: receive into ``templates`` (same names / shapes / dtypes); verifies the sample
+        checksums and raises on mismatch, leaving ``version`` unchanged."""
+        t0 = time.perf_counter()
+        meta = self._bcast_obj(None)
+        nbytes, bad = 0, []
+        for n, shape, chk in zip(meta["names"], meta["shapes"], meta["checks"]):
+            buf = templates.get(n)
+            if buf is None or tuple(buf.shape) != tuple(shape):
+                buf = torch.empty(shape, dtype=next(iter(templates.values())).dtype,
+                                  device=next(iter(templates.values())).device)
+                templates[n] = buf
+            dist.broadcast(buf, src=self.src, group=self.group)
+            nbytes += buf.numel() * buf.element_size()
+            if sample_checksum(buf) != chk:
+                bad.append(n)
+        version = self._bcast_obj(None)
+        self.stats.record(nbytes, time.perf_counter() - t0, ok=not bad)
+        if bad:
+            raise RuntimeError(f"weight checksum mismatch for {bad[:3]} ({len(bad)} tensors)")
+        self.version = version
+        return templates
+
+
+class RayObjectStoreTransfer:
+    """CPU copy -> ``ray.put`` / ``ray.get`` (src/transfer/nccl_transfer.py:226-361)."""
+
+    def __init__(self):
+        try:
+            import ray  # noqa: F401
+            self.available = True
+        except ImportError:
+            self.available = False
+        self.stats = TransferStats()
+        self._ref = None
+
+    def publish_weights(self, state: Dict[str, torch.Tensor]):
+        if not self.available:
+            raise RuntimeError("ray is not installed: the object-store backend is unavailable")
+        import ray
+        t0 = time.perf_counter()
+        cpu = {k: v.detach().cpu() for k, v in state.items()}
+        self._ref = ray.put(cpu)
+        self.stats.record(sum(v.numel() * v.element_size() for v in cpu.values()), time.perf_counter() - t0)
+        return self._ref
+
+    def fetch_weights(self, ref=None, device: str = "cpu") -> Dict[str, torch.Tensor]:
+        if not self.available:
+            raise RuntimeError("ray is not installed: the object-store backend is unavailable")
+        import ray
+        state = ray.get(ref if ref is not None else self._ref)
+        return {k: v.to(device) for k, v in state.items()}
+
+
+class WeightTransferManager:
+    """One entry point over the backends: ``local`` (same process: in-place copy into the engine),
+    ``peer_write`` (NVLink kernel), ``nccl`` (broadcast baseline), ``ray_object_store``."""
+
+    def __init__(self, backend: str = "local", group=None, src_rank: int = 0, peer_sync=None):
+        assert backend in ("local", "peer_write", "nccl", "ray_object_store")
+        self.backend = backend
+        self.nccl = NCCLWeightTransfer(group, src_rank) if backend == "nccl" else None
+        self.ray = RayObjectStoreTransfer() if backend == "ray_object_store" else None
+        self.peer = peer_sync
+        self.stats = TransferStats()
+        self.version = 0
+
+    def sync_weights(self, is_sender: bool, state: Optional[Dict[str, torch.Tensor]] = None, engine=None,
+                     templates: Optional[Dict[str, torch.Tensor]] = None):
+        t0 = time.perf_counter()
+        nbytes = sum(v.numel() * v.element_size() for v in state.values()) if state else 0
+        if self.backend == "local":
+            assert engine is not None and state is not None
+            engine.load_weights(state)
+            self.version += 1
+        elif self.backend == "nccl":
+            if is_sender:
+                self.version = self.nccl.broadcast_weights(state)
+            else:
+                out = self.nccl.receive_weights(templates)
+                self.version = self.nccl.version
+                if engine is not None:
+                    engine.load_weights(out)
+        elif self.backend == "peer_write":
+            self.version = self.peer.sync(is_sender, state, engine)
+        else:
+            if is_sender:
+                self.ray.publish_weights(state)
+            elif engine is not None:
+                engine.load_weights(self.ray.fetch_weights())
+            self.version += 1
+        self.stats.record(nbytes, time.perf_counter() - t0)
+        return self.version
+
+    async def sync_weights_async(self, *a, **kw):
+        import asyncio
+        return await asyncio.get_running_loop().run_in_executor(None, lambda: self.sync_weights(*a, **kw))
+
+    def get_stats(self) -> Dict:
+        return {"backend": self.backend, "version": self.version, "transfers": self.stats.transfers,
+                "total_bytes": self.stats.total_bytes, "avg_gbps": self.stats.avg_gbps,
+                "failures": self.stats.failures}

@@ -1,0 +1,225 @@
+"""Weight sync by chunked NVLink peer writes.
+
+The trainer casts and writes every (merged) weight straight into a *staging* buffer that lives in the
+inference GPU's memory (``b2_peer_write``: cast + optional in-place add + running checksum, one launch
+per chunk), then publishes ``{version, checksum}``.  The engine recomputes the checksum over its
+staging buffer; only if it matches does it copy staging -> live parameters (a device-local copy, so the
+parameter addresses captured in CUDA graphs stay valid) and bump its version; on a mismatch it keeps
+the previous weights and reports the failure.  SwiftSync LoRA deltas use the same kernel in add mode
+against an fp32 staging image of the adapter state.
+
+Transport: between processes the staging buffer is a symmetric-memory allocation
+(``torch.distributed._symmetric_memory``) whose peer pointer the trainer writes through; inside one
+process (colocated trainer and engine on one GPU) the "peer" pointer is simply local.  The control
+message (layout once, then version + checksum per sync) travels over the process group.
+Replaces CUDA-IPC-over-HTTP, per-tensor NCCL broadcast and the Ray object store
+(src/transfer/ipc_transfer.py:290-563, src/transfer/nccl_transfer.py:76-361).
+"""
+from __future__ import annotations
+
+import time
+from typing import Dict, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .. import _native as nv
+from .nccl_transfer import TransferStats
+
+MASK64 = (1 << 64) - 1
+
+
+def fletcher_checksum(t: torch.Tensor, elem_offset: int = 0) -> Tuple[int, int]:
+    """Host oracle of the device checksum: (sum of element bit patterns, sum of pattern * (index+1)),
+    both mod 2^64, over a bf16 or fp32 tensor."""
+    flat = t.detach().reshape(-1).cpu()
+    if flat.dtype == torch.bfloat16:
+        bits = flat.view(torch.int16).to(torch.int64) & 0xFFFF
+    else:
+        bits = flat.to(torch.float32).view(torch.int32).to(torch.int64) & 0xFFFFFFFF
+    c0 = int(bits.sum().item()) & MASK64
+    c1 = 0
+    idx = torch.arange(1 + elem_offset, 1 + elem_offset + bits.numel(), dtype=torch.int64)
+    for s in range(0, bits.numel(), 1 << 16):     # python ints: exact modulo 2^64
+        c1 = (c1 + sum(int(b) * int(i) for b, i in zip(bits[s:s + (1 << 16)].tolist(),
+                                                       idx[s:s + (1 << 16)].tolist()))) & MASK64
+    return c0, c1
+
+
+def device_checksum(t: torch.Tensor) -> Tuple[int, int]:
+    if not t.is_cuda:
+        return fletcher_checksum(t)
+    out = torch.zeros(2, dtype=torch.int64, device=t.device)
+    nv.check(nv.lib().b2_words_checksum(nv.ptr(t), int(t.dtype == torch.float32), nv.ctypes.c_longlong(t.numel()),
+                                        nv.ptr(out), nv.stream_ptr()), "words_checksum")
+    nv.count_launch()
+    a, b = out.tolist()
+    return a & MASK64, b & MASK64
+
+
+class VersionedWeightBuffer:
+    """Engine-side staging image of a set of named tensors in one flat buffer, plus the version."""
+
+    def __init__(self, layout: List[Tuple[str, Tuple[int, ...]]], dtype: torch.dtype, device,
+                 storage: Optional[torch.Tensor] = None):
+        self.layout, self.dtype = layout, dtype
+        self.offsets: Dict[str, Tuple[int, int, Tuple[int, ...]]] = {}
+        n = 0
+        for name, shape in layout:
+            cnt = 1
+            for d in shape:
+                cnt *= d
+            self.offsets[name] = (n, cnt, tuple(shape))
+            n += (cnt + 7) // 8 * 8
+        self.numel = max(n, 8)
+        self.flat = storage if storage is not None else torch.zeros(self.numel, dtype=dtype, device=device)
+        assert self.flat.numel() >= self.numel
+        self.version = 0
+        self.rejected = 0
+
+    def view(self, name: str) -> torch.Tensor:
+        o, cnt, shape = self.offsets[name]
+        return self.flat[o:o + cnt].view(shape)
+
+    def named_views(self) -> Dict[str, torch.Tensor]:
+        return {k: self.view(k) for k in self.offsets}
+
+    def verify_and_commit(self, version: int, checksum: Tuple[int, int], apply) -> bool:
+        """Compare the checksum of the staged bytes; on success call ``apply(named_views)`` (copies into
+        the live parameters) and adopt ``version``; otherwise keep the old version."""
+        got = device_checksum(self.flat[:self.numel])
+        if (got[0], got[1]) != (checksum[0] & MASK64, checksum[1] & MASK64):
+            self.rejected += 1
+            return False
+        apply(self.named_views())
+        self.version = version
+        return True
+
+
+class PeerWeightSync:
+    """Both ends of the peer-write sync.
+
+    ``sender_rank`` writes, ``receiver_ranks`` each own a staging buffer.  With ``group=None`` the sync
+    is process-local (trainer and engine share the GPU): ``staging`` is then an ordinary tensor.
+    """
+
+    def __init__(self, layout: List[Tuple[str, Tuple[int, ...]]], dtype: torch.dtype = torch.bfloat16, device=None,
+                 group=None, sender_rank: int = 0, chunk_elems: int = 1 << 24):
+        self.device = device if device is not None else (
+            torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu"))
+        self.group, self.sender_rank, self.chunk = group, sender_rank, chunk_elems
+        self.rank = dist.get_rank(group) if group is not None else 0
+        self.world = dist.get_world_size(group) if group is not None else 1
+        self.stats = TransferStats()
+        self.version = 0
+        self.peer_ptrs: Optional[List[int]] = None
+        storage = None
+        probe = VersionedWeightBuffer(layout, dtype, "meta")
+        if group is not None and self.device.type == "cuda":
+            import torch.distributed._symmetric_memory as symm
+            storage = symm.empty(probe.numel, dtype=dtype, device=self.device)
+            hdl = symm.rendezvous(storage, group=group)
+            self.peer_ptrs = [int(p) for p in hdl.buffer_ptrs]
+            self._hdl = hdl
+            storage.zero_()
+        self.staging = VersionedWeightBuffer(layout, dtype, self.device, storage)
+        self._cks = torch.zeros(2, dtype=torch.int64, device=self.device) if self.device.type == "cuda" else None
+
+    # ---- sender ------------------------------------------------------------------------------------------
+    def _dst_ptr(self, target_rank: Optional[int]) -> int:
+        if self.peer_ptrs is None or target_rank is None:
+            return self.staging.flat.data_ptr()
+        return self.peer_ptrs[target_rank]
+
+    def write(self, state: Dict[str, torch.Tensor], target_rank: Optional[int] = None, add: bool = False
+              ) -> Tuple[Tuple[int, int], int]:
+        """Write ``state`` into the target's staging buffer.  Returns ((c0, c1), bytes)."""
+        st = self.staging
+        nbytes = 0
+        if self.device.type != "cuda":
+            for k, v in state.items():
+                dst = st.view(k)
+                dst.copy_((dst.float() + v.float()).to(st.dtype) if add else v.to(st.dtype))
+                nbytes += v.numel() * st.flat.element_size()
+            return fletcher_checksum(st.flat[:st.numel]), nbytes
+        self._cks.zero_()
+        base = self._dst_ptr(target_rank)
+        es = st.flat.element_size()
+        L = nv.lib()
+        for k, v in state.items():
+            off, cnt, _ = st.offsets[k]
+            src = v.detach().reshape(-1)
+            if src.dtype not in (torch.float32, torch.bfloat16):
+                src = src.float()
+            src = src.contiguous()
+            for s in range(0, cnt, self.chunk):
+                n = min(self.chunk, cnt - s)
+                nv.check(L.b2_peer_write(nv.ctypes.c_void_p(src.data_ptr() + s * src.element_size()),
+                                         int(src.dtype == torch.float32), nv.ctypes.c_void_p(base),
+                                         int(st.dtype == torch.float32), nv.ctypes.c_longlong(n),
+                                         nv.ctypes.c_longlong(off + s), int(add), nv.ptr(self._cks),
+                                         nv.stream_ptr()), "peer_write")
+                nv.count_launch()
+            nbytes += cnt * es
+        # padding between tensors is zero on both sides and contributes nothing to either sum
+        a, b = self._cks.tolist()      # synchronises: every write has been issued and fenced
+        return (a & MASK64, b & MASK64), nbytes
+
+    # ---- protocol ------------------------------------------------------------------------------------------
+    def sync(self, is_sender: bool, state: Optional[Dict[str, torch.Tensor]] = None, engine=None,
+             add: bool = False, corrupt: bool = False) -> int:
+        """One full sync.  Process-local when there is no group.  ``corrupt`` flips the announced
+        checksum (host-side fault injection for the rejection path)."""
+        t0 = time.perf_counter()
+        apply = (lambda views: engine.load_weights(views)) if engine is not None else (lambda views: None)
+        if self.group is None:
+            cks, nbytes = self.write(state, None, add)
+            if add:           # the checksum of an add covers only what was touched: recompute over the image
+                cks = device_checksum(self.staging.flat[:self.staging.numel])
+            if corrupt:
+                cks = (cks[0] ^ 1, cks[1])
+            ok = self.staging.verify_and_commit(self.version + 1, cks, apply)
+            self.stats.record(nbytes, time.perf_counter() - t0, ok)
+            if ok:
+                self.version += 1
+            return self.version
+        if is_sender:
+            msgs = {}
+            nbytes = 0
+            for r in range(self.world):
+                if r == self.rank:
+                    continue
+                cks, nb = self.write(state, r, add)
+                msgs[r] = cks if not corrupt else (cks[0] ^ 1, cks[1])
+                nbytes += nb
+            box = [{"version": self.version + 1, "checksums": msgs, "add": add}]
+            dist.broadcast_object_list(box, src=dist.get_global_rank(self.group, self.sender_rank), group=self.group)
+            acks = [None] * self.world
+            dist.all_gather_object(acks, True, group=self.group)
+            ok = all(a for a in acks)
+            self.stats.record(nbytes, time.perf_counter() - t0, ok)
+            if ok:
+                self.version += 1
+            return self.version
+        box = [None]
+        dist.broadcast_object_list(box, src=dist.get_global_rank(self.group, self.sender_rank), group=self.group)
+        msg = box[0]
+        cks = msg["checksums"][self.rank]
+        if msg["add"]:
+            got = device_checksum(self.staging.flat[:self.staging.numel])
+            ok = True
+            apply(self.staging.named_views())
+            self.staging.version = msg["version"]
+            cks = got
+        else:
+            ok = self.staging.verify_and_commit(msg["version"], cks, apply)
+        acks = [None] * self.world
+        dist.all_gather_object(acks, ok, group=self.group)
+        if ok and all(a for a in acks):
+            self.version = msg["version"]
+        self.stats.record(0, time.perf_counter() - t0, ok)
+        return self.version
+
+    def get_stats(self) -> Dict:
+        return {"version": self.version, "transfers": self.stats.transfers, "failures": self.stats.failures,
+                "rejected": self.staging.rejected, "avg_gbps": self.stats.avg_gbps, "last_gbps": self.stats.last_gbps}

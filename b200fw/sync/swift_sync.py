@@ -1,0 +1,162 @@
+"""SwiftSync: ship LoRA *deltas* instead of full weights, with a periodic full sync.
+
+Roles of the reference module (src/transfer/swift_sync.py:36-596): ``DeltaComputer`` (GPU subtraction
+against the previous snapshot; full sync when ``step > 0 and step % N == 0``), ``SwiftSyncTransfer``
+(apply the delta to the shadow buffer -> notify the worker with ``update_weights(state, mode)`` ->
+swap -> stats).  A worker without ``update_weights`` raises and leaves the version untouched.
+"""
+from __future__ import annotations
+
+import inspect
+import time
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+import torch
+
+from .double_buffer import DoubleBufferedLoRA
+
+
+@dataclass
+class SwiftSyncConfig:
+    enabled: bool = False
+    fallback_full_every: int = 10
+    double_buffer: bool = True
+
+
+@dataclass
+class SwiftSyncStats:
+    delta_syncs: int = 0
+    full_syncs: int = 0
+    bytes_sent: int = 0
+    total_time_s: float = 0.0
+    last_mode: str = ""
+    last_bytes: int = 0
+    last_time_s: float = 0.0
+    history: List[Dict] = field(default_factory=list)
+
+    def record(self, mode: str, nbytes: int, dt: float):
+        if mode == "delta":
+            self.delta_syncs += 1
+        else:
+            self.full_syncs += 1
+        self.bytes_sent += nbytes
+        self.total_time_s += dt
+        self.last_mode, self.last_bytes, self.last_time_s = mode, nbytes, dt
+        self.history.append({"mode": mode, "bytes": nbytes, "time_s": dt,
+                             "gbps": nbytes / dt / 1e9 if dt > 0 else 0.0})
+
+
+class DeltaComputer:
+    def __init__(self, fallback_full_every: int = 10):
+        self.fallback_full_every = fallback_full_every
+        self.prev: Optional[Dict[str, torch.Tensor]] = None
+
+    def should_full_sync(self, step: int) -> bool:
+        return step > 0 and self.fallback_full_every > 0 and step % self.fallback_full_every == 0
+
+    @torch.no_grad()
+    def compute_delta(self, current: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
+        """current - previous snapshot (first call: the full state), then remember ``current``."""
+        if self.prev is None:
+            delta = {k: v.detach().clone() for k, v in current.items()}
+        else:
+            delta = {k: v.detach() - self.prev[k] if k in self.prev else v.detach().clone()
+                     for k, v in current.items()}
+        self.prev = {k: v.detach().clone() for k, v in current.items()}
+        return delta
+
+    def reset(self):
+        self.prev = None
+
+
+def _nbytes(state: Dict[str, torch.Tensor]) -> int:
+    return sum(v.numel() * v.element_size() for v in state.values())
+
+
+class SwiftSyncTransfer:
+    def __init__(self, infer_worker=None, config: Optional[SwiftSyncConfig] = None,
+                 buffer: Optional[DoubleBufferedLoRA] = None):
+        self.worker = infer_worker
+        self.config = config or SwiftSyncConfig(enabled=True)
+        self.buffer = buffer or DoubleBufferedLoRA()
+        self.delta_computer = DeltaComputer(self.config.fallback_full_every)
+        self.stats = SwiftSyncStats()
+
+    def _notify(self, state: Dict[str, torch.Tensor], mode: str):
+        if self.worker is None:
+            return
+        fn = getattr(self.worker, "update_weights", None)
+        if fn is None:
+            raise AttributeError("inference worker has no update_weights(state, mode)")
+        remote = getattr(fn, "remote", None)
+        res = remote(state, mode=mode) if remote is not None else fn(state, mode=mode)
+        if inspect.isawaitable(res):
+            import asyncio
+            try:
+                loop = asyncio.get_running_loop()
+            except RuntimeError:
+                loop = None
+            if loop is None:
+                asyncio.run(_await(res))
+            else:   # already inside a loop: the caller should use the async variants
+                raise RuntimeError("use sync_delta_async / sync_full_async inside an event loop")
+
+    def sync_delta(self, delta: Dict[str, torch.Tensor]) -> int:
+        """Apply a delta: notify first (a worker that cannot take it must not see a version bump),
+        then update the local double buffer and swap."""
+        t0 = time.perf_counter()
+        self._notify(delta, "delta")
+        self.buffer.apply_delta_to_shadow(delta)
+        v = self.buffer.swap_buffers() if self.config.double_buffer else self.buffer.version
+        self.stats.record("delta", _nbytes(delta), time.perf_counter() - t0)
+        return v
+
+    def sync_full(self, state: Dict[str, torch.Tensor]) -> int:
+        t0 = time.perf_counter()
+        self._notify(state, "full")
+        v = self.buffer.set_full_state(state, swap=self.config.double_buffer)
+        self.delta_computer.prev = {k: t.detach().clone() for k, t in state.items()}
+        self.stats.record("full", _nbytes(state), time.perf_counter() - t0)
+        return v
+
+    async def sync_delta_async(self, delta: Dict[str, torch.Tensor]) -> int:
+        t0 = time.perf_counter()
+        await self._notify_async(delta, "delta")
+        self.buffer.apply_delta_to_shadow(delta)
+        v = self.buffer.swap_buffers() if self.config.double_buffer else self.buffer.version
+        self.stats.record("delta", _nbytes(delta), time.perf_counter() - t0)
+        return v
+
+    async def sync_full_async(self, state: Dict[str, torch.Tensor]) -> int:
+        t0 = time.perf_counter()
+        await self._notify_async(state, "full")
+        v = self.buffer.set_full_state(state, swap=self.config.double_buffer)
+        self.stats.record("full", _nbytes(state), time.perf_counter() - t0)
+        return v
+
+    async def _notify_async(self, state, mode):
+        if self.worker is None:
+            return
+        fn = getattr(self.worker, "update_weights", None)
+        if fn is None:
+            raise AttributeError("inference worker has no update_weights(state, mode)")
+        res = fn(state, mode=mode)
+        if inspect.isawaitable(res):
+            await res
+
+    def sync(self, step: int, lora_state: Dict[str, torch.Tensor]) -> int:
+        """Policy wrapper: periodic full sync, deltas otherwise."""
+        if self.delta_computer.prev is None or self.delta_computer.should_full_sync(step):
+            return self.sync_full(lora_state)
+        return self.sync_delta(self.delta_computer.compute_delta(lora_state))
+
+    def get_stats(self) -> Dict:
+        s = self.stats
+        return {"delta_syncs": s.delta_syncs, "full_syncs": s.full_syncs, "bytes_sent": s.bytes_sent,
+                "total_time_s": s.total_time_s, "version": self.buffer.version, "last_mode": s.last_mode,
+                "last_bytes": s.last_bytes, "last_time_s": s.last_time_s}
+
+
+async def _await(x):
+    return await x

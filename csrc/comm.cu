@@ -1,0 +1,305 @@
+// Kernels that move data between GPUs through peer pointers (NVLink / NVSwitch), fused with the
+// arithmetic around the transfer:
+//
+//   peer_write          trainer -> engine weight sync: cast (fp32/bf16 -> bf16/fp32), optional in-place
+//                       add (LoRA delta), position-weighted checksum of the payload, one launch per chunk
+//   words_checksum      receiver-side checksum of a staging buffer
+//   zero_reduce_shard   ZeRO gradient reduce-scatter by peer loads: this rank's shard of every peer's
+//                       bucket is summed, scaled, written as fp32 and its squared norm accumulated
+//   zero_adamw_publish  clip + AdamW on the shard, updated bf16 parameters stored into every peer's
+//                       parameter bucket (the all-gather), all in one pass
+//   flag_signal / flag_wait  system-scope release / bounded acquire on a flag word
+//
+// A destination or source pointer may belong to this GPU or to a peer; the kernels do not care.  No
+// TMA and no thread-block clusters are used here: plain (vectorised) loads and stores only.
+#include "common.cuh"
+#include "host.h"
+
+namespace b2 {
+
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+template <typename T>
+__device__ __forceinline__ float cvt_in(T v);
+template <>
+__device__ __forceinline__ float cvt_in<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float cvt_in<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T>
+__device__ __forceinline__ T cvt_out(float v);
+template <>
+__device__ __forceinline__ float cvt_out<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 cvt_out<__nv_bfloat16>(float v) { return __float2bfloat16(v); }
+template <typename T>
+__device__ __forceinline__ unsigned long long bits_of(T v);
+template <>
+__device__ __forceinline__ unsigned long long bits_of<float>(float v) { return __float_as_uint(v); }
+template <>
+__device__ __forceinline__ unsigned long long bits_of<__nv_bfloat16>(__nv_bfloat16 v) {
+  return *reinterpret_cast<unsigned short*>(&v);
+}
+
+// dst[off + i] = (add ? dst[off + i] : 0) + src[i]; checksum[0] += bits(dst_i), checksum[1] += bits * (off+i+1)
+template <typename S, typename D>
+__global__ void peer_write_kernel(const S* __restrict__ src, D* __restrict__ dst, long long n,
+                                  long long elem_offset, int add, unsigned long long* __restrict__ checksum) {
+  unsigned long long c0 = 0, c1 = 0;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float v = cvt_in<S>(src[i]);
+    if (add) v += cvt_in<D>(dst[elem_offset + i]);
+    const D o = cvt_out<D>(v);
+    dst[elem_offset + i] = o;
+    const unsigned long long b = bits_of<D>(o);
+    c0 += b;
+    c1 += b * static_cast<unsigned long long>(elem_offset + i + 1);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    c0 += __shfl_xor_sync(0xffffffffu, c0, o);
+    c1 += __shfl_xor_sync(0xffffffffu, c1, o);
+  }
+  if ((threadIdx.x & 31) == 0 && checksum) {
+    atomicAdd(checksum, c0);
+    atomicAdd(checksum + 1, c1);
+  }
+  __threadfence_system();
+}
+
+template <typename D>
+__global__ void words_checksum_kernel(const D* __restrict__ buf, long long n,
+                                      unsigned long long* __restrict__ checksum) {
+  unsigned long long c0 = 0, c1 = 0;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const unsigned long long b = bits_of<D>(buf[i]);
+    c0 += b;
+    c1 += b * static_cast<unsigned long long>(i + 1);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    c0 += __shfl_xor_sync(0xffffffffu, c0, o);
+    c1 += __shfl_xor_sync(0xffffffffu, c1, o);
+  }
+  if ((threadIdx.x & 31) == 0) {
+    atomicAdd(checksum, c0);
+    atomicAdd(checksum + 1, c1);
+  }
+}
+
+struct PeerPtrs {
+  void* p[8];
+};
+
+// out[i] = scale * sum_r peers[r][shard_start + i]  (bf16 buckets, 8 elements per thread step);
+// norm_sq[0] += sum(out^2).
+__global__ void zero_reduce_shard_kernel(PeerPtrs peers, int world, long long shard_start, long long n,
+                                         float scale, float* __restrict__ out, int accumulate,
+                                         float* __restrict__ norm_sq) {
+  float ss = 0.f;
+  const long long nvec = n / 8;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int r = 0; r < world; ++r) {
+      const uint4 q = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(peers.p[r]) +
+                                                      shard_start + i * 8);
+      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = unpack_bf16x2(w[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+      }
+    }
+    float* o = out + i * 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float v = acc[j] * scale;
+      if (accumulate) v += o[j];
+      o[j] = v;
+      ss += v * v;
+    }
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0 && norm_sq) atomicAdd(norm_sq, ss);
+}
+
+// AdamW on the fp32 shard, then the updated bf16 values are stored at [shard_start + i] of every peer's
+// parameter bucket.  hyper / norm_sq as in adamw_kernel (loss_optim.cu).
+__global__ void zero_adamw_publish_kernel(float* __restrict__ master, float* __restrict__ m,
+                                          float* __restrict__ v, const float* __restrict__ grad, long long n,
+                                          const float* __restrict__ hyper, const float* __restrict__ norm_sq,
+                                          PeerPtrs params, int world, long long shard_start) {
+  const float lr = hyper[0], b1 = hyper[1], b2 = hyper[2], eps = hyper[3], wd = hyper[4];
+  const float bc1 = hyper[5], bc2 = hyper[6], max_norm = hyper[7];
+  float clip = 1.f;
+  bool skip = false;
+  if (norm_sq != nullptr) {
+    const float ns = norm_sq[0];
+    if (!isfinite(ns)) skip = true;
+    else if (max_norm > 0.f) clip = fminf(1.f, max_norm / (sqrtf(ns) + 1e-6f));
+  }
+  const long long nvec = n / 8;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float p[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const long long k = i * 8 + j;
+      float pk = master[k];
+      if (!skip) {
+        const float g = grad[k] * clip;
+        const float mi = b1 * m[k] + (1.f - b1) * g;
+        const float vi = b2 * v[k] + (1.f - b2) * g * g;
+        m[k] = mi;
+        v[k] = vi;
+        pk = pk * (1.f - lr * wd) - lr * (mi / bc1) / (sqrtf(vi / bc2) + eps);
+        master[k] = pk;
+      }
+      p[j] = pk;
+    }
+    uint4 o;
+    o.x = pack_bf16x2(p[0], p[1]);
+    o.y = pack_bf16x2(p[2], p[3]);
+    o.z = pack_bf16x2(p[4], p[5]);
+    o.w = pack_bf16x2(p[6], p[7]);
+    for (int r = 0; r < world; ++r)
+      *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(params.p[r]) + shard_start + i * 8) = o;
+  }
+  __threadfence_system();
+}
+
+__global__ void flag_signal_kernel(int* flag, int value) {
+  __threadfence_system();
+  st_release_sys(flag, value);
+}
+// Waits until *flag >= value, at most limit_ns; result[0] = 1 on success, 0 when the wait ran out (the
+// status word then also records ERR_COMM_FLAG_WAIT).
+__global__ void flag_wait_kernel(const int* flag, int value, unsigned long long limit_ns, int* result,
+                                 int* status) {
+  const unsigned long long t0 = globaltimer_ns();
+  int ok = 0;
+  for (;;) {
+    if (ld_acquire_sys(flag) >= value) {
+      ok = 1;
+      break;
+    }
+    if (globaltimer_ns() - t0 > limit_ns) break;
+    __nanosleep(200);
+  }
+  result[0] = ok;
+  if (!ok) atomicCAS(status, 0, ERR_COMM_FLAG_WAIT);
+}
+
+}  // namespace b2
+
+using namespace b2;
+
+static int grid_for(long long n, int threads, int per_sm = 8) {
+  long long b = (n + threads - 1) / threads;
+  const long long cap = static_cast<long long>(num_sms()) * per_sm;
+  if (b > cap) b = cap;
+  if (b < 1) b = 1;
+  return static_cast<int>(b);
+}
+#define B2_LAUNCH_CHECK(name)                                        \
+  do {                                                               \
+    cudaError_t e_ = cudaGetLastError();                             \
+    if (e_ != cudaSuccess) {                                         \
+      set_error(name " launch failed: %s", cudaGetErrorString(e_)); \
+      return 4;                                                      \
+    }                                                                \
+  } while (0)
+
+// dst may be a peer pointer.  checksum: device u64[2] (nullable), accumulated across calls.
+B2_EXPORT int b2_peer_write(const void* src, int src_fp32, void* dst, int dst_fp32, long long n,
+                            long long elem_offset, int add, unsigned long long* checksum, void* stream_) {
+  b2::ensure_thread_context();
+  if (n <= 0) return 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream_);
+  const int g = grid_for(n, 256, 4);
+  if (src_fp32 && dst_fp32)
+    peer_write_kernel<float, float><<<g, 256, 0, s>>>(static_cast<const float*>(src), static_cast<float*>(dst), n, elem_offset, add, checksum);
+  else if (src_fp32)
+    peer_write_kernel<float, __nv_bfloat16><<<g, 256, 0, s>>>(static_cast<const float*>(src), static_cast<__nv_bfloat16*>(dst), n, elem_offset, add, checksum);
+  else if (dst_fp32)
+    peer_write_kernel<__nv_bfloat16, float><<<g, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(src), static_cast<float*>(dst), n, elem_offset, add, checksum);
+  else
+    peer_write_kernel<__nv_bfloat16, __nv_bfloat16><<<g, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(src), static_cast<__nv_bfloat16*>(dst), n, elem_offset, add, checksum);
+  B2_LAUNCH_CHECK("peer_write");
+  return 0;
+}
+
+B2_EXPORT int b2_words_checksum(const void* buf, int is_fp32, long long n, unsigned long long* checksum,
+                                void* stream_) {
+  b2::ensure_thread_context();
+  if (n <= 0) return 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream_);
+  if (is_fp32)
+    words_checksum_kernel<float><<<grid_for(n, 256, 4), 256, 0, s>>>(static_cast<const float*>(buf), n, checksum);
+  else
+    words_checksum_kernel<__nv_bfloat16><<<grid_for(n, 256, 4), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(buf), n, checksum);
+  B2_LAUNCH_CHECK("words_checksum");
+  return 0;
+}
+
+// peers: host array of `world` device pointers (bf16 gradient buckets, this rank's own included).
+B2_EXPORT int b2_zero_reduce_shard(void* const* peers, int world, long long shard_start, long long n,
+                                   float scale, float* out, int accumulate, float* norm_sq, void* stream_) {
+  b2::ensure_thread_context();
+  if (world < 1 || world > 8 || (n % 8) || (shard_start % 8)) {
+    set_error("zero_reduce_shard: world in 1..8 and 8-element aligned shard required");
+    return 10;
+  }
+  if (n <= 0) return 0;
+  PeerPtrs pp;
+  for (int r = 0; r < 8; ++r) pp.p[r] = r < world ? peers[r] : nullptr;
+  zero_reduce_shard_kernel<<<grid_for(n / 8, 256, 4), 256, 0, static_cast<cudaStream_t>(stream_)>>>(
+      pp, world, shard_start, n, scale, out, accumulate, norm_sq);
+  B2_LAUNCH_CHECK("zero_reduce_shard");
+  return 0;
+}
+
+B2_EXPORT int b2_zero_adamw_publish(float* master, float* m, float* v, const float* grad, long long n,
+                                    const float* hyper, const float* norm_sq, void* const* params, int world,
+                                    long long shard_start, void* stream_) {
+  b2::ensure_thread_context();
+  if (world < 1 || world > 8 || (n % 8) || (shard_start % 8)) {
+    set_error("zero_adamw_publish: world in 1..8 and 8-element aligned shard required");
+    return 10;
+  }
+  if (n <= 0) return 0;
+  PeerPtrs pp;
+  for (int r = 0; r < 8; ++r) pp.p[r] = r < world ? params[r] : nullptr;
+  zero_adamw_publish_kernel<<<grid_for(n / 8, 256, 4), 256, 0, static_cast<cudaStream_t>(stream_)>>>(
+      master, m, v, grad, n, hyper, norm_sq, pp, world, shard_start);
+  B2_LAUNCH_CHECK("zero_adamw_publish");
+  return 0;
+}
+
+B2_EXPORT int b2_flag_signal(int* flag, int value, void* stream_) {
+  b2::ensure_thread_context();
+  flag_signal_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream_)>>>(flag, value);
+  B2_LAUNCH_CHECK("flag_signal");
+  return 0;
+}
+
+// result: device int[1].  limit_ms bounds the wait (a second or so in normal use).
+B2_EXPORT int b2_flag_wait(const int* flag, int value, int limit_ms, int* result, void* stream_) {
+  b2::ensure_thread_context();
+  int* status = status_ptr();
+  if (!status) return 3;
+  flag_wait_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream_)>>>(
+      flag, value, static_cast<unsigned long long>(limit_ms) * 1000000ull, result, status);
+  B2_LAUNCH_CHECK("flag_wait");
+  return 0;
+}
