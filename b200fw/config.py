@@ -192,13 +192,13 @@ def build_colocate_config(yaml_cfg: Dict[str, Any], overrides: Optional[Dict[str
         v = get_nested(yaml_cfg, path)
         if v is not None:
             setattr(cfg, name, v)
-    if mode == "sft":      # SFT previews read their sampling knobs from inference_preview.*
-        for key, name in (("max_tokens", "max_tokens"), ("temperature", "temperature"), ("top_p", "top_p"),
-                          ("enabled", "inference_preview_enabled")):
-            v = get_nested(yaml_cfg, f"inference_preview.{key}")
-            if v is not None:
-                setattr(cfg, name, v)
-            known.add(f"inference_preview.{key}")
+    for key, name in (("max_tokens", "max_tokens"), ("temperature", "temperature"), ("top_p", "top_p"),
+                      ("enabled", "inference_preview_enabled")):
+        known.add(f"inference_preview.{key}")
+        v = get_nested(yaml_cfg, f"inference_preview.{key}")
+        # SFT previews read their sampling knobs from inference_preview.*; GRPO reads rollout.*
+        if v is not None and (mode == "sft" or key == "enabled"):
+            setattr(cfg, name, v)
     for k, v in (overrides or {}).items():
         if v is not None:
             if not hasattr(cfg, k):

@@ -1,0 +1,290 @@
+"""Config loading / validation, the colocate loop (native, mock and mocked-vLLM back ends), weight sync
+paths, and host-side fault injection."""
+import asyncio
+import glob
+import json
+import os
+import tempfile
+import threading
+
+import pytest
+import torch
+
+from b200fw.config import (ColocateConfig, build_colocate_config, get_nested, load_yaml_config,
+                           validate_parallel_config)
+from b200fw.orch import ColocateOrchestrator, OrchestratorState
+from b200fw.sync import (DeltaComputer, DoubleBufferedLoRA, IPCWeightTransfer, PeerWeightSync, SwiftSyncTransfer,
+                         VLLMClient, WeightUpdateManager, classify_error, fletcher_checksum)
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_yaml_mapping_overrides_and_unknown_keys():
+    y = {"model": {"name_or_path": "/m", "max_seq_len": 512}, "runtime": {"tp_size": 2, "dp_size": 4, "precision": "fp32"},
+         "distributed": {"pp_size": 1, "zero_stage": 3}, "training": {"mode": "sft", "batch_size": 8},
+         "lora": {"rank": 0, "dropout": 0.1}, "inference_preview": {"max_tokens": 9}, "bogus": {"key": 1}}
+    cfg, unknown = build_colocate_config(y, {"total_iterations": 3, "learning_rate": None})
+    assert (cfg.model_path, cfg.max_seq_len, cfg.tp_size, cfg.dp_size, cfg.amp_dtype) == ("/m", 512, 2, 4, "fp32")
+    assert cfg.zero_stage == 3            # distributed.zero_stage is honoured when training.zero_stage is absent
+    assert cfg.max_tokens == 9 and cfg.total_iterations == 3 and cfg.learning_rate == 1e-5
+    assert unknown == ["bogus.key"]
+    y["training"]["zero_stage"] = 2
+    assert build_colocate_config(y)[0].zero_stage == 2
+    assert get_nested(y, "runtime.tp_size") == 2 and get_nested(y, "a.b", 7) == 7
+    with pytest.raises(KeyError):
+        build_colocate_config({}, {"nope": 1})
+
+
+def test_parallel_validation_rules():
+    ok = ColocateConfig(tp_size=2, dp_size=2, pp_size=2, num_micro_batches=2, batch_size=8, zero_stage=1, training_mode="sft")
+    validate_parallel_config(ok, 8)
+    for bad, world in ((dict(tp_size=2), 8), (dict(num_micro_batches=1), 8), (dict(batch_size=6), 8),
+                       (dict(zero_stage=2), 8), (dict(training_mode="grpo"), 8), (dict(amp_dtype="int8"), 8)):
+        c = ColocateConfig(**{**dict(tp_size=2, dp_size=2, pp_size=2, num_micro_batches=2, batch_size=8, zero_stage=1,
+                                     training_mode="sft"), **bad})
+        with pytest.raises(ValueError):
+            validate_parallel_config(c, world if "tp_size" not in bad else 16)
+
+
+def test_every_shipped_config_parses_and_validates():
+    n = 0
+    for f in glob.glob(os.path.join(ROOT, "configs", "**", "*.yaml"), recursive=True):
+        y = load_yaml_config(f)
+        if "training" not in y:
+            continue
+        cfg, unknown = build_colocate_config(y)
+        assert unknown == [], (f, unknown)
+        validate_parallel_config(cfg, cfg.tp_size * cfg.dp_size * cfg.pp_size)
+        n += 1
+    assert n > 40
+
+
+def _run(cfg, **kw):
+    async def go():
+        o = ColocateOrchestrator(cfg, **kw)
+        await o.initialize()
+        await o.run()
+        s = o.get_summary()
+        await o.shutdown()
+        return o, s
+    return asyncio.run(go())
+
+
+def _tiny_cfg(tmp, **over):
+    base = dict(model_preset="tiny128", training_mode="grpo", total_iterations=3, batch_size=2, num_samples_per_prompt=2,
+                max_tokens=6, max_seq_len=64, lora_rank=0, grpo_beta=0.01, gradient_accumulation_steps=1, amp_dtype="fp32",
+                inference_backend="native", synthetic_data=True, synthetic_prompt_len=12, max_data_samples=64,
+                kv_num_blocks=64, warmup_steps=0, output_dir=os.path.join(tmp, "out"),
+                checkpoint_save_dir=os.path.join(tmp, "ckpt"), tensorboard=False, learning_rate=1e-3)
+    base.update(over)
+    return ColocateConfig(**base)
+
+
+def test_colocate_grpo_native_engine_full_loop():
+    with tempfile.TemporaryDirectory() as d:
+        cfg = _tiny_cfg(d, icepop_enabled=True, c3po_plus_enabled=True, c3po_plus_token_budget=4,
+                        c3po_plus_target_batch_tokens=64, checkpoint_save_interval=2)
+        o, s = _run(cfg)
+        assert o.state == OrchestratorState.DONE and s["results"]["failed_iterations"] == 0
+        assert s["results"]["final_weights_version"] == 3 and s["weight_sync"]["transfers"] == 3
+        per_iter = ["inferring", "rewarding", "training", "sleeping", "syncing"]
+        assert o.state_log[:5] == per_iter and o.state_log[-1] == "done"
+        assert all(m.tokens_generated > 0 and m.train_metrics.grad_norm > 0 for m in o.metrics)
+        out = cfg.output_dir
+        for name in ("config_snapshot.json", "run_summary.json", "metrics_rank0.jsonl", "loss_curve.csv",
+                     "memory_report.json", "memory_timeline_rank0.json"):
+            assert os.path.exists(os.path.join(out, name)), name
+        rows = [json.loads(l) for l in open(os.path.join(out, "metrics_rank0.jsonl"))]
+        assert len(rows) == 3 and {"loss", "avg_reward", "t_training", "weights_version"} <= set(rows[0])
+        assert {"iter_2", "latest", "final"} <= set(os.listdir(cfg.checkpoint_save_dir))
+        # the rollout engine really follows the trainer: after the last sync its weights equal the export
+        from b200fw.model.hf_io import hf_named_tensors
+        want = o.train_engine.export_weights()
+        got = dict(hf_named_tensors(o.infer_engine.model))
+        assert all(torch.equal(want[k], got[k]) for k in want)
+
+
+def test_colocate_lora_swiftsync_and_async_pipeline_staleness():
+    with tempfile.TemporaryDirectory() as d:
+        cfg = _tiny_cfg(d, lora_rank=4, swift_sync_enabled=True, swift_sync_fallback_full_every=2,
+                        async_pipeline_enabled=True, async_pipeline_max_staleness=1, total_iterations=4,
+                        checkpoint_save_enabled=False)
+        o, s = _run(cfg)
+        assert s["results"]["failed_iterations"] == 0
+        sw = s["swift_sync"]
+        assert sw["full_syncs"] >= 2 and sw["delta_syncs"] >= 1 and sw["version"] == 4
+        assert max(m.rollout_staleness for m in o.metrics) <= 1
+
+
+def test_colocate_sft_mode_and_resume():
+    with tempfile.TemporaryDirectory() as d:
+        cfg = _tiny_cfg(d, training_mode="sft", inference_preview_enabled=False, total_iterations=3)
+        o, s = _run(cfg)
+        assert s["results"]["final_loss"] is not None and o.state_log.count("training") == 3
+        cfg2 = _tiny_cfg(d, training_mode="sft", inference_preview_enabled=False, total_iterations=1,
+                         resume_from=os.path.join(cfg.checkpoint_save_dir, "final"))
+        o2, _ = _run(cfg2)
+        assert o2.train_engine.step_count == 4
+
+
+class _FakeResp:
+    def raise_for_status(self):
+        pass
+
+
+class _FakeHttp:
+    """Stand-in for the vLLM HTTP server: records calls, can fail the first N wake-ups."""
+
+    def __init__(self, fail_wake=0, fail_update=False):
+        self.calls, self.fail_wake, self.fail_update = [], fail_wake, fail_update
+
+    async def post(self, url, **kw):
+        self.calls.append(url.split("/")[-1].split("?")[0])
+        if "wake_up" in url and self.fail_wake > 0:
+            self.fail_wake -= 1
+            raise ConnectionError("server busy")
+        if "update_weights" in url and self.fail_update:
+            raise ValueError("bad payload")
+        return _FakeResp()
+
+    async def get(self, url, **kw):
+        self.calls.append("health")
+        return _FakeResp()
+
+
+def test_vllm_client_retry_taxonomy_and_ipc_chunking():
+    assert classify_error(ValueError()) == "fatal" and classify_error(RuntimeError("CUDA out of memory")) == "oom"
+    assert classify_error(ConnectionError()) == "retry"
+    http = _FakeHttp(fail_wake=2)
+    c = VLLMClient("http://x", max_retries=3, backoff_s=0.0, client=http)
+    asyncio.run(c.wake_up())
+    assert http.calls.count("wake_up") == 3
+    state = {f"w{i}": torch.randn(4, 4) for i in range(10)}
+    http = _FakeHttp()
+    ipc = IPCWeightTransfer(VLLMClient("http://x", backoff_s=0.0, client=http), chunk_size=4)
+    assert [len(c) for c in ipc._chunk_handles(ipc.build_ipc_handles(state))] == [4, 4, 2]
+    asyncio.run(ipc.push_weights(state))
+    assert http.calls == ["reset_prefix_cache", "sleep", "init_weight_transfer_engine", "start_weight_update",
+                          "update_weights", "update_weights", "update_weights", "finish_weight_update", "wake_up"]
+    # a non-retriable failure mid-transfer still wakes the server up, then re-raises
+    http = _FakeHttp(fail_update=True)
+    ipc = IPCWeightTransfer(VLLMClient("http://x", backoff_s=0.0, client=http), chunk_size=4)
+    with pytest.raises(ValueError):
+        asyncio.run(ipc.push_weights(state))
+    assert http.calls[-1] == "wake_up" and ipc.stats.failures == 1
+    assert len(IPCWeightTransfer.checksum(state)) == 32
+
+
+def test_weight_update_manager_rolls_back():
+    m = torch.nn.Linear(4, 4)
+    mgr = WeightUpdateManager(m)
+    before = m.weight.detach().clone()
+    assert mgr.update_weights({"weight": torch.ones(4, 4)}) and mgr.version == 1
+    assert not mgr.update_weights({"weight": torch.ones(4, 4) * 2, "bias": torch.full((4,), float("nan"))})
+    assert torch.equal(m.weight, torch.ones(4, 4)) and mgr.rollbacks == 1 and mgr.version == 1
+    assert not mgr.update_weights({"weight": torch.ones(3, 3)})
+    assert not torch.equal(before, m.weight.detach())
+
+
+def test_swift_sync_delta_math_policy_and_double_buffer():
+    dc = DeltaComputer(fallback_full_every=3)
+    s0 = {"a": torch.ones(3)}
+    assert torch.equal(dc.compute_delta(s0)["a"], torch.ones(3))           # first call: full state
+    assert torch.equal(dc.compute_delta({"a": torch.full((3,), 1.5)})["a"], torch.full((3,), 0.5))
+    assert [dc.should_full_sync(i) for i in range(7)] == [False, False, False, True, False, False, True]
+    db = DoubleBufferedLoRA({"a": torch.zeros(2)})
+    db.apply_delta_to_shadow({"a": torch.ones(2)})
+    assert torch.equal(db.get_active_state()["a"], torch.zeros(2))           # not visible before the swap
+    assert db.swap_buffers() == 1 and torch.equal(db.get_active_state()["a"], torch.ones(2))
+    db.apply_delta_to_shadow({"a": torch.ones(2)})                           # shadow was levelled after the swap
+    db.swap_buffers()
+    assert torch.equal(db.get_active_state()["a"], torch.full((2,), 2.0)) and db.version == 2
+
+    class W:
+        def __init__(self):
+            self.seen = []
+
+        def update_weights(self, state, mode="full"):
+            self.seen.append(mode)
+
+    w = W()
+    t = SwiftSyncTransfer(w)
+    t.sync_full({"a": torch.zeros(2)})
+    t.sync_delta({"a": torch.ones(2)})
+    assert w.seen == ["full", "delta"] and t.get_stats()["version"] == 2 and t.stats.bytes_sent == 16
+    t2 = SwiftSyncTransfer(object())                                         # worker without update_weights
+    with pytest.raises(AttributeError):
+        t2.sync_delta({"a": torch.ones(2)})
+    assert t2.buffer.version == 0
+
+
+def test_double_buffer_swap_under_threads():
+    db = DoubleBufferedLoRA({"a": torch.zeros(8)})
+    def work():
+        for _ in range(50):
+            db.apply_delta_to_shadow({"a": torch.ones(8)})
+            db.swap_buffers()
+    ts = [threading.Thread(target=work) for _ in range(4)]
+    [t.start() for t in ts]
+    [t.join() for t in ts]
+    assert db.version == 200 and db.swap_count == 200
+    a = db.get_active_state()["a"]
+    assert torch.all(a == a[0])                                              # never torn
+
+
+def test_peer_write_checksum_rejects_corruption():
+    layout = [("w", (6, 5)), ("b", (7,))]
+    ps = PeerWeightSync(layout, torch.bfloat16, torch.device("cpu"))
+    got = {}
+
+    class Eng:
+        def load_weights(self, views):
+            got.update({k: v.clone() for k, v in views.items()})
+
+    state = {"w": torch.randn(6, 5), "b": torch.randn(7)}
+    assert ps.sync(True, state, Eng()) == 1 and torch.equal(got["w"], state["w"].to(torch.bfloat16))
+    got.clear()
+    assert ps.sync(True, {"w": state["w"] * 2, "b": state["b"]}, Eng(), corrupt=True) == 1     # version kept
+    assert got == {} and ps.get_stats()["rejected"] == 1
+    c0, c1 = fletcher_checksum(torch.tensor([1.0, 2.0], dtype=torch.bfloat16))
+    assert c0 == 0x3F80 + 0x4000 and c1 == 0x3F80 + 2 * 0x4000
+
+
+def _nccl_worker(rank, world):
+    import torch.distributed as dist
+    from b200fw.sync import NCCLWeightTransfer
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    t = NCCLWeightTransfer()
+    if rank == 0:
+        state = {"a": torch.arange(6.0).reshape(2, 3), "b": torch.ones(4)}
+        return t.broadcast_weights(state)
+    out = t.receive_weights({"a": torch.zeros(2, 3), "b": torch.zeros(4)})
+    assert torch.equal(out["a"], torch.arange(6.0).reshape(2, 3)) and t.version == 1
+    return t.version
+
+
+def test_nccl_transfer_baseline_over_gloo():
+    from _dist_util import run_ranks
+    assert run_ranks(_nccl_worker, 2) == [1, 1]
+
+
+def _dead_rank_worker(rank, world):
+    """Host-side failure: rank 1 never joins the collective; rank 0's bounded wait raises."""
+    import datetime
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=3))
+    if rank == 1:
+        return "left"
+    from b200fw.dist.comm import AsyncAllReduce
+    h = AsyncAllReduce().launch(torch.ones(4), dist.group.WORLD)
+    try:
+        h.wait(timeout_sec=1.0)
+    except RuntimeError as e:
+        return f"detected: {e}"
+    return "not detected"
+
+
+def test_missing_rank_is_detected_by_bounded_wait():
+    from _dist_util import run_ranks
+    res = run_ranks(_dead_rank_worker, 2)
+    assert res[1] == "left" and res[0].startswith("detected")

@@ -1,0 +1,154 @@
+"""Observability helpers, reward / data, and the disaggregated loop over gloo (2 trainers + 2 engines)."""
+import json
+import os
+import tempfile
+
+import torch
+
+from b200fw.obs import (ArtifactWriter, CommProfiler, ComputeProfiler, EvalMetrics, MemoryBreakdown, MemoryManager,
+                        MemoryProfiler, MemoryReport, MetricsCollector, ScheduleVisualizer, compute_bleu4,
+                        compute_exact_match, compute_token_f1, get_logger, setup_logger)
+
+
+def test_metrics_collector_and_artifacts():
+    m = MetricsCollector()
+    for i, v in enumerate([1.0, 2.0, 3.0]):
+        m.record("loss", v, i)
+    with m.timer("step"):
+        pass
+    s = m.summary()
+    assert s["loss"]["mean"] == 2.0 and s["loss"]["last"] == 3.0 and s["step"]["count"] == 1
+    assert m.get_latest("loss") == 3.0 and m.get_average("loss", last_n=2) == 2.5
+
+    class TB:
+        def __init__(self):
+            self.rows = []
+
+        def add_scalar(self, k, v, s):
+            self.rows.append((k, v, s))
+
+    tb = TB()
+    m.export_tensorboard(tb, "train/")
+    assert tb.rows[0] == ("train/loss", 1.0, 0)
+    with tempfile.TemporaryDirectory() as d:
+        w0, w1 = ArtifactWriter(d, 0, 2), ArtifactWriter(d, 1, 2)
+        assert w0.write_json("run_summary.json", {"a": 1}) and w1.write_json("run_summary.json", {"a": 2}) is None
+        w1.append_jsonl("metrics", {"x": 1})
+        w1.write_json("memory_timeline.json", [1], all_ranks=True)
+        assert sorted(os.listdir(d)) == ["memory_timeline_rank1.json", "metrics_rank1.jsonl", "run_summary.json"]
+        assert json.load(open(os.path.join(d, "run_summary.json"))) == {"a": 1}
+
+
+def test_profilers_formulas():
+    assert abs(CommProfiler.bus_bandwidth("all_reduce", 10 ** 9, 8, 1.0) - 1750.0) < 1e-6
+    assert abs(CommProfiler.bus_bandwidth("all_gather", 8 * 10 ** 8, 8, 1.0) - 700.0) < 1e-6
+    r = CommProfiler.fused_roofline(flops=1.0737e12, wire_bytes=146.8e6, ms=1.2, peak_tflops=1392.7, link_gbs=770.0)
+    assert r["bound"] == "compute" and abs(r["t_compute_ms"] - 0.771) < 0.01 and 0.6 < r["fraction"] < 0.7
+    cp = CommProfiler()
+    cp.add("all_reduce", 1 << 20, 8, 0.1)
+    cp.set_step_time(1.0)
+    s = cp.get_summary()
+    assert s["ops"]["all_reduce"]["count"] == 1 and abs(s["comm_ratio"] - 0.1) < 1e-9
+    # the reference formula: L*2*B*S*(4H^2+3HI) + 2*B*S*H*V, x3 for full fine-tuning
+    f = ComputeProfiler.reference_formula_flops(L=2, B=1, S=4, H=8, I=16, V=32, full=True)
+    assert f == 3 * (2 * 2 * 4 * (4 * 64 + 3 * 8 * 16) + 2 * 4 * 8 * 32)
+    from b200fw.model import PRESETS
+    ex = ComputeProfiler.exact_flops(PRESETS["qwen3-0.6b"], 8, 1024)
+    assert 3.0e13 < ex < 3.4e13
+    prof = ComputeProfiler(peak_tflops=1000.0)
+    assert abs(prof.compute_mfu(5e14, 1.0) - 0.5) < 1e-9
+
+
+def test_timeline_gantt_and_chrome_trace():
+    v = ScheduleVisualizer()
+    v.add_event("F0", "forward", "stage0", 0, 10)
+    v.add_event("B0", "backward", "stage0", 20, 40)
+    v.add_event("F0", "forward", "stage1", 10, 20)
+    g = v.ascii_gantt(40)
+    assert "stage0" in g and "F" in g and "B" in g
+    tr = v.chrome_trace()
+    assert len([e for e in tr["traceEvents"] if e["ph"] == "X"]) == 3
+    u = v.utilisation()
+    assert abs(u["stage0"]["utilisation"] - 0.75) < 1e-9 and abs(u["stage1"]["bubble_ratio"] - 0.75) < 1e-9
+    assert ScheduleVisualizer.compare(v, v)["speedup"] == 1.0
+
+
+def test_memory_helpers_on_cpu():
+    p = MemoryProfiler()
+    s = p.snapshot("x")
+    assert s.allocated_gb == 0.0 and p.timeline()[0]["tag"] == "x"
+    b = MemoryBreakdown.estimate(600_000_000, dp=8, zero_stage=3, batch_tokens=8192, hidden=1024, layers=28,
+                                 vocab=151936, intermediate=3072)
+    b1 = MemoryBreakdown.estimate(600_000_000, dp=8, zero_stage=1, batch_tokens=8192, hidden=1024, layers=28,
+                                  vocab=151936, intermediate=3072)
+    assert b.params_gb < b1.params_gb and b.grads_gb < b1.grads_gb and abs(b.optimizer_gb - b1.optimizer_gb) < 1e-9
+    rep = MemoryReport.from_profiler(p, b)
+    assert "static estimate" in rep.to_text() and rep.to_dict()["breakdown"]["total_gb"] > 0
+    assert MemoryManager().check() == "ok"
+
+
+def test_eval_utils_and_logger(tmp_path):
+    assert compute_exact_match("The Answer.", "answer") == 1.0
+    assert abs(compute_token_f1("a cat sat", "the cat sat down") - 0.8) < 1e-9
+    assert compute_bleu4("the quick brown fox jumps", "the quick brown fox jumps") == 1.0
+    assert 0 < compute_bleu4("the quick brown dog jumps high", "the quick brown fox jumps high") < 1
+    e = EvalMetrics()
+    e.add("42", "42")
+    e.add("x", "y")
+    assert e.summary()["exact_match"] == 0.5
+    log = tmp_path / "run.log"
+    setup_logger(log_file=str(log))
+    get_logger("test").info("hello %d", 7)
+    assert "[INFO] [b200fw.test] hello 7" in log.read_text()
+    setup_logger()
+
+
+def _disagg_worker(rank, world, mode):
+    import torch.distributed as dist
+    from b200fw.dist.context import ParallelContext
+    from b200fw.infer import InferenceConfig, InferenceEngine
+    from b200fw.model import PRESETS, ModelConfig, ParallelTransformerModel
+    from b200fw.orch import DisaggConfig, DisaggOrchestrator
+    from b200fw.train import TrainConfig, TrainEngine
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    mc = ModelConfig(vocab_size=128, hidden_size=32, num_layers=2, num_heads=2, num_kv_heads=2, head_dim=16,
+                     intermediate_size=48, max_position_embeddings=128, tie_word_embeddings=True)
+    cfg = DisaggConfig(num_train_gpus=2, num_infer_gpus=2, total_iterations=2, batch_size=4, num_samples_per_prompt=2,
+                       prompt_len=8, max_tokens=5, mode=mode, kv_num_blocks=64)
+
+    def trainer(group, n, r):
+        ctx = ParallelContext(1, n, 1, r, n, r, "gloo")
+        ctx.dp_group, ctx.dp_ranks = group, list(range(n))
+        ParallelContext._instance = ctx
+        tc = TrainConfig(model_config=mc, dp_size=n, lora_rank=0, zero_stage=2, gradient_accumulation_steps=1,
+                         grpo_beta=0.0, max_seq_len=32, warmup_steps=0, use_amp=False, amp_dtype="fp32", learning_rate=1e-3)
+        return TrainEngine(tc).initialize(ctx)
+
+    def engine(i):
+        m = ParallelTransformerModel(mc)
+        m.init_weights(0)
+        ic = InferenceConfig.from_model_config(mc, num_blocks=64, inference_mode="kv_cache", seed=i, eos_token_id=None)
+        return InferenceEngine(ic, m).initialize()
+
+    o = DisaggOrchestrator(cfg, trainer, engine).initialize()
+    o.run()
+    s = o.get_summary()
+    if not o.is_trainer:
+        from b200fw.model.hf_io import hf_named_tensors
+        s["checksum"] = float(sum(v.double().sum() for _, v in hf_named_tensors(o.infer_engine.model)))
+    else:
+        with o.train_engine.optimizer.eval_mode():
+            from b200fw.model.hf_io import hf_named_tensors
+            s["checksum"] = float(sum(v.double().sum() for _, v in hf_named_tensors(o.train_engine.model)))
+    return s
+
+
+def test_disaggregated_loop_two_trainers_two_engines():
+    from _dist_util import run_ranks
+    for mode in ("sequential", "pipeline"):
+        res = run_ranks(_disagg_worker, 4, mode, timeout=600)
+        assert [r["role"] for r in res] == ["trainer", "trainer", "rollout", "rollout"]
+        assert all(r["weights_version"] == r["iterations"] for r in res)
+        # after the final sync every engine holds exactly the trainers' weights
+        assert len({round(r["checksum"], 6) for r in res}) == 1, [r["checksum"] for r in res]
+        assert res[0]["final_loss"] is not None
