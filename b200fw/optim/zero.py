@@ -76,6 +76,12 @@ class _Bucket:
         self.param_buf = None
 
     def ensure_grad_buf(self, use_main_grad: bool):
+        if getattr(self, "persistent_grad", False):
+            if use_main_grad and not hasattr(self.params[0], "main_grad"):
+                for p, o in zip(self.params, self.offsets):
+                    p.main_grad = self.grad_buf[o:o + p.numel()].view(p.shape)
+                    p.grad_filled = False
+            return
         if self.grad_buf is None:
             self.grad_buf = torch.zeros(self.numel, dtype=self.grad_dtype, device=self.device)
             if use_main_grad:
@@ -84,6 +90,10 @@ class _Bucket:
                     p.grad_filled = False
 
     def release_grad_buf(self):
+        if getattr(self, "persistent_grad", False):
+            for p in self.params:
+                p.grad_filled = False
+            return
         self.grad_buf = None
         for p in self.params:
             if hasattr(p, "main_grad"):
@@ -101,7 +111,7 @@ class ZeROOptimizer:
     def __init__(self, params, lr=1e-5, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, stage: int = 1,
                  ctx: Optional[ParallelContext] = None, dp_group=None, bucket_mb: float = 64.0,
                  max_grad_norm: float = 0.0, grad_dtype: Optional[torch.dtype] = None,
-                 overlap: bool = True):
+                 overlap: bool = True, comm_backend: str = "nccl"):
         params = [p for p in params if p.requires_grad]
         assert params, "no trainable parameters"
         self.ctx = ctx
@@ -124,6 +134,11 @@ class ZeROOptimizer:
         self.comm_stream = torch.cuda.Stream(device=self.device, priority=-1) if self.overlap else None
         self.sync_this_backward = True
         self.params_gathered = True
+        # "p2p": gradient reduce-scatter and parameter all-gather run inside the optimizer kernels
+        # through peer pointers (stage 1/2, bf16, CUDA, world <= 8); "nccl": library collectives.
+        self.p2p = (comm_backend == "p2p" and self.on_cuda and self.world > 1 and self.world <= 8
+                    and self.dtype == torch.bfloat16 and 1 <= self.stage <= 2)
+        self.flags = None
 
         # ---- bucket assignment: by TP kind, big ones split by size in reverse (backward) order -----
         by_kind: Dict[int, List[torch.nn.Parameter]] = {0: [], 1: [], 2: []}
@@ -143,6 +158,8 @@ class ZeROOptimizer:
                 cur_n += p.numel()
             if cur:
                 self.buckets.append(_Bucket(cur, kind, self.world, self.rank, self.dtype, self.device, self.grad_dtype))
+        if self.p2p:
+            self._make_symmetric()
         for b in self.buckets:
             for p in b.params:
                 p._zero_bucket = b
@@ -171,6 +188,63 @@ class ZeROOptimizer:
         if self.stage >= 3:
             self._release_params()
         self._prepare_backward()
+
+    # ---- peer-to-peer (in-kernel) communication ---------------------------------------------------
+    def _make_symmetric(self):
+        """Move every bucket's parameter and gradient storage into symmetric memory so that peers can
+        read gradients and write parameters directly."""
+        from ..dist.symm import FlagBarrier, SymmetricBuffer
+        self.overlap = False          # reduction happens inside step(), ordered by the flag barrier
+        for b in self.buckets:
+            sp = SymmetricBuffer(b.numel, b.dtype, self.dp_group, self.device)
+            sp.tensor.copy_(b.param_buf)
+            b.param_buf = sp.tensor
+            b.symm_param = sp
+            b.bind_params()
+            sg = SymmetricBuffer(b.numel, self.grad_dtype, self.dp_group, self.device)
+            b.grad_buf = sg.tensor
+            b.symm_grad = sg
+            b.persistent_grad = True
+        self.flags = FlagBarrier(self.dp_group, self.device)
+        self._p2p_grad = None
+
+    def _p2p_reduce(self):
+        """All ranks' backward passes are complete (flag barrier), then every rank sums its shard of
+        each bucket straight out of the peers' gradient buffers."""
+        from .. import _native as nv
+        import ctypes
+        if self._p2p_grad is None:
+            self._p2p_grad = torch.empty_like(self.master)
+        self.flags.barrier(0)
+        self._norm_parts.zero_()
+        inv = 1.0 / self.world
+        L = nv.lib()
+        for i, b in enumerate(self.buckets):
+            if b.kind == KIND_TP_PARTIAL and self._tp_group() is not None:
+                dist.all_reduce(b.grad_buf, group=self._tp_group())
+            out = self._shard_view(self._p2p_grad, i)
+            norm = self._norm_parts[1:2] if b.kind == KIND_TP_SHARDED else self._norm_parts[0:1]
+            nv.check(L.b2_zero_reduce_shard(b.symm_grad.ptr_array, self.world, ctypes.c_longlong(b.shard_start),
+                                            ctypes.c_longlong(b.shard_numel), ctypes.c_float(inv), nv.ptr(out), 0,
+                                            nv.ptr(norm), nv.stream_ptr()), "zero_reduce_shard")
+            nv.count_launch()
+            b.reduced = True
+
+    def _p2p_step(self, use_norm: bool):
+        from .. import _native as nv
+        import ctypes
+        L = nv.lib()
+        for i, b in enumerate(self.buckets):
+            nv.check(L.b2_zero_adamw_publish(nv.ptr(self._shard_view(self.master, i)),
+                                             nv.ptr(self._shard_view(self.exp_avg, i)),
+                                             nv.ptr(self._shard_view(self.exp_avg_sq, i)),
+                                             nv.ptr(self._shard_view(self._p2p_grad, i)),
+                                             ctypes.c_longlong(b.shard_numel), nv.ptr(self.hyper),
+                                             nv.ptr(self.norm_sq if use_norm else None), b.symm_param.ptr_array,
+                                             self.world, ctypes.c_longlong(b.shard_start), nv.stream_ptr()),
+                     "zero_adamw_publish")
+            nv.count_launch()
+        self.flags.barrier(1)     # every peer's parameter writes have landed before the next forward
 
     # ---- helpers -----------------------------------------------------------------------------
     def _shard_view(self, flat: torch.Tensor, i: int) -> torch.Tensor:
@@ -250,6 +324,8 @@ class ZeROOptimizer:
         """Finish this backward's gradient reduction.  Stage 2/3: every call reduces and releases the
         full gradients (and stage 3 the full parameters); stage 0/1: a no-op until ``step``."""
         self.accumulation_count += 1
+        if self.p2p:
+            return          # gradients accumulate in the persistent symmetric buckets until step()
         if self.stage >= 2:
             self._reduce_all()
             self.grad_acc_filled = True
@@ -328,14 +404,19 @@ class ZeROOptimizer:
         non-finite norm; ``step`` then leaves the weights untouched), without a host sync."""
         if max_norm is not None:
             self.max_grad_norm = max_norm
-        if self.stage < 2:
-            self._reduce_all()
         inv = 1.0 / self.world
-        self._norm_parts.zero_()
-        for i, b in enumerate(self.buckets):
-            g = self._grad_shard(i)
-            ops.sumsq(g, self._norm_parts[1:2] if b.kind == KIND_TP_SHARDED else self._norm_parts[0:1])
-        parts = self._norm_parts * (inv * inv)
+        if self.p2p:
+            if not all(b.reduced for b in self.buckets):
+                self._p2p_reduce()
+            parts = self._norm_parts.clone()        # already of the averaged gradient
+        else:
+            if self.stage < 2:
+                self._reduce_all()
+            self._norm_parts.zero_()
+            for i, b in enumerate(self.buckets):
+                g = self._grad_shard(i)
+                ops.sumsq(g, self._norm_parts[1:2] if b.kind == KIND_TP_SHARDED else self._norm_parts[0:1])
+            parts = self._norm_parts * (inv * inv)
         if self.world > 1 and self.stage >= 1:
             dist.all_reduce(parts, group=self.dp_group)
         if self._tp_group() is not None:
@@ -360,6 +441,13 @@ class ZeROOptimizer:
     def step(self, use_norm: bool = True):
         """AdamW on the owned shards (clipped by the norm armed in ``clip_grad_norm``; skipped on the
         device when that norm is not finite), then publish the updated bf16 parameters."""
+        if self.p2p:
+            if not all(b.reduced for b in self.buckets):
+                self._p2p_reduce()
+            self._write_hyper()
+            self._p2p_step(use_norm)
+            self.step_count += 1
+            return
         if self.stage < 2:
             self._reduce_all()
         self._write_hyper()

@@ -76,6 +76,7 @@ class TrainConfig:
     adam_beta2: float = 0.999
     adam_eps: float = 1e-8
     bucket_mb: float = 64.0
+    zero_comm_backend: str = "nccl"           # "nccl" | "p2p" (reduce-scatter / all-gather inside the optimizer kernels)
     build_ref_model: Optional[bool] = None      # default: grpo_beta > 0, as in the reference
     backend: Optional[str] = None               # nccl / gloo (default by device)
 
@@ -178,7 +179,7 @@ class TrainEngine:
             trainable, cfg.zero_stage if (cfg.dp_size > 1 or cfg.tp_size > 1 or cfg.zero_stage == 0) else 1,
             lr=cfg.learning_rate, betas=(cfg.adam_beta1, cfg.adam_beta2), eps=cfg.adam_eps,
             weight_decay=cfg.weight_decay, ctx=ctx, bucket_mb=cfg.bucket_mb, max_grad_norm=cfg.max_grad_norm,
-            overlap=True)
+            overlap=True, comm_backend=cfg.zero_comm_backend)
         self.lr_scheduler = LRSchedule(cfg.learning_rate, cfg.lr_scheduler_type, cfg.warmup_steps,
                                        cfg.total_training_steps, cfg.min_lr_ratio)
         self.optimizer.param_groups[0]["lr"] = self.lr_scheduler.lr_at(0)

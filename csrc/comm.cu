@@ -303,3 +303,59 @@ B2_EXPORT int b2_flag_wait(const int* flag, int value, int limit_ms, int* result
   B2_LAUNCH_CHECK("flag_wait");
   return 0;
 }
+
+namespace b2 {
+// Signal every peer: flags_of_peer[r][my_rank * channels + channel] = value (system-scope release).
+__global__ void flag_signal_all_kernel(PeerPtrs flag_bufs, int world, int my_rank, int channels, int channel,
+                                       int value) {
+  __threadfence_system();
+  const int r = threadIdx.x;
+  if (r < world) st_release_sys(static_cast<int*>(flag_bufs.p[r]) + my_rank * channels + channel, value);
+}
+// Wait until my_flags[src * channels + channel] >= value for every src, at most limit_ns.
+__global__ void flag_wait_all_kernel(const int* my_flags, int world, int channels, int channel, int value,
+                                     unsigned long long limit_ns, int* result, int* status) {
+  const int src = threadIdx.x;
+  __shared__ int failed;
+  if (threadIdx.x == 0) failed = 0;
+  __syncthreads();
+  if (src < world) {
+    const unsigned long long t0 = globaltimer_ns();
+    for (;;) {
+      if (ld_acquire_sys(my_flags + src * channels + channel) >= value) break;
+      if (globaltimer_ns() - t0 > limit_ns) {
+        atomicExch(&failed, 1 + src);
+        break;
+      }
+      __nanosleep(200);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (result) result[0] = failed ? 0 : 1;
+    if (failed) atomicCAS(status, 0, ERR_COMM_FLAG_WAIT);
+  }
+}
+}  // namespace b2
+
+// flag_bufs: host array of `world` device pointers to each rank's int32 flag buffer [world * channels].
+B2_EXPORT int b2_flag_signal_all(void* const* flag_bufs, int world, int my_rank, int channels, int channel,
+                                 int value, void* stream_) {
+  b2::ensure_thread_context();
+  if (world < 1 || world > 8) { set_error("flag_signal_all: world must be 1..8"); return 10; }
+  PeerPtrs pp;
+  for (int r = 0; r < 8; ++r) pp.p[r] = r < world ? flag_bufs[r] : nullptr;
+  flag_signal_all_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream_)>>>(pp, world, my_rank, channels, channel, value);
+  B2_LAUNCH_CHECK("flag_signal_all");
+  return 0;
+}
+B2_EXPORT int b2_flag_wait_all(const int* my_flags, int world, int channels, int channel, int value, int limit_ms,
+                               int* result, void* stream_) {
+  b2::ensure_thread_context();
+  int* status = status_ptr();
+  if (!status) return 3;
+  flag_wait_all_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream_)>>>(
+      my_flags, world, channels, channel, value, static_cast<unsigned long long>(limit_ms) * 1000000ull, result, status);
+  B2_LAUNCH_CHECK("flag_wait_all");
+  return 0;
+}

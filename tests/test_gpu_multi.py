@@ -1,0 +1,126 @@
+"""Multi-GPU paths (need >= 2 GPUs): flag barrier, ZeRO with in-kernel peer reduce-scatter / all-gather
+against the NCCL path, peer-write weight sync across GPUs, fused tensor-parallel GEMM kernels."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+needs2 = pytest.mark.skipif(not torch.cuda.is_available() or torch.cuda.device_count() < 2,
+                            reason="needs at least 2 GPUs")
+
+
+def _world():
+    return min(torch.cuda.device_count(), 8)
+
+
+def _flag_worker(rank, world):
+    import torch.distributed as dist
+    from b200fw.dist.symm import FlagBarrier, SymmetricBuffer
+    g = dist.group.WORLD
+    fb = FlagBarrier(g, limit_ms=2000)
+    buf = SymmetricBuffer(1024, torch.float32, g)
+    ok = True
+    for it in range(1, 6):
+        buf.tensor.fill_(float(rank * 100 + it))
+        fb.barrier(0)
+        # read every peer's buffer through its pointer (a device-to-device copy from peer memory)
+        for r in range(world):
+            peer = torch.empty(1024, device="cuda")
+            torch.cuda.current_stream().synchronize()
+            import ctypes
+            from b200fw import _native as nv
+            nv.check(nv.lib().b2_peer_write(ctypes.c_void_p(buf.peer_ptrs[r]), 1, nv.ptr(peer), 1,
+                                            ctypes.c_longlong(1024), ctypes.c_longlong(0), 0, nv.ptr(None),
+                                            nv.stream_ptr()), "peer_read")
+            ok = ok and bool((peer == float(r * 100 + it)).all())
+        fb.barrier(1)
+    return ok and fb.ok()
+
+
+@needs2
+def test_flag_barrier_and_peer_pointers():
+    from _gpu_dist_util import run_gpu_ranks
+    assert all(run_gpu_ranks(_flag_worker, _world()))
+
+
+def _wait_timeout_worker(rank, world):
+    """A wait on a flag nobody sets runs out after its limit and reports through the status word; the
+    context stays usable afterwards."""
+    import torch.distributed as dist
+    from b200fw import _native as nv
+    from b200fw.dist.symm import FlagBarrier
+    fb = FlagBarrier(dist.group.WORLD, limit_ms=300)
+    fb.wait(channel=3, epoch=7)                 # no rank ever signals channel 3
+    ok_before = fb.ok()
+    status = nv.read_status()                   # reads and clears
+    x = torch.ones(8, device="cuda") * 2        # the device still works
+    fb.barrier(0)
+    return (ok_before, status, float(x.sum()), fb.ok())
+
+
+@needs2
+def test_bounded_wait_reports_instead_of_hanging():
+    from _gpu_dist_util import run_gpu_ranks
+    for ok_before, status, s, ok_after in run_gpu_ranks(_wait_timeout_worker, 2):
+        assert ok_before is False and status == 301 and s == 16.0 and ok_after is True
+
+
+def _zero_worker(rank, world, backend, stage):
+    from b200fw.train import TrainConfig, TrainEngine
+    cfg = TrainConfig(model_preset="tiny128", dp_size=world, lora_rank=0, grpo_beta=0.0, learning_rate=1e-3,
+                      gradient_accumulation_steps=2, zero_stage=stage, warmup_steps=0, max_seq_len=256,
+                      amp_dtype="bf16", zero_comm_backend=backend, bucket_mb=1.0)
+    eng = TrainEngine(cfg).initialize()
+    assert eng.optimizer.p2p == (backend == "p2p")
+    out = []
+    for s in range(6):
+        g = torch.Generator().manual_seed(s * 31 + rank)
+        ids = torch.randint(0, 8192, (2, 256), generator=g)
+        labels = ids.clone()
+        labels[:, :128] = -100
+        m = eng.sft_step_tensors(ids, labels)
+        out.append((m.loss, m.grad_norm))
+    flat = torch.cat([p.detach().float().reshape(-1) for p in eng.model.parameters()])
+    return out, float(flat.double().sum()), float(flat.abs().double().sum())
+
+
+@needs2
+@pytest.mark.parametrize("stage", [1, 2])
+def test_zero_p2p_matches_nccl(stage):
+    from _gpu_dist_util import run_gpu_ranks
+    w = _world()
+    a = run_gpu_ranks(_zero_worker, w, "nccl", stage)
+    b = run_gpu_ranks(_zero_worker, w, "p2p", stage)
+    for r in range(w):
+        assert a[r][1] == a[0][1] and b[r][1] == b[0][1]            # ranks hold identical weights
+        for (la, ga), (lb, gb) in zip(a[r][0], b[r][0]):
+            assert abs(la - lb) < 5e-2 and abs(ga - gb) / max(ga, 1e-6) < 5e-2
+        assert abs(a[r][2] - b[r][2]) / a[r][2] < 1e-3
+
+
+def _peer_sync_worker(rank, world):
+    import torch.distributed as dist
+    from b200fw.sync import PeerWeightSync
+    layout = [("w1", (513, 257)), ("w2", (1000,)), ("w3", (64, 64))]
+    ps = PeerWeightSync(layout, torch.bfloat16, group=dist.group.WORLD, sender_rank=0)
+    got = {}
+
+    class Eng:
+        def load_weights(self, views):
+            got.update({k: v.clone() for k, v in views.items()})
+
+    g = torch.Generator().manual_seed(5)
+    state = {k: torch.empty(shape).normal_(generator=g).cuda() for k, shape in layout}   # fp32 source: cast in flight
+    v1 = ps.sync(rank == 0, state if rank == 0 else None, None if rank == 0 else Eng())
+    ok1 = rank == 0 or all(torch.equal(got[k], state[k].to(torch.bfloat16)) for k in state)
+    got.clear()
+    v2 = ps.sync(rank == 0, {k: v * 2 for k, v in state.items()} if rank == 0 else None,
+                 None if rank == 0 else Eng(), corrupt=True)
+    return v1, ok1, v2, len(got), ps.get_stats()["rejected"]
+
+
+@needs2
+def test_peer_write_weight_sync_across_gpus():
+    from _gpu_dist_util import run_gpu_ranks
+    res = run_gpu_ranks(_peer_sync_worker, 2)
+    assert res[0][:3] == (1, True, 1) and res[1][:4] == (1, True, 1, 0) and res[1][4] == 1
