@@ -9,14 +9,18 @@
 //   attn_bwd_dq     one CTA per (128-row q tile, q head, batch); streams 64-row K/V tiles;
 //                   S = Q K^T, dP = dO V^T, dQ += dS K.
 // S/dP accumulators are double-buffered in TMEM so the MMAs of step i+1 overlap the elementwise
-// work of step i.  Recomputing S and dP in both kernels costs 7 instead of 5 GEMMs per tile pair
+// work of step i.  The elementwise work (exp2, dS, bf16 pack, swizzled shared-memory stores) is the
+// critical path, so eight warps share it: warps 2..5 take columns 0..31 of every 64-column tile,
+// warps 6..9 columns 32..63 (a warp may touch the TMEM lane quarter warp%4, which both groups cover).  Recomputing S and dP in both kernels costs 7 instead of 5 GEMMs per tile pair
 // but needs no atomics and is deterministic.
 #include "common.cuh"
 #include "host.h"
 
 namespace b2 {
 
-constexpr int ATB_THREADS = 192;
+constexpr int ATB_THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2..9 elementwise (two column halves)
+
+__device__ __forceinline__ void ew_barrier() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 constexpr float LOG2E = 1.4426950408889634f;
 
 // ---------------------------------------------------------------------------------------------
@@ -46,7 +50,7 @@ struct DkDvSmem {
   static constexpr int PT = DO + 2 * 16384;   // 2 x 16 KiB [128 x 64]
   static constexpr int DST = PT + 2 * 16384;  // 2 x 16 KiB
   static constexpr int BARS = DST + 2 * 16384;
-  static constexpr int TOTAL = BARS + 256 + 1024;
+  static constexpr int TOTAL = BARS + 128 + 1024 /*lse, D*/ + 1024;
 };
 
 __global__ void __launch_bounds__(ATB_THREADS, 1)
@@ -68,6 +72,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_con
   uint64_t* pds_empty = bars + 11;  // [2]
   uint64_t* acc_done = bars + 13;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  float* s_lse = reinterpret_cast<float*>(bars + 16);   // [2][64], pre-multiplied by log2(e)
+  float* s_D = s_lse + 128;                             // [2][64]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int jt = blockIdx.x;  // kv tile (128 rows); light tiles (large jt) are scheduled last anyway
@@ -86,8 +92,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_con
       mbar_init(&qdo_full[i], 1);
       mbar_init(&qdo_empty[i], 1);
       mbar_init(&sdp_full[i], 1);
-      mbar_init(&sdp_empty[i], 128);
-      mbar_init(&pds_full[i], 128);
+      mbar_init(&sdp_empty[i], 256);
+      mbar_init(&pds_full[i], 256);
       mbar_init(&pds_empty[i], 1);
     }
     mbar_init(acc_done, 1);
@@ -197,7 +203,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_con
     }
   } else {
     const int quarter = warp & 3;
-    const int r = quarter * 32 + lane;  // kv row in tile
+    const int half = (warp - 2) >> 2;           // which 32 columns of the 64-column tile
+    const int etid = (warp - 2) * 32 + lane;    // 0..255 among the elementwise threads
+    const int r = quarter * 32 + lane;          // kv row in tile
     const int kv_pos = jt * 128 + r;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     const float sl2 = scale * LOG2E;
@@ -207,49 +215,55 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_con
       const uint32_t ph = (it >> 1) & 1;
       const int head = kvh * G + it / per_head;
       const int q0 = (i_begin + it % per_head) * 64;  // first q position of this tile
-      if (!mbar_wait(&sdp_full[st], ph, status, ERR_ATTN_WAIT)) { ok = false; break; }
-      tc_fence_after();
-      float s[64], dp[64];
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t t[32];
-        tmem_ld_32x32b_x32(tmem_ST + lane_off + st * 64 + c * 32, t);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(t[i]);
-        tmem_ld_32x32b_x32(tmem_DPT + lane_off + st * 64 + c * 32, t);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) dp[c * 32 + i] = __uint_as_float(t[i]);
+      // stage this tile's row statistics (64 q positions) in shared memory
+      if (etid < 128) {
+        const int c = etid & 63;
+        const int qc = min(q0 + c, S - 1);
+        const size_t o = static_cast<size_t>(head) * T + batch * S + qc;
+        if (etid < 64) s_lse[st * 64 + c] = lse[o] * LOG2E;
+        else s_D[st * 64 + c] = Dsum[o];
       }
+      ew_barrier();   // every elementwise thread reaches this each iteration, also after a failed wait
+      if (ok) ok = mbar_wait(&sdp_full[st], ph, status, ERR_ATTN_WAIT);
+      if (!ok) continue;
+      tc_fence_after();
+      uint32_t ts[32], tp[32];
+      tmem_ld_32x32b_x32(tmem_ST + lane_off + st * 64 + half * 32, ts);
+      tmem_ld_32x32b_x32(tmem_DPT + lane_off + st * 64 + half * 32, tp);
+      tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(&sdp_empty[st]);
-      const float* lse_h = lse + static_cast<size_t>(head) * T + batch * S;
-      const float* D_h = Dsum + static_cast<size_t>(head) * T + batch * S;
+      const float* lse_s = s_lse + st * 64 + half * 32;
+      const float* D_s = s_D + st * 64 + half * 32;
+      const int qb = q0 + half * 32;
+      const bool need_mask = (qb < jt * 128 + 128) || (qb + 32 > S) || (jt * 128 + 128 > S);
+      float pv[32], dsv[32];
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        const int qp = q0 + c;
-        const bool valid = (qp < S) && (kv_pos <= qp) && (kv_pos < S);
-        const int qc = qp < S ? qp : S - 1;
-        const float p = valid ? exp2f(s[c] * sl2 - lse_h[qc] * LOG2E) : 0.f;
-        s[c] = p;
-        dp[c] = p * (dp[c] - D_h[qc]) * scale;
+      for (int c = 0; c < 32; ++c) {
+        float p = exp2f(__uint_as_float(ts[c]) * sl2 - lse_s[c]);
+        if (need_mask) {
+          const int qp = qb + c;
+          if (!((qp < S) && (kv_pos <= qp) && (kv_pos < S))) p = 0.f;
+        }
+        pv[c] = p;
+        dsv[c] = p * (__uint_as_float(tp[c]) - D_s[c]) * scale;
       }
-      if (!mbar_wait(&pds_empty[st], ph ^ 1, status, ERR_ATTN_WAIT)) { ok = false; break; }
+      ok = mbar_wait(&pds_empty[st], ph ^ 1, status, ERR_ATTN_WAIT);
+      if (!ok) continue;
       uint8_t* sPT = smem + DkDvSmem::PT + st * 16384 + r * 128;
       uint8_t* sDST = smem + DkDvSmem::DST + st * 16384 + r * 128;
 #pragma unroll
-      for (int cc = 0; cc < 8; ++cc) {
+      for (int c4 = 0; c4 < 4; ++c4) {
         uint4 a, b;
-        a.x = pack_bf16x2(s[cc * 8 + 0], s[cc * 8 + 1]);
-        a.y = pack_bf16x2(s[cc * 8 + 2], s[cc * 8 + 3]);
-        a.z = pack_bf16x2(s[cc * 8 + 4], s[cc * 8 + 5]);
-        a.w = pack_bf16x2(s[cc * 8 + 6], s[cc * 8 + 7]);
-        b.x = pack_bf16x2(dp[cc * 8 + 0], dp[cc * 8 + 1]);
-        b.y = pack_bf16x2(dp[cc * 8 + 2], dp[cc * 8 + 3]);
-        b.z = pack_bf16x2(dp[cc * 8 + 4], dp[cc * 8 + 5]);
-        b.w = pack_bf16x2(dp[cc * 8 + 6], dp[cc * 8 + 7]);
-        const int sw = (cc ^ (r & 7)) << 4;
+        a.x = pack_bf16x2(pv[c4 * 8 + 0], pv[c4 * 8 + 1]);
+        a.y = pack_bf16x2(pv[c4 * 8 + 2], pv[c4 * 8 + 3]);
+        a.z = pack_bf16x2(pv[c4 * 8 + 4], pv[c4 * 8 + 5]);
+        a.w = pack_bf16x2(pv[c4 * 8 + 6], pv[c4 * 8 + 7]);
+        b.x = pack_bf16x2(dsv[c4 * 8 + 0], dsv[c4 * 8 + 1]);
+        b.y = pack_bf16x2(dsv[c4 * 8 + 2], dsv[c4 * 8 + 3]);
+        b.z = pack_bf16x2(dsv[c4 * 8 + 4], dsv[c4 * 8 + 5]);
+        b.w = pack_bf16x2(dsv[c4 * 8 + 6], dsv[c4 * 8 + 7]);
+        const int sw = (((half * 4 + c4) ^ (r & 7)) << 4);
         *reinterpret_cast<uint4*>(sPT + sw) = a;
         *reinterpret_cast<uint4*>(sDST + sw) = b;
       }
@@ -257,38 +271,32 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_con
       tc_fence_before();
       mbar_arrive(&pds_full[st]);
     }
+    // write-out: the first column group stores dV, the second dK
     const bool in_range = kv_pos < S;
-    __nv_bfloat16* dk_row = dk + static_cast<size_t>(kv_row0 + r) * ld_dk + kvh * 128;
-    __nv_bfloat16* dv_row = dv + static_cast<size_t>(kv_row0 + r) * ld_dv + kvh * 128;
+    __nv_bfloat16* orow = half ? dk + static_cast<size_t>(kv_row0 + r) * ld_dk + kvh * 128
+                               : dv + static_cast<size_t>(kv_row0 + r) * ld_dv + kvh * 128;
     if (n_it == 0) {
       if (in_range) {
         const uint4 z = make_uint4(0, 0, 0, 0);
-        for (int c = 0; c < 16; ++c) {
-          *reinterpret_cast<uint4*>(dk_row + c * 8) = z;
-          *reinterpret_cast<uint4*>(dv_row + c * 8) = z;
-        }
+        for (int c = 0; c < 16; ++c) *reinterpret_cast<uint4*>(orow + c * 8) = z;
       }
     } else if (ok && mbar_wait(acc_done, 0, status, ERR_ATTN_WAIT)) {
       tc_fence_after();
+      const uint32_t tb = (half ? tmem_DK : tmem_DV) + lane_off;
 #pragma unroll
-      for (int which = 0; which < 2; ++which) {
-        __nv_bfloat16* orow = which ? dk_row : dv_row;
-        const uint32_t tb = (which ? tmem_DK : tmem_DV) + lane_off;
+      for (int c = 0; c < 4; ++c) {
+        uint32_t t[32];
+        tmem_ld_32x32b_x32(tb + c * 32, t);
+        tmem_ld_wait();
+        if (in_range) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t t[32];
-          tmem_ld_32x32b_x32(tb + c * 32, t);
-          tmem_ld_wait();
-          if (in_range) {
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              uint4 o;
-              o.x = pack_bf16x2(__uint_as_float(t[v * 8 + 0]), __uint_as_float(t[v * 8 + 1]));
-              o.y = pack_bf16x2(__uint_as_float(t[v * 8 + 2]), __uint_as_float(t[v * 8 + 3]));
-              o.z = pack_bf16x2(__uint_as_float(t[v * 8 + 4]), __uint_as_float(t[v * 8 + 5]));
-              o.w = pack_bf16x2(__uint_as_float(t[v * 8 + 6]), __uint_as_float(t[v * 8 + 7]));
-              *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) = o;
-            }
+          for (int v = 0; v < 4; ++v) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(t[v * 8 + 0]), __uint_as_float(t[v * 8 + 1]));
+            o.y = pack_bf16x2(__uint_as_float(t[v * 8 + 2]), __uint_as_float(t[v * 8 + 3]));
+            o.z = pack_bf16x2(__uint_as_float(t[v * 8 + 4]), __uint_as_float(t[v * 8 + 5]));
+            o.w = pack_bf16x2(__uint_as_float(t[v * 8 + 6]), __uint_as_float(t[v * 8 + 7]));
+            *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) = o;
           }
         }
       }
@@ -354,8 +362,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       mbar_init(&kv_full[i], 1);
       mbar_init(&kv_empty[i], 1);
       mbar_init(&sdp_full[i], 1);
-      mbar_init(&sdp_empty[i], 128);
-      mbar_init(&ds_full[i], 128);
+      mbar_init(&sdp_empty[i], 256);
+      mbar_init(&ds_full[i], 256);
       mbar_init(&ds_empty[i], 1);
     }
     mbar_init(acc_done, 1);
@@ -457,6 +465,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
   } else {
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;
     const int q_pos = qt * 128 + r;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
@@ -470,39 +479,34 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const uint32_t ph = (it >> 1) & 1;
       if (!mbar_wait(&sdp_full[st], ph, status, ERR_ATTN_WAIT)) { ok = false; break; }
       tc_fence_after();
-      float s[64], dp[64];
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t t[32];
-        tmem_ld_32x32b_x32(tmem_S + lane_off + st * 64 + c * 32, t);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(t[i]);
-        tmem_ld_32x32b_x32(tmem_DP + lane_off + st * 64 + c * 32, t);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) dp[c * 32 + i] = __uint_as_float(t[i]);
-      }
+      uint32_t ts[32], tp[32];
+      tmem_ld_32x32b_x32(tmem_S + lane_off + st * 64 + half * 32, ts);
+      tmem_ld_32x32b_x32(tmem_DP + lane_off + st * 64 + half * 32, tp);
+      tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(&sdp_empty[st]);
-      const int k0 = it * 64;
+      const int k0 = it * 64 + half * 32;
+      const bool need_mask = (k0 + 32 > qt * 128) || (k0 + 32 > S) || (qt * 128 + 128 > S);
+      float dsv[32];
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        const int kp = k0 + c;
-        const bool valid = (q_pos < S) && (kp <= q_pos) && (kp < S);
-        const float p = valid ? exp2f(s[c] * sl2 - lse_r) : 0.f;
-        dp[c] = p * (dp[c] - D_r) * scale;
+      for (int c = 0; c < 32; ++c) {
+        float p = exp2f(__uint_as_float(ts[c]) * sl2 - lse_r);
+        if (need_mask) {
+          const int kp = k0 + c;
+          if (!((q_pos < S) && (kp <= q_pos) && (kp < S))) p = 0.f;
+        }
+        dsv[c] = p * (__uint_as_float(tp[c]) - D_r) * scale;
       }
       if (!mbar_wait(&ds_empty[st], ph ^ 1, status, ERR_ATTN_WAIT)) { ok = false; break; }
       uint8_t* sDS = smem + DqSmem::DS + st * 16384 + r * 128;
 #pragma unroll
-      for (int cc = 0; cc < 8; ++cc) {
+      for (int c4 = 0; c4 < 4; ++c4) {
         uint4 b;
-        b.x = pack_bf16x2(dp[cc * 8 + 0], dp[cc * 8 + 1]);
-        b.y = pack_bf16x2(dp[cc * 8 + 2], dp[cc * 8 + 3]);
-        b.z = pack_bf16x2(dp[cc * 8 + 4], dp[cc * 8 + 5]);
-        b.w = pack_bf16x2(dp[cc * 8 + 6], dp[cc * 8 + 7]);
-        *reinterpret_cast<uint4*>(sDS + ((cc ^ (r & 7)) << 4)) = b;
+        b.x = pack_bf16x2(dsv[c4 * 8 + 0], dsv[c4 * 8 + 1]);
+        b.y = pack_bf16x2(dsv[c4 * 8 + 2], dsv[c4 * 8 + 3]);
+        b.z = pack_bf16x2(dsv[c4 * 8 + 4], dsv[c4 * 8 + 5]);
+        b.w = pack_bf16x2(dsv[c4 * 8 + 6], dsv[c4 * 8 + 7]);
+        *reinterpret_cast<uint4*>(sDS + (((half * 4 + c4) ^ (r & 7)) << 4)) = b;
       }
       fence_proxy_async_smem();
       tc_fence_before();
@@ -511,11 +515,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     if (ok && mbar_wait(acc_done, 0, status, ERR_ATTN_WAIT)) {
       tc_fence_after();
       const bool in_range = q_pos < S;
-      __nv_bfloat16* orow = dq + (static_cast<size_t>(row0 + r) * Hq + head) * 128;
+      __nv_bfloat16* orow = dq + (static_cast<size_t>(row0 + r) * Hq + head) * 128 + half * 64;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t t[32];
-        tmem_ld_32x32b_x32(tmem_DQ + lane_off + c * 32, t);
+        tmem_ld_32x32b_x32(tmem_DQ + lane_off + half * 64 + c * 32, t);
         tmem_ld_wait();
         if (in_range) {
 #pragma unroll

@@ -163,6 +163,124 @@ __global__ void __launch_bounds__(RMS_THREADS) rmsnorm_bwd_kernel(
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------
+// Warp-per-row variants for H <= 2048 (NV = H/256 rounded up, <= 8 vectors of 8 per lane): no block-wide
+// barriers on the critical path, rows stay in registers, 8 rows in flight per 256-thread CTA.
+// ---------------------------------------------------------------------------------------------
+template <int NV>
+__global__ void __launch_bounds__(256) rmsnorm_fwd_warp_kernel(
+    const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+    __nv_bfloat16* __restrict__ y, float* __restrict__ rstd_out, int M, int H, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_grid = (gridDim.x * blockDim.x) >> 5;
+  const int nvec = H / 8;
+  float wv[NV][8];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = lane + i * 32;
+    if (c < nvec) load8(w + c * 8, wv[i]);
+  }
+  for (int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; row < M; row += warps_per_grid) {
+    const __nv_bfloat16* xr = x + static_cast<size_t>(row) * H;
+    float v[NV][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = lane + i * 32;
+      if (c < nvec) {
+        load8(xr + c * 8, v[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += v[i][j] * v[i][j];
+      }
+    }
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / H + eps);
+    if (lane == 0 && rstd_out) rstd_out[row] = rstd;
+    __nv_bfloat16* yr = y + static_cast<size_t>(row) * H;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = lane + i * 32;
+      if (c < nvec) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = v[i][j] * rstd * wv[i][j];
+        store8(yr + c * 8, o);
+      }
+    }
+  }
+}
+
+template <int NV>
+__global__ void __launch_bounds__(256) rmsnorm_bwd_warp_kernel(
+    const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd_in,
+    __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_partial, int M, int H, int add_to_dx) {
+  extern __shared__ float sdw[];   // [H]
+  const int lane = threadIdx.x & 31;
+  const int warps_per_grid = (gridDim.x * blockDim.x) >> 5;
+  const int nvec = H / 8;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) sdw[i] = 0.f;
+  float wv[NV][8], dwacc[NV][8];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = lane + i * 32;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
+    if (c < nvec) load8(w + c * 8, wv[i]);
+  }
+  __syncthreads();
+  for (int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; row < M; row += warps_per_grid) {
+    const __nv_bfloat16* xr = x + static_cast<size_t>(row) * H;
+    const __nv_bfloat16* dyr = dy + static_cast<size_t>(row) * H;
+    __nv_bfloat16* dxr = dx + static_cast<size_t>(row) * H;
+    const float rstd = rstd_in[row];
+    float xh[NV][8], g[NV][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = lane + i * 32;
+      if (c < nvec) {
+        float xv[8], dv[8];
+        load8(xr + c * 8, xv);
+        load8(dyr + c * 8, dv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[i][j] = xv[j] * rstd;
+          dwacc[i][j] += dv[j] * xh[i][j];
+          g[i][j] = dv[j] * wv[i][j];
+          dot += g[i][j] * xh[i][j];
+        }
+      }
+    }
+    dot = warp_sum(dot) / H;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = lane + i * 32;
+      if (c < nvec) {
+        float o[8];
+        if (add_to_dx) load8(dxr + c * 8, o);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float d = rstd * (g[i][j] - xh[i][j] * dot);
+          o[j] = add_to_dx ? o[j] + d : d;
+        }
+        store8(dxr + c * 8, o);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int c = lane + i * 32;
+    if (c < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) atomicAdd(&sdw[c * 8 + j], dwacc[i][j]);
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < H; i += blockDim.x) dw_partial[static_cast<size_t>(blockIdx.x) * H + i] = sdw[i];
+}
+
 // dw[h] (+)= sum_p partial[p, h]   (bf16 or fp32 destination)
 __global__ void reduce_partials_kernel(const float* __restrict__ partial, void* __restrict__ dw,
                                        int P, int H, int accumulate, int out_fp32) {
@@ -247,6 +365,13 @@ __global__ void __launch_bounds__(256) qknorm_rope_bwd_kernel(
   const int lane = threadIdx.x & 31;
   const long long total = static_cast<long long>(M) * heads;
   const long long warps_per_grid = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
+  // a lane always owns the same four head dimensions: weight gradients accumulate in registers
+  float dwq[4] = {0.f, 0.f, 0.f, 0.f}, dwk[4] = {0.f, 0.f, 0.f, 0.f};
+  uint2 wq_raw = *reinterpret_cast<const uint2*>(qw + lane * 4);
+  uint2 wk_raw = *reinterpret_cast<const uint2*>(kw + lane * 4);
+  const float2 wqa = unpack_bf16x2(wq_raw.x), wqb = unpack_bf16x2(wq_raw.y);
+  const float2 wka = unpack_bf16x2(wk_raw.x), wkb = unpack_bf16x2(wk_raw.y);
+  const float wqv[4] = {wqa.x, wqa.y, wqb.x, wqb.y}, wkv[4] = {wka.x, wka.y, wkb.x, wkb.y};
   for (long long gw = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; gw < total;
        gw += warps_per_grid) {
     const int tok = static_cast<int>(gw / heads);
@@ -267,27 +392,30 @@ __global__ void __launch_bounds__(256) qknorm_rope_bwd_kernel(
     uint2 xraw = *reinterpret_cast<const uint2*>(qkv + off);
     float2 xa = unpack_bf16x2(xraw.x), xb = unpack_bf16x2(xraw.y);
     const float xv[4] = {xa.x, xa.y, xb.x, xb.y};
-    uint2 wraw = *reinterpret_cast<const uint2*>((is_q ? qw : kw) + lane * 4);
-    float2 wa = unpack_bf16x2(wraw.x), wb = unpack_bf16x2(wraw.y);
-    const float wv[4] = {wa.x, wa.y, wb.x, wb.y};
     const float rstd = rstd_in[static_cast<size_t>(tok) * heads + head];
-    float dn[4], xh[4], gw_[4];
+    float xh[4], gw_[4];
     float dot = 0.f;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const float partner = __shfl_xor_sync(0xffffffffu, g[j], 16);
       // inverse rotation: dx1 = dy1*c + dy2*s ; dx2 = dy2*c - dy1*s
-      dn[j] = (lane < 16) ? g[j] * cs[j] + partner * sn[j] : g[j] * cs[j] - partner * sn[j];
+      const float dn = (lane < 16) ? g[j] * cs[j] + partner * sn[j] : g[j] * cs[j] - partner * sn[j];
       xh[j] = xv[j] * rstd;
-      gw_[j] = dn[j] * wv[j];
+      gw_[j] = dn * (is_q ? wqv[j] : wkv[j]);
       dot += gw_[j] * xh[j];
-      atomicAdd(&sdw[is_q ? 0 : 1][lane * 4 + j], dn[j] * xh[j]);
+      if (is_q) dwq[j] += dn * xh[j];
+      else dwk[j] += dn * xh[j];
     }
     dot = warp_sum(dot) * (1.f / 128.f);
     uint2 ov;
     ov.x = pack_bf16x2(rstd * (gw_[0] - xh[0] * dot), rstd * (gw_[1] - xh[1] * dot));
     ov.y = pack_bf16x2(rstd * (gw_[2] - xh[2] * dot), rstd * (gw_[3] - xh[3] * dot));
     *reinterpret_cast<uint2*>(dqkv + off) = ov;
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    atomicAdd(&sdw[0][lane * 4 + j], dwq[j]);
+    atomicAdd(&sdw[1][lane * 4 + j], dwk[j]);
   }
   __syncthreads();
   for (int i = threadIdx.x; i < 128; i += blockDim.x) {
@@ -384,6 +512,19 @@ B2_EXPORT int b2_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd,
   b2::ensure_thread_context();
   if (H % 8) { set_error("rmsnorm: H %% 8 != 0"); return 10; }
   if (M <= 0) return 0;
+  if (H <= 2048) {
+    int blocks = (M + 7) / 8;
+    const int cap = num_sms() * 8;
+    if (blocks > cap) blocks = cap;
+    auto xs = static_cast<const __nv_bfloat16*>(x);
+    auto ws = static_cast<const __nv_bfloat16*>(w);
+    auto ys = static_cast<__nv_bfloat16*>(y);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (H <= 1024) rmsnorm_fwd_warp_kernel<4><<<blocks, 256, 0, st>>>(xs, ws, ys, rstd, M, H, eps);
+    else rmsnorm_fwd_warp_kernel<8><<<blocks, 256, 0, st>>>(xs, ws, ys, rstd, M, H, eps);
+    B2_LAUNCH_CHECK("rmsnorm_fwd");
+    return 0;
+  }
   rmsnorm_fwd_kernel<<<M, RMS_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(w),
       static_cast<__nv_bfloat16*>(y), rstd, H, eps);
@@ -404,6 +545,18 @@ B2_EXPORT int b2_rmsnorm_bwd(const void* dy, const void* x, const void* w, const
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   int ctas = num_sms() * 2;
   if (ctas > M) ctas = M;
+  if (H <= 1024) {
+    auto dys = static_cast<const __nv_bfloat16*>(dy);
+    auto xs = static_cast<const __nv_bfloat16*>(x);
+    auto ws = static_cast<const __nv_bfloat16*>(w);
+    auto dxs = static_cast<__nv_bfloat16*>(dx);
+    const int smem = H * static_cast<int>(sizeof(float));
+    rmsnorm_bwd_warp_kernel<4><<<ctas, 256, smem, stream>>>(dys, xs, ws, rstd, dxs, dw_partial, M, H, add_to_dx);
+    B2_LAUNCH_CHECK("rmsnorm_bwd");
+    reduce_partials_kernel<<<(H + 255) / 256, 256, 0, stream>>>(dw_partial, dw, ctas, H, accumulate_dw, dw_fp32);
+    B2_LAUNCH_CHECK("rmsnorm_bwd_reduce");
+    return 0;
+  }
   rmsnorm_bwd_kernel<<<ctas, RMS_THREADS, 0, stream>>>(
       static_cast<const __nv_bfloat16*>(dy), static_cast<const __nv_bfloat16*>(x),
       static_cast<const __nv_bfloat16*>(w), rstd, static_cast<__nv_bfloat16*>(dx), dw_partial, M, H,
