@@ -9,7 +9,12 @@
 // grad-weight GEMMs all run without a transpose pass.
 //
 // CTA layout (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer (one elected lane) and TMEM
-// owner, warps 2..5 = epilogue (one TMEM lane quarter each).  Two TMEM accumulators of BN columns
+// owner, warps 2..5 = epilogue (one TMEM lane quarter each).  The bf16 epilogue goes through shared
+// memory: every thread converts its row of a 64-column slab and writes it in the 128-byte-swizzled
+// layout, then one thread issues a TMA store of the [128 x 64] slab (two slab buffers alternate); the
+// residual / accumulate operand comes in the same way by a TMA load into the slab buffer.  Direct
+// per-thread global stores would touch 32 different cache lines per warp instruction and made the
+// epilogue, not the MMA, the limiter for short-K GEMMs.  Two TMEM accumulators of BN columns
 // let the epilogue of tile i overlap the main loop of tile i+1.  One CTA per SM (TMEM and shared
 // memory are sized for that), grid = min(#tiles, #SMs), static round-robin tile schedule with
 // M-grouped rasterisation for L2 reuse.
@@ -34,7 +39,8 @@ struct GemmCfg {
   static constexpr int B_BYTES = BN * GEMM_BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = (BN == 256) ? 4 : 6;
-  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int SLAB_BYTES = GEMM_BM * 64 * 2;   // one [128 x 64] bf16 epilogue slab
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 2 * SLAB_BYTES + 1024 /*align*/ + 256 /*barriers*/;
   static constexpr int TMEM_COLS = 2 * BN;  // 512 or 256: powers of two
 };
 
@@ -45,18 +51,21 @@ struct GemmMnDesc {
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmR,
                  void* __restrict__ Cout, const __nv_bfloat16* __restrict__ R, int M, int N, int K,
                  int ldc, int flags, GemmMnDesc mn, int* status) {
   using Cfg = GemmCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
+  uint8_t* slabs = smem + Cfg::STAGES * Cfg::STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(slabs + 2 * Cfg::SLAB_BYTES);
   uint64_t* full_bar = bars;
   uint64_t* empty_bar = bars + Cfg::STAGES;
   uint64_t* tmem_full = bars + 2 * Cfg::STAGES;
   uint64_t* tmem_empty = tmem_full + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  uint64_t* addend_bar = tmem_empty + 2;   // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(addend_bar + 2);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -74,6 +83,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     for (int a = 0; a < 2; ++a) {
       mbar_init(&tmem_full[a], 1);
       mbar_init(&tmem_empty[a], 128);
+      mbar_init(&addend_bar[a], 1);
     }
     mbar_fence_init();
     tma_prefetch_desc(&tmA);
@@ -178,6 +188,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const bool out_fp32 = flags & GEMM_OUT_FP32;
     const bool accumulate = flags & GEMM_ACCUMULATE;
     const bool residual = flags & GEMM_RESIDUAL;
+    uint32_t slab_count = 0;
     for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
       int m_blk, n_blk;
       tile_coords(t, m_blk, n_blk);
@@ -186,6 +197,81 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (!mbar_wait(&tmem_full[acc], acc_phase, status, ERR_GEMM_EPI_WAIT)) break;
       tc_fence_after();
       const uint32_t t_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+      if (!out_fp32) {
+        // ---- bf16 output: shared-memory slabs + TMA store ------------------------------------------
+        const int r = quarter * 32 + lane;
+        const bool issuer = (warp == 2 && lane == 0);
+        const bool addend = accumulate || residual;
+        const int m0 = m_blk * GEMM_BM;
+        bool ok = true;
+#pragma unroll 1
+        for (int sl = 0; sl < BN / 64; ++sl) {
+          const int buf = slab_count & 1;
+          uint8_t* sbuf = slabs + buf * Cfg::SLAB_BYTES;
+          const int col0 = n0 + sl * 64;
+          if (issuer) tma_store_wait_read<1>();     // the store that used this buffer two slabs ago is done
+          named_barrier(1, 128);
+          if (addend && issuer && col0 < N) {
+            mbar_expect_tx(&addend_bar[buf], Cfg::SLAB_BYTES);
+            tma_load_2d(sbuf, accumulate ? &tmC : &tmR, &addend_bar[buf], col0, m0);
+          }
+          uint32_t v[64];
+          {
+            uint32_t t[32];
+            tmem_ld_32x32b_x32(t_base + sl * 64, t);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = t[i];
+            tmem_ld_32x32b_x32(t_base + sl * 64 + 32, t);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[32 + i] = t[i];
+          }
+          if (sl == BN / 64 - 1) {   // accumulator fully read: hand it back to the MMA warp
+            tc_fence_before();
+            mbar_arrive(&tmem_empty[acc]);
+          }
+          if (col0 < N) {
+            uint8_t* rowp = sbuf + r * 128;
+            if (addend) {
+              if (ok) ok = mbar_wait(&addend_bar[buf], (slab_count >> 1) & 1, status, ERR_GEMM_EPI_WAIT);
+#pragma unroll
+              for (int c8 = 0; c8 < 8; ++c8) {
+                const uint4 q = *reinterpret_cast<const uint4*>(rowp + ((c8 ^ (r & 7)) << 4));
+                const uint32_t qq[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const float2 f = unpack_bf16x2(qq[j]);
+                  v[c8 * 8 + 2 * j] = __float_as_uint(__uint_as_float(v[c8 * 8 + 2 * j]) + f.x);
+                  v[c8 * 8 + 2 * j + 1] = __float_as_uint(__uint_as_float(v[c8 * 8 + 2 * j + 1]) + f.y);
+                }
+              }
+            }
+#pragma unroll
+            for (int c8 = 0; c8 < 8; ++c8) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(v[c8 * 8 + 0]), __uint_as_float(v[c8 * 8 + 1]));
+              o.y = pack_bf16x2(__uint_as_float(v[c8 * 8 + 2]), __uint_as_float(v[c8 * 8 + 3]));
+              o.z = pack_bf16x2(__uint_as_float(v[c8 * 8 + 4]), __uint_as_float(v[c8 * 8 + 5]));
+              o.w = pack_bf16x2(__uint_as_float(v[c8 * 8 + 6]), __uint_as_float(v[c8 * 8 + 7]));
+              *reinterpret_cast<uint4*>(rowp + ((c8 ^ (r & 7)) << 4)) = o;
+            }
+          }
+          fence_proxy_async_smem();
+          named_barrier(1, 128);
+          if (col0 < N) {
+            if (issuer) {
+              tma_store_2d(&tmC, sbuf, col0, m0);
+              tma_store_commit();
+            }
+            ++slab_count;    // buffer parity and addend-barrier phase advance only when a slab was used
+          }
+        }
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+        if (named_barrier_or(1, 128, !ok)) break;   // all 128 epilogue threads leave together
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -271,6 +357,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1;
     }
+    if (warp == 2 && lane == 0) tma_store_wait_all<0>();   // shared memory stays valid until stores have read it
   }
 
   // Common tail: every thread arrives here, also after a wait that ran out.
@@ -311,6 +398,10 @@ static int launch_gemm(const void* A, const void* B, void* C, const void* R, int
   const CUtensorMap* tb = B_MN ? tensor_map_2d_bf16(B, K, N, ldb, 64, 64)
                                : tensor_map_2d_bf16(B, N, K, ldb, BN, 64);
   if (!ta || !tb) return 2;
+  const bool out_fp32 = flags & GEMM_OUT_FP32;
+  const CUtensorMap* tc = out_fp32 ? ta : tensor_map_2d_bf16(C, M, N, ldc, GEMM_BM, 64);
+  const CUtensorMap* tr = (!out_fp32 && (flags & GEMM_RESIDUAL)) ? tensor_map_2d_bf16(R, M, N, ldc, GEMM_BM, 64) : tc;
+  if (!tc || !tr) return 2;
   int* status = status_ptr();
   if (!status) return 3;
   const int num_tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + BN - 1) / BN);
@@ -318,7 +409,7 @@ static int launch_gemm(const void* A, const void* B, void* C, const void* R, int
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (num_tiles < grid) grid = num_tiles;
   kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(
-      *ta, *tb, C, reinterpret_cast<const __nv_bfloat16*>(R), M, N, K, ldc, flags, g_mn_desc, status);
+      *ta, *tb, *tc, *tr, C, reinterpret_cast<const __nv_bfloat16*>(R), M, N, K, ldc, flags, g_mn_desc, status);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_error("gemm launch failed: %s", cudaGetErrorString(e));
