@@ -52,7 +52,7 @@ class _RMSNorm(torch.autograd.Function):
             nv.check(L.b2_rmsnorm_bwd(nv.ptr(dy), nv.ptr(x), nv.ptr(w), nv.ptr(rstd), nv.ptr(dx),
                                       nv.ptr(tgt), nv.ptr(partial), M, H, 0, int(acc),
                                       int(tgt.dtype == torch.float32), nv.stream_ptr()), "rmsnorm_bwd")
-            nv.count_launch(2)
+            nv.count_launch(3)
             return tgt
 
         dw = grad_into_main(w, run)

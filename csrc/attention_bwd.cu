@@ -42,15 +42,17 @@ __global__ void attn_bwd_prep_kernel(const __nv_bfloat16* __restrict__ o,
 }
 
 // ---------------------------------------------------------------------------------------------
+constexpr int ATB_STAGES = 3;   // streamed-tile ring depth: TMA latency spans about two iterations
+
 struct DkDvSmem {
   static constexpr int K = 0;                 // 32 KiB  [128 x 128]
   static constexpr int V = K + 32768;         // 32 KiB
-  static constexpr int Q = V + 32768;         // 2 x 16 KiB [64 x 128]
-  static constexpr int DO = Q + 2 * 16384;    // 2 x 16 KiB
-  static constexpr int PT = DO + 2 * 16384;   // 2 x 16 KiB [128 x 64]
+  static constexpr int Q = V + 32768;         // STAGES x 16 KiB [64 x 128]
+  static constexpr int DO = Q + ATB_STAGES * 16384;    // STAGES x 16 KiB
+  static constexpr int PT = DO + ATB_STAGES * 16384;   // 2 x 16 KiB [128 x 64]
   static constexpr int DST = PT + 2 * 16384;  // 2 x 16 KiB
   static constexpr int BARS = DST + 2 * 16384;
-  static constexpr int TOTAL = BARS + 128 + 1024 /*lse, D*/ + 1024;
+  static constexpr int TOTAL = BARS + 144 + 1024 /*lse, D*/ + 1024;
 };
 
 __global__ void __launch_bounds__(ATB_THREADS, 1)
@@ -64,15 +66,15 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_con
                                              ~static_cast<uintptr_t>(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + DkDvSmem::BARS);
   uint64_t* kv_full = bars + 0;
-  uint64_t* qdo_full = bars + 1;    // [2]
-  uint64_t* qdo_empty = bars + 3;   // [2]
-  uint64_t* sdp_full = bars + 5;    // [2]
-  uint64_t* sdp_empty = bars + 7;   // [2]
-  uint64_t* pds_full = bars + 9;    // [2]
-  uint64_t* pds_empty = bars + 11;  // [2]
-  uint64_t* acc_done = bars + 13;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
-  float* s_lse = reinterpret_cast<float*>(bars + 16);   // [2][64], pre-multiplied by log2(e)
+  uint64_t* qdo_full = bars + 1;    // [3]
+  uint64_t* qdo_empty = bars + 4;   // [3]
+  uint64_t* sdp_full = bars + 7;    // [2]
+  uint64_t* sdp_empty = bars + 9;   // [2]
+  uint64_t* pds_full = bars + 11;   // [2]
+  uint64_t* pds_empty = bars + 13;  // [2]
+  uint64_t* acc_done = bars + 15;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  float* s_lse = reinterpret_cast<float*>(bars + 18);   // [2][64], pre-multiplied by log2(e)
   float* s_D = s_lse + 128;                             // [2][64]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -88,9 +90,11 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_con
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < ATB_STAGES; ++i) {
       mbar_init(&qdo_full[i], 1);
       mbar_init(&qdo_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
       mbar_init(&sdp_full[i], 1);
       mbar_init(&sdp_empty[i], 256);
       mbar_init(&pds_full[i], 256);
@@ -120,8 +124,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_con
       tma_load_2d(smem + DkDvSmem::V, &tmV, kv_full, kvh * 128, kv_row0);
       tma_load_2d(smem + DkDvSmem::V + 16384, &tmV, kv_full, kvh * 128 + 64, kv_row0);
       for (int it = 0; it < n_it; ++it) {
-        const int st = it & 1;
-        const uint32_t ph = (it >> 1) & 1;
+        const int st = it % ATB_STAGES;
+        const uint32_t ph = (it / ATB_STAGES) & 1;
         const int head = kvh * G + it / per_head;
         const int qrow = batch * S + (i_begin + it % per_head) * 64;
         if (!mbar_wait(&qdo_empty[st], ph ^ 1, status, ERR_ATTN_WAIT)) break;
@@ -142,8 +146,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_con
       const uint32_t v_base = smem_u32(smem + DkDvSmem::V);
       auto issue_sdp = [&](int it) {
         const int st = it & 1;
-        const uint32_t q_base = smem_u32(smem + DkDvSmem::Q + st * 16384);
-        const uint32_t do_base = smem_u32(smem + DkDvSmem::DO + st * 16384);
+        const int ks = it % ATB_STAGES;
+        const uint32_t q_base = smem_u32(smem + DkDvSmem::Q + ks * 16384);
+        const uint32_t do_base = smem_u32(smem + DkDvSmem::DO + ks * 16384);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
           const uint32_t oa = (ks >> 2) * 16384 + (ks & 3) * 32;
@@ -170,7 +175,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_con
         if (it + 1 < n_it) {
           const int st = (it + 1) & 1;
           const uint32_t ph = ((it + 1) >> 1) & 1;
-          if (!mbar_wait(&qdo_full[st], ph, status, ERR_ATTN_WAIT) ||
+          if (!mbar_wait(&qdo_full[(it + 1) % ATB_STAGES], ((it + 1) / ATB_STAGES) & 1, status, ERR_ATTN_WAIT) ||
               !mbar_wait(&sdp_empty[st], ph ^ 1, status, ERR_ATTN_WAIT)) {
             ok = false;
             break;
@@ -186,8 +191,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_con
         tc_fence_after();
         const uint32_t pt_base = smem_u32(smem + DkDvSmem::PT + st * 16384);
         const uint32_t dst_base = smem_u32(smem + DkDvSmem::DST + st * 16384);
-        const uint32_t q_base = smem_u32(smem + DkDvSmem::Q + st * 16384);
-        const uint32_t do_base = smem_u32(smem + DkDvSmem::DO + st * 16384);
+        const int kst = it % ATB_STAGES;
+        const uint32_t q_base = smem_u32(smem + DkDvSmem::Q + kst * 16384);
+        const uint32_t do_base = smem_u32(smem + DkDvSmem::DO + kst * 16384);
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
           umma_f16_ss(tmem_DV, make_smem_desc_sw128(pt_base + ks * 32, 16, 1024),
@@ -196,7 +202,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_con
         for (int ks = 0; ks < 4; ++ks)
           umma_f16_ss(tmem_DK, make_smem_desc_sw128(dst_base + ks * 32, 16, 1024),
                       make_smem_desc_sw128(q_base + ks * 2048, 8192, 1024), idesc_acc, (it | ks) != 0);
-        umma_commit(&qdo_empty[st]);
+        umma_commit(&qdo_empty[kst]);
         umma_commit(&pds_empty[st]);
       }
       if (ok) umma_commit(acc_done);
@@ -320,9 +326,9 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_con
 struct DqSmem {
   static constexpr int Q = 0;                // 32 KiB [128 x 128]
   static constexpr int DO = Q + 32768;       // 32 KiB
-  static constexpr int K = DO + 32768;       // 2 x 16 KiB [64 x 128]
-  static constexpr int V = K + 2 * 16384;    // 2 x 16 KiB
-  static constexpr int DS = V + 2 * 16384;   // 2 x 16 KiB [128 x 64]
+  static constexpr int K = DO + 32768;       // STAGES x 16 KiB [64 x 128]
+  static constexpr int V = K + ATB_STAGES * 16384;    // STAGES x 16 KiB
+  static constexpr int DS = V + ATB_STAGES * 16384;   // 2 x 16 KiB [128 x 64]
   static constexpr int BARS = DS + 2 * 16384;
   static constexpr int TOTAL = BARS + 256 + 1024;
 };
@@ -337,14 +343,14 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
                                              ~static_cast<uintptr_t>(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + DqSmem::BARS);
   uint64_t* q_full = bars + 0;
-  uint64_t* kv_full = bars + 1;    // [2]
-  uint64_t* kv_empty = bars + 3;   // [2]
-  uint64_t* sdp_full = bars + 5;   // [2]
-  uint64_t* sdp_empty = bars + 7;  // [2]
-  uint64_t* ds_full = bars + 9;    // [2]
-  uint64_t* ds_empty = bars + 11;  // [2]
-  uint64_t* acc_done = bars + 13;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint64_t* kv_full = bars + 1;    // [3]
+  uint64_t* kv_empty = bars + 4;   // [3]
+  uint64_t* sdp_full = bars + 7;   // [2]
+  uint64_t* sdp_empty = bars + 9;  // [2]
+  uint64_t* ds_full = bars + 11;   // [2]
+  uint64_t* ds_empty = bars + 13;  // [2]
+  uint64_t* acc_done = bars + 15;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_q_tiles = (S + 127) / 128;
@@ -358,9 +364,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < ATB_STAGES; ++i) {
       mbar_init(&kv_full[i], 1);
       mbar_init(&kv_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
       mbar_init(&sdp_full[i], 1);
       mbar_init(&sdp_empty[i], 256);
       mbar_init(&ds_full[i], 256);
@@ -389,8 +397,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tma_load_2d(smem + DqSmem::DO, &tmdO, q_full, head * 128, row0);
       tma_load_2d(smem + DqSmem::DO + 16384, &tmdO, q_full, head * 128 + 64, row0);
       for (int it = 0; it < n_it; ++it) {
-        const int st = it & 1;
-        const uint32_t ph = (it >> 1) & 1;
+        const int st = it % ATB_STAGES;
+        const uint32_t ph = (it / ATB_STAGES) & 1;
         const int krow = batch * S + it * 64;
         if (!mbar_wait(&kv_empty[st], ph ^ 1, status, ERR_ATTN_WAIT)) break;
         uint8_t* sK = smem + DqSmem::K + st * 16384;
@@ -410,8 +418,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const uint32_t do_base = smem_u32(smem + DqSmem::DO);
       auto issue_sdp = [&](int it) {
         const int st = it & 1;
-        const uint32_t k_base = smem_u32(smem + DqSmem::K + st * 16384);
-        const uint32_t v_base = smem_u32(smem + DqSmem::V + st * 16384);
+        const int ks_ = it % ATB_STAGES;
+        const uint32_t k_base = smem_u32(smem + DqSmem::K + ks_ * 16384);
+        const uint32_t v_base = smem_u32(smem + DqSmem::V + ks_ * 16384);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
           const uint32_t oa = (ks >> 2) * 16384 + (ks & 3) * 32;
@@ -438,7 +447,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (it + 1 < n_it) {
           const int st = (it + 1) & 1;
           const uint32_t ph = ((it + 1) >> 1) & 1;
-          if (!mbar_wait(&kv_full[st], ph, status, ERR_ATTN_WAIT) ||
+          if (!mbar_wait(&kv_full[(it + 1) % ATB_STAGES], ((it + 1) / ATB_STAGES) & 1, status, ERR_ATTN_WAIT) ||
               !mbar_wait(&sdp_empty[st], ph ^ 1, status, ERR_ATTN_WAIT)) {
             ok = false;
             break;
@@ -452,13 +461,14 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           break;
         }
         tc_fence_after();
+        const int kst = it % ATB_STAGES;
         const uint32_t ds_base = smem_u32(smem + DqSmem::DS + st * 16384);
-        const uint32_t k_base = smem_u32(smem + DqSmem::K + st * 16384);
+        const uint32_t k_base = smem_u32(smem + DqSmem::K + kst * 16384);
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
           umma_f16_ss(tmem_DQ, make_smem_desc_sw128(ds_base + ks * 32, 16, 1024),
                       make_smem_desc_sw128(k_base + ks * 2048, 8192, 1024), idesc_acc, (it | ks) != 0);
-        umma_commit(&kv_empty[st]);
+        umma_commit(&kv_empty[kst]);
         umma_commit(&ds_empty[st]);
       }
       if (ok) umma_commit(acc_done);

@@ -175,12 +175,6 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_warp_kernel(
   const int lane = threadIdx.x & 31;
   const int warps_per_grid = (gridDim.x * blockDim.x) >> 5;
   const int nvec = H / 8;
-  float wv[NV][8];
-#pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    const int c = lane + i * 32;
-    if (c < nvec) load8(w + c * 8, wv[i]);
-  }
   for (int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; row < M; row += warps_per_grid) {
     const __nv_bfloat16* xr = x + static_cast<size_t>(row) * H;
     float v[NV][8];
@@ -202,9 +196,10 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_warp_kernel(
     for (int i = 0; i < NV; ++i) {
       const int c = lane + i * 32;
       if (c < nvec) {
-        float o[8];
+        float o[8], wv[8];
+        load8(w + c * 8, wv);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = v[i][j] * rstd * wv[i][j];
+        for (int j = 0; j < 8; ++j) o[j] = v[i][j] * rstd * wv[j];
         store8(yr + c * 8, o);
       }
     }
@@ -276,6 +271,108 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_warp_kernel(
 #pragma unroll
       for (int j = 0; j < 8; ++j) atomicAdd(&sdw[c * 8 + j], dwacc[i][j]);
     }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < H; i += blockDim.x) dw_partial[static_cast<size_t>(blockIdx.x) * H + i] = sdw[i];
+}
+
+// ---------------------------------------------------------------------------------------------
+// RMSNorm backward split in two high-occupancy kernels (H <= 2048):
+//   dx kernel: one warp per row, nothing carried across rows (few registers, many warps in flight);
+//   dw kernel: column reduction dw[h] = sum_r dy[r,h] * x[r,h] * rstd[r]; a thread owns 8 columns and
+//              strides over rows with four independent loads in flight; per-CTA partials.
+// x and dy are read twice, the second time from L2.
+// ---------------------------------------------------------------------------------------------
+template <int NV>
+__global__ void __launch_bounds__(256) rmsnorm_bwd_dx_kernel(
+    const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd_in,
+    __nv_bfloat16* __restrict__ dx, int M, int H, int add_to_dx) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_grid = (gridDim.x * blockDim.x) >> 5;
+  const int nvec = H / 8;
+  for (int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; row < M; row += warps_per_grid) {
+    const __nv_bfloat16* xr = x + static_cast<size_t>(row) * H;
+    const __nv_bfloat16* dyr = dy + static_cast<size_t>(row) * H;
+    __nv_bfloat16* dxr = dx + static_cast<size_t>(row) * H;
+    const float rstd = rstd_in[row];
+    float xh[NV][8], g[NV][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = lane + i * 32;
+      if (c < nvec) {
+        float dv[8], wv[8];
+        load8(xr + c * 8, xh[i]);
+        load8(dyr + c * 8, dv);
+        load8(w + c * 8, wv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[i][j] *= rstd;
+          g[i][j] = dv[j] * wv[j];
+          dot += g[i][j] * xh[i][j];
+        }
+      }
+    }
+    dot = warp_sum(dot) / H;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = lane + i * 32;
+      if (c < nvec) {
+        float o[8];
+        if (add_to_dx) load8(dxr + c * 8, o);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float d = rstd * (g[i][j] - xh[i][j] * dot);
+          o[j] = add_to_dx ? o[j] + d : d;
+        }
+        store8(dxr + c * 8, o);
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) rmsnorm_bwd_dw_kernel(
+    const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
+    const float* __restrict__ rstd_in, float* __restrict__ dw_partial, int M, int H) {
+  // thread -> column vector c = threadIdx.x % nvec (nvec <= 256), row lane rl = threadIdx.x / nvec
+  const int nvec = H / 8;
+  const int rows_per_cta_step = blockDim.x / nvec;       // 1 for H=2048, 2 for H=1024, ...
+  const int c = threadIdx.x % nvec, rl = threadIdx.x / nvec;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  const int stride = gridDim.x * rows_per_cta_step;
+  int row = blockIdx.x * rows_per_cta_step + rl;
+  if (rl < rows_per_cta_step) {
+    for (; row + 3 * stride < M; row += 4 * stride) {
+      float xv[4][8], dv[4][8], rs[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const size_t o = static_cast<size_t>(row + u * stride) * H + c * 8;
+        load8(x + o, xv[u]);
+        load8(dy + o, dv[u]);
+        rs[u] = rstd_in[row + u * stride];
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += dv[u][j] * xv[u][j] * rs[u];
+    }
+    for (; row < M; row += stride) {
+      float xv[8], dv[8];
+      const size_t o = static_cast<size_t>(row) * H + c * 8;
+      load8(x + o, xv);
+      load8(dy + o, dv);
+      const float rs = rstd_in[row];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += dv[j] * xv[j] * rs;
+    }
+  }
+  extern __shared__ float sdw[];   // [H]
+  for (int i = threadIdx.x; i < H; i += blockDim.x) sdw[i] = 0.f;
+  __syncthreads();
+  if (rl < rows_per_cta_step) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) atomicAdd(&sdw[c * 8 + j], acc[j]);
   }
   __syncthreads();
   for (int i = threadIdx.x; i < H; i += blockDim.x) dw_partial[static_cast<size_t>(blockIdx.x) * H + i] = sdw[i];
@@ -514,7 +611,7 @@ B2_EXPORT int b2_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd,
   if (M <= 0) return 0;
   if (H <= 2048) {
     int blocks = (M + 7) / 8;
-    const int cap = num_sms() * 8;
+    const int cap = num_sms() * 16;
     if (blocks > cap) blocks = cap;
     auto xs = static_cast<const __nv_bfloat16*>(x);
     auto ws = static_cast<const __nv_bfloat16*>(w);
@@ -545,15 +642,21 @@ B2_EXPORT int b2_rmsnorm_bwd(const void* dy, const void* x, const void* w, const
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   int ctas = num_sms() * 2;
   if (ctas > M) ctas = M;
-  if (H <= 1024) {
+  if (H <= 2048 && 256 % (H / 8) == 0) {
     auto dys = static_cast<const __nv_bfloat16*>(dy);
     auto xs = static_cast<const __nv_bfloat16*>(x);
     auto ws = static_cast<const __nv_bfloat16*>(w);
     auto dxs = static_cast<__nv_bfloat16*>(dx);
-    const int smem = H * static_cast<int>(sizeof(float));
-    rmsnorm_bwd_warp_kernel<4><<<ctas, 256, smem, stream>>>(dys, xs, ws, rstd, dxs, dw_partial, M, H, add_to_dx);
-    B2_LAUNCH_CHECK("rmsnorm_bwd");
-    reduce_partials_kernel<<<(H + 255) / 256, 256, 0, stream>>>(dw_partial, dw, ctas, H, accumulate_dw, dw_fp32);
+    int blocks = (M + 7) / 8;
+    const int cap = num_sms() * 8;
+    if (blocks > cap) blocks = cap;
+    if (H <= 1024) rmsnorm_bwd_dx_kernel<4><<<blocks, 256, 0, stream>>>(dys, xs, ws, rstd, dxs, M, H, add_to_dx);
+    else rmsnorm_bwd_dx_kernel<8><<<blocks, 256, 0, stream>>>(dys, xs, ws, rstd, dxs, M, H, add_to_dx);
+    B2_LAUNCH_CHECK("rmsnorm_bwd_dx");
+    const int dw_ctas = ctas > num_sms() ? num_sms() : ctas;
+    rmsnorm_bwd_dw_kernel<<<dw_ctas, 256, H * static_cast<int>(sizeof(float)), stream>>>(dys, xs, rstd, dw_partial, M, H);
+    B2_LAUNCH_CHECK("rmsnorm_bwd_dw");
+    reduce_partials_kernel<<<(H + 63) / 64, 64, 0, stream>>>(dw_partial, dw, dw_ctas, H, accumulate_dw, dw_fp32);
     B2_LAUNCH_CHECK("rmsnorm_bwd_reduce");
     return 0;
   }
