@@ -756,3 +756,65 @@ B2_EXPORT int b2_embedding_bwd(const long long* ids, const void* dout, void* dta
   B2_LAUNCH_CHECK("embedding_bwd");
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of the RMSNorm backward (declared and documented in no_alloc.h).
+// ---------------------------------------------------------------------------------------------
+#include "no_alloc.h"
+
+// Per-CTA partial sums of the weight gradient.  In host code this name is only a handle for the
+// runtime's symbol lookup, never a device address: the address is fetched once per device below.
+static __device__ __align__(256) float g_noalloc_dw_partial[B2_NOALLOC_MAX_PARTIALS * B2_NOALLOC_MAX_H];
+
+static float* noalloc_scratch_ptr() {
+  static float* ptrs[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    set_error("rmsnorm_bwd_noalloc: cannot determine the current device");
+    return nullptr;
+  }
+  if (ptrs[dev] == nullptr) {
+    float* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_dw_partial);
+    if (e != cudaSuccess || p == nullptr) {
+      set_error("rmsnorm_bwd_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return nullptr;
+    }
+    ptrs[dev] = p;
+  }
+  return ptrs[dev];
+}
+
+B2_EXPORT int b2_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd,
+                                     void* dx, void* dw, int M, int H, int add_to_dx, int accumulate_dw,
+                                     int dw_fp32, void* stream_) {
+  b2::ensure_thread_context();
+  if (M <= 0) return 0;
+  if (H <= 0 || H % 8 != 0 || H > B2_NOALLOC_MAX_H || 256 % (H / 8) != 0) {
+    set_error("rmsnorm_bwd_noalloc: H=%d is outside the built-in scratch (multiple of 8, <= %d, 256 %% (H/8) == 0)",
+              H, B2_NOALLOC_MAX_H);
+    return 10;
+  }
+  float* partial = noalloc_scratch_ptr();   // first call per device: symbol lookup (not during capture)
+  if (partial == nullptr) return 3;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  int dw_ctas = num_sms();
+  if (dw_ctas > B2_NOALLOC_MAX_PARTIALS) dw_ctas = B2_NOALLOC_MAX_PARTIALS;
+  if (dw_ctas > M) dw_ctas = M;
+  auto dys = static_cast<const __nv_bfloat16*>(dy);
+  auto xs = static_cast<const __nv_bfloat16*>(x);
+  auto ws = static_cast<const __nv_bfloat16*>(w);
+  auto dxs = static_cast<__nv_bfloat16*>(dx);
+  int blocks = (M + 7) / 8;
+  const int cap = num_sms() * 8;
+  if (blocks > cap) blocks = cap;
+  if (H <= 1024) rmsnorm_bwd_dx_kernel<4><<<blocks, 256, 0, stream>>>(dys, xs, ws, rstd, dxs, M, H, add_to_dx);
+  else rmsnorm_bwd_dx_kernel<8><<<blocks, 256, 0, stream>>>(dys, xs, ws, rstd, dxs, M, H, add_to_dx);
+  B2_LAUNCH_CHECK("rmsnorm_bwd_noalloc(dx)");
+  // every CTA writes its whole [H] row of partials, so stale contents of the shared array are never read
+  rmsnorm_bwd_dw_kernel<<<dw_ctas, 256, H * static_cast<int>(sizeof(float)), stream>>>(dys, xs, rstd, partial, M, H);
+  B2_LAUNCH_CHECK("rmsnorm_bwd_noalloc(dw)");
+  reduce_partials_kernel<<<(H + 63) / 64, 64, 0, stream>>>(partial, dw, dw_ctas, H, accumulate_dw, dw_fp32);
+  B2_LAUNCH_CHECK("rmsnorm_bwd_noalloc(reduce)");
+  return 0;
+}
