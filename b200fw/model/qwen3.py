@@ -63,12 +63,17 @@ class ColumnParallelLinear(nn.Module):
         self.in_features, self.out_features = in_features, out_features
         self.out_local = out_features // self.tp_size
         self.gather_output, self.sequence_parallel = gather_output, sequence_parallel
+        self.fused_comm = False     # set by the model: run the collective inside the GEMM kernel
         self.weight = nn.Parameter(torch.empty(self.out_local, in_features, dtype=dtype, device=device))
         nn.init.normal_(self.weight, std=init_std)
 
     def forward(self, x):
         shape = x.shape
         x = x.reshape(-1, shape[-1])
+        if self.tp_size > 1 and self.sequence_parallel and self.fused_comm and x.is_cuda and x.shape[0] % 128 == 0:
+            from ..ops import fused_tp
+            y = fused_tp.column_linear_sp(x, self.weight, self.tp_group)    # all-gather inside the GEMM
+            return y
         if self.tp_size > 1:
             x = comm.gather_sequence(x, self.tp_group) if self.sequence_parallel \
                 else comm.copy_to_parallel_region(x, self.tp_group)
@@ -96,6 +101,7 @@ class RowParallelLinear(nn.Module):
         self.in_features, self.out_features = in_features, out_features
         self.in_local = in_features // self.tp_size
         self.sequence_parallel = sequence_parallel
+        self.fused_comm = False
         self.weight = nn.Parameter(torch.empty(out_features, self.in_local, dtype=dtype, device=device))
         nn.init.normal_(self.weight, std=init_std)
 
@@ -104,6 +110,9 @@ class RowParallelLinear(nn.Module):
         x = x.reshape(-1, shape[-1])
         if self.tp_size == 1:
             y = ops.linear(x, self.weight, residual)
+        elif self.sequence_parallel and self.fused_comm and x.is_cuda and (x.shape[0] // self.tp_size) % 128 == 0:
+            from ..ops import fused_tp
+            return fused_tp.row_linear_sp(x, self.weight, residual, self.tp_group)   # reduce-scatter inside the GEMM
         elif self.sequence_parallel:
             y = comm.reduce_scatter_sequence(ops.linear(x, self.weight), self.tp_group)
             if residual is not None:
@@ -214,6 +223,13 @@ class ParallelTransformerModel(nn.Module):
                 self.lm_head = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device))
                 nn.init.normal_(self.lm_head, std=cfg.init_std)
         self._tag_parameters()
+
+    def set_fused_comm(self, on: bool = True):
+        """Run every sequence-parallel linear's collective inside its GEMM kernel (peer loads / stores
+        over NVLink) instead of as separate NCCL calls."""
+        for m in self.modules():
+            if isinstance(m, (ColumnParallelLinear, RowParallelLinear)):
+                m.fused_comm = on and self.sequence_parallel
 
     def _tag_parameters(self):
         # parameters whose per-rank gradient is only a partial sum under TP (their inputs are head-

@@ -1,0 +1,184 @@
+"""Tensor-parallel linear layers whose collective runs INSIDE the tcgen05 GEMM kernel.
+
+* :func:`allgather_gemm`   — column-parallel forward (and the input-gradient GEMM of a row-parallel
+  layer): the sequence-parallel activation shards of all ranks are pulled into a local gather buffer by
+  extra warps of the GEMM kernel while its MMA pipeline already works on the rows that have arrived.
+* :func:`gemm_reduce_scatter` — row-parallel forward (and the input-gradient GEMM of a column-parallel
+  layer): every output tile goes straight to the rank that owns those rows; each rank sums its rows
+  over the source ranks (and adds the residual) as soon as the tiles land.
+
+Replaces ``all_gather`` / ``all_reduce`` + ``F.linear`` pairs of the reference's parallel layers
+(src/distributed/tensor_parallel.py:156-159,236-239; the reference all-reduces replicated activations,
+it has no sequence parallelism).  Buffers live in symmetric memory (:mod:`b200fw.dist.symm`); two
+parities alternate so that a rank that runs ahead never overwrites data a peer still reads; counters
+and flags only grow (epochs), nothing is reset between calls.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from .. import _native as nv
+from ..dist.symm import FlagBarrier, SymmetricBuffer
+from .gemm import gemm, grad_into_main
+
+
+class _RSState:
+    def __init__(self, group, rows, N, bn, device):
+        self.world = dist.get_world_size(group)
+        nb = (N + bn - 1) // bn
+        self.recv = [SymmetricBuffer(self.world * rows * N, torch.bfloat16, group, device) for _ in range(2)]
+        self.cnt = [SymmetricBuffer((rows // 128) * nb, torch.int32, group, device) for _ in range(2)]
+        self.epoch = [0, 0]
+        self.calls = 0
+
+
+class _AGState:
+    def __init__(self, group, rows, K, device):
+        self.world = dist.get_world_size(group)
+        self.src = [SymmetricBuffer(rows * K, torch.bfloat16, group, device) for _ in range(2)]
+        self.flags = torch.zeros(self.world * rows // 128, dtype=torch.int32, device=device)
+        self.epoch = 0
+        self.calls = 0
+
+
+class FusedTPContext:
+    """Per-TP-group workspace cache and the flag barrier that orders buffer reuse across ranks."""
+
+    _by_group: Dict[int, "FusedTPContext"] = {}
+
+    def __init__(self, group):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        self.rs: Dict[Tuple[int, int, int], _RSState] = {}
+        self.ag: Dict[Tuple[int, int], _AGState] = {}
+        self.barrier = FlagBarrier(group, self.device)
+
+    @classmethod
+    def get(cls, group) -> "FusedTPContext":
+        key = id(group)
+        if key not in cls._by_group:
+            cls._by_group[key] = cls(group)
+        return cls._by_group[key]
+
+
+def _bn_for(M: int, N: int) -> int:
+    return 256 if (N % 256 == 0 and ((M + 127) // 128) * (N // 256) >= 148) else 128
+
+
+def gemm_reduce_scatter(x: torch.Tensor, w: torch.Tensor, group, *, b_mn: bool = False,
+                        residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``reduce_scatter_rows(x @ w^T) (+ residual)``: ``x [M, K_local]``, ``w [N, K_local]`` (or
+    ``[K_local, N]`` with ``b_mn``); returns this rank's ``[M/world, N]`` rows."""
+    ctx = FusedTPContext.get(group)
+    M, K = x.shape
+    N = w.shape[1] if b_mn else w.shape[0]
+    rows = M // ctx.world
+    assert M % ctx.world == 0 and rows % 128 == 0 and x.is_contiguous() and w.stride(-1) == 1
+    bn = _bn_for(M, N)
+    key = (rows, N, bn)
+    st = ctx.rs.get(key)
+    if st is None:
+        st = ctx.rs[key] = _RSState(group, rows, N, bn, ctx.device)
+        ctx.barrier.barrier(2)       # everyone's buffers exist and are zeroed before the first tile lands
+    par = st.calls & 1
+    st.calls += 1
+    st.epoch[par] += 1
+    out = torch.empty((rows, N), device=x.device, dtype=torch.bfloat16)
+    if residual is not None:
+        assert residual.shape == (rows, N) and residual.is_contiguous()
+    nv.check(nv.lib().b2_gemm_bf16_comm(
+        1, nv.ptr(x), nv.ptr(w), nv.ptr(None), M, N, K, w.stride(0), int(b_mn), bn, st.recv[par].ptr_array,
+        st.cnt[par].ptr_array, nv.ptr(out), nv.ptr(residual), None, nv.ptr(None), nv.ptr(None), ctx.world, ctx.rank,
+        rows, st.epoch[par], nv.stream_ptr()), "gemm_reduce_scatter")
+    nv.count_launch()
+    return out
+
+
+def allgather_gemm(x_shard: torch.Tensor, w: torch.Tensor, group, *, b_mn: bool = False
+                   ) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``all_gather_rows(x_shard) @ w^T``: ``x_shard [M/world, K]``; returns ``(y [M, N], gathered x
+    [M, K])`` — the gathered activations are kept for the weight-gradient GEMM."""
+    ctx = FusedTPContext.get(group)
+    rows, K = x_shard.shape
+    N = w.shape[1] if b_mn else w.shape[0]
+    M = rows * ctx.world
+    assert rows % 128 == 0 and w.stride(-1) == 1
+    key = (rows, K)
+    st = ctx.ag.get(key)
+    if st is None:
+        st = ctx.ag[key] = _AGState(group, rows, K, ctx.device)
+    par = st.calls & 1
+    st.calls += 1
+    st.epoch += 1
+    src = st.src[par]
+    src.tensor.view(rows, K).copy_(x_shard)
+    # all ranks have published their shard (and finished reading this parity's previous contents)
+    ctx.barrier.barrier(3)
+    gathered = torch.empty((M, K), device=x_shard.device, dtype=torch.bfloat16)
+    y = torch.empty((M, N), device=x_shard.device, dtype=torch.bfloat16)
+    bn = _bn_for(M, N)
+    nv.check(nv.lib().b2_gemm_bf16_comm(
+        2, nv.ptr(None), nv.ptr(w), nv.ptr(y), M, N, K, w.stride(0), int(b_mn), bn, None, None, nv.ptr(None),
+        nv.ptr(None), src.ptr_array, nv.ptr(gathered), nv.ptr(st.flags), ctx.world, ctx.rank, rows, st.epoch,
+        nv.stream_ptr()), "allgather_gemm")
+    nv.count_launch()
+    return y, gathered
+
+
+class _ColumnLinearSP(torch.autograd.Function):
+    """y = all_gather(x) @ W^T with the gather inside the GEMM; backward: dx = reduce_scatter(dy @ W)
+    inside the GEMM, dW = dy^T @ gathered x."""
+
+    @staticmethod
+    def forward(ctx, x, w, group):
+        y, xg = allgather_gemm(x, w, group)
+        ctx.save_for_backward(xg, w)
+        ctx.group = group
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        xg, w = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = gemm_reduce_scatter(dy, w, ctx.group, b_mn=True)
+        dw = grad_into_main(w, lambda out, acc: gemm(dy, xg, a_mn=True, b_mn=True, out=out, accumulate=acc))
+        return dx, dw, None
+
+
+class _RowLinearSP(torch.autograd.Function):
+    """y = reduce_scatter(x @ W^T) + residual inside the GEMM; backward: dx = all_gather(dy) @ W with
+    the gather inside the GEMM, dW = gathered dy^T @ x."""
+
+    @staticmethod
+    def forward(ctx, x, w, residual, group):
+        ctx.save_for_backward(x, w)
+        ctx.group = group
+        ctx.has_res = residual is not None
+        return gemm_reduce_scatter(x, w, group, residual=residual)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx, dyg = allgather_gemm(dy, w, ctx.group, b_mn=True)
+        dw = grad_into_main(w, lambda out, acc: gemm(dyg, x, a_mn=True, b_mn=True, out=out, accumulate=acc))
+        return dx, dw, (dy if ctx.has_res else None), None
+
+
+def column_linear_sp(x: torch.Tensor, w: torch.Tensor, group) -> torch.Tensor:
+    return _ColumnLinearSP.apply(x.contiguous(), w, group)
+
+
+def row_linear_sp(x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor], group) -> torch.Tensor:
+    return _RowLinearSP.apply(x.contiguous(), w, residual, group)
+
+
+def supported(x_rows_local_or_total: int, world: int, sharded_rows: bool) -> bool:
+    rows = x_rows_local_or_total if sharded_rows else x_rows_local_or_total // max(world, 1)
+    return rows > 0 and rows % 128 == 0 and world <= 8

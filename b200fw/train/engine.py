@@ -76,6 +76,7 @@ class TrainConfig:
     adam_beta2: float = 0.999
     adam_eps: float = 1e-8
     bucket_mb: float = 64.0
+    fused_tp_comm: bool = False                 # TP+SP: all-gather / reduce-scatter inside the GEMM kernels
     zero_comm_backend: str = "nccl"           # "nccl" | "p2p" (reduce-scatter / all-gather inside the optimizer kernels)
     build_ref_model: Optional[bool] = None      # default: grpo_beta > 0, as in the reference
     backend: Optional[str] = None               # nccl / gloo (default by device)
@@ -160,6 +161,8 @@ class TrainEngine:
             mc, ctx, layer_range, first, last, sequence_parallel=cfg.sequence_parallel,
             gradient_checkpointing=cfg.use_gradient_checkpoint, dtype=self.dtype, device=self.device)
         self.model.init_weights(cfg.seed)
+        if cfg.fused_tp_comm and cfg.sequence_parallel and self.device.type == "cuda":
+            self.model.set_fused_comm(True)
         if cfg.model_path and os.path.isdir(cfg.model_path):
             loaded, missing = load_from_hf_checkpoint(self.model, cfg.model_path)
             logger.info("loaded %d tensors from %s (%d missing)", loaded, cfg.model_path, missing)

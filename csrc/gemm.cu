@@ -18,6 +18,8 @@
 // let the epilogue of tile i overlap the main loop of tile i+1.  One CTA per SM (TMEM and shared
 // memory are sized for that), grid = min(#tiles, #SMs), static round-robin tile schedule with
 // M-grouped rasterisation for L2 reuse.
+#include <cstring>
+
 #include "common.cuh"
 #include "host.h"
 
@@ -48,13 +50,70 @@ struct GemmMnDesc {
   uint32_t lbo, sbo, kstep;
 };
 
-template <int BN, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+// Communication fused into the GEMM (tensor-parallel layers with sequence-parallel activations):
+//   COMM 1  GEMM -> reduce-scatter: every output tile is stored straight into the receive buffer of
+//           the rank that owns those rows (peer stores over NVLink), a per-tile counter on the owner
+//           is bumped with a system-scope release, and after its own tiles each CTA reduces finished
+//           row blocks of THIS rank's shard (sum over source ranks + residual).
+//   COMM 2  all-gather -> GEMM: four extra warps per CTA pull 128-row blocks of the peers' activation
+//           shards into a local gather buffer (plain peer loads, local stores) and publish a flag per
+//           block; the TMA producer waits for a block's flag before loading A tiles from the LOCAL
+//           gather buffer.  No TMA ever targets another GPU's memory and no clusters are used.
+struct GemmComm {
+  void* peer_recv[8];       // COMM 1: [world][rows_per_rank][N] bf16 receive buffer on each rank
+  int* peer_cnt[8];         // COMM 1: per (row block, n block) arrival counters on each rank
+  const void* peer_src[8];  // COMM 2: [rows_per_rank][K] bf16 activation shard on each rank
+  void* gather;             // COMM 2: local [M][K] bf16 gather buffer (the A operand)
+  int* gather_flags;        // COMM 2: local per-128-row-block flags
+  void* out;                // COMM 1: [rows_per_rank][N] bf16 result of the reduce
+  const void* residual;     // COMM 1: optional [rows_per_rank][N] bf16 added in the reduce
+  int world, rank, rows_per_rank, epoch;
+};
+
+__device__ __forceinline__ void red_release_sys_add(int* p, int v) {
+  asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys_s32(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ int ld_acquire_gpu_s32(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu_s32(int* p, int v) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// Bounded spin until *p >= value (acquire).  sys: the writer is another GPU.
+template <bool SYS>
+__device__ __forceinline__ bool wait_flag_ge(const int* p, int value, int* status, int code) {
+  unsigned long long t0 = 0;
+  for (uint32_t it = 0;; ++it) {
+    const int v = SYS ? ld_acquire_sys_s32(p) : ld_acquire_gpu_s32(p);
+    if (v >= value) return true;
+    if ((it & 63u) == 63u) {
+      const unsigned long long now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      if (*reinterpret_cast<volatile int*>(status) != 0) return false;
+      if (now - t0 > WAIT_LIMIT_NS) {
+        atomicCAS(status, 0, code);
+        return false;
+      }
+    }
+    __nanosleep(100);
+  }
+}
+
+template <int BN, bool A_MN, bool B_MN, int COMM>
+__global__ void __launch_bounds__(COMM == 2 ? GEMM_THREADS + 128 : GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmR,
                  void* __restrict__ Cout, const __nv_bfloat16* __restrict__ R, int M, int N, int K,
-                 int ldc, int flags, GemmMnDesc mn, int* status) {
+                 int ldc, int flags, GemmMnDesc mn, const __grid_constant__ GemmComm comm, int* status) {
   using Cfg = GemmCfg<BN>;
+  static_assert(COMM == 0 || !A_MN, "fused communication paths take a K-major A operand");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -106,6 +165,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int r = t - g * per_group;
     m_blk = first_m + (r % gsz);
     n_blk = r / gsz;
+    if (COMM != 0) {
+      // COMM 1: tiles owned by other ranks first (rank+1, rank+2, ...), own rows last, so that peers
+      // can start reducing early.  COMM 2: own rows first (already local), then in ring order.
+      const int bpr = comm.rows_per_rank / GEMM_BM;
+      const int rot = (COMM == 1 ? (comm.rank + 1) % comm.world : comm.rank) * bpr;
+      m_blk = (m_blk + rot) % num_m;
+    }
   };
 
   if (warp == 0) {
@@ -116,6 +182,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         int m_blk, n_blk;
         tile_coords(t, m_blk, n_blk);
         const int m0 = m_blk * GEMM_BM, n0 = n_blk * BN;
+        if (COMM == 2) {   // the A rows of this tile must have arrived in the local gather buffer
+          if (!wait_flag_ge<false>(comm.gather_flags + m_blk, comm.epoch, status, ERR_COMM_FLAG_WAIT)) {
+            ok = false;
+            break;
+          }
+          asm volatile("fence.proxy.async;" ::: "memory");
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, status, ERR_GEMM_PRODUCER_WAIT)) {
             ok = false;
@@ -182,6 +255,25 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (acc == 0) acc_phase ^= 1;
       }
     }
+  } else if (COMM == 2 && warp >= 6) {
+    // ---- gather warps: pull peers' shards into the local gather buffer, block by block -------------
+    const int ct = threadIdx.x - 192;                 // 0..127
+    const int bpr = comm.rows_per_rank / GEMM_BM;
+    const int vec_per_row = K / 8;
+    const int total_vec = GEMM_BM * vec_per_row;
+    for (int i = blockIdx.x; i < num_m; i += gridDim.x) {
+      const int rb = (comm.rank * bpr + i) % num_m;   // own blocks first, then ring order
+      const int src = rb / bpr;
+      const uint4* from = reinterpret_cast<const uint4*>(
+          static_cast<const __nv_bfloat16*>(comm.peer_src[src]) + static_cast<size_t>(rb % bpr) * GEMM_BM * K);
+      uint4* to = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(comm.gather) +
+                                           static_cast<size_t>(rb) * GEMM_BM * K);
+      for (int v = ct; v < total_vec; v += 128) to[v] = __ldcg(from + v);
+      asm volatile("fence.proxy.async;" ::: "memory");   // generic-proxy writes -> visible to TMA reads
+      __threadfence();
+      named_barrier(2, 128);
+      if (ct == 0) st_release_gpu_s32(comm.gather_flags + rb, comm.epoch);
+    }
   } else {
     const int quarter = warp & 3;  // TMEM lane quarter this warp may read
     uint32_t acc = 0, acc_phase = 0;
@@ -194,9 +286,51 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tile_coords(t, m_blk, n_blk);
       const int n0 = n_blk * BN;
       const int row = m_blk * GEMM_BM + quarter * 32 + lane;
-      if (!mbar_wait(&tmem_full[acc], acc_phase, status, ERR_GEMM_EPI_WAIT)) break;
+      if (COMM == 1) {
+        // leave together: the epilogue threads meet at named barriers further down
+        const bool got = mbar_wait(&tmem_full[acc], acc_phase, status, ERR_GEMM_EPI_WAIT);
+        if (named_barrier_or(1, 128, !got)) break;
+      } else if (!mbar_wait(&tmem_full[acc], acc_phase, status, ERR_GEMM_EPI_WAIT)) {
+        break;
+      }
       tc_fence_after();
       const uint32_t t_base = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+      if (COMM == 1) {
+        // ---- reduce-scatter: store the tile into the owner's receive slot for this source rank -------
+        const int owner = (m_blk * GEMM_BM) / comm.rows_per_rank;
+        const int lrow = row - owner * comm.rows_per_rank;        // row inside the owner's shard
+        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(comm.peer_recv[owner]) +
+                             (static_cast<size_t>(comm.rank) * comm.rows_per_rank + lrow) * N;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(t_base + c * 32, r);
+          tmem_ld_wait();
+          const int col0 = n0 + c * 32;
+          if (row < M && col0 + 32 <= N) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
+              o.y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+              o.z = pack_bf16x2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+              o.w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+              *reinterpret_cast<uint4*>(dst + col0 + v * 8) = o;
+            }
+          }
+        }
+        tc_fence_before();
+        mbar_arrive(&tmem_empty[acc]);
+        __threadfence_system();            // this thread's peer stores are ordered before the signal
+        named_barrier(1, 128);
+        if (warp == 2 && lane == 0) {
+          const int rb = (m_blk * GEMM_BM - owner * comm.rows_per_rank) / GEMM_BM;
+          red_release_sys_add(comm.peer_cnt[owner] + rb * num_n + n_blk, 1);
+        }
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1;
+        continue;
+      }
       if (!out_fp32) {
         // ---- bf16 output: shared-memory slabs + TMA store ------------------------------------------
         const int r = quarter * 32 + lane;
@@ -358,6 +492,55 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (acc == 0) acc_phase ^= 1;
     }
     if (warp == 2 && lane == 0) tma_store_wait_all<0>();   // shared memory stays valid until stores have read it
+    if (COMM == 1) {
+      // ---- reduce phase: sum this rank's row blocks over all source ranks as they complete -----------
+      const int et = threadIdx.x - 64;               // 0..127
+      const int ewarp = et >> 5;
+      const int bpr = comm.rows_per_rank / GEMM_BM;
+      const int jobs = bpr * num_n;
+      const __nv_bfloat16* recv = static_cast<const __nv_bfloat16*>(comm.peer_recv[comm.rank]);
+      const int* cnt = comm.peer_cnt[comm.rank];
+      bool ok = true;
+      for (int j = blockIdx.x; j < jobs; j += gridDim.x) {
+        const int rb = j / num_n, nb = j % num_n;
+        if (et == 0 && ok) ok = wait_flag_ge<true>(cnt + rb * num_n + nb, comm.world * comm.epoch, status, ERR_COMM_FLAG_WAIT);
+        if (named_barrier_or(1, 128, !ok)) break;
+        const int c = nb * BN + lane * 8;            // 32 lanes x 8 columns = one 256-column row segment
+        for (int rr = ewarp; rr < GEMM_BM; rr += 4) {
+          const int lrow = rb * GEMM_BM + rr;
+          if (c >= N || (BN == 128 && lane >= 16)) continue;
+          float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          for (int s_ = 0; s_ < comm.world; ++s_) {
+            const uint4 q = __ldcg(reinterpret_cast<const uint4*>(
+                recv + (static_cast<size_t>(s_) * comm.rows_per_rank + lrow) * N + c));
+            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const float2 f = unpack_bf16x2(w[k]);
+              a[2 * k] += f.x;
+              a[2 * k + 1] += f.y;
+            }
+          }
+          if (comm.residual) {
+            const uint4 q = *reinterpret_cast<const uint4*>(
+                static_cast<const __nv_bfloat16*>(comm.residual) + static_cast<size_t>(lrow) * N + c);
+            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const float2 f = unpack_bf16x2(w[k]);
+              a[2 * k] += f.x;
+              a[2 * k + 1] += f.y;
+            }
+          }
+          uint4 o;
+          o.x = pack_bf16x2(a[0], a[1]);
+          o.y = pack_bf16x2(a[2], a[3]);
+          o.z = pack_bf16x2(a[4], a[5]);
+          o.w = pack_bf16x2(a[6], a[7]);
+          *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(comm.out) + static_cast<size_t>(lrow) * N + c) = o;
+        }
+      }
+    }
   }
 
   // Common tail: every thread arrives here, also after a wait that ran out.
@@ -377,11 +560,15 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
 static GemmMnDesc g_mn_desc = {8192u, 1024u, 2048u};
 
-template <int BN, bool A_MN, bool B_MN>
+template <int BN, bool A_MN, bool B_MN, int COMM = 0>
 static int launch_gemm(const void* A, const void* B, void* C, const void* R, int M, int N, int K,
-                       int lda, int ldb, int ldc, int flags, int max_ctas, cudaStream_t stream) {
+                       int lda, int ldb, int ldc, int flags, int max_ctas, cudaStream_t stream,
+                       const GemmComm* comm_in = nullptr) {
   using Cfg = GemmCfg<BN>;
-  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN>;
+  auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, COMM>;
+  GemmComm comm;
+  memset(&comm, 0, sizeof(comm));
+  if (comm_in) comm = *comm_in;
   static bool configured[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -399,7 +586,7 @@ static int launch_gemm(const void* A, const void* B, void* C, const void* R, int
                                : tensor_map_2d_bf16(B, N, K, ldb, BN, 64);
   if (!ta || !tb) return 2;
   const bool out_fp32 = flags & GEMM_OUT_FP32;
-  const CUtensorMap* tc = out_fp32 ? ta : tensor_map_2d_bf16(C, M, N, ldc, GEMM_BM, 64);
+  const CUtensorMap* tc = (out_fp32 || COMM == 1) ? ta : tensor_map_2d_bf16(C, M, N, ldc, GEMM_BM, 64);
   const CUtensorMap* tr = (!out_fp32 && (flags & GEMM_RESIDUAL)) ? tensor_map_2d_bf16(R, M, N, ldc, GEMM_BM, 64) : tc;
   if (!tc || !tr) return 2;
   int* status = status_ptr();
@@ -408,8 +595,8 @@ static int launch_gemm(const void* A, const void* B, void* C, const void* R, int
   int grid = num_sms();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (num_tiles < grid) grid = num_tiles;
-  kern<<<grid, GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(
-      *ta, *tb, *tc, *tr, C, reinterpret_cast<const __nv_bfloat16*>(R), M, N, K, ldc, flags, g_mn_desc, status);
+  kern<<<grid, COMM == 2 ? GEMM_THREADS + 128 : GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(
+      *ta, *tb, *tc, *tr, C, reinterpret_cast<const __nv_bfloat16*>(R), M, N, K, ldc, flags, g_mn_desc, comm, status);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_error("gemm launch failed: %s", cudaGetErrorString(e));
@@ -467,4 +654,65 @@ B2_EXPORT void b2_gemm_set_mn_desc(unsigned lbo, unsigned sbo, unsigned kstep) {
   b2::g_mn_desc.lbo = lbo;
   b2::g_mn_desc.sbo = sbo;
   b2::g_mn_desc.kstep = kstep;
+}
+
+
+// Tensor-parallel GEMMs with the collective inside the kernel.  mode 1: GEMM -> reduce-scatter,
+// mode 2: all-gather -> GEMM.  b_mn as in b2_gemm_bf16; A is K-major.  M = world * rows_per_rank rows in
+// total, rows_per_rank a multiple of 128.  Pointer arrays have `world` entries (peer pointers of the
+// symmetric buffers).  epoch: the 1-based call count of this (buffer, counter) set; counters and flags
+// only ever grow, nothing is reset between calls.
+//   mode 1: A [M,K] local, out [rows_per_rank, N]; recv[r]: [world, rows_per_rank, N] on rank r; cnt[r]:
+//           int32 [(rows_per_rank/128) * ceil(N/bn)] on rank r.
+//   mode 2: src[r]: rank r's [rows_per_rank, K] shard; gather: local [M, K]; gather_flags: local
+//           int32 [M/128]; C [M, N] local output.
+B2_EXPORT int b2_gemm_bf16_comm(int mode, const void* A, const void* B, void* C, int M, int N, int K, int ldb,
+                                int b_mn, int bn, void* const* recv, void* const* cnt, void* out,
+                                const void* residual, void* const* src, void* gather, void* gather_flags,
+                                int world, int rank, int rows_per_rank, int epoch, void* stream_) {
+  using namespace b2;
+  b2::ensure_thread_context();
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (world < 1 || world > 8 || rows_per_rank % GEMM_BM != 0 || M != world * rows_per_rank || (K % 8) || (N % 8) ||
+      (mode != 1 && mode != 2) || (bn != 128 && bn != 256)) {
+    set_error("gemm_comm: need world <= 8, rows_per_rank %% 128 == 0, M == world*rows_per_rank, K,N %% 8 == 0");
+    return 10;
+  }
+  if (mode == 1 && (N % 32) != 0) {
+    set_error("gemm_comm: reduce-scatter mode needs N %% 32 == 0");
+    return 10;
+  }
+  GemmComm comm;
+  memset(&comm, 0, sizeof(comm));
+  for (int r = 0; r < world; ++r) {
+    if (mode == 1) {
+      comm.peer_recv[r] = recv[r];
+      comm.peer_cnt[r] = static_cast<int*>(cnt[r]);
+    } else {
+      comm.peer_src[r] = src[r];
+    }
+  }
+  comm.gather = gather;
+  comm.gather_flags = static_cast<int*>(gather_flags);
+  comm.out = out;
+  comm.residual = residual;
+  comm.world = world;
+  comm.rank = rank;
+  comm.rows_per_rank = rows_per_rank;
+  comm.epoch = epoch;
+  const void* Aop = mode == 2 ? gather : A;
+#define B2_COMM_CASE(BN_, BMN_, MODE_)                                                                   \
+  if (bn == BN_ && b_mn == BMN_ && mode == MODE_)                                                        \
+    return launch_gemm<BN_, false, BMN_ != 0, MODE_>(Aop, B, C, nullptr, M, N, K, K, ldb, N, 0, 0, stream, &comm);
+  B2_COMM_CASE(256, 0, 1)
+  B2_COMM_CASE(256, 1, 1)
+  B2_COMM_CASE(128, 0, 1)
+  B2_COMM_CASE(128, 1, 1)
+  B2_COMM_CASE(256, 0, 2)
+  B2_COMM_CASE(256, 1, 2)
+  B2_COMM_CASE(128, 0, 2)
+  B2_COMM_CASE(128, 1, 2)
+#undef B2_COMM_CASE
+  set_error("gemm_comm: unsupported configuration");
+  return 11;
 }
