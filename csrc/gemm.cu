@@ -106,6 +106,61 @@ __device__ __forceinline__ bool wait_flag_ge(const int* p, int value, int* statu
   }
 }
 
+// Sum ROWS rows per step over up to MAXW source ranks (all loads issued before the first add, so that
+// enough requests are in flight to be bound by HBM bandwidth), add the residual, store bf16.
+template <int ROWS, int MAXW>
+__device__ __forceinline__ void reduce_rows(const __nv_bfloat16* __restrict__ recv, const GemmComm& comm, int rb,
+                                            int c, int N, int ewarp) {
+  for (int rr = ewarp * ROWS; rr < GEMM_BM; rr += 4 * ROWS) {
+    uint4 q[ROWS][MAXW];
+    uint4 rq[ROWS];
+#pragma unroll
+    for (int u = 0; u < ROWS; ++u) {
+      const int lrow = rb * GEMM_BM + rr + u;
+#pragma unroll
+      for (int s_ = 0; s_ < MAXW; ++s_)
+        if (s_ < comm.world)
+          q[u][s_] = __ldcg(reinterpret_cast<const uint4*>(
+              recv + (static_cast<size_t>(s_) * comm.rows_per_rank + lrow) * N + c));
+      if (comm.residual)
+        rq[u] = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(comm.residual) +
+                                                static_cast<size_t>(lrow) * N + c);
+    }
+#pragma unroll
+    for (int u = 0; u < ROWS; ++u) {
+      const int lrow = rb * GEMM_BM + rr + u;
+      float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int s_ = 0; s_ < MAXW; ++s_) {
+        if (s_ < comm.world) {
+          const uint32_t w[4] = {q[u][s_].x, q[u][s_].y, q[u][s_].z, q[u][s_].w};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float2 f = unpack_bf16x2(w[k]);
+            a[2 * k] += f.x;
+            a[2 * k + 1] += f.y;
+          }
+        }
+      }
+      if (comm.residual) {
+        const uint32_t w[4] = {rq[u].x, rq[u].y, rq[u].z, rq[u].w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 f = unpack_bf16x2(w[k]);
+          a[2 * k] += f.x;
+          a[2 * k + 1] += f.y;
+        }
+      }
+      uint4 o;
+      o.x = pack_bf16x2(a[0], a[1]);
+      o.y = pack_bf16x2(a[2], a[3]);
+      o.z = pack_bf16x2(a[4], a[5]);
+      o.w = pack_bf16x2(a[6], a[7]);
+      *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(comm.out) + static_cast<size_t>(lrow) * N + c) = o;
+    }
+  }
+}
+
 template <int BN, bool A_MN, bool B_MN, int COMM>
 __global__ void __launch_bounds__(COMM == 2 ? GEMM_THREADS + 128 : GEMM_THREADS, 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -268,7 +323,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           static_cast<const __nv_bfloat16*>(comm.peer_src[src]) + static_cast<size_t>(rb % bpr) * GEMM_BM * K);
       uint4* to = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(comm.gather) +
                                            static_cast<size_t>(rb) * GEMM_BM * K);
-      for (int v = ct; v < total_vec; v += 128) to[v] = __ldcg(from + v);
+      // sixteen independent 16-byte peer loads in flight per thread: the copy is bound by NVLink
+      // bandwidth, not by one round trip per load
+      for (int v = ct; v < total_vec; v += 128 * 16) {
+        uint4 t[16];
+#pragma unroll
+        for (int u = 0; u < 16; ++u)
+          if (v + u * 128 < total_vec) t[u] = __ldcg(from + v + u * 128);
+#pragma unroll
+        for (int u = 0; u < 16; ++u)
+          if (v + u * 128 < total_vec) to[v + u * 128] = t[u];
+      }
       asm volatile("fence.proxy.async;" ::: "memory");   // generic-proxy writes -> visible to TMA reads
       __threadfence();
       named_barrier(2, 128);
@@ -298,24 +363,49 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (COMM == 1) {
         // ---- reduce-scatter: store the tile into the owner's receive slot for this source rank -------
         const int owner = (m_blk * GEMM_BM) / comm.rows_per_rank;
-        const int lrow = row - owner * comm.rows_per_rank;        // row inside the owner's shard
+        const int lrow0 = m_blk * GEMM_BM - owner * comm.rows_per_rank;   // tile's first row inside the owner's shard
         __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(comm.peer_recv[owner]) +
-                             (static_cast<size_t>(comm.rank) * comm.rows_per_rank + lrow) * N;
+                             (static_cast<size_t>(comm.rank) * comm.rows_per_rank + lrow0) * N;
+        const int r = quarter * 32 + lane;
+        const int et = threadIdx.x - 64;          // 0..127
+        uint8_t* sbuf = slabs;
+        // Each 64-column slab goes registers -> swizzled shared memory -> full 128-byte row segments to
+        // the owner (8 lanes per row), so the NVLink writes are whole lines instead of scattered 16-byte pieces.
 #pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(t_base + c * 32, r);
-          tmem_ld_wait();
-          const int col0 = n0 + c * 32;
-          if (row < M && col0 + 32 <= N) {
+        for (int sl = 0; sl < BN / 64; ++sl) {
+          uint32_t v[64];
+          {
+            uint32_t t[32];
+            tmem_ld_32x32b_x32(t_base + sl * 64, t);
+            tmem_ld_wait();
 #pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              uint4 o;
-              o.x = pack_bf16x2(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
-              o.y = pack_bf16x2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
-              o.z = pack_bf16x2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
-              o.w = pack_bf16x2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
-              *reinterpret_cast<uint4*>(dst + col0 + v * 8) = o;
+            for (int i = 0; i < 32; ++i) v[i] = t[i];
+            tmem_ld_32x32b_x32(t_base + sl * 64 + 32, t);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[32 + i] = t[i];
+          }
+          named_barrier(1, 128);                  // the previous slab has been read out of shared memory
+          uint8_t* rowp = sbuf + r * 128;
+#pragma unroll
+          for (int c8 = 0; c8 < 8; ++c8) {
+            uint4 o;
+            o.x = pack_bf16x2(__uint_as_float(v[c8 * 8 + 0]), __uint_as_float(v[c8 * 8 + 1]));
+            o.y = pack_bf16x2(__uint_as_float(v[c8 * 8 + 2]), __uint_as_float(v[c8 * 8 + 3]));
+            o.z = pack_bf16x2(__uint_as_float(v[c8 * 8 + 4]), __uint_as_float(v[c8 * 8 + 5]));
+            o.w = pack_bf16x2(__uint_as_float(v[c8 * 8 + 6]), __uint_as_float(v[c8 * 8 + 7]));
+            *reinterpret_cast<uint4*>(rowp + ((c8 ^ (r & 7)) << 4)) = o;
+          }
+          named_barrier(1, 128);
+          const int col0 = n0 + sl * 64;
+          const int ch = et & 7;
+          if (col0 + ch * 8 < N) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int rowi = (et >> 3) + 16 * i;
+              const uint4 val = *reinterpret_cast<const uint4*>(sbuf + rowi * 128 + ((ch ^ (rowi & 7)) << 4));
+              if (m_blk * GEMM_BM + rowi < M)
+                *reinterpret_cast<uint4*>(dst + static_cast<size_t>(rowi) * N + col0 + ch * 8) = val;
             }
           }
         }
@@ -506,39 +596,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (et == 0 && ok) ok = wait_flag_ge<true>(cnt + rb * num_n + nb, comm.world * comm.epoch, status, ERR_COMM_FLAG_WAIT);
         if (named_barrier_or(1, 128, !ok)) break;
         const int c = nb * BN + lane * 8;            // 32 lanes x 8 columns = one 256-column row segment
-        for (int rr = ewarp; rr < GEMM_BM; rr += 4) {
-          const int lrow = rb * GEMM_BM + rr;
-          if (c >= N || (BN == 128 && lane >= 16)) continue;
-          float a[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-          for (int s_ = 0; s_ < comm.world; ++s_) {
-            const uint4 q = __ldcg(reinterpret_cast<const uint4*>(
-                recv + (static_cast<size_t>(s_) * comm.rows_per_rank + lrow) * N + c));
-            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              const float2 f = unpack_bf16x2(w[k]);
-              a[2 * k] += f.x;
-              a[2 * k + 1] += f.y;
-            }
-          }
-          if (comm.residual) {
-            const uint4 q = *reinterpret_cast<const uint4*>(
-                static_cast<const __nv_bfloat16*>(comm.residual) + static_cast<size_t>(lrow) * N + c);
-            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              const float2 f = unpack_bf16x2(w[k]);
-              a[2 * k] += f.x;
-              a[2 * k + 1] += f.y;
-            }
-          }
-          uint4 o;
-          o.x = pack_bf16x2(a[0], a[1]);
-          o.y = pack_bf16x2(a[2], a[3]);
-          o.z = pack_bf16x2(a[4], a[5]);
-          o.w = pack_bf16x2(a[6], a[7]);
-          *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(comm.out) + static_cast<size_t>(lrow) * N + c) = o;
-        }
+        if (c >= N || (BN == 128 && lane >= 16)) continue;
+        if (comm.world <= 4)
+          reduce_rows<4, 4>(recv, comm, rb, c, N, ewarp);
+        else
+          reduce_rows<2, 8>(recv, comm, rb, c, N, ewarp);
       }
     }
   }
