@@ -232,6 +232,15 @@ class InferenceEngine:
         for r, n in zip(batch, counts):
             r.num_computed_tokens += n
             self.scheduler.promote_if_prefilled(r)
+        if done and self.prefix_cache is not None:
+            # a finished prefill's full prompt blocks are immutable from here on: publish them right away
+            # so that requests admitted in later steps can share them while this one is still decoding
+            for i in done:
+                r = batch[i]
+                if not getattr(r, "_prefix_published", False):
+                    for bid in self.prefix_cache.insert(r.prompt_tokens, self.kv.get_block_table(r.request_id)):
+                        self.pool.share(bid)
+                    r._prefix_published = True
         if done:
             rows = torch.tensor(done, device=self.device)
             new, lps = self._sample([batch[i] for i in done], logits.index_select(0, rows))
@@ -377,7 +386,8 @@ class InferenceEngine:
         if self.kv is None or r.request_id not in self.kv.tables:
             return
         table = self.kv.get_block_table(r.request_id)
-        if cache_prefix and self.prefix_cache is not None and r.is_prefill_complete:
+        if cache_prefix and self.prefix_cache is not None and r.is_prefill_complete \
+                and not getattr(r, "_prefix_published", False):
             for bid in self.prefix_cache.insert(r.prompt_tokens, table):
                 self.pool.share(bid)            # the cache holds its own reference
         if self.prefix_cache is not None and r.num_cached_tokens:

@@ -75,20 +75,37 @@ class ModelRunner:
     def prepare_decode(self, seq_ids: Sequence, pad_to: int = 0, max_blocks: int = 0) -> InferenceContext:
         """Metadata for one decode step: every sequence's newest token sits at position ``len-1`` (its
         slot must already be allocated with ``append_token``)."""
+        import numpy as np
         bs = self.block_size
         n = len(seq_ids)
         B = max(n, pad_to)
-        tables = [self.mgr.get_block_table(s) for s in seq_ids]
-        lens = [self.mgr.get_seq_token_count(s) for s in seq_ids]
-        width = max(max_blocks, max((len(t) for t in tables), default=1), 1)
-        bt = [t + [-1] * (width - len(t)) for t in tables] + [[-1] * width] * (B - n)
-        segs = [[t[(l - 1) // bs], i, 1, (l - 1) % bs] for i, (t, l) in enumerate(zip(tables, lens))]
-        segs += [[-1, 0, 0, 0]] * (B - n)
+        tables = [self.mgr.tables[s] for s in seq_ids]
+        lens = np.fromiter((t.num_tokens for t in tables), dtype=np.int32, count=n)
+        width = max(max_blocks, max((t.num_blocks for t in tables), default=1), 1)
+        bt = np.full((B, width), -1, dtype=np.int32)
+        for i, t in enumerate(tables):
+            ids = t.get_physical_block_ids()
+            bt[i, :len(ids)] = ids
+        segs = np.zeros((B, 4), dtype=np.int32)
+        segs[:, 0] = -1
+        if n:
+            last = lens - 1
+            segs[:n, 0] = bt[np.arange(n), last // bs]
+            segs[:n, 1] = np.arange(n)
+            segs[:n, 2] = 1
+            segs[:n, 3] = last % bs
+        ctx_lens = np.zeros(B, dtype=np.int32)
+        ctx_lens[:n] = lens
+        pos = np.zeros(B, dtype=np.int32)
+        pos[:n] = lens - 1
+
+        def dev(a):
+            t = torch.from_numpy(a)
+            return t.pin_memory().to(self.device, non_blocking=True) if self.device.type == "cuda" else t
+
         return InferenceContext(
-            is_prefill=False, num_seqs=B, block_tables=self._dev(bt, torch.int32),
-            context_lens=self._dev(lens + [0] * (B - n), torch.int32), max_context_len=max(lens, default=0),
-            store_segments=self._dev(segs, torch.int32),
-            positions=self._dev([l - 1 for l in lens] + [0] * (B - n), torch.int32))
+            is_prefill=False, num_seqs=B, block_tables=dev(bt), context_lens=dev(ctx_lens),
+            max_context_len=int(lens.max()) if n else 0, store_segments=dev(segs), positions=dev(pos))
 
     # ---- forward -----------------------------------------------------------------------------------------
     def _split_plan(self, ctx: InferenceContext) -> Tuple[int, int]:
