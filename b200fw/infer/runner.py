@@ -149,7 +149,7 @@ class ModelRunner:
         if ctx.is_prefill and not all_rows:
             h = h.index_select(0, ctx.last_token_rows)
         h = ops.rmsnorm(h.contiguous(), m.norm.weight, cfg.rms_norm_eps)
-        return ops.linear(h, m.lm_head_weight)
+        return m.logits_from_hidden(h)
 
     # ---- sampling ------------------------------------------------------------------------------------------
     def sample(self, logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor,

@@ -109,6 +109,8 @@ def load_from_hf_checkpoint(model, path: str, strict: bool = False) -> Tuple[int
         t = sd.get("lm_head.weight")
         if t is None:
             t = sd.get("model.embed_tokens.weight")  # tied checkpoints omit lm_head
+        if t is not None and getattr(model, "vocab_parallel", False):
+            t = _rows(t, rank, tp)
         put(model.lm_head, t)
     return loaded, missing
 
@@ -151,7 +153,8 @@ def hf_named_tensors(model, gather_tp: bool = True) -> Iterator[Tuple[str, torch
     if model.norm is not None:
         yield "model.norm.weight", model.norm.weight.detach()
     if model.is_last_stage and not model.tied:
-        yield "lm_head.weight", model.lm_head.detach()
+        w = model.lm_head.detach()
+        yield "lm_head.weight", gather(w, 0) if getattr(model, "vocab_parallel", False) else w
 
 
 def save_hf_checkpoint(model, path: str, write: bool = True, shard_name: str = "model.safetensors") -> None:

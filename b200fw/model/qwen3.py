@@ -198,7 +198,8 @@ class ParallelTransformerModel(nn.Module):
     def __init__(self, cfg: ModelConfig, ctx: Optional[ParallelContext] = None,
                  layer_range: Optional[Tuple[int, int]] = None, is_first_stage: bool = True,
                  is_last_stage: bool = True, sequence_parallel: bool = False,
-                 gradient_checkpointing: bool = False, dtype=None, device=None):
+                 gradient_checkpointing: bool = False, dtype=None, device=None,
+                 vocab_parallel: bool = True):
         super().__init__()
         self.cfg, self.ctx = cfg, ctx
         self.tp_size, self.tp_rank, self.tp_group = _tp(ctx)
@@ -216,11 +217,18 @@ class ParallelTransformerModel(nn.Module):
         self.norm = None
         self.lm_head = None
         self.tied = False
+        # An untied LM head is sharded over the vocabulary across the TP group (each rank computes its
+        # slice of the logits; the losses exchange three floats per token).  A tied head stays
+        # replicated with the embedding, as the reference keeps both (tensor_parallel.py:784-851).
+        self.vocab_parallel = bool(vocab_parallel and is_last_stage and self.tp_size > 1
+                                   and not (cfg.tie_word_embeddings and is_first_stage)
+                                   and cfg.vocab_size % (8 * self.tp_size) == 0)
         if is_last_stage:
             self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, dtype=dtype, device=device)
             self.tied = cfg.tie_word_embeddings and is_first_stage
             if not self.tied:
-                self.lm_head = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device))
+                rows = cfg.vocab_size // self.tp_size if self.vocab_parallel else cfg.vocab_size
+                self.lm_head = nn.Parameter(torch.empty(rows, cfg.hidden_size, dtype=dtype, device=device))
                 nn.init.normal_(self.lm_head, std=cfg.init_std)
         self._tag_parameters()
 
@@ -239,8 +247,9 @@ class ParallelTransformerModel(nn.Module):
             p.tp_partial_grad = self.tp_size > 1 and (
                 "q_norm" in name or "k_norm" in name or
                 (self.sequence_parallel and ("layernorm" in name or name == "norm.weight")))
-            p.tp_sharded = ("qkv_proj" in name or "gate_up_proj" in name or "o_proj" in name or "down_proj" in name) \
-                and self.tp_size > 1
+            p.tp_sharded = self.tp_size > 1 and (
+                "qkv_proj" in name or "gate_up_proj" in name or "o_proj" in name or "down_proj" in name
+                or (name == "lm_head" and self.vocab_parallel))
         if self.tied and self.embed_tokens is not None:
             self.embed_tokens.grad_contribs = 2  # LM head (in the loss) and embedding both write its gradient
 
@@ -267,7 +276,8 @@ class ParallelTransformerModel(nn.Module):
         p0 = next(self.parameters())
         other = ParallelTransformerModel(self.cfg, self.ctx, (self.layer_start, self.layer_end),
                                          self.is_first_stage, self.is_last_stage, self.sequence_parallel,
-                                         self.gradient_checkpointing, dtype=p0.dtype, device=p0.device)
+                                         self.gradient_checkpointing, dtype=p0.dtype, device=p0.device,
+                                         vocab_parallel=self.vocab_parallel)
         with torch.no_grad():
             for a, b in zip(other.parameters(), self.parameters()):
                 a.copy_(b)
@@ -299,11 +309,27 @@ class ParallelTransformerModel(nn.Module):
         return h
 
     def final_hidden(self, h: torch.Tensor) -> torch.Tensor:
-        """Final norm; under sequence parallelism the result is gathered to all tokens."""
+        """Final norm; under sequence parallelism the result is gathered to all tokens.  With a
+        vocabulary-sharded head every rank's hidden-state gradient is a partial sum, so the gather's
+        backward is a reduce-scatter; with a replicated head it is a plain slice."""
         h = self.norm(h)
         if self.sequence_parallel:
-            h = comm.gather_sequence_replicated(h, self.tp_group)
+            h = (comm.gather_sequence if self.vocab_parallel else comm.gather_sequence_replicated)(h, self.tp_group)
         return h
+
+    def vocab_shard(self) -> Optional[ops.VocabShard]:
+        if not self.vocab_parallel:
+            return None
+        return ops.VocabShard(self.tp_group, self.tp_rank, self.tp_size, self.cfg.vocab_size,
+                              reduce_dh=not self.sequence_parallel)
+
+    def logits_from_hidden(self, h: torch.Tensor) -> torch.Tensor:
+        """``[M,H]`` final hidden states -> ``[M,V]`` logits (all-gathered over the vocabulary shards)."""
+        if not self.vocab_parallel:
+            return ops.linear(h, self.lm_head_weight)
+        if not self.sequence_parallel:
+            h = comm.copy_to_parallel_region(h, self.tp_group)
+        return comm.gather_from_parallel_region(ops.linear(h, self.lm_head), self.tp_group)
 
     # ---- public entry points ---------------------------------------------------------------------
     def forward_hidden(self, input_or_hidden: torch.Tensor, B: int, S: int, positions=None) -> torch.Tensor:
@@ -326,8 +352,7 @@ class ParallelTransformerModel(nn.Module):
         h = self.forward_hidden(input_ids, B, S, positions)
         if not self.is_last_stage:
             return h
-        logits = ops.linear(h, self.lm_head_weight)
-        return logits.reshape(B, S, -1)
+        return self.logits_from_hidden(h).reshape(B, S, -1)
 
     def loss(self, input_ids: torch.Tensor, labels: torch.Tensor, loss_scale: float = 1.0,
              hidden: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -338,7 +363,8 @@ class ParallelTransformerModel(nn.Module):
         h = hidden if hidden is not None else self.forward_hidden(input_ids, B, S)
         shifted = torch.full_like(labels, -100)
         shifted[:, :-1] = labels[:, 1:]
-        return ops.lm_head_cross_entropy(h, self.lm_head_weight, shifted.reshape(-1), loss_scale=loss_scale)
+        return ops.lm_head_cross_entropy(h, self.lm_head_weight, shifted.reshape(-1), loss_scale=loss_scale,
+                                         shard=self.vocab_shard())
 
     def token_logprobs(self, input_ids: torch.Tensor, temperature: float = 1.0,
                        hidden: Optional[torch.Tensor] = None,
@@ -350,5 +376,5 @@ class ParallelTransformerModel(nn.Module):
         src = input_ids if labels is None else labels
         tgt = torch.full_like(input_ids, -100)
         tgt[:, :-1] = src[:, 1:]
-        lp = ops.lm_head_logprob(h, self.lm_head_weight, tgt.reshape(-1), temperature)
+        lp = ops.lm_head_logprob(h, self.lm_head_weight, tgt.reshape(-1), temperature, shard=self.vocab_shard())
         return lp.reshape(B, S)[:, :-1]

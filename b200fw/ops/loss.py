@@ -23,48 +23,91 @@ IGNORE = -100
 DEFAULT_CHUNK = 4096
 
 
-def _rows(logits, labels, mode, scale=None, loss_sum=None, lse=None, logp=None, g=None, inv_t=1.0):
+def _rows(logits, labels, mode, scale=None, loss_sum=None, lse=None, logp=None, g=None, inv_t=1.0,
+          vocab_start=0, vocab_total=0, stats=None):
     rows, V = logits.shape
     nv.check(nv.lib().b2_vocab_rows(nv.ptr(logits), nv.ptr(labels), rows, V, logits.stride(0), mode,
                                     nv.ptr(scale), nv.ptr(loss_sum), nv.ptr(lse), nv.ptr(logp), nv.ptr(g),
-                                    nv.ctypes.c_longlong(IGNORE), nv.ctypes.c_float(inv_t), nv.stream_ptr()),
+                                    nv.ctypes.c_longlong(IGNORE), nv.ctypes.c_float(inv_t),
+                                    nv.ctypes.c_longlong(vocab_start), nv.ctypes.c_longlong(vocab_total),
+                                    nv.ptr(stats), nv.stream_ptr()),
              "vocab_rows")
     nv.count_launch()
 
 
+class VocabShard:
+    """Which slice of the vocabulary a tensor-parallel rank's LM-head rows cover, and the group to
+    combine the per-row softmax statistics over.  ``reduce_dh``: sum the hidden-state gradient over
+    the group inside the loss (set it to False when the producer of ``h`` reduce-scatters the
+    gradient itself, as the sequence-parallel gather does)."""
+
+    def __init__(self, group, rank: int, world: int, vocab_total: int, reduce_dh: bool = True):
+        self.group, self.rank, self.world, self.total = group, rank, world, vocab_total
+        if vocab_total % world:
+            raise ValueError(f"vocab {vocab_total} is not divisible by the tensor-parallel size {world}")
+        self.local = vocab_total // world
+        self.start = rank * self.local
+        self.reduce_dh = reduce_dh
+
+
+def _combine_shard_stats(stats: torch.Tensor, shard: VocabShard):
+    """``[rows,3]`` local (max, sumexp, label logit) -> global (lse, label_logit), one all-gather."""
+    import torch.distributed as dist
+    allst = torch.empty((shard.world,) + tuple(stats.shape), device=stats.device, dtype=stats.dtype)
+    dist.all_gather_into_tensor(allst, stats, group=shard.group)
+    m = allst[..., 0]
+    gm = m.max(dim=0).values
+    ssum = (allst[..., 1] * torch.exp(m - gm)).sum(dim=0)
+    return gm + torch.log(ssum), allst[..., 2].sum(dim=0)
+
+
+def _dw_step(ctx_holder, w, logits, hs):
+    """dW (+)= logits^T hs, written into ``w.main_grad`` when the optimizer provides one."""
+    if ctx_holder["first"]:
+        ctx_holder["dw"] = grad_into_main(w, lambda out, acc: gemm(logits, hs, a_mn=True, b_mn=True,
+                                                                     out=out, accumulate=acc))
+        ctx_holder["first"] = False
+    else:
+        tgt = getattr(w, "main_grad", None)
+        gemm(logits, hs, a_mn=True, b_mn=True, out=tgt if tgt is not None else ctx_holder["dw"],
+             accumulate=True)
+
+
 class _LMHeadCE(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, h, w, labels, loss_scale, chunk, n_valid):
+    def forward(ctx, h, w, labels, loss_scale, chunk, n_valid, shard):
         M, H = h.shape
-        V = w.shape[0]
         need_grad = h.requires_grad or w.requires_grad
         n_valid_f = n_valid.to(torch.float32).clamp_(min=1.0)
         scale = (loss_scale / n_valid_f).reshape(1).contiguous()
         loss_sum = torch.zeros(1, device=h.device, dtype=torch.float32)
         dh = torch.empty_like(h) if need_grad else None
-        first = True
+        holder = {"dw": None, "first": True}
         for s in range(0, M, chunk):
             e = min(M, s + chunk)
             logits = gemm(h[s:e], w)
-            _rows(logits, labels[s:e], 0, scale=scale, loss_sum=loss_sum)
+            if shard is None:
+                _rows(logits, labels[s:e], 0, scale=scale, loss_sum=loss_sum)
+            else:
+                st = torch.empty(e - s, 3, device=h.device, dtype=torch.float32)
+                _rows(logits, labels[s:e], 3, stats=st, vocab_start=shard.start, vocab_total=shard.total)
+                lse, label_logit = _combine_shard_stats(st, shard)
+                ok = (labels[s:e] != IGNORE) & (labels[s:e] >= 0) & (labels[s:e] < shard.total)
+                loss_sum += torch.where(ok, lse - label_logit, torch.zeros_like(lse)).sum()
+                if need_grad:
+                    _rows(logits, labels[s:e], 4, scale=scale, lse=lse.contiguous(),
+                          vocab_start=shard.start, vocab_total=shard.total)
             if not need_grad:
                 continue  # logits hold gradients nobody wants; only loss_sum matters
             gemm(logits, w, b_mn=True, out=dh[s:e])
             if w.requires_grad:
-                hs = h[s:e]
-                if first:
-                    ctx.dw = grad_into_main(w, lambda out, acc: gemm(logits, hs, a_mn=True, b_mn=True,
-                                                                      out=out, accumulate=acc))
-                    first = False
-                else:
-                    tgt = getattr(w, "main_grad", None)
-                    gemm(logits, hs, a_mn=True, b_mn=True, out=tgt if tgt is not None else ctx.dw,
-                         accumulate=True)
+                _dw_step(holder, w, logits, h[s:e])
             del logits
+        if shard is not None and shard.reduce_dh and dh is not None:
+            import torch.distributed as dist
+            dist.all_reduce(dh, group=shard.group)
         ctx.dh = dh
-        ctx.w_needs = w.requires_grad
-        if not hasattr(ctx, "dw"):
-            ctx.dw = None
+        ctx.dw = holder["dw"]
         return (loss_sum / n_valid_f).squeeze(0)
 
     @staticmethod
@@ -77,26 +120,53 @@ class _LMHeadCE(torch.autograd.Function):
             dh = dh * gout.to(dh.dtype)
         if dw is not None:
             dw = dw * gout.to(dw.dtype)
-        return dh, dw, None, None, None, None
+        return dh, dw, None, None, None, None, None
+
+
+def _sharded_logprob_torch(h, w, labels, inv_t, shard: VocabShard):
+    """Plain-PyTorch (autograd) form of the vocabulary-sharded log-softmax pick: returns per-row
+    ``(logp, lse, label_logit)``; used on CPU and as the oracle of the CUDA path."""
+    from ..dist import comm
+    if shard.reduce_dh:
+        h = comm.copy_to_parallel_region(h, shard.group)
+    logits = torch.nn.functional.linear(h, w.to(h.dtype)).float() * inv_t
+    gm = comm.all_reduce(logits.detach().max(dim=-1).values, shard.group, op=torch.distributed.ReduceOp.MAX)
+    ssum = comm.reduce_from_parallel_region(torch.exp(logits - gm[:, None]).sum(-1), shard.group)
+    lse = gm + torch.log(ssum)
+    local = labels - shard.start
+    mine = (labels != IGNORE) & (local >= 0) & (local < shard.local)
+    picked = logits.gather(-1, local.clamp(0, shard.local - 1)[:, None]).squeeze(-1)
+    label_logit = comm.reduce_from_parallel_region(torch.where(mine, picked, torch.zeros_like(picked)), shard.group)
+    ok = (labels != IGNORE) & (labels >= 0) & (labels < shard.total)
+    return torch.where(ok, label_logit - lse, torch.zeros_like(lse)), ok
 
 
 def lm_head_cross_entropy(h: torch.Tensor, w: torch.Tensor, labels: torch.Tensor, loss_scale: float = 1.0,
-                          chunk: int = DEFAULT_CHUNK, n_valid: Optional[torch.Tensor] = None) -> torch.Tensor:
+                          chunk: int = DEFAULT_CHUNK, n_valid: Optional[torch.Tensor] = None,
+                          shard: Optional[VocabShard] = None) -> torch.Tensor:
     """Mean CE of ``h @ w^T`` against ``labels`` (``-100`` ignored) without materialising the logits.
 
     The returned loss is the unscaled mean; the gradients carry ``loss_scale`` (use it for
     ``1/grad_accum`` and call ``backward()`` on the returned value directly — scaling the loss again
     would scale the gradients twice).  ``n_valid`` overrides the normaliser (e.g. a global count).
+    With ``shard`` the rows of ``w`` are this rank's slice of the vocabulary: every rank computes its
+    slice of the logits and the ranks exchange three floats per token (max, sum-exp, label logit).
+    The reference keeps the LM head replicated on every TP rank (src/distributed/tensor_parallel.py:845).
     """
     labels = labels.reshape(-1)
     if n_valid is None:
         n_valid = (labels != IGNORE).sum()
     if not h.is_cuda:
+        if shard is not None:
+            lp, ok = _sharded_logprob_torch(h, w, labels, 1.0, shard)
+            loss = -(lp.sum()) / n_valid.clamp(min=1).float()
+            return _ScaleGrad.apply(loss, loss_scale)
         logits = torch.nn.functional.linear(h, w.to(h.dtype)).float()
         tot = torch.nn.functional.cross_entropy(logits, labels, ignore_index=IGNORE, reduction="sum")
         loss = tot / n_valid.clamp(min=1).float()
         return _ScaleGrad.apply(loss, loss_scale)
-    return _LMHeadCE.apply(h.contiguous(), w, labels.long().contiguous(), float(loss_scale), int(chunk), n_valid)
+    return _LMHeadCE.apply(h.contiguous(), w, labels.long().contiguous(), float(loss_scale), int(chunk),
+                           n_valid, shard)
 
 
 class _ScaleGrad(torch.autograd.Function):
@@ -114,57 +184,66 @@ class _ScaleGrad(torch.autograd.Function):
 
 class _LMHeadLogprob(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, h, w, labels, inv_t, chunk):
+    def forward(ctx, h, w, labels, inv_t, chunk, shard):
         M = h.shape[0]
         lse = torch.empty(M, device=h.device, dtype=torch.float32)
         logp = torch.empty(M, device=h.device, dtype=torch.float32)
         for s in range(0, M, chunk):
             e = min(M, s + chunk)
             logits = gemm(h[s:e], w)
-            _rows(logits, labels[s:e], 1, lse=lse[s:e], logp=logp[s:e], inv_t=inv_t)
+            if shard is None:
+                _rows(logits, labels[s:e], 1, lse=lse[s:e], logp=logp[s:e], inv_t=inv_t)
+            else:
+                st = torch.empty(e - s, 3, device=h.device, dtype=torch.float32)
+                _rows(logits, labels[s:e], 3, stats=st, inv_t=inv_t, vocab_start=shard.start,
+                      vocab_total=shard.total)
+                l, label_logit = _combine_shard_stats(st, shard)
+                ok = (labels[s:e] != IGNORE) & (labels[s:e] >= 0) & (labels[s:e] < shard.total)
+                lse[s:e] = l
+                logp[s:e] = torch.where(ok, label_logit - l, torch.zeros_like(l))
             del logits
         ctx.save_for_backward(h, w, labels, lse)
-        ctx.args = (inv_t, chunk)
+        ctx.args = (inv_t, chunk, shard)
         return logp
 
     @staticmethod
     def backward(ctx, g):
         h, w, labels, lse = ctx.saved_tensors
-        inv_t, chunk = ctx.args
+        inv_t, chunk, shard = ctx.args
         M = h.shape[0]
         g = g.contiguous().float()
         dh = torch.empty_like(h)
         dw_holder = {"dw": None, "first": True}
+        vs, vt = (0, 0) if shard is None else (shard.start, shard.total)
         for s in range(0, M, chunk):
             e = min(M, s + chunk)
             logits = gemm(h[s:e], w)
-            _rows(logits, labels[s:e], 2, lse=lse[s:e], g=g[s:e], inv_t=inv_t)
+            _rows(logits, labels[s:e], 2, lse=lse[s:e], g=g[s:e], inv_t=inv_t, vocab_start=vs, vocab_total=vt)
             gemm(logits, w, b_mn=True, out=dh[s:e])
             if w.requires_grad:
-                hs = h[s:e]
-                if dw_holder["first"]:
-                    dw_holder["dw"] = grad_into_main(
-                        w, lambda out, acc: gemm(logits, hs, a_mn=True, b_mn=True, out=out, accumulate=acc))
-                    dw_holder["first"] = False
-                else:
-                    tgt = getattr(w, "main_grad", None)
-                    gemm(logits, hs, a_mn=True, b_mn=True, out=tgt if tgt is not None else dw_holder["dw"],
-                         accumulate=True)
+                _dw_step(dw_holder, w, logits, h[s:e])
             del logits
-        return dh, dw_holder["dw"], None, None, None
+        if shard is not None and shard.reduce_dh:
+            import torch.distributed as dist
+            dist.all_reduce(dh, group=shard.group)
+        return dh, dw_holder["dw"], None, None, None, None
 
 
 def lm_head_logprob(h: torch.Tensor, w: torch.Tensor, labels: torch.Tensor, temperature: float = 1.0,
-                    chunk: int = DEFAULT_CHUNK) -> torch.Tensor:
-    """``log softmax(h @ w^T / temperature)[label]`` per row as fp32 ``[M]`` (0 where label is -100)."""
+                    chunk: int = DEFAULT_CHUNK, shard: Optional[VocabShard] = None) -> torch.Tensor:
+    """``log softmax(h @ w^T / temperature)[label]`` per row as fp32 ``[M]`` (0 where label is -100).
+    ``shard``: ``w`` holds this rank's slice of the vocabulary (see :func:`lm_head_cross_entropy`)."""
     labels = labels.reshape(-1)
+    if not h.is_cuda and shard is not None:
+        return _sharded_logprob_torch(h, w, labels, 1.0 / temperature, shard)[0]
     if not h.is_cuda:
         logits = torch.nn.functional.linear(h, w.to(h.dtype)).float() / temperature
         lp = torch.log_softmax(logits, dim=-1)
         safe = labels.clamp(min=0)
         out = lp.gather(-1, safe[:, None]).squeeze(-1)
         return torch.where(labels == IGNORE, torch.zeros_like(out), out)
-    return _LMHeadLogprob.apply(h.contiguous(), w, labels.long().contiguous(), 1.0 / temperature, int(chunk))
+    return _LMHeadLogprob.apply(h.contiguous(), w, labels.long().contiguous(), 1.0 / temperature, int(chunk),
+                                shard)
 
 
 def _grpo_ref(lp, old_lp, ref_lp, mask, adv, clip_eps, beta):

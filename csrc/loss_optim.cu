@@ -44,20 +44,27 @@ __device__ __forceinline__ MaxSum block_maxsum(MaxSum v, MaxSum* scratch) {
 //         coef = *scale for rows whose label != ignore (else 0); loss_sum += (lse - logit[label]).
 // mode 1: log-prob forward only: lse_out[row], logp_out[row] (0 for ignored rows).
 // mode 2: log-prob backward in place: dlogits = g[row] * (onehot - softmax), using lse_in[row].
+// mode 3: vocabulary-sharded pass 1: stats_out[row] = {max, sum exp(x - max), label logit or 0} of
+//         this shard's columns [vocab_start, vocab_start + V) of a vocab_total-wide row.
+// mode 4: vocabulary-sharded CE backward in place with the row's global lse given in lse_io.
+// Modes 2 and 4 accept a shard (labels are global ids; the one-hot lands only in its owner).
 // logits: [rows, ld] bf16, V valid columns (V % 8 == 0).  labels int64.
 __global__ void __launch_bounds__(ROW_THREADS) vocab_rows_kernel(
     __nv_bfloat16* __restrict__ logits, const long long* __restrict__ labels, int V, int ld, int mode,
     const float* __restrict__ scale, float* __restrict__ loss_sum, float* __restrict__ lse_io,
     float* __restrict__ logp_out, const float* __restrict__ g_in, long long ignore_index,
-    float inv_temperature) {
+    float inv_temperature, long long vocab_start, long long vocab_total, float* __restrict__ stats_out) {
   __shared__ MaxSum scratch[32];
   const size_t row = blockIdx.x;
   __nv_bfloat16* lr = logits + row * ld;
-  const long long label = labels[row];
-  const bool valid = label != ignore_index && label >= 0 && label < V;
+  // labels index the whole vocabulary; this launch sees columns [vocab_start, vocab_start + V) of it
+  const long long label_global = labels[row];
+  const bool valid = label_global != ignore_index && label_global >= 0 && label_global < vocab_total;
+  const long long label = label_global - vocab_start;
+  const bool in_shard = valid && label >= 0 && label < V;
   const int nvec = V / 8;
   float lse;
-  if (mode != 2) {
+  if (mode == 0 || mode == 1 || mode == 3) {
     MaxSum ms{-INFINITY, 0.f};
     for (int c = threadIdx.x; c < nvec; c += ROW_THREADS) {
       uint4 q = *reinterpret_cast<const uint4*>(lr + c * 8);
@@ -80,11 +87,21 @@ __global__ void __launch_bounds__(ROW_THREADS) vocab_rows_kernel(
       ms.s = s;
     }
     ms = block_maxsum(ms, scratch);
+    if (mode == 3) {
+      // vocabulary-sharded pass 1: this shard's (max, sum exp(x - max), label logit or 0); the caller
+      // combines the shards' triples into the row's log-sum-exp.
+      if (threadIdx.x == 0) {
+        stats_out[row * 3 + 0] = ms.m;
+        stats_out[row * 3 + 1] = ms.s;
+        stats_out[row * 3 + 2] = in_shard ? __bfloat162float(lr[label]) * inv_temperature : 0.f;
+      }
+      return;
+    }
     lse = ms.m + __logf(ms.s);
   } else {
     lse = lse_io[row];
   }
-  const float label_logit = valid ? __bfloat162float(lr[label]) * inv_temperature : 0.f;
+  const float label_logit = in_shard ? __bfloat162float(lr[label]) * inv_temperature : 0.f;
   if (mode == 1) {
     if (threadIdx.x == 0) {
       lse_io[row] = lse;
@@ -96,6 +113,8 @@ __global__ void __launch_bounds__(ROW_THREADS) vocab_rows_kernel(
   if (mode == 0) {
     coef = valid ? *scale : 0.f;
     if (threadIdx.x == 0 && valid) atomicAdd(loss_sum, lse - label_logit);
+  } else if (mode == 4) {
+    coef = valid ? *scale : 0.f;  // sharded CE: the loss itself was summed by the caller
   } else {
     coef = valid ? -g_in[row] : 0.f;  // dlogits = g*(onehot - softmax) = (-g)*(softmax - onehot)
   }
@@ -111,7 +130,7 @@ __global__ void __launch_bounds__(ROW_THREADS) vocab_rows_kernel(
       f[2 * j] = coef * __expf(t.x * inv_temperature - lse);
       f[2 * j + 1] = coef * __expf(t.y * inv_temperature - lse);
     }
-    if (valid && label >= c * 8 && label < c * 8 + 8) f[label - c * 8] -= coef;
+    if (in_shard && label >= c * 8 && label < c * 8 + 8) f[label - c * 8] -= coef;
     uint4 o;
     o.x = pack_bf16x2(f[0], f[1]);
     o.y = pack_bf16x2(f[2], f[3]);
@@ -301,13 +320,19 @@ static int grid_for(long long n, int threads) {
 
 B2_EXPORT int b2_vocab_rows(void* logits, const long long* labels, int rows, int V, int ld, int mode,
                             const float* scale, float* loss_sum, float* lse, float* logp,
-                            const float* g, long long ignore_index, float inv_temperature, void* stream) {
+                            const float* g, long long ignore_index, float inv_temperature,
+                            long long vocab_start, long long vocab_total, float* stats, void* stream) {
   b2::ensure_thread_context();
   if (V % 8 || ld % 8) { set_error("vocab_rows: V and ld must be multiples of 8"); return 10; }
+  if (mode < 0 || mode > 4 || (mode == 3 && !stats) || ((mode == 2 || mode == 4) && !lse)) {
+    set_error("vocab_rows: bad mode or missing buffer");
+    return 11;
+  }
   if (rows <= 0) return 0;
+  if (vocab_total <= 0) vocab_total = V;
   vocab_rows_kernel<<<rows, ROW_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<__nv_bfloat16*>(logits), labels, V, ld, mode, scale, loss_sum, lse, logp, g,
-      ignore_index, inv_temperature);
+      ignore_index, inv_temperature, vocab_start, vocab_total, stats);
   B2_LAUNCH_CHECK("vocab_rows");
   return 0;
 }

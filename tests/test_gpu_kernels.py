@@ -193,6 +193,44 @@ def test_lm_head_ce_and_logprob():
     assert relerr(h.grad, hf.grad) < 3e-2 and relerr(w.grad, wf.grad) < 3e-2
 
 
+def test_vocab_rows_sharded_modes_match_full_softmax():
+    """Two vocabulary shards handled as two launches on column halves of one logits matrix: the
+    combined statistics give the full log-sum-exp and the in-place gradients equal
+    (softmax - onehot) * scale of the full row."""
+    from b200fw import _native as nv
+    from b200fw.ops.loss import _rows
+    torch.manual_seed(5)
+    rows, V = 96, 1024
+    logits = (torch.randn(rows, V, device="cuda") * 3).bfloat16()
+    labels = torch.randint(0, V, (rows,), device="cuda")
+    labels[::7] = -100
+    ref = logits.float()
+    lse_ref = torch.logsumexp(ref, -1)
+    half = V // 2
+    stats = []
+    for r in range(2):
+        st = torch.empty(rows, 3, device="cuda")
+        _rows(logits[:, r * half:(r + 1) * half], labels, 3, stats=st, vocab_start=r * half, vocab_total=V)
+        stats.append(st)
+    allst = torch.stack(stats)
+    gm = allst[..., 0].max(0).values
+    lse = gm + torch.log((allst[..., 1] * torch.exp(allst[..., 0] - gm)).sum(0))
+    assert (lse - lse_ref).abs().max() < 1e-3
+    ok = labels >= 0
+    picked = ref.gather(-1, labels.clamp(min=0)[:, None]).squeeze(-1)
+    assert (allst[..., 2].sum(0)[ok] - picked[ok]).abs().max() < 1e-6
+    scale = torch.tensor([0.25], device="cuda")
+    work = logits.clone()
+    for r in range(2):
+        _rows(work[:, r * half:(r + 1) * half], labels, 4, scale=scale, lse=lse.contiguous(),
+              vocab_start=r * half, vocab_total=V)
+    want = torch.softmax(ref, -1)
+    want[ok, labels[ok]] -= 1.0
+    want = want * 0.25 * ok[:, None]
+    assert (work.float() - want).abs().max() < 2e-3
+    assert nv.read_status() == 0
+
+
 def test_grpo_loss():
     from b200fw.ops import grpo_token_loss
     from b200fw.ops.loss import _grpo_ref

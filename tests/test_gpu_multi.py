@@ -167,6 +167,51 @@ def test_fused_tp_gemm_kernels_match_reference():
             assert e1 < 2e-2 and e2 < 2e-2 and e3 == 0.0, (e1, e2, e3)
 
 
+def _vocab_parallel_worker(rank, world):
+    import torch.distributed as dist
+    from b200fw.ops import VocabShard, lm_head_cross_entropy, lm_head_logprob
+    torch.manual_seed(11)
+    M, H, V = 384, 256, 4096
+    h0 = (torch.randn(M, H, device="cuda") * 0.5).bfloat16()
+    w0 = (torch.randn(V, H, device="cuda") * 0.05).bfloat16()
+    labels = torch.randint(0, V, (M,), device="cuda")
+    labels[::5] = -100
+    vl = V // world
+    out = []
+    for fn in ("ce", "logp"):
+        h = h0.clone().requires_grad_(True)
+        w = w0.clone().requires_grad_(True)
+        hs = h0.clone().requires_grad_(True)
+        ws = w0[rank * vl:(rank + 1) * vl].clone().requires_grad_(True)
+        shard = VocabShard(dist.group.WORLD, rank, world, V)
+        if fn == "ce":
+            a = lm_head_cross_entropy(h, w, labels, chunk=128)
+            b = lm_head_cross_entropy(hs, ws, labels, chunk=128, shard=shard)
+            a.backward()
+            b.backward()
+            e0 = (a - b).abs().item()
+        else:
+            a = lm_head_logprob(h, w, labels, temperature=0.9, chunk=128)
+            b = lm_head_logprob(hs, ws, labels, temperature=0.9, chunk=128, shard=shard)
+            gsel = torch.randn(M, device="cuda")
+            (a * gsel).sum().backward()
+            (b * gsel).sum().backward()
+            e0 = (a - b).abs().max().item()
+        e1 = ((h.grad.float() - hs.grad.float()).abs().max() / h.grad.float().abs().max()).item()
+        e2 = ((w.grad.float()[rank * vl:(rank + 1) * vl] - ws.grad.float()).abs().max()
+              / w.grad.float().abs().max()).item()
+        out.append((e0, e1, e2))
+    return out
+
+
+@needs2
+def test_vocab_parallel_lm_head_matches_replicated():
+    from _gpu_dist_util import run_gpu_ranks
+    for res in run_gpu_ranks(_vocab_parallel_worker, 2):
+        for e0, e1, e2 in res:
+            assert e0 < 5e-3 and e1 < 3e-2 and e2 < 3e-2, res
+
+
 def _tp_train_worker(rank, world, fused):
     from b200fw.model import ModelConfig
     from b200fw.train import TrainConfig, TrainEngine

@@ -67,6 +67,12 @@ def _tp_worker(rank, world, path, seq_par):
         assert not ln.tp_partial_grad
         assert (ln.grad - ref.layers[0].input_layernorm.weight.grad).abs().max() < 1e-5
     assert (m.embed_tokens.grad - ref.embed_tokens.grad).abs().max() < 1e-5
+    # the untied LM head is sharded over the vocabulary; its grad is the matching row slice
+    assert m.vocab_parallel and m.lm_head.shape[0] == CFG.vocab_size // world and m.lm_head.tp_sharded
+    vl = CFG.vocab_size // world
+    assert (m.lm_head.grad - ref.lm_head.grad[rank * vl:(rank + 1) * vl]).abs().max() < 1e-5
+    lp, lpr = m.token_logprobs(ids, temperature=0.7), ref.token_logprobs(ids, temperature=0.7)
+    assert (lp - lpr).abs().max() < 1e-4
     # gathered export equals the original full tensors
     from b200fw.model.hf_io import hf_named_tensors
     full = dict(hf_named_tensors(m))
