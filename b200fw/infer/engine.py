@@ -41,6 +41,7 @@ class InferenceEngine:
         self.kv: Optional[KVCacheManager] = None
         self.runner: Optional[ModelRunner] = None
         self.prefix_cache = None
+        self._inflight_prefix: Dict[tuple, str] = {}
         self.graph_runner: Optional[CUDAGraphRunner] = None
         self.spec: Optional[SpeculativeDecoder] = None
         self.requests: Dict[str, Request] = {}
@@ -87,6 +88,8 @@ class InferenceEngine:
             self.prefix_cache = RadixAttentionCache(cfg.block_size, cfg.radix_cache_max_nodes) if cfg.use_radix_cache \
                 else PrefixCache(cfg.block_size, cfg.max_cached_blocks)
             self.prefix_cache.on_evict = lambda bid: self.pool.free(self.pool.get_block(bid))
+            if cfg.enable_prefix_reuse:
+                self.scheduler.defer = self._defer_for_shared_prefix
         if cfg.enable_cuda_graph and self.device.type == "cuda":
             self.graph_runner = CUDAGraphRunner(cfg.max_num_sequences)
         if cfg.speculative_enabled:
@@ -176,6 +179,23 @@ class InferenceEngine:
         return produced
 
     # ---- prefill --------------------------------------------------------------------------------------------
+    def _first_block_key(self, r: Request):
+        bs = self.config.block_size
+        return tuple(r.prompt_tokens[:bs]) if r.num_prompt_tokens > bs else None
+
+    def _defer_for_shared_prefix(self, r: Request) -> bool:
+        """True while another request that starts with the same block is still prefilling: once that
+        one publishes its prompt blocks, this one shares them instead of recomputing them (requests of
+        one GRPO group arrive together with identical prompts)."""
+        key = self._first_block_key(r)
+        if key is None:
+            return False
+        owner = self._inflight_prefix.get(key)
+        if owner is None or owner not in self.requests:
+            self._inflight_prefix[key] = r.request_id      # this request computes the prefix for the others
+            return False
+        return owner != r.request_id
+
     def _admit(self, r: Request) -> bool:
         """First chunk of a request: allocate its block table, sharing cached prefix blocks."""
         shared: List[int] = []
@@ -241,6 +261,7 @@ class InferenceEngine:
                     for bid in self.prefix_cache.insert(r.prompt_tokens, self.kv.get_block_table(r.request_id)):
                         self.pool.share(bid)
                     r._prefix_published = True
+                    self._drop_inflight(r)
         if done:
             rows = torch.tensor(done, device=self.device)
             new, lps = self._sample([batch[i] for i in done], logits.index_select(0, rows))
@@ -382,7 +403,13 @@ class InferenceEngine:
         return t
 
     # ---- lifecycle ------------------------------------------------------------------------------------------------
+    def _drop_inflight(self, r: Request):
+        key = self._first_block_key(r)
+        if key is not None and self._inflight_prefix.get(key) == r.request_id:
+            del self._inflight_prefix[key]
+
     def _release(self, r: Request, cache_prefix: bool = True):
+        self._drop_inflight(r)
         if self.kv is None or r.request_id not in self.kv.tables:
             return
         table = self.kv.get_block_table(r.request_id)
@@ -416,6 +443,7 @@ class InferenceEngine:
             self.requests.pop(r.request_id, None)
         if self.prefix_cache is not None:
             self.prefix_cache.invalidate_all()
+            self._inflight_prefix.clear()
         if self.kv is not None:
             self.kv.reset()
         if self.graph_runner is not None:
@@ -498,6 +526,7 @@ class InferenceEngine:
                 self.requests.pop(r.request_id, None)
         if self.prefix_cache is not None:
             self.prefix_cache.invalidate_all()
+            self._inflight_prefix.clear()
 
     def get_stats(self) -> dict:
         s = dict(self.stats)

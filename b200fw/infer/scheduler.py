@@ -102,6 +102,10 @@ class ContinuousBatchingScheduler:
         self.waiting_queue: List[Request] = []
         self.running_queue: List[Request] = []
         self.total_scheduled = self.total_preempted = self.total_finished = 0
+        # Optional hook ``defer(request) -> bool``: a not-yet-started request for which it returns True
+        # is skipped this step (the engine uses it to hold back requests whose prompt prefix is being
+        # prefilled by another request right now, so that they can share its blocks one step later).
+        self.defer = None
 
     def add_request(self, request: Request):
         request.state = RequestState.WAITING
@@ -150,6 +154,8 @@ class ContinuousBatchingScheduler:
             for i, r in enumerate(self.waiting_queue):
                 if len(out.prefill_requests) >= slots:
                     break
+                if self.defer is not None and r.num_computed_tokens == 0 and self.defer(r):
+                    continue
                 want = r.remaining_prefill_tokens
                 if self.enable_chunked_prefill:
                     want = min(want, chunk)

@@ -56,6 +56,35 @@ def verify_sampling(draft_tokens: torch.Tensor, draft_probs: torch.Tensor, targe
     return K, int(torch.multinomial(pt[K], 1, generator=generator))
 
 
+def verify_greedy_batch(draft_tokens: torch.Tensor, target_logits: torch.Tensor):
+    """Batched :func:`verify_greedy`: ``draft_tokens [B,K]``, ``target_logits [B,K+1,V]`` ->
+    ``(accepted [B], next_token [B])`` as device tensors (no host sync)."""
+    pred = target_logits.argmax(-1)
+    K = draft_tokens.shape[1]
+    n = (pred[:, :K] == draft_tokens).long().cumprod(1).sum(1)
+    return n, pred.gather(1, n[:, None]).squeeze(1)
+
+
+def verify_sampling_batch(draft_tokens: torch.Tensor, draft_probs: torch.Tensor, target_logits: torch.Tensor,
+                          temperature: float, generator: Optional[torch.Generator] = None):
+    """Batched :func:`verify_sampling` (same acceptance rule, one draw of uniforms per position and one
+    residual / bonus draw per sequence).  Returns ``(accepted [B], next_token [B])`` on the device."""
+    B, K = draft_tokens.shape
+    pt = torch.softmax(target_logits.float() / max(temperature, 1e-6), -1)          # [B,K+1,V]
+    idx = draft_tokens[..., None]
+    ratio = pt[:, :K].gather(2, idx).squeeze(2) / draft_probs.gather(2, idx).squeeze(2).clamp(min=1e-20)
+    u = torch.rand(B, K, device=pt.device, generator=generator)
+    n = (u < ratio.clamp(max=1.0)).long().cumprod(1).sum(1)                         # first rejection
+    rows = torch.arange(B, device=pt.device)
+    p_at = pt[rows, n]                                                              # [B,V]
+    d_at = draft_probs[rows, n.clamp(max=K - 1)]
+    resid = (p_at - d_at).clamp(min=0)
+    ssum = resid.sum(-1, keepdim=True)
+    resid = torch.where(ssum > 0, resid / ssum.clamp(min=1e-30), p_at)
+    dist = torch.where((n == K)[:, None], p_at, resid)
+    return n, torch.multinomial(dist, 1, generator=generator).squeeze(1)
+
+
 class SpeculativeDecoder:
     """Drives draft + target runners for a batch of sequences that already finished prefill in both
     caches.  ``target`` / ``draft`` are :class:`ModelRunner` objects with their own block managers."""
@@ -111,13 +140,16 @@ class SpeculativeDecoder:
         logits = tgt.forward(ids.reshape(-1), ctx, all_rows=True).reshape(len(seq_ids), K + 1, -1)
         out: List[List[int]] = []
         catch_up: List[int] = []
+        if temperature <= 0:
+            n_dev, nxt_dev = verify_greedy_batch(d_tokens, logits)
+        else:
+            n_dev, nxt_dev = verify_sampling_batch(d_tokens, d_probs, logits, temperature, generator)
+        # the only host sync of the round: accepted counts, next tokens and the drafts in one copy
+        packed = torch.cat([n_dev[:, None], nxt_dev[:, None], d_tokens], 1).tolist()
         for i, s in enumerate(seq_ids):
-            if temperature <= 0:
-                n, nxt = verify_greedy(d_tokens[i], logits[i])
-            else:
-                n, nxt = verify_sampling(d_tokens[i], d_probs[i], logits[i], temperature, generator)
+            n, nxt = packed[i][0], packed[i][1]
             self.tracker.record(n, K)
-            out.append(d_tokens[i, :n].tolist() + [nxt])
+            out.append(packed[i][2:2 + n] + [nxt])
             # both caches must end up holding history + last + the n accepted drafts; the returned
             # final token is the next round's `last` and is not stored yet
             tgt.mgr.trim(s, base[i] + 1 + n)

@@ -42,6 +42,8 @@ def parse():
     ap.add_argument("--grad-ckpt", action="store_true")
     ap.add_argument("--sequence-parallel", action="store_true")
     ap.add_argument("--zero-comm", default="nccl", choices=["nccl", "p2p"])
+    ap.add_argument("--fused-tp", action="store_true",
+                    help="run the sequence-parallel collectives inside the GEMM kernels (peer memory) instead of NCCL")
     return ap.parse_args()
 
 
@@ -134,7 +136,8 @@ def run_ours(a):
                       use_gradient_checkpoint=a.grad_ckpt, lora_rank=a.lora_rank, learning_rate=1e-5,
                       gradient_accumulation_steps=a.grad_accum if a.pp == 1 else 1, grpo_beta=0.0,
                       zero_stage=a.zero_stage, warmup_steps=2, total_training_steps=a.steps + a.warmup + 8,
-                      sequence_parallel=a.sequence_parallel, amp_dtype="bf16", zero_comm_backend=a.zero_comm)
+                      sequence_parallel=a.sequence_parallel, amp_dtype="bf16", zero_comm_backend=a.zero_comm,
+                      fused_tp_comm=a.fused_tp)
     eng = TrainEngine(cfg).initialize()
     dev = eng.device
     accum = a.grad_accum
@@ -204,7 +207,8 @@ def run_ours(a):
             "config": {"model": f"{a.model}-arch full SFT" if a.lora_rank <= 0 else f"{a.model}-arch LoRA r{a.lora_rank}",
                        "global_batch": a.micro_batch * micro_per_step * dp, "micro_batch_per_gpu": a.micro_batch,
                        "grad_accum": a.grad_accum, "seq_len": a.seq_len, "parallelism": par,
-                       "zero_stage": a.zero_stage, "zero_comm": a.zero_comm, "l2": "inputs larger than L2 (weights+activations >> 126 MB)",
+                       "zero_stage": a.zero_stage, "zero_comm": a.zero_comm,
+                       "sequence_parallel": a.sequence_parallel, "fused_tp_comm": a.fused_tp, "grad_ckpt": a.grad_ckpt, "l2": "inputs larger than L2 (weights+activations >> 126 MB)",
                        "step": "one optimizer step = grad_accum micro-batches + reduce + clip + AdamW"},
             "mfu_exact_of_measured_sustained": flops / (step_s * world * peaks["bf16_tflops_sustained"] * 1e12),
             "model_tflops_per_gpu": flops / step_s / world / 1e12,

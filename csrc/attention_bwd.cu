@@ -55,12 +55,31 @@ struct DkDvSmem {
   static constexpr int TOTAL = BARS + 144 + 1024 /*lse, D*/ + 1024;
 };
 
+// Persistent: each CTA walks the work items (kv tile, kv head, batch) dealt in boustrophedon order,
+// heaviest first (small kv tile index = most q tiles).  Barriers, TMEM and the Q/dO
+// ring live across items; the K/V tiles of the next item are requested as soon as the last S^T/dP^T
+// MMAs of the current one retire.
+struct DkDvItem {
+  int jt, kvh, batch, i_begin, per_head, n_it;
+};
+__device__ __forceinline__ DkDvItem dkdv_item(int w, int Hkv, int B, int nq64, int G) {
+  DkDvItem it;
+  const int hb = w % (Hkv * B);
+  it.jt = w / (Hkv * B);
+  it.kvh = hb % Hkv;
+  it.batch = hb / Hkv;
+  it.i_begin = 2 * it.jt;  // first 64-row q tile that can see this kv tile
+  it.per_head = nq64 - it.i_begin;
+  it.n_it = it.per_head > 0 ? it.per_head * G : 0;
+  return it;
+}
+
 __global__ void __launch_bounds__(ATB_THREADS, 1)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_constant__ CUtensorMap tmdO64,
                      const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                      const float* __restrict__ lse, const float* __restrict__ Dsum,
                      __nv_bfloat16* __restrict__ dk, __nv_bfloat16* __restrict__ dv, int ld_dk, int ld_dv,
-                     int S, int Hq, int Hkv, float scale, int* status) {
+                     int B, int S, int Hq, int Hkv, float scale, int* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -73,31 +92,28 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_con
   uint64_t* pds_full = bars + 11;   // [2]
   uint64_t* pds_empty = bars + 13;  // [2]
   uint64_t* acc_done = bars + 15;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  uint64_t* kv_empty = bars + 16;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
   float* s_lse = reinterpret_cast<float*>(bars + 18);   // [2][64], pre-multiplied by log2(e)
   float* s_D = s_lse + 128;                             // [2][64]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int jt = blockIdx.x;  // kv tile (128 rows); light tiles (large jt) are scheduled last anyway
-  const int kvh = blockIdx.y, batch = blockIdx.z;
   const int G = Hq / Hkv;
-  const int T = gridDim.z * S;
+  const int T = B * S;
   const int nq64 = (S + 63) / 64;
-  const int i_begin = 2 * jt;  // first 64-row q tile that can see this kv tile
-  const int per_head = nq64 - i_begin;
-  const int n_it = per_head > 0 ? per_head * G : 0;
-  const int kv_row0 = batch * S + jt * 128;
+  const int n_items = ((S + 127) / 128) * Hkv * B;
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
+    mbar_init(kv_empty, 1);
     for (int i = 0; i < ATB_STAGES; ++i) {
       mbar_init(&qdo_full[i], 1);
       mbar_init(&qdo_empty[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&sdp_full[i], 1);
-      mbar_init(&sdp_empty[i], 256);
-      mbar_init(&pds_full[i], 256);
+      mbar_init(&sdp_empty[i], 8);   // one arrive per elementwise warp
+      mbar_init(&pds_full[i], 8);
       mbar_init(&pds_empty[i], 1);
     }
     mbar_init(acc_done, 1);
@@ -117,176 +133,244 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_con
   const uint32_t tmem_DK = tmem_base + 384;   // 128
 
   if (warp == 0) {
-    if (lane == 0 && n_it > 0) {
-      mbar_expect_tx(kv_full, 65536);
-      tma_load_2d(smem + DkDvSmem::K, &tmK, kv_full, kvh * 128, kv_row0);
-      tma_load_2d(smem + DkDvSmem::K + 16384, &tmK, kv_full, kvh * 128 + 64, kv_row0);
-      tma_load_2d(smem + DkDvSmem::V, &tmV, kv_full, kvh * 128, kv_row0);
-      tma_load_2d(smem + DkDvSmem::V + 16384, &tmV, kv_full, kvh * 128 + 64, kv_row0);
-      for (int it = 0; it < n_it; ++it) {
-        const int st = it % ATB_STAGES;
-        const uint32_t ph = (it / ATB_STAGES) & 1;
-        const int head = kvh * G + it / per_head;
-        const int qrow = batch * S + (i_begin + it % per_head) * 64;
-        if (!mbar_wait(&qdo_empty[st], ph ^ 1, status, ERR_ATTN_WAIT)) break;
-        uint8_t* sQ = smem + DkDvSmem::Q + st * 16384;
-        uint8_t* sdO = smem + DkDvSmem::DO + st * 16384;
-        mbar_expect_tx(&qdo_full[st], 32768);
-        tma_load_2d(sQ, &tmQ64, &qdo_full[st], head * 128, qrow);
-        tma_load_2d(sQ + 8192, &tmQ64, &qdo_full[st], head * 128 + 64, qrow);
-        tma_load_2d(sdO, &tmdO64, &qdo_full[st], head * 128, qrow);
-        tma_load_2d(sdO + 8192, &tmdO64, &qdo_full[st], head * 128 + 64, qrow);
+    if (lane == 0) {
+      int g = 0, n = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < n_items && ok; w = snake_next(w)) {
+        const DkDvItem item = dkdv_item(w, Hkv, B, nq64, G);
+        if (item.n_it == 0) continue;
+        const int kv_row0 = item.batch * S + item.jt * 128;
+        if (!mbar_wait(kv_empty, (n & 1) ^ 1, status, ERR_ATTN_WAIT)) break;
+        mbar_expect_tx(kv_full, 65536);
+        tma_load_2d(smem + DkDvSmem::K, &tmK, kv_full, item.kvh * 128, kv_row0);
+        tma_load_2d(smem + DkDvSmem::K + 16384, &tmK, kv_full, item.kvh * 128 + 64, kv_row0);
+        tma_load_2d(smem + DkDvSmem::V, &tmV, kv_full, item.kvh * 128, kv_row0);
+        tma_load_2d(smem + DkDvSmem::V + 16384, &tmV, kv_full, item.kvh * 128 + 64, kv_row0);
+        for (int it = 0; it < item.n_it; ++it, ++g) {
+          const int st = g % ATB_STAGES;
+          const uint32_t ph = (g / ATB_STAGES) & 1;
+          const int head = item.kvh * G + it / item.per_head;
+          const int qrow = item.batch * S + (item.i_begin + it % item.per_head) * 64;
+          if (!mbar_wait(&qdo_empty[st], ph ^ 1, status, ERR_ATTN_WAIT)) { ok = false; break; }
+          uint8_t* sQ = smem + DkDvSmem::Q + st * 16384;
+          uint8_t* sdO = smem + DkDvSmem::DO + st * 16384;
+          mbar_expect_tx(&qdo_full[st], 32768);
+          tma_load_2d(sQ, &tmQ64, &qdo_full[st], head * 128, qrow);
+          tma_load_2d(sQ + 8192, &tmQ64, &qdo_full[st], head * 128 + 64, qrow);
+          tma_load_2d(sdO, &tmdO64, &qdo_full[st], head * 128, qrow);
+          tma_load_2d(sdO + 8192, &tmdO64, &qdo_full[st], head * 128 + 64, qrow);
+        }
+        ++n;
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && n_it > 0) {
+    // The whole warp runs this (uniform) control flow so that descriptors and addresses stay in the
+    // uniform datapath; only the tcgen05 instructions themselves are issued by one elected lane.
+    {
+      const bool leader = elect_one();
       constexpr uint32_t idesc_s = make_idesc_f16(1, 128, 64, 0, 0);     // [128 kv] x [64 q], K = d
       constexpr uint32_t idesc_acc = make_idesc_f16(1, 128, 128, 0, 1);  // [128 kv] x [128 d], K = q
-      const uint32_t k_base = smem_u32(smem + DkDvSmem::K);
-      const uint32_t v_base = smem_u32(smem + DkDvSmem::V);
-      auto issue_sdp = [&](int it) {
-        const int st = it & 1;
-        const int ks = it % ATB_STAGES;
-        const uint32_t q_base = smem_u32(smem + DkDvSmem::Q + ks * 16384);
-        const uint32_t do_base = smem_u32(smem + DkDvSmem::DO + ks * 16384);
+      const uint64_t d_k = make_smem_desc_sw128(smem_u32(smem + DkDvSmem::K), 16, 1024);
+      const uint64_t d_v = make_smem_desc_sw128(smem_u32(smem + DkDvSmem::V), 16, 1024);
+      auto issue_sdp = [&](int g) {
+        const int st = g & 1;
+        const int ks_ = g % ATB_STAGES;
+        const uint64_t d_q = make_smem_desc_sw128(smem_u32(smem + DkDvSmem::Q + ks_ * 16384), 16, 1024);
+        const uint64_t d_do = make_smem_desc_sw128(smem_u32(smem + DkDvSmem::DO + ks_ * 16384), 16, 1024);
+        if (leader) {
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t oa = (ks >> 2) * 16384 + (ks & 3) * 32;
-          const uint32_t ob = (ks >> 2) * 8192 + (ks & 3) * 32;
-          umma_f16_ss(tmem_ST + st * 64, make_smem_desc_sw128(k_base + oa, 16, 1024),
-                      make_smem_desc_sw128(q_base + ob, 16, 1024), idesc_s, ks != 0);
-        }
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t oa = (ks >> 2) * 16384 + (ks & 3) * 32;
-          const uint32_t ob = (ks >> 2) * 8192 + (ks & 3) * 32;
-          umma_f16_ss(tmem_DPT + st * 64, make_smem_desc_sw128(v_base + oa, 16, 1024),
-                      make_smem_desc_sw128(do_base + ob, 16, 1024), idesc_s, ks != 0);
-        }
-        umma_commit(&sdp_full[st]);
-      };
-      bool ok = mbar_wait(kv_full, 0, status, ERR_ATTN_WAIT) &&
-                mbar_wait(&qdo_full[0], 0, status, ERR_ATTN_WAIT);
-      if (ok) {
-        tc_fence_after();
-        issue_sdp(0);
-      }
-      for (int it = 0; it < n_it && ok; ++it) {
-        if (it + 1 < n_it) {
-          const int st = (it + 1) & 1;
-          const uint32_t ph = ((it + 1) >> 1) & 1;
-          if (!mbar_wait(&qdo_full[(it + 1) % ATB_STAGES], ((it + 1) / ATB_STAGES) & 1, status, ERR_ATTN_WAIT) ||
-              !mbar_wait(&sdp_empty[st], ph ^ 1, status, ERR_ATTN_WAIT)) {
-            ok = false;
-            break;
+          for (int ks = 0; ks < 8; ++ks) {
+            const uint32_t oa = (ks >> 2) * 16384 + (ks & 3) * 32;
+            const uint32_t ob = (ks >> 2) * 8192 + (ks & 3) * 32;
+            umma_f16_ss(tmem_ST + st * 64, desc_advance(d_k, oa), desc_advance(d_q, ob), idesc_s, ks != 0);
           }
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks) {
+            const uint32_t oa = (ks >> 2) * 16384 + (ks & 3) * 32;
+            const uint32_t ob = (ks >> 2) * 8192 + (ks & 3) * 32;
+            umma_f16_ss(tmem_DPT + st * 64, desc_advance(d_v, oa), desc_advance(d_do, ob), idesc_s, ks != 0);
+          }
+        }
+        if (leader) umma_commit(&sdp_full[st]);
+      };
+      auto wait_sdp_inputs = [&](int g) -> bool {
+        return mbar_wait(&qdo_full[g % ATB_STAGES], (g / ATB_STAGES) & 1, status, ERR_ATTN_WAIT) &&
+               mbar_wait(&sdp_empty[g & 1], ((g >> 1) & 1) ^ 1, status, ERR_ATTN_WAIT);
+      };
+      // index of the next item with work after w (n_items if none)
+      auto next_item = [&](int w) {
+        int x = snake_next(w);
+        while (x < n_items && dkdv_item(x, Hkv, B, nq64, G).n_it == 0) x = snake_next(x);
+        return x;
+      };
+      int g = 0, n = 0;
+      bool ok = true, primed = false;
+      int w = blockIdx.x;
+      if (w < n_items && dkdv_item(w, Hkv, B, nq64, G).n_it == 0) w = next_item(w);
+      for (; w < n_items && ok; ++n) {
+        const DkDvItem item = dkdv_item(w, Hkv, B, nq64, G);
+        const int w_next = next_item(w);
+        if (!primed) {
+          ok = mbar_wait(kv_full, n & 1, status, ERR_ATTN_WAIT) && wait_sdp_inputs(g);
+          if (!ok) break;
           tc_fence_after();
-          issue_sdp(it + 1);
+          issue_sdp(g);
+          if (item.n_it == 1) if (leader) umma_commit(kv_empty);
         }
-        const int st = it & 1;
-        if (!mbar_wait(&pds_full[st], (it >> 1) & 1, status, ERR_ATTN_WAIT)) {
-          ok = false;
-          break;
+        primed = false;
+        for (int it = 0; it < item.n_it; ++it, ++g) {
+          if (it + 1 < item.n_it) {
+            if (!wait_sdp_inputs(g + 1)) { ok = false; break; }
+            tc_fence_after();
+            issue_sdp(g + 1);
+            if (it + 2 == item.n_it) if (leader) umma_commit(kv_empty);   // last S^T/dP^T of the item: K/V may be reloaded
+          }
+          const int st = g & 1;
+          if (!mbar_wait(&pds_full[st], (g >> 1) & 1, status, ERR_ATTN_WAIT)) { ok = false; break; }
+          tc_fence_after();
+          const int kst = g % ATB_STAGES;
+          const uint64_t d_pt = make_smem_desc_sw128(smem_u32(smem + DkDvSmem::PT + st * 16384), 16, 1024);
+          const uint64_t d_dst = make_smem_desc_sw128(smem_u32(smem + DkDvSmem::DST + st * 16384), 16, 1024);
+          const uint64_t d_qm = make_smem_desc_sw128(smem_u32(smem + DkDvSmem::Q + kst * 16384), 8192, 1024);
+          const uint64_t d_dom = make_smem_desc_sw128(smem_u32(smem + DkDvSmem::DO + kst * 16384), 8192, 1024);
+          const uint32_t acc0 = it != 0;
+          if (leader) {
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)
+              umma_f16_ss(tmem_DV, desc_advance(d_pt, ks * 32), desc_advance(d_dom, ks * 2048), idesc_acc,
+                          ks ? 1u : acc0);
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)
+              umma_f16_ss(tmem_DK, desc_advance(d_dst, ks * 32), desc_advance(d_qm, ks * 2048), idesc_acc,
+                          ks ? 1u : acc0);
+          }
+          if (leader) umma_commit(&qdo_empty[kst]);
+          if (leader) umma_commit(&pds_empty[st]);
+          if (it + 1 == item.n_it) {
+            if (leader) umma_commit(acc_done);
+            if (w_next < n_items) {
+              if (!mbar_wait(kv_full, (n + 1) & 1, status, ERR_ATTN_WAIT) || !wait_sdp_inputs(g + 1)) {
+                ok = false;
+                break;
+              }
+              tc_fence_after();
+              issue_sdp(g + 1);
+              if (dkdv_item(w_next, Hkv, B, nq64, G).n_it == 1) if (leader) umma_commit(kv_empty);
+              primed = true;
+            }
+          }
         }
-        tc_fence_after();
-        const uint32_t pt_base = smem_u32(smem + DkDvSmem::PT + st * 16384);
-        const uint32_t dst_base = smem_u32(smem + DkDvSmem::DST + st * 16384);
-        const int kst = it % ATB_STAGES;
-        const uint32_t q_base = smem_u32(smem + DkDvSmem::Q + kst * 16384);
-        const uint32_t do_base = smem_u32(smem + DkDvSmem::DO + kst * 16384);
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          umma_f16_ss(tmem_DV, make_smem_desc_sw128(pt_base + ks * 32, 16, 1024),
-                      make_smem_desc_sw128(do_base + ks * 2048, 8192, 1024), idesc_acc, (it | ks) != 0);
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          umma_f16_ss(tmem_DK, make_smem_desc_sw128(dst_base + ks * 32, 16, 1024),
-                      make_smem_desc_sw128(q_base + ks * 2048, 8192, 1024), idesc_acc, (it | ks) != 0);
-        umma_commit(&qdo_empty[kst]);
-        umma_commit(&pds_empty[st]);
+        w = w_next;
       }
-      if (ok) umma_commit(acc_done);
     }
   } else {
     const int quarter = warp & 3;
     const int half = (warp - 2) >> 2;           // which 32 columns of the 64-column tile
     const int etid = (warp - 2) * 32 + lane;    // 0..255 among the elementwise threads
     const int r = quarter * 32 + lane;          // kv row in tile
-    const int kv_pos = jt * 128 + r;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     const float sl2 = scale * LOG2E;
-    bool ok = n_it > 0;
-    for (int it = 0; it < n_it; ++it) {
-      const int st = it & 1;
-      const uint32_t ph = (it >> 1) & 1;
-      const int head = kvh * G + it / per_head;
-      const int q0 = (i_begin + it % per_head) * 64;  // first q position of this tile
-      // stage this tile's row statistics (64 q positions) in shared memory
-      if (etid < 128) {
-        const int c = etid & 63;
-        const int qc = min(q0 + c, S - 1);
-        const size_t o = static_cast<size_t>(head) * T + batch * S + qc;
-        if (etid < 64) s_lse[st * 64 + c] = lse[o] * LOG2E;
-        else s_D[st * 64 + c] = Dsum[o];
-      }
-      ew_barrier();   // every elementwise thread reaches this each iteration, also after a failed wait
-      if (ok) ok = mbar_wait(&sdp_full[st], ph, status, ERR_ATTN_WAIT);
-      if (!ok) continue;
-      tc_fence_after();
-      uint32_t ts[32], tp[32];
-      tmem_ld_32x32b_x32(tmem_ST + lane_off + st * 64 + half * 32, ts);
-      tmem_ld_32x32b_x32(tmem_DPT + lane_off + st * 64 + half * 32, tp);
-      tmem_ld_wait();
-      tc_fence_before();
-      mbar_arrive(&sdp_empty[st]);
-      const float* lse_s = s_lse + st * 64 + half * 32;
-      const float* D_s = s_D + st * 64 + half * 32;
-      const int qb = q0 + half * 32;
-      const bool need_mask = (qb < jt * 128 + 128) || (qb + 32 > S) || (jt * 128 + 128 > S);
-      float pv[32], dsv[32];
-#pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        float p = exp2f(__uint_as_float(ts[c]) * sl2 - lse_s[c]);
-        if (need_mask) {
-          const int qp = qb + c;
-          if (!((qp < S) && (kv_pos <= qp) && (kv_pos < S))) p = 0.f;
+    bool ok = true;
+    int g = 0, n = 0;
+    // Row statistics (lse, D) of a 64-row q tile go through shared memory; the global loads for
+    // the next tile (of this or the next item) are issued at the top of an iteration and stored at
+    // its end, so their latency hides behind the elementwise work.
+    auto stat_load = [&](const DkDvItem& item, int it) -> float {
+      if (etid >= 128) return 0.f;
+      const int head_ = item.kvh * G + it / item.per_head;
+      const int q0_ = (item.i_begin + it % item.per_head) * 64;
+      const int qc = min(q0_ + (etid & 63), S - 1);
+      const size_t o = static_cast<size_t>(head_) * T + item.batch * S + qc;
+      return etid < 64 ? lse[o] * LOG2E : Dsum[o];
+    };
+    auto stat_store = [&](int g_, float v) {
+      if (etid < 64) s_lse[(g_ & 1) * 64 + etid] = v;
+      else if (etid < 128) s_D[(g_ & 1) * 64 + (etid & 63)] = v;
+    };
+    bool first = true;
+    for (int w = blockIdx.x; w < n_items; w = snake_next(w)) {
+      const DkDvItem item = dkdv_item(w, Hkv, B, nq64, G);
+      const int kv_pos = item.jt * 128 + r;
+      const int kv_row0 = item.batch * S + item.jt * 128;
+      const bool in_range = kv_pos < S;
+      __nv_bfloat16* orow = half ? dk + static_cast<size_t>(kv_row0 + r) * ld_dk + item.kvh * 128
+                                 : dv + static_cast<size_t>(kv_row0 + r) * ld_dv + item.kvh * 128;
+      if (item.n_it == 0) {   // no query sees this kv tile: zero gradients
+        if (in_range) {
+          const uint4 z = make_uint4(0, 0, 0, 0);
+          for (int c = 0; c < 16; ++c) *reinterpret_cast<uint4*>(orow + c * 8) = z;
         }
-        pv[c] = p;
-        dsv[c] = p * (__uint_as_float(tp[c]) - D_s[c]) * scale;
+        continue;
       }
-      ok = mbar_wait(&pds_empty[st], ph ^ 1, status, ERR_ATTN_WAIT);
-      if (!ok) continue;
-      uint8_t* sPT = smem + DkDvSmem::PT + st * 16384 + r * 128;
-      uint8_t* sDST = smem + DkDvSmem::DST + st * 16384 + r * 128;
+      // the next item with work (its first tile's statistics are prefetched in the last iteration)
+      int wn = snake_next(w);
+      while (wn < n_items && dkdv_item(wn, Hkv, B, nq64, G).n_it == 0) wn = snake_next(wn);
+      if (first) {
+        stat_store(g, stat_load(item, 0));
+        first = false;
+      }
+      for (int it = 0; it < item.n_it; ++it, ++g) {
+        const int st = g & 1;
+        const uint32_t ph = (g >> 1) & 1;
+        const int q0 = (item.i_begin + it % item.per_head) * 64;  // first q position of this tile
+        float next_stat = 0.f;
+        if (it + 1 < item.n_it) next_stat = stat_load(item, it + 1);
+        else if (wn < n_items) next_stat = stat_load(dkdv_item(wn, Hkv, B, nq64, G), 0);
+        ew_barrier();   // publishes this tile's statistics; every elementwise thread reaches it each
+                        // iteration, also after a failed wait
+        if (ok) ok = mbar_wait_warp(&sdp_full[st], ph, status, ERR_ATTN_WAIT);
+        if (!ok) continue;
+        tc_fence_after();
+        uint32_t ts[32], tp[32];
+        tmem_ld_32x32b_x32(tmem_ST + lane_off + st * 64 + half * 32, ts);
+        tmem_ld_32x32b_x32(tmem_DPT + lane_off + st * 64 + half * 32, tp);
+        tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive_warp(&sdp_empty[st]);
+        const float* lse_s = s_lse + st * 64 + half * 32;
+        const float* D_s = s_D + st * 64 + half * 32;
+        const int qb = q0 + half * 32;
+        const bool need_mask = (qb < item.jt * 128 + 128) || (qb + 32 > S) || (item.jt * 128 + 128 > S);
+        float pv[32], dsv[32];
 #pragma unroll
-      for (int c4 = 0; c4 < 4; ++c4) {
-        uint4 a, b;
-        a.x = pack_bf16x2(pv[c4 * 8 + 0], pv[c4 * 8 + 1]);
-        a.y = pack_bf16x2(pv[c4 * 8 + 2], pv[c4 * 8 + 3]);
-        a.z = pack_bf16x2(pv[c4 * 8 + 4], pv[c4 * 8 + 5]);
-        a.w = pack_bf16x2(pv[c4 * 8 + 6], pv[c4 * 8 + 7]);
-        b.x = pack_bf16x2(dsv[c4 * 8 + 0], dsv[c4 * 8 + 1]);
-        b.y = pack_bf16x2(dsv[c4 * 8 + 2], dsv[c4 * 8 + 3]);
-        b.z = pack_bf16x2(dsv[c4 * 8 + 4], dsv[c4 * 8 + 5]);
-        b.w = pack_bf16x2(dsv[c4 * 8 + 6], dsv[c4 * 8 + 7]);
-        const int sw = (((half * 4 + c4) ^ (r & 7)) << 4);
-        *reinterpret_cast<uint4*>(sPT + sw) = a;
-        *reinterpret_cast<uint4*>(sDST + sw) = b;
+        for (int c = 0; c < 32; ++c) {
+          float p = exp2f(__uint_as_float(ts[c]) * sl2 - lse_s[c]);
+          if (need_mask) {
+            const int qp = qb + c;
+            if (!((qp < S) && (kv_pos <= qp) && (kv_pos < S))) p = 0.f;
+          }
+          pv[c] = p;
+          dsv[c] = p * (__uint_as_float(tp[c]) - D_s[c]) * scale;
+        }
+        stat_store(g + 1, next_stat);   // slot (g+1)&1 was last read in iteration g-1
+        ok = mbar_wait_warp(&pds_empty[st], ph ^ 1, status, ERR_ATTN_WAIT);
+        if (!ok) continue;
+        uint8_t* sPT = smem + DkDvSmem::PT + st * 16384 + r * 128;
+        uint8_t* sDST = smem + DkDvSmem::DST + st * 16384 + r * 128;
+#pragma unroll
+        for (int c4 = 0; c4 < 4; ++c4) {
+          uint4 a, b;
+          a.x = pack_bf16x2(pv[c4 * 8 + 0], pv[c4 * 8 + 1]);
+          a.y = pack_bf16x2(pv[c4 * 8 + 2], pv[c4 * 8 + 3]);
+          a.z = pack_bf16x2(pv[c4 * 8 + 4], pv[c4 * 8 + 5]);
+          a.w = pack_bf16x2(pv[c4 * 8 + 6], pv[c4 * 8 + 7]);
+          b.x = pack_bf16x2(dsv[c4 * 8 + 0], dsv[c4 * 8 + 1]);
+          b.y = pack_bf16x2(dsv[c4 * 8 + 2], dsv[c4 * 8 + 3]);
+          b.z = pack_bf16x2(dsv[c4 * 8 + 4], dsv[c4 * 8 + 5]);
+          b.w = pack_bf16x2(dsv[c4 * 8 + 6], dsv[c4 * 8 + 7]);
+          const int sw = (((half * 4 + c4) ^ (r & 7)) << 4);
+          *reinterpret_cast<uint4*>(sPT + sw) = a;
+          *reinterpret_cast<uint4*>(sDST + sw) = b;
+        }
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive_warp(&pds_full[st]);
       }
-      fence_proxy_async_smem();
-      tc_fence_before();
-      mbar_arrive(&pds_full[st]);
-    }
-    // write-out: the first column group stores dV, the second dK
-    const bool in_range = kv_pos < S;
-    __nv_bfloat16* orow = half ? dk + static_cast<size_t>(kv_row0 + r) * ld_dk + kvh * 128
-                               : dv + static_cast<size_t>(kv_row0 + r) * ld_dv + kvh * 128;
-    if (n_it == 0) {
-      if (in_range) {
-        const uint4 z = make_uint4(0, 0, 0, 0);
-        for (int c = 0; c < 16; ++c) *reinterpret_cast<uint4*>(orow + c * 8) = z;
-      }
-    } else if (ok && mbar_wait(acc_done, 0, status, ERR_ATTN_WAIT)) {
+      // write-out: the first column group stores dV, the second dK.  The next item's first dV/dK MMAs
+      // are ordered after it by this warp's next pds_full arrive.
+      if (ok) ok = mbar_wait_warp(acc_done, n & 1, status, ERR_ATTN_WAIT);
+      ++n;
+      if (!ok) continue;
       tc_fence_after();
       const uint32_t tb = (half ? tmem_DK : tmem_DV) + lane_off;
 #pragma unroll
@@ -306,6 +390,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_con
           }
         }
       }
+      tc_fence_before();
     }
   }
 
@@ -333,11 +418,30 @@ struct DqSmem {
   static constexpr int TOTAL = BARS + 256 + 1024;
 };
 
+// Persistent: each CTA walks the work items (q tile, head, batch) dealt in boustrophedon order,
+// heaviest first.  Barriers, TMEM and the K/V ring live across items, so a
+// new item costs one Q/dO reload (issued as soon as the previous item's last S/dP MMAs retire, i.e.
+// hidden behind its last elementwise step, dQ MMA and write-out) instead of a CTA launch, a TMEM
+// allocation and a cold pipeline.
+struct DqItem {
+  int qt, head, batch, n_it;
+};
+__device__ __forceinline__ DqItem dq_item(int w, int num_q_tiles, int Hq, int B, int nkv64) {
+  DqItem it;
+  const int hb = w % (Hq * B);
+  it.qt = num_q_tiles - 1 - w / (Hq * B);  // heaviest tiles first
+  it.head = hb % Hq;
+  it.batch = hb / Hq;
+  it.n_it = min(nkv64, 2 * it.qt + 2);
+  return it;
+}
+
 __global__ void __launch_bounds__(ATB_THREADS, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
                    const __grid_constant__ CUtensorMap tmK64, const __grid_constant__ CUtensorMap tmV64,
                    const float* __restrict__ lse, const float* __restrict__ Dsum,
-                   __nv_bfloat16* __restrict__ dq, int S, int Hq, int Hkv, float scale, int* status) {
+                   __nv_bfloat16* __restrict__ dq, int B, int S, int Hq, int Hkv, float scale,
+                   int* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -350,28 +454,27 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint64_t* ds_full = bars + 11;   // [2]
   uint64_t* ds_empty = bars + 13;  // [2]
   uint64_t* acc_done = bars + 15;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  uint64_t* q_empty = bars + 16;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_q_tiles = (S + 127) / 128;
-  const int qt = num_q_tiles - 1 - blockIdx.x;
-  const int head = blockIdx.y, batch = blockIdx.z;
-  const int kvh = head / (Hq / Hkv);
-  const int T = gridDim.z * S;
+  const int T = B * S;
   const int nkv64 = (S + 63) / 64;
-  const int n_it = min(nkv64, 2 * qt + 2);
-  const int row0 = batch * S + qt * 128;
+  const int n_items = num_q_tiles * Hq * B;
+  const int G = Hq / Hkv;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
+    mbar_init(q_empty, 1);
     for (int i = 0; i < ATB_STAGES; ++i) {
       mbar_init(&kv_full[i], 1);
       mbar_init(&kv_empty[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&sdp_full[i], 1);
-      mbar_init(&sdp_empty[i], 256);
-      mbar_init(&ds_full[i], 256);
+      mbar_init(&sdp_empty[i], 8);   // one arrive per elementwise warp
+      mbar_init(&ds_full[i], 8);
       mbar_init(&ds_empty[i], 1);
     }
     mbar_init(acc_done, 1);
@@ -391,141 +494,195 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
   if (warp == 0) {
     if (lane == 0) {
-      mbar_expect_tx(q_full, 65536);
-      tma_load_2d(smem + DqSmem::Q, &tmQ, q_full, head * 128, row0);
-      tma_load_2d(smem + DqSmem::Q + 16384, &tmQ, q_full, head * 128 + 64, row0);
-      tma_load_2d(smem + DqSmem::DO, &tmdO, q_full, head * 128, row0);
-      tma_load_2d(smem + DqSmem::DO + 16384, &tmdO, q_full, head * 128 + 64, row0);
-      for (int it = 0; it < n_it; ++it) {
-        const int st = it % ATB_STAGES;
-        const uint32_t ph = (it / ATB_STAGES) & 1;
-        const int krow = batch * S + it * 64;
-        if (!mbar_wait(&kv_empty[st], ph ^ 1, status, ERR_ATTN_WAIT)) break;
-        uint8_t* sK = smem + DqSmem::K + st * 16384;
-        uint8_t* sV = smem + DqSmem::V + st * 16384;
-        mbar_expect_tx(&kv_full[st], 32768);
-        tma_load_2d(sK, &tmK64, &kv_full[st], kvh * 128, krow);
-        tma_load_2d(sK + 8192, &tmK64, &kv_full[st], kvh * 128 + 64, krow);
-        tma_load_2d(sV, &tmV64, &kv_full[st], kvh * 128, krow);
-        tma_load_2d(sV + 8192, &tmV64, &kv_full[st], kvh * 128 + 64, krow);
+      int g = 0;   // K/V tiles loaded so far (ring position, continues across items)
+      int n = 0;   // items started
+      bool ok = true;
+      for (int w = blockIdx.x; w < n_items && ok; w = snake_next(w), ++n) {
+        const DqItem item = dq_item(w, num_q_tiles, Hq, B, nkv64);
+        const int row0 = item.batch * S + item.qt * 128;
+        const int kvh = item.head / G;
+        if (!mbar_wait(q_empty, (n & 1) ^ 1, status, ERR_ATTN_WAIT)) break;
+        mbar_expect_tx(q_full, 65536);
+        tma_load_2d(smem + DqSmem::Q, &tmQ, q_full, item.head * 128, row0);
+        tma_load_2d(smem + DqSmem::Q + 16384, &tmQ, q_full, item.head * 128 + 64, row0);
+        tma_load_2d(smem + DqSmem::DO, &tmdO, q_full, item.head * 128, row0);
+        tma_load_2d(smem + DqSmem::DO + 16384, &tmdO, q_full, item.head * 128 + 64, row0);
+        for (int it = 0; it < item.n_it; ++it, ++g) {
+          const int st = g % ATB_STAGES;
+          const uint32_t ph = (g / ATB_STAGES) & 1;
+          const int krow = item.batch * S + it * 64;
+          if (!mbar_wait(&kv_empty[st], ph ^ 1, status, ERR_ATTN_WAIT)) { ok = false; break; }
+          uint8_t* sK = smem + DqSmem::K + st * 16384;
+          uint8_t* sV = smem + DqSmem::V + st * 16384;
+          mbar_expect_tx(&kv_full[st], 32768);
+          tma_load_2d(sK, &tmK64, &kv_full[st], kvh * 128, krow);
+          tma_load_2d(sK + 8192, &tmK64, &kv_full[st], kvh * 128 + 64, krow);
+          tma_load_2d(sV, &tmV64, &kv_full[st], kvh * 128, krow);
+          tma_load_2d(sV + 8192, &tmV64, &kv_full[st], kvh * 128 + 64, krow);
+        }
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    // The whole warp runs this (uniform) control flow so that descriptors and addresses stay in the
+    // uniform datapath; only the tcgen05 instructions themselves are issued by one elected lane.
+    {
+      const bool leader = elect_one();
       constexpr uint32_t idesc_s = make_idesc_f16(1, 128, 64, 0, 0);     // [128 q] x [64 kv], K = d
       constexpr uint32_t idesc_acc = make_idesc_f16(1, 128, 128, 0, 1);  // [128 q] x [128 d], K = kv
-      const uint32_t q_base = smem_u32(smem + DqSmem::Q);
-      const uint32_t do_base = smem_u32(smem + DqSmem::DO);
-      auto issue_sdp = [&](int it) {
-        const int st = it & 1;
-        const int ks_ = it % ATB_STAGES;
-        const uint32_t k_base = smem_u32(smem + DqSmem::K + ks_ * 16384);
-        const uint32_t v_base = smem_u32(smem + DqSmem::V + ks_ * 16384);
+      const uint64_t d_q = make_smem_desc_sw128(smem_u32(smem + DqSmem::Q), 16, 1024);
+      const uint64_t d_do = make_smem_desc_sw128(smem_u32(smem + DqSmem::DO), 16, 1024);
+      // S/dP of global iteration g (ring stage g % STAGES, TMEM buffer g & 1)
+      auto issue_sdp = [&](int g) {
+        const int st = g & 1;
+        const int ks_ = g % ATB_STAGES;
+        const uint64_t d_k = make_smem_desc_sw128(smem_u32(smem + DqSmem::K + ks_ * 16384), 16, 1024);
+        const uint64_t d_v = make_smem_desc_sw128(smem_u32(smem + DqSmem::V + ks_ * 16384), 16, 1024);
+        if (leader) {
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t oa = (ks >> 2) * 16384 + (ks & 3) * 32;
-          const uint32_t ob = (ks >> 2) * 8192 + (ks & 3) * 32;
-          umma_f16_ss(tmem_S + st * 64, make_smem_desc_sw128(q_base + oa, 16, 1024),
-                      make_smem_desc_sw128(k_base + ob, 16, 1024), idesc_s, ks != 0);
-        }
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t oa = (ks >> 2) * 16384 + (ks & 3) * 32;
-          const uint32_t ob = (ks >> 2) * 8192 + (ks & 3) * 32;
-          umma_f16_ss(tmem_DP + st * 64, make_smem_desc_sw128(do_base + oa, 16, 1024),
-                      make_smem_desc_sw128(v_base + ob, 16, 1024), idesc_s, ks != 0);
-        }
-        umma_commit(&sdp_full[st]);
-      };
-      bool ok = mbar_wait(q_full, 0, status, ERR_ATTN_WAIT) &&
-                mbar_wait(&kv_full[0], 0, status, ERR_ATTN_WAIT);
-      if (ok) {
-        tc_fence_after();
-        issue_sdp(0);
-      }
-      for (int it = 0; it < n_it && ok; ++it) {
-        if (it + 1 < n_it) {
-          const int st = (it + 1) & 1;
-          const uint32_t ph = ((it + 1) >> 1) & 1;
-          if (!mbar_wait(&kv_full[(it + 1) % ATB_STAGES], ((it + 1) / ATB_STAGES) & 1, status, ERR_ATTN_WAIT) ||
-              !mbar_wait(&sdp_empty[st], ph ^ 1, status, ERR_ATTN_WAIT)) {
-            ok = false;
-            break;
+          for (int ks = 0; ks < 8; ++ks) {
+            const uint32_t oa = (ks >> 2) * 16384 + (ks & 3) * 32;
+            const uint32_t ob = (ks >> 2) * 8192 + (ks & 3) * 32;
+            umma_f16_ss(tmem_S + st * 64, desc_advance(d_q, oa), desc_advance(d_k, ob), idesc_s, ks != 0);
           }
-          tc_fence_after();
-          issue_sdp(it + 1);
-        }
-        const int st = it & 1;
-        if (!mbar_wait(&ds_full[st], (it >> 1) & 1, status, ERR_ATTN_WAIT)) {
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        const int kst = it % ATB_STAGES;
-        const uint32_t ds_base = smem_u32(smem + DqSmem::DS + st * 16384);
-        const uint32_t k_base = smem_u32(smem + DqSmem::K + kst * 16384);
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          umma_f16_ss(tmem_DQ, make_smem_desc_sw128(ds_base + ks * 32, 16, 1024),
-                      make_smem_desc_sw128(k_base + ks * 2048, 8192, 1024), idesc_acc, (it | ks) != 0);
-        umma_commit(&kv_empty[kst]);
-        umma_commit(&ds_empty[st]);
+          for (int ks = 0; ks < 8; ++ks) {
+            const uint32_t oa = (ks >> 2) * 16384 + (ks & 3) * 32;
+            const uint32_t ob = (ks >> 2) * 8192 + (ks & 3) * 32;
+            umma_f16_ss(tmem_DP + st * 64, desc_advance(d_do, oa), desc_advance(d_v, ob), idesc_s, ks != 0);
+          }
+        }
+        if (leader) umma_commit(&sdp_full[st]);
+      };
+      auto wait_sdp_inputs = [&](int g) -> bool {
+        return mbar_wait(&kv_full[g % ATB_STAGES], (g / ATB_STAGES) & 1, status, ERR_ATTN_WAIT) &&
+               mbar_wait(&sdp_empty[g & 1], ((g >> 1) & 1) ^ 1, status, ERR_ATTN_WAIT);
+      };
+      int g = 0, n = 0;
+      bool ok = true;
+      // S/dP run one iteration ahead of dQ, also across the item boundary: the first S/dP of the next
+      // item is issued (after its Q/dO landed) before this item's last dQ MMA.
+      bool primed = false;   // S/dP of (this item, iteration 0) already issued
+      for (int w = blockIdx.x; w < n_items && ok; w = snake_next(w), ++n) {
+        const DqItem item = dq_item(w, num_q_tiles, Hq, B, nkv64);
+        const bool has_next = snake_next(w) < n_items;
+        if (!primed) {
+          ok = mbar_wait(q_full, n & 1, status, ERR_ATTN_WAIT) && wait_sdp_inputs(g);
+          if (!ok) break;
+          tc_fence_after();
+          issue_sdp(g);
+          if (item.n_it == 1) if (leader) umma_commit(q_empty);
+        }
+        primed = false;
+        for (int it = 0; it < item.n_it; ++it, ++g) {
+          if (it + 1 < item.n_it) {
+            if (!wait_sdp_inputs(g + 1)) { ok = false; break; }
+            tc_fence_after();
+            issue_sdp(g + 1);
+            if (it + 2 == item.n_it) if (leader) umma_commit(q_empty);   // last S/dP of the item: Q/dO may be reloaded
+          }
+          const int st = g & 1;
+          if (!mbar_wait(&ds_full[st], (g >> 1) & 1, status, ERR_ATTN_WAIT)) { ok = false; break; }
+          tc_fence_after();
+          const int kst = g % ATB_STAGES;
+          const uint64_t d_ds = make_smem_desc_sw128(smem_u32(smem + DqSmem::DS + st * 16384), 16, 1024);
+          const uint64_t d_km = make_smem_desc_sw128(smem_u32(smem + DqSmem::K + kst * 16384), 8192, 1024);
+          const uint32_t acc0 = it != 0;
+          if (leader) {
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)
+              umma_f16_ss(tmem_DQ, desc_advance(d_ds, ks * 32), desc_advance(d_km, ks * 2048), idesc_acc,
+                          ks ? 1u : acc0);
+          }
+          if (leader) umma_commit(&kv_empty[kst]);
+          if (leader) umma_commit(&ds_empty[st]);
+          if (it + 1 == item.n_it) {
+            if (leader) umma_commit(acc_done);
+            if (has_next) {
+              // the next item's Q/dO were requested when q_empty fired; its first S/dP is issued as
+              // soon as they land, while the elementwise warps write this item's dQ out
+              if (!mbar_wait(q_full, (n + 1) & 1, status, ERR_ATTN_WAIT) || !wait_sdp_inputs(g + 1)) {
+                ok = false;
+                break;
+              }
+              tc_fence_after();
+              issue_sdp(g + 1);
+              const DqItem nxt = dq_item(snake_next(w), num_q_tiles, Hq, B, nkv64);
+              if (nxt.n_it == 1) if (leader) umma_commit(q_empty);
+              primed = true;
+            }
+          }
+        }
       }
-      if (ok) umma_commit(acc_done);
     }
   } else {
     const int quarter = warp & 3;
     const int half = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;
-    const int q_pos = qt * 128 + r;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     const float sl2 = scale * LOG2E;
-    const int qc = q_pos < S ? q_pos : S - 1;
-    const float lse_r = lse[static_cast<size_t>(head) * T + batch * S + qc] * LOG2E;
-    const float D_r = Dsum[static_cast<size_t>(head) * T + batch * S + qc];
     bool ok = true;
-    for (int it = 0; it < n_it; ++it) {
-      const int st = it & 1;
-      const uint32_t ph = (it >> 1) & 1;
-      if (!mbar_wait(&sdp_full[st], ph, status, ERR_ATTN_WAIT)) { ok = false; break; }
-      tc_fence_after();
-      uint32_t ts[32], tp[32];
-      tmem_ld_32x32b_x32(tmem_S + lane_off + st * 64 + half * 32, ts);
-      tmem_ld_32x32b_x32(tmem_DP + lane_off + st * 64 + half * 32, tp);
-      tmem_ld_wait();
-      tc_fence_before();
-      mbar_arrive(&sdp_empty[st]);
-      const int k0 = it * 64 + half * 32;
-      const bool need_mask = (k0 + 32 > qt * 128) || (k0 + 32 > S) || (qt * 128 + 128 > S);
-      float dsv[32];
+    int g = 0, n = 0;
+    auto row_stats = [&](const DqItem& item, float* lse_r, float* D_r) {
+      const int q_pos = item.qt * 128 + r;
+      const int qc = q_pos < S ? q_pos : S - 1;
+      const size_t o = static_cast<size_t>(item.head) * T + item.batch * S + qc;
+      *lse_r = lse[o] * LOG2E;
+      *D_r = Dsum[o];
+    };
+    float lse_r = 0.f, D_r = 0.f;
+    if (static_cast<int>(blockIdx.x) < n_items) row_stats(dq_item(blockIdx.x, num_q_tiles, Hq, B, nkv64), &lse_r, &D_r);
+    for (int w = blockIdx.x; w < n_items && ok; w = snake_next(w), ++n) {
+      const DqItem item = dq_item(w, num_q_tiles, Hq, B, nkv64);
+      const int qt = item.qt;
+      const int q_pos = qt * 128 + r;
+      const int row0 = item.batch * S + qt * 128;
+      // next item's row statistics: requested now, consumed after this item's write-out
+      float lse_n = 0.f, D_n = 0.f;
+      if (snake_next(w) < n_items)
+        row_stats(dq_item(snake_next(w), num_q_tiles, Hq, B, nkv64), &lse_n, &D_n);
+      for (int it = 0; it < item.n_it; ++it, ++g) {
+        const int st = g & 1;
+        const uint32_t ph = (g >> 1) & 1;
+        if (!mbar_wait_warp(&sdp_full[st], ph, status, ERR_ATTN_WAIT)) { ok = false; break; }
+        tc_fence_after();
+        uint32_t ts[32], tp[32];
+        tmem_ld_32x32b_x32(tmem_S + lane_off + st * 64 + half * 32, ts);
+        tmem_ld_32x32b_x32(tmem_DP + lane_off + st * 64 + half * 32, tp);
+        tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive_warp(&sdp_empty[st]);
+        const int k0 = it * 64 + half * 32;
+        const bool need_mask = (k0 + 32 > qt * 128) || (k0 + 32 > S) || (qt * 128 + 128 > S);
+        float dsv[32];
 #pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        float p = exp2f(__uint_as_float(ts[c]) * sl2 - lse_r);
-        if (need_mask) {
-          const int kp = k0 + c;
-          if (!((q_pos < S) && (kp <= q_pos) && (kp < S))) p = 0.f;
+        for (int c = 0; c < 32; ++c) {
+          float p = exp2f(__uint_as_float(ts[c]) * sl2 - lse_r);
+          if (need_mask) {
+            const int kp = k0 + c;
+            if (!((q_pos < S) && (kp <= q_pos) && (kp < S))) p = 0.f;
+          }
+          dsv[c] = p * (__uint_as_float(tp[c]) - D_r) * scale;
         }
-        dsv[c] = p * (__uint_as_float(tp[c]) - D_r) * scale;
-      }
-      if (!mbar_wait(&ds_empty[st], ph ^ 1, status, ERR_ATTN_WAIT)) { ok = false; break; }
-      uint8_t* sDS = smem + DqSmem::DS + st * 16384 + r * 128;
+        if (!mbar_wait_warp(&ds_empty[st], ph ^ 1, status, ERR_ATTN_WAIT)) { ok = false; break; }
+        uint8_t* sDS = smem + DqSmem::DS + st * 16384 + r * 128;
 #pragma unroll
-      for (int c4 = 0; c4 < 4; ++c4) {
-        uint4 b;
-        b.x = pack_bf16x2(dsv[c4 * 8 + 0], dsv[c4 * 8 + 1]);
-        b.y = pack_bf16x2(dsv[c4 * 8 + 2], dsv[c4 * 8 + 3]);
-        b.z = pack_bf16x2(dsv[c4 * 8 + 4], dsv[c4 * 8 + 5]);
-        b.w = pack_bf16x2(dsv[c4 * 8 + 6], dsv[c4 * 8 + 7]);
-        *reinterpret_cast<uint4*>(sDS + (((half * 4 + c4) ^ (r & 7)) << 4)) = b;
+        for (int c4 = 0; c4 < 4; ++c4) {
+          uint4 b;
+          b.x = pack_bf16x2(dsv[c4 * 8 + 0], dsv[c4 * 8 + 1]);
+          b.y = pack_bf16x2(dsv[c4 * 8 + 2], dsv[c4 * 8 + 3]);
+          b.z = pack_bf16x2(dsv[c4 * 8 + 4], dsv[c4 * 8 + 5]);
+          b.w = pack_bf16x2(dsv[c4 * 8 + 6], dsv[c4 * 8 + 7]);
+          *reinterpret_cast<uint4*>(sDS + (((half * 4 + c4) ^ (r & 7)) << 4)) = b;
+        }
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive_warp(&ds_full[st]);
       }
-      fence_proxy_async_smem();
-      tc_fence_before();
-      mbar_arrive(&ds_full[st]);
-    }
-    if (ok && mbar_wait(acc_done, 0, status, ERR_ATTN_WAIT)) {
+      if (!ok || !mbar_wait_warp(acc_done, n & 1, status, ERR_ATTN_WAIT)) { ok = false; break; }
       tc_fence_after();
+      // write-out; the next item's first dQ MMA is ordered after it by this warp's next ds_full arrive
       const bool in_range = q_pos < S;
-      __nv_bfloat16* orow = dq + (static_cast<size_t>(row0 + r) * Hq + head) * 128 + half * 64;
+      __nv_bfloat16* orow = dq + (static_cast<size_t>(row0 + r) * Hq + item.head) * 128 + half * 64;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t t[32];
@@ -543,6 +700,9 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           }
         }
       }
+      tc_fence_before();
+      lse_r = lse_n;
+      D_r = D_n;
     }
   }
 
@@ -609,11 +769,13 @@ B2_EXPORT int b2_attn_bwd(const void* q, const void* k, const void* v, const voi
         static_cast<long long>(T), Hq);
   }
   const int nt = (S + 127) / 128;
-  attn_bwd_dkdv_kernel<<<dim3(nt, Hkv, B), ATB_THREADS, DkDvSmem::TOTAL, stream>>>(
+  const int dkdv_items = nt * Hkv * B;
+  attn_bwd_dkdv_kernel<<<dkdv_items < num_sms() ? dkdv_items : num_sms(), ATB_THREADS, DkDvSmem::TOTAL, stream>>>(
       *tq64, *tdo64, *tk128, *tv128, lse, Dsum, static_cast<__nv_bfloat16*>(dk),
-      static_cast<__nv_bfloat16*>(dv), ld_dk, ld_dv, S, Hq, Hkv, scale, status);
-  attn_bwd_dq_kernel<<<dim3(nt, Hq, B), ATB_THREADS, DqSmem::TOTAL, stream>>>(
-      *tq128, *tdo128, *tk64, *tv64, lse, Dsum, static_cast<__nv_bfloat16*>(dq), S, Hq, Hkv, scale, status);
+      static_cast<__nv_bfloat16*>(dv), ld_dk, ld_dv, B, S, Hq, Hkv, scale, status);
+  const int dq_items = nt * Hq * B;
+  attn_bwd_dq_kernel<<<dq_items < num_sms() ? dq_items : num_sms(), ATB_THREADS, DqSmem::TOTAL, stream>>>(
+      *tq128, *tdo128, *tk64, *tv64, lse, Dsum, static_cast<__nv_bfloat16*>(dq), B, S, Hq, Hkv, scale, status);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_error("attn_bwd launch failed: %s", cudaGetErrorString(e));

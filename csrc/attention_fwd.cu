@@ -1,6 +1,7 @@
 // Causal flash-attention forward for sm_100a (head_dim 128, GQA), tcgen05 MMAs with S and O in TMEM.
 //
-// One CTA handles one 128-row query tile of one (batch, q-head).  Warp 0 streams K/V tiles with TMA
+// A work item is one 128-row query tile of one (batch, q-head); a persistent CTA per SM walks the
+// items.  Warp 0 streams K/V tiles with TMA
 // (two stages each), warp 1 issues the MMAs, warps 2..5 (128 threads, one query row each) run the
 // online softmax: they read S from TMEM, write P (bf16) to shared memory in the 128-byte-swizzled
 // K-major layout the PV MMA consumes, and rescale the O accumulator in TMEM only when the running
@@ -29,11 +30,55 @@ struct AttnFwdSmem {
   static constexpr int TOTAL = BARS + 256 + 1024;
 };
 
+// One work item: a 128-row query tile of one (batch, q head).
+struct FwdItem {
+  int head, kvh, qt, q_len, kv_len, kv_off, k_begin, row0, n_kv;
+  bool active;
+};
+struct FwdParams {
+  int S, Hq, Hkv, B, max_tiles, total_q;
+  const int* cu_q;
+  const int* cu_k;
+};
+// Fixed-length mode (cu_q == nullptr): every sequence has S query and S key tokens.  Variable
+// length mode: sequence b owns query rows cu_q[b]..cu_q[b+1] and key rows cu_k[b]..cu_k[b+1]; its
+// queries are the LAST q_len positions of its kv_len keys (chunked prefill / speculative verify), so
+// query i sees keys 0..(kv_len - q_len + i).
+__device__ __forceinline__ FwdItem fwd_item(int w, const FwdParams& p) {
+  FwdItem it;
+  const int hb = w % (p.Hq * p.B);
+  const int x = w / (p.Hq * p.B);   // tile rank counted from the last (heaviest) tile
+  it.head = hb % p.Hq;
+  const int batch = hb / p.Hq;
+  const int q_begin = p.cu_q ? p.cu_q[batch] : batch * p.S;
+  it.q_len = p.cu_q ? p.cu_q[batch + 1] - q_begin : p.S;
+  it.k_begin = p.cu_k ? p.cu_k[batch] : batch * p.S;
+  it.kv_len = p.cu_k ? p.cu_k[batch + 1] - it.k_begin : p.S;
+  it.kv_off = it.kv_len - it.q_len;
+  const int num_q_tiles = (it.q_len + 127) / 128;
+  it.qt = num_q_tiles - 1 - x;
+  it.active = it.qt >= 0 && it.q_len > 0;
+  it.kvh = it.head / (p.Hq / p.Hkv);
+  const int last_key = min(it.kv_len, it.kv_off + (it.qt + 1) * 128);  // exclusive
+  it.n_kv = it.active ? (last_key + 127) / 128 : 0;
+  it.active = it.active && it.n_kv > 0;
+  it.row0 = q_begin + it.qt * 128;
+  return it;
+}
+__device__ __forceinline__ int fwd_next_active(int w, int n_items, const FwdParams& p) {
+  int x = snake_next(w);
+  while (x < n_items && !fwd_item(x, p).active) x = snake_next(x);
+  return x;
+}
+
+// Persistent: each CTA walks its share of the items (heaviest tiles first, dealt in boustrophedon order).  Barriers, TMEM and
+// the K/V ring live across items; the next item's Q is requested as soon as the last Q*K^T of the
+// current item retires, and its first Q*K^T is issued while the softmax warps write the current
+// item's output.
 __global__ void __launch_bounds__(AT_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, __nv_bfloat16* __restrict__ out,
-                float* __restrict__ lse_out, int S, int Hq, int Hkv, float scale,
-                const int* __restrict__ cu_q, const int* __restrict__ cu_k, int total_q, int* status) {
+                float* __restrict__ lse_out, const FwdParams prm, float scale, int* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -47,38 +92,25 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* s_empty = bars + 11;  // [2]
   uint64_t* p_full = bars + 13;
   uint64_t* pv_done = bars + 14;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  uint64_t* q_empty = bars + 15;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // Fixed-length mode (cu_q == nullptr): every sequence has S query and S key tokens.  Variable
-  // length mode: sequence b owns query rows cu_q[b]..cu_q[b+1] and key rows cu_k[b]..cu_k[b+1]; its
-  // queries are the LAST q_len positions of its kv_len keys (chunked prefill / speculative verify), so
-  // query i sees keys 0..(kv_len - q_len + i).
-  const int head = blockIdx.y, batch = blockIdx.z;
-  const int q_begin = cu_q ? cu_q[batch] : batch * S;
-  const int q_len = cu_q ? cu_q[batch + 1] - q_begin : S;
-  const int k_begin = cu_k ? cu_k[batch] : batch * S;
-  const int kv_len = cu_k ? cu_k[batch + 1] - k_begin : S;
-  const int kv_off = kv_len - q_len;
-  const int num_q_tiles = (q_len + 127) / 128;
-  const int qt = num_q_tiles - 1 - static_cast<int>(blockIdx.x);  // heaviest tiles first
-  const bool active = qt >= 0 && q_len > 0;
-  const int kvh = head / (Hq / Hkv);
-  const int last_key = min(kv_len, kv_off + (qt + 1) * 128);  // exclusive
-  const int n_kv = active ? (last_key + 127) / 128 : 0;
-  const int row0 = q_begin + qt * 128;
+  const int Hq = prm.Hq;
+  const int n_items = prm.max_tiles * prm.Hq * prm.B;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
+    mbar_init(q_empty, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1);
       mbar_init(&v_full[i], 1);
       mbar_init(&k_empty[i], 1);
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 128);
+      mbar_init(&s_empty[i], 4);   // one arrive per softmax warp
     }
-    mbar_init(p_full, 128);
+    mbar_init(p_full, 4);
     mbar_init(pv_done, 1);
     mbar_fence_init();
     tma_prefetch_desc(&tmQ);
@@ -96,168 +128,209 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const uint32_t tmem_S = tmem_base;        // 2 x 128 columns
   const uint32_t tmem_O = tmem_base + 256;  // 128 columns
 
+  int w0 = blockIdx.x;
+  if (w0 < n_items && !fwd_item(w0, prm).active) w0 = fwd_next_active(w0, n_items, prm);
+
   if (warp == 0) {
-    if (lane == 0 && active) {
-      mbar_expect_tx(q_full, AT_TILE_BYTES);
-      tma_load_2d(smem + AttnFwdSmem::Q, &tmQ, q_full, head * 128, row0);
-      tma_load_2d(smem + AttnFwdSmem::Q + AT_HALF_BYTES, &tmQ, q_full, head * 128 + 64, row0);
-      for (int j = 0; j < n_kv; ++j) {
-        const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        const int krow = k_begin + j * 128;
-        if (!mbar_wait(&k_empty[st], ph ^ 1, status, ERR_ATTN_WAIT)) break;
-        uint8_t* sK = smem + AttnFwdSmem::K + st * AT_TILE_BYTES;
-        mbar_expect_tx(&k_full[st], AT_TILE_BYTES);
-        tma_load_2d(sK, &tmK, &k_full[st], kvh * 128, krow);
-        tma_load_2d(sK + AT_HALF_BYTES, &tmK, &k_full[st], kvh * 128 + 64, krow);
-        if (!mbar_wait(&v_empty[st], ph ^ 1, status, ERR_ATTN_WAIT)) break;
-        uint8_t* sV = smem + AttnFwdSmem::V + st * AT_TILE_BYTES;
-        mbar_expect_tx(&v_full[st], AT_TILE_BYTES);
-        tma_load_2d(sV, &tmV, &v_full[st], kvh * 128, krow);
-        tma_load_2d(sV + AT_HALF_BYTES, &tmV, &v_full[st], kvh * 128 + 64, krow);
+    if (lane == 0) {
+      int g = 0, n = 0;
+      bool ok = true;
+      for (int w = w0; w < n_items && ok; w = fwd_next_active(w, n_items, prm), ++n) {
+        const FwdItem item = fwd_item(w, prm);
+        if (!mbar_wait(q_empty, (n & 1) ^ 1, status, ERR_ATTN_WAIT)) break;
+        mbar_expect_tx(q_full, AT_TILE_BYTES);
+        tma_load_2d(smem + AttnFwdSmem::Q, &tmQ, q_full, item.head * 128, item.row0);
+        tma_load_2d(smem + AttnFwdSmem::Q + AT_HALF_BYTES, &tmQ, q_full, item.head * 128 + 64, item.row0);
+        for (int j = 0; j < item.n_kv; ++j, ++g) {
+          const int st = g & 1;
+          const uint32_t ph = (g >> 1) & 1;
+          const int krow = item.k_begin + j * 128;
+          if (!mbar_wait(&k_empty[st], ph ^ 1, status, ERR_ATTN_WAIT)) { ok = false; break; }
+          uint8_t* sK = smem + AttnFwdSmem::K + st * AT_TILE_BYTES;
+          mbar_expect_tx(&k_full[st], AT_TILE_BYTES);
+          tma_load_2d(sK, &tmK, &k_full[st], item.kvh * 128, krow);
+          tma_load_2d(sK + AT_HALF_BYTES, &tmK, &k_full[st], item.kvh * 128 + 64, krow);
+          if (!mbar_wait(&v_empty[st], ph ^ 1, status, ERR_ATTN_WAIT)) { ok = false; break; }
+          uint8_t* sV = smem + AttnFwdSmem::V + st * AT_TILE_BYTES;
+          mbar_expect_tx(&v_full[st], AT_TILE_BYTES);
+          tma_load_2d(sV, &tmV, &v_full[st], item.kvh * 128, krow);
+          tma_load_2d(sV + AT_HALF_BYTES, &tmV, &v_full[st], item.kvh * 128 + 64, krow);
+        }
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && active) {
+    // The whole warp runs this (uniform) control flow so that descriptors and addresses stay in the
+    // uniform datapath; only the tcgen05 instructions themselves are issued by one elected lane.
+    {
+      const bool leader = elect_one();
       constexpr uint32_t idesc_s = make_idesc_f16(1, 128, 128, 0, 0);
       constexpr uint32_t idesc_pv = make_idesc_f16(1, 128, 128, 0, 1);
-      const uint32_t q_base = smem_u32(smem + AttnFwdSmem::Q);
-      const uint32_t p_base = smem_u32(smem + AttnFwdSmem::P);
-      auto issue_s = [&](int j) {
-        const uint32_t k_base = smem_u32(smem + AttnFwdSmem::K + (j & 1) * AT_TILE_BYTES);
+      const uint64_t d_q = make_smem_desc_sw128(smem_u32(smem + AttnFwdSmem::Q), 16, 1024);
+      const uint64_t d_p = make_smem_desc_sw128(smem_u32(smem + AttnFwdSmem::P), 16, 1024);
+      // Q*K^T of global iteration g: K stage g & 1, S buffer g & 1
+      auto issue_s = [&](int g) {
+        const uint64_t d_k = make_smem_desc_sw128(smem_u32(smem + AttnFwdSmem::K + (g & 1) * AT_TILE_BYTES), 16, 1024);
+        if (leader) {
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t o = (ks >> 2) * AT_HALF_BYTES + (ks & 3) * 32;
-          umma_f16_ss(tmem_S + (j & 1) * 128, make_smem_desc_sw128(q_base + o, 16, 1024),
-                      make_smem_desc_sw128(k_base + o, 16, 1024), idesc_s, ks != 0);
+          for (int ks = 0; ks < 8; ++ks) {
+            const uint32_t o = (ks >> 2) * AT_HALF_BYTES + (ks & 3) * 32;
+            umma_f16_ss(tmem_S + (g & 1) * 128, desc_advance(d_q, o), desc_advance(d_k, o), idesc_s, ks != 0);
+          }
         }
-        umma_commit(&k_empty[j & 1]);
-        umma_commit(&s_full[j & 1]);
+        if (leader) umma_commit(&k_empty[g & 1]);
+        if (leader) umma_commit(&s_full[g & 1]);
       };
-      bool ok = mbar_wait(q_full, 0, status, ERR_ATTN_WAIT) &&
-                mbar_wait(&k_full[0], 0, status, ERR_ATTN_WAIT);
-      if (ok) {
-        tc_fence_after();
-        issue_s(0);
-      }
-      for (int j = 0; j < n_kv && ok; ++j) {
-        if (j + 1 < n_kv) {
-          const int st = (j + 1) & 1;
-          const uint32_t ph = ((j + 1) >> 1) & 1;
-          if (!mbar_wait(&k_full[st], ph, status, ERR_ATTN_WAIT) ||
-              !mbar_wait(&s_empty[st], ph ^ 1, status, ERR_ATTN_WAIT)) {
+      auto wait_s_inputs = [&](int g) -> bool {
+        return mbar_wait(&k_full[g & 1], (g >> 1) & 1, status, ERR_ATTN_WAIT) &&
+               mbar_wait(&s_empty[g & 1], ((g >> 1) & 1) ^ 1, status, ERR_ATTN_WAIT);
+      };
+      int g = 0, n = 0;
+      bool ok = true, primed = false;
+      for (int w = w0; w < n_items && ok; ++n) {
+        const FwdItem item = fwd_item(w, prm);
+        const int w_next = fwd_next_active(w, n_items, prm);
+        if (!primed) {
+          ok = mbar_wait(q_full, n & 1, status, ERR_ATTN_WAIT) && wait_s_inputs(g);
+          if (!ok) break;
+          tc_fence_after();
+          issue_s(g);
+          if (item.n_kv == 1) if (leader) umma_commit(q_empty);
+        }
+        primed = false;
+        for (int j = 0; j < item.n_kv; ++j, ++g) {
+          if (j + 1 < item.n_kv) {
+            if (!wait_s_inputs(g + 1)) { ok = false; break; }
+            tc_fence_after();
+            issue_s(g + 1);
+            if (j + 2 == item.n_kv) if (leader) umma_commit(q_empty);   // last Q*K^T of the item: Q may be reloaded
+          }
+          if (!mbar_wait(p_full, g & 1, status, ERR_ATTN_WAIT) ||
+              !mbar_wait(&v_full[g & 1], (g >> 1) & 1, status, ERR_ATTN_WAIT)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          issue_s(j + 1);
-        }
-        if (!mbar_wait(p_full, j & 1, status, ERR_ATTN_WAIT) ||
-            !mbar_wait(&v_full[j & 1], (j >> 1) & 1, status, ERR_ATTN_WAIT)) {
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        const uint32_t v_base = smem_u32(smem + AttnFwdSmem::V + (j & 1) * AT_TILE_BYTES);
+          const uint64_t d_v = make_smem_desc_sw128(smem_u32(smem + AttnFwdSmem::V + (g & 1) * AT_TILE_BYTES),
+                                                    AT_HALF_BYTES, 1024);
+          const uint32_t acc0 = j != 0;
+          if (leader) {
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-          const uint32_t o = (ks >> 2) * AT_HALF_BYTES + (ks & 3) * 32;
-          umma_f16_ss(tmem_O, make_smem_desc_sw128(p_base + o, 16, 1024),
-                      make_smem_desc_sw128(v_base + ks * 2048, AT_HALF_BYTES, 1024), idesc_pv,
-                      (j | ks) != 0);
+            for (int ks = 0; ks < 8; ++ks) {
+              const uint32_t o = (ks >> 2) * AT_HALF_BYTES + (ks & 3) * 32;
+              umma_f16_ss(tmem_O, desc_advance(d_p, o), desc_advance(d_v, ks * 2048), idesc_pv, ks ? 1u : acc0);
+            }
+          }
+          if (leader) umma_commit(&v_empty[g & 1]);
+          if (leader) umma_commit(pv_done);
+          if (j + 1 == item.n_kv && w_next < n_items) {
+            if (!mbar_wait(q_full, (n + 1) & 1, status, ERR_ATTN_WAIT) || !wait_s_inputs(g + 1)) {
+              ok = false;
+              break;
+            }
+            tc_fence_after();
+            issue_s(g + 1);
+            if (fwd_item(w_next, prm).n_kv == 1) if (leader) umma_commit(q_empty);
+            primed = true;
+          }
         }
-        umma_commit(&v_empty[j & 1]);
-        umma_commit(pv_done);
+        w = w_next;
       }
     }
   } else {
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;        // query row inside the tile
-    const int q_idx = qt * 128 + r;           // index among this sequence's queries
-    const int q_pos = kv_off + q_idx;         // last key this query may see
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     const float sl2 = scale * 1.4426950408889634f;
-    float m_used = -INFINITY, l = 0.f;
     uint8_t* sP = smem + AttnFwdSmem::P;
     bool ok = true;
-    for (int j = 0; j < n_kv; ++j) {
-      if (!mbar_wait(&s_full[j & 1], (j >> 1) & 1, status, ERR_ATTN_WAIT)) { ok = false; break; }
-      tc_fence_after();
-      float s[128];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t t[32];
-        tmem_ld_32x32b_x32(tmem_S + lane_off + (j & 1) * 128 + c * 32, t);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(t[i]);
-      }
-      tc_fence_before();
-      mbar_arrive(&s_empty[j & 1]);
-      const bool need_mask = ((j + 1) * 128 > kv_off + qt * 128 + 1) || ((j + 1) * 128 > kv_len);
-      if (need_mask) {
-        const int col0 = j * 128;
-#pragma unroll
-        for (int i = 0; i < 128; ++i)
-          if (col0 + i > q_pos || col0 + i >= kv_len) s[i] = -INFINITY;
-      }
-      float mx = s[0];
-#pragma unroll
-      for (int i = 1; i < 128; ++i) mx = fmaxf(mx, s[i]);
-      const float m_new = fmaxf(m_used, mx);
-      if (j > 0) {
-        // previous PV must be complete before P is overwritten or O is rescaled
-        if (!mbar_wait(pv_done, (j - 1) & 1, status, ERR_ATTN_WAIT)) { ok = false; break; }
+    int g = 0;
+    for (int w = w0; w < n_items && ok; w = fwd_next_active(w, n_items, prm)) {
+      const FwdItem item = fwd_item(w, prm);
+      const int q_idx = item.qt * 128 + r;      // index among this sequence's queries
+      const int q_pos = item.kv_off + q_idx;    // last key this query may see
+      float m_used = -INFINITY, l = 0.f;
+      for (int j = 0; j < item.n_kv; ++j, ++g) {
+        if (!mbar_wait_warp(&s_full[g & 1], (g >> 1) & 1, status, ERR_ATTN_WAIT)) { ok = false; break; }
         tc_fence_after();
-        const bool need = (m_new - m_used) * sl2 > 8.f;
-        if (__any_sync(0xffffffffu, need)) {
-          const float alpha = need ? exp2f((m_used - m_new) * sl2) : 1.f;
+        float s[128];
 #pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            uint32_t t[16];
-            tmem_ld_32x32b_x16(tmem_O + lane_off + c * 16, t);
-            tmem_ld_wait();
+        for (int c = 0; c < 4; ++c) {
+          uint32_t t[32];
+          tmem_ld_32x32b_x32(tmem_S + lane_off + (g & 1) * 128 + c * 32, t);
+          tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 16; ++i) t[i] = __float_as_uint(__uint_as_float(t[i]) * alpha);
-            tmem_st_32x32b_x16(tmem_O + lane_off + c * 16, t);
-          }
-          tmem_st_wait();
-          if (need) {
-            l *= alpha;
-            m_used = m_new;
-          }
+          for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(t[i]);
         }
-      } else {
-        m_used = m_new;
-      }
-      const float mb = m_used * sl2;
-      float rs = 0.f;
+        tc_fence_before();
+        mbar_arrive_warp(&s_empty[g & 1]);
+        const bool need_mask = ((j + 1) * 128 > item.kv_off + item.qt * 128 + 1) || ((j + 1) * 128 > item.kv_len);
+        if (need_mask) {
+          const int col0 = j * 128;
 #pragma unroll
-      for (int c8 = 0; c8 < 16; ++c8) {
-        float p[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          p[i] = exp2f(s[c8 * 8 + i] * sl2 - mb);
-          rs += p[i];
+          for (int i = 0; i < 128; ++i)
+            if (col0 + i > q_pos || col0 + i >= item.kv_len) s[i] = -INFINITY;
         }
-        uint4 o;
-        o.x = pack_bf16x2(p[0], p[1]);
-        o.y = pack_bf16x2(p[2], p[3]);
-        o.z = pack_bf16x2(p[4], p[5]);
-        o.w = pack_bf16x2(p[6], p[7]);
-        const int sub = c8 >> 3, cc = c8 & 7;
-        *reinterpret_cast<uint4*>(sP + sub * AT_HALF_BYTES + r * 128 + ((cc ^ (r & 7)) << 4)) = o;
+        float mx = s[0];
+#pragma unroll
+        for (int i = 1; i < 128; ++i) mx = fmaxf(mx, s[i]);
+        const float m_new = fmaxf(m_used, mx);
+        if (g > 0) {
+          // the previous PV (of this or the previous item) must be complete before P is overwritten
+          // or O is rescaled
+          if (!mbar_wait_warp(pv_done, (g - 1) & 1, status, ERR_ATTN_WAIT)) { ok = false; break; }
+          tc_fence_after();
+        }
+        if (j > 0) {
+          const bool need = (m_new - m_used) * sl2 > 8.f;
+          if (__any_sync(0xffffffffu, need)) {
+            const float alpha = need ? exp2f((m_used - m_new) * sl2) : 1.f;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              uint32_t t[16];
+              tmem_ld_32x32b_x16(tmem_O + lane_off + c * 16, t);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 16; ++i) t[i] = __float_as_uint(__uint_as_float(t[i]) * alpha);
+              tmem_st_32x32b_x16(tmem_O + lane_off + c * 16, t);
+            }
+            tmem_st_wait();
+            if (need) {
+              l *= alpha;
+              m_used = m_new;
+            }
+          }
+        } else {
+          m_used = m_new;
+        }
+        const float mb = m_used * sl2;
+        float rs = 0.f;
+#pragma unroll
+        for (int c8 = 0; c8 < 16; ++c8) {
+          float p[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            p[i] = exp2f(s[c8 * 8 + i] * sl2 - mb);
+            rs += p[i];
+          }
+          uint4 o;
+          o.x = pack_bf16x2(p[0], p[1]);
+          o.y = pack_bf16x2(p[2], p[3]);
+          o.z = pack_bf16x2(p[4], p[5]);
+          o.w = pack_bf16x2(p[6], p[7]);
+          const int sub = c8 >> 3, cc = c8 & 7;
+          *reinterpret_cast<uint4*>(sP + sub * AT_HALF_BYTES + r * 128 + ((cc ^ (r & 7)) << 4)) = o;
+        }
+        l += rs;
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive_warp(p_full);
       }
-      l += rs;
-      fence_proxy_async_smem();
-      tc_fence_before();
-      mbar_arrive(p_full);
-    }
-    if (ok && active && mbar_wait(pv_done, (n_kv - 1) & 1, status, ERR_ATTN_WAIT)) {
+      if (!ok || !mbar_wait_warp(pv_done, (g - 1) & 1, status, ERR_ATTN_WAIT)) { ok = false; break; }
       tc_fence_after();
+      // write-out; the next item's first PV is ordered after it by this warp's next p_full arrive
       const float inv = 1.f / l;
-      const bool in_range = q_idx < q_len;
-      __nv_bfloat16* orow = out + (static_cast<size_t>(row0 + r) * Hq + head) * 128;
+      const bool in_range = q_idx < item.q_len;
+      __nv_bfloat16* orow = out + (static_cast<size_t>(item.row0 + r) * Hq + item.head) * 128;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t t[32];
@@ -275,8 +348,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           }
         }
       }
+      tc_fence_before();
       if (in_range && lse_out)
-        lse_out[static_cast<size_t>(head) * total_q + row0 + r] = m_used * scale + __logf(l);
+        lse_out[static_cast<size_t>(item.head) * prm.total_q + item.row0 + r] = m_used * scale + __logf(l);
     }
   }
 
@@ -339,9 +413,13 @@ B2_EXPORT int b2_attn_fwd_varlen(const void* q, const void* k, const void* v, vo
   if (!tq || !tk || !tv) return 2;
   int* status = status_ptr();
   if (!status) return 3;
-  dim3 grid((max_q + 127) / 128, Hq, B);
+  FwdParams prm;
+  prm.S = S; prm.Hq = Hq; prm.Hkv = Hkv; prm.B = B; prm.max_tiles = (max_q + 127) / 128; prm.total_q = total_q;
+  prm.cu_q = cu_q; prm.cu_k = cu_k;
+  const long long n_items = static_cast<long long>(prm.max_tiles) * Hq * B;
+  const int grid = n_items < num_sms() ? static_cast<int>(n_items) : num_sms();
   attn_fwd_kernel<<<grid, AT_THREADS, AttnFwdSmem::TOTAL, stream>>>(
-      *tq, *tk, *tv, static_cast<__nv_bfloat16*>(out), lse, S, Hq, Hkv, scale, cu_q, cu_k, total_q, status);
+      *tq, *tk, *tv, static_cast<__nv_bfloat16*>(out), lse, prm, scale, status);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_error("attn_fwd launch failed: %s", cudaGetErrorString(e));

@@ -78,13 +78,36 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking probe of the phase (test_wait never suspends the thread).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Bounded wait.  Returns false (and records `code`) after WAIT_LIMIT_NS, or as soon as another
 // role of the same grid has already recorded an error.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
+#ifdef B2_MBAR_SPIN
+  if (mbar_test_wait(bar, parity)) return true;
+#else
   if (mbar_try_wait(bar, parity)) return true;
+#endif
   unsigned long long t0 = 0;
   for (uint32_t it = 1;; ++it) {
+#ifdef B2_MBAR_SPIN
+    if (mbar_test_wait(bar, parity)) return true;
+#else
     if (mbar_try_wait(bar, parity)) return true;
+#endif
     if ((it & 255u) == 0) {
       unsigned long long now = globaltimer_ns();
       if (t0 == 0) t0 = now;
@@ -95,6 +118,31 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
       }
     }
   }
+}
+
+// Warp-level forms: one lane polls / arrives for the whole warp.  An mbarrier arrive is a
+// shared-memory atomic; with one arrive per thread, 128..256 of them serialise on one word every
+// pipeline step, which costs more than the step's math in the attention kernels.  Barriers used
+// with these helpers are initialised with the number of WARPS that arrive.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, int* status, int code) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, status, code) ? 1 : 0;
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  __syncwarp();  // orders the other lanes after lane 0's acquire
+  return ok != 0;
+}
+// Every lane must have issued its own fences (proxy / tcgen05) for the data it produced or consumed.
+__device__ __forceinline__ void mbar_arrive_warp(uint64_t* bar) {
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+}
+
+// Persistent kernels deal their work items (sorted heaviest first) to the CTAs in boustrophedon
+// order: CTA c takes positions c, 2G-1-c, 2G+c, 4G-1-c, ... (G = gridDim.x), so a CTA that got a heavy
+// item in one row gets a light one in the next and the per-CTA totals stay close.
+__device__ __forceinline__ int snake_next(int w) {
+  const int G = static_cast<int>(gridDim.x);
+  return (w / G + 1) * G + (G - 1 - w % G);
 }
 
 // ---- TMA ---------------------------------------------------------------------------------------
@@ -268,6 +316,9 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uin
   d |= 2ull << 61;
   return d;
 }
+// Same descriptor `bytes` further into the tile (bytes % 16 == 0; the 14-bit address field cannot
+// carry for offsets inside one CTA's shared memory).
+__device__ __forceinline__ uint64_t desc_advance(uint64_t d, uint32_t bytes) { return d + (bytes >> 4); }
 // Instruction descriptor for kind::f16 with bf16 (fmt=1) or fp16 (fmt=0) inputs and fp32 accumulate.
 //   a_mn / b_mn: 1 when that operand's contraction dimension is NOT the contiguous one in smem.
 __host__ __device__ constexpr uint32_t make_idesc_f16(uint32_t fmt, uint32_t M, uint32_t N,

@@ -5,7 +5,7 @@ import torch
 
 from b200fw.infer import (BlockPool, ContinuousBatchingScheduler, InferenceConfig, InferenceEngine, KVCacheManager,
                           PrefixCache, RadixAttentionCache, Request, verify_greedy, verify_sampling)
-from b200fw.model import ModelConfig, ParallelTransformerModel
+from b200fw.model import PRESETS, ModelConfig, ParallelTransformerModel
 
 MC = ModelConfig(vocab_size=128, hidden_size=32, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=8,
                  intermediate_size=48, max_position_embeddings=256, tie_word_embeddings=True)
@@ -179,3 +179,30 @@ def test_speculative_verification_rules():
     wrong[:, 0] = 1.0
     n, nxt = verify_sampling(torch.tensor([0, 0, 0]), wrong, logits, 1.0, g)     # p_t(0) ~ 0: reject at once
     assert n == 0 and nxt == 3
+    # batched forms agree with the per-sequence rules
+    from b200fw.infer.spec import verify_greedy_batch, verify_sampling_batch
+    drafts = torch.tensor([[3, 4, 5], [3, 4, 7], [9, 4, 7]])
+    nb, tb = verify_greedy_batch(drafts, logits[None].repeat(3, 1, 1))
+    assert nb.tolist() == [2, 3, 0] and tb.tolist() == [7, 1, 3]
+    dp = torch.stack([probs, wrong])
+    nb, tb = verify_sampling_batch(torch.tensor([[3, 4, 7], [0, 0, 0]]), dp, logits[None].repeat(2, 1, 1), 1.0, g)
+    assert nb.tolist() == [3, 0] and tb[1] == 3 and 0 <= int(tb[0]) < 10
+
+
+def test_requests_with_a_shared_prefix_wait_for_the_first_prefill_and_share_its_blocks():
+    cfg = PRESETS["tiny"]
+    torch.manual_seed(0)
+    m = ParallelTransformerModel(cfg)
+    m.init_weights(1)
+    e = InferenceEngine(InferenceConfig(inference_mode="kv_cache", block_size=16, num_blocks=128, use_radix_cache=True,
+                                        max_num_batched_tokens=512, max_prefill_tokens=512, dtype="float32"), model=m)
+    e.initialize()
+    g = torch.Generator().manual_seed(3)
+    shared = torch.randint(3, cfg.vocab_size, (48,), generator=g).tolist()
+    prompts = [shared + torch.randint(3, cfg.vocab_size, (5 + i,), generator=g).tolist() for i in range(4)]
+    outs = e.generate(prompts, max_tokens=6, temperature=0.0)
+    assert e.stats["cached_prefix_tokens"] == 3 * 48          # three of the four reused the 48-token prefix
+    ref = InferenceEngine(InferenceConfig(inference_mode="kv_cache", block_size=16, num_blocks=128,
+                                          enable_prefix_reuse=False, dtype="float32"), model=m).initialize()
+    assert ref.generate(prompts, max_tokens=6, temperature=0.0) == outs
+    assert not e._inflight_prefix
