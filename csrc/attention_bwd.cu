@@ -95,7 +95,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_con
   uint64_t* kv_empty = bars + 16;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
   float* s_lse = reinterpret_cast<float*>(bars + 18);   // [2][64], pre-multiplied by log2(e)
-  float* s_D = s_lse + 128;                             // [2][64]
+  float* s_D = s_lse + 128;                             // [2][64], pre-multiplied by the softmax scale
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = Hq / Hkv;
@@ -281,7 +281,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_con
       const int q0_ = (item.i_begin + it % item.per_head) * 64;
       const int qc = min(q0_ + (etid & 63), S - 1);
       const size_t o = static_cast<size_t>(head_) * T + item.batch * S + qc;
-      return etid < 64 ? lse[o] * LOG2E : Dsum[o];
+      return etid < 64 ? lse[o] * LOG2E : Dsum[o] * scale;
     };
     auto stat_store = [&](int g_, float v) {
       if (etid < 64) s_lse[(g_ & 1) * 64 + etid] = v;
@@ -334,13 +334,13 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_con
         float pv[32], dsv[32];
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
-          float p = exp2f(__uint_as_float(ts[c]) * sl2 - lse_s[c]);
+          float p = fast_exp2(fmaf(__uint_as_float(ts[c]), sl2, -lse_s[c]));
           if (need_mask) {
             const int qp = qb + c;
             if (!((qp < S) && (kv_pos <= qp) && (kv_pos < S))) p = 0.f;
           }
           pv[c] = p;
-          dsv[c] = p * (__uint_as_float(tp[c]) - D_s[c]) * scale;
+          dsv[c] = p * fmaf(__uint_as_float(tp[c]), scale, -D_s[c]);   // D_s holds D * scale
         }
         stat_store(g + 1, next_stat);   // slot (g+1)&1 was last read in iteration g-1
         ok = mbar_wait_warp(&pds_empty[st], ph ^ 1, status, ERR_ATTN_WAIT);
@@ -627,7 +627,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       const int qc = q_pos < S ? q_pos : S - 1;
       const size_t o = static_cast<size_t>(item.head) * T + item.batch * S + qc;
       *lse_r = lse[o] * LOG2E;
-      *D_r = Dsum[o];
+      *D_r = Dsum[o] * scale;
     };
     float lse_r = 0.f, D_r = 0.f;
     if (static_cast<int>(blockIdx.x) < n_items) row_stats(dq_item(blockIdx.x, num_q_tiles, Hq, B, nkv64), &lse_r, &D_r);
@@ -656,12 +656,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         float dsv[32];
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
-          float p = exp2f(__uint_as_float(ts[c]) * sl2 - lse_r);
+          float p = fast_exp2(fmaf(__uint_as_float(ts[c]), sl2, -lse_r));
           if (need_mask) {
             const int kp = k0 + c;
             if (!((q_pos < S) && (kp <= q_pos) && (kp < S))) p = 0.f;
           }
-          dsv[c] = p * (__uint_as_float(tp[c]) - D_r) * scale;
+          dsv[c] = p * fmaf(__uint_as_float(tp[c]), scale, -D_r);   // D_r holds D * scale
         }
         if (!mbar_wait_warp(&ds_empty[st], ph ^ 1, status, ERR_ATTN_WAIT)) { ok = false; break; }
         uint8_t* sDS = smem + DqSmem::DS + st * 16384 + r * 128;

@@ -309,7 +309,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           float p[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            p[i] = exp2f(s[c8 * 8 + i] * sl2 - mb);
+            p[i] = fast_exp2(fmaf(s[c8 * 8 + i], sl2, -mb));
             rs += p[i];
           }
           uint4 o;

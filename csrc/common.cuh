@@ -328,6 +328,13 @@ __host__ __device__ constexpr uint32_t make_idesc_f16(uint32_t fmt, uint32_t M, 
 }
 
 // ---- small numeric helpers -----------------------------------------------------------------
+// 2^x on the special-function unit, one instruction (exp2f adds range handling around the same
+// instruction; softmax arguments are <= 0 and -inf maps to 0, so none of it is needed).
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);

@@ -274,7 +274,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    // The whole warp runs this (uniform) control flow so that descriptors and addresses stay in the
+    // uniform datapath; only the tcgen05 instructions themselves are issued by one elected lane.
+    {
+      const bool leader = elect_one();
       constexpr uint32_t idesc = make_idesc_f16(1, GEMM_BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;
@@ -290,22 +293,23 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           tc_fence_after();
           const uint32_t a_base = smem_u32(smem + stage * Cfg::STAGE_BYTES);
           const uint32_t b_base = a_base + Cfg::A_BYTES;
+          const uint64_t a0 = A_MN ? make_smem_desc_sw128(a_base, mn.lbo, mn.sbo) : make_smem_desc_sw128(a_base, 16, 1024);
+          const uint64_t b0 = B_MN ? make_smem_desc_sw128(b_base, mn.lbo, mn.sbo) : make_smem_desc_sw128(b_base, 16, 1024);
+          const uint32_t a_step = A_MN ? mn.kstep : 32u, b_step = B_MN ? mn.kstep : 32u;
+          const uint32_t acc0 = kb != 0 ? 1u : 0u;
+          if (leader) {
 #pragma unroll
-          for (int k = 0; k < GEMM_BK / 16; ++k) {
-            const uint64_t adesc = A_MN ? make_smem_desc_sw128(a_base + k * mn.kstep, mn.lbo, mn.sbo)
-                                        : make_smem_desc_sw128(a_base + k * 32, 16, 1024);
-            const uint64_t bdesc = B_MN ? make_smem_desc_sw128(b_base + k * mn.kstep, mn.lbo, mn.sbo)
-                                        : make_smem_desc_sw128(b_base + k * 32, 16, 1024);
-            umma_f16_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            for (int k = 0; k < GEMM_BK / 16; ++k)
+              umma_f16_ss(d_tmem, desc_advance(a0, k * a_step), desc_advance(b0, k * b_step), idesc, k ? 1u : acc0);
+            umma_commit(&empty_bar[stage]);
           }
-          umma_commit(&empty_bar[stage]);
           if (++stage == Cfg::STAGES) {
             stage = 0;
             phase ^= 1;
           }
         }
         if (!ok) break;
-        umma_commit(&tmem_full[acc]);
+        if (leader) umma_commit(&tmem_full[acc]);
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1;
       }
