@@ -112,6 +112,7 @@ class ColocateConfig:
     # ---- additions -----------------------------------------------------------------------------------
     synthetic_data: bool = False            # seeded random-token prompts + the synthetic token reward
     synthetic_prompt_len: int = 256
+    synthetic_reward_dense_weight: float = 0.0   # > 0 adds a dense shaping term (non-zero advantages for a random policy)
     kv_cache_dtype: str = "fp16"
     kv_num_blocks: int = 0                  # 0: size from free memory
     enable_cuda_graph: bool = False
@@ -146,6 +147,7 @@ _YAML_MAP: List[Tuple[str, str]] = [
     ("data.prompt_field", "prompt_field"), ("data.input_field", "input_field"),
     ("data.response_field", "response_field"), ("data.answer_field", "answer_field"),
     ("data.synthetic", "synthetic_data"), ("data.synthetic_prompt_len", "synthetic_prompt_len"),
+    ("data.synthetic_reward_dense_weight", "synthetic_reward_dense_weight"),
     ("eval.max_tokens", "eval_max_tokens"), ("eval.num_prompts", "eval_num_prompts"),
     ("checkpoint.save_dir", "checkpoint_save_dir"), ("checkpoint.save_interval", "checkpoint_save_interval"),
     ("checkpoint.save_enabled", "checkpoint_save_enabled"), ("checkpoint.resume_from", "resume_from"),

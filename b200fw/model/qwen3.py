@@ -207,6 +207,7 @@ class ParallelTransformerModel(nn.Module):
         self.gradient_checkpointing = gradient_checkpointing
         self.layer_start, self.layer_end = layer_range if layer_range is not None else (0, cfg.num_layers)
         self.is_first_stage, self.is_last_stage = is_first_stage, is_last_stage
+        self.compact_ignored_rows = True   # LM head runs on rows with a real label only (exact)
         self.embed_tokens = None
         if is_first_stage:
             self.embed_tokens = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device))
@@ -363,7 +364,16 @@ class ParallelTransformerModel(nn.Module):
         h = hidden if hidden is not None else self.forward_hidden(input_ids, B, S)
         shifted = torch.full_like(labels, -100)
         shifted[:, :-1] = labels[:, 1:]
-        return ops.lm_head_cross_entropy(h, self.lm_head_weight, shifted.reshape(-1), loss_scale=loss_scale,
+        shifted = shifted.reshape(-1)
+        if self.compact_ignored_rows:
+            # masked positions (prompt tokens, padding) add nothing to the loss or its gradient: run the
+            # LM head on the supervised rows only
+            idx = ops.valid_rows(shifted)
+            if idx is not None:
+                if idx.numel() == 0:
+                    return h.float().sum() * 0.0
+                h, shifted = h.index_select(0, idx), shifted.index_select(0, idx)
+        return ops.lm_head_cross_entropy(h, self.lm_head_weight, shifted, loss_scale=loss_scale,
                                          shard=self.vocab_shard())
 
     def token_logprobs(self, input_ids: torch.Tensor, temperature: float = 1.0,
@@ -376,5 +386,14 @@ class ParallelTransformerModel(nn.Module):
         src = input_ids if labels is None else labels
         tgt = torch.full_like(input_ids, -100)
         tgt[:, :-1] = src[:, 1:]
-        lp = ops.lm_head_logprob(h, self.lm_head_weight, tgt.reshape(-1), temperature, shard=self.vocab_shard())
+        tgt = tgt.reshape(-1)
+        idx = ops.valid_rows(tgt) if (labels is not None and self.compact_ignored_rows) else None
+        if idx is None:
+            lp = ops.lm_head_logprob(h, self.lm_head_weight, tgt, temperature, shard=self.vocab_shard())
+        else:
+            lp = torch.zeros(B * S, dtype=torch.float32, device=h.device)
+            if idx.numel() > 0:
+                sel = ops.lm_head_logprob(h.index_select(0, idx), self.lm_head_weight, tgt.index_select(0, idx),
+                                          temperature, shard=self.vocab_shard())
+                lp = lp.index_copy(0, idx, sel)
         return lp.reshape(B, S)[:, :-1]

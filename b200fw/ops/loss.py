@@ -35,6 +35,33 @@ def _rows(logits, labels, mode, scale=None, loss_sum=None, lse=None, logp=None, 
     nv.count_launch()
 
 
+_side_stream = {}
+
+
+def valid_rows(labels: torch.Tensor) -> Optional[torch.Tensor]:
+    """Indices of the rows whose label is not ``-100``, or ``None`` when every row counts.
+
+    Rows with an ignored label contribute neither loss nor gradient, so the LM-head GEMMs only need the
+    others (in SFT the prompt half of every sequence is masked).  Their number has to reach the host to
+    size the GEMMs; the count runs on a side stream that only waits for the labels, so the host does not
+    drain the forward pass it has already queued on the main stream."""
+    if not labels.is_cuda:
+        idx = torch.nonzero(labels != IGNORE).squeeze(-1)
+        return None if idx.numel() == labels.numel() else idx
+    dev = labels.device
+    side = _side_stream.get(dev.index)
+    if side is None:
+        side = _side_stream[dev.index] = torch.cuda.Stream(device=dev)
+    ready = torch.cuda.current_stream(dev).record_event()
+    with torch.cuda.stream(side):
+        side.wait_event(ready)
+        idx = torch.nonzero(labels != IGNORE).squeeze(-1)      # synchronises the side stream only
+    labels.record_stream(side)
+    idx.record_stream(torch.cuda.current_stream(dev))
+    torch.cuda.current_stream(dev).wait_stream(side)
+    return None if idx.numel() == labels.numel() else idx
+
+
 class VocabShard:
     """Which slice of the vocabulary a tensor-parallel rank's LM-head rows cover, and the group to
     combine the per-row softmax statistics over.  ``reduce_dh``: sum the hidden-state gradient over

@@ -147,7 +147,8 @@ class ColocateOrchestrator:
                     response_field=cfg.response_field, answer_field=cfg.answer_field or "answer",
                     dp_rank=ctx.dp_rank, dp_size=ctx.dp_size)
         if self.reward_fn is None:
-            self.reward_fn = SyntheticTokenReward(eng.model_config.vocab_size, cfg.seed) if cfg.synthetic_data \
+            self.reward_fn = SyntheticTokenReward(eng.model_config.vocab_size, cfg.seed,
+                                                  dense_weight=cfg.synthetic_reward_dense_weight) if cfg.synthetic_data \
                 else GSM8KRewardFunction()
         # ---- rollout backend ----------------------------------------------------------------------------------
         if cfg.training_mode == "grpo" or cfg.inference_preview_enabled:

@@ -46,7 +46,10 @@ class DisaggConfig:
     transfer_backend: str = "nccl"       # "peer_write" | "nccl"
     max_staleness: int = 1
     kv_cache_dtype: str = "fp16"
-    kv_num_blocks: int = 4096
+    kv_num_blocks: int = 0               # 0: sized for one iteration's rollouts of this rank (+10 %)
+    c3po_plus_enabled: bool = True       # train in token-budgeted chunks instead of one B*K-sequence forward
+    c3po_plus_token_budget: int = 256
+    c3po_plus_target_batch_tokens: int = 16384
     seed: int = 0
     output_dir: str = "outputs_disagg"
     backend: Optional[str] = None        # process-group backend (default by device)
@@ -138,7 +141,20 @@ class DisaggOrchestrator:
         P = [prompts[j] for j in mine]
         R = [samples[j] for j in mine]
         rewards = self.reward_fn(R, mine)
-        m = self.train_engine.grpo_step(P, R, rewards)
+        eng = self.train_engine
+        if cfg.c3po_plus_enabled:
+            from ..train.c3po import C3POConfig, C3POPlusScheduler
+            from ..train.engine import TrainEngine
+            sched = C3POPlusScheduler(C3POConfig(True, cfg.c3po_plus_token_budget, cfg.c3po_plus_target_batch_tokens))
+            adv = [TrainEngine.group_advantages(r) for r in rewards]
+            subs = sched.split_and_pack(P, R, rewards, adv)
+            m = None
+            for i, sb in enumerate(subs):
+                m = eng.grpo_step(**sb, skip_optimizer_step=(i < len(subs) - 1), reset_behavior_baseline=True)
+                if i == len(subs) - 2:
+                    eng._accumulation_count = eng.config.gradient_accumulation_steps
+        else:
+            m = eng.grpo_step(P, R, rewards)
         self._last_reward = sum(x for g in rewards for x in g) / max(1, sum(len(g) for g in rewards))
         return m.loss
 

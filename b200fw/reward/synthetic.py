@@ -1,8 +1,8 @@
 """Synthetic rule reward on token ids: 1.0 if the response contains a seed-derived 3-token target
-sequence, plus 0.1 if it ends with EOS, plus a dense shaping term (``dense_weight`` times the fraction
-of response tokens whose id is congruent to the prompt index modulo 7).  The dense term keeps the
-group-normalised advantages non-zero for a random-init policy, so the RL loop does real gradient
-work when benchmarked without a tokenizer or dataset."""
+sequence, plus 0.1 if it ends with EOS, else 0.  Optionally (``dense_weight > 0``) a dense shaping term
+is added: ``dense_weight`` times the fraction of response tokens whose id is congruent to the prompt
+index modulo 7; it keeps the group-normalised advantages non-zero for a random-init policy, whose
+chance of hitting the 3-token target is nil.  Needs no tokenizer and no dataset."""
 from __future__ import annotations
 
 import random
@@ -11,7 +11,7 @@ from typing import List, Sequence
 
 class SyntheticTokenReward:
     def __init__(self, vocab_size: int, seed: int = 0, eos_token_id: int = 2, target_len: int = 3,
-                 target_vocab: int = 0, dense_weight: float = 0.5):
+                 target_vocab: int = 0, dense_weight: float = 0.0):
         self.vocab_size, self.seed, self.eos, self.target_len = vocab_size, seed, eos_token_id, target_len
         self.dense_weight = dense_weight
         self.target_vocab = target_vocab or vocab_size

@@ -114,10 +114,48 @@ __global__ void kv_gather_kernel(const void* __restrict__ k_cache, const void* _
 // otherwise unnormalised partials + (max, sum) go to a workspace for the merge kernel.
 // ---------------------------------------------------------------------------------------------
 constexpr int DEC_THREADS = 128;
-constexpr int DEC_CHUNK = 64;
+constexpr int DEC_CHUNK = 64;   // partitions are multiples of this many tokens
 constexpr int DEC_MAX_G = 8;
+constexpr int DEC_UNROLL = 4;   // cache rows in flight per lane group
+constexpr float DEC_LOG2E = 1.4426950408889634f;
+constexpr float DEC_LN2 = 0.6931471805599453f;
 
 template <bool FP8>
+__device__ __forceinline__ void dec_unpack(const uint4& u, float* f);
+template <>
+__device__ __forceinline__ void dec_unpack<false>(const uint4& u, float* f) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 t = unpack_bf16x2(w[j]);
+    f[2 * j] = t.x;
+    f[2 * j + 1] = t.y;
+  }
+}
+template <>
+__device__ __forceinline__ void dec_unpack<true>(const uint4& u, float* f) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const __half2_raw r = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>((w[j] >> (16 * h)) & 0xFFFFu),
+                                                       __NV_E4M3);
+      const float2 t = __half22float2(*reinterpret_cast<const __half2*>(&r));
+      f[4 * j + 2 * h] = t.x;
+      f[4 * j + 2 * h + 1] = t.y;
+    }
+  }
+}
+
+// Decode attention over the paged cache, one CTA per (sequence, kv head, head group, partition).
+// No shared-memory staging: a cache row (128 dims) is spread over LPT = 16 (bf16) or 8 (fp8) lanes of
+// a warp, 16 bytes each, so one warp-wide load covers 2 (4) tokens and every lane keeps DEC_UNROLL K and
+// V pieces in flight.  Each lane group runs its own online softmax over the tokens it sees (running
+// maximum, sum and DPL accumulator dims per head, base-2 exponent domain); groups and warps are merged
+// once at the end with the exact log-sum-exp rule.  GH query heads of the kv head are handled per CTA
+// (their q pieces sit in registers); larger GQA ratios use several CTAs (head groups) per kv head.
+template <bool FP8, int GH>
 __global__ void __launch_bounds__(DEC_THREADS) paged_decode_kernel(
     const __nv_bfloat16* __restrict__ q, const void* __restrict__ k_cache, const void* __restrict__ v_cache,
     const float* __restrict__ k_scale, const float* __restrict__ v_scale,
@@ -125,158 +163,163 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_decode_kernel(
     __nv_bfloat16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml, int Hq, int Hkv,
     int partition, float scale) {
   constexpr int ESZ = FP8 ? 1 : 2;
-  constexpr int ROW = HD * ESZ + 16;  // padded row: conflict-free 16-byte reads across rows
-  __shared__ __align__(16) uint8_t sK[DEC_CHUNK * ROW];
-  __shared__ __align__(16) uint8_t sV[DEC_CHUNK * ROW];
-  __shared__ float sQ[DEC_MAX_G][HD];
-  __shared__ float sS[DEC_MAX_G][DEC_CHUNK];
-  __shared__ float sM[DEC_MAX_G], sL[DEC_MAX_G], sAlpha[DEC_MAX_G];
-  __shared__ float sKs[DEC_CHUNK / PAGE], sVs[DEC_CHUNK / PAGE];
+  constexpr int LPT = HD * ESZ / 16;   // lanes per token row
+  constexpr int TPW = 32 / LPT;        // token rows per warp-wide load
+  constexpr int DPL = 16 / ESZ;        // dims per lane
+  constexpr int U = DEC_UNROLL;
+  __shared__ float sAcc[DEC_THREADS / 32][GH][HD];
+  __shared__ float sM[DEC_THREADS / 32][GH], sL[DEC_THREADS / 32][GH];
 
-  const int b = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z, nsplit = gridDim.z;
   const int G = Hq / Hkv;
+  const int groups_per_kv = G / GH;
+  const int b = blockIdx.x, kvh = blockIdx.y / groups_per_kv, hg = blockIdx.y % groups_per_kv;
+  const int split = blockIdx.z, nsplit = gridDim.z;
+  const int head0 = kvh * G + hg * GH;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int group = lane / LPT, sub = lane % LPT;
   const int ctx = context_lens[b];
   const int t_begin = split * partition;
   const int t_end = min(ctx, t_begin + partition);
   const int* table = block_tables + static_cast<size_t>(b) * max_blocks;
   const size_t tok_stride = static_cast<size_t>(Hkv) * HD * ESZ;
+  const uint8_t* kc = reinterpret_cast<const uint8_t*>(k_cache) + static_cast<size_t>(kvh) * HD * ESZ + sub * 16;
+  const uint8_t* vc = reinterpret_cast<const uint8_t*>(v_cache) + static_cast<size_t>(kvh) * HD * ESZ + sub * 16;
 
-  for (int i = tid; i < G * HD; i += DEC_THREADS)
-    sQ[i / HD][i % HD] = __bfloat162float(q[(static_cast<size_t>(b) * Hq + kvh * G + i / HD) * HD + i % HD]) * scale;
-  if (tid < DEC_MAX_G) {
-    sM[tid] = -INFINITY;
-    sL[tid] = 0.f;
-  }
-  float acc[DEC_MAX_G / 2][2];
+  float qr[GH][DPL], acc[GH][DPL], m[GH], l[GH];
+  const float qs = scale * DEC_LOG2E;
 #pragma unroll
-  for (int i = 0; i < DEC_MAX_G / 2; ++i) acc[i][0] = acc[i][1] = 0.f;
-  __syncthreads();
+  for (int g = 0; g < GH; ++g) {
+    const __nv_bfloat16* qp = q + (static_cast<size_t>(b) * Hq + head0 + g) * HD + sub * DPL;
+#pragma unroll
+    for (int d = 0; d < DPL; ++d) {
+      qr[g][d] = __bfloat162float(qp[d]) * qs;
+      acc[g][d] = 0.f;
+    }
+    m[g] = -INFINITY;
+    l[g] = 0.f;
+  }
 
-  for (int c0 = t_begin; c0 < t_end; c0 += DEC_CHUNK) {
-    const int n = min(DEC_CHUNK, t_end - c0);
-    // stage K and V rows of this chunk (16-byte pieces)
-    constexpr int PIECES = HD * ESZ / 16;
-    for (int i = tid; i < n * PIECES; i += DEC_THREADS) {
-      const int t = i / PIECES, pc = i % PIECES;
-      const int pos = c0 + t;
-      const int blk = table[pos / PAGE];
-      const size_t a = (static_cast<size_t>(blk) * PAGE + pos % PAGE) * tok_stride +
-                       static_cast<size_t>(kvh) * HD * ESZ + pc * 16;
-      *reinterpret_cast<uint4*>(sK + t * ROW + pc * 16) =
-          *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(k_cache) + a);
-      *reinterpret_cast<uint4*>(sV + t * ROW + pc * 16) =
-          *reinterpret_cast<const uint4*>(reinterpret_cast<const uint8_t*>(v_cache) + a);
-    }
-    if (FP8 && tid < DEC_CHUNK / PAGE) {
-      const int pos = c0 + tid * PAGE;
-      if (pos < t_end) {
-        const int blk = table[pos / PAGE];
-        sKs[tid] = k_scale[static_cast<size_t>(blk) * Hkv + kvh];
-        sVs[tid] = v_scale[static_cast<size_t>(blk) * Hkv + kvh];
-      }
-    }
-    __syncthreads();
-    // scores
-    for (int i = tid; i < G * DEC_CHUNK; i += DEC_THREADS) {
-      const int t = i % DEC_CHUNK, g = i / DEC_CHUNK;
-      float s = -INFINITY;
-      if (t < n) {
-        s = 0.f;
-        const uint8_t* row = sK + t * ROW;
+  for (int base = t_begin + warp * (TPW * U); base < t_end; base += (DEC_THREADS / 32) * TPW * U) {
+    uint4 kq[U], vq[U];
+    float ks[U], vs[U];
+    bool valid[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int tok = base + u * TPW + group;
+      valid[u] = tok < t_end;
+      kq[u] = make_uint4(0, 0, 0, 0);
+      vq[u] = make_uint4(0, 0, 0, 0);
+      ks[u] = vs[u] = 1.f;
+      if (valid[u]) {
+        const int blk = table[tok / PAGE];
+        const size_t a = (static_cast<size_t>(blk) * PAGE + tok % PAGE) * tok_stride;
+        kq[u] = *reinterpret_cast<const uint4*>(kc + a);
+        vq[u] = *reinterpret_cast<const uint4*>(vc + a);
         if (FP8) {
-#pragma unroll
-          for (int pc = 0; pc < 8; ++pc) {
-            uint4 u = *reinterpret_cast<const uint4*>(row + pc * 16);
-            const uint8_t* e = reinterpret_cast<const uint8_t*>(&u);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) s += sQ[g][pc * 16 + j] * fp8_to_float(e[j]);
-          }
-          s *= sKs[t / PAGE];
-        } else {
-#pragma unroll
-          for (int pc = 0; pc < 16; ++pc) {
-            uint4 u = *reinterpret_cast<const uint4*>(row + pc * 16);
-            const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              float2 f = unpack_bf16x2(w[j]);
-              s += sQ[g][pc * 8 + 2 * j] * f.x + sQ[g][pc * 8 + 2 * j + 1] * f.y;
-            }
-          }
+          ks[u] = k_scale[static_cast<size_t>(blk) * Hkv + kvh];
+          vs[u] = v_scale[static_cast<size_t>(blk) * Hkv + kvh];
         }
       }
-      sS[g][t] = s;
     }
-    __syncthreads();
-    // online softmax: warp w owns query heads w, w+4
-    for (int g = warp; g < G; g += DEC_THREADS / 32) {
-      const float s0 = sS[g][lane], s1 = sS[g][lane + 32];
-      const float cm = warp_max(fmaxf(s0, s1));
-      const float m_old = sM[g];
-      const float m_new = fmaxf(m_old, cm);
-      const float p0 = __expf(s0 - m_new), p1 = __expf(s1 - m_new);
-      const float ps = warp_sum(p0 + p1);
-      sS[g][lane] = p0;
-      sS[g][lane + 32] = p1;
-      if (lane == 0) {
-        const float alpha = m_old == -INFINITY ? 0.f : __expf(m_old - m_new);
-        sAlpha[g] = alpha;
-        sL[g] = sL[g] * alpha + ps;
-        sM[g] = m_new;
-      }
-    }
-    __syncthreads();
-    // P*V: thread owns (g, two dims)
+    float sc[U][GH];
 #pragma unroll
-    for (int it = 0; it < DEC_MAX_G / 2; ++it) {
-      const int p = tid + it * DEC_THREADS;
-      if (p < G * (HD / 2)) {
-        const int g = p / (HD / 2), dp = (p % (HD / 2)) * 2;
-        float a0 = acc[it][0] * sAlpha[g], a1 = acc[it][1] * sAlpha[g];
-        for (int t = 0; t < n; ++t) {
-          const float pw = sS[g][t];
-          float v0, v1;
-          if (FP8) {
-            const uint8_t* e = sV + t * ROW + dp;
-            const float vs = sVs[t / PAGE];
-            v0 = fp8_to_float(e[0]) * vs;
-            v1 = fp8_to_float(e[1]) * vs;
-          } else {
-            float2 f = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(sV + t * ROW + dp * 2));
-            v0 = f.x;
-            v1 = f.y;
-          }
-          a0 += pw * v0;
-          a1 += pw * v1;
-        }
-        acc[it][0] = a0;
-        acc[it][1] = a1;
+    for (int u = 0; u < U; ++u) {
+      float kf[DPL];
+      dec_unpack<FP8>(kq[u], kf);
+#pragma unroll
+      for (int g = 0; g < GH; ++g) {
+        float d0 = 0.f;
+#pragma unroll
+        for (int d = 0; d < DPL; ++d) d0 = fmaf(qr[g][d], kf[d], d0);
+#pragma unroll
+        for (int o = LPT / 2; o > 0; o >>= 1) d0 += __shfl_xor_sync(0xffffffffu, d0, o);
+        sc[u][g] = valid[u] ? d0 * ks[u] : -INFINITY;
       }
     }
-    __syncthreads();
+#pragma unroll
+    for (int g = 0; g < GH; ++g) {
+      float mn = m[g];
+#pragma unroll
+      for (int u = 0; u < U; ++u) mn = fmaxf(mn, sc[u][g]);
+      if (mn == -INFINITY) continue;   // this lane group has not seen a token yet
+      const float alpha = fast_exp2(m[g] - mn);
+      m[g] = mn;
+      float ps = 0.f;
+#pragma unroll
+      for (int d = 0; d < DPL; ++d) acc[g][d] *= alpha;
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const float p = fast_exp2(sc[u][g] - mn);
+        ps += p;
+        sc[u][g] = p * vs[u];
+      }
+      l[g] = l[g] * alpha + ps;
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      float vf[DPL];
+      dec_unpack<FP8>(vq[u], vf);
+#pragma unroll
+      for (int g = 0; g < GH; ++g)
+#pragma unroll
+        for (int d = 0; d < DPL; ++d) acc[g][d] = fmaf(sc[u][g], vf[d], acc[g][d]);
+    }
   }
+
+  // merge the lane groups of the warp, then the warps
 #pragma unroll
-  for (int it = 0; it < DEC_MAX_G / 2; ++it) {
-    const int p = tid + it * DEC_THREADS;
-    if (p < G * (HD / 2)) {
-      const int g = p / (HD / 2), dp = (p % (HD / 2)) * 2;
-      const int head = kvh * G + g;
-      if (nsplit == 1) {
-        const float inv = sL[g] > 0.f ? 1.f / sL[g] : 0.f;
-        *reinterpret_cast<uint32_t*>(out + (static_cast<size_t>(b) * Hq + head) * HD + dp) =
-            pack_bf16x2(acc[it][0] * inv, acc[it][1] * inv);
-      } else {
-        float* po = part_o + ((static_cast<size_t>(b) * Hq + head) * nsplit + split) * HD + dp;
-        po[0] = acc[it][0];
-        po[1] = acc[it][1];
+  for (int o = LPT; o < 32; o <<= 1) {
+#pragma unroll
+    for (int g = 0; g < GH; ++g) {
+      const float mo = __shfl_xor_sync(0xffffffffu, m[g], o);
+      const float lo = __shfl_xor_sync(0xffffffffu, l[g], o);
+      const float mn = fmaxf(m[g], mo);
+      const float wa = mn == -INFINITY ? 0.f : fast_exp2(m[g] - mn);
+      const float wb = mn == -INFINITY ? 0.f : fast_exp2(mo - mn);
+#pragma unroll
+      for (int d = 0; d < DPL; ++d) {
+        const float ao = __shfl_xor_sync(0xffffffffu, acc[g][d], o);
+        acc[g][d] = acc[g][d] * wa + ao * wb;
+      }
+      l[g] = l[g] * wa + lo * wb;
+      m[g] = mn;
+    }
+  }
+  if (group == 0) {
+#pragma unroll
+    for (int g = 0; g < GH; ++g) {
+#pragma unroll
+      for (int d = 0; d < DPL; ++d) sAcc[warp][g][sub * DPL + d] = acc[g][d];
+      if (sub == 0) {
+        sM[warp][g] = m[g];
+        sL[warp][g] = l[g];
       }
     }
   }
-  if (nsplit > 1 && tid < G) {
-    float* ml = part_ml + ((static_cast<size_t>(b) * Hq + kvh * G + tid) * nsplit + split) * 2;
-    ml[0] = sM[tid];
-    ml[1] = sL[tid];
+  __syncthreads();
+#pragma unroll
+  for (int g = 0; g < GH; ++g) {
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < DEC_THREADS / 32; ++w) M = fmaxf(M, sM[w][g]);
+    float L = 0.f, o = 0.f;
+#pragma unroll
+    for (int w = 0; w < DEC_THREADS / 32; ++w) {
+      const float wgt = sM[w][g] == -INFINITY ? 0.f : fast_exp2(sM[w][g] - M);
+      L += sL[w][g] * wgt;
+      o += sAcc[w][g][tid] * wgt;
+    }
+    const int head = head0 + g;
+    if (nsplit == 1) {
+      out[(static_cast<size_t>(b) * Hq + head) * HD + tid] = __float2bfloat16(L > 0.f ? o / L : 0.f);
+    } else {
+      part_o[((static_cast<size_t>(b) * Hq + head) * nsplit + split) * HD + tid] = o;
+      if (tid == 0) {
+        float* ml = part_ml + ((static_cast<size_t>(b) * Hq + head) * nsplit + split) * 2;
+        ml[0] = M * DEC_LN2;   // natural-log domain for the merge kernel
+        ml[1] = L;
+      }
+    }
   }
 }
 
@@ -369,15 +412,25 @@ B2_EXPORT int b2_paged_decode(const void* q, const void* k_cache, const void* v_
   }
   if (B <= 0) return 0;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  dim3 grid(B, Hkv, nsplit);
-  if (fp8)
-    paged_decode_kernel<true><<<grid, DEC_THREADS, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(q), k_cache, v_cache, k_scale, v_scale, block_tables, context_lens,
-        max_blocks, static_cast<__nv_bfloat16*>(out), part_o, part_ml, Hq, Hkv, partition, scale);
-  else
-    paged_decode_kernel<false><<<grid, DEC_THREADS, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(q), k_cache, v_cache, k_scale, v_scale, block_tables, context_lens,
-        max_blocks, static_cast<__nv_bfloat16*>(out), part_o, part_ml, Hq, Hkv, partition, scale);
+  const int G = Hq / Hkv;
+  // query heads per CTA (their q pieces and accumulators live in registers: fp8 rows put 16 dims on a
+  // lane, so four heads would leave room for only two CTAs per SM)
+  const int GH = (G % 4 == 0 && !fp8) ? 4 : (G % 2 == 0 ? 2 : 1);
+  dim3 grid(B, Hkv * (G / GH), nsplit);
+#define B2_DECODE_LAUNCH(F8, GHV)                                                                          \
+  paged_decode_kernel<F8, GHV><<<grid, DEC_THREADS, 0, stream>>>(                                          \
+      static_cast<const __nv_bfloat16*>(q), k_cache, v_cache, k_scale, v_scale, block_tables, context_lens, \
+      max_blocks, static_cast<__nv_bfloat16*>(out), part_o, part_ml, Hq, Hkv, partition, scale)
+  if (fp8) {
+    if (GH == 4) B2_DECODE_LAUNCH(true, 4);
+    else if (GH == 2) B2_DECODE_LAUNCH(true, 2);
+    else B2_DECODE_LAUNCH(true, 1);
+  } else {
+    if (GH == 4) B2_DECODE_LAUNCH(false, 4);
+    else if (GH == 2) B2_DECODE_LAUNCH(false, 2);
+    else B2_DECODE_LAUNCH(false, 1);
+  }
+#undef B2_DECODE_LAUNCH
   B2_LAUNCH_CHECK("paged_decode");
   if (nsplit > 1) {
     paged_merge_kernel<<<B * Hq, HD, 0, stream>>>(part_o, part_ml, static_cast<__nv_bfloat16*>(out), lse, nsplit);

@@ -29,6 +29,8 @@ def main():
     ap.add_argument("--zero-stage", type=int, default=2)
     ap.add_argument("--no-c3po", action="store_true")
     ap.add_argument("--async-pipeline", action="store_true")
+    ap.add_argument("--dense-reward", type=float, default=0.0,
+                    help="weight of the dense shaping term of the synthetic reward (0 = the plain rule reward)")
     ap.add_argument("--output-dir", default="outputs/bench_grpo")
     a = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -39,6 +41,7 @@ def main():
         batch_size=a.prompts, num_samples_per_prompt=a.num_samples, max_tokens=a.max_tokens, temperature=0.8,
         top_p=0.95, lora_rank=a.lora_rank, grpo_beta=0.01, grpo_clip_eps=0.2, gradient_accumulation_steps=1,
         zero_stage=a.zero_stage, inference_backend="native", synthetic_data=True, synthetic_prompt_len=a.prompt_len,
+        synthetic_reward_dense_weight=a.dense_reward,
         max_seq_len=a.prompt_len + a.max_tokens, max_data_samples=max(1024, a.prompts * (a.iterations + 2)),
         icepop_enabled=True, c3po_plus_enabled=not a.no_c3po, c3po_plus_token_budget=256,
         c3po_plus_target_batch_tokens=16384, swift_sync_enabled=a.lora_rank > 0,

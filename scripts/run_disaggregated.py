@@ -75,7 +75,9 @@ def main(argv=None):
         model.init_weights(0)
         for p in model.parameters():
             p.requires_grad_(False)
-        ic = InferenceConfig.from_model_config(mc, num_blocks=cfg.kv_num_blocks, inference_mode="kv_cache",
+        seqs = -(-a.batch_size // max(1, a.num_infer_gpus)) * a.num_samples
+        blocks = cfg.kv_num_blocks or int(seqs * (-(-(a.prompt_len + a.max_tokens) // 16) + 1) * 1.1) + 64
+        ic = InferenceConfig.from_model_config(mc, num_blocks=blocks, inference_mode="kv_cache",
                                                kv_cache_dtype=a.kv_cache_dtype, max_num_batched_tokens=8192,
                                                max_prefill_tokens=4096, seed=i)
         return InferenceEngine(ic, model).initialize()
