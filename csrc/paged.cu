@@ -241,7 +241,11 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_decode_kernel(
       float mn = m[g];
 #pragma unroll
       for (int u = 0; u < U; ++u) mn = fmaxf(mn, sc[u][g]);
-      if (mn == -INFINITY) continue;   // this lane group has not seen a token yet
+      if (mn == -INFINITY) {   // this lane group has not seen a token yet: its weights are zero
+#pragma unroll
+        for (int u = 0; u < U; ++u) sc[u][g] = 0.f;
+        continue;
+      }
       const float alpha = fast_exp2(m[g] - mn);
       m[g] = mn;
       float ps = 0.f;
