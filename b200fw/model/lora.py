@@ -54,13 +54,17 @@ class LoRAColumnParallel(LoRALayer):
 
 
 class LoRARowParallel(LoRALayer):
-    """A ``[r, in/tp]`` sharded, B ``[out, r]`` replicated; the rank-r intermediate is all-reduced."""
+    """A ``[r, in/tp]`` sharded, B ``[out, r]`` replicated; the rank-r intermediate is all-reduced
+    (reduce-scattered over the sequence under sequence parallelism)."""
 
-    def __init__(self, in_local, out_features, rank, alpha, tp_group=None, device=None):
+    def __init__(self, in_local, out_features, rank, alpha, tp_group=None, device=None,
+                 sequence_parallel: bool = False):
         super().__init__(in_local, out_features, rank, alpha, device)
         self.tp_group = tp_group
         self.lora_A.tp_sharded = tp_group is not None
-        self.lora_B.tp_partial_grad = False  # every rank sees the full gradient after the all-reduce
+        # after a plain all-reduce every rank sees the full gradient of B; under sequence parallelism
+        # each rank only sees its own tokens' contribution
+        self.lora_B.tp_partial_grad = tp_group is not None and sequence_parallel
 
     def delta(self, x):
         a = self.lora_A.to(x.dtype)
@@ -85,35 +89,45 @@ class LinearWithLoRA(nn.Module):
     def weight(self):
         return self.base.weight
 
+    def _stacked(self, dtype):
+        """All adapters of this layer as one pair: ``A_cat [R, in]`` (adapters stacked along the rank
+        dimension) and ``B_bd [out_local, R]`` (each adapter's B, times its scaling, in its own row range
+        and rank columns; zero elsewhere), so the layer's whole LoRA update is two GEMMs."""
+        order = sorted(self.ranges.items(), key=lambda kv: kv[1][0])
+        ads = [self.adapters[name] for name, _ in order]
+        if len(ads) == 1 and order[0][1] == (0, self.base.weight.shape[0]):
+            return ads[0].lora_A.to(dtype), (ads[0].lora_B * ads[0].scaling).to(dtype)
+        a_cat = torch.cat([ad.lora_A for ad in ads], 0).to(dtype)
+        b_bd = torch.zeros(self.base.weight.shape[0], a_cat.shape[0], dtype=dtype, device=a_cat.device)
+        r0 = 0
+        for ad, (_, (s0, e0)) in zip(ads, order):
+            b_bd[s0:e0, r0:r0 + ad.rank] = (ad.lora_B * ad.scaling).to(dtype)
+            r0 += ad.rank
+        return a_cat, b_bd
+
     def forward(self, x, residual=None):
-        is_row = isinstance(self.base, RowParallelLinear)
-        y = self.base(x, residual) if is_row else self.base(x)
+        from .. import ops
+        base = self.base
+        is_row = isinstance(base, RowParallelLinear)
+        y = base(x, residual) if is_row else base(x)
         if self.merged or not self.adapters:
             return y
+        tp, grp, sp = base.tp_size, base.tp_group, base.sequence_parallel
         x2 = x.reshape(-1, x.shape[-1])
-        if not is_row and self.base.tp_size > 1:
-            x2 = comm.gather_sequence(x2, self.base.tp_group) if self.base.sequence_parallel \
-                else comm.copy_to_parallel_region(x2, self.base.tp_group)
+        a_cat, b_bd = self._stacked(x2.dtype)
+        if is_row:
+            # x holds this rank's input columns: the rank-R intermediate is a partial sum over TP
+            mid = ops.linear(x2, a_cat)
+            if tp > 1:
+                mid = comm.reduce_scatter_sequence(mid, grp) if sp else comm.reduce_from_parallel_region(mid, grp)
+        else:
+            if tp > 1 and not sp:
+                x2 = comm.copy_to_parallel_region(x2, grp)
+            mid = ops.linear(x2, a_cat)
+            if tp > 1 and sp:
+                mid = comm.gather_sequence(mid, grp)   # [tokens/tp, R] -> [tokens, R]: R columns, not hidden
         shape = y.shape
-        y2 = y.reshape(-1, shape[-1])
-        full = len(self.ranges) == 1 and next(iter(self.ranges.values())) == (0, y2.shape[-1])
-        if full:
-            name = next(iter(self.ranges))
-            d = self.adapters[name].delta(x2)
-            if is_row and self.base.sequence_parallel and self.base.tp_size > 1:
-                n = d.shape[0] // self.base.tp_size
-                d = d[self.base.tp_rank * n:(self.base.tp_rank + 1) * n]
-            return (y2 + d).reshape(shape)
-        pieces = []
-        cur = 0
-        for name, (s, e) in sorted(self.ranges.items(), key=lambda kv: kv[1][0]):
-            if s > cur:
-                pieces.append(y2[:, cur:s])
-            pieces.append(y2[:, s:e] + self.adapters[name].delta(x2))
-            cur = e
-        if cur < y2.shape[-1]:
-            pieces.append(y2[:, cur:])
-        return torch.cat(pieces, dim=-1).reshape(shape)
+        return ops.linear(mid, b_bd, residual=y.reshape(-1, shape[-1])).reshape(shape)
 
 
 def _sub_ranges(parent) -> Dict[str, Tuple[str, int, int]]:
@@ -158,7 +172,8 @@ def apply_lora(model: nn.Module, rank: int = 16, alpha: float = 32.0,
             dev = base.weight.device
             grp = base.tp_group if base.tp_size > 1 else None
             if isinstance(base, RowParallelLinear):
-                ad = LoRARowParallel(base.in_local, base.out_features, rank, alpha, grp, dev)
+                ad = LoRARowParallel(base.in_local, base.out_features, rank, alpha, grp, dev,
+                                     sequence_parallel=base.sequence_parallel)
             else:
                 ad = LoRAColumnParallel(base.in_features, e - s, rank, alpha, grp, dev)
             per_attr.setdefault(attr, {})[tgt] = (ad, s, e)

@@ -78,16 +78,21 @@ class _Bucket:
     def ensure_grad_buf(self, use_main_grad: bool):
         if getattr(self, "persistent_grad", False):
             if use_main_grad and not hasattr(self.params[0], "main_grad"):
-                for p, o in zip(self.params, self.offsets):
-                    p.main_grad = self.grad_buf[o:o + p.numel()].view(p.shape)
-                    p.grad_filled = False
+                self._bind_main_grads()
             return
         if self.grad_buf is None:
             self.grad_buf = torch.zeros(self.numel, dtype=self.grad_dtype, device=self.device)
             if use_main_grad:
-                for p, o in zip(self.params, self.offsets):
-                    p.main_grad = self.grad_buf[o:o + p.numel()].view(p.shape)
-                    p.grad_filled = False
+                self._bind_main_grads()
+
+    def _bind_main_grads(self):
+        # recorded shapes, not p.shape: under ZeRO-3 the parameters may be unbound (empty) right now
+        for p, o, shp in zip(self.params, self.offsets, self.shapes):
+            n = 1
+            for d in shp:
+                n *= d
+            p.main_grad = self.grad_buf[o:o + n].view(shp)
+            p.grad_filled = False
 
     def release_grad_buf(self):
         if getattr(self, "persistent_grad", False):

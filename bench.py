@@ -42,6 +42,8 @@ def parse():
     ap.add_argument("--grad-ckpt", action="store_true")
     ap.add_argument("--sequence-parallel", action="store_true")
     ap.add_argument("--zero-comm", default="nccl", choices=["nccl", "p2p"])
+    ap.add_argument("--layers", type=int, default=0,
+                    help="override the preset's layer count (smoke runs of a large architecture; not a benchmark config)")
     ap.add_argument("--fused-tp", action="store_true",
                     help="run the sequence-parallel collectives inside the GEMM kernels (peer memory) instead of NCCL")
     return ap.parse_args()
@@ -130,8 +132,11 @@ def run_ours(a):
     assert world == a.gpus, f"--gpus {a.gpus} but WORLD_SIZE={world}"
     torch.cuda.set_device(local)
     dp = world // (a.tp * a.pp)
-    mc = PRESETS[a.model]
-    cfg = TrainConfig(model_preset=a.model, tp_size=a.tp, dp_size=dp, pp_size=a.pp,
+    import copy
+    mc = copy.deepcopy(PRESETS[a.model])
+    if a.layers > 0:
+        mc.num_layers = a.layers
+    cfg = TrainConfig(model_config=mc, tp_size=a.tp, dp_size=dp, pp_size=a.pp,
                       num_micro_batches=max(a.pp, a.grad_accum) if a.pp > 1 else 1, max_seq_len=a.seq_len,
                       use_gradient_checkpoint=a.grad_ckpt, lora_rank=a.lora_rank, learning_rate=1e-5,
                       gradient_accumulation_steps=a.grad_accum if a.pp == 1 else 1, grpo_beta=0.0,
@@ -204,7 +209,8 @@ def run_ours(a):
             "warmup": a.warmup, "ms_per_step": ms / a.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded uniform tokens, random-init weights)",
             "impl": "b200fw",
-            "config": {"model": f"{a.model}-arch full SFT" if a.lora_rank <= 0 else f"{a.model}-arch LoRA r{a.lora_rank}",
+            "config": {"model": (f"{a.model}-arch full SFT" if a.lora_rank <= 0 else f"{a.model}-arch LoRA r{a.lora_rank}")
+                       + (f" (layers cut to {a.layers}: smoke run, not the named config)" if a.layers > 0 else ""),
                        "global_batch": a.micro_batch * micro_per_step * dp, "micro_batch_per_gpu": a.micro_batch,
                        "grad_accum": a.grad_accum, "seq_len": a.seq_len, "parallelism": par,
                        "zero_stage": a.zero_stage, "zero_comm": a.zero_comm,

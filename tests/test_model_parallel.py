@@ -166,3 +166,75 @@ def test_lora_tp2_merge_consistent_across_ranks():
         _full_model(d)
         outs = run_ranks(_lora_tp_worker, 2, d)
         assert (torch.tensor(outs[0]) - torch.tensor(outs[1])).abs().max() < 1e-5
+
+
+def _lora_sp_worker(rank, world, path):
+    """LoRA x TP x sequence parallelism against the same adapters on an unsharded model: equal loss, and
+    adapter gradients that match the unsharded ones (shards: the matching slice; partial-gradient
+    tensors: after the sum over the TP group)."""
+    import torch.distributed as dist
+    from b200fw.dist.context import ParallelContext
+    from b200fw.model.lora import iter_lora
+    ctx = ParallelContext.init_distributed(tp_size=world, backend="gloo")
+    ref = ParallelTransformerModel(CFG)
+    load_from_hf_checkpoint(ref, path, strict=True)
+    apply_lora(ref, rank=4, alpha=8.0)
+    m = ParallelTransformerModel(CFG, ctx, sequence_parallel=True)
+    load_from_hf_checkpoint(m, path, strict=True)
+    apply_lora(m, rank=4, alpha=8.0)
+    g = torch.Generator().manual_seed(5)
+    full = {}
+    for name, tgt, mod, ad in iter_lora(ref):
+        with torch.no_grad():
+            ad.lora_A.copy_(torch.empty(ad.lora_A.shape).normal_(0, 0.05, generator=g))
+            ad.lora_B.copy_(torch.empty(ad.lora_B.shape).normal_(0, 0.05, generator=g))
+        full[(name, tgt)] = ad
+    for name, tgt, mod, ad in iter_lora(m):
+        fa = full[(name, tgt)]
+        with torch.no_grad():
+            if ad.lora_A.shape == fa.lora_A.shape:
+                ad.lora_A.copy_(fa.lora_A)
+            else:                                              # row parallel: A sharded along its columns
+                n = ad.lora_A.shape[1]
+                ad.lora_A.copy_(fa.lora_A[:, rank * n:(rank + 1) * n])
+            if ad.lora_B.shape == fa.lora_B.shape:
+                ad.lora_B.copy_(fa.lora_B)
+            else:                                              # column parallel: B sharded along its rows
+                n = ad.lora_B.shape[0]
+                ad.lora_B.copy_(_shard_rows_like(fa.lora_B, tgt, rank, world))
+    ids = torch.randint(0, CFG.vocab_size, (2, 16), generator=torch.Generator().manual_seed(2))
+    labels = ids.clone()
+    labels[:, :5] = -100
+    l, lr = m.loss(ids, labels), ref.loss(ids, labels)
+    assert abs(l.item() - lr.item()) < 1e-5, (l.item(), lr.item())
+    l.backward()
+    lr.backward()
+    worst = 0.0
+    for name, tgt, mod, ad in iter_lora(m):
+        fa = full[(name, tgt)]
+        for leaf in ("lora_A", "lora_B"):
+            p, fp = getattr(ad, leaf), getattr(fa, leaf)
+            gr = p.grad.clone()
+            if getattr(p, "tp_partial_grad", False):
+                dist.all_reduce(gr, group=ctx.tp_group)
+            if gr.shape == fp.grad.shape:
+                want = fp.grad
+            elif leaf == "lora_A":
+                n = gr.shape[1]
+                want = fp.grad[:, rank * n:(rank + 1) * n]
+            else:
+                want = _shard_rows_like(fp.grad, tgt, rank, world)
+            worst = max(worst, float((gr - want).abs().max()))
+    assert worst < 1e-5, worst
+    return worst
+
+
+def _shard_rows_like(t, tgt, rank, world):
+    n = t.shape[0] // world
+    return t[rank * n:(rank + 1) * n]
+
+
+def test_lora_tp2_sequence_parallel_gradients_match_unsharded():
+    with tempfile.TemporaryDirectory() as d:
+        _full_model(d)
+        run_ranks(_lora_sp_worker, 2, d)
