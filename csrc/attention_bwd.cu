@@ -18,9 +18,8 @@
 
 namespace b2 {
 
-constexpr int ATB_THREADS = 320;  // warp 0 TMA, warp 1 MMA, warps 2..9 elementwise (two column halves)
+constexpr int ATB_THREADS = 352;  // warp 0 TMA, warps 1 and 10 MMA issue, warps 2..9 elementwise (two groups)
 
-__device__ __forceinline__ void ew_barrier() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 constexpr float LOG2E = 1.4426950408889634f;
 
 // ---------------------------------------------------------------------------------------------
@@ -52,7 +51,7 @@ struct DkDvSmem {
   static constexpr int PT = DO + ATB_STAGES * 16384;   // 2 x 16 KiB [128 x 64]
   static constexpr int DST = PT + 2 * 16384;  // 2 x 16 KiB
   static constexpr int BARS = DST + 2 * 16384;
-  static constexpr int TOTAL = BARS + 144 + 1024 /*lse, D*/ + 1024;
+  static constexpr int TOTAL = BARS + 160 + 1024 /*lse, D*/ + 1024;
 };
 
 // Persistent: each CTA walks the work items (kv tile, kv head, batch) dealt in boustrophedon order,
@@ -74,6 +73,10 @@ __device__ __forceinline__ DkDvItem dkdv_item(int w, int Hkv, int B, int nq64, i
   return it;
 }
 
+// Roles (ATB_THREADS = 352): warp 0 streams tiles with TMA; warp 1 issues the S^T / dP^T MMAs; warp 10
+// issues the dV / dK MMAs; warps 2..5 (group 0) do the elementwise step of the even global iterations,
+// warps 6..9 (group 1) that of the odd ones, each thread owning one kv row and all 64 q columns of its
+// iteration (two passes of 32).  See the dQ kernel for why there are two groups and two issuers.
 __global__ void __launch_bounds__(ATB_THREADS, 1)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_constant__ CUtensorMap tmdO64,
                      const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
@@ -93,15 +96,21 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_con
   uint64_t* pds_empty = bars + 13;  // [2]
   uint64_t* acc_done = bars + 15;
   uint64_t* kv_empty = bars + 16;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
-  float* s_lse = reinterpret_cast<float*>(bars + 18);   // [2][64], pre-multiplied by log2(e)
-  float* s_D = s_lse + 128;                             // [2][64], pre-multiplied by the softmax scale
+  uint64_t* acc_free = bars + 17;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
+  float* s_lse = reinterpret_cast<float*>(bars + 20);   // [group][64], pre-multiplied by log2(e)
+  float* s_D = s_lse + 128;                             // [group][64], pre-multiplied by the softmax scale
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = Hq / Hkv;
   const int T = B * S;
   const int nq64 = (S + 63) / 64;
   const int n_items = ((S + 127) / 128) * Hkv * B;
+  // first item with work at or after w along this CTA's path (n_items if none)
+  auto first_with_work = [&](int w) {
+    while (w < n_items && dkdv_item(w, Hkv, B, nq64, G).n_it == 0) w = snake_next(w);
+    return w;
+  };
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
@@ -112,11 +121,12 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_con
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&sdp_full[i], 1);
-      mbar_init(&sdp_empty[i], 8);   // one arrive per elementwise warp
-      mbar_init(&pds_full[i], 8);
+      mbar_init(&sdp_empty[i], 4);   // one arrive per warp of the group that owns buffer i
+      mbar_init(&pds_full[i], 4);
       mbar_init(&pds_empty[i], 1);
     }
     mbar_init(acc_done, 1);
+    mbar_init(acc_free, 8);          // every elementwise warp, after it has read its part of dV / dK
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -136,9 +146,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_con
     if (lane == 0) {
       int g = 0, n = 0;
       bool ok = true;
-      for (int w = blockIdx.x; w < n_items && ok; w = snake_next(w)) {
+      for (int w = first_with_work(blockIdx.x); w < n_items && ok; w = first_with_work(snake_next(w)), ++n) {
         const DkDvItem item = dkdv_item(w, Hkv, B, nq64, G);
-        if (item.n_it == 0) continue;
         const int kv_row0 = item.batch * S + item.jt * 128;
         if (!mbar_wait(kv_empty, (n & 1) ^ 1, status, ERR_ATTN_WAIT)) break;
         mbar_expect_tx(kv_full, 65536);
@@ -160,21 +169,28 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_con
           tma_load_2d(sdO, &tmdO64, &qdo_full[st], head * 128, qrow);
           tma_load_2d(sdO + 8192, &tmdO64, &qdo_full[st], head * 128 + 64, qrow);
         }
-        ++n;
       }
     }
   } else if (warp == 1) {
-    // The whole warp runs this (uniform) control flow so that descriptors and addresses stay in the
-    // uniform datapath; only the tcgen05 instructions themselves are issued by one elected lane.
-    {
-      const bool leader = elect_one();
-      constexpr uint32_t idesc_s = make_idesc_f16(1, 128, 64, 0, 0);     // [128 kv] x [64 q], K = d
-      constexpr uint32_t idesc_acc = make_idesc_f16(1, 128, 128, 0, 1);  // [128 kv] x [128 d], K = q
-      const uint64_t d_k = make_smem_desc_sw128(smem_u32(smem + DkDvSmem::K), 16, 1024);
-      const uint64_t d_v = make_smem_desc_sw128(smem_u32(smem + DkDvSmem::V), 16, 1024);
-      auto issue_sdp = [&](int g) {
+    // ---- S^T = K Q^T and dP^T = V dO^T of every global iteration ------------------------------------
+    const bool leader = elect_one();
+    constexpr uint32_t idesc_s = make_idesc_f16(1, 128, 64, 0, 0);     // [128 kv] x [64 q], K = d
+    const uint64_t d_k = make_smem_desc_sw128(smem_u32(smem + DkDvSmem::K), 16, 1024);
+    const uint64_t d_v = make_smem_desc_sw128(smem_u32(smem + DkDvSmem::V), 16, 1024);
+    int g = 0, n = 0;
+    bool ok = true;
+    for (int w = first_with_work(blockIdx.x); w < n_items && ok; w = first_with_work(snake_next(w)), ++n) {
+      const DkDvItem item = dkdv_item(w, Hkv, B, nq64, G);
+      if (!mbar_wait(kv_full, n & 1, status, ERR_ATTN_WAIT)) break;
+      for (int it = 0; it < item.n_it; ++it, ++g) {
         const int st = g & 1;
         const int ks_ = g % ATB_STAGES;
+        if (!mbar_wait(&qdo_full[ks_], (g / ATB_STAGES) & 1, status, ERR_ATTN_WAIT) ||
+            !mbar_wait(&sdp_empty[st], ((g >> 1) & 1) ^ 1, status, ERR_ATTN_WAIT)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
         const uint64_t d_q = make_smem_desc_sw128(smem_u32(smem + DkDvSmem::Q + ks_ * 16384), 16, 1024);
         const uint64_t d_do = make_smem_desc_sw128(smem_u32(smem + DkDvSmem::DO + ks_ * 16384), 16, 1024);
         if (leader) {
@@ -190,102 +206,84 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_con
             const uint32_t ob = (ks >> 2) * 8192 + (ks & 3) * 32;
             umma_f16_ss(tmem_DPT + st * 64, desc_advance(d_v, oa), desc_advance(d_do, ob), idesc_s, ks != 0);
           }
+          umma_commit(&sdp_full[st]);
+          if (it + 1 == item.n_it) umma_commit(kv_empty);   // last S^T/dP^T of the item: K/V may be reloaded
         }
-        if (leader) umma_commit(&sdp_full[st]);
-      };
-      auto wait_sdp_inputs = [&](int g) -> bool {
-        return mbar_wait(&qdo_full[g % ATB_STAGES], (g / ATB_STAGES) & 1, status, ERR_ATTN_WAIT) &&
-               mbar_wait(&sdp_empty[g & 1], ((g >> 1) & 1) ^ 1, status, ERR_ATTN_WAIT);
-      };
-      // index of the next item with work after w (n_items if none)
-      auto next_item = [&](int w) {
-        int x = snake_next(w);
-        while (x < n_items && dkdv_item(x, Hkv, B, nq64, G).n_it == 0) x = snake_next(x);
-        return x;
-      };
-      int g = 0, n = 0;
-      bool ok = true, primed = false;
-      int w = blockIdx.x;
-      if (w < n_items && dkdv_item(w, Hkv, B, nq64, G).n_it == 0) w = next_item(w);
-      for (; w < n_items && ok; ++n) {
-        const DkDvItem item = dkdv_item(w, Hkv, B, nq64, G);
-        const int w_next = next_item(w);
-        if (!primed) {
-          ok = mbar_wait(kv_full, n & 1, status, ERR_ATTN_WAIT) && wait_sdp_inputs(g);
-          if (!ok) break;
-          tc_fence_after();
-          issue_sdp(g);
-          if (item.n_it == 1) if (leader) umma_commit(kv_empty);
+      }
+    }
+  } else if (warp == 10) {
+    // ---- dV += P^T dO and dK += dS^T Q of every global iteration --------------------------------------
+    const bool leader = elect_one();
+    constexpr uint32_t idesc_acc = make_idesc_f16(1, 128, 128, 0, 1);  // [128 kv] x [128 d], K = q
+    int g = 0, n = 0;
+    bool ok = true;
+    for (int w = first_with_work(blockIdx.x); w < n_items && ok; w = first_with_work(snake_next(w)), ++n) {
+      const DkDvItem item = dkdv_item(w, Hkv, B, nq64, G);
+      // the elementwise warps must have read the previous item's dV / dK before they are overwritten
+      if (n > 0 && !mbar_wait(acc_free, (n - 1) & 1, status, ERR_ATTN_WAIT)) break;
+      for (int it = 0; it < item.n_it; ++it, ++g) {
+        const int st = g & 1;
+        const int kst = g % ATB_STAGES;
+        if (!mbar_wait(&qdo_full[kst], (g / ATB_STAGES) & 1, status, ERR_ATTN_WAIT) ||
+            !mbar_wait(&pds_full[st], (g >> 1) & 1, status, ERR_ATTN_WAIT)) {
+          ok = false;
+          break;
         }
-        primed = false;
-        for (int it = 0; it < item.n_it; ++it, ++g) {
-          if (it + 1 < item.n_it) {
-            if (!wait_sdp_inputs(g + 1)) { ok = false; break; }
-            tc_fence_after();
-            issue_sdp(g + 1);
-            if (it + 2 == item.n_it) if (leader) umma_commit(kv_empty);   // last S^T/dP^T of the item: K/V may be reloaded
-          }
-          const int st = g & 1;
-          if (!mbar_wait(&pds_full[st], (g >> 1) & 1, status, ERR_ATTN_WAIT)) { ok = false; break; }
-          tc_fence_after();
-          const int kst = g % ATB_STAGES;
-          const uint64_t d_pt = make_smem_desc_sw128(smem_u32(smem + DkDvSmem::PT + st * 16384), 16, 1024);
-          const uint64_t d_dst = make_smem_desc_sw128(smem_u32(smem + DkDvSmem::DST + st * 16384), 16, 1024);
-          const uint64_t d_qm = make_smem_desc_sw128(smem_u32(smem + DkDvSmem::Q + kst * 16384), 8192, 1024);
-          const uint64_t d_dom = make_smem_desc_sw128(smem_u32(smem + DkDvSmem::DO + kst * 16384), 8192, 1024);
-          const uint32_t acc0 = it != 0;
-          if (leader) {
+        tc_fence_after();
+        const uint64_t d_pt = make_smem_desc_sw128(smem_u32(smem + DkDvSmem::PT + st * 16384), 16, 1024);
+        const uint64_t d_dst = make_smem_desc_sw128(smem_u32(smem + DkDvSmem::DST + st * 16384), 16, 1024);
+        const uint64_t d_qm = make_smem_desc_sw128(smem_u32(smem + DkDvSmem::Q + kst * 16384), 8192, 1024);
+        const uint64_t d_dom = make_smem_desc_sw128(smem_u32(smem + DkDvSmem::DO + kst * 16384), 8192, 1024);
+        const uint32_t acc0 = it != 0;
+        if (leader) {
 #pragma unroll
-            for (int ks = 0; ks < 4; ++ks)
-              umma_f16_ss(tmem_DV, desc_advance(d_pt, ks * 32), desc_advance(d_dom, ks * 2048), idesc_acc,
-                          ks ? 1u : acc0);
+          for (int ks = 0; ks < 4; ++ks)
+            umma_f16_ss(tmem_DV, desc_advance(d_pt, ks * 32), desc_advance(d_dom, ks * 2048), idesc_acc,
+                        ks ? 1u : acc0);
 #pragma unroll
-            for (int ks = 0; ks < 4; ++ks)
-              umma_f16_ss(tmem_DK, desc_advance(d_dst, ks * 32), desc_advance(d_qm, ks * 2048), idesc_acc,
-                          ks ? 1u : acc0);
-          }
-          if (leader) umma_commit(&qdo_empty[kst]);
-          if (leader) umma_commit(&pds_empty[st]);
-          if (it + 1 == item.n_it) {
-            if (leader) umma_commit(acc_done);
-            if (w_next < n_items) {
-              if (!mbar_wait(kv_full, (n + 1) & 1, status, ERR_ATTN_WAIT) || !wait_sdp_inputs(g + 1)) {
-                ok = false;
-                break;
-              }
-              tc_fence_after();
-              issue_sdp(g + 1);
-              if (dkdv_item(w_next, Hkv, B, nq64, G).n_it == 1) if (leader) umma_commit(kv_empty);
-              primed = true;
-            }
-          }
+          for (int ks = 0; ks < 4; ++ks)
+            umma_f16_ss(tmem_DK, desc_advance(d_dst, ks * 32), desc_advance(d_qm, ks * 2048), idesc_acc,
+                        ks ? 1u : acc0);
+          umma_commit(&qdo_empty[kst]);
+          umma_commit(&pds_empty[st]);
+          if (it + 1 == item.n_it) umma_commit(acc_done);
         }
-        w = w_next;
       }
     }
   } else {
     const int quarter = warp & 3;
-    const int half = (warp - 2) >> 2;           // which 32 columns of the 64-column tile
-    const int etid = (warp - 2) * 32 + lane;    // 0..255 among the elementwise threads
+    const int grp = (warp - 2) >> 2;            // elementwise group = parity of the iterations it handles
+    const int gtid = ((warp - 2) & 3) * 32 + lane;   // 0..127 inside the group
     const int r = quarter * 32 + lane;          // kv row in tile
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     const float sl2 = scale * LOG2E;
     bool ok = true;
     int g = 0, n = 0;
-    // Row statistics (lse, D) of a 64-row q tile go through shared memory; the global loads for
-    // the next tile (of this or the next item) are issued at the top of an iteration and stored at
-    // its end, so their latency hides behind the elementwise work.
-    auto stat_load = [&](const DkDvItem& item, int it) -> float {
-      if (etid >= 128) return 0.f;
+    // Row statistics (lse, D) of a 64-row q tile go through shared memory (one buffer per group).  The
+    // global loads for the group's next tile (two iterations ahead, possibly in the next item) are issued
+    // at the top of an iteration and stored at its end (after a second group barrier: everyone has read
+    // the current ones), so their latency hides behind the elementwise work.
+    auto stat_load = [&](int w, int it) -> float {   // position (item w, iteration it), may run past the item
+      DkDvItem item = dkdv_item(w, Hkv, B, nq64, G);
+      while (it >= item.n_it) {
+        it -= item.n_it;
+        w = first_with_work(snake_next(w));
+        if (w >= n_items) return 0.f;
+        item = dkdv_item(w, Hkv, B, nq64, G);
+      }
       const int head_ = item.kvh * G + it / item.per_head;
       const int q0_ = (item.i_begin + it % item.per_head) * 64;
-      const int qc = min(q0_ + (etid & 63), S - 1);
+      const int qc = min(q0_ + (gtid & 63), S - 1);
       const size_t o = static_cast<size_t>(head_) * T + item.batch * S + qc;
-      return etid < 64 ? lse[o] * LOG2E : Dsum[o] * scale;
+      return gtid < 64 ? lse[o] * LOG2E : Dsum[o] * scale;
     };
-    auto stat_store = [&](int g_, float v) {
-      if (etid < 64) s_lse[(g_ & 1) * 64 + etid] = v;
-      else if (etid < 128) s_D[(g_ & 1) * 64 + (etid & 63)] = v;
+    auto stat_store = [&](float v) {
+      if (gtid < 64) s_lse[grp * 64 + gtid] = v;
+      else s_D[grp * 64 + (gtid & 63)] = v;
+    };
+    auto group_barrier = [&]() {
+      if (grp) asm volatile("bar.sync 2, 128;" ::: "memory");
+      else asm volatile("bar.sync 1, 128;" ::: "memory");
     };
     bool first = true;
     for (int w = blockIdx.x; w < n_items; w = snake_next(w)) {
@@ -293,8 +291,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_con
       const int kv_pos = item.jt * 128 + r;
       const int kv_row0 = item.batch * S + item.jt * 128;
       const bool in_range = kv_pos < S;
-      __nv_bfloat16* orow = half ? dk + static_cast<size_t>(kv_row0 + r) * ld_dk + item.kvh * 128
-                                 : dv + static_cast<size_t>(kv_row0 + r) * ld_dv + item.kvh * 128;
+      __nv_bfloat16* orow = grp ? dk + static_cast<size_t>(kv_row0 + r) * ld_dk + item.kvh * 128
+                                : dv + static_cast<size_t>(kv_row0 + r) * ld_dv + item.kvh * 128;
       if (item.n_it == 0) {   // no query sees this kv tile: zero gradients
         if (in_range) {
           const uint4 z = make_uint4(0, 0, 0, 0);
@@ -302,82 +300,93 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_con
         }
         continue;
       }
-      // the next item with work (its first tile's statistics are prefetched in the last iteration)
-      int wn = snake_next(w);
-      while (wn < n_items && dkdv_item(wn, Hkv, B, nq64, G).n_it == 0) wn = snake_next(wn);
-      if (first) {
-        stat_store(g, stat_load(item, 0));
-        first = false;
-      }
       for (int it = 0; it < item.n_it; ++it, ++g) {
-        const int st = g & 1;
+        if ((g & 1) != grp) continue;
+        const int st = grp;
         const uint32_t ph = (g >> 1) & 1;
         const int q0 = (item.i_begin + it % item.per_head) * 64;  // first q position of this tile
-        float next_stat = 0.f;
-        if (it + 1 < item.n_it) next_stat = stat_load(item, it + 1);
-        else if (wn < n_items) next_stat = stat_load(dkdv_item(wn, Hkv, B, nq64, G), 0);
-        ew_barrier();   // publishes this tile's statistics; every elementwise thread reaches it each
-                        // iteration, also after a failed wait
-        if (ok) ok = mbar_wait_warp(&sdp_full[st], ph, status, ERR_ATTN_WAIT);
-        if (!ok) continue;
-        tc_fence_after();
-        uint32_t ts[32], tp[32];
-        tmem_ld_32x32b_x32(tmem_ST + lane_off + st * 64 + half * 32, ts);
-        tmem_ld_32x32b_x32(tmem_DPT + lane_off + st * 64 + half * 32, tp);
-        tmem_ld_wait();
-        tc_fence_before();
-        mbar_arrive_warp(&sdp_empty[st]);
-        const float* lse_s = s_lse + st * 64 + half * 32;
-        const float* D_s = s_D + st * 64 + half * 32;
-        const int qb = q0 + half * 32;
-        const bool need_mask = (qb < item.jt * 128 + 128) || (qb + 32 > S) || (item.jt * 128 + 128 > S);
-        float pv[32], dsv[32];
-#pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          float p = fast_exp2(fmaf(__uint_as_float(ts[c]), sl2, -lse_s[c]));
-          if (need_mask) {
-            const int qp = qb + c;
-            if (!((qp < S) && (kv_pos <= qp) && (kv_pos < S))) p = 0.f;
-          }
-          pv[c] = p;
-          dsv[c] = p * fmaf(__uint_as_float(tp[c]), scale, -D_s[c]);   // D_s holds D * scale
+        if (first) {
+          stat_store(stat_load(w, it));
+          first = false;
         }
-        stat_store(g + 1, next_stat);   // slot (g+1)&1 was last read in iteration g-1
-        ok = mbar_wait_warp(&pds_empty[st], ph ^ 1, status, ERR_ATTN_WAIT);
-        if (!ok) continue;
+        const float next_stat = stat_load(w, it + 2);
+        group_barrier();   // publishes this tile's statistics; every thread of the group reaches both
+                           // barriers in each of the group's iterations, also after a failed wait
+        if (ok) ok = mbar_wait_warp(&sdp_full[st], ph, status, ERR_ATTN_WAIT);
+        if (!ok) {
+          group_barrier();
+          continue;
+        }
+        tc_fence_after();
         uint8_t* sPT = smem + DkDvSmem::PT + st * 16384 + r * 128;
         uint8_t* sDST = smem + DkDvSmem::DST + st * 16384 + r * 128;
 #pragma unroll
-        for (int c4 = 0; c4 < 4; ++c4) {
-          uint4 a, b;
-          a.x = pack_bf16x2(pv[c4 * 8 + 0], pv[c4 * 8 + 1]);
-          a.y = pack_bf16x2(pv[c4 * 8 + 2], pv[c4 * 8 + 3]);
-          a.z = pack_bf16x2(pv[c4 * 8 + 4], pv[c4 * 8 + 5]);
-          a.w = pack_bf16x2(pv[c4 * 8 + 6], pv[c4 * 8 + 7]);
-          b.x = pack_bf16x2(dsv[c4 * 8 + 0], dsv[c4 * 8 + 1]);
-          b.y = pack_bf16x2(dsv[c4 * 8 + 2], dsv[c4 * 8 + 3]);
-          b.z = pack_bf16x2(dsv[c4 * 8 + 4], dsv[c4 * 8 + 5]);
-          b.w = pack_bf16x2(dsv[c4 * 8 + 6], dsv[c4 * 8 + 7]);
-          const int sw = (((half * 4 + c4) ^ (r & 7)) << 4);
-          *reinterpret_cast<uint4*>(sPT + sw) = a;
-          *reinterpret_cast<uint4*>(sDST + sw) = b;
+        for (int half = 0; half < 2; ++half) {
+          uint32_t ts[32], tp[32];
+          tmem_ld_32x32b_x32(tmem_ST + lane_off + st * 64 + half * 32, ts);
+          tmem_ld_32x32b_x32(tmem_DPT + lane_off + st * 64 + half * 32, tp);
+          tmem_ld_wait();
+          if (half == 1) {
+            tc_fence_before();
+            mbar_arrive_warp(&sdp_empty[st]);   // both halves are in registers: the buffer may be refilled
+          }
+          const float* lse_s = s_lse + grp * 64 + half * 32;
+          const float* D_s = s_D + grp * 64 + half * 32;
+          const int qb = q0 + half * 32;
+          const bool need_mask = (qb < item.jt * 128 + 128) || (qb + 32 > S) || (item.jt * 128 + 128 > S);
+          float pv[32], dsv[32];
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            float p = fast_exp2(fmaf(__uint_as_float(ts[c]), sl2, -lse_s[c]));
+            if (need_mask) {
+              const int qp = qb + c;
+              if (!((qp < S) && (kv_pos <= qp) && (kv_pos < S))) p = 0.f;
+            }
+            pv[c] = p;
+            dsv[c] = p * fmaf(__uint_as_float(tp[c]), scale, -D_s[c]);   // D_s holds D * scale
+          }
+          if (half == 0) {
+            ok = mbar_wait_warp(&pds_empty[st], ph ^ 1, status, ERR_ATTN_WAIT);
+            if (!ok) break;
+          }
+#pragma unroll
+          for (int c4 = 0; c4 < 4; ++c4) {
+            uint4 a, b;
+            a.x = pack_bf16x2(pv[c4 * 8 + 0], pv[c4 * 8 + 1]);
+            a.y = pack_bf16x2(pv[c4 * 8 + 2], pv[c4 * 8 + 3]);
+            a.z = pack_bf16x2(pv[c4 * 8 + 4], pv[c4 * 8 + 5]);
+            a.w = pack_bf16x2(pv[c4 * 8 + 6], pv[c4 * 8 + 7]);
+            b.x = pack_bf16x2(dsv[c4 * 8 + 0], dsv[c4 * 8 + 1]);
+            b.y = pack_bf16x2(dsv[c4 * 8 + 2], dsv[c4 * 8 + 3]);
+            b.z = pack_bf16x2(dsv[c4 * 8 + 4], dsv[c4 * 8 + 5]);
+            b.w = pack_bf16x2(dsv[c4 * 8 + 6], dsv[c4 * 8 + 7]);
+            const int sw = (((half * 4 + c4) ^ (r & 7)) << 4);
+            *reinterpret_cast<uint4*>(sPT + sw) = a;
+            *reinterpret_cast<uint4*>(sDST + sw) = b;
+          }
         }
+        group_barrier();          // every thread of the group has read this tile's statistics
+        stat_store(next_stat);
+        if (!ok) continue;
         fence_proxy_async_smem();
         tc_fence_before();
         mbar_arrive_warp(&pds_full[st]);
       }
-      // write-out: the first column group stores dV, the second dK.  The next item's first dV/dK MMAs
-      // are ordered after it by this warp's next pds_full arrive.
+      // write-out: group 0 stores dV, group 1 dK
       if (ok) ok = mbar_wait_warp(acc_done, n & 1, status, ERR_ATTN_WAIT);
       ++n;
       if (!ok) continue;
       tc_fence_after();
-      const uint32_t tb = (half ? tmem_DK : tmem_DV) + lane_off;
+      const uint32_t tb = (grp ? tmem_DK : tmem_DV) + lane_off;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t t[32];
         tmem_ld_32x32b_x32(tb + c * 32, t);
         tmem_ld_wait();
+        if (c == 3) {
+          tc_fence_before();
+          mbar_arrive_warp(acc_free);   // this warp's part of the accumulators is in registers
+        }
         if (in_range) {
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
@@ -390,7 +399,6 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_con
           }
         }
       }
-      tc_fence_before();
     }
   }
 
@@ -436,6 +444,14 @@ __device__ __forceinline__ DqItem dq_item(int w, int num_q_tiles, int Hq, int B,
   return it;
 }
 
+// Roles (ATB_THREADS = 352): warp 0 streams tiles with TMA; warp 1 issues the S / dP MMAs; warp 10
+// issues the dQ MMAs; warps 2..5 (group 0) do the elementwise step of the even global iterations and
+// warps 6..9 (group 1) that of the odd ones, each thread owning one q row and all 64 kv columns of its
+// iteration (two passes of 32).  With two groups every elementwise chain (wait for S/dP, tcgen05.ld,
+// exp2 / dS, swizzled stores, arrive) has two iterations of time, and with two issuing warps the 16
+// S/dP instructions of iteration g+1 and the 4 dQ instructions of iteration g are issued concurrently:
+// a single issuing lane and a single elementwise group each needed ~1900 cycles per iteration against
+// ~800 cycles of tensor work.
 __global__ void __launch_bounds__(ATB_THREADS, 1)
 attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmdO,
                    const __grid_constant__ CUtensorMap tmK64, const __grid_constant__ CUtensorMap tmV64,
@@ -455,7 +471,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint64_t* ds_empty = bars + 13;  // [2]
   uint64_t* acc_done = bars + 15;
   uint64_t* q_empty = bars + 16;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
+  uint64_t* acc_free = bars + 17;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_q_tiles = (S + 127) / 128;
@@ -473,11 +490,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&sdp_full[i], 1);
-      mbar_init(&sdp_empty[i], 8);   // one arrive per elementwise warp
-      mbar_init(&ds_full[i], 8);
+      mbar_init(&sdp_empty[i], 4);   // one arrive per warp of the group that owns buffer i
+      mbar_init(&ds_full[i], 4);
       mbar_init(&ds_empty[i], 1);
     }
     mbar_init(acc_done, 1);
+    mbar_init(acc_free, 8);          // every elementwise warp, after it has read its part of dQ
     mbar_fence_init();
   }
   if (warp == 1) {
@@ -523,18 +541,25 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
     }
   } else if (warp == 1) {
-    // The whole warp runs this (uniform) control flow so that descriptors and addresses stay in the
-    // uniform datapath; only the tcgen05 instructions themselves are issued by one elected lane.
-    {
-      const bool leader = elect_one();
-      constexpr uint32_t idesc_s = make_idesc_f16(1, 128, 64, 0, 0);     // [128 q] x [64 kv], K = d
-      constexpr uint32_t idesc_acc = make_idesc_f16(1, 128, 128, 0, 1);  // [128 q] x [128 d], K = kv
-      const uint64_t d_q = make_smem_desc_sw128(smem_u32(smem + DqSmem::Q), 16, 1024);
-      const uint64_t d_do = make_smem_desc_sw128(smem_u32(smem + DqSmem::DO), 16, 1024);
-      // S/dP of global iteration g (ring stage g % STAGES, TMEM buffer g & 1)
-      auto issue_sdp = [&](int g) {
+    // ---- S = Q K^T and dP = dO V^T of every global iteration (uniform control flow, one issuing lane) ----
+    const bool leader = elect_one();
+    constexpr uint32_t idesc_s = make_idesc_f16(1, 128, 64, 0, 0);     // [128 q] x [64 kv], K = d
+    const uint64_t d_q = make_smem_desc_sw128(smem_u32(smem + DqSmem::Q), 16, 1024);
+    const uint64_t d_do = make_smem_desc_sw128(smem_u32(smem + DqSmem::DO), 16, 1024);
+    int g = 0, n = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < n_items && ok; w = snake_next(w), ++n) {
+      const DqItem item = dq_item(w, num_q_tiles, Hq, B, nkv64);
+      if (!mbar_wait(q_full, n & 1, status, ERR_ATTN_WAIT)) break;
+      for (int it = 0; it < item.n_it; ++it, ++g) {
         const int st = g & 1;
         const int ks_ = g % ATB_STAGES;
+        if (!mbar_wait(&kv_full[ks_], (g / ATB_STAGES) & 1, status, ERR_ATTN_WAIT) ||
+            !mbar_wait(&sdp_empty[st], ((g >> 1) & 1) ^ 1, status, ERR_ATTN_WAIT)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
         const uint64_t d_k = make_smem_desc_sw128(smem_u32(smem + DqSmem::K + ks_ * 16384), 16, 1024);
         const uint64_t d_v = make_smem_desc_sw128(smem_u32(smem + DqSmem::V + ks_ * 16384), 16, 1024);
         if (leader) {
@@ -550,73 +575,47 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
             const uint32_t ob = (ks >> 2) * 8192 + (ks & 3) * 32;
             umma_f16_ss(tmem_DP + st * 64, desc_advance(d_do, oa), desc_advance(d_v, ob), idesc_s, ks != 0);
           }
+          umma_commit(&sdp_full[st]);
+          if (it + 1 == item.n_it) umma_commit(q_empty);   // last S/dP of the item: Q/dO may be reloaded
         }
-        if (leader) umma_commit(&sdp_full[st]);
-      };
-      auto wait_sdp_inputs = [&](int g) -> bool {
-        return mbar_wait(&kv_full[g % ATB_STAGES], (g / ATB_STAGES) & 1, status, ERR_ATTN_WAIT) &&
-               mbar_wait(&sdp_empty[g & 1], ((g >> 1) & 1) ^ 1, status, ERR_ATTN_WAIT);
-      };
-      int g = 0, n = 0;
-      bool ok = true;
-      // S/dP run one iteration ahead of dQ, also across the item boundary: the first S/dP of the next
-      // item is issued (after its Q/dO landed) before this item's last dQ MMA.
-      bool primed = false;   // S/dP of (this item, iteration 0) already issued
-      for (int w = blockIdx.x; w < n_items && ok; w = snake_next(w), ++n) {
-        const DqItem item = dq_item(w, num_q_tiles, Hq, B, nkv64);
-        const bool has_next = snake_next(w) < n_items;
-        if (!primed) {
-          ok = mbar_wait(q_full, n & 1, status, ERR_ATTN_WAIT) && wait_sdp_inputs(g);
-          if (!ok) break;
-          tc_fence_after();
-          issue_sdp(g);
-          if (item.n_it == 1) if (leader) umma_commit(q_empty);
+      }
+    }
+  } else if (warp == 10) {
+    // ---- dQ += dS K of every global iteration ------------------------------------------------------
+    const bool leader = elect_one();
+    constexpr uint32_t idesc_acc = make_idesc_f16(1, 128, 128, 0, 1);  // [128 q] x [128 d], K = kv
+    int g = 0, n = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < n_items && ok; w = snake_next(w), ++n) {
+      const DqItem item = dq_item(w, num_q_tiles, Hq, B, nkv64);
+      // the elementwise warps must have read the previous item's dQ before it is overwritten
+      if (n > 0 && !mbar_wait(acc_free, (n - 1) & 1, status, ERR_ATTN_WAIT)) break;
+      for (int it = 0; it < item.n_it; ++it, ++g) {
+        const int st = g & 1;
+        const int kst = g % ATB_STAGES;
+        if (!mbar_wait(&kv_full[kst], (g / ATB_STAGES) & 1, status, ERR_ATTN_WAIT) ||
+            !mbar_wait(&ds_full[st], (g >> 1) & 1, status, ERR_ATTN_WAIT)) {
+          ok = false;
+          break;
         }
-        primed = false;
-        for (int it = 0; it < item.n_it; ++it, ++g) {
-          if (it + 1 < item.n_it) {
-            if (!wait_sdp_inputs(g + 1)) { ok = false; break; }
-            tc_fence_after();
-            issue_sdp(g + 1);
-            if (it + 2 == item.n_it) if (leader) umma_commit(q_empty);   // last S/dP of the item: Q/dO may be reloaded
-          }
-          const int st = g & 1;
-          if (!mbar_wait(&ds_full[st], (g >> 1) & 1, status, ERR_ATTN_WAIT)) { ok = false; break; }
-          tc_fence_after();
-          const int kst = g % ATB_STAGES;
-          const uint64_t d_ds = make_smem_desc_sw128(smem_u32(smem + DqSmem::DS + st * 16384), 16, 1024);
-          const uint64_t d_km = make_smem_desc_sw128(smem_u32(smem + DqSmem::K + kst * 16384), 8192, 1024);
-          const uint32_t acc0 = it != 0;
-          if (leader) {
+        tc_fence_after();
+        const uint64_t d_ds = make_smem_desc_sw128(smem_u32(smem + DqSmem::DS + st * 16384), 16, 1024);
+        const uint64_t d_km = make_smem_desc_sw128(smem_u32(smem + DqSmem::K + kst * 16384), 8192, 1024);
+        const uint32_t acc0 = it != 0;
+        if (leader) {
 #pragma unroll
-            for (int ks = 0; ks < 4; ++ks)
-              umma_f16_ss(tmem_DQ, desc_advance(d_ds, ks * 32), desc_advance(d_km, ks * 2048), idesc_acc,
-                          ks ? 1u : acc0);
-          }
-          if (leader) umma_commit(&kv_empty[kst]);
-          if (leader) umma_commit(&ds_empty[st]);
-          if (it + 1 == item.n_it) {
-            if (leader) umma_commit(acc_done);
-            if (has_next) {
-              // the next item's Q/dO were requested when q_empty fired; its first S/dP is issued as
-              // soon as they land, while the elementwise warps write this item's dQ out
-              if (!mbar_wait(q_full, (n + 1) & 1, status, ERR_ATTN_WAIT) || !wait_sdp_inputs(g + 1)) {
-                ok = false;
-                break;
-              }
-              tc_fence_after();
-              issue_sdp(g + 1);
-              const DqItem nxt = dq_item(snake_next(w), num_q_tiles, Hq, B, nkv64);
-              if (nxt.n_it == 1) if (leader) umma_commit(q_empty);
-              primed = true;
-            }
-          }
+          for (int ks = 0; ks < 4; ++ks)
+            umma_f16_ss(tmem_DQ, desc_advance(d_ds, ks * 32), desc_advance(d_km, ks * 2048), idesc_acc,
+                        ks ? 1u : acc0);
+          umma_commit(&kv_empty[kst]);
+          umma_commit(&ds_empty[st]);
+          if (it + 1 == item.n_it) umma_commit(acc_done);
         }
       }
     }
   } else {
     const int quarter = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int grp = (warp - 2) >> 2;            // elementwise group = parity of the iterations it handles
     const int r = quarter * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     const float sl2 = scale * LOG2E;
@@ -641,53 +640,64 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (snake_next(w) < n_items)
         row_stats(dq_item(snake_next(w), num_q_tiles, Hq, B, nkv64), &lse_n, &D_n);
       for (int it = 0; it < item.n_it; ++it, ++g) {
-        const int st = g & 1;
+        if ((g & 1) != grp) continue;
+        const int st = grp;
         const uint32_t ph = (g >> 1) & 1;
         if (!mbar_wait_warp(&sdp_full[st], ph, status, ERR_ATTN_WAIT)) { ok = false; break; }
         tc_fence_after();
-        uint32_t ts[32], tp[32];
-        tmem_ld_32x32b_x32(tmem_S + lane_off + st * 64 + half * 32, ts);
-        tmem_ld_32x32b_x32(tmem_DP + lane_off + st * 64 + half * 32, tp);
-        tmem_ld_wait();
-        tc_fence_before();
-        mbar_arrive_warp(&sdp_empty[st]);
-        const int k0 = it * 64 + half * 32;
-        const bool need_mask = (k0 + 32 > qt * 128) || (k0 + 32 > S) || (qt * 128 + 128 > S);
-        float dsv[32];
-#pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          float p = fast_exp2(fmaf(__uint_as_float(ts[c]), sl2, -lse_r));
-          if (need_mask) {
-            const int kp = k0 + c;
-            if (!((q_pos < S) && (kp <= q_pos) && (kp < S))) p = 0.f;
-          }
-          dsv[c] = p * fmaf(__uint_as_float(tp[c]), scale, -D_r);   // D_r holds D * scale
-        }
-        if (!mbar_wait_warp(&ds_empty[st], ph ^ 1, status, ERR_ATTN_WAIT)) { ok = false; break; }
         uint8_t* sDS = smem + DqSmem::DS + st * 16384 + r * 128;
 #pragma unroll
-        for (int c4 = 0; c4 < 4; ++c4) {
-          uint4 b;
-          b.x = pack_bf16x2(dsv[c4 * 8 + 0], dsv[c4 * 8 + 1]);
-          b.y = pack_bf16x2(dsv[c4 * 8 + 2], dsv[c4 * 8 + 3]);
-          b.z = pack_bf16x2(dsv[c4 * 8 + 4], dsv[c4 * 8 + 5]);
-          b.w = pack_bf16x2(dsv[c4 * 8 + 6], dsv[c4 * 8 + 7]);
-          *reinterpret_cast<uint4*>(sDS + (((half * 4 + c4) ^ (r & 7)) << 4)) = b;
+        for (int half = 0; half < 2; ++half) {
+          uint32_t ts[32], tp[32];
+          tmem_ld_32x32b_x32(tmem_S + lane_off + st * 64 + half * 32, ts);
+          tmem_ld_32x32b_x32(tmem_DP + lane_off + st * 64 + half * 32, tp);
+          tmem_ld_wait();
+          if (half == 1) {
+            tc_fence_before();
+            mbar_arrive_warp(&sdp_empty[st]);   // both halves are in registers: S/dP buffer may be refilled
+          }
+          const int k0 = it * 64 + half * 32;
+          const bool need_mask = (k0 + 32 > qt * 128) || (k0 + 32 > S) || (qt * 128 + 128 > S);
+          float dsv[32];
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            float p = fast_exp2(fmaf(__uint_as_float(ts[c]), sl2, -lse_r));
+            if (need_mask) {
+              const int kp = k0 + c;
+              if (!((q_pos < S) && (kp <= q_pos) && (kp < S))) p = 0.f;
+            }
+            dsv[c] = p * fmaf(__uint_as_float(tp[c]), scale, -D_r);   // D_r holds D * scale
+          }
+          if (half == 0 && !mbar_wait_warp(&ds_empty[st], ph ^ 1, status, ERR_ATTN_WAIT)) { ok = false; break; }
+#pragma unroll
+          for (int c4 = 0; c4 < 4; ++c4) {
+            uint4 b;
+            b.x = pack_bf16x2(dsv[c4 * 8 + 0], dsv[c4 * 8 + 1]);
+            b.y = pack_bf16x2(dsv[c4 * 8 + 2], dsv[c4 * 8 + 3]);
+            b.z = pack_bf16x2(dsv[c4 * 8 + 4], dsv[c4 * 8 + 5]);
+            b.w = pack_bf16x2(dsv[c4 * 8 + 6], dsv[c4 * 8 + 7]);
+            *reinterpret_cast<uint4*>(sDS + (((half * 4 + c4) ^ (r & 7)) << 4)) = b;
+          }
         }
+        if (!ok) break;
         fence_proxy_async_smem();
         tc_fence_before();
         mbar_arrive_warp(&ds_full[st]);
       }
       if (!ok || !mbar_wait_warp(acc_done, n & 1, status, ERR_ATTN_WAIT)) { ok = false; break; }
       tc_fence_after();
-      // write-out; the next item's first dQ MMA is ordered after it by this warp's next ds_full arrive
+      // write-out: group 0 stores dQ columns 0..63, group 1 columns 64..127
       const bool in_range = q_pos < S;
-      __nv_bfloat16* orow = dq + (static_cast<size_t>(row0 + r) * Hq + item.head) * 128 + half * 64;
+      __nv_bfloat16* orow = dq + (static_cast<size_t>(row0 + r) * Hq + item.head) * 128 + grp * 64;
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t t[32];
-        tmem_ld_32x32b_x32(tmem_DQ + lane_off + half * 64 + c * 32, t);
+        tmem_ld_32x32b_x32(tmem_DQ + lane_off + grp * 64 + c * 32, t);
         tmem_ld_wait();
+        if (c == 1) {
+          tc_fence_before();
+          mbar_arrive_warp(acc_free);   // this warp's part of dQ is in registers
+        }
         if (in_range) {
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
@@ -700,7 +710,6 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           }
         }
       }
-      tc_fence_before();
       lse_r = lse_n;
       D_r = D_n;
     }
