@@ -356,7 +356,7 @@ class ParallelTransformerModel(nn.Module):
         return self.logits_from_hidden(h).reshape(B, S, -1)
 
     def loss(self, input_ids: torch.Tensor, labels: torch.Tensor, loss_scale: float = 1.0,
-             hidden: Optional[torch.Tensor] = None) -> torch.Tensor:
+             hidden: Optional[torch.Tensor] = None, valid_idx: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Next-token CE with the shift done on the labels (``labels[:, t]`` supervises the logits at
         ``t-1``); ``-100`` is ignored.  Same value as the reference's shifted ``F.cross_entropy``
         (src/engines/train_engine.py:44-50)."""
@@ -368,7 +368,8 @@ class ParallelTransformerModel(nn.Module):
         if self.compact_ignored_rows:
             # masked positions (prompt tokens, padding) add nothing to the loss or its gradient: run the
             # LM head on the supervised rows only
-            idx = ops.valid_rows(shifted)
+            # ``valid_idx``: the caller already knows the supervised rows (computed on the host)
+            idx = valid_idx if valid_idx is not None else ops.valid_rows(shifted)
             if idx is not None:
                 if idx.numel() == 0:
                     return h.float().sum() * 0.0

@@ -271,13 +271,22 @@ class TrainEngine:
     def sft_step_tensors(self, input_ids: torch.Tensor, labels: torch.Tensor, sync: bool = True):
         """SFT step on ready ``[B,S]`` tensors (host tensors are copied to the device asynchronously).
         ``sync=False`` returns ``(loss_tensor, grad_norm_tensor_or_None)`` without a host sync."""
+        valid_idx = None
         if input_ids.device != self.device:
+            if labels.device.type == "cpu" and self.device.type == "cuda":
+                # the supervised rows (label of the next token is not -100) are known on the host before the
+                # copy: ship their indices along, so the LM head never needs a device -> host count
+                nxt = torch.full_like(labels, -100)
+                nxt[:, :-1] = labels[:, 1:]
+                idx = torch.nonzero(nxt.reshape(-1) != -100).squeeze(-1)
+                if idx.numel() < nxt.numel():
+                    valid_idx = idx.pin_memory().to(self.device, non_blocking=True)
             input_ids = input_ids.to(self.device, non_blocking=True)
             labels = labels.to(self.device, non_blocking=True)
         if self.pp_context is not None and self.pp_context.pp_size > 1:
             loss, gn = self._pp_batch_step(input_ids, labels)
         else:
-            loss, gn = self._single_batch_step(input_ids, labels)
+            loss, gn = self._single_batch_step(input_ids, labels, valid_idx)
         if not sync:
             if gn is not None:   # optimistic bookkeeping; call resolve_step(gn) to apply the NaN guard
                 self.lr_scheduler.step()
@@ -291,11 +300,12 @@ class TrainEngine:
             self.metrics_collector.record("loss", lv)
         return TrainMetrics(lv, lv, 0.0, g, lr, self.step_count)
 
-    def _single_batch_step(self, input_ids, labels):
+    def _single_batch_step(self, input_ids, labels, valid_idx=None):
         cfg, opt = self.config, self.optimizer
         opt.pre_forward()
         opt.begin_backward(sync=self._accumulation_count + 1 >= cfg.gradient_accumulation_steps)
-        loss = self.model.loss(input_ids, labels, loss_scale=1.0 / cfg.gradient_accumulation_steps)
+        loss = self.model.loss(input_ids, labels, loss_scale=1.0 / cfg.gradient_accumulation_steps,
+                               valid_idx=valid_idx)
         loss.backward()
         opt.post_backward()
         self._accumulation_count += 1

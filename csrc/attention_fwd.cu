@@ -1,13 +1,10 @@
 // Causal flash-attention forward for sm_100a (head_dim 128, GQA), tcgen05 MMAs with S and O in TMEM.
 //
 // A work item is one 128-row query tile of one (batch, q-head); a persistent CTA per SM walks the
-// items.  Warp 0 streams K/V tiles with TMA
-// (two stages each), warp 1 issues the MMAs, warps 2..5 (128 threads, one query row each) run the
-// online softmax: they read S from TMEM, write P (bf16) to shared memory in the 128-byte-swizzled
+// items.  The softmax warps read S from TMEM, write P (bf16) to shared memory in the 128-byte-swizzled
 // K-major layout the PV MMA consumes, and rescale the O accumulator in TMEM only when the running
 // row maximum grew by more than 2^8 (the final normalisation uses the same reference maximum for
 // P and for the row sum, so a stale maximum is exact as long as nothing overflows).
-// S is double-buffered so that Q*K^T of tile j+1 overlaps the softmax of tile j.
 //
 // Layouts: q [T, Hq*128], k [T, Hkv*128], v [T, ld_v] (a column slice of the fused projection output),
 // out [T, Hq*128], lse [Hq, T] (natural log, scaled scores).  T = B*S; sequence b owns rows b*S..b*S+S-1.
@@ -16,7 +13,7 @@
 
 namespace b2 {
 
-constexpr int AT_THREADS = 192;
+constexpr int AT_THREADS = 352;  // warp 0 TMA, warps 1 and 10 MMA issue, warps 2..9 softmax (two threads per row)
 constexpr int AT_TILE_BYTES = 128 * 128 * 2;  // 32 KiB: two [128 x 64] swizzled halves
 constexpr int AT_HALF_BYTES = 128 * 64 * 2;
 
@@ -25,9 +22,9 @@ struct AttnFwdSmem {
   static constexpr int Q = 0;
   static constexpr int K = Q + AT_TILE_BYTES;           // 2 stages
   static constexpr int V = K + 2 * AT_TILE_BYTES;       // 2 stages
-  static constexpr int P = V + 2 * AT_TILE_BYTES;
-  static constexpr int BARS = P + AT_TILE_BYTES;        // 196608
-  static constexpr int TOTAL = BARS + 256 + 1024;
+  static constexpr int P = V + 2 * AT_TILE_BYTES;       // 2 tiles
+  static constexpr int BARS = P + 2 * AT_TILE_BYTES;    // 229376: barriers (256 B), then the row exchange buffer (1 KiB)
+  static constexpr int TOTAL = BARS + 256 + 1024 + 1024;
 };
 
 // One work item: a 128-row query tile of one (batch, q head).
@@ -71,10 +68,16 @@ __device__ __forceinline__ int fwd_next_active(int w, int n_items, const FwdPara
   return x;
 }
 
-// Persistent: each CTA walks its share of the items (heaviest tiles first, dealt in boustrophedon order).  Barriers, TMEM and
-// the K/V ring live across items; the next item's Q is requested as soon as the last Q*K^T of the
-// current item retires, and its first Q*K^T is issued while the softmax warps write the current
-// item's output.
+// Persistent: each CTA walks its share of the items (heaviest tiles first, dealt in boustrophedon order).
+// Barriers, TMEM and the K/V ring live across items; the next item's Q is requested as soon as the last
+// Q*K^T of the current item retires.
+//
+// Roles (AT_THREADS = 352): warp 0 streams K/V with TMA, warp 1 issues the Q*K^T MMAs, warp 10 the P*V
+// MMAs, warps 2..9 run the softmax.  A query row is shared by two threads (warps w and w+4 touch the same
+// TMEM lane quarter): each takes 64 of the tile's 128 key columns, the pair exchanges its partial row
+// maximum through shared memory and keeps partial row sums that are added at the end.  S and P are
+// double-buffered, so the softmax of tile j+1 never waits for P*V of tile j unless the running maximum
+// grew enough to force a rescale of O.
 __global__ void __launch_bounds__(AT_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, __nv_bfloat16* __restrict__ out,
@@ -90,10 +93,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* v_empty = bars + 7;   // [2]
   uint64_t* s_full = bars + 9;    // [2]
   uint64_t* s_empty = bars + 11;  // [2]
-  uint64_t* p_full = bars + 13;
-  uint64_t* pv_done = bars + 14;
-  uint64_t* q_empty = bars + 15;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  uint64_t* p_full = bars + 13;   // [2]
+  uint64_t* pv_done = bars + 15;  // [2]
+  uint64_t* q_empty = bars + 17;
+  uint64_t* o_free = bars + 18;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
+  float* xchg = reinterpret_cast<float*>(smem + AttnFwdSmem::BARS + 256);   // [2 column halves][128 rows]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int Hq = prm.Hq;
@@ -102,16 +107,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
     mbar_init(q_empty, 1);
+    mbar_init(o_free, 8);            // every softmax warp, after it has read its part of O
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1);
       mbar_init(&v_full[i], 1);
       mbar_init(&k_empty[i], 1);
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 4);   // one arrive per softmax warp
+      mbar_init(&s_empty[i], 8);     // one arrive per softmax warp
+      mbar_init(&p_full[i], 8);
+      mbar_init(&pv_done[i], 1);
     }
-    mbar_init(p_full, 4);
-    mbar_init(pv_done, 1);
     mbar_fence_init();
     tma_prefetch_desc(&tmQ);
     tma_prefetch_desc(&tmK);
@@ -159,139 +165,143 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
     }
   } else if (warp == 1) {
-    // The whole warp runs this (uniform) control flow so that descriptors and addresses stay in the
-    // uniform datapath; only the tcgen05 instructions themselves are issued by one elected lane.
-    {
-      const bool leader = elect_one();
-      constexpr uint32_t idesc_s = make_idesc_f16(1, 128, 128, 0, 0);
-      constexpr uint32_t idesc_pv = make_idesc_f16(1, 128, 128, 0, 1);
-      const uint64_t d_q = make_smem_desc_sw128(smem_u32(smem + AttnFwdSmem::Q), 16, 1024);
-      const uint64_t d_p = make_smem_desc_sw128(smem_u32(smem + AttnFwdSmem::P), 16, 1024);
-      // Q*K^T of global iteration g: K stage g & 1, S buffer g & 1
-      auto issue_s = [&](int g) {
-        const uint64_t d_k = make_smem_desc_sw128(smem_u32(smem + AttnFwdSmem::K + (g & 1) * AT_TILE_BYTES), 16, 1024);
+    // ---- S = Q K^T of every global iteration (uniform control flow, one issuing lane) --------------
+    const bool leader = elect_one();
+    constexpr uint32_t idesc_s = make_idesc_f16(1, 128, 128, 0, 0);
+    const uint64_t d_q = make_smem_desc_sw128(smem_u32(smem + AttnFwdSmem::Q), 16, 1024);
+    int g = 0, n = 0;
+    bool ok = true;
+    for (int w = w0; w < n_items && ok; w = fwd_next_active(w, n_items, prm), ++n) {
+      const FwdItem item = fwd_item(w, prm);
+      if (!mbar_wait(q_full, n & 1, status, ERR_ATTN_WAIT)) break;
+      for (int j = 0; j < item.n_kv; ++j, ++g) {
+        const int st = g & 1;
+        if (!mbar_wait(&k_full[st], (g >> 1) & 1, status, ERR_ATTN_WAIT) ||
+            !mbar_wait(&s_empty[st], ((g >> 1) & 1) ^ 1, status, ERR_ATTN_WAIT)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint64_t d_k = make_smem_desc_sw128(smem_u32(smem + AttnFwdSmem::K + st * AT_TILE_BYTES), 16, 1024);
         if (leader) {
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
             const uint32_t o = (ks >> 2) * AT_HALF_BYTES + (ks & 3) * 32;
-            umma_f16_ss(tmem_S + (g & 1) * 128, desc_advance(d_q, o), desc_advance(d_k, o), idesc_s, ks != 0);
+            umma_f16_ss(tmem_S + st * 128, desc_advance(d_q, o), desc_advance(d_k, o), idesc_s, ks != 0);
           }
+          umma_commit(&k_empty[st]);
+          umma_commit(&s_full[st]);
+          if (j + 1 == item.n_kv) umma_commit(q_empty);   // last Q*K^T of the item: Q may be reloaded
         }
-        if (leader) umma_commit(&k_empty[g & 1]);
-        if (leader) umma_commit(&s_full[g & 1]);
-      };
-      auto wait_s_inputs = [&](int g) -> bool {
-        return mbar_wait(&k_full[g & 1], (g >> 1) & 1, status, ERR_ATTN_WAIT) &&
-               mbar_wait(&s_empty[g & 1], ((g >> 1) & 1) ^ 1, status, ERR_ATTN_WAIT);
-      };
-      int g = 0, n = 0;
-      bool ok = true, primed = false;
-      for (int w = w0; w < n_items && ok; ++n) {
-        const FwdItem item = fwd_item(w, prm);
-        const int w_next = fwd_next_active(w, n_items, prm);
-        if (!primed) {
-          ok = mbar_wait(q_full, n & 1, status, ERR_ATTN_WAIT) && wait_s_inputs(g);
-          if (!ok) break;
-          tc_fence_after();
-          issue_s(g);
-          if (item.n_kv == 1) if (leader) umma_commit(q_empty);
+      }
+    }
+  } else if (warp == 10) {
+    // ---- O += P V of every global iteration ------------------------------------------------------
+    const bool leader = elect_one();
+    constexpr uint32_t idesc_pv = make_idesc_f16(1, 128, 128, 0, 1);
+    int g = 0, n = 0;
+    bool ok = true;
+    for (int w = w0; w < n_items && ok; w = fwd_next_active(w, n_items, prm), ++n) {
+      const FwdItem item = fwd_item(w, prm);
+      // the softmax warps must have read the previous item's O before it is overwritten
+      if (n > 0 && !mbar_wait(o_free, (n - 1) & 1, status, ERR_ATTN_WAIT)) break;
+      for (int j = 0; j < item.n_kv; ++j, ++g) {
+        const int st = g & 1;
+        if (!mbar_wait(&p_full[st], (g >> 1) & 1, status, ERR_ATTN_WAIT) ||
+            !mbar_wait(&v_full[st], (g >> 1) & 1, status, ERR_ATTN_WAIT)) {
+          ok = false;
+          break;
         }
-        primed = false;
-        for (int j = 0; j < item.n_kv; ++j, ++g) {
-          if (j + 1 < item.n_kv) {
-            if (!wait_s_inputs(g + 1)) { ok = false; break; }
-            tc_fence_after();
-            issue_s(g + 1);
-            if (j + 2 == item.n_kv) if (leader) umma_commit(q_empty);   // last Q*K^T of the item: Q may be reloaded
-          }
-          if (!mbar_wait(p_full, g & 1, status, ERR_ATTN_WAIT) ||
-              !mbar_wait(&v_full[g & 1], (g >> 1) & 1, status, ERR_ATTN_WAIT)) {
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          const uint64_t d_v = make_smem_desc_sw128(smem_u32(smem + AttnFwdSmem::V + (g & 1) * AT_TILE_BYTES),
-                                                    AT_HALF_BYTES, 1024);
-          const uint32_t acc0 = j != 0;
-          if (leader) {
+        tc_fence_after();
+        const uint64_t d_p = make_smem_desc_sw128(smem_u32(smem + AttnFwdSmem::P + st * AT_TILE_BYTES), 16, 1024);
+        const uint64_t d_v = make_smem_desc_sw128(smem_u32(smem + AttnFwdSmem::V + st * AT_TILE_BYTES),
+                                                  AT_HALF_BYTES, 1024);
+        const uint32_t acc0 = j != 0;
+        if (leader) {
 #pragma unroll
-            for (int ks = 0; ks < 8; ++ks) {
-              const uint32_t o = (ks >> 2) * AT_HALF_BYTES + (ks & 3) * 32;
-              umma_f16_ss(tmem_O, desc_advance(d_p, o), desc_advance(d_v, ks * 2048), idesc_pv, ks ? 1u : acc0);
-            }
+          for (int ks = 0; ks < 8; ++ks) {
+            const uint32_t o = (ks >> 2) * AT_HALF_BYTES + (ks & 3) * 32;
+            umma_f16_ss(tmem_O, desc_advance(d_p, o), desc_advance(d_v, ks * 2048), idesc_pv, ks ? 1u : acc0);
           }
-          if (leader) umma_commit(&v_empty[g & 1]);
-          if (leader) umma_commit(pv_done);
-          if (j + 1 == item.n_kv && w_next < n_items) {
-            if (!mbar_wait(q_full, (n + 1) & 1, status, ERR_ATTN_WAIT) || !wait_s_inputs(g + 1)) {
-              ok = false;
-              break;
-            }
-            tc_fence_after();
-            issue_s(g + 1);
-            if (fwd_item(w_next, prm).n_kv == 1) if (leader) umma_commit(q_empty);
-            primed = true;
-          }
+          umma_commit(&v_empty[st]);
+          umma_commit(&pv_done[st]);
         }
-        w = w_next;
       }
     }
   } else {
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;         // which 64 key columns of every tile this thread handles
     const int r = quarter * 32 + lane;        // query row inside the tile
     const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     const float sl2 = scale * 1.4426950408889634f;
-    uint8_t* sP = smem + AttnFwdSmem::P;
+    // the two threads of a row meet at a 64-thread named barrier (one per lane quarter)
+    auto pair_barrier = [&]() {
+      switch (quarter) {
+        case 0: asm volatile("bar.sync 1, 64;" ::: "memory"); break;
+        case 1: asm volatile("bar.sync 2, 64;" ::: "memory"); break;
+        case 2: asm volatile("bar.sync 3, 64;" ::: "memory"); break;
+        default: asm volatile("bar.sync 4, 64;" ::: "memory"); break;
+      }
+    };
     bool ok = true;
-    int g = 0;
-    for (int w = w0; w < n_items && ok; w = fwd_next_active(w, n_items, prm)) {
+    int g = 0, n = 0;
+    for (int w = w0; w < n_items && ok; w = fwd_next_active(w, n_items, prm), ++n) {
       const FwdItem item = fwd_item(w, prm);
       const int q_idx = item.qt * 128 + r;      // index among this sequence's queries
       const int q_pos = item.kv_off + q_idx;    // last key this query may see
-      float m_used = -INFINITY, l = 0.f;
+      float m_used = -INFINITY, l = 0.f;        // l: this thread's 64 columns only
       for (int j = 0; j < item.n_kv; ++j, ++g) {
-        if (!mbar_wait_warp(&s_full[g & 1], (g >> 1) & 1, status, ERR_ATTN_WAIT)) { ok = false; break; }
+        const int st = g & 1;
+        const uint32_t ph = (g >> 1) & 1;
+        if (!mbar_wait_warp(&s_full[st], ph, status, ERR_ATTN_WAIT)) { ok = false; break; }
         tc_fence_after();
-        float s[128];
+        float s[64];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
           uint32_t t[32];
-          tmem_ld_32x32b_x32(tmem_S + lane_off + (g & 1) * 128 + c * 32, t);
+          tmem_ld_32x32b_x32(tmem_S + lane_off + st * 128 + half * 64 + c * 32, t);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(t[i]);
         }
         tc_fence_before();
-        mbar_arrive_warp(&s_empty[g & 1]);
+        mbar_arrive_warp(&s_empty[st]);
         const bool need_mask = ((j + 1) * 128 > item.kv_off + item.qt * 128 + 1) || ((j + 1) * 128 > item.kv_len);
         if (need_mask) {
-          const int col0 = j * 128;
+          const int col0 = j * 128 + half * 64;
 #pragma unroll
-          for (int i = 0; i < 128; ++i)
+          for (int i = 0; i < 64; ++i)
             if (col0 + i > q_pos || col0 + i >= item.kv_len) s[i] = -INFINITY;
         }
-        float mx = s[0];
+        // four independent max chains, then the partner's half through shared memory
+        float mx0 = s[0], mx1 = s[1], mx2 = s[2], mx3 = s[3];
 #pragma unroll
-        for (int i = 1; i < 128; ++i) mx = fmaxf(mx, s[i]);
-        const float m_new = fmaxf(m_used, mx);
-        if (g > 0) {
-          // the previous PV (of this or the previous item) must be complete before P is overwritten
-          // or O is rescaled
-          if (!mbar_wait_warp(pv_done, (g - 1) & 1, status, ERR_ATTN_WAIT)) { ok = false; break; }
-          tc_fence_after();
+        for (int i = 4; i < 64; i += 4) {
+          mx0 = fmaxf(mx0, s[i]);
+          mx1 = fmaxf(mx1, s[i + 1]);
+          mx2 = fmaxf(mx2, s[i + 2]);
+          mx3 = fmaxf(mx3, s[i + 3]);
         }
+        xchg[half * 128 + r] = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+        pair_barrier();
+        const float mx = fmaxf(xchg[r], xchg[128 + r]);
+        pair_barrier();   // both have read before either writes the next tile's value
+        const float m_new = fmaxf(m_used, mx);
         if (j > 0) {
-          const bool need = (m_new - m_used) * sl2 > 8.f;
+          const bool need = (m_new - m_used) * sl2 > 8.f;   // same decision in both threads of the row
           if (__any_sync(0xffffffffu, need)) {
+            // rare: O is rescaled, which needs the previous P*V complete
+            if (!mbar_wait_warp(&pv_done[(g - 1) & 1], ((g - 1) >> 1) & 1, status, ERR_ATTN_WAIT)) { ok = false; break; }
+            tc_fence_after();
             const float alpha = need ? exp2f((m_used - m_new) * sl2) : 1.f;
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
+            for (int c = 0; c < 4; ++c) {   // this thread's 64 columns of O
               uint32_t t[16];
-              tmem_ld_32x32b_x16(tmem_O + lane_off + c * 16, t);
+              tmem_ld_32x32b_x16(tmem_O + lane_off + half * 64 + c * 16, t);
               tmem_ld_wait();
 #pragma unroll
               for (int i = 0; i < 16; ++i) t[i] = __float_as_uint(__uint_as_float(t[i]) * alpha);
-              tmem_st_32x32b_x16(tmem_O + lane_off + c * 16, t);
+              tmem_st_32x32b_x16(tmem_O + lane_off + half * 64 + c * 16, t);
             }
             tmem_st_wait();
             if (need) {
@@ -302,40 +312,50 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         } else {
           m_used = m_new;
         }
+        // the P buffer of this tile was last read by P*V two tiles ago
+        if (g >= 2 && !mbar_wait_warp(&pv_done[st], ph ^ 1, status, ERR_ATTN_WAIT)) { ok = false; break; }
         const float mb = m_used * sl2;
-        float rs = 0.f;
+        uint8_t* sP = smem + AttnFwdSmem::P + st * AT_TILE_BYTES + half * AT_HALF_BYTES + r * 128;
+        float rs0 = 0.f, rs1 = 0.f;
 #pragma unroll
-        for (int c8 = 0; c8 < 16; ++c8) {
+        for (int c8 = 0; c8 < 8; ++c8) {
           float p[8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            p[i] = fast_exp2(fmaf(s[c8 * 8 + i], sl2, -mb));
-            rs += p[i];
-          }
+          for (int i = 0; i < 8; ++i) p[i] = fast_exp2(fmaf(s[c8 * 8 + i], sl2, -mb));
+          rs0 += (p[0] + p[1]) + (p[2] + p[3]);
+          rs1 += (p[4] + p[5]) + (p[6] + p[7]);
           uint4 o;
           o.x = pack_bf16x2(p[0], p[1]);
           o.y = pack_bf16x2(p[2], p[3]);
           o.z = pack_bf16x2(p[4], p[5]);
           o.w = pack_bf16x2(p[6], p[7]);
-          const int sub = c8 >> 3, cc = c8 & 7;
-          *reinterpret_cast<uint4*>(sP + sub * AT_HALF_BYTES + r * 128 + ((cc ^ (r & 7)) << 4)) = o;
+          *reinterpret_cast<uint4*>(sP + ((c8 ^ (r & 7)) << 4)) = o;
         }
-        l += rs;
+        l += rs0 + rs1;
         fence_proxy_async_smem();
         tc_fence_before();
-        mbar_arrive_warp(p_full);
+        mbar_arrive_warp(&p_full[st]);
       }
-      if (!ok || !mbar_wait_warp(pv_done, (g - 1) & 1, status, ERR_ATTN_WAIT)) { ok = false; break; }
+      // the last P*V of the item
+      if (!ok || !mbar_wait_warp(&pv_done[(g - 1) & 1], ((g - 1) >> 1) & 1, status, ERR_ATTN_WAIT)) { ok = false; break; }
       tc_fence_after();
-      // write-out; the next item's first PV is ordered after it by this warp's next p_full arrive
-      const float inv = 1.f / l;
+      // row sum = both halves; write-out: each thread normalises and stores its 64 columns of O
+      xchg[half * 128 + r] = l;
+      pair_barrier();
+      const float lsum = xchg[r] + xchg[128 + r];
+      pair_barrier();
+      const float inv = 1.f / lsum;
       const bool in_range = q_idx < item.q_len;
-      __nv_bfloat16* orow = out + (static_cast<size_t>(item.row0 + r) * Hq + item.head) * 128;
+      __nv_bfloat16* orow = out + (static_cast<size_t>(item.row0 + r) * Hq + item.head) * 128 + half * 64;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 0; c < 2; ++c) {
         uint32_t t[32];
-        tmem_ld_32x32b_x32(tmem_O + lane_off + c * 32, t);
+        tmem_ld_32x32b_x32(tmem_O + lane_off + half * 64 + c * 32, t);
         tmem_ld_wait();
+        if (c == 1) {
+          tc_fence_before();
+          mbar_arrive_warp(o_free);   // this warp's part of O is in registers
+        }
         if (in_range) {
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
@@ -348,9 +368,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           }
         }
       }
-      tc_fence_before();
-      if (in_range && lse_out)
-        lse_out[static_cast<size_t>(item.head) * prm.total_q + item.row0 + r] = m_used * scale + __logf(l);
+      if (half == 0 && in_range && lse_out)
+        lse_out[static_cast<size_t>(item.head) * prm.total_q + item.row0 + r] = m_used * scale + __logf(lsum);
     }
   }
 
