@@ -1,8 +1,8 @@
 // Causal flash-attention forward for sm_100a (head_dim 128, GQA), tcgen05 MMAs with S and O in TMEM.
 //
 // A work item is one 128-row query tile of one (batch, q-head); a persistent CTA per SM walks the
-// items.  The softmax warps read S from TMEM, write P (bf16) to shared memory in the 128-byte-swizzled
-// K-major layout the PV MMA consumes, and rescale the O accumulator in TMEM only when the running
+// items.  The softmax warps read S from TMEM, write P (bf16 pairs) back to TMEM, from where the PV MMA
+// takes it as its A operand (no shared-memory round trip), and rescale the O accumulator in TMEM only when the running
 // row maximum grew by more than 2^8 (the final normalisation uses the same reference maximum for
 // P and for the row sum, so a stale maximum is exact as long as nothing overflows).
 //
@@ -19,12 +19,11 @@ constexpr int AT_HALF_BYTES = 128 * 64 * 2;
 
 struct AttnFwdSmem {
   // offsets into the 1024-byte aligned dynamic shared memory
-  static constexpr int Q = 0;
-  static constexpr int K = Q + AT_TILE_BYTES;           // 2 stages
+  static constexpr int Q = 0;                           // 2 tiles (this item's and the next item's)
+  static constexpr int K = Q + 2 * AT_TILE_BYTES;       // 2 stages
   static constexpr int V = K + 2 * AT_TILE_BYTES;       // 2 stages
-  static constexpr int P = V + 2 * AT_TILE_BYTES;       // 2 tiles
-  static constexpr int BARS = P + 2 * AT_TILE_BYTES;    // 229376: barriers (256 B), then the row exchange buffer (1 KiB)
-  static constexpr int TOTAL = BARS + 256 + 1024 + 1024;
+  static constexpr int BARS = V + 2 * AT_TILE_BYTES;    // 196608: barriers (256 B), then the row exchange buffer (1 KiB)
+  static constexpr int TOTAL = BARS + 256 + 1024 + 1024;   // 198912
 };
 
 // One work item: a 128-row query tile of one (batch, q head).
@@ -76,8 +75,9 @@ __device__ __forceinline__ int fwd_next_active(int w, int n_items, const FwdPara
 // MMAs, warps 2..9 run the softmax.  A query row is shared by two threads (warps w and w+4 touch the same
 // TMEM lane quarter): each takes 64 of the tile's 128 key columns, the pair exchanges its partial row
 // maximum through shared memory and keeps partial row sums that are added at the end.  S and P are
-// double-buffered, so the softmax of tile j+1 never waits for P*V of tile j unless the running maximum
-// grew enough to force a rescale of O.
+// double-buffered in TMEM (S 2 x 128 columns, O 128, P 2 x 64 = all 512), so the softmax of tile j+1 never
+// waits for P*V of tile j unless the running maximum grew enough to force a rescale of O.  Q is double-
+// buffered in shared memory: the next item's Q arrives while the current item is still being processed.
 __global__ void __launch_bounds__(AT_THREADS, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, __nv_bfloat16* __restrict__ out,
@@ -86,7 +86,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + AttnFwdSmem::BARS);
-  uint64_t* q_full = bars + 0;
+  uint64_t* q_full = bars + 0;    // [2] with q_empty at bars + 17
   uint64_t* k_full = bars + 1;    // [2]
   uint64_t* v_full = bars + 3;    // [2]
   uint64_t* k_empty = bars + 5;   // [2]
@@ -95,9 +95,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   uint64_t* s_empty = bars + 11;  // [2]
   uint64_t* p_full = bars + 13;   // [2]
   uint64_t* pv_done = bars + 15;  // [2]
-  uint64_t* q_empty = bars + 17;
-  uint64_t* o_free = bars + 18;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
+  uint64_t* q_empty = bars + 17;  // [2]
+  uint64_t* o_free = bars + 19;
+  uint64_t* q_full2 = bars + 20;  // second Q slot's full barrier
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 21);
   float* xchg = reinterpret_cast<float*>(smem + AttnFwdSmem::BARS + 256);   // [2 column halves][128 rows]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -106,7 +107,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    mbar_init(q_empty, 1);
+    mbar_init(q_full2, 1);
+    mbar_init(&q_empty[0], 1);
+    mbar_init(&q_empty[1], 1);
     mbar_init(o_free, 8);            // every softmax warp, after it has read its part of O
     for (int i = 0; i < 2; ++i) {
       mbar_init(&k_full[i], 1);
@@ -133,6 +136,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
   const uint32_t tmem_S = tmem_base;        // 2 x 128 columns
   const uint32_t tmem_O = tmem_base + 256;  // 128 columns
+  const uint32_t tmem_P = tmem_base + 384;  // 2 x 64 columns: P as bf16 pairs, the A operand of P*V
 
   int w0 = blockIdx.x;
   if (w0 < n_items && !fwd_item(w0, prm).active) w0 = fwd_next_active(w0, n_items, prm);
@@ -143,10 +147,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       bool ok = true;
       for (int w = w0; w < n_items && ok; w = fwd_next_active(w, n_items, prm), ++n) {
         const FwdItem item = fwd_item(w, prm);
-        if (!mbar_wait(q_empty, (n & 1) ^ 1, status, ERR_ATTN_WAIT)) break;
-        mbar_expect_tx(q_full, AT_TILE_BYTES);
-        tma_load_2d(smem + AttnFwdSmem::Q, &tmQ, q_full, item.head * 128, item.row0);
-        tma_load_2d(smem + AttnFwdSmem::Q + AT_HALF_BYTES, &tmQ, q_full, item.head * 128 + 64, item.row0);
+        // Q slot n & 1: free once the last Q*K^T of item n-2 has retired, i.e. long before item n starts
+        uint64_t* qf = (n & 1) ? q_full2 : q_full;
+        uint8_t* sQ = smem + AttnFwdSmem::Q + (n & 1) * AT_TILE_BYTES;
+        if (!mbar_wait(&q_empty[n & 1], ((n >> 1) & 1) ^ 1, status, ERR_ATTN_WAIT)) break;
+        mbar_expect_tx(qf, AT_TILE_BYTES);
+        tma_load_2d(sQ, &tmQ, qf, item.head * 128, item.row0);
+        tma_load_2d(sQ + AT_HALF_BYTES, &tmQ, qf, item.head * 128 + 64, item.row0);
         for (int j = 0; j < item.n_kv; ++j, ++g) {
           const int st = g & 1;
           const uint32_t ph = (g >> 1) & 1;
@@ -168,12 +175,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     // ---- S = Q K^T of every global iteration (uniform control flow, one issuing lane) --------------
     const bool leader = elect_one();
     constexpr uint32_t idesc_s = make_idesc_f16(1, 128, 128, 0, 0);
-    const uint64_t d_q = make_smem_desc_sw128(smem_u32(smem + AttnFwdSmem::Q), 16, 1024);
     int g = 0, n = 0;
     bool ok = true;
     for (int w = w0; w < n_items && ok; w = fwd_next_active(w, n_items, prm), ++n) {
       const FwdItem item = fwd_item(w, prm);
-      if (!mbar_wait(q_full, n & 1, status, ERR_ATTN_WAIT)) break;
+      if (!mbar_wait((n & 1) ? q_full2 : q_full, (n >> 1) & 1, status, ERR_ATTN_WAIT)) break;
+      const uint64_t d_q = make_smem_desc_sw128(smem_u32(smem + AttnFwdSmem::Q + (n & 1) * AT_TILE_BYTES), 16, 1024);
       for (int j = 0; j < item.n_kv; ++j, ++g) {
         const int st = g & 1;
         if (!mbar_wait(&k_full[st], (g >> 1) & 1, status, ERR_ATTN_WAIT) ||
@@ -191,7 +198,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           }
           umma_commit(&k_empty[st]);
           umma_commit(&s_full[st]);
-          if (j + 1 == item.n_kv) umma_commit(q_empty);   // last Q*K^T of the item: Q may be reloaded
+          if (j + 1 == item.n_kv) umma_commit(&q_empty[n & 1]);   // last Q*K^T of the item: its Q slot is free
         }
       }
     }
@@ -213,15 +220,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           break;
         }
         tc_fence_after();
-        const uint64_t d_p = make_smem_desc_sw128(smem_u32(smem + AttnFwdSmem::P + st * AT_TILE_BYTES), 16, 1024);
         const uint64_t d_v = make_smem_desc_sw128(smem_u32(smem + AttnFwdSmem::V + st * AT_TILE_BYTES),
                                                   AT_HALF_BYTES, 1024);
         const uint32_t acc0 = j != 0;
         if (leader) {
 #pragma unroll
           for (int ks = 0; ks < 8; ++ks) {
-            const uint32_t o = (ks >> 2) * AT_HALF_BYTES + (ks & 3) * 32;
-            umma_f16_ss(tmem_O, desc_advance(d_p, o), desc_advance(d_v, ks * 2048), idesc_pv, ks ? 1u : acc0);
+            // A = P from TMEM: 16 bf16 of K per instruction = 8 columns
+            umma_f16_ts(tmem_O, tmem_P + st * 64 + ks * 8, desc_advance(d_v, ks * 2048), idesc_pv, ks ? 1u : acc0);
           }
           umma_commit(&v_empty[st]);
           umma_commit(&pv_done[st]);
@@ -315,24 +321,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         // the P buffer of this tile was last read by P*V two tiles ago
         if (g >= 2 && !mbar_wait_warp(&pv_done[st], ph ^ 1, status, ERR_ATTN_WAIT)) { ok = false; break; }
         const float mb = m_used * sl2;
-        uint8_t* sP = smem + AttnFwdSmem::P + st * AT_TILE_BYTES + half * AT_HALF_BYTES + r * 128;
+        const uint32_t tP = tmem_P + lane_off + st * 64 + half * 32;   // this thread's 64 keys = 32 packed columns
         float rs0 = 0.f, rs1 = 0.f;
 #pragma unroll
-        for (int c8 = 0; c8 < 8; ++c8) {
-          float p[8];
+        for (int c16 = 0; c16 < 2; ++c16) {
+          uint32_t pk[16];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) p[i] = fast_exp2(fmaf(s[c8 * 8 + i], sl2, -mb));
-          rs0 += (p[0] + p[1]) + (p[2] + p[3]);
-          rs1 += (p[4] + p[5]) + (p[6] + p[7]);
-          uint4 o;
-          o.x = pack_bf16x2(p[0], p[1]);
-          o.y = pack_bf16x2(p[2], p[3]);
-          o.z = pack_bf16x2(p[4], p[5]);
-          o.w = pack_bf16x2(p[6], p[7]);
-          *reinterpret_cast<uint4*>(sP + ((c8 ^ (r & 7)) << 4)) = o;
+          for (int i = 0; i < 16; ++i) {
+            const float p0 = fast_exp2(fmaf(s[c16 * 32 + 2 * i], sl2, -mb));
+            const float p1 = fast_exp2(fmaf(s[c16 * 32 + 2 * i + 1], sl2, -mb));
+            rs0 += p0;
+            rs1 += p1;
+            pk[i] = pack_bf16x2(p0, p1);
+          }
+          tmem_st_32x32b_x16(tP + c16 * 16, pk);
         }
+        tmem_st_wait();
         l += rs0 + rs1;
-        fence_proxy_async_smem();
         tc_fence_before();
         mbar_arrive_warp(&p_full[st]);
       }

@@ -206,76 +206,6 @@ __global__ void __launch_bounds__(256) rmsnorm_fwd_warp_kernel(
   }
 }
 
-template <int NV>
-__global__ void __launch_bounds__(256) rmsnorm_bwd_warp_kernel(
-    const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
-    const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd_in,
-    __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_partial, int M, int H, int add_to_dx) {
-  extern __shared__ float sdw[];   // [H]
-  const int lane = threadIdx.x & 31;
-  const int warps_per_grid = (gridDim.x * blockDim.x) >> 5;
-  const int nvec = H / 8;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) sdw[i] = 0.f;
-  float wv[NV][8], dwacc[NV][8];
-#pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    const int c = lane + i * 32;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) dwacc[i][j] = 0.f;
-    if (c < nvec) load8(w + c * 8, wv[i]);
-  }
-  __syncthreads();
-  for (int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; row < M; row += warps_per_grid) {
-    const __nv_bfloat16* xr = x + static_cast<size_t>(row) * H;
-    const __nv_bfloat16* dyr = dy + static_cast<size_t>(row) * H;
-    __nv_bfloat16* dxr = dx + static_cast<size_t>(row) * H;
-    const float rstd = rstd_in[row];
-    float xh[NV][8], g[NV][8];
-    float dot = 0.f;
-#pragma unroll
-    for (int i = 0; i < NV; ++i) {
-      const int c = lane + i * 32;
-      if (c < nvec) {
-        float xv[8], dv[8];
-        load8(xr + c * 8, xv);
-        load8(dyr + c * 8, dv);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          xh[i][j] = xv[j] * rstd;
-          dwacc[i][j] += dv[j] * xh[i][j];
-          g[i][j] = dv[j] * wv[i][j];
-          dot += g[i][j] * xh[i][j];
-        }
-      }
-    }
-    dot = warp_sum(dot) / H;
-#pragma unroll
-    for (int i = 0; i < NV; ++i) {
-      const int c = lane + i * 32;
-      if (c < nvec) {
-        float o[8];
-        if (add_to_dx) load8(dxr + c * 8, o);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const float d = rstd * (g[i][j] - xh[i][j] * dot);
-          o[j] = add_to_dx ? o[j] + d : d;
-        }
-        store8(dxr + c * 8, o);
-      }
-    }
-  }
-#pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    const int c = lane + i * 32;
-    if (c < nvec) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) atomicAdd(&sdw[c * 8 + j], dwacc[i][j]);
-    }
-  }
-  __syncthreads();
-  for (int i = threadIdx.x; i < H; i += blockDim.x) dw_partial[static_cast<size_t>(blockIdx.x) * H + i] = sdw[i];
-}
-
 // ---------------------------------------------------------------------------------------------
 // RMSNorm backward split in two high-occupancy kernels (H <= 2048):
 //   dx kernel: one warp per row, nothing carried across rows (few registers, many warps in flight);
@@ -383,8 +313,15 @@ __global__ void reduce_partials_kernel(const float* __restrict__ partial, void* 
                                        int P, int H, int accumulate, int out_fp32) {
   const int h = blockIdx.x * blockDim.x + threadIdx.x;
   if (h >= H) return;
-  float s = 0.f;
-  for (int p = 0; p < P; ++p) s += partial[static_cast<size_t>(p) * H + h];
+  // eight independent chains: the loads of a chain's next element do not wait for its add
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  int p = 0;
+  for (; p + 8 <= P; p += 8) {
+#pragma unroll
+    for (int u = 0; u < 8; ++u) acc[u] += partial[static_cast<size_t>(p + u) * H + h];
+  }
+  for (; p < P; ++p) acc[0] += partial[static_cast<size_t>(p) * H + h];
+  const float s = ((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7]));
   if (out_fp32) {
     float* o = reinterpret_cast<float*>(dw);
     o[h] = accumulate ? o[h] + s : s;
@@ -400,6 +337,8 @@ __global__ void reduce_partials_kernel(const float* __restrict__ partial, void* 
 // qkv: [M, (Hq + 2*Hkv) * 128] (the fused projection output); q_out [M,Hq,128], k_out [M,Hkv,128].
 // cos/sin: fp32 tables [max_pos, 64].  rstd_out: [M, Hq+Hkv] fp32 for backward.
 // ---------------------------------------------------------------------------------------------
+constexpr int QKR_UNITS = 4;   // (token, head) units per warp step: their loads are issued together
+
 __global__ void __launch_bounds__(256) qknorm_rope_fwd_kernel(
     const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ qw,
     const __nv_bfloat16* __restrict__ kw, const int* __restrict__ pos,
@@ -407,43 +346,61 @@ __global__ void __launch_bounds__(256) qknorm_rope_fwd_kernel(
     __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_out,
     float* __restrict__ rstd_out, int M, int Hq, int Hkv, int ld_qkv, float eps) {
   const int heads = Hq + Hkv;
-  const long long gw = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const long long total = static_cast<long long>(M) * heads;
+  const long long warps_per_grid = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
   const int lane = threadIdx.x & 31;
-  if (gw >= static_cast<long long>(M) * heads) return;
-  const int tok = static_cast<int>(gw / heads);
-  const int head = static_cast<int>(gw % heads);
-  const bool is_q = head < Hq;
-  const __nv_bfloat16* src = qkv + static_cast<size_t>(tok) * ld_qkv + head * 128 + lane * 4;
-  const __nv_bfloat16* w = (is_q ? qw : kw) + lane * 4;
-  uint2 raw = *reinterpret_cast<const uint2*>(src);
-  float2 a = unpack_bf16x2(raw.x), b = unpack_bf16x2(raw.y);
-  float v[4] = {a.x, a.y, b.x, b.y};
-  float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
-  ss = warp_sum(ss);
-  const float rstd = rsqrtf(ss * (1.f / 128.f) + eps);
-  uint2 wraw = *reinterpret_cast<const uint2*>(w);
-  float2 wa = unpack_bf16x2(wraw.x), wb = unpack_bf16x2(wraw.y);
-  const float wv[4] = {wa.x, wa.y, wb.x, wb.y};
-  const int p = pos[tok];
   const int fi = (lane & 15) * 4;  // frequency index of this lane's first element
-  const float4 c4 = *reinterpret_cast<const float4*>(cos_t + static_cast<size_t>(p) * 64 + fi);
-  const float4 s4 = *reinterpret_cast<const float4*>(sin_t + static_cast<size_t>(p) * 64 + fi);
-  const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
-  float o[4];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    const float n = v[j] * rstd * wv[j];
-    const float partner = __shfl_xor_sync(0xffffffffu, n, 16);
-    // first half: y = x1*c - x2*s ; second half: y = x2*c + x1*s
-    o[j] = (lane < 16) ? n * cs[j] - partner * sn[j] : n * cs[j] + partner * sn[j];
+  float wqv[4], wkv[4];
+  {
+    const uint2 a = *reinterpret_cast<const uint2*>(qw + lane * 4);
+    const uint2 b = *reinterpret_cast<const uint2*>(kw + lane * 4);
+    const float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), b0 = unpack_bf16x2(b.x), b1 = unpack_bf16x2(b.y);
+    wqv[0] = a0.x; wqv[1] = a0.y; wqv[2] = a1.x; wqv[3] = a1.y;
+    wkv[0] = b0.x; wkv[1] = b0.y; wkv[2] = b1.x; wkv[3] = b1.y;
   }
-  __nv_bfloat16* dst = is_q ? q_out + (static_cast<size_t>(tok) * Hq + head) * 128 + lane * 4
-                            : k_out + (static_cast<size_t>(tok) * Hkv + (head - Hq)) * 128 + lane * 4;
-  uint2 ov;
-  ov.x = pack_bf16x2(o[0], o[1]);
-  ov.y = pack_bf16x2(o[2], o[3]);
-  *reinterpret_cast<uint2*>(dst) = ov;
-  if (lane == 0 && rstd_out) rstd_out[static_cast<size_t>(tok) * heads + head] = rstd;
+  for (long long g0 = ((static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5) * QKR_UNITS;
+       g0 < total; g0 += warps_per_grid * QKR_UNITS) {
+    uint2 raw[QKR_UNITS];
+    float4 c4[QKR_UNITS], s4[QKR_UNITS];
+    int tok[QKR_UNITS], head[QKR_UNITS];
+#pragma unroll
+    for (int u = 0; u < QKR_UNITS; ++u) {
+      const long long gw = g0 + u < total ? g0 + u : total - 1;   // tail units repeat the last one (not stored)
+      tok[u] = static_cast<int>(gw / heads);
+      head[u] = static_cast<int>(gw % heads);
+      raw[u] = *reinterpret_cast<const uint2*>(qkv + static_cast<size_t>(tok[u]) * ld_qkv + head[u] * 128 + lane * 4);
+      const int p = pos[tok[u]];
+      c4[u] = *reinterpret_cast<const float4*>(cos_t + static_cast<size_t>(p) * 64 + fi);
+      s4[u] = *reinterpret_cast<const float4*>(sin_t + static_cast<size_t>(p) * 64 + fi);
+    }
+#pragma unroll
+    for (int u = 0; u < QKR_UNITS; ++u) {
+      const bool is_q = head[u] < Hq;
+      const float2 a = unpack_bf16x2(raw[u].x), b = unpack_bf16x2(raw[u].y);
+      const float v[4] = {a.x, a.y, b.x, b.y};
+      float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+      ss = warp_sum(ss);
+      const float rstd = rsqrtf(ss * (1.f / 128.f) + eps);
+      const float cs[4] = {c4[u].x, c4[u].y, c4[u].z, c4[u].w}, sn[4] = {s4[u].x, s4[u].y, s4[u].z, s4[u].w};
+      float o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float n = v[j] * rstd * (is_q ? wqv[j] : wkv[j]);
+        const float partner = __shfl_xor_sync(0xffffffffu, n, 16);
+        // first half: y = x1*c - x2*s ; second half: y = x2*c + x1*s
+        o[j] = (lane < 16) ? n * cs[j] - partner * sn[j] : n * cs[j] + partner * sn[j];
+      }
+      if (g0 + u < total) {
+        __nv_bfloat16* dst = is_q ? q_out + (static_cast<size_t>(tok[u]) * Hq + head[u]) * 128 + lane * 4
+                                  : k_out + (static_cast<size_t>(tok[u]) * Hkv + (head[u] - Hq)) * 128 + lane * 4;
+        uint2 ov;
+        ov.x = pack_bf16x2(o[0], o[1]);
+        ov.y = pack_bf16x2(o[2], o[3]);
+        *reinterpret_cast<uint2*>(dst) = ov;
+        if (lane == 0 && rstd_out) rstd_out[static_cast<size_t>(tok[u]) * heads + head[u]] = rstd;
+      }
+    }
+  }
 }
 
 // Backward: dq/dk (post-RoPE grads) -> grads w.r.t. the projection output (written into dqkv's q and
@@ -469,45 +426,62 @@ __global__ void __launch_bounds__(256) qknorm_rope_bwd_kernel(
   const float2 wqa = unpack_bf16x2(wq_raw.x), wqb = unpack_bf16x2(wq_raw.y);
   const float2 wka = unpack_bf16x2(wk_raw.x), wkb = unpack_bf16x2(wk_raw.y);
   const float wqv[4] = {wqa.x, wqa.y, wqb.x, wqb.y}, wkv[4] = {wka.x, wka.y, wkb.x, wkb.y};
-  for (long long gw = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5; gw < total;
-       gw += warps_per_grid) {
-    const int tok = static_cast<int>(gw / heads);
-    const int head = static_cast<int>(gw % heads);
-    const bool is_q = head < Hq;
-    const __nv_bfloat16* gsrc =
-        is_q ? dq + (static_cast<size_t>(tok) * Hq + head) * 128 + lane * 4
-             : dk + (static_cast<size_t>(tok) * Hkv + (head - Hq)) * 128 + lane * 4;
-    uint2 graw = *reinterpret_cast<const uint2*>(gsrc);
-    float2 ga = unpack_bf16x2(graw.x), gb = unpack_bf16x2(graw.y);
-    const float g[4] = {ga.x, ga.y, gb.x, gb.y};
-    const int p = pos[tok];
-    const int fi = (lane & 15) * 4;
-    const float4 c4 = *reinterpret_cast<const float4*>(cos_t + static_cast<size_t>(p) * 64 + fi);
-    const float4 s4 = *reinterpret_cast<const float4*>(sin_t + static_cast<size_t>(p) * 64 + fi);
-    const float cs[4] = {c4.x, c4.y, c4.z, c4.w}, sn[4] = {s4.x, s4.y, s4.z, s4.w};
-    const size_t off = static_cast<size_t>(tok) * ld_qkv + head * 128 + lane * 4;
-    uint2 xraw = *reinterpret_cast<const uint2*>(qkv + off);
-    float2 xa = unpack_bf16x2(xraw.x), xb = unpack_bf16x2(xraw.y);
-    const float xv[4] = {xa.x, xa.y, xb.x, xb.y};
-    const float rstd = rstd_in[static_cast<size_t>(tok) * heads + head];
-    float xh[4], gw_[4];
-    float dot = 0.f;
+  const int fi = (lane & 15) * 4;
+  for (long long g0 = ((static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5) * QKR_UNITS;
+       g0 < total; g0 += warps_per_grid * QKR_UNITS) {
+    uint2 graw[QKR_UNITS], xraw[QKR_UNITS];
+    float4 c4[QKR_UNITS], s4[QKR_UNITS];
+    float rstd_[QKR_UNITS];
+    int tok[QKR_UNITS], head[QKR_UNITS];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float partner = __shfl_xor_sync(0xffffffffu, g[j], 16);
-      // inverse rotation: dx1 = dy1*c + dy2*s ; dx2 = dy2*c - dy1*s
-      const float dn = (lane < 16) ? g[j] * cs[j] + partner * sn[j] : g[j] * cs[j] - partner * sn[j];
-      xh[j] = xv[j] * rstd;
-      gw_[j] = dn * (is_q ? wqv[j] : wkv[j]);
-      dot += gw_[j] * xh[j];
-      if (is_q) dwq[j] += dn * xh[j];
-      else dwk[j] += dn * xh[j];
+    for (int u = 0; u < QKR_UNITS; ++u) {
+      const long long gw = g0 + u < total ? g0 + u : total - 1;   // tail units repeat the last one (masked below)
+      tok[u] = static_cast<int>(gw / heads);
+      head[u] = static_cast<int>(gw % heads);
+      const bool is_q = head[u] < Hq;
+      const __nv_bfloat16* gsrc =
+          is_q ? dq + (static_cast<size_t>(tok[u]) * Hq + head[u]) * 128 + lane * 4
+               : dk + (static_cast<size_t>(tok[u]) * Hkv + (head[u] - Hq)) * 128 + lane * 4;
+      graw[u] = *reinterpret_cast<const uint2*>(gsrc);
+      xraw[u] = *reinterpret_cast<const uint2*>(qkv + static_cast<size_t>(tok[u]) * ld_qkv + head[u] * 128 + lane * 4);
+      rstd_[u] = rstd_in[static_cast<size_t>(tok[u]) * heads + head[u]];
+      const int p = pos[tok[u]];
+      c4[u] = *reinterpret_cast<const float4*>(cos_t + static_cast<size_t>(p) * 64 + fi);
+      s4[u] = *reinterpret_cast<const float4*>(sin_t + static_cast<size_t>(p) * 64 + fi);
     }
-    dot = warp_sum(dot) * (1.f / 128.f);
-    uint2 ov;
-    ov.x = pack_bf16x2(rstd * (gw_[0] - xh[0] * dot), rstd * (gw_[1] - xh[1] * dot));
-    ov.y = pack_bf16x2(rstd * (gw_[2] - xh[2] * dot), rstd * (gw_[3] - xh[3] * dot));
-    *reinterpret_cast<uint2*>(dqkv + off) = ov;
+#pragma unroll
+    for (int u = 0; u < QKR_UNITS; ++u) {
+      const bool live = g0 + u < total;
+      const bool is_q = head[u] < Hq;
+      const float2 ga = unpack_bf16x2(graw[u].x), gb = unpack_bf16x2(graw[u].y);
+      const float g[4] = {ga.x, ga.y, gb.x, gb.y};
+      const float cs[4] = {c4[u].x, c4[u].y, c4[u].z, c4[u].w}, sn[4] = {s4[u].x, s4[u].y, s4[u].z, s4[u].w};
+      const float2 xa = unpack_bf16x2(xraw[u].x), xb = unpack_bf16x2(xraw[u].y);
+      const float xv[4] = {xa.x, xa.y, xb.x, xb.y};
+      const float rstd = rstd_[u];
+      float xh[4], gw_[4];
+      float dot = 0.f;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float partner = __shfl_xor_sync(0xffffffffu, g[j], 16);
+        // inverse rotation: dx1 = dy1*c + dy2*s ; dx2 = dy2*c - dy1*s
+        const float dn = (lane < 16) ? g[j] * cs[j] + partner * sn[j] : g[j] * cs[j] - partner * sn[j];
+        xh[j] = xv[j] * rstd;
+        gw_[j] = dn * (is_q ? wqv[j] : wkv[j]);
+        dot += gw_[j] * xh[j];
+        if (live) {
+          if (is_q) dwq[j] += dn * xh[j];
+          else dwk[j] += dn * xh[j];
+        }
+      }
+      dot = warp_sum(dot) * (1.f / 128.f);
+      if (live) {
+        uint2 ov;
+        ov.x = pack_bf16x2(rstd * (gw_[0] - xh[0] * dot), rstd * (gw_[1] - xh[1] * dot));
+        ov.y = pack_bf16x2(rstd * (gw_[2] - xh[2] * dot), rstd * (gw_[3] - xh[3] * dot));
+        *reinterpret_cast<uint2*>(dqkv + static_cast<size_t>(tok[u]) * ld_qkv + head[u] * 128 + lane * 4) = ov;
+      }
+    }
   }
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
@@ -594,6 +568,7 @@ __global__ void embedding_bwd_kernel(const long long* __restrict__ ids,
 }  // namespace b2
 
 using namespace b2;
+using b2::QKR_UNITS;
 
 #define B2_LAUNCH_CHECK(name)                                        \
   do {                                                               \
@@ -677,9 +652,11 @@ B2_EXPORT int b2_qknorm_rope_fwd(const void* qkv, const void* qw, const void* kw
   b2::ensure_thread_context();
   if (head_dim != 128) { set_error("qknorm_rope: head_dim must be 128"); return 10; }
   if (M <= 0) return 0;
-  const long long warps = static_cast<long long>(M) * (Hq + Hkv);
-  const int blocks = static_cast<int>((warps + 7) / 8);
-  qknorm_rope_fwd_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  const long long warps = (static_cast<long long>(M) * (Hq + Hkv) + QKR_UNITS - 1) / QKR_UNITS;
+  long long blocks = (warps + 7) / 8;
+  const long long fcap = static_cast<long long>(num_sms()) * 16;
+  if (blocks > fcap) blocks = fcap;
+  qknorm_rope_fwd_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(qkv), static_cast<const __nv_bfloat16*>(qw),
       static_cast<const __nv_bfloat16*>(kw), pos, cos_t, sin_t, static_cast<__nv_bfloat16*>(q_out),
       static_cast<__nv_bfloat16*>(k_out), rstd, M, Hq, Hkv, ld_qkv, eps);
@@ -695,7 +672,7 @@ B2_EXPORT int b2_qknorm_rope_bwd(const void* dq, const void* dk, const void* qkv
   b2::ensure_thread_context();
   if (head_dim != 128) { set_error("qknorm_rope: head_dim must be 128"); return 10; }
   if (M <= 0) return 0;
-  const long long warps = static_cast<long long>(M) * (Hq + Hkv);
+  const long long warps = (static_cast<long long>(M) * (Hq + Hkv) + QKR_UNITS - 1) / QKR_UNITS;
   long long blocks = (warps + 7) / 8;
   const long long cap = static_cast<long long>(num_sms()) * 8;
   if (blocks > cap) blocks = cap;

@@ -80,10 +80,11 @@ def test_rmsnorm(H):
     assert relerr(y, yr) < 1e-2 and relerr(x.grad, xf.grad) < 1.5e-2 and relerr(w.grad, wf.grad) < 1.5e-2
 
 
-def test_qknorm_rope_fwd_bwd():
+@pytest.mark.parametrize("M,Hq,Hkv", [(200, 4, 2), (77, 2, 1)])   # 77 * 3 units: a tail that is not a multiple of 4
+def test_qknorm_rope_fwd_bwd(M, Hq, Hkv):
     from b200fw.ops import qknorm_rope, rope_tables
     torch.manual_seed(4)
-    M, Hq, Hkv, D = 200, 4, 2, 128
+    D = 128
     qkv = torch.randn(M, (Hq + 2 * Hkv) * D, device=DEV, dtype=torch.bfloat16, requires_grad=True)
     qw = (1 + 0.1 * torch.randn(D, device=DEV)).to(torch.bfloat16).requires_grad_()
     kw = (1 + 0.1 * torch.randn(D, device=DEV)).to(torch.bfloat16).requires_grad_()
