@@ -131,6 +131,23 @@ def allgather_gemm(x_shard: torch.Tensor, w: torch.Tensor, group, *, b_mn: bool 
     return y, gathered
 
 
+# GEMM -> reduce-scatter pays off when the GEMM is long enough to hide the peer stores and the owner's
+# reduction: measured on 8 GPUs at 16384 tokens x 5120 outputs, K = 3200 runs 1.16x faster fused, K = 1024
+# runs 0.78x (the reduce phase and the NVLink stores are exposed behind a 0.12 ms GEMM).  Below this
+# contraction length the product path is the plain GEMM followed by NCCL's reduce-scatter.
+FUSED_RS_MIN_K = 2048
+
+
+def _reduce_scatter_gemm(x: torch.Tensor, w: torch.Tensor, group, *, b_mn: bool = False,
+                         residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    K = x.shape[1]
+    if K >= FUSED_RS_MIN_K:
+        return gemm_reduce_scatter(x, w, group, b_mn=b_mn, residual=residual)
+    from ..dist import comm
+    y = comm.reduce_scatter(gemm(x, w, b_mn=b_mn), group)
+    return y if residual is None else y.add_(residual)
+
+
 class _ColumnLinearSP(torch.autograd.Function):
     """y = all_gather(x) @ W^T with the gather inside the GEMM; backward: dx = reduce_scatter(dy @ W)
     inside the GEMM, dW = dy^T @ gathered x."""
@@ -146,7 +163,7 @@ class _ColumnLinearSP(torch.autograd.Function):
     def backward(ctx, dy):
         xg, w = ctx.saved_tensors
         dy = dy.contiguous()
-        dx = gemm_reduce_scatter(dy, w, ctx.group, b_mn=True)
+        dx = _reduce_scatter_gemm(dy, w, ctx.group, b_mn=True)
         dw = grad_into_main(w, lambda out, acc: gemm(dy, xg, a_mn=True, b_mn=True, out=out, accumulate=acc))
         return dx, dw, None
 
@@ -160,7 +177,7 @@ class _RowLinearSP(torch.autograd.Function):
         ctx.save_for_backward(x, w)
         ctx.group = group
         ctx.has_res = residual is not None
-        return gemm_reduce_scatter(x, w, group, residual=residual)
+        return _reduce_scatter_gemm(x, w, group, residual=residual)
 
     @staticmethod
     def backward(ctx, dy):
