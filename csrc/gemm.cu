@@ -166,7 +166,8 @@ __global__ void __launch_bounds__(COMM == 2 ? GEMM_THREADS + 128 : GEMM_THREADS,
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmR,
                  void* __restrict__ Cout, const __nv_bfloat16* __restrict__ R, int M, int N, int K,
-                 int ldc, int flags, GemmMnDesc mn, const __grid_constant__ GemmComm comm, int* status) {
+                 int ldc, int flags, GemmMnDesc mn, const __grid_constant__ GemmComm comm, int* status,
+                 int split_k) {
   using Cfg = GemmCfg<BN>;
   static_assert(COMM == 0 || !A_MN, "fused communication paths take a K-major A operand");
   extern __shared__ uint8_t smem_raw[];
@@ -188,6 +189,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int num_n = (N + BN - 1) / BN;
   const int num_tiles = num_m * num_n;
   const int num_kb = (K + GEMM_BK - 1) / GEMM_BK;
+  // Split-K (fp32 accumulate outputs only): a work unit is (tile, K slice); unit u covers tile
+  // u % num_tiles and k-blocks [ks * num_kb / split_k, (ks + 1) * num_kb / split_k) with ks = u / num_tiles,
+  // and its epilogue adds into C with fp32 atomics.  Weight-gradient GEMMs have few output tiles and a
+  // very long contraction (the token count): without the split, 96 tiles leave a third of the SMs idle.
+  const int num_units = num_tiles * split_k;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::STAGES; ++s) {
@@ -233,7 +239,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
+        const int t = u % num_tiles, ks = u / num_tiles;
+        const int kb_begin = ks * num_kb / split_k, kb_end = (ks + 1) * num_kb / split_k;
         int m_blk, n_blk;
         tile_coords(t, m_blk, n_blk);
         const int m0 = m_blk * GEMM_BM, n0 = n_blk * BN;
@@ -244,7 +252,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           asm volatile("fence.proxy.async;" ::: "memory");
         }
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, status, ERR_GEMM_PRODUCER_WAIT)) {
             ok = false;
             break;
@@ -281,11 +289,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       constexpr uint32_t idesc = make_idesc_f16(1, GEMM_BM, BN, A_MN ? 1 : 0, B_MN ? 1 : 0);
       uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
+        const int ks = u / num_tiles;
+        const int kb_begin = ks * num_kb / split_k, kb_end = (ks + 1) * num_kb / split_k;
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, status, ERR_GEMM_MMA_WAIT_TMEM)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, status, ERR_GEMM_MMA_WAIT_FULL)) {
             ok = false;
             break;
@@ -296,7 +306,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const uint64_t a0 = A_MN ? make_smem_desc_sw128(a_base, mn.lbo, mn.sbo) : make_smem_desc_sw128(a_base, 16, 1024);
           const uint64_t b0 = B_MN ? make_smem_desc_sw128(b_base, mn.lbo, mn.sbo) : make_smem_desc_sw128(b_base, 16, 1024);
           const uint32_t a_step = A_MN ? mn.kstep : 32u, b_step = B_MN ? mn.kstep : 32u;
-          const uint32_t acc0 = kb != 0 ? 1u : 0u;
+          const uint32_t acc0 = kb != kb_begin ? 1u : 0u;
           if (leader) {
 #pragma unroll
             for (int k = 0; k < GEMM_BK / 16; ++k)
@@ -350,7 +360,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const bool accumulate = flags & GEMM_ACCUMULATE;
     const bool residual = flags & GEMM_RESIDUAL;
     uint32_t slab_count = 0;
-    for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+    const bool atomic_out = split_k > 1;   // several units add into the same fp32 tile
+    for (int u = blockIdx.x; u < num_units; u += gridDim.x) {
+      const int t = u % num_tiles;
       int m_blk, n_blk;
       tile_coords(t, m_blk, n_blk);
       const int n0 = n_blk * BN;
@@ -535,6 +547,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
               for (int v = 0; v < 8; ++v) {
                 float4 o = make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
                                        __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3]));
+                if (atomic_out) {
+                  atomicAdd(reinterpret_cast<float4*>(cp + 4 * v), o);
+                  continue;
+                }
                 if (accumulate) {
                   float4 p = *reinterpret_cast<float4*>(cp + 4 * v);
                   o.x += p.x; o.y += p.y; o.z += p.z; o.w += p.w;
@@ -542,8 +558,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 *reinterpret_cast<float4*>(cp + 4 * v) = o;
               }
             } else {
-              for (int j = 0; j < 32 && col0 + j < N; ++j)
-                cp[j] = __uint_as_float(r[j]) + (accumulate ? cp[j] : 0.f);
+              for (int j = 0; j < 32 && col0 + j < N; ++j) {
+                if (atomic_out) atomicAdd(cp + j, __uint_as_float(r[j]));
+                else cp[j] = __uint_as_float(r[j]) + (accumulate ? cp[j] : 0.f);
+              }
             }
           } else {
             __nv_bfloat16* cp = reinterpret_cast<__nv_bfloat16*>(Cout) + off;
@@ -660,9 +678,31 @@ static int launch_gemm(const void* A, const void* B, void* C, const void* R, int
   const int num_tiles = ((M + GEMM_BM - 1) / GEMM_BM) * ((N + BN - 1) / BN);
   int grid = num_sms();
   if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
-  if (num_tiles < grid) grid = num_tiles;
+  // Split-K for fp32 outputs with a long contraction: pick the split that minimises the number of
+  // waves times the work per unit (ties go to the smaller split); every slice keeps >= 16 k-blocks.
+  int split_k = 1;
+  if (COMM == 0 && out_fp32 && !(flags & GEMM_RESIDUAL)) {
+    const int num_kb = (K + GEMM_BK - 1) / GEMM_BK;
+    double best = static_cast<double>((num_tiles + grid - 1) / grid);
+    for (int sk = 2; sk <= 4 && num_kb / sk >= 16; ++sk) {
+      const double cost = static_cast<double>((num_tiles * sk + grid - 1) / grid) / sk;
+      if (cost < best * 0.95) {
+        best = cost;
+        split_k = sk;
+      }
+    }
+    if (split_k > 1 && !(flags & GEMM_ACCUMULATE)) {
+      // the slices add into C with atomics: an overwriting GEMM starts from zero
+      if (cudaMemset2DAsync(C, static_cast<size_t>(ldc) * 4, 0, static_cast<size_t>(N) * 4, M, stream) != cudaSuccess) {
+        set_error("gemm: clearing the split-K output failed");
+        return 5;
+      }
+    }
+  }
+  if (num_tiles * split_k < grid) grid = num_tiles * split_k;
   kern<<<grid, COMM == 2 ? GEMM_THREADS + 128 : GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(
-      *ta, *tb, *tc, *tr, C, reinterpret_cast<const __nv_bfloat16*>(R), M, N, K, ldc, flags, g_mn_desc, comm, status);
+      *ta, *tb, *tc, *tr, C, reinterpret_cast<const __nv_bfloat16*>(R), M, N, K, ldc, flags, g_mn_desc, comm, status,
+      split_k);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_error("gemm launch failed: %s", cudaGetErrorString(e));
@@ -697,6 +737,8 @@ B2_EXPORT int b2_gemm_bf16(const void* A, const void* B, void* C, const void* R,
     const int sms = num_sms();
     const int tiles256 = ((M + 127) / 128) * ((N + 255) / 256);
     bn = (tiles256 >= sms || N % 256 == 0) && tiles256 * 2 > sms ? 256 : 128;
+    // fp32 accumulate outputs with a long contraction can split K instead of shrinking the tile
+    if (out_fp32 && N % 256 == 0 && K >= 4096) bn = 256;
   }
 #define B2_GEMM_CASE(BN_, AMN_, BMN_)                                                              \
   if (bn == BN_ && a_mn == AMN_ && b_mn == BMN_)                                                   \

@@ -63,6 +63,7 @@ def main():
     ap.add_argument("--ctx", type=int, default=1024)
     ap.add_argument("--vocab", type=int, default=151936)
     ap.add_argument("--fp8", action="store_true")
+    ap.add_argument("--fp32-acc", action="store_true", help="gemm: accumulate into an fp32 output (weight-gradient form)")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-flush", action="store_true")
@@ -74,8 +75,8 @@ def main():
     if a.kernel == "gemm":
         A = torch.randn((a.k, a.m) if a.a_mn else (a.m, a.k), device=DEV, dtype=bf)
         B = torch.randn((a.k, a.n) if a.b_mn else (a.n, a.k), device=DEV, dtype=bf)
-        C = torch.empty(a.m, a.n, device=DEV, dtype=bf)
-        fn = lambda: ops.gemm(A, B, a_mn=bool(a.a_mn), b_mn=bool(a.b_mn), out=C, bn=a.bn)
+        C = torch.zeros(a.m, a.n, device=DEV, dtype=torch.float32 if a.fp32_acc else bf)
+        fn = lambda: ops.gemm(A, B, a_mn=bool(a.a_mn), b_mn=bool(a.b_mn), out=C, bn=a.bn, accumulate=a.fp32_acc)
         flops = 2.0 * a.m * a.n * a.k
         bytes_ = 2.0 * (a.m * a.k + a.n * a.k + a.m * a.n)
     elif a.kernel in ("attn_fwd", "attn_bwd"):

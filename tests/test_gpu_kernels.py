@@ -51,6 +51,25 @@ def test_gemm_epilogues():
     assert relerr(big[:, :N], ref) < 1e-2 and big[:, N:].abs().max().item() == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(1024, 3072, 8192), (1000, 776, 4100)])
+def test_gemm_split_k_fp32_weight_gradient_shapes(M, N, K):
+    """Few output tiles and a long contraction (the shape of a weight gradient): the launcher splits K
+    and the slices add into the fp32 output with atomics; overwrite, accumulate and a strided output."""
+    from b200fw.ops import gemm
+    torch.manual_seed(3)
+    At = torch.randn(K, M, device=DEV, dtype=torch.bfloat16)      # both operands MN-major, as in dW = dy^T x
+    Bt = torch.randn(K, N, device=DEV, dtype=torch.bfloat16)
+    ref = At.float().t() @ Bt.float()
+    out = torch.full((M, N), 7.0, device=DEV)                      # overwrite: stale contents must vanish
+    gemm(At, Bt, a_mn=True, b_mn=True, out=out)
+    assert relerr(out, ref) < 1e-4
+    gemm(At, Bt, a_mn=True, b_mn=True, out=out, accumulate=True)
+    assert relerr(out, 2 * ref) < 1e-4
+    wide = torch.full((M, N + 8), 3.0, device=DEV)
+    gemm(At, Bt, a_mn=True, b_mn=True, out=wide[:, :N])
+    assert relerr(wide[:, :N], ref) < 1e-4 and float((wide[:, N:] - 3.0).abs().max()) == 0.0
+
+
 def test_linear_autograd():
     from b200fw.ops import linear
     torch.manual_seed(2)
