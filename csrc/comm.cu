@@ -48,11 +48,68 @@ __device__ __forceinline__ unsigned long long bits_of<__nv_bfloat16>(__nv_bfloat
 }
 
 // dst[off + i] = (add ? dst[off + i] : 0) + src[i]; checksum[0] += bits(dst_i), checksum[1] += bits * (off+i+1)
+template <typename T>
+__device__ __forceinline__ void load8_as_float(const T* p, float* f);
+template <>
+__device__ __forceinline__ void load8_as_float<float>(const float* p, float* f) {
+  const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8_as_float<__nv_bfloat16>(const __nv_bfloat16* p, float* f) {
+  const uint4 q = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 t = unpack_bf16x2(w[j]);
+    f[2 * j] = t.x;
+    f[2 * j + 1] = t.y;
+  }
+}
+template <typename T>
+__device__ __forceinline__ void store8(T* p, const T* v);
+template <>
+__device__ __forceinline__ void store8<float>(float* p, const float* v) {
+  reinterpret_cast<float4*>(p)[0] = make_float4(v[0], v[1], v[2], v[3]);
+  reinterpret_cast<float4*>(p)[1] = make_float4(v[4], v[5], v[6], v[7]);
+}
+template <>
+__device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* p, const __nv_bfloat16* v) {
+  *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(v);
+}
+
 template <typename S, typename D>
 __global__ void peer_write_kernel(const S* __restrict__ src, D* __restrict__ dst, long long n,
                                   long long elem_offset, int add, unsigned long long* __restrict__ checksum) {
   unsigned long long c0 = 0, c1 = 0;
-  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+  // Vector body: 8 elements per thread step (16- or 32-byte accesses, so a warp's peer store is one or two
+  // full 512-byte runs instead of 64 bytes); used when source and destination are 16-byte aligned.
+  long long nvec = 0;
+  if ((reinterpret_cast<uintptr_t>(src) % 16 == 0) &&
+      (reinterpret_cast<uintptr_t>(dst + elem_offset) % 16 == 0))
+    nvec = n / 8;
+  for (long long vi = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; vi < nvec;
+       vi += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long i0 = vi * 8;
+    float f[8];
+    load8_as_float<S>(src + i0, f);
+    if (add) {
+      float d[8];
+      load8_as_float<D>(dst + elem_offset + i0, d);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] += d[j];
+    }
+    alignas(16) D o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      o[j] = cvt_out<D>(f[j]);
+      const unsigned long long b = bits_of<D>(o[j]);
+      c0 += b;
+      c1 += b * static_cast<unsigned long long>(elem_offset + i0 + j + 1);
+    }
+    store8<D>(dst + elem_offset + i0, o);
+  }
+  for (long long i = nvec * 8 + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
     float v = cvt_in<S>(src[i]);
     if (add) v += cvt_in<D>(dst[elem_offset + i]);
@@ -120,14 +177,21 @@ __global__ void zero_reduce_shard_kernel(PeerPtrs peers, int world, long long sh
         acc[2 * j + 1] += f.y;
       }
     }
-    float* o = out + i * 8;
+    float4* o = reinterpret_cast<float4*>(out + i * 8);
+    float4 prev[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};
+    if (accumulate) {
+      prev[0] = o[0];
+      prev[1] = o[1];
+    }
+    const float pv[8] = {prev[0].x, prev[0].y, prev[0].z, prev[0].w, prev[1].x, prev[1].y, prev[1].z, prev[1].w};
+    float r[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      float v = acc[j] * scale;
-      if (accumulate) v += o[j];
-      o[j] = v;
-      ss += v * v;
+      r[j] = acc[j] * scale + pv[j];
+      ss += r[j] * r[j];
     }
+    o[0] = make_float4(r[0], r[1], r[2], r[3]);
+    o[1] = make_float4(r[4], r[5], r[6], r[7]);
   }
   ss = warp_sum(ss);
   if ((threadIdx.x & 31) == 0 && norm_sq) atomicAdd(norm_sq, ss);
@@ -151,21 +215,34 @@ __global__ void zero_adamw_publish_kernel(float* __restrict__ master, float* __r
   const long long nvec = n / 8;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    float p[8];
+    // 8 consecutive elements per thread as two float4 per array: consecutive threads read consecutive
+    // 32-byte pieces, so every warp access is fully coalesced
+    float4* mp = reinterpret_cast<float4*>(master + i * 8);
+    float4* mm = reinterpret_cast<float4*>(m + i * 8);
+    float4* mv = reinterpret_cast<float4*>(v + i * 8);
+    const float4* mg = reinterpret_cast<const float4*>(grad + i * 8);
+    float4 pw[2] = {mp[0], mp[1]};
+    float p[8] = {pw[0].x, pw[0].y, pw[0].z, pw[0].w, pw[1].x, pw[1].y, pw[1].z, pw[1].w};
+    if (!skip) {
+      const float4 gw[2] = {mg[0], mg[1]};
+      float4 m4[2] = {mm[0], mm[1]};
+      float4 v4[2] = {mv[0], mv[1]};
+      const float gq[8] = {gw[0].x, gw[0].y, gw[0].z, gw[0].w, gw[1].x, gw[1].y, gw[1].z, gw[1].w};
+      float mq[8] = {m4[0].x, m4[0].y, m4[0].z, m4[0].w, m4[1].x, m4[1].y, m4[1].z, m4[1].w};
+      float vq[8] = {v4[0].x, v4[0].y, v4[0].z, v4[0].w, v4[1].x, v4[1].y, v4[1].z, v4[1].w};
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const long long k = i * 8 + j;
-      float pk = master[k];
-      if (!skip) {
-        const float g = grad[k] * clip;
-        const float mi = b1 * m[k] + (1.f - b1) * g;
-        const float vi = b2 * v[k] + (1.f - b2) * g * g;
-        m[k] = mi;
-        v[k] = vi;
-        pk = pk * (1.f - lr * wd) - lr * (mi / bc1) / (sqrtf(vi / bc2) + eps);
-        master[k] = pk;
+      for (int j = 0; j < 8; ++j) {
+        const float g = gq[j] * clip;
+        mq[j] = b1 * mq[j] + (1.f - b1) * g;
+        vq[j] = b2 * vq[j] + (1.f - b2) * g * g;
+        p[j] = p[j] * (1.f - lr * wd) - lr * (mq[j] / bc1) / (sqrtf(vq[j] / bc2) + eps);
       }
-      p[j] = pk;
+      mm[0] = make_float4(mq[0], mq[1], mq[2], mq[3]);
+      mm[1] = make_float4(mq[4], mq[5], mq[6], mq[7]);
+      mv[0] = make_float4(vq[0], vq[1], vq[2], vq[3]);
+      mv[1] = make_float4(vq[4], vq[5], vq[6], vq[7]);
+      mp[0] = make_float4(p[0], p[1], p[2], p[3]);
+      mp[1] = make_float4(p[4], p[5], p[6], p[7]);
     }
     uint4 o;
     o.x = pack_bf16x2(p[0], p[1]);
