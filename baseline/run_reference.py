@@ -1,8 +1,8 @@
 """Reference arm of ``bench.py``: the unmodified reference package, through its own public API.
 
-The reference is installed once, offline, with
-``python -m pip install --no-index --no-build-isolation --no-deps --find-links /opt/wheelhouse --target
-baseline/_ref /root/reference`` (dependency resolution fails without an index, hence ``--no-deps``).
+The reference is installed once, offline, into ``baseline/_ref`` with
+``python -m pip install --no-index --no-build-isolation --no-deps --find-links <wheel dir> --target
+baseline/_ref <reference checkout>`` (dependency resolution fails without an index, hence ``--no-deps``).
 This module only *drives* it: it writes a Hugging Face style directory (``config.json`` plus seeded
 N(0, 0.02) weights under the HF key names) for the benchmark architecture, builds the reference's
 ``TrainEngine`` with the same parallel layout, and calls its ``sft_step`` with the same synthetic token
