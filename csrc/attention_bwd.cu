@@ -378,26 +378,37 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ64, const __grid_con
       if (!ok) continue;
       tc_fence_after();
       const uint32_t tb = (grp ? tmem_DK : tmem_DV) + lane_off;
+      // Staged through this group's P^T buffer: every MMA that read it has completed (acc_done) and the
+      // group itself is its only writer.
+      uint8_t* stage = smem + DkDvSmem::PT + grp * 16384 + ((warp - 2) & 3) * 4096;
+      const int wrow0 = item.jt * 128 + quarter * 32;   // first kv position of this warp's 32 rows
+      __nv_bfloat16* obase = grp ? dk + static_cast<size_t>(kv_row0 + quarter * 32) * ld_dk + item.kvh * 128
+                                 : dv + static_cast<size_t>(kv_row0 + quarter * 32) * ld_dv + item.kvh * 128;
+      const size_t ld_o = grp ? ld_dk : ld_dv;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t t[32];
-        tmem_ld_32x32b_x32(tb + c * 32, t);
-        tmem_ld_wait();
-        if (c == 3) {
-          tc_fence_before();
-          mbar_arrive_warp(acc_free);   // this warp's part of the accumulators is in registers
-        }
-        if (in_range) {
+      for (int hc = 0; hc < 2; ++hc) {   // two halves of 64 columns = 128 bytes per row each
+        uint4 ov[8];
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t t[32];
+          tmem_ld_32x32b_x32(tb + hc * 64 + c * 32, t);
+          tmem_ld_wait();
+          if (hc == 1 && c == 1) {
+            tc_fence_before();
+            mbar_arrive_warp(acc_free);   // this warp's part of the accumulators is in registers
+          }
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
-            uint4 o;
-            o.x = pack_bf16x2(__uint_as_float(t[v * 8 + 0]), __uint_as_float(t[v * 8 + 1]));
-            o.y = pack_bf16x2(__uint_as_float(t[v * 8 + 2]), __uint_as_float(t[v * 8 + 3]));
-            o.z = pack_bf16x2(__uint_as_float(t[v * 8 + 4]), __uint_as_float(t[v * 8 + 5]));
-            o.w = pack_bf16x2(__uint_as_float(t[v * 8 + 6]), __uint_as_float(t[v * 8 + 7]));
-            *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) = o;
+            ov[c * 4 + v].x = pack_bf16x2(__uint_as_float(t[v * 8 + 0]), __uint_as_float(t[v * 8 + 1]));
+            ov[c * 4 + v].y = pack_bf16x2(__uint_as_float(t[v * 8 + 2]), __uint_as_float(t[v * 8 + 3]));
+            ov[c * 4 + v].z = pack_bf16x2(__uint_as_float(t[v * 8 + 4]), __uint_as_float(t[v * 8 + 5]));
+            ov[c * 4 + v].w = pack_bf16x2(__uint_as_float(t[v * 8 + 6]), __uint_as_float(t[v * 8 + 7]));
           }
         }
+        warp_store_rows_128B(stage, ov, [&](int row) -> uint8_t* {
+          if (wrow0 + row >= S) return nullptr;
+          return reinterpret_cast<uint8_t*>(obase + static_cast<size_t>(row) * ld_o + hc * 64);
+        });
       }
     }
   }
@@ -422,7 +433,8 @@ struct DqSmem {
   static constexpr int K = DO + 32768;       // STAGES x 16 KiB [64 x 128]
   static constexpr int V = K + ATB_STAGES * 16384;    // STAGES x 16 KiB
   static constexpr int DS = V + ATB_STAGES * 16384;   // 2 x 16 KiB [128 x 64]
-  static constexpr int BARS = DS + 2 * 16384;
+  static constexpr int EPI = DS + 2 * 16384;           // 8 warps x 4 KiB write-out staging
+  static constexpr int BARS = EPI + 8 * 4096;
   static constexpr int TOTAL = BARS + 256 + 1024;
 };
 
@@ -686,9 +698,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
       if (!ok || !mbar_wait_warp(acc_done, n & 1, status, ERR_ATTN_WAIT)) { ok = false; break; }
       tc_fence_after();
-      // write-out: group 0 stores dQ columns 0..63, group 1 columns 64..127
-      const bool in_range = q_pos < S;
-      __nv_bfloat16* orow = dq + (static_cast<size_t>(row0 + r) * Hq + item.head) * 128 + grp * 64;
+      // write-out: group 0 stores dQ columns 0..63, group 1 columns 64..127 (128 bytes per row and thread)
+      uint4 ov[8];
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t t[32];
@@ -698,17 +709,21 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           tc_fence_before();
           mbar_arrive_warp(acc_free);   // this warp's part of dQ is in registers
         }
-        if (in_range) {
 #pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            uint4 o;
-            o.x = pack_bf16x2(__uint_as_float(t[v * 8 + 0]), __uint_as_float(t[v * 8 + 1]));
-            o.y = pack_bf16x2(__uint_as_float(t[v * 8 + 2]), __uint_as_float(t[v * 8 + 3]));
-            o.z = pack_bf16x2(__uint_as_float(t[v * 8 + 4]), __uint_as_float(t[v * 8 + 5]));
-            o.w = pack_bf16x2(__uint_as_float(t[v * 8 + 6]), __uint_as_float(t[v * 8 + 7]));
-            *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) = o;
-          }
+        for (int v = 0; v < 4; ++v) {
+          ov[c * 4 + v].x = pack_bf16x2(__uint_as_float(t[v * 8 + 0]), __uint_as_float(t[v * 8 + 1]));
+          ov[c * 4 + v].y = pack_bf16x2(__uint_as_float(t[v * 8 + 2]), __uint_as_float(t[v * 8 + 3]));
+          ov[c * 4 + v].z = pack_bf16x2(__uint_as_float(t[v * 8 + 4]), __uint_as_float(t[v * 8 + 5]));
+          ov[c * 4 + v].w = pack_bf16x2(__uint_as_float(t[v * 8 + 6]), __uint_as_float(t[v * 8 + 7]));
         }
+      }
+      {
+        const int wrow0 = qt * 128 + quarter * 32;   // first q position of this warp's 32 rows
+        __nv_bfloat16* base = dq + (static_cast<size_t>(row0 + quarter * 32) * Hq + item.head) * 128 + grp * 64;
+        warp_store_rows_128B(smem + DqSmem::EPI + (warp - 2) * 4096, ov, [&](int row) -> uint8_t* {
+          if (wrow0 + row >= S) return nullptr;
+          return reinterpret_cast<uint8_t*>(base + static_cast<size_t>(row) * Hq * 128);
+        });
       }
       lse_r = lse_n;
       D_r = D_n;

@@ -22,7 +22,8 @@ struct AttnFwdSmem {
   static constexpr int Q = 0;                           // 2 tiles (this item's and the next item's)
   static constexpr int K = Q + 2 * AT_TILE_BYTES;       // 2 stages
   static constexpr int V = K + 2 * AT_TILE_BYTES;       // 2 stages
-  static constexpr int BARS = V + 2 * AT_TILE_BYTES;    // 196608: barriers (256 B), then the row exchange buffer (1 KiB)
+  static constexpr int EPI = V + 2 * AT_TILE_BYTES;     // 8 warps x 4 KiB write-out staging
+  static constexpr int BARS = EPI + 8 * 4096;           // barriers (256 B), then the row exchange buffer (1 KiB)
   static constexpr int TOTAL = BARS + 256 + 1024 + 1024;   // 198912
 };
 
@@ -351,7 +352,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       pair_barrier();
       const float inv = 1.f / lsum;
       const bool in_range = q_idx < item.q_len;
-      __nv_bfloat16* orow = out + (static_cast<size_t>(item.row0 + r) * Hq + item.head) * 128 + half * 64;
+      uint4 ov[8];
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         uint32_t t[32];
@@ -361,17 +362,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           tc_fence_before();
           mbar_arrive_warp(o_free);   // this warp's part of O is in registers
         }
-        if (in_range) {
 #pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            uint4 o;
-            o.x = pack_bf16x2(__uint_as_float(t[v * 8 + 0]) * inv, __uint_as_float(t[v * 8 + 1]) * inv);
-            o.y = pack_bf16x2(__uint_as_float(t[v * 8 + 2]) * inv, __uint_as_float(t[v * 8 + 3]) * inv);
-            o.z = pack_bf16x2(__uint_as_float(t[v * 8 + 4]) * inv, __uint_as_float(t[v * 8 + 5]) * inv);
-            o.w = pack_bf16x2(__uint_as_float(t[v * 8 + 6]) * inv, __uint_as_float(t[v * 8 + 7]) * inv);
-            *reinterpret_cast<uint4*>(orow + c * 32 + v * 8) = o;
-          }
+        for (int v = 0; v < 4; ++v) {
+          ov[c * 4 + v].x = pack_bf16x2(__uint_as_float(t[v * 8 + 0]) * inv, __uint_as_float(t[v * 8 + 1]) * inv);
+          ov[c * 4 + v].y = pack_bf16x2(__uint_as_float(t[v * 8 + 2]) * inv, __uint_as_float(t[v * 8 + 3]) * inv);
+          ov[c * 4 + v].z = pack_bf16x2(__uint_as_float(t[v * 8 + 4]) * inv, __uint_as_float(t[v * 8 + 5]) * inv);
+          ov[c * 4 + v].w = pack_bf16x2(__uint_as_float(t[v * 8 + 6]) * inv, __uint_as_float(t[v * 8 + 7]) * inv);
         }
+      }
+      {
+        const int wq0 = item.qt * 128 + quarter * 32;   // index (within the sequence) of this warp's first query row
+        __nv_bfloat16* base = out + (static_cast<size_t>(item.row0 + quarter * 32) * Hq + item.head) * 128 + half * 64;
+        warp_store_rows_128B(smem + AttnFwdSmem::EPI + (warp - 2) * 4096, ov, [&](int row) -> uint8_t* {
+          if (wq0 + row >= item.q_len) return nullptr;
+          return reinterpret_cast<uint8_t*>(base + static_cast<size_t>(row) * Hq * 128);
+        });
       }
       if (half == 0 && in_range && lse_out)
         lse_out[static_cast<size_t>(item.head) * prm.total_q + item.row0 + r] = m_used * scale + __logf(lsum);

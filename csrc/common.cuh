@@ -327,6 +327,29 @@ __host__ __device__ constexpr uint32_t make_idesc_f16(uint32_t fmt, uint32_t M, 
          ((M >> 4) << 24);
 }
 
+// Coalesced write-out of a block of 32 rows x 128 bytes that a warp holds one row per lane (8 x 16 bytes
+// per lane).  Written directly, every store instruction would touch 32 different cache lines with 16
+// bytes each (partial-sector writes: ~2000 cycles for a 32 KiB tile); staged through 4 KiB of shared
+// memory private to the warp, every instruction writes four complete 128-byte lines.
+// row_ptr(row) returns the global address of that row's 128 bytes, or nullptr to skip the row.
+template <typename RowPtr>
+__device__ __forceinline__ void warp_store_rows_128B(uint8_t* stage, const uint4 (&v)[8], RowPtr row_ptr) {
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    *reinterpret_cast<uint4*>(stage + lane * 128 + ((j ^ (lane & 7)) << 4)) = v[j];
+  __syncwarp();
+  const int chunk = lane & 7;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const int row = 4 * k + (lane >> 3);
+    const uint4 val = *reinterpret_cast<const uint4*>(stage + row * 128 + ((chunk ^ (row & 7)) << 4));
+    uint8_t* dst = row_ptr(row);
+    if (dst) *reinterpret_cast<uint4*>(dst + chunk * 16) = val;
+  }
+  __syncwarp();
+}
+
 // ---- small numeric helpers -----------------------------------------------------------------
 // 2^x on the special-function unit, one instruction (exp2f adds range handling around the same
 // instruction; softmax arguments are <= 0 and -inf maps to 0, so none of it is needed).

@@ -309,19 +309,30 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_dw_kernel(
 }
 
 // dw[h] (+)= sum_p partial[p, h]   (bf16 or fp32 destination)
-__global__ void reduce_partials_kernel(const float* __restrict__ partial, void* __restrict__ dw,
-                                       int P, int H, int accumulate, int out_fp32) {
-  const int h = blockIdx.x * blockDim.x + threadIdx.x;
-  if (h >= H) return;
-  // eight independent chains: the loads of a chain's next element do not wait for its add
-  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-  int p = 0;
-  for (; p + 8 <= P; p += 8) {
+// Column sums of partial[P, H].  Block = 32 columns x 8 warps: warp w sums rows w, w+8, ... with four
+// independent chains, the eight warp results meet in shared memory.  (One thread per column walking all P
+// rows is a single dependent chain of P L2 round trips: 9-12 us for 256 x 1024.)
+__global__ void __launch_bounds__(256) reduce_partials_kernel(const float* __restrict__ partial,
+                                                              void* __restrict__ dw, int P, int H,
+                                                              int accumulate, int out_fp32) {
+  __shared__ float part[8][32];
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  const int h = blockIdx.x * 32 + lane;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  if (h < H) {
+    int p = w;
+    for (; p + 24 < P; p += 32) {
 #pragma unroll
-    for (int u = 0; u < 8; ++u) acc[u] += partial[static_cast<size_t>(p + u) * H + h];
+      for (int u = 0; u < 4; ++u) acc[u] += partial[static_cast<size_t>(p + 8 * u) * H + h];
+    }
+    for (; p < P; p += 8) acc[0] += partial[static_cast<size_t>(p) * H + h];
   }
-  for (; p < P; ++p) acc[0] += partial[static_cast<size_t>(p) * H + h];
-  const float s = ((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7]));
+  part[w][lane] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+  __syncthreads();
+  if (w != 0 || h >= H) return;
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) s += part[i][lane];
   if (out_fp32) {
     float* o = reinterpret_cast<float*>(dw);
     o[h] = accumulate ? o[h] + s : s;
@@ -332,12 +343,39 @@ __global__ void reduce_partials_kernel(const float* __restrict__ partial, void* 
 }
 
 // ---------------------------------------------------------------------------------------------
-// Fused per-head RMSNorm (q_norm / k_norm) + half-rotation RoPE.  head_dim = 128, one warp per
-// (token, head); lane l holds elements 4l..4l+3, the rotation partner (i +- 64) lives in lane l^16.
+// Fused per-head RMSNorm (q_norm / k_norm) + half-rotation RoPE, head_dim = 128.
 // qkv: [M, (Hq + 2*Hkv) * 128] (the fused projection output); q_out [M,Hq,128], k_out [M,Hkv,128].
 // cos/sin: fp32 tables [max_pos, 64].  rstd_out: [M, Hq+Hkv] fp32 for backward.
 // ---------------------------------------------------------------------------------------------
-constexpr int QKR_UNITS = 4;   // (token, head) units per warp step: their loads are issued together
+// One warp per token.  A head (128 dims) is spread over 16 lanes at 8 elements (16 bytes) each, so one
+// warp-wide access covers two heads; the rotation partner (dim +- 64) sits in lane ^ 8.  The token's
+// cos / sin row is loaded once and reused by all its q and k heads, and QKR_PAIRS head pairs are loaded
+// before the first is processed.  (A warp per (token, head) with 8-byte accesses and a dependent
+// position -> table load per unit ran at a third of the memory bandwidth.)
+constexpr int QKR_PAIRS = 4;
+
+__device__ __forceinline__ void qkr_unpack8(const uint4& q, float* f) {
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 t = unpack_bf16x2(w[j]);
+    f[2 * j] = t.x;
+    f[2 * j + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 qkr_pack8(const float* f) {
+  uint4 o;
+  o.x = pack_bf16x2(f[0], f[1]);
+  o.y = pack_bf16x2(f[2], f[3]);
+  o.z = pack_bf16x2(f[4], f[5]);
+  o.w = pack_bf16x2(f[6], f[7]);
+  return o;
+}
+__device__ __forceinline__ float sum16(float v) {   // over the 16 lanes that share a head
+#pragma unroll
+  for (int o = 8; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
 
 __global__ void __launch_bounds__(256) qknorm_rope_fwd_kernel(
     const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ qw,
@@ -346,58 +384,56 @@ __global__ void __launch_bounds__(256) qknorm_rope_fwd_kernel(
     __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_out,
     float* __restrict__ rstd_out, int M, int Hq, int Hkv, int ld_qkv, float eps) {
   const int heads = Hq + Hkv;
-  const long long total = static_cast<long long>(M) * heads;
-  const long long warps_per_grid = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
-  const int lane = threadIdx.x & 31;
-  const int fi = (lane & 15) * 4;  // frequency index of this lane's first element
-  float wqv[4], wkv[4];
-  {
-    const uint2 a = *reinterpret_cast<const uint2*>(qw + lane * 4);
-    const uint2 b = *reinterpret_cast<const uint2*>(kw + lane * 4);
-    const float2 a0 = unpack_bf16x2(a.x), a1 = unpack_bf16x2(a.y), b0 = unpack_bf16x2(b.x), b1 = unpack_bf16x2(b.y);
-    wqv[0] = a0.x; wqv[1] = a0.y; wqv[2] = a1.x; wqv[3] = a1.y;
-    wkv[0] = b0.x; wkv[1] = b0.y; wkv[2] = b1.x; wkv[3] = b1.y;
-  }
-  for (long long g0 = ((static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5) * QKR_UNITS;
-       g0 < total; g0 += warps_per_grid * QKR_UNITS) {
-    uint2 raw[QKR_UNITS];
-    float4 c4[QKR_UNITS], s4[QKR_UNITS];
-    int tok[QKR_UNITS], head[QKR_UNITS];
-#pragma unroll
-    for (int u = 0; u < QKR_UNITS; ++u) {
-      const long long gw = g0 + u < total ? g0 + u : total - 1;   // tail units repeat the last one (not stored)
-      tok[u] = static_cast<int>(gw / heads);
-      head[u] = static_cast<int>(gw % heads);
-      raw[u] = *reinterpret_cast<const uint2*>(qkv + static_cast<size_t>(tok[u]) * ld_qkv + head[u] * 128 + lane * 4);
-      const int p = pos[tok[u]];
-      c4[u] = *reinterpret_cast<const float4*>(cos_t + static_cast<size_t>(p) * 64 + fi);
-      s4[u] = *reinterpret_cast<const float4*>(sin_t + static_cast<size_t>(p) * 64 + fi);
+  const int lane = threadIdx.x & 31, l16 = lane & 15, sub = lane >> 4;
+  const int warps_per_grid = (gridDim.x * blockDim.x) >> 5;
+  const bool upper = l16 >= 8;              // this lane holds dims 64..127 of its head
+  float wq[8], wk[8];
+  qkr_unpack8(*reinterpret_cast<const uint4*>(qw + l16 * 8), wq);
+  qkr_unpack8(*reinterpret_cast<const uint4*>(kw + l16 * 8), wk);
+  const int npairs = (heads + 1) / 2;
+  for (int tok = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; tok < M; tok += warps_per_grid) {
+    const int p = pos[tok];
+    const int fi = (l16 & 7) * 8;           // frequency index of this lane's first element
+    float cs[8], sn[8];
+    {
+      const float4* c = reinterpret_cast<const float4*>(cos_t + static_cast<size_t>(p) * 64 + fi);
+      const float4* s_ = reinterpret_cast<const float4*>(sin_t + static_cast<size_t>(p) * 64 + fi);
+      const float4 c0 = c[0], c1 = c[1], s0 = s_[0], s1 = s_[1];
+      cs[0] = c0.x; cs[1] = c0.y; cs[2] = c0.z; cs[3] = c0.w; cs[4] = c1.x; cs[5] = c1.y; cs[6] = c1.z; cs[7] = c1.w;
+      sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
     }
+    const __nv_bfloat16* row = qkv + static_cast<size_t>(tok) * ld_qkv + l16 * 8;
+    for (int hp0 = 0; hp0 < npairs; hp0 += QKR_PAIRS) {
+      uint4 raw[QKR_PAIRS];
 #pragma unroll
-    for (int u = 0; u < QKR_UNITS; ++u) {
-      const bool is_q = head[u] < Hq;
-      const float2 a = unpack_bf16x2(raw[u].x), b = unpack_bf16x2(raw[u].y);
-      const float v[4] = {a.x, a.y, b.x, b.y};
-      float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
-      ss = warp_sum(ss);
-      const float rstd = rsqrtf(ss * (1.f / 128.f) + eps);
-      const float cs[4] = {c4[u].x, c4[u].y, c4[u].z, c4[u].w}, sn[4] = {s4[u].x, s4[u].y, s4[u].z, s4[u].w};
-      float o[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float n = v[j] * rstd * (is_q ? wqv[j] : wkv[j]);
-        const float partner = __shfl_xor_sync(0xffffffffu, n, 16);
-        // first half: y = x1*c - x2*s ; second half: y = x2*c + x1*s
-        o[j] = (lane < 16) ? n * cs[j] - partner * sn[j] : n * cs[j] + partner * sn[j];
+      for (int u = 0; u < QKR_PAIRS; ++u) {
+        const int head = min(2 * (hp0 + u) + sub, heads - 1);   // tail units repeat the last head (not stored)
+        raw[u] = *reinterpret_cast<const uint4*>(row + head * 128);
       }
-      if (g0 + u < total) {
-        __nv_bfloat16* dst = is_q ? q_out + (static_cast<size_t>(tok[u]) * Hq + head[u]) * 128 + lane * 4
-                                  : k_out + (static_cast<size_t>(tok[u]) * Hkv + (head[u] - Hq)) * 128 + lane * 4;
-        uint2 ov;
-        ov.x = pack_bf16x2(o[0], o[1]);
-        ov.y = pack_bf16x2(o[2], o[3]);
-        *reinterpret_cast<uint2*>(dst) = ov;
-        if (lane == 0 && rstd_out) rstd_out[static_cast<size_t>(tok[u]) * heads + head[u]] = rstd;
+#pragma unroll
+      for (int u = 0; u < QKR_PAIRS; ++u) {
+        const int head = 2 * (hp0 + u) + sub;
+        const bool is_q = head < Hq;
+        float v[8];
+        qkr_unpack8(raw[u], v);
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ss += v[j] * v[j];
+        const float rstd = rsqrtf(sum16(ss) * (1.f / 128.f) + eps);
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float n = v[j] * rstd * (is_q ? wq[j] : wk[j]);
+          const float partner = __shfl_xor_sync(0xffffffffu, n, 8);
+          // first half: y = x1*c - x2*s ; second half: y = x2*c + x1*s
+          o[j] = upper ? n * cs[j] + partner * sn[j] : n * cs[j] - partner * sn[j];
+        }
+        if (head < heads) {
+          __nv_bfloat16* dst = is_q ? q_out + (static_cast<size_t>(tok) * Hq + head) * 128 + l16 * 8
+                                    : k_out + (static_cast<size_t>(tok) * Hkv + (head - Hq)) * 128 + l16 * 8;
+          *reinterpret_cast<uint4*>(dst) = qkr_pack8(o);
+          if (l16 == 0 && rstd_out) rstd_out[static_cast<size_t>(tok) * heads + head] = rstd;
+        }
       }
     }
   }
@@ -416,77 +452,77 @@ __global__ void __launch_bounds__(256) qknorm_rope_bwd_kernel(
   for (int i = threadIdx.x; i < 256; i += blockDim.x) (&sdw[0][0])[i] = 0.f;
   __syncthreads();
   const int heads = Hq + Hkv;
-  const int lane = threadIdx.x & 31;
-  const long long total = static_cast<long long>(M) * heads;
-  const long long warps_per_grid = (static_cast<long long>(gridDim.x) * blockDim.x) >> 5;
-  // a lane always owns the same four head dimensions: weight gradients accumulate in registers
-  float dwq[4] = {0.f, 0.f, 0.f, 0.f}, dwk[4] = {0.f, 0.f, 0.f, 0.f};
-  uint2 wq_raw = *reinterpret_cast<const uint2*>(qw + lane * 4);
-  uint2 wk_raw = *reinterpret_cast<const uint2*>(kw + lane * 4);
-  const float2 wqa = unpack_bf16x2(wq_raw.x), wqb = unpack_bf16x2(wq_raw.y);
-  const float2 wka = unpack_bf16x2(wk_raw.x), wkb = unpack_bf16x2(wk_raw.y);
-  const float wqv[4] = {wqa.x, wqa.y, wqb.x, wqb.y}, wkv[4] = {wka.x, wka.y, wkb.x, wkb.y};
-  const int fi = (lane & 15) * 4;
-  for (long long g0 = ((static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5) * QKR_UNITS;
-       g0 < total; g0 += warps_per_grid * QKR_UNITS) {
-    uint2 graw[QKR_UNITS], xraw[QKR_UNITS];
-    float4 c4[QKR_UNITS], s4[QKR_UNITS];
-    float rstd_[QKR_UNITS];
-    int tok[QKR_UNITS], head[QKR_UNITS];
+  const int lane = threadIdx.x & 31, l16 = lane & 15, sub = lane >> 4;
+  const int warps_per_grid = (gridDim.x * blockDim.x) >> 5;
+  const bool upper = l16 >= 8;
+  // a lane always owns the same eight head dimensions: weight gradients accumulate in registers
+  float dwq[8], dwk[8], wq[8], wk[8];
 #pragma unroll
-    for (int u = 0; u < QKR_UNITS; ++u) {
-      const long long gw = g0 + u < total ? g0 + u : total - 1;   // tail units repeat the last one (masked below)
-      tok[u] = static_cast<int>(gw / heads);
-      head[u] = static_cast<int>(gw % heads);
-      const bool is_q = head[u] < Hq;
-      const __nv_bfloat16* gsrc =
-          is_q ? dq + (static_cast<size_t>(tok[u]) * Hq + head[u]) * 128 + lane * 4
-               : dk + (static_cast<size_t>(tok[u]) * Hkv + (head[u] - Hq)) * 128 + lane * 4;
-      graw[u] = *reinterpret_cast<const uint2*>(gsrc);
-      xraw[u] = *reinterpret_cast<const uint2*>(qkv + static_cast<size_t>(tok[u]) * ld_qkv + head[u] * 128 + lane * 4);
-      rstd_[u] = rstd_in[static_cast<size_t>(tok[u]) * heads + head[u]];
-      const int p = pos[tok[u]];
-      c4[u] = *reinterpret_cast<const float4*>(cos_t + static_cast<size_t>(p) * 64 + fi);
-      s4[u] = *reinterpret_cast<const float4*>(sin_t + static_cast<size_t>(p) * 64 + fi);
+  for (int j = 0; j < 8; ++j) dwq[j] = dwk[j] = 0.f;
+  qkr_unpack8(*reinterpret_cast<const uint4*>(qw + l16 * 8), wq);
+  qkr_unpack8(*reinterpret_cast<const uint4*>(kw + l16 * 8), wk);
+  const int npairs = (heads + 1) / 2;
+  for (int tok = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; tok < M; tok += warps_per_grid) {
+    const int p = pos[tok];
+    const int fi = (l16 & 7) * 8;
+    float cs[8], sn[8];
+    {
+      const float4* c = reinterpret_cast<const float4*>(cos_t + static_cast<size_t>(p) * 64 + fi);
+      const float4* s_ = reinterpret_cast<const float4*>(sin_t + static_cast<size_t>(p) * 64 + fi);
+      const float4 c0 = c[0], c1 = c[1], s0 = s_[0], s1 = s_[1];
+      cs[0] = c0.x; cs[1] = c0.y; cs[2] = c0.z; cs[3] = c0.w; cs[4] = c1.x; cs[5] = c1.y; cs[6] = c1.z; cs[7] = c1.w;
+      sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
     }
+    const size_t xoff = static_cast<size_t>(tok) * ld_qkv + l16 * 8;
+    for (int hp0 = 0; hp0 < npairs; hp0 += QKR_PAIRS) {
+      uint4 graw[QKR_PAIRS], xraw[QKR_PAIRS];
+      float rs[QKR_PAIRS];
 #pragma unroll
-    for (int u = 0; u < QKR_UNITS; ++u) {
-      const bool live = g0 + u < total;
-      const bool is_q = head[u] < Hq;
-      const float2 ga = unpack_bf16x2(graw[u].x), gb = unpack_bf16x2(graw[u].y);
-      const float g[4] = {ga.x, ga.y, gb.x, gb.y};
-      const float cs[4] = {c4[u].x, c4[u].y, c4[u].z, c4[u].w}, sn[4] = {s4[u].x, s4[u].y, s4[u].z, s4[u].w};
-      const float2 xa = unpack_bf16x2(xraw[u].x), xb = unpack_bf16x2(xraw[u].y);
-      const float xv[4] = {xa.x, xa.y, xb.x, xb.y};
-      const float rstd = rstd_[u];
-      float xh[4], gw_[4];
-      float dot = 0.f;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float partner = __shfl_xor_sync(0xffffffffu, g[j], 16);
-        // inverse rotation: dx1 = dy1*c + dy2*s ; dx2 = dy2*c - dy1*s
-        const float dn = (lane < 16) ? g[j] * cs[j] + partner * sn[j] : g[j] * cs[j] - partner * sn[j];
-        xh[j] = xv[j] * rstd;
-        gw_[j] = dn * (is_q ? wqv[j] : wkv[j]);
-        dot += gw_[j] * xh[j];
-        if (live) {
-          if (is_q) dwq[j] += dn * xh[j];
-          else dwk[j] += dn * xh[j];
-        }
+      for (int u = 0; u < QKR_PAIRS; ++u) {
+        const int head = min(2 * (hp0 + u) + sub, heads - 1);   // tail units repeat the last head (masked below)
+        const __nv_bfloat16* gsrc = head < Hq ? dq + (static_cast<size_t>(tok) * Hq + head) * 128 + l16 * 8
+                                              : dk + (static_cast<size_t>(tok) * Hkv + (head - Hq)) * 128 + l16 * 8;
+        graw[u] = *reinterpret_cast<const uint4*>(gsrc);
+        xraw[u] = *reinterpret_cast<const uint4*>(qkv + xoff + head * 128);
+        rs[u] = rstd_in[static_cast<size_t>(tok) * heads + head];
       }
-      dot = warp_sum(dot) * (1.f / 128.f);
-      if (live) {
-        uint2 ov;
-        ov.x = pack_bf16x2(rstd * (gw_[0] - xh[0] * dot), rstd * (gw_[1] - xh[1] * dot));
-        ov.y = pack_bf16x2(rstd * (gw_[2] - xh[2] * dot), rstd * (gw_[3] - xh[3] * dot));
-        *reinterpret_cast<uint2*>(dqkv + static_cast<size_t>(tok[u]) * ld_qkv + head[u] * 128 + lane * 4) = ov;
+#pragma unroll
+      for (int u = 0; u < QKR_PAIRS; ++u) {
+        const int head = 2 * (hp0 + u) + sub;
+        const bool live = head < heads;
+        const bool is_q = head < Hq;
+        float g[8], xv[8], xh[8], gw_[8];
+        qkr_unpack8(graw[u], g);
+        qkr_unpack8(xraw[u], xv);
+        const float rstd = rs[u];
+        float dot = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float partner = __shfl_xor_sync(0xffffffffu, g[j], 8);
+          // inverse rotation: dx1 = dy1*c + dy2*s ; dx2 = dy2*c - dy1*s
+          const float dn = upper ? g[j] * cs[j] - partner * sn[j] : g[j] * cs[j] + partner * sn[j];
+          xh[j] = xv[j] * rstd;
+          gw_[j] = dn * (is_q ? wq[j] : wk[j]);
+          dot += gw_[j] * xh[j];
+          if (live) {
+            if (is_q) dwq[j] += dn * xh[j];
+            else dwk[j] += dn * xh[j];
+          }
+        }
+        dot = sum16(dot) * (1.f / 128.f);
+        if (live) {
+          float o[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = rstd * (gw_[j] - xh[j] * dot);
+          *reinterpret_cast<uint4*>(dqkv + xoff + head * 128) = qkr_pack8(o);
+        }
       }
     }
   }
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    atomicAdd(&sdw[0][lane * 4 + j], dwq[j]);
-    atomicAdd(&sdw[1][lane * 4 + j], dwk[j]);
+  for (int j = 0; j < 8; ++j) {
+    atomicAdd(&sdw[0][l16 * 8 + j], dwq[j]);
+    atomicAdd(&sdw[1][l16 * 8 + j], dwk[j]);
   }
   __syncthreads();
   for (int i = threadIdx.x; i < 128; i += blockDim.x) {
@@ -568,7 +604,6 @@ __global__ void embedding_bwd_kernel(const long long* __restrict__ ids,
 }  // namespace b2
 
 using namespace b2;
-using b2::QKR_UNITS;
 
 #define B2_LAUNCH_CHECK(name)                                        \
   do {                                                               \
@@ -631,7 +666,7 @@ B2_EXPORT int b2_rmsnorm_bwd(const void* dy, const void* x, const void* w, const
     const int dw_ctas = ctas > num_sms() ? num_sms() : ctas;
     rmsnorm_bwd_dw_kernel<<<dw_ctas, 256, H * static_cast<int>(sizeof(float)), stream>>>(dys, xs, rstd, dw_partial, M, H);
     B2_LAUNCH_CHECK("rmsnorm_bwd_dw");
-    reduce_partials_kernel<<<(H + 63) / 64, 64, 0, stream>>>(dw_partial, dw, dw_ctas, H, accumulate_dw, dw_fp32);
+    reduce_partials_kernel<<<(H + 31) / 32, 256, 0, stream>>>(dw_partial, dw, dw_ctas, H, accumulate_dw, dw_fp32);
     B2_LAUNCH_CHECK("rmsnorm_bwd_reduce");
     return 0;
   }
@@ -640,7 +675,7 @@ B2_EXPORT int b2_rmsnorm_bwd(const void* dy, const void* x, const void* w, const
       static_cast<const __nv_bfloat16*>(w), rstd, static_cast<__nv_bfloat16*>(dx), dw_partial, M, H,
       add_to_dx);
   B2_LAUNCH_CHECK("rmsnorm_bwd");
-  reduce_partials_kernel<<<(H + 255) / 256, 256, 0, stream>>>(dw_partial, dw, ctas, H, accumulate_dw, dw_fp32);
+  reduce_partials_kernel<<<(H + 31) / 32, 256, 0, stream>>>(dw_partial, dw, ctas, H, accumulate_dw, dw_fp32);
   B2_LAUNCH_CHECK("rmsnorm_bwd_reduce");
   return 0;
 }
@@ -652,8 +687,7 @@ B2_EXPORT int b2_qknorm_rope_fwd(const void* qkv, const void* qw, const void* kw
   b2::ensure_thread_context();
   if (head_dim != 128) { set_error("qknorm_rope: head_dim must be 128"); return 10; }
   if (M <= 0) return 0;
-  const long long warps = (static_cast<long long>(M) * (Hq + Hkv) + QKR_UNITS - 1) / QKR_UNITS;
-  long long blocks = (warps + 7) / 8;
+  long long blocks = (static_cast<long long>(M) + 7) / 8;   // one warp per token
   const long long fcap = static_cast<long long>(num_sms()) * 16;
   if (blocks > fcap) blocks = fcap;
   qknorm_rope_fwd_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
@@ -672,8 +706,7 @@ B2_EXPORT int b2_qknorm_rope_bwd(const void* dq, const void* dk, const void* qkv
   b2::ensure_thread_context();
   if (head_dim != 128) { set_error("qknorm_rope: head_dim must be 128"); return 10; }
   if (M <= 0) return 0;
-  const long long warps = (static_cast<long long>(M) * (Hq + Hkv) + QKR_UNITS - 1) / QKR_UNITS;
-  long long blocks = (warps + 7) / 8;
+  long long blocks = (static_cast<long long>(M) + 7) / 8;   // one warp per token
   const long long cap = static_cast<long long>(num_sms()) * 8;
   if (blocks > cap) blocks = cap;
   qknorm_rope_bwd_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
@@ -791,7 +824,7 @@ B2_EXPORT int b2_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* 
   // every CTA writes its whole [H] row of partials, so stale contents of the shared array are never read
   rmsnorm_bwd_dw_kernel<<<dw_ctas, 256, H * static_cast<int>(sizeof(float)), stream>>>(dys, xs, rstd, partial, M, H);
   B2_LAUNCH_CHECK("rmsnorm_bwd_noalloc(dw)");
-  reduce_partials_kernel<<<(H + 63) / 64, 64, 0, stream>>>(partial, dw, dw_ctas, H, accumulate_dw, dw_fp32);
+  reduce_partials_kernel<<<(H + 31) / 32, 256, 0, stream>>>(partial, dw, dw_ctas, H, accumulate_dw, dw_fp32);
   B2_LAUNCH_CHECK("rmsnorm_bwd_noalloc(reduce)");
   return 0;
 }
