@@ -356,10 +356,18 @@ class ParallelTransformerModel(nn.Module):
         return self.logits_from_hidden(h).reshape(B, S, -1)
 
     def loss(self, input_ids: torch.Tensor, labels: torch.Tensor, loss_scale: float = 1.0,
-             hidden: Optional[torch.Tensor] = None, valid_idx: Optional[torch.Tensor] = None) -> torch.Tensor:
+             hidden: Optional[torch.Tensor] = None, valid_idx: Optional[torch.Tensor] = None,
+             valid_labels: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Next-token CE with the shift done on the labels (``labels[:, t]`` supervises the logits at
         ``t-1``); ``-100`` is ignored.  Same value as the reference's shifted ``F.cross_entropy``
         (src/engines/train_engine.py:44-50)."""
+        if valid_labels is not None:
+            # static-shape form (CUDA-graph replay): row indices and their labels come padded to a fixed
+            # length, padding rows carry label -100 and add nothing
+            B, S = input_ids.shape
+            h = hidden if hidden is not None else self.forward_hidden(input_ids, B, S)
+            return ops.lm_head_cross_entropy(h.index_select(0, valid_idx), self.lm_head_weight, valid_labels,
+                                             loss_scale=loss_scale, shard=self.vocab_shard())
         B, S = labels.shape
         h = hidden if hidden is not None else self.forward_hidden(input_ids, B, S)
         shifted = torch.full_like(labels, -100)

@@ -42,6 +42,8 @@ def parse():
     ap.add_argument("--grad-ckpt", action="store_true")
     ap.add_argument("--sequence-parallel", action="store_true")
     ap.add_argument("--zero-comm", default="nccl", choices=["nccl", "p2p"])
+    ap.add_argument("--cuda-graph", action="store_true",
+                    help="replay forward + backward of each micro-batch as one CUDA graph (DP / single GPU, ZeRO <= 1)")
     ap.add_argument("--layers", type=int, default=0,
                     help="override the preset's layer count (smoke runs of a large architecture; not a benchmark config)")
     ap.add_argument("--fused-tp", action="store_true",
@@ -142,7 +144,7 @@ def run_ours(a):
                       gradient_accumulation_steps=a.grad_accum if a.pp == 1 else 1, grpo_beta=0.0,
                       zero_stage=a.zero_stage, warmup_steps=2, total_training_steps=a.steps + a.warmup + 8,
                       sequence_parallel=a.sequence_parallel, amp_dtype="bf16", zero_comm_backend=a.zero_comm,
-                      fused_tp_comm=a.fused_tp)
+                      fused_tp_comm=a.fused_tp, cuda_graph_step=a.cuda_graph)
     eng = TrainEngine(cfg).initialize()
     dev = eng.device
     accum = a.grad_accum
@@ -214,7 +216,8 @@ def run_ours(a):
                        "global_batch": a.micro_batch * micro_per_step * dp, "micro_batch_per_gpu": a.micro_batch,
                        "grad_accum": a.grad_accum, "seq_len": a.seq_len, "parallelism": par,
                        "zero_stage": a.zero_stage, "zero_comm": a.zero_comm,
-                       "sequence_parallel": a.sequence_parallel, "fused_tp_comm": a.fused_tp, "grad_ckpt": a.grad_ckpt, "l2": "inputs larger than L2 (weights+activations >> 126 MB)",
+                       "sequence_parallel": a.sequence_parallel, "fused_tp_comm": a.fused_tp, "grad_ckpt": a.grad_ckpt,
+                       "cuda_graph_step": a.cuda_graph, "l2": "inputs larger than L2 (weights+activations >> 126 MB)",
                        "step": "one optimizer step = grad_accum micro-batches + reduce + clip + AdamW"},
             "mfu_exact_of_measured_sustained": flops / (step_s * world * peaks["bf16_tflops_sustained"] * 1e12),
             "model_tflops_per_gpu": flops / step_s / world / 1e12,
