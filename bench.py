@@ -42,8 +42,9 @@ def parse():
     ap.add_argument("--grad-ckpt", action="store_true")
     ap.add_argument("--sequence-parallel", action="store_true")
     ap.add_argument("--zero-comm", default="nccl", choices=["nccl", "p2p"])
-    ap.add_argument("--cuda-graph", action="store_true",
-                    help="replay forward + backward of each micro-batch as one CUDA graph (DP / single GPU, ZeRO <= 1)")
+    ap.add_argument("--no-cuda-graph", dest="cuda_graph", action="store_false",
+                    help="launch the micro-step kernel by kernel instead of replaying forward + backward as one CUDA "
+                         "graph (the graph path applies to DP / single GPU with ZeRO <= 1; other layouts run eagerly)")
     ap.add_argument("--layers", type=int, default=0,
                     help="override the preset's layer count (smoke runs of a large architecture; not a benchmark config)")
     ap.add_argument("--fused-tp", action="store_true",
