@@ -163,11 +163,8 @@ class ColocateOrchestrator:
             self.comm_profiler = CommProfiler()
             self.compute_profiler = ComputeProfiler()
         if cfg.tensorboard and ctx.is_main:
-            try:
-                from torch.utils.tensorboard import SummaryWriter
-                self.tb = SummaryWriter(os.path.join(cfg.output_dir, "tensorboard"))
-            except Exception:  # noqa: BLE001 - optional dependency
-                self.tb = None
+            from ..obs.tb_events import open_writer
+            self.tb = open_writer(os.path.join(cfg.output_dir, "tensorboard"))
         self.memory.snapshot("init")
         return self
 

@@ -10,6 +10,48 @@ from b200fw.obs import (ArtifactWriter, CommProfiler, ComputeProfiler, EvalMetri
                         compute_exact_match, compute_token_f1, get_logger, setup_logger)
 
 
+def test_event_files_round_trip_without_the_tensorboard_package(capsys):
+    """Scalar event files: CRC-32C check value, TFRecord framing, proto fields, the loss-printing helper."""
+    import importlib.util
+    from b200fw.obs.tb_events import EventFileWriter, crc32c, read_scalars
+    assert crc32c(b"123456789") == 0xE3069283                      # the standard CRC-32C check value
+    with tempfile.TemporaryDirectory() as d:
+        with EventFileWriter(d) as w:
+            for i in range(4):
+                w.add_scalar("train/loss", 2.0 - 0.25 * i, i)
+            w.add_scalar("train/lr", 1e-5, 300)
+        m = MetricsCollector()
+        m.record("reward", 0.5, 7)
+        with EventFileWriter(d) as w2:
+            m.export_tensorboard(w2, "rollout/")
+        files = [f for f in os.listdir(d) if "tfevents" in f]
+        assert files and all(f.startswith("events.out.tfevents.") for f in files)
+        sc = read_scalars(d)
+        assert [(s, v) for s, v, _ in sc["train/loss"]] == [(0, 2.0), (1, 1.75), (2, 1.5), (3, 1.25)]
+        assert sc["train/lr"][0][0] == 300 and abs(sc["train/lr"][0][1] - 1e-5) < 1e-12
+        assert sc["rollout/reward"][0][:2] == (7, 0.5)
+        # a flipped payload byte is caught by the record checksum
+        path = os.path.join(d, sorted(files)[0])
+        raw = bytearray(open(path, "rb").read())
+        raw[-6] ^= 0xFF
+        bad = os.path.join(d, "bad.tfevents")
+        open(bad, "wb").write(bytes(raw))
+        try:
+            read_scalars(bad)
+            raise AssertionError("corruption not detected")
+        except ValueError:
+            pass
+        os.remove(bad)
+        spec = importlib.util.spec_from_file_location(
+            "plot_loss", os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "scripts", "plot_loss.py"))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        assert mod.main([d]) == 0
+        out = capsys.readouterr().out
+        assert "train/loss" in out and "1.7500" in out
+        assert mod.main([d, "--tag", "missing"]) == 1
+
+
 def test_metrics_collector_and_artifacts():
     m = MetricsCollector()
     for i, v in enumerate([1.0, 2.0, 3.0]):
