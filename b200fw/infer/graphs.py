@@ -8,7 +8,7 @@ syncs; only shape changes (block-table width) force a re-capture.
 """
 from __future__ import annotations
 
-from typing import Callable, Dict, List, Optional
+from typing import Callable, Dict, Optional
 
 import torch
 

@@ -9,7 +9,7 @@ with one fp32 scale per (block, kv head) — the reference keeps per-token scale
 from __future__ import annotations
 
 from collections import deque
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Deque, Dict, List, Optional
 
 import torch

@@ -8,7 +8,7 @@ prefill attention -> GEMMs with the residual in the epilogue.  It also builds th
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import List, Optional, Sequence, Tuple
 
 import torch
 

@@ -16,7 +16,7 @@ import torch
 import torch.nn as nn
 
 from ..dist import comm
-from .qwen3 import ColumnParallelLinear, RowParallelLinear, ParallelAttention, ParallelMLP
+from .qwen3 import RowParallelLinear, ParallelAttention, ParallelMLP
 
 DEFAULT_TARGETS = ["q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"]
 

@@ -15,7 +15,6 @@ and flags only grow (epochs), nothing is reset between calls.
 """
 from __future__ import annotations
 
-import ctypes
 from typing import Dict, Optional, Tuple
 
 import torch

@@ -26,7 +26,6 @@ embedding's and LM head's gradients by ``tp`` — src/engines/train_engine.py:14
 """
 from __future__ import annotations
 
-import math
 from typing import Dict, List, Optional
 
 import torch

@@ -20,7 +20,7 @@ import enum
 import os
 import time
 from concurrent.futures import ThreadPoolExecutor
-from dataclasses import asdict, dataclass, field
+from dataclasses import dataclass, field
 from typing import Dict, List, Optional
 
 import torch
@@ -28,9 +28,9 @@ import torch
 from ..config import ColocateConfig, config_snapshot
 from ..data import GRPOBatch, GSM8KDataPipeline, SyntheticTokenPipeline
 from ..infer import InferenceConfig, InferenceEngine
-from ..obs import ArtifactWriter, CommProfiler, ComputeProfiler, MemoryProfiler, MemoryReport, MetricsCollector, get_logger
+from ..obs import ArtifactWriter, CommProfiler, ComputeProfiler, MemoryProfiler, MetricsCollector, get_logger
 from ..reward import GSM8KRewardFunction, SyntheticTokenReward
-from ..sync import DeltaComputer, PeerWeightSync, SwiftSyncConfig, SwiftSyncTransfer
+from ..sync import PeerWeightSync, SwiftSyncConfig, SwiftSyncTransfer
 from ..train import C3POConfig, C3POPlusScheduler, TrainConfig, TrainEngine, TrainMetrics
 
 logger = get_logger("orch.colocate")

@@ -12,7 +12,7 @@ ratio reported is ``min(train, rollout) / max(train, rollout)`` of the concurren
 from __future__ import annotations
 
 import time
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Dict, List, Optional
 
 import torch

@@ -14,7 +14,6 @@ import base64
 import hashlib
 import pickle
 import time
-from dataclasses import dataclass, field
 from typing import Any, Callable, Dict, List, Optional
 
 import torch

@@ -12,7 +12,6 @@ prints achieved throughput against the measured peaks.  Also the command line us
 """
 import argparse
 import json
-import math
 import os
 import sys
 

@@ -2,7 +2,6 @@
 """Memory profile of one training step: static estimate, per-phase peaks, per-layer peaks, optimizer bytes
 (the reference's scripts/profile_memory.py:22-28 flags)."""
 import argparse
-import json
 import os
 import sys
 

@@ -1,6 +1,5 @@
 """Inference kernels and the native paged engine on the GPU, each against the CPU fp32 oracle of the
 same op (b200fw.ops CPU paths) or the eager engine."""
-import math
 
 import pytest
 import torch

@@ -3,8 +3,6 @@ import json
 import os
 import tempfile
 
-import torch
-
 from b200fw.obs import (ArtifactWriter, CommProfiler, ComputeProfiler, EvalMetrics, MemoryBreakdown, MemoryManager,
                         MemoryProfiler, MemoryReport, MetricsCollector, ScheduleVisualizer, compute_bleu4,
                         compute_exact_match, compute_token_f1, get_logger, setup_logger)

@@ -67,7 +67,6 @@ def test_tiny_qwen3_sft_dp2_zero1_matches_single_process():
 
 
 def _pp_worker(rank, world, path):
-    from b200fw.dist.context import ParallelContext
     from b200fw.model import load_from_hf_checkpoint
     cfg = TrainConfig(model_config=SMALL, pp_size=world, num_micro_batches=4, lora_rank=0, grpo_beta=0.0,
                       learning_rate=1e-3, gradient_accumulation_steps=1, zero_stage=1, use_amp=False,

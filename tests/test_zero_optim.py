@@ -1,6 +1,5 @@
 """ZeRO stage 0/1/2/3 against torch.optim.AdamW, rank consistency, the non-finite guard, the 3-D global
 gradient norm, schedules and optimizer state round-trip (gloo, CPU, fp32)."""
-import copy
 import math
 
 import torch
