@@ -138,6 +138,8 @@ class ZeROOptimizer:
         self.comm_stream = torch.cuda.Stream(device=self.device, priority=-1) if self.overlap else None
         self.sync_this_backward = True
         self.params_gathered = True
+        self._gather_events: Dict[int, "torch.cuda.Event"] = {}   # bucket -> gather finished, not yet waited for
+        self._prefetch_hooks: List = []
         # "p2p": gradient reduce-scatter and parameter all-gather run inside the optimizer kernels
         # through peer pointers (stage 1/2, bf16, CUDA, world <= 8); "nccl": library collectives.
         self.p2p = (comm_backend == "p2p" and self.on_cuda and self.world > 1 and self.world <= 8
@@ -359,20 +361,73 @@ class ZeROOptimizer:
     def _release_params(self):
         if not self.params_gathered:
             return
+        self.wait_gathered()        # a gather nobody waited for must not outlive its buffer
         for b in self.buckets:
             b.unbind_params()
         self.params_gathered = False
 
-    def pre_forward(self):
-        """Stage 3: all-gather every bucket's parameters from the bf16 image of the fp32 shards."""
+    def pre_forward(self, lazy: bool = False):
+        """Stage 3: all-gather every bucket's parameters from the bf16 image of the fp32 shards.
+
+        On a GPU the gathers are queued bucket by bucket on the communication stream.  With ``lazy=True``
+        (and :meth:`attach_prefetch_hooks` installed on the model) the compute stream only waits for the
+        first bucket here; each transformer layer's forward pre-hook waits for the buckets that layer reads,
+        so the gather of layer ``i+1`` runs under the GEMMs of layer ``i`` instead of in front of the forward
+        (the reference gathers the whole flat model up front: src/distributed/zero_optim_v3.py:252-296).
+        Without ``lazy`` every gather is waited for before returning."""
         if self.stage < 3 or self.params_gathered:
             return
+        import contextlib
+        side = self.overlap and self.comm_stream is not None
+        if side:
+            self.comm_stream.wait_stream(torch.cuda.current_stream())     # the shards hold the last AdamW result
         for i, b in enumerate(self.buckets):
+            # allocated on the compute stream (its consumer and the stream that frees it); written on the side stream
             b.param_buf = torch.empty(b.numel, dtype=b.dtype, device=self.device)
-            shard = self._shard_view(self.master, i).to(b.dtype)
-            dist.all_gather_into_tensor(b.param_buf, shard, group=self.dp_group)
+            with (torch.cuda.stream(self.comm_stream) if side else contextlib.nullcontext()):
+                shard = self._shard_view(self.master, i).to(b.dtype)
+                dist.all_gather_into_tensor(b.param_buf, shard, group=self.dp_group)
+                if side:
+                    ev = torch.cuda.Event()
+                    ev.record(self.comm_stream)
+                    self._gather_events[i] = ev
             b.bind_params()
         self.params_gathered = True
+        if side:
+            self.wait_gathered([0] if (lazy and self._prefetch_hooks) else None)
+
+    def wait_gathered(self, idxs=None):
+        """Make the current stream wait for the parameter gathers of the given buckets (all when ``None``)."""
+        if not self._gather_events:
+            return
+        cur = torch.cuda.current_stream()
+        for i in (list(self._gather_events) if idxs is None else idxs):
+            ev = self._gather_events.pop(i, None)
+            if ev is not None:
+                cur.wait_event(ev)
+
+    def attach_prefetch_hooks(self, model) -> bool:
+        """Stage 3 on a GPU: forward pre-hooks on every transformer layer (waits for that layer's buckets)
+        and on the final norm (waits for everything left: the LM head follows it), so that
+        ``pre_forward(lazy=True)`` can overlap the parameter gathers with the forward pass."""
+        layers, norm = getattr(model, "layers", None), getattr(model, "norm", None)
+        if self.stage < 3 or not self.overlap or layers is None or norm is None or self._prefetch_hooks:
+            return bool(self._prefetch_hooks)
+        if self._tp_group() is not None:
+            return False        # keep data-parallel gathers and tensor-parallel collectives from running concurrently
+        index = {id(p): i for i, b in enumerate(self.buckets) for p in b.params}
+
+        def make(idxs):
+            def hook(module, args):
+                if self._gather_events:
+                    self.wait_gathered(idxs)
+            return hook
+
+        for layer in layers:
+            idxs = sorted({index[id(p)] for p in layer.parameters() if id(p) in index})
+            self._prefetch_hooks.append(layer.register_forward_pre_hook(make(idxs)))
+        self._prefetch_hooks.append(norm.register_forward_pre_hook(make(None)))
+        return True
 
     def pre_eval(self):
         self.pre_forward()

@@ -188,6 +188,7 @@ class TrainEngine:
             lr=cfg.learning_rate, betas=(cfg.adam_beta1, cfg.adam_beta2), eps=cfg.adam_eps,
             weight_decay=cfg.weight_decay, ctx=ctx, bucket_mb=cfg.bucket_mb, max_grad_norm=cfg.max_grad_norm,
             overlap=True, comm_backend=cfg.zero_comm_backend)
+        self.optimizer.attach_prefetch_hooks(self.model)     # ZeRO-3 on a GPU: parameter gathers overlap the forward
         self.lr_scheduler = LRSchedule(cfg.learning_rate, cfg.lr_scheduler_type, cfg.warmup_steps,
                                        cfg.total_training_steps, cfg.min_lr_ratio)
         self.optimizer.param_groups[0]["lr"] = self.lr_scheduler.lr_at(0)
@@ -307,7 +308,7 @@ class TrainEngine:
 
     def _single_batch_step(self, input_ids, labels, valid_idx=None):
         cfg, opt = self.config, self.optimizer
-        opt.pre_forward()
+        opt.pre_forward(lazy=True)
         if self._graph_eligible():
             loss = self._graphed_micro_step(input_ids, labels, valid_idx)
             if loss is not None:
@@ -465,7 +466,7 @@ class TrainEngine:
         ids, labels = self._build_batch(P, R)
         adv_t = torch.tensor(A, dtype=torch.float32).to(self.device, non_blocking=True)
         mask = (labels[:, 1:] != -100).float()
-        opt.pre_forward()
+        opt.pre_forward(lazy=True)
         opt.begin_backward(sync=self._accumulation_count + 1 >= cfg.gradient_accumulation_steps)
         lp = self.model.token_logprobs(ids, labels=labels)
         self.last_icepop_info = {}

@@ -65,6 +65,59 @@ def test_zero_stages_match_adamw_dp2():
         assert res[0][1] == res[1][1], f"stage {stage}: ranks diverged"
 
 
+def _prefetch_worker(rank, world):
+    """ZeRO-3 gather prefetch bookkeeping, with fake events standing in for the side stream's."""
+    from b200fw.dist.context import ParallelContext
+    ctx = ParallelContext.init_distributed(dp_size=world, backend="gloo")
+    m = ParallelTransformerModel(CFG, ctx)
+    m.init_weights(3)
+    opt = build_optimizer(m.parameters(), 3, lr=1e-2, ctx=ctx, bucket_mb=0.02)
+    assert not opt.attach_prefetch_hooks(m)            # CPU: no side stream, nothing to overlap
+    opt.overlap = True
+    assert opt.attach_prefetch_hooks(m) and len(opt._prefetch_hooks) == CFG.num_layers + 1
+    waited = []
+
+    class Stream:
+        def wait_event(self, ev):
+            waited.append(ev)
+
+        def wait_stream(self, other):
+            pass
+
+    real = torch.cuda.current_stream
+    torch.cuda.current_stream = lambda *a, **k: Stream()
+    try:
+        opt.pre_forward(lazy=True)                      # gloo gather, synchronous
+        n = len(opt.buckets)
+        index = {id(p): i for i, b in enumerate(opt.buckets) for p in b.params}
+        opt._gather_events.update({i: i for i in range(n)})
+        opt.wait_gathered([0])
+        assert waited == [0]
+        seen_at_layer = []
+        hooks = [layer.register_forward_pre_hook(lambda mod, a: seen_at_layer.append(list(waited))) for layer in m.layers]
+        ids, labels = _data(rank)
+        opt.begin_backward(sync=True)
+        m.loss(ids, labels).backward()
+        for h in hooks:
+            h.remove()
+        # every layer's own buckets were waited for before it ran; later layers' buckets were not all forced early
+        for li, layer in enumerate(m.layers):
+            need = {index[id(p)] for p in layer.parameters()}
+            assert need <= set(seen_at_layer[li]), (li, need, seen_at_layer[li])
+        assert len(seen_at_layer[0]) < n
+        assert sorted(waited) == list(range(n)) and not opt._gather_events     # the final norm's hook drained the rest
+        opt._gather_events[0] = "late"
+        opt.post_backward()                             # releases the parameters: pending gathers are waited for first
+        assert waited[-1] == "late" and not opt._gather_events
+    finally:
+        torch.cuda.current_stream = real
+    return True
+
+
+def test_zero3_gather_prefetch_hooks():
+    assert all(run_ranks(_prefetch_worker, 2))
+
+
 def test_zero_local_mode_single_process():
     m = ParallelTransformerModel(CFG)
     m.init_weights(1)
