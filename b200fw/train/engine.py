@@ -79,6 +79,7 @@ class TrainConfig:
     bucket_mb: float = 64.0
     fused_tp_comm: bool = False                 # TP+SP: all-gather / reduce-scatter inside the GEMM kernels
     zero_comm_backend: str = "nccl"           # "nccl" | "p2p" (reduce-scatter / all-gather inside the optimizer kernels)
+    zero3_prefetch: bool = True                 # ZeRO-3: overlap the per-bucket parameter gathers with the forward
     build_ref_model: Optional[bool] = None      # default: grpo_beta > 0, as in the reference
     backend: Optional[str] = None               # nccl / gloo (default by device)
 
@@ -188,7 +189,8 @@ class TrainEngine:
             lr=cfg.learning_rate, betas=(cfg.adam_beta1, cfg.adam_beta2), eps=cfg.adam_eps,
             weight_decay=cfg.weight_decay, ctx=ctx, bucket_mb=cfg.bucket_mb, max_grad_norm=cfg.max_grad_norm,
             overlap=True, comm_backend=cfg.zero_comm_backend)
-        self.optimizer.attach_prefetch_hooks(self.model)     # ZeRO-3 on a GPU: parameter gathers overlap the forward
+        if cfg.zero3_prefetch:
+            self.optimizer.attach_prefetch_hooks(self.model)  # ZeRO-3 on a GPU: parameter gathers overlap the forward
         self.lr_scheduler = LRSchedule(cfg.learning_rate, cfg.lr_scheduler_type, cfg.warmup_steps,
                                        cfg.total_training_steps, cfg.min_lr_ratio)
         self.optimizer.param_groups[0]["lr"] = self.lr_scheduler.lr_at(0)

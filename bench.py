@@ -41,6 +41,8 @@ def parse():
     ap.add_argument("--grad-ckpt", action="store_true")
     ap.add_argument("--sequence-parallel", action="store_true")
     ap.add_argument("--zero-comm", default="nccl", choices=["nccl", "p2p"])
+    ap.add_argument("--no-zero3-prefetch", dest="zero3_prefetch", action="store_false",
+                    help="ZeRO-3: wait for every parameter gather before the forward instead of layer by layer")
     ap.add_argument("--no-cuda-graph", dest="cuda_graph", action="store_false",
                     help="launch the micro-step kernel by kernel instead of replaying forward + backward as one CUDA "
                          "graph (the graph path applies to DP / single GPU with ZeRO <= 1; other layouts run eagerly)")
@@ -144,7 +146,7 @@ def run_ours(a):
                       gradient_accumulation_steps=a.grad_accum if a.pp == 1 else 1, grpo_beta=0.0,
                       zero_stage=a.zero_stage, warmup_steps=2, total_training_steps=a.steps + a.warmup + 8,
                       sequence_parallel=a.sequence_parallel, amp_dtype="bf16", zero_comm_backend=a.zero_comm,
-                      fused_tp_comm=a.fused_tp, cuda_graph_step=a.cuda_graph)
+                      fused_tp_comm=a.fused_tp, cuda_graph_step=a.cuda_graph, zero3_prefetch=a.zero3_prefetch)
     eng = TrainEngine(cfg).initialize()
     dev = eng.device
     accum = a.grad_accum
@@ -215,7 +217,7 @@ def run_ours(a):
                        + (f" (layers cut to {a.layers}: smoke run, not the named config)" if a.layers > 0 else ""),
                        "global_batch": a.micro_batch * micro_per_step * dp, "micro_batch_per_gpu": a.micro_batch,
                        "grad_accum": a.grad_accum, "seq_len": a.seq_len, "parallelism": par,
-                       "zero_stage": a.zero_stage, "zero_comm": a.zero_comm,
+                       "zero_stage": a.zero_stage, "zero_comm": a.zero_comm, "zero3_prefetch": a.zero3_prefetch,
                        "sequence_parallel": a.sequence_parallel, "fused_tp_comm": a.fused_tp, "grad_ckpt": a.grad_ckpt,
                        "cuda_graph_step": a.cuda_graph, "l2": "inputs larger than L2 (weights+activations >> 126 MB)",
                        "step": "one optimizer step = grad_accum micro-batches + reduce + clip + AdamW"},
