@@ -140,6 +140,8 @@ class ZeROOptimizer:
         self.params_gathered = True
         self._gather_events: Dict[int, "torch.cuda.Event"] = {}   # bucket -> gather finished, not yet waited for
         self._prefetch_hooks: List = []
+        self._prefetch_first: List[int] = []      # buckets read before the first layer (embedding table)
+        self._gather_order: List[int] = []        # bucket indices in the order the forward pass reads them
         # "p2p": gradient reduce-scatter and parameter all-gather run inside the optimizer kernels
         # through peer pointers (stage 1/2, bf16, CUDA, world <= 8); "nccl": library collectives.
         self.p2p = (comm_backend == "p2p" and self.on_cuda and self.world > 1 and self.world <= 8
@@ -381,7 +383,9 @@ class ZeROOptimizer:
         side = self.overlap and self.comm_stream is not None
         if side:
             self.comm_stream.wait_stream(torch.cuda.current_stream())     # the shards hold the last AdamW result
-        for i, b in enumerate(self.buckets):
+        order = self._gather_order if (lazy and self._prefetch_hooks) else range(len(self.buckets))
+        for i in order:
+            b = self.buckets[i]
             # allocated on the compute stream (its consumer and the stream that frees it); written on the side stream
             b.param_buf = torch.empty(b.numel, dtype=b.dtype, device=self.device)
             with (torch.cuda.stream(self.comm_stream) if side else contextlib.nullcontext()):
@@ -394,7 +398,7 @@ class ZeROOptimizer:
             b.bind_params()
         self.params_gathered = True
         if side:
-            self.wait_gathered([0] if (lazy and self._prefetch_hooks) else None)
+            self.wait_gathered(self._prefetch_first if (lazy and self._prefetch_hooks) else None)
 
     def wait_gathered(self, idxs=None):
         """Make the current stream wait for the parameter gathers of the given buckets (all when ``None``)."""
@@ -423,9 +427,22 @@ class ZeROOptimizer:
                     self.wait_gathered(idxs)
             return hook
 
+        # buckets are filled in reverse parameter order (the order gradients become ready), so the
+        # embedding table sits in the last one: gather in the order the forward pass reads them
+        in_layers = {id(p) for layer in layers for p in layer.parameters()}
+        tail = {id(p) for p in norm.parameters()}
+        head = getattr(model, "lm_head", None)
+        if isinstance(head, torch.Tensor):
+            tail.add(id(head))
+        first = sorted({i for i, b in enumerate(self.buckets) for p in b.params
+                        if id(p) not in in_layers and id(p) not in tail})     # embedding (and anything unknown)
+        order = list(first)
         for layer in layers:
-            idxs = sorted({index[id(p)] for p in layer.parameters() if id(p) in index})
-            self._prefetch_hooks.append(layer.register_forward_pre_hook(make(idxs)))
+            idxs = sorted({index[id(p)] for p in layer.parameters() if id(p) in index}, reverse=True)
+            order += [i for i in idxs if i not in order]
+            self._prefetch_hooks.append(layer.register_forward_pre_hook(make(sorted(idxs))))
+        order += [i for i in range(len(self.buckets)) if i not in order]
+        self._prefetch_first, self._gather_order = first, order
         self._prefetch_hooks.append(norm.register_forward_pre_hook(make(None)))
         return True
 

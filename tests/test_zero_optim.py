@@ -90,9 +90,14 @@ def _prefetch_worker(rank, world):
         opt.pre_forward(lazy=True)                      # gloo gather, synchronous
         n = len(opt.buckets)
         index = {id(p): i for i, b in enumerate(opt.buckets) for p in b.params}
+        emb = index[id(m.embed_tokens)]
+        assert opt._prefetch_first == [emb] and opt._gather_order[0] == emb and sorted(opt._gather_order) == list(range(n))
+        pos = {b: k for k, b in enumerate(opt._gather_order)}      # gathers are queued in the order layers run
+        firsts = [min(pos[index[id(p)]] for p in layer.parameters()) for layer in m.layers]
+        assert firsts == sorted(firsts) and firsts[0] > pos[emb]
         opt._gather_events.update({i: i for i in range(n)})
-        opt.wait_gathered([0])
-        assert waited == [0]
+        opt.wait_gathered(opt._prefetch_first)
+        assert waited == [emb]
         seen_at_layer = []
         hooks = [layer.register_forward_pre_hook(lambda mod, a: seen_at_layer.append(list(waited))) for layer in m.layers]
         ids, labels = _data(rank)
