@@ -54,6 +54,7 @@ class _Bucket:
         self.param_buf: Optional[torch.Tensor] = torch.zeros(self.numel, dtype=dtype, device=device)
         self.grad_buf: Optional[torch.Tensor] = None
         self.pending = 0
+        self.contribs = 0
         self.reduced = False
         self.work = None
         with torch.no_grad():
@@ -262,17 +263,23 @@ class ZeROOptimizer:
         for b in self.buckets:
             b.reduced = False
             b.work = None
-            b.pending = sum(int(getattr(p, "grad_contribs", 1)) for p in b.params)
+            b.contribs = sum(int(getattr(p, "grad_contribs", 1)) for p in b.params)
+            b.pending = b.contribs
             if self.use_main_grad:
                 b.ensure_grad_buf(True)
                 for p in b.params:
                     if self.accumulation_count == 0 or self.stage >= 2:
                         p.grad_filled = False
 
-    def begin_backward(self, sync: bool = True):
+    def begin_backward(self, sync: bool = True, backward_passes: int = 1):
         """Declare whether the coming backward is the last of the accumulation window (stage 1 only
-        reduces then; stages 2/3 reduce after every backward)."""
+        reduces then; stages 2/3 reduce after every backward).  ``backward_passes`` is how many backward
+        passes write the gradients before they may be reduced (the micro-batches of a pipeline schedule):
+        a bucket's reduce-scatter is launched from the gradient hooks once every parameter in it has
+        received all of its contributions."""
         self.sync_this_backward = sync or self.stage >= 2
+        for b in self.buckets:
+            b.pending = b.contribs * max(1, int(backward_passes))
 
     # ---- gradient reduction ----------------------------------------------------------------------
     def _on_grad_ready(self, p):
@@ -318,6 +325,36 @@ class ZeROOptimizer:
                 b.grad_buf.record_stream(self.comm_stream)
         b.reduced = True
 
+    # ---- reductions captured in a CUDA graph ----------------------------------------------------------
+    def finish_captured_reduces(self) -> Dict[int, torch.Tensor]:
+        """Call at the end of a stream capture whose backward ran with ``begin_backward(sync=True)``: reduce
+        the buckets the gradient hooks did not reach, join the side stream back into the capturing stream
+        (a capture may not end with a forked stream) and hand back the reduced shards.  Those live in the
+        graph's memory pool and are rewritten by every replay; pass them to :meth:`adopt_reduced` after one."""
+        for b in self.buckets:
+            if not b.reduced:
+                self._launch_reduce(b, async_op=self.overlap)
+        if self.overlap:
+            torch.cuda.current_stream().wait_stream(self.comm_stream)
+        for b in self.buckets:
+            b.work = None           # recorded inside the capture: meaningless outside it
+        return dict(self._reduced_shards)
+
+    def abandon_captured_reduces(self):
+        """A capture failed half-way: nothing it recorded has run, so no bucket counts as reduced."""
+        self._reduced_shards.clear()
+        for b in self.buckets:
+            b.reduced = False
+            b.work = None
+
+    def adopt_reduced(self, shards: Dict[int, torch.Tensor]):
+        """After a graph replay that contained the reduce-scatters: the buckets are reduced, the shards are
+        the graph's static outputs (already ordered behind the replay on the current stream)."""
+        self._reduced_shards.update(shards)
+        for b in self.buckets:
+            b.reduced = True
+            b.work = None
+
     def _pack_autograd_grads(self):
         """CPU / non-fused path: copy ``p.grad`` into the bucket buffers."""
         for b in self.buckets:
@@ -349,14 +386,14 @@ class ZeROOptimizer:
             self._prepare_backward()
 
     def _reduce_all(self):
-        if all(b.reduced for b in self.buckets):
-            return
-        if not self.use_main_grad:
-            self._pack_autograd_grads()
-        for b in self.buckets:
-            if not b.reduced:
-                self._launch_reduce(b, async_op=False)
+        if not all(b.reduced for b in self.buckets):
+            if not self.use_main_grad:
+                self._pack_autograd_grads()
+            for b in self.buckets:
+                if not b.reduced:
+                    self._launch_reduce(b, async_op=False)
         if self.overlap:
+            # also when every bucket was already reduced from the gradient hooks: those ran on the side stream
             torch.cuda.current_stream().wait_stream(self.comm_stream)
 
     # ---- ZeRO-3 parameter residency --------------------------------------------------------------

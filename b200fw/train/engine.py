@@ -44,6 +44,7 @@ class TrainConfig:
     attention_backend: str = "sdpa"       # native flash kernel on GPU
     use_gradient_checkpoint: bool = False
     cuda_graph_step: bool = False              # replay forward + backward of a micro-batch as one CUDA graph
+    cuda_graph_reduce: bool = True              # ... with the last micro-batch's gradient reduce-scatters captured in it
     lora_rank: int = 16
     lora_alpha: float = 32.0
     lora_target_modules: List[str] = field(default_factory=lambda: [
@@ -356,7 +357,11 @@ class TrainEngine:
             return None
         rows = -(-n // 512) * 512                                       # bucket the row count
         first = self._accumulation_count == 0
-        key = (B, S, rows, first)
+        # last micro-batch of the window on several data-parallel ranks: the bucket reduce-scatters are captured
+        # too, on the optimizer's side stream, so they overlap the rest of the backward pass inside the graph
+        reduce_in_graph = (cfg.cuda_graph_reduce and opt.world > 1 and opt.stage == 1
+                           and self._accumulation_count + 1 >= cfg.gradient_accumulation_steps)
+        key = (B, S, rows, first, reduce_in_graph)
         seen = self._graph_seen.get(key, 0)
         self._graph_seen[key] = seen + 1
         if seen < 2:
@@ -371,7 +376,8 @@ class TrainEngine:
         g["lab"].fill_(-100)                                            # padding rows carry no label
         g["lab"][:n].copy_(shifted.index_select(0, valid_idx))
         if "graph" not in g:
-            opt.begin_backward(sync=False)      # no reduction launches from the gradient hooks inside the capture
+            # the gradient hooks launch reductions inside the capture only when they are meant to be part of it
+            opt.begin_backward(sync=reduce_in_graph)
             before = nv.launch_count
             try:
                 torch.cuda.synchronize()
@@ -381,9 +387,12 @@ class TrainEngine:
                                            valid_idx=g["idx"], valid_labels=g["lab"])
                     loss.backward()
                     g["loss"] = loss.detach()
+                    if reduce_in_graph:
+                        g["reduced"] = opt.finish_captured_reduces()
             except Exception as e:  # noqa: BLE001 - fall back to eager for good
                 logger.warning("CUDA-graph capture of the training micro-step failed (%s): running eagerly", e)
                 self._graph_disabled = True
+                opt.abandon_captured_reduces()
                 torch.cuda.synchronize()
                 return None
             if self._graph_pool is None:
@@ -398,11 +407,13 @@ class TrainEngine:
         for b in opt.buckets:
             for p in b.params:
                 p.grad_filled = True
+        if g.get("reduced") is not None:
+            opt.adopt_reduced(g["reduced"])
         return g["loss"].clone()
 
     def _pp_batch_step(self, input_ids, labels):
         cfg, opt = self.config, self.optimizer
-        opt.begin_backward(sync=True)
+        opt.begin_backward(sync=True, backward_passes=cfg.num_micro_batches)
         loss = self.pipeline_scheduler.run_1f1b_schedule(input_ids, labels)
         opt.post_backward()
         self._accumulation_count = cfg.gradient_accumulation_steps

@@ -46,6 +46,8 @@ def parse():
     ap.add_argument("--no-cuda-graph", dest="cuda_graph", action="store_false",
                     help="launch the micro-step kernel by kernel instead of replaying forward + backward as one CUDA "
                          "graph (the graph path applies to DP / single GPU with ZeRO <= 1; other layouts run eagerly)")
+    ap.add_argument("--no-graph-reduce", dest="graph_reduce", action="store_false",
+                    help="keep the gradient reduce-scatters out of the last micro-batch's CUDA graph (run them after it)")
     ap.add_argument("--layers", type=int, default=0,
                     help="override the preset's layer count (smoke runs of a large architecture; not a benchmark config)")
     ap.add_argument("--fused-tp", action="store_true",
@@ -146,7 +148,8 @@ def run_ours(a):
                       gradient_accumulation_steps=a.grad_accum if a.pp == 1 else 1, grpo_beta=0.0,
                       zero_stage=a.zero_stage, warmup_steps=2, total_training_steps=a.steps + a.warmup + 8,
                       sequence_parallel=a.sequence_parallel, amp_dtype="bf16", zero_comm_backend=a.zero_comm,
-                      fused_tp_comm=a.fused_tp, cuda_graph_step=a.cuda_graph, zero3_prefetch=a.zero3_prefetch)
+                      fused_tp_comm=a.fused_tp, cuda_graph_step=a.cuda_graph, zero3_prefetch=a.zero3_prefetch,
+                      cuda_graph_reduce=a.graph_reduce)
     eng = TrainEngine(cfg).initialize()
     dev = eng.device
     accum = a.grad_accum
@@ -219,7 +222,7 @@ def run_ours(a):
                        "grad_accum": a.grad_accum, "seq_len": a.seq_len, "parallelism": par,
                        "zero_stage": a.zero_stage, "zero_comm": a.zero_comm, "zero3_prefetch": a.zero3_prefetch,
                        "sequence_parallel": a.sequence_parallel, "fused_tp_comm": a.fused_tp, "grad_ckpt": a.grad_ckpt,
-                       "cuda_graph_step": a.cuda_graph, "l2": "inputs larger than L2 (weights+activations >> 126 MB)",
+                       "cuda_graph_step": a.cuda_graph, "cuda_graph_reduce": a.graph_reduce, "l2": "inputs larger than L2 (weights+activations >> 126 MB)",
                        "step": "one optimizer step = grad_accum micro-batches + reduce + clip + AdamW"},
             "mfu_exact_of_measured_sustained": flops / (step_s * world * peaks["bf16_tflops_sustained"] * 1e12),
             "model_tflops_per_gpu": flops / step_s / world / 1e12,

@@ -139,6 +139,46 @@ def test_zero3_prefetched_gathers_match_zero1():
         assert abs(a[r][1][1] - b[r][1][1]) / a[r][1][1] < 2e-3
 
 
+def _graph_dp_worker(rank, world, graph, reduce_in_graph):
+    from b200fw.train import TrainConfig, TrainEngine
+    cfg = TrainConfig(model_preset="tiny128", dp_size=world, lora_rank=0, grpo_beta=0.0, learning_rate=1e-3,
+                      gradient_accumulation_steps=2, zero_stage=1, warmup_steps=0, max_seq_len=256, amp_dtype="bf16",
+                      bucket_mb=1.0, cuda_graph_step=graph, cuda_graph_reduce=reduce_in_graph)
+    eng = TrainEngine(cfg).initialize()
+    out = []
+    for s in range(14):                      # 7 optimizer steps: two eager occurrences per graph key, then replays
+        g = torch.Generator().manual_seed(s * 31 + rank)
+        ids = torch.randint(0, 8192, (2, 256), generator=g)
+        labels = ids.clone()
+        labels[:, :128] = -100
+        m = eng.sft_step_tensors(ids, labels)
+        out.append((m.loss, m.grad_norm))
+    flat = torch.cat([p.detach().float().reshape(-1) for p in eng.model.parameters()])
+    keys = sorted(k[3:] for k in eng._graphs)
+    return out, float(flat.double().sum()), float(flat.abs().double().sum()), keys, eng._graph_disabled
+
+
+@needs2
+def test_graphed_micro_step_with_captured_reduce_scatter_matches_eager():
+    """Data parallel: the last micro-batch's graph contains the bucket reduce-scatters (side stream forked
+    and joined inside the capture); losses, gradient norms and weights follow the eager run."""
+    from _gpu_dist_util import run_gpu_ranks
+    w = _world()
+    eager = run_gpu_ranks(_graph_dp_worker, w, False, False)
+    fused = run_gpu_ranks(_graph_dp_worker, w, True, True)
+    plain = run_gpu_ranks(_graph_dp_worker, w, True, False)
+    assert fused[0][3] == [(False, True), (True, False)] and not fused[0][4]       # (first, reduce captured) keys
+    assert plain[0][3] == [(False, False), (True, False)] and eager[0][3] == []
+    for r in range(w):
+        for other in (fused, plain):
+            assert other[r][1] == other[0][1]                                     # ranks hold identical weights
+            for i, ((la, ga), (lb, gb)) in enumerate(zip(eager[r][0], other[r][0])):
+                assert abs(la - lb) < 2e-2, (i, la, lb)
+                if i < 8:     # later steps amplify the rounding noise of the atomically accumulated gradients
+                    assert ga > 0 and abs(ga - gb) / ga < 5e-2, (i, ga, gb)
+            assert abs(eager[r][2] - other[r][2]) / eager[r][2] < 1e-3
+
+
 def _peer_sync_worker(rank, world):
     import torch.distributed as dist
     from b200fw.sync import PeerWeightSync
