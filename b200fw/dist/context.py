@@ -104,7 +104,17 @@ class ParallelContext:
     def reset(cls):
         cls._instance = None
 
+    def on_destroy(self, fn):
+        """Run ``fn()`` before the process groups are torn down (``destroy``).  CUDA graphs that captured
+        collectives must be released first: a communicator waits for every graph that references it."""
+        self.__dict__.setdefault("_destroy_callbacks", []).append(fn)
+
     def destroy(self):
+        for fn in reversed(self.__dict__.pop("_destroy_callbacks", [])):
+            try:
+                fn()
+            except Exception:  # noqa: BLE001 - teardown goes on
+                pass
         if self.owns_process_group and dist.is_initialized():
             dist.destroy_process_group()
         ParallelContext._instance = None

@@ -195,6 +195,7 @@ class TrainEngine:
         self.lr_scheduler = LRSchedule(cfg.learning_rate, cfg.lr_scheduler_type, cfg.warmup_steps,
                                        cfg.total_training_steps, cfg.min_lr_ratio)
         self.optimizer.param_groups[0]["lr"] = self.lr_scheduler.lr_at(0)
+        ctx.on_destroy(self.release_graphs)
         if cfg.pp_size > 1:
             self.pipeline_scheduler = PipelineScheduler(self.model, self.pp_context, cfg.num_micro_batches)
         if cfg.icepop_enabled:
@@ -327,6 +328,22 @@ class TrainEngine:
         return loss.detach(), self._maybe_step()
 
     # ---- CUDA-graph micro-step ----------------------------------------------------------------------
+    def release_graphs(self):
+        """Drop every captured micro-step graph (and the memory pool they share).  Graphs that contain
+        reduce-scatters hold references on the NCCL communicator, which cannot be destroyed before them;
+        the parallel context calls this ahead of its own teardown."""
+        if self._graphs:
+            if self.device.type == "cuda":
+                torch.cuda.synchronize()
+            self._graphs.clear()
+            self._graph_pool = None
+            if self.optimizer is not None:
+                self.optimizer._reduced_shards.clear()      # may point into the released pool
+            import gc
+            gc.collect()
+            if self.device.type == "cuda":
+                torch.cuda.synchronize()
+
     def _graph_eligible(self) -> bool:
         cfg, opt = self.config, self.optimizer
         return (cfg.cuda_graph_step and not self._graph_disabled and self.device.type == "cuda"

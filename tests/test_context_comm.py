@@ -114,3 +114,17 @@ def test_stream_manager_cpu_noop():
         pass
     sm.sync_compute_to_comm()
     assert sm.get_stats()["comm_ops"] == 1
+
+
+def test_destroy_runs_registered_callbacks_first():
+    """Teardown hooks (release of CUDA graphs that captured collectives) run before the groups go, newest
+    first, and a failing one does not stop the teardown."""
+    ctx = ParallelContext.init_single_process()
+    order = []
+    ctx.on_destroy(lambda: order.append("a"))
+    ctx.on_destroy(lambda: 1 / 0)
+    ctx.on_destroy(lambda: order.append("b"))
+    ctx.destroy()
+    assert order == ["b", "a"] and ParallelContext._instance is None
+    ctx.destroy()                                   # callbacks ran once
+    assert order == ["b", "a"]
