@@ -44,7 +44,7 @@ class TrainConfig:
     attention_backend: str = "sdpa"       # native flash kernel on GPU
     use_gradient_checkpoint: bool = False
     cuda_graph_step: bool = False              # replay forward + backward of a micro-batch as one CUDA graph
-    cuda_graph_reduce: bool = True              # ... with the last micro-batch's gradient reduce-scatters captured in it
+    cuda_graph_reduce: bool = False             # ... with the last micro-batch's gradient reduce-scatters captured in it
     lora_rank: int = 16
     lora_alpha: float = 32.0
     lora_target_modules: List[str] = field(default_factory=lambda: [

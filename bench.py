@@ -46,8 +46,9 @@ def parse():
     ap.add_argument("--no-cuda-graph", dest="cuda_graph", action="store_false",
                     help="launch the micro-step kernel by kernel instead of replaying forward + backward as one CUDA "
                          "graph (the graph path applies to DP / single GPU with ZeRO <= 1; other layouts run eagerly)")
-    ap.add_argument("--no-graph-reduce", dest="graph_reduce", action="store_false",
-                    help="keep the gradient reduce-scatters out of the last micro-batch's CUDA graph (run them after it)")
+    ap.add_argument("--graph-reduce", dest="graph_reduce", action="store_true",
+                    help="capture the gradient reduce-scatters inside the last micro-batch's CUDA graph, overlapped with "
+                         "its backward (default: they run after the replay)")
     ap.add_argument("--layers", type=int, default=0,
                     help="override the preset's layer count (smoke runs of a large architecture; not a benchmark config)")
     ap.add_argument("--fused-tp", action="store_true",
