@@ -17,6 +17,7 @@ from typing import Dict, List, Optional
 import torch
 
 from ..model import ModelConfig, ParallelTransformerModel, load_from_hf_checkpoint, read_hf_config
+from ..obs import nvtx
 from ..obs.logging import get_logger
 from .config import InferenceConfig
 from .graphs import CUDAGraphRunner
@@ -156,7 +157,8 @@ class InferenceEngine:
     def step(self) -> Dict[str, List[int]]:
         """Schedule, run prefill chunks and one decode token for every running sequence.  Returns the
         tokens produced in this step per request id."""
-        out = self.scheduler.schedule()
+        with nvtx.range("infer/schedule"):
+            out = self.scheduler.schedule()
         self.stats["steps"] += 1
         for r in out.preempted_requests:
             self._release(r, cache_prefix=False)
@@ -166,9 +168,11 @@ class InferenceEngine:
         try:
             decode = [r for r in out.decode_requests if r.request_id not in out.prefill_tokens]
             if out.prefill_requests:
-                self._execute_prefill(out, produced)
+                with nvtx.range("infer/prefill"):
+                    self._execute_prefill(out, produced)
             if decode:
-                self._execute_decode(decode, produced)
+                with nvtx.range("infer/decode"):
+                    self._execute_decode(decode, produced)
         except torch.cuda.OutOfMemoryError:
             self._recover_from_oom()
             return produced

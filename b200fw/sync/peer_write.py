@@ -24,6 +24,7 @@ import torch
 import torch.distributed as dist
 
 from .. import _native as nv
+from ..obs import nvtx
 from .nccl_transfer import TransferStats
 
 MASK64 = (1 << 64) - 1
@@ -166,6 +167,7 @@ class PeerWeightSync:
         return (a & MASK64, b & MASK64), nbytes
 
     # ---- protocol ------------------------------------------------------------------------------------------
+    @nvtx.annotate("sync/peer_write")
     def sync(self, is_sender: bool, state: Optional[Dict[str, torch.Tensor]] = None, engine=None,
              add: bool = False, corrupt: bool = False) -> int:
         """One full sync.  Process-local when there is no group.  ``corrupt`` flips the announced

@@ -25,6 +25,7 @@ from ..obs.logging import get_logger
 from ..obs.memory import MemoryBreakdown, MemoryProfiler, MemoryReport
 from ..obs.metrics import MetricsCollector
 from ..ops import grpo_token_loss
+from ..obs import nvtx
 from ..optim import LRSchedule, ZeROOptimizer, build_optimizer
 from ..pipeline import PipelineParallelContext, PipelineScheduler
 from .icepop import IcePopConfig, IcePopFilter
@@ -250,8 +251,10 @@ class TrainEngine:
             return None
         opt = self.optimizer
         opt.param_groups[0]["lr"] = self.lr_scheduler.get_last_lr()[0]
-        gn = opt.clip_grad_norm(cfg.max_grad_norm)
-        opt.step()           # the kernel itself skips the update when the norm is not finite
+        with nvtx.range("train/reduce_and_clip"):
+            gn = opt.clip_grad_norm(cfg.max_grad_norm)
+        with nvtx.range("train/adamw_and_publish"):
+            opt.step()           # the kernel itself skips the update when the norm is not finite
         opt.zero_grad()
         self._accumulation_count = 0
         return gn
@@ -314,15 +317,18 @@ class TrainEngine:
         cfg, opt = self.config, self.optimizer
         opt.pre_forward(lazy=True)
         if self._graph_eligible():
-            loss = self._graphed_micro_step(input_ids, labels, valid_idx)
+            with nvtx.range("train/micro_step/graph"):
+                loss = self._graphed_micro_step(input_ids, labels, valid_idx)
             if loss is not None:
                 opt.post_backward()
                 self._accumulation_count += 1
                 return loss, self._maybe_step()
         opt.begin_backward(sync=self._accumulation_count + 1 >= cfg.gradient_accumulation_steps)
-        loss = self.model.loss(input_ids, labels, loss_scale=1.0 / cfg.gradient_accumulation_steps,
-                               valid_idx=valid_idx)
-        loss.backward()
+        with nvtx.range("train/micro_step/forward"):
+            loss = self.model.loss(input_ids, labels, loss_scale=1.0 / cfg.gradient_accumulation_steps,
+                                   valid_idx=valid_idx)
+        with nvtx.range("train/micro_step/backward"):
+            loss.backward()
         opt.post_backward()
         self._accumulation_count += 1
         return loss.detach(), self._maybe_step()

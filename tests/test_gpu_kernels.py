@@ -297,3 +297,27 @@ def test_sumsq_adamw():
     before = master.clone()
     fused_adamw(master, m, v, g, hyper, norm_sq=torch.tensor([float("inf")], device=DEV))
     assert torch.equal(before, master)
+
+
+def test_kernels_write_only_inside_their_outputs():
+    """Every tensor the ops allocate sits between guard bands; the tile-edge cases of the tests above are run
+    again and no kernel may have written outside its payload (host-side check after a synchronize)."""
+    from b200fw.ops.debug import canary_arena
+    with canary_arena() as arena:
+        test_gemm_layouts(0, 0, (1000, 776, 520), 0)
+        test_gemm_layouts(1, 1, (136, 72, 2056), 128)
+        test_gemm_layouts(0, 1, (136, 72, 2056), 256)
+        test_gemm_epilogues()
+        test_gemm_split_k_fp32_weight_gradient_shapes(1000, 776, 4100)
+        test_linear_autograd()
+        test_rmsnorm(264)
+        test_rmsnorm(5120)
+        test_qknorm_rope_fwd_bwd(77, 2, 1)
+        test_swiglu_embedding()
+        test_flash_attention(2, 200, 2, 2)
+        test_flash_attention(1, 77, 2, 1)
+        test_fused_qkv_attention()
+        test_lm_head_ce_and_logprob()
+        test_grpo_loss()
+        test_sumsq_adamw()
+    assert len(arena.records) > 40 and arena.violations() == []

@@ -50,6 +50,30 @@ def test_event_files_round_trip_without_the_tensorboard_package(capsys):
         assert mod.main([d, "--tag", "missing"]) == 1
 
 
+def test_nvtx_ranges_are_free_when_off_and_balanced_when_on():
+    from b200fw.obs import nvtx
+    was = nvtx.enabled()
+    try:
+        nvtx.enable(False)
+        assert nvtx.range("a") is nvtx.range("b")               # shared no-op context
+        calls = []
+
+        @nvtx.annotate("unit/fn")
+        def f(x):
+            calls.append(x)
+            return x + 1
+
+        assert f(1) == 2
+        before = nvtx._state["pushed"]
+        nvtx.enable(True)
+        with nvtx.range("outer"):
+            with nvtx.range("inner"):
+                assert f(2) == 3
+        assert nvtx._state["pushed"] == before + 3 and calls == [1, 2]
+    finally:
+        nvtx.enable(was)
+
+
 def test_metrics_collector_and_artifacts():
     m = MetricsCollector()
     for i, v in enumerate([1.0, 2.0, 3.0]):
