@@ -1,4 +1,4 @@
-"""Observability helpers, reward / data, and the disaggregated loop over gloo (2 trainers + 2 engines)."""
+"""Observability helpers (metrics, event files, NVTX, profilers, timeline, memory, eval) and the disaggregated loop over gloo."""
 import json
 import os
 import tempfile
