@@ -71,6 +71,8 @@ PRESETS: Dict[str, ModelConfig] = {
                               head_dim=128, intermediate_size=3072, tie_word_embeddings=True),
     "qwen3-4b": ModelConfig(vocab_size=151936, hidden_size=2560, num_layers=36, num_heads=32, num_kv_heads=8,
                             head_dim=128, intermediate_size=9728, tie_word_embeddings=True),
+    "qwen3-8b": ModelConfig(vocab_size=151936, hidden_size=4096, num_layers=36, num_heads=32, num_kv_heads=8,
+                            head_dim=128, intermediate_size=12288, tie_word_embeddings=False),
     "qwen3-32b": ModelConfig(vocab_size=151936, hidden_size=5120, num_layers=64, num_heads=64, num_kv_heads=8,
                              head_dim=128, intermediate_size=25600, tie_word_embeddings=False),
 }
