@@ -169,7 +169,11 @@ class TrainEngine:
             mc, ctx, layer_range, first, last, sequence_parallel=cfg.sequence_parallel,
             gradient_checkpointing=cfg.use_gradient_checkpoint, dtype=self.dtype, device=self.device)
         self.model.init_weights(cfg.seed)
-        if cfg.fused_tp_comm and cfg.sequence_parallel and self.device.type == "cuda":
+        # `enable_comm_overlap` is the reference's switch for overlapping tensor-parallel communication with
+        # compute (its async MLP all-reduce: src/distributed/tensor_parallel.py:718-720); here the overlap is
+        # the fused all-gather -> GEMM / GEMM -> reduce-scatter kernels, which need the sequence-parallel layout
+        if ((cfg.fused_tp_comm or cfg.enable_comm_overlap) and cfg.sequence_parallel and cfg.tp_size > 1
+                and self.device.type == "cuda"):
             self.model.set_fused_comm(True)
         if cfg.model_path and os.path.isdir(cfg.model_path):
             loaded, missing = load_from_hf_checkpoint(self.model, cfg.model_path)
