@@ -17,6 +17,7 @@ from __future__ import annotations
 import asyncio
 import csv
 import enum
+import math
 import os
 import time
 from concurrent.futures import ThreadPoolExecutor
@@ -28,7 +29,8 @@ import torch
 from ..config import ColocateConfig, config_snapshot
 from ..data import GRPOBatch, GSM8KDataPipeline, SyntheticTokenPipeline
 from ..infer import InferenceConfig, InferenceEngine
-from ..obs import ArtifactWriter, CommProfiler, ComputeProfiler, MemoryProfiler, MetricsCollector, get_logger
+from ..obs import (ArtifactWriter, CommProfiler, ComputeProfiler, EvalMetrics, MemoryProfiler, MetricsCollector,
+                   compute_bleu4, compute_exact_match, compute_token_f1, get_logger)
 from ..reward import GSM8KRewardFunction, SyntheticTokenReward
 from ..sync import PeerWeightSync, SwiftSyncConfig, SwiftSyncTransfer
 from ..train import C3POConfig, C3POPlusScheduler, TrainConfig, TrainEngine, TrainMetrics
@@ -93,6 +95,8 @@ class ColocateOrchestrator:
         self.swift: Optional[SwiftSyncTransfer] = None
         self.weight_sync: Optional[PeerWeightSync] = None
         self.tb = None
+        self._eval_snapshots: Dict[str, List[Dict]] = {}
+        self.eval_results: Dict[str, Dict] = {}
         self.state_log: List[str] = []
         self.weights_version = 0
         self._batches = None
@@ -311,6 +315,8 @@ class ColocateOrchestrator:
         self._start_time = time.time()
         loop = asyncio.get_running_loop()
         pending: Optional[asyncio.Future] = None
+        if cfg.eval_num_prompts > 0:
+            self._do_eval("before")
         for it in range(cfg.total_iterations):
             im = IterationMetrics(it)
             t_iter = time.perf_counter()
@@ -385,6 +391,8 @@ class ColocateOrchestrator:
                 await pending
             except Exception:  # noqa: BLE001
                 pass
+        if cfg.eval_num_prompts > 0:
+            self._do_eval("after")
         if cfg.checkpoint_save_enabled:
             self._save_checkpoint("final")
         self._set_state(OrchestratorState.DONE)
@@ -454,6 +462,62 @@ class ColocateOrchestrator:
                                                      mc.intermediate_size, mc.vocab_size, full=cfg.lora_rank <= 0)
         return self.compute_profiler.compute_mfu(fl / (cfg.tp_size * cfg.pp_size), t)
 
+    def _do_eval(self, stage: str) -> Dict:
+        """Fixed-prompt evaluation before / after training (src/orchestrator/colocate_orchestrator.py:940-1060):
+        SFT loss and perplexity on the reference responses, then one sampled generation per prompt scored by
+        exact match, token F1 and BLEU-4.  Writes ``eval_<stage>.json`` and, after the second stage,
+        ``fixed_prompt_comparison.json``.  Every rank evaluates its own data shard (ZeRO-3 needs all ranks in
+        the forward); rank 0 writes."""
+        cfg, eng = self.config, self.train_engine
+        if cfg.eval_num_prompts <= 0 or self.data is None:
+            return {}
+        batch = next(iter(self.data.get_batches(cfg.eval_num_prompts)), None)
+        if batch is None:
+            logger.warning("no data for the %s evaluation (%d prompts wanted)", stage, cfg.eval_num_prompts)
+            return {}
+        tok = self.data.tokenizer
+        eos = getattr(tok, "eos_token_id", None)
+        references = batch.reference_responses or [str(g) for g in batch.ground_truths]
+        eval_loss = perplexity = None
+        if batch.reference_responses:
+            resp = [list(tok.encode(t)) + ([eos] if eos is not None else []) for t in references]
+            eval_loss = eng.eval_sft_loss(batch.prompt_tokens, resp)
+            perplexity = math.exp(min(eval_loss, 20.0))
+        samples, em = [], EvalMetrics()
+        for i, (prompt, ptoks, ref) in enumerate(zip(batch.prompts, batch.prompt_tokens, references)):
+            out = eng.generate(ptoks, cfg.eval_max_tokens, 0.7, 0.95, eos)
+            text = tok.decode(out, skip_special_tokens=True)
+            em.add(text, ref)
+            samples.append({"index": i, "prompt": prompt, "generated": text, "reference": ref,
+                            "generated_tokens": len(out), "exact_match": bool(compute_exact_match(text, ref)),
+                            "token_f1": compute_token_f1(text, ref), "bleu4": compute_bleu4(text, ref)})
+        n = max(1, len(samples))
+        metrics = {"stage": stage, "step": eng.step_count, "eval_loss": eval_loss, "perplexity": perplexity,
+                   "exact_match": sum(s["exact_match"] for s in samples) / n,
+                   "token_f1": sum(s["token_f1"] for s in samples) / n,
+                   "bleu4": sum(s["bleu4"] for s in samples) / n, "num_samples": len(samples)}
+        logger.info("eval (%s): loss=%s ppl=%s exact_match=%.4f token_f1=%.4f bleu4=%.4f", stage,
+                    "n/a" if eval_loss is None else f"{eval_loss:.4f}",
+                    "n/a" if perplexity is None else f"{perplexity:.3f}",
+                    metrics["exact_match"], metrics["token_f1"], metrics["bleu4"])
+        if self.tb is not None:
+            if eval_loss is not None:
+                self.tb.add_scalar(f"eval/{stage}_loss", eval_loss, eng.step_count)
+                self.tb.add_scalar(f"eval/{stage}_perplexity", perplexity, eng.step_count)
+            self.tb.add_scalar(f"eval/{stage}_exact_match", metrics["exact_match"], eng.step_count)
+            self.tb.add_scalar(f"eval/{stage}_token_f1", metrics["token_f1"], eng.step_count)
+        self._eval_snapshots[stage] = samples
+        self.eval_results[stage] = metrics
+        self.artifacts.write_json(f"eval_{stage}.json", {"metrics": metrics, "samples": samples})
+        if stage == "after" and "before" in self._eval_snapshots:
+            rows = [{"index": b["index"], "prompt": b["prompt"], "reference": b["reference"],
+                     "before_generated": b["generated"], "after_generated": a["generated"],
+                     "before_token_f1": b["token_f1"], "after_token_f1": a["token_f1"],
+                     "before_exact_match": b["exact_match"], "after_exact_match": a["exact_match"]}
+                    for b, a in zip(self._eval_snapshots["before"], samples)]
+            self.artifacts.write_json("fixed_prompt_comparison.json", {"samples": rows})
+        return metrics
+
     def _save_checkpoint(self, tag: str):
         base = self.config.checkpoint_save_dir
         for name in (tag, "latest"):
@@ -482,6 +546,7 @@ class ColocateOrchestrator:
                             "tokens_generated": sum(m.tokens_generated for m in ok),
                             "mfu_samples": self.collector.series.get("mfu", [])},
             "metrics": self.collector.summary(),
+            "eval": self.eval_results,
             "state_log_tail": self.state_log[-16:],
         }
         if self.infer_engine is not None:
@@ -501,11 +566,34 @@ class ColocateOrchestrator:
                 for m in self.metrics:
                     if m.train_metrics is not None:
                         w.writerow([m.iteration, m.train_metrics.loss, m.train_metrics.grad_norm, m.avg_reward])
+            self._render_loss_curve()
         self.artifacts.write_json("memory_timeline.json", self.memory.timeline(), all_ranks=True)
         rep = self.train_engine.generate_memory_report(self.config.batch_size * self.config.max_seq_len)
         self.artifacts.write_json("memory_report.json", rep.to_dict())
         if self.tb is not None:
             self.tb.flush()
+
+    def _render_loss_curve(self):
+        """``loss_curve.png`` next to the CSV when matplotlib is importable (the CSV is always written)."""
+        rows = [(m.iteration, m.train_metrics.loss) for m in self.metrics if m.train_metrics is not None]
+        if not rows:
+            return
+        try:
+            import matplotlib
+            matplotlib.use("Agg")
+            import matplotlib.pyplot as plt
+        except Exception:  # noqa: BLE001 - optional dependency
+            logger.info("matplotlib is not installed: loss_curve.png skipped, loss_curve.csv written")
+            return
+        plt.figure(figsize=(8, 4.5))
+        plt.plot([r[0] for r in rows], [r[1] for r in rows], marker="o", linewidth=1.5)
+        plt.xlabel("Iteration")
+        plt.ylabel("Loss")
+        plt.title("Training loss")
+        plt.grid(True, alpha=0.3)
+        plt.tight_layout()
+        plt.savefig(self.artifacts.path("loss_curve.png"), dpi=160)
+        plt.close()
 
     async def shutdown(self):
         self._pool.shutdown(wait=True)

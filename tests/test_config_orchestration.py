@@ -3,6 +3,7 @@ paths, and host-side fault injection."""
 import asyncio
 import glob
 import json
+import math
 import os
 import tempfile
 import threading
@@ -125,6 +126,42 @@ def test_colocate_sft_mode_and_resume():
                          resume_from=os.path.join(cfg.checkpoint_save_dir, "final"))
         o2, _ = _run(cfg2)
         assert o2.train_engine.step_count == 4
+
+
+def test_eval_before_after_artifacts_and_fixed_prompt_comparison():
+    import json
+    from b200fw.data.pipeline import GSM8KDataPipeline
+    recs = [{"question": f"{i} plus {i}?", "answer": f"#### {2 * i}"} for i in range(8)]
+    with tempfile.TemporaryDirectory() as d:
+        cfg = _tiny_cfg(d, training_mode="sft", inference_preview_enabled=False, total_iterations=2, synthetic_data=False,
+                        eval_num_prompts=2, eval_max_tokens=4, checkpoint_save_enabled=False, tensorboard=True)
+        data = GSM8KDataPipeline(records=recs, prompt_template="plain")
+        o, s = _run(cfg, data=data)
+        out = cfg.output_dir
+        before = json.load(open(os.path.join(out, "eval_before.json")))
+        after = json.load(open(os.path.join(out, "eval_after.json")))
+        cmp_ = json.load(open(os.path.join(out, "fixed_prompt_comparison.json")))
+        for payload, stage in ((before, "before"), (after, "after")):
+            m = payload["metrics"]
+            assert m["stage"] == stage and m["num_samples"] == 2 and m["eval_loss"] > 0
+            assert abs(m["perplexity"] - math.exp(min(m["eval_loss"], 20.0))) < 1e-6
+            assert 0.0 <= m["token_f1"] <= 1.0 and 0.0 <= m["bleu4"] <= 1.0 and 0.0 <= m["exact_match"] <= 1.0
+            assert [x["index"] for x in payload["samples"]] == [0, 1]
+            assert all(x["generated_tokens"] <= 4 and x["reference"].startswith("####") for x in payload["samples"])
+        assert before["metrics"]["step"] == 0 and after["metrics"]["step"] == 2
+        assert after["metrics"]["eval_loss"] < before["metrics"]["eval_loss"]          # the same two prompts were trained on
+        assert [r["prompt"] for r in cmp_["samples"]] == [x["prompt"] for x in before["samples"]]
+        assert set(cmp_["samples"][0]) >= {"before_generated", "after_generated", "before_token_f1", "after_exact_match"}
+        assert s["eval"]["before"]["num_samples"] == 2 and "after" in s["eval"]
+        from b200fw.obs import read_scalars
+        tags = read_scalars(os.path.join(out, "tensorboard"))
+        assert "eval/before_loss" in tags and "eval/after_token_f1" in tags and "train/loss" in tags
+        assert os.path.exists(os.path.join(out, "loss_curve.csv"))
+    with tempfile.TemporaryDirectory() as d:                                            # eval.num_prompts: 0 -> no files
+        cfg = _tiny_cfg(d, training_mode="sft", inference_preview_enabled=False, total_iterations=1,
+                        checkpoint_save_enabled=False)
+        _run(cfg)
+        assert not os.path.exists(os.path.join(cfg.output_dir, "eval_before.json"))
 
 
 class _FakeResp:
