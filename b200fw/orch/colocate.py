@@ -97,6 +97,7 @@ class ColocateOrchestrator:
         self.tb = None
         self._eval_snapshots: Dict[str, List[Dict]] = {}
         self.eval_results: Dict[str, Dict] = {}
+        self.last_preview: Optional[str] = None
         self.state_log: List[str] = []
         self.weights_version = 0
         self._batches = None
@@ -328,6 +329,18 @@ class ColocateOrchestrator:
                     im.train_metrics = self._train_sft(batch)
                     im.state_durations["training"] = time.perf_counter() - t0
                     im.tokens_trained = sum(len(p) for p in batch.prompt_tokens)
+                    if cfg.inference_preview_enabled and cfg.max_tokens > 0 and self.infer_engine is not None:
+                        # preview only, not used for the loss (src/orchestrator/colocate_orchestrator.py:459-466):
+                        # one sample for the batch's first prompt from the weights just trained
+                        self._set_state(OrchestratorState.INFERRING)
+                        t0 = time.perf_counter()
+                        im.weights_version = self._sync_weights(it)
+                        out = self.infer_engine.generate(batch.prompt_tokens[:1], cfg.max_tokens, cfg.temperature, cfg.top_p)
+                        im.tokens_generated = len(out[0]) if out and out[0] else 0
+                        if out and out[0] and self.data is not None:
+                            self.last_preview = self.data.tokenizer.decode(out[0], skip_special_tokens=True)
+                            logger.info("preview: %s", ascii(self.last_preview[:120]))
+                        im.state_durations["inferring"] = time.perf_counter() - t0
                 else:
                     # ---- rollout (possibly prefetched while the previous iteration trained) ----------------
                     self._set_state(OrchestratorState.INFERRING)

@@ -122,6 +122,13 @@ def test_colocate_sft_mode_and_resume():
         cfg = _tiny_cfg(d, training_mode="sft", inference_preview_enabled=False, total_iterations=3)
         o, s = _run(cfg)
         assert s["results"]["final_loss"] is not None and o.state_log.count("training") == 3
+        # with the preview on, every iteration also generates one sample from the freshly synced weights
+        cfgp = _tiny_cfg(os.path.join(d, "p"), training_mode="sft", inference_preview_enabled=True, total_iterations=2,
+                         checkpoint_save_enabled=False)
+        op, _ = _run(cfgp)
+        assert op.state_log.count("inferring") == 2 and op.last_preview is not None
+        assert all(0 < m.tokens_generated <= cfgp.max_tokens and "inferring" in m.state_durations for m in op.metrics)
+        assert op.infer_engine.weights_version >= 2
         cfg2 = _tiny_cfg(d, training_mode="sft", inference_preview_enabled=False, total_iterations=1,
                          resume_from=os.path.join(cfg.checkpoint_save_dir, "final"))
         o2, _ = _run(cfg2)
