@@ -98,6 +98,7 @@ class ColocateOrchestrator:
         self._eval_snapshots: Dict[str, List[Dict]] = {}
         self.eval_results: Dict[str, Dict] = {}
         self.last_preview: Optional[str] = None
+        self._last_checkpoint_path: Optional[str] = None
         self.state_log: List[str] = []
         self.weights_version = 0
         self._batches = None
@@ -535,6 +536,7 @@ class ColocateOrchestrator:
         base = self.config.checkpoint_save_dir
         for name in (tag, "latest"):
             self.train_engine.save_checkpoint(os.path.join(base, name))
+        self._last_checkpoint_path = os.path.join(base, tag)
 
     def get_summary(self) -> Dict:
         ok = [m for m in self.metrics if m.error is None]
@@ -570,8 +572,59 @@ class ColocateOrchestrator:
             summary["weight_sync"] = self.weight_sync.get_stats()
         return summary
 
+    def _performance_block(self) -> Dict:
+        """Throughput and MFU of the run (src/orchestrator/colocate_orchestrator.py:1145-1280).  Two MFU
+        figures: the reference's formula (no attention S^2 term, ``4H^2`` projections; kept for comparison
+        with its published numbers) and exact matmul FLOPs; both against the measured sustained bf16 GEMM
+        throughput of the device instead of a datasheet peak."""
+        cfg, eng = self.config, self.train_engine
+        mc = eng.model_config
+        ok = [m for m in self.metrics if m.error is None]
+        times = [m.state_durations.get("training", m.total_time) for m in ok]
+        if not times or sum(times) <= 0:
+            return {}
+        step = sum(times) / len(times)
+        full = cfg.lora_rank <= 0
+        tp, pp, dp = max(1, cfg.tp_size), max(1, cfg.pp_size), max(1, cfg.dp_size)
+        prof = self.compute_profiler or ComputeProfiler()
+        ref_fl = ComputeProfiler.reference_formula_flops(mc.num_layers, cfg.batch_size, cfg.max_seq_len, mc.hidden_size,
+                                                         mc.intermediate_size, mc.vocab_size, full=full) / (tp * pp)
+        exact_fl = ComputeProfiler.exact_flops(mc, cfg.batch_size, cfg.max_seq_len, full=full,
+                                               grad_checkpoint=cfg.use_gradient_checkpoint) / (tp * pp)
+        gbs = cfg.batch_size * dp
+        return {
+            "mfu_percent": round(100 * prof.compute_mfu(ref_fl, step), 2),
+            "mfu_exact_percent": round(100 * prof.compute_mfu(exact_fl, step), 2),
+            "per_gpu_training_flops": int(ref_fl), "per_gpu_training_flops_exact": int(exact_fl),
+            "actual_tflops_per_gpu": round(ref_fl / step / 1e12, 2), "device_peak_tflops": prof.peak_tflops,
+            "world_size": tp * pp * dp, "tp_size": tp, "pp_size": pp, "dp_size": dp, "global_batch_size": gbs,
+            "tokens_per_second": round(gbs * cfg.max_seq_len / step), "samples_per_second": round(gbs / step, 2),
+            "avg_step_time_s": round(step, 4), "model_params": mc.num_params(),
+            "model_arch": {"num_layers": mc.num_layers, "hidden_size": mc.hidden_size,
+                           "intermediate_size": mc.intermediate_size, "vocab_size": mc.vocab_size,
+                           "seq_len": cfg.max_seq_len},
+            "primary_metric": "mfu" if full else "tokens_per_second",
+            "note": (f"MFU = forward FLOPs x {3 if full else 2} / (tp x pp) / (step time x peak); peak = measured "
+                     f"sustained bf16 GEMM throughput of this device class ({prof.peak_tflops:.0f} TFLOP/s); tokens/s "
+                     f"assumes batch_size x max_seq_len tokens per rank and step (padding counted, as the reference does)"),
+        }
+
     def _write_final_artifacts(self):
-        self.artifacts.write_json("run_summary.json", self.get_summary())
+        summary = self.get_summary()
+        cfg = self.config
+        summary["status"] = "completed" if self.metrics else "no_data"
+        summary["mode"] = cfg.training_mode
+        summary["run"] = {"started_at_unix": self._start_time, "ended_at_unix": time.time(), "output_dir": cfg.output_dir,
+                          "resume_from": cfg.resume_from, "last_checkpoint_path": self._last_checkpoint_path}
+        names = ["config_snapshot.json", "run_summary.json", "loss_curve.csv", "loss_curve.png", "eval_before.json",
+                 "eval_after.json", "fixed_prompt_comparison.json", "memory_report.json", "tensorboard"]
+        summary["artifacts"] = {n.split(".")[0]: self.artifacts.path(n) for n in names}
+        summary["artifacts"]["metrics_jsonl"] = self.artifacts.path(f"metrics_rank{self.artifacts.rank}.jsonl")
+        try:
+            summary["performance"].update(self._performance_block())
+        except Exception as e:  # noqa: BLE001 - the summary is written regardless
+            logger.warning("performance block not computed: %s", e)
+        self.artifacts.write_json("run_summary.json", summary)
         if self.artifacts.is_main:
             with open(self.artifacts.path("loss_curve.csv"), "w", newline="") as f:
                 w = csv.writer(f)

@@ -160,6 +160,14 @@ def test_eval_before_after_artifacts_and_fixed_prompt_comparison():
         assert [r["prompt"] for r in cmp_["samples"]] == [x["prompt"] for x in before["samples"]]
         assert set(cmp_["samples"][0]) >= {"before_generated", "after_generated", "before_token_f1", "after_exact_match"}
         assert s["eval"]["before"]["num_samples"] == 2 and "after" in s["eval"]
+        rs = json.load(open(os.path.join(out, "run_summary.json")))
+        assert rs["status"] == "completed" and rs["mode"] == "sft" and rs["run"]["output_dir"] == out
+        assert rs["run"]["ended_at_unix"] >= rs["run"]["started_at_unix"] > 0
+        assert rs["artifacts"]["eval_before"].endswith("eval_before.json") and "metrics_jsonl" in rs["artifacts"]
+        perf = rs["performance"]
+        assert perf["world_size"] == 1 and perf["global_batch_size"] == cfg.batch_size and perf["avg_step_time_s"] > 0
+        assert perf["tokens_per_second"] > 0 and perf["model_arch"]["vocab_size"] == 8192
+        assert 0 < perf["mfu_percent"] < 100 and perf["primary_metric"] == "mfu" and perf["model_params"] > 0
         from b200fw.obs import read_scalars
         tags = read_scalars(os.path.join(out, "tensorboard"))
         assert "eval/before_loss" in tags and "eval/after_token_f1" in tags and "train/loss" in tags
