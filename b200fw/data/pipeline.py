@@ -70,6 +70,10 @@ def _load_records(dataset_name: str, dataset_config: Optional[str], split: str) 
             data = json.load(f)
             return data[split] if isinstance(data, dict) and split in data else data
     if os.path.isdir(dataset_name):
+        plain = os.path.join(dataset_name, "data.jsonl")        # written by prepare_data.py without `datasets`
+        if os.path.isfile(plain):
+            with open(plain) as f:
+                return [json.loads(l) for l in f if l.strip()]
         from datasets import load_from_disk
         ds = load_from_disk(dataset_name)
         ds = ds[split] if hasattr(ds, "keys") and split in ds else ds

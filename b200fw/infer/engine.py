@@ -80,6 +80,8 @@ class InferenceEngine:
             self.initialized = True
             return self
         mc = self.model.cfg
+        if self.device.type == "cuda" and cfg.block_size != 16:
+            raise ValueError(f"block_size={cfg.block_size}: the paged KV kernels are built for 16-token blocks")
         self.pool = BlockPool(cfg.num_blocks, cfg.block_size, mc.num_layers, mc.num_kv_heads, mc.head_dim,
                               p0.dtype, self.device, cfg.kv_cache_dtype)
         self.kv = KVCacheManager(self.pool, cfg.block_size)

@@ -21,7 +21,7 @@ from b200fw.orch import ColocateOrchestrator  # noqa: E402
 def parse_args(argv=None):
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("--config", type=str, default=None)
-    ap.add_argument("--model-path", type=str, default=None)
+    ap.add_argument("--model", "--model-path", dest="model_path", type=str, default=None, help="HF model directory")
     ap.add_argument("--model-preset", type=str, default=None, help="random-init architecture (e.g. qwen3-0.6b)")
     ap.add_argument("--tp-size", type=int, default=None)
     ap.add_argument("--dp-size", type=int, default=None)

@@ -25,10 +25,13 @@ from b200fw.train import TrainConfig, TrainEngine  # noqa: E402
 
 def parse_args(argv=None):
     ap = argparse.ArgumentParser(description=__doc__)
-    ap.add_argument("--model-path", default="")
+    ap.add_argument("--model", "--model-path", dest="model_path", default="", help="HF model directory")
     ap.add_argument("--model-preset", default=None)
-    ap.add_argument("--num-train-gpus", type=int, default=4)
-    ap.add_argument("--num-infer-gpus", type=int, default=4)
+    ap.add_argument("--num-train-gpus", "--train-tp", dest="num_train_gpus", type=int, default=4,
+                    help="ranks in the trainer group (data parallel + ZeRO; the reference's --train-tp sized its "
+                         "trainer actor the same way)")
+    ap.add_argument("--num-infer-gpus", "--infer-tp", dest="num_infer_gpus", type=int, default=4,
+                    help="ranks running rollout engines (one engine per rank)")
     ap.add_argument("--iterations", type=int, default=4)
     ap.add_argument("--batch-size", type=int, default=64)
     ap.add_argument("--num-samples", type=int, default=8)
@@ -36,15 +39,27 @@ def parse_args(argv=None):
     ap.add_argument("--max-tokens", type=int, default=512)
     ap.add_argument("--zero-stage", type=int, default=2)
     ap.add_argument("--lora-rank", type=int, default=0)
+    ap.add_argument("--lr", type=float, default=1e-5)
     ap.add_argument("--mode", choices=["pipeline", "sequential"], default="pipeline")
-    ap.add_argument("--transfer-backend", choices=["nccl", "peer_write"], default="nccl")
+    ap.add_argument("--no-overlap", action="store_true", help="same as --mode sequential")
+    ap.add_argument("--transfer-backend", "--weight-backend", dest="transfer_backend",
+                    choices=["nccl", "peer_write", "ray"], default="nccl",
+                    help="'ray' (object store) is not available in a torchrun world and falls back to nccl")
     ap.add_argument("--kv-cache-dtype", choices=["fp16", "fp8"], default="fp16")
     ap.add_argument("--backend", default=None)
+    ap.add_argument("--log-file", default=None)
     return ap.parse_args(argv)
 
 
 def main(argv=None):
     a = parse_args(argv)
+    if a.no_overlap:
+        a.mode = "sequential"
+    if a.transfer_backend == "ray":
+        a.transfer_backend = "nccl"
+    if a.log_file:
+        from b200fw.obs import setup_logger
+        setup_logger("b200fw", log_file=a.log_file)
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     cuda = torch.cuda.is_available()
@@ -56,7 +71,7 @@ def main(argv=None):
     dist.init_process_group(backend, rank=rank, world_size=world)
     mc = PRESETS[a.model_preset] if a.model_preset else read_hf_config(a.model_path)
     cfg = DisaggConfig(a.model_path, a.model_preset, a.num_train_gpus, a.num_infer_gpus, a.zero_stage, a.iterations,
-                       a.batch_size, a.num_samples, a.prompt_len, a.max_tokens, lora_rank=a.lora_rank, mode=a.mode,
+                       a.batch_size, a.num_samples, a.prompt_len, a.max_tokens, learning_rate=a.lr, lora_rank=a.lora_rank, mode=a.mode,
                        transfer_backend=a.transfer_backend, kv_cache_dtype=a.kv_cache_dtype)
 
     def make_trainer(group, n, r):
@@ -64,7 +79,7 @@ def main(argv=None):
         ctx.dp_group, ctx.dp_ranks = (group if n > 1 else None), list(range(n))
         ParallelContext._instance = ctx
         tc = TrainConfig(model_path=a.model_path, model_preset=a.model_preset, dp_size=n, lora_rank=a.lora_rank,
-                         zero_stage=a.zero_stage, gradient_accumulation_steps=1, grpo_beta=cfg.grpo_beta,
+                         zero_stage=a.zero_stage, gradient_accumulation_steps=1, grpo_beta=cfg.grpo_beta, learning_rate=a.lr,
                          max_seq_len=a.prompt_len + a.max_tokens, warmup_steps=0,
                          amp_dtype="bf16" if cuda else "fp32", use_amp=cuda)
         return TrainEngine(tc).initialize(ctx)

@@ -1,0 +1,103 @@
+"""Entry-point scripts: the reference's command-line flags are accepted, and the small flows run on CPU."""
+import importlib.util
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+# flags of the reference's scripts (scripts/*.py of the reference project) that a user may have in a launcher
+REFERENCE_FLAGS = {
+    "run_inference.py": ["--model", "-m", "--mode", "--prompt", "-p", "--input", "-i", "--output", "-o", "--max-tokens",
+                         "--temperature", "--top-p", "--batch-size", "--num-samples", "--interactive", "--config",
+                         "--num-blocks", "--block-size", "--enable-prefix-cache", "--enable-cuda-graph", "--enable-async",
+                         "--enable-partitioned-attn"],
+    "run_colocate.py": ["--config", "--model", "--tp-size", "--dp-size", "--iterations", "--batch-size", "--num-samples",
+                        "--training-mode", "--inference-backend", "--vllm-url", "--lr", "--lora-rank", "--max-tokens",
+                        "--resume-from", "--log-file"],
+    "run_disaggregated.py": ["--model", "--train-tp", "--infer-tp", "--iterations", "--batch-size", "--num-samples",
+                             "--weight-backend", "--no-overlap", "--lr", "--lora-rank", "--max-tokens", "--log-file"],
+    "benchmark_all.py": ["--model", "--iterations", "--batch-size", "--num-samples", "--quick", "--vllm-url", "--output",
+                         "--tp-size", "--train-tp", "--infer-tp"],
+    "prepare_data.py": ["--dataset", "--config", "--split", "--output", "--max-samples", "--required-field"],
+    "profile_memory.py": ["--config", "--output", "--device", "--skip-backward"],
+}
+
+
+def _load(name):
+    spec = importlib.util.spec_from_file_location(name[:-3], os.path.join(ROOT, "scripts", name))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+@pytest.mark.parametrize("script", sorted(REFERENCE_FLAGS))
+def test_reference_flags_are_accepted(script):
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "scripts", script), "--help"], capture_output=True, text=True,
+                       timeout=300)
+    assert r.returncode == 0, r.stderr[-500:]
+    words = set(r.stdout.replace(",", " ").replace("[", " ").replace("]", " ").split())
+    missing = [f for f in REFERENCE_FLAGS[script] if f not in words]
+    assert not missing, f"{script}: flags of the reference not accepted: {missing}"
+
+
+def test_run_inference_jsonl_in_jsonl_out(tmp_path, capsys):
+    src = tmp_path / "prompts.jsonl"
+    src.write_text('"hello there"\n{"prompt": "two plus two"}\n\n{"text": "third"}\n')
+    out = tmp_path / "out.jsonl"
+    mod = _load("run_inference.py")
+    assert mod.load_prompts_from_file(str(src)) == ["hello there", "two plus two", "third"]
+    mod.main(["--model-preset", "tiny128", "--mode", "kv_cache", "-i", str(src), "-p", "from the cli", "--num-samples", "2",
+              "--batch-size", "3", "--max-tokens", "4", "-o", str(out), "--enable-prefix-cache", "--num-blocks", "64"])
+    rows = [json.loads(l) for l in out.read_text().splitlines()]
+    assert len(rows) == 8 and [r["sample_idx"] for r in rows[:2]] == [0, 1]
+    assert rows[0]["prompt"] == "from the cli" and rows[-1]["prompt"] == "third"
+    assert all(0 < r["num_tokens"] <= 4 and set(r) == {"prompt", "sample_idx", "output", "num_tokens", "time_s",
+                                                       "tokens_per_s"} for r in rows)
+    summary = json.loads(capsys.readouterr().out)
+    assert summary["prompts"] == 4 and summary["samples"] == 8 and summary["mode"] == "kv_cache"
+
+
+def test_run_inference_interactive_reads_until_quit():
+    import io
+    mod = _load("run_inference.py")
+    a = mod.parse_args(["--model-preset", "tiny128", "--mode", "mock", "--interactive", "--max-tokens", "3"])
+    cfg = mod.create_inference_config(a, {})
+    eng = mod.InferenceEngine(cfg).initialize()
+    from b200fw.data import SimpleTokenizer
+    lines = []
+    mod.run_interactive(eng, SimpleTokenizer(), a, 3, cfg.vocab_size, stdin=io.StringIO("first\n\nsecond\nquit\nnever\n"),
+                        out=lines.append)
+    assert len(lines) == 3 and lines[1].startswith("[") and "tok/s" in lines[2]
+
+
+def test_prepare_data_file_directory_and_required_fields(tmp_path):
+    mod = _load("prepare_data.py")
+    f = tmp_path / "syn.jsonl"
+    assert mod.main(["--dataset", "synthetic", "--num-synthetic", "30", "--max-samples", "12", "--output", str(f),
+                     "--required-field", "question", "--required-field", "answer"]) == 0
+    rows = [json.loads(l) for l in f.read_text().splitlines()]
+    assert len(rows) == 12 and "####" in rows[0]["answer"]
+    man = json.load(open(str(f) + ".manifest.json"))
+    assert man["rows"] == 12 and man["required_fields"] == ["question", "answer"] and man["split"] == "train"
+    with pytest.raises(ValueError, match="missing required field"):
+        mod.main(["--dataset", str(f), "--output", str(tmp_path / "x.jsonl"), "--required-field", "nope"])
+    d = tmp_path / "as_dir"
+    assert mod.main(["--dataset", str(f), "--output", str(d), "--max-samples", "5"]) == 0
+    assert json.load(open(d / "train_infer_manifest.json"))["rows"] == 5
+    from b200fw.data.pipeline import GSM8KDataPipeline
+    assert len(GSM8KDataPipeline(None, str(d))) == 5          # the pipeline reads what the script wrote
+    from b200fw.reward import GSM8KRewardFunction
+    assert GSM8KRewardFunction().score(rows[0]["answer"], rows[0]["answer"]) == 1.0
+
+
+def test_profile_memory_from_yaml(tmp_path):
+    mod = _load("profile_memory.py")
+    out = tmp_path / "rep" / "memory_report.json"
+    rep = mod.main(["--config", os.path.join(ROOT, "configs", "training", "sft.yaml"), "--model-preset", "tiny128",
+                    "--batch-size", "2", "--seq-len", "64", "--device", "cpu", "--skip-backward", "--output", str(out)])
+    d = json.load(open(out))
+    assert set(d) >= {"breakdown", "phase_peaks", "optimizer_bytes"} and "forward" in d["phase_peaks"] and rep is not None
