@@ -11,6 +11,7 @@ class ArtifactWriter:
     def __init__(self, output_dir: str, rank: int = 0, world_size: int = 1):
         self.output_dir, self.rank, self.world_size = output_dir, rank, world_size
         os.makedirs(output_dir, exist_ok=True)
+        self._started = set()        # per-rank JSONL stems already truncated by write_rank_jsonl in this run
 
     @property
     def is_main(self) -> bool:
@@ -46,3 +47,29 @@ class ArtifactWriter:
         with open(self.path(name), "w") as f:
             f.write(text)
         return self.path(name)
+
+    # ---- the reference's method names (src/utils/artifact_writer.py:39-86) ---------------------------------
+    def write_main_json(self, filename: str, data: Any):
+        """Rank 0 only: ``<output_dir>/<filename>``."""
+        return self.write_json(filename, data)
+
+    def write_main_text(self, filename: str, text: str):
+        return self.write_text(filename, text)
+
+    def write_rank_json(self, base_filename: str, data: Any):
+        """Every rank: ``metrics.json`` -> ``metrics_rank{r}.json``."""
+        return self.write_json(base_filename, data, all_ranks=True)
+
+    def write_rank_jsonl(self, base_filename: str, row: Dict[str, Any]):
+        """Every rank: ``metrics.jsonl`` -> one appended line in ``metrics_rank{r}.jsonl``.  The first write of
+        a run truncates the file, so that rows of an earlier run in the same directory do not mix in."""
+        stem = os.path.splitext(base_filename)[0]
+        if stem not in self._started:
+            self._started.add(stem)
+            open(self.rank_path(stem, "jsonl"), "w").close()
+        return self.append_jsonl(stem, row)
+
+    def close(self):
+        """Files are opened per write; nothing stays open.  Kept so that callers of the reference's API work."""
+        self._started.clear()
+

@@ -70,3 +70,28 @@ class EvalMetrics:
         n = max(1, len(self.f1))
         return {"count": len(self.f1), "exact_match": sum(self.exact_match) / n, "token_f1": sum(self.f1) / n,
                 "bleu4": sum(self.bleu4) / n}
+
+    # ---- the reference's method names (src/utils/eval_utils.py:144-178) -----------------------------------------
+    def compute_single(self, prediction: str, reference: str) -> Dict[str, float]:
+        self.add(prediction, reference)
+        return {"token_f1": self.f1[-1], "bleu4": self.bleu4[-1], "exact_match": self.exact_match[-1]}
+
+    def compute_batch(self, predictions: List[str], references: List[str]) -> Dict[str, float]:
+        """Scores every pair (they are kept for ``get_summary``) and returns this batch's averages."""
+        assert len(predictions) == len(references) and predictions
+        rows = [self.compute_single(p, r) for p, r in zip(predictions, references)]
+        return {k: sum(r[k] for r in rows) / len(rows) for k in rows[0]}
+
+    def get_summary(self) -> Dict[str, float]:
+        """``<metric>_mean / _max / _min`` over everything scored so far (``{}`` when nothing was)."""
+        out: Dict[str, float] = {}
+        for k, v in (("token_f1", self.f1), ("bleu4", self.bleu4), ("exact_match", self.exact_match)):
+            if v:
+                out[f"{k}_mean"], out[f"{k}_max"], out[f"{k}_min"] = sum(v) / len(v), max(v), min(v)
+        return out
+
+    def reset(self):
+        self.exact_match.clear()
+        self.f1.clear()
+        self.bleu4.clear()
+

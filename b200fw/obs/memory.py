@@ -26,6 +26,24 @@ class MemorySnapshot:
     peak_reserved_gb: float
     free_gb: float = 0.0
     total_gb: float = 0.0
+    device_id: int = -1
+
+    # the reference's field names (src/utils/memory_profiler.py:16-24), in MB
+    @property
+    def stage(self) -> str:
+        return self.tag
+
+    @property
+    def allocated_mb(self) -> float:
+        return self.allocated_gb * 1024
+
+    @property
+    def reserved_mb(self) -> float:
+        return self.reserved_gb * 1024
+
+    @property
+    def peak_mb(self) -> float:
+        return self.peak_allocated_gb * 1024
 
 
 @dataclass
@@ -55,6 +73,36 @@ class MemoryBreakdown:
         b = cls(params / GB, grads / GB, opt / GB, acts / GB, logits / GB)
         b.total_gb = b.params_gb + b.grads_gb + b.optimizer_gb + b.activations_gb + b.logits_gb
         return b
+
+
+    @staticmethod
+    def analyze(model: Optional[torch.nn.Module] = None, optimizer=None) -> Dict[str, float]:
+        """Measured bytes held right now by a model's parameters, their gradients and an optimizer's state, in
+        MB (the reference's ``MemoryBreakdown(model, optimizer).analyze()``: src/utils/memory_profiler.py:196-251)."""
+        mb = 1024 ** 2
+        out = {"model_params_mb": 0.0, "gradients_mb": 0.0, "optimizer_states_mb": 0.0}
+        if model is not None:
+            for p in model.parameters():
+                out["model_params_mb"] += p.numel() * p.element_size() / mb
+                g = getattr(p, "main_grad", None)
+                g = p.grad if g is None else g
+                if g is not None:
+                    out["gradients_mb"] += g.numel() * g.element_size() / mb
+        if optimizer is not None:
+            if hasattr(optimizer, "memory_bytes"):
+                b = optimizer.memory_bytes()
+                out["optimizer_states_mb"] = (sum(v for k, v in b.items() if k != "params") if isinstance(b, dict) else b) / mb
+            else:
+                for st in getattr(optimizer, "state", {}).values():
+                    out["optimizer_states_mb"] += sum(v.numel() * v.element_size() for v in st.values()
+                                                      if torch.is_tensor(v)) / mb
+        out["total_mb"] = sum(out.values())
+        return out
+
+    def report(self) -> str:
+        rows = [("params", self.params_gb), ("gradients", self.grads_gb), ("optimizer", self.optimizer_gb),
+                ("activations", self.activations_gb), ("logits", self.logits_gb), ("total", self.total_gb)]
+        return "\n".join(["== memory estimate (GB per rank) =="] + [f"  {k:12s} {v:8.2f}" for k, v in rows])
 
 
 class MemoryProfiler:
@@ -109,6 +157,32 @@ class MemoryProfiler:
     def timeline(self) -> List[Dict[str, Any]]:
         return [asdict(s) for s in self.snapshots]
 
+    # ---- the reference's method names (src/utils/memory_profiler.py:90-160) ------------------------------------
+    def get_timeline(self) -> List[MemorySnapshot]:
+        return list(self.snapshots)
+
+    @property
+    def peak_memory_mb(self) -> float:
+        return max((s.peak_mb for s in self.snapshots), default=0.0)
+
+    def delta(self, stage_a: str, stage_b: str) -> float:
+        """Allocated-memory change in MB from the first snapshot tagged ``stage_a`` to the first tagged
+        ``stage_b`` (0 when either is missing)."""
+        a = next((s for s in self.snapshots if s.tag == stage_a), None)
+        b = next((s for s in self.snapshots if s.tag == stage_b), None)
+        return 0.0 if a is None or b is None else b.allocated_mb - a.allocated_mb
+
+    def report(self) -> str:
+        lines = ["== memory timeline ==", f"{'stage':24s} {'allocated MB':>14s} {'reserved MB':>14s} {'peak MB':>12s}"]
+        lines += [f"{s.tag:24s} {s.allocated_mb:14.1f} {s.reserved_mb:14.1f} {s.peak_mb:12.1f}" for s in self.snapshots]
+        return "\n".join(lines)
+
+    def reset(self):
+        self.snapshots.clear()
+        self.layer_peaks.clear()
+        self.phase_peaks.clear()
+        self.reset_peak()
+
 
 @dataclass
 class MemoryReport:
@@ -124,6 +198,46 @@ class MemoryReport:
                       optimizer_bytes: Optional[Dict[str, int]] = None) -> "MemoryReport":
         return cls(breakdown, prof.timeline(), dict(prof.phase_peaks), dict(prof.layer_peaks),
                    dict(optimizer_bytes or {}))
+
+    # ---- the reference's entry points (src/utils/memory_profiler.py:454-546): there ``MemoryReport(model,
+    # optimizer, config)`` is an object with these two methods; here they are constructors of the report ---------
+    @classmethod
+    def profile_step(cls, input_ids, labels, train_step_fn, model: Optional[torch.nn.Module] = None, optimizer=None,
+                     breakdown: Optional[MemoryBreakdown] = None) -> "MemoryReport":
+        """Run ``train_step_fn(input_ids, labels)`` once with snapshots around it, the step's peak and (with a
+        ``model``) per-layer peaks from forward hooks."""
+        prof = MemoryProfiler()
+        if model is not None:
+            prof.attach_layer_hooks(model)
+        prof.snapshot("before_step")
+        prof.reset_peak()
+        try:
+            train_step_fn(input_ids, labels)
+        finally:
+            prof.detach_hooks()
+        prof.mark_phase("step")
+        prof.snapshot("after_step")
+        rep = cls.from_profiler(prof, breakdown, cls._optimizer_bytes(optimizer))
+        if model is not None:
+            rep.notes.append("measured MB: " + json.dumps(MemoryBreakdown.analyze(model, optimizer)))
+        return rep
+
+    @classmethod
+    def generate_report_without_step(cls, model: Optional[torch.nn.Module] = None, optimizer=None,
+                                     breakdown: Optional[MemoryBreakdown] = None) -> "MemoryReport":
+        """Static part only: what the model and optimizer hold now, no training step."""
+        prof = MemoryProfiler()
+        prof.snapshot("static")
+        rep = cls.from_profiler(prof, breakdown, cls._optimizer_bytes(optimizer))
+        rep.notes.append("measured MB: " + json.dumps(MemoryBreakdown.analyze(model, optimizer)))
+        return rep
+
+    @staticmethod
+    def _optimizer_bytes(optimizer) -> Dict[str, int]:
+        if optimizer is None or not hasattr(optimizer, "memory_bytes"):
+            return {}
+        b = optimizer.memory_bytes()
+        return dict(b) if isinstance(b, dict) else {"total": int(b)}
 
     def to_dict(self) -> Dict[str, Any]:
         d = asdict(self)
@@ -185,3 +299,36 @@ class MemoryManager:
         self._reserve = None
         self.defragment()
         return had
+
+    # ---- the reference's method names (src/utils/memory_manager.py:25-100) ---------------------------------------
+    def get_stats(self) -> Dict[str, float]:
+        """Allocated / reserved / peak / total GB of the device, without side effects (``{}`` without CUDA)."""
+        if not self.enabled:
+            return {}
+        return {"allocated_gb": torch.cuda.memory_allocated(self.device) / 1e9,
+                "reserved_gb": torch.cuda.memory_reserved(self.device) / 1e9,
+                "peak_gb": torch.cuda.max_memory_allocated(self.device) / 1e9,
+                "total_gb": torch.cuda.get_device_properties(self.device or 0).total_memory / 1e9}
+
+    def check_memory_pressure(self) -> Dict[str, float]:
+        """Current figures plus ``utilization`` (allocated / total) and ``fragmentation_gb``; records a warn /
+        critical event when a threshold is crossed."""
+        if not self.enabled:
+            return {"allocated_gb": 0, "reserved_gb": 0, "total_gb": 0, "utilization": 0}
+        st = self.get_stats()
+        st["utilization"] = st["allocated_gb"] / st["total_gb"] if st["total_gb"] else 0.0
+        st["fragmentation_gb"] = st["reserved_gb"] - st["allocated_gb"]
+        if st["utilization"] >= self.critical:
+            self.events.append(f"critical {st['utilization']:.3f}")
+        elif st["utilization"] >= self.warn:
+            self.events.append(f"warn {st['utilization']:.3f}")
+        return st
+
+    def reserve_buffer(self, size_mb: int = 512):
+        """Hold back ``size_mb`` of device memory to hand out when an out-of-memory error is being handled."""
+        if self.enabled and self._reserve is None:
+            self._reserve = torch.empty(size_mb * 1024 * 1024, dtype=torch.uint8, device=self.device or "cuda")
+
+    def release_buffer(self):
+        self.release_reserve()
+

@@ -14,6 +14,7 @@ class MetricsCollector:
         self.steps: Dict[str, List[int]] = defaultdict(list)
         self.timers: Dict[str, List[float]] = defaultdict(list)
         self._open: Dict[str, float] = {}
+        self._start_time = time.time()
 
     def record(self, name: str, value: float, step: Optional[int] = None):
         self.series[name].append(float(value))
@@ -58,6 +59,45 @@ class MetricsCollector:
                               "last": v[-1], "total": sum(v)}
         return out
 
+    # ---- the reference's method names (src/utils/metrics.py:103-203) ------------------------------------------
+    def record_step(self, comm_time_ms: Optional[float] = None, grad_norm: Optional[float] = None,
+                    peak_memory_gb: Optional[float] = None, learning_rate: Optional[float] = None):
+        """Record whichever per-step figures are given under their usual names."""
+        for k, v in (("comm_time_ms", comm_time_ms), ("grad_norm", grad_norm), ("peak_memory_gb", peak_memory_gb),
+                     ("learning_rate", learning_rate)):
+            if v is not None:
+                self.record(k, v)
+
+    def get_summary(self) -> Dict:
+        """``{"total_elapsed_s", "timers": {name: count/total_s/mean_s/min_s/max_s}, "metrics": {key:
+        count/mean/min/max/last}, "throughput"}`` (``throughput`` when an ``iteration`` timer was used)."""
+        total = self.elapsed_time
+        out: Dict = {"total_elapsed_s": total, "timers": {}, "metrics": {}}
+        for k, v in self.timers.items():
+            if v:
+                out["timers"][k] = {"count": len(v), "total_s": sum(v), "mean_s": sum(v) / len(v), "min_s": min(v),
+                                    "max_s": max(v)}
+        for k, v in self.series.items():
+            if v:
+                out["metrics"][k] = {"count": len(v), "mean": sum(v) / len(v), "min": min(v), "max": max(v), "last": v[-1]}
+        n = len(self.timers.get("iteration", []))
+        if n and total > 0:
+            out["throughput"] = {"iterations_total": n, "iterations_per_hour": n / total * 3600}
+        return out
+
+    def to_tensorboard(self, writer, step: int):
+        """Latest value of every series (``metrics/<key>``) and timer (``timers/<name>_duration_s``) at ``step``."""
+        for k, v in self.series.items():
+            if v:
+                writer.add_scalar(f"metrics/{k}", v[-1], step)
+        for k, v in self.timers.items():
+            if v:
+                writer.add_scalar(f"timers/{k}_duration_s", v[-1], step)
+
+    @property
+    def elapsed_time(self) -> float:
+        return time.time() - self._start_time
+
     def export_tensorboard(self, writer, prefix: str = ""):
         for k, v in self.series.items():
             for step, val in zip(self.steps[k], v):
@@ -68,3 +108,4 @@ class MetricsCollector:
         self.steps.clear()
         self.timers.clear()
         self._open.clear()
+        self._start_time = time.time()

@@ -23,11 +23,15 @@ class TimelineEvent:
         return self.end_ms - self.start_ms
 
 
+ScheduleEvent = TimelineEvent      # the reference's name for an event record
+
+
 class ScheduleVisualizer:
     SYMBOLS = {"forward": "F", "backward": "B", "comm": "c", "optimizer": "O", "rollout": "R", "sync": "s", "idle": "."}
 
     def __init__(self):
         self.events: List[TimelineEvent] = []
+        self._open: Dict = {}
         self._t0 = time.perf_counter()
 
     def now_ms(self) -> float:
@@ -110,3 +114,50 @@ class ScheduleVisualizer:
 
     def to_rows(self) -> List[Dict]:
         return [asdict(e) for e in self.events]
+
+    # ---- the reference's method names (src/profiling/schedule_visualizer.py:103-467): events are named after the
+    # orchestrator stage ("training", "inference", "sync", ...) and live on a device lane ("GPU:0") ----------------
+    _STAGE_CATEGORY = {"training": "backward", "inference": "rollout", "inferring": "rollout", "sync": "sync",
+                       "syncing": "sync", "sleep": "idle", "wake": "idle", "idle": "idle", "forward": "forward",
+                       "backward": "backward", "comm": "comm", "optimizer": "optimizer", "rewarding": "optimizer"}
+
+    def begin_event(self, name: str, device: str = "GPU:0", **metadata):
+        self._open[(name, device)] = (self.now_ms(), metadata or None)
+
+    def end_event(self, name: str, device: str = "GPU:0"):
+        """Close the matching ``begin_event`` (ignored when there is none)."""
+        start = self._open.pop((name, device), None)
+        if start is not None:
+            self.add_event(name, self._STAGE_CATEGORY.get(name, name), device, start[0], self.now_ms(), start[1])
+
+    def render_ascii(self, width: int = 80) -> str:
+        return self.ascii_gantt(width)
+
+    def render_json(self) -> str:
+        """Chrome-trace JSON text (load in chrome://tracing or Perfetto)."""
+        return json.dumps(self.chrome_trace())
+
+    def get_utilization_stats(self) -> dict:
+        u = self.utilisation()
+        busy = sum(v["busy_ms"] for v in u.values())
+        span = max((v["span_ms"] for v in u.values()), default=0.0)
+        by_name: Dict[str, float] = {}
+        for e in self.events:
+            by_name[e.name] = by_name.get(e.name, 0.0) + e.duration_ms
+        return {"total_time_ms": span, "busy_time_ms": busy, "devices": u,
+                "utilization": busy / (span * len(u)) if span > 0 and u else 0.0,
+                "stage_time_ms": by_name, "stage_ratio": {k: v / busy for k, v in by_name.items()} if busy > 0 else {}}
+
+    def report(self) -> str:
+        st = self.get_utilization_stats()
+        lines = ["== schedule ==", self.ascii_gantt(80),
+                 f"span {st['total_time_ms']:.2f} ms, mean utilisation {100 * st['utilization']:.1f} %"]
+        lines += [f"  {k:16s} {v:10.2f} ms  {100 * st['stage_ratio'].get(k, 0.0):5.1f} %"
+                  for k, v in sorted(st["stage_time_ms"].items(), key=lambda kv: -kv[1])]
+        return "\n".join(lines)
+
+    def reset(self):
+        self.events.clear()
+        self._open.clear()
+        self._t0 = time.perf_counter()
+
