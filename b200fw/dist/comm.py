@@ -207,6 +207,10 @@ class AsyncHandle:
             return self.event.query()
         return self.work.is_completed()
 
+    def is_done(self) -> bool:
+        """Non-blocking completion query (the reference's name: src/distributed/comm.py:355-359)."""
+        return self.is_completed()
+
     def wait(self, timeout_sec: float = 300.0, poll_s: float = 0.01):
         if self.done:
             return
@@ -230,8 +234,20 @@ class AsyncHandle:
 class AsyncAllReduce:
     """All-reduce issued on the communication stream; the caller overlaps compute and then waits."""
 
-    def __init__(self, stream_manager: Optional[StreamManager] = None):
-        self.sm = stream_manager
+    def __init__(self, stream_manager: Optional[StreamManager] = None, group=None, timeout_sec: float = 300.0):
+        # the reference's argument order is (group, stream_manager, timeout_sec): accept either
+        if isinstance(group, StreamManager) or (stream_manager is not None and not isinstance(stream_manager, StreamManager)):
+            stream_manager, group = (group if isinstance(group, StreamManager) else None), stream_manager
+        self.sm, self.group, self.timeout_sec = stream_manager, group, timeout_sec
+
+    @property
+    def stream_manager(self):
+        return self.sm
+
+    def start(self, tensor: torch.Tensor) -> "AsyncHandle":
+        """All-reduce ``tensor`` in place over the group given at construction; ``handle.wait()`` before use
+        (src/distributed/comm.py:260-300)."""
+        return self.launch(tensor, self.group)
 
     def launch(self, t: torch.Tensor, group=None) -> AsyncHandle:
         if group is None or _size(group) == 1:
@@ -245,6 +261,13 @@ class AsyncAllReduce:
             return AsyncHandle(event=ev, stream_manager=self.sm)
         work = dist.all_reduce(t, group=group, async_op=True)
         return AsyncHandle(work=work)
+
+
+def all_reduce_async(tensor: torch.Tensor, group, stream_manager: Optional[StreamManager] = None,
+                     timeout_sec: float = 300.0) -> AsyncHandle:
+    """``handle = all_reduce_async(t, group, sm)``; compute that does not need ``t``; ``handle.wait()``
+    (src/distributed/comm.py:362-385)."""
+    return AsyncAllReduce(stream_manager, group, timeout_sec).start(tensor)
 
 
 # ---- pipeline p2p -------------------------------------------------------------------------------

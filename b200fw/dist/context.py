@@ -104,6 +104,20 @@ class ParallelContext:
     def reset(cls):
         cls._instance = None
 
+    # ---- the reference's property names (src/distributed/parallel_context.py:239-286) -----------------------
+    @property
+    def rank(self) -> int:
+        return self.global_rank
+
+    @property
+    def prev_rank(self) -> Optional[int]:
+        """Global rank of the previous pipeline stage (``rank - tp_size``); ``None`` on the first stage."""
+        return self.pp_prev_rank
+
+    @property
+    def next_rank(self) -> Optional[int]:
+        return self.pp_next_rank
+
     def on_destroy(self, fn):
         """Run ``fn()`` before the process groups are torn down (``destroy``).  CUDA graphs that captured
         collectives must be released first: a communicator waits for every graph that references it."""

@@ -63,3 +63,28 @@ class StreamManager:
 
     def get_stats(self) -> Dict[str, int]:
         return dict(self.stats)
+
+    # ---- the reference's method names (src/distributed/stream_manager.py:60-171) -----------------------------
+    def compute_scope(self):
+        return self._ctx(self.compute_stream)
+
+    def comm_scope(self):
+        return self.comm_context()
+
+    def transfer_scope(self):
+        return self.transfer_context()
+
+    def sync_all(self):
+        self.synchronize_all()
+
+    def get_stream_stats(self) -> Dict[str, int]:
+        return self.get_stats()
+
+    def reset_stats(self):
+        for k in self.stats:
+            self.stats[k] = 0
+
+    @property
+    def _enabled(self) -> bool:
+        return self.enabled
+

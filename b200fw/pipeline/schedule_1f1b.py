@@ -23,6 +23,7 @@ class PipelineScheduler:
         self.model, self.pp, self.num_micro = model, pp_context, num_micro_batches
         self._act_shape: Optional[Tuple[int, ...]] = None
         self.timeline = None  # optional ScheduleVisualizer
+        self._fifo: deque = deque()   # (input, output) pairs queued by forward_step for backward_step
 
     # ---- shape handshake ---------------------------------------------------------------------------
     def _handshake(self, mb_tokens: int, device, dtype):
@@ -59,6 +60,31 @@ class PipelineScheduler:
         else:
             out.backward(grad)
         return None if inp is None else inp.grad
+
+    # ---- single-micro-batch steps under the reference's names (src/distributed/pipeline_scheduler.py:105-172):
+    # forward_step queues (input, output); backward_step consumes the oldest pair -------------------------------
+    def forward_step(self, model, input_tensor: torch.Tensor, labels: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """First stage: ``input_tensor`` is ``[mbs, S]`` token ids; later stages: the received activations
+        ``[mbs*S(/tp), H]`` (``labels`` then gives the micro-batch shape on every stage; the last stage needs them
+        for the loss).  Returns what ``send_forward`` sends on (the scaled loss on the last stage)."""
+        assert labels is not None or self.pp.is_first_stage, "labels give the micro-batch shape on later stages"
+        shape_src = labels if labels is not None else input_tensor
+        saved, self.model = self.model, model
+        try:
+            if self.pp.is_first_stage:
+                inp, out, _ = self._forward(input_tensor, shape_src, None)
+            else:
+                inp, out, _ = self._forward(None, shape_src, input_tensor)
+        finally:
+            self.model = saved
+        self._fifo.append((inp, out))
+        return out
+
+    def backward_step(self, grad_output: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        """Backward of the oldest queued micro-batch; ``grad_output`` is ``None`` on the last stage.  Returns the
+        gradient to send upstream (``None`` on the first stage)."""
+        inp, out = self._fifo.popleft()
+        return self._backward(inp, out, None if self.pp.is_last_stage else grad_output)
 
     def _track(self, name, cat):
         import contextlib

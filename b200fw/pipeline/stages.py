@@ -53,3 +53,17 @@ class PipelineParallelContext:
 
     def local_to_global(self, i: int) -> int:
         return self.layer_start + i
+
+    # ---- the reference's property names (src/distributed/pipeline_parallel.py:96-143) -------------------------
+    @property
+    def pp_group(self):
+        return self.group
+
+    @property
+    def stage_layer_range(self) -> Tuple[int, int]:
+        """Layers ``[start, end)`` of this stage."""
+        return self.layer_start, self.layer_end
+
+    @property
+    def num_layers_this_stage(self) -> int:
+        return self.num_local_layers
