@@ -28,3 +28,41 @@ class InferenceContext:
                                                      # every sequence starts at position 0 -> use the chunk's own K/V)
     positions: Optional[torch.Tensor] = None         # int32 [total_q]
     last_token_rows: Optional[torch.Tensor] = None   # int64 [num_seqs]: row of each sequence's last query
+    # ---- fields of the reference's context that the kernels here do not need (src/inference/context.py:22-40):
+    max_seqlen_k: int = 0                            # filled by prepare_prefill for callers that want it
+    slot_mapping: Optional[torch.Tensor] = None      # per-token slot ids; the store kernel takes `store_segments`
+
+    def slots_from_segments(self, block_size: int = 16) -> Optional[torch.Tensor]:
+        """The reference's ``slot_mapping`` (int64 ``[tokens]``: ``block * block_size + offset``, ``-1`` = skip)
+        expanded from the segment list."""
+        if self.store_segments is None:
+            return None
+        seg = self.store_segments.cpu().tolist()
+        n = max((row + cnt for blk, row, cnt, _ in seg if blk >= 0), default=0)
+        out = torch.full((n,), -1, dtype=torch.int64)
+        for blk, row, cnt, first in seg:
+            if blk >= 0 and cnt > 0:
+                out[row:row + cnt] = blk * block_size + first + torch.arange(cnt)
+        return out
+
+
+# The reference passes the context through a module-level global that attention layers read
+# (src/inference/context.py:43-75); the engine here hands it to ``ModelRunner.forward`` explicitly, and these
+# three helpers exist for code written against the global style.
+_CONTEXT: Optional[InferenceContext] = None
+
+
+def set_context(is_prefill: bool, **fields) -> InferenceContext:
+    global _CONTEXT
+    _CONTEXT = InferenceContext(is_prefill, fields.pop("num_seqs", 0), **fields)
+    return _CONTEXT
+
+
+def get_context() -> Optional[InferenceContext]:
+    return _CONTEXT
+
+
+def reset_context():
+    global _CONTEXT
+    _CONTEXT = None
+

@@ -35,6 +35,11 @@ class CUDAGraphRunner:
     def has(self, size: int) -> bool:
         return size in self.graphs
 
+    def is_captured(self, batch_size: int) -> bool:
+        """True when the bucket that ``batch_size`` pads to has a graph (src/inference/cuda_graph.py:207-210)."""
+        padded = self.padded_size(batch_size)
+        return padded is not None and padded in self.graphs
+
     def capture(self, size: int, make_inputs: Callable[[int], Dict[str, torch.Tensor]],
                 fn: Callable[[Dict[str, torch.Tensor]], torch.Tensor]):
         """``make_inputs(size)`` returns the static input tensors; ``fn(inputs)`` is the step."""

@@ -25,9 +25,23 @@ class Block:
     ref_count: int = 0
     token_count: int = 0
     block_hash: Optional[int] = None
+    block_size: int = 16
 
     def reset(self):
         self.ref_count, self.token_count, self.block_hash = 0, 0, None
+
+    # the reference's field names (src/inference/kv_cache.py:48-60)
+    @property
+    def hash_value(self) -> Optional[int]:
+        return self.block_hash
+
+    @hash_value.setter
+    def hash_value(self, v: Optional[int]):
+        self.block_hash = v
+
+    @property
+    def is_full(self) -> bool:
+        return self.token_count >= self.block_size
 
 
 class BlockPool:
@@ -38,7 +52,7 @@ class BlockPool:
         self.num_layers, self.num_kv_heads, self.head_dim = num_layers, num_kv_heads, head_dim
         self.fp8 = kv_cache_dtype == "fp8"
         self.dtype, self.device = dtype, torch.device(device)
-        self.blocks = [Block(i) for i in range(num_blocks)]
+        self.blocks = [Block(i, block_size=block_size) for i in range(num_blocks)]
         self.free_list: Deque[int] = deque(range(num_blocks))
         self.kv: Optional[torch.Tensor] = None
         self.scales: Optional[torch.Tensor] = None
@@ -114,6 +128,14 @@ class BlockPool:
     @property
     def kv_cache_tensor(self) -> Optional[torch.Tensor]:
         return self.kv
+
+    def get_flattened_kv_cache(self) -> Optional[torch.Tensor]:
+        """``[2, layers, blocks * block_size, kv_heads, head_dim]`` view of the pool, indexable by slot
+        (``block_id * block_size + offset``); shares memory with the pool (src/inference/kv_cache.py:241-256)."""
+        if self.kv is None:
+            return None
+        two, L, nb, bs = self.kv.shape[:4]
+        return self.kv.view(two, L, nb * bs, *self.kv.shape[4:])
 
 
 class BlockTable:

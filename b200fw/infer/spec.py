@@ -10,6 +10,7 @@ chunk of ``K+1`` tokens per sequence, and rejected positions are trimmed from bo
 from __future__ import annotations
 
 from collections import deque
+from dataclasses import dataclass
 from typing import Deque, List, Optional, Tuple
 
 import torch
@@ -85,18 +86,99 @@ def verify_sampling_batch(draft_tokens: torch.Tensor, draft_probs: torch.Tensor,
     return n, torch.multinomial(dist, 1, generator=generator).squeeze(1)
 
 
+@dataclass
+class SpeculativeConfig:
+    """The reference's knobs (src/inference/speculative.py:29-41)."""
+    enabled: bool = False
+    draft_model_path: str = ""
+    num_speculative_tokens: int = 5
+    temperature: float = 0.0                    # draft sampling temperature (0 = greedy)
+    use_batch_draft: bool = True
+    use_sampling_verification: bool = False
+    verification_temperature: float = 1.0
+    verification_top_p: float = 0.9
+    min_acceptance_prob: float = 0.1
+
+
 class SpeculativeDecoder:
     """Drives draft + target runners for a batch of sequences that already finished prefill in both
     caches.  ``target`` / ``draft`` are :class:`ModelRunner` objects with their own block managers."""
 
-    def __init__(self, target, draft, num_tokens: int = 4, window: int = 100):
+    def __init__(self, target, draft, num_tokens: int = 4, window: int = 100,
+                 config: Optional[SpeculativeConfig] = None):
+        self.config = config or SpeculativeConfig(enabled=True, num_speculative_tokens=num_tokens)
+        if config is not None:
+            num_tokens = config.num_speculative_tokens
         self.target, self.draft, self.K = target, draft, num_tokens
         self.tracker = AcceptanceTracker(window)
         self.steps = 0
+        self.total_proposed = 0
+        self.total_accepted = 0
+        self._last_sync_count = 0
 
     @property
     def acceptance_rate(self) -> float:
         return self.tracker.rate
+
+    # ---- the reference's stateless API (src/inference/speculative.py:71-533): one sequence, tensors in and out,
+    # no paged caches involved.  The engine uses :meth:`step` instead. --------------------------------------------
+    @property
+    def is_loaded(self) -> bool:
+        return self.draft is not None
+
+    def load_draft_model(self) -> bool:
+        """The draft runner is handed to the constructor already built (the engine builds it from
+        ``speculative_draft_model_path`` or as a shallow random-init model); reports whether there is one."""
+        return self.is_loaded
+
+    def _draft_module(self):
+        return getattr(self.draft, "model", self.draft)
+
+    @torch.no_grad()
+    def speculate(self, input_ids: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+        """``input_ids [1, S]`` -> ``(draft_tokens [K], draft_logits [K, V])`` by K full re-forwards of the draft."""
+        assert self.is_loaded, "Draft model not loaded"
+        ids = input_ids
+        toks, logs = [], []
+        t = self.config.temperature
+        for _ in range(self.K):
+            logits = self._draft_module()(ids)[:, -1].float()
+            nxt = logits.argmax(-1) if t <= 0 else torch.multinomial(torch.softmax(logits / t, -1), 1).squeeze(-1)
+            toks.append(nxt)
+            logs.append(logits[0])
+            ids = torch.cat([ids, nxt[:, None]], 1)
+        return torch.cat(toks), torch.stack(logs)
+
+    def verify(self, input_ids: torch.Tensor, draft_tokens: torch.Tensor, target_logits: torch.Tensor,
+               draft_logits: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, int]:
+        """``target_logits [1, K+1, V]`` over (last token, draft tokens) -> ``(accepted tokens followed by the
+        target's own next token, number of draft tokens accepted)``.  Greedy prefix match, or the sampling-aware
+        rule when ``config.use_sampling_verification`` and ``draft_logits`` are given."""
+        tl = target_logits[0] if target_logits.dim() == 3 else target_logits
+        if self.config.use_sampling_verification and draft_logits is not None:
+            temp = self.config.verification_temperature
+            dp = torch.softmax(draft_logits.float() / max(temp, 1e-6), -1)
+            n, nxt = verify_sampling(draft_tokens, dp, tl, temp)
+        else:
+            n, nxt = verify_greedy(draft_tokens, tl)
+        self._account(n, draft_tokens.numel())
+        return torch.cat([draft_tokens[:n], torch.tensor([nxt], dtype=draft_tokens.dtype, device=draft_tokens.device)]), n
+
+    def sync_kv_cache(self, accepted_tokens: torch.Tensor, target_kv_cache=None):
+        """Marks how many tokens the caller has to add to the target cache.  With the paged runners nothing is
+        left to do: :meth:`step` trims both caches to the accepted history itself."""
+        self._last_sync_count = int(accepted_tokens.numel())
+
+    def _account(self, accepted: int, proposed: int):
+        self.tracker.record(accepted, proposed)
+        self.total_accepted += accepted
+        self.total_proposed += proposed
+
+    def get_stats(self) -> dict:
+        return {"enabled": self.config.enabled, "loaded": self.is_loaded, "acceptance_rate": self.acceptance_rate,
+                "total_proposed": self.total_proposed, "total_accepted": self.total_accepted,
+                "num_speculative_tokens": self.K, "history_window_size": len(self.tracker.events),
+                "rounds": self.steps}
 
     def _draft_propose(self, seq_ids: List, last_tokens: List[int], temperature: float,
                        generator=None) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
@@ -148,7 +230,7 @@ class SpeculativeDecoder:
         packed = torch.cat([n_dev[:, None], nxt_dev[:, None], d_tokens], 1).tolist()
         for i, s in enumerate(seq_ids):
             n, nxt = packed[i][0], packed[i][1]
-            self.tracker.record(n, K)
+            self._account(n, K)
             out.append(packed[i][2:2 + n] + [nxt])
             # both caches must end up holding history + last + the n accepted drafts; the returned
             # final token is the next round's `last` and is not stored yet
