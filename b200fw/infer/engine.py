@@ -95,6 +95,7 @@ class InferenceEngine:
                 self.scheduler.defer = self._defer_for_shared_prefix
         if cfg.enable_cuda_graph and self.device.type == "cuda":
             self.graph_runner = CUDAGraphRunner(cfg.max_num_sequences)
+            self.runner.graph_runner = self.graph_runner
         if cfg.speculative_enabled:
             self._init_speculative()
         self.initialized = True

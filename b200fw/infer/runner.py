@@ -8,6 +8,7 @@ prefill attention -> GEMMs with the residual in the epilogue.  It also builds th
 """
 from __future__ import annotations
 
+from dataclasses import dataclass
 from typing import List, Optional, Sequence, Tuple
 
 import torch
@@ -16,6 +17,30 @@ from .. import ops
 from ..model.qwen3 import ParallelTransformerModel
 from .context import InferenceContext
 from .kv_cache import BlockPool, KVCacheManager
+
+
+@dataclass
+class ModelRunnerConfig:
+    """Model-side slice of ``InferenceConfig`` (src/inference/model_runner.py:32-47); ``from_runner`` fills it
+    from a live runner."""
+    num_layers: int = 32
+    num_heads: int = 32
+    num_kv_heads: int = 8
+    head_dim: int = 128
+    hidden_size: int = 4096
+    vocab_size: int = 151936
+    block_size: int = 16
+    max_num_blocks: int = 1024
+    dtype: torch.dtype = torch.bfloat16
+    device: str = "cuda"
+    enable_cuda_graph: bool = True
+    max_cuda_graph_batch_size: int = 64
+
+    @classmethod
+    def from_runner(cls, r: "ModelRunner") -> "ModelRunnerConfig":
+        c = r.cfg
+        return cls(c.num_layers, c.num_heads, c.num_kv_heads, c.head_dim, c.hidden_size, c.vocab_size, r.block_size,
+                   r.pool.num_blocks, r.dtype, str(r.device), getattr(r, "graph_runner", None) is not None)
 
 
 class ModelRunner:
@@ -150,6 +175,69 @@ class ModelRunner:
             h = h.index_select(0, ctx.last_token_rows)
         h = ops.rmsnorm(h.contiguous(), m.norm.weight, cfg.rms_norm_eps)
         return m.logits_from_hidden(h)
+
+    # ---- the reference's entry points (src/inference/model_runner.py:82-160, 639-812) ----------------------------
+    def run(self, input_ids: torch.Tensor, ctx_or_positions=None, is_prefill: bool = True) -> torch.Tensor:
+        """``run(token_ids, ctx)``; or, in the reference's style, ``run(token_ids, positions, is_prefill)`` after
+        ``b200fw.infer.context.set_context(...)`` published the step's metadata."""
+        if isinstance(ctx_or_positions, InferenceContext):
+            return self.forward(input_ids.reshape(-1), ctx_or_positions)
+        from .context import get_context
+        ctx = get_context()
+        if ctx is None:
+            raise RuntimeError("no InferenceContext: pass one, or call set_context() first")
+        if ctx.positions is None and ctx_or_positions is not None:
+            ctx.positions = ctx_or_positions.to(torch.int32)
+        return self.forward(input_ids.reshape(-1), ctx)
+
+    def run_batch_decode(self, input_ids: torch.Tensor, positions: torch.Tensor, block_tables: torch.Tensor,
+                         context_lens: torch.Tensor) -> torch.Tensor:
+        """One decode token for every sequence from raw metadata tensors: ``input_ids [B]`` or ``[B,1]``,
+        ``positions [B]`` (index of the new token), ``block_tables [B, max_blocks]`` (``-1`` padded),
+        ``context_lens [B]`` (including the new token).  Returns ``[B, V]`` logits; the new K/V rows are written
+        to ``block_tables[b, positions[b] // block_size]``."""
+        B = input_ids.shape[0]
+        dev, bs = self.device, self.block_size
+        pos = positions.to(dev, torch.int64)
+        bt = block_tables.to(dev, torch.int32)
+        blk = bt.gather(1, (pos // bs)[:, None]).squeeze(1)
+        rows = torch.arange(B, device=dev, dtype=torch.int32)
+        seg = torch.stack([blk, rows, torch.ones_like(rows), (pos % bs).to(torch.int32)], 1).contiguous()
+        lens = context_lens.to(dev, torch.int32)
+        ctx = InferenceContext(is_prefill=False, num_seqs=B, block_tables=bt.contiguous(), context_lens=lens,
+                               max_context_len=int(lens.max()) if B else 0, store_segments=seg,
+                               positions=pos.to(torch.int32))
+        return self.forward(input_ids.reshape(-1).to(dev), ctx)
+
+    def bind_kv_cache(self, pool: BlockPool, manager: Optional[KVCacheManager] = None):
+        """Point the runner at another block pool (and its manager)."""
+        self.pool, self.block_size = pool, pool.block_size
+        if manager is not None:
+            self.mgr = manager
+
+    def bind_hf_model(self, model):
+        """Swap the model the runner drives.  It has to be this framework's ``ParallelTransformerModel`` (load a
+        Hugging Face checkpoint into one with ``load_from_hf_checkpoint``): the kernels address its fused
+        projection weights directly, a ``transformers`` module cannot be driven."""
+        if not isinstance(model, ParallelTransformerModel):
+            raise TypeError("ModelRunner drives a ParallelTransformerModel; load the HF checkpoint into one with "
+                            "b200fw.model.load_from_hf_checkpoint")
+        self.model, self.cfg = model, model.cfg
+        self.device, self.dtype = next(model.parameters()).device, next(model.parameters()).dtype
+
+    def capture_cuda_graphs(self, batch_sizes: Optional[List[int]] = None) -> List[int]:
+        """Decode graphs are captured lazily, per batch-size bucket, by the engine's ``CUDAGraphRunner`` the first
+        time a bucket is used; this returns the buckets that would be used for ``batch_sizes``."""
+        gr = getattr(self, "graph_runner", None)
+        if gr is None:
+            return []
+        sizes = batch_sizes or gr.sizes
+        return sorted({gr.padded_size(b) for b in sizes if gr.padded_size(b) is not None})
+
+    def invalidate_cuda_graphs(self):
+        gr = getattr(self, "graph_runner", None)
+        if gr is not None:
+            gr.invalidate()
 
     # ---- sampling ------------------------------------------------------------------------------------------
     def sample(self, logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor,
