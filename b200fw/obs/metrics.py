@@ -4,8 +4,21 @@ from __future__ import annotations
 
 import contextlib
 import time
+from dataclasses import dataclass
 from collections import defaultdict
 from typing import Dict, List, Optional
+
+
+@dataclass
+class TimerRecord:
+    """One finished timer interval (src/utils/metrics.py:15-27); ``MetricsCollector.timer_records`` lists them."""
+    name: str
+    start_time: float
+    end_time: float
+
+    @property
+    def duration(self) -> float:
+        return self.end_time - self.start_time
 
 
 class MetricsCollector:
@@ -14,6 +27,7 @@ class MetricsCollector:
         self.steps: Dict[str, List[int]] = defaultdict(list)
         self.timers: Dict[str, List[float]] = defaultdict(list)
         self._open: Dict[str, float] = {}
+        self.timer_records: List[TimerRecord] = []
         self._start_time = time.time()
 
     def record(self, name: str, value: float, step: Optional[int] = None):
@@ -27,8 +41,10 @@ class MetricsCollector:
         t0 = self._open.pop(name, None)
         if t0 is None:
             return 0.0
-        dt = time.perf_counter() - t0
+        now = time.perf_counter()
+        dt = now - t0
         self.timers[name].append(dt)
+        self.timer_records.append(TimerRecord(name, t0, now))
         return dt
 
     @contextlib.contextmanager
@@ -108,4 +124,5 @@ class MetricsCollector:
         self.steps.clear()
         self.timers.clear()
         self._open.clear()
+        self.timer_records.clear()
         self._start_time = time.time()

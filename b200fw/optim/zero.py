@@ -638,6 +638,19 @@ class ZeROOptimizer:
             src = b.param_shard() if self.stage >= 1 else b.param_buf
             self._shard_view(self.master, i).copy_(src.float())
 
+    @property
+    def state_memory_usage(self) -> int:
+        """Bytes of AdamW moments held by this rank (two fp32 tensors over its shard;
+        src/distributed/zero_optim.py:232-247)."""
+        return (self.exp_avg.numel() + self.exp_avg_sq.numel()) * 4
+
+    @property
+    def total_optimizer_state_savings(self) -> str:
+        total = sum(b.numel for b in self.buckets)
+        standard, mine = total * 2 * 4, self.state_memory_usage
+        return (f"Standard Adam: {standard / 1024 ** 2:.1f} MB | ZeRO-{self.stage} (rank {self.rank}): "
+                f"{mine / 1024 ** 2:.1f} MB | Savings: {(1 - mine / standard) * 100 if standard else 0.0:.1f}%")
+
     def memory_bytes(self) -> Dict[str, int]:
         es = torch.tensor([], dtype=self.dtype).element_size()
         return {

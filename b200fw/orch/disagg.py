@@ -53,6 +53,37 @@ class DisaggConfig:
     seed: int = 0
     output_dir: str = "outputs_disagg"
     backend: Optional[str] = None        # process-group backend (default by device)
+    # ---- accepted for configs written against the reference (src/orchestrator/disagg_orchestrator.py:39-70) ----
+    use_flash_attn: bool = True          # every attention_backend value runs the native flash kernel
+    attention_backend: str = "flash_attn"
+    inference_backend: str = "custom"    # rollout ranks run the native engine; a vLLM server is not driven from here
+    async_weight_update: bool = True
+    max_data_samples: int = 0
+
+    # the reference sizes its two groups by tensor-parallel degree and GPU lists
+    @property
+    def train_tp_size(self) -> int:
+        return self.num_train_gpus
+
+    @property
+    def infer_tp_size(self) -> int:
+        return self.num_infer_gpus
+
+    @property
+    def train_gpus(self) -> List[int]:
+        return list(range(self.num_train_gpus))
+
+    @property
+    def infer_gpus(self) -> List[int]:
+        return list(range(self.num_train_gpus, self.num_train_gpus + self.num_infer_gpus))
+
+    @property
+    def weight_sync_backend(self) -> str:
+        return self.transfer_backend
+
+    @property
+    def overlap_training_inference(self) -> bool:
+        return self.mode == "pipeline"
 
 
 @dataclass
@@ -66,6 +97,17 @@ class DisaggIterationMetrics:
     loss: float = 0.0
     avg_reward: float = 0.0
     weights_version: int = 0
+    accuracy: float = 0.0
+    train_metrics: Optional[object] = None       # TrainMetrics of the iteration's last optimizer step (trainer ranks)
+
+    # the reference's field names (src/orchestrator/disagg_orchestrator.py:73-85)
+    @property
+    def infer_time(self) -> float:
+        return self.rollout_time
+
+    @property
+    def weight_version(self) -> int:
+        return self.weights_version
 
 
 class DisaggOrchestrator:

@@ -52,8 +52,14 @@ class GSM8KRewardFunction:
         self.total = 0
         self.num_correct = 0
         self.num_formatted = 0
+        self.reward_sum = 0.0
 
     def score(self, response: str, ground_truth) -> float:
+        r = self._score(response, ground_truth)
+        self.reward_sum += r
+        return r
+
+    def _score(self, response: str, ground_truth) -> float:
         self.total += 1
         pred = extract_answer(response)
         gt = ground_truth if isinstance(ground_truth, (int, float)) else extract_answer(str(ground_truth))
@@ -74,9 +80,19 @@ class GSM8KRewardFunction:
     def accuracy(self) -> float:
         return self.num_correct / self.total if self.total else 0.0
 
+    @property
+    def format_accuracy(self) -> float:
+        """Share of scored responses that state their answer explicitly."""
+        return self.num_formatted / self.total if self.total else 0.0
+
+    @property
+    def average_reward(self) -> float:
+        return self.reward_sum / self.total if self.total else 0.0
+
     def get_stats(self) -> Dict[str, float]:
         return {"total": self.total, "accuracy": self.accuracy,
                 "format_rate": self.num_formatted / self.total if self.total else 0.0}
 
     def reset_stats(self):
         self.total = self.num_correct = self.num_formatted = 0
+        self.reward_sum = 0.0

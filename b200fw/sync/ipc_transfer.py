@@ -14,6 +14,7 @@ import base64
 import hashlib
 import pickle
 import time
+from dataclasses import dataclass
 from typing import Any, Callable, Dict, List, Optional
 
 import torch
@@ -81,6 +82,10 @@ class VLLMClient:
         except Exception:  # noqa: BLE001
             return False
 
+    async def health_check(self) -> bool:
+        """The reference's name for :meth:`health` (src/transfer/ipc_transfer.py:215-222)."""
+        return await self.health()
+
     async def reset_prefix_cache(self):
         return await self._request("POST", "/reset_prefix_cache")
 
@@ -115,6 +120,17 @@ def _gpu_uuid(device_index: int = 0) -> str:
         return f"cpu-{device_index}"
 
 
+@dataclass
+class IPCHandle:
+    """One exported tensor (src/transfer/ipc_transfer.py:68-75); ``build_ipc_handles`` produces the same records
+    as plain dicts with these keys."""
+    name: str
+    handle: object
+    shape: tuple
+    dtype: torch.dtype
+    device_id: int = 0
+
+
 class IPCWeightTransfer:
     def __init__(self, client: VLLMClient, chunk_size: int = 16, device_index: int = 0):
         self.client, self.chunk_size, self.device_index = client, chunk_size, device_index
@@ -143,6 +159,34 @@ class IPCWeightTransfer:
         blob = base64.b64encode(pickle.dumps([h["handle"] for h in chunk])).decode()
         return {"names": [h["name"] for h in chunk], "shapes": [list(h["shape"]) for h in chunk],
                 "dtypes": [h["dtype"] for h in chunk], "ipc_handles": {_gpu_uuid(self.device_index): blob}}
+
+    def push_weights_sync(self, state_dict: Dict[str, torch.Tensor], sleep_level: int = 0) -> bool:
+        """Blocking wrapper around :meth:`push_weights` (a worker thread when an event loop is already running);
+        ``sleep_level > 0`` puts the server to sleep first.  Returns whether the push went through."""
+        import concurrent.futures
+
+        def run():
+            return asyncio.run(self.push_weights(state_dict, sleep_first=sleep_level > 0))
+        try:
+            try:
+                asyncio.get_running_loop()
+            except RuntimeError:
+                run()
+            else:
+                with concurrent.futures.ThreadPoolExecutor(1) as pool:
+                    pool.submit(run).result()
+            return True
+        except Exception as e:  # noqa: BLE001 - reported as the return value, as the reference does
+            logger.error("push_weights failed: %s", e)
+            return False
+
+    def verify_consistency(self, local_dict: Dict[str, torch.Tensor], remote_checksum: Optional[str] = None) -> bool:
+        """md5 over the full tensors in name order against the receiver's checksum (``True`` when none is given)."""
+        return remote_checksum is None or self.checksum(local_dict) == remote_checksum
+
+    def release_refs(self):
+        """Drop the references that keep exported tensors alive (only after the receiver has imported them)."""
+        self._keepalive.clear()
 
     @staticmethod
     def checksum(state: Dict[str, torch.Tensor]) -> str:
@@ -208,3 +252,13 @@ class WeightUpdateManager:
             self.rollbacks += 1
             logger.warning("weight update rolled back: %s", e)
             return False
+
+    # the reference's property names (src/transfer/ipc_transfer.py:659-667)
+    @property
+    def current_version(self) -> int:
+        return self.version
+
+    @property
+    def rollback_count(self) -> int:
+        return self.rollbacks
+

@@ -39,6 +39,58 @@ class TransferStats:
     def avg_gbps(self) -> float:
         return self.total_bytes / self.total_time_s / 1e9 if self.total_time_s > 0 else 0.0
 
+    # ---- the reference's field names; its two transfer modules each have a TransferStats with these
+    # (src/transfer/ipc_transfer.py:77-102, src/transfer/nccl_transfer.py:57-73) ------------------------------
+    total_params: int = 0
+    chunks_sent: int = 0
+    build_handle_time: float = 0.0
+    serialization_time: float = 0.0
+    _start_time: float = field(default=0.0, repr=False)
+
+    def start(self):
+        self._start_time = time.perf_counter()
+
+    def finish(self):
+        """Close the interval opened by ``start`` into ``total_time``."""
+        if self._start_time:
+            self.total_time_s += time.perf_counter() - self._start_time
+            self._start_time = 0.0
+
+    @property
+    def total_time(self) -> float:
+        return self.total_time_s
+
+    @property
+    def transfer_time(self) -> float:
+        return self.total_time_s
+
+    @property
+    def broadcast_time(self) -> float:
+        return self.total_time_s
+
+    @property
+    def sync_count(self) -> int:
+        return self.transfers
+
+    @property
+    def errors(self) -> int:
+        return self.failures
+
+    @property
+    def bandwidth_gbps(self) -> float:
+        return self.avg_gbps
+
+
+@dataclass
+class WeightVersion:
+    """Version stamp of a published weight set (src/transfer/nccl_transfer.py:40-54)."""
+    version: int = 0
+    timestamp: float = field(default_factory=time.time)
+    checksum: str = ""
+
+    def increment(self, checksum: str = "") -> "WeightVersion":
+        return WeightVersion(self.version + 1, time.time(), checksum)
+
 
 def sample_checksum(t: torch.Tensor, n: int = 64) -> str:
     """md5 of the first ``n`` elements (cheap integrity probe, as the reference does)."""
@@ -46,7 +98,23 @@ def sample_checksum(t: torch.Tensor, n: int = 64) -> str:
     return hashlib.md5(flat.numpy().tobytes()).hexdigest()
 
 
-class NCCLWeightTransfer:
+class _VersionedMixin:
+    """``current_version`` / ``has_new_version`` as in the reference's transfer classes
+    (src/transfer/nccl_transfer.py:204-211, 332-351, 480-486): the integer ``version`` wrapped in a
+    :class:`WeightVersion` record."""
+
+    @property
+    def current_version(self) -> WeightVersion:
+        return WeightVersion(int(self.version), self.__dict__.get("_version_time", 0.0), self.__dict__.get("_version_checksum", ""))
+
+    def has_new_version(self, version: int) -> bool:
+        return int(self.version) > int(version)
+
+    def get_version_info(self) -> WeightVersion:
+        return self.current_version
+
+
+class NCCLWeightTransfer(_VersionedMixin):
     def __init__(self, group=None, src_rank: int = 0):
         self.group, self.src = group, src_rank
         self.version = 0
@@ -97,7 +165,7 @@ class NCCLWeightTransfer:
         return templates
 
 
-class RayObjectStoreTransfer:
+class RayObjectStoreTransfer(_VersionedMixin):
     """CPU copy -> ``ray.put`` / ``ray.get`` (src/transfer/nccl_transfer.py:226-361)."""
 
     def __init__(self):
@@ -108,6 +176,7 @@ class RayObjectStoreTransfer:
             self.available = False
         self.stats = TransferStats()
         self._ref = None
+        self.version = 0
 
     def publish_weights(self, state: Dict[str, torch.Tensor]):
         if not self.available:
@@ -116,6 +185,7 @@ class RayObjectStoreTransfer:
         t0 = time.perf_counter()
         cpu = {k: v.detach().cpu() for k, v in state.items()}
         self._ref = ray.put(cpu)
+        self.version += 1
         self.stats.record(sum(v.numel() * v.element_size() for v in cpu.values()), time.perf_counter() - t0)
         return self._ref
 
@@ -127,7 +197,7 @@ class RayObjectStoreTransfer:
         return {k: v.to(device) for k, v in state.items()}
 
 
-class WeightTransferManager:
+class WeightTransferManager(_VersionedMixin):
     """One entry point over the backends: ``local`` (same process: in-place copy into the engine),
     ``peer_write`` (NVLink kernel), ``nccl`` (broadcast baseline), ``ray_object_store``."""
 
@@ -170,6 +240,28 @@ class WeightTransferManager:
     async def sync_weights_async(self, *a, **kw):
         import asyncio
         return await asyncio.get_running_loop().run_in_executor(None, lambda: self.sync_weights(*a, **kw))
+
+    def sync_weights_sync(self, state_dict: Optional[Dict[str, torch.Tensor]] = None, is_sender: bool = True,
+                          state_dict_template: Optional[Dict[str, torch.Tensor]] = None, engine=None) -> WeightVersion:
+        """The reference's blocking entry point and argument order (src/transfer/nccl_transfer.py:448-478): the
+        receiver's tensors arrive in ``state_dict_template`` (or ``state_dict``) and are copied into
+        ``state_dict`` in place."""
+        template = state_dict_template if state_dict_template is not None else state_dict
+        self.sync_weights(is_sender, state_dict, engine, templates=None if is_sender else template)
+        if not is_sender and state_dict is not None and template is not state_dict:
+            for k, v in template.items():
+                if k in state_dict:
+                    state_dict[k].copy_(v)
+        return self.current_version
+
+    def get_transfer_stats(self) -> Dict:
+        st = self.stats
+        return {"backend": self.backend, "current_version": int(self.version), "total_syncs": st.sync_count,
+                "last_transfer": {"total_params": st.total_params, "total_bytes": st.total_bytes,
+                                  "total_bytes_human": f"{st.total_bytes / 1e9:.2f} GB",
+                                  "broadcast_time_s": st.broadcast_time, "serialization_time_s": st.serialization_time,
+                                  "total_time_s": st.total_time, "bandwidth_gbps": st.bandwidth_gbps},
+                "history": list(st.history)}
 
     def get_stats(self) -> Dict:
         return {"backend": self.backend, "version": self.version, "transfers": self.stats.transfers,

@@ -22,6 +22,22 @@ class SwiftSyncConfig:
     enabled: bool = False
     fallback_full_every: int = 10
     double_buffer: bool = True
+    # further fields of the reference's config (src/transfer/swift_sync.py:36-52)
+    delta_threshold: float = 1e-8        # reserved there for sparse deltas; not used by either implementation
+    async_transfer: bool = True          # the orchestrator picks sync_*_async when it runs inside an event loop
+
+    @property
+    def enable_double_buffer(self) -> bool:
+        return self.double_buffer
+
+
+@dataclass
+class DeltaVersion:
+    """What one delta sync carried (src/transfer/swift_sync.py:55-68)."""
+    version: int
+    timestamp: float
+    num_params: int
+    delta_bytes: int
 
 
 @dataclass
@@ -47,6 +63,39 @@ class SwiftSyncStats:
                              "gbps": nbytes / dt / 1e9 if dt > 0 else 0.0})
 
 
+    # the reference's counter names (SyncStats, src/transfer/swift_sync.py:71-83)
+    @property
+    def total_delta_syncs(self) -> int:
+        return self.delta_syncs
+
+    @property
+    def total_full_syncs(self) -> int:
+        return self.full_syncs
+
+    @property
+    def total_delta_bytes(self) -> int:
+        return sum(h["bytes"] for h in self.history if h["mode"] == "delta")
+
+    @property
+    def total_full_bytes(self) -> int:
+        return sum(h["bytes"] for h in self.history if h["mode"] != "delta")
+
+    @property
+    def last_sync_time(self) -> float:
+        return self.last_time_s
+
+    @property
+    def last_sync_type(self) -> str:
+        return self.last_mode
+
+    @property
+    def cumulative_time(self) -> float:
+        return self.total_time_s
+
+
+SyncStats = SwiftSyncStats
+
+
 class DeltaComputer:
     def __init__(self, fallback_full_every: int = 10):
         self.fallback_full_every = fallback_full_every
@@ -68,6 +117,10 @@ class DeltaComputer:
 
     def reset(self):
         self.prev = None
+
+    @staticmethod
+    def compute_delta_bytes(delta: Dict[str, torch.Tensor]) -> int:
+        return _nbytes(delta)
 
 
 def _nbytes(state: Dict[str, torch.Tensor]) -> int:
@@ -150,6 +203,41 @@ class SwiftSyncTransfer:
         if self.delta_computer.prev is None or self.delta_computer.should_full_sync(step):
             return self.sync_full(lora_state)
         return self.sync_delta(self.delta_computer.compute_delta(lora_state))
+
+    # ---- the reference's names (src/transfer/swift_sync.py:340-596) -------------------------------------------
+    def initialize(self, initial_lora_state: Dict[str, torch.Tensor]) -> None:
+        """Seed the previous-state snapshot and both buffers with the adapters' initial state, so that the first
+        ``sync`` already sends a delta.  Without it the first ``sync`` is a full one."""
+        self.delta_computer.prev = {k: v.detach().clone() for k, v in initial_lora_state.items()}
+        self.buffer.set_full_state(initial_lora_state, swap=self.config.double_buffer)
+
+    @property
+    def initialized(self) -> bool:
+        return self.delta_computer.prev is not None
+
+    @property
+    def prev_snapshot(self) -> Optional[Dict[str, torch.Tensor]]:
+        return self.delta_computer.prev
+
+    @property
+    def double_buffer(self) -> DoubleBufferedLoRA:
+        return self.buffer
+
+    @property
+    def version(self) -> int:
+        return self.buffer.version
+
+    @property
+    def last_delta_version(self) -> Optional[DeltaVersion]:
+        h = next((x for x in reversed(self.stats.history) if x["mode"] == "delta"), None)
+        return None if h is None else DeltaVersion(self.version, time.time(), len(self.buffer.get_active_state()), h["bytes"])
+
+    def get_stats_summary(self) -> Dict:
+        s = self.stats
+        return {"version": self.version, "initialized": self.initialized, "total_delta_syncs": s.total_delta_syncs,
+                "total_full_syncs": s.total_full_syncs, "total_delta_bytes": s.total_delta_bytes,
+                "total_full_bytes": s.total_full_bytes, "last_sync_time": s.last_sync_time,
+                "last_sync_type": s.last_sync_type, "cumulative_time": s.cumulative_time}
 
     def get_stats(self) -> Dict:
         s = self.stats

@@ -337,6 +337,15 @@ class TrainEngine:
         self._accumulation_count += 1
         return loss.detach(), self._maybe_step()
 
+    @property
+    def trainable_params_count(self) -> int:
+        """Trainable parameters on this rank (src/engines/train_engine.py:1756-1768)."""
+        return 0 if self.model is None else sum(p.numel() for p in self.model.parameters() if p.requires_grad)
+
+    @property
+    def total_params_count(self) -> int:
+        return 0 if self.model is None else sum(p.numel() for p in self.model.parameters())
+
     # ---- CUDA-graph micro-step ----------------------------------------------------------------------
     def release_graphs(self):
         """Drop every captured micro-step graph (and the memory pool they share).  Graphs that contain
