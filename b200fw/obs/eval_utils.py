@@ -4,17 +4,29 @@ from __future__ import annotations
 
 import math
 import re
-import string
 from collections import Counter
 from dataclasses import dataclass, field
 from typing import Dict, List
 
 
 def normalize_text(s: str) -> str:
-    s = s.lower()
-    s = "".join(ch for ch in s if ch not in set(string.punctuation))
-    s = re.sub(r"\b(a|an|the)\b", " ", s)
+    """Lower-case, every character that is neither a word character, white space nor a CJK ideograph becomes a
+    space (so ASCII and full-width punctuation both separate words), runs of white space collapse
+    (src/utils/eval_utils.py:22-37)."""
+    s = re.sub(r"[^\w\s\u4e00-\u9fff]", " ", s.lower())
     return " ".join(s.split())
+
+
+def tokenize_for_eval(text: str) -> List[str]:
+    """Evaluation tokens of mixed text: white-space words, except that a word containing CJK ideographs is split
+    into its characters (src/utils/eval_utils.py:39-54)."""
+    out: List[str] = []
+    for word in normalize_text(text).split():
+        if any("\u4e00" <= c <= "\u9fff" for c in word):
+            out.extend(word)
+        else:
+            out.append(word)
+    return out
 
 
 def compute_exact_match(pred: str, ref: str) -> float:
@@ -22,7 +34,7 @@ def compute_exact_match(pred: str, ref: str) -> float:
 
 
 def compute_token_f1(pred: str, ref: str) -> float:
-    p, r = normalize_text(pred).split(), normalize_text(ref).split()
+    p, r = tokenize_for_eval(pred), tokenize_for_eval(ref)
     if not p or not r:
         return float(p == r)
     common = Counter(p) & Counter(r)
@@ -35,7 +47,7 @@ def compute_token_f1(pred: str, ref: str) -> float:
 
 def compute_bleu4(pred: str, ref: str) -> float:
     """Sentence BLEU-4 with add-one smoothing on the higher-order precisions and brevity penalty."""
-    p, r = normalize_text(pred).split(), normalize_text(ref).split()
+    p, r = tokenize_for_eval(pred), tokenize_for_eval(ref)
     if not p or not r:
         return 0.0
     logs = 0.0

@@ -17,6 +17,13 @@ import torch.distributed as dist
 from ..dist import comm
 
 
+def default_loss_fn(logits: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
+    """Token-mean cross-entropy of ``[*, V]`` logits against ``[*]`` labels, no next-token shift
+    (src/distributed/pipeline_scheduler.py:55-65).  The scheduler itself uses the model's fused LM-head loss, which
+    never materialises the logits; this function is the plain form for callers that already have them."""
+    return torch.nn.functional.cross_entropy(logits.reshape(-1, logits.shape[-1]).float(), labels.reshape(-1).long())
+
+
 class PipelineScheduler:
     def __init__(self, model, pp_context, num_micro_batches: int):
         assert num_micro_batches >= pp_context.pp_size, "need num_micro_batches >= pp_size to fill the pipe"

@@ -1,8 +1,9 @@
 """Rule-based GSM8K reward (behaviour of src/reward/gsm8k_reward.py:17-223).
 
 Answer extraction tries, in order: ``#### <number>``, ``\\boxed{...}``, "the answer is" / "答案是" phrases,
-then the last number in the text.  Reward: +1 for a correct answer, -0.5 for a well-formed but wrong one,
--1 when no answer can be extracted.  Running accuracy statistics are kept.
+then the last number in the text.  Reward: +1 for a correct answer; a wrong or missing answer gets -0.5 when
+the response is well formed (step markers, several lines or an explicit answer marker) and -1 otherwise.
+Running accuracy statistics are kept.
 """
 from __future__ import annotations
 
@@ -41,9 +42,33 @@ def extract_answer(text: str) -> Optional[float]:
     return _to_float(nums[-1]) if nums else None
 
 
+_STEPS = [re.compile(r"(步骤|step|第\s*\d+\s*步)", re.IGNORECASE), re.compile(r"\d+[.)]\s+\S")]
+
+
 def check_format(text: str) -> bool:
-    """True when the response states its answer explicitly (marker, box or answer phrase)."""
-    return any(p.search(text) for p in _PATTERNS)
+    """True when the response shows its work or marks its answer: step markers ("Step 2", "1. ...", "第 3 步"),
+    at least three lines, or an explicit answer marker (``####``, ``\\boxed{}``, "the answer is", "答案是")
+    (src/reward/gsm8k_reward.py:74-99)."""
+    if not text:
+        return False
+    has_steps = any(p.search(text) for p in _STEPS) or text.count("\n") >= 2
+    return has_steps or any(p.search(text) for p in _PATTERNS)
+
+
+def compute_reward(response: str, ground_truth, tol: float = 1e-4) -> float:
+    """+1.0 correct answer; otherwise -0.5 when the response is well formed (:func:`check_format`), -1.0 when it is
+    not (src/reward/gsm8k_reward.py:102-125)."""
+    pred = extract_answer(response or "")
+    gt = ground_truth if isinstance(ground_truth, (int, float)) else extract_answer(str(ground_truth))
+    if pred is not None and gt is not None and abs(pred - gt) <= tol * max(1.0, abs(gt)):
+        return 1.0
+    return -0.5 if check_format(response or "") else -1.0
+
+
+def compute_batch_rewards(responses: List[str], ground_truths: List) -> List[float]:
+    assert len(responses) == len(ground_truths), \
+        f"responses({len(responses)}) and ground_truths({len(ground_truths)}) must have same length"
+    return [compute_reward(r, g) for r, g in zip(responses, ground_truths)]
 
 
 class GSM8KRewardFunction:
@@ -61,16 +86,14 @@ class GSM8KRewardFunction:
 
     def _score(self, response: str, ground_truth) -> float:
         self.total += 1
-        pred = extract_answer(response)
+        formatted = check_format(response or "")
+        self.num_formatted += int(formatted)
+        pred = extract_answer(response or "")
         gt = ground_truth if isinstance(ground_truth, (int, float)) else extract_answer(str(ground_truth))
-        if check_format(response):
-            self.num_formatted += 1
-        if pred is None or gt is None:
-            return self.no_answer
-        if abs(pred - gt) <= self.tol * max(1.0, abs(gt)):
+        if pred is not None and gt is not None and abs(pred - gt) <= self.tol * max(1.0, abs(gt)):
             self.num_correct += 1
             return self.correct
-        return self.wrong
+        return self.wrong if formatted else self.no_answer
 
     def __call__(self, responses: List[List[str]], ground_truths: List) -> List[List[float]]:
         """``responses[b][k]`` -> rewards of the same shape."""

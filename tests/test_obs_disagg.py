@@ -152,8 +152,12 @@ def test_memory_helpers_on_cpu():
 
 
 def test_eval_utils_and_logger(tmp_path):
-    assert compute_exact_match("The Answer.", "answer") == 1.0
-    assert abs(compute_token_f1("a cat sat", "the cat sat down") - 0.8) < 1e-9
+    assert compute_exact_match("The  Answer.", "the answer") == 1.0 and compute_exact_match("The Answer.", "answer") == 0.0
+    assert abs(compute_token_f1("cat sat", "cat sat down") - 0.8) < 1e-9
+    from b200fw.obs.eval_utils import normalize_text, tokenize_for_eval
+    assert normalize_text("Hello, World!  x=3") == "hello world x 3" and normalize_text("答案是：18。") == "答案是 18"
+    assert tokenize_for_eval("The answer 是18个苹果, ok") == ["the", "answer", "是", "1", "8", "个", "苹", "果", "ok"]
+    assert abs(compute_token_f1("答案是十八", "答案是十九") - 0.8) < 1e-9
     assert compute_bleu4("the quick brown fox jumps", "the quick brown fox jumps") == 1.0
     assert 0 < compute_bleu4("the quick brown dog jumps high", "the quick brown fox jumps high") < 1
     e = EvalMetrics()

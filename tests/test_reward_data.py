@@ -28,18 +28,27 @@ def test_answer_extraction_misses_and_format():
     assert extract_answer("no digits here") is None
     assert extract_answer("") is None
     assert check_format("#### 7") and check_format("\\boxed{3}") and check_format("the answer is 4")
-    assert not check_format("maybe 7?")
+    assert check_format("Step 1: add the apples") and check_format("1. first thing") and check_format("a\nb\nc")
+    assert check_format("第 2 步：相加") and not check_format("maybe 7?") and not check_format("")
 
 
 def test_gsm8k_reward_values_and_stats():
+    from b200fw.reward import compute_batch_rewards, compute_reward
+    # correct: +1; wrong or missing answer: -0.5 when well formed, -1 otherwise
+    assert compute_batch_rewards(["... #### 72", "I think it is 70", "cannot tell", "Step 1: add\nStep 2: 71", "#### 71"],
+                                 ["#### 72"] * 5) == [1.0, -1.0, -1.0, -0.5, -0.5]
+    assert compute_reward("so 72 it is", 72) == 1.0                 # the last number counts when nothing marks the answer
+    with pytest.raises(AssertionError):
+        compute_batch_rewards(["a"], [])
     rf = GSM8KRewardFunction()
     rewards = rf([["... #### 72", "I think it is 70", "cannot tell"],
                   ["\\boxed{10}", "#### 10.00004", "#### 11"]], ["#### 72", 10])
-    assert rewards == [[1.0, -0.5, -1.0], [1.0, 1.0, -0.5]]
+    assert rewards == [[1.0, -1.0, -1.0], [1.0, 1.0, -0.5]]
     st = rf.get_stats()
     assert st["total"] == 6 and st["accuracy"] == pytest.approx(3 / 6) and st["format_rate"] == pytest.approx(4 / 6)
+    assert rf.format_accuracy == pytest.approx(4 / 6) and rf.average_reward == pytest.approx(0.5 / 6)
     rf.reset_stats()
-    assert rf.get_stats()["total"] == 0 and rf.accuracy == 0.0
+    assert rf.get_stats()["total"] == 0 and rf.accuracy == 0.0 and rf.average_reward == 0.0
     assert GSM8KRewardFunction(correct=2.0, wrong=0.0, no_answer=-2.0).score("#### 1", 1) == 2.0
 
 
