@@ -114,7 +114,8 @@ class MemoryProfiler:
         self._hooks = []
         self.phase_peaks: Dict[str, float] = {}
 
-    def snapshot(self, tag: str) -> MemorySnapshot:
+    def snapshot(self, tag: Optional[str] = None, stage: Optional[str] = None) -> MemorySnapshot:
+        tag = tag if tag is not None else (stage or "")            # `stage`: the reference's parameter name
         if self.enabled:
             free, total = torch.cuda.mem_get_info(self.device)
             s = MemorySnapshot(tag, time.time(), torch.cuda.memory_allocated(self.device) / GB,

@@ -13,7 +13,9 @@ import torch
 
 
 class DoubleBufferedLoRA:
-    def __init__(self, initial_state: Optional[Dict[str, torch.Tensor]] = None):
+    def __init__(self, initial_state: Optional[Dict[str, torch.Tensor]] = None,
+                 initial_lora_state: Optional[Dict[str, torch.Tensor]] = None):
+        initial_state = initial_state if initial_state is not None else initial_lora_state
         self._lock = threading.Lock()
         self.active: Dict[str, torch.Tensor] = {}
         self.shadow: Dict[str, torch.Tensor] = {}

@@ -40,8 +40,9 @@ def classify_error(e: BaseException) -> str:
 
 class VLLMClient:
     def __init__(self, base_url: str = "http://localhost:8000", timeout: float = 60.0, max_retries: int = 3,
-                 backoff_s: float = 1.0, client=None):
+                 backoff_s: float = 1.0, client=None, retry_delay: Optional[float] = None):
         self.base_url = base_url.rstrip("/")
+        backoff_s = retry_delay if retry_delay is not None else backoff_s      # `retry_delay`: the reference's name
         self.timeout, self.max_retries, self.backoff_s = timeout, max_retries, backoff_s
         self._client = client
         self.calls: List[str] = []
@@ -132,7 +133,10 @@ class IPCHandle:
 
 
 class IPCWeightTransfer:
-    def __init__(self, client: VLLMClient, chunk_size: int = 16, device_index: int = 0):
+    def __init__(self, client: Optional[VLLMClient] = None, chunk_size: int = 16, device_index: int = 0,
+                 vllm_client: Optional[VLLMClient] = None):
+        client = client if client is not None else vllm_client                  # `vllm_client`: the reference's name
+        assert client is not None, "IPCWeightTransfer needs a VLLMClient"
         self.client, self.chunk_size, self.device_index = client, chunk_size, device_index
         self.stats = TransferStats()
         self._keepalive: List[torch.Tensor] = []     # exported tensors must outlive the receiver's import

@@ -155,9 +155,11 @@ class SwiftSyncTransfer:
             else:   # already inside a loop: the caller should use the async variants
                 raise RuntimeError("use sync_delta_async / sync_full_async inside an event loop")
 
-    def sync_delta(self, delta: Dict[str, torch.Tensor]) -> int:
+    def sync_delta(self, delta: Dict[str, torch.Tensor], infer_worker=None) -> int:
         """Apply a delta: notify first (a worker that cannot take it must not see a version bump),
-        then update the local double buffer and swap."""
+        then update the local double buffer and swap.  ``infer_worker`` replaces the worker given at construction."""
+        if infer_worker is not None:
+            self.worker = infer_worker
         t0 = time.perf_counter()
         self._notify(delta, "delta")
         self.buffer.apply_delta_to_shadow(delta)
@@ -165,7 +167,9 @@ class SwiftSyncTransfer:
         self.stats.record("delta", _nbytes(delta), time.perf_counter() - t0)
         return v
 
-    def sync_full(self, state: Dict[str, torch.Tensor]) -> int:
+    def sync_full(self, state: Dict[str, torch.Tensor], infer_worker=None) -> int:
+        if infer_worker is not None:
+            self.worker = infer_worker
         t0 = time.perf_counter()
         self._notify(state, "full")
         v = self.buffer.set_full_state(state, swap=self.config.double_buffer)

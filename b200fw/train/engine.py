@@ -623,10 +623,10 @@ class TrainEngine:
         return out
 
     @torch.no_grad()
-    def export_lora_delta(self) -> Dict[str, torch.Tensor]:
+    def export_lora_delta(self, device: Optional[str] = None) -> Dict[str, torch.Tensor]:
         """Current LoRA tensors minus the previous export's snapshot (the first call returns the full
-        state).  Feeds the SwiftSync delta path."""
-        cur = {k: v.clone() for k, v in get_lora_state_dict(self.model).items()}
+        state), on ``device`` when given.  Feeds the SwiftSync delta path."""
+        cur = {k: (v.clone() if device is None else v.to(device, copy=True)) for k, v in get_lora_state_dict(self.model).items()}
         if self._prev_lora_snapshot is None:
             delta = {k: v.clone() for k, v in cur.items()}
         else:
