@@ -43,6 +43,22 @@ class DoubleBufferedLoRA:
                 n += 1
         return n
 
+    def update_in_place(self, payload: Dict[str, torch.Tensor], add: bool) -> int:
+        """Single-buffer mode: add ``payload`` to (or overwrite) the active tensors directly, keep the shadow
+        level with them, bump the version."""
+        with self._lock:
+            for k, t in payload.items():
+                cur = self.active.get(k)
+                if cur is None or cur.shape != t.shape:
+                    self.active[k] = t.detach().clone()
+                elif add:
+                    cur.add_(t.to(cur.dtype).to(cur.device))
+                else:
+                    cur.copy_(t)
+                self.shadow[k] = self.active[k].clone()
+            self.version += 1
+            return self.version
+
     def swap_buffers(self) -> int:
         with self._lock:
             self.active, self.shadow = self.shadow, self.active

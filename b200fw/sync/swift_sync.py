@@ -25,10 +25,12 @@ class SwiftSyncConfig:
     # further fields of the reference's config (src/transfer/swift_sync.py:36-52)
     delta_threshold: float = 1e-8        # reserved there for sparse deltas; not used by either implementation
     async_transfer: bool = True          # the orchestrator picks sync_*_async when it runs inside an event loop
+    enable_double_buffer: Optional[bool] = None   # the reference's name for ``double_buffer``; wins when given
 
-    @property
-    def enable_double_buffer(self) -> bool:
-        return self.double_buffer
+    def __post_init__(self):
+        if self.enable_double_buffer is not None:
+            self.double_buffer = bool(self.enable_double_buffer)
+        self.enable_double_buffer = self.double_buffer
 
 
 @dataclass
@@ -97,16 +99,26 @@ SyncStats = SwiftSyncStats
 
 
 class DeltaComputer:
-    def __init__(self, fallback_full_every: int = 10):
-        self.fallback_full_every = fallback_full_every
+    def __init__(self, fallback_full_every=10):
+        """``fallback_full_every``: the period, or a :class:`SwiftSyncConfig` carrying it (the reference passes
+        its config: src/transfer/swift_sync.py:90-110)."""
+        if isinstance(fallback_full_every, SwiftSyncConfig):
+            fallback_full_every = fallback_full_every.fallback_full_every
+        self.fallback_full_every = int(fallback_full_every)
         self.prev: Optional[Dict[str, torch.Tensor]] = None
+        self._step_count = 0
 
     def should_full_sync(self, step: int) -> bool:
         return step > 0 and self.fallback_full_every > 0 and step % self.fallback_full_every == 0
 
     @torch.no_grad()
-    def compute_delta(self, current: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
-        """current - previous snapshot (first call: the full state), then remember ``current``."""
+    def compute_delta(self, current: Dict[str, torch.Tensor],
+                      prev: Optional[Dict[str, torch.Tensor]] = None) -> Dict[str, torch.Tensor]:
+        """current - previous snapshot (first call: the full state), then remember ``current``.  With an explicit
+        ``prev`` the call is stateless: ``current - prev`` per key, a key missing from ``prev`` yields itself."""
+        self._step_count += 1
+        if prev is not None:
+            return {k: v.detach() - prev[k].to(v.device) if k in prev else v.detach().clone() for k, v in current.items()}
         if self.prev is None:
             delta = {k: v.detach().clone() for k, v in current.items()}
         else:
@@ -130,11 +142,23 @@ def _nbytes(state: Dict[str, torch.Tensor]) -> int:
 class SwiftSyncTransfer:
     def __init__(self, infer_worker=None, config: Optional[SwiftSyncConfig] = None,
                  buffer: Optional[DoubleBufferedLoRA] = None):
+        if isinstance(infer_worker, SwiftSyncConfig):      # the reference's constructor takes the config first
+            infer_worker, config = None, infer_worker
         self.worker = infer_worker
         self.config = config or SwiftSyncConfig(enabled=True)
         self.buffer = buffer or DoubleBufferedLoRA()
         self.delta_computer = DeltaComputer(self.config.fallback_full_every)
         self.stats = SwiftSyncStats()
+
+    def _commit(self, payload: Dict[str, torch.Tensor], mode: str) -> int:
+        """Update the local copy after the worker accepted the payload: shadow + swap with double buffering, in
+        place without.  Returns the new version."""
+        if not self.config.double_buffer:
+            return self.buffer.update_in_place(payload, add=mode == "delta")
+        if mode == "delta":
+            self.buffer.apply_delta_to_shadow(payload)
+            return self.buffer.swap_buffers()
+        return self.buffer.set_full_state(payload, swap=True)
 
     def _notify(self, state: Dict[str, torch.Tensor], mode: str):
         if self.worker is None:
@@ -162,8 +186,7 @@ class SwiftSyncTransfer:
             self.worker = infer_worker
         t0 = time.perf_counter()
         self._notify(delta, "delta")
-        self.buffer.apply_delta_to_shadow(delta)
-        v = self.buffer.swap_buffers() if self.config.double_buffer else self.buffer.version
+        v = self._commit(delta, "delta")
         self.stats.record("delta", _nbytes(delta), time.perf_counter() - t0)
         return v
 
@@ -172,23 +195,27 @@ class SwiftSyncTransfer:
             self.worker = infer_worker
         t0 = time.perf_counter()
         self._notify(state, "full")
-        v = self.buffer.set_full_state(state, swap=self.config.double_buffer)
+        v = self._commit(state, "full")
         self.delta_computer.prev = {k: t.detach().clone() for k, t in state.items()}
         self.stats.record("full", _nbytes(state), time.perf_counter() - t0)
         return v
 
-    async def sync_delta_async(self, delta: Dict[str, torch.Tensor]) -> int:
+    async def sync_delta_async(self, delta: Dict[str, torch.Tensor], infer_worker=None) -> int:
+        if infer_worker is not None:
+            self.worker = infer_worker
         t0 = time.perf_counter()
         await self._notify_async(delta, "delta")
-        self.buffer.apply_delta_to_shadow(delta)
-        v = self.buffer.swap_buffers() if self.config.double_buffer else self.buffer.version
+        v = self._commit(delta, "delta")
         self.stats.record("delta", _nbytes(delta), time.perf_counter() - t0)
         return v
 
-    async def sync_full_async(self, state: Dict[str, torch.Tensor]) -> int:
+    async def sync_full_async(self, state: Dict[str, torch.Tensor], infer_worker=None) -> int:
+        if infer_worker is not None:
+            self.worker = infer_worker
         t0 = time.perf_counter()
         await self._notify_async(state, "full")
-        v = self.buffer.set_full_state(state, swap=self.config.double_buffer)
+        v = self._commit(state, "full")
+        self.delta_computer.prev = {k: t.detach().clone() for k, t in state.items()}   # next delta is relative to this
         self.stats.record("full", _nbytes(state), time.perf_counter() - t0)
         return v
 
@@ -213,7 +240,7 @@ class SwiftSyncTransfer:
         """Seed the previous-state snapshot and both buffers with the adapters' initial state, so that the first
         ``sync`` already sends a delta.  Without it the first ``sync`` is a full one."""
         self.delta_computer.prev = {k: v.detach().clone() for k, v in initial_lora_state.items()}
-        self.buffer.set_full_state(initial_lora_state, swap=self.config.double_buffer)
+        self.buffer = DoubleBufferedLoRA(initial_lora_state)         # version 0: nothing has been synced yet
 
     @property
     def initialized(self) -> bool:
@@ -224,8 +251,10 @@ class SwiftSyncTransfer:
         return self.delta_computer.prev
 
     @property
-    def double_buffer(self) -> DoubleBufferedLoRA:
-        return self.buffer
+    def double_buffer(self) -> Optional[DoubleBufferedLoRA]:
+        """The local double buffer (``None`` when the config turns double buffering off: the state is then kept
+        in a single buffer that is updated in place)."""
+        return self.buffer if self.config.double_buffer else None
 
     @property
     def version(self) -> int:
@@ -241,7 +270,9 @@ class SwiftSyncTransfer:
         return {"version": self.version, "initialized": self.initialized, "total_delta_syncs": s.total_delta_syncs,
                 "total_full_syncs": s.total_full_syncs, "total_delta_bytes": s.total_delta_bytes,
                 "total_full_bytes": s.total_full_bytes, "last_sync_time": s.last_sync_time,
-                "last_sync_type": s.last_sync_type, "cumulative_time": s.cumulative_time}
+                "last_sync_type": s.last_sync_type, "cumulative_time": s.cumulative_time,
+                "config": {"enabled": self.config.enabled, "fallback_full_every": self.config.fallback_full_every,
+                           "enable_double_buffer": self.config.double_buffer, "async_transfer": self.config.async_transfer}}
 
     def get_stats(self) -> Dict:
         s = self.stats

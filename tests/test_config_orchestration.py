@@ -14,7 +14,7 @@ import torch
 from b200fw.config import (ColocateConfig, build_colocate_config, get_nested, load_yaml_config,
                            validate_parallel_config)
 from b200fw.orch import ColocateOrchestrator, OrchestratorState
-from b200fw.sync import (DeltaComputer, DoubleBufferedLoRA, IPCWeightTransfer, PeerWeightSync, SwiftSyncTransfer,
+from b200fw.sync import (DeltaComputer, DoubleBufferedLoRA, IPCWeightTransfer, PeerWeightSync, SwiftSyncConfig, SwiftSyncTransfer,
                          VLLMClient, WeightUpdateManager, classify_error, fletcher_checksum)
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -268,6 +268,40 @@ def test_swift_sync_delta_math_policy_and_double_buffer():
     with pytest.raises(AttributeError):
         t2.sync_delta({"a": torch.ones(2)})
     assert t2.buffer.version == 0
+
+
+def test_swift_sync_single_buffer_mode_async_full_and_stateless_delta():
+    class W:
+        def __init__(self):
+            self.modes = []
+
+        async def update_weights(self, state, mode="delta"):
+            self.modes.append(mode)
+    t = SwiftSyncTransfer(SwiftSyncConfig(enabled=True, enable_double_buffer=False))      # config first, as the reference
+    t.initialize({"A": torch.zeros(2, 2)})
+    assert t.version == 0 and t.double_buffer is None and t.initialized
+    w = W()
+    assert t.sync_delta({"A": torch.ones(2, 2)}, w) == 1                                   # async worker from sync code
+    assert torch.equal(t.buffer.get_active_state()["A"], torch.ones(2, 2))                 # updated in place
+    assert asyncio.run(t.sync_full_async({"A": torch.full((2, 2), 9.0)})) == 2
+    assert torch.equal(t.prev_snapshot["A"], torch.full((2, 2), 9.0)) and w.modes == ["delta", "full"]
+    assert asyncio.run(t.sync_delta_async({"A": torch.ones(2, 2)}, w)) == 3
+    assert float(t.buffer.get_active_state()["A"][0, 0]) == 10.0 and t.get_stats_summary()["config"]["enable_double_buffer"] is False
+
+    class NoApi:
+        pass
+    t2 = SwiftSyncTransfer(SwiftSyncConfig(enabled=True))
+    t2.initialize({"A": torch.zeros(2, 2)})
+    try:
+        t2.sync_delta({"A": torch.ones(2, 2)}, NoApi())
+        raise AssertionError("a worker without update_weights must be refused")
+    except AttributeError:
+        pass
+    assert t2.version == 0 and float(t2.buffer.get_active_state()["A"].sum()) == 0.0
+    c = DeltaComputer(SwiftSyncConfig(enabled=True, fallback_full_every=5))
+    assert c.should_full_sync(5) and not c.should_full_sync(0) and not c.should_full_sync(7)
+    d = c.compute_delta({"a": torch.ones(1), "b": torch.full((1,), 3.0)}, {"a": torch.zeros(1)})
+    assert float(d["a"]) == 1.0 and float(d["b"]) == 3.0 and c._step_count == 1 and c.prev is None
 
 
 def test_double_buffer_swap_under_threads():
