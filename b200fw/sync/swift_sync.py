@@ -10,6 +10,7 @@ from __future__ import annotations
 import inspect
 import time
 from dataclasses import dataclass, field
+from collections.abc import Coroutine
 from typing import Dict, List, Optional
 
 import torch
@@ -96,6 +97,34 @@ class SwiftSyncStats:
 
 
 SyncStats = SwiftSyncStats
+
+
+class SyncResult(int, Coroutine):
+    """What ``sync_delta`` / ``sync_full`` return: the new version as an ``int`` that can also be awaited.
+
+    The reference declares these two methods ``async`` (src/transfer/swift_sync.py:352-470), so code written
+    against it says ``await transfer.sync_delta(delta, worker)`` or ``asyncio.run(transfer.sync_full(...))``;
+    here the work is done by the time the call returns, and awaiting the result yields the
+    :class:`DeltaVersion` record at once."""
+
+    def __new__(cls, version: int, info: "DeltaVersion"):
+        obj = int.__new__(cls, version)
+        obj.info = info
+        return obj
+
+    def __await__(self):
+        if False:
+            yield
+        return self.info
+
+    def send(self, value):
+        raise StopIteration(self.info)
+
+    def throw(self, typ, val=None, tb=None):
+        raise val if val is not None else (typ() if isinstance(typ, type) else typ)
+
+    def close(self):
+        pass
 
 
 class DeltaComputer:
@@ -188,7 +217,7 @@ class SwiftSyncTransfer:
         self._notify(delta, "delta")
         v = self._commit(delta, "delta")
         self.stats.record("delta", _nbytes(delta), time.perf_counter() - t0)
-        return v
+        return SyncResult(v, DeltaVersion(v, time.time(), len(delta), _nbytes(delta)))
 
     def sync_full(self, state: Dict[str, torch.Tensor], infer_worker=None) -> int:
         if infer_worker is not None:
@@ -198,7 +227,7 @@ class SwiftSyncTransfer:
         v = self._commit(state, "full")
         self.delta_computer.prev = {k: t.detach().clone() for k, t in state.items()}
         self.stats.record("full", _nbytes(state), time.perf_counter() - t0)
-        return v
+        return SyncResult(v, DeltaVersion(v, time.time(), len(state), _nbytes(state)))
 
     async def sync_delta_async(self, delta: Dict[str, torch.Tensor], infer_worker=None) -> int:
         if infer_worker is not None:

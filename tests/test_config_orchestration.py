@@ -298,6 +298,16 @@ def test_swift_sync_single_buffer_mode_async_full_and_stateless_delta():
     except AttributeError:
         pass
     assert t2.version == 0 and float(t2.buffer.get_active_state()["A"].sum()) == 0.0
+    # the reference declares sync_delta / sync_full async: the returned version can be awaited as well
+    class SyncW:
+        def update_weights(self, state, mode="delta"):
+            pass
+    r = t2.sync_delta({"A": torch.ones(2, 2)}, SyncW())
+    assert r == 1 and isinstance(r, int) and r + 1 == 2 and asyncio.run(r).delta_bytes == 16
+
+    async def awaited():
+        return await t2.sync_full({"A": torch.zeros(2, 2)}, SyncW())
+    assert asyncio.run(awaited()).version == 2 and t2.version == 2
     c = DeltaComputer(SwiftSyncConfig(enabled=True, fallback_full_every=5))
     assert c.should_full_sync(5) and not c.should_full_sync(0) and not c.should_full_sync(7)
     d = c.compute_delta({"a": torch.ones(1), "b": torch.full((1,), 3.0)}, {"a": torch.zeros(1)})
