@@ -413,6 +413,35 @@ class ColocateOrchestrator:
         self._write_final_artifacts()
         return self.metrics
 
+    # ---- stage methods under the reference's names (src/orchestrator/colocate_orchestrator.py:886-1060,
+    # 1644-1740): its loop and its tests address the stages as _do_* coroutines --------------------------------
+    async def _do_inference(self, batch: GRPOBatch, num_samples: Optional[int] = None) -> List[List[List[int]]]:
+        """K sampled responses per prompt of ``batch`` as token-id lists ``[B][K][tokens]``."""
+        if num_samples is not None and num_samples != self.config.num_samples_per_prompt:
+            saved, self.config.num_samples_per_prompt = self.config.num_samples_per_prompt, num_samples
+            try:
+                return self._rollout(batch).responses
+            finally:
+                self.config.num_samples_per_prompt = saved
+        return self._rollout(batch).responses
+
+    async def _do_inference_async(self, batch: GRPOBatch, num_samples: Optional[int] = None):
+        """The rollout on the worker thread, so that it overlaps training on the event-loop thread."""
+        loop = asyncio.get_running_loop()
+        return (await loop.run_in_executor(self._pool, self._rollout, batch)).responses
+
+    async def _do_training(self, batch: GRPOBatch, responses: List[List[List[int]]], rewards: List[List[float]]) -> TrainMetrics:
+        return self._train_grpo(_Rollout(batch, responses, None, self.weights_version, 0.0), rewards)
+
+    async def _do_sft_training(self, batch: GRPOBatch) -> TrainMetrics:
+        return self._train_sft(batch)
+
+    async def _do_weight_sync(self, iteration: int = 0):
+        await self._sync(iteration)
+
+    async def _do_weight_sync_async(self, iteration: int = 0):
+        await self._sync(iteration)
+
     async def _sync(self, iteration: int):
         if self.vllm_client is not None:
             state = self.train_engine.export_weights("cuda" if torch.cuda.is_available() else None)
