@@ -50,16 +50,19 @@ class VLLMClient:
     async def _get_client(self):
         if self._client is None:
             import httpx
-            self._client = httpx.AsyncClient(timeout=self.timeout)
+            self._client = httpx.AsyncClient(base_url=self.base_url, timeout=httpx.Timeout(self.timeout))
         return self._client
 
     async def _request(self, method: str, path: str, **kw) -> Any:
+        """One request with the retry policy; ``path`` is relative to the client's base URL.  ``None``-valued
+        keyword arguments are dropped, so a call without parameters reaches the HTTP client as ``get("/health")``."""
         client = await self._get_client()
+        kw = {k: v for k, v in kw.items() if v is not None}
         attempt, oom_retried = 0, False
         while True:
             try:
                 self.calls.append(f"{method} {path}")
-                resp = await getattr(client, method.lower())(self.base_url + path, **kw)
+                resp = await getattr(client, method.lower())(path, **kw)
                 if hasattr(resp, "raise_for_status"):
                     resp.raise_for_status()
                 return resp
@@ -76,42 +79,67 @@ class VLLMClient:
                     raise
                 await asyncio.sleep(self.backoff_s * attempt)
 
+    # ---- control endpoints of the vLLM server (src/transfer/ipc_transfer.py:215-287): every call returns True and
+    # raises when the server refuses after the retries ------------------------------------------------------
     async def health(self) -> bool:
         try:
-            await self._request("GET", "/health")
-            return True
+            resp = await self._request("GET", "/health")
+            return getattr(resp, "status_code", 200) == 200
         except Exception:  # noqa: BLE001
             return False
 
     async def health_check(self) -> bool:
-        """The reference's name for :meth:`health` (src/transfer/ipc_transfer.py:215-222)."""
         return await self.health()
 
-    async def reset_prefix_cache(self):
-        return await self._request("POST", "/reset_prefix_cache")
+    async def reset_prefix_cache(self) -> bool:
+        await self._request("POST", "/reset_prefix_cache",
+                            params={"reset_running_requests": False, "reset_external": False})
+        return True
 
-    async def sleep(self, level: int = 1):
-        await self.reset_prefix_cache()
-        return await self._request("POST", f"/sleep?level={level}")
+    async def sleep(self, level: int = 1) -> bool:
+        """Level 0 pauses scheduling, 1 offloads weights and drops the KV cache, 2 frees all device memory.  The
+        prefix cache is reset first (a failure there is not fatal)."""
+        try:
+            await self.reset_prefix_cache()
+        except Exception as e:  # noqa: BLE001
+            logger.warning("reset_prefix_cache failed (non-fatal): %s", e)
+        await self._request("POST", "/sleep", params={"level": level})
+        return True
 
-    async def wake_up(self, tags: Optional[str] = None):
-        return await self._request("POST", "/wake_up" + (f"?tags={tags}" if tags else ""))
+    async def wake_up(self, tags=None) -> bool:
+        """``tags``: a list such as ``["weights", "kv_cache"]`` (sent as repeated query parameters) or one tag."""
+        if isinstance(tags, str):
+            tags = [tags]
+        await self._request("POST", "/wake_up", params={"tags": list(tags)} if tags else None)
+        return True
 
-    async def init_weight_transfer(self, payload: Optional[Dict] = None):
-        return await self._request("POST", "/init_weight_transfer_engine", json=payload or {})
+    async def init_weight_transfer(self, init_info: Optional[Dict] = None) -> bool:
+        await self._request("POST", "/init_weight_transfer_engine", json={"init_info": init_info or {}})
+        return True
 
-    async def start_weight_update(self, payload: Optional[Dict] = None):
-        return await self._request("POST", "/start_weight_update", json=payload or {})
+    async def start_weight_update(self, is_checkpoint_format=True) -> bool:
+        if isinstance(is_checkpoint_format, dict):           # older call style: a ready-made body
+            body = is_checkpoint_format
+        else:
+            body = {"is_checkpoint_format": bool(is_checkpoint_format)}
+        await self._request("POST", "/start_weight_update", json=body)
+        return True
 
-    async def update_weights(self, payload: Dict):
-        return await self._request("POST", "/update_weights", json=payload)
+    async def update_weights(self, update_info: Dict, weight_version: Optional[str] = None) -> bool:
+        body: Dict[str, Any] = {"update_info": update_info}
+        if weight_version is not None:
+            body["weight_version"] = weight_version
+        await self._request("POST", "/update_weights", json=body)
+        return True
 
-    async def finish_weight_update(self, payload: Optional[Dict] = None):
-        return await self._request("POST", "/finish_weight_update", json=payload or {})
+    async def finish_weight_update(self) -> bool:
+        await self._request("POST", "/finish_weight_update", json={})
+        return True
 
     async def close(self):
         if self._client is not None and hasattr(self._client, "aclose"):
             await self._client.aclose()
+        self._client = None
 
 
 def _gpu_uuid(device_index: int = 0) -> str:
@@ -208,7 +236,7 @@ class IPCWeightTransfer:
                 await self.client.sleep()
             handles = self.build_ipc_handles(state)
             await self.client.init_weight_transfer()
-            await self.client.start_weight_update({"num_tensors": len(handles)})
+            await self.client.start_weight_update(True)
             for chunk in self._chunk_handles(handles):
                 await self.client.update_weights(self._build_http_payload(chunk))
             await self.client.finish_weight_update()

@@ -56,17 +56,17 @@ class TransferStats:
             self.total_time_s += time.perf_counter() - self._start_time
             self._start_time = 0.0
 
+    # settable, as the reference's dataclass fields are; when unset they read the measured total
+    transfer_time: float = 0.0
+    broadcast_time: float = 0.0
+
     @property
     def total_time(self) -> float:
         return self.total_time_s
 
-    @property
-    def transfer_time(self) -> float:
-        return self.total_time_s
-
-    @property
-    def broadcast_time(self) -> float:
-        return self.total_time_s
+    @total_time.setter
+    def total_time(self, v: float):
+        self.total_time_s = float(v)
 
     @property
     def sync_count(self) -> int:
@@ -78,7 +78,9 @@ class TransferStats:
 
     @property
     def bandwidth_gbps(self) -> float:
-        return self.avg_gbps
+        """Bytes over the transfer (or broadcast) time when one was set, else over the total time."""
+        t = self.transfer_time or self.broadcast_time or self.total_time_s
+        return self.total_bytes / t / 1e9 if t > 0 else 0.0
 
 
 @dataclass

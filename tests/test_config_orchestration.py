@@ -188,9 +188,10 @@ class _FakeHttp:
     """Stand-in for the vLLM HTTP server: records calls, can fail the first N wake-ups."""
 
     def __init__(self, fail_wake=0, fail_update=False):
-        self.calls, self.fail_wake, self.fail_update = [], fail_wake, fail_update
+        self.calls, self.fail_wake, self.fail_update, self.bodies = [], fail_wake, fail_update, []
 
     async def post(self, url, **kw):
+        self.bodies.append((url, kw))
         self.calls.append(url.split("/")[-1].split("?")[0])
         if "wake_up" in url and self.fail_wake > 0:
             self.fail_wake -= 1
@@ -218,6 +219,16 @@ def test_vllm_client_retry_taxonomy_and_ipc_chunking():
     asyncio.run(ipc.push_weights(state))
     assert http.calls == ["reset_prefix_cache", "sleep", "init_weight_transfer_engine", "start_weight_update",
                           "update_weights", "update_weights", "update_weights", "finish_weight_update", "wake_up"]
+    # request shapes of the vLLM control protocol: relative paths, query parameters, JSON bodies
+    by_path = {u: kw for u, kw in http.bodies}
+    assert by_path["/sleep"] == {"params": {"level": 1}} and by_path["/wake_up"] == {}
+    assert by_path["/reset_prefix_cache"]["params"] == {"reset_running_requests": False, "reset_external": False}
+    assert by_path["/start_weight_update"] == {"json": {"is_checkpoint_format": True}}
+    assert set(by_path["/update_weights"]["json"]["update_info"]) == {"names", "shapes", "dtypes", "ipc_handles"}
+    assert by_path["/init_weight_transfer_engine"] == {"json": {"init_info": {}}} and by_path["/finish_weight_update"] == {"json": {}}
+    c2 = VLLMClient("http://x", backoff_s=0.0, client=_FakeHttp(), retry_delay=0.0)
+    assert asyncio.run(c2.wake_up(tags=["weights", "kv_cache"])) is True and asyncio.run(c2.health_check()) is True
+    assert c2._client.bodies[0] == ("/wake_up", {"params": {"tags": ["weights", "kv_cache"]}})
     # a non-retriable failure mid-transfer still wakes the server up, then re-raises
     http = _FakeHttp(fail_update=True)
     ipc = IPCWeightTransfer(VLLMClient("http://x", backoff_s=0.0, client=http), chunk_size=4)
