@@ -20,14 +20,17 @@ class ParallelContext:
     _instance: Optional["ParallelContext"] = None
 
     def __init__(self, tp_size=1, dp_size=1, pp_size=1, rank=0, world_size=1, local_rank=0,
-                 backend="gloo"):
+                 backend="gloo", tp_group=None, dp_group=None, pp_group=None):
+        """Plain construction describes one rank's coordinates; ``init_distributed`` / ``init_single_process``
+        create the process groups.  Ready-made groups may be handed in (the reference's constructor takes
+        ``tp_size, tp_group, dp_size, dp_group, pp_size, pp_group``: src/distributed/parallel_context.py:38-66)."""
         self.tp_size, self.dp_size, self.pp_size = tp_size, dp_size, pp_size
         self.global_rank, self.world_size, self.local_rank = rank, world_size, local_rank
         self.backend = backend
         self.tp_rank = rank % tp_size
         self.pp_rank = (rank // tp_size) % pp_size
         self.dp_rank = rank // (tp_size * pp_size)
-        self.tp_group = self.pp_group = self.dp_group = None
+        self.tp_group, self.pp_group, self.dp_group = tp_group, pp_group, dp_group
         self.tp_ranks: List[int] = [rank]
         self.pp_ranks: List[int] = [rank]
         self.dp_ranks: List[int] = [rank]

@@ -8,7 +8,10 @@ from ..dist.context import ParallelContext
 
 
 def split_layers_to_stages(num_layers: int, pp_size: int) -> List[Tuple[int, int]]:
-    assert pp_size >= 1 and num_layers >= pp_size, "need at least one layer per stage"
+    """``[start, end)`` per stage; the ``num_layers % pp_size`` extra layers go to the first stages.  With fewer
+    layers than stages the last stages are empty (``(n, n)``), as in the reference; the engine refuses such a
+    layout when it builds the model."""
+    assert pp_size >= 1 and num_layers >= 0
     base, extra = divmod(num_layers, pp_size)
     out, start = [], 0
     for s in range(pp_size):
@@ -19,8 +22,23 @@ def split_layers_to_stages(num_layers: int, pp_size: int) -> List[Tuple[int, int
 
 
 class PipelineParallelContext:
-    def __init__(self, num_layers: int, ctx: Optional[ParallelContext] = None, pp_size: Optional[int] = None,
-                 pp_rank: Optional[int] = None):
+    def __init__(self, *args, num_layers: Optional[int] = None, ctx: Optional[ParallelContext] = None,
+                 pp_size: Optional[int] = None, pp_rank: Optional[int] = None,
+                 parallel_context: Optional[ParallelContext] = None):
+        """``PipelineParallelContext(num_layers, ctx)`` or, in the reference's order,
+        ``PipelineParallelContext(parallel_context, num_layers)``; ``pp_size`` / ``pp_rank`` override the context's
+        (or stand in for it when there is none)."""
+        for a in args:
+            if isinstance(a, ParallelContext):
+                ctx = a
+            elif isinstance(a, int) and num_layers is None:
+                num_layers = a
+            elif isinstance(a, int) and pp_size is None:
+                pp_size = a
+            elif isinstance(a, int):
+                pp_rank = a
+        ctx = ctx if ctx is not None else parallel_context
+        assert isinstance(num_layers, int), "PipelineParallelContext needs num_layers"
         self.ctx = ctx
         self.pp_size = pp_size if pp_size is not None else (ctx.pp_size if ctx else 1)
         self.pp_rank = pp_rank if pp_rank is not None else (ctx.pp_rank if ctx else 0)

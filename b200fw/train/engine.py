@@ -158,6 +158,8 @@ class TrainEngine:
         self.model_config = mc
         layer_range, first, last = None, True, True
         if cfg.pp_size > 1:
+            if mc.num_layers < cfg.pp_size:
+                raise ValueError(f"{mc.num_layers} layers cannot fill {cfg.pp_size} pipeline stages")
             self.pp_context = PipelineParallelContext(mc.num_layers, ctx)
             layer_range = (self.pp_context.layer_start, self.pp_context.layer_end)
             first, last = self.pp_context.is_first_stage, self.pp_context.is_last_stage
