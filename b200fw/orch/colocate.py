@@ -567,7 +567,18 @@ class ColocateOrchestrator:
             self.train_engine.save_checkpoint(os.path.join(base, name))
         self._last_checkpoint_path = os.path.join(base, tag)
 
+    @property
+    def metrics_history(self) -> List[IterationMetrics]:
+        """The per-iteration records under the reference's attribute name."""
+        return self.metrics
+
+    async def _transition(self, new_state: OrchestratorState):
+        """State change as a coroutine (the reference's loop awaits its transitions)."""
+        self._set_state(new_state)
+
     def get_summary(self) -> Dict:
+        if not self.metrics:
+            return {"status": "no_data"}
         ok = [m for m in self.metrics if m.error is None]
         losses = [m.train_metrics.loss for m in ok if m.train_metrics is not None]
         stage: Dict[str, float] = {}
@@ -581,8 +592,17 @@ class ColocateOrchestrator:
                         "final_loss": losses[-1] if losses else None, "initial_loss": losses[0] if losses else None,
                         "avg_reward": sum(m.avg_reward for m in ok) / n,
                         "avg_iteration_time": sum(m.total_time for m in ok) / n,
-                        "final_weights_version": self.weights_version},
+                        "final_weights_version": self.weights_version,
+                        # the reference's key names (src/orchestrator/colocate_orchestrator.py:1808-1815)
+                        "completed_iterations": len(self.metrics),
+                        "final_accuracy": self.metrics[-1].accuracy, "final_avg_reward": self.metrics[-1].avg_reward,
+                        "best_accuracy": max(m.accuracy for m in self.metrics),
+                        "avg_iteration_time_s": sum(m.total_time for m in self.metrics) / len(self.metrics),
+                        "total_time_s": sum(m.total_time for m in self.metrics)},
             "stage_averages": {k: v / n for k, v in stage.items()},
+            "stage_avg_durations": {k: v / n for k, v in stage.items()},
+            "memory": {"peak_mb": self.memory.peak_memory_mb},
+            "metrics_summary": self.collector.get_summary(),
             "system": {"world_size": self.train_engine.parallel_ctx.world_size if self.train_engine else 1,
                        "device": torch.cuda.get_device_name(0) if torch.cuda.is_available() else "cpu",
                        "wall_time_s": time.time() - self._start_time if self._start_time else 0.0},
@@ -650,7 +670,7 @@ class ColocateOrchestrator:
         summary["artifacts"] = {n.split(".")[0]: self.artifacts.path(n) for n in names}
         summary["artifacts"]["metrics_jsonl"] = self.artifacts.path(f"metrics_rank{self.artifacts.rank}.jsonl")
         try:
-            summary["performance"].update(self._performance_block())
+            summary.setdefault("performance", {}).update(self._performance_block())
         except Exception as e:  # noqa: BLE001 - the summary is written regardless
             logger.warning("performance block not computed: %s", e)
         self.artifacts.write_json("run_summary.json", summary)

@@ -69,7 +69,7 @@ def main(argv=None):
 
     summary = asyncio.run(go())
     if rank == 0:
-        print(json.dumps(summary["results"], indent=2))
+        print(json.dumps(summary.get("results", summary), indent=2))
 
 
 if __name__ == "__main__":

@@ -117,6 +117,13 @@ def test_colocate_lora_swiftsync_and_async_pipeline_staleness():
         assert max(m.rollout_staleness for m in o.metrics) <= 1
 
 
+def test_summary_without_iterations_and_state_transition_coroutine():
+    o = ColocateOrchestrator(ColocateConfig(model_preset="tiny128"))
+    assert o.get_summary() == {"status": "no_data"} and o.state == OrchestratorState.INIT
+    asyncio.run(o._transition(OrchestratorState.TRAINING))
+    assert o.state == OrchestratorState.TRAINING and o.state_log[-1] == "training"
+
+
 def test_colocate_sft_mode_and_resume():
     with tempfile.TemporaryDirectory() as d:
         cfg = _tiny_cfg(d, training_mode="sft", inference_preview_enabled=False, total_iterations=3)
@@ -160,6 +167,10 @@ def test_eval_before_after_artifacts_and_fixed_prompt_comparison():
         assert [r["prompt"] for r in cmp_["samples"]] == [x["prompt"] for x in before["samples"]]
         assert set(cmp_["samples"][0]) >= {"before_generated", "after_generated", "before_token_f1", "after_exact_match"}
         assert s["eval"]["before"]["num_samples"] == 2 and "after" in s["eval"]
+        res = s["results"]
+        assert res["completed_iterations"] == 2 and res["total_time_s"] >= res["avg_iteration_time_s"] > 0
+        assert set(s["stage_avg_durations"]) == set(s["stage_averages"]) and "peak_mb" in s["memory"]
+        assert "timers" in s["metrics_summary"] and o.metrics_history is o.metrics
         rs = json.load(open(os.path.join(out, "run_summary.json")))
         assert rs["status"] == "completed" and rs["mode"] == "sft" and rs["run"]["output_dir"] == out
         assert rs["run"]["ended_at_unix"] >= rs["run"]["started_at_unix"] > 0
