@@ -1,7 +1,6 @@
 """Public surface: classes keep the method, property and field names of the reference project, so that code written
 against it finds them here.  The table lists names by class; a few of the adapters are exercised for behaviour."""
 import importlib
-import io
 import json
 
 import pytest
