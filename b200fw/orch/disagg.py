@@ -246,8 +246,10 @@ class DisaggOrchestrator:
                 times = times.cuda()
             dist.all_reduce(times, op=dist.ReduceOp.MAX)
             m.train_time, m.rollout_time = float(times[0]), float(times[1])
+            # pipeline mode runs the two phases side by side: the shorter one is hidden entirely; sequential mode
+            # runs them back to back, nothing overlaps
             hi = max(m.train_time, m.rollout_time)
-            m.overlap_ratio = min(m.train_time, m.rollout_time) / hi if hi > 0 else 0.0
+            m.overlap_ratio = min(m.train_time, m.rollout_time) / hi if (hi > 0 and cfg.mode == "pipeline") else 0.0
             m.avg_reward = getattr(self, "_last_reward", 0.0)
             m.weights_version = self.weights_version
             self.metrics.append(m)

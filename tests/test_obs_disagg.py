@@ -220,3 +220,5 @@ def test_disaggregated_loop_two_trainers_two_engines():
         # after the final sync every engine holds exactly the trainers' weights
         assert len({round(r["checksum"], 6) for r in res}) == 1, [r["checksum"] for r in res]
         assert res[0]["final_loss"] is not None
+        # overlap: back-to-back phases hide nothing; pipelined phases hide the shorter one
+        assert (res[0]["avg_overlap_ratio"] == 0.0) == (mode == "sequential"), (mode, res[0]["avg_overlap_ratio"])
