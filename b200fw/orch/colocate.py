@@ -104,6 +104,7 @@ class ColocateOrchestrator:
         self._batches = None
         self._pool = ThreadPoolExecutor(max_workers=1)
         self._rollout_stream = None
+        self._tp_exchange_group = None
         self._start_time = 0.0
 
     # ---- state --------------------------------------------------------------------------------------------
@@ -185,7 +186,10 @@ class ColocateOrchestrator:
             self.ipc = IPCWeightTransfer(self.vllm_client, cfg.ipc_chunk_size)
             return
         mc = eng.model_config
-        if backend == "mock" or eng.parallel_ctx.tp_size > 1 or eng.parallel_ctx.pp_size > 1:
+        # pipeline parallelism: every stage holds a slice of the layers, rollouts are not served (the reference allows
+        # PP for SFT only).  Tensor parallelism: every rank keeps a full single-GPU copy for its rollout engine (the
+        # weights fit) and the ranks of a TP group split the group's prompts between them.
+        if backend == "mock" or eng.parallel_ctx.pp_size > 1:
             ic = InferenceConfig.from_model_config(mc, inference_mode="mock", temperature=cfg.temperature, top_p=cfg.top_p)
             self.infer_engine = InferenceEngine(ic).initialize()
             return
@@ -200,7 +204,18 @@ class ColocateOrchestrator:
             auto = InferenceConfig.auto_from_device(mc.num_layers, mc.num_kv_heads, mc.head_dim, gpu_memory_fraction=0.3,
                                                     kv_cache_dtype=cfg.kv_cache_dtype)
             ic = InferenceConfig.from_model_config(mc, num_blocks=auto.num_blocks, **kw)
-        rollout_model = eng.model.clone(requires_grad=False) if cfg.lora_rank <= 0 else self._merged_clone()
+        pctx = eng.parallel_ctx
+        if pctx.tp_size > 1 and self._tp_exchange_group is None:
+            # a group of its own (gloo: plain host objects) for handing rollouts round the TP group, so that the
+            # exchange - which may run on the rollout worker thread - never interleaves with training collectives
+            import torch.distributed as dist
+            tp_groups, _, _ = pctx.group_table(pctx.world_size, pctx.tp_size, pctx.dp_size, pctx.pp_size)
+            for ranks in tp_groups:
+                g = dist.new_group(ranks, backend="gloo")
+                if pctx.global_rank in ranks:
+                    self._tp_exchange_group = g
+        plain = cfg.lora_rank <= 0 and pctx.tp_size == 1
+        rollout_model = eng.model.clone(requires_grad=False) if plain else self._merged_clone()
         self.infer_engine = InferenceEngine(ic, rollout_model).initialize()
         from ..model.hf_io import hf_named_tensors
         layout = [(k, tuple(v.shape)) for k, v in hf_named_tensors(rollout_model)]
@@ -209,19 +224,16 @@ class ColocateOrchestrator:
             self._rollout_stream = torch.cuda.Stream()
 
     def _merged_clone(self):
-        """Plain (adapter-free) copy of the policy with the LoRA branch merged in."""
-        from ..model import ParallelTransformerModel, merge_lora_weights
+        """Plain single-GPU copy of the policy: adapters merged in, tensor-parallel shards gathered (every rank of
+        the TP group takes part in the gather), ZeRO-3 shards collected."""
+        from ..model import ParallelTransformerModel
+        from ..model.hf_io import hf_named_tensors
         eng = self.train_engine
         m = ParallelTransformerModel(eng.model_config, dtype=eng.dtype, device=eng.device)
-        from ..model.hf_io import hf_named_tensors
-        merge_lora_weights(eng.model)
-        try:
-            src = dict(hf_named_tensors(eng.model))
-            with torch.no_grad():
-                for k, v in hf_named_tensors(m):
-                    v.copy_(src[k])
-        finally:
-            merge_lora_weights(eng.model, unmerge=True)
+        src = eng.export_weights()
+        with torch.no_grad():
+            for k, v in hf_named_tensors(m):
+                v.copy_(src[k])
         for p in m.parameters():
             p.requires_grad_(False)
         return m
@@ -243,13 +255,26 @@ class ColocateOrchestrator:
         K = cfg.num_samples_per_prompt
         prompts = [p for p in batch.prompt_tokens for _ in range(K)]
         version = self.weights_version
+        ctx = self.train_engine.parallel_ctx
+        share = ctx.tp_size > 1 and self.infer_engine.config.inference_mode != "mock"
+        mine = list(range(ctx.tp_rank, len(prompts), ctx.tp_size)) if share else list(range(len(prompts)))
+        local = [prompts[i] for i in mine]
         if self._rollout_stream is not None:
             self._rollout_stream.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(self._rollout_stream):
-                outs, lps = self.infer_engine.generate(prompts, cfg.max_tokens, cfg.temperature, cfg.top_p, return_logprobs=True)
+                outs, lps = self.infer_engine.generate(local, cfg.max_tokens, cfg.temperature, cfg.top_p, return_logprobs=True)
             self._rollout_stream.synchronize()
         else:
-            outs, lps = self.infer_engine.generate(prompts, cfg.max_tokens, cfg.temperature, cfg.top_p, return_logprobs=True)
+            outs, lps = self.infer_engine.generate(local, cfg.max_tokens, cfg.temperature, cfg.top_p, return_logprobs=True)
+        if share:
+            # the ranks of a TP group train on the same batch: exchange the token ids each one generated
+            import torch.distributed as dist
+            parts = [None] * ctx.tp_size
+            dist.all_gather_object(parts, (mine, outs, lps), group=self._tp_exchange_group)
+            outs, lps = [None] * len(prompts), [None] * len(prompts)
+            for idx, o, l in parts:
+                for j, i in enumerate(idx):
+                    outs[i], lps[i] = o[j], (l[j] if l is not None else None)
         outs = [o if o else [0] for o in outs]
         responses = [outs[i * K:(i + 1) * K] for i in range(len(batch.prompt_tokens))]
         seq_lp = [sum(l) / max(1, len(l)) if l else 0.0 for l in lps] if lps and lps[0] is not None else None

@@ -117,6 +117,33 @@ def test_colocate_lora_swiftsync_and_async_pipeline_staleness():
         assert max(m.rollout_staleness for m in o.metrics) <= 1
 
 
+def _tp_colocate_worker(rank, world, tmp, async_pipeline):
+    cfg = _tiny_cfg(os.path.join(tmp, f"r{rank}"), tp_size=world, total_iterations=2, batch_size=2, num_samples_per_prompt=2,
+                    sequence_parallel=True, checkpoint_save_enabled=False, async_pipeline_enabled=async_pipeline,
+                    async_pipeline_max_staleness=1)
+    o, s = _run(cfg)
+    eng = o.infer_engine
+    from b200fw.model.hf_io import hf_named_tensors
+    full = {k: v.clone() for k, v in o.train_engine.export_weights().items()}
+    mine = dict(hf_named_tensors(eng.model))
+    same = all(torch.equal(full[k], mine[k]) for k in full)
+    ro = o._rollout(o._next_batch())
+    return (eng.config.inference_mode, eng.model.tp_size, same, ro.responses, s["results"]["completed_iterations"],
+            [m.error for m in o.metrics], eng.stats["decode_tokens"] + eng.stats["prefill_tokens"])
+
+
+def test_tensor_parallel_grpo_uses_native_rollouts_shared_over_the_tp_group():
+    """TP 2: every rank serves rollouts from a full single-GPU copy of the policy (not the mock engine), the two
+    ranks split the prompts and end up with the same responses; the copy tracks the trained weights."""
+    from _dist_util import run_ranks
+    for async_pipeline in (False, True):
+        with tempfile.TemporaryDirectory() as d:
+            res = run_ranks(_tp_colocate_worker, 2, d, async_pipeline, timeout=600)
+        for mode, tp, same, responses, done, errors, work in res:
+            assert mode == "kv_cache" and tp == 1 and same and done == 2 and errors == [None, None] and work > 0
+        assert res[0][3] == res[1][3] and len(res[0][3]) == 2 and len(res[0][3][0]) == 2     # identical [B][K] token lists
+
+
 def test_summary_without_iterations_and_state_transition_coroutine():
     o = ColocateOrchestrator(ColocateConfig(model_preset="tiny128"))
     assert o.get_summary() == {"status": "no_data"} and o.state == OrchestratorState.INIT
