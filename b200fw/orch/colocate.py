@@ -105,6 +105,7 @@ class ColocateOrchestrator:
         self._pool = ThreadPoolExecutor(max_workers=1)
         self._rollout_stream = None
         self._tp_exchange_group = None
+        self.ipc = None
         self._start_time = 0.0
 
     # ---- state --------------------------------------------------------------------------------------------
@@ -178,12 +179,14 @@ class ColocateOrchestrator:
     async def _init_inference(self):
         cfg, eng = self.config, self.train_engine
         backend = cfg.inference_backend
-        if self.infer_engine is not None or backend == "vllm" and self.vllm_client is not None:
+        if self.infer_engine is not None:
             return
         if backend == "vllm":
             from ..sync import IPCWeightTransfer, VLLMClient
-            self.vllm_client = VLLMClient(cfg.vllm_url, max_retries=cfg.max_retries, backoff_s=cfg.retry_delay)
-            self.ipc = IPCWeightTransfer(self.vllm_client, cfg.ipc_chunk_size)
+            if self.vllm_client is None:
+                self.vllm_client = VLLMClient(cfg.vllm_url, max_retries=cfg.max_retries, backoff_s=cfg.retry_delay)
+            if self.ipc is None:
+                self.ipc = IPCWeightTransfer(self.vllm_client, cfg.ipc_chunk_size)
             return
         mc = eng.model_config
         # pipeline parallelism: every stage holds a slice of the layers, rollouts are not served (the reference allows
@@ -279,6 +282,23 @@ class ColocateOrchestrator:
         responses = [outs[i * K:(i + 1) * K] for i in range(len(batch.prompt_tokens))]
         seq_lp = [sum(l) / max(1, len(l)) if l else 0.0 for l in lps] if lps and lps[0] is not None else None
         return _Rollout(batch, responses, seq_lp, version, time.perf_counter() - t0)
+
+    async def _rollout_vllm(self, batch: GRPOBatch) -> _Rollout:
+        """Rollouts from a vLLM server: K text completions per prompt over HTTP, tokenised for the trainer.  The
+        server reports no per-token log-probabilities here, so IcePop recomputes the rollout policy's on the trainer."""
+        cfg, t0 = self.config, time.perf_counter()
+        tok = self.data.tokenizer
+        version = self.weights_version
+        responses = []
+        for prompt in batch.prompts:
+            texts = await self.vllm_client.completions(prompt, cfg.num_samples_per_prompt, cfg.max_tokens, cfg.temperature,
+                                                       cfg.top_p, cfg.model_path or None)
+            texts = (texts + [""] * cfg.num_samples_per_prompt)[:cfg.num_samples_per_prompt]
+            responses.append([list(tok.encode(t)) or [getattr(tok, "eos_token_id", 0) or 0] for t in texts])
+        return _Rollout(batch, responses, None, version, time.perf_counter() - t0)
+
+    def _uses_vllm(self) -> bool:
+        return self.vllm_client is not None and self.infer_engine is None
 
     def _rewards(self, ro: _Rollout) -> List[List[float]]:
         if isinstance(self.reward_fn, SyntheticTokenReward):
@@ -380,7 +400,8 @@ class ColocateOrchestrator:
                             logger.info("dropping a rollout that is %d versions stale", stale)
                             ro = None
                     if ro is None:
-                        ro = self._rollout(self._next_batch())
+                        nb = self._next_batch()
+                        ro = await self._rollout_vllm(nb) if self._uses_vllm() else self._rollout(nb)
                     im.rollout_staleness = self.weights_version - ro.weights_version
                     im.state_durations["inferring"] = time.perf_counter() - t0
                     im.tokens_generated = sum(len(r) for g in ro.responses for r in g)
@@ -397,7 +418,8 @@ class ColocateOrchestrator:
                     t0 = time.perf_counter()
                     if cfg.async_pipeline_enabled and it + 1 < cfg.total_iterations:
                         nxt = self._next_batch()
-                        pending = loop.run_in_executor(self._pool, self._rollout, nxt)
+                        pending = (asyncio.ensure_future(self._rollout_vllm(nxt)) if self._uses_vllm()
+                                   else loop.run_in_executor(self._pool, self._rollout, nxt))
                     im.train_metrics = self._train_grpo(ro, rewards)
                     im.tokens_trained = sum(len(p) + len(r) for p, g in zip(ro.batch.prompt_tokens, ro.responses) for r in g)
                     im.state_durations["training"] = time.perf_counter() - t0

@@ -113,6 +113,16 @@ class VLLMClient:
         await self._request("POST", "/wake_up", params={"tags": list(tags)} if tags else None)
         return True
 
+    async def completions(self, prompt: str, n: int = 1, max_tokens: int = 512, temperature: float = 0.7,
+                          top_p: float = 0.95, model: Optional[str] = None) -> List[str]:
+        """``n`` sampled continuations of ``prompt`` through the server's OpenAI-style ``/v1/completions`` endpoint
+        (the rollout call of the reference's vLLM backend: src/orchestrator/colocate_orchestrator.py:1406-1433)."""
+        body = {"prompt": prompt, "n": n, "max_tokens": max_tokens, "temperature": temperature, "top_p": top_p}
+        if model:
+            body["model"] = model
+        resp = await self._request("POST", "/v1/completions", json=body)
+        return [c["text"] for c in resp.json()["choices"]]
+
     async def init_weight_transfer(self, init_info: Optional[Dict] = None) -> bool:
         await self._request("POST", "/init_weight_transfer_engine", json={"init_info": init_info or {}})
         return True

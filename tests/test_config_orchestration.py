@@ -218,8 +218,14 @@ def test_eval_before_after_artifacts_and_fixed_prompt_comparison():
 
 
 class _FakeResp:
+    def __init__(self, payload=None):
+        self.payload, self.status_code = payload or {}, 200
+
     def raise_for_status(self):
         pass
+
+    def json(self):
+        return self.payload
 
 
 class _FakeHttp:
@@ -236,6 +242,9 @@ class _FakeHttp:
             raise ConnectionError("server busy")
         if "update_weights" in url and self.fail_update:
             raise ValueError("bad payload")
+        if url.endswith("/v1/completions"):
+            body = kw["json"]
+            return _FakeResp({"choices": [{"text": f"Step 1: think\n#### {7 + i}"} for i in range(body["n"])]})
         return _FakeResp()
 
     async def get(self, url, **kw):
@@ -274,6 +283,26 @@ def test_vllm_client_retry_taxonomy_and_ipc_chunking():
         asyncio.run(ipc.push_weights(state))
     assert http.calls[-1] == "wake_up" and ipc.stats.failures == 1
     assert len(IPCWeightTransfer.checksum(state)) == 32
+
+
+def test_colocate_grpo_with_a_vllm_server_for_rollouts_and_ipc_weight_push():
+    """inference_backend "vllm": completions over HTTP (K per prompt), rule reward on the text, training on the
+    re-tokenised responses, then sleep -> weight push in chunks -> wake."""
+    from b200fw.data.pipeline import GSM8KDataPipeline
+    recs = [{"question": f"{i} plus 7?", "answer": f"#### {7 + (i % 2)}"} for i in range(8)]
+    http = _FakeHttp()
+    with tempfile.TemporaryDirectory() as d:
+        cfg = _tiny_cfg(d, inference_backend="vllm", synthetic_data=False, total_iterations=2, batch_size=2,
+                        num_samples_per_prompt=2, checkpoint_save_enabled=False, max_seq_len=128)
+        o, s = _run(cfg, data=GSM8KDataPipeline(records=recs, prompt_template="plain"),
+                    vllm_client=VLLMClient("http://x", backoff_s=0.0, client=http))
+    assert o.infer_engine is None and s["results"]["completed_iterations"] == 2 and s["results"]["failed_iterations"] == 0
+    comps = [kw["json"] for u, kw in http.bodies if u == "/v1/completions"]
+    assert len(comps) == 4 and all(c["n"] == 2 and c["max_tokens"] == cfg.max_tokens and "plus 7?" in c["prompt"] for c in comps)
+    assert http.calls.count("sleep") == 2 and http.calls.count("update_weights") >= 2 and http.calls.count("wake_up") >= 2
+    # responses "#### 7" / "#### 8" against answers 7 / 8: some right (+1), the rest well formed but wrong (-0.5)
+    assert {m.avg_reward for m in o.metrics} <= {1.0, 0.25, -0.5} and all(m.train_metrics is not None for m in o.metrics)
+    assert all(m.tokens_generated > 0 for m in o.metrics) and o.weights_version == 2
 
 
 def test_weight_update_manager_rolls_back():
