@@ -217,8 +217,9 @@ class ColocateOrchestrator:
                 g = dist.new_group(ranks, backend="gloo")
                 if pctx.global_rank in ranks:
                     self._tp_exchange_group = g
-        plain = cfg.lora_rank <= 0 and pctx.tp_size == 1
-        rollout_model = eng.model.clone(requires_grad=False) if plain else self._merged_clone()
+        # one path for every layout: export (adapters merged, TP shards gathered, ZeRO-3 shards collected) into a
+        # fresh single-GPU model
+        rollout_model = self._merged_clone()
         self.infer_engine = InferenceEngine(ic, rollout_model).initialize()
         from ..model.hf_io import hf_named_tensors
         layout = [(k, tuple(v.shape)) for k, v in hf_named_tensors(rollout_model)]

@@ -144,6 +144,28 @@ def test_tensor_parallel_grpo_uses_native_rollouts_shared_over_the_tp_group():
         assert res[0][3] == res[1][3] and len(res[0][3]) == 2 and len(res[0][3][0]) == 2     # identical [B][K] token lists
 
 
+def _dp_colocate_worker(rank, world, tmp, stage):
+    cfg = _tiny_cfg(os.path.join(tmp, f"r{rank}"), dp_size=world, zero_stage=stage, total_iterations=2, batch_size=4,
+                    num_samples_per_prompt=2, checkpoint_save_enabled=False)
+    o, s = _run(cfg)
+    from b200fw.model.hf_io import hf_named_tensors
+    want = o.train_engine.export_weights()
+    got = dict(hf_named_tensors(o.infer_engine.model))
+    return (s["results"]["failed_iterations"], all(torch.equal(want[k], got[k]) for k in want),
+            float(sum(v.double().sum() for v in want.values())), [b.prompt_indices for b in [o._next_batch()]])
+
+
+def test_colocate_data_parallel_with_sharded_optimizer_states_and_parameters():
+    """DP 2 with ZeRO-2 and ZeRO-3 (parameters released between steps): the rollout copy is built from the gathered
+    weights, follows the trainer, the ranks stay in step and draw different prompts."""
+    from _dist_util import run_ranks
+    for stage in (2, 3):
+        with tempfile.TemporaryDirectory() as d:
+            res = run_ranks(_dp_colocate_worker, 2, d, stage, timeout=600)
+        assert [r[0] for r in res] == [0, 0] and all(r[1] for r in res), stage
+        assert res[0][2] == res[1][2] and res[0][3] != res[1][3], stage
+
+
 def test_summary_without_iterations_and_state_transition_coroutine():
     o = ColocateOrchestrator(ColocateConfig(model_preset="tiny128"))
     assert o.get_summary() == {"status": "no_data"} and o.state == OrchestratorState.INIT
