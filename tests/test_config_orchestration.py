@@ -227,7 +227,9 @@ def test_eval_before_after_artifacts_and_fixed_prompt_comparison():
         perf = rs["performance"]
         assert perf["world_size"] == 1 and perf["global_batch_size"] == cfg.batch_size and perf["avg_step_time_s"] > 0
         assert perf["tokens_per_second"] > 0 and perf["model_arch"]["vocab_size"] == 8192
-        assert 0 < perf["mfu_percent"] < 100 and perf["primary_metric"] == "mfu" and perf["model_params"] > 0
+        # a tiny model on a CPU is a vanishing fraction of the B200 peak: the rounded percentage may be 0.00
+        assert 0 <= perf["mfu_percent"] < 100 and perf["per_gpu_training_flops"] > 0 and perf["actual_tflops_per_gpu"] >= 0
+        assert perf["primary_metric"] == "mfu" and perf["model_params"] > 0
         from b200fw.obs import read_scalars
         tags = read_scalars(os.path.join(out, "tensorboard"))
         assert "eval/before_loss" in tags and "eval/after_token_f1" in tags and "train/loss" in tags
