@@ -39,6 +39,8 @@ def parse_args(argv=None):
     ap.add_argument("--resume-from", type=str, default=None)
     ap.add_argument("--output-dir", type=str, default=None)
     ap.add_argument("--synthetic", action="store_true", default=None, help="seeded random-token data + rule reward")
+    ap.add_argument("--no-synthetic", dest="synthetic", action="store_false",
+                    help="read data.dataset_name (a local JSON / JSONL file or save_to_disk directory) even if the YAML says synthetic")
     ap.add_argument("--log-file", type=str, default=None)
     return ap.parse_args(argv)
 
