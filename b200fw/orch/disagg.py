@@ -142,8 +142,28 @@ class DisaggOrchestrator:
         else:
             self.infer_engine = self.infer_engine_factory(self.rank - cfg.num_train_gpus)
         from ..sync import WeightTransferManager
+        want_peer = cfg.transfer_backend == "peer_write"
+        if want_peer and not torch.cuda.is_available():
+            logger.warning("transfer_backend=peer_write needs CUDA peer memory; using the collective broadcast")
+            want_peer = False
+        # every trainer rank takes part in the export (TP / ZeRO-3 gathers); rank 0 needs the tensor layout
+        layout_state = self.train_engine.export_weights() if (want_peer and self.is_trainer) else None
         if self.rank == 0 or not self.is_trainer:
-            self.transfer = WeightTransferManager("nccl", self.sync_group, src_rank=0)
+            if want_peer:
+                # cast + checksum kernel writes straight into every engine's staging buffer over NVLink; the buffers
+                # are symmetric memory of the (trainer leader + engines) group, so all its members build it together
+                from ..model.hf_io import hf_named_tensors
+                from ..sync import PeerWeightSync
+                if self.is_trainer:
+                    layout = [(k, tuple(v.shape)) for k, v in layout_state.items()]
+                    dtype = next(iter(layout_state.values())).dtype
+                else:
+                    layout = [(k, tuple(v.shape)) for k, v in hf_named_tensors(self.infer_engine.model)]
+                    dtype = next(self.infer_engine.model.parameters()).dtype
+                peer = PeerWeightSync(layout, dtype, group=self.sync_group, sender_rank=0)
+                self.transfer = WeightTransferManager("peer_write", peer_sync=peer)
+            else:
+                self.transfer = WeightTransferManager("nccl", self.sync_group, src_rank=0)
         if self.reward_fn is None:
             from ..reward import SyntheticTokenReward
             vocab = (self.train_engine.model_config.vocab_size if self.is_trainer else self.infer_engine.config.vocab_size)

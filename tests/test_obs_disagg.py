@@ -182,7 +182,9 @@ def _disagg_worker(rank, world, mode):
     mc = ModelConfig(vocab_size=128, hidden_size=32, num_layers=2, num_heads=2, num_kv_heads=2, head_dim=16,
                      intermediate_size=48, max_position_embeddings=128, tie_word_embeddings=True)
     cfg = DisaggConfig(num_train_gpus=2, num_infer_gpus=2, total_iterations=2, batch_size=4, num_samples_per_prompt=2,
-                       prompt_len=8, max_tokens=5, mode=mode, kv_num_blocks=64)
+                       prompt_len=8, max_tokens=5, mode=mode, kv_num_blocks=64,
+                       # without CUDA peer memory the peer-write request falls back to the collective broadcast
+                       transfer_backend="peer_write" if mode == "sequential" else "nccl")
 
     def trainer(group, n, r):
         ctx = ParallelContext(1, n, 1, r, n, r, "gloo")
