@@ -110,10 +110,16 @@ class DisaggIterationMetrics:
         return self.weights_version
 
 
+class _PromptBatch(list):
+    """Prompt token lists of one iteration with their ground truths attached."""
+    truths: Optional[List] = None
+
+
 class DisaggOrchestrator:
     """Run the same object on every rank of the world; the rank decides its role."""
 
-    def __init__(self, config: DisaggConfig, train_engine_factory=None, infer_engine_factory=None, reward_fn=None):
+    def __init__(self, config: DisaggConfig, train_engine_factory=None, infer_engine_factory=None, reward_fn=None,
+                 data=None):
         self.config = config
         self.rank = dist.get_rank() if dist.is_initialized() else 0
         self.world = dist.get_world_size() if dist.is_initialized() else 1
@@ -123,6 +129,7 @@ class DisaggOrchestrator:
         self.train_group = self.infer_group = None
         self.train_engine_factory, self.infer_engine_factory = train_engine_factory, infer_engine_factory
         self.reward_fn = reward_fn
+        self.data, self._batches = data, None       # optional GSM8KDataPipeline-style source (dp_rank 0 of 1 everywhere)
         self.metrics: List[DisaggIterationMetrics] = []
         self.weights_version = 0
         self.transfer = None
@@ -164,6 +171,9 @@ class DisaggOrchestrator:
                 self.transfer = WeightTransferManager("peer_write", peer_sync=peer)
             else:
                 self.transfer = WeightTransferManager("nccl", self.sync_group, src_rank=0)
+        if self.reward_fn is None and self.data is not None:
+            from ..reward import GSM8KRewardFunction
+            self.reward_fn = GSM8KRewardFunction()
         if self.reward_fn is None:
             from ..reward import SyntheticTokenReward
             vocab = (self.train_engine.model_config.vocab_size if self.is_trainer else self.infer_engine.config.vocab_size)
@@ -172,7 +182,20 @@ class DisaggOrchestrator:
 
     # ---- phases ------------------------------------------------------------------------------------------------
     def _prompts(self, iteration: int) -> List[List[int]]:
-        """Seeded prompts, identical on every rank (no data transfer needed for them)."""
+        """This iteration's prompts, identical on every rank (no transfer needed for them): the next batch of the
+        data pipeline when one was given (every rank reads the same un-sharded pipeline; the ground truths ride
+        along on the returned list for the reward), else seeded random tokens."""
+        if self.data is not None:
+            if self._batches is None:
+                self._batches = self.data.get_batches(self.config.batch_size)
+            try:
+                b = next(self._batches)
+            except StopIteration:
+                self._batches = self.data.get_batches(self.config.batch_size)
+                b = next(self._batches)
+            out = _PromptBatch(b.prompt_tokens)
+            out.truths = list(b.ground_truths)
+            return out
         import random
         rng = random.Random(self.config.seed * 7919 + iteration)
         vocab = (self.train_engine.model_config.vocab_size if self.is_trainer else self.infer_engine.config.vocab_size)
@@ -202,7 +225,13 @@ class DisaggOrchestrator:
         mine = list(range(self.rank, len(prompts), n_tr))
         P = [prompts[j] for j in mine]
         R = [samples[j] for j in mine]
-        rewards = self.reward_fn(R, mine)
+        truths = getattr(prompts, "truths", None)
+        if truths is not None:      # text rule reward: decode the sampled ids, score against the ground truths
+            tok = self.data.tokenizer
+            rewards = self.reward_fn([[tok.decode(r, skip_special_tokens=True) for r in g] for g in R],
+                                     [truths[j] for j in mine])
+        else:
+            rewards = self.reward_fn(R, mine)
         eng = self.train_engine
         if cfg.c3po_plus_enabled:
             from ..train.c3po import C3POConfig, C3POPlusScheduler

@@ -48,6 +48,9 @@ def parse_args(argv=None):
     ap.add_argument("--kv-cache-dtype", choices=["fp16", "fp8"], default="fp16")
     ap.add_argument("--backend", default=None)
     ap.add_argument("--log-file", default=None)
+    ap.add_argument("--dataset", default=None, help="local JSON / JSONL file or save_to_disk directory with question / "
+                                                    "answer fields (default: seeded random-token prompts + token-rule reward)")
+    ap.add_argument("--prompt-template", default="qwen3_math")
     return ap.parse_args(argv)
 
 
@@ -97,7 +100,12 @@ def main(argv=None):
                                                max_prefill_tokens=4096, seed=i)
         return InferenceEngine(ic, model).initialize()
 
-    orch = DisaggOrchestrator(cfg, make_trainer, make_engine).initialize()
+    data = None
+    if a.dataset:
+        from b200fw.data import GSM8KDataPipeline
+        data = GSM8KDataPipeline(tokenizer_name=a.model_path or None, dataset_name=a.dataset,
+                                 prompt_template=a.prompt_template, max_prompt_tokens=a.prompt_len)
+    orch = DisaggOrchestrator(cfg, make_trainer, make_engine, data=data).initialize()
     orch.run()
     summaries = [None] * world
     dist.all_gather_object(summaries, orch.get_summary())

@@ -179,7 +179,9 @@ def _disagg_worker(rank, world, mode):
     from b200fw.orch import DisaggConfig, DisaggOrchestrator
     from b200fw.train import TrainConfig, TrainEngine
     dist.init_process_group("gloo", rank=rank, world_size=world)
-    mc = ModelConfig(vocab_size=128, hidden_size=32, num_layers=2, num_heads=2, num_kv_heads=2, head_dim=16,
+    use_data = mode.endswith("+data")
+    mode = mode.split("+")[0]
+    mc = ModelConfig(vocab_size=320 if use_data else 128, hidden_size=32, num_layers=2, num_heads=2, num_kv_heads=2, head_dim=16,
                      intermediate_size=48, max_position_embeddings=128, tie_word_embeddings=True)
     cfg = DisaggConfig(num_train_gpus=2, num_infer_gpus=2, total_iterations=2, batch_size=4, num_samples_per_prompt=2,
                        prompt_len=8, max_tokens=5, mode=mode, kv_num_blocks=64,
@@ -200,9 +202,17 @@ def _disagg_worker(rank, world, mode):
         ic = InferenceConfig.from_model_config(mc, num_blocks=64, inference_mode="kv_cache", seed=i, eos_token_id=None)
         return InferenceEngine(ic, m).initialize()
 
-    o = DisaggOrchestrator(cfg, trainer, engine).initialize()
+    data = None
+    if use_data:        # text prompts with ground truths: every rank reads the same un-sharded pipeline
+        from b200fw.data.pipeline import GSM8KDataPipeline
+        recs = [{"question": f"{i}+1?", "answer": f"#### {i + 1}"} for i in range(16)]
+        data = GSM8KDataPipeline(records=recs, prompt_template="plain", max_prompt_tokens=8)
+    o = DisaggOrchestrator(cfg, trainer, engine, data=data).initialize()
     o.run()
     s = o.get_summary()
+    if use_data:
+        s["reward_fn"] = type(o.reward_fn).__name__
+        s["reward_total"] = o.reward_fn.total
     if not o.is_trainer:
         from b200fw.model.hf_io import hf_named_tensors
         s["checksum"] = float(sum(v.double().sum() for _, v in hf_named_tensors(o.infer_engine.model)))
@@ -211,6 +221,16 @@ def _disagg_worker(rank, world, mode):
             from b200fw.model.hf_io import hf_named_tensors
             s["checksum"] = float(sum(v.double().sum() for _, v in hf_named_tensors(o.train_engine.model)))
     return s
+
+
+def test_disaggregated_loop_with_a_text_dataset_and_the_rule_reward():
+    from _dist_util import run_ranks
+    res = run_ranks(_disagg_worker, 4, "pipeline+data", timeout=600)
+    assert all(r["weights_version"] == r["iterations"] for r in res)
+    assert len({round(r["checksum"], 6) for r in res}) == 1
+    assert all(r["reward_fn"] == "GSM8KRewardFunction" for r in res)
+    # each trainer scored its half of 2 iterations x 4 prompts x 2 samples; rollout ranks score nothing
+    assert [r["reward_total"] for r in res] == [8, 8, 0, 0]
 
 
 def test_disaggregated_loop_two_trainers_two_engines():
