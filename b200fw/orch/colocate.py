@@ -187,6 +187,7 @@ class ColocateOrchestrator:
                 self.vllm_client = VLLMClient(cfg.vllm_url, max_retries=cfg.max_retries, backoff_s=cfg.retry_delay)
             if self.ipc is None:
                 self.ipc = IPCWeightTransfer(self.vllm_client, cfg.ipc_chunk_size)
+            self._ensure_tp_exchange_group()
             return
         mc = eng.model_config
         # pipeline parallelism: every stage holds a slice of the layers, rollouts are not served (the reference allows
@@ -208,15 +209,7 @@ class ColocateOrchestrator:
                                                     kv_cache_dtype=cfg.kv_cache_dtype)
             ic = InferenceConfig.from_model_config(mc, num_blocks=auto.num_blocks, **kw)
         pctx = eng.parallel_ctx
-        if pctx.tp_size > 1 and self._tp_exchange_group is None:
-            # a group of its own (gloo: plain host objects) for handing rollouts round the TP group, so that the
-            # exchange - which may run on the rollout worker thread - never interleaves with training collectives
-            import torch.distributed as dist
-            tp_groups, _, _ = pctx.group_table(pctx.world_size, pctx.tp_size, pctx.dp_size, pctx.pp_size)
-            for ranks in tp_groups:
-                g = dist.new_group(ranks, backend="gloo")
-                if pctx.global_rank in ranks:
-                    self._tp_exchange_group = g
+        self._ensure_tp_exchange_group()
         # one path for every layout: export (adapters merged, TP shards gathered, ZeRO-3 shards collected) into a
         # fresh single-GPU model
         rollout_model = self._merged_clone()
@@ -226,6 +219,19 @@ class ColocateOrchestrator:
         self.weight_sync = PeerWeightSync(layout, next(rollout_model.parameters()).dtype, eng.device)
         if torch.cuda.is_available():
             self._rollout_stream = torch.cuda.Stream()
+
+    def _ensure_tp_exchange_group(self):
+        """A group of its own (gloo: plain host objects) for handing rollouts round the TP group, so that the
+        exchange - which may run on the rollout worker thread - never interleaves with training collectives."""
+        pctx = self.train_engine.parallel_ctx
+        if pctx.tp_size <= 1 or self._tp_exchange_group is not None:
+            return
+        import torch.distributed as dist
+        tp_groups, _, _ = pctx.group_table(pctx.world_size, pctx.tp_size, pctx.dp_size, pctx.pp_size)
+        for ranks in tp_groups:
+            g = dist.new_group(ranks, backend="gloo")
+            if pctx.global_rank in ranks:
+                self._tp_exchange_group = g
 
     def _merged_clone(self):
         """Plain single-GPU copy of the policy: adapters merged in, tensor-parallel shards gathered (every rank of
@@ -291,11 +297,18 @@ class ColocateOrchestrator:
         tok = self.data.tokenizer
         version = self.weights_version
         responses = []
-        for prompt in batch.prompts:
-            texts = await self.vllm_client.completions(prompt, cfg.num_samples_per_prompt, cfg.max_tokens, cfg.temperature,
-                                                       cfg.top_p, cfg.model_path or None)
-            texts = (texts + [""] * cfg.num_samples_per_prompt)[:cfg.num_samples_per_prompt]
-            responses.append([list(tok.encode(t)) or [getattr(tok, "eos_token_id", 0) or 0] for t in texts])
+        pctx = self.train_engine.parallel_ctx
+        if pctx.tp_rank == 0:       # one query per TP group; its other ranks receive the answers below
+            for prompt in batch.prompts:
+                texts = await self.vllm_client.completions(prompt, cfg.num_samples_per_prompt, cfg.max_tokens,
+                                                           cfg.temperature, cfg.top_p, cfg.model_path or None)
+                texts = (texts + [""] * cfg.num_samples_per_prompt)[:cfg.num_samples_per_prompt]
+                responses.append([list(tok.encode(t)) or [getattr(tok, "eos_token_id", 0) or 0] for t in texts])
+        if pctx.tp_size > 1:
+            import torch.distributed as dist
+            box = [responses]
+            dist.broadcast_object_list(box, src=pctx.tp_ranks[0], group=self._tp_exchange_group)
+            responses = box[0]
         return _Rollout(batch, responses, None, version, time.perf_counter() - t0)
 
     def _uses_vllm(self) -> bool:

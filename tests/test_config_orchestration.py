@@ -329,6 +329,27 @@ def test_colocate_grpo_with_a_vllm_server_for_rollouts_and_ipc_weight_push():
     assert all(m.tokens_generated > 0 for m in o.metrics) and o.weights_version == 2
 
 
+def _tp_vllm_worker(rank, world, tmp):
+    from b200fw.data.pipeline import GSM8KDataPipeline
+    recs = [{"question": f"{i} plus 7?", "answer": f"#### {7 + (i % 2)}"} for i in range(8)]
+    http = _FakeHttp()
+    cfg = _tiny_cfg(os.path.join(tmp, f"r{rank}"), inference_backend="vllm", synthetic_data=False, total_iterations=1,
+                    batch_size=2, num_samples_per_prompt=2, checkpoint_save_enabled=False, max_seq_len=128, tp_size=world,
+                    sequence_parallel=True)
+    o, s = _run(cfg, data=GSM8KDataPipeline(records=recs, prompt_template="plain"),
+                vllm_client=VLLMClient("http://x", backoff_s=0.0, client=http))
+    return (http.calls.count("completions"), s["results"]["failed_iterations"], o.metrics[0].avg_reward,
+            o.metrics[0].train_metrics.loss)
+
+
+def test_vllm_rollouts_are_queried_once_per_tensor_parallel_group():
+    from _dist_util import run_ranks
+    with tempfile.TemporaryDirectory() as d:
+        res = run_ranks(_tp_vllm_worker, 2, d, timeout=600)
+    assert [r[0] for r in res] == [2, 0] and [r[1] for r in res] == [0, 0]      # rank 0 asked, rank 1 received
+    assert res[0][2] == res[1][2] and abs(res[0][3] - res[1][3]) < 1e-6         # same rewards, same loss
+
+
 def test_weight_update_manager_rolls_back():
     m = torch.nn.Linear(4, 4)
     mgr = WeightUpdateManager(m)
