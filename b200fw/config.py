@@ -94,6 +94,7 @@ class ColocateConfig:
     enable_profiling: bool = False
     profile_interval: int = 10
     enable_comm_overlap: bool = False
+    deterministic: bool = False            # fixed seeds, deterministic torch algorithms, no split-K atomics in the GEMM
     icepop_enabled: bool = False
     icepop_divergence_threshold: float = 0.5
     icepop_max_mask_ratio: float = 0.5
@@ -128,7 +129,7 @@ _YAML_MAP: List[Tuple[str, str]] = [
     ("model.use_gradient_checkpoint", "use_gradient_checkpoint"),
     ("runtime.tp_size", "tp_size"), ("runtime.dp_size", "dp_size"), ("runtime.precision", "amp_dtype"),
     ("runtime.inference_backend", "inference_backend"), ("runtime.enable_comm_overlap", "enable_comm_overlap"),
-    ("runtime.sequence_parallel", "sequence_parallel"), ("runtime.seed", "seed"),
+    ("runtime.sequence_parallel", "sequence_parallel"), ("runtime.seed", "seed"), ("runtime.deterministic", "deterministic"),
     ("distributed.pp_size", "pp_size"), ("distributed.num_micro_batches", "num_micro_batches"),
     ("distributed.zero_stage", "zero_stage"),
     ("training.mode", "training_mode"), ("training.total_iterations", "total_iterations"),
@@ -167,7 +168,7 @@ _YAML_MAP: List[Tuple[str, str]] = [
     ("inference.enable_cuda_graph", "enable_cuda_graph"), ("inference.use_radix_cache", "use_radix_cache"),
 ]
 # keys present in the reference's YAML files that no code reads; accepted silently
-_DOCUMENTATION_ONLY = {"lora.dropout", "lora.enabled", "runtime.deterministic", "experiment.name",
+_DOCUMENTATION_ONLY = {"lora.dropout", "lora.enabled", "experiment.name",
                        "experiment.seed", "profiling.memory", "profiling.comm", "profiling.compute"}
 
 
@@ -232,3 +233,33 @@ def validate_parallel_config(cfg: ColocateConfig, world_size: Optional[int] = No
 
 def config_snapshot(cfg) -> Dict[str, Any]:
     return {f.name: getattr(cfg, f.name) for f in fields(cfg)}
+
+
+def apply_determinism(enabled: bool, seed: int = 0) -> None:
+    """``runtime.deterministic`` (scripts/run_colocate.py:144-170 of the reference).  On: seed Python / NumPy / torch,
+    ask torch for deterministic algorithms (warn only), fix cuDNN's choices, and set ``B200FW_DETERMINISTIC=1`` so the
+    GEMM keeps one unit per output tile instead of split-K slices that add with float atomics.  What stays
+    order-dependent in fp32: the loss sum, the norm weight-gradient and embedding-gradient accumulations (float
+    atomics inside those kernels) - runs then agree to summation-order rounding, not bit for bit.  Off: the switches
+    are cleared, so a previous setting in the process or its environment does not linger."""
+    import os
+    import random
+
+    import torch
+    if enabled:
+        os.environ["B200FW_DETERMINISTIC"] = "1"
+        os.environ.setdefault("CUBLAS_WORKSPACE_CONFIG", ":4096:8")
+        random.seed(seed)
+        try:
+            import numpy as np
+            np.random.seed(seed % (1 << 32))
+        except ImportError:
+            pass
+        torch.manual_seed(seed)
+        torch.use_deterministic_algorithms(True, warn_only=True)
+        torch.backends.cudnn.deterministic, torch.backends.cudnn.benchmark = True, False
+    else:
+        os.environ.pop("B200FW_DETERMINISTIC", None)
+        torch.use_deterministic_algorithms(False)
+        torch.backends.cudnn.deterministic, torch.backends.cudnn.benchmark = False, True
+

@@ -18,6 +18,7 @@
 // let the epilogue of tile i overlap the main loop of tile i+1.  One CTA per SM (TMEM and shared
 // memory are sized for that), grid = min(#tiles, #SMs), static round-robin tile schedule with
 // M-grouped rasterisation for L2 reuse.
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -681,7 +682,13 @@ static int launch_gemm(const void* A, const void* B, void* C, const void* R, int
   // Split-K for fp32 outputs with a long contraction: pick the split that minimises the number of
   // waves times the work per unit (ties go to the smaller split); every slice keeps >= 16 k-blocks.
   int split_k = 1;
-  if (COMM == 0 && out_fp32 && !(flags & GEMM_RESIDUAL)) {
+  // B200FW_DETERMINISTIC=1 keeps one unit per output tile: split-K slices add into C with float atomics, whose
+  // order changes from run to run
+  static const bool deterministic = [] {
+    const char* e = std::getenv("B200FW_DETERMINISTIC");
+    return e != nullptr && e[0] == '1';
+  }();
+  if (COMM == 0 && out_fp32 && !(flags & GEMM_RESIDUAL) && !deterministic) {
     const int num_kb = (K + GEMM_BK - 1) / GEMM_BK;
     double best = static_cast<double>((num_tiles + grid - 1) / grid);
     for (int sk = 2; sk <= 4 && num_kb / sk >= 16; ++sk) {

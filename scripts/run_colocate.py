@@ -13,7 +13,7 @@ import sys
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
-from b200fw.config import build_colocate_config, load_yaml_config, validate_parallel_config  # noqa: E402
+from b200fw.config import apply_determinism, build_colocate_config, load_yaml_config, validate_parallel_config  # noqa: E402
 from b200fw.obs import setup_logger  # noqa: E402
 from b200fw.orch import ColocateOrchestrator  # noqa: E402
 
@@ -60,6 +60,7 @@ def main(argv=None):
     if unknown and rank == 0:
         print(f"[config] keys not used by this framework: {unknown}", file=sys.stderr)
     validate_parallel_config(cfg)
+    apply_determinism(cfg.deterministic, cfg.seed)        # before the first CUDA call: the GEMM reads its switch once
 
     async def go():
         orch = ColocateOrchestrator(cfg)

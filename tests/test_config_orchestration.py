@@ -36,6 +36,27 @@ def test_yaml_mapping_overrides_and_unknown_keys():
         build_colocate_config({}, {"nope": 1})
 
 
+def test_deterministic_switch_is_read_from_yaml_and_applied(tmp_path):
+    from b200fw.config import apply_determinism
+    y = tmp_path / "c.yaml"
+    y.write_text("runtime:\n  deterministic: true\n  seed: 11\n")
+    cfg, unknown = build_colocate_config(load_yaml_config(str(y)))
+    assert cfg.deterministic is True and cfg.seed == 11 and unknown == []
+    was = os.environ.get("B200FW_DETERMINISTIC")
+    try:
+        apply_determinism(True, 11)
+        a = torch.rand(3)
+        assert os.environ["B200FW_DETERMINISTIC"] == "1" and torch.are_deterministic_algorithms_enabled()
+        apply_determinism(True, 11)
+        assert torch.equal(a, torch.rand(3))                      # same seed, same draws
+        apply_determinism(False)
+        assert "B200FW_DETERMINISTIC" not in os.environ and not torch.are_deterministic_algorithms_enabled()
+    finally:
+        apply_determinism(False)
+        if was is not None:
+            os.environ["B200FW_DETERMINISTIC"] = was
+
+
 def test_parallel_validation_rules():
     ok = ColocateConfig(tp_size=2, dp_size=2, pp_size=2, num_micro_batches=2, batch_size=8, zero_stage=1, training_mode="sft")
     validate_parallel_config(ok, 8)
