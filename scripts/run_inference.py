@@ -56,25 +56,43 @@ def parse_args(argv=None):
     return ap.parse_args(argv)
 
 
+def _first(y, paths, default=None):
+    for path in paths:
+        v = get_nested(y, path)
+        if v is not None:
+            return v
+    return default
+
+
 def create_inference_config(a, y) -> InferenceConfig:
-    pick = lambda cli, path, default: cli if cli is not None else get_nested(y, path, default)
+    """CLI over YAML over defaults.  The YAML may use this repository's keys (configs/inference/standalone.yaml) or the
+    reference's (``model.path``, ``inference.temperature``, ``kv_cache.enable_cuda_graph``, ``advanced.*``)."""
+    def pick(cli, paths, default):
+        return cli if cli is not None else _first(y, paths if isinstance(paths, (list, tuple)) else [paths], default)
+
     preset = a.model_preset or get_nested(y, "model.preset")
-    path = a.model_path or get_nested(y, "model.name_or_path", "")
+    path = a.model_path or _first(y, ["model.name_or_path", "model.path"], "")
     mc = PRESETS[preset] if preset else read_hf_config(path)
+    radix = pick(a.radix_cache, ["optimizations.radix_cache", "advanced.use_radix_cache"], False)
     kw = dict(
         inference_mode=pick(a.mode, "inference.mode", "kv_cache"), model_path="" if preset else path,
-        temperature=pick(a.temperature, "sampling.temperature", 0.7), top_p=pick(a.top_p, "sampling.top_p", 0.9),
+        temperature=pick(a.temperature, ["sampling.temperature", "inference.temperature"], 0.7),
+        top_p=pick(a.top_p, ["sampling.top_p", "inference.top_p"], 0.9),
         kv_cache_dtype=pick(a.kv_cache_dtype, "kv_cache.dtype", "fp16"),
         block_size=int(pick(a.block_size, "kv_cache.block_size", 16)),
-        enable_async_scheduling=bool(pick(a.async_scheduling, "optimizations.async_scheduling", False)),
+        enable_async_scheduling=bool(pick(a.async_scheduling, ["optimizations.async_scheduling",
+                                                               "advanced.enable_async_scheduling"], False)),
         max_num_batched_tokens=get_nested(y, "scheduler.max_num_batched_tokens", 8192),
         max_num_sequences=get_nested(y, "scheduler.max_num_sequences", 256),
         max_prefill_tokens=get_nested(y, "scheduler.max_prefill_tokens", 4096),
         chunk_size=get_nested(y, "scheduler.chunk_size", 512),
-        enable_cuda_graph=bool(pick(a.cuda_graph, "optimizations.cuda_graph", False)),
-        use_radix_cache=bool(pick(a.radix_cache, "optimizations.radix_cache", False)),
-        enable_prefix_caching=bool(a.prefix_cache or pick(a.radix_cache, "optimizations.prefix_caching", False)),
-        enable_partitioned_attention=bool(pick(a.partitioned_attention, "optimizations.partitioned_attention", False)),
+        enable_cuda_graph=bool(pick(a.cuda_graph, ["optimizations.cuda_graph", "kv_cache.enable_cuda_graph"], False)),
+        use_radix_cache=bool(radix),
+        enable_prefix_caching=bool(a.prefix_cache or radix or _first(y, ["optimizations.prefix_caching",
+                                                                         "kv_cache.enable_prefix_caching"], False)),
+        enable_prefix_reuse=bool(_first(y, ["optimizations.prefix_reuse", "kv_cache.enable_prefix_reuse"], True)),
+        enable_partitioned_attention=bool(pick(a.partitioned_attention, ["optimizations.partitioned_attention",
+                                                                         "advanced.enable_partitioned_attention"], False)),
         attention_partition_size=get_nested(y, "optimizations.partition_size", 512),
         speculative_enabled=bool(pick(a.speculative, "speculative.enabled", False)),
         speculative_num_tokens=get_nested(y, "speculative.num_tokens", 4), seed=a.seed)
@@ -142,7 +160,11 @@ def main(argv=None):
     y = load_yaml_config(a.config)
     cfg = create_inference_config(a, y)
     eng = InferenceEngine(cfg).initialize()
-    max_tokens = a.max_tokens if a.max_tokens is not None else get_nested(y, "sampling.max_tokens", 64)
+    max_tokens = a.max_tokens if a.max_tokens is not None else _first(y, ["sampling.max_tokens", "inference.max_tokens"], 64)
+    if a.num_samples == 1:
+        a.num_samples = int(get_nested(y, "inference.num_samples", 1))
+    if a.batch_size == 0:
+        a.batch_size = int(get_nested(y, "inference.batch_size", 0))
     from b200fw.data.pipeline import _load_tokenizer
     tok = _load_tokenizer(a.model_path or None)          # the model directory's tokenizer, else byte-level
     if a.interactive:

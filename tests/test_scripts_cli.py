@@ -61,6 +61,24 @@ def test_run_inference_jsonl_in_jsonl_out(tmp_path, capsys):
     assert summary["prompts"] == 4 and summary["samples"] == 8 and summary["mode"] == "kv_cache"
 
 
+def test_run_inference_reads_both_yaml_dialects(tmp_path):
+    mod = _load("run_inference.py")
+    ref = tmp_path / "ref.yaml"
+    ref.write_text("model:\n  path: ''\ninference:\n  mode: mock\n  max_tokens: 5\n  temperature: 0.3\n  top_p: 0.5\n"
+                   "kv_cache:\n  num_blocks: 48\n  block_size: 16\n  enable_prefix_caching: true\n  enable_cuda_graph: true\n"
+                   "advanced:\n  enable_partitioned_attention: true\n  use_radix_cache: true\n  enable_async_scheduling: true\n")
+    from b200fw.config import load_yaml_config
+    a = mod.parse_args(["--config", str(ref), "--model-preset", "tiny128"])
+    c = mod.create_inference_config(a, load_yaml_config(str(ref)))
+    assert (c.inference_mode, c.temperature, c.top_p, c.num_blocks) == ("mock", 0.3, 0.5, 48)
+    assert c.enable_prefix_caching and c.enable_cuda_graph and c.enable_partitioned_attention and c.use_radix_cache
+    assert c.enable_async_scheduling
+    own = os.path.join(ROOT, "configs", "inference", "standalone.yaml")
+    a = mod.parse_args(["--config", own, "--temperature", "0.1", "--num-blocks", "32"])       # the command line wins
+    c = mod.create_inference_config(a, load_yaml_config(own))
+    assert c.temperature == 0.1 and c.num_blocks == 32 and c.top_p == 0.95 and c.use_radix_cache and c.chunk_size == 512
+
+
 def test_run_inference_interactive_reads_until_quit():
     import io
     mod = _load("run_inference.py")
