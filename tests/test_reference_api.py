@@ -258,7 +258,7 @@ def test_transfer_adapters():
     assert s["total_delta_syncs"] == 1 and s["total_full_syncs"] == 0 and s["total_delta_bytes"] == 8
     assert torch.equal(t.double_buffer.get_active_state()["a"], torch.full((2,), 1.5)) and t.last_delta_version.delta_bytes == 8
     assert DeltaComputer.compute_delta_bytes({"a": torch.ones(3)}) == 12 and t.config.enable_double_buffer
-    ipc = IPCWeightTransfer(VLLMClient("http://127.0.0.1:9"))
+    ipc = IPCWeightTransfer(VLLMClient("http://127.0.0.1:9", timeout=2.0, max_retries=0, backoff_s=0.0))
     st = {"w": torch.arange(4.0)}
     assert ipc.verify_consistency(st) and ipc.verify_consistency(st, ipc.checksum(st)) and not ipc.verify_consistency(st, "bad")
     assert ipc.push_weights_sync(st) is False                       # nothing listens there: reported, not raised
