@@ -251,11 +251,11 @@ class ColocateOrchestrator:
     # =================================================================================================
     def _next_batch(self) -> GRPOBatch:
         if self._batches is None:
-            self._batches = self.data.get_batches(max(1, self.config.batch_size // max(1, self.train_engine.parallel_ctx.dp_size)))
+            self._batches = self.data.get_batches(self._per_rank_batch())
         try:
             return next(self._batches)
         except StopIteration:
-            self._batches = self.data.get_batches(max(1, self.config.batch_size // max(1, self.train_engine.parallel_ctx.dp_size)))
+            self._batches = self.data.get_batches(self._per_rank_batch())
             return next(self._batches)
 
     def _rollout(self, batch: GRPOBatch) -> _Rollout:
@@ -562,9 +562,15 @@ class ColocateOrchestrator:
         t = im.state_durations.get("training", 0.0)
         if t <= 0:
             return 0.0
-        fl = ComputeProfiler.reference_formula_flops(mc.num_layers, cfg.batch_size, cfg.max_seq_len, mc.hidden_size,
+        fl = ComputeProfiler.reference_formula_flops(mc.num_layers, self._per_rank_batch(), cfg.max_seq_len, mc.hidden_size,
                                                      mc.intermediate_size, mc.vocab_size, full=cfg.lora_rank <= 0)
         return self.compute_profiler.compute_mfu(fl / (cfg.tp_size * cfg.pp_size), t)
+
+    def _per_rank_batch(self) -> int:
+        """``training.batch_size`` is the GLOBAL batch of an iteration here: every data-parallel rank takes
+        ``batch_size // dp_size`` of it.  (The reference's validator calls the key ``global_batch`` too, while its
+        data path hands the full value to every rank; scale the key by ``dp_size`` when porting such a config.)"""
+        return max(1, self.config.batch_size // max(1, self.config.dp_size))
 
     def _do_eval(self, stage: str) -> Dict:
         """Fixed-prompt evaluation before / after training (src/orchestrator/colocate_orchestrator.py:940-1060):
@@ -697,11 +703,12 @@ class ColocateOrchestrator:
         full = cfg.lora_rank <= 0
         tp, pp, dp = max(1, cfg.tp_size), max(1, cfg.pp_size), max(1, cfg.dp_size)
         prof = self.compute_profiler or ComputeProfiler()
-        ref_fl = ComputeProfiler.reference_formula_flops(mc.num_layers, cfg.batch_size, cfg.max_seq_len, mc.hidden_size,
+        per_rank = self._per_rank_batch()
+        ref_fl = ComputeProfiler.reference_formula_flops(mc.num_layers, per_rank, cfg.max_seq_len, mc.hidden_size,
                                                          mc.intermediate_size, mc.vocab_size, full=full) / (tp * pp)
-        exact_fl = ComputeProfiler.exact_flops(mc, cfg.batch_size, cfg.max_seq_len, full=full,
+        exact_fl = ComputeProfiler.exact_flops(mc, per_rank, cfg.max_seq_len, full=full,
                                                grad_checkpoint=cfg.use_gradient_checkpoint) / (tp * pp)
-        gbs = cfg.batch_size * dp
+        gbs = per_rank * dp
         return {
             "mfu_percent": round(100 * prof.compute_mfu(ref_fl, step), 2),
             "mfu_exact_percent": round(100 * prof.compute_mfu(exact_fl, step), 2),
@@ -716,7 +723,8 @@ class ColocateOrchestrator:
             "primary_metric": "mfu" if full else "tokens_per_second",
             "note": (f"MFU = forward FLOPs x {3 if full else 2} / (tp x pp) / (step time x peak); peak = measured "
                      f"sustained bf16 GEMM throughput of this device class ({prof.peak_tflops:.0f} TFLOP/s); tokens/s "
-                     f"assumes batch_size x max_seq_len tokens per rank and step (padding counted, as the reference does)"),
+                     f"assumes {per_rank} sequences x max_seq_len tokens per rank and step (padding counted, as the "
+                     f"reference does); training.batch_size is the global batch"),
         }
 
     def _write_final_artifacts(self):
@@ -744,7 +752,7 @@ class ColocateOrchestrator:
                         w.writerow([m.iteration, m.train_metrics.loss, m.train_metrics.grad_norm, m.avg_reward])
             self._render_loss_curve()
         self.artifacts.write_json("memory_timeline.json", self.memory.timeline(), all_ranks=True)
-        rep = self.train_engine.generate_memory_report(self.config.batch_size * self.config.max_seq_len)
+        rep = self.train_engine.generate_memory_report(self._per_rank_batch() * self.config.max_seq_len)
         self.artifacts.write_json("memory_report.json", rep.to_dict())
         if self.tb is not None:
             self.tb.flush()
