@@ -94,6 +94,9 @@ class ColocateConfig:
     enable_profiling: bool = False
     profile_interval: int = 10
     enable_comm_overlap: bool = False
+    reward_correct: float = 1.0            # reward.correct_reward: the answer is right
+    reward_format: float = -0.5            # reward.format_reward: wrong or missing answer, well-formed response
+    reward_wrong: float = -1.0             # reward.wrong_reward: wrong or missing answer, no recognisable format
     deterministic: bool = False            # fixed seeds, deterministic torch algorithms, no split-K atomics in the GEMM
     icepop_enabled: bool = False
     icepop_divergence_threshold: float = 0.5
@@ -130,6 +133,8 @@ _YAML_MAP: List[Tuple[str, str]] = [
     ("runtime.tp_size", "tp_size"), ("runtime.dp_size", "dp_size"), ("runtime.precision", "amp_dtype"),
     ("runtime.inference_backend", "inference_backend"), ("runtime.enable_comm_overlap", "enable_comm_overlap"),
     ("runtime.sequence_parallel", "sequence_parallel"), ("runtime.seed", "seed"), ("runtime.deterministic", "deterministic"),
+    ("reward.correct_reward", "reward_correct"), ("reward.format_reward", "reward_format"),
+    ("reward.wrong_reward", "reward_wrong"),
     ("distributed.pp_size", "pp_size"), ("distributed.num_micro_batches", "num_micro_batches"),
     ("distributed.zero_stage", "zero_stage"),
     ("training.mode", "training_mode"), ("training.total_iterations", "total_iterations"),
@@ -168,8 +173,12 @@ _YAML_MAP: List[Tuple[str, str]] = [
     ("inference.enable_cuda_graph", "enable_cuda_graph"), ("inference.use_radix_cache", "use_radix_cache"),
 ]
 # keys present in the reference's YAML files that no code reads; accepted silently
-_DOCUMENTATION_ONLY = {"lora.dropout", "lora.enabled", "experiment.name",
-                       "experiment.seed", "profiling.memory", "profiling.comm", "profiling.compute"}
+# keys of the reference's YAML files that neither it nor this framework acts on (accepted silently)
+_DOCUMENTATION_ONLY = {"lora.dropout", "lora.enabled", "experiment.name", "experiment.seed", "experiment.stage",
+                       "experiment.algorithm", "profiling.memory", "profiling.comm", "profiling.compute",
+                       "profiling.compute_mfu", "profiling.memory_breakdown", "profiling.metrics",
+                       "profiling.track_communication", "reward.type", "reward.answer_format", "runtime.device",
+                       "model.trust_remote_code", "icepop.log_diagnostics"}
 
 
 def _flatten(d: Dict[str, Any], prefix: str = "") -> Dict[str, Any]:

@@ -157,7 +157,7 @@ class ColocateOrchestrator:
         if self.reward_fn is None:
             self.reward_fn = SyntheticTokenReward(eng.model_config.vocab_size, cfg.seed,
                                                   dense_weight=cfg.synthetic_reward_dense_weight) if cfg.synthetic_data \
-                else GSM8KRewardFunction()
+                else GSM8KRewardFunction(correct=cfg.reward_correct, wrong=cfg.reward_format, no_answer=cfg.reward_wrong)
         # ---- rollout backend ----------------------------------------------------------------------------------
         if cfg.training_mode == "grpo" or cfg.inference_preview_enabled:
             await self._init_inference()

@@ -57,6 +57,17 @@ def test_deterministic_switch_is_read_from_yaml_and_applied(tmp_path):
             os.environ["B200FW_DETERMINISTIC"] = was
 
 
+def test_reward_values_come_from_yaml(tmp_path):
+    y = tmp_path / "c.yaml"
+    y.write_text("reward:\n  type: gsm8k_rule\n  correct_reward: 2.0\n  format_reward: -0.25\n  wrong_reward: -3.0\n"
+                 "experiment:\n  stage: rl\nruntime:\n  device: auto\n")
+    cfg, unknown = build_colocate_config(load_yaml_config(str(y)))
+    assert (cfg.reward_correct, cfg.reward_format, cfg.reward_wrong) == (2.0, -0.25, -3.0) and unknown == []
+    from b200fw.reward import GSM8KRewardFunction
+    rf = GSM8KRewardFunction(correct=cfg.reward_correct, wrong=cfg.reward_format, no_answer=cfg.reward_wrong)
+    assert rf([["#### 4", "#### 5", "dunno"]], [4]) == [[2.0, -0.25, -3.0]]
+
+
 def test_parallel_validation_rules():
     ok = ColocateConfig(tp_size=2, dp_size=2, pp_size=2, num_micro_batches=2, batch_size=8, zero_stage=1, training_mode="sft")
     validate_parallel_config(ok, 8)
