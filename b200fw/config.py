@@ -178,7 +178,7 @@ _DOCUMENTATION_ONLY = {"lora.dropout", "lora.enabled", "experiment.name", "exper
                        "experiment.algorithm", "profiling.memory", "profiling.comm", "profiling.compute",
                        "profiling.compute_mfu", "profiling.memory_breakdown", "profiling.metrics",
                        "profiling.track_communication", "reward.type", "reward.answer_format", "runtime.device",
-                       "model.trust_remote_code", "icepop.log_diagnostics"}
+                       "model.trust_remote_code", "model.sft_checkpoint", "icepop.log_diagnostics"}
 
 
 def _flatten(d: Dict[str, Any], prefix: str = "") -> Dict[str, Any]:
