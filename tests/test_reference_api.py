@@ -268,3 +268,63 @@ def test_transfer_adapters():
     c = DisaggConfig(num_train_gpus=2, num_infer_gpus=2)
     assert c.train_gpus == [0, 1] and c.infer_gpus == [2, 3] and c.infer_tp_size == 2 and c.overlap_training_inference
     assert DisaggIterationMetrics(0, rollout_time=1.5).infer_time == 1.5
+
+
+def test_colocate_replaced_stages_drive_the_loop():
+    """A caller (or subclass) that replaces ``_do_inference`` / ``_do_training`` / ``_do_weight_sync`` gets a loop that
+    runs exactly those stages in order, with the sleep / wake calls of a server around the sync, and the collaborators
+    are reachable under the reference's private names (tests/test_colocate_loop.py of the reference drives it so)."""
+    import asyncio
+    from b200fw.config import ColocateConfig
+    from b200fw.data.pipeline import GRPOBatch
+    from b200fw.orch.colocate import ColocateOrchestrator, OrchestratorState
+    from b200fw.reward.gsm8k import GSM8KRewardFunction
+    from b200fw.train.engine import TrainMetrics
+
+    class Server:
+        slept = woke = 0
+
+        async def sleep(self, level=1):
+            Server.slept += 1
+
+        async def wake_up(self, tags=None):
+            Server.woke += 1
+
+    class Data:
+        def get_batches(self, n):            # a list, not an iterator, and shorter than the run: it is cycled
+            return [GRPOBatch(["6*7?"], [[5, 6, 7]], ["42"])]
+
+    orch = ColocateOrchestrator(ColocateConfig(model_path="x", total_iterations=3, batch_size=1, num_samples_per_prompt=2,
+                                               retry_delay=0.0))
+    assert not orch._stages_overridden()
+    orch._vllm_client, orch._reward_fn, orch._data_pipeline = Server(), GSM8KRewardFunction(), Data()
+    assert orch.vllm_client is orch._vllm_client and orch.data is orch._data_pipeline
+    order = []
+
+    async def infer(batch):
+        order.append("infer")
+        return [["Step 1: 6*7=42\n#### 42", "Step 1: guess\n#### 41"] for _ in batch.prompts]
+
+    async def train(batch, responses, rewards):
+        order.append("train")
+        assert rewards == [[1.0, -0.5]]
+        if len(order) == 5:                  # second iteration fails in training
+            raise RuntimeError("boom")
+        return TrainMetrics(0.25, 0.2, 0.01, 1.0, 1e-5, step=len(order))
+
+    async def sync():
+        order.append("sync")
+
+    orch._do_inference, orch._do_training, orch._do_weight_sync = infer, train, sync
+    assert orch._stages_overridden()
+    metrics = asyncio.run(orch.run())
+    assert order == ["infer", "train", "sync", "infer", "train", "infer", "train", "sync"]
+    assert len(metrics) == 3 and orch.state == OrchestratorState.DONE
+    assert metrics[0].avg_reward == 0.25 and metrics[0].accuracy == 0.5 and metrics[0].train_metrics.loss == 0.25
+    assert "boom" in metrics[1].error and metrics[2].error is None
+    assert Server.slept == 2 and Server.woke == 3        # the failed iteration wakes the server on recovery
+    assert set(metrics[0].state_durations) == {"inferring", "rewarding", "training", "syncing"}
+
+    # the reference's (error, stage) call form of the recovery hook
+    asyncio.run(orch._handle_error(RuntimeError("late"), "syncing"))
+    assert orch.state == OrchestratorState.ERROR and Server.woke == 4
