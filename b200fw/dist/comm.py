@@ -179,6 +179,23 @@ def gather_from_parallel_region(x, group=None):
     return x if group is None else _GatherFromParallelRegion.apply(x, group)
 
 
+class _ScatterToParallelRegion(torch.autograd.Function):
+    """Keep this rank's slice of the last dim (forward) / all-gather the gradient slices along it (backward)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return x.chunk(_size(group), dim=-1)[dist.get_rank(group)].contiguous()
+
+    @staticmethod
+    def backward(ctx, g):
+        return all_gather_last_dim(g.contiguous(), ctx.group), None
+
+
+def scatter_to_parallel_region(x, group=None):
+    return x if group is None else _ScatterToParallelRegion.apply(x, group)
+
+
 def gather_sequence(x, group=None):
     return x if group is None else _GatherSeq.apply(x, group)
 

@@ -53,9 +53,14 @@ class ParallelContext:
     # ---- construction --------------------------------------------------------------------------
     @classmethod
     def init_distributed(cls, tp_size=1, dp_size=1, pp_size=1, backend: Optional[str] = None,
-                         timeout_s: float = 1800.0) -> "ParallelContext":
+                         timeout_s: float = 1800.0, init_single_process: bool = False) -> "ParallelContext":
+        """Reads RANK / WORLD_SIZE / LOCAL_RANK, creates the process group if none exists and the tp / pp / dp
+        sub-groups.  ``init_single_process=True`` (the reference's flag, src/distributed/parallel_context.py:94-130)
+        returns the one-rank context when the job has a single process."""
         rank = int(os.environ.get("RANK", "0"))
         world = int(os.environ.get("WORLD_SIZE", "1"))
+        if init_single_process and world == 1 and tp_size * dp_size * pp_size == 1:
+            return cls.init_single_process()
         local_rank = int(os.environ.get("LOCAL_RANK", "0"))
         if backend is None:
             backend = "nccl" if torch.cuda.is_available() else "gloo"

@@ -56,10 +56,13 @@ class ColumnParallelLinear(nn.Module):
     """
 
     def __init__(self, in_features, out_features, ctx=None, gather_output=False, sequence_parallel=False,
-                 init_std=0.02, dtype=None, device=None):
+                 init_std=0.02, dtype=None, device=None, bias=False):
         super().__init__()
         self.tp_size, self.tp_rank, self.tp_group = _tp(ctx)
         assert out_features % self.tp_size == 0
+        # the model's projections carry no bias; the option is for layers used on their own
+        # (src/distributed/tensor_parallel.py:60-118 has it): the bias is sharded with the output features
+        self.bias = nn.Parameter(torch.zeros(out_features // self.tp_size, dtype=dtype, device=device)) if bias else None
         self.in_features, self.out_features = in_features, out_features
         self.out_local = out_features // self.tp_size
         self.gather_output, self.sequence_parallel = gather_output, sequence_parallel
@@ -70,7 +73,8 @@ class ColumnParallelLinear(nn.Module):
     def forward(self, x):
         shape = x.shape
         x = x.reshape(-1, shape[-1])
-        if self.tp_size > 1 and self.sequence_parallel and self.fused_comm and x.is_cuda and x.shape[0] % 128 == 0:
+        if (self.tp_size > 1 and self.sequence_parallel and self.fused_comm and x.is_cuda and x.shape[0] % 128 == 0
+                and self.bias is None):
             from ..ops import fused_tp
             y = fused_tp.column_linear_sp(x, self.weight, self.tp_group)    # all-gather inside the GEMM
             return y
@@ -78,6 +82,8 @@ class ColumnParallelLinear(nn.Module):
             x = comm.gather_sequence(x, self.tp_group) if self.sequence_parallel \
                 else comm.copy_to_parallel_region(x, self.tp_group)
         y = ops.linear(x, self.weight)
+        if self.bias is not None:
+            y = y + self.bias
         if self.gather_output and self.tp_size > 1:
             y = comm.gather_from_parallel_region(y, self.tp_group)
         if not self.sequence_parallel:
@@ -94,10 +100,14 @@ class RowParallelLinear(nn.Module):
     Without TP the residual add rides in the GEMM epilogue."""
 
     def __init__(self, in_features, out_features, ctx=None, sequence_parallel=False, init_std=0.02,
-                 dtype=None, device=None):
+                 dtype=None, device=None, bias=False, input_is_parallel=True):
         super().__init__()
         self.tp_size, self.tp_rank, self.tp_group = _tp(ctx)
         assert in_features % self.tp_size == 0
+        # bias: replicated, added once after the reduction; input_is_parallel=False: the input carries all
+        # features and this rank takes its slice of the last dim (src/distributed/tensor_parallel.py:121-190)
+        self.bias = nn.Parameter(torch.zeros(out_features, dtype=dtype, device=device)) if bias else None
+        self.input_is_parallel = input_is_parallel
         self.in_features, self.out_features = in_features, out_features
         self.in_local = in_features // self.tp_size
         self.sequence_parallel = sequence_parallel
@@ -106,8 +116,13 @@ class RowParallelLinear(nn.Module):
         nn.init.normal_(self.weight, std=init_std)
 
     def forward(self, x, residual=None):
+        if not self.input_is_parallel and self.tp_size > 1:
+            x = comm.scatter_to_parallel_region(x, self.tp_group)
         shape = x.shape
         x = x.reshape(-1, shape[-1])
+        if self.bias is not None:
+            y = self._forward_plain(x, residual) + self.bias
+            return y if self.sequence_parallel else y.reshape(*shape[:-1], y.shape[-1])
         if self.tp_size == 1:
             y = ops.linear(x, self.weight, residual)
         elif self.sequence_parallel and self.fused_comm and x.is_cuda and (x.shape[0] // self.tp_size) % 128 == 0:
@@ -126,11 +141,43 @@ class RowParallelLinear(nn.Module):
         return y
 
 
+def _row_forward_plain(self, x, residual=None):
+    """Library-collective form of the row-parallel product on 2-D ``x`` (no fused kernel, no epilogue add)."""
+    y = ops.linear(x, self.weight)
+    if self.tp_size > 1:
+        y = comm.reduce_scatter_sequence(y, self.tp_group) if self.sequence_parallel \
+            else comm.reduce_from_parallel_region(y, self.tp_group)
+    return y if residual is None else y + residual.reshape(y.shape)
+
+
+RowParallelLinear._forward_plain = _row_forward_plain
+
+
+class _ProjectionView:
+    """Half of a fused projection under the name a separate layer would have (``mlp.gate_proj.weight``)."""
+
+    def __init__(self, fused: ColumnParallelLinear, half: int):
+        self._fused, self._half = fused, half
+
+    @property
+    def weight(self) -> torch.Tensor:
+        n = self._fused.out_local // 2
+        return self._fused.weight[self._half * n:(self._half + 1) * n]
+
+
 class ParallelMLP(nn.Module):
     """SwiGLU FFN; gate and up projections are one fused column-parallel GEMM ([gate_local | up_local])."""
 
-    def __init__(self, cfg: ModelConfig, ctx=None, sequence_parallel=False, dtype=None, device=None):
+    def __init__(self, cfg, ctx=None, sequence_parallel=False, dtype=None, device=None):
+        """``ParallelMLP(model_config, ctx, ...)``; the reference's ``ParallelMLP(hidden_size, intermediate_size, ctx)``
+        (src/distributed/tensor_parallel.py:300-340) is accepted as well."""
         super().__init__()
+        if isinstance(cfg, int):
+            from types import SimpleNamespace
+            hidden, inter = cfg, ctx
+            ctx = None if isinstance(sequence_parallel, bool) else sequence_parallel
+            sequence_parallel = False
+            cfg = SimpleNamespace(hidden_size=hidden, intermediate_size=inter, init_std=0.02)
         self.gate_up_proj = ColumnParallelLinear(cfg.hidden_size, 2 * cfg.intermediate_size, ctx,
                                                  sequence_parallel=sequence_parallel, init_std=cfg.init_std,
                                                  dtype=dtype, device=device)
@@ -138,9 +185,20 @@ class ParallelMLP(nn.Module):
                                            sequence_parallel=sequence_parallel, init_std=cfg.init_std,
                                            dtype=dtype, device=device)
 
+    @property
+    def gate_proj(self) -> _ProjectionView:
+        return _ProjectionView(self.gate_up_proj, 0)
+
+    @property
+    def up_proj(self) -> _ProjectionView:
+        return _ProjectionView(self.gate_up_proj, 1)
+
     def forward(self, x, residual=None):
         gu = self.gate_up_proj(x)
-        return self.down_proj(ops.swiglu(gu.reshape(-1, gu.shape[-1])), residual)
+        y = self.down_proj(ops.swiglu(gu.reshape(-1, gu.shape[-1])), residual)
+        if not self.down_proj.sequence_parallel and x.dim() > 2:
+            y = y.reshape(*x.shape[:-1], y.shape[-1])
+        return y
 
 
 class ParallelAttention(nn.Module):

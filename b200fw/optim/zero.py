@@ -116,7 +116,15 @@ class ZeROOptimizer:
     def __init__(self, params, lr=1e-5, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01, stage: int = 1,
                  ctx: Optional[ParallelContext] = None, dp_group=None, bucket_mb: float = 64.0,
                  max_grad_norm: float = 0.0, grad_dtype: Optional[torch.dtype] = None,
-                 overlap: bool = True, comm_backend: str = "nccl"):
+                 overlap: bool = True, comm_backend: str = "nccl", optimizer_class=None, parallel_context=None):
+        """``optimizer_class`` / ``parallel_context`` are the reference's keyword names
+        (src/distributed/zero_optim.py:60-110): the update rule here is always the fused AdamW, so any other
+        class is refused rather than silently replaced."""
+        if optimizer_class is not None and optimizer_class not in (torch.optim.AdamW, torch.optim.Adam):
+            raise ValueError(f"ZeROOptimizer implements AdamW; got optimizer_class={optimizer_class.__name__}")
+        if optimizer_class is torch.optim.Adam:
+            weight_decay = 0.0 if weight_decay == 0.01 else weight_decay
+        ctx = ctx if ctx is not None else parallel_context
         params = [p for p in params if p.requires_grad]
         assert params, "no trainable parameters"
         self.ctx = ctx
@@ -637,6 +645,29 @@ class ZeROOptimizer:
             assert b.param_buf is not None, "gather parameters first"
             src = b.param_shard() if self.stage >= 1 else b.param_buf
             self._shard_view(self.master, i).copy_(src.float())
+
+    # ---- the reference's view of the layout: one flat, padded parameter vector cut into equal shards ------------
+    @property
+    def group(self):
+        return self.dp_group
+
+    @property
+    def world_size(self) -> int:
+        return self.world
+
+    @staticmethod
+    def _pad_to_divisible(n: int, divisor: int) -> int:
+        return (n + divisor - 1) // divisor * divisor
+
+    @property
+    def padded_size(self) -> int:
+        """Elements over all buckets, padding included (each bucket is padded to ``8 * world`` elements)."""
+        return sum(b.numel for b in self.buckets)
+
+    @property
+    def shard_size(self) -> int:
+        """Elements of optimizer state this rank owns."""
+        return sum(b.shard_numel if self.world > 1 else b.numel for b in self.buckets)
 
     @property
     def state_memory_usage(self) -> int:

@@ -128,3 +128,50 @@ def test_destroy_runs_registered_callbacks_first():
     assert order == ["b", "a"] and ParallelContext._instance is None
     ctx.destroy()                                   # callbacks ran once
     assert order == ["b", "a"]
+
+
+def _biased_tp_layers(rank, world):
+    """Column- and row-parallel layers with a bias, a row layer fed the unsplit input, and the MLP built from plain
+    sizes: each against ``nn.Linear`` holding the concatenated weights (outputs and input gradients)."""
+    import torch.distributed as dist
+    import torch.nn.functional as F
+    from b200fw.dist import comm
+    from b200fw.model.qwen3 import ColumnParallelLinear, ParallelMLP, RowParallelLinear
+    ctx = ParallelContext.init_distributed(tp_size=world, backend="gloo")
+    g = ctx.tp_group
+    torch.manual_seed(7)                     # same stream on every rank: full reference weights
+    w_col, b_col = torch.randn(24, 16) * 0.1, torch.randn(24)
+    w_row, b_row = torch.randn(12, 24) * 0.1, torch.randn(12)
+    x = torch.randn(3, 5, 16, requires_grad=True)
+    xr = x.detach().clone().requires_grad_(True)
+
+    col = ColumnParallelLinear(16, 24, ctx, bias=True, gather_output=True)
+    row = RowParallelLinear(24, 12, ctx, bias=True, input_is_parallel=False)
+    n_c, n_r = 24 // world, 24 // world
+    with torch.no_grad():
+        col.weight.copy_(w_col[rank * n_c:(rank + 1) * n_c]); col.bias.copy_(b_col[rank * n_c:(rank + 1) * n_c])
+        row.weight.copy_(w_row[:, rank * n_r:(rank + 1) * n_r]); row.bias.copy_(b_row)
+    y = row(col(x))                           # gathered column output -> row layer slices it again
+    ref = F.linear(F.linear(xr, w_col, b_col), w_row, b_row)
+    y.sum().backward(); ref.sum().backward()
+    err = [(y - ref).abs().max().item(), (x.grad - xr.grad).abs().max().item(),
+           (row.bias.grad - torch.full((12,), 15.0)).abs().max().item()]
+
+    mlp = ParallelMLP(16, 32, ctx)
+    assert mlp.gate_proj.weight.shape == (32 // world, 16) and mlp.up_proj.weight.shape == (32 // world, 16)
+    parts = lambda t: [torch.empty_like(t) for _ in range(world)]
+    gw, uw, dw = parts(mlp.gate_proj.weight.data), parts(mlp.up_proj.weight.data), parts(mlp.down_proj.weight.data)
+    dist.all_gather(gw, mlp.gate_proj.weight.data.contiguous(), group=g)
+    dist.all_gather(uw, mlp.up_proj.weight.data.contiguous(), group=g)
+    dist.all_gather(dw, mlp.down_proj.weight.data.contiguous(), group=g)
+    xm = torch.randn(2, 4, 16)
+    out = mlp(xm)
+    ref_m = F.linear(F.silu(F.linear(xm, torch.cat(gw, 0))) * F.linear(xm, torch.cat(uw, 0)), torch.cat(dw, 1))
+    assert out.shape == ref_m.shape
+    err.append((out - ref_m).abs().max().item())
+    return err
+
+
+def test_tp_layers_with_bias_and_unsplit_input():
+    for err in run_ranks(_biased_tp_layers, 2):
+        assert max(err) < 1e-5, err

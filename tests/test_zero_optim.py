@@ -215,3 +215,21 @@ def test_optimizer_state_roundtrip():
     for a, b in zip(m.parameters(), m2.parameters()):
         assert torch.equal(a, b)
     assert not opt2.load_state_dict({**sd, "world": 4})
+
+
+def test_reference_keyword_names_and_layout_view():
+    """``optimizer_class`` / ``parallel_context`` keywords, the flat-vector view of the layout and the one-rank
+    case (no group, nothing sharded), as the reference's optimizer exposes them."""
+    import pytest
+    import torch
+    from b200fw.dist.context import ParallelContext
+    from b200fw.optim.zero import ZeROOptimizer
+    lin = torch.nn.Linear(32, 32, bias=False)
+    ctx = ParallelContext(tp_size=2, tp_group=None, dp_size=1, dp_group=None)
+    opt = ZeROOptimizer(lin.parameters(), optimizer_class=torch.optim.AdamW, parallel_context=ctx, lr=1e-3, weight_decay=0.0)
+    assert opt.group is None and opt.world_size == 1
+    assert opt.shard_size == opt.padded_size == 1024 == ZeROOptimizer._pad_to_divisible(1024, 8)
+    assert ZeROOptimizer._pad_to_divisible(1025, 8) == 1032
+    with pytest.raises(ValueError):
+        ZeROOptimizer(lin.parameters(), optimizer_class=torch.optim.SGD, lr=1e-3)
+    assert ParallelContext.init_distributed(tp_size=1, dp_size=1, backend="gloo", init_single_process=True).world_size == 1
