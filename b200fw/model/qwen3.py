@@ -178,6 +178,7 @@ class ParallelMLP(nn.Module):
             ctx = None if isinstance(sequence_parallel, bool) else sequence_parallel
             sequence_parallel = False
             cfg = SimpleNamespace(hidden_size=hidden, intermediate_size=inter, init_std=0.02)
+        self.sequence_parallel = sequence_parallel
         self.gate_up_proj = ColumnParallelLinear(cfg.hidden_size, 2 * cfg.intermediate_size, ctx,
                                                  sequence_parallel=sequence_parallel, init_std=cfg.init_std,
                                                  dtype=dtype, device=device)
@@ -196,7 +197,7 @@ class ParallelMLP(nn.Module):
     def forward(self, x, residual=None):
         gu = self.gate_up_proj(x)
         y = self.down_proj(ops.swiglu(gu.reshape(-1, gu.shape[-1])), residual)
-        if not self.down_proj.sequence_parallel and x.dim() > 2:
+        if x.dim() > 2 and y.dim() == 2 and not self.sequence_parallel:
             y = y.reshape(*x.shape[:-1], y.shape[-1])
         return y
 
