@@ -115,9 +115,10 @@ def load_from_hf_checkpoint(model, path: str, strict: bool = False) -> Tuple[int
     return loaded, missing
 
 
-def hf_named_tensors(model, gather_tp: bool = True) -> Iterator[Tuple[str, torch.Tensor]]:
+def hf_named_tensors(model, gather_tp: bool = True, merge_lora: bool = False) -> Iterator[Tuple[str, torch.Tensor]]:
     """Yield ``(hf_name, full_tensor)`` for this stage's weights.  With TP>1 and ``gather_tp`` the
-    shards are all-gathered over the TP group so every rank sees full tensors."""
+    shards are all-gathered over the TP group so every rank sees full tensors.  ``merge_lora`` yields
+    ``W + scaling * B A`` for adapted projections, built out of place (the live base weights stay as they are)."""
     import torch.distributed as dist
 
     tp, group = model.tp_size, model.tp_group
@@ -131,23 +132,28 @@ def hf_named_tensors(model, gather_tp: bool = True) -> Iterator[Tuple[str, torch
         dist.all_gather(parts, t.contiguous(), group=group)
         return torch.cat(parts, dim=dim)
 
+    def weight_of(mod):
+        if merge_lora and hasattr(mod, "merged_weight"):
+            return mod.merged_weight()
+        return mod.weight.detach()
+
     if model.embed_tokens is not None:
         yield "model.embed_tokens.weight", model.embed_tokens.detach()
     for i, layer in enumerate(model.layers):
         g = f"model.layers.{model.layer_start + i}."
         hq, hk = layer.self_attn.heads_local * D, layer.self_attn.kv_heads_local * D
-        w = layer.self_attn.qkv_proj.weight.detach()
+        w = weight_of(layer.self_attn.qkv_proj)
         yield g + "self_attn.q_proj.weight", gather(w[:hq], 0)
         yield g + "self_attn.k_proj.weight", gather(w[hq:hq + hk], 0)
         yield g + "self_attn.v_proj.weight", gather(w[hq + hk:], 0)
-        yield g + "self_attn.o_proj.weight", gather(layer.self_attn.o_proj.weight.detach(), 1)
+        yield g + "self_attn.o_proj.weight", gather(weight_of(layer.self_attn.o_proj), 1)
         yield g + "self_attn.q_norm.weight", layer.self_attn.q_norm.weight.detach()
         yield g + "self_attn.k_norm.weight", layer.self_attn.k_norm.weight.detach()
-        gu = layer.mlp.gate_up_proj.weight.detach()
+        gu = weight_of(layer.mlp.gate_up_proj)
         il = gu.shape[0] // 2
         yield g + "mlp.gate_proj.weight", gather(gu[:il], 0)
         yield g + "mlp.up_proj.weight", gather(gu[il:], 0)
-        yield g + "mlp.down_proj.weight", gather(layer.mlp.down_proj.weight.detach(), 1)
+        yield g + "mlp.down_proj.weight", gather(weight_of(layer.mlp.down_proj), 1)
         yield g + "input_layernorm.weight", layer.input_layernorm.weight.detach()
         yield g + "post_attention_layernorm.weight", layer.post_attention_layernorm.weight.detach()
     if model.norm is not None:

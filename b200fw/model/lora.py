@@ -89,6 +89,25 @@ class LinearWithLoRA(nn.Module):
     def weight(self):
         return self.base.weight
 
+    @torch.no_grad()
+    def merged_weight(self) -> torch.Tensor:
+        """A new tensor ``W + sum_i scaling_i * B_i A_i`` (shard-local under TP); the frozen base weight is not
+        touched, as in the reference's export (src/distributed/lora.py:385-391).  A bf16 ``(W + d) - d`` does
+        not give back ``W`` bit for bit, so merging in place and undoing it would move the base a little on
+        every export."""
+        w = self.base.weight.detach().clone()
+        if self.merged:
+            return w
+        row = isinstance(self.base, RowParallelLinear)
+        for name, ad in self.adapters.items():
+            dw = ad.delta_weight().to(w.dtype)
+            if row:
+                w.add_(dw)
+            else:
+                s, e = self.ranges[name]
+                w[s:e].add_(dw)
+        return w
+
     def _stacked(self, dtype):
         """All adapters of this layer as one pair: ``A_cat [R, in]`` (adapters stacked along the rank
         dimension) and ``B_bd [out_local, R]`` (each adapter's B, times its scaling, in its own row range

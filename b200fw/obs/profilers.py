@@ -209,18 +209,25 @@ class ComputeProfiler:
 
     @staticmethod
     def exact_flops(cfg, B: int, S: int, full: bool = True, causal: bool = True,
-                    grad_checkpoint: bool = False) -> float:
-        """Matmul FLOPs of one training step's forward+backward: GQA-sized projections, SwiGLU FFN,
-        causal attention (S^2 terms halved), LM head."""
+                    grad_checkpoint: bool = False, supervised_fraction: float = 1.0,
+                    count_recompute: bool = False) -> float:
+        """Matmul FLOPs of one training step's forward+backward as the kernels execute them: GQA-sized
+        projections, SwiGLU FFN, causal attention (S^2 terms halved), and the LM head on the supervised rows
+        only (``supervised_fraction`` of the tokens: rows whose label is ignored never reach the LM head).
+        The forward pass that gradient checkpointing repeats is hardware work, not model work: it is added
+        only with ``count_recompute`` (use that figure for HFU, the default for MFU)."""
         T = B * S
         D = cfg.head_dim
         proj = cfg.hidden_size * D * (2 * cfg.num_heads + 2 * cfg.num_kv_heads)
         ffn = 3 * cfg.hidden_size * cfg.intermediate_size
         attn = 2 * S * cfg.num_heads * D * (0.5 if causal else 1.0)  # per token: QK^T and PV, MACs
-        per_tok = cfg.num_layers * (proj + ffn + attn) + cfg.hidden_size * cfg.vocab_size
-        fwd = 2.0 * T * per_tok
-        mult = (3 if full else 2) + (1 if grad_checkpoint else 0)
-        return fwd * mult
+        body = 2.0 * T * cfg.num_layers * (proj + ffn + attn)
+        head = 2.0 * T * supervised_fraction * cfg.hidden_size * cfg.vocab_size
+        mult = 3 if full else 2
+        total = (body + head) * mult
+        if grad_checkpoint and count_recompute:
+            total += body                                  # the layers' forward runs a second time
+        return total
 
     def compute_mfu(self, flops: float, step_s: float, n_gpus: int = 1) -> float:
         return flops / (step_s * n_gpus * self.peak_tflops * 1e12) if step_s > 0 else 0.0

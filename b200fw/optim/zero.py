@@ -151,11 +151,18 @@ class ZeROOptimizer:
         self._prefetch_hooks: List = []
         self._prefetch_first: List[int] = []      # buckets read before the first layer (embedding table)
         self._gather_order: List[int] = []        # bucket indices in the order the forward pass reads them
-        # "p2p": gradient reduce-scatter and parameter all-gather run inside the optimizer kernels
-        # through peer pointers (stage 1/2, bf16, CUDA, world <= 8); "nccl": library collectives.
-        self.p2p = (comm_backend == "p2p" and self.on_cuda and self.world > 1 and self.world <= 8
-                    and self.dtype == torch.bfloat16 and 1 <= self.stage <= 2)
+        # "p2p": gradient reduce-scatter and parameter all-gather run inside the optimizer kernels through peer
+        # pointers or NVLS multimem (stage 1/2, bf16, CUDA, 2..8 ranks of one node); "nccl": library collectives;
+        # "auto": p2p where it applies to a plain data-parallel layout, NCCL otherwise.
+        can_p2p = (self.on_cuda and 1 < self.world <= 8 and self.dtype == torch.bfloat16 and 1 <= self.stage <= 2)
+        if comm_backend == "auto":
+            pure_dp = ctx is None or (ctx.tp_size == 1 and ctx.pp_size == 1)
+            comm_backend = "p2p" if (can_p2p and pure_dp and self.stage == 1) else "nccl"
+        self.comm_backend = comm_backend
+        self.p2p = comm_backend == "p2p" and can_p2p
         self.flags = None
+        self._p2p_grad: Optional[torch.Tensor] = None
+        self._norm_ar = None
 
         # ---- bucket assignment: by TP kind, big ones split by size in reverse (backward) order -----
         by_kind: Dict[int, List[torch.nn.Parameter]] = {0: [], 1: [], 2: []}
@@ -194,13 +201,16 @@ class ZeROOptimizer:
             self._shard_view(self.master, i).copy_(src.float())
         self.exp_avg = torch.zeros_like(self.master)
         self.exp_avg_sq = torch.zeros_like(self.master)
-        self.grad_acc = torch.zeros_like(self.master) if self.stage >= 2 else None
+        self.grad_acc = torch.zeros_like(self.master) if (self.stage >= 2 and not self.p2p) else None
         self.grad_acc_filled = False
         self.hyper = torch.zeros(8, dtype=torch.float32, device=self.device)
         self._hyper_host = torch.zeros(8, dtype=torch.float32, pin_memory=self.on_cuda)
         self.norm_sq = torch.zeros(1, dtype=torch.float32, device=self.device)
         self._norm_parts = torch.zeros(2, dtype=torch.float32, device=self.device)
         self._reduced_shards: Dict[int, torch.Tensor] = {}
+        self._grad_norm_out = torch.zeros(1, dtype=torch.float32, device=self.device)
+        if self.p2p:
+            self._p2p_grad = torch.zeros_like(self.master)      # this rank's reduced (averaged) fp32 gradient shards
         self.param_groups = [{"lr": lr, "weight_decay": weight_decay, "betas": betas, "eps": eps}]
         if self.stage >= 3:
             self._release_params()
@@ -209,9 +219,8 @@ class ZeROOptimizer:
     # ---- peer-to-peer (in-kernel) communication ---------------------------------------------------
     def _make_symmetric(self):
         """Move every bucket's parameter and gradient storage into symmetric memory so that peers can
-        read gradients and write parameters directly."""
-        from ..dist.symm import FlagBarrier, SymmetricBuffer
-        self.overlap = False          # reduction happens inside step(), ordered by the flag barrier
+        read gradients and write parameters directly (or through the switch's multicast address)."""
+        from ..dist.symm import FlagBarrier, NormAllReduce, SymmetricBuffer
         for b in self.buckets:
             sp = SymmetricBuffer(b.numel, b.dtype, self.dp_group, self.device)
             sp.tensor.copy_(b.param_buf)
@@ -222,46 +231,58 @@ class ZeROOptimizer:
             b.grad_buf = sg.tensor
             b.symm_grad = sg
             b.persistent_grad = True
-        self.flags = FlagBarrier(self.dp_group, self.device)
-        self._p2p_grad = None
+        nb = len(self.buckets)
+        # channel i: "bucket i's gradients are complete on every rank"; nb: end of step; nb + 1: norm exchange
+        self.flags = FlagBarrier(self.dp_group, self.device, channels=max(8, nb + 2))
+        self._ch_step_end, self._ch_norm = nb, nb + 1
+        self._norm_ar = NormAllReduce(self.flags, self.dp_group, self._ch_norm, self.device)
+        self.nvls = all(b.symm_grad.mc_ptr and b.symm_param.mc_ptr for b in self.buckets)
 
-    def _p2p_reduce(self):
-        """All ranks' backward passes are complete (flag barrier), then every rank sums its shard of
-        each bucket straight out of the peers' gradient buffers."""
+    def _p2p_reduce_bucket(self, b: _Bucket, idx: int):
+        """Runs on the current stream: wait (bounded, on the device) until every rank has finished writing bucket
+        ``idx``, then sum this rank's shard out of all ranks' gradient buckets, scale by 1/world, keep it as fp32
+        and add its squared norm to the step's partial sums.  One barrier launch + one reduce launch; both are
+        CUDA-graph capturable (the barrier's epoch lives on the device)."""
         from .. import _native as nv
         import ctypes
-        if self._p2p_grad is None:
-            self._p2p_grad = torch.empty_like(self.master)
-        self.flags.barrier(0)
-        self._norm_parts.zero_()
-        inv = 1.0 / self.world
         L = nv.lib()
-        for i, b in enumerate(self.buckets):
-            if b.kind == KIND_TP_PARTIAL and self._tp_group() is not None:
-                dist.all_reduce(b.grad_buf, group=self._tp_group())
-            out = self._shard_view(self._p2p_grad, i)
-            norm = self._norm_parts[1:2] if b.kind == KIND_TP_SHARDED else self._norm_parts[0:1]
+        if b.kind == KIND_TP_PARTIAL and self._tp_group() is not None:
+            dist.all_reduce(b.grad_buf, group=self._tp_group())
+        self.flags.barrier_dev(idx)
+        out = self._shard_view(self._p2p_grad, idx)
+        norm = self._norm_parts[1:2] if b.kind == KIND_TP_SHARDED else self._norm_parts[0:1]
+        inv = 1.0 / self.world
+        if self.nvls:
+            nv.check(L.b2_zero_reduce_shard_mc(ctypes.c_void_p(b.symm_grad.mc_ptr), ctypes.c_longlong(b.shard_start),
+                                               ctypes.c_longlong(b.shard_numel), ctypes.c_float(inv), nv.ptr(out), 0,
+                                               nv.ptr(norm), nv.stream_ptr()), "zero_reduce_shard_mc")
+        else:
             nv.check(L.b2_zero_reduce_shard(b.symm_grad.ptr_array, self.world, ctypes.c_longlong(b.shard_start),
                                             ctypes.c_longlong(b.shard_numel), ctypes.c_float(inv), nv.ptr(out), 0,
                                             nv.ptr(norm), nv.stream_ptr()), "zero_reduce_shard")
-            nv.count_launch()
-            b.reduced = True
+        nv.count_launch()
 
     def _p2p_step(self, use_norm: bool):
+        """Clip + AdamW on the owned shards with the updated bf16 values stored into every rank's parameter bucket
+        (one multimem store through the switch, or one store per peer), then the end-of-step barrier: every peer's
+        parameter writes have landed, and every peer has finished reading this rank's gradient buckets, before the
+        next forward / backward touches either.  A bounded wait that ran out earlier in the step cleared
+        ``flags.ok_dev``; the kernel then leaves masters, moments and parameters as they are."""
         from .. import _native as nv
         import ctypes
         L = nv.lib()
         for i, b in enumerate(self.buckets):
-            nv.check(L.b2_zero_adamw_publish(nv.ptr(self._shard_view(self.master, i)),
-                                             nv.ptr(self._shard_view(self.exp_avg, i)),
-                                             nv.ptr(self._shard_view(self.exp_avg_sq, i)),
-                                             nv.ptr(self._shard_view(self._p2p_grad, i)),
-                                             ctypes.c_longlong(b.shard_numel), nv.ptr(self.hyper),
-                                             nv.ptr(self.norm_sq if use_norm else None), b.symm_param.ptr_array,
-                                             self.world, ctypes.c_longlong(b.shard_start), nv.stream_ptr()),
-                     "zero_adamw_publish")
+            mc = ctypes.c_void_p(b.symm_param.mc_ptr if self.nvls else 0)
+            nv.check(L.b2_zero_adamw_publish2(nv.ptr(self._shard_view(self.master, i)),
+                                              nv.ptr(self._shard_view(self.exp_avg, i)),
+                                              nv.ptr(self._shard_view(self.exp_avg_sq, i)),
+                                              nv.ptr(self._shard_view(self._p2p_grad, i)),
+                                              ctypes.c_longlong(b.shard_numel), nv.ptr(self.hyper),
+                                              nv.ptr(self.norm_sq if use_norm else None), b.symm_param.ptr_array, mc,
+                                              self.world, ctypes.c_longlong(b.shard_start), nv.ptr(self.flags.ok_dev),
+                                              nv.stream_ptr()), "zero_adamw_publish2")
             nv.count_launch()
-        self.flags.barrier(1)     # every peer's parameter writes have landed before the next forward
+        self.flags.barrier_dev(self._ch_step_end)
 
     # ---- helpers -----------------------------------------------------------------------------
     def _shard_view(self, flat: torch.Tensor, i: int) -> torch.Tensor:
@@ -285,7 +306,7 @@ class ZeROOptimizer:
         passes write the gradients before they may be reduced (the micro-batches of a pipeline schedule):
         a bucket's reduce-scatter is launched from the gradient hooks once every parameter in it has
         received all of its contributions."""
-        self.sync_this_backward = sync or self.stage >= 2
+        self.sync_this_backward = sync or (self.stage >= 2 and not self.p2p)
         for b in self.buckets:
             b.pending = b.contribs * max(1, int(backward_passes))
 
@@ -309,6 +330,13 @@ class ZeROOptimizer:
             import contextlib
             stream_ctx = contextlib.nullcontext()
         with stream_ctx:
+            if self.p2p:
+                self._p2p_reduce_bucket(b, idx)
+                if async_op:
+                    b.work = torch.cuda.Event()
+                    b.work.record(self.comm_stream)
+                b.reduced = True
+                return
             if b.kind == KIND_TP_PARTIAL and self._tp_group() is not None:
                 dist.all_reduce(b.grad_buf, group=self._tp_group())
             if self.world > 1 and self.stage == 0:
@@ -513,6 +541,8 @@ class ZeROOptimizer:
 
     # ---- norm / step ---------------------------------------------------------------------------
     def _grad_shard(self, i: int) -> torch.Tensor:
+        if self.p2p:
+            return self._shard_view(self._p2p_grad, i)
         if self.stage >= 2:
             return self._shard_view(self.grad_acc, i)
         if self.stage == 0 or self.world == 1:
@@ -527,8 +557,11 @@ class ZeROOptimizer:
             self.max_grad_norm = max_norm
         inv = 1.0 / self.world
         if self.p2p:
-            if not all(b.reduced for b in self.buckets):
-                self._p2p_reduce()
+            self._reduce_all()
+            if self._tp_group() is None and (self.ctx is None or self.ctx.pp_size == 1):
+                # plain data parallelism: the ranks' partial sums are exchanged and added by one kernel
+                self._norm_ar(self._norm_parts, self.norm_sq, self._grad_norm_out)
+                return self._grad_norm_out[0]
             parts = self._norm_parts.clone()        # already of the averaged gradient
         else:
             if self.stage < 2:
@@ -563,8 +596,7 @@ class ZeROOptimizer:
         """AdamW on the owned shards (clipped by the norm armed in ``clip_grad_norm``; skipped on the
         device when that norm is not finite), then publish the updated bf16 parameters."""
         if self.p2p:
-            if not all(b.reduced for b in self.buckets):
-                self._p2p_reduce()
+            self._reduce_all()
             self._write_hyper()
             self._p2p_step(use_norm)
             self.step_count += 1
@@ -592,13 +624,16 @@ class ZeROOptimizer:
             if out is not None and out_arg is None:
                 out.copy_(self._shard_view(self.master, i).to(out.dtype))
             if gather and self.stage < 3:
-                dist.all_gather_into_tensor(b.param_buf, b.param_shard().clone(), group=self.dp_group)
+                # in place: this rank's shard already sits at its own offset of the output (NCCL's in-place form)
+                dist.all_gather_into_tensor(b.param_buf, b.param_shard(), group=self.dp_group)
         self.step_count += 1
 
     def zero_grad(self, set_to_none: bool = True):
         self.accumulation_count = 0
         self.grad_acc_filled = False
         self._reduced_shards.clear()
+        if self.p2p:
+            self._norm_parts.zero_()        # the reduce kernels of the next step add their squared norms here
         for b in self.buckets:
             for p in b.params:
                 p.grad = None

@@ -330,9 +330,8 @@ class ColocateOrchestrator:
             subs = self.c3po.split_and_pack(prompts, ro.responses, rewards, adv)
             m = None
             for i, sb in enumerate(subs):
-                m = eng.grpo_step(**sb, skip_optimizer_step=(i < len(subs) - 1),
-                                  reset_behavior_baseline=True)
-                eng._accumulation_count = cfg.gradient_accumulation_steps if i == len(subs) - 2 else eng._accumulation_count
+                last = i == len(subs) - 1
+                m = eng.grpo_step(**sb, skip_optimizer_step=not last, reset_behavior_baseline=True, close_window=last)
             return m
         m = None
         for s in range(cfg.train_steps_per_iteration):

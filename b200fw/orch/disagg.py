@@ -241,9 +241,8 @@ class DisaggOrchestrator:
             subs = sched.split_and_pack(P, R, rewards, adv)
             m = None
             for i, sb in enumerate(subs):
-                m = eng.grpo_step(**sb, skip_optimizer_step=(i < len(subs) - 1), reset_behavior_baseline=True)
-                if i == len(subs) - 2:
-                    eng._accumulation_count = eng.config.gradient_accumulation_steps
+                last = i == len(subs) - 1
+                m = eng.grpo_step(**sb, skip_optimizer_step=not last, reset_behavior_baseline=True, close_window=last)
         else:
             m = eng.grpo_step(P, R, rewards)
         self._last_reward = sum(x for g in rewards for x in g) / max(1, sum(len(g) for g in rewards))

@@ -124,6 +124,7 @@ class TrainEngine:
         self._graph_pool = None
         self._graph_seen: Dict[tuple, int] = {}
         self._graph_disabled = False
+        self.last_h2d_bytes = 0                       # bytes the last sft_step_tensors call copied host -> device
 
     # =============================================================================================
     def initialize(self, parallel_context: Optional[ParallelContext] = None):
@@ -223,31 +224,40 @@ class TrainEngine:
             return prompt[:keep], response[:L - keep]
         return prompt[:L - len(response)], response
 
-    def _to_device(self, name: str, rows: List[List[int]], fill: int) -> torch.Tensor:
-        """Pad ``rows`` to a rectangle in a reusable pinned host buffer and copy it to the device."""
+    def _pinned_buf(self, name: str, numel: int) -> torch.Tensor:
+        """A reusable pinned int64 staging buffer (page-locking memory per call costs more than the copy)."""
+        buf = self._pinned.get(name)
+        if buf is None or buf.numel() < numel:
+            buf = torch.empty(max(numel, 1), dtype=torch.long, pin_memory=True)
+            self._pinned[name] = buf
+        return buf[:numel]
+
+    def _to_device(self, name: str, rows: List[List[int]], fill: int, on_host: bool = False) -> torch.Tensor:
+        """Pad ``rows`` to a rectangle in a reusable pinned host buffer and copy it to the device
+        (``on_host``: hand back the pinned view itself; the caller copies)."""
         n, m = len(rows), max(len(r) for r in rows)
         if self.device.type != "cuda":
             t = torch.full((n, m), fill, dtype=torch.long)
             for i, r in enumerate(rows):
                 t[i, :len(r)] = torch.tensor(r, dtype=torch.long)
             return t
-        buf = self._pinned.get(name)
-        if buf is None or buf.numel() < n * m:
-            buf = torch.empty(max(n * m, 1), dtype=torch.long, pin_memory=True)
-            self._pinned[name] = buf
-        view = buf[:n * m].view(n, m)
-        view.fill_(fill)
-        for i, r in enumerate(rows):
-            view[i, :len(r)] = torch.tensor(r, dtype=torch.long)
-        return view.to(self.device, non_blocking=True)
+        view = self._pinned_buf(name, n * m).view(n, m)
+        if all(len(r) == m for r in rows):
+            view.copy_(torch.tensor(rows, dtype=torch.long))          # one conversion for a rectangular batch
+        else:
+            view.fill_(fill)
+            for i, r in enumerate(rows):
+                view[i, :len(r)] = torch.tensor(r, dtype=torch.long)
+        return view if on_host else view.to(self.device, non_blocking=True)
 
-    def _build_batch(self, prompts: List[List[int]], responses: List[List[int]]):
+    def _build_batch(self, prompts: List[List[int]], responses: List[List[int]], on_host: bool = False):
         ids, labels = [], []
         for p, r in zip(prompts, responses):
             p, r = self._truncate_prompt_response(list(p), list(r))
             ids.append(p + r)
             labels.append([-100] * len(p) + r)
-        return self._to_device("ids", ids, self.config.pad_token_id), self._to_device("labels", labels, -100)
+        return (self._to_device("ids", ids, self.config.pad_token_id, on_host),
+                self._to_device("labels", labels, -100, on_host))
 
     # ---- optimizer step --------------------------------------------------------------------------
     def _maybe_step(self, skip: bool = False):
@@ -265,12 +275,26 @@ class TrainEngine:
         self._accumulation_count = 0
         return gn
 
+    def _check_device_status(self):
+        """Read the kernels' status word once per optimizer step, at a host sync that exists anyway.  A bounded
+        device wait that ran out (a peer's gradient flag, a GEMM / attention pipeline barrier) leaves a code
+        there and returns; without this check training would go on over whatever the abandoned kernel left."""
+        if self.device.type != "cuda":
+            return
+        from .. import _native as nv
+        st = nv.read_status()
+        if st != 0:
+            raise nv.NativeError(f"device status {st} after optimizer step {self.step_count}: a bounded wait in a "
+                                 "kernel ran out (301: a peer's flag never arrived; 1xx/2xx: a pipeline barrier); "
+                                 "the update of this step is not trustworthy")
+
     def _finish_step(self, gn: Optional[torch.Tensor]) -> float:
         """Host side of the NaN/Inf guard: a non-finite norm (reported as -1) means the device skipped
         the update, so neither the step counter nor the schedule advance."""
         if gn is None:
             return 0.0
         g = float(gn)
+        self._check_device_status()
         if g < 0:
             logger.warning("non-finite gradient norm: optimizer step skipped")
             self.optimizer.step_count -= 1
@@ -284,7 +308,9 @@ class TrainEngine:
     # =============================================================================================
     def sft_step(self, prompts_tokens: List[List[int]], response_tokens: List[List[int]]) -> TrainMetrics:
         """Teacher-forced SFT step; prompt positions are not supervised."""
-        ids, labels = self._build_batch(prompts_tokens, response_tokens)
+        # on a GPU the batch stays in pinned host memory until sft_step_tensors ships it together with the
+        # supervised-row indices (known on the host, so the LM head needs no device -> host count)
+        ids, labels = self._build_batch(prompts_tokens, response_tokens, on_host=self.device.type == "cuda")
         return self.sft_step_tensors(ids, labels)
 
     def sft_step_tensors(self, input_ids: torch.Tensor, labels: torch.Tensor, sync: bool = True):
@@ -299,7 +325,13 @@ class TrainEngine:
                 nxt[:, :-1] = labels[:, 1:]
                 idx = torch.nonzero(nxt.reshape(-1) != -100).squeeze(-1)
                 if idx.numel() < nxt.numel():
-                    valid_idx = idx.pin_memory().to(self.device, non_blocking=True)
+                    if sync:    # this call ends with a host sync, so the staging buffer is free again next call
+                        stage = self._pinned_buf("valid_idx", idx.numel())
+                        stage.copy_(idx)
+                    else:
+                        stage = idx.pin_memory()
+                    valid_idx = stage.to(self.device, non_blocking=True)
+                self.last_h2d_bytes = 8 * (input_ids.numel() + labels.numel() + (idx.numel() if valid_idx is not None else 0))
             input_ids = input_ids.to(self.device, non_blocking=True)
             labels = labels.to(self.device, non_blocking=True)
         if self.pp_context is not None and self.pp_context.pp_size > 1:
@@ -307,7 +339,7 @@ class TrainEngine:
         else:
             loss, gn = self._single_batch_step(input_ids, labels, valid_idx)
         if not sync:
-            if gn is not None:   # optimistic bookkeeping; call resolve_step(gn) to apply the NaN guard
+            if gn is not None:   # optimistic bookkeeping; resolve_step(gn) applies the NaN guard later
                 self.lr_scheduler.step()
                 self.step_count += 1
             return loss, gn
@@ -318,6 +350,36 @@ class TrainEngine:
             self.metrics_collector.record("learning_rate", lr)
             self.metrics_collector.record("loss", lv)
         return TrainMetrics(lv, lv, 0.0, g, lr, self.step_count)
+
+    def resolve_step(self, gn: Optional[torch.Tensor]) -> float:
+        """Settle one ``sft_step_tensors(..., sync=False)`` optimizer step after the fact (this synchronises):
+        reads the norm, checks the device status word, and when the norm was not finite (the device skipped
+        AdamW) takes back the optimistic bookkeeping: the optimizer's bias-correction step, the schedule and
+        the step counter.  Call it in step order, before the learning rate of a later step matters.  Returns the
+        gradient norm (``-1`` for a skipped step, ``0`` when ``gn`` is ``None``: no optimizer step happened)."""
+        if gn is None:
+            return 0.0
+        g = float(gn)
+        self._check_device_status()
+        if g < 0:
+            logger.warning("non-finite gradient norm: optimizer step skipped")
+            self.optimizer.step_count = max(0, self.optimizer.step_count - 1)
+            self.lr_scheduler.step_count = max(0, self.lr_scheduler.step_count - 1)
+            self.step_count = max(0, self.step_count - 1)
+        elif self.metrics_collector is not None:
+            self.metrics_collector.record("grad_norm", g)
+        return g
+
+    def close_accumulation_window(self) -> TrainMetrics:
+        """Run the optimizer step now, over however many micro-batches have been accumulated (C3PO++ packs a
+        batch into a variable number of chunks; the last chunk closes the window).  No-op when nothing is
+        pending."""
+        lr = self.lr_scheduler.get_last_lr()[0]
+        if self._accumulation_count == 0:
+            return TrainMetrics(0.0, 0.0, 0.0, 0.0, lr, self.step_count)
+        self._accumulation_count = max(self._accumulation_count, self.config.gradient_accumulation_steps)
+        g = self._finish_step(self._maybe_step())
+        return TrainMetrics(0.0, 0.0, 0.0, g, lr, self.step_count)
 
     def _single_batch_step(self, input_ids, labels, valid_idx=None):
         cfg, opt = self.config, self.optimizer
@@ -499,9 +561,12 @@ class TrainEngine:
     def grpo_step(self, prompts_tokens: List[List[int]], responses_group: List[List[List[int]]],
                   rewards_group: List[List[float]], infer_log_probs: Optional[torch.Tensor] = None,
                   skip_optimizer_step: bool = False, reset_behavior_baseline: bool = True,
-                  precomputed_advantages: Optional[List[List[float]]] = None) -> TrainMetrics:
+                  precomputed_advantages: Optional[List[List[float]]] = None,
+                  close_window: bool = False) -> TrainMetrics:
         """One GRPO step over ``batch x K`` sequences: group-relative advantages, clipped token-level
-        surrogate against the behaviour log-probs, KL to the frozen reference, optional IcePop."""
+        surrogate against the behaviour log-probs, KL to the frozen reference, optional IcePop.
+        ``close_window`` makes this backward the last of the accumulation window whatever the count says
+        (C3PO++ packs a batch into a variable number of chunks and closes the window on the last one)."""
         assert self.pp_context is None or self.pp_context.pp_size == 1, "GRPO needs pp_size == 1"
         cfg, opt = self.config, self.optimizer
         if reset_behavior_baseline:
@@ -518,6 +583,8 @@ class TrainEngine:
         adv_t = torch.tensor(A, dtype=torch.float32).to(self.device, non_blocking=True)
         mask = (labels[:, 1:] != -100).float()
         opt.pre_forward(lazy=True)
+        if close_window:
+            self._accumulation_count = max(self._accumulation_count, cfg.gradient_accumulation_steps - 1)
         opt.begin_backward(sync=self._accumulation_count + 1 >= cfg.gradient_accumulation_steps)
         lp = self.model.token_logprobs(ids, labels=labels)
         self.last_icepop_info = {}
@@ -614,14 +681,10 @@ class TrainEngine:
         """HF-named full weights with LoRA merged (TP shards gathered); stage-3 gathers first."""
         from ..model.hf_io import hf_named_tensors
         with self.optimizer.eval_mode():
-            has_lora = any(isinstance(m, LinearWithLoRA) for m in self.model.modules())
-            if has_lora:
-                merge_lora_weights(self.model)
-            try:
-                out = {k: (v.to(device) if device else v).clone() for k, v in hf_named_tensors(self.model)}
-            finally:
-                if has_lora:
-                    merge_lora_weights(self.model, unmerge=True)
+            # merged tensors are built out of place: the frozen base weights (also the KL reference under LoRA)
+            # must come out of an export bit-identical
+            out = {k: (v.to(device) if device else v).clone()
+                   for k, v in hf_named_tensors(self.model, merge_lora=True)}
         return out
 
     @torch.no_grad()

@@ -14,7 +14,6 @@ from __future__ import annotations
 import argparse
 import json
 import os
-import subprocess
 import sys
 import threading
 
@@ -22,6 +21,8 @@ import torch
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
+
+from b200fw.obs.clocks import ClockSampler  # noqa: E402
 
 
 def parse():
@@ -54,55 +55,6 @@ def parse():
     ap.add_argument("--fused-tp", action="store_true",
                     help="run the sequence-parallel collectives inside the GEMM kernels (peer memory) instead of NCCL")
     return ap.parse_args()
-
-
-class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
-
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
-
-    def __init__(self, index: int):
-        self.index, self.samples, self.proc = index, [], None
-
-    def start(self):
-        try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
-                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            threading.Thread(target=self._read, daemon=True).start()
-        except OSError:
-            self.proc = None
-
-    def _read(self):
-        for line in self.proc.stdout:
-            self.samples.append(line.strip())
-
-    def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()   # the exact child started above
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, mx, reasons = [], None, set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for s in self.samples:
-            parts = [p.strip() for p in s.split(",")]
-            if len(parts) < 6:
-                continue
-            try:
-                sm.append(float(parts[0]))
-                mx = float(parts[1])
-            except ValueError:
-                continue
-            for n, v in zip(names, parts[2:6]):
-                if v.lower().startswith("active"):
-                    reasons.add(n)
-        sm.sort()
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
-                "samples": len(sm)}
 
 
 def synthetic_batches(vocab, micro_batch, seq, count, seed, pinned):
@@ -157,6 +109,9 @@ def run_ours(a):
     n_micro = (a.warmup + a.steps) * accum
     host = synthetic_batches(mc.vocab_size, a.micro_batch, a.seq_len, accum * 2, 1234 + eng.parallel_ctx.dp_rank, True)
     on_dev = [(i.to(dev), l.to(dev)) for i, l in host]
+    # the same batches as the token lists the public step takes (prompt = unsupervised half, response = the rest)
+    half = a.seq_len // 2
+    as_lists = [([r[:half].tolist() for r in i], [r[half:].tolist() for r in i]) for i, _ in host]
 
     def micro_dev(k):
         ids, labels = on_dev[k % len(on_dev)]
@@ -188,14 +143,20 @@ def run_ours(a):
     ms = max_over_ranks(s.elapsed_time(e), world, dev)
     launches = nv.launch_count - launches0
     status = nv.read_status()
-    # ---- end to end: pinned host -> device copy of every micro-batch, loss read back every step -------
+    # ---- end to end through the public step: TrainEngine.sft_step(prompt token lists, response token lists),
+    # the call the orchestrators make.  Inside it, every micro-batch: lists -> pinned host buffer -> device copy
+    # (ids, labels, supervised-row indices), and the loss (and the gradient norm on optimizer steps) read back.
     barrier()
     s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     s2.record()
-    last_loss = 0.0
+    last_loss, h2d = 0.0, 0
     for k in range(a.steps * micro_per_step):
-        ids, labels = host[k % len(host)]
-        m = eng.sft_step_tensors(ids, labels, sync=True)   # H2D inside; float(loss) is the D2H read
+        if a.pp > 1:
+            ids, labels = host[k % len(host)]
+            m = eng.sft_step_tensors(ids, labels, sync=True)
+        else:
+            m = eng.sft_step(*as_lists[k % len(as_lists)])
+        h2d += eng.last_h2d_bytes
         last_loss = m.loss
     e2.record()
     barrier()
@@ -205,8 +166,14 @@ def run_ours(a):
     tokens_per_step = a.micro_batch * a.seq_len * micro_per_step * dp * (a.grad_accum if a.pp > 1 and False else 1)
     tps = tokens_per_step * a.steps / (ms * 1e-3)
     tps_e2e = tokens_per_step * a.steps / (ms_e2e * 1e-3)
-    flops = ComputeProfiler.exact_flops(mc, a.micro_batch * micro_per_step * dp, a.seq_len, full=a.lora_rank <= 0,
-                                        grad_checkpoint=a.grad_ckpt)
+    # executed FLOPs: the LM head runs on the supervised rows only (half of every sequence here); the forward
+    # that gradient checkpointing repeats counts for hardware utilisation (HFU), not for model FLOPs (MFU)
+    sup = (a.seq_len - a.seq_len // 2) / a.seq_len
+    gb = a.micro_batch * micro_per_step * dp
+    flops = ComputeProfiler.exact_flops(mc, gb, a.seq_len, full=a.lora_rank <= 0, grad_checkpoint=a.grad_ckpt,
+                                        supervised_fraction=sup)
+    flops_hw = ComputeProfiler.exact_flops(mc, gb, a.seq_len, full=a.lora_rank <= 0, grad_checkpoint=a.grad_ckpt,
+                                           supervised_fraction=sup, count_recompute=True)
     peaks = measured_peaks()
     step_s = ms * 1e-3 / a.steps
     if rank == 0:
@@ -225,22 +192,26 @@ def run_ours(a):
                        "sequence_parallel": a.sequence_parallel, "fused_tp_comm": a.fused_tp, "grad_ckpt": a.grad_ckpt,
                        "cuda_graph_step": a.cuda_graph, "cuda_graph_reduce": a.graph_reduce, "l2": "inputs larger than L2 (weights+activations >> 126 MB)",
                        "step": "one optimizer step = grad_accum micro-batches + reduce + clip + AdamW"},
-            "mfu_exact_of_measured_sustained": flops / (step_s * world * peaks["bf16_tflops_sustained"] * 1e12),
+            "mfu_model_of_measured_sustained": flops / (step_s * world * peaks["bf16_tflops_sustained"] * 1e12),
+            "hfu_of_measured_sustained": flops_hw / (step_s * world * peaks["bf16_tflops_sustained"] * 1e12),
             "model_tflops_per_gpu": flops / step_s / world / 1e12,
+            "flops_note": "LM head counted on the supervised rows only; hfu adds the checkpoint recompute",
             "e2e": {"value": tps_e2e, "unit": "tokens/s", "ms_per_step": ms_e2e / a.steps,
-                    "h2d_bytes_per_step": 2 * a.micro_batch * a.seq_len * 8 * micro_per_step,
-                    "d2h_bytes_per_step": 8, "final_loss": last_loss},
+                    "h2d_bytes_per_step": h2d // a.steps,
+                    "d2h_bytes_per_step": 4 * micro_per_step + 8, "final_loss": last_loss,
+                    "api": "TrainEngine.sft_step(prompt token lists, response token lists)" if a.pp == 1
+                           else "TrainEngine.sft_step_tensors(pinned host tensors)"},
             "gpu_launches": launches, "device_status": status, "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
-    # the result is out: a teardown that does not finish must not hold the launcher
-    guard = threading.Timer(60.0, os._exit, (0,))
+    # the result is out; a teardown that hangs or raises still fails the run (exit code 3 / the exception)
+    def _hung():
+        print("[bench] teardown did not finish within 120 s", file=sys.stderr, flush=True)
+        os._exit(3)
+    guard = threading.Timer(120.0, _hung)
     guard.daemon = True
     guard.start()
-    try:
-        eng.parallel_ctx.destroy()
-    except Exception as e:  # noqa: BLE001 - the measurement is complete; a teardown error must not fail the run
-        print(f"[bench] teardown: {e}", file=sys.stderr)
+    eng.parallel_ctx.destroy()
     guard.cancel()
 
 

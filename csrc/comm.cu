@@ -382,6 +382,277 @@ B2_EXPORT int b2_flag_wait(const int* flag, int value, int limit_ms, int* result
 }
 
 namespace b2 {
+
+// ---- multimem (NVLS) forms: one instruction addresses every GPU bound to the multicast object --------------
+// Sum over all GPUs of 8 bf16 at the same offset, accumulated in fp32 inside the switch.
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc) {
+  uint4 r;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(mc) : "memory");
+  return r;
+}
+// 16 bytes stored at the same offset of every GPU's buffer (this GPU's own included).
+__device__ __forceinline__ void multimem_st_16B(void* mc, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(mc), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w) : "memory");
+}
+
+// Group barrier in one launch with the epoch kept on the device, so the launch can sit inside a CUDA graph:
+// epoch = ++epochs[channel]; every peer's slot [my_rank][channel] = epoch (release, system scope); then wait,
+// bounded, until every source's slot in this rank's own buffer has reached the epoch.  All ranks call it the same
+// number of times per channel, so their epochs agree.  ok[0] is cleared (and stays cleared until the host resets
+// it) when a wait runs out; the status word records ERR_COMM_FLAG_WAIT.
+__global__ void flag_barrier_kernel(PeerPtrs flag_bufs, const int* my_flags, int* epochs, int world, int my_rank,
+                                    int channels, int channel, unsigned long long limit_ns, int* ok, int* status) {
+  const int lane = threadIdx.x;
+  int e = 0;
+  if (lane == 0) {
+    e = epochs[channel] + 1;
+    epochs[channel] = e;
+  }
+  e = __shfl_sync(0xffffffffu, e, 0);
+  __threadfence_system();
+  bool failed = false;
+  if (lane < world) {
+    st_release_sys(static_cast<int*>(flag_bufs.p[lane]) + my_rank * channels + channel, e);
+    const unsigned long long t0 = globaltimer_ns();
+    for (;;) {
+      if (ld_acquire_sys(my_flags + lane * channels + channel) >= e) break;
+      if (globaltimer_ns() - t0 > limit_ns) {
+        failed = true;
+        break;
+      }
+      __nanosleep(100);
+    }
+  }
+  if (__any_sync(0xffffffffu, failed) && lane == 0) {
+    ok[0] = 0;
+    atomicCAS(status, 0, ERR_COMM_FLAG_WAIT);
+  }
+}
+
+// Reduce-scatter through the switch: out[i] = scale * sum over GPUs of bucket[shard_start + i], one
+// multimem.ld_reduce per 8 elements instead of one load per peer.
+__global__ void zero_reduce_shard_mc_kernel(const __nv_bfloat16* __restrict__ mc_bucket, long long shard_start,
+                                            long long n, float scale, float* __restrict__ out, int accumulate,
+                                            float* __restrict__ norm_sq) {
+  float ss = 0.f;
+  const long long nvec = n / 8;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const uint4 q = multimem_ld_reduce_bf16x8(mc_bucket + shard_start + i * 8);
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+    float4* o = reinterpret_cast<float4*>(out + i * 8);
+    float pv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (accumulate) {
+      const float4 p0 = o[0], p1 = o[1];
+      pv[0] = p0.x; pv[1] = p0.y; pv[2] = p0.z; pv[3] = p0.w; pv[4] = p1.x; pv[5] = p1.y; pv[6] = p1.z; pv[7] = p1.w;
+    }
+    float r[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = unpack_bf16x2(w[j]);
+      r[2 * j] = f.x * scale + pv[2 * j];
+      r[2 * j + 1] = f.y * scale + pv[2 * j + 1];
+      ss += r[2 * j] * r[2 * j] + r[2 * j + 1] * r[2 * j + 1];
+    }
+    o[0] = make_float4(r[0], r[1], r[2], r[3]);
+    o[1] = make_float4(r[4], r[5], r[6], r[7]);
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0 && norm_sq) atomicAdd(norm_sq, ss);
+}
+
+// All-reduce of the two squared-norm partial sums (replicated / TP-sharded parameters) of a data-parallel group in
+// one launch: every rank stores its pair into every peer's slot [parity][my_rank], a barrier (as above) orders the
+// stores, then each rank sums the slots.  norm_sq[0] = total; grad_norm[0] = sqrt(total), or -1 when not finite.
+// Slots are double-buffered by epoch parity: a rank that is one step ahead writes the other half.
+__global__ void norm_allreduce_kernel(PeerPtrs slot_bufs, const float* my_slots, PeerPtrs flag_bufs,
+                                      const int* my_flags, int* epochs, int world, int my_rank, int channels,
+                                      int channel, const float* parts, float* norm_sq, float* grad_norm,
+                                      unsigned long long limit_ns, int* ok, int* status) {
+  const int lane = threadIdx.x;
+  int e = 0;
+  if (lane == 0) {
+    e = epochs[channel] + 1;
+    epochs[channel] = e;
+  }
+  e = __shfl_sync(0xffffffffu, e, 0);
+  const int half = (e & 1) * 16;      // [2 halves][8 ranks][2 floats]
+  bool failed = false;
+  if (lane < world) {
+    float* dst = static_cast<float*>(slot_bufs.p[lane]) + half + my_rank * 2;
+    dst[0] = parts[0];
+    dst[1] = parts[1];
+    __threadfence_system();
+    st_release_sys(static_cast<int*>(flag_bufs.p[lane]) + my_rank * channels + channel, e);
+    const unsigned long long t0 = globaltimer_ns();
+    for (;;) {
+      if (ld_acquire_sys(my_flags + lane * channels + channel) >= e) break;
+      if (globaltimer_ns() - t0 > limit_ns) {
+        failed = true;
+        break;
+      }
+      __nanosleep(100);
+    }
+  }
+  failed = __any_sync(0xffffffffu, failed);
+  float mine = 0.f;
+  if (lane < world) {
+    const volatile float* src = my_slots + half + lane * 2;
+    mine = src[0] + src[1];
+  }
+  mine = warp_sum(mine);
+  if (lane == 0) {
+    if (failed) {
+      ok[0] = 0;
+      atomicCAS(status, 0, ERR_COMM_FLAG_WAIT);
+    }
+    norm_sq[0] = mine;
+    const float g = sqrtf(mine);
+    grad_norm[0] = isfinite(g) ? g : -1.f;
+  }
+}
+
+// AdamW + publish through the switch: one multimem.st writes the updated bf16 values into every GPU's bucket.
+// `ok` (nullable): when it reads 0 (an earlier bounded wait of this step ran out) the update is skipped.
+__global__ void zero_adamw_publish_any_kernel(float* __restrict__ master, float* __restrict__ m,
+                                              float* __restrict__ v, const float* __restrict__ grad, long long n,
+                                              const float* __restrict__ hyper, const float* __restrict__ norm_sq,
+                                              PeerPtrs params, __nv_bfloat16* mc_params, int world,
+                                              long long shard_start, const int* __restrict__ ok) {
+  const float lr = hyper[0], b1 = hyper[1], b2 = hyper[2], eps = hyper[3], wd = hyper[4];
+  const float bc1 = hyper[5], bc2 = hyper[6], max_norm = hyper[7];
+  float clip = 1.f;
+  bool skip = ok != nullptr && ok[0] == 0;
+  if (norm_sq != nullptr) {
+    const float ns = norm_sq[0];
+    if (!isfinite(ns)) skip = true;
+    else if (max_norm > 0.f) clip = fminf(1.f, max_norm / (sqrtf(ns) + 1e-6f));
+  }
+  const long long nvec = n / 8;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float4* mp = reinterpret_cast<float4*>(master + i * 8);
+    float4* mm = reinterpret_cast<float4*>(m + i * 8);
+    float4* mv = reinterpret_cast<float4*>(v + i * 8);
+    const float4* mg = reinterpret_cast<const float4*>(grad + i * 8);
+    float4 pw[2] = {mp[0], mp[1]};
+    float p[8] = {pw[0].x, pw[0].y, pw[0].z, pw[0].w, pw[1].x, pw[1].y, pw[1].z, pw[1].w};
+    if (!skip) {
+      const float4 gw[2] = {mg[0], mg[1]};
+      float4 m4[2] = {mm[0], mm[1]};
+      float4 v4[2] = {mv[0], mv[1]};
+      const float gq[8] = {gw[0].x, gw[0].y, gw[0].z, gw[0].w, gw[1].x, gw[1].y, gw[1].z, gw[1].w};
+      float mq[8] = {m4[0].x, m4[0].y, m4[0].z, m4[0].w, m4[1].x, m4[1].y, m4[1].z, m4[1].w};
+      float vq[8] = {v4[0].x, v4[0].y, v4[0].z, v4[0].w, v4[1].x, v4[1].y, v4[1].z, v4[1].w};
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float g = gq[j] * clip;
+        mq[j] = b1 * mq[j] + (1.f - b1) * g;
+        vq[j] = b2 * vq[j] + (1.f - b2) * g * g;
+        p[j] = p[j] * (1.f - lr * wd) - lr * (mq[j] / bc1) / (sqrtf(vq[j] / bc2) + eps);
+      }
+      mm[0] = make_float4(mq[0], mq[1], mq[2], mq[3]);
+      mm[1] = make_float4(mq[4], mq[5], mq[6], mq[7]);
+      mv[0] = make_float4(vq[0], vq[1], vq[2], vq[3]);
+      mv[1] = make_float4(vq[4], vq[5], vq[6], vq[7]);
+      mp[0] = make_float4(p[0], p[1], p[2], p[3]);
+      mp[1] = make_float4(p[4], p[5], p[6], p[7]);
+    }
+    uint4 o;
+    o.x = pack_bf16x2(p[0], p[1]);
+    o.y = pack_bf16x2(p[2], p[3]);
+    o.z = pack_bf16x2(p[4], p[5]);
+    o.w = pack_bf16x2(p[6], p[7]);
+    if (mc_params != nullptr) {
+      multimem_st_16B(mc_params + shard_start + i * 8, o);
+    } else {
+      for (int r = 0; r < world; ++r)
+        *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(params.p[r]) + shard_start + i * 8) = o;
+    }
+  }
+  __threadfence_system();
+}
+}  // namespace b2
+
+static PeerPtrs peer_ptrs_of(void* const* a, int world) {
+  PeerPtrs pp;
+  for (int r = 0; r < 8; ++r) pp.p[r] = (a != nullptr && r < world) ? a[r] : nullptr;
+  return pp;
+}
+
+// One-launch barrier over the group with a device-side epoch (see flag_barrier_kernel).  epochs: device int[channels];
+// ok: device int[1], cleared on a wait that ran out.
+B2_EXPORT int b2_flag_barrier(void* const* flag_bufs, const int* my_flags, int* epochs, int world, int my_rank,
+                              int channels, int channel, int limit_ms, int* ok, void* stream_) {
+  b2::ensure_thread_context();
+  if (world < 1 || world > 8 || channel < 0 || channel >= channels) {
+    set_error("flag_barrier: world in 1..8 and 0 <= channel < channels required");
+    return 10;
+  }
+  int* status = status_ptr();
+  if (!status) return 3;
+  flag_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream_)>>>(
+      peer_ptrs_of(flag_bufs, world), my_flags, epochs, world, my_rank, channels, channel,
+      static_cast<unsigned long long>(limit_ms) * 1000000ull, ok, status);
+  B2_LAUNCH_CHECK("flag_barrier");
+  return 0;
+}
+
+// mc_bucket: multicast address of the bf16 gradient bucket (torch symmetric memory's multicast_ptr).
+B2_EXPORT int b2_zero_reduce_shard_mc(const void* mc_bucket, long long shard_start, long long n, float scale,
+                                      float* out, int accumulate, float* norm_sq, void* stream_) {
+  b2::ensure_thread_context();
+  if (mc_bucket == nullptr || (n % 8) || (shard_start % 8)) {
+    set_error("zero_reduce_shard_mc: multicast pointer and 8-element aligned shard required");
+    return 10;
+  }
+  if (n <= 0) return 0;
+  zero_reduce_shard_mc_kernel<<<grid_for(n / 8, 256, 4), 256, 0, static_cast<cudaStream_t>(stream_)>>>(
+      static_cast<const __nv_bfloat16*>(mc_bucket), shard_start, n, scale, out, accumulate, norm_sq);
+  B2_LAUNCH_CHECK("zero_reduce_shard_mc");
+  return 0;
+}
+
+// parts: device float[2]; slot_bufs: each rank's float[32] slot buffer; results in norm_sq[0] and grad_norm[0].
+B2_EXPORT int b2_norm_allreduce(void* const* slot_bufs, const float* my_slots, void* const* flag_bufs,
+                                const int* my_flags, int* epochs, int world, int my_rank, int channels, int channel,
+                                const float* parts, float* norm_sq, float* grad_norm, int limit_ms, int* ok,
+                                void* stream_) {
+  b2::ensure_thread_context();
+  if (world < 1 || world > 8 || channel < 0 || channel >= channels) {
+    set_error("norm_allreduce: world in 1..8 and 0 <= channel < channels required");
+    return 10;
+  }
+  int* status = status_ptr();
+  if (!status) return 3;
+  norm_allreduce_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream_)>>>(
+      peer_ptrs_of(slot_bufs, world), my_slots, peer_ptrs_of(flag_bufs, world), my_flags, epochs, world, my_rank,
+      channels, channel, parts, norm_sq, grad_norm, static_cast<unsigned long long>(limit_ms) * 1000000ull, ok, status);
+  B2_LAUNCH_CHECK("norm_allreduce");
+  return 0;
+}
+
+// AdamW + parameter publish; params: host array of peer pointers (plain stores) or mc_params: the bucket's multicast
+// address (one store through the switch).  ok (nullable): device int, 0 skips the update.
+B2_EXPORT int b2_zero_adamw_publish2(float* master, float* m, float* v, const float* grad, long long n,
+                                     const float* hyper, const float* norm_sq, void* const* params, void* mc_params,
+                                     int world, long long shard_start, const int* ok, void* stream_) {
+  b2::ensure_thread_context();
+  if (world < 1 || world > 8 || (n % 8) || (shard_start % 8) || (params == nullptr && mc_params == nullptr)) {
+    set_error("zero_adamw_publish2: world in 1..8, 8-element aligned shard and a destination required");
+    return 10;
+  }
+  if (n <= 0) return 0;
+  zero_adamw_publish_any_kernel<<<grid_for(n / 8, 256, 4), 256, 0, static_cast<cudaStream_t>(stream_)>>>(
+      master, m, v, grad, n, hyper, norm_sq, peer_ptrs_of(params, world), static_cast<__nv_bfloat16*>(mc_params),
+      world, shard_start, ok);
+  B2_LAUNCH_CHECK("zero_adamw_publish2");
+  return 0;
+}
+
+namespace b2 {
 // Signal every peer: flags_of_peer[r][my_rank * channels + channel] = value (system-scope release).
 __global__ void flag_signal_all_kernel(PeerPtrs flag_bufs, int world, int my_rank, int channels, int channel,
                                        int value) {

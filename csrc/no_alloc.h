@@ -31,8 +31,11 @@ extern "C" {
 // Returns 0 on success; a non-zero code with a message in b2_last_error() when the size exceeds the
 // built-in scratch, an argument is malformed, or a CUDA call fails.
 //
-// The first call on each device looks up the device address of the scratch array; make that first
-// call outside of any stream capture.  All calls on a device share the one scratch array: the kernel
+// The first call on each device looks up the device address of the scratch array, and the first call
+// from each host thread makes the library's device current on that thread (cudaSetDevice, or an empty
+// cudaFree when no device was announced): make the first call of every (thread, device) pair outside of
+// any stream capture.  Null data pointers, a negative M and an H outside the limits above are rejected
+// with code 10 before anything is launched; M == 0 is a successful no-op.  All calls on a device share the one scratch array: the kernel
 // overwrites the part it uses before reading it, so nothing has to be cleared between calls, but two
 // calls whose kernels overlap in time on the same device (different streams) would corrupt each
 // other's partial sums — issue them on one stream or order them with events.

@@ -1,6 +1,8 @@
 // RMSNorm forward/backward, fused per-head QK-RMSNorm + rotary embedding forward/backward, SwiGLU
 // forward/backward, embedding gather / scatter-add.  All HBM-bound: 16-byte vector accesses, fp32
 // math, bf16 storage.
+#include <atomic>
+
 #include "common.cuh"
 #include "host.h"
 
@@ -777,32 +779,41 @@ B2_EXPORT int b2_embedding_bwd(const long long* ids, const void* dout, void* dta
 static __device__ __align__(256) float g_noalloc_dw_partial[B2_NOALLOC_MAX_PARTIALS * B2_NOALLOC_MAX_H];
 
 static float* noalloc_scratch_ptr() {
-  static float* ptrs[64] = {nullptr};
+  static std::atomic<float*> ptrs[64];   // zero-initialised; racing first calls store the same address
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
     set_error("rmsnorm_bwd_noalloc: cannot determine the current device");
     return nullptr;
   }
-  if (ptrs[dev] == nullptr) {
-    float* p = nullptr;
+  float* p = ptrs[dev].load(std::memory_order_acquire);
+  if (p == nullptr) {
     const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_noalloc_dw_partial);
     if (e != cudaSuccess || p == nullptr) {
       set_error("rmsnorm_bwd_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
       return nullptr;
     }
-    ptrs[dev] = p;
+    ptrs[dev].store(p, std::memory_order_release);
   }
-  return ptrs[dev];
+  return p;
 }
 
 B2_EXPORT int b2_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd,
                                      void* dx, void* dw, int M, int H, int add_to_dx, int accumulate_dw,
                                      int dw_fp32, void* stream_) {
   b2::ensure_thread_context();
-  if (M <= 0) return 0;
   if (H <= 0 || H % 8 != 0 || H > B2_NOALLOC_MAX_H || 256 % (H / 8) != 0) {
     set_error("rmsnorm_bwd_noalloc: H=%d is outside the built-in scratch (multiple of 8, <= %d, 256 %% (H/8) == 0)",
               H, B2_NOALLOC_MAX_H);
+    return 10;
+  }
+  if (M < 0) {
+    set_error("rmsnorm_bwd_noalloc: M=%d is negative", M);
+    return 10;
+  }
+  if (M == 0) return 0;
+  if (!dy || !x || !w || !rstd || !dx || !dw) {
+    set_error("rmsnorm_bwd_noalloc: null pointer (dy=%p x=%p w=%p rstd=%p dx=%p dw=%p)", dy, x, w,
+              static_cast<const void*>(rstd), dx, dw);
     return 10;
   }
   float* partial = noalloc_scratch_ptr();   // first call per device: symbol lookup (not during capture)

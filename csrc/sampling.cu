@@ -329,11 +329,13 @@ __global__ void __launch_bounds__(SMP_THREADS) topp_sample_kernel(
   };
   if (mine > 0.f && r >= before && r < incl) atomicMax(&s_pick, walk(r));
   __syncthreads();
-  if (s_pick < 0) {
-    // numerical corner (r rounded up to the kept mass): the last kept token
-    if (mine > 0.f) atomicMax(&s_pick, walk(INFINITY));
-    __syncthreads();
-  }
+  // every thread takes its own copy before anyone may write again: branching on the shared word itself would
+  // let a late thread see a neighbour's fallback write and skip the barrier below
+  const bool need_fallback = s_pick < 0;
+  __syncthreads();
+  // numerical corner (r rounded up to the kept mass): the last kept token
+  if (need_fallback && mine > 0.f) atomicMax(&s_pick, walk(INFINITY));
+  __syncthreads();
   if (tid == 0) {
     const int pick = max(s_pick, 0);
     out_ids[row] = pick;

@@ -14,6 +14,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 import torch  # noqa: E402
 
 from b200fw.config import ColocateConfig  # noqa: E402
+from b200fw.obs.clocks import ClockSampler  # noqa: E402
 from b200fw.orch import ColocateOrchestrator  # noqa: E402
 
 
@@ -29,8 +30,9 @@ def main():
     ap.add_argument("--zero-stage", type=int, default=2)
     ap.add_argument("--no-c3po", action="store_true")
     ap.add_argument("--async-pipeline", action="store_true")
-    ap.add_argument("--dense-reward", type=float, default=0.0,
-                    help="weight of the dense shaping term of the synthetic reward (0 = the plain rule reward)")
+    ap.add_argument("--dense-reward", type=float, default=0.5,
+                    help="weight of the dense shaping term of the synthetic reward (0 = the plain rule reward, which a "
+                         "random-init policy never earns: every advantage is then zero and the backward carries no signal)")
     ap.add_argument("--output-dir", default="outputs/bench_grpo")
     a = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -56,14 +58,18 @@ def main():
         await o.shutdown()
         return s, o.metrics
 
+    sampler = ClockSampler(int(os.environ.get("LOCAL_RANK", "0")))
+    sampler.start()
     s, metrics = asyncio.run(go())
+    clocks = sampler.stop()
     if int(os.environ.get("RANK", "0")) == 0:
         steady = metrics[1:] or metrics
         avg = lambda k: sum(m.state_durations.get(k, 0.0) for m in steady) / len(steady)
         print(json.dumps({"metric": "grpo_iteration_s", "value": sum(m.total_time for m in steady) / len(steady),
                           "n_gpus": world, "rollout_s": avg("inferring"), "train_s": avg("training"),
                           "sync_ms": avg("syncing") * 1e3, "reward_s": avg("rewarding"),
-                          "tokens_generated_per_iter": steady[-1].tokens_generated,
+                          "tokens_generated_per_iter": steady[-1].tokens_generated, "dense_reward": a.dense_reward,
+                          "avg_reward": sum(m.avg_reward for m in steady) / len(steady), "clocks": clocks,
                           "errors": [m.error for m in metrics if m.error], "results": s["results"]}))
 
 

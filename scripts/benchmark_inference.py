@@ -19,6 +19,7 @@ import torch  # noqa: E402
 
 from b200fw.infer import InferenceConfig, InferenceEngine  # noqa: E402
 from b200fw.model import PRESETS, ParallelTransformerModel  # noqa: E402
+from b200fw.obs.clocks import ClockSampler  # noqa: E402
 
 
 def parse_args(argv=None):
@@ -87,6 +88,8 @@ def main(argv=None):
     for i, p in enumerate(prompts):
         eng.add_request(f"b{i}", p, a.output_tokens)
     s0, s1, s2 = ev(), ev(), ev()
+    sampler = ClockSampler(0)
+    sampler.start()
     s0.record()
     steps_prefill = 0
     while any(r.num_generated_tokens == 0 for r in eng.requests.values()):
@@ -100,6 +103,7 @@ def main(argv=None):
         steps_decode += 1
     s2.record()
     torch.cuda.synchronize()
+    clocks = sampler.stop()
     prefill_ms, decode_ms = s0.elapsed_time(s1), s1.elapsed_time(s2)
     gen = len(prompts) * a.output_tokens
     st = eng.get_stats()
@@ -113,6 +117,8 @@ def main(argv=None):
         "decode_ms_per_step": decode_ms / max(1, steps_decode),
         "decode_tokens_per_s": (gen - first) / (decode_ms * 1e-3) if decode_ms > 0 else 0.0,
         "end_to_end_tokens_per_s": gen / ((prefill_ms + decode_ms) * 1e-3),
+        # the figure the reference arm (baseline/run_reference_extras.py decode) reports: output tokens over the whole call
+        "generation_output_tokens_per_s": gen / ((prefill_ms + decode_ms) * 1e-3), "clocks": clocks,
         "spec_acceptance": st.get("speculative", {}).get("acceptance_rate"),
         "graph_replays": st.get("graph_replays"), "kv_blocks": blocks}))
 

@@ -9,6 +9,12 @@ prints achieved throughput against the measured peaks.  Also the command line us
     python scripts/kernel_bench.py paged_decode --batch 256 --ctx 1024
     python scripts/kernel_bench.py sampler --batch 256
     python scripts/kernel_bench.py adamw --n 100000000
+    python scripts/kernel_bench.py gemm --m 8192 --n 6144 --k 1024 --lib      # cuBLAS (torch.matmul) on the same shape
+    python scripts/kernel_bench.py attn_fwd --lib                             # flash-attn 2 on the same shape
+    python scripts/kernel_bench.py suite                                      # the training step's shapes, both arms
+
+Every line carries the SM clock sampled while the kernel ran (median MHz, throttle reasons) and
+``ms_x_mhz`` (milliseconds x median MHz: proportional to cycles, comparable across differently clocked boxes).
 """
 import argparse
 import json
@@ -20,6 +26,7 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 import torch  # noqa: E402
 
 from b200fw import ops  # noqa: E402
+from b200fw.obs.clocks import ClockSampler  # noqa: E402
 from b200fw.obs.profilers import measured_peaks  # noqa: E402
 
 DEV = "cuda"
@@ -44,9 +51,114 @@ def timeit(fn, iters, warmup, flush):
     return times[len(times) // 2], times[0]
 
 
+def timed_line(name, fn, flops, bytes_, iters, warmup, flush, peaks, extra=None):
+    """Time ``fn`` with the clock sampler running; one result dict."""
+    sampler = ClockSampler(torch.cuda.current_device())
+    sampler.start()
+    # keep the GPU busy long enough for a few 200 ms clock samples
+    med, best = timeit(fn, iters, warmup, flush)
+    reps = 0
+    import time as _t
+    t0 = _t.time()
+    while _t.time() - t0 < 0.7:
+        fn()
+        reps += 1
+        if reps % 16 == 0:
+            torch.cuda.synchronize()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    out = {"kernel": name, "ms_median": med, "ms_best": best, "peaks": peaks["source"], "clocks": clocks}
+    if clocks.get("sm_mhz"):
+        out["ms_x_mhz"] = med * clocks["sm_mhz"]
+    if flops:
+        out["tflops"] = flops / (med * 1e-3) / 1e12
+        out["frac_of_measured_bf16_burst"] = out["tflops"] / peaks["bf16_tflops"]
+    if bytes_:
+        out["gbs"] = bytes_ / (med * 1e-3) / 1e9
+        out["frac_of_measured_hbm"] = out["gbs"] / peaks["hbm_gbs"]
+    if extra:
+        out.update(extra)
+    return out
+
+
+def suite(a, peaks):
+    """The Qwen3-0.6B training step's GEMMs (forward, input-gradient and weight-gradient forms at 8192 tokens, and
+    the 16384-token forms of the 32B TP8 step) and its attention shapes, this library against cuBLAS
+    (``torch.matmul``) and flash-attn 2 on the same tensors.  One JSON line per (kernel, arm)."""
+    bf = torch.bfloat16
+    lines = []
+    gemms = [  # name, M, N, K, a_mn, b_mn, fp32 accumulate
+        ("fwd qkv 8192x4096x1024", 8192, 4096, 1024, 0, 0, False),
+        ("fwd gate_up 8192x6144x1024", 8192, 6144, 1024, 0, 0, False),
+        ("fwd down 8192x1024x3072", 8192, 1024, 3072, 0, 0, False),
+        ("dX gate_up 8192x1024x6144 (B mn-major)", 8192, 1024, 6144, 0, 1, False),
+        ("dW gate_up 6144x1024x8192 (A,B mn-major, fp32 acc)", 6144, 1024, 8192, 1, 1, True),
+        ("dW down 1024x3072x8192 (A,B mn-major, fp32 acc)", 1024, 3072, 8192, 1, 1, True),
+        ("fwd 32b gate_up/8 16384x6400x5120", 16384, 6400, 5120, 0, 0, False),
+        ("dW 32b gate_up/8 6400x5120x16384", 6400, 5120, 16384, 1, 1, True),
+        ("square 8192^3", 8192, 8192, 8192, 0, 0, False),
+    ]
+    for name, M, N, K, amn, bmn, acc in gemms:
+        A = torch.randn((K, M) if amn else (M, K), device=DEV, dtype=bf)
+        B = torch.randn((K, N) if bmn else (N, K), device=DEV, dtype=bf)
+        C = torch.zeros(M, N, device=DEV, dtype=torch.float32 if acc else bf)
+        fl = 2.0 * M * N * K
+        ours = lambda: ops.gemm(A, B, a_mn=bool(amn), b_mn=bool(bmn), out=C, accumulate=acc)
+        Ab = A.t() if amn else A
+        Bb = B if bmn else B.t()
+        Cb = torch.zeros(M, N, device=DEV, dtype=bf)
+        if acc:   # the library form of an fp32-accumulated weight gradient: bf16 GEMM, then add into fp32
+            lib = lambda: C.add_(torch.matmul(Ab, Bb))
+        else:
+            lib = lambda: torch.matmul(Ab, Bb, out=Cb)
+        lines.append(timed_line("gemm " + name, ours, fl, 0, a.iters, a.warmup, True, peaks, {"arm": "b200fw"}))
+        lines.append(timed_line("gemm " + name, lib, fl, 0, a.iters, a.warmup, True, peaks, {"arm": "cublas"}))
+        print(json.dumps(lines[-2]), flush=True)
+        print(json.dumps(lines[-1]), flush=True)
+        del A, B, C, Cb
+    try:
+        from flash_attn import flash_attn_func
+    except Exception as e:  # noqa: BLE001
+        flash_attn_func = None
+        print(json.dumps({"kernel": "attention", "arm": "flash_attn", "unavailable": f"{type(e).__name__}: {e}"}))
+    for batch, seq, hq, hkv in [(8, 1024, 16, 8), (8, 2048, 8, 1), (2, 8192, 16, 8)]:
+        T, D = batch * seq, 128
+        q = torch.randn(T, hq * D, device=DEV, dtype=bf, requires_grad=True)
+        k = torch.randn(T, hkv * D, device=DEV, dtype=bf, requires_grad=True)
+        v = torch.randn(T, hkv * D, device=DEV, dtype=bf, requires_grad=True)
+        ff = 4.0 * batch * hq * seq * seq * D / 2
+        tag = f"b{batch} s{seq} h{hq}:{hkv}"
+        o = ops.flash_attention(q, k, v, batch, seq, hq, hkv)
+        g = torch.randn_like(o)
+
+        def ours_f():
+            with torch.no_grad():
+                ops.flash_attention(q, k, v, batch, seq, hq, hkv)
+        ours_b = lambda: torch.autograd.grad(o, (q, k, v), g, retain_graph=True)
+        r = [timed_line("attn_fwd " + tag, ours_f, ff, 0, a.iters, a.warmup, True, peaks, {"arm": "b200fw"}),
+             timed_line("attn_bwd " + tag, ours_b, 2.5 * ff, 0, a.iters, a.warmup, True, peaks, {"arm": "b200fw"})]
+        if flash_attn_func is not None:
+            q4 = q.detach().view(batch, seq, hq, D).requires_grad_()
+            k4 = k.detach().view(batch, seq, hkv, D).requires_grad_()
+            v4 = v.detach().view(batch, seq, hkv, D).requires_grad_()
+            o4 = flash_attn_func(q4, k4, v4, causal=True)
+            g4 = torch.randn_like(o4)
+
+            def lib_f():
+                with torch.no_grad():
+                    flash_attn_func(q4, k4, v4, causal=True)
+            lib_b = lambda: torch.autograd.grad(o4, (q4, k4, v4), g4, retain_graph=True)
+            r.append(timed_line("attn_fwd " + tag, lib_f, ff, 0, a.iters, a.warmup, True, peaks, {"arm": "flash_attn"}))
+            r.append(timed_line("attn_bwd " + tag, lib_b, 2.5 * ff, 0, a.iters, a.warmup, True, peaks, {"arm": "flash_attn"}))
+        for x in r:
+            print(json.dumps(x), flush=True)
+        lines += r
+    return lines
+
+
 def main():
     ap = argparse.ArgumentParser(description=__doc__)
-    ap.add_argument("kernel", choices=["gemm", "attn_fwd", "attn_bwd", "rmsnorm", "rmsnorm_bwd", "qknorm_rope", "swiglu",
+    ap.add_argument("kernel", choices=["suite", "gemm", "attn_fwd", "attn_bwd", "rmsnorm", "rmsnorm_bwd", "qknorm_rope", "swiglu",
                                        "lmhead_ce", "paged_decode", "sampler", "adamw", "kv_store"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=6144)
@@ -66,16 +178,25 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--lib", action="store_true",
+                    help="time the library counterpart instead (gemm: torch.matmul / cuBLAS; attn_*: flash-attn 2)")
     a = ap.parse_args()
     torch.manual_seed(0)
     peaks = measured_peaks()
     bf = torch.bfloat16
     flops = bytes_ = 0.0
+    if a.kernel == "suite":
+        suite(a, peaks)
+        return
     if a.kernel == "gemm":
         A = torch.randn((a.k, a.m) if a.a_mn else (a.m, a.k), device=DEV, dtype=bf)
         B = torch.randn((a.k, a.n) if a.b_mn else (a.n, a.k), device=DEV, dtype=bf)
         C = torch.zeros(a.m, a.n, device=DEV, dtype=torch.float32 if a.fp32_acc else bf)
         fn = lambda: ops.gemm(A, B, a_mn=bool(a.a_mn), b_mn=bool(a.b_mn), out=C, bn=a.bn, accumulate=a.fp32_acc)
+        if a.lib:
+            Ab, Bb = (A.t() if a.a_mn else A), (B if a.b_mn else B.t())
+            Cb = torch.zeros(a.m, a.n, device=DEV, dtype=bf)
+            fn = (lambda: C.add_(torch.matmul(Ab, Bb))) if a.fp32_acc else (lambda: torch.matmul(Ab, Bb, out=Cb))
         flops = 2.0 * a.m * a.n * a.k
         bytes_ = 2.0 * (a.m * a.k + a.n * a.k + a.m * a.n)
     elif a.kernel in ("attn_fwd", "attn_bwd"):
@@ -96,6 +217,18 @@ def main():
             g = torch.randn_like(o)
             fn = lambda: torch.autograd.grad(o, (q, k, v), g, retain_graph=True)
             flops = 2.5 * fwd_flops
+        if a.lib:
+            from flash_attn import flash_attn_func
+            q4 = q.detach().view(a.batch, a.seq, a.hq, D).requires_grad_()
+            k4 = k.detach().view(a.batch, a.seq, a.hkv, D).requires_grad_()
+            v4 = v.detach().view(a.batch, a.seq, a.hkv, D).requires_grad_()
+            if a.kernel == "attn_fwd":
+                fn = lambda: flash_attn_func(q4, k4, v4, causal=True)
+            else:
+                torch.set_grad_enabled(True)
+                o4 = flash_attn_func(q4, k4, v4, causal=True)
+                g4 = torch.randn_like(o4)
+                fn = lambda: torch.autograd.grad(o4, (q4, k4, v4), g4, retain_graph=True)
         bytes_ = 2.0 * T * D * (2 * a.hq + 2 * a.hkv)
     elif a.kernel in ("rmsnorm", "rmsnorm_bwd"):
         x = torch.randn(a.m, a.h, device=DEV, dtype=bf, requires_grad=True)
@@ -179,14 +312,8 @@ def main():
         segs = torch.tensor([[i, 16 * i, 16, 0] for i in range(a.m // 16)], dtype=torch.int32, device=DEV)
         fn = lambda: ops.kv_store(k, k, kc, vc, segs, ks, vs)
         bytes_ = a.m * a.hkv * 128 * 2 * (2 + (1 if a.fp8 else 2))
-    med, best = timeit(fn, a.iters, a.warmup, not a.no_flush)
-    out = {"kernel": a.kernel, "ms_median": med, "ms_best": best, "peaks": peaks["source"]}
-    if flops:
-        out["tflops"] = flops / (med * 1e-3) / 1e12
-        out["frac_of_measured_bf16_burst"] = out["tflops"] / peaks["bf16_tflops"]
-    if bytes_:
-        out["gbs"] = bytes_ / (med * 1e-3) / 1e9
-        out["frac_of_measured_hbm"] = out["gbs"] / peaks["hbm_gbs"]
+    out = timed_line(a.kernel, fn, flops, bytes_, a.iters, a.warmup, not a.no_flush, peaks,
+                     {"arm": "library" if a.lib else "b200fw"})
     print(json.dumps(out))
 
 

@@ -199,3 +199,56 @@ def test_truncation_and_sampling_helpers():
     picks = {int(TrainEngine.sample_next_token(logits, 1.0, 0.5, g)) for _ in range(50)}
     assert picks == {1}                                        # nucleus 0.5 keeps only the top token
     assert math.isclose(sum(TrainEngine.group_advantages([1.0, 2.0, 3.0])), 0.0, abs_tol=1e-6)
+
+
+def test_export_weights_leaves_the_lora_base_bit_identical():
+    """The merged export is built out of place: N exports (one per RL weight sync) must not move the frozen
+    base, which under LoRA is also the KL reference.  bf16 makes an in-place merge + unmerge lossy."""
+    cfg = TrainConfig(model_config=SMALL, lora_rank=4, grpo_beta=0.0, learning_rate=1e-2,
+                      gradient_accumulation_steps=1, use_amp=False, amp_dtype="fp32", warmup_steps=0, max_seq_len=32)
+    eng = TrainEngine(cfg).initialize()
+    eng.model.to(torch.bfloat16)
+    from b200fw.model.lora import LinearWithLoRA
+    mods = [m for m in eng.model.modules() if isinstance(m, LinearWithLoRA)]
+    assert mods
+    with torch.no_grad():
+        for m in mods:
+            for ad in m.adapters.values():
+                ad.lora_B.normal_(0, 0.3)                      # a delta large enough to round in bf16
+    before = [m.base.weight.detach().clone() for m in mods]
+    first = eng.export_weights()
+    for _ in range(4):
+        again = eng.export_weights()
+    for m, w0 in zip(mods, before):
+        assert torch.equal(m.base.weight, w0)
+        assert not m.merged
+    k = "model.layers.0.self_attn.q_proj.weight"
+    assert torch.equal(first[k], again[k])
+    hq = mods[0].ranges["q_proj"]
+    assert not torch.equal(first[k], before[0][hq[0]:hq[1]])   # the export does carry the adapters
+
+
+def test_resolve_step_takes_back_the_bookkeeping_of_a_skipped_step():
+    cfg = TrainConfig(model_config=SMALL, lora_rank=0, grpo_beta=0.0, learning_rate=1e-2, warmup_steps=0,
+                      gradient_accumulation_steps=1, use_amp=False, amp_dtype="fp32", max_seq_len=32)
+    eng = TrainEngine(cfg).initialize()
+    ids, labels = _tiny_batch(0, 0, 2, 16, 256)
+    loss, gn = eng.sft_step_tensors(ids, labels, sync=False)
+    assert eng.step_count == 1 and eng.resolve_step(gn) > 0 and eng.step_count == 1
+    assert eng.optimizer.step_count == 1 and eng.lr_scheduler.step_count == 1
+    # a non-finite norm arrives as -1: counters, schedule and the optimizer's bias-correction step go back
+    eng.step_count, eng.optimizer.step_count, eng.lr_scheduler.step_count = 2, 2, 2
+    assert eng.resolve_step(torch.tensor(-1.0)) < 0
+    assert (eng.step_count, eng.optimizer.step_count, eng.lr_scheduler.step_count) == (1, 1, 1)
+    assert eng.resolve_step(None) == 0.0
+
+
+def test_close_window_steps_after_any_number_of_chunks():
+    cfg = TrainConfig(model_config=SMALL, lora_rank=0, grpo_beta=0.0, learning_rate=1e-2, warmup_steps=0,
+                      gradient_accumulation_steps=4, use_amp=False, amp_dtype="fp32", max_seq_len=32)
+    eng = TrainEngine(cfg).initialize()
+    P, R, W = [[1, 2, 3]], [[[4, 5], [6, 7]]], [[1.0, 0.0]]
+    eng.grpo_step(P, R, W, skip_optimizer_step=True)
+    assert eng.step_count == 0
+    m = eng.grpo_step(P, R, W, close_window=True)
+    assert eng.step_count == 1 and m.grad_norm > 0 and eng._accumulation_count == 0

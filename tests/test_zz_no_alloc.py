@@ -71,3 +71,22 @@ def test_noalloc_entry_rejects_sizes_beyond_its_scratch():
     rc = lib.b2_rmsnorm_bwd_noalloc(_c(x), _c(x), _c(w), _c(rstd), _c(x.clone()), _c(dw), 8, 4096, 0, 0, 1,
                                     ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
     assert rc != 0 and b"outside the built-in scratch" in lib.b2_last_error()
+
+
+def test_noalloc_entry_rejects_null_pointers_and_checks_h_before_the_empty_case():
+    from b200fw import _native as nv
+    lib = nv.lib()
+    lib.b2_rmsnorm_bwd_noalloc.restype = ctypes.c_int
+    x = torch.zeros(8, 1024, device="cuda", dtype=torch.bfloat16)
+    w = torch.ones(1024, device="cuda", dtype=torch.bfloat16)
+    rstd = torch.ones(8, device="cuda")
+    dw = torch.zeros(1024, device="cuda")
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    rc = lib.b2_rmsnorm_bwd_noalloc(_c(x), _c(x), _c(w), ctypes.c_void_p(0), _c(x.clone()), _c(dw), 8, 1024, 0, 0, 1, stream)
+    assert rc == 10 and b"null pointer" in lib.b2_last_error()
+    # an out-of-range H is an error even when there are no rows to process
+    rc = lib.b2_rmsnorm_bwd_noalloc(_c(x), _c(x), _c(w), _c(rstd), _c(x.clone()), _c(dw), 0, 4096, 0, 0, 1, stream)
+    assert rc == 10
+    rc = lib.b2_rmsnorm_bwd_noalloc(_c(x), _c(x), _c(w), _c(rstd), _c(x.clone()), _c(dw), 0, 1024, 0, 0, 1, stream)
+    assert rc == 0
+    assert nv.read_status() == 0
