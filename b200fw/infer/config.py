@@ -48,6 +48,9 @@ class InferenceConfig:
     seed: int = 0
     speculative_draft_layers: int = 2    # random-init draft model of the same width when no path is given
     adaptive_chunking: bool = True
+    # a weight update does not abort running requests: they go on under the new weights and keep the K/V their
+    # earlier tokens produced under the old ones, for at most this many versions (0 = abort on every update)
+    max_weight_staleness: int = 1
 
     @classmethod
     def from_model_config(cls, mc, **kw) -> "InferenceConfig":

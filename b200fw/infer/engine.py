@@ -149,6 +149,7 @@ class InferenceEngine:
         r = Request(request_id, list(prompt_tokens), max_tokens,
                     self.config.temperature if temperature is None else temperature,
                     self.config.top_p if top_p is None else top_p, eos_token_id=self.config.eos_token_id)
+        r.weights_version = self.weights_version        # the version this request started under
         self.requests[request_id] = r
         self.scheduler.add_request(r)
         return r
@@ -522,18 +523,35 @@ class InferenceEngine:
         self.on_weights_updated()
         return n
 
-    def on_weights_updated(self):
-        """KV computed with the old weights is stale: drop the prefix cache and abort running requests.
-        Graphs are kept when weights were updated in place."""
+    def on_weights_updated(self, abort_running: Optional[bool] = None):
+        """The live weights changed (in place, so captured graphs stay valid).  Running requests keep decoding:
+        the K/V of their earlier tokens came from the previous version, which is bounded staleness, not an error.
+        A request is dropped only when it started more than ``config.max_weight_staleness`` versions ago (or when
+        ``abort_running`` says so).  The prefix cache is emptied either way: no new request may share blocks
+        computed under old weights."""
         self.weights_version += 1
+        limit = self.config.max_weight_staleness
+        abort_all = abort_running if abort_running is not None else limit <= 0
         if self.scheduler is not None:
-            for r in self.scheduler.abort_all():
+            if abort_all:
+                dropped = self.scheduler.abort_all()
+            else:
+                too_old = lambda r: self.weights_version - getattr(r, "weights_version", self.weights_version) > limit
+                dropped = [r for r in self.scheduler.running_queue + self.scheduler.waiting_queue if too_old(r)]
+                self.scheduler.running_queue = [r for r in self.scheduler.running_queue if not too_old(r)]
+                self.scheduler.waiting_queue = [r for r in self.scheduler.waiting_queue if not too_old(r)]
+            for r in dropped:
                 self._release(r, cache_prefix=False)
                 self.finished[r.request_id] = r
                 self.requests.pop(r.request_id, None)
+            self.stats["aborted_stale"] = self.stats.get("aborted_stale", 0) + len(dropped)
         if self.prefix_cache is not None:
             self.prefix_cache.invalidate_all()
             self._inflight_prefix.clear()
+            # blocks of still-running requests stay theirs; they are never published to the cache again
+            for r in (self.scheduler.running_queue if self.scheduler is not None else []):
+                r._prefix_published = True
+                r.num_cached_tokens = 0
 
     def get_stats(self) -> dict:
         s = dict(self.stats)

@@ -233,8 +233,9 @@ class ZeROOptimizer:
             b.persistent_grad = True
         nb = len(self.buckets)
         # channel i: "bucket i's gradients are complete on every rank"; nb: end of step; nb + 1: norm exchange
-        self.flags = FlagBarrier(self.dp_group, self.device, channels=max(8, nb + 2))
-        self._ch_step_end, self._ch_norm = nb, nb + 1
+        # (nb + 2 is spare: nothing in the optimizer uses it)
+        self.flags = FlagBarrier(self.dp_group, self.device, channels=max(8, nb + 3))
+        self._ch_step_end, self._ch_norm, self._ch_spare = nb, nb + 1, nb + 2
         self._norm_ar = NormAllReduce(self.flags, self.dp_group, self._ch_norm, self.device)
         self.nvls = all(b.symm_grad.mc_ptr and b.symm_param.mc_ptr for b in self.buckets)
 

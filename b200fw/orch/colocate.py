@@ -863,14 +863,65 @@ class ColocateOrchestrator:
 
 
 class _LoRAWorker:
-    """SwiftSync's view of the in-process rollout engine: takes adapter states / deltas and re-merges
-    them into the engine's plain weights (in place)."""
+    """SwiftSync's view of the in-process rollout engine.
+
+    The engine holds plain merged weights ``W_base + s * B A``.  A sync does not re-export the model: for every
+    adapted projection one low-rank GEMM updates the engine's weight rows in place,
+
+    * delta:  ``W += [s B_new | -s B_old] @ [A_new ; A_old]``   (contraction length 2r, accumulate epilogue), where
+      ``new = old + delta`` and ``old`` is this worker's record of what the engine currently carries;
+    * full:   ``W  = W_base + s B_new A_new``                    (the trainer's frozen base rows as the residual
+      operand), which also wipes the bf16 rounding the in-place deltas have accumulated.
+
+    Same role as the reference's delta application on the worker (src/transfer/swift_sync.py:181-292), which adds
+    the adapter deltas into a worker-side LoRA copy and re-merges.  Under tensor parallelism the trainer holds
+    shards of the base, so the worker falls back to a gathered export."""
 
     def __init__(self, orch: ColocateOrchestrator):
         self.orch = orch
+        self.applied: Optional[Dict[str, torch.Tensor]] = None      # adapter state the engine's weights carry
 
+    def _engine_rows(self, mod_name: str, tgt: str, mod):
+        """The engine model's weight rows that projection ``tgt`` of trainer module ``mod_name`` maps to."""
+        m = self.orch.infer_engine.model
+        for part in mod_name.split("."):
+            m = getattr(m, part) if not part.isdigit() else m[int(part)]
+        w = m.weight
+        from ..model.qwen3 import RowParallelLinear
+        if isinstance(mod.base, RowParallelLinear):
+            return w, mod.base.weight
+        s0, e0 = mod.ranges[tgt]
+        return w[s0:e0], mod.base.weight[s0:e0]
+
+    @torch.no_grad()
     def update_weights(self, state, mode: str = "full"):
+        from .. import ops
+        from ..model.lora import iter_lora
         orch = self.orch
-        merged = orch._merged_clone()
-        from ..model.hf_io import hf_named_tensors
-        orch.infer_engine.load_weights(dict(hf_named_tensors(merged)))
+        eng = orch.train_engine
+        if eng.parallel_ctx.tp_size > 1 or eng.device.type != "cuda":
+            merged = orch._merged_clone()
+            from ..model.hf_io import hf_named_tensors
+            orch.infer_engine.load_weights(dict(hf_named_tensors(merged)))
+            return
+        dev, dt = eng.device, eng.dtype
+        if mode == "delta" and self.applied is not None:
+            new = {k: self.applied[k] + state[k].to(dev, torch.float32) for k in self.applied if k in state}
+            for k, v in self.applied.items():
+                new.setdefault(k, v)
+        else:
+            mode = "full"
+            new = {k: v.detach().to(dev, torch.float32).clone() for k, v in state.items()}
+        for name, tgt, mod, ad in iter_lora(eng.model):
+            ka, kb = f"{name}.{tgt}.lora_A", f"{name}.{tgt}.lora_B"
+            if ka not in new or kb not in new:
+                continue
+            w_rows, base_rows = self._engine_rows(name, tgt, mod)
+            if mode == "full":
+                ops.gemm((new[kb] * ad.scaling).to(dt), new[ka].to(dt), b_mn=True, out=w_rows, residual=base_rows)
+            else:
+                b_cat = torch.cat([new[kb] * ad.scaling, self.applied[kb] * (-ad.scaling)], 1).to(dt)
+                a_cat = torch.cat([new[ka], self.applied[ka]], 0).to(dt)
+                ops.gemm(b_cat, a_cat, b_mn=True, out=w_rows, accumulate=True)
+        self.applied = new
+        orch.infer_engine.on_weights_updated()

@@ -98,11 +98,14 @@ class VersionedWeightBuffer:
 
 
 class PeerWeightSync:
-    """Both ends of the peer-write sync.
+    """Both ends of the peer-write sync.  A full sync is verified against the checksum of the whole staged image;
+    a delta (``add=True``) against the checksum of exactly the spans it touched, which the control message lists.
 
     ``sender_rank`` writes, ``receiver_ranks`` each own a staging buffer.  With ``group=None`` the sync
     is process-local (trainer and engine share the GPU): ``staging`` is then an ordinary tensor.
     """
+
+    UNIT = 1 << 20        # elements per unit of the batched write
 
     def __init__(self, layout: List[Tuple[str, Tuple[int, ...]]], dtype: torch.dtype = torch.bfloat16, device=None,
                  group=None, sender_rank: int = 0, chunk_elems: int = 1 << 24):
@@ -125,6 +128,7 @@ class PeerWeightSync:
             storage.zero_()
         self.staging = VersionedWeightBuffer(layout, dtype, self.device, storage)
         self._cks = torch.zeros(2, dtype=torch.int64, device=self.device) if self.device.type == "cuda" else None
+        self.last_spans: List[Tuple[int, int]] = []
 
     # ---- sender ------------------------------------------------------------------------------------------
     def _dst_ptr(self, target_rank: Optional[int]) -> int:
@@ -138,33 +142,64 @@ class PeerWeightSync:
         st = self.staging
         nbytes = 0
         if self.device.type != "cuda":
+            self.last_spans = []
             for k, v in state.items():
                 dst = st.view(k)
                 dst.copy_((dst.float() + v.float()).to(st.dtype) if add else v.to(st.dtype))
                 nbytes += v.numel() * st.flat.element_size()
-            return fletcher_checksum(st.flat[:st.numel]), nbytes
+                self.last_spans.append(st.offsets[k][:2])
+            return (self.spans_checksum(self.last_spans) if add else fletcher_checksum(st.flat[:st.numel])), nbytes
         self._cks.zero_()
         base = self._dst_ptr(target_rank)
         es = st.flat.element_size()
         L = nv.lib()
+        # one launch for the whole image (two when the sources mix fp32 and bf16): a table of
+        # (source pointer, destination offset, element count) units, large tensors cut into UNIT-element pieces
+        keep, by_dtype = [], {True: [], False: []}
         for k, v in state.items():
             off, cnt, _ = st.offsets[k]
             src = v.detach().reshape(-1)
             if src.dtype not in (torch.float32, torch.bfloat16):
                 src = src.float()
             src = src.contiguous()
-            for s in range(0, cnt, self.chunk):
-                n = min(self.chunk, cnt - s)
-                nv.check(L.b2_peer_write(nv.ctypes.c_void_p(src.data_ptr() + s * src.element_size()),
-                                         int(src.dtype == torch.float32), nv.ctypes.c_void_p(base),
-                                         int(st.dtype == torch.float32), nv.ctypes.c_longlong(n),
-                                         nv.ctypes.c_longlong(off + s), int(add), nv.ptr(self._cks),
-                                         nv.stream_ptr()), "peer_write")
-                nv.count_launch()
+            keep.append(src)                       # alive until the host sync below
+            sz, ptr0 = src.element_size(), src.data_ptr()
+            rows = by_dtype[src.dtype == torch.float32]
+            for s0 in range(0, cnt, self.UNIT):
+                rows.append((ptr0 + s0 * sz, off + s0, min(self.UNIT, cnt - s0)))
             nbytes += cnt * es
+        self.last_spans = [(off, n) for rows in by_dtype.values() for _, off, n in rows]
+        for is_fp32, rows in by_dtype.items():
+            if not rows:
+                continue
+            table = torch.tensor(rows, dtype=torch.int64).pin_memory().to(self.device, non_blocking=True)
+            keep.append(table)
+            nv.check(L.b2_peer_write_batch(nv.ptr(table), len(rows), int(is_fp32), nv.ctypes.c_void_p(base),
+                                           int(st.dtype == torch.float32), int(add), nv.ptr(self._cks),
+                                           nv.stream_ptr()), "peer_write_batch")
+            nv.count_launch()
         # padding between tensors is zero on both sides and contributes nothing to either sum
         a, b = self._cks.tolist()      # synchronises: every write has been issued and fenced
         return (a & MASK64, b & MASK64), nbytes
+
+    def spans_checksum(self, spans) -> Tuple[int, int]:
+        """Checksum of the given ``(element offset, count)`` spans of this rank's staging image (what a delta
+        touched), with the same position weights the writer used."""
+        st = self.staging
+        if self.device.type != "cuda":
+            c0 = c1 = 0
+            for off, n in spans:
+                a, b = fletcher_checksum(st.flat[off:off + n], off)
+                c0, c1 = (c0 + a) & MASK64, (c1 + b) & MASK64
+            return c0, c1
+        out = torch.zeros(2, dtype=torch.int64, device=self.device)
+        table = torch.tensor([(0, off, n) for off, n in spans], dtype=torch.int64).pin_memory().to(self.device, non_blocking=True)
+        nv.check(nv.lib().b2_spans_checksum(nv.ptr(table), len(spans), nv.ptr(st.flat),
+                                            int(st.dtype == torch.float32), nv.ptr(out), nv.stream_ptr()),
+                 "spans_checksum")
+        nv.count_launch()
+        a, b = out.tolist()
+        return a & MASK64, b & MASK64
 
     # ---- protocol ------------------------------------------------------------------------------------------
     @nvtx.annotate("sync/peer_write")
@@ -176,11 +211,17 @@ class PeerWeightSync:
         apply = (lambda views: engine.load_weights(views)) if engine is not None else (lambda views: None)
         if self.group is None:
             cks, nbytes = self.write(state, None, add)
-            if add:           # the checksum of an add covers only what was touched: recompute over the image
-                cks = device_checksum(self.staging.flat[:self.staging.numel])
             if corrupt:
                 cks = (cks[0] ^ 1, cks[1])
-            ok = self.staging.verify_and_commit(self.version + 1, cks, apply)
+            if add:           # a delta's checksum covers exactly the spans it touched
+                ok = self.spans_checksum(self.last_spans) == (cks[0] & MASK64, cks[1] & MASK64)
+                if ok:
+                    apply(self.staging.named_views())
+                    self.staging.version = self.version + 1
+                else:
+                    self.staging.rejected += 1
+            else:
+                ok = self.staging.verify_and_commit(self.version + 1, cks, apply)
             self.stats.record(nbytes, time.perf_counter() - t0, ok)
             if ok:
                 self.version += 1
@@ -194,7 +235,7 @@ class PeerWeightSync:
                 cks, nb = self.write(state, r, add)
                 msgs[r] = cks if not corrupt else (cks[0] ^ 1, cks[1])
                 nbytes += nb
-            box = [{"version": self.version + 1, "checksums": msgs, "add": add}]
+            box = [{"version": self.version + 1, "checksums": msgs, "add": add, "spans": self.last_spans if add else None}]
             dist.broadcast_object_list(box, src=dist.get_global_rank(self.group, self.sender_rank), group=self.group)
             acks = [None] * self.world
             dist.all_gather_object(acks, True, group=self.group)
@@ -208,11 +249,15 @@ class PeerWeightSync:
         msg = box[0]
         cks = msg["checksums"][self.rank]
         if msg["add"]:
-            got = device_checksum(self.staging.flat[:self.staging.numel])
-            ok = True
-            apply(self.staging.named_views())
-            self.staging.version = msg["version"]
-            cks = got
+            # the writer's checksum is over the values it stored into exactly these spans: a corrupted delta is
+            # rejected like a corrupted full image (the additions have landed in staging, the live weights and the
+            # version stay as they were; the next full sync rewrites staging)
+            ok = self.spans_checksum(msg["spans"]) == (cks[0] & MASK64, cks[1] & MASK64)
+            if ok:
+                apply(self.staging.named_views())
+                self.staging.version = msg["version"]
+            else:
+                self.staging.rejected += 1
         else:
             ok = self.staging.verify_and_commit(msg["version"], cks, apply)
         acks = [None] * self.world

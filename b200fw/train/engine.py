@@ -45,7 +45,8 @@ class TrainConfig:
     attention_backend: str = "sdpa"       # native flash kernel on GPU
     use_gradient_checkpoint: bool = False
     cuda_graph_step: bool = False              # replay forward + backward of a micro-batch as one CUDA graph
-    cuda_graph_reduce: bool = False             # ... with the last micro-batch's gradient reduce-scatters captured in it
+    cuda_graph_reduce: Optional[bool] = None    # ... with the last micro-batch's gradient reduce-scatters captured in it
+                                                # (None: yes for the in-kernel "p2p" ZeRO backend, no for NCCL)
     lora_rank: int = 16
     lora_alpha: float = 32.0
     lora_target_modules: List[str] = field(default_factory=lambda: [
@@ -80,7 +81,9 @@ class TrainConfig:
     adam_eps: float = 1e-8
     bucket_mb: float = 64.0
     fused_tp_comm: bool = False                 # TP+SP: all-gather / reduce-scatter inside the GEMM kernels
-    zero_comm_backend: str = "nccl"           # "nccl" | "p2p" (reduce-scatter / all-gather inside the optimizer kernels)
+    zero_comm_backend: str = "auto"           # "p2p": reduce-scatter / all-gather inside the optimizer kernels over
+                                                # peer memory / NVLS; "nccl": library collectives; "auto": p2p for plain
+                                                # data parallelism with ZeRO-1 on 2..8 GPUs of a node, NCCL otherwise
     zero3_prefetch: bool = True                 # ZeRO-3: overlap the per-bucket parameter gathers with the forward
     build_ref_model: Optional[bool] = None      # default: grpo_beta > 0, as in the reference
     backend: Optional[str] = None               # nccl / gloo (default by device)
@@ -284,6 +287,9 @@ class TrainEngine:
         from .. import _native as nv
         st = nv.read_status()
         if st != 0:
+            flags = getattr(self.optimizer, "flags", None)
+            if flags is not None:
+                flags.reset_ok()        # the failed step's update was skipped on the device; later steps may proceed
             raise nv.NativeError(f"device status {st} after optimizer step {self.step_count}: a bounded wait in a "
                                  "kernel ran out (301: a peer's flag never arrived; 1xx/2xx: a pipeline barrier); "
                                  "the update of this step is not trustworthy")
@@ -431,8 +437,7 @@ class TrainEngine:
         cfg, opt = self.config, self.optimizer
         return (cfg.cuda_graph_step and not self._graph_disabled and self.device.type == "cuda"
                 and cfg.tp_size == 1 and cfg.pp_size == 1 and not cfg.use_gradient_checkpoint
-                and getattr(opt, "stage", 0) <= 1 and getattr(opt, "use_main_grad", False)
-                and not getattr(opt, "p2p", False))
+                and getattr(opt, "stage", 0) <= 1 and getattr(opt, "use_main_grad", False))
 
     def _graphed_micro_step(self, input_ids, labels, valid_idx):
         """Forward + loss + backward of one micro-batch as a replayed CUDA graph.
@@ -459,7 +464,8 @@ class TrainEngine:
         first = self._accumulation_count == 0
         # last micro-batch of the window on several data-parallel ranks: the bucket reduce-scatters are captured
         # too, on the optimizer's side stream, so they overlap the rest of the backward pass inside the graph
-        reduce_in_graph = (cfg.cuda_graph_reduce and opt.world > 1 and opt.stage == 1
+        want = cfg.cuda_graph_reduce if cfg.cuda_graph_reduce is not None else bool(getattr(opt, "p2p", False))
+        reduce_in_graph = (want and opt.world > 1 and opt.stage == 1
                            and self._accumulation_count + 1 >= cfg.gradient_accumulation_steps)
         key = (B, S, rows, first, reduce_in_graph)
         seen = self._graph_seen.get(key, 0)

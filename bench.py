@@ -41,15 +41,18 @@ def parse():
     ap.add_argument("--lora-rank", type=int, default=0)
     ap.add_argument("--grad-ckpt", action="store_true")
     ap.add_argument("--sequence-parallel", action="store_true")
-    ap.add_argument("--zero-comm", default="nccl", choices=["nccl", "p2p"])
+    ap.add_argument("--zero-comm", default="auto", choices=["auto", "nccl", "p2p"],
+                    help="ZeRO gradient reduce-scatter / parameter all-gather: inside the optimizer kernels over peer memory "
+                         "(p2p), NCCL, or auto (p2p for plain data parallelism with ZeRO-1, NCCL otherwise)")
     ap.add_argument("--no-zero3-prefetch", dest="zero3_prefetch", action="store_false",
                     help="ZeRO-3: wait for every parameter gather before the forward instead of layer by layer")
     ap.add_argument("--no-cuda-graph", dest="cuda_graph", action="store_false",
                     help="launch the micro-step kernel by kernel instead of replaying forward + backward as one CUDA "
                          "graph (the graph path applies to DP / single GPU with ZeRO <= 1; other layouts run eagerly)")
-    ap.add_argument("--graph-reduce", dest="graph_reduce", action="store_true",
+    ap.add_argument("--graph-reduce", dest="graph_reduce", action="store_true", default=None,
                     help="capture the gradient reduce-scatters inside the last micro-batch's CUDA graph, overlapped with "
-                         "its backward (default: they run after the replay)")
+                         "its backward (default: on for the p2p ZeRO backend, off for NCCL)")
+    ap.add_argument("--no-graph-reduce", dest="graph_reduce", action="store_false")
     ap.add_argument("--layers", type=int, default=0,
                     help="override the preset's layer count (smoke runs of a large architecture; not a benchmark config)")
     ap.add_argument("--fused-tp", action="store_true",
@@ -188,7 +191,8 @@ def run_ours(a):
                        + (f" (layers cut to {a.layers}: smoke run, not the named config)" if a.layers > 0 else ""),
                        "global_batch": a.micro_batch * micro_per_step * dp, "micro_batch_per_gpu": a.micro_batch,
                        "grad_accum": a.grad_accum, "seq_len": a.seq_len, "parallelism": par,
-                       "zero_stage": a.zero_stage, "zero_comm": a.zero_comm, "zero3_prefetch": a.zero3_prefetch,
+                       "zero_stage": a.zero_stage, "zero_comm": getattr(eng.optimizer, "comm_backend", a.zero_comm) if world > 1 else "none (1 GPU)",
+                       "zero_nvls": bool(getattr(eng.optimizer, "nvls", False)), "zero3_prefetch": a.zero3_prefetch,
                        "sequence_parallel": a.sequence_parallel, "fused_tp_comm": a.fused_tp, "grad_ckpt": a.grad_ckpt,
                        "cuda_graph_step": a.cuda_graph, "cuda_graph_reduce": a.graph_reduce, "l2": "inputs larger than L2 (weights+activations >> 126 MB)",
                        "step": "one optimizer step = grad_accum micro-batches + reduce + clip + AdamW"},

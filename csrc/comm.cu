@@ -152,6 +152,98 @@ __global__ void words_checksum_kernel(const D* __restrict__ buf, long long n,
   }
 }
 
+// One unit of a batched copy: n elements from src (element index 0) to dst + dst_off.  A tensor larger than the unit
+// size is cut into several units, so that one launch spreads a whole weight image evenly over the grid.
+struct CopyUnit {
+  const void* src;
+  long long dst_off;
+  long long n;
+};
+
+template <typename S, typename D>
+__device__ __forceinline__ void peer_write_span(const S* __restrict__ src, D* __restrict__ dst, long long n,
+                                                long long elem_offset, int add, unsigned long long& c0,
+                                                unsigned long long& c1, int tid, int nthreads) {
+  long long nvec = 0;
+  if ((reinterpret_cast<uintptr_t>(src) % 16 == 0) && (reinterpret_cast<uintptr_t>(dst + elem_offset) % 16 == 0))
+    nvec = n / 8;
+  for (long long vi = tid; vi < nvec; vi += nthreads) {
+    const long long i0 = vi * 8;
+    float f[8];
+    load8_as_float<S>(src + i0, f);
+    if (add) {
+      float d[8];
+      load8_as_float<D>(dst + elem_offset + i0, d);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) f[j] += d[j];
+    }
+    alignas(16) D o[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      o[j] = cvt_out<D>(f[j]);
+      const unsigned long long b = bits_of<D>(o[j]);
+      c0 += b;
+      c1 += b * static_cast<unsigned long long>(elem_offset + i0 + j + 1);
+    }
+    store8<D>(dst + elem_offset + i0, o);
+  }
+  for (long long i = nvec * 8 + tid; i < n; i += nthreads) {
+    float v = cvt_in<S>(src[i]);
+    if (add) v += cvt_in<D>(dst[elem_offset + i]);
+    const D o = cvt_out<D>(v);
+    dst[elem_offset + i] = o;
+    const unsigned long long b = bits_of<D>(o);
+    c0 += b;
+    c1 += b * static_cast<unsigned long long>(elem_offset + i + 1);
+  }
+}
+
+// The whole image in one launch: block b handles units b, b + grid, ...; cast, optional add and the
+// position-weighted checksum as in peer_write_kernel (positions are offsets into the destination image).
+template <typename S, typename D>
+__global__ void peer_write_batch_kernel(const CopyUnit* __restrict__ units, int nunits, D* __restrict__ dst, int add,
+                                        unsigned long long* __restrict__ checksum) {
+  unsigned long long c0 = 0, c1 = 0;
+  for (int u = blockIdx.x; u < nunits; u += gridDim.x) {
+    const CopyUnit cu = units[u];
+    peer_write_span<S, D>(static_cast<const S*>(cu.src), dst, cu.n, cu.dst_off, add, c0, c1, threadIdx.x, blockDim.x);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    c0 += __shfl_xor_sync(0xffffffffu, c0, o);
+    c1 += __shfl_xor_sync(0xffffffffu, c1, o);
+  }
+  if ((threadIdx.x & 31) == 0 && checksum) {
+    atomicAdd(checksum, c0);
+    atomicAdd(checksum + 1, c1);
+  }
+  __threadfence_system();
+}
+
+// Checksum of the same spans on the receiving side (src is ignored): only what a delta touched is summed.
+template <typename D>
+__global__ void spans_checksum_kernel(const CopyUnit* __restrict__ units, int nunits, const D* __restrict__ buf,
+                                      unsigned long long* __restrict__ checksum) {
+  unsigned long long c0 = 0, c1 = 0;
+  for (int u = blockIdx.x; u < nunits; u += gridDim.x) {
+    const CopyUnit cu = units[u];
+    for (long long i = threadIdx.x; i < cu.n; i += blockDim.x) {
+      const unsigned long long b = bits_of<D>(buf[cu.dst_off + i]);
+      c0 += b;
+      c1 += b * static_cast<unsigned long long>(cu.dst_off + i + 1);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    c0 += __shfl_xor_sync(0xffffffffu, c0, o);
+    c1 += __shfl_xor_sync(0xffffffffu, c1, o);
+  }
+  if ((threadIdx.x & 31) == 0) {
+    atomicAdd(checksum, c0);
+    atomicAdd(checksum + 1, c1);
+  }
+}
+
 struct PeerPtrs {
   void* p[8];
 };
@@ -313,6 +405,45 @@ B2_EXPORT int b2_peer_write(const void* src, int src_fp32, void* dst, int dst_fp
   else
     peer_write_kernel<__nv_bfloat16, __nv_bfloat16><<<g, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(src), static_cast<__nv_bfloat16*>(dst), n, elem_offset, add, checksum);
   B2_LAUNCH_CHECK("peer_write");
+  return 0;
+}
+
+// units: device array of {src pointer, destination element offset, element count} (24 bytes each); every source has
+// the same element type.  One launch writes the whole image into dst (local or peer pointer).
+B2_EXPORT int b2_peer_write_batch(const void* units, int nunits, int src_fp32, void* dst, int dst_fp32, int add,
+                                  unsigned long long* checksum, void* stream_) {
+  b2::ensure_thread_context();
+  if (nunits <= 0) return 0;
+  if (units == nullptr || dst == nullptr) { set_error("peer_write_batch: null table or destination"); return 10; }
+  cudaStream_t s = static_cast<cudaStream_t>(stream_);
+  const CopyUnit* u = static_cast<const CopyUnit*>(units);
+  int g = num_sms() * 4;
+  if (g > nunits) g = nunits;
+  if (src_fp32 && dst_fp32)
+    peer_write_batch_kernel<float, float><<<g, 256, 0, s>>>(u, nunits, static_cast<float*>(dst), add, checksum);
+  else if (src_fp32)
+    peer_write_batch_kernel<float, __nv_bfloat16><<<g, 256, 0, s>>>(u, nunits, static_cast<__nv_bfloat16*>(dst), add, checksum);
+  else if (dst_fp32)
+    peer_write_batch_kernel<__nv_bfloat16, float><<<g, 256, 0, s>>>(u, nunits, static_cast<float*>(dst), add, checksum);
+  else
+    peer_write_batch_kernel<__nv_bfloat16, __nv_bfloat16><<<g, 256, 0, s>>>(u, nunits, static_cast<__nv_bfloat16*>(dst), add, checksum);
+  B2_LAUNCH_CHECK("peer_write_batch");
+  return 0;
+}
+
+B2_EXPORT int b2_spans_checksum(const void* units, int nunits, const void* buf, int is_fp32,
+                                unsigned long long* checksum, void* stream_) {
+  b2::ensure_thread_context();
+  if (nunits <= 0) return 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream_);
+  const CopyUnit* u = static_cast<const CopyUnit*>(units);
+  int g = num_sms() * 4;
+  if (g > nunits) g = nunits;
+  if (is_fp32)
+    spans_checksum_kernel<float><<<g, 256, 0, s>>>(u, nunits, static_cast<const float*>(buf), checksum);
+  else
+    spans_checksum_kernel<__nv_bfloat16><<<g, 256, 0, s>>>(u, nunits, static_cast<const __nv_bfloat16*>(buf), checksum);
+  B2_LAUNCH_CHECK("spans_checksum");
   return 0;
 }
 

@@ -227,12 +227,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const int r = t - g * per_group;
     m_blk = first_m + (r % gsz);
     n_blk = r / gsz;
-    if (COMM != 0) {
-      // COMM 1: tiles owned by other ranks first (rank+1, rank+2, ...), own rows last, so that peers
-      // can start reducing early.  COMM 2: own rows first (already local), then in ring order.
+    if (COMM == 1) {
+      // Consecutive row blocks of the schedule belong to consecutive owners (starting with the next rank, own rows
+      // last): every rank works on row block j of ALL owners before block j + 1, so block j of every shard is
+      // complete on all sources after (j + 1) / blocks-per-rank of the kernel and its owner can reduce it while the
+      // GEMM goes on.  (A rank-by-rank order finishes every shard only at the very end: the whole reduce is exposed.)
       const int bpr = comm.rows_per_rank / GEMM_BM;
-      const int rot = (COMM == 1 ? (comm.rank + 1) % comm.world : comm.rank) * bpr;
-      m_blk = (m_blk + rot) % num_m;
+      const int j = m_blk / comm.world, s_ = m_blk % comm.world;
+      m_blk = ((s_ + comm.rank + 1) % comm.world) * bpr + j;
+    } else if (COMM == 2) {
+      // own rows first (already local), then in ring order
+      const int bpr = comm.rows_per_rank / GEMM_BM;
+      m_blk = (m_blk + comm.rank * bpr) % num_m;
     }
   };
 
@@ -362,6 +368,21 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const bool residual = flags & GEMM_RESIDUAL;
     uint32_t slab_count = 0;
     const bool atomic_out = split_k > 1;   // several units add into the same fp32 tile
+    // COMM 1: reduce jobs (row block rb of this rank's shard x column block nb) are dealt to the CTAs in the order
+    // the row blocks complete; a CTA looks at its next job after every tile and runs it when its counter is full.
+    int rjob = blockIdx.x;
+    const int rjobs = COMM == 1 ? (comm.rows_per_rank / GEMM_BM) * num_n : 0;
+    auto run_reduce_job = [&](int job) {
+      const int rb = job / num_n, nb = job % num_n;
+      const int c = nb * BN + lane * 8;            // 32 lanes x 8 columns = one 256-column row segment
+      if (c >= N || (BN == 128 && lane >= 16)) return;
+      const __nv_bfloat16* recv = static_cast<const __nv_bfloat16*>(comm.peer_recv[comm.rank]);
+      const int ewarp = (threadIdx.x - 64) >> 5;
+      if (comm.world <= 4)
+        reduce_rows<4, 4>(recv, comm, rb, c, N, ewarp);
+      else
+        reduce_rows<2, 8>(recv, comm, rb, c, N, ewarp);
+    };
     for (int u = blockIdx.x; u < num_units; u += gridDim.x) {
       const int t = u % num_tiles;
       int m_blk, n_blk;
@@ -436,6 +457,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1;
+        if (rjob < rjobs) {
+          // one look (no spin) at the next reduce job: all sources' tiles landed -> reduce it now, under the MMAs
+          // of the tiles that follow
+          bool ready = false;
+          if (threadIdx.x == 64)
+            ready = ld_acquire_sys_s32(comm.peer_cnt[comm.rank] + rjob) >= comm.world * comm.epoch;
+          if (named_barrier_or(1, 128, ready)) {
+            run_reduce_job(rjob);
+            rjob += gridDim.x;
+          }
+        }
         continue;
       }
       if (!out_fp32) {
@@ -606,24 +638,14 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     if (warp == 2 && lane == 0) tma_store_wait_all<0>();   // shared memory stays valid until stores have read it
     if (COMM == 1) {
-      // ---- reduce phase: sum this rank's row blocks over all source ranks as they complete -----------
+      // ---- the reduce jobs still open after the last tile: wait (bounded) for each and run it -----------
       const int et = threadIdx.x - 64;               // 0..127
-      const int ewarp = et >> 5;
-      const int bpr = comm.rows_per_rank / GEMM_BM;
-      const int jobs = bpr * num_n;
-      const __nv_bfloat16* recv = static_cast<const __nv_bfloat16*>(comm.peer_recv[comm.rank]);
       const int* cnt = comm.peer_cnt[comm.rank];
       bool ok = true;
-      for (int j = blockIdx.x; j < jobs; j += gridDim.x) {
-        const int rb = j / num_n, nb = j % num_n;
-        if (et == 0 && ok) ok = wait_flag_ge<true>(cnt + rb * num_n + nb, comm.world * comm.epoch, status, ERR_COMM_FLAG_WAIT);
+      for (; rjob < rjobs; rjob += gridDim.x) {
+        if (et == 0 && ok) ok = wait_flag_ge<true>(cnt + rjob, comm.world * comm.epoch, status, ERR_COMM_FLAG_WAIT);
         if (named_barrier_or(1, 128, !ok)) break;
-        const int c = nb * BN + lane * 8;            // 32 lanes x 8 columns = one 256-column row segment
-        if (c >= N || (BN == 128 && lane >= 16)) continue;
-        if (comm.world <= 4)
-          reduce_rows<4, 4>(recv, comm, rb, c, N, ewarp);
-        else
-          reduce_rows<2, 8>(recv, comm, rb, c, N, ewarp);
+        run_reduce_job(rjob);
       }
     }
   }

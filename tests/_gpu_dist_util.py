@@ -12,9 +12,10 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _entry(rank, world, port, fn, args, q):
+def _entry(rank, world, port, fn, args, q, env=None):
     os.environ.update({"RANK": str(rank), "WORLD_SIZE": str(world), "LOCAL_RANK": str(rank),
                        "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": str(port), "NCCL_NVLS_ENABLE": "0"})
+    os.environ.update(env or {})
     import torch
     import torch.distributed as dist
     try:
@@ -33,11 +34,11 @@ def _entry(rank, world, port, fn, args, q):
             dist.destroy_process_group()
 
 
-def run_gpu_ranks(fn, world: int, *args, timeout: float = 300.0):
+def run_gpu_ranks(fn, world: int, *args, timeout: float = 300.0, env=None):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_entry, args=(r, world, port, fn, args, q)) for r in range(world)]
+    procs = [ctx.Process(target=_entry, args=(r, world, port, fn, args, q, env)) for r in range(world)]
     for p in procs:
         p.start()
     results = {}

@@ -497,6 +497,14 @@ def test_peer_write_checksum_rejects_corruption():
     got.clear()
     assert ps.sync(True, {"w": state["w"] * 2, "b": state["b"]}, Eng(), corrupt=True) == 1     # version kept
     assert got == {} and ps.get_stats()["rejected"] == 1
+    # a delta (add mode) touches one tensor only; its checksum covers exactly that span and is verified too
+    ps.sync(True, state, Eng())                                   # clean image again (version 2)
+    got.clear()
+    d = {"b": torch.ones(7)}
+    assert ps.sync(True, d, Eng(), add=True) == 3
+    assert torch.equal(got["b"], (state["b"].to(torch.bfloat16).float() + 1).to(torch.bfloat16))
+    got.clear()
+    assert ps.sync(True, d, Eng(), add=True, corrupt=True) == 3 and got == {} and ps.get_stats()["rejected"] == 2
     c0, c1 = fletcher_checksum(torch.tensor([1.0, 2.0], dtype=torch.bfloat16))
     assert c0 == 0x3F80 + 0x4000 and c1 == 0x3F80 + 2 * 0x4000
 

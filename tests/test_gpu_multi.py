@@ -72,6 +72,9 @@ def _zero_worker(rank, world, backend, stage):
                       amp_dtype="bf16", zero_comm_backend=backend, bucket_mb=1.0)
     eng = TrainEngine(cfg).initialize()
     assert eng.optimizer.p2p == (backend == "p2p")
+    import os
+    if backend == "p2p" and os.environ.get("B200FW_NVLS") == "0":
+        assert not eng.optimizer.nvls
     out = []
     for s in range(6):
         g = torch.Generator().manual_seed(s * 31 + rank)
@@ -85,12 +88,15 @@ def _zero_worker(rank, world, backend, stage):
 
 
 @needs2
-@pytest.mark.parametrize("stage", [1, 2])
-def test_zero_p2p_matches_nccl(stage):
+@pytest.mark.parametrize("stage,nvls", [(1, "1"), (2, "1"), (1, "0")])
+def test_zero_p2p_matches_nccl(stage, nvls):
+    """The in-kernel data plane (per-bucket device barrier + reduce launched from the gradient hooks, one-kernel
+    norm exchange, AdamW + publish, end-of-step barrier) against NCCL reduce-scatter / all-gather; with the
+    switch's multimem reduce / store where the platform offers it (nvls "1") and with plain peer loads / stores."""
     from _gpu_dist_util import run_gpu_ranks
     w = _world()
     a = run_gpu_ranks(_zero_worker, w, "nccl", stage)
-    b = run_gpu_ranks(_zero_worker, w, "p2p", stage)
+    b = run_gpu_ranks(_zero_worker, w, "p2p", stage, env={"B200FW_NVLS": nvls})
     for r in range(w):
         assert a[r][1] == a[0][1] and b[r][1] == b[0][1]            # ranks hold identical weights
         for i, ((la, ga), (lb, gb)) in enumerate(zip(a[r][0], b[r][0])):
@@ -98,6 +104,46 @@ def test_zero_p2p_matches_nccl(stage):
             if i < 2:     # later steps amplify bf16 rounding differences between the two reduction orders
                 assert abs(ga - gb) / max(ga, 1e-6) < 5e-2, (i, ga, gb)
         assert abs(a[r][2] - b[r][2]) / a[r][2] < 2e-3
+
+
+def _zero_wait_runs_out_worker(rank, world):
+    """Rank 0 waits (300 ms limit) on a barrier channel that rank 1 never enters: the wait runs out, the device-side
+    ``ok`` word is cleared, this step's AdamW leaves rank 0's shard untouched, and the host raises at the step's
+    sync instead of training on.  Nothing faults; both ranks finish the step's collectives and leave between steps."""
+    from b200fw import _native as nv
+    from b200fw.train import TrainConfig, TrainEngine
+    cfg = TrainConfig(model_preset="tiny128", dp_size=world, lora_rank=0, grpo_beta=0.0, learning_rate=1e-3,
+                      gradient_accumulation_steps=1, zero_stage=1, warmup_steps=0, max_seq_len=256,
+                      amp_dtype="bf16", zero_comm_backend="p2p", bucket_mb=1.0)
+    eng = TrainEngine(cfg).initialize()
+    opt = eng.optimizer
+    g = torch.Generator().manual_seed(rank)
+    ids = torch.randint(0, 8192, (2, 256), generator=g)
+    labels = ids.clone()
+    labels[:, :128] = -100
+    eng.sft_step_tensors(ids, labels)                    # a clean step first
+    before = opt.master.clone()
+    raised = False
+    if rank == 0:
+        opt.flags.limit_ms = 300
+        opt.flags.barrier_dev(opt._ch_spare)             # nobody else signals this channel
+        opt.flags.limit_ms = 2000
+    try:
+        eng.sft_step_tensors(ids, labels)
+    except nv.NativeError as e:
+        raised = "301" in str(e)
+    torch.cuda.synchronize()
+    unchanged = bool(torch.equal(opt.master, before))
+    alive = float((torch.ones(4, device="cuda") * 3).sum())
+    return raised, unchanged, alive
+
+
+@needs2
+def test_zero_p2p_wait_that_runs_out_skips_the_update_and_raises():
+    from _gpu_dist_util import run_gpu_ranks
+    r0, r1 = run_gpu_ranks(_zero_wait_runs_out_worker, 2, env={"B200FW_NVLS": "0"})
+    assert r0 == (True, True, 12.0)                      # raised, shard untouched, device usable
+    assert r1 == (False, False, 12.0)                    # the healthy rank stepped normally
 
 
 def _zero3_worker(rank, world, stage):
@@ -139,12 +185,14 @@ def test_zero3_prefetched_gathers_match_zero1():
         assert abs(a[r][1][1] - b[r][1][1]) / a[r][1][1] < 2e-3
 
 
-def _graph_dp_worker(rank, world, graph, reduce_in_graph):
+def _graph_dp_worker(rank, world, graph, reduce_in_graph, backend="nccl"):
     from b200fw.train import TrainConfig, TrainEngine
     cfg = TrainConfig(model_preset="tiny128", dp_size=world, lora_rank=0, grpo_beta=0.0, learning_rate=1e-3,
                       gradient_accumulation_steps=2, zero_stage=1, warmup_steps=0, max_seq_len=256, amp_dtype="bf16",
-                      bucket_mb=1.0, cuda_graph_step=graph, cuda_graph_reduce=reduce_in_graph)
+                      bucket_mb=1.0, cuda_graph_step=graph, cuda_graph_reduce=reduce_in_graph,
+                      zero_comm_backend=backend)
     eng = TrainEngine(cfg).initialize()
+    assert eng.optimizer.comm_backend == ("p2p" if backend in ("p2p", "auto") else "nccl")
     out = []
     for s in range(14):                      # 7 optimizer steps: two eager occurrences per graph key, then replays
         g = torch.Generator().manual_seed(s * 31 + rank)
@@ -159,14 +207,17 @@ def _graph_dp_worker(rank, world, graph, reduce_in_graph):
 
 
 @needs2
-def test_graphed_micro_step_with_captured_reduce_scatter_matches_eager():
+@pytest.mark.parametrize("backend", ["nccl", "auto"])
+def test_graphed_micro_step_with_captured_reduce_scatter_matches_eager(backend):
     """Data parallel: the last micro-batch's graph contains the bucket reduce-scatters (side stream forked
-    and joined inside the capture); losses, gradient norms and weights follow the eager run."""
+    and joined inside the capture); losses, gradient norms and weights follow the eager NCCL run.  With the
+    default ("auto") backend the captured reductions are the in-kernel ones: device-epoch barrier + peer /
+    multimem reduce per bucket."""
     from _gpu_dist_util import run_gpu_ranks
-    w = min(_world(), 2)
-    eager = run_gpu_ranks(_graph_dp_worker, w, False, False)
-    fused = run_gpu_ranks(_graph_dp_worker, w, True, True)
-    plain = run_gpu_ranks(_graph_dp_worker, w, True, False)
+    w = min(_world(), 2) if backend == "nccl" else _world()
+    eager = run_gpu_ranks(_graph_dp_worker, w, False, False, "nccl")
+    fused = run_gpu_ranks(_graph_dp_worker, w, True, True, backend)
+    plain = run_gpu_ranks(_graph_dp_worker, w, True, False, backend)
     assert fused[0][3] == [(False, True), (True, False)] and not fused[0][4]       # (first, reduce captured) keys
     assert plain[0][3] == [(False, False), (True, False)] and eager[0][3] == []
     for r in range(w):
@@ -198,7 +249,16 @@ def _peer_sync_worker(rank, world):
     got.clear()
     v2 = ps.sync(rank == 0, {k: v * 2 for k, v in state.items()} if rank == 0 else None,
                  None if rank == 0 else Eng(), corrupt=True)
-    return v1, ok1, v2, len(got), ps.get_stats()["rejected"]
+    rej = ps.get_stats()["rejected"]
+    # delta on one tensor: verified over the spans it touched; a corrupted delta is rejected as well
+    v3 = ps.sync(rank == 0, state if rank == 0 else None, None if rank == 0 else Eng())       # clean image
+    got.clear()
+    delta = {"w2": torch.ones(1000, device="cuda")}
+    v4 = ps.sync(rank == 0, delta if rank == 0 else None, None if rank == 0 else Eng(), add=True)
+    ok4 = rank == 0 or torch.equal(got["w2"], (state["w2"].to(torch.bfloat16).float() + 1).to(torch.bfloat16))
+    got.clear()
+    v5 = ps.sync(rank == 0, delta if rank == 0 else None, None if rank == 0 else Eng(), add=True, corrupt=True)
+    return v1, ok1, v2, len(got), rej, (v3, v4, ok4, v5, ps.get_stats()["rejected"])
 
 
 @needs2
@@ -206,6 +266,7 @@ def test_peer_write_weight_sync_across_gpus():
     from _gpu_dist_util import run_gpu_ranks
     res = run_gpu_ranks(_peer_sync_worker, 2)
     assert res[0][:3] == (1, True, 1) and res[1][:4] == (1, True, 1, 0) and res[1][4] == 1
+    assert res[0][5][:4] == (2, 3, True, 3) and res[1][5] == (2, 3, True, 3, 2)
 
 
 def _fused_tp_ops_worker(rank, world):

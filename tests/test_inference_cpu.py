@@ -114,8 +114,16 @@ def test_mock_engine_lifecycle():
     e.add_request("x", [1] * 10, max_tokens=50)
     e.step()
     assert e.has_pending()
+    # a weight update keeps running requests (staleness 1 is within the default bound) ...
     e.on_weights_updated()
-    assert not e.has_pending() and e.get_stats()["weights_version"] == 1
+    assert e.has_pending() and e.get_stats()["weights_version"] == 1 and e.requests["x"].weights_version == 0
+    # ... a second one makes the request two versions stale: it is dropped, as is everything on abort_running=True
+    e.on_weights_updated()
+    assert not e.has_pending() and e.get_stats()["aborted_stale"] == 1
+    e.add_request("y", [1] * 10, max_tokens=50)
+    e.step()
+    e.on_weights_updated(abort_running=True)
+    assert not e.has_pending() and e.get_stats()["weights_version"] == 3
     k = e.generate([[7, 8]] * 4, max_tokens=3)           # K samples of one prompt
     assert len(k) == 4
 
