@@ -337,3 +337,71 @@ def send_backward_recv_forward(grad: torch.Tensor, shape, dtype, device, peer: O
     buf = torch.empty(tuple(shape), dtype=dtype, device=device)
     _batch([dist.P2POp(dist.isend, grad.contiguous(), peer, group), dist.P2POp(dist.irecv, buf, peer, group)])
     return buf
+
+
+class PipeChannel:
+    """One direction of one pipeline-stage boundary: an ordered stream of equally shaped tensors to ``peer`` (a
+    sender) or from it (a receiver), on a communicator and a CUDA stream of its own.
+
+    The reference's stage-to-stage primitives (src/distributed/comm.py:404-558) post a send / receive pair and wait
+    for it on the compute stream, with a fresh receive buffer per call.  Here activations (downstream) and
+    gradients (upstream) travel on separate communicators, so a receive can be *posted* well before its data is
+    needed and a send never holds the compute stream:
+
+    * ``post_recv()`` enqueues the receive into the next buffer of a persistent ring on the communication stream
+      (which first waits for the compute work queued so far: the buffer's previous use is over) and returns a handle;
+      ``wait(handle)`` makes the compute stream wait for it and returns the buffer.  Between the two calls the
+      transfer runs under whatever compute was queued in between.
+    * ``send(t)`` enqueues the send on the communication stream after the compute work that produced ``t``; the
+      compute stream does not wait for it.
+
+    On CPU (gloo) the same calls are plain ``irecv`` / ``isend`` with ``wait`` at the matching point."""
+
+    def __init__(self, group, peer: Optional[int], shape, dtype, device, depth: int = 4):
+        self.group, self.peer = group, peer
+        self.device = torch.device(device)
+        self.cuda = self.device.type == "cuda"
+        self.ring = [torch.empty(tuple(shape), dtype=dtype, device=device) for _ in range(depth)] if peer is not None else []
+        self.next = 0
+        self.stream = torch.cuda.Stream(device=self.device) if (self.cuda and peer is not None) else None
+        self._sends: List = []
+
+    def post_recv(self):
+        if self.peer is None:
+            return None
+        buf = self.ring[self.next % len(self.ring)]
+        self.next += 1
+        if self.cuda:
+            self.stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self.stream):
+                work = dist.irecv(buf, src=self.peer, group=self.group)
+        else:
+            work = dist.irecv(buf, src=self.peer, group=self.group)
+        return buf, work
+
+    def wait(self, handle) -> Optional[torch.Tensor]:
+        if handle is None:
+            return None
+        buf, work = handle
+        work.wait()          # NCCL: the current (compute) stream waits for the transfer; gloo: the host does
+        return buf
+
+    def send(self, t: torch.Tensor):
+        if self.peer is None:
+            return
+        t = t.contiguous()
+        if self.cuda:
+            self.stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self.stream):
+                work = dist.isend(t, dst=self.peer, group=self.group)
+            t.record_stream(self.stream)
+        else:
+            work = dist.isend(t, dst=self.peer, group=self.group)
+        self._sends = [(w, x) for w, x in self._sends if not w.is_completed()] + [(work, t)]
+
+    def flush(self):
+        """End of a schedule: every send has left (gloo needs the explicit wait; on NCCL this orders the
+        communication stream before whatever the compute stream does next with the sent tensors' memory)."""
+        for w, _ in self._sends:
+            w.wait()
+        self._sends = []

@@ -31,6 +31,7 @@ class ParallelContext:
         self.pp_rank = (rank // tp_size) % pp_size
         self.dp_rank = rank // (tp_size * pp_size)
         self.tp_group, self.pp_group, self.dp_group = tp_group, pp_group, dp_group
+        self.pp_fwd_group = self.pp_bwd_group = None      # per-direction pipeline communicators (init_distributed)
         self.tp_ranks: List[int] = [rank]
         self.pp_ranks: List[int] = [rank]
         self.dp_ranks: List[int] = [rank]
@@ -87,8 +88,13 @@ class ParallelContext:
                     ctx.tp_group, ctx.tp_ranks = g, ranks
             for ranks in pp_groups:
                 g = dist.new_group(ranks) if pp_size > 1 else None
+                # one more communicator per direction of the pipeline (activations downstream, gradients upstream):
+                # the two flows then never queue behind each other and each can be posted ahead of its use
+                gf = dist.new_group(ranks) if pp_size > 1 else None
+                gb = dist.new_group(ranks) if pp_size > 1 else None
                 if rank in ranks:
                     ctx.pp_group, ctx.pp_ranks = g, ranks
+                    ctx.pp_fwd_group, ctx.pp_bwd_group = gf, gb
             for ranks in dp_groups:
                 g = dist.new_group(ranks) if dp_size > 1 else None
                 if rank in ranks:

@@ -76,7 +76,8 @@ class ColumnParallelLinear(nn.Module):
         if (self.tp_size > 1 and self.sequence_parallel and self.fused_comm and x.is_cuda and x.shape[0] % 128 == 0
                 and self.bias is None):
             from ..ops import fused_tp
-            y = fused_tp.column_linear_sp(x, self.weight, self.tp_group)    # all-gather inside the GEMM
+            y = fused_tp.column_linear_sp(x, self.weight, self.tp_group,    # all-gather inside the GEMM
+                                          slot=getattr(self, "fused_slot", None))
             return y
         if self.tp_size > 1:
             x = comm.gather_sequence(x, self.tp_group) if self.sequence_parallel \
@@ -295,9 +296,17 @@ class ParallelTransformerModel(nn.Module):
     def set_fused_comm(self, on: bool = True):
         """Run every sequence-parallel linear's collective inside its GEMM kernel (peer loads / stores
         over NVLink) instead of as separate NCCL calls."""
-        for m in self.modules():
+        import re
+        for name, m in self.named_modules():
             if isinstance(m, (ColumnParallelLinear, RowParallelLinear)):
                 m.fused_comm = on and self.sequence_parallel
+                # gather-buffer slot of a column-parallel layer: its gathered input is saved for the weight gradient.
+                # With gradient checkpointing a layer's forward is recomputed right before its backward, so one slot
+                # per role serves all layers; without it every layer keeps its own until the backward pass.
+                role = [p for p in name.split(".") if p.endswith("_proj")]
+                li = re.search(r"layers\.(\d+)\.", name)
+                m.fused_slot = (role[0] if role else name,
+                                -1 if (self.gradient_checkpointing or li is None) else int(li.group(1)))
 
     def _tag_parameters(self):
         # parameters whose per-rank gradient is only a partial sum under TP (their inputs are head-

@@ -1,8 +1,9 @@
 """Tensor-parallel linear layers whose collective runs INSIDE the tcgen05 GEMM kernel.
 
 * :func:`allgather_gemm`   — column-parallel forward (and the input-gradient GEMM of a row-parallel
-  layer): the sequence-parallel activation shards of all ranks are pulled into a local gather buffer by
-  extra warps of the GEMM kernel while its MMA pipeline already works on the rows that have arrived.
+  layer): extra warps of the GEMM kernel push this rank's sequence-parallel activation shard into every
+  rank's gather buffer (one ``multimem.st`` through the switch per 16 bytes where NVLS is available, else one
+  store per peer) while the MMA pipeline already works on the row blocks whose pieces have all arrived.
 * :func:`gemm_reduce_scatter` — row-parallel forward (and the input-gradient GEMM of a column-parallel
   layer): every output tile goes straight to the rank that owns those rows; each rank sums its rows
   over the source ranks (and adds the residual) as soon as the tiles land.
@@ -35,12 +36,17 @@ class _RSState:
         self.calls = 0
 
 
-class _AGState:
+class _AGSlot:
+    """The gather buffers of one call site ("slot"): two parities of a symmetric ``[M, K]`` buffer with their
+    arrival counters.  The gathered activations a call returns ARE the buffer (no copy): a slot must not be used
+    again twice before the tensor returned earlier has been consumed (``generation`` lets the consumer check)."""
+
     def __init__(self, group, rows, K, device):
         self.world = dist.get_world_size(group)
-        self.src = [SymmetricBuffer(rows * K, torch.bfloat16, group, device) for _ in range(2)]
-        self.flags = torch.zeros(self.world * rows // 128, dtype=torch.int32, device=device)
-        self.epoch = 0
+        M = rows * self.world
+        self.buf = [SymmetricBuffer(M * K, torch.bfloat16, group, device) for _ in range(2)]
+        self.flags = [SymmetricBuffer(M // 128, torch.int32, group, device) for _ in range(2)]
+        self.uses = [0, 0]
         self.calls = 0
 
 
@@ -55,8 +61,11 @@ class FusedTPContext:
         self.rank = dist.get_rank(group)
         self.device = torch.device("cuda", torch.cuda.current_device())
         self.rs: Dict[Tuple[int, int, int], _RSState] = {}
-        self.ag: Dict[Tuple[int, int], _AGState] = {}
+        self.ag: Dict[tuple, _AGSlot] = {}
         self.barrier = FlagBarrier(group, self.device)
+        # "rank p has entered fused all-gather call number c": written by the peers, read by the push warps
+        self.ag_ready = SymmetricBuffer(8, torch.int32, group, self.device)
+        self.ag_calls = 0
 
     @classmethod
     def get(cls, group) -> "FusedTPContext":
@@ -93,40 +102,47 @@ def gemm_reduce_scatter(x: torch.Tensor, w: torch.Tensor, group, *, b_mn: bool =
         assert residual.shape == (rows, N) and residual.is_contiguous()
     nv.check(nv.lib().b2_gemm_bf16_comm(
         1, nv.ptr(x), nv.ptr(w), nv.ptr(None), M, N, K, w.stride(0), int(b_mn), bn, st.recv[par].ptr_array,
-        st.cnt[par].ptr_array, nv.ptr(out), nv.ptr(residual), None, nv.ptr(None), nv.ptr(None), ctx.world, ctx.rank,
+        st.cnt[par].ptr_array, nv.ptr(out), nv.ptr(residual), None, nv.ptr(None), None, None, 0, ctx.world, ctx.rank,
         rows, st.epoch[par], nv.stream_ptr()), "gemm_reduce_scatter")
     nv.count_launch()
     return out
 
 
-def allgather_gemm(x_shard: torch.Tensor, w: torch.Tensor, group, *, b_mn: bool = False
+def allgather_gemm(x_shard: torch.Tensor, w: torch.Tensor, group, *, b_mn: bool = False, slot=None
                    ) -> Tuple[torch.Tensor, torch.Tensor]:
     """``all_gather_rows(x_shard) @ w^T``: ``x_shard [M/world, K]``; returns ``(y [M, N], gathered x
-    [M, K])`` — the gathered activations are kept for the weight-gradient GEMM."""
+    [M, K])`` — the gathered activations are kept for the weight-gradient GEMM.
+
+    ``slot`` names the call site whose (double-buffered) symmetric gather buffers are used; the returned
+    ``gathered`` is then a view of the buffer and stays valid until the slot's second next call.  Callers whose
+    gathered activations live longer (saved for a backward pass that runs after other calls of the same shape) pass
+    a slot of their own; without a slot the buffers are shared per shape and ``gathered`` is a private copy whenever
+    autograd is recording."""
     ctx = FusedTPContext.get(group)
     rows, K = x_shard.shape
     N = w.shape[1] if b_mn else w.shape[0]
     M = rows * ctx.world
-    assert rows % 128 == 0 and w.stride(-1) == 1
-    key = (rows, K)
+    assert rows % 128 == 0 and w.stride(-1) == 1 and x_shard.is_contiguous()
+    key = ("slot", slot, rows, K) if slot is not None else ("shape", rows, K)
     st = ctx.ag.get(key)
     if st is None:
-        st = ctx.ag[key] = _AGState(group, rows, K, ctx.device)
+        st = ctx.ag[key] = _AGSlot(group, rows, K, ctx.device)
+        ctx.barrier.barrier(3)       # everyone's buffers and counters exist (zeroed) before the first piece lands
     par = st.calls & 1
     st.calls += 1
-    st.epoch += 1
-    src = st.src[par]
-    src.tensor.view(rows, K).copy_(x_shard)
-    # all ranks have published their shard (and finished reading this parity's previous contents)
-    ctx.barrier.barrier(3)
-    gathered = torch.empty((M, K), device=x_shard.device, dtype=torch.bfloat16)
+    st.uses[par] += 1
+    ctx.ag_calls += 1
+    buf, flags = st.buf[par], st.flags[par]
     y = torch.empty((M, N), device=x_shard.device, dtype=torch.bfloat16)
     bn = _bn_for(M, N)
     nv.check(nv.lib().b2_gemm_bf16_comm(
-        2, nv.ptr(None), nv.ptr(w), nv.ptr(y), M, N, K, w.stride(0), int(b_mn), bn, None, None, nv.ptr(None),
-        nv.ptr(None), src.ptr_array, nv.ptr(gathered), nv.ptr(st.flags), ctx.world, ctx.rank, rows, st.epoch,
-        nv.stream_ptr()), "allgather_gemm")
+        2, nv.ptr(x_shard), nv.ptr(w), nv.ptr(y), M, N, K, w.stride(0), int(b_mn), bn, None, None, nv.ptr(None),
+        nv.ptr(None), buf.ptr_array, nv.ctypes.c_void_p(buf.mc_ptr), flags.ptr_array, ctx.ag_ready.ptr_array,
+        ctx.ag_calls, ctx.world, ctx.rank, rows, st.uses[par], nv.stream_ptr()), "allgather_gemm")
     nv.count_launch()
+    gathered = buf.tensor.view(M, K)
+    if slot is None and torch.is_grad_enabled():
+        gathered = gathered.clone()
     return y, gathered
 
 
@@ -152,8 +168,8 @@ class _ColumnLinearSP(torch.autograd.Function):
     inside the GEMM, dW = dy^T @ gathered x."""
 
     @staticmethod
-    def forward(ctx, x, w, group):
-        y, xg = allgather_gemm(x, w, group)
+    def forward(ctx, x, w, group, slot):
+        y, xg = allgather_gemm(x, w, group, slot=slot)
         ctx.save_for_backward(xg, w)
         ctx.group = group
         return y
@@ -164,7 +180,7 @@ class _ColumnLinearSP(torch.autograd.Function):
         dy = dy.contiguous()
         dx = _reduce_scatter_gemm(dy, w, ctx.group, b_mn=True)
         dw = grad_into_main(w, lambda out, acc: gemm(dy, xg, a_mn=True, b_mn=True, out=out, accumulate=acc))
-        return dx, dw, None
+        return dx, dw, None, None
 
 
 class _RowLinearSP(torch.autograd.Function):
@@ -182,13 +198,15 @@ class _RowLinearSP(torch.autograd.Function):
     def backward(ctx, dy):
         x, w = ctx.saved_tensors
         dy = dy.contiguous()
-        dx, dyg = allgather_gemm(dy, w, ctx.group, b_mn=True)
+        # the gathered gradient is consumed by the weight-gradient GEMM right below: one shared slot serves every layer
+        dx, dyg = allgather_gemm(dy, w, ctx.group, b_mn=True, slot="backward")
         dw = grad_into_main(w, lambda out, acc: gemm(dyg, x, a_mn=True, b_mn=True, out=out, accumulate=acc))
         return dx, dw, (dy if ctx.has_res else None), None
 
 
-def column_linear_sp(x: torch.Tensor, w: torch.Tensor, group) -> torch.Tensor:
-    return _ColumnLinearSP.apply(x.contiguous(), w, group)
+def column_linear_sp(x: torch.Tensor, w: torch.Tensor, group, slot=None) -> torch.Tensor:
+    """``slot``: see :func:`allgather_gemm` (the gathered input is saved for the weight gradient)."""
+    return _ColumnLinearSP.apply(x.contiguous(), w, group, slot)
 
 
 def row_linear_sp(x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor], group) -> torch.Tensor:

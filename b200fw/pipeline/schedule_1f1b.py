@@ -5,6 +5,11 @@ warm-up forwards, steady one-forward-one-backward with combined send/recv pairs 
 deadlock), cool-down backwards; each micro-batch's loss is scaled by ``1/num_micro``; a one-time
 ``int64[3]`` shape handshake travels stage to stage; received activations become autograd leaves.
 Gradients accumulate into the optimizer's bucket buffers across micro-batches.
+
+Transfers overlap compute: activations and gradients use one communicator and one CUDA stream per direction
+(:class:`b200fw.dist.comm.PipeChannel`), receives land in persistent ring buffers and are posted one compute phase
+ahead (the gradient for this step's backward before its forward is queued, the next forward's activations before
+this backward), sends never hold the compute stream.
 """
 from __future__ import annotations
 
@@ -53,7 +58,7 @@ class PipelineScheduler:
             inp = None
             out = self.model.forward_hidden(ids_mb, B, S)
         else:
-            inp = recv.requires_grad_(True)
+            inp = recv.detach().requires_grad_(True)     # a fresh leaf over the (reused) receive buffer
             out = self.model.forward_hidden(inp, B, S)
         if self.pp.is_last_stage:
             loss = self.model.loss(None, labels_mb, loss_scale=1.0 / self.num_micro, hidden=out)
@@ -127,36 +132,55 @@ class PipelineScheduler:
             f += 1
             return out
 
-        recv = None
+        ch = self._channels(shape, dtype, dev)
+        act_in, act_out, grad_in, grad_out = ch
         for _ in range(warm):
-            recv = comm.recv_forward(shape, dtype, dev, prev, grp)
+            recv = act_in.wait(act_in.post_recv())
             out = fwd(recv)
-            comm.send_forward(out.detach(), nxt, grp)
-        if steady > 0:
-            recv = comm.recv_forward(shape, dtype, dev, prev, grp)
+            act_out.send(out.detach())
+        pending_act = act_in.post_recv() if steady > 0 else None
         for i in range(steady):
+            recv = act_in.wait(pending_act)
+            # the gradient this step's backward needs is posted before the forward is queued: it arrives under it
+            pending_grad = grad_in.post_recv()
             out = fwd(recv)
-            if pp.is_last_stage:
-                grad = None
-            else:
-                grad = comm.send_forward_recv_backward(out.detach(), shape, dtype, dev, nxt, grp)
+            if not pp.is_last_stage:
+                act_out.send(out.detach())
+            # ... and the next forward's activations are posted before the backward: they arrive under it
+            pending_act = act_in.post_recv() if i < steady - 1 else None
+            grad = grad_in.wait(pending_grad)
             inp, o = fifo.popleft()
             with self._track(f"B{i}", "backward"):
                 gin = self._backward(inp, o, grad)
-            last_steady = i == steady - 1
-            if last_steady:
-                comm.send_backward(gin, prev, grp) if gin is not None else None
-            else:
-                recv = comm.send_backward_recv_forward(gin, shape, dtype, dev, prev, grp) if gin is not None \
-                    else comm.recv_forward(shape, dtype, dev, prev, grp)
+            if gin is not None:
+                grad_out.send(gin)
         for _ in range(warm):
-            grad = comm.recv_backward(shape, dtype, dev, nxt, grp)
+            grad = grad_in.wait(grad_in.post_recv())
             inp, o = fifo.popleft()
             with self._track("Bc", "backward"):
                 gin = self._backward(inp, o, grad)
             if gin is not None:
-                comm.send_backward(gin, prev, grp)
+                grad_out.send(gin)
+        for c in ch:
+            c.flush()
         return total
+
+    def _channels(self, shape, dtype, dev):
+        """(activations in, activations out, gradients in, gradients out) of this stage, built once per activation
+        shape.  Activations and gradients use a communicator each (``ParallelContext.pp_fwd_group`` /
+        ``pp_bwd_group``; the plain pipeline group when the context has none)."""
+        key = (tuple(shape), dtype, str(dev))
+        if getattr(self, "_ch_key", None) != key:
+            pp = self.pp
+            gf = getattr(pp.ctx, "pp_fwd_group", None) or pp.group
+            gb = getattr(pp.ctx, "pp_bwd_group", None) or pp.group
+            depth = pp.pp_size + 2          # received activations stay alive until their backward, plus one in flight
+            self._ch = (comm.PipeChannel(gf, pp.prev_rank, shape, dtype, dev, depth),
+                        comm.PipeChannel(gf, pp.next_rank, shape, dtype, dev, 0),
+                        comm.PipeChannel(gb, pp.next_rank, shape, dtype, dev, 3),
+                        comm.PipeChannel(gb, pp.prev_rank, shape, dtype, dev, 0))
+            self._ch_key = key
+        return self._ch
 
     def broadcast_loss(self, loss: torch.Tensor) -> torch.Tensor:
         """Share the last stage's loss with every stage of this pipeline."""

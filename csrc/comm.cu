@@ -569,26 +569,39 @@ __global__ void zero_reduce_shard_mc_kernel(const __nv_bfloat16* __restrict__ mc
                                             float* __restrict__ norm_sq) {
   float ss = 0.f;
   const long long nvec = n / 8;
-  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const uint4 q = multimem_ld_reduce_bf16x8(mc_bucket + shard_start + i * 8);
-    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-    float4* o = reinterpret_cast<float4*>(out + i * 8);
-    float pv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    if (accumulate) {
-      const float4 p0 = o[0], p1 = o[1];
-      pv[0] = p0.x; pv[1] = p0.y; pv[2] = p0.z; pv[3] = p0.w; pv[4] = p1.x; pv[5] = p1.y; pv[6] = p1.z; pv[7] = p1.w;
-    }
-    float r[8];
+  const long long stride = static_cast<long long>(gridDim.x) * blockDim.x;
+  constexpr int U = 4;    // independent reductions in flight per thread: a multimem.ld_reduce is a round trip to the switch
+  for (long long i0 = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < nvec; i0 += stride * U) {
+    uint4 q[U];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const float2 f = unpack_bf16x2(w[j]);
-      r[2 * j] = f.x * scale + pv[2 * j];
-      r[2 * j + 1] = f.y * scale + pv[2 * j + 1];
-      ss += r[2 * j] * r[2 * j] + r[2 * j + 1] * r[2 * j + 1];
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      q[u] = make_uint4(0u, 0u, 0u, 0u);
+      if (i < nvec) q[u] = multimem_ld_reduce_bf16x8(mc_bucket + shard_start + i * 8);
     }
-    o[0] = make_float4(r[0], r[1], r[2], r[3]);
-    o[1] = make_float4(r[4], r[5], r[6], r[7]);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < nvec) {
+        const uint32_t w[4] = {q[u].x, q[u].y, q[u].z, q[u].w};
+        float4* o = reinterpret_cast<float4*>(out + i * 8);
+        float pv[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        if (accumulate) {
+          const float4 p0 = o[0], p1 = o[1];
+          pv[0] = p0.x; pv[1] = p0.y; pv[2] = p0.z; pv[3] = p0.w; pv[4] = p1.x; pv[5] = p1.y; pv[6] = p1.z; pv[7] = p1.w;
+        }
+        float r[8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = unpack_bf16x2(w[j]);
+          r[2 * j] = f.x * scale + pv[2 * j];
+          r[2 * j + 1] = f.y * scale + pv[2 * j + 1];
+          ss += r[2 * j] * r[2 * j] + r[2 * j + 1] * r[2 * j + 1];
+        }
+        o[0] = make_float4(r[0], r[1], r[2], r[3]);
+        o[1] = make_float4(r[4], r[5], r[6], r[7]);
+      }
+    }
   }
   ss = warp_sum(ss);
   if ((threadIdx.x & 31) == 0 && norm_sq) atomicAdd(norm_sq, ss);

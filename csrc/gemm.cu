@@ -56,16 +56,25 @@ struct GemmMnDesc {
 //           the rank that owns those rows (peer stores over NVLink), a per-tile counter on the owner
 //           is bumped with a system-scope release, and after its own tiles each CTA reduces finished
 //           row blocks of THIS rank's shard (sum over source ranks + residual).
-//   COMM 2  all-gather -> GEMM: four extra warps per CTA pull 128-row blocks of the peers' activation
-//           shards into a local gather buffer (plain peer loads, local stores) and publish a flag per
-//           block; the TMA producer waits for a block's flag before loading A tiles from the LOCAL
-//           gather buffer.  No TMA ever targets another GPU's memory and no clusters are used.
+//   COMM 2  all-gather -> GEMM: four extra warps per CTA PUSH this rank's activation shard, piece by piece
+//           (128 rows x 256 columns), into the gather buffer of every rank: one multimem.st through the
+//           switch where the buffers are bound to a multicast object, else one store per peer.  Stores need
+//           no round trip, so a few warps per SM keep NVLink full (loads from a peer are latency-bound).  A
+//           piece ends with a system-scope release add on every rank's counter of that row block; the TMA
+//           producer waits until the counter of the block it is about to load has all its pieces, then reads
+//           A tiles from the LOCAL gather buffer.  No TMA ever targets another GPU's memory, no clusters.
 struct GemmComm {
   void* peer_recv[8];       // COMM 1: [world][rows_per_rank][N] bf16 receive buffer on each rank
   int* peer_cnt[8];         // COMM 1: per (row block, n block) arrival counters on each rank
-  const void* peer_src[8];  // COMM 2: [rows_per_rank][K] bf16 activation shard on each rank
-  void* gather;             // COMM 2: local [M][K] bf16 gather buffer (the A operand)
-  int* gather_flags;        // COMM 2: local per-128-row-block flags
+  void* peer_gather[8];     // COMM 2: [M][K] bf16 gather buffer on each rank (the A operand there)
+  void* mc_gather;          // COMM 2: multicast address of the gather buffers (one store reaches every rank), or null
+  int* peer_flags[8];       // COMM 2: per-128-row-block arrival counters on each rank
+  int* peer_ready[8];       // COMM 2: [world] "rank p has entered call c" words on each rank
+  const void* local_src;    // COMM 2: this rank's [rows_per_rank][K] bf16 activation shard (ordinary local memory)
+  void* gather;             // COMM 2: this rank's gather buffer
+  int* gather_flags;        // COMM 2: this rank's arrival counters
+  int ready_epoch;          // COMM 2: number of this call among the context's fused all-gather calls
+  int pieces_per_block;     // COMM 2: column chunks a 128-row block is pushed in (arrivals per block and call)
   void* out;                // COMM 1: [rows_per_rank][N] bf16 result of the reduce
   const void* residual;     // COMM 1: optional [rows_per_rank][N] bf16 added in the reduce
   int world, rank, rows_per_rank, epoch;
@@ -109,10 +118,10 @@ __device__ __forceinline__ bool wait_flag_ge(const int* p, int value, int* statu
 
 // Sum ROWS rows per step over up to MAXW source ranks (all loads issued before the first add, so that
 // enough requests are in flight to be bound by HBM bandwidth), add the residual, store bf16.
-template <int ROWS, int MAXW>
+template <int ROWS, int MAXW, int WARPS>
 __device__ __forceinline__ void reduce_rows(const __nv_bfloat16* __restrict__ recv, const GemmComm& comm, int rb,
                                             int c, int N, int ewarp) {
-  for (int rr = ewarp * ROWS; rr < GEMM_BM; rr += 4 * ROWS) {
+  for (int rr = ewarp * ROWS; rr < GEMM_BM; rr += WARPS * ROWS) {
     uint4 q[ROWS][MAXW];
     uint4 rq[ROWS];
 #pragma unroll
@@ -163,7 +172,7 @@ __device__ __forceinline__ void reduce_rows(const __nv_bfloat16* __restrict__ re
 }
 
 template <int BN, bool A_MN, bool B_MN, int COMM>
-__global__ void __launch_bounds__(COMM == 2 ? GEMM_THREADS + 128 : GEMM_THREADS, 1)
+__global__ void __launch_bounds__(GEMM_THREADS + (COMM == 2 ? 128 : COMM == 1 ? 64 : 0), 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmR,
                  void* __restrict__ Cout, const __nv_bfloat16* __restrict__ R, int M, int N, int K,
@@ -236,9 +245,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int j = m_blk / comm.world, s_ = m_blk % comm.world;
       m_blk = ((s_ + comm.rank + 1) % comm.world) * bpr + j;
     } else if (COMM == 2) {
-      // own rows first (already local), then in ring order
+      // every rank pushes its row block j at about the same time: consume block j of all sources (own first),
+      // then block j + 1
       const int bpr = comm.rows_per_rank / GEMM_BM;
-      m_blk = (m_blk + comm.rank * bpr) % num_m;
+      const int j = m_blk / comm.world, s_ = m_blk % comm.world;
+      m_blk = ((s_ + comm.rank) % comm.world) * bpr + j;
     }
   };
 
@@ -253,7 +264,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tile_coords(t, m_blk, n_blk);
         const int m0 = m_blk * GEMM_BM, n0 = n_blk * BN;
         if (COMM == 2) {   // the A rows of this tile must have arrived in the local gather buffer
-          if (!wait_flag_ge<false>(comm.gather_flags + m_blk, comm.epoch, status, ERR_COMM_FLAG_WAIT)) {
+          if (!wait_flag_ge<true>(comm.gather_flags + m_blk, comm.epoch * comm.pieces_per_block, status,
+                                  ERR_COMM_FLAG_WAIT)) {
             ok = false;
             break;
           }
@@ -331,34 +343,85 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (acc == 0) acc_phase ^= 1;
       }
     }
+  } else if (COMM == 1 && warp >= 6) {
+    // ---- reduce warps: sum this rank's row blocks over all source ranks as they complete --------------------
+    // A job is (row block rb of this rank's shard, column block nb), dealt to the CTAs in the order the row blocks
+    // complete (see tile_coords).  These two warps only wait and move memory (two, not four: 256 threads per CTA
+    // keep the full register budget for the epilogue), so the reduction of block j runs under the MMAs and
+    // epilogues of the blocks after it instead of behind the last tile.
+    const int ct = threadIdx.x - 192;                 // 0..63
+    const int rwarp = ct >> 5;
+    const int rjobs = (comm.rows_per_rank / GEMM_BM) * num_n;
+    const __nv_bfloat16* recv = static_cast<const __nv_bfloat16*>(comm.peer_recv[comm.rank]);
+    const int* cnt = comm.peer_cnt[comm.rank];
+    bool ok = true;
+    for (int job = blockIdx.x; job < rjobs; job += gridDim.x) {
+      if (ct == 0 && ok) ok = wait_flag_ge<true>(cnt + job, comm.world * comm.epoch, status, ERR_COMM_FLAG_WAIT);
+      if (named_barrier_or(2, 64, !ok)) break;
+      const int rb = job / num_n, nb = job % num_n;
+      const int c = nb * BN + lane * 8;               // 32 lanes x 8 columns = one 256-column row segment
+      if (c >= N || (BN == 128 && lane >= 16)) continue;
+      if (comm.world <= 4)
+        reduce_rows<4, 4, 2>(recv, comm, rb, c, N, rwarp);
+      else
+        reduce_rows<2, 8, 2>(recv, comm, rb, c, N, rwarp);
+    }
   } else if (COMM == 2 && warp >= 6) {
-    // ---- gather warps: pull peers' shards into the local gather buffer, block by block -------------
+    // ---- push warps: this rank's shard -> every rank's gather buffer, piece by piece ---------------------
     const int ct = threadIdx.x - 192;                 // 0..127
     const int bpr = comm.rows_per_rank / GEMM_BM;
-    const int vec_per_row = K / 8;
-    const int total_vec = GEMM_BM * vec_per_row;
-    for (int i = blockIdx.x; i < num_m; i += gridDim.x) {
-      const int rb = (comm.rank * bpr + i) % num_m;   // own blocks first, then ring order
-      const int src = rb / bpr;
-      const uint4* from = reinterpret_cast<const uint4*>(
-          static_cast<const __nv_bfloat16*>(comm.peer_src[src]) + static_cast<size_t>(rb % bpr) * GEMM_BM * K);
-      uint4* to = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(comm.gather) +
-                                           static_cast<size_t>(rb) * GEMM_BM * K);
-      // sixteen independent 16-byte peer loads in flight per thread: the copy is bound by NVLink
-      // bandwidth, not by one round trip per load
-      for (int v = ct; v < total_vec; v += 128 * 16) {
-        uint4 t[16];
+    // Arrival: a peer that has entered this call has (in its stream order) finished every earlier kernel that
+    // read the gather buffer this call overwrites.
+    if (blockIdx.x == 0 && ct < comm.world) {
+      __threadfence_system();
+      asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(comm.peer_ready[ct] + comm.rank), "r"(comm.ready_epoch) : "memory");
+    }
+    bool ok = true;
+    if (ct < comm.world)
+      ok = wait_flag_ge<true>(comm.peer_ready[comm.rank] + ct, comm.ready_epoch, status, ERR_COMM_FLAG_WAIT);
+    if (!named_barrier_or(2, 128, !ok)) {
+      constexpr int CW = 256;                          // columns per piece
+      const bool use_mc = comm.mc_gather != nullptr;
+      const int chunks = comm.pieces_per_block;
+      const int pieces = bpr * chunks;
+      const __nv_bfloat16* src0 = static_cast<const __nv_bfloat16*>(comm.local_src);
+      for (int p = blockIdx.x; p < pieces; p += gridDim.x) {
+        const int b = p / chunks, c0 = (p % chunks) * CW;
+        const int cw = min(CW, K - c0);
+        const int vpr = cw >> 3;                       // 16-byte vectors per row of the piece
+        const int total = GEMM_BM * vpr;
+        const __nv_bfloat16* src = src0 + static_cast<size_t>(b) * GEMM_BM * K + c0;
+        const size_t dst_off = (static_cast<size_t>(comm.rank) * bpr + b) * GEMM_BM * K + c0;
+        for (int v = ct; v < total; v += 128 * 8) {
+          uint4 t[8];
 #pragma unroll
-        for (int u = 0; u < 16; ++u)
-          if (v + u * 128 < total_vec) t[u] = __ldcg(from + v + u * 128);
+          for (int u = 0; u < 8; ++u) {
+            const int vv = v + u * 128;
+            t[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (vv < total) t[u] = *reinterpret_cast<const uint4*>(src + static_cast<size_t>(vv / vpr) * K + (vv % vpr) * 8);
+          }
 #pragma unroll
-        for (int u = 0; u < 16; ++u)
-          if (v + u * 128 < total_vec) to[v + u * 128] = t[u];
+          for (int u = 0; u < 8; ++u) {
+            const int vv = v + u * 128;
+            if (vv < total) {
+              const size_t off = dst_off + static_cast<size_t>(vv / vpr) * K + (vv % vpr) * 8;
+              if (use_mc) {
+                asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};" ::"l"(
+                                 static_cast<__nv_bfloat16*>(comm.mc_gather) + off),
+                             "r"(t[u].x), "r"(t[u].y), "r"(t[u].z), "r"(t[u].w) : "memory");
+              } else {
+#pragma unroll
+                for (int r = 0; r < 8; ++r)
+                  if (r < comm.world)
+                    *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(comm.peer_gather[r]) + off) = t[u];
+              }
+            }
+          }
+        }
+        __threadfence_system();                        // this thread's stores are ordered before the arrival below
+        named_barrier(2, 128);
+        if (ct < comm.world) red_release_sys_add(comm.peer_flags[ct] + comm.rank * bpr + b, 1);
       }
-      asm volatile("fence.proxy.async;" ::: "memory");   // generic-proxy writes -> visible to TMA reads
-      __threadfence();
-      named_barrier(2, 128);
-      if (ct == 0) st_release_gpu_s32(comm.gather_flags + rb, comm.epoch);
     }
   } else {
     const int quarter = warp & 3;  // TMEM lane quarter this warp may read
@@ -368,21 +431,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const bool residual = flags & GEMM_RESIDUAL;
     uint32_t slab_count = 0;
     const bool atomic_out = split_k > 1;   // several units add into the same fp32 tile
-    // COMM 1: reduce jobs (row block rb of this rank's shard x column block nb) are dealt to the CTAs in the order
-    // the row blocks complete; a CTA looks at its next job after every tile and runs it when its counter is full.
-    int rjob = blockIdx.x;
-    const int rjobs = COMM == 1 ? (comm.rows_per_rank / GEMM_BM) * num_n : 0;
-    auto run_reduce_job = [&](int job) {
-      const int rb = job / num_n, nb = job % num_n;
-      const int c = nb * BN + lane * 8;            // 32 lanes x 8 columns = one 256-column row segment
-      if (c >= N || (BN == 128 && lane >= 16)) return;
-      const __nv_bfloat16* recv = static_cast<const __nv_bfloat16*>(comm.peer_recv[comm.rank]);
-      const int ewarp = (threadIdx.x - 64) >> 5;
-      if (comm.world <= 4)
-        reduce_rows<4, 4>(recv, comm, rb, c, N, ewarp);
-      else
-        reduce_rows<2, 8>(recv, comm, rb, c, N, ewarp);
-    };
     for (int u = blockIdx.x; u < num_units; u += gridDim.x) {
       const int t = u % num_tiles;
       int m_blk, n_blk;
@@ -457,17 +505,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1;
-        if (rjob < rjobs) {
-          // one look (no spin) at the next reduce job: all sources' tiles landed -> reduce it now, under the MMAs
-          // of the tiles that follow
-          bool ready = false;
-          if (threadIdx.x == 64)
-            ready = ld_acquire_sys_s32(comm.peer_cnt[comm.rank] + rjob) >= comm.world * comm.epoch;
-          if (named_barrier_or(1, 128, ready)) {
-            run_reduce_job(rjob);
-            rjob += gridDim.x;
-          }
-        }
         continue;
       }
       if (!out_fp32) {
@@ -637,17 +674,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (acc == 0) acc_phase ^= 1;
     }
     if (warp == 2 && lane == 0) tma_store_wait_all<0>();   // shared memory stays valid until stores have read it
-    if (COMM == 1) {
-      // ---- the reduce jobs still open after the last tile: wait (bounded) for each and run it -----------
-      const int et = threadIdx.x - 64;               // 0..127
-      const int* cnt = comm.peer_cnt[comm.rank];
-      bool ok = true;
-      for (; rjob < rjobs; rjob += gridDim.x) {
-        if (et == 0 && ok) ok = wait_flag_ge<true>(cnt + rjob, comm.world * comm.epoch, status, ERR_COMM_FLAG_WAIT);
-        if (named_barrier_or(1, 128, !ok)) break;
-        run_reduce_job(rjob);
-      }
-    }
   }
 
   // Common tail: every thread arrives here, also after a wait that ran out.
@@ -729,7 +755,7 @@ static int launch_gemm(const void* A, const void* B, void* C, const void* R, int
     }
   }
   if (num_tiles * split_k < grid) grid = num_tiles * split_k;
-  kern<<<grid, COMM == 2 ? GEMM_THREADS + 128 : GEMM_THREADS, Cfg::SMEM_BYTES, stream>>>(
+  kern<<<grid, GEMM_THREADS + (COMM == 2 ? 128 : COMM == 1 ? 64 : 0), Cfg::SMEM_BYTES, stream>>>(
       *ta, *tb, *tc, *tr, C, reinterpret_cast<const __nv_bfloat16*>(R), M, N, K, ldc, flags, g_mn_desc, comm, status,
       split_k);
   cudaError_t e = cudaGetLastError();
@@ -797,16 +823,19 @@ B2_EXPORT void b2_gemm_set_mn_desc(unsigned lbo, unsigned sbo, unsigned kstep) {
 // Tensor-parallel GEMMs with the collective inside the kernel.  mode 1: GEMM -> reduce-scatter,
 // mode 2: all-gather -> GEMM.  b_mn as in b2_gemm_bf16; A is K-major.  M = world * rows_per_rank rows in
 // total, rows_per_rank a multiple of 128.  Pointer arrays have `world` entries (peer pointers of the
-// symmetric buffers).  epoch: the 1-based call count of this (buffer, counter) set; counters and flags
+// symmetric buffers).  epoch: the 1-based use count of this (buffer, counter) set; counters and flags
 // only ever grow, nothing is reset between calls.
 //   mode 1: A [M,K] local, out [rows_per_rank, N]; recv[r]: [world, rows_per_rank, N] on rank r; cnt[r]:
 //           int32 [(rows_per_rank/128) * ceil(N/bn)] on rank r.
-//   mode 2: src[r]: rank r's [rows_per_rank, K] shard; gather: local [M, K]; gather_flags: local
-//           int32 [M/128]; C [M, N] local output.
+//   mode 2: A: this rank's [rows_per_rank, K] shard (ordinary memory); gathers[r]: rank r's [M, K] gather buffer
+//           (mc_gather: their multicast address or null); flags[r]: int32 [M/128] arrival counters on rank r;
+//           ready[r]: int32 [world] on rank r; ready_epoch: 1-based count of mode-2 calls on this context;
+//           C [M, N] local output.  The gathered activations are left in gathers[rank].
 B2_EXPORT int b2_gemm_bf16_comm(int mode, const void* A, const void* B, void* C, int M, int N, int K, int ldb,
                                 int b_mn, int bn, void* const* recv, void* const* cnt, void* out,
-                                const void* residual, void* const* src, void* gather, void* gather_flags,
-                                int world, int rank, int rows_per_rank, int epoch, void* stream_) {
+                                const void* residual, void* const* gathers, void* mc_gather, void* const* flags,
+                                void* const* ready, int ready_epoch, int world, int rank, int rows_per_rank,
+                                int epoch, void* stream_) {
   using namespace b2;
   b2::ensure_thread_context();
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
@@ -826,18 +855,26 @@ B2_EXPORT int b2_gemm_bf16_comm(int mode, const void* A, const void* B, void* C,
       comm.peer_recv[r] = recv[r];
       comm.peer_cnt[r] = static_cast<int*>(cnt[r]);
     } else {
-      comm.peer_src[r] = src[r];
+      comm.peer_gather[r] = gathers[r];
+      comm.peer_flags[r] = static_cast<int*>(flags[r]);
+      comm.peer_ready[r] = static_cast<int*>(ready[r]);
     }
   }
-  comm.gather = gather;
-  comm.gather_flags = static_cast<int*>(gather_flags);
+  if (mode == 2) {
+    comm.gather = gathers[rank];
+    comm.gather_flags = static_cast<int*>(flags[rank]);
+    comm.mc_gather = mc_gather;
+    comm.local_src = A;
+    comm.ready_epoch = ready_epoch;
+    comm.pieces_per_block = (K + 255) / 256;
+  }
   comm.out = out;
   comm.residual = residual;
   comm.world = world;
   comm.rank = rank;
   comm.rows_per_rank = rows_per_rank;
   comm.epoch = epoch;
-  const void* Aop = mode == 2 ? gather : A;
+  const void* Aop = mode == 2 ? comm.gather : A;
 #define B2_COMM_CASE(BN_, BMN_, MODE_)                                                                   \
   if (bn == BN_ && b_mn == BMN_ && mode == MODE_)                                                        \
     return launch_gemm<BN_, false, BMN_ != 0, MODE_>(Aop, B, C, nullptr, M, N, K, K, ldb, N, 0, 0, stream, &comm);

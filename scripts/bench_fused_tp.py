@@ -20,6 +20,7 @@ import torch  # noqa: E402
 import torch.distributed as dist  # noqa: E402
 
 from b200fw import _native as nv  # noqa: E402
+from b200fw.obs.clocks import ClockSampler  # noqa: E402
 from b200fw.obs.profilers import CommProfiler, measured_peaks  # noqa: E402
 from b200fw.ops import fused_tp, gemm  # noqa: E402
 
@@ -58,6 +59,9 @@ def main():
     rows = M // world
     torch.manual_seed(rank)
     out = []
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
     cases = [("F1 all-gather->GEMM qkv", "ag", 1280, 5120), ("F2 all-gather->GEMM gate|up", "ag", 6400, 5120),
              ("F3 GEMM->reduce-scatter o_proj", "rs", 5120, 1024), ("F4 GEMM->reduce-scatter down_proj", "rs", 5120, 3200)]
     for name, kind, N, K in cases:
@@ -66,7 +70,7 @@ def main():
         if kind == "ag":
             xs = torch.randn(rows, K, device=dev, dtype=torch.bfloat16)
             full = torch.empty(M, K, device=dev, dtype=torch.bfloat16)
-            fused = lambda: fused_tp.allgather_gemm(xs, w, g)
+            fused = lambda: fused_tp.allgather_gemm(xs, w, g, slot="bench")
             def unfused():
                 dist.all_gather_into_tensor(full, xs)
                 return gemm(full, w)
@@ -81,15 +85,27 @@ def main():
                 dist.reduce_scatter_tensor(o, y)
                 return o + res
             wire = (world - 1) / world * M * N * 2
+        # numerics on every rank before timing: the fused kernel against NCCL + the same GEMM
+        yf = fused()
+        yf = (yf[0] if isinstance(yf, tuple) else yf).float()
+        yu = unfused().float()
+        err = ((yf - yu).abs().max() / yu.abs().max().clamp_min(1e-6)).reshape(1)
+        dist.all_reduce(err, op=dist.ReduceOp.MAX)
+        rel_err = float(err)
+        assert rel_err < 2e-2, f"{name}: fused result differs from NCCL + GEMM on some rank (max relative error {rel_err})"
         t_f = timed(fused, a.iters, a.warmup, world, dev)
         t_u = timed(unfused, a.iters, a.warmup, world, dev)
         roof = CommProfiler.fused_roofline(flops, wire, t_f, peaks["bf16_tflops_sustained"])
+        t_wire_900 = wire / 900e9 * 1e3
         out.append({"path": name, "M": M, "N": N, "K": K, "world": world, "fused_ms": t_f, "nccl_plus_gemm_ms": t_u,
                     "speedup_vs_unfused": t_u / t_f, "t_compute_ms": roof["t_compute_ms"], "t_wire_ms": roof["t_wire_ms"],
-                    "bound": roof["bound"], "roofline_fraction_of_measured": roof["fraction"]})
+                    "bound": roof["bound"], "roofline_fraction_of_measured": roof["fraction"],
+                    "roofline_fraction_at_900GBs_wire": max(roof["t_compute_ms"], t_wire_900) / t_f,
+                    "max_rel_err_vs_unfused_all_ranks": rel_err})
     status = nv.read_status()
+    clocks = sampler.stop() if rank == 0 else None
     if rank == 0:
-        print(json.dumps({"fused_tp": out, "device_status": status, "peaks": peaks["source"]}, indent=1))
+        print(json.dumps({"fused_tp": out, "device_status": status, "peaks": peaks["source"], "clocks": clocks}, indent=1))
     dist.destroy_process_group()
 
 

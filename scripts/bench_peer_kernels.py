@@ -75,6 +75,10 @@ def main():
     v = torch.zeros(shard, device="cuda")
     hyper = torch.tensor([1e-5, 0.9, 0.999, 1e-8, 0.01, 0.1, 0.001, 1.0], device="cuda")
     res = []
+    from b200fw.obs.clocks import ClockSampler
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
 
     def reduce():
         nv.check(L.b2_zero_reduce_shard(grads.ptr_array, world, ctypes.c_longlong(rank * shard), ctypes.c_longlong(shard),
@@ -93,6 +97,20 @@ def main():
                                          nv.ptr(hyper), nv.ptr(norm), params.ptr_array, world,
                                          ctypes.c_longlong(rank * shard), nv.stream_ptr()), "zero_adamw_publish")
 
+    if grads.mc_ptr:
+        def reduce_mc():
+            nv.check(L.b2_zero_reduce_shard_mc(ctypes.c_void_p(grads.mc_ptr), ctypes.c_longlong(rank * shard),
+                                               ctypes.c_longlong(shard), ctypes.c_float(1.0 / world), nv.ptr(out), 0,
+                                               nv.ptr(norm), nv.stream_ptr()), "zero_reduce_shard_mc")
+        t = timed(reduce_mc, barrier, a.iters, a.warmup)
+        res.append({"kernel": "zero_reduce_shard (multimem.ld_reduce through the switch)", "ms": t, "wire_mb": wire / 1e6,
+                    "roofline_ms": roof, "roofline_fraction": roof / t, "served_gbs": wire / t / 1e6})
+    # the library form of the same step: NCCL reduce-scatter of the bf16 bucket
+    rs_out = torch.empty(shard, device="cuda", dtype=torch.bfloat16)
+    t = timed(lambda: dist.reduce_scatter_tensor(rs_out, grads.tensor), barrier, a.iters, a.warmup)
+    res.append({"kernel": "NCCL reduce_scatter (bf16, same bucket)", "ms": t, "wire_mb": wire / 1e6, "roofline_ms": roof,
+                "roofline_fraction": roof / t})
+
     norm.fill_(1.0)
     t = timed(publish, barrier, a.iters, a.warmup)
     wire = shard * 2 * (world - 1)                              # bf16 result pushed to every peer
@@ -100,6 +118,21 @@ def main():
     roof = max(wire / (LINK_GBS * 1e9), local_bytes / (hbm * 1e9)) * 1e3
     res.append({"kernel": "zero_adamw_publish", "ms": t, "wire_mb": wire / 1e6, "hbm_mb": local_bytes / 1e6,
                 "roofline_ms": roof, "roofline_fraction": roof / t})
+
+    if params.mc_ptr:
+        ok = torch.ones(1, dtype=torch.int32, device="cuda")
+
+        def publish_mc():
+            nv.check(L.b2_zero_adamw_publish2(nv.ptr(master), nv.ptr(m), nv.ptr(v), nv.ptr(out), ctypes.c_longlong(shard),
+                                              nv.ptr(hyper), nv.ptr(norm), params.ptr_array, ctypes.c_void_p(params.mc_ptr),
+                                              world, ctypes.c_longlong(rank * shard), nv.ptr(ok), nv.stream_ptr()),
+                     "zero_adamw_publish2")
+        t = timed(publish_mc, barrier, a.iters, a.warmup)
+        res.append({"kernel": "zero_adamw_publish (multimem.st through the switch)", "ms": t, "wire_mb": wire / 1e6,
+                    "hbm_mb": local_bytes / 1e6, "roofline_ms": roof, "roofline_fraction": roof / t})
+    t = timed(lambda: dist.all_gather_into_tensor(params.tensor, params.tensor[rank * shard:(rank + 1) * shard]), barrier,
+              a.iters, a.warmup)
+    res.append({"kernel": "NCCL all_gather (bf16, same bucket; AdamW not included)", "ms": t, "wire_mb": wire / 1e6})
 
     # weight sync: rank 0's fp32 master shard -> bf16 staging buffer on the next rank (cast + checksum)
     src = torch.randn(n // 2, device="cuda")
@@ -118,8 +151,10 @@ def main():
                 "roofline_fraction": roof / t, "push_gbs": wire / t / 1e6})
     torch.cuda.synchronize()
     status = nv.read_status()
+    clocks = sampler.stop() if rank == 0 else None
     if rank == 0:
-        print(json.dumps({"world": world, "params": n, "results": res, "device_status": status,
+        print(json.dumps({"world": world, "params": n, "results": res, "device_status": status, "clocks": clocks,
+                          "nvls_multicast": bool(grads.mc_ptr),
                           "link_gbs_measured": LINK_GBS, "hbm_gbs": hbm}, indent=1))
     dist.destroy_process_group()
 

@@ -292,7 +292,9 @@ def _fused_tp_ops_worker(rank, world):
             # ---- all-gather -> GEMM: rows are sharded, N is local
             xs = x_full[rank * rows:(rank + 1) * rows, :K].contiguous()
             wn = w_full[:, :K].contiguous()
-            y, xg = fused_tp.allgather_gemm(xs, wn.t().contiguous() if b_mn else wn, g, b_mn=b_mn)
+            # odd repetitions use a call-site slot: the gathered activations are then the buffer itself (no copy)
+            y, xg = fused_tp.allgather_gemm(xs, wn.t().contiguous() if b_mn else wn, g, b_mn=b_mn,
+                                            slot="test" if rep % 2 else None)
             want_y = x_full[:, :K].float() @ wn.float().t()
             e2 = ((y.float() - want_y).abs().max() / want_y.abs().max()).item()
             e3 = float((xg != x_full[:, :K]).sum())
@@ -301,9 +303,13 @@ def _fused_tp_ops_worker(rank, world):
 
 
 @needs2
-def test_fused_tp_gemm_kernels_match_reference():
+@pytest.mark.parametrize("nvls", ["1", "0"])
+def test_fused_tp_gemm_kernels_match_reference(nvls):
+    """GEMM -> reduce-scatter and all-gather -> GEMM against fp32 matmuls of the full tensors, on every visible GPU
+    (2, 4 or 8); the all-gather pushes through the switch's multicast address (nvls "1", where the platform has it)
+    or with one store per peer (nvls "0")."""
     from _gpu_dist_util import run_gpu_ranks
-    for res in run_gpu_ranks(_fused_tp_ops_worker, _world() if _world() in (2, 4, 8) else 2):
+    for res in run_gpu_ranks(_fused_tp_ops_worker, _world() if _world() in (2, 4, 8) else 2, env={"B200FW_NVLS": nvls}):
         for e1, e2, e3 in res:
             assert e1 < 2e-2 and e2 < 2e-2 and e3 == 0.0, (e1, e2, e3)
 
