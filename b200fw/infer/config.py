@@ -51,6 +51,10 @@ class InferenceConfig:
     # a weight update does not abort running requests: they go on under the new weights and keep the K/V their
     # earlier tokens produced under the old ones, for at most this many versions (0 = abort on every update)
     max_weight_staleness: int = 1
+    # decode-only steps leave the sampled ids on the device: the next step's forward is launched from them before the
+    # host has read them (one step late), so host-side scheduling overlaps the GPU's work.  The cost is one discarded
+    # token after an EOS.  Turned off with speculative decoding (which needs the values every round).
+    async_decode: bool = True
 
     @classmethod
     def from_model_config(cls, mc, **kw) -> "InferenceConfig":

@@ -49,6 +49,9 @@ class InferenceEngine:
         self.finished: Dict[str, Request] = {}
         self.initialized = False
         self.weights_version = 0
+        self._inflight: Optional[dict] = None       # the decode launch whose sampled ids are still on the device
+        self._stage_rings: dict = {}
+        self._samp_cache = None
         self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "cached_prefix_tokens": 0,
                       "oom_recoveries": 0, "request_errors": 0, "graph_replays": 0, "spec_rounds": 0}
         self._rng = random.Random(config.seed)
@@ -167,24 +170,60 @@ class InferenceEngine:
         for r in out.preempted_requests:
             self._release(r, cache_prefix=False)
         produced: Dict[str, List[int]] = {}
+        if out.preempted_requests or out.is_empty:
+            self._resolve_inflight(produced)        # a preempted request's progress is reset: settle its tokens first
         if out.is_empty:
+            self._finish_done(produced)
             return produced
         try:
             decode = [r for r in out.decode_requests if r.request_id not in out.prefill_tokens]
             if out.prefill_requests:
+                self._resolve_inflight(produced)    # steps with prefill chunks run synchronously
                 with nvtx.range("infer/prefill"):
                     self._execute_prefill(out, produced)
             if decode:
                 with nvtx.range("infer/decode"):
-                    self._execute_decode(decode, produced)
+                    self._execute_decode(decode, produced, lookahead=not out.prefill_requests)
         except torch.cuda.OutOfMemoryError:
+            self._inflight = None
             self._recover_from_oom()
             return produced
+        self._finish_done(produced)
+        return produced
+
+    def _finish_done(self, produced: Dict[str, List[int]]):
+        """Retire requests that are complete.  A request whose last token is still on the device (sampled by the
+        launch in flight) is complete by count: its values are read now, so that nothing unresolved leaves the engine."""
+        inf = self._inflight
+        if inf is not None and any(r.is_finished for r in inf["reqs"]):
+            self._resolve_inflight(produced)
         for rid in list(produced):
             r = self.requests.get(rid)
             if r is not None and r.is_finished:
                 self._finish(r)
-        return produced
+
+    # ---- sampled ids that are still on the device ------------------------------------------------------------------
+    PLACEHOLDER = -1
+
+    def _resolve_inflight(self, produced: Optional[Dict[str, List[int]]] = None):
+        """Read the ids (and log-probs) of the decode launch in flight into the requests' output lists (this waits
+        for that launch).  An EOS found here ends its request: whatever the following launch sampled for it is
+        dropped."""
+        inf, self._inflight = self._inflight, None
+        if inf is None:
+            return
+        inf["event"].synchronize()
+        ids, lps = inf["host_ids"][:len(inf["reqs"])].tolist(), inf["host_lps"][:len(inf["reqs"])].tolist()
+        for r, slot, t, lp in zip(inf["reqs"], inf["slots"], ids, lps):
+            if slot >= len(r.output_tokens) or r.output_tokens[slot] != self.PLACEHOLDER:
+                continue                            # the request ended (EOS) or was reset since this launch
+            r.output_tokens[slot] = t
+            r.output_logprobs[slot] = lp
+            if produced is not None:
+                produced.setdefault(r.request_id, []).append(t)
+            if r.eos_token_id is not None and t == r.eos_token_id:
+                del r.output_tokens[slot + 1:]
+                del r.output_logprobs[slot + 1:]
 
     # ---- prefill --------------------------------------------------------------------------------------------
     def _first_block_key(self, r: Request):
@@ -291,7 +330,7 @@ class InferenceEngine:
         dm.forward(torch.tensor(r.prompt_tokens, dtype=torch.long, device=self.device), ctx)
 
     # ---- decode ---------------------------------------------------------------------------------------------
-    def _execute_decode(self, reqs: List[Request], produced: Dict[str, List[int]]):
+    def _execute_decode(self, reqs: List[Request], produced: Dict[str, List[int]], lookahead: bool = False):
         cfg = self.config
         if cfg.inference_mode == "mock":
             for r in reqs:
@@ -300,7 +339,10 @@ class InferenceEngine:
             self.stats["decode_tokens"] += len(reqs)
             return
         if self.spec is not None and self._use_speculation(reqs):
+            self._resolve_inflight(produced)
             return self._execute_speculative(reqs, produced)
+        # a request that ended on an EOS found since scheduling needs no further token
+        reqs = [r for r in reqs if not (r.output_tokens and r.output_tokens[-1] != self.PLACEHOLDER and r.is_finished)]
         live = []
         for r in reqs:
             try:
@@ -312,18 +354,78 @@ class InferenceEngine:
                         raise RuntimeError("KV cache exhausted during decode")
                 live.append(r)
             except Exception as e:  # noqa: BLE001
+                self._resolve_inflight(produced)
                 self._fail(r, e)
         if not live:
             return
-        last = torch.tensor([r.output_tokens[-1] for r in live], dtype=torch.long)
-        last = last.pin_memory().to(self.device, non_blocking=True) if self.device.type == "cuda" else last
+        use_async = (lookahead and cfg.async_decode and self.device.type == "cuda" and self.spec is None)
+        inf = self._inflight
+        last = None
+        if inf is not None:
+            rows = inf["rows"]
+            if use_async and all(r.request_id in rows for r in live):
+                # the ids sampled by the launch in flight feed this launch straight from the device
+                idx = [rows[r.request_id] for r in live]
+                if idx == list(range(len(inf["reqs"]))):
+                    last = inf["ids_dev"]
+                else:
+                    sel = self._stage("sel", torch.tensor(idx, dtype=torch.long))
+                    last = inf["ids_dev"].index_select(0, sel)
+            else:
+                self._resolve_inflight(produced)
+                live = [r for r in live if not r.is_finished] or live[:0]
+                if not live:
+                    return
+        if last is None:
+            last = self._stage("last", torch.tensor([r.output_tokens[-1] for r in live], dtype=torch.long))
         logits = self._decode_forward(live, last)
-        new, lps = self._sample(live, logits[:len(live)])
-        for r, t, lp in zip(live, new, lps):
-            r.output_tokens.append(t)
-            r.output_logprobs.append(lp)
-            produced.setdefault(r.request_id, []).append(t)
         self.stats["decode_tokens"] += len(live)
+        if not use_async:
+            new, lps = self._sample(live, logits[:len(live)])
+            for r, t, lp in zip(live, new, lps):
+                r.output_tokens.append(t)
+                r.output_logprobs.append(lp)
+                produced.setdefault(r.request_id, []).append(t)
+            return
+        ids_dev, lps_dev = self._sample_device(live, logits[:len(live)])
+        n = len(live)
+        host_ids, host_lps = self._pinned_out(n)
+        host_ids[:n].copy_(ids_dev, non_blocking=True)
+        host_lps[:n].copy_(lps_dev, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        slots = []
+        for r in live:
+            slots.append(len(r.output_tokens))
+            r.output_tokens.append(self.PLACEHOLDER)
+            r.output_logprobs.append(0.0)
+        # settle the previous launch now: the GPU finished it before it could start the one just queued, and the host
+        # work of this step ran while it was executing
+        self._resolve_inflight(produced)
+        self._inflight = {"reqs": live, "rows": {r.request_id: i for i, r in enumerate(live)}, "slots": slots,
+                          "ids_dev": ids_dev, "host_ids": host_ids, "host_lps": host_lps, "event": ev}
+
+    def _stage(self, name: str, t: torch.Tensor) -> torch.Tensor:
+        """Host tensor -> device through a small ring of pinned staging buffers (no page-locking per call; a ring
+        because the copy of the previous step may not have run yet when this step's values are written)."""
+        if self.device.type != "cuda":
+            return t
+        ring = self._stage_rings.setdefault((name, t.dtype), {"bufs": [None] * 4, "i": 0})
+        i = ring["i"] = (ring["i"] + 1) % 4
+        buf = ring["bufs"][i]
+        if buf is None or buf.numel() < t.numel():
+            buf = ring["bufs"][i] = torch.empty(max(256, t.numel()), dtype=t.dtype, pin_memory=True)
+        view = buf[:t.numel()].view(t.shape)
+        view.copy_(t)
+        return view.to(self.device, non_blocking=True)
+
+    def _pinned_out(self, n: int):
+        ring = self._stage_rings.setdefault("out", {"bufs": [None] * 4, "i": 0})
+        i = ring["i"] = (ring["i"] + 1) % 4
+        if ring["bufs"][i] is None or ring["bufs"][i][0].numel() < n:
+            ring["bufs"][i] = (torch.empty(max(256, n), dtype=torch.long, pin_memory=True),
+                               torch.empty(max(256, n), dtype=torch.float32, pin_memory=True))
+        return ring["bufs"][i]
 
     def _decode_forward(self, live: List[Request], last: torch.Tensor) -> torch.Tensor:
         ids = [r.request_id for r in live]
@@ -398,10 +500,21 @@ class InferenceEngine:
             self.stats["decode_tokens"] += len(toks)
 
     # ---- sampling / mock ----------------------------------------------------------------------------------------
+    def _sampling_params(self, reqs: List[Request]):
+        """Per-row temperature / top-p on the device, rebuilt only when the batch changes."""
+        key = tuple((r.request_id, r.temperature, r.top_p) for r in reqs)
+        if self._samp_cache is None or self._samp_cache[0] != key:
+            both = self._stage("samp", torch.tensor([[r.temperature for r in reqs], [r.top_p for r in reqs]],
+                                                    dtype=torch.float32))
+            self._samp_cache = (key, both[0].contiguous(), both[1].contiguous())
+        return self._samp_cache[1], self._samp_cache[2]
+
+    def _sample_device(self, reqs: List[Request], logits: torch.Tensor):
+        temp, topp = self._sampling_params(reqs)
+        return self.runner.sample(logits.contiguous(), temp, topp, self._gen, return_logprob=True)
+
     def _sample(self, reqs: List[Request], logits: torch.Tensor):
-        temp = torch.tensor([r.temperature for r in reqs], dtype=torch.float32, device=self.device)
-        topp = torch.tensor([r.top_p for r in reqs], dtype=torch.float32, device=self.device)
-        ids, lps = self.runner.sample(logits.contiguous(), temp, topp, self._gen, return_logprob=True)
+        ids, lps = self._sample_device(reqs, logits)
         return ids.tolist(), lps.tolist()
 
     def _mock_token(self, r: Request) -> int:
@@ -529,6 +642,7 @@ class InferenceEngine:
         A request is dropped only when it started more than ``config.max_weight_staleness`` versions ago (or when
         ``abort_running`` says so).  The prefix cache is emptied either way: no new request may share blocks
         computed under old weights."""
+        self._resolve_inflight()
         self.weights_version += 1
         limit = self.config.max_weight_staleness
         abort_all = abort_running if abort_running is not None else limit <= 0

@@ -56,11 +56,24 @@ class ModelRunner:
         self.forward_calls = 0
 
     # ---- metadata ----------------------------------------------------------------------------------------
+    def _stage(self, t: torch.Tensor) -> torch.Tensor:
+        """Host tensor -> device through a ring of reusable pinned buffers.  Page-locking a fresh buffer per tensor
+        costs more than the copy; a ring (not one buffer) because the engine queues a step's copies while the GPU
+        may still be running the previous step, whose staging memory must stay untouched until its copy has run."""
+        if self.device.type != "cuda":
+            return t
+        n = t.numel() * t.element_size()
+        ring = self.__dict__.setdefault("_rings", {})
+        r = ring.setdefault(t.dtype, {"bufs": [None] * 16, "i": 0})
+        i = r["i"] = (r["i"] + 1) % len(r["bufs"])
+        if r["bufs"][i] is None or r["bufs"][i].numel() < t.numel():
+            r["bufs"][i] = torch.empty(max(1024, t.numel()), dtype=t.dtype, pin_memory=True)
+        view = r["bufs"][i][:t.numel()].view(t.shape)
+        view.copy_(t)
+        return view.to(self.device, non_blocking=True)
+
     def _dev(self, data, dtype) -> torch.Tensor:
-        t = torch.tensor(data, dtype=dtype)
-        if self.device.type == "cuda":
-            return t.pin_memory().to(self.device, non_blocking=True)
-        return t
+        return self._stage(torch.tensor(data, dtype=dtype))
 
     @staticmethod
     def _segments(table: List[int], start: int, count: int, row0: int, bs: int) -> List[List[int]]:
@@ -125,8 +138,7 @@ class ModelRunner:
         pos[:n] = lens - 1
 
         def dev(a):
-            t = torch.from_numpy(a)
-            return t.pin_memory().to(self.device, non_blocking=True) if self.device.type == "cuda" else t
+            return self._stage(torch.from_numpy(a))
 
         return InferenceContext(
             is_prefill=False, num_seqs=B, block_tables=dev(bt), context_lens=dev(ctx_lens),

@@ -245,11 +245,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int j = m_blk / comm.world, s_ = m_blk % comm.world;
       m_blk = ((s_ + comm.rank + 1) % comm.world) * bpr + j;
     } else if (COMM == 2) {
-      // every rank pushes its row block j at about the same time: consume block j of all sources (own first),
-      // then block j + 1
+      // this rank's own row blocks first (they are read from the local shard and depend on nobody), then, since
+      // every rank pushes its row block j at about the same time, block j of all other sources before block j + 1
       const int bpr = comm.rows_per_rank / GEMM_BM;
-      const int j = m_blk / comm.world, s_ = m_blk % comm.world;
-      m_blk = ((s_ + comm.rank) % comm.world) * bpr + j;
+      if (m_blk < bpr || comm.world == 1) {
+        m_blk = comm.rank * bpr + m_blk;
+      } else {
+        const int v = m_blk - bpr;
+        const int j = v / (comm.world - 1), s_ = v % (comm.world - 1) + 1;
+        m_blk = ((comm.rank + s_) % comm.world) * bpr + j;
+      }
     }
   };
 
@@ -263,7 +268,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         int m_blk, n_blk;
         tile_coords(t, m_blk, n_blk);
         const int m0 = m_blk * GEMM_BM, n0 = n_blk * BN;
-        if (COMM == 2) {   // the A rows of this tile must have arrived in the local gather buffer
+        // COMM 2: own rows come straight from this rank's shard (tensor map tmR); a peer's rows must have arrived
+        // in the local gather buffer
+        const int own0 = COMM == 2 ? comm.rank * (comm.rows_per_rank / GEMM_BM) : 0;
+        const bool own = COMM == 2 && m_blk >= own0 && m_blk < own0 + comm.rows_per_rank / GEMM_BM;
+        if (COMM == 2 && !own) {
           if (!wait_flag_ge<true>(comm.gather_flags + m_blk, comm.epoch * comm.pieces_per_block, status,
                                   ERR_COMM_FLAG_WAIT)) {
             ok = false;
@@ -271,6 +280,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           }
           asm volatile("fence.proxy.async;" ::: "memory");
         }
+        const CUtensorMap* mapA = own ? &tmR : &tmA;
+        const int a_row = own ? m0 - own0 * GEMM_BM : m0;
         for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, status, ERR_GEMM_PRODUCER_WAIT)) {
             ok = false;
@@ -280,7 +291,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           uint8_t* sB = sA + Cfg::A_BYTES;
           mbar_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
           if (!A_MN) {
-            tma_load_2d(sA, &tmA, &full_bar[stage], kb * GEMM_BK, m0);
+            tma_load_2d(sA, mapA, &full_bar[stage], kb * GEMM_BK, a_row);
           } else {
 #pragma unroll
             for (int c = 0; c < GEMM_BM / 64; ++c)
@@ -418,7 +429,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
           }
         }
-        __threadfence_system();                        // this thread's stores are ordered before the arrival below
+        // the piece's stores (all 128 threads) happen before the barrier; the release below, by one lane per
+        // destination rank, is cumulative over them: no system-scope fence in every thread
         named_barrier(2, 128);
         if (ct < comm.world) red_release_sys_add(comm.peer_flags[ct] + comm.rank * bpr + b, 1);
       }
@@ -497,7 +509,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         tc_fence_before();
         mbar_arrive(&tmem_empty[acc]);
-        __threadfence_system();            // this thread's peer stores are ordered before the signal
+        // every thread's peer stores happen before this barrier; the system-scope release below (one lane) is
+        // cumulative over them, so the other 127 threads go on to the next tile without a fence of their own
         named_barrier(1, 128);
         if (warp == 2 && lane == 0) {
           const int rb = (m_blk * GEMM_BM - owner * comm.rows_per_rank) / GEMM_BM;
@@ -721,6 +734,8 @@ static int launch_gemm(const void* A, const void* B, void* C, const void* R, int
   const bool out_fp32 = flags & GEMM_OUT_FP32;
   const CUtensorMap* tc = (out_fp32 || COMM == 1) ? ta : tensor_map_2d_bf16(C, M, N, ldc, GEMM_BM, 64);
   const CUtensorMap* tr = (!out_fp32 && (flags & GEMM_RESIDUAL)) ? tensor_map_2d_bf16(R, M, N, ldc, GEMM_BM, 64) : tc;
+  if (COMM == 2)   // the second A map: this rank's own activation shard, read in place
+    tr = tensor_map_2d_bf16(comm.local_src, comm.rows_per_rank, K, K, GEMM_BM, 64);
   if (!tc || !tr) return 2;
   int* status = status_ptr();
   if (!status) return 3;

@@ -6,6 +6,8 @@
 // scales [num_blocks, Hkv] fp32 (value = stored * scale).
 #include <cuda_fp8.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "host.h"
 
@@ -155,7 +157,7 @@ __device__ __forceinline__ void dec_unpack<true>(const uint4& u, float* f) {
 // maximum, sum and DPL accumulator dims per head, base-2 exponent domain); groups and warps are merged
 // once at the end with the exact log-sum-exp rule.  GH query heads of the kv head are handled per CTA
 // (their q pieces sit in registers); larger GQA ratios use several CTAs (head groups) per kv head.
-template <bool FP8, int GH>
+template <bool FP8, int GH, bool PIPE>
 __global__ void __launch_bounds__(DEC_THREADS) paged_decode_kernel(
     const __nv_bfloat16* __restrict__ q, const void* __restrict__ k_cache, const void* __restrict__ v_cache,
     const float* __restrict__ k_scale, const float* __restrict__ v_scale,
@@ -199,28 +201,40 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_decode_kernel(
     l[g] = 0.f;
   }
 
-  for (int base = t_begin + warp * (TPW * U); base < t_end; base += (DEC_THREADS / 32) * TPW * U) {
+  // Software pipeline over the cache rows: the loads of step i + 1 (block-table entry, then K and V pieces) are
+  // issued before the arithmetic of step i, so every lane keeps 2 * U sixteen-byte loads in flight instead of
+  // alternating between "waiting for loads" and "computing".
+  struct Rows {
     uint4 kq[U], vq[U];
     float ks[U], vs[U];
     bool valid[U];
+  };
+  auto load_rows = [&](Rows& r, int base) {
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int tok = base + u * TPW + group;
-      valid[u] = tok < t_end;
-      kq[u] = make_uint4(0, 0, 0, 0);
-      vq[u] = make_uint4(0, 0, 0, 0);
-      ks[u] = vs[u] = 1.f;
-      if (valid[u]) {
+      r.valid[u] = tok < t_end;
+      r.kq[u] = make_uint4(0, 0, 0, 0);
+      r.vq[u] = make_uint4(0, 0, 0, 0);
+      r.ks[u] = r.vs[u] = 1.f;
+      if (r.valid[u]) {
         const int blk = table[tok / PAGE];
         const size_t a = (static_cast<size_t>(blk) * PAGE + tok % PAGE) * tok_stride;
-        kq[u] = *reinterpret_cast<const uint4*>(kc + a);
-        vq[u] = *reinterpret_cast<const uint4*>(vc + a);
+        r.kq[u] = *reinterpret_cast<const uint4*>(kc + a);
+        r.vq[u] = *reinterpret_cast<const uint4*>(vc + a);
         if (FP8) {
-          ks[u] = k_scale[static_cast<size_t>(blk) * Hkv + kvh];
-          vs[u] = v_scale[static_cast<size_t>(blk) * Hkv + kvh];
+          r.ks[u] = k_scale[static_cast<size_t>(blk) * Hkv + kvh];
+          r.vs[u] = v_scale[static_cast<size_t>(blk) * Hkv + kvh];
         }
       }
     }
+  };
+  auto consume = [&](const Rows& r) {
+    const uint4* kq = r.kq;
+    const uint4* vq = r.vq;
+    const float* ks = r.ks;
+    const float* vs = r.vs;
+    const bool* valid = r.valid;
     float sc[U][GH];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
@@ -267,6 +281,29 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_decode_kernel(
       for (int g = 0; g < GH; ++g)
 #pragma unroll
         for (int d = 0; d < DPL; ++d) acc[g][d] = fmaf(sc[u][g], vf[d], acc[g][d]);
+    }
+  };
+  {
+    constexpr int STEP = (DEC_THREADS / 32) * TPW * U;
+    int base = t_begin + warp * (TPW * U);
+    if (PIPE) {
+      Rows ra, rb;
+      if (base < t_end) load_rows(ra, base);
+      while (base < t_end) {
+        if (base + STEP < t_end) load_rows(rb, base + STEP);
+        consume(ra);
+        base += STEP;
+        if (base >= t_end) break;
+        if (base + STEP < t_end) load_rows(ra, base + STEP);
+        consume(rb);
+        base += STEP;
+      }
+    } else {
+      for (; base < t_end; base += STEP) {
+        Rows r;
+        load_rows(r, base);
+        consume(r);
+      }
     }
   }
 
@@ -421,10 +458,23 @@ B2_EXPORT int b2_paged_decode(const void* q, const void* k_cache, const void* v_
   // lane, so four heads would leave room for only two CTAs per SM)
   const int GH = (G % 4 == 0 && !fp8) ? 4 : (G % 2 == 0 ? 2 : 1);
   dim3 grid(B, Hkv * (G / GH), nsplit);
+  // B200FW_DECODE_PIPE=1 selects the software-pipelined row loop (loads of the next step under this step's
+  // arithmetic; more registers, fewer resident CTAs), 0 the plain loop
+  static const bool pipe = [] {
+    const char* e = std::getenv("B200FW_DECODE_PIPE");
+    return e != nullptr && e[0] == '1';
+  }();
 #define B2_DECODE_LAUNCH(F8, GHV)                                                                          \
-  paged_decode_kernel<F8, GHV><<<grid, DEC_THREADS, 0, stream>>>(                                          \
-      static_cast<const __nv_bfloat16*>(q), k_cache, v_cache, k_scale, v_scale, block_tables, context_lens, \
-      max_blocks, static_cast<__nv_bfloat16*>(out), part_o, part_ml, Hq, Hkv, partition, scale)
+  do {                                                                                                     \
+    if (pipe)                                                                                              \
+      paged_decode_kernel<F8, GHV, true><<<grid, DEC_THREADS, 0, stream>>>(                                \
+          static_cast<const __nv_bfloat16*>(q), k_cache, v_cache, k_scale, v_scale, block_tables, context_lens, \
+          max_blocks, static_cast<__nv_bfloat16*>(out), part_o, part_ml, Hq, Hkv, partition, scale);       \
+    else                                                                                                   \
+      paged_decode_kernel<F8, GHV, false><<<grid, DEC_THREADS, 0, stream>>>(                               \
+          static_cast<const __nv_bfloat16*>(q), k_cache, v_cache, k_scale, v_scale, block_tables, context_lens, \
+          max_blocks, static_cast<__nv_bfloat16*>(out), part_o, part_ml, Hq, Hkv, partition, scale);       \
+  } while (0)
   if (fp8) {
     if (GH == 4) B2_DECODE_LAUNCH(true, 4);
     else if (GH == 2) B2_DECODE_LAUNCH(true, 2);

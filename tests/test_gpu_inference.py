@@ -178,6 +178,33 @@ def test_native_engine_matches_eager_and_feature_switches(gpu_model):
     assert _agree(fp8, base) >= 0.5
 
 
+def test_one_step_late_decode_equals_synchronous_decode(gpu_model):
+    """Decode-only steps keep the sampled ids on the device and read them one step late; tokens, lengths and the
+    EOS cut must equal the synchronous engine's (greedy, so both are deterministic)."""
+    prompts = _prompts()
+    sync = _gpu_engine(gpu_model, async_decode=False)
+    want = sync.generate(prompts, max_tokens=24)
+    e = _gpu_engine(gpu_model, async_decode=True)
+    assert e.generate(prompts, max_tokens=24) == want
+    assert all(t >= 0 for o in want for t in o) and e._inflight is None
+    # an EOS in the middle: pick a token the greedy run emits at position 5 of the first prompt
+    eos = want[0][5]
+    cut = [o[:o.index(eos) + 1] if eos in o else o for o in want]
+    for flag in (False, True):
+        out = _gpu_engine(gpu_model, async_decode=flag, eos_token_id=eos).generate(prompts, max_tokens=24)
+        assert out == cut, flag
+    # different lengths per request (some finish by count while others are in flight)
+    e2 = _gpu_engine(gpu_model, async_decode=True)
+    for i, p in enumerate(prompts):
+        e2.add_request(f"r{i}", p, max_tokens=min(24, 6 + 5 * i))
+    while e2.has_pending():
+        e2.step()
+    got = [e2.finished[f"r{i}"].output_tokens for i in range(len(prompts))]
+    assert [len(o) for o in got] == [min(24, 6 + 5 * i) for i in range(len(prompts))]
+    assert all(t >= 0 for o in got for t in o)
+    assert _agree(got, [w[:len(o)] for w, o in zip(want, got)]) >= 0.9
+
+
 def test_speculative_decoding_is_lossless_under_greedy(gpu_model):
     prompts = _prompts()
     base = _gpu_engine(gpu_model).generate(prompts, max_tokens=16)
