@@ -73,6 +73,7 @@ class _Rollout:
     logprobs: Optional[List[List[float]]]        # mean per-token log-prob per response, flattened B*K
     weights_version: int
     seconds: float
+    token_logprobs: Optional[List[List[List[float]]]] = None     # per-token log-probs, [prompt][sample][token]
 
 
 class ColocateOrchestrator:
@@ -288,7 +289,10 @@ class ColocateOrchestrator:
         outs = [o if o else [0] for o in outs]
         responses = [outs[i * K:(i + 1) * K] for i in range(len(batch.prompt_tokens))]
         seq_lp = [sum(l) / max(1, len(l)) if l else 0.0 for l in lps] if lps and lps[0] is not None else None
-        return _Rollout(batch, responses, seq_lp, version, time.perf_counter() - t0)
+        tok_lp = None
+        if seq_lp is not None and all(l is not None for l in lps):
+            tok_lp = [lps[i * K:(i + 1) * K] for i in range(len(batch.prompt_tokens))]
+        return _Rollout(batch, responses, seq_lp, version, time.perf_counter() - t0, tok_lp)
 
     async def _rollout_vllm(self, batch: GRPOBatch) -> _Rollout:
         """Rollouts from a vLLM server: K text completions per prompt over HTTP, tokenised for the trainer.  The
@@ -327,7 +331,8 @@ class ColocateOrchestrator:
         infer_lp = torch.tensor(ro.logprobs) if (ro.logprobs is not None and cfg.icepop_enabled) else None
         if self.c3po is not None:
             adv = [TrainEngine.group_advantages(r) for r in rewards]
-            subs = self.c3po.split_and_pack(prompts, ro.responses, rewards, adv)
+            subs = self.c3po.split_and_pack(prompts, ro.responses, rewards, adv,
+                                            ro.token_logprobs if cfg.icepop_enabled else None)
             m = None
             for i, sb in enumerate(subs):
                 last = i == len(subs) - 1

@@ -119,16 +119,19 @@ class InferWorker:
 
     ``model`` (a built ``ParallelTransformerModel``) or ``model_path`` (HF directory) selects the paged
     ``kv_cache`` engine; with neither the engine runs in ``mock`` mode (scheduler + random tokens), which
-    is what the reference's custom backend always does.  ``backend="vllm"`` is not served in-process: use
-    ``VLLMClient`` against a running server.
+    is what the reference's custom backend always does.  ``backend="vllm"`` builds an in-process ``vllm.LLM`` on
+    ``model_path`` as the reference does (src/engines/infer_worker.py:90-99,139-162): a library engine, kept for
+    parity; it needs a real HF model directory and takes text (or token-id) prompts.  Weight updates reach it through
+    ``VLLMClient`` / ``IPCWeightTransfer`` against a server, not through this class.
     """
 
     def __init__(self, model_path: Optional[str] = None, tp_size: int = 1, gpu_memory_utilization: float = 0.85,
                  max_model_len: int = 4096, backend: str = "custom", inference_config: Optional[InferenceConfig] = None,
                  model=None, tokenizer=None, merge_fn: Optional[Callable[[Dict[str, torch.Tensor]], Dict[str, torch.Tensor]]] = None):
-        if backend not in ("custom", "mock"):
-            raise ValueError(f"InferWorker backend {backend!r}: only the native engine runs in-process "
-                             "(a vLLM server is driven through b200fw.sync.VLLMClient)")
+        if backend not in ("custom", "mock", "vllm"):
+            raise ValueError(f"InferWorker backend {backend!r}: expected 'custom' (native engine), 'mock' or 'vllm'")
+        if backend == "vllm" and not model_path:
+            raise ValueError("InferWorker backend 'vllm' needs model_path (a Hugging Face model directory)")
         self.model_path, self.tp_size = model_path, tp_size
         self.gpu_memory_utilization, self.max_model_len, self.backend = gpu_memory_utilization, max_model_len, backend
         self._config, self._model, self._tokenizer, self._merge_fn = inference_config, model, tokenizer, merge_fn
@@ -141,6 +144,16 @@ class InferWorker:
 
     # ---- lifecycle ------------------------------------------------------------------------------------
     def initialize(self) -> bool:
+        if self.backend == "vllm":
+            try:
+                from vllm import LLM
+            except Exception as e:  # noqa: BLE001
+                raise RuntimeError(f"InferWorker backend 'vllm': the vllm package cannot be imported ({e})") from e
+            self._vllm = LLM(model=self.model_path, tensor_parallel_size=self.tp_size,
+                             gpu_memory_utilization=self.gpu_memory_utilization, max_model_len=self.max_model_len,
+                             trust_remote_code=True)
+            self._initialized = True
+            return True
         cfg = self._config
         if cfg is None:
             have_model = self._model is not None or (self.model_path is not None and self.backend != "mock")
@@ -176,6 +189,16 @@ class InferWorker:
         assert self._initialized, "InferWorker not initialized. Call initialize() first."
         t0 = time.perf_counter()
         as_text = [isinstance(p, str) for p in prompts]
+        if self.backend == "vllm":
+            from vllm import SamplingParams
+            sp = SamplingParams(n=num_samples, max_tokens=max_tokens, temperature=temperature,
+                                top_p=0.95 if top_p is None else top_p)
+            inputs = [p if t else {"prompt_token_ids": list(p)} for p, t in zip(prompts, as_text)]
+            outs = self._vllm.generate(inputs, sp)
+            results = [[(c.text if t else list(c.token_ids)) for c in o.outputs] for o, t in zip(outs, as_text)]
+            self._total_generate_time += time.perf_counter() - t0
+            self._total_requests += len(prompts)
+            return results
         toks = [list(self._tok().encode(p)) if t else list(p) for p, t in zip(prompts, as_text)]
         batch = [t for t in toks for _ in range(num_samples)]
         outs = self._engine.generate(batch, max_tokens=max_tokens, temperature=temperature, top_p=top_p) if batch else []
@@ -199,6 +222,9 @@ class InferWorker:
         state); with a ``merge_fn`` the active adapter state is merged and loaded too.  Returns ``False``
         (and leaves the version alone) on any failure."""
         assert self._initialized, "InferWorker not initialized."
+        if self.backend == "vllm":
+            logger.error("InferWorker backend 'vllm' takes weight updates through VLLMClient / IPCWeightTransfer")
+            return False
         try:
             if mode == "delta":
                 if self._double_buffer is None:
@@ -225,6 +251,8 @@ class InferWorker:
 
     # ---- status ---------------------------------------------------------------------------------------
     def health_check(self) -> bool:
+        if self.backend == "vllm":
+            return self._initialized and getattr(self, "_vllm", None) is not None
         return self._initialized and self._engine is not None and self._engine.initialized
 
     def get_status(self) -> dict:

@@ -28,6 +28,7 @@ class ResponseChunk:
     reward: float
     source_idx: Tuple[int, int]
     advantage: float = 0.0
+    infer_logprob: Optional[float] = None       # mean rollout log-prob of this chunk's tokens (IcePop), when known
 
     @property
     def length(self) -> int:
@@ -39,15 +40,24 @@ class C3POPlusScheduler:
         self.config = config
         self.last_stats: Dict[str, float] = {}
 
-    def split(self, prompts_tokens, responses_group, rewards_group, advantages_group=None) -> List[ResponseChunk]:
+    def split(self, prompts_tokens, responses_group, rewards_group, advantages_group=None,
+              token_logprobs_group=None) -> List[ResponseChunk]:
+        """``token_logprobs_group[b][k]``: the rollout engine's per-token log-probs of response ``k`` of prompt ``b``
+        (optional); each chunk then carries the mean over its own tokens, so IcePop can compare it with the
+        trainer's without an extra inference-mode forward."""
         budget = max(1, self.config.token_budget)
         chunks: List[ResponseChunk] = []
         for b, (prompt, responses, rewards) in enumerate(zip(prompts_tokens, responses_group, rewards_group)):
             for k, (resp, rew) in enumerate(zip(responses, rewards)):
                 adv = advantages_group[b][k] if advantages_group is not None else 0.0
+                tlp = token_logprobs_group[b][k] if token_logprobs_group is not None else None
                 starts = range(0, max(len(resp), 1), budget)
                 for s in starts:
-                    chunks.append(ResponseChunk(prompt, resp[s:s + budget], resp[:s], rew, (b, k), adv))
+                    lp = None
+                    if tlp is not None and len(tlp) >= min(len(resp), s + budget) and len(resp) > s:
+                        piece = tlp[s:s + budget]
+                        lp = sum(piece) / len(piece)
+                    chunks.append(ResponseChunk(prompt, resp[s:s + budget], resp[:s], rew, (b, k), adv, lp))
         return chunks
 
     def pack(self, chunks: List[ResponseChunk]) -> List[List[ResponseChunk]]:
@@ -70,15 +80,20 @@ class C3POPlusScheduler:
 
     @staticmethod
     def to_grpo_kwargs(bin_chunks: List[ResponseChunk]) -> Dict:
-        return {
+        kw = {
             "prompts_tokens": [c.prompt_tokens + c.response_prefix for c in bin_chunks],
             "responses_group": [[c.response_tokens] for c in bin_chunks],
             "rewards_group": [[c.reward] for c in bin_chunks],
             "precomputed_advantages": [[c.advantage] for c in bin_chunks],
         }
+        if bin_chunks and all(c.infer_logprob is not None for c in bin_chunks):
+            import torch
+            kw["infer_log_probs"] = torch.tensor([c.infer_logprob for c in bin_chunks], dtype=torch.float32)
+        return kw
 
     def split_and_pack(self, prompts_tokens: List[List[int]], responses_group: List[List[List[int]]],
                        rewards_group: List[List[float]],
-                       advantages_group: Optional[List[List[float]]] = None) -> List[Dict]:
-        chunks = self.split(prompts_tokens, responses_group, rewards_group, advantages_group)
+                       advantages_group: Optional[List[List[float]]] = None,
+                       token_logprobs_group=None) -> List[Dict]:
+        chunks = self.split(prompts_tokens, responses_group, rewards_group, advantages_group, token_logprobs_group)
         return [self.to_grpo_kwargs(b) for b in self.pack(chunks)]

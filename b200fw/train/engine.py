@@ -294,6 +294,13 @@ class TrainEngine:
                                  "kernel ran out (301: a peer's flag never arrived; 1xx/2xx: a pipeline barrier); "
                                  "the update of this step is not trustworthy")
 
+    def _clip_grad_norm(self) -> float:
+        """Global L2 norm of the gradients over DP x TP x PP, with the clip to ``max_grad_norm`` armed for the next
+        ``optimizer.step()``; ``-1.0`` when the norm is not finite (the step then leaves the weights untouched).
+        The reference's unit of the same name (src/engines/train_engine.py:1451-1530) scales ``p.grad`` in place;
+        here the scale is applied inside the fused AdamW kernel, so the gradients themselves stay as they are."""
+        return float(self.optimizer.clip_grad_norm(self.config.max_grad_norm))
+
     def _finish_step(self, gn: Optional[torch.Tensor]) -> float:
         """Host side of the NaN/Inf guard: a non-finite norm (reported as -1) means the device skipped
         the update, so neither the step counter nor the schedule advance."""

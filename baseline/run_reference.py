@@ -86,14 +86,17 @@ def run_reference(a) -> None:
     root = os.path.dirname(HERE)
     sys.path.insert(0, root)
     from b200fw.model.config import PRESETS   # architecture numbers only (a dataclass of ints)
-    preset = PRESETS[a.model]
+    import copy
+    preset = copy.deepcopy(PRESETS[a.model])
+    if getattr(a, "layers", 0) > 0:
+        preset.num_layers = a.layers        # smoke runs of a large architecture; not a benchmark config
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     dp = world // (a.tp * a.pp)
     # ---- fake HF directory (rank 0 writes, the others wait for the marker file) -----------------------
-    hf_dir = f"/tmp/b200fw_ref_hf_{a.model}"
+    hf_dir = f"/tmp/b200fw_ref_hf_{a.model}" + (f"_L{a.layers}" if getattr(a, "layers", 0) > 0 else "")
     marker = os.path.join(hf_dir, ".ready")
     if rank == 0 and not os.path.exists(marker):
         write_fake_hf_dir(hf_dir, preset, with_weights=preset.num_params() < 5e9)
@@ -169,7 +172,9 @@ def run_reference(a) -> None:
             "warmup": a.warmup, "ms_per_step": ms / a.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic (seeded uniform tokens, random-init weights)",
             "impl": "reference",
-            "config": {"model": f"{a.model}-arch full SFT" if a.lora_rank <= 0 else f"{a.model}-arch LoRA r{a.lora_rank}",
+            "config": {"model": (f"{a.model}-arch full SFT" if a.lora_rank <= 0 else f"{a.model}-arch LoRA r{a.lora_rank}")
+                       + (f" (layers cut to {a.layers}: smoke run, not the named config)" if getattr(a, "layers", 0) > 0 else ""),
+                       "grad_ckpt": a.grad_ckpt,
                        "global_batch": a.micro_batch * micro_per_step * dp, "micro_batch_per_gpu": a.micro_batch,
                        "grad_accum": a.grad_accum, "seq_len": a.seq_len,
                        "parallelism": f"dp{dp}" + (f"+tp{a.tp}" if a.tp > 1 else "") + (f"+pp{a.pp}" if a.pp > 1 else ""),

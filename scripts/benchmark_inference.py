@@ -42,6 +42,10 @@ def parse_args(argv=None):
     ap.add_argument("--top-p", type=float, default=0.95)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--warmup", type=int, default=1)
+    ap.add_argument("--profile-decode-steps", type=int, default=0,
+                    help="bracket this many decode steps with cudaProfilerStart/Stop (for `ncu --profile-from-start off`)")
+    ap.add_argument("--no-async-decode", dest="async_decode", action="store_false",
+                    help="read every step's sampled ids back before the next step is launched")
     return ap.parse_args(argv)
 
 
@@ -78,7 +82,7 @@ def main(argv=None):
         max_cached_blocks=blocks, enable_cuda_graph=a.cuda_graph, speculative_enabled=a.speculative,
         speculative_num_tokens=4, speculative_draft_layers=2, enable_partitioned_attention=bool(a.long_context),
         attention_partition_size=512, temperature=a.temperature, top_p=a.top_p, eos_token_id=None, seed=a.seed,
-        adaptive_chunking=False)
+        adaptive_chunking=False, async_decode=a.async_decode)
     eng = InferenceEngine(cfg, model).initialize()
     for _ in range(a.warmup):     # compile-free warm-up: allocator, graphs, tensor maps
         eng.generate(prompts[: min(8, len(prompts))], 8)
@@ -98,9 +102,15 @@ def main(argv=None):
     s1.record()
     first = sum(r.num_generated_tokens for r in eng.requests.values())
     steps_decode = 0
+    if a.profile_decode_steps:
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
     while eng.has_pending():
         eng.step()
         steps_decode += 1
+        if a.profile_decode_steps and steps_decode == a.profile_decode_steps:
+            torch.cuda.synchronize()
+            torch.cuda.profiler.stop()
     s2.record()
     torch.cuda.synchronize()
     clocks = sampler.stop()

@@ -174,6 +174,7 @@ def main():
     ap.add_argument("--ctx", type=int, default=1024)
     ap.add_argument("--vocab", type=int, default=151936)
     ap.add_argument("--fp8", action="store_true")
+    ap.add_argument("--partition", type=int, default=0, help="paged_decode: tokens per split-KV partition (0 = automatic)")
     ap.add_argument("--fp32-acc", action="store_true", help="gemm: accumulate into an fp32 output (weight-gradient form)")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
@@ -281,6 +282,8 @@ def main():
         need_split = a.batch * a.hkv < 296
         part = 512 if need_split else 0
         ns = (a.ctx + 511) // 512 if need_split else 1
+        if a.partition:
+            part, ns = a.partition, (a.ctx + a.partition - 1) // a.partition
         fn = lambda: ops.paged_decode_attention(q, kc, vc, bt, cl, a.hq, k_scale=ks, v_scale=ks, partition=part, nsplit=ns)
         bytes_ = 2.0 * a.batch * a.ctx * a.hkv * 128 * (1 if a.fp8 else 2)
     elif a.kernel == "sampler":

@@ -61,3 +61,16 @@ def test_icepop_with_c3po_chunk_count():
     adv = torch.tensor([a[0] for sb in subs for a in sb["precomputed_advantages"]])
     out, _ = f.filter_divergent_responses(torch.zeros(n), torch.zeros(n), adv)
     assert torch.equal(out, adv)
+
+
+def test_c3po_chunks_carry_their_own_mean_rollout_logprob():
+    from b200fw.train.c3po import C3POConfig, C3POPlusScheduler
+    s = C3POPlusScheduler(C3POConfig(True, token_budget=4, target_batch_tokens=64))
+    prompts, resp = [[1, 2, 3]], [[[10, 11, 12, 13, 14, 15], [20, 21]]]
+    tlp = [[[-1.0, -1.0, -1.0, -1.0, -3.0, -5.0], [-2.0, -4.0]]]
+    chunks = s.split(prompts, resp, [[1.0, 0.0]], [[0.5, -0.5]], tlp)
+    got = {(c.source_idx, len(c.response_prefix)): c.infer_logprob for c in chunks}
+    assert got == {((0, 0), 0): -1.0, ((0, 0), 4): -4.0, ((0, 1), 0): -3.0}
+    subs = s.split_and_pack(prompts, resp, [[1.0, 0.0]], [[0.5, -0.5]], tlp)
+    assert all("infer_log_probs" in sb and len(sb["infer_log_probs"]) == len(sb["prompts_tokens"]) for sb in subs)
+    assert all("infer_log_probs" not in sb for sb in s.split_and_pack(prompts, resp, [[1.0, 0.0]], [[0.5, -0.5]]))

@@ -67,7 +67,39 @@ def test_infer_worker_mock_backend_and_errors():
     st = w.get_status()
     assert st["total_requests"] == 3 and st["backend"] == "custom" and "scheduler" in st["engine_stats"]
     with pytest.raises(ValueError):
-        InferWorker(backend="vllm")
+        InferWorker(backend="vllm")                      # the library backend needs a model directory
+    with pytest.raises(ValueError):
+        InferWorker(backend="nonsense")
+
+
+def test_infer_worker_vllm_backend_drives_the_library_engine(monkeypatch):
+    """``backend="vllm"`` builds ``vllm.LLM`` on the model directory and maps text / token-id prompts to its
+    ``generate`` call, like the reference worker; checked against a stand-in module (no model files here)."""
+    import sys
+    import types
+    calls = {}
+
+    class FakeLLM:
+        def __init__(self, **kw):
+            calls["init"] = kw
+
+        def generate(self, inputs, sp):
+            calls["inputs"], calls["sp"] = inputs, sp
+            comp = lambda i, k: types.SimpleNamespace(text=f"t{i}-{k}", token_ids=[i, k])
+            return [types.SimpleNamespace(outputs=[comp(i, k) for k in range(sp.n)]) for i in range(len(inputs))]
+
+    class FakeParams:
+        def __init__(self, **kw):
+            self.__dict__.update(kw)
+
+    monkeypatch.setitem(sys.modules, "vllm", types.SimpleNamespace(LLM=FakeLLM, SamplingParams=FakeParams))
+    w = InferWorker(model_path="/models/x", tp_size=2, backend="vllm", max_model_len=1024)
+    assert w.initialize() and w.health_check()
+    assert calls["init"]["model"] == "/models/x" and calls["init"]["tensor_parallel_size"] == 2
+    out = w.generate(["hello", [4, 5, 6]], num_samples=2, max_tokens=7, temperature=0.5)
+    assert out == [["t0-0", "t0-1"], [[1, 0], [1, 1]]]
+    assert calls["inputs"][1] == {"prompt_token_ids": [4, 5, 6]} and calls["sp"].max_tokens == 7 and calls["sp"].top_p == 0.95
+    assert w.update_weights({}, mode="full") is False and w.get_status()["backend"] == "vllm"
 
 
 def test_trainer_to_rollout_weight_flow_full_and_delta():
