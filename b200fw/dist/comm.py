@@ -345,13 +345,13 @@ class PipeChannel:
 
     The reference's stage-to-stage primitives (src/distributed/comm.py:404-558) post a send / receive pair and wait
     for it on the compute stream, with a fresh receive buffer per call.  Here activations (downstream) and
-    gradients (upstream) travel on separate communicators, so a receive can be *posted* well before its data is
-    needed and a send never holds the compute stream:
+    gradients (upstream) travel on separate communicators and a send never holds the compute stream:
 
     * ``post_recv()`` enqueues the receive into the next buffer of a persistent ring on the communication stream
       (which first waits for the compute work queued so far: the buffer's previous use is over) and returns a handle;
-      ``wait(handle)`` makes the compute stream wait for it and returns the buffer.  Between the two calls the
-      transfer runs under whatever compute was queued in between.
+      ``wait(handle)`` makes the compute stream wait for it and returns the buffer.  Post a receive where its data
+      is used: an NCCL receive occupies the GPU until its sender arrives, and left pending ahead of unrelated compute
+      it can stall that compute when streams outnumber the hardware queues.
     * ``send(t)`` enqueues the send on the communication stream after the compute work that produced ``t``; the
       compute stream does not wait for it.
 

@@ -55,6 +55,8 @@ class InferenceConfig:
     # host has read them (one step late), so host-side scheduling overlaps the GPU's work.  The cost is one discarded
     # token after an EOS.  Turned off with speculative decoding (which needs the values every round).
     async_decode: bool = True
+    # split every sequence's keys over a few CTAs when one CTA per (sequence, kv head) would fill only a few waves
+    decode_balance_splits: bool = False
 
     @classmethod
     def from_model_config(cls, mc, **kw) -> "InferenceConfig":

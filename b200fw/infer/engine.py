@@ -90,6 +90,7 @@ class InferenceEngine:
         self.kv = KVCacheManager(self.pool, cfg.block_size)
         self.runner = ModelRunner(self.model, self.pool, self.kv, cfg.attention_partition_size,
                                   cfg.enable_partitioned_attention)
+        self.runner.balance_splits = cfg.decode_balance_splits
         if cfg.enable_prefix_caching or cfg.use_radix_cache:
             self.prefix_cache = RadixAttentionCache(cfg.block_size, cfg.radix_cache_max_nodes) if cfg.use_radix_cache \
                 else PrefixCache(cfg.block_size, cfg.max_cached_blocks)

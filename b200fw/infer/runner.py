@@ -146,10 +146,26 @@ class ModelRunner:
 
     # ---- forward -----------------------------------------------------------------------------------------
     def _split_plan(self, ctx: InferenceContext) -> Tuple[int, int]:
-        if not self.enable_partitioned or ctx.max_context_len <= self.partition_size:
-            return 0, 1
-        part = max(64, self.partition_size // 64 * 64)
-        return part, (ctx.max_context_len + part - 1) // part
+        if self.enable_partitioned and ctx.max_context_len > self.partition_size:
+            part = max(64, self.partition_size // 64 * 64)
+            return part, (ctx.max_context_len + part - 1) // part
+        if getattr(self, "balance_splits", False) and ctx.max_context_len > 256:
+            # One CTA per (sequence, kv head group) leaves the last of ~3.5 waves (256 sequences x 8 kv heads over
+            # 148 SMs x 4 resident CTAs) mostly empty, and a long sequence pins its CTA while the others finish.
+            # Splitting every sequence into a few partitions gives ~8 waves of shorter CTAs; the exact log-sum-exp
+            # merge costs one small kernel.
+            cfg = self.cfg
+            g = cfg.num_heads // cfg.num_kv_heads
+            gh = 4 if g % 4 == 0 and not self.pool.fp8 else (2 if g % 2 == 0 else 1)
+            ctas = ctx.num_seqs * cfg.num_kv_heads * (g // gh)
+            want = 8 * 148 * 4
+            if ctas < want:
+                nsplit = min((ctx.max_context_len + 255) // 256, -(-want // ctas))
+                if nsplit > 1:
+                    part = -(-ctx.max_context_len // nsplit)
+                    part = (part + 63) // 64 * 64
+                    return part, (ctx.max_context_len + part - 1) // part
+        return 0, 1
 
     @torch.no_grad()
     def forward(self, token_ids: torch.Tensor, ctx: InferenceContext, all_rows: bool = False,

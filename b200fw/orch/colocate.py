@@ -202,7 +202,9 @@ class ColocateOrchestrator:
                   kv_cache_dtype=cfg.kv_cache_dtype, enable_cuda_graph=cfg.enable_cuda_graph,
                   use_radix_cache=cfg.use_radix_cache, enable_prefix_caching=cfg.use_radix_cache,
                   max_num_batched_tokens=8192, max_prefill_tokens=4096, chunk_size=512, seed=cfg.seed,
-                  max_num_sequences=256)
+                  # every sample of the iteration's prompts decodes concurrently when the pool has room for it (one
+                  # decode wave instead of two halves the number of engine steps of a rollout)
+                  max_num_sequences=max(256, min(1024, self._per_rank_batch() * cfg.num_samples_per_prompt)))
         if cfg.kv_num_blocks > 0:
             ic = InferenceConfig.from_model_config(mc, num_blocks=cfg.kv_num_blocks, **kw)
         else:

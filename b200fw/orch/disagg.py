@@ -51,6 +51,8 @@ class DisaggConfig:
     c3po_plus_token_budget: int = 256
     c3po_plus_target_batch_tokens: int = 16384
     seed: int = 0
+    synthetic_reward_dense_weight: float = 0.5   # dense shaping term of the synthetic rule reward: a random-init policy
+                                                 # never earns the sparse reward, and all-zero advantages train nothing
     output_dir: str = "outputs_disagg"
     backend: Optional[str] = None        # process-group backend (default by device)
     # ---- accepted for configs written against the reference (src/orchestrator/disagg_orchestrator.py:39-70) ----
@@ -177,7 +179,7 @@ class DisaggOrchestrator:
         if self.reward_fn is None:
             from ..reward import SyntheticTokenReward
             vocab = (self.train_engine.model_config.vocab_size if self.is_trainer else self.infer_engine.config.vocab_size)
-            self.reward_fn = SyntheticTokenReward(vocab, cfg.seed)
+            self.reward_fn = SyntheticTokenReward(vocab, cfg.seed, dense_weight=cfg.synthetic_reward_dense_weight)
         return self
 
     # ---- phases ------------------------------------------------------------------------------------------------

@@ -6,10 +6,10 @@ deadlock), cool-down backwards; each micro-batch's loss is scaled by ``1/num_mic
 ``int64[3]`` shape handshake travels stage to stage; received activations become autograd leaves.
 Gradients accumulate into the optimizer's bucket buffers across micro-batches.
 
-Transfers overlap compute: activations and gradients use one communicator and one CUDA stream per direction
-(:class:`b200fw.dist.comm.PipeChannel`), receives land in persistent ring buffers and are posted one compute phase
-ahead (the gradient for this step's backward before its forward is queued, the next forward's activations before
-this backward), sends never hold the compute stream.
+Transfers: activations and gradients use one communicator and one CUDA stream per direction
+(:class:`b200fw.dist.comm.PipeChannel`); sends are queued behind the compute that produced their data and never hold
+the compute stream (a stage goes straight on to its next micro-batch), receives land in persistent ring buffers and
+are posted where their data is used.
 """
 from __future__ import annotations
 
@@ -138,17 +138,17 @@ class PipelineScheduler:
             recv = act_in.wait(act_in.post_recv())
             out = fwd(recv)
             act_out.send(out.detach())
-        pending_act = act_in.post_recv() if steady > 0 else None
         for i in range(steady):
-            recv = act_in.wait(pending_act)
-            # the gradient this step's backward needs is posted before the forward is queued: it arrives under it
-            pending_grad = grad_in.post_recv()
+            # A receive is posted where its data is used, never ahead of compute it does not depend on: an NCCL
+            # receive is a kernel that sits on the GPU until its sender arrives, and with more streams than hardware
+            # queues it can hold back this rank's own compute, whose result the peer is waiting for in turn (two
+            # stages that each posted a receive early stopped each other this way).  Sends are the asynchronous half:
+            # a pending send only waits for the peer's host to reach its receive.
+            recv = act_in.wait(act_in.post_recv())
             out = fwd(recv)
             if not pp.is_last_stage:
                 act_out.send(out.detach())
-            # ... and the next forward's activations are posted before the backward: they arrive under it
-            pending_act = act_in.post_recv() if i < steady - 1 else None
-            grad = grad_in.wait(pending_grad)
+            grad = grad_in.wait(grad_in.post_recv())
             inp, o = fifo.popleft()
             with self._track(f"B{i}", "backward"):
                 gin = self._backward(inp, o, grad)

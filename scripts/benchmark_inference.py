@@ -44,6 +44,8 @@ def parse_args(argv=None):
     ap.add_argument("--warmup", type=int, default=1)
     ap.add_argument("--profile-decode-steps", type=int, default=0,
                     help="bracket this many decode steps with cudaProfilerStart/Stop (for `ncu --profile-from-start off`)")
+    ap.add_argument("--balance-splits", action="store_true",
+                    help="split every sequence's keys over a few CTAs when the decode grid would fill only a few waves")
     ap.add_argument("--no-async-decode", dest="async_decode", action="store_false",
                     help="read every step's sampled ids back before the next step is launched")
     return ap.parse_args(argv)
@@ -82,7 +84,8 @@ def main(argv=None):
         max_cached_blocks=blocks, enable_cuda_graph=a.cuda_graph, speculative_enabled=a.speculative,
         speculative_num_tokens=4, speculative_draft_layers=2, enable_partitioned_attention=bool(a.long_context),
         attention_partition_size=512, temperature=a.temperature, top_p=a.top_p, eos_token_id=None, seed=a.seed,
-        adaptive_chunking=False, async_decode=a.async_decode)
+        adaptive_chunking=False, async_decode=a.async_decode,
+        decode_balance_splits=a.balance_splits)
     eng = InferenceEngine(cfg, model).initialize()
     for _ in range(a.warmup):     # compile-free warm-up: allocator, graphs, tensor maps
         eng.generate(prompts[: min(8, len(prompts))], 8)

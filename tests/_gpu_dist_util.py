@@ -34,7 +34,7 @@ def _entry(rank, world, port, fn, args, q, env=None):
             dist.destroy_process_group()
 
 
-def run_gpu_ranks(fn, world: int, *args, timeout: float = 300.0, env=None):
+def run_gpu_ranks(fn, world: int, *args, timeout: float = 120.0, env=None):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
