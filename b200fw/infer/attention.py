@@ -80,6 +80,11 @@ class PagedAttention(torch.nn.Module):
         return out.reshape(T, self.num_heads, self.head_dim)
 
     def _prefill_attention(self, q, k, v, ctx: InferenceContext) -> torch.Tensor:
+        if ctx.block_tables is not None and self.k_cache is not None and ctx.cu_seqlens_k is not None:
+            # keys / values read in place through the block table (src/inference/attention.py:248-257)
+            return ops.paged_prefill_attention(q, self.k_cache, self.v_cache, ctx.block_tables, ctx.cu_seqlens_q,
+                                               ctx.cu_seqlens_k, ctx.max_seqlen_q, self.num_heads, self.scale,
+                                               self.k_scale, self.v_scale)
         if ctx.gather_slots is not None:          # part of the keys (a cached prefix, earlier chunks) lives in pages
             k, v = ops.kv_gather(self.k_cache, self.v_cache, ctx.gather_slots, q.dtype, self.k_scale, self.v_scale)
         cu_k = ctx.cu_seqlens_k if ctx.cu_seqlens_k is not None else ctx.cu_seqlens_q

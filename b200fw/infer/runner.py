@@ -94,21 +94,30 @@ class ModelRunner:
         bs = self.block_size
         cu_q, cu_k, segs, pos, slots, last = [0], [0], [], [], [], []
         need_gather = any(s > 0 for s in starts)
+        # a bf16 cache is read in place through the block table; only an fp8 cache (dequantised) is gathered
+        paged = need_gather and self.device.type == "cuda" and not self.pool.fp8
+        tables = []
         for sid, st, n in zip(seq_ids, starts, counts):
             table = self.mgr.get_block_table(sid)
             segs += self._segments(table, st, n, cu_q[-1], bs)
             pos += list(range(st, st + n))
-            if need_gather:
+            if paged:
+                tables.append(table[:(st + n + bs - 1) // bs])
+            elif need_gather:
                 slots += [table[p // bs] * bs + p % bs for p in range(st + n)]
             cu_q.append(cu_q[-1] + n)
             cu_k.append(cu_k[-1] + (st + n if need_gather else n))
             last.append(cu_q[-1] - 1)
+        bt = None
+        if paged:
+            width = max(len(t) for t in tables)
+            bt = self._dev([list(t) + [0] * (width - len(t)) for t in tables], torch.int32)
         return InferenceContext(
             is_prefill=True, num_seqs=len(seq_ids), store_segments=self._dev(segs, torch.int32),
             cu_seqlens_q=self._dev(cu_q, torch.int32), cu_seqlens_k=self._dev(cu_k, torch.int32),
             max_seqlen_q=max(counts), total_q=cu_q[-1], total_k=cu_k[-1],
-            gather_slots=self._dev(slots, torch.int32) if need_gather else None,
-            positions=self._dev(pos, torch.int32), last_token_rows=self._dev(last, torch.long))
+            gather_slots=self._dev(slots, torch.int32) if (need_gather and not paged) else None,
+            block_tables=bt, positions=self._dev(pos, torch.int32), last_token_rows=self._dev(last, torch.long))
 
     def prepare_decode(self, seq_ids: Sequence, pad_to: int = 0, max_blocks: int = 0) -> InferenceContext:
         """Metadata for one decode step: every sequence's newest token sits at position ``len-1`` (its
@@ -187,11 +196,16 @@ class ModelRunner:
             ks, vs = self.pool.layer_scales(li)
             ops.kv_store(k, v, kc, vc, ctx.store_segments, ks, vs)
             if ctx.is_prefill:
-                if ctx.gather_slots is not None:
-                    K, V = ops.kv_gather(kc, vc, ctx.gather_slots, self.dtype, ks, vs)
+                if ctx.block_tables is not None:
+                    # chunks with earlier context: keys / values are read in place through the block table
+                    att = ops.paged_prefill_attention(q, kc, vc, ctx.block_tables, ctx.cu_seqlens_q, ctx.cu_seqlens_k,
+                                                      ctx.max_seqlen_q, Hq)
                 else:
-                    K, V = k, v
-                att = ops.varlen_attention(q, K, V, ctx.cu_seqlens_q, ctx.cu_seqlens_k, ctx.max_seqlen_q, Hq, Hkv)
+                    if ctx.gather_slots is not None:
+                        K, V = ops.kv_gather(kc, vc, ctx.gather_slots, self.dtype, ks, vs)
+                    else:
+                        K, V = k, v
+                    att = ops.varlen_attention(q, K, V, ctx.cu_seqlens_q, ctx.cu_seqlens_k, ctx.max_seqlen_q, Hq, Hkv)
             else:
                 att = ops.paged_decode_attention(q, kc, vc, ctx.block_tables, ctx.context_lens, Hq,
                                                  k_scale=ks, v_scale=vs, partition=part, nsplit=nsplit)

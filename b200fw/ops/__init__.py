@@ -10,10 +10,11 @@ from .elementwise import rmsnorm, qknorm_rope, swiglu, embedding, rope_tables
 from .attention import flash_attention
 from .loss import lm_head_cross_entropy, lm_head_logprob, grpo_token_loss, VocabShard, valid_rows
 from .optim import sumsq, fused_adamw
-from .paged import kv_store, kv_gather, paged_decode_attention, varlen_attention, topp_sample
+from .paged import (kv_store, kv_gather, paged_decode_attention, paged_prefill_attention, varlen_attention,
+                    topp_sample)
 
 __all__ = [
     "gemm", "linear", "grad_into_main", "rmsnorm", "qknorm_rope", "swiglu", "embedding", "rope_tables",
     "flash_attention", "VocabShard", "valid_rows", "lm_head_cross_entropy", "lm_head_logprob", "grpo_token_loss", "sumsq",
-    "fused_adamw", "kv_store", "kv_gather", "paged_decode_attention", "varlen_attention", "topp_sample",
+    "fused_adamw", "kv_store", "kv_gather", "paged_decode_attention", "paged_prefill_attention", "varlen_attention", "topp_sample",
 ]

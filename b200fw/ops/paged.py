@@ -158,6 +158,40 @@ def varlen_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, cu_q: to
     return out
 
 
+def paged_prefill_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_tables: torch.Tensor,
+                            cu_q: torch.Tensor, cu_k: torch.Tensor, max_q: int, Hq: int,
+                            scale: Optional[float] = None, k_scale: Optional[torch.Tensor] = None,
+                            v_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal attention of prefill chunks straight over the paged cache: sequence ``b`` owns query rows
+    ``cu_q[b]:cu_q[b+1]``; its keys / values are the first ``cu_k[b+1] - cu_k[b]`` tokens of the cache blocks
+    ``block_tables[b]`` (the chunk's own K / V already stored), its queries the last positions of them.  The kernel's
+    TMA producer walks the block table, so the context is never gathered into a contiguous buffer (the reference
+    hands ``block_table=`` to ``flash_attn_varlen_func``: src/inference/attention.py:248-257).  bf16 caches only;
+    an fp8 cache is dequantised by :func:`kv_gather` and goes through :func:`varlen_attention`."""
+    nblk, bs, Hkv, D = k_cache.shape
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    B = cu_q.numel() - 1
+    if not q.is_cuda or k_cache.dtype == torch.uint8:
+        ck = cu_k.tolist()
+        slots = []
+        for b in range(B):
+            pos = torch.arange(ck[b + 1] - ck[b])
+            slots.append((block_tables[b, pos // bs].long() * bs + pos % bs).to(torch.int32))
+        slot = torch.cat(slots).to(q.device)
+        K, V = kv_gather(k_cache, v_cache, slot, q.dtype if q.is_cuda else torch.float32, k_scale, v_scale)
+        return varlen_attention(q, K.to(q.dtype), V.to(q.dtype), cu_q, cu_k, max_q, Hq, Hkv, scale)
+    assert D == 128 and bs == 16 and k_cache.is_contiguous() and v_cache.is_contiguous()
+    assert block_tables.dtype == torch.int32 and block_tables.is_contiguous()
+    q = q.contiguous()
+    out = torch.empty_like(q)
+    nv.check(nv.lib().b2_attn_fwd_paged(nv.ptr(q), nv.ptr(k_cache), nv.ptr(v_cache), nv.ptr(out), nv.ptr(None), B, Hq,
+                                        Hkv, D, nblk, nv.ctypes.c_float(scale), nv.ptr(cu_q), nv.ptr(cu_k),
+                                        nv.ptr(block_tables), block_tables.shape[1], int(max_q), q.shape[0],
+                                        nv.stream_ptr()), "attn_fwd_paged")
+    nv.count_launch()
+    return out
+
+
 # ---- sampling ------------------------------------------------------------------------------------------
 def topp_sample(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Tensor, uniform: torch.Tensor,
                 return_logprob: bool = False):

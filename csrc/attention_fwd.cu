@@ -29,13 +29,18 @@ struct AttnFwdSmem {
 
 // One work item: a 128-row query tile of one (batch, q head).
 struct FwdItem {
-  int head, kvh, qt, q_len, kv_len, kv_off, k_begin, row0, n_kv;
+  int head, kvh, qt, q_len, kv_len, kv_off, k_begin, row0, n_kv, batch;
   bool active;
 };
 struct FwdParams {
   int S, Hq, Hkv, B, max_tiles, total_q;
   const int* cu_q;
   const int* cu_k;
+  // Paged keys / values (chunked prefill straight out of the KV cache): block_tables[b][i] is the cache block
+  // that holds keys 16 i .. 16 i + 15 of sequence b; the K / V tensor maps then describe the cache as a
+  // [blocks * 16, Hkv * 128] matrix with 16-row boxes, and cu_k only carries the key counts.
+  const int* block_tables;
+  int max_blocks;
 };
 // Fixed-length mode (cu_q == nullptr): every sequence has S query and S key tokens.  Variable
 // length mode: sequence b owns query rows cu_q[b]..cu_q[b+1] and key rows cu_k[b]..cu_k[b+1]; its
@@ -47,6 +52,7 @@ __device__ __forceinline__ FwdItem fwd_item(int w, const FwdParams& p) {
   const int x = w / (p.Hq * p.B);   // tile rank counted from the last (heaviest) tile
   it.head = hb % p.Hq;
   const int batch = hb / p.Hq;
+  it.batch = batch;
   const int q_begin = p.cu_q ? p.cu_q[batch] : batch * p.S;
   it.q_len = p.cu_q ? p.cu_q[batch + 1] - q_begin : p.S;
   it.k_begin = p.cu_k ? p.cu_k[batch] : batch * p.S;
@@ -161,11 +167,35 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           const int krow = item.k_begin + j * 128;
           if (!mbar_wait(&k_empty[st], ph ^ 1, status, ERR_ATTN_WAIT)) { ok = false; break; }
           uint8_t* sK = smem + AttnFwdSmem::K + st * AT_TILE_BYTES;
+          uint8_t* sV = smem + AttnFwdSmem::V + st * AT_TILE_BYTES;
+          if (prm.block_tables != nullptr) {
+            // a 128-key tile is eight 16-token pages: each lands as a [16 x 64] box at its row offset of the
+            // swizzled tile (16 rows x 128 B = 2 KiB, a whole number of swizzle atoms).  Pages past the end of the
+            // sequence repeat its last page: those keys are masked, the bytes only have to be finite.
+            const int* tbl = prm.block_tables + static_cast<size_t>(item.batch) * prm.max_blocks;
+            const int last_page = (item.kv_len - 1) / 16;
+            int rows[8];
+#pragma unroll
+            for (int pg = 0; pg < 8; ++pg) rows[pg] = tbl[min(j * 8 + pg, last_page)] * 16;
+            mbar_expect_tx(&k_full[st], AT_TILE_BYTES);
+#pragma unroll
+            for (int pg = 0; pg < 8; ++pg) {
+              tma_load_2d(sK + pg * 2048, &tmK, &k_full[st], item.kvh * 128, rows[pg]);
+              tma_load_2d(sK + AT_HALF_BYTES + pg * 2048, &tmK, &k_full[st], item.kvh * 128 + 64, rows[pg]);
+            }
+            if (!mbar_wait(&v_empty[st], ph ^ 1, status, ERR_ATTN_WAIT)) { ok = false; break; }
+            mbar_expect_tx(&v_full[st], AT_TILE_BYTES);
+#pragma unroll
+            for (int pg = 0; pg < 8; ++pg) {
+              tma_load_2d(sV + pg * 2048, &tmV, &v_full[st], item.kvh * 128, rows[pg]);
+              tma_load_2d(sV + AT_HALF_BYTES + pg * 2048, &tmV, &v_full[st], item.kvh * 128 + 64, rows[pg]);
+            }
+            continue;
+          }
           mbar_expect_tx(&k_full[st], AT_TILE_BYTES);
           tma_load_2d(sK, &tmK, &k_full[st], item.kvh * 128, krow);
           tma_load_2d(sK + AT_HALF_BYTES, &tmK, &k_full[st], item.kvh * 128 + 64, krow);
           if (!mbar_wait(&v_empty[st], ph ^ 1, status, ERR_ATTN_WAIT)) { ok = false; break; }
-          uint8_t* sV = smem + AttnFwdSmem::V + st * AT_TILE_BYTES;
           mbar_expect_tx(&v_full[st], AT_TILE_BYTES);
           tma_load_2d(sV, &tmV, &v_full[st], item.kvh * 128, krow);
           tma_load_2d(sV + AT_HALF_BYTES, &tmV, &v_full[st], item.kvh * 128 + 64, krow);
@@ -445,6 +475,7 @@ B2_EXPORT int b2_attn_fwd_varlen(const void* q, const void* k, const void* v, vo
   FwdParams prm;
   prm.S = S; prm.Hq = Hq; prm.Hkv = Hkv; prm.B = B; prm.max_tiles = (max_q + 127) / 128; prm.total_q = total_q;
   prm.cu_q = cu_q; prm.cu_k = cu_k;
+  prm.block_tables = nullptr; prm.max_blocks = 0;
   const long long n_items = static_cast<long long>(prm.max_tiles) * Hq * B;
   const int grid = n_items < num_sms() ? static_cast<int>(n_items) : num_sms();
   attn_fwd_kernel<<<grid, AT_THREADS, AttnFwdSmem::TOTAL, stream>>>(
@@ -452,6 +483,55 @@ B2_EXPORT int b2_attn_fwd_varlen(const void* q, const void* k, const void* v, vo
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_error("attn_fwd launch failed: %s", cudaGetErrorString(e));
+    return 4;
+  }
+  return 0;
+}
+
+// Chunked prefill over the paged KV cache: the keys / values of sequence b are the first kv_len[b] tokens of the
+// cache blocks block_tables[b][*] (16 tokens per block, bf16, layout [blocks, 16, Hkv, 128]); its queries are the last
+// q_len[b] of them (the chunk's own K / V must already be stored).  cu_q / cu_k: int32 [B+1] prefix sums of the query
+// and key counts.  No gather of the context into a contiguous buffer: the TMA producer walks the block table.
+B2_EXPORT int b2_attn_fwd_paged(const void* q, const void* k_cache, const void* v_cache, void* out, float* lse, int B,
+                                int Hq, int Hkv, int head_dim, int num_blocks, float scale, const int* cu_q,
+                                const int* cu_k, const int* block_tables, int max_blocks, int max_q, int total_q,
+                                void* stream_) {
+  b2::ensure_thread_context();
+  if (head_dim != 128 || Hq % Hkv != 0 || block_tables == nullptr || cu_q == nullptr || cu_k == nullptr || max_blocks <= 0) {
+    set_error("attn_fwd_paged: head_dim 128, Hq %% Hkv == 0, block tables and prefix sums required");
+    return 10;
+  }
+  if (B <= 0 || max_q <= 0 || total_q <= 0) return 0;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  static bool configured[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!configured[dev]) {
+    if (cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             AttnFwdSmem::TOTAL) != cudaSuccess) {
+      set_error("attn_fwd_paged: cannot set shared memory size");
+      return 1;
+    }
+    configured[dev] = true;
+  }
+  const uint64_t W = static_cast<uint64_t>(Hkv) * 128;
+  const CUtensorMap* tq = tensor_map_2d_bf16(q, total_q, static_cast<uint64_t>(Hq) * 128, static_cast<uint64_t>(Hq) * 128, 128, 64);
+  const CUtensorMap* tk = tensor_map_2d_bf16(k_cache, static_cast<uint64_t>(num_blocks) * 16, W, W, 16, 64);
+  const CUtensorMap* tv = tensor_map_2d_bf16(v_cache, static_cast<uint64_t>(num_blocks) * 16, W, W, 16, 64);
+  if (!tq || !tk || !tv) return 2;
+  int* status = status_ptr();
+  if (!status) return 3;
+  FwdParams prm;
+  prm.S = 0; prm.Hq = Hq; prm.Hkv = Hkv; prm.B = B; prm.max_tiles = (max_q + 127) / 128; prm.total_q = total_q;
+  prm.cu_q = cu_q; prm.cu_k = cu_k;
+  prm.block_tables = block_tables; prm.max_blocks = max_blocks;
+  const long long n_items = static_cast<long long>(prm.max_tiles) * Hq * B;
+  const int grid = n_items < num_sms() ? static_cast<int>(n_items) : num_sms();
+  attn_fwd_kernel<<<grid, AT_THREADS, AttnFwdSmem::TOTAL, stream>>>(
+      *tq, *tk, *tv, static_cast<__nv_bfloat16*>(out), lse, prm, scale, status);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("attn_fwd_paged launch failed: %s", cudaGetErrorString(e));
     return 4;
   }
   return 0;

@@ -86,6 +86,35 @@ def test_varlen_attention_with_context_offset(lens):
     assert relerr(out, ref) < 2e-2
 
 
+@pytest.mark.parametrize("Hq,Hkv", [(4, 2), (8, 1)])
+@pytest.mark.parametrize("lens", [[(16, 300), (3, 131), (77, 77)], [(1, 300)], [(128, 256), (200, 200)]])
+def test_paged_prefill_attention_reads_the_block_table(lens, Hq, Hkv):
+    """Chunk queries against keys / values read in place from the paged cache (TMA producer walks the block table),
+    compared with the fp32 oracle on gathered keys: (q_len, kv_len) per sequence, queries are the last positions."""
+    from b200fw.ops import paged_prefill_attention
+    k, v, kc, vc, _, _, perm = _fill_cache(False, Hkv=Hkv)
+    D = 128
+    B = len(lens)
+    cq, ck = [0], [0]
+    for a, b in lens:
+        cq.append(cq[-1] + a)
+        ck.append(ck[-1] + b)
+    width = max((b + 15) // 16 for _, b in lens)
+    bt = torch.zeros((B, width), dtype=torch.int32)
+    for i, (_, b) in enumerate(lens):
+        nb = (b + 15) // 16
+        # every sequence reads the same stored keys, through its own (rotated) view of the block list where it can
+        bt[i, :nb] = torch.tensor(perm[:nb])
+    torch.manual_seed(3)
+    q = torch.randn(cq[-1], Hq * D, device=DEV, dtype=torch.bfloat16)
+    cu_q = torch.tensor(cq, dtype=torch.int32)
+    cu_k = torch.tensor(ck, dtype=torch.int32)
+    max_q = max(a for a, _ in lens)
+    out = paged_prefill_attention(q, kc, vc, bt.to(DEV), cu_q.to(DEV), cu_k.to(DEV), max_q, Hq)
+    ref = paged_prefill_attention(q.cpu().float(), kc.cpu().float(), vc.cpu().float(), bt, cu_q, cu_k, max_q, Hq)
+    assert relerr(out, ref) < 2e-2
+
+
 def test_topp_sampler_distribution_and_greedy():
     from b200fw.ops import topp_sample
     torch.manual_seed(2)
