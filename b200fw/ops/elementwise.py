@@ -10,7 +10,7 @@ from typing import Tuple
 import torch
 
 from .. import _native as nv
-from .gemm import grad_into_main
+from .gemm import NO_GRAD_CTX, grad_into_main, no_grad_needed
 
 _rope_cache = {}
 
@@ -64,6 +64,8 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float = 1e-6) -> torch.Tensor
     if not x.is_cuda:
         xf = x.float()
         return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * w.float()).to(x.dtype)
+    if no_grad_needed(x, w):
+        return _RMSNorm.forward(NO_GRAD_CTX, x.contiguous(), w, eps)
     return _RMSNorm.apply(x.contiguous(), w, eps)
 
 
@@ -143,6 +145,9 @@ def qknorm_rope(qkv: torch.Tensor, qw: torch.Tensor, kw: torch.Tensor, pos: torc
         kn = _rope_ref(hn(k, kw, Hkv), pos.long(), cos, sin).reshape(M, Hkv * D).to(qkv.dtype)
         return qn, kn, v
     assert head_dim == 128, "CUDA qknorm_rope kernel is specialised for head_dim 128"
+    if no_grad_needed(qkv, qw, kw):
+        return _QKNormRope.forward(NO_GRAD_CTX, qkv, qw, kw, pos if pos.dtype == torch.int32 else pos.to(torch.int32),
+                                   cos, sin, Hq, Hkv, eps)
     return _QKNormRope.apply(qkv, qw, kw, pos.to(torch.int32), cos, sin, Hq, Hkv, eps)
 
 
@@ -174,6 +179,8 @@ def swiglu(gu: torch.Tensor) -> torch.Tensor:
     if not gu.is_cuda:
         g, u = gu.chunk(2, dim=-1)
         return (torch.nn.functional.silu(g.float()) * u.float()).to(gu.dtype)
+    if no_grad_needed(gu):
+        return _SwiGLU.forward(NO_GRAD_CTX, gu.contiguous())
     return _SwiGLU.apply(gu.contiguous())
 
 
@@ -219,4 +226,6 @@ def embedding(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
     ids = ids.reshape(-1)
     if not table.is_cuda:
         return torch.nn.functional.embedding(ids, table)
+    if no_grad_needed(table):
+        return _Embedding.forward(NO_GRAD_CTX, ids.long().contiguous(), table)
     return _Embedding.apply(ids.long().contiguous(), table)

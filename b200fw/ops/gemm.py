@@ -58,6 +58,30 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     return out
 
 
+class _NoGradCtx:
+    """Stand-in for an autograd context when nothing will be differentiated (inference, evaluation): the ops call
+    their ``forward`` with it directly and skip ``Function.apply``, whose bookkeeping costs several microseconds per
+    call: a decode step issues about 300 such calls."""
+
+    needs_input_grad = (False,) * 16
+
+    def save_for_backward(self, *tensors):
+        pass
+
+    def __setattr__(self, name, value):      # forward() may park tensors on its context: keep none of them alive
+        pass
+
+
+NO_GRAD_CTX = _NoGradCtx()
+
+
+def no_grad_needed(*tensors) -> bool:
+    """True when autograd records nothing for an op over ``tensors``."""
+    if not torch.is_grad_enabled():
+        return True
+    return not any(t is not None and t.requires_grad for t in tensors)
+
+
 def grad_into_main(param: torch.Tensor, compute) -> Optional[torch.Tensor]:
     """Gradient-accumulation fusion.
 
@@ -100,4 +124,6 @@ def linear(x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = 
     if not x.is_cuda:
         y = torch.nn.functional.linear(x, w.to(x.dtype))
         return y if residual is None else y + residual
+    if no_grad_needed(x, w, residual):
+        return gemm(x, w, residual=residual)
     return _Linear.apply(x, w, residual)

@@ -875,8 +875,8 @@ class _LoRAWorker:
     The engine holds plain merged weights ``W_base + s * B A``.  A sync does not re-export the model: for every
     adapted projection one low-rank GEMM updates the engine's weight rows in place,
 
-    * delta:  ``W += [s B_new | -s B_old] @ [A_new ; A_old]``   (contraction length 2r, accumulate epilogue), where
-      ``new = old + delta`` and ``old`` is this worker's record of what the engine currently carries;
+    * delta:  ``W += (s B_new) A_new + (-s B_old) A_old``   (two GEMMs of contraction length r, accumulate epilogue),
+      where ``new = old + delta`` and ``old`` is this worker's record of what the engine currently carries;
     * full:   ``W  = W_base + s B_new A_new``                    (the trainer's frozen base rows as the residual
       operand), which also wipes the bf16 rounding the in-place deltas have accumulated.
 
@@ -887,6 +887,7 @@ class _LoRAWorker:
     def __init__(self, orch: ColocateOrchestrator):
         self.orch = orch
         self.applied: Optional[Dict[str, torch.Tensor]] = None      # adapter state the engine's weights carry
+        self._plan = None
 
     def _engine_rows(self, mod_name: str, tgt: str, mod):
         """The engine model's weight rows that projection ``tgt`` of trainer module ``mod_name`` maps to."""
@@ -900,10 +901,31 @@ class _LoRAWorker:
         s0, e0 = mod.ranges[tgt]
         return w[s0:e0], mod.base.weight[s0:e0]
 
+    def _build_plan(self, eng):
+        """One flat fp32 image of all adapter tensors (A and B of every adapted projection, in a fixed order) with a
+        scale vector (1 on A entries, alpha/r on B entries), so that a sync is a handful of bulk tensor ops plus one
+        or two GEMM launches per projection instead of half a dozen small tensor ops per adapter."""
+        from ..model.lora import iter_lora
+        keys, shapes, offs, scale, jobs, n = [], [], [], [], [], 0
+        for name, tgt, mod, ad in iter_lora(eng.model):
+            w_rows, base_rows = self._engine_rows(name, tgt, mod)
+            ent = {}
+            for leaf, t, sc in (("lora_A", ad.lora_A, 1.0), ("lora_B", ad.lora_B, float(ad.scaling))):
+                keys.append(f"{name}.{tgt}.{leaf}")
+                shapes.append(tuple(t.shape))
+                offs.append(n)
+                ent[leaf] = (n, tuple(t.shape))
+                scale.append(torch.full((t.numel(),), sc, dtype=torch.float32))
+                n += t.numel()
+            jobs.append((ent["lora_A"], ent["lora_B"], w_rows, base_rows))
+        dev = eng.device
+        self._plan = {"keys": keys, "shapes": shapes, "offs": offs, "numel": n, "jobs": jobs,
+                      "scale": torch.cat(scale).to(dev), "flat": torch.zeros(n, dtype=torch.float32, device=dev)}
+        return self._plan
+
     @torch.no_grad()
     def update_weights(self, state, mode: str = "full"):
         from .. import ops
-        from ..model.lora import iter_lora
         orch = self.orch
         eng = orch.train_engine
         if eng.parallel_ctx.tp_size > 1 or eng.device.type != "cuda":
@@ -911,24 +933,29 @@ class _LoRAWorker:
             from ..model.hf_io import hf_named_tensors
             orch.infer_engine.load_weights(dict(hf_named_tensors(merged)))
             return
+        plan = self._plan or self._build_plan(eng)
         dev, dt = eng.device, eng.dtype
-        if mode == "delta" and self.applied is not None:
-            new = {k: self.applied[k] + state[k].to(dev, torch.float32) for k in self.applied if k in state}
-            for k, v in self.applied.items():
-                new.setdefault(k, v)
-        else:
-            mode = "full"
-            new = {k: v.detach().to(dev, torch.float32).clone() for k, v in state.items()}
-        for name, tgt, mod, ad in iter_lora(eng.model):
-            ka, kb = f"{name}.{tgt}.lora_A", f"{name}.{tgt}.lora_B"
-            if ka not in new or kb not in new:
-                continue
-            w_rows, base_rows = self._engine_rows(name, tgt, mod)
-            if mode == "full":
-                ops.gemm((new[kb] * ad.scaling).to(dt), new[ka].to(dt), b_mn=True, out=w_rows, residual=base_rows)
+        if any(k not in state for k in plan["keys"]):
+            raise KeyError("SwiftSync payload does not cover every adapter tensor of the model")
+        incoming = torch.cat([state[k].reshape(-1).to(dev, torch.float32) for k in plan["keys"]])
+        old = plan["flat"]
+        delta = mode == "delta" and self.applied is not None
+        new = old + incoming if delta else incoming
+        new_bf = (new * plan["scale"]).to(dt)                 # A_new and s * B_new, all adapters at once
+        old_neg = (old * (-plan["scale"])).to(dt) if delta else None    # its B entries: -s * B_old
+        old_pos = old.to(dt) if delta else None                         # its A entries: A_old
+
+        def view(buf, ent):
+            off, shape = ent
+            return buf[off:off + shape[0] * shape[1]].view(shape)
+
+        for a_ent, b_ent, w_rows, base_rows in plan["jobs"]:
+            if delta:
+                # W += (s B_new) A_new + (-s B_old) A_old: two accumulate GEMMs with contraction length r
+                ops.gemm(view(new_bf, b_ent), view(new_bf, a_ent), b_mn=True, out=w_rows, accumulate=True)
+                ops.gemm(view(old_neg, b_ent), view(old_pos, a_ent), b_mn=True, out=w_rows, accumulate=True)
             else:
-                b_cat = torch.cat([new[kb] * ad.scaling, self.applied[kb] * (-ad.scaling)], 1).to(dt)
-                a_cat = torch.cat([new[ka], self.applied[ka]], 0).to(dt)
-                ops.gemm(b_cat, a_cat, b_mn=True, out=w_rows, accumulate=True)
-        self.applied = new
+                ops.gemm(view(new_bf, b_ent), view(new_bf, a_ent), b_mn=True, out=w_rows, residual=base_rows)
+        plan["flat"] = new
+        self.applied = {k: view(new, (o, sh)) for k, o, sh in zip(plan["keys"], plan["offs"], plan["shapes"])}
         orch.infer_engine.on_weights_updated()

@@ -75,6 +75,8 @@ def _zero_worker(rank, world, backend, stage):
     import os
     if backend == "p2p" and os.environ.get("B200FW_NVLS") == "0":
         assert not eng.optimizer.nvls
+    if backend == "p2p" and os.environ.get("B200FW_ZERO_NVLS") == "1" and eng.optimizer.buckets[0].symm_grad.mc_ptr:
+        assert eng.optimizer.nvls
     out = []
     for s in range(6):
         g = torch.Generator().manual_seed(s * 31 + rank)
@@ -96,7 +98,9 @@ def test_zero_p2p_matches_nccl(stage, nvls):
     from _gpu_dist_util import run_gpu_ranks
     w = _world()
     a = run_gpu_ranks(_zero_worker, w, "nccl", stage)
-    b = run_gpu_ranks(_zero_worker, w, "p2p", stage, env={"B200FW_NVLS": nvls})
+    # B200FW_ZERO_NVLS forces the multimem reduce / publish kernels on (or off) whatever the rank count: the automatic
+    # choice keeps them for more than two ranks
+    b = run_gpu_ranks(_zero_worker, w, "p2p", stage, env={"B200FW_NVLS": nvls, "B200FW_ZERO_NVLS": nvls})
     for r in range(w):
         assert a[r][1] == a[0][1] and b[r][1] == b[0][1]            # ranks hold identical weights
         for i, ((la, ga), (lb, gb)) in enumerate(zip(a[r][0], b[r][0])):
