@@ -26,6 +26,11 @@ from ..dist.symm import FlagBarrier, SymmetricBuffer
 from .gemm import gemm, grad_into_main
 
 
+import os as _os
+
+_AG_NVLS = _os.environ.get("B200FW_AG_NVLS", "auto")     # "1" / "0" force multimem stores on / off in all-gather -> GEMM
+
+
 class _RSState:
     def __init__(self, group, rows, N, bn, device):
         self.world = dist.get_world_size(group)
@@ -135,9 +140,12 @@ def allgather_gemm(x_shard: torch.Tensor, w: torch.Tensor, group, *, b_mn: bool 
     buf, flags = st.buf[par], st.flags[par]
     y = torch.empty((M, N), device=x_shard.device, dtype=torch.bfloat16)
     bn = _bn_for(M, N)
+    # one multimem.st per 16 bytes reaches every rank; with two ranks there is nothing to save and plain stores
+    # measured faster (F1 0.246 vs 0.322 ms), with four the switch wins on the long GEMM (F2 0.809 vs 0.873 ms)
+    mc = buf.mc_ptr if (ctx.world > 2 or _AG_NVLS == "1") and _AG_NVLS != "0" else 0
     nv.check(nv.lib().b2_gemm_bf16_comm(
         2, nv.ptr(x_shard), nv.ptr(w), nv.ptr(y), M, N, K, w.stride(0), int(b_mn), bn, None, None, nv.ptr(None),
-        nv.ptr(None), buf.ptr_array, nv.ctypes.c_void_p(buf.mc_ptr), flags.ptr_array, ctx.ag_ready.ptr_array,
+        nv.ptr(None), buf.ptr_array, nv.ctypes.c_void_p(mc), flags.ptr_array, ctx.ag_ready.ptr_array,
         ctx.ag_calls, ctx.world, ctx.rank, rows, st.uses[par], nv.stream_ptr()), "allgather_gemm")
     nv.count_launch()
     gathered = buf.tensor.view(M, K)

@@ -237,12 +237,13 @@ class ZeROOptimizer:
         self.flags = FlagBarrier(self.dp_group, self.device, channels=max(8, nb + 3))
         self._ch_step_end, self._ch_norm, self._ch_spare = nb, nb + 1, nb + 2
         self._norm_ar = NormAllReduce(self.flags, self.dp_group, self._ch_norm, self.device)
-        # through the switch (multimem.ld_reduce / multimem.st) one instruction stands for `world` peer accesses; with two
-        # ranks there is nothing to save and the plain peer loads measured faster (0.95 vs 1.83 ms for a 1.2 GB bucket)
+        # Through the switch (multimem.ld_reduce / multimem.st) one instruction stands for `world` peer accesses, but the
+        # plain peer loads / stores measured faster for these streaming kernels (1.2 GB bucket set: reduce 0.95 vs 1.79 ms
+        # at 2 ranks, 1.40 vs 1.71 ms at 4; AdamW + publish 1.43 vs 1.80 ms at 4), so multimem is opt-in here
+        # (B200FW_ZERO_NVLS=1).
         import os
-        want = os.environ.get("B200FW_ZERO_NVLS", "auto")
-        self.nvls = (all(b.symm_grad.mc_ptr and b.symm_param.mc_ptr for b in self.buckets)
-                     and (want == "1" or (want == "auto" and self.world > 2)))
+        self.nvls = (os.environ.get("B200FW_ZERO_NVLS", "0") == "1"
+                     and all(b.symm_grad.mc_ptr and b.symm_param.mc_ptr for b in self.buckets))
 
     def _p2p_reduce_bucket(self, b: _Bucket, idx: int):
         """Runs on the current stream: wait (bounded, on the device) until every rank has finished writing bucket
