@@ -154,11 +154,11 @@ def allgather_gemm(x_shard: torch.Tensor, w: torch.Tensor, group, *, b_mn: bool 
     return y, gathered
 
 
-# GEMM -> reduce-scatter pays off when the GEMM is long enough to hide the peer stores and the owner's
-# reduction: measured on 8 GPUs at 16384 tokens x 5120 outputs, K = 3200 runs 1.16x faster fused, K = 1024
-# runs 0.78x (the reduce phase and the NVLink stores are exposed behind a 0.12 ms GEMM).  Below this
-# contraction length the product path is the plain GEMM followed by NCCL's reduce-scatter.
-FUSED_RS_MIN_K = 2048
+# Every contraction length takes the fused kernel: with reductions on their own warps, row blocks scheduled so that
+# they complete progressively, and one cumulative release per tile, the short-K case (o_proj, K = 1024 per rank at
+# TP8: the GEMM is 0.12 ms, the wire 0.11-0.19 ms) runs 0.28 / 0.30 ms at 2 / 4 GPUs against 0.39 / 0.40 ms for the
+# plain GEMM followed by NCCL's reduce-scatter.  The threshold stays as a knob (contractions shorter than it use NCCL).
+FUSED_RS_MIN_K = 0
 
 
 def _reduce_scatter_gemm(x: torch.Tensor, w: torch.Tensor, group, *, b_mn: bool = False,

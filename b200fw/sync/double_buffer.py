@@ -34,6 +34,10 @@ class DoubleBufferedLoRA:
         """``shadow[k] += delta[k]`` in place (unknown keys start from zero).  Returns the count applied."""
         n = 0
         with self._lock:
+            if delta and all(k in self.shadow and self.shadow[k].shape == d.shape and self.shadow[k].dtype == d.dtype
+                             and self.shadow[k].device == d.device for k, d in delta.items()):
+                torch._foreach_add_([self.shadow[k] for k in delta], [d.detach() for d in delta.values()])
+                return len(delta)
             for k, d in delta.items():
                 cur = self.shadow.get(k)
                 if cur is None:
@@ -63,6 +67,13 @@ class DoubleBufferedLoRA:
         with self._lock:
             self.active, self.shadow = self.shadow, self.active
             # level the new shadow with the new active
+            if self.active and list(self.active) == list(self.shadow) and all(
+                    s.shape == v.shape and s.dtype == v.dtype and s.device == v.device
+                    for s, v in zip(self.shadow.values(), self.active.values())):
+                torch._foreach_copy_(list(self.shadow.values()), list(self.active.values()))
+                self.version += 1
+                self.swap_count += 1
+                return self.version
             for k, v in self.active.items():
                 s = self.shadow.get(k)
                 if s is None or s.shape != v.shape:

@@ -148,12 +148,21 @@ class DeltaComputer:
         self._step_count += 1
         if prev is not None:
             return {k: v.detach() - prev[k].to(v.device) if k in prev else v.detach().clone() for k, v in current.items()}
+        keys = list(current)
+        cur = [current[k].detach() for k in keys]
+        if self.prev is not None and list(self.prev) == keys and all(
+                p.shape == c.shape and p.device == c.device and p.dtype == c.dtype
+                for p, c in zip(self.prev.values(), cur)):
+            # same tensors as last time: two multi-tensor launches instead of two small kernels per tensor
+            old = list(self.prev.values())
+            delta = dict(zip(keys, torch._foreach_sub(cur, old)))
+            torch._foreach_copy_(old, cur)                 # the snapshot is updated in place
+            return delta
         if self.prev is None:
-            delta = {k: v.detach().clone() for k, v in current.items()}
+            delta = {k: v.clone() for k, v in zip(keys, cur)}
         else:
-            delta = {k: v.detach() - self.prev[k] if k in self.prev else v.detach().clone()
-                     for k, v in current.items()}
-        self.prev = {k: v.detach().clone() for k, v in current.items()}
+            delta = {k: v - self.prev[k] if k in self.prev else v.clone() for k, v in zip(keys, cur)}
+        self.prev = {k: v.clone() for k, v in zip(keys, cur)}
         return delta
 
     def reset(self):
