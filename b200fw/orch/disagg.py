@@ -272,23 +272,32 @@ class DisaggOrchestrator:
             m = DisaggIterationMetrics(it)
             prompts = self._prompts(it)
             do_rollout = it < cfg.total_iterations
+            # wall-clock spans of this rank's phases (same node: time.time() is comparable across the processes)
+            span_train, span_roll = [float("inf"), float("-inf")], [float("inf"), float("-inf")]
             t0 = time.perf_counter()
+            w0 = time.time()
             local = self._rollout_share(prompts) if (not self.is_trainer and do_rollout) else None
             if not self.is_trainer:
                 m.rollout_time = time.perf_counter() - t0
+                if do_rollout:
+                    span_roll = [w0, time.time()]
             if cfg.mode == "pipeline":
                 if self.is_trainer and prev is not None:
                     t1 = time.perf_counter()
+                    w1 = time.time()
                     m.loss = self._train(*prev)
                     m.train_time = time.perf_counter() - t1
+                    span_train = [w1, time.time()]
                 samples = self._exchange_samples(local)
                 prev = (prompts, samples) if do_rollout else None
             else:
                 samples = self._exchange_samples(local)
                 if self.is_trainer:
                     t1 = time.perf_counter()
+                    w1 = time.time()
                     m.loss = self._train(prompts, samples)
                     m.train_time = time.perf_counter() - t1
+                    span_train = [w1, time.time()]
             m.sync_time = self._sync_weights()
             m.total_time = time.perf_counter() - t_iter
             times = torch.tensor([m.train_time, m.rollout_time], dtype=torch.float64)
@@ -296,10 +305,20 @@ class DisaggOrchestrator:
                 times = times.cuda()
             dist.all_reduce(times, op=dist.ReduceOp.MAX)
             m.train_time, m.rollout_time = float(times[0]), float(times[1])
-            # pipeline mode runs the two phases side by side: the shorter one is hidden entirely; sequential mode
-            # runs them back to back, nothing overlaps
-            hi = max(m.train_time, m.rollout_time)
-            m.overlap_ratio = min(m.train_time, m.rollout_time) / hi if (hi > 0 and cfg.mode == "pipeline") else 0.0
+            # measured overlap: the training phase spans [earliest trainer start, latest trainer end], the rollout
+            # phase likewise; the ratio is the time both were running over the shorter phase (1 = fully hidden)
+            lo = torch.tensor([span_train[0], span_roll[0]], dtype=torch.float64)
+            hi = torch.tensor([span_train[1], span_roll[1]], dtype=torch.float64)
+            if times.is_cuda:
+                lo, hi = lo.cuda(), hi.cuda()
+            dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+            dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+            lo, hi = lo.tolist(), hi.tolist()
+            m.overlap_ratio = 0.0
+            if all(map(lambda v: v not in (float("inf"), float("-inf")), lo + hi)):
+                both = min(hi[0], hi[1]) - max(lo[0], lo[1])
+                shorter = min(hi[0] - lo[0], hi[1] - lo[1])
+                m.overlap_ratio = max(0.0, both) / shorter if shorter > 0 else 0.0
             m.avg_reward = getattr(self, "_last_reward", 0.0)
             m.weights_version = self.weights_version
             self.metrics.append(m)
