@@ -213,7 +213,8 @@ class InferenceEngine:
         inf, self._inflight = self._inflight, None
         if inf is None:
             return
-        inf["event"].synchronize()
+        if inf["event"] is not None:
+            inf["event"].synchronize()
         ids, lps = inf["host_ids"][:len(inf["reqs"])].tolist(), inf["host_lps"][:len(inf["reqs"])].tolist()
         for r, slot, t, lp in zip(inf["reqs"], inf["slots"], ids, lps):
             if slot >= len(r.output_tokens) or r.output_tokens[slot] != self.PLACEHOLDER:
@@ -359,7 +360,9 @@ class InferenceEngine:
                 self._fail(r, e)
         if not live:
             return
-        use_async = (lookahead and cfg.async_decode and self.device.type == "cuda" and self.spec is None)
+        # on a GPU by default; "force" runs the same bookkeeping on the CPU too (tests of the one-step-late logic)
+        use_async = (lookahead and bool(cfg.async_decode) and self.spec is None
+                     and (self.device.type == "cuda" or cfg.async_decode == "force"))
         inf = self._inflight
         last = None
         if inf is not None:
@@ -390,11 +393,14 @@ class InferenceEngine:
             return
         ids_dev, lps_dev = self._sample_device(live, logits[:len(live)])
         n = len(live)
-        host_ids, host_lps = self._pinned_out(n)
-        host_ids[:n].copy_(ids_dev, non_blocking=True)
-        host_lps[:n].copy_(lps_dev, non_blocking=True)
-        ev = torch.cuda.Event()
-        ev.record()
+        if self.device.type == "cuda":
+            host_ids, host_lps = self._pinned_out(n)
+            host_ids[:n].copy_(ids_dev, non_blocking=True)
+            host_lps[:n].copy_(lps_dev, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+        else:
+            host_ids, host_lps, ev = ids_dev, lps_dev, None
         slots = []
         for r in live:
             slots.append(len(r.output_tokens))

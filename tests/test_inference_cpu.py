@@ -214,3 +214,41 @@ def test_requests_with_a_shared_prefix_wait_for_the_first_prefill_and_share_its_
                                           enable_prefix_reuse=False, dtype="float32"), model=m).initialize()
     assert ref.generate(prompts, max_tokens=6, temperature=0.0) == outs
     assert not e._inflight_prefix
+
+
+def test_one_step_late_decode_bookkeeping_on_cpu(model, oracle):
+    """The one-step-late decode path (sampled ids consumed by the next launch before the host has read them) with
+    its bookkeeping forced on the CPU: same tokens as the synchronous engine, EOS cuts, per-request lengths, a
+    weight update in the middle, and nothing unresolved ever leaves the engine."""
+    e = _engine(model, async_decode="force")
+    assert e.generate(PROMPTS, max_tokens=10) == oracle
+    assert e._inflight is None
+    # EOS in the middle of the stream: the token after it (sampled one step ahead) is dropped
+    eos = oracle[0][4]
+    cut = [o[:o.index(eos) + 1] if eos in o else o for o in oracle]
+    for flag in (False, "force"):
+        assert _engine(model, async_decode=flag, eos_token_id=eos).generate(PROMPTS, max_tokens=10) == cut, flag
+    # different lengths: some requests finish by count while others have a launch in flight
+    e2 = _engine(model, async_decode="force")
+    want_len = [3 + 2 * i for i in range(len(PROMPTS))]
+    for i, (p, n) in enumerate(zip(PROMPTS, want_len)):
+        e2.add_request(f"r{i}", p, max_tokens=n)
+    seen = {}
+    while e2.has_pending():
+        for rid, toks in e2.step().items():
+            seen.setdefault(rid, []).extend(toks)
+    for i, n in enumerate(want_len):
+        out = e2.finished[f"r{i}"].output_tokens
+        assert out == oracle[i][:n] and all(t >= 0 for t in out) and seen[f"r{i}"] == out
+    # a weight update between steps settles the launch in flight first; requests go on
+    e3 = _engine(model, async_decode="force")
+    for i, p in enumerate(PROMPTS):
+        e3.add_request(f"q{i}", p, max_tokens=8)
+    for _ in range(6):
+        e3.step()
+    e3.on_weights_updated()
+    assert e3._inflight is None and e3.has_pending()
+    while e3.has_pending():
+        e3.step()
+    assert all(len(e3.finished[f"q{i}"].output_tokens) == 8 and min(e3.finished[f"q{i}"].output_tokens) >= 0
+               for i in range(len(PROMPTS)))
