@@ -234,7 +234,11 @@ class ZeROOptimizer:
         nb = len(self.buckets)
         # channel i: "bucket i's gradients are complete on every rank"; nb: end of step; nb + 1: norm exchange
         # (nb + 2 is spare: nothing in the optimizer uses it)
-        self.flags = FlagBarrier(self.dp_group, self.device, channels=max(8, nb + 3))
+        # a peer may arrive seconds late at a bucket's barrier (graph capture, checkpoint save, logging on one rank):
+        # the bound is a stall detector, not a pipeline timeout (B200FW_PEER_WAIT_MS overrides it)
+        import os
+        self.flags = FlagBarrier(self.dp_group, self.device, channels=max(8, nb + 3),
+                                 limit_ms=int(os.environ.get("B200FW_PEER_WAIT_MS", "30000")))
         self._ch_step_end, self._ch_norm, self._ch_spare = nb, nb + 1, nb + 2
         self._norm_ar = NormAllReduce(self.flags, self.dp_group, self._ch_norm, self.device)
         # Through the switch (multimem.ld_reduce / multimem.st) one instruction stands for `world` peer accesses, but the

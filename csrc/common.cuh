@@ -25,7 +25,10 @@ enum : int {
   ERR_BAD_ARGUMENT = 900,
 };
 
-constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s
+constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s: waits inside one kernel's own pipeline
+// Waits for a flag that ANOTHER GPU writes: a peer may legitimately arrive seconds late (it was capturing a graph,
+// saving a checkpoint, logging), so the bound is what a collective library would call a stall, not a pipeline hiccup.
+constexpr unsigned long long PEER_WAIT_LIMIT_NS = 30000000000ull;  // 30 s
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));

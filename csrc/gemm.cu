@@ -107,7 +107,7 @@ __device__ __forceinline__ bool wait_flag_ge(const int* p, int value, int* statu
       const unsigned long long now = globaltimer_ns();
       if (t0 == 0) t0 = now;
       if (*reinterpret_cast<volatile int*>(status) != 0) return false;
-      if (now - t0 > WAIT_LIMIT_NS) {
+      if (now - t0 > (SYS ? PEER_WAIT_LIMIT_NS : WAIT_LIMIT_NS)) {
         atomicCAS(status, 0, code);
         return false;
       }

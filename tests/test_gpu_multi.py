@@ -129,9 +129,10 @@ def _zero_wait_runs_out_worker(rank, world):
     before = opt.master.clone()
     raised = False
     if rank == 0:
+        keep = opt.flags.limit_ms
         opt.flags.limit_ms = 300
         opt.flags.barrier_dev(opt._ch_spare)             # nobody else signals this channel
-        opt.flags.limit_ms = 2000
+        opt.flags.limit_ms = keep
     try:
         eng.sft_step_tensors(ids, labels)
     except nv.NativeError as e:
