@@ -98,7 +98,8 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
 
 // Bounded wait.  Returns false (and records `code`) after WAIT_LIMIT_NS, or as soon as another
 // role of the same grid has already recorded an error.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int code,
+                                          unsigned long long limit_ns = WAIT_LIMIT_NS) {
 #ifdef B2_MBAR_SPIN
   if (mbar_test_wait(bar, parity)) return true;
 #else
@@ -115,7 +116,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
       unsigned long long now = globaltimer_ns();
       if (t0 == 0) t0 = now;
       if (*reinterpret_cast<volatile int*>(status) != 0) return false;
-      if (now - t0 > WAIT_LIMIT_NS) {
+      if (now - t0 > limit_ns) {
         atomicCAS(status, 0, code);
         return false;
       }

@@ -194,6 +194,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
+  // in the fused kernels every pipeline wait sits downstream of a wait for another GPU: same (long) bound
+  constexpr unsigned long long LIM = COMM != 0 ? PEER_WAIT_LIMIT_NS : WAIT_LIMIT_NS;
 
   const int num_m = (M + GEMM_BM - 1) / GEMM_BM;
   const int num_n = (N + BN - 1) / BN;
@@ -283,7 +285,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const CUtensorMap* mapA = own ? &tmR : &tmA;
         const int a_row = own ? m0 - own0 * GEMM_BM : m0;
         for (int kb = kb_begin; kb < kb_end; ++kb) {
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1, status, ERR_GEMM_PRODUCER_WAIT)) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, status, ERR_GEMM_PRODUCER_WAIT, LIM)) {
             ok = false;
             break;
           }
@@ -322,11 +324,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       for (int u = blockIdx.x; u < num_units && ok; u += gridDim.x) {
         const int ks = u / num_tiles;
         const int kb_begin = ks * num_kb / split_k, kb_end = (ks + 1) * num_kb / split_k;
-        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, status, ERR_GEMM_MMA_WAIT_TMEM)) break;
+        if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, status, ERR_GEMM_MMA_WAIT_TMEM, LIM)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = kb_begin; kb < kb_end; ++kb) {
-          if (!mbar_wait(&full_bar[stage], phase, status, ERR_GEMM_MMA_WAIT_FULL)) {
+          if (!mbar_wait(&full_bar[stage], phase, status, ERR_GEMM_MMA_WAIT_FULL, LIM)) {
             ok = false;
             break;
           }
@@ -451,9 +453,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int row = m_blk * GEMM_BM + quarter * 32 + lane;
       if (COMM == 1) {
         // leave together: the epilogue threads meet at named barriers further down
-        const bool got = mbar_wait(&tmem_full[acc], acc_phase, status, ERR_GEMM_EPI_WAIT);
+        const bool got = mbar_wait(&tmem_full[acc], acc_phase, status, ERR_GEMM_EPI_WAIT, LIM);
         if (named_barrier_or(1, 128, !got)) break;
-      } else if (!mbar_wait(&tmem_full[acc], acc_phase, status, ERR_GEMM_EPI_WAIT)) {
+      } else if (!mbar_wait(&tmem_full[acc], acc_phase, status, ERR_GEMM_EPI_WAIT, LIM)) {
         break;
       }
       tc_fence_after();
