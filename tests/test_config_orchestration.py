@@ -547,3 +547,35 @@ def test_missing_rank_is_detected_by_bounded_wait():
     from _dist_util import run_ranks
     res = run_ranks(_dead_rank_worker, 2)
     assert res[1] == "left" and res[0].startswith("detected")
+
+
+def test_ray_object_store_transfer_against_a_stand_in_ray(monkeypatch):
+    """The object-store backend (CPU copy -> ray.put / ray.get) with a stand-in ``ray`` module: publish bumps the
+    version, fetch returns the tensors on the requested device, the manager routes both ends."""
+    import sys
+    import types
+    from b200fw.sync.nccl_transfer import RayObjectStoreTransfer, WeightTransferManager
+    store = {}
+
+    def put(obj):
+        ref = f"ref{len(store)}"
+        store[ref] = obj
+        return ref
+
+    monkeypatch.setitem(sys.modules, "ray", types.SimpleNamespace(put=put, get=lambda ref: store[ref]))
+    t = RayObjectStoreTransfer()
+    assert t.available
+    state = {"w": torch.arange(6.0).reshape(2, 3), "b": torch.ones(4)}
+    ref = t.publish_weights(state)
+    assert ref in store and t.version == 1
+    got = t.fetch_weights(device="cpu")
+    assert torch.equal(got["w"], state["w"]) and got["w"] is not state["w"]
+    loaded = {}
+
+    class Eng:
+        def load_weights(self, s):
+            loaded.update(s)
+
+    m = WeightTransferManager("ray_object_store")
+    assert m.sync_weights(True, state) == 1
+    assert m.sync_weights(False, engine=Eng()) == 2 and torch.equal(loaded["b"], state["b"])

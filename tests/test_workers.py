@@ -131,3 +131,25 @@ def test_trainer_to_rollout_weight_flow_full_and_delta():
     assert torch.equal(merged[-1]["a"], torch.full((2,), 1.5)) and iw2.get_status()["lora_buffer_version"] >= 1
     assert iw2.update_weights({"a": torch.ones(3)}, mode="delta") is False                  # wrong shape: rejected
     assert iw2.get_status()["weight_version"] == 2
+
+
+def test_worker_classes_become_ray_actors_when_ray_is_importable(monkeypatch):
+    """``get_train_worker_class`` / ``get_infer_worker_class`` wrap the plain classes with ``ray.remote(num_gpus=n)``
+    when Ray imports (src/engines/train_worker.py:26-31, infer_worker.py:31-36); checked with a stand-in module."""
+    import sys
+    import types
+    from b200fw.orch.workers import get_infer_worker_class, get_train_worker_class
+    seen = []
+
+    def remote(num_gpus=0):
+        def wrap(cls):
+            seen.append((cls.__name__, num_gpus))
+            return types.SimpleNamespace(remote=lambda *a, **k: cls(*a, **k), cls=cls)
+        return wrap
+
+    monkeypatch.setitem(sys.modules, "ray", types.SimpleNamespace(remote=remote))
+    tw, iw = get_train_worker_class(2), get_infer_worker_class(1)
+    assert seen == [("TrainWorker", 2), ("InferWorker", 1)]
+    w = iw.remote(backend="mock")
+    assert w.initialize() and w.get_status()["backend"] == "mock"
+    monkeypatch.delitem(sys.modules, "ray")
