@@ -451,19 +451,22 @@ class InferenceEngine:
                         "positions": torch.zeros(n, dtype=torch.int32, device=self.device),
                         "block_tables": torch.full((n, width), -1, dtype=torch.int32, device=self.device),
                         "context_lens": torch.zeros(n, dtype=torch.int32, device=self.device),
-                        "segments": torch.tensor([[-1, 0, 0, 0]] * n, dtype=torch.int32, device=self.device)}
+                        "segments": torch.tensor([[-1, 0, 0, 0]] * n, dtype=torch.int32, device=self.device),
+                        "slots": torch.full((n,), -1, dtype=torch.int32, device=self.device)}
 
             def fn(inp):
                 from .context import InferenceContext
                 c = InferenceContext(False, inp["tokens"].shape[0], inp["block_tables"], inp["context_lens"],
-                                     width * self.config.block_size, inp["segments"], positions=inp["positions"])
+                                     width * self.config.block_size, inp["segments"], positions=inp["positions"],
+                                     slot_mapping=inp["slots"])
                 return self.runner.forward(inp["tokens"], c, split_plan=plan)
             gr.capture(size, make, fn)
         tokens = torch.zeros(size, dtype=torch.long, device=self.device)
         tokens[:len(live)] = last
         self.stats["graph_replays"] += 1
         return gr.replay(size, {"tokens": tokens, "positions": ctx.positions, "block_tables": ctx.block_tables,
-                                "context_lens": ctx.context_lens, "segments": ctx.store_segments})
+                                "context_lens": ctx.context_lens, "segments": ctx.store_segments,
+                                "slots": ctx.slot_mapping})
 
     def _graph_table_width(self) -> int:
         """Block-table width the graphs are captured for (grows in powers of two with the longest

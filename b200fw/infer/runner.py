@@ -54,6 +54,7 @@ class ModelRunner:
         self.partition_size, self.enable_partitioned = partition_size, enable_partitioned
         self.block_size = pool.block_size
         self.forward_calls = 0
+        self.fuse_kv_store = True     # norm + RoPE + cache store in one launch for 16-bit caches (False: two launches)
 
     # ---- metadata ----------------------------------------------------------------------------------------
     def _stage(self, t: torch.Tensor) -> torch.Tensor:
@@ -97,10 +98,12 @@ class ModelRunner:
         # a bf16 cache is read in place through the block table; only an fp8 cache (dequantised) is gathered
         paged = need_gather and self.device.type == "cuda" and not self.pool.fp8
         tables = []
+        new_slots = []                                   # cache row of every new token (the fused norm + RoPE + store)
         for sid, st, n in zip(seq_ids, starts, counts):
             table = self.mgr.get_block_table(sid)
             segs += self._segments(table, st, n, cu_q[-1], bs)
             pos += list(range(st, st + n))
+            new_slots += [table[p // bs] * bs + p % bs for p in range(st, st + n)]
             if paged:
                 tables.append(table[:(st + n + bs - 1) // bs])
             elif need_gather:
@@ -117,7 +120,8 @@ class ModelRunner:
             cu_seqlens_q=self._dev(cu_q, torch.int32), cu_seqlens_k=self._dev(cu_k, torch.int32),
             max_seqlen_q=max(counts), total_q=cu_q[-1], total_k=cu_k[-1],
             gather_slots=self._dev(slots, torch.int32) if (need_gather and not paged) else None,
-            block_tables=bt, positions=self._dev(pos, torch.int32), last_token_rows=self._dev(last, torch.long))
+            block_tables=bt, positions=self._dev(pos, torch.int32), last_token_rows=self._dev(last, torch.long),
+            slot_mapping=self._dev(new_slots, torch.int32))
 
     def prepare_decode(self, seq_ids: Sequence, pad_to: int = 0, max_blocks: int = 0) -> InferenceContext:
         """Metadata for one decode step: every sequence's newest token sits at position ``len-1`` (its
@@ -141,6 +145,9 @@ class ModelRunner:
             segs[:n, 1] = np.arange(n)
             segs[:n, 2] = 1
             segs[:n, 3] = last % bs
+        slots = np.full(B, -1, dtype=np.int32)
+        if n:
+            slots[:n] = segs[:n, 0] * bs + segs[:n, 3]
         ctx_lens = np.zeros(B, dtype=np.int32)
         ctx_lens[:n] = lens
         pos = np.zeros(B, dtype=np.int32)
@@ -151,7 +158,8 @@ class ModelRunner:
 
         return InferenceContext(
             is_prefill=False, num_seqs=B, block_tables=dev(bt), context_lens=dev(ctx_lens),
-            max_context_len=int(lens.max()) if n else 0, store_segments=dev(segs), positions=dev(pos))
+            max_context_len=int(lens.max()) if n else 0, store_segments=dev(segs), positions=dev(pos),
+            slot_mapping=dev(slots))
 
     # ---- forward -----------------------------------------------------------------------------------------
     def _split_plan(self, ctx: InferenceContext) -> Tuple[int, int]:
@@ -186,15 +194,24 @@ class ModelRunner:
         cos, sin = ops.rope_tables(cfg.max_position_embeddings, D, cfg.rope_theta, self.device)
         part, nsplit = split_plan if split_plan is not None else (self._split_plan(ctx) if not ctx.is_prefill else (0, 1))
         h = ops.embedding(token_ids, m.embed_tokens)
+        # a 16-bit cache takes the new rows straight from the norm + RoPE kernel; the fp8 cache keeps its own store
+        # kernel (it maintains the per-block scale and requantises a block when the scale grows)
+        fused_store = (self.fuse_kv_store and not self.pool.fp8 and ctx.slot_mapping is not None
+                       and ctx.slot_mapping.dtype == torch.int32 and (D == 128 or self.device.type != "cuda"))
         for li, layer in enumerate(m.layers):
             att_mod = layer.self_attn
             x = ops.rmsnorm(h, layer.input_layernorm.weight, cfg.rms_norm_eps)
             qkv = ops.linear(x, att_mod.qkv_proj.weight)
-            q, k, v = ops.qknorm_rope(qkv, att_mod.q_norm.weight, att_mod.k_norm.weight, ctx.positions, cos, sin,
-                                      Hq, Hkv, D, cfg.rms_norm_eps)
             kc, vc = self.pool.layer_kv(li)
             ks, vs = self.pool.layer_scales(li)
-            ops.kv_store(k, v, kc, vc, ctx.store_segments, ks, vs)
+            if fused_store:
+                # split + per-head norm + rotation + store of the new K / V rows: one launch
+                q, k, v = ops.qknorm_rope_store(qkv, att_mod.q_norm.weight, att_mod.k_norm.weight, ctx.positions, cos, sin,
+                                                Hq, Hkv, D, cfg.rms_norm_eps, kc, vc, ctx.slot_mapping)
+            else:
+                q, k, v = ops.qknorm_rope(qkv, att_mod.q_norm.weight, att_mod.k_norm.weight, ctx.positions, cos, sin,
+                                          Hq, Hkv, D, cfg.rms_norm_eps)
+                ops.kv_store(k, v, kc, vc, ctx.store_segments, ks, vs)
             if ctx.is_prefill:
                 if ctx.block_tables is not None:
                     # chunks with earlier context: keys / values are read in place through the block table
@@ -245,10 +262,11 @@ class ModelRunner:
         blk = bt.gather(1, (pos // bs)[:, None]).squeeze(1)
         rows = torch.arange(B, device=dev, dtype=torch.int32)
         seg = torch.stack([blk, rows, torch.ones_like(rows), (pos % bs).to(torch.int32)], 1).contiguous()
+        slots = (blk.to(torch.int64) * bs + pos % bs).to(torch.int32)
         lens = context_lens.to(dev, torch.int32)
         ctx = InferenceContext(is_prefill=False, num_seqs=B, block_tables=bt.contiguous(), context_lens=lens,
                                max_context_len=int(lens.max()) if B else 0, store_segments=seg,
-                               positions=pos.to(torch.int32))
+                               positions=pos.to(torch.int32), slot_mapping=slots)
         return self.forward(input_ids.reshape(-1).to(dev), ctx)
 
     def bind_kv_cache(self, pool: BlockPool, manager: Optional[KVCacheManager] = None):

@@ -151,6 +151,33 @@ def qknorm_rope(qkv: torch.Tensor, qw: torch.Tensor, kw: torch.Tensor, pos: torc
     return _QKNormRope.apply(qkv, qw, kw, pos.to(torch.int32), cos, sin, Hq, Hkv, eps)
 
 
+def qknorm_rope_store(qkv: torch.Tensor, qw: torch.Tensor, kw: torch.Tensor, pos: torch.Tensor, cos: torch.Tensor,
+                      sin: torch.Tensor, Hq: int, Hkv: int, head_dim: int, eps: float, k_cache: torch.Tensor,
+                      v_cache: torch.Tensor, slots: torch.Tensor):
+    """Inference form of :func:`qknorm_rope`: the same split / norm / rotation, and the new keys and values are
+    written into the 16-bit paged cache ``[blocks, block_size, Hkv, D]`` at row ``slots[t]`` (``block * block_size +
+    offset``; negative = padding row, nothing stored) by the same kernel.  One launch replaces the reference's
+    rotary call plus its ``store_kvcache`` kernel (src/inference/attention.py:32-110).  No gradient."""
+    if not qkv.is_cuda:
+        q, k, v = qknorm_rope(qkv, qw, kw, pos, cos, sin, Hq, Hkv, head_dim, eps)
+        keep = (slots >= 0).nonzero().flatten()
+        rows = slots.long().index_select(0, keep)
+        k_cache.view(-1, Hkv, head_dim).index_copy_(0, rows, k.reshape(-1, Hkv, head_dim).index_select(0, keep).to(k_cache.dtype))
+        v_cache.view(-1, Hkv, head_dim).index_copy_(0, rows, v.reshape(-1, Hkv, head_dim).index_select(0, keep).to(v_cache.dtype))
+        return q, k, v
+    assert head_dim == 128 and k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype
+    M = qkv.shape[0]
+    q = torch.empty((M, Hq * 128), device=qkv.device, dtype=qkv.dtype)
+    k = torch.empty((M, Hkv * 128), device=qkv.device, dtype=qkv.dtype)
+    pos = pos if pos.dtype == torch.int32 else pos.to(torch.int32)
+    nv.check(nv.lib().b2_qknorm_rope_store(nv.ptr(qkv), nv.ptr(qw), nv.ptr(kw), nv.ptr(pos), nv.ptr(cos), nv.ptr(sin),
+                                           nv.ptr(q), nv.ptr(k), M, Hq, Hkv, 128, qkv.stride(0),
+                                           nv.ctypes.c_float(eps), nv.ptr(slots), nv.ptr(k_cache), nv.ptr(v_cache),
+                                           nv.stream_ptr()), "qknorm_rope_store")
+    nv.count_launch()
+    return q, k, qkv[:, (Hq + Hkv) * 128:]
+
+
 # ---- SwiGLU ---------------------------------------------------------------------------------------
 class _SwiGLU(torch.autograd.Function):
     @staticmethod

@@ -379,12 +379,17 @@ __device__ __forceinline__ float sum16(float v) {   // over the 16 lanes that sh
   return v;
 }
 
+// STORE: the inference form.  Token `tok` owns row slots[tok] (= block * block_size + offset; negative: padding, no
+// store) of a bf16 paged cache laid out [rows, Hkv, 128]; its rotated keys and its values (copied from the projection
+// output) are written there by the same warp, so the runner needs no separate store launch and K / V are not re-read.
+template <bool STORE>
 __global__ void __launch_bounds__(256) qknorm_rope_fwd_kernel(
     const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ qw,
     const __nv_bfloat16* __restrict__ kw, const int* __restrict__ pos,
     const float* __restrict__ cos_t, const float* __restrict__ sin_t,
     __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_out,
-    float* __restrict__ rstd_out, int M, int Hq, int Hkv, int ld_qkv, float eps) {
+    float* __restrict__ rstd_out, int M, int Hq, int Hkv, int ld_qkv, float eps,
+    const int* __restrict__ slots, __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache) {
   const int heads = Hq + Hkv;
   const int lane = threadIdx.x & 31, l16 = lane & 15, sub = lane >> 4;
   const int warps_per_grid = (gridDim.x * blockDim.x) >> 5;
@@ -405,6 +410,13 @@ __global__ void __launch_bounds__(256) qknorm_rope_fwd_kernel(
       sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
     }
     const __nv_bfloat16* row = qkv + static_cast<size_t>(tok) * ld_qkv + l16 * 8;
+    const int slot = STORE ? slots[tok] : -1;
+    if (STORE && slot >= 0) {
+      // values: plain copy of the Hkv value heads, two heads per warp-wide access
+      for (int hv = sub; hv < Hkv; hv += 2)
+        *reinterpret_cast<uint4*>(v_cache + (static_cast<size_t>(slot) * Hkv + hv) * 128 + l16 * 8) =
+            *reinterpret_cast<const uint4*>(row + (heads + hv) * 128);
+    }
     for (int hp0 = 0; hp0 < npairs; hp0 += QKR_PAIRS) {
       uint4 raw[QKR_PAIRS];
 #pragma unroll
@@ -433,7 +445,10 @@ __global__ void __launch_bounds__(256) qknorm_rope_fwd_kernel(
         if (head < heads) {
           __nv_bfloat16* dst = is_q ? q_out + (static_cast<size_t>(tok) * Hq + head) * 128 + l16 * 8
                                     : k_out + (static_cast<size_t>(tok) * Hkv + (head - Hq)) * 128 + l16 * 8;
-          *reinterpret_cast<uint4*>(dst) = qkr_pack8(o);
+          const uint4 packed = qkr_pack8(o);
+          *reinterpret_cast<uint4*>(dst) = packed;
+          if (STORE && !is_q && slot >= 0)
+            *reinterpret_cast<uint4*>(k_cache + (static_cast<size_t>(slot) * Hkv + (head - Hq)) * 128 + l16 * 8) = packed;
           if (l16 == 0 && rstd_out) rstd_out[static_cast<size_t>(tok) * heads + head] = rstd;
         }
       }
@@ -692,11 +707,36 @@ B2_EXPORT int b2_qknorm_rope_fwd(const void* qkv, const void* qw, const void* kw
   long long blocks = (static_cast<long long>(M) + 7) / 8;   // one warp per token
   const long long fcap = static_cast<long long>(num_sms()) * 16;
   if (blocks > fcap) blocks = fcap;
-  qknorm_rope_fwd_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  qknorm_rope_fwd_kernel<false><<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(qkv), static_cast<const __nv_bfloat16*>(qw),
       static_cast<const __nv_bfloat16*>(kw), pos, cos_t, sin_t, static_cast<__nv_bfloat16*>(q_out),
-      static_cast<__nv_bfloat16*>(k_out), rstd, M, Hq, Hkv, ld_qkv, eps);
+      static_cast<__nv_bfloat16*>(k_out), rstd, M, Hq, Hkv, ld_qkv, eps, nullptr, nullptr, nullptr);
   B2_LAUNCH_CHECK("qknorm_rope_fwd");
+  return 0;
+}
+
+// Inference form: QK-norm + RoPE + store of the new K / V rows into a bf16 paged cache ([rows, Hkv, 128], row =
+// block * block_size + offset) in one launch.  slots: int32 [M], negative = no store (padding rows of a graph batch).
+B2_EXPORT int b2_qknorm_rope_store(const void* qkv, const void* qw, const void* kw, const int* pos,
+                                   const float* cos_t, const float* sin_t, void* q_out, void* k_out, int M, int Hq,
+                                   int Hkv, int head_dim, int ld_qkv, float eps, const int* slots, void* k_cache,
+                                   void* v_cache, void* stream) {
+  b2::ensure_thread_context();
+  if (head_dim != 128) { set_error("qknorm_rope_store: head_dim must be 128"); return 10; }
+  if (slots == nullptr || k_cache == nullptr || v_cache == nullptr) {
+    set_error("qknorm_rope_store: slots and both caches are required");
+    return 10;
+  }
+  if (M <= 0) return 0;
+  long long blocks = (static_cast<long long>(M) + 7) / 8;   // one warp per token
+  const long long fcap = static_cast<long long>(num_sms()) * 16;
+  if (blocks > fcap) blocks = fcap;
+  qknorm_rope_fwd_kernel<true><<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(qkv), static_cast<const __nv_bfloat16*>(qw),
+      static_cast<const __nv_bfloat16*>(kw), pos, cos_t, sin_t, static_cast<__nv_bfloat16*>(q_out),
+      static_cast<__nv_bfloat16*>(k_out), nullptr, M, Hq, Hkv, ld_qkv, eps, slots,
+      static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache));
+  B2_LAUNCH_CHECK("qknorm_rope_store");
   return 0;
 }
 

@@ -119,6 +119,7 @@ constexpr int DEC_THREADS = 128;
 constexpr int DEC_CHUNK = 64;   // partitions are multiples of this many tokens
 constexpr int DEC_MAX_G = 8;
 constexpr int DEC_UNROLL = 4;   // cache rows in flight per lane group
+constexpr int DEC_DEFAULT_MODE = 0;   // row loop of the decode kernel when B200FW_DECODE_MODE is unset
 constexpr float DEC_LOG2E = 1.4426950408889634f;
 constexpr float DEC_LN2 = 0.6931471805599453f;
 
@@ -157,7 +158,11 @@ __device__ __forceinline__ void dec_unpack<true>(const uint4& u, float* f) {
 // maximum, sum and DPL accumulator dims per head, base-2 exponent domain); groups and warps are merged
 // once at the end with the exact log-sum-exp rule.  GH query heads of the kv head are handled per CTA
 // (their q pieces sit in registers); larger GQA ratios use several CTAs (head groups) per kv head.
-template <bool FP8, int GH, bool PIPE>
+// MODE 0: plain row loop.  MODE 1: register software pipeline (loads of step i + 1 under the arithmetic of step i).
+// MODE 3 / 4: every warp owns a ring of that many stages in shared memory, filled by 16-byte asynchronous copies
+// (cp.async.cg, no register staging); a lane reads back exactly the bytes it copied, so no barrier is needed, and
+// MODE - 1 steps' worth of K and V rows stay in flight per warp without growing the register count.
+template <bool FP8, int GH, int MODE>
 __global__ void __launch_bounds__(DEC_THREADS) paged_decode_kernel(
     const __nv_bfloat16* __restrict__ q, const void* __restrict__ k_cache, const void* __restrict__ v_cache,
     const float* __restrict__ k_scale, const float* __restrict__ v_scale,
@@ -169,8 +174,11 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_decode_kernel(
   constexpr int TPW = 32 / LPT;        // token rows per warp-wide load
   constexpr int DPL = 16 / ESZ;        // dims per lane
   constexpr int U = DEC_UNROLL;
+  constexpr bool PIPE = MODE == 1;
+  constexpr int STAGES = MODE >= 2 ? MODE : 1;
   __shared__ float sAcc[DEC_THREADS / 32][GH][HD];
   __shared__ float sM[DEC_THREADS / 32][GH], sL[DEC_THREADS / 32][GH];
+  extern __shared__ __align__(16) uint8_t dec_ring[];   // [warp][stage][u][K | V][32 lanes x 16 B] (MODE >= 2)
 
   const int G = Hq / Hkv;
   const int groups_per_kv = G / GH;
@@ -286,7 +294,56 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_decode_kernel(
   {
     constexpr int STEP = (DEC_THREADS / 32) * TPW * U;
     int base = t_begin + warp * (TPW * U);
-    if (PIPE) {
+    if (MODE >= 2) {
+      const uint32_t ring = smem_u32(dec_ring) + (warp * STAGES * U * 2 * 32 + lane) * 16;
+      auto issue = [&](int stage, int at) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int tok = at + u * TPW + group;
+          if (tok < t_end) {
+            const int blk = table[tok / PAGE];
+            const size_t a = (static_cast<size_t>(blk) * PAGE + tok % PAGE) * tok_stride;
+            const uint32_t dst = ring + ((stage * U + u) * 2) * 512;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(kc + a) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + 512), "l"(vc + a) : "memory");
+          }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");   // one group per stage, empty ones included
+      };
+#pragma unroll
+      for (int s = 0; s < STAGES - 1; ++s) issue(s, base + s * STEP);
+      int slot = 0;
+      for (; base < t_end; base += STEP) {
+        issue(slot == 0 ? STAGES - 1 : slot - 1, base + (STAGES - 1) * STEP);
+        asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 1) : "memory");
+        Rows r;
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const int tok = base + u * TPW + group;
+          r.valid[u] = tok < t_end;
+          r.kq[u] = make_uint4(0, 0, 0, 0);
+          r.vq[u] = make_uint4(0, 0, 0, 0);
+          r.ks[u] = r.vs[u] = 1.f;
+          if (r.valid[u]) {
+            const uint32_t src = ring + ((slot * U + u) * 2) * 512;
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(r.kq[u].x), "=r"(r.kq[u].y), "=r"(r.kq[u].z), "=r"(r.kq[u].w)
+                         : "r"(src));
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(r.vq[u].x), "=r"(r.vq[u].y), "=r"(r.vq[u].z), "=r"(r.vq[u].w)
+                         : "r"(src + 512));
+            if (FP8) {
+              const int blk = table[tok / PAGE];
+              r.ks[u] = k_scale[static_cast<size_t>(blk) * Hkv + kvh];
+              r.vs[u] = v_scale[static_cast<size_t>(blk) * Hkv + kvh];
+            }
+          }
+        }
+        consume(r);
+        slot = slot + 1 == STAGES ? 0 : slot + 1;
+      }
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    } else if (PIPE) {
       Rows ra, rb;
       if (base < t_end) load_rows(ra, base);
       while (base < t_end) {
@@ -458,22 +515,38 @@ B2_EXPORT int b2_paged_decode(const void* q, const void* k_cache, const void* v_
   // lane, so four heads would leave room for only two CTAs per SM)
   const int GH = (G % 4 == 0 && !fp8) ? 4 : (G % 2 == 0 ? 2 : 1);
   dim3 grid(B, Hkv * (G / GH), nsplit);
-  // B200FW_DECODE_PIPE=1 selects the software-pipelined row loop (loads of the next step under this step's
-  // arithmetic; more registers, fewer resident CTAs), 0 the plain loop
-  static const bool pipe = [] {
-    const char* e = std::getenv("B200FW_DECODE_PIPE");
-    return e != nullptr && e[0] == '1';
+  // B200FW_DECODE_MODE selects the row loop: 0 plain, 1 register software pipeline, 3 / 4 a ring of that many
+  // cp.async stages per warp in shared memory (B200FW_DECODE_PIPE=1 is the older spelling of mode 1)
+  // (read on every call, so that one process can compare them)
+  const int mode = [] {
+    const char* e = std::getenv("B200FW_DECODE_MODE");
+    if (e != nullptr && e[0] >= '0' && e[0] <= '4' && e[0] != '2') return e[0] - '0';
+    const char* p = std::getenv("B200FW_DECODE_PIPE");
+    return (p != nullptr && p[0] == '1') ? 1 : DEC_DEFAULT_MODE;
   }();
+#define B2_DECODE_LAUNCH_M(F8, GHV, MD)                                                                    \
+  do {                                                                                                     \
+    constexpr int ring = MD >= 2 ? (DEC_THREADS / 32) * MD * DEC_UNROLL * 2 * 512 : 0;                     \
+    auto kern = paged_decode_kernel<F8, GHV, MD>;                                                          \
+    if (ring > 0) {                                                                                        \
+      static bool attr_set[64] = {};                                                                       \
+      int dev = 0;                                                                                         \
+      cudaGetDevice(&dev);                                                                                 \
+      if (!attr_set[dev & 63]) {                                                                           \
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, ring);                     \
+        attr_set[dev & 63] = true;                                                                         \
+      }                                                                                                    \
+    }                                                                                                      \
+    kern<<<grid, DEC_THREADS, ring, stream>>>(                                                             \
+        static_cast<const __nv_bfloat16*>(q), k_cache, v_cache, k_scale, v_scale, block_tables, context_lens, \
+        max_blocks, static_cast<__nv_bfloat16*>(out), part_o, part_ml, Hq, Hkv, partition, scale);         \
+  } while (0)
 #define B2_DECODE_LAUNCH(F8, GHV)                                                                          \
   do {                                                                                                     \
-    if (pipe)                                                                                              \
-      paged_decode_kernel<F8, GHV, true><<<grid, DEC_THREADS, 0, stream>>>(                                \
-          static_cast<const __nv_bfloat16*>(q), k_cache, v_cache, k_scale, v_scale, block_tables, context_lens, \
-          max_blocks, static_cast<__nv_bfloat16*>(out), part_o, part_ml, Hq, Hkv, partition, scale);       \
-    else                                                                                                   \
-      paged_decode_kernel<F8, GHV, false><<<grid, DEC_THREADS, 0, stream>>>(                               \
-          static_cast<const __nv_bfloat16*>(q), k_cache, v_cache, k_scale, v_scale, block_tables, context_lens, \
-          max_blocks, static_cast<__nv_bfloat16*>(out), part_o, part_ml, Hq, Hkv, partition, scale);       \
+    if (mode == 1) B2_DECODE_LAUNCH_M(F8, GHV, 1);                                                         \
+    else if (mode == 3) B2_DECODE_LAUNCH_M(F8, GHV, 3);                                                    \
+    else if (mode == 4) B2_DECODE_LAUNCH_M(F8, GHV, 4);                                                    \
+    else B2_DECODE_LAUNCH_M(F8, GHV, 0);                                                                   \
   } while (0)
   if (fp8) {
     if (GH == 4) B2_DECODE_LAUNCH(true, 4);
@@ -484,6 +557,7 @@ B2_EXPORT int b2_paged_decode(const void* q, const void* k_cache, const void* v_
     else if (GH == 2) B2_DECODE_LAUNCH(false, 2);
     else B2_DECODE_LAUNCH(false, 1);
   }
+#undef B2_DECODE_LAUNCH_M
 #undef B2_DECODE_LAUNCH
   B2_LAUNCH_CHECK("paged_decode");
   if (nsplit > 1) {

@@ -175,6 +175,8 @@ def main():
     ap.add_argument("--vocab", type=int, default=151936)
     ap.add_argument("--fp8", action="store_true")
     ap.add_argument("--partition", type=int, default=0, help="paged_decode: tokens per split-KV partition (0 = automatic)")
+    ap.add_argument("--decode-mode", default=None, choices=["0", "1", "3", "4"],
+                    help="paged_decode: row loop of the kernel (0 plain, 1 register pipeline, 3 / 4 cp.async ring stages)")
     ap.add_argument("--fp32-acc", action="store_true", help="gemm: accumulate into an fp32 output (weight-gradient form)")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
@@ -267,6 +269,8 @@ def main():
         flops = 6.0 * a.m * a.h * a.vocab
     elif a.kernel == "paged_decode":
         torch.set_grad_enabled(False)
+        if a.decode_mode is not None:
+            os.environ["B200FW_DECODE_MODE"] = a.decode_mode
         nblk = a.batch * ((a.ctx + 15) // 16) + 1
         dt = torch.uint8 if a.fp8 else bf
         kc = torch.zeros(nblk, 16, a.hkv, 128, dtype=dt, device=DEV)

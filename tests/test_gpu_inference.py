@@ -45,11 +45,45 @@ def test_kv_store_and_gather(fp8):
     assert relerr(K, k) <= tol and relerr(V, v) <= tol
 
 
+@pytest.mark.parametrize("Hq,Hkv", [(4, 2), (8, 1), (3, 3)])
+def test_qknorm_rope_store_equals_the_two_launch_form(Hq, Hkv):
+    """Norm + RoPE + cache store in one launch: q / k equal the training-path kernel's, the cache rows equal what the
+    separate store kernel writes, padding rows (slot -1) store nothing."""
+    from b200fw.ops import qknorm_rope, qknorm_rope_store, rope_tables
+    torch.manual_seed(3)
+    D, M, nblk = 128, 77, 12
+    qkv = torch.randn(M, (Hq + 2 * Hkv) * D, device=DEV, dtype=torch.bfloat16)
+    qw = (1 + 0.1 * torch.randn(D, device=DEV)).to(torch.bfloat16)
+    kw = (1 + 0.1 * torch.randn(D, device=DEV)).to(torch.bfloat16)
+    pos = torch.randint(0, 500, (M,), device=DEV, dtype=torch.int32)
+    cos, sin = rope_tables(1024, D, 1e6, torch.device(DEV))
+    slots = torch.randperm(nblk * 16)[:M].to(torch.int32)
+    slots[5] = -1
+    slots[M - 1] = -1
+    kc = torch.full((nblk, 16, Hkv, D), 7.0, device=DEV, dtype=torch.bfloat16)
+    vc = torch.full_like(kc, 7.0)
+    q, k, v = qknorm_rope_store(qkv, qw, kw, pos, cos, sin, Hq, Hkv, D, 1e-6, kc, vc, slots.to(DEV))
+    q0, k0, v0 = qknorm_rope(qkv, qw, kw, pos, cos, sin, Hq, Hkv, D, 1e-6)
+    assert torch.equal(q, q0) and torch.equal(k, k0) and torch.equal(v, v0)
+    want_k = torch.full_like(kc, 7.0).view(-1, Hkv * D)
+    want_v = torch.full_like(vc, 7.0).view(-1, Hkv * D)
+    keep = (slots >= 0).nonzero().flatten().to(DEV)
+    want_k[slots[keep.cpu()].long().to(DEV)] = k0[keep]
+    want_v[slots[keep.cpu()].long().to(DEV)] = v0[keep]
+    assert torch.equal(kc.view(-1, Hkv * D), want_k) and torch.equal(vc.view(-1, Hkv * D), want_v)
+    # and against the fp32 formula on the CPU
+    qc, kcpu, _ = qknorm_rope(qkv.cpu().float(), qw.cpu().float(), kw.cpu().float(), pos.cpu(), cos.cpu(), sin.cpu(),
+                              Hq, Hkv, D, 1e-6)
+    assert relerr(q, qc) < 2e-2 and relerr(k, kcpu) < 2e-2
+
+
 @pytest.mark.parametrize("fp8", [False, True])
 @pytest.mark.parametrize("Hq,Hkv", [(4, 2), (8, 1), (2, 2)])
 @pytest.mark.parametrize("split", [(0, 1), (64, 0)])
-def test_paged_decode_attention(fp8, Hq, Hkv, split):
+@pytest.mark.parametrize("mode", ["0", "1", "3", "4"])     # row loop of the kernel: plain, register pipeline, cp.async rings
+def test_paged_decode_attention(fp8, Hq, Hkv, split, mode, monkeypatch):
     from b200fw.ops import paged_decode_attention
+    monkeypatch.setenv("B200FW_DECODE_MODE", mode)
     k, v, kc, vc, ks, vs, perm = _fill_cache(fp8, Hkv=Hkv)
     B, D = 3, 128
     lens = [300, 17, 64]

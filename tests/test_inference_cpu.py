@@ -252,3 +252,28 @@ def test_one_step_late_decode_bookkeeping_on_cpu(model, oracle):
         e3.step()
     assert all(len(e3.finished[f"q{i}"].output_tokens) == 8 and min(e3.finished[f"q{i}"].output_tokens) >= 0
                for i in range(len(PROMPTS)))
+
+
+def test_fused_norm_rope_store_path_equals_the_two_step_path(model, oracle):
+    """The runner stores the new K / V rows from the norm + RoPE op when the cache is 16-bit; with the switch off it
+    runs the separate store.  Both give the oracle's tokens, and the op's cache rows equal ``kv_store``'s."""
+    from b200fw.ops import kv_store, qknorm_rope, qknorm_rope_store, rope_tables
+    e = _engine(model)
+    assert e.runner.fuse_kv_store
+    assert e.generate(PROMPTS, max_tokens=10) == oracle
+    e2 = _engine(model)
+    e2.runner.fuse_kv_store = False
+    assert e2.generate(PROMPTS, max_tokens=10) == oracle
+    torch.manual_seed(0)
+    Hq, Hkv, D, M = 4, 2, 8, 21
+    qkv = torch.randn(M, (Hq + 2 * Hkv) * D)
+    qw, kw = torch.rand(D) + 0.5, torch.rand(D) + 0.5
+    pos = torch.arange(M, dtype=torch.int32)
+    cos, sin = rope_tables(64, D, 1e4, torch.device("cpu"))
+    kc, vc = torch.zeros(3, 16, Hkv, D), torch.zeros(3, 16, Hkv, D)
+    slots = torch.tensor([32 + i for i in range(16)] + [-1] + [3, 4, 5, 6], dtype=torch.int32)
+    q, k, v = qknorm_rope_store(qkv, qw, kw, pos, cos, sin, Hq, Hkv, D, 1e-6, kc, vc, slots)
+    q0, k0, v0 = qknorm_rope(qkv, qw, kw, pos, cos, sin, Hq, Hkv, D, 1e-6)
+    kc0, vc0 = torch.zeros_like(kc), torch.zeros_like(vc)
+    kv_store(k0, v0, kc0, vc0, torch.tensor([[2, 0, 16, 0], [0, 17, 4, 3]], dtype=torch.int32))
+    assert torch.equal(q, q0) and torch.equal(kc, kc0) and torch.equal(vc, vc0)
