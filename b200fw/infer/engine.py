@@ -214,7 +214,13 @@ class InferenceEngine:
         if inf is None:
             return
         if inf["event"] is not None:
-            inf["event"].synchronize()
+            if inf["event"].query():
+                self.stats["inflight_ready"] = self.stats.get("inflight_ready", 0) + 1    # the GPU was ahead of the host
+            else:
+                t0 = time.perf_counter()
+                inf["event"].synchronize()
+                self.stats["inflight_wait_s"] = self.stats.get("inflight_wait_s", 0.0) + time.perf_counter() - t0
+                self.stats["inflight_waited"] = self.stats.get("inflight_waited", 0) + 1
         ids, lps = inf["host_ids"][:len(inf["reqs"])].tolist(), inf["host_lps"][:len(inf["reqs"])].tolist()
         for r, slot, t, lp in zip(inf["reqs"], inf["slots"], ids, lps):
             if slot >= len(r.output_tokens) or r.output_tokens[slot] != self.PLACEHOLDER:

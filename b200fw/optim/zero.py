@@ -155,6 +155,7 @@ class ZeROOptimizer:
         # pointers or NVLS multimem (stage 1/2, bf16, CUDA, 2..8 ranks of one node); "nccl": library collectives;
         # "auto": p2p where it applies to a plain data-parallel layout, NCCL otherwise.
         can_p2p = (self.on_cuda and 1 < self.world <= 8 and self.dtype == torch.bfloat16 and 1 <= self.stage <= 2)
+        self._auto_backend = comm_backend == "auto"
         if comm_backend == "auto":
             pure_dp = ctx is None or (ctx.tp_size == 1 and ctx.pp_size == 1)
             comm_backend = "p2p" if (can_p2p and pure_dp and self.stage == 1) else "nccl"
@@ -183,7 +184,21 @@ class ZeROOptimizer:
             if cur:
                 self.buckets.append(_Bucket(cur, kind, self.world, self.rank, self.dtype, self.device, self.grad_dtype))
         if self.p2p:
-            self._make_symmetric()
+            try:
+                self._make_symmetric()
+                failed = 0
+            except Exception as e:  # noqa: BLE001 - decided together below
+                failed, err = 1, e
+            # every rank has to take the same path: agree before anything launches
+            flag = torch.tensor([failed], device=self.device, dtype=torch.int32)
+            dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=self.dp_group)
+            if int(flag.item()):
+                if not self._auto_backend:
+                    raise RuntimeError("ZeRO comm_backend='p2p': symmetric memory could not be set up on every rank") \
+                        from (err if failed else None)
+                import warnings
+                warnings.warn("ZeRO: symmetric memory is not available on every rank; using NCCL collectives")
+                self._drop_symmetric()
         for b in self.buckets:
             for p in b.params:
                 p._zero_bucket = b
@@ -248,6 +263,15 @@ class ZeROOptimizer:
         import os
         self.nvls = (os.environ.get("B200FW_ZERO_NVLS", "0") == "1"
                      and all(b.symm_grad.mc_ptr and b.symm_param.mc_ptr for b in self.buckets))
+
+    def _drop_symmetric(self):
+        """Back to library collectives: the buckets keep whatever storage they have (a symmetric tensor is an ordinary
+        tensor to NCCL), the peer-memory bookkeeping goes."""
+        self.p2p, self.comm_backend, self.flags, self._norm_ar, self.nvls = False, "nccl", None, None, False
+        for b in self.buckets:
+            b.symm_param = b.symm_grad = None
+            b.persistent_grad = False
+            b.grad_buf = None           # allocated (and bound as main_grad) again on first use
 
     def _p2p_reduce_bucket(self, b: _Bucket, idx: int):
         """Runs on the current stream: wait (bounded, on the device) until every rank has finished writing bucket

@@ -133,7 +133,11 @@ def main(argv=None):
         # the figure the reference arm (baseline/run_reference_extras.py decode) reports: output tokens over the whole call
         "generation_output_tokens_per_s": gen / ((prefill_ms + decode_ms) * 1e-3), "clocks": clocks,
         "spec_acceptance": st.get("speculative", {}).get("acceptance_rate"),
-        "graph_replays": st.get("graph_replays"), "kv_blocks": blocks}))
+        "graph_replays": st.get("graph_replays"), "kv_blocks": blocks,
+        # who waits for whom with the one-step-late read-back: launches whose result was already there when the host
+        # came for it (the host is the limit) against those the host had to wait for (the GPU is), and that wait
+        "host_found_result_ready": st.get("inflight_ready", 0), "host_waited_for_gpu": st.get("inflight_waited", 0),
+        "host_wait_ms_per_decode_step": 1e3 * st.get("inflight_wait_s", 0.0) / max(1, steps_decode)}))
 
 
 if __name__ == "__main__":

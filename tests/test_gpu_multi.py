@@ -110,6 +110,43 @@ def test_zero_p2p_matches_nccl(stage, nvls):
         assert abs(a[r][2] - b[r][2]) / a[r][2] < 2e-3
 
 
+def _zero_symm_failure_worker(rank, world):
+    from b200fw.optim import zero
+    from b200fw.train import TrainConfig, TrainEngine
+    real = zero.ZeROOptimizer._make_symmetric
+
+    def broken(self):
+        real(self)                      # the collective part (rendezvous) runs on every rank
+        if rank == world - 1:
+            raise RuntimeError("set-up failed on this rank after the rendezvous (made up by the test)")
+    zero.ZeROOptimizer._make_symmetric = broken
+    cfg = TrainConfig(model_preset="tiny128", dp_size=world, lora_rank=0, grpo_beta=0.0, learning_rate=1e-3,
+                      gradient_accumulation_steps=1, zero_stage=1, warmup_steps=0, max_seq_len=128,
+                      amp_dtype="bf16", zero_comm_backend="auto", bucket_mb=1.0)
+    import warnings
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore")
+        eng = TrainEngine(cfg).initialize()
+    assert not eng.optimizer.p2p and eng.optimizer.comm_backend == "nccl" and eng.optimizer.flags is None
+    losses = []
+    for s in range(3):
+        ids = torch.randint(0, 8192, (2, 128), generator=torch.Generator().manual_seed(s * 7 + rank))
+        losses.append(eng.sft_step_tensors(ids, ids.clone()).loss)
+    flat = torch.cat([p.detach().float().reshape(-1) for p in eng.model.parameters()])
+    return losses, float(flat.double().sum())
+
+
+@needs2
+def test_zero_auto_backend_falls_back_together_when_one_rank_has_no_symmetric_memory():
+    """The failure is made on the host (an exception in one rank's set-up); every rank must end up on the NCCL path,
+    hold identical weights and make progress."""
+    from _gpu_dist_util import run_gpu_ranks
+    w = _world()
+    out = run_gpu_ranks(_zero_symm_failure_worker, w)
+    assert all(out[r][1] == out[0][1] for r in range(w))
+    assert out[0][0][-1] < out[0][0][0]
+
+
 def _zero_wait_runs_out_worker(rank, world):
     """Rank 0 waits (300 ms limit) on a barrier channel that rank 1 never enters: the wait runs out, the device-side
     ``ok`` word is cleared, this step's AdamW leaves rank 0's shard untouched, and the host raises at the step's
