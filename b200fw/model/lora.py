@@ -84,6 +84,7 @@ class LinearWithLoRA(nn.Module):
         self.adapters = nn.ModuleDict({k: v[0] for k, v in adapters.items()})
         self.ranges = {k: (v[1], v[2]) for k, v in adapters.items()}
         self.merged = False
+        self.fuse_into_base = True      # False: base projection, then two adapter GEMMs (the only form under TP)
 
     @property
     def weight(self):
@@ -128,12 +129,19 @@ class LinearWithLoRA(nn.Module):
         from .. import ops
         base = self.base
         is_row = isinstance(base, RowParallelLinear)
-        y = base(x, residual) if is_row else base(x)
         if self.merged or not self.adapters:
-            return y
+            return base(x, residual) if is_row else base(x)
         tp, grp, sp = base.tp_size, base.tp_group, base.sequence_parallel
         x2 = x.reshape(-1, x.shape[-1])
         a_cat, b_bd = self._stacked(x2.dtype)
+        if (self.fuse_into_base and tp == 1 and x2.is_cuda and base.bias is None and a_cat.shape[0] % 8 == 0
+                and x2.dtype == torch.bfloat16):
+            # one device: the rank-R update rides in the base projection's GEMM (forward and input gradient), the
+            # frozen base weight gets no gradient GEMM at all
+            y = ops.lora_linear(x2 if x2.is_contiguous() else x2.contiguous(), base.weight, a_cat.contiguous(), b_bd,
+                                residual.reshape(-1, base.weight.shape[0]) if residual is not None else None)
+            return y.reshape(*x.shape[:-1], y.shape[-1])
+        y = base(x, residual) if is_row else base(x)
         if is_row:
             # x holds this rank's input columns: the rank-R intermediate is a partial sum over TP
             mid = ops.linear(x2, a_cat)

@@ -5,7 +5,7 @@
 * CPU tensors run a plain PyTorch fp32-accurate implementation, which is the numerical oracle of the
   test-suite and the path used by the gloo plumbing tests.
 """
-from .gemm import gemm, linear, grad_into_main
+from .gemm import gemm, linear, lora_linear, grad_into_main
 from .elementwise import rmsnorm, qknorm_rope, qknorm_rope_store, swiglu, embedding, rope_tables
 from .attention import flash_attention
 from .loss import lm_head_cross_entropy, lm_head_logprob, grpo_token_loss, VocabShard, valid_rows
@@ -14,7 +14,7 @@ from .paged import (kv_store, kv_gather, paged_decode_attention, paged_prefill_a
                     topp_sample)
 
 __all__ = [
-    "gemm", "linear", "grad_into_main", "rmsnorm", "qknorm_rope", "qknorm_rope_store", "swiglu", "embedding", "rope_tables",
+    "gemm", "linear", "lora_linear", "grad_into_main", "rmsnorm", "qknorm_rope", "qknorm_rope_store", "swiglu", "embedding", "rope_tables",
     "flash_attention", "VocabShard", "valid_rows", "lm_head_cross_entropy", "lm_head_logprob", "grpo_token_loss", "sumsq",
     "fused_adamw", "kv_store", "kv_gather", "paged_decode_attention", "paged_prefill_attention", "varlen_attention", "topp_sample",
 ]

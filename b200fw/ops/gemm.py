@@ -17,17 +17,22 @@ OUT_FP32, ACCUMULATE, RESIDUAL = 1, 2, 4
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
          out: Optional[torch.Tensor] = None, accumulate: bool = False,
          residual: Optional[torch.Tensor] = None, out_dtype: torch.dtype = torch.bfloat16,
-         bn: int = 0, max_ctas: int = 0) -> torch.Tensor:
-    """``C[M,N] (+)= A @ B^T (+ residual)``.
+         bn: int = 0, max_ctas: int = 0, ext=None) -> torch.Tensor:
+    """``C[M,N] (+)= A @ B^T (+ A2 @ B2^T) (+ residual)``.
 
     ``a`` is ``[M,K]`` (or ``[K,M]`` when ``a_mn``); ``b`` is ``[N,K]`` (or ``[K,N]`` when ``b_mn``).
     Rows may be strided (last dim contiguous).  CUDA bf16 inputs run the tcgen05 kernel; CPU inputs
-    run ``torch.matmul`` in the input dtype.
+    run ``torch.matmul`` in the input dtype.  ``ext=(a2, b2)`` appends a second operand pair along the contraction
+    (``a2 [M,K2]``; ``b2 [N,K2]``, or ``[K2,N]`` when ``b_mn``; ``K2 % 8 == 0``): both products are accumulated in
+    the same pass of the kernel, so a low-rank update costs no second trip over the ``[M,N]`` output.
     """
     if not a.is_cuda:
         A = a.t() if a_mn else a
         Bm = b.t() if b_mn else b
         r = A.float() @ Bm.float().t()
+        if ext is not None:
+            b2 = ext[1].t() if b_mn else ext[1]
+            r = r + ext[0].float() @ b2.float().t()
         if residual is not None:
             r = r + residual.float()
         if out is not None:
@@ -50,6 +55,18 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     if residual is not None:
         assert residual.shape == (M, N) and residual.stride(0) == out.stride(0) and residual.dtype == torch.bfloat16
         flags |= RESIDUAL
+    if ext is not None:
+        a2, b2 = ext
+        K2 = a2.shape[1]
+        assert not a_mn and not accumulate and a2.dtype == torch.bfloat16 and b2.dtype == torch.bfloat16
+        assert a2.shape == (M, K2) and b2.shape == ((K2, N) if b_mn else (N, K2)) and K2 % 8 == 0
+        assert a2.stride(-1) == 1 and b2.stride(-1) == 1
+        rc = nv.lib().b2_gemm_bf16_ext(nv.ptr(a), nv.ptr(b), nv.ptr(out), nv.ptr(residual), M, N, K, a.stride(0),
+                                       b.stride(0), out.stride(0), int(b_mn), flags, bn, nv.ptr(a2), nv.ptr(b2), K2,
+                                       a2.stride(0), b2.stride(0), nv.stream_ptr())
+        nv.check(rc, "gemm_ext")
+        nv.count_launch()
+        return out
     rc = nv.lib().b2_gemm_bf16(nv.ptr(a), nv.ptr(b), nv.ptr(out), nv.ptr(residual), M, N, K,
                                a.stride(0), b.stride(0), out.stride(0), int(a_mn), int(b_mn), flags, bn,
                                max_ctas, nv.stream_ptr())
@@ -127,3 +144,45 @@ def linear(x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = 
     if no_grad_needed(x, w, residual):
         return gemm(x, w, residual=residual)
     return _Linear.apply(x, w, residual)
+
+
+class _LoRALinear(torch.autograd.Function):
+    """``y = x W^T + (x A^T) Bs^T (+ residual)`` with the low-rank product riding in the base GEMM's accumulator
+    (``gemm(..., ext=...)``), forward and input-gradient alike.  ``a_cat [R, K]`` and ``bs [N, R]`` (B already times
+    its scaling) are the layer's stacked adapters in the activation dtype; ``w`` is the frozen base weight."""
+
+    @staticmethod
+    def forward(ctx, x, w, a_cat, bs, residual):
+        mid = gemm(x, a_cat)                                     # [M, R]
+        y = gemm(x, w, residual=residual, ext=(mid, bs))
+        ctx.save_for_backward(x, w, a_cat, bs, mid)
+        ctx.has_res = residual is not None
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, a_cat, bs, mid = ctx.saved_tensors
+        dy = dy if dy.stride(-1) == 1 else dy.contiguous()
+        dmid = gemm(dy, bs, b_mn=True)                           # [M, R] = dy @ Bs
+        dx = gemm(dy, w, b_mn=True, ext=(dmid, a_cat)) if ctx.needs_input_grad[0] else None    # dy W + dmid A
+        da = gemm(dmid, x, a_mn=True, b_mn=True, out_dtype=torch.float32) if ctx.needs_input_grad[2] else None
+        db = gemm(dy, mid, a_mn=True, b_mn=True, out_dtype=torch.float32) if ctx.needs_input_grad[3] else None
+        dw = None
+        if w.requires_grad:
+            dw = grad_into_main(w, lambda out, acc: gemm(dy, x, a_mn=True, b_mn=True, out=out, accumulate=acc))
+        return dx, dw, (da.to(a_cat.dtype) if da is not None else None), (db.to(bs.dtype) if db is not None else None), \
+            (dy if ctx.has_res else None)
+
+
+def lora_linear(x: torch.Tensor, w: torch.Tensor, a_cat: torch.Tensor, bs: torch.Tensor,
+                residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """LoRA-adapted linear for 2-D ``x``: ``x @ w^T + (x @ a_cat^T) @ bs^T (+ residual)``.  On CUDA the rank-R update
+    is accumulated inside the base projection's GEMM (the reference runs three matmuls and an add per adapted layer:
+    src/distributed/lora.py:172-177,227-235); R (the stacked rank) must be a multiple of 8 there."""
+    if not x.is_cuda or a_cat.shape[0] % 8:
+        y = torch.nn.functional.linear(x, w.to(x.dtype))
+        y = y + torch.nn.functional.linear(torch.nn.functional.linear(x, a_cat.to(x.dtype)), bs.to(x.dtype))
+        return y if residual is None else y + residual
+    if no_grad_needed(x, w, a_cat, bs, residual):
+        return gemm(x, w, residual=residual, ext=(gemm(x, a_cat), bs))
+    return _LoRALinear.apply(x, w, a_cat, bs, residual)

@@ -875,10 +875,11 @@ class _LoRAWorker:
     The engine holds plain merged weights ``W_base + s * B A``.  A sync does not re-export the model: for every
     adapted projection one low-rank GEMM updates the engine's weight rows in place,
 
-    * delta:  ``W += (s B_new) A_new + (-s B_old) A_old``   (two GEMMs of contraction length r, accumulate epilogue),
-      where ``new = old + delta`` and ``old`` is this worker's record of what the engine currently carries;
-    * full:   ``W  = W_base + s B_new A_new``                    (the trainer's frozen base rows as the residual
-      operand), which also wipes the bf16 rounding the in-place deltas have accumulated.
+    * delta:  ``W += (s B_new) A_new + (-s B_old) A_old``   (ONE GEMM per adapted module: the new and old adapters of
+      all its sub-projections stacked along the contraction, accumulate epilogue), where ``new = old + delta`` and
+      ``old`` is this worker's record of what the engine currently carries;
+    * full:   ``W  = W_base + s B_new A_new``                    (the trainer's frozen base as the residual operand),
+      which also wipes the bf16 rounding the in-place deltas have accumulated.
 
     Same role as the reference's delta application on the worker (src/transfer/swift_sync.py:181-292), which adds
     the adapter deltas into a worker-side LoRA copy and re-merges.  Under tensor parallelism the trainer holds
@@ -888,39 +889,71 @@ class _LoRAWorker:
         self.orch = orch
         self.applied: Optional[Dict[str, torch.Tensor]] = None      # adapter state the engine's weights carry
         self._plan = None
+        self.lowrank_on_cpu = False      # tests: run the low-rank path (through the ops' CPU forms) without a GPU
 
-    def _engine_rows(self, mod_name: str, tgt: str, mod):
-        """The engine model's weight rows that projection ``tgt`` of trainer module ``mod_name`` maps to."""
+    def _engine_weight(self, mod_name: str) -> torch.Tensor:
+        """The engine model's weight of the module that trainer module ``mod_name`` maps to."""
         m = self.orch.infer_engine.model
         for part in mod_name.split("."):
             m = getattr(m, part) if not part.isdigit() else m[int(part)]
-        w = m.weight
-        from ..model.qwen3 import RowParallelLinear
-        if isinstance(mod.base, RowParallelLinear):
-            return w, mod.base.weight
-        s0, e0 = mod.ranges[tgt]
-        return w[s0:e0], mod.base.weight[s0:e0]
+        return m.weight
 
     def _build_plan(self, eng):
-        """One flat fp32 image of all adapter tensors (A and B of every adapted projection, in a fixed order) with a
-        scale vector (1 on A entries, alpha/r on B entries), so that a sync is a handful of bulk tensor ops plus one
-        or two GEMM launches per projection instead of half a dozen small tensor ops per adapter."""
-        from ..model.lora import iter_lora
-        keys, shapes, offs, scale, jobs, n = [], [], [], [], [], 0
-        for name, tgt, mod, ad in iter_lora(eng.model):
-            w_rows, base_rows = self._engine_rows(name, tgt, mod)
-            ent = {}
-            for leaf, t, sc in (("lora_A", ad.lora_A, 1.0), ("lora_B", ad.lora_B, float(ad.scaling))):
-                keys.append(f"{name}.{tgt}.{leaf}")
-                shapes.append(tuple(t.shape))
-                offs.append(n)
-                ent[leaf] = (n, tuple(t.shape))
-                scale.append(torch.full((t.numel(),), sc, dtype=torch.float32))
-                n += t.numel()
-            jobs.append((ent["lora_A"], ent["lora_B"], w_rows, base_rows))
-        dev = eng.device
-        self._plan = {"keys": keys, "shapes": shapes, "offs": offs, "numel": n, "jobs": jobs,
-                      "scale": torch.cat(scale).to(dev), "flat": torch.zeros(n, dtype=torch.float32, device=dev)}
+        """Layout of a sync, built once.
+
+        * ``flat``: one fp32 image of all adapter tensors (A and B of every adapted projection, in the key order of
+          the payload) with a scale vector (1 on A entries, alpha/r on B entries).
+        * ``cat``: one bf16 buffer holding, per adapted MODULE (a fused q|k|v or gate|up layer carries several
+          adapters), the stacked operands ``Bcat [N, 2R]`` and ``Acat [2R, K]``: columns / rows ``[0, R)`` take the new
+          adapters (each B in its own row range and rank columns: block diagonal), ``[R, 2R)`` the old ones, so that
+          ``W += Bcat Acat`` is ``W += sum_i s B_i,new A_i,new - s B_i,old A_i,old`` in ONE GEMM per module.  The
+          zero blocks are never written.  ``dst_new`` / ``dst_old`` map every entry of ``flat`` to its place in
+          ``cat``: a sync fills ``cat`` with two bulk index copies, whatever the number of adapters."""
+        from ..model.lora import LinearWithLoRA
+        dev, dt = eng.device, eng.dtype
+        keys, shapes, offs, scale, n = [], [], [], [], 0
+        dst_new, dst_old, sign_old, mods, cat_n = [], [], [], [], 0
+        for name, mod in eng.model.named_modules():
+            if not isinstance(mod, LinearWithLoRA) or not mod.adapters:
+                continue
+            N, K = mod.base.weight.shape
+            order = sorted(mod.ranges.items(), key=lambda kv: kv[1][0])
+            R = sum(mod.adapters[t].rank for t, _ in order)
+            b_off, a_off = cat_n, cat_n + N * 2 * R
+            cat_n = a_off + 2 * R * K
+            r0 = 0
+            for tgt, (s0, e0) in order:
+                ad = mod.adapters[tgt]
+                r = ad.rank
+                for leaf, t, sc in (("lora_A", ad.lora_A, 1.0), ("lora_B", ad.lora_B, float(ad.scaling))):
+                    keys.append(f"{name}.{tgt}.{leaf}")
+                    shapes.append(tuple(t.shape))
+                    offs.append(n)
+                    scale.append(torch.full((t.numel(),), sc, dtype=torch.float32))
+                    n += t.numel()
+                    if leaf == "lora_A":        # [r, K] -> rows r0.. of Acat (new), rows R + r0.. (old)
+                        i = torch.arange(r)[:, None] * K + torch.arange(K)[None, :]
+                        dst_new.append((a_off + r0 * K + i).reshape(-1))
+                        dst_old.append((a_off + (R + r0) * K + i).reshape(-1))
+                        sign_old.append(torch.ones(t.numel()))
+                    else:                       # [e0 - s0, r] -> rows s0.. of Bcat, columns r0.. (new) / R + r0.. (old)
+                        i = (s0 + torch.arange(e0 - s0))[:, None] * (2 * R) + torch.arange(r)[None, :]
+                        dst_new.append((b_off + r0 + i).reshape(-1))
+                        dst_old.append((b_off + R + r0 + i).reshape(-1))
+                        sign_old.append(-torch.ones(t.numel()))
+                r0 += r
+            mods.append((name, N, K, R, b_off, a_off, mod.base.weight))
+        cat = torch.zeros(cat_n, dtype=dt, device=dev)
+        jobs = []
+        for name, N, K, R, b_off, a_off, base_w in mods:
+            bcat = cat[b_off:b_off + N * 2 * R].view(N, 2 * R)
+            acat = cat[a_off:a_off + 2 * R * K].view(2 * R, K)
+            jobs.append((bcat, acat, bcat[:, :R], acat[:R], self._engine_weight(name), base_w))
+        sc = torch.cat(scale).to(dev)
+        self._plan = {"keys": keys, "shapes": shapes, "offs": offs, "numel": n, "jobs": jobs, "scale": sc,
+                      "scale_old": sc * torch.cat(sign_old).to(dev), "cat": cat,
+                      "dst_new": torch.cat(dst_new).to(dev), "dst_old": torch.cat(dst_old).to(dev),
+                      "flat": torch.zeros(n, dtype=torch.float32, device=dev)}
         return self._plan
 
     @torch.no_grad()
@@ -928,7 +961,7 @@ class _LoRAWorker:
         from .. import ops
         orch = self.orch
         eng = orch.train_engine
-        if eng.parallel_ctx.tp_size > 1 or eng.device.type != "cuda":
+        if eng.parallel_ctx.tp_size > 1 or (eng.device.type != "cuda" and not self.lowrank_on_cpu):
             merged = orch._merged_clone()
             from ..model.hf_io import hf_named_tensors
             orch.infer_engine.load_weights(dict(hf_named_tensors(merged)))
@@ -937,25 +970,19 @@ class _LoRAWorker:
         dev, dt = eng.device, eng.dtype
         if any(k not in state for k in plan["keys"]):
             raise KeyError("SwiftSync payload does not cover every adapter tensor of the model")
-        incoming = torch.cat([state[k].reshape(-1).to(dev, torch.float32) for k in plan["keys"]])
-        old = plan["flat"]
+        incoming = torch.cat([state[k].reshape(-1) for k in plan["keys"]]).to(dev, torch.float32)
+        old, cat = plan["flat"], plan["cat"]
         delta = mode == "delta" and self.applied is not None
         new = old + incoming if delta else incoming
-        new_bf = (new * plan["scale"]).to(dt)                 # A_new and s * B_new, all adapters at once
-        old_neg = (old * (-plan["scale"])).to(dt) if delta else None    # its B entries: -s * B_old
-        old_pos = old.to(dt) if delta else None                         # its A entries: A_old
-
-        def view(buf, ent):
-            off, shape = ent
-            return buf[off:off + shape[0] * shape[1]].view(shape)
-
-        for a_ent, b_ent, w_rows, base_rows in plan["jobs"]:
+        cat.index_copy_(0, plan["dst_new"], (new * plan["scale"]).to(dt))          # A_new and s * B_new
+        if delta:
+            cat.index_copy_(0, plan["dst_old"], (old * plan["scale_old"]).to(dt))   # A_old and -s * B_old
+        for bcat, acat, b_new, a_new, w, base_w in plan["jobs"]:
             if delta:
-                # W += (s B_new) A_new + (-s B_old) A_old: two accumulate GEMMs with contraction length r
-                ops.gemm(view(new_bf, b_ent), view(new_bf, a_ent), b_mn=True, out=w_rows, accumulate=True)
-                ops.gemm(view(old_neg, b_ent), view(old_pos, a_ent), b_mn=True, out=w_rows, accumulate=True)
+                # W += [s B_new | -s B_old] [A_new ; A_old]: one accumulate GEMM of contraction length 2R per module
+                ops.gemm(bcat, acat, b_mn=True, out=w, accumulate=True)
             else:
-                ops.gemm(view(new_bf, b_ent), view(new_bf, a_ent), b_mn=True, out=w_rows, residual=base_rows)
+                ops.gemm(b_new, a_new, b_mn=True, out=w, residual=base_w)
         plan["flat"] = new
-        self.applied = {k: view(new, (o, sh)) for k, o, sh in zip(plan["keys"], plan["offs"], plan["shapes"])}
+        self.applied = {k: new[o:o + sh[0] * sh[1]].view(sh) for k, o, sh in zip(plan["keys"], plan["offs"], plan["shapes"])}
         orch.infer_engine.on_weights_updated()

@@ -171,13 +171,22 @@ __device__ __forceinline__ void reduce_rows(const __nv_bfloat16* __restrict__ re
   }
 }
 
+// Second operand pair appended along the contraction: C = A * B^T + A2 * B2^T in ONE accumulator pass (k-blocks of
+// the first pair, then of the second).  A2 is K-major [M, K2]; B2 has the layout of B ([N, K2], or [K2, N] when B is
+// MN-major).  A LoRA update rides in the base projection this way: A2 = x * A_lora^T (rank columns), B2 = scaled B_lora,
+// with no second pass over the [M, N] output.  K2 = 0: no second pair.
+struct GemmExt {
+  CUtensorMap tmA2, tmB2;
+  int K2;
+};
+
 template <int BN, bool A_MN, bool B_MN, int COMM>
 __global__ void __launch_bounds__(GEMM_THREADS + (COMM == 2 ? 128 : COMM == 1 ? 64 : 0), 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmR,
                  void* __restrict__ Cout, const __nv_bfloat16* __restrict__ R, int M, int N, int K,
                  int ldc, int flags, GemmMnDesc mn, const __grid_constant__ GemmComm comm, int* status,
-                 int split_k) {
+                 int split_k, const __grid_constant__ GemmExt ext) {
   using Cfg = GemmCfg<BN>;
   static_assert(COMM == 0 || !A_MN, "fused communication paths take a K-major A operand");
   extern __shared__ uint8_t smem_raw[];
@@ -201,6 +210,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int num_n = (N + BN - 1) / BN;
   const int num_tiles = num_m * num_n;
   const int num_kb = (K + GEMM_BK - 1) / GEMM_BK;
+  const int num_kb2 = (COMM == 0 && !A_MN && split_k == 1) ? (ext.K2 + GEMM_BK - 1) / GEMM_BK : 0;
   // Split-K (fp32 accumulate outputs only): a work unit is (tile, K slice); unit u covers tile
   // u % num_tiles and k-blocks [ks * num_kb / split_k, (ks + 1) * num_kb / split_k) with ks = u / num_tiles,
   // and its epilogue adds into C with fp32 atomics.  Weight-gradient GEMMs have few output tiles and a
@@ -311,6 +321,28 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             phase ^= 1;
           }
         }
+        // the second operand pair's k-blocks (rows past K2 are filled with zeros by the TMA unit)
+        for (int kb = 0; kb < num_kb2 && ok; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, status, ERR_GEMM_PRODUCER_WAIT, LIM)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sA = smem + stage * Cfg::STAGE_BYTES;
+          uint8_t* sB = sA + Cfg::A_BYTES;
+          mbar_expect_tx(&full_bar[stage], Cfg::STAGE_BYTES);
+          tma_load_2d(sA, &ext.tmA2, &full_bar[stage], kb * GEMM_BK, m0);
+          if (!B_MN) {
+            tma_load_2d(sB, &ext.tmB2, &full_bar[stage], kb * GEMM_BK, n0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(sB + c * 8192, &ext.tmB2, &full_bar[stage], n0 + c * 64, kb * GEMM_BK);
+          }
+          if (++stage == Cfg::STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
       }
     }
   } else if (warp == 1) {
@@ -327,7 +359,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (!mbar_wait(&tmem_empty[acc], acc_phase ^ 1, status, ERR_GEMM_MMA_WAIT_TMEM, LIM)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = kb_begin; kb < kb_end; ++kb) {
+        for (int kb = kb_begin; kb < kb_end + num_kb2; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, status, ERR_GEMM_MMA_WAIT_FULL, LIM)) {
             ok = false;
             break;
@@ -339,10 +371,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           const uint64_t b0 = B_MN ? make_smem_desc_sw128(b_base, mn.lbo, mn.sbo) : make_smem_desc_sw128(b_base, 16, 1024);
           const uint32_t a_step = A_MN ? mn.kstep : 32u, b_step = B_MN ? mn.kstep : 32u;
           const uint32_t acc0 = kb != kb_begin ? 1u : 0u;
+          // a k-block of the second pair holds K2 - 64 * i valid columns: skip the 16-wide steps that are all zeros
+          const int ksteps = kb < kb_end ? GEMM_BK / 16 : min(GEMM_BK / 16, (ext.K2 - (kb - kb_end) * GEMM_BK + 15) / 16);
           if (leader) {
 #pragma unroll
             for (int k = 0; k < GEMM_BK / 16; ++k)
-              umma_f16_ss(d_tmem, desc_advance(a0, k * a_step), desc_advance(b0, k * b_step), idesc, k ? 1u : acc0);
+              if (k < ksteps)
+                umma_f16_ss(d_tmem, desc_advance(a0, k * a_step), desc_advance(b0, k * b_step), idesc, k ? 1u : acc0);
             umma_commit(&empty_bar[stage]);
           }
           if (++stage == Cfg::STAGES) {
@@ -711,7 +746,8 @@ static GemmMnDesc g_mn_desc = {8192u, 1024u, 2048u};
 template <int BN, bool A_MN, bool B_MN, int COMM = 0>
 static int launch_gemm(const void* A, const void* B, void* C, const void* R, int M, int N, int K,
                        int lda, int ldb, int ldc, int flags, int max_ctas, cudaStream_t stream,
-                       const GemmComm* comm_in = nullptr) {
+                       const GemmComm* comm_in = nullptr, const void* A2 = nullptr, const void* B2 = nullptr,
+                       int K2 = 0, int lda2 = 0, int ldb2 = 0) {
   using Cfg = GemmCfg<BN>;
   auto kern = gemm_bf16_kernel<BN, A_MN, B_MN, COMM>;
   GemmComm comm;
@@ -772,9 +808,26 @@ static int launch_gemm(const void* A, const void* B, void* C, const void* R, int
     }
   }
   if (num_tiles * split_k < grid) grid = num_tiles * split_k;
+  GemmExt ext;
+  ext.tmA2 = *ta;
+  ext.tmB2 = *tb;
+  ext.K2 = 0;
+  if (K2 > 0) {
+    if (COMM != 0 || A_MN || split_k != 1) {
+      set_error("gemm: a second operand pair needs a K-major A, no split-K and no fused collective");
+      return 6;
+    }
+    const CUtensorMap* ta2 = tensor_map_2d_bf16(A2, M, K2, lda2, GEMM_BM, 64);
+    const CUtensorMap* tb2 = B_MN ? tensor_map_2d_bf16(B2, K2, N, ldb2, 64, 64)
+                                  : tensor_map_2d_bf16(B2, N, K2, ldb2, BN, 64);
+    if (!ta2 || !tb2) return 2;
+    ext.tmA2 = *ta2;
+    ext.tmB2 = *tb2;
+    ext.K2 = K2;
+  }
   kern<<<grid, GEMM_THREADS + (COMM == 2 ? 128 : COMM == 1 ? 64 : 0), Cfg::SMEM_BYTES, stream>>>(
       *ta, *tb, *tc, *tr, C, reinterpret_cast<const __nv_bfloat16*>(R), M, N, K, ldc, flags, g_mn_desc, comm, status,
-      split_k);
+      split_k, ext);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_error("gemm launch failed: %s", cudaGetErrorString(e));
@@ -825,6 +878,51 @@ B2_EXPORT int b2_gemm_bf16(const void* A, const void* B, void* C, const void* R,
   B2_GEMM_CASE(128, 1, 0)
 #undef B2_GEMM_CASE
   set_error("gemm: unsupported configuration bn=%d a_mn=%d b_mn=%d", bn, a_mn, b_mn);
+  return 11;
+}
+
+// C[M,N] = A * B^T + A2 * B2^T (+ R) with both products in one accumulator pass (see GemmExt).  A and A2 are K-major
+// ([M, K], [M, K2]); B2 has B's layout.  K2 and both leading dimensions must be multiples of 8 elements.  Output bf16
+// (flags: 2 accumulate into C, 4 add residual R) or fp32 (flag 1, no split-K).
+B2_EXPORT int b2_gemm_bf16_ext(const void* A, const void* B, void* C, const void* R, int M, int N, int K, int lda,
+                               int ldb, int ldc, int b_mn, int flags, int bn, const void* A2, const void* B2, int K2,
+                               int lda2, int ldb2, void* stream_) {
+  b2::ensure_thread_context();
+  using namespace b2;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  const bool out_fp32 = flags & GEMM_OUT_FP32;
+  if ((lda % 8) || (ldb % 8) || (ldc % (out_fp32 ? 4 : 8)) || (reinterpret_cast<uintptr_t>(A) & 15) ||
+      (reinterpret_cast<uintptr_t>(B) & 15) || (reinterpret_cast<uintptr_t>(C) & 15) ||
+      ((flags & GEMM_RESIDUAL) && (R == nullptr || (reinterpret_cast<uintptr_t>(R) & 15)))) {
+    set_error("gemm_ext: operands need 16-byte aligned bases and leading dimensions (lda %d ldb %d ldc %d)", lda, ldb, ldc);
+    return 10;
+  }
+  if (K2 <= 0 || (K2 % 8) || A2 == nullptr || B2 == nullptr || (lda2 % 8) || (ldb2 % 8) ||
+      (reinterpret_cast<uintptr_t>(A2) & 15) || (reinterpret_cast<uintptr_t>(B2) & 15)) {
+    set_error("gemm_ext: the second pair needs K2 %% 8 == 0 and 16-byte aligned operands (K2 %d lda2 %d ldb2 %d)", K2,
+              lda2, ldb2);
+    return 10;
+  }
+  if (out_fp32 && !(flags & GEMM_RESIDUAL)) {
+    set_error("gemm_ext: fp32 outputs may split K, which the second pair does not support");
+    return 10;
+  }
+  if (bn == 0) {
+    const int sms = num_sms();
+    const int tiles256 = ((M + 127) / 128) * ((N + 255) / 256);
+    bn = (tiles256 >= sms || N % 256 == 0) && tiles256 * 2 > sms ? 256 : 128;
+  }
+#define B2_GEMM_EXT_CASE(BN_, BMN_)                                                                              \
+  if (bn == BN_ && b_mn == BMN_)                                                                                 \
+    return launch_gemm<BN_, false, BMN_ != 0>(A, B, C, R, M, N, K, lda, ldb, ldc, flags, 0, stream, nullptr, A2, B2, \
+                                              K2, lda2, ldb2);
+  B2_GEMM_EXT_CASE(256, 0)
+  B2_GEMM_EXT_CASE(256, 1)
+  B2_GEMM_EXT_CASE(128, 0)
+  B2_GEMM_EXT_CASE(128, 1)
+#undef B2_GEMM_EXT_CASE
+  set_error("gemm_ext: unsupported configuration bn=%d b_mn=%d", bn, b_mn);
   return 11;
 }
 

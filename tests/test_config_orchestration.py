@@ -579,3 +579,49 @@ def test_ray_object_store_transfer_against_a_stand_in_ray(monkeypatch):
     m = WeightTransferManager("ray_object_store")
     assert m.sync_weights(True, state) == 1
     assert m.sync_weights(False, engine=Eng()) == 2 and torch.equal(loaded["b"], state["b"])
+
+
+def test_swiftsync_low_rank_worker_keeps_engine_equal_to_merged_export(tmp_path):
+    """The colocated SwiftSync worker's plan (stacked per-module operands filled by two bulk index copies, one GEMM per
+    module) run through the ops' CPU forms: after delta and full syncs the engine's weights equal a fresh merged
+    export, the trainer's frozen base never moves."""
+    import asyncio
+    from b200fw.config import ColocateConfig
+    from b200fw.model.hf_io import hf_named_tensors
+    from b200fw.model.lora import LinearWithLoRA
+    from b200fw.orch import ColocateOrchestrator
+    cfg = ColocateConfig(model_preset="tiny", training_mode="grpo", total_iterations=1, batch_size=2,
+                         num_samples_per_prompt=2, max_tokens=4, lora_rank=8, lora_alpha=16.0, grpo_beta=0.0,
+                         gradient_accumulation_steps=1, zero_stage=1, inference_backend="native", synthetic_data=True,
+                         synthetic_prompt_len=8, max_seq_len=16, max_data_samples=8, swift_sync_enabled=True,
+                         swift_sync_fallback_full_every=3, warmup_steps=0, checkpoint_save_enabled=False,
+                         output_dir=str(tmp_path), tensorboard=False, kv_num_blocks=32, amp_dtype="fp32")
+
+    async def go():
+        o = ColocateOrchestrator(cfg)
+        await o.initialize()
+        return o
+
+    o = asyncio.run(go())
+    eng = o.train_engine
+    o.swift.worker.lowrank_on_cpu = True
+    mods = [m for m in eng.model.modules() if isinstance(m, LinearWithLoRA)]
+    assert any(len(m.adapters) > 1 for m in mods)             # fused q|k|v / gate|up: several adapters per module
+    base0 = [m.base.weight.detach().clone() for m in mods]
+    g = torch.Generator().manual_seed(3)
+    modes = []
+    for it in range(5):
+        with torch.no_grad():
+            for m in mods:
+                for ad in m.adapters.values():
+                    ad.lora_A.add_(0.05 * torch.randn(ad.lora_A.shape, generator=g))
+                    ad.lora_B.add_(0.05 * torch.randn(ad.lora_B.shape, generator=g))
+        o._sync_weights(it)
+        modes.append(o.swift.stats.last_mode)
+        got, want = dict(hf_named_tensors(o.infer_engine.model)), eng.export_weights()
+        for k, v in want.items():
+            assert torch.allclose(got[k].float(), v.float(), atol=2e-4, rtol=1e-4), (it, modes, k)
+    assert "delta" in modes and "full" in modes
+    assert o.swift.worker._plan is not None
+    for m, w0 in zip(mods, base0):
+        assert torch.equal(m.base.weight, w0)

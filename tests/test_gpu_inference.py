@@ -277,16 +277,20 @@ def test_speculative_decoding_is_lossless_under_greedy(gpu_model):
     assert e.get_stats()["spec_rounds"] > 0
 
 
-def test_inference_kernels_write_only_inside_their_outputs():
-    """KV store, paged decode (split and unsplit, fp8 and bf16), variable-length prefill attention and the
-    sampler, run with guard bands around every tensor the ops allocate."""
+def test_inference_kernels_write_only_inside_their_outputs(monkeypatch):
+    """KV store (separate and fused into the norm + RoPE kernel), paged decode (split and unsplit, fp8 and bf16, every
+    row-loop variant), variable-length prefill attention and the sampler, run with guard bands around every tensor
+    the ops allocate."""
     from b200fw.ops.debug import canary_arena
     with canary_arena() as arena:
         test_kv_store_and_gather(False)
         test_kv_store_and_gather(True)
-        test_paged_decode_attention(False, 4, 2, (0, 1))
-        test_paged_decode_attention(True, 8, 1, (64, 0))
-        test_paged_decode_attention(False, 2, 2, (64, 0))
+        test_qknorm_rope_store_equals_the_two_launch_form(3, 3)
+        test_paged_decode_attention(False, 4, 2, (0, 1), "0", monkeypatch)
+        test_paged_decode_attention(True, 8, 1, (64, 0), "3", monkeypatch)
+        test_paged_decode_attention(False, 2, 2, (64, 0), "3", monkeypatch)
+        test_paged_decode_attention(False, 4, 2, (0, 1), "4", monkeypatch)
+        test_paged_decode_attention(True, 2, 2, (0, 1), "1", monkeypatch)
         test_varlen_attention_with_context_offset([(16, 300), (3, 131), (77, 77)])
         test_varlen_attention_with_context_offset([(1, 513)])
         test_topp_sampler_distribution_and_greedy()

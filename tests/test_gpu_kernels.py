@@ -70,6 +70,77 @@ def test_gemm_split_k_fp32_weight_gradient_shapes(M, N, K):
     assert relerr(wide[:, :N], ref) < 1e-4 and float((wide[:, N:] - 3.0).abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("b_mn", [0, 1])
+@pytest.mark.parametrize("shape", [(512, 768, 256, 16), (1000, 776, 520, 48), (136, 72, 2056, 8), (300, 256, 64, 136)])
+@pytest.mark.parametrize("bn", [0, 128, 256])
+def test_gemm_with_second_operand_pair(b_mn, shape, bn):
+    """C = A B^T + A2 B2^T (+ R) in one accumulator pass: the second pair's k-blocks follow the first pair's; K2 below,
+    at and above one 64-wide k-block; bf16 and (with a residual) fp32 outputs."""
+    from b200fw.ops import gemm
+    torch.manual_seed(5)
+    M, N, K, K2 = shape
+    A = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    B = torch.randn((K, N) if b_mn else (N, K), device=DEV, dtype=torch.bfloat16)
+    A2 = torch.randn(M, K2, device=DEV, dtype=torch.bfloat16)
+    B2 = torch.randn((K2, N) if b_mn else (N, K2), device=DEV, dtype=torch.bfloat16)
+    R = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    ref = A.float() @ (B.float() if b_mn else B.float().t()) + A2.float() @ (B2.float() if b_mn else B2.float().t())
+    assert relerr(gemm(A, B, b_mn=bool(b_mn), bn=bn, ext=(A2, B2)), ref) < 1e-2
+    assert relerr(gemm(A, B, b_mn=bool(b_mn), bn=bn, ext=(A2, B2), residual=R), ref + R.float()) < 1e-2
+    # operands that are column slices of wider buffers (row stride != width)
+    wide_a2 = torch.randn(M, K2 + 24, device=DEV, dtype=torch.bfloat16)
+    wide_a2[:, :K2] = A2
+    assert relerr(gemm(A, B, b_mn=bool(b_mn), bn=bn, ext=(wide_a2[:, :K2], B2)), ref) < 1e-2
+
+
+def test_lora_linear_matches_the_three_gemm_form():
+    from b200fw.ops import lora_linear
+    torch.manual_seed(6)
+    M, K, N, Rk = 640, 512, 768, 24
+    mk = lambda *sh, s=1.0: (s * torch.randn(*sh, device=DEV)).to(torch.bfloat16).requires_grad_()
+    x, a, b, r = mk(M, K), mk(Rk, K, s=0.1), mk(N, Rk, s=0.1), mk(M, N)
+    w = torch.randn(N, K, device=DEV, dtype=torch.bfloat16)          # frozen base
+    y = lora_linear(x, w, a, b, r)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xf, af, bf_, rf = [t.detach().float().requires_grad_() for t in (x, a, b, r)]
+    yf = xf @ w.float().t() + (xf @ af.t()) @ bf_.t() + rf
+    yf.backward(g.float())
+    assert relerr(y, yf) < 1e-2
+    for got, want in ((x.grad, xf.grad), (a.grad, af.grad), (b.grad, bf_.grad), (r.grad, rf.grad)):
+        assert relerr(got, want) < 2e-2
+    with torch.no_grad():
+        assert relerr(lora_linear(x, w, a, b), yf - rf) < 1e-2
+
+
+def test_lora_model_fused_and_unfused_paths_agree():
+    """A LoRA model's loss and adapter gradients with the rank-R update inside the base GEMMs against the same model
+    with base projection + two adapter GEMMs."""
+    from b200fw.model import PRESETS, ParallelTransformerModel, apply_lora
+    from b200fw.model.lora import LinearWithLoRA
+    torch.manual_seed(0)
+    m = ParallelTransformerModel(PRESETS["tiny128"], dtype=torch.bfloat16, device=torch.device(DEV))
+    m.init_weights(0)
+    apply_lora(m, rank=8, alpha=16.0)
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if "lora_B" in n:
+                p.normal_(0, 0.05)
+    ids = torch.randint(0, 8192, (2, 128), device=DEV)
+    out = {}
+    for fused in (True, False):
+        for mod in m.modules():
+            if isinstance(mod, LinearWithLoRA):
+                mod.fuse_into_base = fused
+        m.zero_grad(set_to_none=True)
+        loss = m.loss(ids, ids)
+        loss.backward()
+        out[fused] = (loss.item(), {n: p.grad.float().clone() for n, p in m.named_parameters() if p.requires_grad})
+    assert abs(out[True][0] - out[False][0]) < 2e-2 * abs(out[False][0])
+    worst = max(relerr(out[True][1][n], out[False][1][n]) for n in out[True][1])
+    assert worst < 5e-2, worst
+
+
 def test_linear_autograd():
     from b200fw.ops import linear
     torch.manual_seed(2)

@@ -238,3 +238,26 @@ def test_lora_tp2_sequence_parallel_gradients_match_unsharded():
     with tempfile.TemporaryDirectory() as d:
         _full_model(d)
         run_ranks(_lora_sp_worker, 2, d)
+
+
+def test_lora_linear_autograd_function_against_plain_autograd():
+    """The fused LoRA linear's hand-written backward (run here through the GEMM op's CPU forms): gradients of x, the
+    stacked adapters and the residual against autograd of the plain formula."""
+    from b200fw.ops.gemm import _LoRALinear, gemm
+    torch.manual_seed(1)
+    M, K, N, R = 40, 24, 56, 16
+    x, a, b, r = [torch.randn(*sh, requires_grad=True) for sh in ((M, K), (R, K), (N, R), (M, N))]
+    w = torch.randn(N, K)
+    y = _LoRALinear.apply(x, w, a, b, r)
+    g = torch.randn(M, N)
+    y.backward(g)
+    x2, a2, b2, r2 = [t.detach().clone().requires_grad_() for t in (x, a, b, r)]
+    y2 = x2 @ w.t() + (x2 @ a2.t()) @ b2.t() + r2
+    y2.backward(g)
+    assert torch.allclose(y, y2, atol=1e-4)
+    for got, want in ((x.grad, x2.grad), (a.grad, a2.grad), (b.grad, b2.grad), (r.grad, r2.grad)):
+        assert torch.allclose(got, want, atol=1e-4, rtol=1e-4)
+    # the extended GEMM by itself, both layouts of the second operand
+    A2, B2 = torch.randn(M, R), torch.randn(N, R)
+    assert torch.allclose(gemm(x.detach(), w, ext=(A2, B2)), x.detach() @ w.t() + A2 @ B2.t(), atol=1e-4)
+    assert torch.allclose(gemm(g, w, b_mn=True, ext=(A2, a.detach())), g @ w + A2 @ a.detach(), atol=1e-4)
