@@ -10,6 +10,7 @@ Adapter parameters are fp32; the low-rank products run in the activation dtype.
 from __future__ import annotations
 
 import math
+import os
 from typing import Dict, Iterable, List, Optional, Tuple
 
 import torch
@@ -84,7 +85,15 @@ class LinearWithLoRA(nn.Module):
         self.adapters = nn.ModuleDict({k: v[0] for k, v in adapters.items()})
         self.ranges = {k: (v[1], v[2]) for k, v in adapters.items()}
         self.merged = False
-        self.fuse_into_base = True      # False: base projection, then two adapter GEMMs (the only form under TP)
+        # False (or B200FW_LORA_FUSE=0): base projection, then two adapter GEMMs (the only form under TP)
+        self.fuse_into_base = os.environ.get("B200FW_LORA_FUSE", "1") != "0"
+        self._plan_cache = None
+        if getattr(base, "tp_size", 1) == 1 and self.fuse_into_base:
+            # the fused op writes these parameters' gradients itself (into the optimizer's bucket views when it has
+            # them): an optimizer may bind ``main_grad`` buffers to them as it does for bf16 weights
+            for ad in self.adapters.values():
+                ad.lora_A.direct_grad = True
+                ad.lora_B.direct_grad = True
 
     @property
     def weight(self):
@@ -125,6 +134,23 @@ class LinearWithLoRA(nn.Module):
             r0 += ad.rank
         return a_cat, b_bd
 
+    def _total_rank(self) -> int:
+        return sum(ad.rank for ad in self.adapters.values())
+
+    def _grad_plan(self):
+        """``(rank offset, rank, first row, last row, scaling)`` per adapter in the stacking order of ``_stacked``, and
+        the adapters' parameters ``A_0, B_0, A_1, B_1, ...``: how the fused op hands the stacked gradients back."""
+        if self._plan_cache is None:
+            order = sorted(self.ranges.items(), key=lambda kv: kv[1][0])
+            plan, params, r0 = [], [], 0
+            for name, (s0, e0) in order:
+                ad = self.adapters[name]
+                plan.append((r0, ad.rank, s0, e0, float(ad.scaling)))
+                params += [ad.lora_A, ad.lora_B]
+                r0 += ad.rank
+            self._plan_cache = (tuple(plan), tuple(params))
+        return self._plan_cache
+
     def forward(self, x, residual=None):
         from .. import ops
         base = self.base
@@ -133,13 +159,17 @@ class LinearWithLoRA(nn.Module):
             return base(x, residual) if is_row else base(x)
         tp, grp, sp = base.tp_size, base.tp_group, base.sequence_parallel
         x2 = x.reshape(-1, x.shape[-1])
-        a_cat, b_bd = self._stacked(x2.dtype)
-        if (self.fuse_into_base and tp == 1 and x2.is_cuda and base.bias is None and a_cat.shape[0] % 8 == 0
-                and x2.dtype == torch.bfloat16):
+        fused = (self.fuse_into_base and tp == 1 and x2.is_cuda and base.bias is None and self._total_rank() % 8 == 0
+                 and x2.dtype == torch.bfloat16)
+        with torch.set_grad_enabled(torch.is_grad_enabled() and not fused):
+            a_cat, b_bd = self._stacked(x2.dtype)        # fused: no autograd graph through the stacking
+        if fused:
             # one device: the rank-R update rides in the base projection's GEMM (forward and input gradient), the
             # frozen base weight gets no gradient GEMM at all
+            plan, params = self._grad_plan()
             y = ops.lora_linear(x2 if x2.is_contiguous() else x2.contiguous(), base.weight, a_cat.contiguous(), b_bd,
-                                residual.reshape(-1, base.weight.shape[0]) if residual is not None else None)
+                                residual.reshape(-1, base.weight.shape[0]) if residual is not None else None,
+                                plan=plan, params=params)
             return y.reshape(*x.shape[:-1], y.shape[-1])
         y = base(x, residual) if is_row else base(x)
         if is_row:
@@ -246,6 +276,23 @@ def get_lora_state_dict(model: nn.Module) -> Dict[str, torch.Tensor]:
         out[f"{name}.{tgt}.lora_A"] = ad.lora_A.detach()
         out[f"{name}.{tgt}.lora_B"] = ad.lora_B.detach()
     return out
+
+
+@torch.no_grad()
+def flat_lora_state(model: nn.Module):
+    """The same content as :func:`get_lora_state_dict` as a :class:`b200fw.sync.double_buffer.FlatState`: one fp32
+    tensor holding a COPY of every adapter tensor back to back (one concatenation), with the named tensors as views
+    on demand.  The layout is computed once per model."""
+    from ..sync.double_buffer import FlatLayout, FlatState
+    cache = model.__dict__.get("_flat_lora_cache")
+    if cache is None:
+        keys, params = [], []
+        for name, tgt, _, ad in iter_lora(model):
+            keys += [f"{name}.{tgt}.lora_A", f"{name}.{tgt}.lora_B"]
+            params += [ad.lora_A, ad.lora_B]
+        cache = model.__dict__["_flat_lora_cache"] = (FlatLayout(keys, [p.shape for p in params]), params)
+    layout, params = cache
+    return FlatState(layout, torch.cat([p.detach().reshape(-1).float() for p in params]))
 
 
 @torch.no_grad()

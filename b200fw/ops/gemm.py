@@ -149,40 +149,71 @@ def linear(x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor] = 
 class _LoRALinear(torch.autograd.Function):
     """``y = x W^T + (x A^T) Bs^T (+ residual)`` with the low-rank product riding in the base GEMM's accumulator
     (``gemm(..., ext=...)``), forward and input-gradient alike.  ``a_cat [R, K]`` and ``bs [N, R]`` (B already times
-    its scaling) are the layer's stacked adapters in the activation dtype; ``w`` is the frozen base weight."""
+    its scaling) are the layer's stacked adapters in the activation dtype; ``w`` is the frozen base weight.
+
+    Two ways to receive the adapter gradients.  ``plan is None``: ``a_cat`` and ``bs`` are differentiable inputs and
+    get ``[R, K]`` / ``[N, R]`` gradients.  Otherwise ``a_cat`` / ``bs`` were built without autograd, ``plan`` lists
+    ``(rank offset, rank, first row, last row, scaling)`` per adapter and ``params`` are the adapters' own fp32
+    ``A_0, B_0, A_1, B_1, ...``: each gets its slice of the stacked gradient, written straight into its
+    ``main_grad`` bucket view when the optimizer provides one (no autograd graph through the stacking, and the
+    micro-step stays CUDA-graph capturable)."""
 
     @staticmethod
-    def forward(ctx, x, w, a_cat, bs, residual):
+    def forward(ctx, x, w, a_cat, bs, residual, plan, *params):
         mid = gemm(x, a_cat)                                     # [M, R]
         y = gemm(x, w, residual=residual, ext=(mid, bs))
         ctx.save_for_backward(x, w, a_cat, bs, mid)
-        ctx.has_res = residual is not None
+        ctx.has_res, ctx.plan, ctx.params = residual is not None, plan, params
         return y
 
     @staticmethod
     def backward(ctx, dy):
         x, w, a_cat, bs, mid = ctx.saved_tensors
+        plan, params = ctx.plan, ctx.params
         dy = dy if dy.stride(-1) == 1 else dy.contiguous()
         dmid = gemm(dy, bs, b_mn=True)                           # [M, R] = dy @ Bs
         dx = gemm(dy, w, b_mn=True, ext=(dmid, a_cat)) if ctx.needs_input_grad[0] else None    # dy W + dmid A
-        da = gemm(dmid, x, a_mn=True, b_mn=True, out_dtype=torch.float32) if ctx.needs_input_grad[2] else None
-        db = gemm(dy, mid, a_mn=True, b_mn=True, out_dtype=torch.float32) if ctx.needs_input_grad[3] else None
+        want_ab = plan is not None or ctx.needs_input_grad[2] or ctx.needs_input_grad[3]
+        da = gemm(dmid, x, a_mn=True, b_mn=True, out_dtype=torch.float32) if want_ab else None     # [R, K]
+        db = gemm(dy, mid, a_mn=True, b_mn=True, out_dtype=torch.float32) if want_ab else None     # [N, R]
         dw = None
         if w.requires_grad:
             dw = grad_into_main(w, lambda out, acc: gemm(dy, x, a_mn=True, b_mn=True, out=out, accumulate=acc))
-        return dx, dw, (da.to(a_cat.dtype) if da is not None else None), (db.to(bs.dtype) if db is not None else None), \
-            (dy if ctx.has_res else None)
+        head = (dx, dw, None, None, dy if ctx.has_res else None, None)
+        if plan is None:
+            return (dx, dw, da.to(a_cat.dtype) if ctx.needs_input_grad[2] else None,
+                    db.to(bs.dtype) if ctx.needs_input_grad[3] else None, dy if ctx.has_res else None, None)
+        grads = []
+        for i, (r0, r, s0, e0, sc) in enumerate(plan):
+            pa, pb = params[2 * i], params[2 * i + 1]
+            ga, gb = da[r0:r0 + r], db[s0:e0, r0:r0 + r]
+
+            def into_a(out, acc, g=ga):
+                if out is None:
+                    return g.clone()
+                return out.add_(g) if acc else out.copy_(g)
+
+            def into_b(out, acc, g=gb, s_=sc):
+                if out is None:
+                    return g * s_
+                return out.add_(g, alpha=s_) if acc else torch.mul(g, s_, out=out)
+
+            grads.append(grad_into_main(pa, into_a) if pa.requires_grad else None)
+            grads.append(grad_into_main(pb, into_b) if pb.requires_grad else None)
+        return head + tuple(grads)
 
 
 def lora_linear(x: torch.Tensor, w: torch.Tensor, a_cat: torch.Tensor, bs: torch.Tensor,
-                residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+                residual: Optional[torch.Tensor] = None, plan=None, params=()) -> torch.Tensor:
     """LoRA-adapted linear for 2-D ``x``: ``x @ w^T + (x @ a_cat^T) @ bs^T (+ residual)``.  On CUDA the rank-R update
     is accumulated inside the base projection's GEMM (the reference runs three matmuls and an add per adapted layer:
-    src/distributed/lora.py:172-177,227-235); R (the stacked rank) must be a multiple of 8 there."""
+    src/distributed/lora.py:172-177,227-235); R (the stacked rank) must be a multiple of 8 there.  ``plan`` /
+    ``params``: see :class:`_LoRALinear`."""
     if not x.is_cuda or a_cat.shape[0] % 8:
+        assert plan is None, "the per-adapter gradient plan belongs to the CUDA path"
         y = torch.nn.functional.linear(x, w.to(x.dtype))
         y = y + torch.nn.functional.linear(torch.nn.functional.linear(x, a_cat.to(x.dtype)), bs.to(x.dtype))
         return y if residual is None else y + residual
-    if no_grad_needed(x, w, a_cat, bs, residual):
+    if no_grad_needed(x, w, a_cat, bs, residual, *params):
         return gemm(x, w, residual=residual, ext=(gemm(x, a_cat), bs))
-    return _LoRALinear.apply(x, w, a_cat, bs, residual)
+    return _LoRALinear.apply(x, w, a_cat, bs, residual, plan, *params)

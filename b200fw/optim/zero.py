@@ -141,7 +141,9 @@ class ZeROOptimizer:
         self.dtype = params[0].dtype
         self.on_cuda = self.device.type == "cuda"
         # gradient-accumulation fusion (GEMM epilogues write into bucket buffers) needs the kernels
-        self.use_main_grad = self.on_cuda and self.dtype == torch.bfloat16
+        # (bf16 weights), or parameters whose op writes its gradient itself (``direct_grad``: fused LoRA adapters)
+        self.use_main_grad = self.on_cuda and (self.dtype == torch.bfloat16
+                                               or all(getattr(p, "direct_grad", False) for p in params))
         self.grad_dtype = grad_dtype or (torch.bfloat16 if self.dtype == torch.bfloat16 else torch.float32)
         self.overlap = overlap and self.on_cuda
         self.comm_stream = torch.cuda.Stream(device=self.device, priority=-1) if self.overlap else None
@@ -456,10 +458,29 @@ class ZeROOptimizer:
                 self._release_params()
             self._prepare_backward()
 
+    def _fold_autograd_grads(self):
+        """``main_grad`` mode: a gradient that arrived through plain autograd after all (a layer took a path without
+        the fused epilogue) is added into its bucket view; nothing is lost by mixing the two routes."""
+        for b in self.buckets:
+            for p in b.params:
+                g = p.grad
+                if g is None:
+                    continue
+                mg = getattr(p, "main_grad", None)
+                if mg is not None:
+                    if getattr(p, "grad_filled", False):
+                        mg.add_(g.to(mg.dtype))
+                    else:
+                        mg.copy_(g)
+                        p.grad_filled = True
+                p.grad = None
+
     def _reduce_all(self):
         if not all(b.reduced for b in self.buckets):
             if not self.use_main_grad:
                 self._pack_autograd_grads()
+            else:
+                self._fold_autograd_grads()
             for b in self.buckets:
                 if not b.reduced:
                     self._launch_reduce(b, async_op=False)

@@ -368,8 +368,8 @@ class ColocateOrchestrator:
             self.weights_version += 1
             return self.weights_version
         if self.swift is not None:
-            from ..model import get_lora_state_dict
-            self.swift.sync(iteration, get_lora_state_dict(eng.model))
+            from ..model.lora import flat_lora_state
+            self.swift.sync(iteration, flat_lora_state(eng.model))
         else:
             state = eng.export_weights()
             self.weight_sync.sync(True, state, self.infer_engine)
@@ -950,7 +950,9 @@ class _LoRAWorker:
             acat = cat[a_off:a_off + 2 * R * K].view(2 * R, K)
             jobs.append((bcat, acat, bcat[:, :R], acat[:R], self._engine_weight(name), base_w))
         sc = torch.cat(scale).to(dev)
+        from ..sync.double_buffer import FlatLayout
         self._plan = {"keys": keys, "shapes": shapes, "offs": offs, "numel": n, "jobs": jobs, "scale": sc,
+                      "layout": FlatLayout(keys, shapes),
                       "scale_old": sc * torch.cat(sign_old).to(dev), "cat": cat,
                       "dst_new": torch.cat(dst_new).to(dev), "dst_old": torch.cat(dst_old).to(dev),
                       "flat": torch.zeros(n, dtype=torch.float32, device=dev)}
@@ -970,7 +972,11 @@ class _LoRAWorker:
         dev, dt = eng.device, eng.dtype
         if any(k not in state for k in plan["keys"]):
             raise KeyError("SwiftSync payload does not cover every adapter tensor of the model")
-        incoming = torch.cat([state[k].reshape(-1) for k in plan["keys"]]).to(dev, torch.float32)
+        from ..sync.double_buffer import FlatState
+        if isinstance(state, FlatState) and state.layout.keys == tuple(plan["keys"]):
+            incoming = state.flat.to(dev, torch.float32)          # already one tensor in the plan's order
+        else:
+            incoming = torch.cat([state[k].reshape(-1) for k in plan["keys"]]).to(dev, torch.float32)
         old, cat = plan["flat"], plan["cat"]
         delta = mode == "delta" and self.applied is not None
         new = old + incoming if delta else incoming
@@ -984,5 +990,5 @@ class _LoRAWorker:
             else:
                 ops.gemm(b_new, a_new, b_mn=True, out=w, residual=base_w)
         plan["flat"] = new
-        self.applied = {k: new[o:o + sh[0] * sh[1]].view(sh) for k, o, sh in zip(plan["keys"], plan["offs"], plan["shapes"])}
+        self.applied = FlatState(plan["layout"], new)       # name -> view of the image, made when asked for
         orch.infer_engine.on_weights_updated()

@@ -15,7 +15,7 @@ from typing import Dict, List, Optional
 
 import torch
 
-from .double_buffer import DoubleBufferedLoRA
+from .double_buffer import DoubleBufferedLoRA, FlatState
 
 
 @dataclass
@@ -148,6 +148,14 @@ class DeltaComputer:
         self._step_count += 1
         if prev is not None:
             return {k: v.detach() - prev[k].to(v.device) if k in prev else v.detach().clone() for k, v in current.items()}
+        if isinstance(current, FlatState):
+            # one subtraction for all adapters; ``current.flat`` is the caller's fresh copy and becomes the snapshot
+            if isinstance(self.prev, FlatState) and self.prev.same_layout(current):
+                delta = FlatState(current.layout, current.flat - self.prev.flat)
+            else:
+                delta = current.clone()
+            self.prev = current
+            return delta
         keys = list(current)
         cur = [current[k].detach() for k in keys]
         if self.prev is not None and list(self.prev) == keys and all(
@@ -174,6 +182,8 @@ class DeltaComputer:
 
 
 def _nbytes(state: Dict[str, torch.Tensor]) -> int:
+    if isinstance(state, FlatState):
+        return state.flat.numel() * state.flat.element_size()
     return sum(v.numel() * v.element_size() for v in state.values())
 
 
@@ -234,7 +244,8 @@ class SwiftSyncTransfer:
         t0 = time.perf_counter()
         self._notify(state, "full")
         v = self._commit(state, "full")
-        self.delta_computer.prev = {k: t.detach().clone() for k, t in state.items()}
+        self.delta_computer.prev = state.clone() if isinstance(state, FlatState) else \
+            {k: t.detach().clone() for k, t in state.items()}
         self.stats.record("full", _nbytes(state), time.perf_counter() - t0)
         return SyncResult(v, DeltaVersion(v, time.time(), len(state), _nbytes(state)))
 
@@ -253,7 +264,8 @@ class SwiftSyncTransfer:
         t0 = time.perf_counter()
         await self._notify_async(state, "full")
         v = self._commit(state, "full")
-        self.delta_computer.prev = {k: t.detach().clone() for k, t in state.items()}   # next delta is relative to this
+        self.delta_computer.prev = state.clone() if isinstance(state, FlatState) else \
+            {k: t.detach().clone() for k, t in state.items()}   # next delta is relative to this
         self.stats.record("full", _nbytes(state), time.perf_counter() - t0)
         return v
 
@@ -277,7 +289,8 @@ class SwiftSyncTransfer:
     def initialize(self, initial_lora_state: Dict[str, torch.Tensor]) -> None:
         """Seed the previous-state snapshot and both buffers with the adapters' initial state, so that the first
         ``sync`` already sends a delta.  Without it the first ``sync`` is a full one."""
-        self.delta_computer.prev = {k: v.detach().clone() for k, v in initial_lora_state.items()}
+        self.delta_computer.prev = initial_lora_state.clone() if isinstance(initial_lora_state, FlatState) else \
+            {k: v.detach().clone() for k, v in initial_lora_state.items()}
         self.buffer = DoubleBufferedLoRA(initial_lora_state)         # version 0: nothing has been synced yet
 
     @property

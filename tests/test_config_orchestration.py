@@ -625,3 +625,55 @@ def test_swiftsync_low_rank_worker_keeps_engine_equal_to_merged_export(tmp_path)
     assert o.swift.worker._plan is not None
     for m, w0 in zip(mods, base0):
         assert torch.equal(m.base.weight, w0)
+
+
+def test_flat_adapter_state_takes_the_same_path_as_a_dict_of_tensors():
+    """``FlatState`` (all adapter tensors in one flat tensor) through the delta computer, the double buffer and the
+    transfer's commit gives what a plain dict of tensors gives; mixing the two falls back to the per-key path."""
+    from b200fw.sync import DeltaComputer, DoubleBufferedLoRA, SwiftSyncConfig, SwiftSyncTransfer
+    from b200fw.sync.double_buffer import FlatLayout, FlatState
+    torch.manual_seed(0)
+    shapes = {"a.lora_A": (4, 6), "a.lora_B": (10, 4), "b.lora_A": (4, 3)}
+    layout = FlatLayout(list(shapes), list(shapes.values()))
+
+    def state(seed):
+        g = torch.Generator().manual_seed(seed)
+        return FlatState(layout, torch.randn(layout.numel, generator=g))
+
+    s0, s1, s2 = state(0), state(1), state(2)
+    assert list(s0) == list(shapes) and "a.lora_B" in s0 and "zzz" not in s0 and s0["a.lora_B"].shape == (10, 4)
+    assert s0["b.lora_A"].data_ptr() == s0.flat[64:].data_ptr()                   # a view, not a copy
+    flat_dc, dict_dc = DeltaComputer(100), DeltaComputer(100)
+    for cur in (s0, s1, s2):
+        d_flat = flat_dc.compute_delta(FlatState(layout, cur.flat.clone()))
+        d_dict = dict_dc.compute_delta({k: v.clone() for k, v in cur.items()})
+        assert isinstance(d_flat, FlatState)
+        for k in shapes:
+            assert torch.equal(d_flat[k], d_dict[k])
+
+    class Worker:
+        def __init__(self):
+            self.calls = []
+
+        def update_weights(self, st, mode="full"):
+            self.calls.append((mode, {k: v.clone() for k, v in st.items()}))
+
+    wf, wd = Worker(), Worker()
+    tf = SwiftSyncTransfer(wf, SwiftSyncConfig(True, fallback_full_every=100))
+    td = SwiftSyncTransfer(wd, SwiftSyncConfig(True, fallback_full_every=100))
+    for step, cur in enumerate((s0, s1, s2)):
+        tf.sync(step, FlatState(layout, cur.flat.clone()))
+        td.sync(step, {k: v.clone() for k, v in cur.items()})
+    assert [m for m, _ in wf.calls] == [m for m, _ in wd.calls] == ["full", "delta", "delta"]
+    for (_, a), (_, b) in zip(wf.calls, wd.calls):
+        assert all(torch.equal(a[k], b[k]) for k in shapes)
+    assert tf.buffer.version == td.buffer.version == 3
+    fa, da = tf.buffer.get_active_state(), td.buffer.get_active_state()
+    assert all(torch.allclose(fa[k], da[k], atol=1e-6) and torch.allclose(fa[k], s2[k], atol=1e-5) for k in shapes)
+    assert tf.stats.last_bytes == td.stats.last_bytes == layout.numel * 4
+    # a plain-dict delta on a flat buffer: the per-key path takes over and still lands in the same tensors
+    buf = DoubleBufferedLoRA(s0)
+    buf.apply_delta_to_shadow({"a.lora_A": torch.ones(4, 6), "new.lora_A": torch.ones(2, 2)})
+    buf.swap_buffers()
+    act = buf.get_active_state()
+    assert torch.allclose(act["a.lora_A"], s0["a.lora_A"] + 1) and torch.equal(act["new.lora_A"], torch.ones(2, 2))

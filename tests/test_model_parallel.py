@@ -248,7 +248,7 @@ def test_lora_linear_autograd_function_against_plain_autograd():
     M, K, N, R = 40, 24, 56, 16
     x, a, b, r = [torch.randn(*sh, requires_grad=True) for sh in ((M, K), (R, K), (N, R), (M, N))]
     w = torch.randn(N, K)
-    y = _LoRALinear.apply(x, w, a, b, r)
+    y = _LoRALinear.apply(x, w, a, b, r, None)
     g = torch.randn(M, N)
     y.backward(g)
     x2, a2, b2, r2 = [t.detach().clone().requires_grad_() for t in (x, a, b, r)]
@@ -261,3 +261,49 @@ def test_lora_linear_autograd_function_against_plain_autograd():
     A2, B2 = torch.randn(M, R), torch.randn(N, R)
     assert torch.allclose(gemm(x.detach(), w, ext=(A2, B2)), x.detach() @ w.t() + A2 @ B2.t(), atol=1e-4)
     assert torch.allclose(gemm(g, w, b_mn=True, ext=(A2, a.detach())), g @ w + A2 @ a.detach(), atol=1e-4)
+
+
+def test_lora_linear_hands_stacked_gradients_to_the_adapters_parameters():
+    """The plan form: stacked operands built without autograd, every adapter's fp32 A / B receives its slice of the
+    stacked gradient (B's times the scaling), into ``main_grad`` when the parameter has one (overwrite, then
+    accumulate) and through autograd otherwise."""
+    from b200fw.ops.gemm import _LoRALinear
+    torch.manual_seed(2)
+    M, K, N = 24, 16, 40
+    rows, ranks, scal = [(0, 16), (16, 24), (24, 40)], [8, 8, 8], [2.0, 0.5, 1.0]
+    As = [torch.randn(r, K, requires_grad=True) for r in ranks]
+    Bs = [torch.randn(e - s, r, requires_grad=True) for (s, e), r in zip(rows, ranks)]
+    x = torch.randn(M, K, requires_grad=True)
+    w, g = torch.randn(N, K), torch.randn(M, N)
+
+    def stacked():
+        a_cat = torch.cat(As, 0)
+        b_bd = torch.zeros(N, sum(ranks))
+        r0 = 0
+        for B, (s0, e0), r, sc in zip(Bs, rows, ranks, scal):
+            b_bd[s0:e0, r0:r0 + r] = B * sc
+            r0 += r
+        return a_cat, b_bd
+
+    y_ref = x @ w.t() + (x @ stacked()[0].t()) @ stacked()[1].t()
+    y_ref.backward(g)
+    want = [p.grad.clone() for pair in zip(As, Bs) for p in pair]
+    want_x = x.grad.clone()
+    for p in As + Bs + [x]:
+        p.grad = None
+    plan, r0 = [], 0
+    for (s0, e0), r, sc in zip(rows, ranks, scal):
+        plan.append((r0, r, s0, e0, sc))
+        r0 += r
+    params = [p for pair in zip(As, Bs) for p in pair]
+    params[0].main_grad = torch.full_like(params[0], 7.0)          # one parameter with an optimizer bucket view
+    with torch.no_grad():
+        a_cat, b_bd = stacked()
+    for rep in range(2):
+        y = _LoRALinear.apply(x, w, a_cat, b_bd, None, tuple(plan), *params)
+        y.backward(g)
+    assert torch.allclose(y, y_ref, atol=1e-4)
+    assert params[0].grad is None and torch.allclose(params[0].main_grad, 2 * want[0], atol=1e-4)   # overwrite + accumulate
+    for p, wgt in list(zip(params, want))[1:]:
+        assert torch.allclose(p.grad, 2 * wgt, atol=1e-4, rtol=1e-4)
+    assert torch.allclose(x.grad, 2 * want_x, atol=1e-4)
