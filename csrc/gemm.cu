@@ -21,10 +21,6 @@
 #include <cstdlib>
 #include <cstring>
 
-#include <map>
-#include <mutex>
-#include <utility>
-
 #include "common.cuh"
 #include "host.h"
 
@@ -182,12 +178,6 @@ __device__ __forceinline__ void reduce_rows(const __nv_bfloat16* __restrict__ re
 struct GemmExt {
   CUtensorMap tmA2, tmB2;
   int K2;
-  // split-K with a bf16 output (skinny GEMMs: a decode batch against a whole weight matrix leaves most SMs without
-  // a tile): every (tile, K slice) unit parks its fp32 partial in `ws` and bumps the tile's counter; the unit that
-  // arrives last adds the others' partials to its own accumulator and runs the ordinary epilogue.  One launch, no
-  // zeroing pass; the counters go back to zero by themselves.
-  float* ws;        // [split_k][num_tiles][128 * BN] fp32
-  int* tile_cnt;    // [num_tiles]
 };
 
 template <int BN, bool A_MN, bool B_MN, int COMM>
@@ -210,7 +200,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint64_t* tmem_empty = tmem_full + 2;
   uint64_t* addend_bar = tmem_empty + 2;   // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(addend_bar + 2);
-  volatile uint32_t* last_flag = tmem_slot + 1;     // bf16 split-K: "this CTA's unit arrived last at its tile"
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -575,41 +564,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const bool addend = accumulate || residual;
         const int m0 = m_blk * GEMM_BM;
         bool ok = true;
-        const int my_ks = u / num_tiles;
-        if (split_k > 1) {
-          // park this unit's partial, then find out whether it was the last of its tile
-          float* mine = ext.ws + (static_cast<size_t>(my_ks) * num_tiles + t) * (GEMM_BM * BN) + static_cast<size_t>(r) * BN;
-#pragma unroll 1
-          for (int c = 0; c < BN / 32; ++c) {
-            uint32_t pr[32];
-            tmem_ld_32x32b_x32(t_base + c * 32, pr);
-            tmem_ld_wait();
-#pragma unroll
-            for (int q4 = 0; q4 < 8; ++q4)
-              *reinterpret_cast<float4*>(mine + c * 32 + q4 * 4) =
-                  make_float4(__uint_as_float(pr[4 * q4]), __uint_as_float(pr[4 * q4 + 1]),
-                              __uint_as_float(pr[4 * q4 + 2]), __uint_as_float(pr[4 * q4 + 3]));
-          }
-          __threadfence();
-          named_barrier(1, 128);
-          if (issuer) {
-            const int old = atomicAdd(ext.tile_cnt + t, 1);
-            const bool last = old == split_k - 1;
-            if (last) ext.tile_cnt[t] = 0;          // every unit of this tile has arrived: ready for the next launch
-            *last_flag = last ? 1u : 0u;
-          }
-          named_barrier(1, 128);
-          const bool last = *last_flag != 0u;
-          if (!last) {
-            tc_fence_before();
-            mbar_arrive(&tmem_empty[acc]);
-            acc ^= 1;
-            if (acc == 0) acc_phase ^= 1;
-            named_barrier(1, 128);                  // last_flag is rewritten by the next unit only after all have read it
-            continue;
-          }
-          __threadfence();                          // the other units' partials, published before their counter adds
-        }
 #pragma unroll 1
         for (int sl = 0; sl < BN / 64; ++sl) {
           const int buf = slab_count & 1;
@@ -636,21 +590,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (sl == BN / 64 - 1) {   // accumulator fully read: hand it back to the MMA warp
             tc_fence_before();
             mbar_arrive(&tmem_empty[acc]);
-          }
-          if (split_k > 1) {
-            for (int ks2 = 0; ks2 < split_k; ++ks2) {
-              if (ks2 == my_ks) continue;
-              const float* other = ext.ws + (static_cast<size_t>(ks2) * num_tiles + t) * (GEMM_BM * BN) +
-                                   static_cast<size_t>(r) * BN + sl * 64;
-#pragma unroll
-              for (int q4 = 0; q4 < 16; ++q4) {
-                const float4 f = __ldcg(reinterpret_cast<const float4*>(other) + q4);
-                v[4 * q4] = __float_as_uint(__uint_as_float(v[4 * q4]) + f.x);
-                v[4 * q4 + 1] = __float_as_uint(__uint_as_float(v[4 * q4 + 1]) + f.y);
-                v[4 * q4 + 2] = __float_as_uint(__uint_as_float(v[4 * q4 + 2]) + f.z);
-                v[4 * q4 + 3] = __float_as_uint(__uint_as_float(v[4 * q4 + 3]) + f.w);
-              }
-            }
           }
           if (col0 < N) {
             uint8_t* rowp = sbuf + r * 128;
@@ -804,44 +743,6 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
 static GemmMnDesc g_mn_desc = {8192u, 1024u, 2048u};
 
-// Workspace of the bf16 split-K path, one per (device, stream): launches on one stream are ordered, two streams
-// never share partials or counters.  Allocated on first use outside stream capture; a launch that finds none
-// while its stream is being captured simply does not split.
-constexpr size_t SPLIT_WS_BYTES = 32u << 20;
-constexpr int SPLIT_WS_TILES = 4096;
-struct SplitWs {
-  float* ws;
-  int* cnt;
-};
-static bool get_split_ws(cudaStream_t stream, SplitWs* out) {
-  static std::mutex mu;
-  static std::map<std::pair<int, cudaStream_t>, SplitWs> table;
-  int dev = 0;
-  cudaGetDevice(&dev);
-  std::lock_guard<std::mutex> lock(mu);
-  auto it = table.find({dev, stream});
-  if (it != table.end()) {
-    *out = it->second;
-    return true;
-  }
-  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-  if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
-    cudaGetLastError();
-    return false;
-  }
-  SplitWs w{nullptr, nullptr};
-  if (cudaMalloc(&w.ws, SPLIT_WS_BYTES) != cudaSuccess || cudaMalloc(&w.cnt, SPLIT_WS_TILES * sizeof(int)) != cudaSuccess ||
-      cudaMemsetAsync(w.cnt, 0, SPLIT_WS_TILES * sizeof(int), stream) != cudaSuccess) {
-    cudaGetLastError();
-    if (w.ws) cudaFree(w.ws);
-    if (w.cnt) cudaFree(w.cnt);
-    return false;
-  }
-  table[{dev, stream}] = w;
-  *out = w;
-  return true;
-}
-
 template <int BN, bool A_MN, bool B_MN, int COMM = 0>
 static int launch_gemm(const void* A, const void* B, void* C, const void* R, int M, int N, int K,
                        int lda, int ldb, int ldc, int flags, int max_ctas, cudaStream_t stream,
@@ -906,33 +807,11 @@ static int launch_gemm(const void* A, const void* B, void* C, const void* R, int
       }
     }
   }
+  if (num_tiles * split_k < grid) grid = num_tiles * split_k;
   GemmExt ext;
   ext.tmA2 = *ta;
   ext.tmB2 = *tb;
   ext.K2 = 0;
-  ext.ws = nullptr;
-  ext.tile_cnt = nullptr;
-  // Skinny bf16-output GEMMs (a decode batch against a whole weight matrix): few tiles, each with the full
-  // contraction to walk alone.  Split K over the idle SMs; the unit that arrives last at a tile finishes it.
-  static const bool split_bf16 = [] {
-    const char* e = std::getenv("B200FW_GEMM_SPLITK_BF16");
-    return !(e != nullptr && e[0] == '0');
-  }();
-  if (COMM == 0 && !out_fp32 && !(flags & GEMM_ACCUMULATE) && K2 == 0 && M <= 512 && split_bf16 && !deterministic &&
-      num_tiles <= SPLIT_WS_TILES) {
-    const int num_kb = (K + GEMM_BK - 1) / GEMM_BK;
-    int sk = grid / num_tiles;
-    if (sk > num_kb / 4) sk = num_kb / 4;
-    if (sk > 8) sk = 8;
-    SplitWs w;
-    if (sk >= 2 && static_cast<size_t>(sk) * num_tiles * GEMM_BM * BN * sizeof(float) <= SPLIT_WS_BYTES &&
-        get_split_ws(stream, &w)) {
-      split_k = sk;
-      ext.ws = w.ws;
-      ext.tile_cnt = w.cnt;
-    }
-  }
-  if (num_tiles * split_k < grid) grid = num_tiles * split_k;
   if (K2 > 0) {
     if (COMM != 0 || A_MN || split_k != 1) {
       set_error("gemm: a second operand pair needs a K-major A, no split-K and no fused collective");
