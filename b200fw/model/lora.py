@@ -88,7 +88,7 @@ class LinearWithLoRA(nn.Module):
         # False (or B200FW_LORA_FUSE=0): base projection, then two adapter GEMMs (the only form under TP)
         self.fuse_into_base = os.environ.get("B200FW_LORA_FUSE", "1") != "0"
         self._plan_cache = None
-        if getattr(base, "tp_size", 1) == 1 and self.fuse_into_base:
+        if getattr(base, "tp_size", 1) == 1 and self.fuse_into_base and base.weight.dtype == torch.bfloat16:
             # the fused op writes these parameters' gradients itself (into the optimizer's bucket views when it has
             # them): an optimizer may bind ``main_grad`` buffers to them as it does for bf16 weights
             for ad in self.adapters.values():
