@@ -255,12 +255,31 @@ class ParallelTransformerModel(nn.Module):
     possible when one stage holds both (src/distributed/tensor_parallel.py:784-851).
     """
 
-    def __init__(self, cfg: ModelConfig, ctx: Optional[ParallelContext] = None,
+    def __init__(self, cfg: Optional[ModelConfig] = None, ctx: Optional[ParallelContext] = None,
                  layer_range: Optional[Tuple[int, int]] = None, is_first_stage: bool = True,
                  is_last_stage: bool = True, sequence_parallel: bool = False,
                  gradient_checkpointing: bool = False, dtype=None, device=None,
-                 vocab_parallel: bool = True):
+                 vocab_parallel: bool = True, **reference_kwargs):
         super().__init__()
+        if cfg is None or reference_kwargs:
+            # the reference's keyword form (src/distributed/tensor_parallel.py:750-770): the architecture spelled out
+            # field by field, ``parallel_context`` and an optional ``pp_context`` that selects this stage's layers
+            kw = dict(reference_kwargs)
+            ctx = kw.pop("parallel_context", ctx)
+            ppc = kw.pop("pp_context", None)
+            gradient_checkpointing = bool(kw.pop("use_gradient_checkpoint", gradient_checkpointing))
+            for ignored in ("use_flash_attn", "enable_comm_overlap", "stream_manager", "attention_backend"):
+                kw.pop(ignored, None)           # attention is always the native kernel; overlap needs no switch here
+            if cfg is None:
+                kw.setdefault("tie_word_embeddings", False)
+                cfg = ModelConfig(**kw)
+            elif kw:
+                raise TypeError(f"unexpected arguments: {sorted(kw)}")
+            if ppc is not None and ppc.pp_size > 1:
+                layer_range = (ppc.layer_start, ppc.layer_end)
+                is_first_stage, is_last_stage = ppc.is_first_stage, ppc.is_last_stage
+            if ctx is not None and not hasattr(ctx, "tp_rank"):
+                ctx = None
         self.cfg, self.ctx = cfg, ctx
         self.tp_size, self.tp_rank, self.tp_group = _tp(ctx)
         self.sequence_parallel = sequence_parallel and self.tp_size > 1
@@ -417,11 +436,23 @@ class ParallelTransformerModel(nn.Module):
         :meth:`loss` / :meth:`token_logprobs`, which never build this tensor).  ``attention_mask`` is
         accepted for API compatibility: attention is causal and padding sits on the right, so padded
         positions never influence real ones."""
-        B, S = input_ids.shape
-        h = self.forward_hidden(input_ids, B, S, positions)
+        if input_ids.dim() == 3:
+            # a later pipeline stage fed ``[B,S,H]`` activations (the reference's stage models take and return them
+            # in this shape: src/distributed/tensor_parallel.py:853-905)
+            assert not self.is_first_stage and not self.sequence_parallel
+            B, S, H = input_ids.shape
+            h = self.forward_hidden(input_ids.reshape(B * S, H), B, S, positions)
+        else:
+            B, S = input_ids.shape
+            h = self.forward_hidden(input_ids, B, S, positions)
         if not self.is_last_stage:
-            return h
+            return h if self.sequence_parallel else h.reshape(B, S, -1)
         return self.logits_from_hidden(h).reshape(B, S, -1)
+
+    @property
+    def stage_start(self) -> int:
+        """Global index of this stage's first layer (the reference's name)."""
+        return self.layer_start
 
     def loss(self, input_ids: torch.Tensor, labels: torch.Tensor, loss_scale: float = 1.0,
              hidden: Optional[torch.Tensor] = None, valid_idx: Optional[torch.Tensor] = None,

@@ -30,9 +30,19 @@ def default_loss_fn(logits: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
 
 
 class PipelineScheduler:
-    def __init__(self, model, pp_context, num_micro_batches: int):
+    def __init__(self, model, pp_context=None, num_micro_batches: Optional[int] = None, loss_fn=None):
+        """``PipelineScheduler(model, pp_context, num_micro_batches)``; or, in the reference's form
+        (src/distributed/pipeline_scheduler.py:82-103), ``PipelineScheduler(pp_context, num_micro_batches,
+        loss_fn=None)`` with the stage model handed to :meth:`run_1f1b_schedule`.  With a ``loss_fn(logits, labels)``
+        the last stage materialises its logits and calls it; without one it uses the model's fused next-token loss."""
+        from .stages import PipelineParallelContext
+        if isinstance(model, PipelineParallelContext):
+            model, pp_context, num_micro_batches = None, model, (pp_context if num_micro_batches is None
+                                                                else num_micro_batches)
+        assert pp_context is not None and num_micro_batches is not None
         assert num_micro_batches >= pp_context.pp_size, "need num_micro_batches >= pp_size to fill the pipe"
-        self.model, self.pp, self.num_micro = model, pp_context, num_micro_batches
+        self.model, self.pp, self.num_micro = model, pp_context, int(num_micro_batches)
+        self.loss_fn = loss_fn
         self._act_shape: Optional[Tuple[int, ...]] = None
         self.timeline = None  # optional ScheduleVisualizer
         self._fifo: deque = deque()   # (input, output) pairs queued by forward_step for backward_step
@@ -61,6 +71,10 @@ class PipelineScheduler:
             inp = recv.detach().requires_grad_(True)     # a fresh leaf over the (reused) receive buffer
             out = self.model.forward_hidden(inp, B, S)
         if self.pp.is_last_stage:
+            if self.loss_fn is not None:
+                logits = self.model.logits_from_hidden(out).reshape(B, S, -1)
+                loss = self.loss_fn(logits, labels_mb) / self.num_micro
+                return inp, loss, loss.detach()
             loss = self.model.loss(None, labels_mb, loss_scale=1.0 / self.num_micro, hidden=out)
             return inp, loss, loss.detach() / self.num_micro
         return inp, out, None
@@ -105,9 +119,19 @@ class PipelineScheduler:
         return self.timeline.track(name, cat, lane=f"stage{self.pp.pp_rank}")
 
     # ---- schedule ------------------------------------------------------------------------------------
-    def run_1f1b_schedule(self, input_ids: torch.Tensor, labels: torch.Tensor) -> torch.Tensor:
+    def run_1f1b_schedule(self, input_ids, labels=None):
         """Run all micro-batches of ``[B,S]`` (split along B).  Returns the mean loss on the last stage
-        and zeros elsewhere; use :meth:`broadcast_loss` to share it."""
+        and zeros elsewhere; use :meth:`broadcast_loss` to share it.
+
+        The reference's form ``run_1f1b_schedule(stage_model, data_iterator)`` (``num_micro_batches`` pairs of
+        ``(input_ids, labels)``; src/distributed/pipeline_scheduler.py:174-320) is accepted too and returns what the
+        reference returns: the accumulated loss on the last stage, ``None`` on the others."""
+        if isinstance(input_ids, torch.nn.Module):
+            self.model = input_ids
+            pairs = [next(labels) for _ in range(self.num_micro)] if hasattr(labels, "__next__") else list(labels)
+            assert len(pairs) == self.num_micro, "the iterator must yield num_micro_batches (input_ids, labels) pairs"
+            total = self.run_1f1b_schedule(torch.cat([p[0] for p in pairs], 0), torch.cat([p[1] for p in pairs], 0))
+            return total if self.pp.is_last_stage else None
         pp = self.pp
         dev = labels.device
         dtype = next(self.model.parameters()).dtype

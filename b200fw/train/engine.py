@@ -16,6 +16,7 @@ from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Tuple
 
 import torch
+import torch.distributed as dist
 
 from ..dist.context import ParallelContext
 from ..model import (ModelConfig, PRESETS, ParallelTransformerModel, apply_lora, get_lora_state_dict,
@@ -298,8 +299,39 @@ class TrainEngine:
         """Global L2 norm of the gradients over DP x TP x PP, with the clip to ``max_grad_norm`` armed for the next
         ``optimizer.step()``; ``-1.0`` when the norm is not finite (the step then leaves the weights untouched).
         The reference's unit of the same name (src/engines/train_engine.py:1451-1530) scales ``p.grad`` in place;
-        here the scale is applied inside the fused AdamW kernel, so the gradients themselves stay as they are."""
-        return float(self.optimizer.clip_grad_norm(self.config.max_grad_norm))
+        here the scale is applied inside the fused AdamW kernel, so the gradients themselves stay as they are.
+
+        An object without a bucketed optimizer (a bare model whose gradients sit in ``p.grad``: the form the
+        reference's ``tests/test_grad_norm_3d.py`` drives with a stub engine) gets the plain form: the sum of squares
+        of the local gradients is all-reduced over every parallel group that has more than one rank, gradients of
+        parameters marked ``_tp_replicated`` are first summed over TP, and ``p.grad`` is scaled in place when the
+        norm exceeds ``max_grad_norm``."""
+        opt = getattr(self, "optimizer", None)
+        if opt is not None and hasattr(opt, "clip_grad_norm"):
+            return float(opt.clip_grad_norm(self.config.max_grad_norm))
+        params = [p for p in self.model.parameters() if p.requires_grad and p.grad is not None]
+        if not params:
+            return 0.0
+        ctx = getattr(self, "parallel_ctx", None)
+        if ctx is not None and ctx.tp_size > 1 and ctx.tp_group is not None:
+            for p in params:
+                if getattr(p, "_tp_replicated", False):
+                    dist.all_reduce(p.grad, group=ctx.tp_group)
+        sq = torch.stack([p.grad.detach().double().pow(2).sum() for p in params]).sum()
+        if ctx is not None and ctx.world_size > 1:
+            for size, group in ((ctx.dp_size, ctx.dp_group), (ctx.tp_size, ctx.tp_group), (ctx.pp_size, ctx.pp_group)):
+                if size > 1 and group is not None:
+                    dist.all_reduce(sq, group=group)
+        if not bool(torch.isfinite(sq)):       # after the reductions: a NaN on one rank reaches all, nobody leaves early
+            return -1.0
+        norm = float(sq.sqrt())
+        scale = float(self.config.max_grad_norm) / (norm + 1e-6)
+        if scale < 1.0:
+            torch._foreach_mul_([p.grad for p in params], scale)
+        mc = getattr(self, "metrics_collector", None)
+        if mc is not None:
+            mc.record("grad_norm", norm)
+        return norm
 
     def _finish_step(self, gn: Optional[torch.Tensor]) -> float:
         """Host side of the NaN/Inf guard: a non-finite norm (reported as -1) means the device skipped

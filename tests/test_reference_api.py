@@ -328,3 +328,50 @@ def test_colocate_replaced_stages_drive_the_loop():
     # the reference's (error, stage) call form of the recovery hook
     asyncio.run(orch._handle_error(RuntimeError("late"), "syncing"))
     assert orch.state == OrchestratorState.ERROR and Server.woke == 4
+
+
+def _reference_form_pipeline_worker(rank, world):
+    """The reference's way of building and driving a pipeline: the model from architecture keywords + ``pp_context``,
+    ``PipelineScheduler(pp_context, num_micro_batches, loss_fn)``, ``run_1f1b_schedule(stage_model, iterator)``."""
+    from b200fw.dist.context import ParallelContext
+    from b200fw.model import ParallelTransformerModel
+    from b200fw.pipeline import PipelineParallelContext, PipelineScheduler
+    from b200fw.pipeline.schedule_1f1b import default_loss_fn
+    arch = dict(vocab_size=64, hidden_size=32, num_layers=4, num_heads=4, num_kv_heads=2, head_dim=8,
+                intermediate_size=48, max_position_embeddings=32)
+    ctx = ParallelContext.init_distributed(tp_size=1, dp_size=1, pp_size=2, backend="gloo")
+    ppc = PipelineParallelContext(ctx, num_layers=4)
+    torch.manual_seed(5)
+    full = ParallelTransformerModel(parallel_context=ParallelContext(tp_size=1, tp_group=None), **arch)
+    g = torch.Generator().manual_seed(9)
+    batches = [(torch.randint(0, 64, (2, 8), generator=g), torch.randint(0, 64, (2, 8), generator=g)) for _ in range(4)]
+    ref = 0.0
+    for ids, labels in batches:
+        loss = default_loss_fn(full(ids), labels) / 4
+        ref += float(loss)
+        loss.backward()
+    stage = ParallelTransformerModel(parallel_context=ctx, pp_context=ppc, use_gradient_checkpoint=False, **arch)
+    assert stage.stage_start == ppc.stage_layer_range[0] and len(stage.layers) == 2
+    assert (stage.embed_tokens is not None) == ppc.is_first_stage and (stage.norm is not None) == ppc.is_last_stage
+    sd = full.state_dict()
+    stage.load_state_dict({k: sd[k if not k.startswith("layers.") else
+                                 f"layers.{int(k.split('.')[1]) + stage.stage_start}.{k.split('.', 2)[2]}"]
+                           for k in stage.state_dict()})
+    hidden_or_logits = stage(batches[0][0] if ppc.is_first_stage else torch.randn(2, 8, 32))
+    assert hidden_or_logits.shape == ((2, 8, 32) if not ppc.is_last_stage else (2, 8, 64))
+    stage.zero_grad(set_to_none=True)
+    got = PipelineScheduler(ppc, num_micro_batches=4, loss_fn=default_loss_fn).run_1f1b_schedule(stage, iter(batches))
+    if not ppc.is_last_stage:
+        assert got is None
+    else:
+        assert abs(float(got) - ref) < 1e-5 * abs(ref)
+    named = dict(full.named_parameters())
+    for n, p in stage.named_parameters():
+        k = n if not n.startswith("layers.") else f"layers.{int(n.split('.')[1]) + stage.stage_start}.{n.split('.', 2)[2]}"
+        assert p.grad is not None and torch.allclose(p.grad, named[k].grad, atol=1e-5), n
+    return True
+
+
+def test_pipeline_in_the_reference_call_form_matches_the_full_model():
+    from _dist_util import run_ranks
+    assert all(run_ranks(_reference_form_pipeline_worker, 2))

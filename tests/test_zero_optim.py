@@ -187,6 +187,39 @@ def test_grad_norm_3d_pp2_tp2_dp2():
     assert all(run_ranks(_norm_worker, 8, 2, 2, 2, timeout=600))
 
 
+def _plain_norm_worker(rank, world, tp, pp, dp):
+    """``TrainEngine._clip_grad_norm`` on an object without a bucketed optimizer (gradients in ``p.grad``): the norm
+    covers every rank of the (pp, tp, dp) world, gradients are scaled in place only above the limit."""
+    import types
+    import torch.distributed as dist
+    from b200fw.dist.context import ParallelContext
+    from b200fw.train import TrainEngine
+    ctx = ParallelContext.init_distributed(tp_size=tp, dp_size=dp, pp_size=pp, backend="gloo")
+    torch.manual_seed(7 + rank)
+    model = torch.nn.Sequential(torch.nn.Linear(8, 16, bias=False), torch.nn.Linear(16, 4, bias=False))
+    for p in model.parameters():
+        p.grad = torch.randn_like(p) * (rank + 1)
+    sq = torch.stack([p.grad.double().pow(2).sum() for p in model.parameters()]).sum()
+    dist.all_reduce(sq)
+    want = math.sqrt(float(sq))
+    stub = types.SimpleNamespace(model=model, parallel_ctx=ctx, metrics_collector=None,
+                                 config=types.SimpleNamespace(max_grad_norm=1e30))
+    before = [p.grad.clone() for p in model.parameters()]
+    got = TrainEngine._clip_grad_norm(stub)
+    assert abs(got - want) / want < 1e-9 and all(torch.equal(a, p.grad) for a, p in zip(before, model.parameters()))
+    stub.config.max_grad_norm = want / 4
+    TrainEngine._clip_grad_norm(stub)
+    assert all(torch.allclose(p.grad, a / 4, rtol=1e-5) for a, p in zip(before, model.parameters()))
+    if rank == 1:                       # a non-finite gradient on ONE rank: every rank must report it (and none hang)
+        model[0].weight.grad.fill_(float("nan"))
+    assert TrainEngine._clip_grad_norm(stub) == -1.0
+    return True
+
+
+def test_plain_grad_norm_unit_covers_all_parallel_groups():
+    assert all(run_ranks(_plain_norm_worker, 4, 2, 1, 2))
+
+
 def test_lr_schedule_shapes():
     s = LRSchedule(1e-3, "cosine", warmup_steps=10, total_steps=110, min_lr_ratio=0.1)
     assert abs(s.lr_at(0) - 1e-5) < 1e-12 and abs(s.lr_at(10) - 1e-3) < 1e-12
