@@ -272,7 +272,9 @@ class WeightUpdateManager:
         self.rollbacks = 0
 
     @torch.no_grad()
-    def update_weights(self, state: Dict[str, torch.Tensor]) -> bool:
+    def update_weights(self, state: Optional[Dict[str, torch.Tensor]] = None, *,
+                       new_state_dict: Optional[Dict[str, torch.Tensor]] = None) -> bool:
+        state = state if state is not None else new_state_dict      # ``new_state_dict``: the reference's keyword
         params = dict(self.model.named_parameters())
         backup = {k: params[k].detach().clone() for k in state if k in params}
         try:

@@ -143,9 +143,13 @@ class NCCLWeightTransfer(_VersionedMixin):
         self.stats.record(nbytes, time.perf_counter() - t0)
         return self.version
 
-    def receive_weights(self, templates: Dict[str, torch.Tensor]) -> Dict[str, torch.Tensor]:
-        """Engine side: receive into ``templates`` (same names / shapes / dtypes); verifies the sample
-        checksums and raises on mismatch, leaving ``version`` unchanged."""
+    def receive_weights(self, templates: Optional[Dict[str, torch.Tensor]] = None, *,
+                        state_dict_template: Optional[Dict[str, torch.Tensor]] = None) -> Dict[str, torch.Tensor]:
+        """Engine side: receive into ``templates`` (same names / shapes / dtypes; ``state_dict_template`` is the
+        reference's keyword for it); verifies the sample checksums and raises on mismatch, leaving ``version``
+        unchanged."""
+        templates = templates if templates is not None else state_dict_template
+        assert templates is not None, "receive_weights needs the template tensors"
         t0 = time.perf_counter()
         meta = self._bcast_obj(None)
         nbytes, bad = 0, []
@@ -180,7 +184,9 @@ class RayObjectStoreTransfer(_VersionedMixin):
         self._ref = None
         self.version = 0
 
-    def publish_weights(self, state: Dict[str, torch.Tensor]):
+    def publish_weights(self, state: Optional[Dict[str, torch.Tensor]] = None, *,
+                        state_dict: Optional[Dict[str, torch.Tensor]] = None):
+        state = state if state is not None else state_dict          # ``state_dict``: the reference's keyword
         if not self.available:
             raise RuntimeError("ray is not installed: the object-store backend is unavailable")
         import ray
@@ -212,8 +218,17 @@ class WeightTransferManager(_VersionedMixin):
         self.stats = TransferStats()
         self.version = 0
 
-    def sync_weights(self, is_sender: bool, state: Optional[Dict[str, torch.Tensor]] = None, engine=None,
-                     templates: Optional[Dict[str, torch.Tensor]] = None):
+    def sync_weights(self, is_sender=True, state: Optional[Dict[str, torch.Tensor]] = None, engine=None,
+                     templates: Optional[Dict[str, torch.Tensor]] = None, *,
+                     state_dict: Optional[Dict[str, torch.Tensor]] = None,
+                     state_dict_template: Optional[Dict[str, torch.Tensor]] = None):
+        """``sync_weights(is_sender, state, engine, templates)``; the reference's call
+        ``sync_weights(state_dict, is_sender=..., state_dict_template=...)`` (src/transfer/nccl_transfer.py:395-446) is
+        recognised by its keywords or by a dict in first place."""
+        if isinstance(is_sender, dict):                     # the reference's order: the state comes first
+            state, is_sender = is_sender, (True if state is None else bool(state))
+        state = state if state is not None else state_dict
+        templates = templates if templates is not None else state_dict_template
         t0 = time.perf_counter()
         nbytes = sum(v.numel() * v.element_size() for v in state.values()) if state else 0
         if self.backend == "local":

@@ -238,7 +238,9 @@ class SwiftSyncTransfer:
         self.stats.record("delta", _nbytes(delta), time.perf_counter() - t0)
         return SyncResult(v, DeltaVersion(v, time.time(), len(delta), _nbytes(delta)))
 
-    def sync_full(self, state: Dict[str, torch.Tensor], infer_worker=None) -> int:
+    def sync_full(self, state: Optional[Dict[str, torch.Tensor]] = None, infer_worker=None, *,
+                  full_state: Optional[Dict[str, torch.Tensor]] = None) -> int:
+        state = state if state is not None else full_state          # ``full_state``: the reference's keyword
         if infer_worker is not None:
             self.worker = infer_worker
         t0 = time.perf_counter()

@@ -265,6 +265,14 @@ def test_transfer_adapters():
     ipc.release_refs()
     wm = WeightUpdateManager(torch.nn.Linear(1, 1))
     assert wm.current_version == 0 and wm.rollback_count == 0
+    # the reference's keyword names and argument order on the transfer entry points
+    assert wm.update_weights(new_state_dict={"weight": torch.full((1, 1), 3.0)}) and float(wm.model.weight) == 3.0
+    mgr2, eng2 = WeightTransferManager("local"), Eng()
+    mgr2.sync_weights({"b": torch.ones(1)}, is_sender=True, engine=eng2)
+    mgr2.sync_weights(state_dict={"c": torch.ones(1)}, is_sender=True, engine=eng2)
+    assert "c" in eng2.state and mgr2.version == 2
+    t2 = SwiftSyncTransfer(None, SwiftSyncConfig(True, 10, True))
+    assert t2.sync_full(full_state={"a": torch.ones(2)}) == 1
     c = DisaggConfig(num_train_gpus=2, num_infer_gpus=2)
     assert c.train_gpus == [0, 1] and c.infer_gpus == [2, 3] and c.infer_tp_size == 2 and c.overlap_training_inference
     assert DisaggIterationMetrics(0, rollout_time=1.5).infer_time == 1.5
