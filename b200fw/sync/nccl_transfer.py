@@ -218,15 +218,25 @@ class WeightTransferManager(_VersionedMixin):
         self.stats = TransferStats()
         self.version = 0
 
-    def sync_weights(self, is_sender=True, state: Optional[Dict[str, torch.Tensor]] = None, engine=None,
-                     templates: Optional[Dict[str, torch.Tensor]] = None, *,
+    def sync_weights(self, *args, is_sender: Optional[bool] = None, state: Optional[Dict[str, torch.Tensor]] = None,
+                     engine=None, templates: Optional[Dict[str, torch.Tensor]] = None,
                      state_dict: Optional[Dict[str, torch.Tensor]] = None,
                      state_dict_template: Optional[Dict[str, torch.Tensor]] = None):
-        """``sync_weights(is_sender, state, engine, templates)``; the reference's call
-        ``sync_weights(state_dict, is_sender=..., state_dict_template=...)`` (src/transfer/nccl_transfer.py:395-446) is
-        recognised by its keywords or by a dict in first place."""
-        if isinstance(is_sender, dict):                     # the reference's order: the state comes first
-            state, is_sender = is_sender, (True if state is None else bool(state))
+        """``sync_weights(is_sender, state, engine, templates)``; or the reference's call
+        ``sync_weights(state_dict, is_sender, state_dict_template)`` (src/transfer/nccl_transfer.py:395-446), told apart
+        by what comes first (a flag or a dict of tensors).  Every argument may also be given by keyword under either
+        set of names."""
+        if args and isinstance(args[0], dict):                      # the reference's order
+            names = ("state", "is_sender", "templates")
+        else:
+            names = ("is_sender", "state", "engine", "templates")
+        given = dict(is_sender=is_sender, state=state, engine=engine, templates=templates)
+        for name, value in zip(names, args):
+            if given[name] is not None:
+                raise TypeError(f"sync_weights() got multiple values for argument {name!r}")
+            given[name] = value
+        is_sender, state, engine, templates = (given[k] for k in ("is_sender", "state", "engine", "templates"))
+        is_sender = True if is_sender is None else bool(is_sender)
         state = state if state is not None else state_dict
         templates = templates if templates is not None else state_dict_template
         t0 = time.perf_counter()
