@@ -110,10 +110,10 @@ __global__ void kv_gather_kernel(const void* __restrict__ k_cache, const void* _
 }
 
 // ---------------------------------------------------------------------------------------------
-// Paged decode attention: one query token per sequence.  Grid (B, Hkv, nsplit); a CTA streams its
-// partition of the sequence's pages (64 tokens per step through shared memory), scores all G = Hq/Hkv
-// query heads of its kv head, and keeps an online softmax.  nsplit == 1 writes the output directly;
-// otherwise unnormalised partials + (max, sum) go to a workspace for the merge kernel.
+// Paged decode attention: one query token per sequence.  Grid (B, Hkv * head groups, nsplit); a CTA streams
+// its partition of the sequence's pages, scores the query heads of its kv head, and keeps an online softmax.
+// nsplit == 1 writes the output directly; otherwise unnormalised partials + (max, sum) go to a workspace for
+// the merge kernel.
 // ---------------------------------------------------------------------------------------------
 constexpr int DEC_THREADS = 128;
 constexpr int DEC_CHUNK = 64;   // partitions are multiples of this many tokens
@@ -152,9 +152,9 @@ __device__ __forceinline__ void dec_unpack<true>(const uint4& u, float* f) {
 }
 
 // Decode attention over the paged cache, one CTA per (sequence, kv head, head group, partition).
-// No shared-memory staging: a cache row (128 dims) is spread over LPT = 16 (bf16) or 8 (fp8) lanes of
-// a warp, 16 bytes each, so one warp-wide load covers 2 (4) tokens and every lane keeps DEC_UNROLL K and
-// V pieces in flight.  Each lane group runs its own online softmax over the tokens it sees (running
+// A cache row (128 dims) is spread over LPT = 16 (bf16) or 8 (fp8) lanes of a warp, 16 bytes each, so one
+// warp-wide access covers 2 (4) tokens and every lane handles DEC_UNROLL K and V pieces per step; no data is
+// ever shared between lanes through memory.  Each lane group runs its own online softmax over the tokens it sees (running
 // maximum, sum and DPL accumulator dims per head, base-2 exponent domain); groups and warps are merged
 // once at the end with the exact log-sum-exp rule.  GH query heads of the kv head are handled per CTA
 // (their q pieces sit in registers); larger GQA ratios use several CTAs (head groups) per kv head.
