@@ -119,7 +119,7 @@ constexpr int DEC_THREADS = 128;
 constexpr int DEC_CHUNK = 64;   // partitions are multiples of this many tokens
 constexpr int DEC_MAX_G = 8;
 constexpr int DEC_UNROLL = 4;   // cache rows in flight per lane group
-constexpr int DEC_DEFAULT_MODE = 3;   // row loop of the decode kernel when B200FW_DECODE_MODE is unset (measured: 3 is fastest)
+constexpr int DEC_DEFAULT_MODE = 3;   // row loop of the decode kernel when B200FW_DECODE_MODE is unset
 constexpr float DEC_LOG2E = 1.4426950408889634f;
 constexpr float DEC_LN2 = 0.6931471805599453f;
 
@@ -158,10 +158,12 @@ __device__ __forceinline__ void dec_unpack<true>(const uint4& u, float* f) {
 // maximum, sum and DPL accumulator dims per head, base-2 exponent domain); groups and warps are merged
 // once at the end with the exact log-sum-exp rule.  GH query heads of the kv head are handled per CTA
 // (their q pieces sit in registers); larger GQA ratios use several CTAs (head groups) per kv head.
-// MODE 0: plain row loop.  MODE 1: register software pipeline (loads of step i + 1 under the arithmetic of step i).
-// MODE 3 / 4: every warp owns a ring of that many stages in shared memory, filled by 16-byte asynchronous copies
+// MODE 0: plain row loop, the K and V pieces of a step are loaded into registers and consumed.
+// MODE 3: every warp owns a ring of three stages in shared memory, filled by 16-byte asynchronous copies
 // (cp.async.cg, no register staging); a lane reads back exactly the bytes it copied, so no barrier is needed, and
-// MODE - 1 steps' worth of K and V rows stay in flight per warp without growing the register count.
+// two steps' worth of K and V rows stay in flight per warp without growing the register count.  (Measured at
+// 256 x 1024: 0.194 ms against 0.231 ms for MODE 0; a four-stage ring, 0.203 ms, and a register software pipeline,
+// 0.283 ms, were tried and dropped.)
 template <bool FP8, int GH, int MODE>
 __global__ void __launch_bounds__(DEC_THREADS) paged_decode_kernel(
     const __nv_bfloat16* __restrict__ q, const void* __restrict__ k_cache, const void* __restrict__ v_cache,
@@ -174,7 +176,7 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_decode_kernel(
   constexpr int TPW = 32 / LPT;        // token rows per warp-wide load
   constexpr int DPL = 16 / ESZ;        // dims per lane
   constexpr int U = DEC_UNROLL;
-  constexpr bool PIPE = MODE == 1;
+  static_assert(MODE == 0 || MODE == 3, "row loop: 0 (registers) or 3 (three-stage cp.async ring)");
   constexpr int STAGES = MODE >= 2 ? MODE : 1;
   __shared__ float sAcc[DEC_THREADS / 32][GH][HD];
   __shared__ float sM[DEC_THREADS / 32][GH], sL[DEC_THREADS / 32][GH];
@@ -209,9 +211,7 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_decode_kernel(
     l[g] = 0.f;
   }
 
-  // Software pipeline over the cache rows: the loads of step i + 1 (block-table entry, then K and V pieces) are
-  // issued before the arithmetic of step i, so every lane keeps 2 * U sixteen-byte loads in flight instead of
-  // alternating between "waiting for loads" and "computing".
+  // One step of a lane group: U cache rows (their K and V pieces, the block's scales, validity).
   struct Rows {
     uint4 kq[U], vq[U];
     float ks[U], vs[U];
@@ -343,18 +343,6 @@ __global__ void __launch_bounds__(DEC_THREADS) paged_decode_kernel(
         slot = slot + 1 == STAGES ? 0 : slot + 1;
       }
       asm volatile("cp.async.wait_group 0;" ::: "memory");
-    } else if (PIPE) {
-      Rows ra, rb;
-      if (base < t_end) load_rows(ra, base);
-      while (base < t_end) {
-        if (base + STEP < t_end) load_rows(rb, base + STEP);
-        consume(ra);
-        base += STEP;
-        if (base >= t_end) break;
-        if (base + STEP < t_end) load_rows(ra, base + STEP);
-        consume(rb);
-        base += STEP;
-      }
     } else {
       for (; base < t_end; base += STEP) {
         Rows r;
@@ -515,14 +503,12 @@ B2_EXPORT int b2_paged_decode(const void* q, const void* k_cache, const void* v_
   // lane, so four heads would leave room for only two CTAs per SM)
   const int GH = (G % 4 == 0 && !fp8) ? 4 : (G % 2 == 0 ? 2 : 1);
   dim3 grid(B, Hkv * (G / GH), nsplit);
-  // B200FW_DECODE_MODE selects the row loop: 0 plain, 1 register software pipeline, 3 / 4 a ring of that many
-  // cp.async stages per warp in shared memory (B200FW_DECODE_PIPE=1 is the older spelling of mode 1)
-  // (read on every call, so that one process can compare them)
+  // B200FW_DECODE_MODE selects the row loop: 0 registers, 3 the cp.async ring (read on every call, so that one
+  // process can compare them)
   const int mode = [] {
     const char* e = std::getenv("B200FW_DECODE_MODE");
-    if (e != nullptr && e[0] >= '0' && e[0] <= '4' && e[0] != '2') return e[0] - '0';
-    const char* p = std::getenv("B200FW_DECODE_PIPE");
-    return (p != nullptr && p[0] == '1') ? 1 : DEC_DEFAULT_MODE;
+    if (e != nullptr && (e[0] == '0' || e[0] == '3')) return e[0] - '0';
+    return DEC_DEFAULT_MODE;
   }();
 #define B2_DECODE_LAUNCH_M(F8, GHV, MD)                                                                    \
   do {                                                                                                     \
@@ -543,9 +529,7 @@ B2_EXPORT int b2_paged_decode(const void* q, const void* k_cache, const void* v_
   } while (0)
 #define B2_DECODE_LAUNCH(F8, GHV)                                                                          \
   do {                                                                                                     \
-    if (mode == 1) B2_DECODE_LAUNCH_M(F8, GHV, 1);                                                         \
-    else if (mode == 3) B2_DECODE_LAUNCH_M(F8, GHV, 3);                                                    \
-    else if (mode == 4) B2_DECODE_LAUNCH_M(F8, GHV, 4);                                                    \
+    if (mode == 3) B2_DECODE_LAUNCH_M(F8, GHV, 3);                                                         \
     else B2_DECODE_LAUNCH_M(F8, GHV, 0);                                                                   \
   } while (0)
   if (fp8) {

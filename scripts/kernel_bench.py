@@ -175,8 +175,8 @@ def main():
     ap.add_argument("--vocab", type=int, default=151936)
     ap.add_argument("--fp8", action="store_true")
     ap.add_argument("--partition", type=int, default=0, help="paged_decode: tokens per split-KV partition (0 = automatic)")
-    ap.add_argument("--decode-mode", default=None, choices=["0", "1", "3", "4"],
-                    help="paged_decode: row loop of the kernel (0 plain, 1 register pipeline, 3 / 4 cp.async ring stages)")
+    ap.add_argument("--decode-mode", default=None, choices=["0", "3"],
+                    help="paged_decode: row loop of the kernel (0 registers, 3 cp.async ring)")
     ap.add_argument("--fp32-acc", action="store_true", help="gemm: accumulate into an fp32 output (weight-gradient form)")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)

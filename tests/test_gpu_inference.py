@@ -80,7 +80,7 @@ def test_qknorm_rope_store_equals_the_two_launch_form(Hq, Hkv):
 @pytest.mark.parametrize("fp8", [False, True])
 @pytest.mark.parametrize("Hq,Hkv", [(4, 2), (8, 1), (2, 2)])
 @pytest.mark.parametrize("split", [(0, 1), (64, 0)])
-@pytest.mark.parametrize("mode", ["0", "1", "3", "4"])     # row loop of the kernel: plain, register pipeline, cp.async rings
+@pytest.mark.parametrize("mode", ["0", "3"])     # row loop of the kernel: registers, cp.async ring
 def test_paged_decode_attention(fp8, Hq, Hkv, split, mode, monkeypatch):
     from b200fw.ops import paged_decode_attention
     monkeypatch.setenv("B200FW_DECODE_MODE", mode)
@@ -289,8 +289,8 @@ def test_inference_kernels_write_only_inside_their_outputs(monkeypatch):
         test_paged_decode_attention(False, 4, 2, (0, 1), "0", monkeypatch)
         test_paged_decode_attention(True, 8, 1, (64, 0), "3", monkeypatch)
         test_paged_decode_attention(False, 2, 2, (64, 0), "3", monkeypatch)
-        test_paged_decode_attention(False, 4, 2, (0, 1), "4", monkeypatch)
-        test_paged_decode_attention(True, 2, 2, (0, 1), "1", monkeypatch)
+        test_paged_decode_attention(False, 4, 2, (0, 1), "3", monkeypatch)
+        test_paged_decode_attention(True, 2, 2, (0, 1), "0", monkeypatch)
         test_varlen_attention_with_context_offset([(16, 300), (3, 131), (77, 77)])
         test_varlen_attention_with_context_offset([(1, 513)])
         test_topp_sampler_distribution_and_greedy()
