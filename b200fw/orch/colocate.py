@@ -369,7 +369,9 @@ class ColocateOrchestrator:
             return self.weights_version
         if self.swift is not None:
             from ..model.lora import flat_lora_state
-            self.swift.sync(iteration, flat_lora_state(eng.model))
+            with eng.optimizer.eval_mode():          # ZeRO-3 keeps the adapters sharded between steps: gather to read
+                state = flat_lora_state(eng.model)
+            self.swift.sync(iteration, state)
         else:
             state = eng.export_weights()
             self.weight_sync.sync(True, state, self.infer_engine)
