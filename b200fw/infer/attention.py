@@ -17,7 +17,11 @@ import torch
 from .. import ops
 from .context import InferenceContext, get_context
 
-__all__ = ["store_kv_cache", "PagedAttention", "PartitionedPagedAttention"]
+# The reference sets this when the flash_attn library imports (src/inference/attention.py:28-32).  Attention here is
+# this package's own kernel: available whenever a CUDA device is (the CPU path is the plain softmax formula).
+HAS_FLASH_ATTN = torch.cuda.is_available()
+
+__all__ = ["store_kv_cache", "PagedAttention", "PartitionedPagedAttention", "HAS_FLASH_ATTN"]
 
 
 def _segments_from_slots(slot_mapping: torch.Tensor, block_size: int) -> torch.Tensor:

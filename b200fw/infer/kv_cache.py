@@ -16,6 +16,11 @@ import torch
 
 from ..obs.logging import get_logger
 
+# fp8 K/V is stored as e4m3 bytes (uint8 tensors, one fp32 scale per block and kv head; the kernels convert); these two
+# names say so in the reference's terms (src/inference/kv_cache.py:30-38)
+HAS_FP8 = hasattr(torch, "float8_e4m3fn")
+_FP8_DTYPE = getattr(torch, "float8_e4m3fn", None)
+
 logger = get_logger("infer.kv_cache")
 
 

@@ -29,9 +29,15 @@ class NonRetriableError(Exception):
     pass
 
 
+# The retry taxonomy under the reference's names (src/transfer/ipc_transfer.py:53-65): network-side failures are worth
+# another attempt, malformed data is not.  ``classify_error`` is what the client consults.
+RETRIABLE_EXCEPTIONS = (TimeoutError, ConnectionError, OSError)
+NON_RETRIABLE_EXCEPTIONS = (ValueError, KeyError, TypeError, NonRetriableError)
+
+
 def classify_error(e: BaseException) -> str:
     """'fatal' (never retry), 'oom' (retry once), or 'retry'."""
-    if isinstance(e, (ValueError, KeyError, TypeError, NonRetriableError)):
+    if isinstance(e, NON_RETRIABLE_EXCEPTIONS):
         return "fatal"
     if "out of memory" in str(e).lower():
         return "oom"

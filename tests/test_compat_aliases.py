@@ -1,0 +1,127 @@
+"""``b200fw.compat``: code written against the reference's ``src.*`` package layout imports unchanged.
+
+The table below lists every ``from src.<module> import <names>`` (and ``import src.<module>``) that occurs in the
+reference's own package, scripts and tests; each must resolve through the aliases to an object of this package."""
+import importlib
+import subprocess
+import sys
+import textwrap
+
+import pytest
+
+REFERENCE_IMPORTS = {
+    "src.data.data_pipeline": ["GRPOBatch", "GSM8KDataPipeline"],
+    "src.distributed": ["ParallelContext", "ParallelTransformerModel", "ZeROOptimizer", "ZeROStage2Optimizer", "ZeROStage3Optimizer", "comm"],
+    "src.distributed.comm": ["AsyncAllReduce", "all_gather", "all_gather_last_dim", "all_reduce", "all_reduce_async", "broadcast", "copy_to_parallel_region", "gather_from_parallel_region", "recv_backward", "recv_forward", "reduce_from_parallel_region", "reduce_scatter", "send_backward", "send_backward_recv_forward", "send_forward", "send_forward_recv_backward"],
+    "src.distributed.lora": ["LinearWithLoRA", "LoRAColumnParallel", "LoRALayer", "LoRARowParallel", "apply_lora", "get_lora_state_dict", "merge_lora_weights"],
+    "src.distributed.parallel_context": ["ParallelContext"],
+    "src.distributed.pipeline_parallel": ["PipelineParallelContext", "split_layers_to_stages"],
+    "src.distributed.pipeline_scheduler": ["PipelineScheduler", "default_loss_fn"],
+    "src.distributed.stream_manager": ["StreamManager"],
+    "src.distributed.tensor_parallel": ["ColumnParallelLinear", "ParallelAttention", "ParallelMLP", "ParallelTransformerLayer", "ParallelTransformerModel", "RMSNorm", "RowParallelLinear", "load_from_hf_checkpoint"],
+    "src.distributed.zero_optim": ["ZeROOptimizer"],
+    "src.distributed.zero_optim_v2": ["ZeROStage2Optimizer"],
+    "src.distributed.zero_optim_v3": ["ZeROStage3Optimizer"],
+    "src.engines.c3po_plus": ["C3POConfig", "C3POPlusScheduler"],
+    "src.engines.icepop": ["IcePopConfig", "IcePopFilter"],
+    "src.engines.infer_worker": ["get_infer_worker_class"],
+    "src.engines.train_engine": ["TrainConfig", "TrainEngine", "TrainMetrics"],
+    "src.engines.train_worker": ["get_train_worker_class"],
+    "src.inference.attention": ["HAS_FLASH_ATTN", "PagedAttention", "PartitionedPagedAttention", "store_kv_cache"],
+    "src.inference.context": ["InferenceContext", "get_context", "reset_context", "set_context"],
+    "src.inference.cuda_graph": ["CUDAGraphRunner"],
+    "src.inference.engine": ["InferenceConfig", "InferenceEngine"],
+    "src.inference.kv_cache": ["Block", "BlockPool", "BlockTable", "HAS_FP8", "KVCacheManager", "_FP8_DTYPE"],
+    "src.inference.model_runner": ["ModelRunner", "ModelRunnerConfig"],
+    "src.inference.prefix_cache": ["CachedBlock", "PrefixCache"],
+    "src.inference.radix_cache": ["RadixAttentionCache", "RadixNode"],
+    "src.inference.scheduler": ["ContinuousBatchingScheduler", "Request", "RequestState", "SchedulerOutput"],
+    "src.inference.speculative": ["SpeculativeConfig", "SpeculativeDecoder"],
+    "src.kernels": ["flash_attention_triton"],
+    "src.orchestrator.colocate_orchestrator": ["ColocateConfig", "ColocateOrchestrator", "IterationMetrics", "OrchestratorState"],
+    "src.orchestrator.disagg_orchestrator": ["DisaggConfig", "DisaggOrchestrator"],
+    "src.profiling.comm_profiler": ["CommProfiler", "CommRecord"],
+    "src.profiling.compute_profiler": ["ComputeProfiler", "LayerProfile"],
+    "src.profiling.schedule_visualizer": ["ScheduleEvent", "ScheduleVisualizer"],
+    "src.reward.gsm8k_reward": ["GSM8KRewardFunction", "compute_batch_rewards", "compute_reward"],
+    "src.transfer.ipc_transfer": ["IPCHandle", "IPCWeightTransfer", "NON_RETRIABLE_EXCEPTIONS", "RETRIABLE_EXCEPTIONS", "TransferStats", "VLLMClient", "WeightUpdateManager"],
+    "src.transfer.nccl_transfer": ["NCCLWeightTransfer", "RayObjectStoreTransfer", "WeightTransferManager"],
+    "src.transfer.swift_sync": ["DeltaComputer", "DeltaVersion", "DoubleBufferedLoRA", "SwiftSyncConfig", "SwiftSyncTransfer"],
+    "src.utils.artifact_writer": ["ArtifactWriter"],
+    "src.utils.eval_utils": ["EvalMetrics", "compute_bleu4", "compute_exact_match", "compute_token_f1", "normalize_text"],
+    "src.utils.logger": ["get_logger", "setup_logger"],
+    "src.utils.memory_manager": ["MemoryManager"],
+    "src.utils.memory_profiler": ["MemoryBreakdown", "MemoryProfiler", "MemoryReport", "MemorySnapshot"],
+    "src.utils.metrics": ["MetricsCollector"],
+}
+
+
+@pytest.fixture()
+def aliases():
+    import b200fw.compat as compat
+    had = compat.installed()
+    if not compat.install():
+        pytest.skip("a real `src` package is importable in this environment")
+    yield compat
+    if not had:
+        compat.uninstall()
+
+
+@pytest.mark.parametrize("module", sorted(REFERENCE_IMPORTS))
+def test_every_name_the_reference_imports_resolves(aliases, module):
+    m = importlib.import_module(module)
+    missing = [n for n in REFERENCE_IMPORTS[module] if not hasattr(m, n)]
+    assert not missing, (module, missing)
+    assert all(t.startswith("b200fw") for t in m.__b200fw_targets__)
+
+
+def test_aliases_give_the_same_objects_and_can_be_removed(aliases):
+    from src.engines.train_engine import TrainConfig, TrainEngine
+    from src.transfer.swift_sync import DoubleBufferedLoRA, SwiftSyncTransfer
+    import b200fw.sync as sync
+    import b200fw.train as train
+    assert TrainEngine is train.TrainEngine and TrainConfig is train.TrainConfig
+    assert DoubleBufferedLoRA is sync.DoubleBufferedLoRA and SwiftSyncTransfer is sync.SwiftSyncTransfer
+    import src.kernels
+    assert src.kernels.flash_attention_triton is None
+    aliases.uninstall()
+    assert not any(k == "src" or k.startswith("src.") for k in sys.modules)
+    with pytest.raises(ImportError):
+        importlib.import_module("src.engines.train_engine")
+    assert aliases.install()
+
+
+def test_reference_style_program_runs_through_the_aliases(tmp_path):
+    """A small program in the reference's style (its imports, its constructor forms) in a fresh interpreter."""
+    prog = tmp_path / "user_code.py"
+    prog.write_text(textwrap.dedent("""
+        import b200fw.compat
+        assert b200fw.compat.install()
+        import torch
+        from src.distributed.parallel_context import ParallelContext
+        from src.distributed.tensor_parallel import ParallelTransformerModel
+        from src.distributed.lora import apply_lora
+        from src.engines.icepop import IcePopConfig, IcePopFilter
+        from src.inference.engine import InferenceConfig, InferenceEngine
+        from src.transfer.swift_sync import DeltaComputer
+        ctx = ParallelContext(tp_size=1, tp_group=None)
+        model = ParallelTransformerModel(vocab_size=64, hidden_size=32, num_layers=2, num_heads=4, num_kv_heads=2,
+                                         head_dim=8, intermediate_size=48, parallel_context=ctx,
+                                         max_position_embeddings=32)
+        logits = model(torch.randint(0, 64, (2, 8)))
+        assert logits.shape == (2, 8, 64)
+        names = apply_lora(model, rank=4, alpha=8.0)
+        assert len(names) == 2 * 7
+        eng = InferenceEngine(InferenceConfig(inference_mode="mock", vocab_size=64)).initialize()
+        out = eng.generate([[5, 6, 7]], max_tokens=4)
+        assert len(out[0]) == 4
+        d = DeltaComputer(10)
+        d.compute_delta({"a": torch.ones(2)})
+        assert torch.equal(d.compute_delta({"a": torch.full((2,), 3.0)})["a"], torch.full((2,), 2.0))
+        print("ok")
+    """))
+    import os
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, PYTHONPATH=root)
+    r = subprocess.run([sys.executable, str(prog)], cwd=str(tmp_path), env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and r.stdout.strip().endswith("ok"), r.stderr[-2000:]
