@@ -46,14 +46,14 @@ def all_gather_last_dim(t: torch.Tensor, group=None) -> torch.Tensor:
     return torch.cat(parts, dim=-1)
 
 
-def reduce_scatter(t: torch.Tensor, group=None) -> torch.Tensor:
-    """Sum over ranks, keep this rank's dim-0 slice."""
+def reduce_scatter(t: torch.Tensor, group=None, op=None) -> torch.Tensor:
+    """Reduce over ranks (sum unless ``op`` says otherwise), keep this rank's dim-0 slice."""
     n = _size(group)
     if n == 1:
         return t
     assert t.shape[0] % n == 0
     out = torch.empty((t.shape[0] // n,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
-    dist.reduce_scatter_tensor(out, t.contiguous(), group=group)
+    dist.reduce_scatter_tensor(out, t.contiguous(), op=op if op is not None else dist.ReduceOp.SUM, group=group)
     return out
 
 

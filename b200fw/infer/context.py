@@ -52,8 +52,22 @@ class InferenceContext:
 _CONTEXT: Optional[InferenceContext] = None
 
 
-def set_context(is_prefill: bool, **fields) -> InferenceContext:
+_SET_CONTEXT_ORDER = ("cu_seqlens_q", "cu_seqlens_k", "max_seqlen_q", "max_seqlen_k", "slot_mapping", "context_lens",
+                      "block_tables")
+
+
+def set_context(is_prefill: bool, *args, **fields) -> InferenceContext:
+    """Publish the step's metadata.  Fields by keyword; positionally they follow the reference's order
+    (src/inference/context.py:43-62): cu_seqlens_q, cu_seqlens_k, max_seqlen_q, max_seqlen_k, slot_mapping,
+    context_lens, block_tables."""
     global _CONTEXT
+    if len(args) > len(_SET_CONTEXT_ORDER):
+        raise TypeError("set_context() takes at most %d positional fields" % len(_SET_CONTEXT_ORDER))
+    for name, value in zip(_SET_CONTEXT_ORDER, args):
+        if name in fields:
+            raise TypeError(f"set_context() got multiple values for {name!r}")
+        if value is not None:
+            fields[name] = value
     _CONTEXT = InferenceContext(is_prefill, fields.pop("num_seqs", 0), **fields)
     return _CONTEXT
 

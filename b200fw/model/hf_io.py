@@ -58,9 +58,13 @@ def _cols(t: torch.Tensor, rank: int, tp: int) -> torch.Tensor:
     return t[:, rank * n:(rank + 1) * n]
 
 
-def load_from_hf_checkpoint(model, path: str, strict: bool = False) -> Tuple[int, int]:
+def load_from_hf_checkpoint(model, path: str, strict=False, parallel_context=None) -> Tuple[int, int]:
     """Copy the weights under ``path`` into ``model`` (any TP rank / PP stage).  Returns
-    ``(loaded, missing)`` parameter counts; missing keys are skipped unless ``strict``."""
+    ``(loaded, missing)`` parameter counts; missing keys are skipped unless ``strict``.  The reference passes its
+    parallel context in third place (src/distributed/tensor_parallel.py:947-1064); here the shard to read follows
+    from the model's own layout, so a context given there (or as ``parallel_context``) is accepted and not needed."""
+    if not isinstance(strict, bool):
+        strict = False
     sd = _load_all(path)
     tp, rank = model.tp_size, model.tp_rank
     loaded = missing = 0

@@ -206,10 +206,22 @@ def _sub_ranges(parent) -> Dict[str, Tuple[str, int, int]]:
     return out
 
 
-def apply_lora(model: nn.Module, rank: int = 16, alpha: float = 32.0,
-               target_modules: Optional[Iterable[str]] = None) -> List[str]:
+def apply_lora(model: nn.Module, rank=16, alpha=32.0, target_modules: Optional[Iterable[str]] = None):
     """Freeze every existing parameter and attach adapters to the targeted projections.
-    Returns the qualified names of the adapted sub-projections."""
+    Returns the qualified names of the adapted sub-projections.
+
+    The reference's call ``apply_lora(model, lora_config, parallel_context)`` (src/distributed/lora.py:259-343: a dict
+    with ``rank`` / ``alpha`` / ``target_modules`` / ``dropout``) is recognised by the dict in second place and returns
+    the model, as the reference does; the names are then in ``model.lora_adapted_names``.  (The parallel layout is
+    read from the layers themselves; adapter dropout is not implemented and a non-zero value is refused.)"""
+    if isinstance(rank, dict):
+        cfg = rank
+        if float(cfg.get("dropout", 0.0) or 0.0) != 0.0:
+            raise ValueError("LoRA dropout is not supported: set lora.dropout to 0")
+        names = apply_lora(model, int(cfg.get("rank", 16)), float(cfg.get("alpha", 32.0)),
+                           cfg.get("target_modules") or None)
+        model.lora_adapted_names = names
+        return model
     targets = list(target_modules) if target_modules is not None else list(DEFAULT_TARGETS)
     for p in model.parameters():
         p.requires_grad_(False)

@@ -24,14 +24,18 @@ class _Formatter(logging.Formatter):
 
 
 def setup_logger(name: str = _ROOT, level: str = "INFO", log_file: Optional[str] = None,
-                 rank: Optional[int] = None) -> logging.Logger:
+                 rank: Optional[int] = None, use_color: Optional[bool] = None) -> logging.Logger:
+    """``use_color`` (the reference's fourth argument, src/utils/logger.py:44-100; a bool given in its place is taken
+    as that): force colours on or off; by default the stream handler colours only when stderr is a terminal."""
+    if isinstance(rank, bool):
+        rank, use_color = None, rank
     logger = logging.getLogger(name)
     logger.setLevel(getattr(logging, level.upper(), logging.INFO))
     logger.propagate = False
     for h in list(logger.handlers):
         logger.removeHandler(h)
     sh = logging.StreamHandler(sys.stderr)
-    sh.setFormatter(_Formatter(color=sys.stderr.isatty()))
+    sh.setFormatter(_Formatter(color=sys.stderr.isatty() if use_color is None else bool(use_color)))
     logger.addHandler(sh)
     if log_file:
         path = log_file if rank is None else f"{log_file}.rank{rank}"

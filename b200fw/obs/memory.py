@@ -185,6 +185,128 @@ class MemoryProfiler:
         self.reset_peak()
 
 
+class StepMemoryReporter:
+    """The reference's way of using its ``MemoryReport``: an object built as ``MemoryReport(model, optimizer, config)``
+    whose ``profile_step(input_ids, labels, train_step_fn)`` / ``generate_report_without_step()`` return a plain dict
+    with the sections ``model_spec``, ``static_memory``, ``dynamic_memory``, ``framework_overhead`` and
+    ``peak_moments`` (src/utils/memory_profiler.py:409-546; ``scripts/profile_memory.py`` prints from them).
+    ``MemoryReport(model, ...)`` returns one of these; the dataclass form is for reports assembled from a
+    :class:`MemoryProfiler`.  Byte counts come from the tensors themselves, peaks from the CUDA allocator (zero on a
+    CPU)."""
+
+    def __init__(self, model: torch.nn.Module, optimizer=None, config: Optional[Dict[str, Any]] = None):
+        self.model, self.optimizer, self.config = model, optimizer, dict(config or {})
+
+    # ---- sections -----------------------------------------------------------------------------------------------
+    @staticmethod
+    def _readable(n: int) -> str:
+        for unit, div in (("B", 1e9), ("M", 1e6), ("K", 1e3)):
+            if n >= div:
+                return f"{n / div:.2f}{unit}"
+        return str(n)
+
+    def _model_spec(self) -> Dict[str, Any]:
+        params = list(self.model.parameters())
+        total = sum(p.numel() for p in params)
+        trainable = sum(p.numel() for p in params if p.requires_grad)
+        by_dtype: Dict[str, int] = {}
+        for p in params:
+            by_dtype[str(p.dtype).replace("torch.", "")] = by_dtype.get(str(p.dtype).replace("torch.", ""), 0) + p.numel()
+        return {"total_params": total, "trainable_params": trainable, "frozen_params": total - trainable,
+                "total_params_readable": self._readable(total), "trainable_params_readable": self._readable(trainable),
+                "trainable_ratio": trainable / total if total else 0.0, "precision_distribution": by_dtype}
+
+    def _static_memory(self) -> Dict[str, float]:
+        gb = 1e9
+        frozen16 = frozen32 = train = grads = 0
+        for p in self.model.parameters():
+            b = p.numel() * p.element_size()
+            if p.requires_grad:
+                train += b
+                mg = getattr(p, "main_grad", None)
+                g = p.grad if p.grad is not None else mg
+                grads += g.numel() * g.element_size() if g is not None else b
+            elif p.element_size() <= 2:
+                frozen16 += b
+            else:
+                frozen32 += b
+        opt = 0
+        o = self.optimizer
+        if o is not None and hasattr(o, "memory_bytes"):
+            mb = o.memory_bytes()
+            opt = sum(mb.values()) if isinstance(mb, dict) else int(mb)
+        elif o is not None and hasattr(o, "state"):
+            opt = sum(t.numel() * t.element_size() for st in o.state.values() for t in st.values() if torch.is_tensor(t))
+        out = {"frozen_weights_bf16_gb": frozen16 / gb, "frozen_weights_fp32_gb": frozen32 / gb,
+               "trainable_weights_gb": train / gb, "gradients_gb": grads / gb, "optimizer_states_gb": opt / gb}
+        out["static_total_gb"] = sum(out.values())
+        return out
+
+    def _overhead(self, device) -> Dict[str, float]:
+        if device.type != "cuda":
+            return {"pytorch_caching_gb": 0.0, "cuda_context_estimated_gb": 0.0}
+        free, total = torch.cuda.mem_get_info(device)
+        return {"pytorch_caching_gb": (torch.cuda.memory_reserved(device) - torch.cuda.memory_allocated(device)) / 1e9,
+                # what the device reports in use beyond this process's allocator: context, libraries, other tenants
+                "cuda_context_estimated_gb": max(0.0, (total - free - torch.cuda.memory_reserved(device)) / 1e9),
+                "device_total_memory_gb": total / 1e9}
+
+    def generate_report_without_step(self) -> Dict[str, Any]:
+        device = next(self.model.parameters()).device
+        return {"model_spec": self._model_spec(), "static_memory": self._static_memory(), "dynamic_memory": {},
+                "framework_overhead": self._overhead(device), "peak_moments": {}, "config": self.config}
+
+    def profile_step(self, input_ids, labels=None, train_step_fn=None) -> Dict[str, Any]:
+        """One measured step.  With ``train_step_fn`` that callable is the step; without one the step is a forward
+        pass, the shifted next-token loss over ``labels`` (``-100`` ignored) and a backward pass."""
+        device = next(self.model.parameters()).device
+        cuda = device.type == "cuda"
+        report = self.generate_report_without_step()
+        prof = MemoryProfiler(device)
+        prof.attach_layer_hooks(self.model)
+
+        def peak_gb():
+            if not cuda:
+                return 0.0
+            torch.cuda.synchronize(device)
+            return torch.cuda.max_memory_allocated(device) / 1e9
+
+        try:
+            before = torch.cuda.memory_allocated(device) if cuda else 0
+            prof.reset_peak()
+            with torch.no_grad():
+                self.model(input_ids)
+            report["peak_moments"]["forward_peak_gb"] = peak_gb()
+            report["peak_moments"]["forward_activation_gb"] = \
+                ((torch.cuda.memory_allocated(device) - before) / 1e9) if cuda else 0.0
+            prof.reset_peak()
+            self.model.train()
+            if train_step_fn is not None:
+                train_step_fn(input_ids, labels)
+            else:
+                logits = self.model(input_ids)
+                if labels is not None:
+                    loss = torch.nn.functional.cross_entropy(
+                        logits[:, :-1, :].reshape(-1, logits.shape[-1]).float(), labels[:, 1:].reshape(-1),
+                        ignore_index=-100)
+                    loss.backward()
+            report["peak_moments"]["backward_peak_gb"] = peak_gb()
+            if train_step_fn is None and self.optimizer is not None and hasattr(self.optimizer, "step"):
+                prof.reset_peak()
+                try:
+                    self.optimizer.step()
+                    self.optimizer.zero_grad()
+                except Exception as e:  # noqa: BLE001 - the report is still useful without the optimizer phase
+                    report["peak_moments"]["optimizer_step_error"] = f"{type(e).__name__}: {e}"
+            report["peak_moments"]["step_peak_gb"] = max(peak_gb(), report["peak_moments"]["backward_peak_gb"])
+        finally:
+            prof.detach_hooks()
+        report["dynamic_memory"] = {"per_layer_peak_mb": dict(prof.layer_peaks)}
+        report["static_memory"] = self._static_memory()      # gradients and optimizer state exist now
+        report["framework_overhead"] = self._overhead(device)
+        return report
+
+
 @dataclass
 class MemoryReport:
     breakdown: Optional[MemoryBreakdown] = None
@@ -193,6 +315,12 @@ class MemoryReport:
     layer_peaks: Dict[str, float] = field(default_factory=dict)
     optimizer_bytes: Dict[str, int] = field(default_factory=dict)
     notes: List[str] = field(default_factory=list)
+
+    def __new__(cls, *args, **kwargs):
+        # the reference's form ``MemoryReport(model, optimizer, config)``: a reporter object (see StepMemoryReporter)
+        if args and isinstance(args[0], torch.nn.Module):
+            return StepMemoryReporter(*args, **kwargs)
+        return super().__new__(cls)
 
     @classmethod
     def from_profiler(cls, prof: MemoryProfiler, breakdown: Optional[MemoryBreakdown] = None,

@@ -125,3 +125,47 @@ def test_reference_style_program_runs_through_the_aliases(tmp_path):
     env = dict(os.environ, PYTHONPATH=root)
     r = subprocess.run([sys.executable, str(prog)], cwd=str(tmp_path), env=env, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0 and r.stdout.strip().endswith("ok"), r.stderr[-2000:]
+
+
+def test_reference_call_forms_of_module_level_functions(tmp_path):
+    """Positional forms that differ from this package's own: ``apply_lora(model, dict, ctx)``,
+    ``load_from_hf_checkpoint(model, path, ctx)``, ``set_context(is_prefill, cu_q, cu_k, ...)``,
+    ``setup_logger(name, level, file, use_color)``, ``MemoryReport(model, optimizer, config)`` as a reporter object."""
+    import torch
+    from b200fw.dist.context import ParallelContext
+    from b200fw.infer.context import get_context, reset_context, set_context
+    from b200fw.model import ModelConfig, ParallelTransformerModel, apply_lora, load_from_hf_checkpoint, save_hf_checkpoint
+    from b200fw.obs.logging import setup_logger
+    from b200fw.obs.memory import MemoryReport, StepMemoryReporter
+    ctx = ParallelContext(tp_size=1, tp_group=None)
+    mc = ModelConfig(vocab_size=64, hidden_size=32, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=8,
+                     intermediate_size=48, max_position_embeddings=32, tie_word_embeddings=False)
+    src = ParallelTransformerModel(mc)
+    src.init_weights(3)
+    save_hf_checkpoint(src, str(tmp_path / "ckpt"))
+    model = ParallelTransformerModel(mc)
+    loaded, missing = load_from_hf_checkpoint(model, str(tmp_path / "ckpt"), ctx)
+    assert loaded > 0 and missing == 0 and torch.equal(model.embed_tokens, src.embed_tokens)
+    out = apply_lora(model, {"rank": 4, "alpha": 8.0, "target_modules": ["q_proj", "v_proj"], "dropout": 0.0}, ctx)
+    assert out is model and len(model.lora_adapted_names) == 2 * 2
+    assert all(("lora_" in n) == p.requires_grad for n, p in model.named_parameters())
+    with pytest.raises(ValueError):
+        apply_lora(ParallelTransformerModel(mc), {"rank": 4, "dropout": 0.1}, ctx)
+    cu = torch.tensor([0, 3], dtype=torch.int32)
+    c = set_context(True, cu, cu, 3, 3, torch.tensor([0, 1, 2]))
+    assert c.is_prefill and c.max_seqlen_q == 3 and c.max_seqlen_k == 3 and get_context() is c and c.slot_mapping.numel() == 3
+    reset_context()
+    lg = setup_logger("b200fw.test_compat", "INFO", None, False)
+    assert lg.handlers
+    opt = torch.optim.AdamW([p for p in model.parameters() if p.requires_grad], lr=1e-3)
+    rep = MemoryReport(model, opt, {"batch_size": 2})
+    assert isinstance(rep, StepMemoryReporter)
+    ids = torch.randint(0, 64, (2, 8))
+    labels = ids.clone()
+    labels[:, :4] = -100
+    r = rep.profile_step(ids, labels, train_step_fn=None)
+    assert set(r) >= {"model_spec", "static_memory", "dynamic_memory", "framework_overhead", "peak_moments"}
+    assert r["model_spec"]["trainable_params"] == sum(p.numel() for p in model.parameters() if p.requires_grad)
+    assert r["static_memory"]["optimizer_states_gb"] > 0 and "backward_peak_gb" in r["peak_moments"]
+    assert rep.generate_report_without_step()["static_memory"]["static_total_gb"] > 0
+    assert isinstance(MemoryReport(), MemoryReport)                     # the dataclass form is untouched
