@@ -62,30 +62,34 @@ class DisaggConfig:
     async_weight_update: bool = True
     max_data_samples: int = 0
 
-    # the reference sizes its two groups by tensor-parallel degree and GPU lists
-    @property
-    def train_tp_size(self) -> int:
-        return self.num_train_gpus
+    # The reference sizes its two groups by tensor-parallel degree and GPU lists and names the sync backend and the
+    # overlap switch differently (src/orchestrator/disagg_orchestrator.py:40-70; its run_disaggregated.py passes
+    # these as keywords).  Given, they set the fields above; afterwards they always mirror them.
+    train_tp_size: Optional[int] = None
+    infer_tp_size: Optional[int] = None
+    train_gpus: Optional[List[int]] = None
+    infer_gpus: Optional[List[int]] = None
+    weight_sync_backend: Optional[str] = None           # "nccl" | "peer_write"; "ray_object_store" runs as "nccl" here
+    overlap_training_inference: Optional[bool] = None
 
-    @property
-    def infer_tp_size(self) -> int:
-        return self.num_infer_gpus
-
-    @property
-    def train_gpus(self) -> List[int]:
-        return list(range(self.num_train_gpus))
-
-    @property
-    def infer_gpus(self) -> List[int]:
-        return list(range(self.num_train_gpus, self.num_train_gpus + self.num_infer_gpus))
-
-    @property
-    def weight_sync_backend(self) -> str:
-        return self.transfer_backend
-
-    @property
-    def overlap_training_inference(self) -> bool:
-        return self.mode == "pipeline"
+    def __post_init__(self):
+        if self.train_gpus is not None:
+            self.num_train_gpus = len(self.train_gpus)
+        elif self.train_tp_size is not None:
+            self.num_train_gpus = int(self.train_tp_size)
+        if self.infer_gpus is not None:
+            self.num_infer_gpus = len(self.infer_gpus)
+        elif self.infer_tp_size is not None:
+            self.num_infer_gpus = int(self.infer_tp_size)
+        if self.weight_sync_backend is not None:
+            self.transfer_backend = self.weight_sync_backend if self.weight_sync_backend in ("nccl", "peer_write") else "nccl"
+        if self.overlap_training_inference is not None:
+            self.mode = "pipeline" if self.overlap_training_inference else "sequential"
+        self.train_tp_size, self.infer_tp_size = self.num_train_gpus, self.num_infer_gpus
+        self.train_gpus = list(range(self.num_train_gpus))
+        self.infer_gpus = list(range(self.num_train_gpus, self.num_train_gpus + self.num_infer_gpus))
+        self.weight_sync_backend = self.transfer_backend
+        self.overlap_training_inference = self.mode == "pipeline"
 
 
 @dataclass

@@ -169,3 +169,94 @@ def test_reference_call_forms_of_module_level_functions(tmp_path):
     assert r["static_memory"]["optimizer_states_gb"] > 0 and "backward_peak_gb" in r["peak_moments"]
     assert rep.generate_report_without_step()["static_memory"]["static_total_gb"] > 0
     assert isinstance(MemoryReport(), MemoryReport)                     # the dataclass form is untouched
+
+
+# keyword arguments the reference's entry scripts pass to the config classes (scripts/run_colocate.py,
+# run_disaggregated.py, run_inference.py)
+SCRIPT_CONFIG_KEYWORDS = {
+    "ColocateConfig": ['model_path', 'tp_size', 'pp_size', 'num_micro_batches', 'dp_size', 'max_seq_len', 'use_flash_attn',
+                       'attention_backend', 'use_gradient_checkpoint', 'training_mode', 'output_dir', 'checkpoint_save_dir',
+                       'checkpoint_save_interval', 'checkpoint_save_enabled', 'resume_from', 'total_iterations', 'batch_size',
+                       'train_steps_per_iteration', 'gradient_accumulation_steps', 'inference_backend', 'vllm_url',
+                       'num_samples_per_prompt', 'max_tokens', 'temperature', 'top_p', 'lora_rank', 'lora_alpha',
+                       'lora_target_modules', 'learning_rate', 'weight_decay', 'max_grad_norm', 'amp_dtype', 'grpo_beta',
+                       'grpo_clip_eps', 'lr_scheduler_type', 'warmup_steps', 'min_lr_ratio', 'max_data_samples',
+                       'dataset_name', 'dataset_config', 'dataset_split', 'prompt_template', 'prompt_field', 'input_field',
+                       'response_field', 'answer_field', 'eval_max_tokens', 'eval_num_prompts', 'enable_comm_overlap',
+                       'zero_stage', 'inference_preview_enabled', 'enable_profiling', 'profile_interval', 'icepop_enabled',
+                       'icepop_divergence_threshold', 'icepop_max_mask_ratio', 'c3po_plus_enabled', 'c3po_plus_token_budget',
+                       'c3po_plus_target_batch_tokens', 'c3po_plus_packing_strategy', 'swift_sync_enabled',
+                       'swift_sync_fallback_full_every', 'swift_sync_double_buffer', 'async_pipeline_enabled',
+                       'async_pipeline_max_staleness', 'async_pipeline_queue_size'],
+    "DisaggConfig": ['model_path', 'train_tp_size', 'infer_tp_size', 'total_iterations', 'batch_size',
+                     'num_samples_per_prompt', 'weight_sync_backend', 'overlap_training_inference', 'lora_rank',
+                     'learning_rate', 'max_tokens'],
+    "InferenceConfig": ['model_path', 'inference_mode', 'num_layers', 'num_heads', 'num_kv_heads', 'head_dim', 'hidden_size',
+                        'vocab_size', 'num_blocks', 'block_size', 'max_num_batched_tokens', 'max_num_sequences',
+                        'enable_prefix_caching', 'enable_cuda_graph', 'enable_async_scheduling',
+                        'enable_partitioned_attention', 'temperature', 'top_p'],
+}
+
+
+def test_config_classes_take_every_keyword_the_reference_scripts_pass():
+    import dataclasses
+    from b200fw.config import ColocateConfig
+    from b200fw.infer import InferenceConfig
+    from b200fw.orch import DisaggConfig
+    for cls in (ColocateConfig, DisaggConfig, InferenceConfig):
+        fields = {f.name for f in dataclasses.fields(cls)}
+        missing = [k for k in SCRIPT_CONFIG_KEYWORDS[cls.__name__] if k not in fields]
+        assert not missing, (cls.__name__, missing)
+
+
+def test_text_data_run_in_the_reference_style(tmp_path):
+    """What the reference's ``scripts/run_colocate.py`` does with a YAML that names an HF model directory and a local
+    JSONL dataset: ``ColocateConfig`` from the reference's keywords, ``ColocateOrchestrator.initialize`` / ``run`` /
+    ``get_summary`` / ``shutdown``, SFT and GRPO, text prompts through a tokenizer, the artefact files."""
+    pytest.importorskip("transformers")
+    pytest.importorskip("tokenizers")
+    import asyncio
+    import json
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    from transformers import PreTrainedTokenizerFast
+    from b200fw.config import ColocateConfig
+    from b200fw.model import ModelConfig, ParallelTransformerModel, save_hf_checkpoint
+    from b200fw.orch import ColocateOrchestrator
+    vocab = {"<pad>": 0, "<unk>": 1, "</s>": 2}
+    words = "what is plus the sum answer".split() + [str(i) for i in range(40)] + ["####", "?", "."]
+    for w in words:
+        vocab.setdefault(w, len(vocab))
+    tok = Tokenizer(models.WordLevel(vocab, unk_token="<unk>"))
+    tok.pre_tokenizer = pre_tokenizers.Whitespace()
+    mdir = tmp_path / "model"
+    mc = ModelConfig(vocab_size=64, hidden_size=32, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=8,
+                     intermediate_size=48, max_position_embeddings=128, tie_word_embeddings=False)
+    m = ParallelTransformerModel(mc)
+    m.init_weights(0)
+    save_hf_checkpoint(m, str(mdir))
+    PreTrainedTokenizerFast(tokenizer_object=tok, pad_token="<pad>", unk_token="<unk>", eos_token="</s>").save_pretrained(str(mdir))
+    rows = [{"question": f"what is {i} plus {i + 1} ?", "answer": f"the sum is {2 * i + 1} . #### {2 * i + 1}"} for i in range(12)]
+    (tmp_path / "data.jsonl").write_text("\n".join(json.dumps(r) for r in rows))
+    for mode in ("sft", "grpo"):
+        cfg = ColocateConfig(model_path=str(mdir), tp_size=1, pp_size=1, dp_size=1, num_micro_batches=1, max_seq_len=64,
+                             use_flash_attn=False, attention_backend="sdpa", training_mode=mode,
+                             output_dir=str(tmp_path / f"out_{mode}"), checkpoint_save_enabled=False, total_iterations=2,
+                             batch_size=2, gradient_accumulation_steps=1, inference_backend="custom",
+                             num_samples_per_prompt=2, max_tokens=4, lora_rank=4, lora_alpha=8.0, amp_dtype="fp32",
+                             grpo_beta=0.01, warmup_steps=0, max_data_samples=8, dataset_name=str(tmp_path / "data.jsonl"),
+                             dataset_split="train", prompt_field="question", response_field="answer",
+                             answer_field="answer", zero_stage=1, eval_num_prompts=0)
+
+        async def go():
+            o = ColocateOrchestrator(cfg)
+            await o.initialize()
+            await o.run()
+            s = o.get_summary()
+            await o.shutdown()
+            return s
+
+        s = asyncio.run(go())
+        assert s["results"]["completed_iterations"] == 2 and s["results"]["failed_iterations"] == 0
+        out = tmp_path / f"out_{mode}"
+        for name in ("config_snapshot.json", "run_summary.json", "metrics_rank0.jsonl", "loss_curve.csv"):
+            assert (out / name).exists(), name
