@@ -25,8 +25,12 @@ DEFAULT_TARGETS = ["q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj
 class LoRALayer(nn.Module):
     """Plain (unsharded) adapter: ``delta(x) = (x A^T) B^T * alpha/r``; A kaiming-uniform, B zero."""
 
-    def __init__(self, in_features, out_features, rank=16, alpha=32.0, device=None):
+    def __init__(self, in_features, out_features, rank=16, alpha=32.0, device=None, dropout: float = 0.0):
         super().__init__()
+        if isinstance(device, float):            # the reference's fifth argument is the dropout rate
+            device, dropout = None, device
+        if dropout:
+            raise ValueError("LoRA dropout is not supported: use dropout=0")
         self.rank, self.alpha, self.scaling = rank, alpha, alpha / rank
         self.lora_A = nn.Parameter(torch.empty(rank, in_features, dtype=torch.float32, device=device))
         self.lora_B = nn.Parameter(torch.zeros(out_features, rank, dtype=torch.float32, device=device))

@@ -393,9 +393,25 @@ class MemoryManager:
     """Watches utilisation; above ``warn`` it logs, above ``critical`` it empties the caching
     allocator; can hold back a reserve block that is released when an OOM is being handled."""
 
-    def __init__(self, warn: float = 0.85, critical: float = 0.95, reserve_mb: int = 0,
-                 device: Optional[torch.device] = None):
-        self.warn, self.critical, self.device = warn, critical, device
+    def __init__(self, *args, warn: float = 0.85, critical: float = 0.95, reserve_mb: int = 0,
+                 device: Optional[torch.device] = None, warning_threshold: Optional[float] = None,
+                 critical_threshold: Optional[float] = None):
+        """``MemoryManager(warn, critical, reserve_mb, device)``; or, in the reference's order
+        (src/utils/memory_manager.py:22-40), ``MemoryManager(device, warning_threshold, critical_threshold)``: a device
+        (index, name or ``torch.device``) in first place selects that form."""
+        if args and (isinstance(args[0], (str, torch.device)) or (isinstance(args[0], int) and not isinstance(args[0], bool))):
+            names = ("device", "warn", "critical")
+        else:
+            names = ("warn", "critical", "reserve_mb", "device")
+        given = dict(warn=warn, critical=critical, reserve_mb=reserve_mb, device=device)
+        for name, value in zip(names, args):
+            given[name] = value
+        warn, critical, reserve_mb, device = given["warn"], given["critical"], given["reserve_mb"], given["device"]
+        warn = warning_threshold if warning_threshold is not None else warn
+        critical = critical_threshold if critical_threshold is not None else critical
+        if isinstance(device, int):
+            device = torch.device("cuda", device)
+        self.warn, self.critical, self.device = float(warn), float(critical), device
         self.enabled = torch.cuda.is_available()
         self._reserve = None
         self.events: List[str] = []

@@ -229,8 +229,35 @@ class ComputeProfiler:
             total += body                                  # the layers' forward runs a second time
         return total
 
-    def compute_mfu(self, flops: float, step_s: float, n_gpus: int = 1) -> float:
-        return flops / (step_s * n_gpus * self.peak_tflops * 1e12) if step_s > 0 else 0.0
+    def compute_mfu(self, *args, flops: Optional[float] = None, step_s: Optional[float] = None,
+                    n_gpus: Optional[int] = None, actual_time_s: Optional[float] = None,
+                    device: Optional[str] = None, num_devices: Optional[int] = None) -> float:
+        """``compute_mfu(flops, step_s, n_gpus=1)``: whole-job FLOPs over ``n_gpus`` devices.
+
+        The reference's form ``compute_mfu(actual_time_s, flops, device="A100", num_devices=1)``
+        (src/profiling/compute_profiler.py:183-223) is accepted as well: there ``flops`` is already per GPU, the
+        device count does not enter, and ``device`` names the peak to divide by.  Positionally the two are told apart
+        by magnitude (a step's FLOPs exceed its seconds by many orders) and by a device name in third place."""
+        reference_form = actual_time_s is not None or device is not None or num_devices is not None
+        f, t = flops, (actual_time_s if actual_time_s is not None else step_s)
+        if len(args) >= 3:
+            if isinstance(args[2], str):                    # (seconds, FLOPs, device name[, count])
+                device, reference_form = args[2], True
+            else:                                           # (FLOPs, seconds, n_gpus)
+                n_gpus = args[2]
+        if len(args) >= 2:
+            t, f = sorted(args[:2])
+            reference_form = reference_form or args[0] < args[1]        # seconds first: the reference's order
+        elif len(args) == 1:
+            if t is not None:                               # compute_mfu(flops, step_s=...)
+                f = args[0]
+            else:                                           # compute_mfu(seconds, flops=...)
+                t, reference_form = args[0], True
+        if f is None or t is None or t <= 0:
+            return 0.0
+        if reference_form:
+            return float(f) / (float(t) * self.get_peak_tflops(device) * 1e12)
+        return float(f) / (float(t) * (n_gpus or 1) * self.peak_tflops * 1e12)
 
     # ---- per-layer timing --------------------------------------------------------------------------
     @contextlib.contextmanager

@@ -117,7 +117,12 @@ class _VersionedMixin:
 
 
 class NCCLWeightTransfer(_VersionedMixin):
-    def __init__(self, group=None, src_rank: int = 0):
+    def __init__(self, group=None, src_rank: int = 0, process_group=None):
+        # the reference's order is (src_rank, process_group) (src/transfer/nccl_transfer.py:68-94): an int in first
+        # place is the source rank
+        if isinstance(group, int) and not isinstance(group, bool):
+            group, src_rank = (src_rank if not isinstance(src_rank, int) else None), group
+        group = group if group is not None else process_group
         self.group, self.src = group, src_rank
         self.version = 0
         self.stats = TransferStats()

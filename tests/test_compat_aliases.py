@@ -260,3 +260,32 @@ def test_text_data_run_in_the_reference_style(tmp_path):
         out = tmp_path / f"out_{mode}"
         for name in ("config_snapshot.json", "run_summary.json", "metrics_rank0.jsonl", "loss_curve.csv"):
             assert (out / name).exists(), name
+
+
+def test_constructor_and_method_orders_of_the_reference():
+    """Positional orders that differ between the two code bases are told apart by type or magnitude."""
+    import torch
+    from b200fw.model.lora import LoRALayer
+    from b200fw.obs.memory import MemoryManager
+    from b200fw.obs.profilers import ComputeProfiler
+    from b200fw.sync.nccl_transfer import NCCLWeightTransfer
+    p = ComputeProfiler(device_name="B200", peak_tflops=1000.0)
+    own = [p.compute_mfu(8e15, 1.0, 8), p.compute_mfu(flops=8e15, step_s=1.0, n_gpus=8), p.compute_mfu(8e15, step_s=1.0, n_gpus=8)]
+    ref = [p.compute_mfu(1.0, 1e15), p.compute_mfu(actual_time_s=1.0, flops=1e15, device="B200", num_devices=8),
+           p.compute_mfu(1.0, 1e15, "B200", 8)]
+    assert all(abs(v - 1.0) < 1e-12 for v in own + ref) and p.compute_mfu(1e15, 0.0) == 0.0
+    m = MemoryManager(0, 0.8, 0.9)
+    assert (m.warn, m.critical, m.device) == (0.8, 0.9, torch.device("cuda", 0))
+    m = MemoryManager(0.7, 0.9)
+    assert (m.warn, m.critical, m.device) == (0.7, 0.9, None)
+    m = MemoryManager(warning_threshold=0.6, critical_threshold=0.7)
+    assert (m.warn, m.critical) == (0.6, 0.7) and MemoryManager().check() == "ok"
+    t = NCCLWeightTransfer(1, "group")
+    assert (t.group, t.src) == ("group", 1)
+    t = NCCLWeightTransfer("group", 2)
+    assert (t.group, t.src) == ("group", 2)
+    t = NCCLWeightTransfer(src_rank=3, process_group="g")
+    assert (t.group, t.src) == ("g", 3)
+    assert LoRALayer(8, 8, 4, 8.0, 0.0).lora_A.shape == (4, 8)
+    with pytest.raises(ValueError):
+        LoRALayer(8, 8, 4, 8.0, 0.1)
