@@ -22,6 +22,27 @@ class TimelineEvent:
     def duration_ms(self) -> float:
         return self.end_ms - self.start_ms
 
+    # the reference's field names (src/profiling/schedule_visualizer.py:50-76): seconds, a device label, a dict
+    @property
+    def duration_s(self) -> float:
+        return self.duration_ms * 1e-3
+
+    @property
+    def start_time(self) -> float:
+        return self.start_ms * 1e-3
+
+    @property
+    def end_time(self) -> float:
+        return self.end_ms * 1e-3
+
+    @property
+    def device(self) -> str:
+        return self.lane
+
+    @property
+    def metadata(self) -> Dict:
+        return self.meta or {}
+
 
 ScheduleEvent = TimelineEvent      # the reference's name for an event record
 
@@ -37,16 +58,38 @@ class ScheduleVisualizer:
     def now_ms(self) -> float:
         return (time.perf_counter() - self._t0) * 1e3
 
-    def add_event(self, name, category, lane, start_ms, end_ms, meta=None):
-        self.events.append(TimelineEvent(name, category, lane, start_ms, end_ms, meta))
+    def add_event(self, name, category, lane="GPU:0", start_ms=None, end_ms=None, meta=None, device=None, **metadata):
+        """``add_event(name, category, lane, start_ms, end_ms, meta)``; the reference's form is
+        ``add_event(name, start_time, end_time, device="GPU:0", **metadata)`` in seconds
+        (src/profiling/schedule_visualizer.py:171-188): numbers in second and third place select it."""
+        if isinstance(category, (int, float)) and not isinstance(category, bool):
+            start_s, end_s = float(category), float(lane)
+            dev = device if device is not None else (start_ms if isinstance(start_ms, str) else "GPU:0")
+            self.events.append(TimelineEvent(name, self._STAGE_CATEGORY.get(name, name), dev, start_s * 1e3, end_s * 1e3,
+                                             metadata or meta))
+            return
+        self.events.append(TimelineEvent(name, category, device if device is not None else lane, start_ms, end_ms,
+                                         meta if meta is not None else (metadata or None)))
 
     @contextlib.contextmanager
-    def track(self, name: str, category: str, lane: str = "main", meta=None):
+    def track(self, name: str, category: Optional[str] = None, lane: Optional[str] = None, meta=None, device=None,
+              **metadata):
+        """``with viz.track(name, category, lane)``; or the reference's ``track(name, device="GPU:0", **metadata)``
+        (src/profiling/schedule_visualizer.py:141-169): without a known category in second place the stage name decides
+        the category and the second argument (or ``device=``) is the lane."""
+        if category is not None and category not in self.SYMBOLS and category not in self._STAGE_CATEGORY.values() \
+                and lane is None and device is None:
+            device, category = category, None              # track("training", "GPU:1")
+        if category is None:
+            category = self._STAGE_CATEGORY.get(name, name)
+            lane = device if device is not None else (lane if lane is not None else "GPU:0")
+        else:
+            lane = device if device is not None else (lane if lane is not None else "main")
         s = self.now_ms()
         try:
             yield
         finally:
-            self.add_event(name, category, lane, s, self.now_ms(), meta)
+            self.add_event(name, category, lane, s, self.now_ms(), meta if meta is not None else (metadata or None))
 
     def lanes(self) -> List[str]:
         seen = []
@@ -103,8 +146,8 @@ class ScheduleVisualizer:
                          "bubble_ratio": max(0.0, 1.0 - busy / span), **{f"{k}_ms": v for k, v in by_cat.items()}}
         return out
 
-    @staticmethod
-    def compare(a: "ScheduleVisualizer", b: "ScheduleVisualizer", names=("a", "b")) -> Dict:
+    def compare(a: "ScheduleVisualizer", b: "ScheduleVisualizer", names=("a", "b")) -> Dict:     # noqa: N805
+        """``ScheduleVisualizer.compare(a, b)`` or, as the reference calls it, ``a.compare(b)``."""
         ua, ub = a.utilisation(), b.utilisation()
         span = lambda u: max((v["span_ms"] for v in u.values()), default=0.0)
         mean_u = lambda u: sum(v["utilisation"] for v in u.values()) / max(1, len(u))

@@ -289,3 +289,28 @@ def test_constructor_and_method_orders_of_the_reference():
     assert LoRALayer(8, 8, 4, 8.0, 0.0).lora_A.shape == (4, 8)
     with pytest.raises(ValueError):
         LoRALayer(8, 8, 4, 8.0, 0.1)
+
+
+def test_schedule_visualizer_in_both_call_forms():
+    import time
+    from b200fw.obs.timeline import ScheduleEvent, ScheduleVisualizer
+    v = ScheduleVisualizer()
+    v.add_event("F0", "forward", "stage0", 0.0, 5.0)                       # own form, milliseconds
+    v.add_event("training", 0.010, 0.020, "GPU:1", tokens=5)                # the reference's form, seconds
+    v.add_event("sync", 0.020, 0.021)
+    with v.track("inference", "GPU:1", batch=3):
+        time.sleep(0.001)
+    with v.track("B0", "backward", "stage0"):
+        pass
+    with v.track("training"):
+        pass
+    e = {(x.name, x.lane): x for x in v.events}
+    assert isinstance(v.events[0], ScheduleEvent)
+    t = e[("training", "GPU:1")]
+    assert (t.category, t.device, t.metadata) == ("backward", "GPU:1", {"tokens": 5})
+    assert abs(t.start_time - 0.010) < 1e-12 and abs(t.duration_s - 0.010) < 1e-12 and abs(t.duration_ms - 10.0) < 1e-9
+    assert e[("sync", "GPU:0")].category == "sync" and e[("inference", "GPU:1")].metadata == {"batch": 3}
+    assert e[("B0", "stage0")].category == "backward" and ("training", "GPU:0") in e
+    w = ScheduleVisualizer()
+    w.add_event("F0", "forward", "stage0", 0.0, 10.0)
+    assert v.compare(w)["speedup"] == ScheduleVisualizer.compare(v, w)["speedup"] > 0
