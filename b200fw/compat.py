@@ -24,6 +24,24 @@ import sys
 import types
 from typing import Dict, List, Tuple
 
+def kwarg_aliases(**aliases: str):
+    """Decorator: ``@kwarg_aliases(state_dict="state")`` lets a function whose parameter is ``state`` also be called
+    with the reference's keyword ``state_dict=``.  Giving both spellings of one parameter is an error."""
+    import functools
+
+    def wrap(fn):
+        @functools.wraps(fn)
+        def inner(*args, **kwargs):
+            for theirs, ours in aliases.items():
+                if theirs in kwargs:
+                    if ours in kwargs:
+                        raise TypeError(f"{fn.__name__}() got both {theirs!r} and {ours!r}")
+                    kwargs[ours] = kwargs.pop(theirs)
+            return fn(*args, **kwargs)
+        return inner
+    return wrap
+
+
 # reference module -> modules of this package that provide its names
 ALIASES: Dict[str, Tuple[str, ...]] = {
     "src.distributed.parallel_context": ("b200fw.dist.context",),

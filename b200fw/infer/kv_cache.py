@@ -52,7 +52,8 @@ class Block:
 class BlockPool:
     def __init__(self, num_blocks: int, block_size: int, num_layers: int, num_kv_heads: int, head_dim: int,
                  dtype: torch.dtype = torch.bfloat16, device="cpu", kv_cache_dtype: str = "fp16",
-                 allocate: bool = True):
+                 allocate: bool = True, cache_dtype: Optional[str] = None):
+        kv_cache_dtype = cache_dtype if cache_dtype is not None else kv_cache_dtype     # `cache_dtype`: the reference's name
         self.num_blocks, self.block_size = num_blocks, block_size
         self.num_layers, self.num_kv_heads, self.head_dim = num_layers, num_kv_heads, head_dim
         self.fp8 = kv_cache_dtype == "fp8"

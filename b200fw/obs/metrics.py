@@ -4,6 +4,7 @@ from __future__ import annotations
 
 import contextlib
 import time
+from ..compat import kwarg_aliases
 from dataclasses import dataclass
 from collections import defaultdict
 from typing import Dict, List, Optional
@@ -30,6 +31,7 @@ class MetricsCollector:
         self.timer_records: List[TimerRecord] = []
         self._start_time = time.time()
 
+    @kwarg_aliases(key="name")
     def record(self, name: str, value: float, step: Optional[int] = None):
         self.series[name].append(float(value))
         self.steps[name].append(len(self.series[name]) - 1 if step is None else int(step))

@@ -91,7 +91,15 @@ class CommProfiler:
         self.compute_ms = 0.0            # ... compute outside the collectives (record_compute_time)
 
     @contextlib.contextmanager
-    def profile_op(self, op: str, nbytes: int, world_size: int):
+    def profile_op(self, op: Optional[str] = None, nbytes=0, world_size: int = 1, op_type: Optional[str] = None,
+                   tensor: Optional[torch.Tensor] = None):
+        """``profile_op(op, nbytes, world_size)``; the reference passes the tensor itself
+        (``profile_op(op_type, tensor, world_size)``: src/profiling/comm_profiler.py:96-150), whose size is then used."""
+        op = op if op is not None else op_type
+        if torch.is_tensor(nbytes):
+            tensor = nbytes
+        if tensor is not None:
+            nbytes = tensor.numel() * tensor.element_size()
         if not self.enabled:
             yield
             return

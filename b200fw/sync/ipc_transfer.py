@@ -21,6 +21,7 @@ import torch
 
 from ..obs.logging import get_logger
 from .nccl_transfer import TransferStats
+from ..compat import kwarg_aliases
 
 logger = get_logger("sync.ipc")
 
@@ -185,6 +186,7 @@ class IPCWeightTransfer:
         self.stats = TransferStats()
         self._keepalive: List[torch.Tensor] = []     # exported tensors must outlive the receiver's import
 
+    @kwarg_aliases(state_dict="state")
     def build_ipc_handles(self, state: Dict[str, torch.Tensor]) -> List[Dict]:
         handles = []
         self._keepalive = []
@@ -244,6 +246,7 @@ class IPCWeightTransfer:
             m.update(state[k].detach().to(torch.float32).cpu().contiguous().numpy().tobytes())
         return m.hexdigest()
 
+    @kwarg_aliases(state_dict="state", sleep_level="sleep_first")
     async def push_weights(self, state: Dict[str, torch.Tensor], sleep_first: bool = True) -> TransferStats:
         t0 = time.perf_counter()
         nbytes = sum(v.numel() * v.element_size() for v in state.values())

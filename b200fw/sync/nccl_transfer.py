@@ -16,6 +16,7 @@ from typing import Dict, List, Optional
 
 import torch
 import torch.distributed as dist
+from ..compat import kwarg_aliases
 
 
 @dataclass
@@ -133,6 +134,7 @@ class NCCLWeightTransfer(_VersionedMixin):
         dist.broadcast_object_list(box, src=self.src, group=self.group)
         return box[0]
 
+    @kwarg_aliases(state_dict="state")
     def broadcast_weights(self, state: Dict[str, torch.Tensor]) -> int:
         """Trainer side.  Returns the new version."""
         t0 = time.perf_counter()

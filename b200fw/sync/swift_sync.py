@@ -16,6 +16,7 @@ from typing import Dict, List, Optional
 import torch
 
 from .double_buffer import DoubleBufferedLoRA, FlatState
+from ..compat import kwarg_aliases
 
 
 @dataclass
@@ -141,6 +142,7 @@ class DeltaComputer:
         return step > 0 and self.fallback_full_every > 0 and step % self.fallback_full_every == 0
 
     @torch.no_grad()
+    @kwarg_aliases(current_lora="current", prev_lora="prev")
     def compute_delta(self, current: Dict[str, torch.Tensor],
                       prev: Optional[Dict[str, torch.Tensor]] = None) -> Dict[str, torch.Tensor]:
         """current - previous snapshot (first call: the full state), then remember ``current``.  With an explicit

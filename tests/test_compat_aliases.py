@@ -314,3 +314,31 @@ def test_schedule_visualizer_in_both_call_forms():
     w = ScheduleVisualizer()
     w.add_event("F0", "forward", "stage0", 0.0, 10.0)
     assert v.compare(w)["speedup"] == ScheduleVisualizer.compare(v, w)["speedup"] > 0
+
+
+def test_keyword_names_of_the_reference_on_transfer_metrics_and_cache_classes():
+    import asyncio
+    import torch
+    from b200fw.infer import BlockPool
+    from b200fw.obs.metrics import MetricsCollector
+    from b200fw.obs.profilers import CommProfiler
+    from b200fw.sync import DeltaComputer, IPCWeightTransfer, VLLMClient
+    d = DeltaComputer(10)
+    d.compute_delta(current_lora={"a": torch.ones(2)})
+    assert torch.equal(d.compute_delta(current_lora={"a": torch.full((2,), 3.0)})["a"], torch.full((2,), 2.0))
+    assert torch.equal(d.compute_delta(current_lora={"a": torch.ones(2)}, prev_lora={"a": torch.ones(2)})["a"], torch.zeros(2))
+    with pytest.raises(TypeError):
+        d.compute_delta(current={"a": torch.ones(2)}, current_lora={"a": torch.ones(2)})
+    m = MetricsCollector()
+    m.record(key="loss", value=2.0)
+    assert m.series["loss"] == [2.0]
+    ipc = IPCWeightTransfer(VLLMClient("http://127.0.0.1:9", timeout=1.0, max_retries=0, backoff_s=0.0))
+    assert isinstance(ipc.build_ipc_handles(state_dict={"w": torch.ones(2)}), list)
+    ipc.release_refs()
+    pool = BlockPool(4, 16, 1, 1, 8, torch.float32, "cpu", cache_dtype="fp8")
+    assert pool.fp8
+    prof = CommProfiler()
+    with prof.profile_op("all_reduce", torch.ones(1024), 2):
+        pass
+    with prof.profile_op(op_type="all_gather", tensor=torch.ones(8), world_size=2):
+        pass
