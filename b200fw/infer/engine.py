@@ -108,6 +108,8 @@ class InferenceEngine:
     def _build_model(self) -> ParallelTransformerModel:
         cfg = self.config
         dev = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+        if cfg.dtype == "float16":
+            logger.warning("dtype float16 runs as bfloat16: the kernels are bf16-only")
         dtype = {"bfloat16": torch.bfloat16, "float32": torch.float32, "float16": torch.bfloat16}[cfg.dtype]
         if dev.type == "cpu":
             dtype = torch.float32

@@ -150,6 +150,8 @@ class TrainEngine:
             if cfg.num_micro_batches < cfg.pp_size:
                 raise ValueError("num_micro_batches must be >= pp_size")
         amp = cfg.amp_dtype if cfg.use_amp else "fp32"
+        if amp == "fp16":
+            logger.warning("precision fp16 runs as bf16: the kernels are bf16-only (and bf16 needs no loss scaling)")
         self.dtype = {"bf16": torch.bfloat16, "fp16": torch.bfloat16, "fp32": torch.float32}[amp]
         if self.device.type == "cpu":
             self.dtype = torch.float32 if amp == "fp32" or not cfg.use_amp else self.dtype
