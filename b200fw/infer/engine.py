@@ -286,7 +286,12 @@ class InferenceEngine:
                 continue
             try:
                 if r.request_id not in self.kv.tables and not self._admit(r):
-                    raise RuntimeError("KV cache exhausted")
+                    if self.kv.tables:
+                        # other sequences hold the blocks: this one waits for them instead of failing
+                        self.scheduler.requeue(r)
+                        self.stats["admission_deferrals"] = self.stats.get("admission_deferrals", 0) + 1
+                        continue
+                    raise RuntimeError("KV cache exhausted")     # it does not fit even into an empty pool
                 n = min(n, r.num_prompt_tokens - r.num_computed_tokens)   # a cached prefix shortens the chunk
                 if n <= 0:
                     n = 1
@@ -355,13 +360,14 @@ class InferenceEngine:
         reqs = [r for r in reqs if not (r.output_tokens and r.output_tokens[-1] != self.PLACEHOLDER and r.is_finished)]
         live = []
         for r in reqs:
+            if r.request_id not in self.kv.tables:
+                continue                    # preempted a moment ago to make room for an older request
             try:
-                if not self.kv.append_token(r.request_id):
-                    if self.prefix_cache is not None and self.prefix_cache.evict_lru(4) and \
-                            self.kv.append_token(r.request_id):
-                        pass
-                    else:
-                        raise RuntimeError("KV cache exhausted during decode")
+                room = self._append_token_making_room(r, live, produced)
+                if room is None:
+                    continue                # r itself was the newest holder of blocks: preempted, it retries later
+                if not room:
+                    raise RuntimeError("KV cache exhausted during decode")
                 live.append(r)
             except Exception as e:  # noqa: BLE001
                 self._resolve_inflight(produced)
@@ -419,6 +425,32 @@ class InferenceEngine:
         self._resolve_inflight(produced)
         self._inflight = {"reqs": live, "rows": {r.request_id: i for i, r in enumerate(live)}, "slots": slots,
                           "ids_dev": ids_dev, "host_ids": host_ids, "host_lps": host_lps, "event": ev}
+
+    def _append_token_making_room(self, r: Request, live: List[Request], produced: Dict[str, List[int]]):
+        """Reserve the KV slot of ``r``'s next token.  When the pool is dry: first the prefix cache gives up blocks, then
+        the newest request that holds blocks is preempted (its blocks are freed, it goes back to the head of the
+        waiting queue and is recomputed later) - the policy the scheduler applies to its sequence limit, extended to
+        memory (the reference preempts on the count limits only: src/inference/scheduler.py:316-339, and fails the
+        request here).  Returns True (slot reserved), None (``r`` itself was the newest and has been preempted) or
+        False (``r`` alone exhausts the pool: it cannot be served)."""
+        while True:
+            if self.kv.append_token(r.request_id):
+                return True
+            if self.prefix_cache is not None and self.prefix_cache.evict_lru(4):
+                continue
+            holders = [q for q in list(self.scheduler.running_queue) + list(self.scheduler.waiting_queue)
+                       if q.request_id in self.kv.tables]
+            if not holders or holders == [r]:
+                return False
+            victim = max(holders, key=lambda q: q.arrival_time)
+            self._resolve_inflight(produced)        # placeholders of the launch in flight are settled before a reset
+            self.scheduler.preempt(victim)
+            self._release(victim, cache_prefix=False)
+            self.stats["memory_preemptions"] = self.stats.get("memory_preemptions", 0) + 1
+            if victim in live:
+                live.remove(victim)
+            if victim is r:
+                return None
 
     def _stage(self, name: str, t: torch.Tensor) -> torch.Tensor:
         """Host tensor -> device through a small ring of pinned staging buffers (no page-locking per call; a ring

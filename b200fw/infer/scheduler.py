@@ -121,6 +121,32 @@ class ContinuousBatchingScheduler:
             return min(self.chunk_size * 2, 2048)
         return self.chunk_size
 
+    def requeue(self, request: Request):
+        """Put a request whose scheduled work could not start (no KV blocks right now) back at the head of the waiting
+        queue with its progress untouched; it is offered again at the next step."""
+        if request in self.running_queue:
+            self.running_queue.remove(request)
+        if request in self.waiting_queue:
+            self.waiting_queue.remove(request)
+        request.state = RequestState.WAITING
+        self.waiting_queue.insert(0, request)
+
+    def preempt(self, victim: Request) -> Request:
+        """Evict ``victim`` (running, or waiting with part of its prompt computed): its progress is reset, it returns
+        to the head of the waiting queue and is recomputed later.  The caller frees its KV blocks."""
+        if victim in self.running_queue:
+            self.running_queue.remove(victim)
+        if victim in self.waiting_queue:
+            self.waiting_queue.remove(victim)
+        victim.num_computed_tokens = 0
+        victim.output_tokens.clear()
+        victim.output_logprobs.clear()
+        victim.preemptions += 1
+        victim.state = RequestState.WAITING
+        self.waiting_queue.insert(0, victim)
+        self.total_preempted += 1
+        return victim
+
     def preempt_one(self) -> Optional[Request]:
         if not self.running_queue:
             return None

@@ -159,6 +159,28 @@ def test_kv_exhaustion_is_isolated_per_request(model):
     assert e.get_stats()["kv_cache"]["used_blocks"] == 0
 
 
+def test_kv_pressure_preempts_the_newest_request_instead_of_failing_it(model):
+    """Two requests that each fit the pool but not together once they grow: the newer one is preempted (blocks freed,
+    recomputed later), nothing fails, both give the oracle's tokens; a third that can only be admitted after the
+    others finished waits instead of failing."""
+    prompts = [[7] * 40, [9] * 40, [11] * 60]
+    ref = InferenceEngine(InferenceConfig.from_model_config(MC, inference_mode="eager", temperature=0.0, eos_token_id=None),
+                          model).initialize()
+    want = [ref.generate([p], max_tokens=30)[0] for p in prompts]
+    e = _engine(model, num_blocks=7, chunk_size=64, max_prefill_tokens=128, max_num_batched_tokens=256)
+    for i, p in enumerate(prompts):
+        e.add_request(f"r{i}", p, 30)
+    steps = 0
+    while e.has_pending():
+        e.step()
+        steps += 1
+        assert steps < 2000
+    st = e.get_stats()
+    assert [e.finished[f"r{i}"].output_tokens for i in range(3)] == want
+    assert st["request_errors"] == 0 and st.get("memory_preemptions", 0) >= 1 and st.get("admission_deferrals", 0) >= 1
+    assert st["kv_cache"]["used_blocks"] == 0 and e.finished["r1"].preemptions >= 1 and e.finished["r0"].preemptions == 0
+
+
 def test_weight_update_in_place_changes_outputs(model, oracle):
     import copy
     m2 = ParallelTransformerModel(MC)

@@ -1,0 +1,159 @@
+"""Property tests of the inference runtime's host logic (hypothesis): block accounting of the paged KV manager under
+random operation sequences, and the paged engine against the eager oracle for random workloads under memory pressure
+(preemption, chunked prefill, prefix sharing, one-step-late decode)."""
+import pytest
+import torch
+
+hypothesis = pytest.importorskip("hypothesis")
+from hypothesis import HealthCheck, given, settings  # noqa: E402
+from hypothesis import strategies as st  # noqa: E402
+
+from b200fw.infer import BlockPool, InferenceConfig, InferenceEngine, KVCacheManager  # noqa: E402
+from b200fw.model import ModelConfig, ParallelTransformerModel  # noqa: E402
+
+BS = 4      # tokens per block in the accounting test
+
+
+def _check_pool(pool: BlockPool, mgr: KVCacheManager, extra_refs):
+    refs = {}
+    for table in mgr.tables.values():
+        for b in table.blocks:
+            refs[b.block_id] = refs.get(b.block_id, 0) + 1
+        assert table.capacity >= table.num_tokens
+    for bid, n in extra_refs.items():
+        refs[bid] = refs.get(bid, 0) + n
+    free = list(pool.free_list)
+    assert len(free) == len(set(free)), "a block sits in the free list twice"
+    for b in pool.blocks:
+        assert b.ref_count == refs.get(b.block_id, 0), (b.block_id, b.ref_count, refs.get(b.block_id, 0))
+        assert (b.block_id in free) == (b.ref_count == 0)
+    assert pool.num_free_blocks + sum(1 for b in pool.blocks if b.ref_count > 0) == pool.num_blocks
+    assert pool.double_free_count == 0
+
+
+OPS = st.lists(st.tuples(st.sampled_from(["new", "new_shared", "append", "grow", "trim", "free", "hold", "drop"]),
+                         st.integers(0, 7), st.integers(0, 40)), min_size=1, max_size=60)
+
+
+@settings(max_examples=150, deadline=None, suppress_health_check=[HealthCheck.too_slow])
+@given(OPS, st.integers(3, 24))
+def test_block_accounting_survives_any_operation_sequence(ops, num_blocks):
+    pool = BlockPool(num_blocks, BS, 1, 1, 4, torch.float32, "cpu", allocate=False)
+    mgr = KVCacheManager(pool, BS)
+    held = {}           # references a prefix cache would hold: block id -> count
+    next_id = 0
+    for op, which, n in ops:
+        ids = sorted(mgr.tables)
+        sid = ids[which % len(ids)] if ids else None
+        free_before = pool.num_free_blocks
+        if op == "new":
+            t = mgr.allocate_for_sequence(next_id, n)
+            if t is None:
+                assert pool.num_free_blocks == free_before, "a failed allocation must roll back completely"
+            else:
+                assert t.num_blocks == mgr.blocks_needed(n) and t.num_tokens == n
+            next_id += 1
+        elif op == "new_shared" and sid is not None:
+            src = mgr.tables[sid]
+            full = [b.block_id for b in src.blocks[:src.num_tokens // BS]]
+            shared = full[:which % (len(full) + 1)]
+            total = len(shared) * BS + n
+            t = mgr.allocate_for_sequence(next_id, total, shared_block_ids=shared)
+            if t is None:
+                assert pool.num_free_blocks == free_before
+            else:
+                assert t.get_physical_block_ids()[:len(shared)] == shared
+            next_id += 1
+        elif op == "append" and sid is not None:
+            before = mgr.get_seq_token_count(sid)
+            ok = mgr.append_token(sid)
+            assert mgr.get_seq_token_count(sid) == before + (1 if ok else 0)
+            if not ok:
+                assert pool.num_free_blocks == free_before
+        elif op == "grow" and sid is not None:
+            ok = mgr.ensure_capacity(sid, mgr.get_seq_token_count(sid) + n)
+            if not ok:
+                assert pool.num_free_blocks == free_before
+        elif op == "trim" and sid is not None:
+            keep = min(mgr.get_seq_token_count(sid), n)
+            mgr.trim(sid, keep)
+            assert mgr.get_seq_token_count(sid) == keep
+            assert mgr.tables[sid].num_blocks <= max(1, mgr.blocks_needed(keep)) or mgr.tables[sid].num_blocks == 0
+        elif op == "free" and sid is not None:
+            mgr.free_sequence(sid)
+            assert sid not in mgr.tables
+        elif op == "hold" and sid is not None and mgr.tables[sid].blocks:
+            b = mgr.tables[sid].blocks[which % mgr.tables[sid].num_blocks]
+            pool.share(b.block_id)
+            held[b.block_id] = held.get(b.block_id, 0) + 1
+        elif op == "drop" and held:
+            bid = sorted(held)[which % len(held)]
+            pool.free(pool.get_block(bid))
+            held[bid] -= 1
+            if held[bid] == 0:
+                del held[bid]
+        _check_pool(pool, mgr, held)
+    mgr.reset()
+    for bid, k in list(held.items()):
+        for _ in range(k):
+            pool.free(pool.get_block(bid))
+    assert pool.num_free_blocks == pool.num_blocks and pool.double_free_count == 0
+
+
+MC = ModelConfig(vocab_size=96, hidden_size=32, num_layers=2, num_heads=4, num_kv_heads=2, head_dim=8,
+                 intermediate_size=48, max_position_embeddings=256, tie_word_embeddings=True)
+
+
+@pytest.fixture(scope="module")
+def model():
+    torch.manual_seed(0)
+    m = ParallelTransformerModel(MC)
+    m.init_weights(0, std=0.3)
+    return m
+
+
+def _engine(model, **kw):
+    base = dict(inference_mode="kv_cache", temperature=0.0, eos_token_id=None, num_blocks=256, block_size=16)
+    base.update(kw)
+    return InferenceEngine(InferenceConfig.from_model_config(MC, **base), model).initialize()
+
+
+WORKLOAD = st.lists(st.tuples(st.integers(1, 70), st.integers(1, 24), st.booleans()), min_size=1, max_size=10)
+
+
+@settings(max_examples=30, deadline=None, suppress_health_check=[HealthCheck.too_slow, HealthCheck.function_scoped_fixture])
+@given(WORKLOAD, st.integers(0, 3), st.sampled_from([8, 16, 48]), st.booleans(), st.booleans(), st.sampled_from([2, 3, 256]))
+def test_paged_engine_equals_eager_oracle_under_memory_pressure(model, workload, slack, chunk, radix, late, max_seqs):
+    """Random prompts (some sharing a 32-token prefix), a block pool barely larger than the largest single request
+    (so running sequences get preempted and recomputed), small prefill chunks, radix cache on or off, read-back one
+    step late or not: greedy outputs must equal the eager full-recompute oracle, and every block must come back."""
+    g = torch.Generator().manual_seed(len(workload) * 1000 + slack)
+    prefix = torch.randint(3, 96, (32,), generator=g).tolist()
+    prompts, outs = [], []
+    for plen, out_len, shared in workload:
+        body = torch.randint(3, 96, (plen,), generator=g).tolist()
+        prompts.append((prefix + body) if shared else body)
+        outs.append(out_len)
+    longest = max(len(p) + o for p, o in zip(prompts, outs))
+    blocks = (longest + 15) // 16 + 2 + slack              # the biggest request fits, several at once usually do not
+    oracle = _engine(model, inference_mode="eager")
+    want = [oracle.generate([p], max_tokens=o)[0] for p, o in zip(prompts, outs)]
+    eng = _engine(model, num_blocks=blocks, chunk_size=chunk, max_prefill_tokens=max(chunk, 16),
+                  max_num_batched_tokens=max(chunk, 16) + 8, use_radix_cache=radix, enable_prefix_caching=radix,
+                  max_cached_blocks=blocks, async_decode="force" if late else False, adaptive_chunking=False,
+                  max_num_sequences=max_seqs)
+    for i, (p, o) in enumerate(zip(prompts, outs)):
+        eng.add_request(f"r{i}", p, o)
+    steps = 0
+    while eng.has_pending():
+        eng.step()
+        steps += 1
+        assert steps < 5000, "the engine stopped making progress"
+    got = [eng.finished[f"r{i}"].output_tokens for i in range(len(prompts))]
+    for i, (a, b) in enumerate(zip(got, want)):
+        assert list(a) == list(b), (i, prompts[i][:6], a, b)
+    # every block is back in the pool except those the prefix cache still references; evicting them frees the rest
+    if eng.prefix_cache is not None:
+        eng.prefix_cache.evict_lru(blocks)
+    assert eng.pool.num_free_blocks == eng.pool.num_blocks, (eng.pool.num_free_blocks, eng.pool.num_blocks)
+    assert eng.pool.double_free_count == 0 and not eng.kv.tables
