@@ -287,7 +287,14 @@ class SwiftSyncTransfer:
         """Policy wrapper: periodic full sync, deltas otherwise."""
         if self.delta_computer.prev is None or self.delta_computer.should_full_sync(step):
             return self.sync_full(lora_state)
-        return self.sync_delta(self.delta_computer.compute_delta(lora_state))
+        delta = self.delta_computer.compute_delta(lora_state)       # also moves the snapshot to ``lora_state``
+        try:
+            return self.sync_delta(delta)
+        except Exception:
+            # the worker never saw this delta but the snapshot already contains it: the next delta would silently skip
+            # it.  Forget the snapshot instead, so that the next sync is a full one.
+            self.delta_computer.reset()
+            raise
 
     # ---- the reference's names (src/transfer/swift_sync.py:340-596) -------------------------------------------
     def initialize(self, initial_lora_state: Dict[str, torch.Tensor]) -> None:
