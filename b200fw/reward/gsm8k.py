@@ -55,12 +55,23 @@ def check_format(text: str) -> bool:
     return has_steps or any(p.search(text) for p in _PATTERNS)
 
 
+def _same_number(pred: Optional[float], gt: Optional[float], tol: float) -> bool:
+    """Equal answers: whole numbers must match exactly (9999 is not 10000, whatever the magnitude); otherwise within
+    ``tol`` absolutely (1/3 against 0.3333) plus float noise.  The reference compares the normalised strings
+    (src/reward/gsm8k_reward.py:102-125), which is exact for integers as well."""
+    if pred is None or gt is None or pred != pred or gt != gt:
+        return False
+    if abs(pred) < 2 ** 53 and abs(gt) < 2 ** 53 and pred == int(pred) and gt == int(gt):
+        return int(pred) == int(gt)
+    return abs(pred - gt) <= max(tol, 1e-9 * abs(gt))
+
+
 def compute_reward(response: str, ground_truth, tol: float = 1e-4) -> float:
     """+1.0 correct answer; otherwise -0.5 when the response is well formed (:func:`check_format`), -1.0 when it is
     not (src/reward/gsm8k_reward.py:102-125)."""
     pred = extract_answer(response or "")
     gt = ground_truth if isinstance(ground_truth, (int, float)) else extract_answer(str(ground_truth))
-    if pred is not None and gt is not None and abs(pred - gt) <= tol * max(1.0, abs(gt)):
+    if _same_number(pred, gt, tol):
         return 1.0
     return -0.5 if check_format(response or "") else -1.0
 
@@ -90,7 +101,7 @@ class GSM8KRewardFunction:
         self.num_formatted += int(formatted)
         pred = extract_answer(response or "")
         gt = ground_truth if isinstance(ground_truth, (int, float)) else extract_answer(str(ground_truth))
-        if pred is not None and gt is not None and abs(pred - gt) <= self.tol * max(1.0, abs(gt)):
+        if _same_number(pred, gt, self.tol):
             self.num_correct += 1
             return self.correct
         return self.wrong if formatted else self.no_answer
