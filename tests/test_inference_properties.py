@@ -122,10 +122,11 @@ WORKLOAD = st.lists(st.tuples(st.integers(1, 70), st.integers(1, 24), st.boolean
 
 
 @settings(max_examples=30, deadline=None, suppress_health_check=[HealthCheck.too_slow, HealthCheck.function_scoped_fixture])
-@given(WORKLOAD, st.integers(0, 3), st.sampled_from([8, 16, 48]), st.booleans(), st.booleans(), st.sampled_from([2, 3, 256]))
-def test_paged_engine_equals_eager_oracle_under_memory_pressure(model, workload, slack, chunk, radix, late, max_seqs):
+@given(WORKLOAD, st.integers(0, 3), st.sampled_from([8, 16, 48]), st.sampled_from(["none", "hash", "radix"]), st.booleans(),
+       st.sampled_from([2, 3, 256]))
+def test_paged_engine_equals_eager_oracle_under_memory_pressure(model, workload, slack, chunk, cache, late, max_seqs):
     """Random prompts (some sharing a 32-token prefix), a block pool barely larger than the largest single request
-    (so running sequences get preempted and recomputed), small prefill chunks, radix cache on or off, read-back one
+    (so running sequences get preempted and recomputed), small prefill chunks, no / hash / radix prefix cache, read-back one
     step late or not: greedy outputs must equal the eager full-recompute oracle, and every block must come back."""
     g = torch.Generator().manual_seed(len(workload) * 1000 + slack)
     prefix = torch.randint(3, 96, (32,), generator=g).tolist()
@@ -139,7 +140,8 @@ def test_paged_engine_equals_eager_oracle_under_memory_pressure(model, workload,
     oracle = _engine(model, inference_mode="eager")
     want = [oracle.generate([p], max_tokens=o)[0] for p, o in zip(prompts, outs)]
     eng = _engine(model, num_blocks=blocks, chunk_size=chunk, max_prefill_tokens=max(chunk, 16),
-                  max_num_batched_tokens=max(chunk, 16) + 8, use_radix_cache=radix, enable_prefix_caching=radix,
+                  max_num_batched_tokens=max(chunk, 16) + 8, use_radix_cache=cache == "radix",
+                  enable_prefix_caching=cache != "none",
                   max_cached_blocks=blocks, async_decode="force" if late else False, adaptive_chunking=False,
                   max_num_sequences=max_seqs)
     for i, (p, o) in enumerate(zip(prompts, outs)):
