@@ -340,7 +340,9 @@ class InferenceEngine:
         prefill (whole prompt in one go: the draft is tiny)."""
         dm = self.draft_runner
         if dm.mgr.allocate_for_sequence(r.request_id, r.num_prompt_tokens) is None:
-            raise RuntimeError("draft KV cache exhausted")
+            # no room in the draft cache: this sequence simply decodes without speculation
+            self.stats["spec_fallbacks"] = self.stats.get("spec_fallbacks", 0) + 1
+            return
         ctx = dm.prepare_prefill([r.request_id], [0], [r.num_prompt_tokens])
         dm.forward(torch.tensor(r.prompt_tokens, dtype=torch.long, device=self.device), ctx)
 
@@ -538,6 +540,13 @@ class InferenceEngine:
 
     def _execute_speculative(self, reqs: List[Request], produced: Dict[str, List[int]]):
         ids = [r.request_id for r in reqs]
+        if not self.spec.can_step(ids):
+            # memory is tight: give up the draft state of these sequences (they continue without speculation) and let
+            # the ordinary decode step deal with the pressure (prefix-cache eviction, preemption of the newest)
+            for rid in ids:
+                self.draft_runner.mgr.free_sequence(rid)
+            self.stats["spec_fallbacks"] = self.stats.get("spec_fallbacks", 0) + len(ids)
+            return self._execute_decode(reqs, produced)
         outs = self.spec.step(ids, [r.output_tokens[-1] for r in reqs], reqs[0].temperature, self._gen)
         self.stats["spec_rounds"] += 1
         for r, toks in zip(reqs, outs):

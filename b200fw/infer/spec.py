@@ -180,6 +180,21 @@ class SpeculativeDecoder:
                 "num_speculative_tokens": self.K, "history_window_size": len(self.tracker.events),
                 "rounds": self.steps}
 
+    def can_step(self, seq_ids: List) -> bool:
+        """True when both caches have room for a whole round of every sequence (K draft tokens + the catch-up slot in
+        the draft cache, K + 1 verified positions in the target cache).  A round that ran out of blocks half-way would
+        leave the two caches at different lengths; the engine asks first and decodes normally when the answer is no."""
+        for runner, extra in ((self.draft, self.K + 1), (self.target, self.K + 1)):
+            mgr, need = runner.mgr, 0
+            for s in seq_ids:
+                table = mgr.tables.get(s)
+                if table is None:
+                    return False
+                need += max(0, mgr.blocks_needed(table.num_tokens + extra) - table.num_blocks)
+            if need > mgr.pool.num_free_blocks:
+                return False
+        return True
+
     def _draft_propose(self, seq_ids: List, last_tokens: List[int], temperature: float,
                        generator=None) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
         """K draft decode steps for all sequences.  Returns tokens ``[B, K]`` and, when sampling, the

@@ -181,6 +181,23 @@ def test_kv_pressure_preempts_the_newest_request_instead_of_failing_it(model):
     assert st["kv_cache"]["used_blocks"] == 0 and e.finished["r1"].preemptions >= 1 and e.finished["r0"].preemptions == 0
 
 
+def test_speculative_decoding_gives_way_under_kv_pressure(model):
+    """A pool too small for a speculative round of every sequence: the engine drops the draft state of those sequences and
+    decodes them normally (preempting if it must) instead of raising out of ``step``; the tokens stay the oracle's."""
+    prompts = [[5, 6, 7, 8, 9] * 3, [11] * 20, list(range(3, 40))]
+    ref = InferenceEngine(InferenceConfig.from_model_config(MC, inference_mode="eager", temperature=0.0, eos_token_id=None),
+                          model).initialize()
+    want = ref.generate(prompts, max_tokens=12)
+    for blocks in (64, 6):
+        e = _engine(model, num_blocks=blocks, speculative_enabled=True, speculative_num_tokens=3, speculative_draft_layers=1,
+                    chunk_size=64, max_prefill_tokens=128, max_num_batched_tokens=256)
+        assert e.generate(prompts, max_tokens=12) == want
+        st = e.get_stats()
+        assert st["request_errors"] == 0 and st["spec_rounds"] >= 1
+        assert (st.get("spec_fallbacks", 0) >= 1) == (blocks == 6)
+        assert st["kv_cache"]["used_blocks"] == 0 and e.draft_runner.mgr.pool.num_used_blocks == 0
+
+
 def test_weight_update_in_place_changes_outputs(model, oracle):
     import copy
     m2 = ParallelTransformerModel(MC)

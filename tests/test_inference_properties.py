@@ -121,13 +121,13 @@ def _engine(model, **kw):
 WORKLOAD = st.lists(st.tuples(st.integers(1, 70), st.integers(1, 24), st.booleans()), min_size=1, max_size=10)
 
 
-@settings(max_examples=30, deadline=None, suppress_health_check=[HealthCheck.too_slow, HealthCheck.function_scoped_fixture])
+@settings(max_examples=40, deadline=None, suppress_health_check=[HealthCheck.too_slow, HealthCheck.function_scoped_fixture])
 @given(WORKLOAD, st.integers(0, 3), st.sampled_from([8, 16, 48]), st.sampled_from(["none", "hash", "radix"]), st.booleans(),
-       st.sampled_from([2, 3, 256]))
-def test_paged_engine_equals_eager_oracle_under_memory_pressure(model, workload, slack, chunk, cache, late, max_seqs):
+       st.sampled_from([2, 3, 256]), st.sampled_from([0, 0, 2, 4]))
+def test_paged_engine_equals_eager_oracle_under_memory_pressure(model, workload, slack, chunk, cache, late, max_seqs, spec_k):
     """Random prompts (some sharing a 32-token prefix), a block pool barely larger than the largest single request
     (so running sequences get preempted and recomputed), small prefill chunks, no / hash / radix prefix cache, read-back one
-    step late or not: greedy outputs must equal the eager full-recompute oracle, and every block must come back."""
+    step late or not, greedy speculative decoding with a one-layer draft or none: outputs must equal the eager full-recompute oracle, and every block must come back."""
     g = torch.Generator().manual_seed(len(workload) * 1000 + slack)
     prefix = torch.randint(3, 96, (32,), generator=g).tolist()
     prompts, outs = [], []
@@ -143,7 +143,8 @@ def test_paged_engine_equals_eager_oracle_under_memory_pressure(model, workload,
                   max_num_batched_tokens=max(chunk, 16) + 8, use_radix_cache=cache == "radix",
                   enable_prefix_caching=cache != "none",
                   max_cached_blocks=blocks, async_decode="force" if late else False, adaptive_chunking=False,
-                  max_num_sequences=max_seqs)
+                  max_num_sequences=max_seqs, speculative_enabled=spec_k > 0, speculative_num_tokens=max(1, spec_k),
+                  speculative_draft_layers=1)
     for i, (p, o) in enumerate(zip(prompts, outs)):
         eng.add_request(f"r{i}", p, o)
     steps = 0
