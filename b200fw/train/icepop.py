@@ -25,10 +25,15 @@ class IcePopFilter:
         self.config = config
         self.total_seen = 0
         self.total_masked = 0
+        self.last_non_finite = 0
 
     def filter_divergent_responses(self, train_log_probs: torch.Tensor, infer_log_probs: torch.Tensor,
                                    advantages: torch.Tensor) -> Tuple[torch.Tensor, Dict[str, float]]:
         gap = (train_log_probs.float() - infer_log_probs.float().to(train_log_probs.device)).abs()
+        # a log-prob that is not a number on either side is the strongest possible disagreement, not "no disagreement"
+        # (a comparison with NaN is false, which would let such a response through with its advantage intact)
+        finite = torch.isfinite(gap)
+        gap = torch.where(finite, gap, torch.full_like(gap, float("inf")))
         n = advantages.shape[0]
         cap = int(n * self.config.max_mask_ratio)
         over = gap > self.config.divergence_threshold
@@ -41,10 +46,11 @@ class IcePopFilter:
         out = torch.where(drop, torch.zeros_like(advantages), advantages)
         self.total_seen += n
         self.total_masked += k
+        self.last_non_finite = int((~finite).sum().item())      # kept off the diagnostics dict: its key set is the reference's
         diag = {
             "icepop_masked_ratio": k / max(n, 1),
-            "icepop_mean_divergence": gap.mean().item() if n else 0.0,
-            "icepop_max_divergence": gap.max().item() if n else 0.0,
+            "icepop_mean_divergence": gap[finite].mean().item() if bool(finite.any()) else 0.0,
+            "icepop_max_divergence": gap[finite].max().item() if bool(finite.any()) else 0.0,
             "icepop_num_masked": k,
             "icepop_threshold": self.config.divergence_threshold,
         }

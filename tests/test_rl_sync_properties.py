@@ -107,3 +107,35 @@ def test_receiver_tracks_the_trainer_through_any_sync_sequence(seeds, full_every
             assert torch.allclose(recv.state[k], want[k], atol=1e-5), (step, k, t.stats.last_mode)
             assert torch.allclose(active[k], want[k], atol=1e-5), (step, k, t.stats.last_mode)
     assert t.stats.delta_syncs + t.stats.full_syncs == last_good_version
+
+
+@settings(max_examples=300, deadline=None)
+@given(st.lists(st.tuples(st.floats(-5, 5, width=32), st.one_of(st.floats(-5, 5, width=32), st.just(float("nan")), st.just(float("inf"))),
+                          st.floats(-3, 3, width=32)), min_size=1, max_size=24),
+       st.sampled_from([0.0, 0.1, 0.5, 2.0]), st.sampled_from([0.0, 0.25, 0.5, 1.0]))
+def test_icepop_masks_exactly_the_most_divergent_responses_up_to_its_cap(rows, threshold, max_ratio):
+    from b200fw.train.icepop import IcePopConfig, IcePopFilter
+    train = torch.tensor([r[0] for r in rows])
+    infer = torch.tensor([r[1] for r in rows])
+    adv = torch.tensor([r[2] for r in rows])
+    f = IcePopFilter(IcePopConfig(True, threshold, max_ratio))
+    out, diag = f.filter_divergent_responses(train, infer, adv)
+    gap = (train - infer).abs()
+    gap = torch.where(torch.isfinite(gap), gap, torch.full_like(gap, float("inf")))
+    over = gap > threshold
+    cap = int(len(rows) * max_ratio)
+    k = min(cap, int(over.sum()))
+    masked = (out == 0) & (adv != 0)
+    assert diag["icepop_num_masked"] == k and f.total_masked == k and f.total_seen == len(rows)
+    assert int(masked.sum()) <= k
+    # untouched entries keep their advantage bit for bit; every masked one was over the threshold
+    assert torch.equal(out[~masked], adv[~masked]) and bool(over[masked].all())
+    if k and k < int(over.sum()):
+        # the cap was binding: nothing that stayed is more divergent than something that was dropped
+        dropped_min = gap[masked].min() if bool(masked.any()) else None
+        kept_over = over & ~masked & (adv != 0)
+        if dropped_min is not None and bool(kept_over.any()):
+            assert float(gap[kept_over].max()) <= float(dropped_min)
+    if k == int(over.sum()):
+        assert bool(((out == 0) | ~over).all())          # below the cap every divergent response is neutralised
+    assert torch.isfinite(torch.tensor(diag["icepop_mean_divergence"])) and f.last_non_finite == int((~torch.isfinite(train - infer)).sum())
