@@ -167,6 +167,10 @@ def qknorm_rope_store(qkv: torch.Tensor, qw: torch.Tensor, kw: torch.Tensor, pos
         return q, k, v
     assert head_dim == 128 and k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype
     M = qkv.shape[0]
+    # the kernel indexes pos / slots by token and the caches by slot: sizes the host knows are checked here
+    assert slots.dtype == torch.int32 and slots.is_cuda and slots.numel() == M and pos.numel() == M
+    assert k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.shape == v_cache.shape
+    assert k_cache.shape[-2:] == (Hkv, 128) and qkv.shape[1] == (Hq + 2 * Hkv) * 128 and qkv.stride(1) == 1
     q = torch.empty((M, Hq * 128), device=qkv.device, dtype=qkv.dtype)
     k = torch.empty((M, Hkv * 128), device=qkv.device, dtype=qkv.dtype)
     pos = pos if pos.dtype == torch.int32 else pos.to(torch.int32)

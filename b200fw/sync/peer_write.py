@@ -144,8 +144,12 @@ class PeerWeightSync:
         if self.device.type != "cuda":
             self.last_spans = []
             for k, v in state.items():
+                if k not in st.offsets:
+                    raise KeyError(f"peer write: {k!r} is not part of the staging layout")
+                if v.numel() != st.offsets[k][1]:
+                    raise ValueError(f"peer write: {k!r} has {v.numel()} elements, the staging layout holds {st.offsets[k][1]}")
                 dst = st.view(k)
-                dst.copy_((dst.float() + v.float()).to(st.dtype) if add else v.to(st.dtype))
+                dst.copy_((dst.float() + v.float()).to(st.dtype) if add else v.reshape(dst.shape).to(st.dtype))
                 nbytes += v.numel() * st.flat.element_size()
                 self.last_spans.append(st.offsets[k][:2])
             return (self.spans_checksum(self.last_spans) if add else fletcher_checksum(st.flat[:st.numel])), nbytes
@@ -157,7 +161,15 @@ class PeerWeightSync:
         # (source pointer, destination offset, element count) units, large tensors cut into UNIT-element pieces
         keep, by_dtype = [], {True: [], False: []}
         for k, v in state.items():
+            if k not in st.offsets:
+                raise KeyError(f"peer write: {k!r} is not part of the staging layout")
             off, cnt, _ = st.offsets[k]
+            if v.numel() != cnt:
+                # the kernel reads `cnt` elements from the source pointer: a shorter tensor would be read past its end
+                raise ValueError(f"peer write: {k!r} has {v.numel()} elements, the staging layout holds {cnt}")
+            if v.device.type != self.device.type or (v.device.index is not None and self.device.index is not None
+                                                     and v.device.index != self.device.index):
+                raise ValueError(f"peer write: {k!r} lives on {v.device}, the writer runs on {self.device}")
             src = v.detach().reshape(-1)
             if src.dtype not in (torch.float32, torch.bfloat16):
                 src = src.float()

@@ -483,6 +483,18 @@ def test_double_buffer_swap_under_threads():
     assert torch.all(a == a[0])                                              # never torn
 
 
+def test_peer_write_refuses_tensors_that_do_not_match_the_layout():
+    """Sizes are checked on the host before anything is launched: the device kernel reads as many elements as the
+    layout says, so a shorter source must never reach it."""
+    ps = PeerWeightSync([("w", (4, 8)), ("b", (8,))], torch.float32, torch.device("cpu"))
+    with pytest.raises(ValueError):
+        ps.write({"w": torch.ones(4, 7)})
+    with pytest.raises(KeyError):
+        ps.write({"unknown": torch.ones(8)})
+    cks, nbytes = ps.write({"w": torch.ones(32), "b": torch.zeros(8)})          # same count, other shape: accepted
+    assert nbytes == 40 * 4 and torch.equal(ps.staging.view("w"), torch.ones(4, 8))
+
+
 def test_peer_write_checksum_rejects_corruption():
     layout = [("w", (6, 5)), ("b", (7,))]
     ps = PeerWeightSync(layout, torch.bfloat16, torch.device("cpu"))
