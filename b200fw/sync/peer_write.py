@@ -25,7 +25,10 @@ import torch.distributed as dist
 
 from .. import _native as nv
 from ..obs import nvtx
+from ..obs.logging import get_logger
 from .nccl_transfer import TransferStats
+
+logger = get_logger("sync.peer_write")
 
 MASK64 = (1 << 64) - 1
 
@@ -146,10 +149,11 @@ class PeerWeightSync:
             for k, v in state.items():
                 if k not in st.offsets:
                     raise KeyError(f"peer write: {k!r} is not part of the staging layout")
-                if v.numel() != st.offsets[k][1]:
+                if v.numel() < st.offsets[k][1]:
                     raise ValueError(f"peer write: {k!r} has {v.numel()} elements, the staging layout holds {st.offsets[k][1]}")
                 dst = st.view(k)
-                dst.copy_((dst.float() + v.float()).to(st.dtype) if add else v.reshape(dst.shape).to(st.dtype))
+                v = v.reshape(-1)[:dst.numel()].reshape(dst.shape)
+                dst.copy_((dst.float() + v.float()).to(st.dtype) if add else v.to(st.dtype))
                 nbytes += v.numel() * st.flat.element_size()
                 self.last_spans.append(st.offsets[k][:2])
             return (self.spans_checksum(self.last_spans) if add else fletcher_checksum(st.flat[:st.numel])), nbytes
@@ -164,9 +168,11 @@ class PeerWeightSync:
             if k not in st.offsets:
                 raise KeyError(f"peer write: {k!r} is not part of the staging layout")
             off, cnt, _ = st.offsets[k]
-            if v.numel() != cnt:
+            if v.numel() < cnt:
                 # the kernel reads `cnt` elements from the source pointer: a shorter tensor would be read past its end
                 raise ValueError(f"peer write: {k!r} has {v.numel()} elements, the staging layout holds {cnt}")
+            if v.numel() > cnt:
+                logger.warning("peer write: %r has %d elements, only the first %d fit the staging layout", k, v.numel(), cnt)
             if v.device.type != self.device.type or (v.device.index is not None and self.device.index is not None
                                                      and v.device.index != self.device.index):
                 raise ValueError(f"peer write: {k!r} lives on {v.device}, the writer runs on {self.device}")
