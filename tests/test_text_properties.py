@@ -52,3 +52,31 @@ def test_eval_metrics_are_bounded_and_symmetric_where_they_should_be(a, b):
     if normalize_text(a):
         assert compute_token_f1(a, a) == pytest.approx(1.0)
     assert normalize_text(normalize_text(a)) == normalize_text(a)
+
+
+@settings(max_examples=150, deadline=None)
+@given(st.integers(1, 60), st.integers(1, 8), st.integers(1, 7), st.booleans(), st.integers(0, 99))
+def test_data_parallel_shards_partition_the_dataset(num_records, dp_size, batch_size, shuffle, seed):
+    """Every record goes to exactly one data-parallel rank, a rank's batches never repeat or invent a record, and the
+    global indices a batch reports point back at the records it carries (text and synthetic pipelines)."""
+    from b200fw.data.pipeline import GSM8KDataPipeline, SimpleTokenizer, SyntheticTokenPipeline
+    records = [{"question": f"what is {i} plus 1 ?", "answer": f"#### {i + 1}"} for i in range(num_records)]
+    seen = []
+    for rank in range(dp_size):
+        p = GSM8KDataPipeline(records=records, tokenizer=SimpleTokenizer(), dp_rank=rank, dp_size=dp_size)
+        assert len(p) == len(records[rank::dp_size])
+        mine = []
+        for b in p.get_batches(batch_size, shuffle=shuffle, seed=seed):
+            assert len(b.prompt_tokens) == batch_size == len(b.prompt_indices)
+            for text, gi, truth in zip(b.prompts, b.prompt_indices, b.ground_truths):
+                assert gi % dp_size == rank and f"what is {gi} plus 1" in text and truth == f"#### {gi + 1}"
+            mine += list(b.prompt_indices)
+        assert len(mine) == len(set(mine)) == (len(p) // batch_size) * batch_size
+        seen.append(set(range(rank, num_records, dp_size)))
+        assert set(mine) <= seen[-1]
+    assert set().union(*seen) == set(range(num_records)) and sum(len(s) for s in seen) == num_records
+    syn = [SyntheticTokenPipeline(64, num_samples=num_records, prompt_len=8, seed=seed, dp_rank=r, dp_size=dp_size)
+           for r in range(dp_size)]
+    idx = [i for s in syn for b in s.get_batches(batch_size, shuffle, seed) for i in b.prompt_indices]
+    assert len(idx) == len(set(idx)) and set(idx) <= set(range(num_records))
+    assert all(a.samples == syn[0].samples for a in syn)            # the same seeded corpus on every rank
