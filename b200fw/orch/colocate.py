@@ -259,7 +259,11 @@ class ColocateOrchestrator:
             return next(self._batches)
         except StopIteration:
             self._batches = iter(self.data.get_batches(self._per_rank_batch()))
-            return next(self._batches)
+            try:
+                return next(self._batches)
+            except StopIteration:
+                raise ValueError(f"this rank's data shard has {len(self.data)} samples, fewer than its batch of "
+                                 f"{self._per_rank_batch()}: lower training.batch_size or raise data.max_samples") from None
 
     def _rollout(self, batch: GRPOBatch) -> _Rollout:
         """K sampled responses per prompt through the rollout backend."""
