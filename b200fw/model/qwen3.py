@@ -504,4 +504,8 @@ class ParallelTransformerModel(nn.Module):
                 sel = ops.lm_head_logprob(h.index_select(0, idx), self.lm_head_weight, tgt.index_select(0, idx),
                                           temperature, shard=self.vocab_shard())
                 lp = lp.index_copy(0, idx, sel)
+            elif torch.is_grad_enabled() and h.requires_grad:
+                # nothing to score on this rank (every response empty): keep the result attached to the graph so that
+                # backward still runs, with zero gradients, and data-parallel peers are not left waiting for this rank
+                lp = lp + h.float().sum() * 0.0
         return lp.reshape(B, S)[:, :-1]

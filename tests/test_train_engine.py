@@ -252,3 +252,35 @@ def test_close_window_steps_after_any_number_of_chunks():
     assert eng.step_count == 0
     m = eng.grpo_step(P, R, W, close_window=True)
     assert eng.step_count == 1 and m.grad_norm > 0 and eng._accumulation_count == 0
+
+
+def _empty_rank_worker(rank, world):
+    """Rank 1's responses are all empty (nothing to score); rank 0 has a normal batch."""
+    import hashlib
+    cfg = TrainConfig(model_preset="tiny", dp_size=world, lora_rank=0, grpo_beta=0.01, learning_rate=1e-3,
+                      gradient_accumulation_steps=1, zero_stage=1, use_amp=False, amp_dtype="fp32", warmup_steps=0,
+                      max_seq_len=32, backend="gloo", bucket_mb=4.0)
+    eng = TrainEngine(cfg).initialize()
+    g = torch.Generator().manual_seed(5)
+    prompt = torch.randint(3, 8192, (6,), generator=g).tolist()
+    resp = [torch.randint(3, 8192, (n,), generator=g).tolist() for n in (5, 7)]
+    mine = resp if rank == 0 else [[], []]
+    out = []
+    m = eng.grpo_step([prompt], [mine], [[0.0, 1.0]])
+    out.append((m.loss, m.grad_norm))
+    m = eng.sft_step([prompt, prompt], mine)
+    out.append((m.loss, m.grad_norm))
+    with eng.optimizer.eval_mode():
+        flat = torch.cat([p.detach().reshape(-1) for p in eng.model.parameters()])
+    return out, hashlib.sha256(flat.numpy().tobytes()).hexdigest()
+
+
+def test_a_rank_with_nothing_to_score_still_takes_part_in_the_step():
+    """A data-parallel rank whose responses are all empty contributes zero gradients instead of failing in backward
+    (which would leave its peers waiting in the gradient reduction); the ranks stay bit-identical."""
+    res = run_ranks(_empty_rank_worker, 2, timeout=600)
+    (out0, h0), (out1, h1) = res
+    assert h0 == h1
+    for (l0, g0), (l1, g1) in zip(out0, out1):
+        assert l1 == 0.0 and math.isfinite(l0) and l0 != 0.0
+        assert g0 > 0 and abs(g0 - g1) < 1e-6 * max(1.0, g0)      # one global norm, seen by both
