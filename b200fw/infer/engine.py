@@ -152,13 +152,45 @@ class InferenceEngine:
     def add_request(self, request_id: str, prompt_tokens: List[int], max_tokens: int = 512,
                     temperature: Optional[float] = None, top_p: Optional[float] = None) -> Request:
         assert self.initialized, "call initialize() first"
-        r = Request(request_id, list(prompt_tokens), max_tokens,
+        prompt_tokens, max_tokens = self._check_request(request_id, prompt_tokens, max_tokens)
+        return self._enqueue(request_id, prompt_tokens, max_tokens, temperature, top_p)
+
+    def _enqueue(self, request_id, prompt_tokens, max_tokens, temperature, top_p) -> Request:
+        r = Request(request_id, prompt_tokens, max_tokens,
                     self.config.temperature if temperature is None else temperature,
                     self.config.top_p if top_p is None else top_p, eos_token_id=self.config.eos_token_id)
         r.weights_version = self.weights_version        # the version this request started under
         self.requests[request_id] = r
         self.scheduler.add_request(r)
         return r
+
+    def _check_request(self, request_id, prompt_tokens, max_tokens: int):
+        """Refuse, at submission, a request that could not be served or would harm the others: the step loop is shared
+        by every request in flight, and the embedding and rotary kernels index their tables with token ids and
+        positions unchecked.  Returns the prompt as a list and ``max_tokens`` shortened to what the position table
+        allows."""
+        prompt = [int(t) for t in prompt_tokens]
+        if not prompt:
+            raise ValueError(f"request {request_id!r}: empty prompt")
+        if request_id in self.requests:
+            raise ValueError(f"request id {request_id!r} is already in flight")
+        mc = getattr(self.model, "cfg", None)
+        if mc is None:                      # mock mode: no model, nothing indexed
+            return prompt, max_tokens
+        lo, hi = min(prompt), max(prompt)
+        if lo < 0 or hi >= mc.vocab_size:
+            raise ValueError(f"request {request_id!r}: token id {lo if lo < 0 else hi} is outside the vocabulary "
+                             f"[0, {mc.vocab_size})")
+        # speculative rounds score up to k drafted tokens past the last accepted one
+        room = mc.max_position_embeddings - len(prompt) - (self.config.speculative_num_tokens + 1 if self.spec else 0)
+        if room < 1:
+            raise ValueError(f"request {request_id!r}: a prompt of {len(prompt)} tokens leaves no room to generate "
+                             f"within max_position_embeddings={mc.max_position_embeddings}")
+        if max_tokens > room:
+            logger.warning("request %s: max_tokens %d shortened to %d (max_position_embeddings=%d)", request_id,
+                           max_tokens, room, mc.max_position_embeddings)
+            max_tokens = room
+        return prompt, max_tokens
 
     def has_pending(self) -> bool:
         return self.scheduler.has_pending_requests()
@@ -637,13 +669,15 @@ class InferenceEngine:
         """Generate for a batch of prompts; returns the output token lists in prompt order (``None`` for
         a prompt whose request was dropped by an out-of-memory recovery)."""
         assert self.initialized
-        if self.config.inference_mode == "eager":
-            return self._generate_eager(prompts_tokens, max_tokens, temperature, top_p)
         base = f"gen{time.monotonic_ns()}"
+        # all or nothing: nothing is queued (or computed) if one prompt is bad
+        checked = [self._check_request(f"{base}-{i}", p, max_tokens) for i, p in enumerate(prompts_tokens)]
+        if self.config.inference_mode == "eager":
+            return self._generate_eager(checked, temperature, top_p)
         rids = []
-        for i, p in enumerate(prompts_tokens):
+        for i, (p, mt) in enumerate(checked):
             rid = f"{base}-{i}"
-            self.add_request(rid, p, max_tokens, temperature, top_p)
+            self._enqueue(rid, p, mt, temperature, top_p)
             rids.append(rid)
         guard = 0
         limit = (max_tokens + 8) * (len(prompts_tokens) + 8) + sum(len(p) for p in prompts_tokens)
@@ -660,13 +694,14 @@ class InferenceEngine:
         return (outs, lps) if return_logprobs else outs
 
     @torch.no_grad()
-    def _generate_eager(self, prompts_tokens, max_tokens, temperature, top_p):
-        """Full re-forward per token, no KV cache: slow, simple, and the oracle for the paged path."""
+    def _generate_eager(self, checked, temperature, top_p):
+        """Full re-forward per token, no KV cache: slow, simple, and the oracle for the paged path.  ``checked``:
+        ``(prompt, max_tokens)`` pairs from :meth:`_check_request`."""
         from ..ops import topp_sample
         t = self.config.temperature if temperature is None else temperature
         p = self.config.top_p if top_p is None else top_p
         outs = []
-        for prompt in prompts_tokens:
+        for prompt, max_tokens in checked:
             seq, new = list(prompt), []
             for _ in range(max_tokens):
                 ids = torch.tensor([seq], dtype=torch.long, device=self.device)

@@ -380,6 +380,9 @@ class ParallelTransformerModel(nn.Module):
     def _positions(self, B: int, S: int, device, positions=None):
         if positions is not None:
             return positions.reshape(-1).to(torch.int32)
+        if S > self.cfg.max_position_embeddings:
+            # the rotary kernels index the cos / sin tables with the position, unchecked
+            raise ValueError(f"sequence length {S} exceeds max_position_embeddings={self.cfg.max_position_embeddings}")
         return torch.arange(S, device=device, dtype=torch.int32).repeat(B)
 
     def embed(self, input_ids: torch.Tensor) -> torch.Tensor:

@@ -163,6 +163,9 @@ class TrainEngine:
         else:
             mc = read_hf_config(cfg.model_path)
         self.model_config = mc
+        if cfg.max_seq_len > mc.max_position_embeddings:
+            raise ValueError(f"max_seq_len={cfg.max_seq_len} exceeds the model's max_position_embeddings="
+                             f"{mc.max_position_embeddings}")
         layer_range, first, last = None, True, True
         if cfg.pp_size > 1:
             if mc.num_layers < cfg.pp_size:
@@ -238,6 +241,29 @@ class TrainEngine:
             self._pinned[name] = buf
         return buf[:numel]
 
+    def _check_host_batch(self, input_ids: Optional[torch.Tensor], labels: Optional[torch.Tensor] = None):
+        """Refuse token ids and labels outside the vocabulary, and rows longer than the position table, while the
+        batch is still in host memory: the embedding, rotary and loss kernels index their tables with these values
+        unchecked, so a bad id would read outside the table on the device.  Device tensors are not inspected (that
+        would cost a synchronisation); their producer is responsible for them."""
+        mc = self.model_config
+        if mc is None:
+            return
+        V = mc.vocab_size
+        if input_ids is not None and input_ids.device.type == "cpu" and input_ids.numel():
+            lo, hi = int(input_ids.min()), int(input_ids.max())
+            if lo < 0 or hi >= V:
+                raise ValueError(f"token id {lo if lo < 0 else hi} is outside the vocabulary [0, {V})")
+            if input_ids.shape[-1] > mc.max_position_embeddings:
+                raise ValueError(f"sequence length {input_ids.shape[-1]} exceeds max_position_embeddings="
+                                 f"{mc.max_position_embeddings}")
+        if labels is not None and labels.device.type == "cpu" and labels.numel():
+            hi = int(labels.max())
+            bad_neg = int(((labels < 0) & (labels != -100)).sum())
+            if hi >= V or bad_neg:
+                raise ValueError(f"labels must be token ids in [0, {V}) or -100 (largest {hi}, "
+                                 f"{bad_neg} negative values other than -100)")
+
     def _to_device(self, name: str, rows: List[List[int]], fill: int, on_host: bool = False) -> torch.Tensor:
         """Pad ``rows`` to a rectangle in a reusable pinned host buffer and copy it to the device
         (``on_host``: hand back the pinned view itself; the caller copies)."""
@@ -246,6 +272,7 @@ class TrainEngine:
             t = torch.full((n, m), fill, dtype=torch.long)
             for i, r in enumerate(rows):
                 t[i, :len(r)] = torch.tensor(r, dtype=torch.long)
+            self._check_host_batch(t if name == "ids" else None, t if name == "labels" else None)
             return t
         view = self._pinned_buf(name, n * m).view(n, m)
         if all(len(r) == m for r in rows):
@@ -254,6 +281,7 @@ class TrainEngine:
             view.fill_(fill)
             for i, r in enumerate(rows):
                 view[i, :len(r)] = torch.tensor(r, dtype=torch.long)
+        self._check_host_batch(view if name == "ids" else None, view if name == "labels" else None)
         return view if on_host else view.to(self.device, non_blocking=True)
 
     def _build_batch(self, prompts: List[List[int]], responses: List[List[int]], on_host: bool = False):
@@ -364,6 +392,7 @@ class TrainEngine:
         """SFT step on ready ``[B,S]`` tensors (host tensors are copied to the device asynchronously).
         ``sync=False`` returns ``(loss_tensor, grad_norm_tensor_or_None)`` without a host sync."""
         valid_idx = None
+        self._check_host_batch(input_ids, labels)
         if input_ids.device != self.device:
             if labels.device.type == "cpu" and self.device.type == "cuda":
                 # the supervised rows (label of the next token is not -100) are known on the host before the

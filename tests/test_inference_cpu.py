@@ -316,3 +316,38 @@ def test_fused_norm_rope_store_path_equals_the_two_step_path(model, oracle):
     kc0, vc0 = torch.zeros_like(kc), torch.zeros_like(vc)
     kv_store(k0, v0, kc0, vc0, torch.tensor([[2, 0, 16, 0], [0, 17, 4, 3]], dtype=torch.int32))
     assert torch.equal(q, q0) and torch.equal(kc, kc0) and torch.equal(vc, vc0)
+
+
+def test_bad_requests_are_refused_at_submission_and_leave_the_engine_serving(model, oracle):
+    """An empty prompt, a token outside the vocabulary, a prompt that fills the position table or a request id that is
+    still in flight raises at ``add_request`` (these values index device tables unchecked); a ``max_tokens`` beyond the
+    position table is shortened; ``generate`` queues nothing if one prompt of the batch is bad; the requests already
+    in flight finish as if nothing happened."""
+    eng = _engine(model)
+    eng.add_request("good", PROMPTS[0], 10)
+    eng.step()
+    for rid, prompt, err in [("e", [], "empty prompt"), ("v", [5, MC.vocab_size, 7], "outside the vocabulary"),
+                             ("n", [5, -1], "outside the vocabulary"), ("good", [5, 6], "already in flight"),
+                             ("l", [9] * MC.max_position_embeddings, "no room")]:
+        with pytest.raises(ValueError, match=err):
+            eng.add_request(rid, prompt, 4)
+    with pytest.raises(ValueError, match="empty prompt"):
+        eng.generate([[4, 5], []], max_tokens=3)
+    assert set(eng.requests) == {"good"}                       # the good half of that batch was not queued either
+    r = eng.add_request("long", [9] * (MC.max_position_embeddings - 5), 50)
+    assert r.max_tokens == 5
+    while eng.has_pending():
+        eng.step()
+    assert eng.finished["good"].output_tokens == oracle[0]
+    assert len(eng.finished["long"].output_tokens) == 5
+    assert eng.pool.num_free_blocks == eng.pool.num_blocks
+    eng.add_request("good", PROMPTS[1], 2)                      # a finished id may be used again
+    # the eager oracle applies the same checks
+    cfg = InferenceConfig.from_model_config(MC, inference_mode="eager", temperature=0.0, eos_token_id=None)
+    with pytest.raises(ValueError, match="empty prompt"):
+        InferenceEngine(cfg, model).initialize().generate([[]], max_tokens=2)
+    # mock mode has no tables to index: only the structural checks apply
+    mock = InferenceEngine(InferenceConfig(inference_mode="mock", num_blocks=8)).initialize()
+    mock.add_request("m", [10 ** 9], 2)
+    with pytest.raises(ValueError, match="empty prompt"):
+        mock.add_request("m2", [], 2)

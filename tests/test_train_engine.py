@@ -284,3 +284,38 @@ def test_a_rank_with_nothing_to_score_still_takes_part_in_the_step():
     for (l0, g0), (l1, g1) in zip(out0, out1):
         assert l1 == 0.0 and math.isfinite(l0) and l0 != 0.0
         assert g0 > 0 and abs(g0 - g1) < 1e-6 * max(1.0, g0)      # one global norm, seen by both
+
+
+def test_token_ids_and_lengths_are_checked_while_the_batch_is_on_the_host():
+    """The embedding, rotary and loss kernels index their tables with ids / positions / labels unchecked: a bad value
+    is refused before the batch leaves host memory, and the step that follows a refusal runs normally."""
+    import pytest
+    cfg = TrainConfig(model_config=SMALL, lora_rank=0, grpo_beta=0.0, gradient_accumulation_steps=1, zero_stage=1,
+                      use_amp=False, amp_dtype="fp32", warmup_steps=0, max_seq_len=32)
+    eng = TrainEngine(cfg).initialize()
+    V = SMALL.vocab_size
+    with pytest.raises(ValueError, match="outside the vocabulary"):
+        eng.sft_step([[3, 4, V]], [[5, 6]])
+    with pytest.raises(ValueError, match="outside the vocabulary"):
+        eng.sft_step([[3, 4]], [[5, -2]])
+    with pytest.raises(ValueError, match="outside the vocabulary"):
+        eng.grpo_step([[3, 4]], [[[5, V + 7], [6]]], [[0.0, 1.0]])
+    ids = torch.randint(0, V, (2, 16))
+    bad_labels = ids.clone()
+    bad_labels[0, 3] = V
+    with pytest.raises(ValueError, match="labels must be"):
+        eng.sft_step_tensors(ids, bad_labels)
+    bad_labels[0, 3] = -1
+    with pytest.raises(ValueError, match="labels must be"):
+        eng.sft_step_tensors(ids, bad_labels)
+    long = torch.randint(0, V, (1, SMALL.max_position_embeddings + 1))
+    with pytest.raises(ValueError, match="max_position_embeddings"):
+        eng.sft_step_tensors(long, long.clone())
+    with pytest.raises(ValueError, match="max_position_embeddings"):
+        eng.model(long)
+    assert eng.step_count == 0
+    m = eng.sft_step([[3, 4, 5]], [[5, 6]])
+    assert math.isfinite(m.loss) and eng.step_count == 1
+    with pytest.raises(ValueError, match="max_seq_len"):
+        TrainEngine(TrainConfig(model_config=SMALL, max_seq_len=SMALL.max_position_embeddings + 1, lora_rank=0,
+                                amp_dtype="fp32")).initialize()
