@@ -156,9 +156,12 @@ class InferenceEngine:
         return self._enqueue(request_id, prompt_tokens, max_tokens, temperature, top_p)
 
     def _enqueue(self, request_id, prompt_tokens, max_tokens, temperature, top_p) -> Request:
-        r = Request(request_id, prompt_tokens, max_tokens,
-                    self.config.temperature if temperature is None else temperature,
-                    self.config.top_p if top_p is None else top_p, eos_token_id=self.config.eos_token_id)
+        t = float(self.config.temperature if temperature is None else temperature)
+        p = float(self.config.top_p if top_p is None else top_p)
+        if not t >= 1e-5:
+            t = 0.0                 # zero, negative, vanishing (1 / t would overflow) or NaN: greedy
+        p = min(max(p, 0.0), 1.0) if p == p else 1.0
+        r = Request(request_id, prompt_tokens, max_tokens, t, p, eos_token_id=self.config.eos_token_id)
         r.weights_version = self.weights_version        # the version this request started under
         self.requests[request_id] = r
         self.scheduler.add_request(r)

@@ -212,7 +212,8 @@ def topp_sample(logits: torch.Tensor, temperature: torch.Tensor, top_p: torch.Te
             lp = torch.log_softmax(row / t, -1)
             p = lp.exp()
             sp, si = p.sort(descending=True)
-            keep_sorted = (sp.cumsum(0) - sp) < float(top_p[b])
+            keep_sorted = (sp.cumsum(0) - sp) < min(max(float(top_p[b]), 0.0), 1.0)
+            keep_sorted[0] = True           # top_p <= 0 keeps the most likely token (the kernel's clamp)
             keep = torch.zeros(V, dtype=torch.bool)
             keep[si[keep_sorted]] = True
             kept = torch.where(keep, p, torch.zeros_like(p))

@@ -342,6 +342,10 @@ def test_bad_requests_are_refused_at_submission_and_leave_the_engine_serving(mod
     assert len(eng.finished["long"].output_tokens) == 5
     assert eng.pool.num_free_blocks == eng.pool.num_blocks
     eng.add_request("good", PROMPTS[1], 2)                      # a finished id may be used again
+    # sampling parameters are made sane: NaN / negative / vanishing temperature is greedy, top_p is clamped to [0, 1]
+    odd = eng.add_request("odd", PROMPTS[1], 2, temperature=float("nan"), top_p=7.0)
+    tiny = eng.add_request("tiny", PROMPTS[1], 2, temperature=1e-30, top_p=float("nan"))
+    assert (odd.temperature, odd.top_p, tiny.temperature, tiny.top_p) == (0.0, 1.0, 0.0, 1.0)
     # the eager oracle applies the same checks
     cfg = InferenceConfig.from_model_config(MC, inference_mode="eager", temperature=0.0, eos_token_id=None)
     with pytest.raises(ValueError, match="empty prompt"):

@@ -160,3 +160,32 @@ def test_paged_engine_equals_eager_oracle_under_memory_pressure(model, workload,
         eng.prefix_cache.evict_lru(blocks)
     assert eng.pool.num_free_blocks == eng.pool.num_blocks, (eng.pool.num_free_blocks, eng.pool.num_blocks)
     assert eng.pool.double_free_count == 0 and not eng.kv.tables
+
+
+@settings(max_examples=200, deadline=None)
+@given(st.lists(st.floats(-30, 30, allow_nan=False, width=32), min_size=2, max_size=40),
+       st.floats(-1.0, 4.0, allow_nan=False), st.floats(-0.5, 1.5, allow_nan=False), st.floats(0.0, 1.0, allow_nan=False))
+def test_cpu_sampler_picks_inside_the_nucleus(row, temp, top_p, u):
+    """The CPU sampler (the oracle of the sampling kernel): the pick is a valid index; greedy at temperature <= 0; at
+    top_p <= 0 the most likely token; otherwise a token of the smallest set of most likely tokens whose mass reaches
+    top_p; the reported log-prob is the tempered full-softmax one."""
+    from b200fw.ops import topp_sample
+    if 0 < temp < 1e-3:
+        temp = 0.0                  # the engine maps vanishing temperatures to greedy before they reach the sampler
+    logits = torch.tensor([row], dtype=torch.float32)
+    ids, lps = topp_sample(logits, torch.tensor([temp]), torch.tensor([top_p]), torch.tensor([u]), return_logprob=True)
+    pick = int(ids[0])
+    assert 0 <= pick < len(row)
+    if temp <= 0:
+        assert logits[0, pick] == logits.max()
+        return
+    lp = torch.log_softmax(logits[0] / temp, -1)
+    assert abs(float(lps[0]) - float(lp[pick])) < 1e-5
+    p = lp.exp()
+    sp, _ = p.sort(descending=True)
+    before = sp.cumsum(0) - sp
+    nucleus = sp[before < min(max(top_p, 0.0), 1.0)]
+    floor = float(nucleus[-1]) if nucleus.numel() else float(sp[0])
+    assert float(p[pick]) >= floor * (1 - 1e-5), (pick, float(p[pick]), floor)
+    if top_p <= 0:
+        assert float(p[pick]) >= float(sp[0]) * (1 - 1e-6)
