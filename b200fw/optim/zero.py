@@ -705,8 +705,23 @@ class ZeROOptimizer:
             "lr": self.param_groups[0]["lr"],
         }
 
+    def state_dict_mismatch(self, sd: Dict) -> Optional[str]:
+        """Why ``sd`` cannot be loaded into this optimizer (``None`` when it can).  Local: no collective."""
+        if not isinstance(sd, dict) or "local_shard" not in sd:
+            return "not a state dict of this optimizer"
+        if sd.get("world") != self.world:
+            return f"saved by {sd.get('world')} data-parallel ranks, this run has {self.world}"
+        if self.stage >= 1 and self.world > 1 and sd.get("rank", self.rank) != self.rank:
+            return f"shard of rank {sd.get('rank')}, this is rank {self.rank}"
+        for k in ("local_shard", "exp_avg", "exp_avg_sq"):
+            if k not in sd or tuple(sd[k].shape) != tuple(self.master.shape):
+                return f"{k}: shape {tuple(sd[k].shape) if k in sd else None}, expected {tuple(self.master.shape)}"
+        return None
+
     def load_state_dict(self, sd: Dict) -> bool:
-        if sd.get("world") != self.world or tuple(sd["local_shard"].shape) != tuple(self.master.shape):
+        """Restore masters and moments, then re-publish the parameters (a collective under ZeRO: every rank of the
+        group must call this, so callers settle with :meth:`state_dict_mismatch` first whether all of them can)."""
+        if self.state_dict_mismatch(sd) is not None:
             return False
         self.master.copy_(sd["local_shard"])
         self.exp_avg.copy_(sd["exp_avg"])

@@ -776,63 +776,116 @@ class TrainEngine:
         return delta
 
     # ---- checkpoints --------------------------------------------------------------------------------
+    @staticmethod
+    def _atomic_save(obj, dest: str, as_json: bool = False):
+        """Write beside the destination and rename over it: a reader (or a restart after a crash in the middle of a
+        save) sees the previous file or the new one, never a torn one."""
+        tmp = f"{dest}.tmp{os.getpid()}"
+        if as_json:
+            with open(tmp, "w") as f:
+                json.dump(obj, f)
+        else:
+            torch.save(obj, tmp)
+        os.replace(tmp, dest)
+
     def save_checkpoint(self, path: str, save_base_weights: Optional[bool] = None) -> None:
         """``lora_weights.pt`` + ``optimizer_state_rank{r}.pt`` (every rank saves its own shard; rank 0
-        also writes the reference-compatible ``optimizer_state.pt``) + ``trainer_state.json`` (step
-        counters, LR schedule, RNG) + HF-format base weights for full fine-tuning."""
+        also writes the reference-compatible ``optimizer_state.pt``) + HF-format base weights for full fine-tuning +
+        ``trainer_state.json`` (step counters, LR schedule, RNG).  Every file is written atomically, and the state
+        file last, after all ranks have finished theirs: its step count names the step every other file belongs to."""
         ctx = self.parallel_ctx
         os.makedirs(path, exist_ok=True)
         rank = ctx.global_rank
         lora = get_lora_state_dict(self.model)
         if lora and ctx.dp_rank == 0:
             name = "lora_weights.pt" if ctx.tp_size == 1 else f"lora_weights_tp{ctx.tp_rank}.pt"
-            torch.save({k: v.cpu() for k, v in lora.items()}, os.path.join(path, name))
+            self._atomic_save({k: v.cpu() for k, v in lora.items()}, os.path.join(path, name))
         sd = self.optimizer.state_dict()
-        torch.save(sd, os.path.join(path, f"optimizer_state_rank{rank}.pt"))
+        sd["trainer_step"] = self.step_count
+        self._atomic_save(sd, os.path.join(path, f"optimizer_state_rank{rank}.pt"))
         if rank == 0:
-            torch.save(sd, os.path.join(path, "optimizer_state.pt"))
-            with open(os.path.join(path, "trainer_state.json"), "w") as f:
-                json.dump({"step_count": self.step_count, "accumulation_count": self._accumulation_count,
-                           "lr_scheduler": self.lr_scheduler.state_dict(), "world_size": ctx.world_size,
-                           "torch_rng_seed": int(torch.initial_seed())}, f)
+            self._atomic_save(sd, os.path.join(path, "optimizer_state.pt"))
         full = save_base_weights if save_base_weights is not None else (self.config.lora_rank <= 0)
         if full:
             with self.optimizer.eval_mode():
                 shard = "model.safetensors" if ctx.pp_size == 1 else f"model-stage{ctx.pp_rank}.safetensors"
                 save_hf_checkpoint(self.model, path, write=(ctx.dp_rank == 0 and ctx.tp_rank == 0), shard_name=shard)
         ctx.barrier()
+        if rank == 0:
+            self._atomic_save({"step_count": self.step_count, "accumulation_count": self._accumulation_count,
+                               "lr_scheduler": self.lr_scheduler.state_dict(), "world_size": ctx.world_size,
+                               "torch_rng_seed": int(torch.initial_seed())},
+                              os.path.join(path, "trainer_state.json"), as_json=True)
+        ctx.barrier()
+
+    def _read_checkpoint(self, path: str) -> Dict[str, object]:
+        """The local half of a restore: read this rank's files and check them against this run, touching neither the
+        model nor the optimizer and calling no collective."""
+        ctx = self.parallel_ctx
+        out: Dict[str, object] = {"weights": False, "lora": None, "opt": None, "state": None}
+        out["weights"] = self.config.lora_rank <= 0 and any(f.endswith(".safetensors") for f in os.listdir(path))
+        lname = "lora_weights.pt" if ctx.tp_size == 1 else f"lora_weights_tp{ctx.tp_rank}.pt"
+        lpath = os.path.join(path, lname)
+        if os.path.exists(lpath):
+            out["lora"] = torch.load(lpath, map_location="cpu", weights_only=True)
+        spath = os.path.join(path, "trainer_state.json")
+        if os.path.exists(spath):
+            with open(spath) as f:
+                out["state"] = json.load(f)
+        opath = os.path.join(path, f"optimizer_state_rank{ctx.global_rank}.pt")
+        if not os.path.exists(opath):
+            # a checkpoint written by the reference, or by one process, has the one file only
+            opath = os.path.join(path, "optimizer_state.pt")
+        if os.path.exists(opath):
+            sd = torch.load(opath, map_location="cpu", weights_only=False)
+            why = self.optimizer.state_dict_mismatch(sd) if hasattr(self.optimizer, "state_dict_mismatch") else None
+            st = out["state"]
+            if why is None and st is not None and "trainer_step" in sd and sd["trainer_step"] != st.get("step_count"):
+                why = (f"optimizer shard is of step {sd['trainer_step']}, trainer_state.json of step "
+                       f"{st.get('step_count')} (a save was interrupted)")
+            if why is None:
+                out["opt"] = sd
+            else:
+                logger.warning("load_checkpoint(%s): optimizer state not restored: %s", path, why)
+        return out
+
+    def _all_ranks_have(self, flags: List[bool]) -> List[bool]:
+        """Element-wise AND of ``flags`` over every rank of the job."""
+        ctx = self.parallel_ctx
+        if ctx.world_size <= 1 or not dist.is_initialized():
+            return list(flags)
+        t = torch.tensor([int(bool(f)) for f in flags], dtype=torch.int32, device=self.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        return [bool(v) for v in t.tolist()]
 
     def load_checkpoint(self, path: str) -> bool:
-        """Tolerant restore (returns False instead of raising when files are absent or do not match)."""
-        ctx = self.parallel_ctx
+        """Tolerant restore: returns False instead of raising when files are absent or do not match; True when the
+        optimizer state came back too.  Reading is local; what gets applied is agreed over all ranks first, because
+        applying ends in collectives (re-publishing parameters from the restored masters): a part that one rank lacks
+        (its optimizer shard is missing, of another layout or of another step) is skipped by every rank."""
         try:
-            ok = True
-            if any(f.endswith(".safetensors") for f in os.listdir(path)) and self.config.lora_rank <= 0:
-                with self.optimizer.eval_mode():
-                    load_from_hf_checkpoint(self.model, path)
-                    self.optimizer.refresh_masters_from_params()
-            lname = "lora_weights.pt" if ctx.tp_size == 1 else f"lora_weights_tp{ctx.tp_rank}.pt"
-            lpath = os.path.join(path, lname)
-            if os.path.exists(lpath):
-                load_lora_state_dict(self.model, torch.load(lpath, map_location="cpu", weights_only=True))
-                self.optimizer.refresh_masters_from_params()
-            opath = os.path.join(path, f"optimizer_state_rank{ctx.global_rank}.pt")
-            if not os.path.exists(opath):
-                opath = os.path.join(path, "optimizer_state.pt")
-            if os.path.exists(opath):
-                ok = self.optimizer.load_state_dict(torch.load(opath, map_location="cpu", weights_only=False)) and ok
-            else:
-                ok = False
-            spath = os.path.join(path, "trainer_state.json")
-            if os.path.exists(spath):
-                with open(spath) as f:
-                    st = json.load(f)
-                self.step_count = int(st.get("step_count", 0))
-                self.lr_scheduler.load_state_dict(st.get("lr_scheduler", {}))
-            return ok
+            got = self._read_checkpoint(path)
+            read_ok = True
         except Exception as e:  # noqa: BLE001 - restore is best-effort by contract
             logger.warning("load_checkpoint(%s) failed: %s", path, e)
+            got, read_ok = {"weights": False, "lora": None, "opt": None, "state": None}, False
+        read_ok, has_w, has_l, has_o = self._all_ranks_have(
+            [read_ok, got["weights"], got["lora"] is not None, got["opt"] is not None])
+        if not read_ok:
             return False
+        if has_w:
+            with self.optimizer.eval_mode():
+                load_from_hf_checkpoint(self.model, path)
+                self.optimizer.refresh_masters_from_params()
+        if has_l:
+            load_lora_state_dict(self.model, got["lora"])
+            self.optimizer.refresh_masters_from_params()
+        ok = has_o and bool(self.optimizer.load_state_dict(got["opt"]))
+        st = got["state"]
+        if st is not None:
+            self.step_count = int(st.get("step_count", 0))
+            self.lr_scheduler.load_state_dict(st.get("lr_scheduler", {}))
+        return ok
 
     # ---- reports ------------------------------------------------------------------------------------
     def generate_memory_report(self, batch_tokens: int = 0) -> MemoryReport:

@@ -319,3 +319,64 @@ def test_token_ids_and_lengths_are_checked_while_the_batch_is_on_the_host():
     with pytest.raises(ValueError, match="max_seq_len"):
         TrainEngine(TrainConfig(model_config=SMALL, max_seq_len=SMALL.max_position_embeddings + 1, lora_rank=0,
                                 amp_dtype="fp32")).initialize()
+
+
+def _ckpt_agreement_worker(rank, world, path):
+    import os
+    import shutil
+    cfg = TrainConfig(model_config=SMALL, dp_size=world, lora_rank=0, grpo_beta=0.0, learning_rate=1e-3,
+                      gradient_accumulation_steps=1, zero_stage=1, use_amp=False, amp_dtype="fp32", warmup_steps=0,
+                      max_seq_len=32, backend="gloo", bucket_mb=0.02)
+    eng = TrainEngine(cfg).initialize()
+    ids, labels = _tiny_batch(0, rank, 2, 16, SMALL.vocab_size)
+    eng.sft_step_tensors(ids, labels)
+    good = os.path.join(path, "good")
+    eng.save_checkpoint(good)
+    assert not [f for f in os.listdir(good) if ".tmp" in f]            # the temporaries were renamed away
+    with eng.optimizer.eval_mode():
+        saved = torch.cat([p.detach().reshape(-1).clone() for p in eng.model.parameters()])
+    saved_m = eng.optimizer.exp_avg.clone()
+    eng.sft_step_tensors(ids, labels)                                   # move on: step 2
+    out = {}
+    # (1) the complete checkpoint restores everything
+    out["good"] = eng.load_checkpoint(good)
+    with eng.optimizer.eval_mode():
+        now = torch.cat([p.detach().reshape(-1) for p in eng.model.parameters()])
+    out["good_exact"] = bool(torch.equal(now, saved) and torch.equal(eng.optimizer.exp_avg, saved_m)) and eng.step_count == 1
+    # (2) rank 1's shard is gone (only rank 0's file and its copy remain): rank 1 must not take rank 0's shard, and
+    #     rank 0 must not walk alone into the parameter re-publication
+    eng.parallel_ctx.barrier()
+    if rank == 0:
+        shutil.copytree(good, os.path.join(path, "lost"))
+        os.remove(os.path.join(path, "lost", "optimizer_state_rank1.pt"))
+    eng.parallel_ctx.barrier()
+    eng.sft_step_tensors(ids, labels)
+    before = eng.optimizer.exp_avg.clone()
+    out["lost"] = eng.load_checkpoint(os.path.join(path, "lost"))
+    out["lost_moments_kept"] = bool(torch.equal(eng.optimizer.exp_avg, before))
+    with eng.optimizer.eval_mode():
+        now = torch.cat([p.detach().reshape(-1) for p in eng.model.parameters()])
+    out["lost_weights_restored"] = bool(torch.equal(now, saved))      # the weights came back, the optimizer did not
+    # (3) a save that was interrupted between the shards and the state file: shards of step 4, state file of step 1
+    eng.sft_step_tensors(ids, labels)
+    torn = os.path.join(path, "torn")
+    eng.save_checkpoint(torn)
+    eng.parallel_ctx.barrier()
+    if rank == 0:
+        shutil.copy(os.path.join(good, "trainer_state.json"), os.path.join(torn, "trainer_state.json"))
+    eng.parallel_ctx.barrier()
+    out["torn"] = eng.load_checkpoint(torn)
+    # (4) a directory that does not exist
+    out["missing"] = eng.load_checkpoint(os.path.join(path, "nothing-here"))
+    # the ranks are still in step with each other
+    m = eng.sft_step_tensors(ids, labels)
+    out["alive"] = math.isfinite(m.loss)
+    return out
+
+
+def test_checkpoint_restore_is_agreed_between_ranks():
+    with tempfile.TemporaryDirectory() as d:
+        res = run_ranks(_ckpt_agreement_worker, 2, d, timeout=600)
+    for out in res:
+        assert out == {"good": True, "good_exact": True, "lost": False, "lost_moments_kept": True,
+                       "lost_weights_restored": True, "torn": False, "missing": False, "alive": True}, out
