@@ -60,7 +60,9 @@ def _cols(t: torch.Tensor, rank: int, tp: int) -> torch.Tensor:
 
 def load_from_hf_checkpoint(model, path: str, strict=False, parallel_context=None) -> Tuple[int, int]:
     """Copy the weights under ``path`` into ``model`` (any TP rank / PP stage).  Returns
-    ``(loaded, missing)`` parameter counts; missing keys are skipped unless ``strict``.  The reference passes its
+    ``(loaded, missing)`` parameter counts; missing keys are skipped unless ``strict``.  Shapes are checked for every
+    tensor before the first one is copied: a checkpoint of another architecture raises ``ValueError`` naming the tensors
+    and leaves the model as it was.  The reference passes its
     parallel context in third place (src/distributed/tensor_parallel.py:947-1064); here the shard to read follows
     from the model's own layout, so a context given there (or as ``parallel_context``) is accepted and not needed."""
     if not isinstance(strict, bool):
@@ -68,6 +70,7 @@ def load_from_hf_checkpoint(model, path: str, strict=False, parallel_context=Non
     sd = _load_all(path)
     tp, rank = model.tp_size, model.tp_rank
     loaded = missing = 0
+    copies, bad = [], []        # (parameter, tensor) to copy once every shape has been checked
 
     def get(name):
         nonlocal missing
@@ -78,44 +81,54 @@ def load_from_hf_checkpoint(model, path: str, strict=False, parallel_context=Non
                 raise KeyError(f"{name} not found in {path}")
         return t
 
-    def put(param, t):
+    def put(param, t, what=""):
         nonlocal loaded
         if t is None:
             return
-        assert tuple(param.shape) == tuple(t.shape), f"shape mismatch {tuple(param.shape)} vs {tuple(t.shape)}"
-        with torch.no_grad():
-            param.copy_(t.to(param.dtype))
+        if tuple(param.shape) != tuple(t.shape):
+            bad.append(f"{what or 'tensor'}: checkpoint {tuple(t.shape)}, model {tuple(param.shape)}")
+            return
+        copies.append((param, t))
         loaded += 1
 
     if model.embed_tokens is not None:
-        put(model.embed_tokens, get("model.embed_tokens.weight"))
+        put(model.embed_tokens, get("model.embed_tokens.weight"), "model.embed_tokens.weight")
     for i, layer in enumerate(model.layers):
         g = f"model.layers.{model.layer_start + i}."
         q, k, v = get(g + "self_attn.q_proj.weight"), get(g + "self_attn.k_proj.weight"), get(g + "self_attn.v_proj.weight")
         if q is not None and k is not None and v is not None:
-            put(layer.self_attn.qkv_proj.weight, torch.cat([_rows(q, rank, tp), _rows(k, rank, tp), _rows(v, rank, tp)], 0))
+            put(layer.self_attn.qkv_proj.weight, torch.cat([_rows(q, rank, tp), _rows(k, rank, tp), _rows(v, rank, tp)], 0),
+                g + "self_attn.{q,k,v}_proj.weight")
             loaded += 2
         o = get(g + "self_attn.o_proj.weight")
-        put(layer.self_attn.o_proj.weight, None if o is None else _cols(o, rank, tp))
-        put(layer.self_attn.q_norm.weight, get(g + "self_attn.q_norm.weight"))
-        put(layer.self_attn.k_norm.weight, get(g + "self_attn.k_norm.weight"))
+        put(layer.self_attn.o_proj.weight, None if o is None else _cols(o, rank, tp), g + "self_attn.o_proj.weight")
+        put(layer.self_attn.q_norm.weight, get(g + "self_attn.q_norm.weight"), g + "self_attn.q_norm.weight")
+        put(layer.self_attn.k_norm.weight, get(g + "self_attn.k_norm.weight"), g + "self_attn.k_norm.weight")
         gate, up = get(g + "mlp.gate_proj.weight"), get(g + "mlp.up_proj.weight")
         if gate is not None and up is not None:
-            put(layer.mlp.gate_up_proj.weight, torch.cat([_rows(gate, rank, tp), _rows(up, rank, tp)], 0))
+            put(layer.mlp.gate_up_proj.weight, torch.cat([_rows(gate, rank, tp), _rows(up, rank, tp)], 0),
+                g + "mlp.{gate,up}_proj.weight")
             loaded += 1
         down = get(g + "mlp.down_proj.weight")
-        put(layer.mlp.down_proj.weight, None if down is None else _cols(down, rank, tp))
-        put(layer.input_layernorm.weight, get(g + "input_layernorm.weight"))
-        put(layer.post_attention_layernorm.weight, get(g + "post_attention_layernorm.weight"))
+        put(layer.mlp.down_proj.weight, None if down is None else _cols(down, rank, tp), g + "mlp.down_proj.weight")
+        put(layer.input_layernorm.weight, get(g + "input_layernorm.weight"), g + "input_layernorm.weight")
+        put(layer.post_attention_layernorm.weight, get(g + "post_attention_layernorm.weight"),
+            g + "post_attention_layernorm.weight")
     if model.norm is not None:
-        put(model.norm.weight, get("model.norm.weight"))
+        put(model.norm.weight, get("model.norm.weight"), "model.norm.weight")
     if model.lm_head is not None:
         t = sd.get("lm_head.weight")
         if t is None:
             t = sd.get("model.embed_tokens.weight")  # tied checkpoints omit lm_head
         if t is not None and getattr(model, "vocab_parallel", False):
             t = _rows(t, rank, tp)
-        put(model.lm_head, t)
+        put(model.lm_head, t, "lm_head.weight")
+    if bad:
+        raise ValueError(f"{path} does not fit this model ({len(bad)} tensors), nothing was loaded: " + "; ".join(bad[:4])
+                         + (" ..." if len(bad) > 4 else ""))
+    with torch.no_grad():
+        for param, t in copies:
+            param.copy_(t.to(param.dtype))
     return loaded, missing
 
 

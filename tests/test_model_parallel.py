@@ -307,3 +307,36 @@ def test_lora_linear_hands_stacked_gradients_to_the_adapters_parameters():
     for p, wgt in list(zip(params, want))[1:]:
         assert torch.allclose(p.grad, 2 * wgt, atol=1e-4, rtol=1e-4)
     assert torch.allclose(x.grad, 2 * want_x, atol=1e-4)
+
+
+def test_a_checkpoint_of_another_shape_is_refused_whole():
+    """Shapes are checked for every tensor before the first copy: a checkpoint that does not fit raises, names the
+    tensors, and leaves the model bit-identical; a missing key under ``strict`` does the same."""
+    import copy as _copy
+    import os
+    import pytest
+    from safetensors.torch import load_file, save_file
+    with tempfile.TemporaryDirectory() as d:
+        _full_model(d)
+        wider = _copy.deepcopy(CFG)
+        wider.intermediate_size = 128                       # only the MLP tensors differ; the embedding comes first and fits
+        m = ParallelTransformerModel(wider)
+        m.init_weights(11)
+        before = [p.detach().clone() for p in m.parameters()]
+        with pytest.raises(ValueError, match=r"mlp\.\{gate,up\}_proj\.weight.*nothing was loaded|nothing was loaded.*mlp"):
+            load_from_hf_checkpoint(m, d)
+        assert all(torch.equal(a, b) for a, b in zip(before, m.parameters()))
+        # strict and a key missing from the file
+        f = os.path.join(d, "model.safetensors")
+        sd = load_file(f)
+        del sd["model.layers.1.self_attn.o_proj.weight"]
+        save_file(sd, f)
+        fit = ParallelTransformerModel(CFG)
+        fit.init_weights(12)
+        before = [p.detach().clone() for p in fit.parameters()]
+        with pytest.raises(KeyError):
+            load_from_hf_checkpoint(fit, d, strict=True)
+        assert all(torch.equal(a, b) for a, b in zip(before, fit.parameters()))
+        loaded, missing = load_from_hf_checkpoint(fit, d)                  # tolerant: everything else is loaded
+        assert missing == 1 and torch.equal(fit.layers[1].self_attn.o_proj.weight, before[[n for n, _ in fit.named_parameters()].index("layers.1.self_attn.o_proj.weight")])
+        assert not torch.equal(fit.layers[0].self_attn.o_proj.weight, before[[n for n, _ in fit.named_parameters()].index("layers.0.self_attn.o_proj.weight")])
