@@ -874,9 +874,14 @@ class TrainEngine:
         if not read_ok:
             return False
         if has_w:
-            with self.optimizer.eval_mode():
-                load_from_hf_checkpoint(self.model, path)
-                self.optimizer.refresh_masters_from_params()
+            try:
+                with self.optimizer.eval_mode():
+                    load_from_hf_checkpoint(self.model, path)
+                    self.optimizer.refresh_masters_from_params()
+            except (ValueError, KeyError, OSError) as e:
+                # every rank reads the same files and fails alike (the loader copies nothing unless all shapes fit)
+                logger.warning("load_checkpoint(%s): weights not restored: %s", path, e)
+                return False
         if has_l:
             load_lora_state_dict(self.model, got["lora"])
             self.optimizer.refresh_masters_from_params()
