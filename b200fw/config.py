@@ -192,10 +192,56 @@ def _flatten(d: Dict[str, Any], prefix: str = "") -> Dict[str, Any]:
     return out
 
 
+_BOOL_WORDS = {"true": True, "yes": True, "on": True, "1": True, "false": False, "no": False, "off": False, "0": False}
+
+
+def _coerce(value, kind: str, where: str):
+    """Bring a YAML / command-line value to the type of its field (named by the dataclass annotation).  YAML reads
+    ``1e-5`` (no dot) as a string and ``2.0`` as a float: both are what the user meant for a float / an int field, so
+    they are converted; anything that does not convert raises ``ValueError`` naming the key."""
+    kind = kind.replace("Optional[", "").rstrip("]") if kind.startswith("Optional[") else kind
+    try:
+        if kind == "float" and not isinstance(value, bool):
+            if isinstance(value, (int, float, str)):
+                return float(value)
+        elif kind == "int" and not isinstance(value, bool):
+            if isinstance(value, int):
+                return value
+            f = float(value)
+            if f == int(f):
+                return int(f)
+            raise ValueError("not a whole number")
+        elif kind == "bool":
+            if isinstance(value, bool):
+                return value
+            if isinstance(value, (int, str)) and str(value).strip().lower() in _BOOL_WORDS:
+                return _BOOL_WORDS[str(value).strip().lower()]
+        elif kind == "str":
+            if isinstance(value, (str, int, float)) and not isinstance(value, bool):
+                return str(value)
+        elif kind.startswith("List["):
+            if isinstance(value, (list, tuple)):
+                return list(value)
+            if isinstance(value, str):
+                return [v.strip() for v in value.split(",") if v.strip()]
+        else:
+            return value                        # a type this function does not know: leave it to the consumer
+    except (TypeError, ValueError) as e:
+        raise ValueError(f"{where}: {value!r} is not a valid {kind} ({e})") from None
+    raise ValueError(f"{where}: {value!r} is not a valid {kind}")
+
+
+def _field_kinds(cls) -> Dict[str, str]:
+    import dataclasses
+    return {f.name: (f.type if isinstance(f.type, str) else getattr(f.type, "__name__", str(f.type)))
+            for f in dataclasses.fields(cls)}
+
+
 def build_colocate_config(yaml_cfg: Dict[str, Any], overrides: Optional[Dict[str, Any]] = None
                           ) -> Tuple[ColocateConfig, List[str]]:
     """Returns the config and the list of YAML keys that were not understood."""
     cfg = ColocateConfig()
+    kinds = _field_kinds(ColocateConfig)
     known = {p for p, _ in _YAML_MAP}
     mode = get_nested(yaml_cfg, "training.mode", cfg.training_mode)
     for path, name in _YAML_MAP:
@@ -203,19 +249,19 @@ def build_colocate_config(yaml_cfg: Dict[str, Any], overrides: Optional[Dict[str
             continue
         v = get_nested(yaml_cfg, path)
         if v is not None:
-            setattr(cfg, name, v)
+            setattr(cfg, name, _coerce(v, kinds.get(name, ""), path))
     for key, name in (("max_tokens", "max_tokens"), ("temperature", "temperature"), ("top_p", "top_p"),
                       ("enabled", "inference_preview_enabled")):
         known.add(f"inference_preview.{key}")
         v = get_nested(yaml_cfg, f"inference_preview.{key}")
         # SFT previews read their sampling knobs from inference_preview.*; GRPO reads rollout.*
         if v is not None and (mode == "sft" or key == "enabled"):
-            setattr(cfg, name, v)
+            setattr(cfg, name, _coerce(v, kinds.get(name, ""), f"inference_preview.{key}"))
     for k, v in (overrides or {}).items():
         if v is not None:
             if not hasattr(cfg, k):
                 raise KeyError(f"unknown override {k!r}")
-            setattr(cfg, k, v)
+            setattr(cfg, k, _coerce(v, kinds.get(k, ""), f"override {k}"))
     unknown = sorted(k for k in _flatten(yaml_cfg) if k not in known and k not in _DOCUMENTATION_ONLY)
     return cfg, unknown
 
@@ -223,6 +269,15 @@ def build_colocate_config(yaml_cfg: Dict[str, Any], overrides: Optional[Dict[str
 def validate_parallel_config(cfg: ColocateConfig, world_size: Optional[int] = None) -> None:
     """The reference's checks (scripts/run_colocate.py:86-136), raising ValueError with the reason."""
     world = world_size if world_size is not None else int(os.environ.get("WORLD_SIZE", "1"))
+    for name, least in (("pp_size", 1), ("tp_size", 1), ("dp_size", 1), ("num_micro_batches", 1), ("batch_size", 1),
+                        ("gradient_accumulation_steps", 1), ("max_seq_len", 2), ("lora_rank", 0), ("zero_stage", 0)):
+        v = getattr(cfg, name, least)
+        if not isinstance(v, int) or isinstance(v, bool) or v < least:
+            raise ValueError(f"{name} must be an integer >= {least}, not {v!r}")
+    if not cfg.learning_rate >= 0 or cfg.learning_rate == float("inf"):
+        raise ValueError(f"learning_rate must be a finite number >= 0, not {cfg.learning_rate!r}")
+    if cfg.zero_stage > 3:
+        raise ValueError(f"zero_stage must be 0, 1, 2 or 3, not {cfg.zero_stage}")
     if cfg.pp_size * cfg.tp_size * cfg.dp_size != world:
         raise ValueError(f"pp({cfg.pp_size}) * tp({cfg.tp_size}) * dp({cfg.dp_size}) != WORLD_SIZE({world})")
     if cfg.num_micro_batches < cfg.pp_size:

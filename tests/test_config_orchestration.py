@@ -79,6 +79,32 @@ def test_parallel_validation_rules():
             validate_parallel_config(c, world if "tp_size" not in bad else 16)
 
 
+def test_yaml_values_are_brought_to_their_field_types(tmp_path):
+    """YAML reads ``1e-5`` (no dot) as a string and ``8.0`` as a float; command lines hand over strings.  Each value is
+    converted to its field's type, and one that cannot be is refused with the key in the message."""
+    y = tmp_path / "c.yaml"
+    y.write_text("training:\n  learning_rate: 1e-5\n  batch_size: 8.0\n  mode: sft\n"
+                 "runtime:\n  tp_size: '2'\n  sequence_parallel: 'yes'\n"
+                 "lora:\n  target_modules: q_proj, v_proj\n  rank: 0\n")
+    cfg, unknown = build_colocate_config(load_yaml_config(str(y)), overrides={"max_grad_norm": "0.5", "dp_size": "1"})
+    assert unknown == []
+    assert cfg.learning_rate == 1e-5 and isinstance(cfg.learning_rate, float)
+    assert cfg.batch_size == 8 and isinstance(cfg.batch_size, int)
+    assert cfg.tp_size == 2 and cfg.sequence_parallel is True and cfg.max_grad_norm == 0.5 and cfg.dp_size == 1
+    assert cfg.lora_target_modules == ["q_proj", "v_proj"] and cfg.lora_rank == 0
+    for text, key in (("training:\n  learning_rate: fast\n", "training.learning_rate"),
+                      ("training:\n  batch_size: 2.5\n", "training.batch_size"),
+                      ("runtime:\n  sequence_parallel: maybe\n", "runtime.sequence_parallel"),
+                      ("runtime:\n  tp_size: [2]\n", "runtime.tp_size")):
+        y.write_text(text)
+        with pytest.raises(ValueError, match=key.replace(".", r"\.")):
+            build_colocate_config(load_yaml_config(str(y)))
+    for bad in (dict(tp_size=0), dict(batch_size=0), dict(gradient_accumulation_steps=0), dict(learning_rate=float("nan")),
+                dict(learning_rate=-1.0), dict(zero_stage=4), dict(lora_rank=-1), dict(max_seq_len=1)):
+        with pytest.raises(ValueError, match=next(iter(bad))):
+            validate_parallel_config(ColocateConfig(**bad), 1)
+
+
 def test_every_shipped_config_parses_and_validates():
     n = 0
     for f in glob.glob(os.path.join(ROOT, "configs", "**", "*.yaml"), recursive=True):
