@@ -17,6 +17,7 @@ from __future__ import annotations
 import asyncio
 import csv
 import enum
+import json
 import math
 import os
 import time
@@ -103,6 +104,8 @@ class ColocateOrchestrator:
         self.state_log: List[str] = []
         self.weights_version = 0
         self._batches = None
+        self.start_iteration = 0        # > 0 after a resume from a checkpoint that recorded its iteration
+        self._skip_batches = 0          # batches the resumed run's completed iterations had consumed
         self._pool = ThreadPoolExecutor(max_workers=1)
         self._rollout_stream = None
         self._tp_exchange_group = None
@@ -142,6 +145,8 @@ class ColocateOrchestrator:
         if cfg.resume_from:
             ok = eng.load_checkpoint(cfg.resume_from)
             logger.info("resume from %s: %s", cfg.resume_from, "ok" if ok else "failed")
+            if ok:
+                self._resume_position(cfg.resume_from)
         # ---- data + reward ----------------------------------------------------------------------------------
         if self.data is None:
             if cfg.synthetic_data:
@@ -252,7 +257,41 @@ class ColocateOrchestrator:
         return m
 
     # =================================================================================================
+    def _resume_position(self, path: str):
+        """Continue the run where the checkpoint left it: ``orchestrator_state.json`` (written by
+        :meth:`_save_checkpoint`) names the iterations that were complete; the loop starts after them and the data
+        stream skips the batches they consumed, so a resumed run sees the batches the uninterrupted one would have.  A
+        checkpoint without that file (one made by ``TrainEngine.save_checkpoint`` alone, or by the reference), or one
+        that already covers ``total_iterations``, restores the engine only and the loop runs from iteration 0, as the
+        reference's does
+        (src/orchestrator/colocate_orchestrator.py:267-272)."""
+        f = os.path.join(path, "orchestrator_state.json")
+        if not os.path.exists(f):
+            return
+        try:
+            with open(f) as fh:
+                st = json.load(fh)
+            done = int(st.get("iterations_completed", 0))
+        except (OSError, ValueError, TypeError) as e:
+            logger.warning("resume: %s is unreadable (%s): starting at iteration 0", f, e)
+            return
+        if done >= self.config.total_iterations:
+            # the checkpoint of a finished (or longer) run: a warm start, ``total_iterations`` more from its weights
+            logger.info("resume: the checkpoint covers %d iterations (total_iterations is %d): warm start, the loop "
+                        "runs from iteration 0", done, self.config.total_iterations)
+            return
+        self.start_iteration = max(0, done)
+        self._skip_batches = max(0, int(st.get("batches_consumed", done)))
+        self.weights_version = int(st.get("weights_version", 0))
+        logger.info("resume: continuing at iteration %d of %d", self.start_iteration, self.config.total_iterations)
+
     def _next_batch(self) -> GRPOBatch:
+        while self._skip_batches > 0:           # resumed run: pass over what the completed iterations consumed
+            self._skip_batches -= 1
+            self._next_batch_raw()
+        return self._next_batch_raw()
+
+    def _next_batch_raw(self) -> GRPOBatch:
         if self._batches is None:
             self._batches = iter(self.data.get_batches(self._per_rank_batch()))
         try:
@@ -390,9 +429,9 @@ class ColocateOrchestrator:
             return await self._run_staged()
         loop = asyncio.get_running_loop()
         pending: Optional[asyncio.Future] = None
-        if cfg.eval_num_prompts > 0:
+        if cfg.eval_num_prompts > 0 and self.start_iteration == 0:
             self._do_eval("before")
-        for it in range(cfg.total_iterations):
+        for it in range(self.start_iteration, cfg.total_iterations):
             im = IterationMetrics(it)
             t_iter = time.perf_counter()
             try:
@@ -472,7 +511,7 @@ class ColocateOrchestrator:
             self.metrics.append(im)
             self._record(im)
             if cfg.checkpoint_save_enabled and cfg.checkpoint_save_interval > 0 and (it + 1) % cfg.checkpoint_save_interval == 0:
-                self._save_checkpoint(f"iter_{it + 1}")
+                self._save_checkpoint(f"iter_{it + 1}", it + 1)
             if cfg.memory_profile_interval > 0 and (it + 1) % cfg.memory_profile_interval == 0:
                 self.memory.snapshot(f"iter_{it + 1}")
         if pending is not None:
@@ -483,7 +522,7 @@ class ColocateOrchestrator:
         if cfg.eval_num_prompts > 0:
             self._do_eval("after")
         if cfg.checkpoint_save_enabled:
-            self._save_checkpoint("final")
+            self._save_checkpoint("final", max(self.start_iteration, cfg.total_iterations))
         self._set_state(OrchestratorState.DONE)
         self._write_final_artifacts()
         return self.metrics
@@ -572,7 +611,7 @@ class ColocateOrchestrator:
         cfg = self.config
         import inspect
         sync_takes_iteration = len(inspect.signature(self._do_weight_sync).parameters) > 0
-        for it in range(cfg.total_iterations):
+        for it in range(self.start_iteration, cfg.total_iterations):
             im = IterationMetrics(it)
             t_iter = time.perf_counter()
             try:
@@ -716,10 +755,21 @@ class ColocateOrchestrator:
             self.artifacts.write_json("fixed_prompt_comparison.json", {"samples": rows})
         return metrics
 
-    def _save_checkpoint(self, tag: str):
+    def _save_checkpoint(self, tag: str, iterations_completed: Optional[int] = None):
+        """The engine's checkpoint under ``tag`` and ``latest``, plus (rank 0) ``orchestrator_state.json``: how many
+        iterations are complete, so that ``resume_from`` continues the loop and the data stream from there.  Every
+        iteration draws one batch; a rollout prefetched for the next iteration is not counted (a resumed run draws
+        it again)."""
         base = self.config.checkpoint_save_dir
+        done = iterations_completed if iterations_completed is not None else len(self.metrics) + self.start_iteration
         for name in (tag, "latest"):
-            self.train_engine.save_checkpoint(os.path.join(base, name))
+            d = os.path.join(base, name)
+            self.train_engine.save_checkpoint(d)
+            if self.train_engine.parallel_ctx.global_rank == 0:
+                self.train_engine._atomic_save({"iterations_completed": done, "batches_consumed": done,
+                                                "weights_version": self.weights_version},
+                                               os.path.join(d, "orchestrator_state.json"), as_json=True)
+        self.train_engine.parallel_ctx.barrier()
         self._last_checkpoint_path = os.path.join(base, tag)
 
     @property

@@ -715,3 +715,43 @@ def test_flat_adapter_state_takes_the_same_path_as_a_dict_of_tensors():
     buf.swap_buffers()
     act = buf.get_active_state()
     assert torch.allclose(act["a.lora_A"], s0["a.lora_A"] + 1) and torch.equal(act["new.lora_A"], torch.ones(2, 2))
+
+
+def test_resume_continues_the_loop_and_the_data_stream_where_the_checkpoint_left_them():
+    """An SFT run interrupted after 2 of 4 iterations and resumed from ``iter_2`` produces, in iterations 2 and 3, the
+    losses of the run that was never interrupted: the loop index, the data position, the weights, the optimizer
+    moments and the learning-rate schedule all come back.  A checkpoint without the orchestrator's state file restores
+    the engine only."""
+    with tempfile.TemporaryDirectory() as d:
+        common = dict(training_mode="sft", total_iterations=4, max_tokens=6, batch_size=2, inference_preview_enabled=False,
+                      lr_scheduler_type="cosine", learning_rate=2e-3)
+        whole, _ = _run(_tiny_cfg(os.path.join(d, "a"), checkpoint_save_enabled=False, **common))
+        want = [m.train_metrics.loss for m in whole.metrics]
+        assert len(want) == 4 and len(set(want)) == 4
+        # the interrupted run: same schedule (total 4), stopped after iteration 2 by its checkpoint interval
+        first_cfg = _tiny_cfg(os.path.join(d, "b"), checkpoint_save_interval=2, **common)
+        first = ColocateOrchestrator(first_cfg)
+
+        async def two_then_stop():
+            await first.initialize()
+            real = first._save_checkpoint
+
+            def stop_after(tag, done=None):
+                real(tag, done)
+                if tag == "iter_2":
+                    raise KeyboardInterrupt           # the process dies right after the checkpoint
+            first._save_checkpoint = stop_after
+            await first.run()
+        with pytest.raises(KeyboardInterrupt):
+            asyncio.run(two_then_stop())
+        ck = os.path.join(first_cfg.checkpoint_save_dir, "iter_2")
+        st = json.load(open(os.path.join(ck, "orchestrator_state.json")))
+        assert st["iterations_completed"] == 2
+        resumed, _ = _run(_tiny_cfg(os.path.join(d, "c"), resume_from=ck, checkpoint_save_enabled=False, **common))
+        assert resumed.start_iteration == 2 and [m.iteration for m in resumed.metrics] == [2, 3]
+        got = [m.train_metrics.loss for m in resumed.metrics]
+        assert got == pytest.approx(want[2:], rel=1e-6), (got, want)
+        # without the state file: engine restored, loop from 0
+        os.remove(os.path.join(ck, "orchestrator_state.json"))
+        plain, _ = _run(_tiny_cfg(os.path.join(d, "e"), resume_from=ck, checkpoint_save_enabled=False, **common))
+        assert plain.start_iteration == 0 and len(plain.metrics) == 4 and plain.train_engine.step_count > 4
