@@ -216,13 +216,19 @@ class DisaggOrchestrator:
         K = cfg.num_samples_per_prompt
         return {j: [o or [0] for o in outs[n * K:(n + 1) * K]] for n, j in enumerate(mine)}
 
-    def _exchange_samples(self, local: Optional[Dict[int, List[List[int]]]]) -> Dict[int, List[List[int]]]:
-        """Rollout ranks publish their samples; everyone ends up with the full set (token id lists)."""
+    def _exchange_samples(self, local: Optional[Dict[int, List[List[int]]]],
+                          error: Optional[str] = None) -> Dict[int, List[List[int]]]:
+        """Rollout ranks publish their samples; everyone ends up with the full set (token id lists).  A rank whose
+        phase failed publishes the error instead, and every rank raises it here, together: nobody is left waiting in
+        a later collective for a rank that has gone."""
         box = [None] * self.world
-        dist.all_gather_object(box, local or {})
+        dist.all_gather_object(box, {"samples": local or {}, "error": error})
+        failed = [(r, d["error"]) for r, d in enumerate(box) if d["error"]]
+        if failed:
+            raise RuntimeError("; ".join(f"rank {r} failed before the sample exchange: {e}" for r, e in failed))
         merged: Dict[int, List[List[int]]] = {}
         for d in box:
-            merged.update(d)
+            merged.update(d["samples"])
         return merged
 
     def _train(self, prompts, samples) -> float:
@@ -280,7 +286,12 @@ class DisaggOrchestrator:
             span_train, span_roll = [float("inf"), float("-inf")], [float("inf"), float("-inf")]
             t0 = time.perf_counter()
             w0 = time.time()
-            local = self._rollout_share(prompts) if (not self.is_trainer and do_rollout) else None
+            local, failure = None, None
+            try:
+                local = self._rollout_share(prompts) if (not self.is_trainer and do_rollout) else None
+            except Exception as e:  # noqa: BLE001 - carried to every rank by the sample exchange
+                logger.error("rollout failed on rank %d: %r", self.rank, e)
+                failure = f"{type(e).__name__}: {e}"
             if not self.is_trainer:
                 m.rollout_time = time.perf_counter() - t0
                 if do_rollout:
@@ -292,10 +303,10 @@ class DisaggOrchestrator:
                     m.loss = self._train(*prev)
                     m.train_time = time.perf_counter() - t1
                     span_train = [w1, time.time()]
-                samples = self._exchange_samples(local)
+                samples = self._exchange_samples(local, failure)
                 prev = (prompts, samples) if do_rollout else None
             else:
-                samples = self._exchange_samples(local)
+                samples = self._exchange_samples(local, failure)
                 if self.is_trainer:
                     t1 = time.perf_counter()
                     w1 = time.time()

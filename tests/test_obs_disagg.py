@@ -179,6 +179,7 @@ def _disagg_worker(rank, world, mode):
     from b200fw.orch import DisaggConfig, DisaggOrchestrator
     from b200fw.train import TrainConfig, TrainEngine
     dist.init_process_group("gloo", rank=rank, world_size=world)
+    mode_arg = mode
     use_data = mode.endswith("+data")
     mode = mode.split("+")[0]
     mc = ModelConfig(vocab_size=320 if use_data else 128, hidden_size=32, num_layers=2, num_heads=2, num_kv_heads=2, head_dim=16,
@@ -208,6 +209,22 @@ def _disagg_worker(rank, world, mode):
         recs = [{"question": f"{i}+1?", "answer": f"#### {i + 1}"} for i in range(16)]
         data = GSM8KDataPipeline(records=recs, prompt_template="plain", max_prompt_tokens=8)
     o = DisaggOrchestrator(cfg, trainer, engine, data=data).initialize()
+    if mode_arg.endswith("+fail"):
+        # the last rank's engine breaks in the second iteration: every rank must leave the loop with that error
+        if rank == world - 1:
+            real, calls = o.infer_engine.generate, []
+
+            def broken(*a, **k):
+                calls.append(1)
+                if len(calls) == 2:
+                    raise ValueError("engine lost its KV pool")
+                return real(*a, **k)
+            o.infer_engine.generate = broken
+        try:
+            o.run()
+        except RuntimeError as e:
+            return {"error": str(e), "iterations": len(o.metrics)}
+        return {"error": None, "iterations": len(o.metrics)}
     o.run()
     s = o.get_summary()
     if use_data:
@@ -244,3 +261,13 @@ def test_disaggregated_loop_two_trainers_two_engines():
         assert res[0]["final_loss"] is not None
         # overlap: back-to-back phases hide nothing; pipelined phases hide the shorter one
         assert (res[0]["avg_overlap_ratio"] == 0.0) == (mode == "sequential"), (mode, res[0]["avg_overlap_ratio"])
+
+
+def test_a_failed_rollout_rank_ends_the_loop_on_every_rank_with_its_error():
+    """One rollout rank's engine raises in the second iteration.  The error travels with the sample exchange: every
+    rank raises it at the same point of the same iteration, none is left waiting in a collective."""
+    from _dist_util import run_ranks
+    for mode in ("sequential+fail", "pipeline+fail"):
+        res = run_ranks(_disagg_worker, 4, mode, timeout=300)
+        assert all(r["error"] and "rank 3 failed" in r["error"] and "KV pool" in r["error"] for r in res), res
+        assert {r["iterations"] for r in res} == {1}, res
