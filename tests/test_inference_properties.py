@@ -123,9 +123,10 @@ WORKLOAD = st.lists(st.tuples(st.integers(1, 70), st.integers(1, 24), st.boolean
 
 @settings(max_examples=40, deadline=None, suppress_health_check=[HealthCheck.too_slow, HealthCheck.function_scoped_fixture])
 @given(WORKLOAD, st.integers(0, 3), st.sampled_from([8, 16, 48]), st.sampled_from(["none", "hash", "radix"]), st.booleans(),
-       st.sampled_from([2, 3, 256]), st.sampled_from([0, 0, 2, 4]), st.sets(st.integers(1, 60), max_size=3))
+       st.sampled_from([2, 3, 256]), st.sampled_from([0, 0, 2, 4]), st.sets(st.integers(1, 60), max_size=3),
+       st.sampled_from([100, 100, 1, 0]))
 def test_paged_engine_equals_eager_oracle_under_memory_pressure(model, workload, slack, chunk, cache, late, max_seqs, spec_k,
-                                                                update_at):
+                                                                update_at, staleness):
     """Random prompts (some sharing a 32-token prefix), a block pool barely larger than the largest single request
     (so running sequences get preempted and recomputed), small prefill chunks, no / hash / radix prefix cache, read-back one
     step late or not, greedy speculative decoding with a one-layer draft or none: outputs must equal the eager full-recompute oracle, and every block must come back."""
@@ -145,7 +146,7 @@ def test_paged_engine_equals_eager_oracle_under_memory_pressure(model, workload,
                   enable_prefix_caching=cache != "none",
                   max_cached_blocks=blocks, async_decode="force" if late else False, adaptive_chunking=False,
                   max_num_sequences=max_seqs, speculative_enabled=spec_k > 0, speculative_num_tokens=max(1, spec_k),
-                  speculative_draft_layers=1, max_weight_staleness=100)
+                  speculative_draft_layers=1, max_weight_staleness=staleness)
     for i, (p, o) in enumerate(zip(prompts, outs)):
         eng.add_request(f"r{i}", p, o)
     steps = 0
@@ -155,10 +156,18 @@ def test_paged_engine_equals_eager_oracle_under_memory_pressure(model, workload,
         if steps in update_at:
             eng.on_weights_updated()
         assert steps < 5000, "the engine stopped making progress"
-    assert eng.stats.get("aborted_stale", 0) == 0
+    dropped = eng.stats.get("aborted_stale", 0)
+    assert dropped == 0 or staleness < 100
     got = [eng.finished[f"r{i}"].output_tokens for i in range(len(prompts))]
+    short = 0
     for i, (a, b) in enumerate(zip(got, want)):
-        assert list(a) == list(b), (i, prompts[i][:6], a, b)
+        assert -1 not in a, "a placeholder of the one-step-late decode left the engine"
+        if len(a) < len(b):
+            short += 1
+            assert list(a) == list(b[:len(a)]), (i, a, b)
+        else:
+            assert list(a) == list(b), (i, prompts[i][:6], a, b)
+    assert short <= dropped
     # every block is back in the pool except those the prefix cache still references; evicting them frees the rest
     if eng.prefix_cache is not None:
         eng.prefix_cache.evict_lru(blocks)
