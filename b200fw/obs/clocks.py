@@ -16,14 +16,15 @@ class ClockSampler:
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
-        self.index, self.samples, self.proc = index, [], None
+        self.index, self.samples, self.proc, self._reader = index, [], None, None
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
                  "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            threading.Thread(target=self._read, daemon=True).start()
+            self._reader = threading.Thread(target=self._read, daemon=True)
+            self._reader.start()
         except OSError:
             self.proc = None
 
@@ -39,9 +40,11 @@ class ClockSampler:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
+        if self._reader is not None:
+            self._reader.join(timeout=2)        # lines still in the pipe when the sampler ended count too
         sm, mx, reasons = [], None, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for s in self.samples:
+        for s in list(self.samples):
             parts = [p.strip() for p in s.split(",")]
             if len(parts) < 6:
                 continue

@@ -271,3 +271,35 @@ def test_a_failed_rollout_rank_ends_the_loop_on_every_rank_with_its_error():
         res = run_ranks(_disagg_worker, 4, mode, timeout=300)
         assert all(r["error"] and "rank 3 failed" in r["error"] and "KV pool" in r["error"] for r in res), res
         assert {r["iterations"] for r in res} == {1}, res
+
+
+def test_clock_sampler_reads_the_median_clock_and_the_active_reasons(tmp_path, monkeypatch):
+    """The sampler against a stand-in ``nvidia-smi`` (a script on PATH that prints the query's CSV lines): the median SM
+    clock, the maximum, the reasons that were active in any sample; malformed lines are passed over; without the tool
+    the summary says so.  Nothing of the GPU's state is written by the sampler: it only runs the query."""
+    import os
+    import stat
+    import time
+    from b200fw.obs.clocks import ClockSampler, clocks_during
+    fake = tmp_path / "nvidia-smi"
+    fake.write_text("#!/bin/sh\n"
+                    "case \"$*\" in *--query-gpu=clocks.sm,clocks.max.sm*-lms*) ;; *) echo unexpected args >&2; exit 3;; esac\n"
+                    "echo '1300, 1965, Not Active, Not Active, Not Active, Active'\n"
+                    "echo '[N/A], 1965, Not Active, Not Active, Not Active, Not Active'\n"
+                    "echo 'garbage'\n"
+                    "echo '1900, 1965, Not Active, Not Active, Not Active, Not Active'\n"
+                    "echo '1400, 1965, Not Active, Active, Not Active, Active'\n"
+                    "sleep 30\n")
+    fake.chmod(fake.stat().st_mode | stat.S_IEXEC)
+    monkeypatch.setenv("PATH", f"{tmp_path}{os.pathsep}{os.environ['PATH']}")
+    with clocks_during(0) as c:
+        deadline = time.time() + 5
+        while len(c.sampler.samples) < 5 and time.time() < deadline:
+            time.sleep(0.02)
+    assert c.summary == {"sm_mhz": 1400.0, "sm_max_mhz": 1965.0, "reasons": ["hw_thermal_slowdown", "sw_power_cap"],
+                         "samples": 3}
+    assert c.sampler.proc.poll() is not None                    # the child it started is gone
+    monkeypatch.setenv("PATH", str(tmp_path / "empty"))
+    s = ClockSampler(0)
+    s.start()
+    assert s.stop() == {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
