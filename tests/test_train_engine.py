@@ -380,3 +380,42 @@ def test_checkpoint_restore_is_agreed_between_ranks():
     for out in res:
         assert out == {"good": True, "good_exact": True, "lost": False, "lost_moments_kept": True,
                        "lost_weights_restored": True, "torn": False, "missing": False, "alive": True}, out
+
+
+def test_lora_delta_export_sequence_logprobs_and_closing_a_window_early():
+    """Three entry points the orchestration layer relies on: ``export_lora_delta`` (full state first, then exactly the
+    change since the previous export), ``compute_sequence_log_probs`` (mean response log-prob, equal to a plain
+    log-softmax evaluation) and ``close_accumulation_window`` (the optimizer step over however many micro-batches have
+    accumulated; nothing when none has)."""
+    from b200fw.model import get_lora_state_dict
+    cfg = TrainConfig(model_config=SMALL, lora_rank=4, lora_alpha=8.0, grpo_beta=0.0, gradient_accumulation_steps=4,
+                      zero_stage=1, use_amp=False, amp_dtype="fp32", warmup_steps=0, max_seq_len=32, learning_rate=1e-2)
+    eng = TrainEngine(cfg).initialize()
+    assert 0 < eng.trainable_params_count < eng.total_params_count
+    first = eng.export_lora_delta()
+    state0 = {k: v.clone() for k, v in get_lora_state_dict(eng.model).items()}
+    assert first.keys() == state0.keys() and all(torch.equal(first[k], state0[k]) for k in first)
+    assert all(float(v.abs().max()) == 0.0 for v in eng.export_lora_delta().values())      # nothing changed since
+    # nothing pending: closing the window is a no-op
+    m0 = eng.close_accumulation_window()
+    assert m0.grad_norm == 0.0 and eng.step_count == 0
+    # two of four micro-batches, then close: one optimizer step over the two
+    P, R = [[3, 4, 5], [6, 7]], [[8, 9, 10], [11, 12]]
+    eng.sft_step(P, R)
+    eng.sft_step(P, R)
+    assert eng.step_count == 0 and eng._accumulation_count == 2
+    m = eng.close_accumulation_window()
+    assert eng.step_count == 1 and eng._accumulation_count == 0 and m.grad_norm > 0
+    delta = eng.export_lora_delta()
+    state1 = get_lora_state_dict(eng.model)
+    assert any(float(v.abs().max()) > 0 for v in delta.values())
+    for k in delta:
+        assert torch.allclose(state0[k] + delta[k], state1[k], atol=1e-7)
+    # sequence log-probs against a plain evaluation
+    got = eng.compute_sequence_log_probs(P, R)
+    for i, (p, r) in enumerate(zip(P, R)):
+        ids = torch.tensor([p + r])
+        with eng.optimizer.eval_mode():
+            lp = torch.log_softmax(eng.model(ids).float(), -1)[0].detach()
+        want = sum(float(lp[len(p) - 1 + j, t]) for j, t in enumerate(r)) / len(r)
+        assert abs(float(got[i]) - want) < 1e-4, (i, float(got[i]), want)
