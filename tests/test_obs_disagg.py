@@ -303,3 +303,59 @@ def test_clock_sampler_reads_the_median_clock_and_the_active_reasons(tmp_path, m
     s = ClockSampler(0)
     s.start()
     assert s.stop() == {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+
+
+def test_compute_profiler_layer_timing_and_memory_manager_thresholds(monkeypatch):
+    """Per-layer timing (context manager and forward hooks on the top-level layers of a model), its report / summary /
+    reset; the memory manager's warn / critical thresholds against a stand-in for the device's free-memory query (a
+    critical reading empties the allocator's cache and the reserve can be handed back exactly once)."""
+    import time
+    import torch
+    from b200fw.model import ModelConfig, ParallelTransformerModel
+    from b200fw.obs import ComputeProfiler, MemoryManager
+    prof = ComputeProfiler()
+    with prof.profile_layer("sleep"):
+        time.sleep(0.01)
+    assert prof.layer_ms["sleep"][0] >= 9.0
+    off = ComputeProfiler(enabled=False)
+    with off.profile_layer("x"):
+        pass
+    assert not off.layer_ms
+    mc = ModelConfig(vocab_size=64, hidden_size=32, num_layers=2, num_heads=2, num_kv_heads=2, head_dim=16,
+                     intermediate_size=48, max_position_embeddings=64, tie_word_embeddings=True)
+    m = ParallelTransformerModel(mc)
+    m.init_weights(0)
+    ids = torch.randint(0, 64, (2, 16))
+    means = prof.profile_model(m, lambda: m(ids), warmup=1, iters=2)
+    assert {"layers.0", "layers.1", "norm"} <= set(means) and all(v > 0 for v in means.values())
+    assert "sleep" not in means                                      # the warm-up cleared earlier samples
+    assert all(len(v) == 2 for v in prof.layer_ms.values())         # warm-up runs are not counted
+    assert not m.layers[0]._forward_hooks and not m.layers[0]._forward_pre_hooks      # hooks removed again
+    rep = prof.report()
+    assert "layers.0" in rep and "%" in rep
+    summ = prof.get_summary()
+    assert summ["layers"]["layers.1"]["count"] == 2 and summ["peak_tflops"] == prof.peak_tflops
+    assert {p.layer_name for p in prof.layer_profiles} == set(means)
+    prof.reset()
+    assert not prof.layer_ms and prof.report().count("\n") == 1
+    # ---- memory manager ----
+    mm = MemoryManager(warn=0.5, critical=0.8)
+    assert mm.check() == "ok" or torch.cuda.is_available()          # no device: utilisation reads 0
+    free = {"v": 90}
+    emptied = []
+    monkeypatch.setattr(torch.cuda, "mem_get_info", lambda dev=None: (free["v"], 100))
+    monkeypatch.setattr(torch.cuda, "empty_cache", lambda: emptied.append(1))
+    mm.enabled = True
+    assert mm.check() == "ok" and not mm.events
+    free["v"] = 40
+    assert mm.check() == "warn" and mm.events == ["warn 0.600"] and not emptied
+    free["v"] = 10
+    assert mm.check() == "critical" and mm.events[-1] == "critical 0.900" and emptied == [1]
+    mm._reserve = object()
+    assert mm.release_reserve() is True and mm.release_reserve() is False and len(emptied) == 3
+    ref_form = MemoryManager("cpu", warning_threshold=0.7, critical_threshold=0.9)
+    assert (ref_form.warn, ref_form.critical) == (0.7, 0.9)
+    ref_form.enabled = False
+    assert ref_form.get_stats() == {} and ref_form.check_memory_pressure()["utilization"] == 0
+    ref_form.reserve_buffer(1)
+    ref_form.release_buffer()
