@@ -620,6 +620,9 @@ class ColocateOrchestrator:
                 t0 = time.perf_counter()
                 responses = await self._do_inference(batch)
                 im.state_durations["inferring"] = time.perf_counter() - t0
+                if not isinstance(next((r for g in responses for r in g), None), str):      # token ids, not text
+                    im.tokens_generated = sum(len(r) for g in responses for r in g)
+                    im.tokens_trained = sum(len(p) + len(r) for p, g in zip(batch.prompt_tokens, responses) for r in g)
                 self._set_state(OrchestratorState.REWARDING)
                 t0 = time.perf_counter()
                 rewards = self._stage_rewards(batch, responses)

@@ -755,3 +755,44 @@ def test_resume_continues_the_loop_and_the_data_stream_where_the_checkpoint_left
         os.remove(os.path.join(ck, "orchestrator_state.json"))
         plain, _ = _run(_tiny_cfg(os.path.join(d, "e"), resume_from=ck, checkpoint_save_enabled=False, **common))
         assert plain.start_iteration == 0 and len(plain.metrics) == 4 and plain.train_engine.step_count > 4
+
+
+def test_replacing_one_stage_leaves_the_native_default_stages_in_the_loop():
+    """A subclass that replaces only the weight-sync coroutine gets the staged loop, in which the rollout and training
+    stages are the native defaults (``_do_inference`` / ``_do_training``): the run is the plain loop's run, iteration
+    for iteration, and the replaced stage is called once per iteration with the iteration number."""
+    calls = []
+
+    class Counting(ColocateOrchestrator):
+        async def _do_weight_sync(self, iteration: int = 0):
+            calls.append(iteration)
+            await super()._do_weight_sync(iteration)
+
+    async def go(cls, cfg):
+        o = cls(cfg)
+        await o.initialize()
+        await o.run()
+        await o.shutdown()
+        return o
+    with tempfile.TemporaryDirectory() as d:
+        plain = asyncio.run(go(ColocateOrchestrator, _tiny_cfg(os.path.join(d, "a"), checkpoint_save_enabled=False)))
+        staged = asyncio.run(go(Counting, _tiny_cfg(os.path.join(d, "b"), checkpoint_save_enabled=False)))
+    assert calls == [0, 1, 2] and staged._stages_overridden() and not plain._stages_overridden()
+    assert [m.error for m in staged.metrics] == [None] * 3
+    assert [m.train_metrics.loss for m in staged.metrics] == pytest.approx([m.train_metrics.loss for m in plain.metrics], rel=1e-6)
+    assert [m.tokens_generated for m in staged.metrics] == [m.tokens_generated for m in plain.metrics]
+    assert staged.weights_version == plain.weights_version == 3
+    # the other default stages, called directly
+    async def direct():
+        o = ColocateOrchestrator(_tiny_cfg(os.path.join(tempfile.mkdtemp(), "c"), checkpoint_save_enabled=False))
+        await o.initialize()
+        b = o._next_batch()
+        one = await o._do_inference(b, num_samples=1)
+        two = await o._do_inference_async(b)
+        assert [len(g) for g in one] == [1, 1] and [len(g) for g in two] == [2, 2]
+        assert o.config.num_samples_per_prompt == 2                  # put back after the one-sample call
+        m = await o._do_sft_training(o._next_batch()) if o.config.training_mode == "sft" else None
+        await o._do_weight_sync_async(0)
+        assert o.weights_version == 1 and m is None
+        await o.shutdown()
+    asyncio.run(direct())
