@@ -383,3 +383,54 @@ def _reference_form_pipeline_worker(rank, world):
 def test_pipeline_in_the_reference_call_form_matches_the_full_model():
     from _dist_util import run_ranks
     assert all(run_ranks(_reference_form_pipeline_worker, 2))
+
+
+def test_small_reference_named_helpers_compute_what_their_names_say():
+    """Helpers that only exist because the reference's callers use them: a LoRA adapter called on its own, the ZeRO
+    memory figures, re-binding a runner's KV pool, the transfer manager's version / statistics views and its coroutine
+    form."""
+    import asyncio
+    from b200fw.infer import BlockPool, InferenceConfig, InferenceEngine, KVCacheManager
+    from b200fw.model import ModelConfig, ParallelTransformerModel
+    from b200fw.model.lora import LoRALayer
+    from b200fw.optim import build_optimizer
+    from b200fw.sync import WeightTransferManager
+    torch.manual_seed(0)
+    # ---- a LoRA adapter on its own: x A^T B^T * alpha / r ----
+    ad = LoRALayer(16, 8, 4, 8.0)
+    with torch.no_grad():
+        ad.lora_B.normal_()
+    x = torch.randn(5, 16)
+    want = x @ ad.lora_A.t() @ ad.lora_B.t() * 2.0
+    assert torch.allclose(ad(x), want, atol=1e-6) and torch.allclose(x @ ad.delta_weight().t(), want, atol=1e-5)
+    with pytest.raises(ValueError):
+        LoRALayer(16, 8, 4, 8.0, 0.1)                 # the reference's fifth positional argument: dropout
+    # ---- ZeRO memory figures (one process: the whole state is local) ----
+    lin = torch.nn.Linear(8, 8, bias=False)
+    opt = build_optimizer(lin.parameters(), 1, lr=1e-3)
+    assert opt.state_memory_usage == 2 * 4 * opt.exp_avg.numel()
+    assert "Savings: 0.0%" in opt.total_optimizer_state_savings and "ZeRO-" in opt.total_optimizer_state_savings
+    # ---- the runner can be pointed at another pool ----
+    mc = ModelConfig(vocab_size=64, hidden_size=32, num_layers=2, num_heads=2, num_kv_heads=2, head_dim=16,
+                     intermediate_size=48, max_position_embeddings=64, tie_word_embeddings=True)
+    m = ParallelTransformerModel(mc)
+    m.init_weights(0)
+    eng = InferenceEngine(InferenceConfig.from_model_config(mc, num_blocks=8, inference_mode="kv_cache", temperature=0.0,
+                                                            eos_token_id=None), m).initialize()
+    first = eng.generate([[3, 4, 5, 6]], max_tokens=4)
+    pool2 = BlockPool(8, 16, 2, 2, 16, torch.float32, "cpu")
+    mgr2 = KVCacheManager(pool2, 16)
+    eng.runner.bind_kv_cache(pool2, mgr2)
+    eng.pool, eng.kv = pool2, mgr2
+    assert eng.runner.pool is pool2 and eng.runner.mgr is mgr2
+    assert eng.generate([[3, 4, 5, 6]], max_tokens=4) == first and pool2.num_free_blocks == 8
+    assert eng.runner.capture_cuda_graphs([1, 2]) == []            # no graph runner on CPU
+    eng.runner.invalidate_cuda_graphs()                             # and nothing to drop
+    with pytest.raises(TypeError):
+        eng.runner.bind_hf_model(torch.nn.Linear(2, 2))
+    # ---- transfer manager views ----
+    tm = WeightTransferManager()
+    assert tm.get_version_info().version == int(tm.version) == tm.current_version.version
+    st = tm.get_stats()
+    assert {"backend", "version", "transfers", "total_bytes", "failures"} <= set(st)
+    assert asyncio.iscoroutinefunction(tm.sync_weights_async)
