@@ -654,13 +654,20 @@ class InferenceEngine:
         logger.warning("CUDA out of memory: clearing KV cache, prefix cache and graphs")
         self.stats["oom_recoveries"] += 1
         for r in self.scheduler.abort_all():
+            # ids the abandoned launch would have produced were never read: the request ends before them
+            if self.PLACEHOLDER in r.output_tokens:
+                cut = r.output_tokens.index(self.PLACEHOLDER)
+                del r.output_tokens[cut:]
+                del r.output_logprobs[cut:]
             self.finished[r.request_id] = r
             self.requests.pop(r.request_id, None)
         if self.prefix_cache is not None:
             self.prefix_cache.invalidate_all()
-            self._inflight_prefix.clear()
+        self._inflight_prefix.clear()
         if self.kv is not None:
             self.kv.reset()
+        if self.spec is not None:
+            self.draft_runner.mgr.reset()
         if self.graph_runner is not None:
             self.graph_runner.invalidate()
         if torch.cuda.is_available():

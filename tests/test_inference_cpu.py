@@ -355,3 +355,38 @@ def test_bad_requests_are_refused_at_submission_and_leave_the_engine_serving(mod
     mock.add_request("m", [10 ** 9], 2)
     with pytest.raises(ValueError, match="empty prompt"):
         mock.add_request("m2", [], 2)
+
+
+@pytest.mark.parametrize("kw", [dict(), dict(async_decode="force"), dict(enable_prefix_caching=True),
+                                dict(speculative_enabled=True, speculative_num_tokens=2, speculative_draft_layers=1)])
+def test_out_of_memory_in_a_step_drops_the_batch_and_leaves_a_clean_engine(model, oracle, kw):
+    """The error is made on the host (the runner's forward raises ``torch.cuda.OutOfMemoryError`` once): the step
+    returns, the requests in flight are handed back with the tokens they had (no unread placeholder among them, each a
+    prefix of the oracle's output), every block of every pool is free again, and the next batch is served in full."""
+    eng = _engine(model, **kw)
+    for i, p in enumerate(PROMPTS):
+        eng.add_request(f"r{i}", p, 10)
+    real, calls = eng.runner.forward, []
+
+    def flaky(*a, **k):
+        calls.append(1)
+        if len(calls) == 6:
+            raise torch.cuda.OutOfMemoryError("CUDA out of memory (made up by the test)")
+        return real(*a, **k)
+    eng.runner.forward = flaky
+    steps = 0
+    while eng.has_pending():
+        eng.step()
+        steps += 1
+        assert steps < 500
+    assert eng.stats["oom_recoveries"] == 1
+    assert set(eng.finished) == {f"r{i}" for i in range(len(PROMPTS))} and not eng.requests
+    for i in range(len(PROMPTS)):
+        out = eng.finished[f"r{i}"].output_tokens
+        assert -1 not in out and out == oracle[i][:len(out)]
+    assert eng.pool.num_free_blocks == eng.pool.num_blocks and not eng.kv.tables
+    if eng.spec is not None:
+        dp = eng.draft_runner.pool
+        assert dp.num_free_blocks == dp.num_blocks and not eng.draft_runner.mgr.tables
+    eng.runner.forward = real
+    assert eng.generate(PROMPTS, max_tokens=10) == oracle
