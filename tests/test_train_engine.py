@@ -3,6 +3,7 @@ equivalence, GRPO step against a plain PyTorch oracle, checkpoints, truncation."
 import math
 import tempfile
 
+import pytest
 import torch
 
 from _dist_util import run_ranks
@@ -419,3 +420,49 @@ def test_lora_delta_export_sequence_logprobs_and_closing_a_window_early():
             lp = torch.log_softmax(eng.model(ids).float(), -1)[0].detach()
         want = sum(float(lp[len(p) - 1 + j, t]) for j, t in enumerate(r)) / len(r)
         assert abs(float(got[i]) - want) < 1e-4, (i, float(got[i]), want)
+
+
+DEEP = ModelConfig(vocab_size=128, hidden_size=32, num_layers=5, num_heads=2, num_kv_heads=2, head_dim=16,
+                   intermediate_size=48, max_position_embeddings=64, tie_word_embeddings=False)
+
+
+def _pp_shape_worker(rank, world, path, num_micro, batch):
+    from b200fw.model import load_from_hf_checkpoint
+    cfg = TrainConfig(model_config=DEEP, pp_size=world, num_micro_batches=num_micro, lora_rank=0, grpo_beta=0.0,
+                      learning_rate=1e-3, gradient_accumulation_steps=1, zero_stage=1, use_amp=False,
+                      amp_dtype="fp32", warmup_steps=0, max_seq_len=32, backend="gloo", max_grad_norm=0.0)
+    eng = TrainEngine(cfg).initialize()
+    load_from_hf_checkpoint(eng.model, path, strict=False)
+    eng.optimizer.refresh_masters_from_params()
+    m = eng.model
+    ids, labels = _tiny_batch(3, 0, batch, 12, DEEP.vocab_size)
+    eng.optimizer.begin_backward(True)
+    loss = eng.pipeline_scheduler.broadcast_loss(eng.pipeline_scheduler.run_1f1b_schedule(ids, labels))
+    grads = {m.layer_start + i: l.mlp.down_proj.weight.grad.clone().tolist() for i, l in enumerate(m.layers)}
+    return float(loss), grads, (m.layer_start, len(m.layers))
+
+
+@pytest.mark.parametrize("world,num_micro", [(3, 3), (3, 5), (4, 4), (4, 6)])
+def test_pipeline_1f1b_other_stage_and_micro_batch_counts(world, num_micro):
+    """Five layers over 3 or 4 stages (uneven split), as many micro-batches as stages or more: the schedule's
+    warm-up / steady / cool-down phases line up (no rank waits for a message nobody sends), every layer is owned by
+    exactly one stage, and loss and gradients equal the single-process accumulation."""
+    from b200fw.model import save_hf_checkpoint
+    with tempfile.TemporaryDirectory() as d:
+        ref = ParallelTransformerModel(DEEP)
+        ref.init_weights(5)
+        save_hf_checkpoint(ref, d)
+        batch = 2 * num_micro
+        res = run_ranks(_pp_shape_worker, world, d, num_micro, batch, timeout=300)
+        ids, labels = _tiny_batch(3, 0, batch, 12, DEEP.vocab_size)
+        total = 0.0
+        for mb_ids, mb_labels in zip(ids.chunk(num_micro), labels.chunk(num_micro)):
+            l = ref.loss(mb_ids, mb_labels)
+            (l / num_micro).backward()
+            total += l.item() / num_micro
+        owned = sorted(k for r in res for k in r[1])
+        assert owned == list(range(DEEP.num_layers)), [r[2] for r in res]
+        for r in res:
+            assert abs(r[0] - total) < 1e-5
+            for k, g in r[1].items():
+                assert (torch.tensor(g) - ref.layers[k].mlp.down_proj.weight.grad).abs().max() < 1e-6
