@@ -105,6 +105,7 @@ class ColocateOrchestrator:
         self.weights_version = 0
         self._batches = None
         self.start_iteration = 0        # > 0 after a resume from a checkpoint that recorded its iteration
+        self._resume_rng_from: Optional[str] = None
         self._skip_batches = 0          # batches the resumed run's completed iterations had consumed
         self._pool = ThreadPoolExecutor(max_workers=1)
         self._rollout_stream = None
@@ -227,6 +228,35 @@ class ColocateOrchestrator:
         self.weight_sync = PeerWeightSync(layout, next(rollout_model.parameters()).dtype, eng.device)
         if torch.cuda.is_available():
             self._rollout_stream = torch.cuda.Stream()
+        self._restore_rollout_rng()
+
+    def _rollout_rng_file(self, path: str) -> str:
+        return os.path.join(path, f"rollout_rng_rank{self.train_engine.parallel_ctx.global_rank}.pt")
+
+    def _save_rollout_rng(self, path: str):
+        """The sampling state of this rank's rollout engine (its device generator and the host generator of the mock
+        mode) beside the checkpoint: a resumed run then draws the samples the uninterrupted run would have drawn."""
+        e = self.infer_engine
+        if e is None or getattr(e, "_gen", None) is None:
+            return
+        self.train_engine._atomic_save({"generator": e._gen.get_state().cpu(), "python": e._rng.getstate(),
+                                        "weights_version": e.weights_version}, self._rollout_rng_file(path))
+
+    def _restore_rollout_rng(self):
+        path, self._resume_rng_from = self._resume_rng_from, None
+        e = self.infer_engine
+        if path is None or e is None or getattr(e, "_gen", None) is None:
+            return
+        f = self._rollout_rng_file(path)
+        if not os.path.exists(f):
+            return
+        try:
+            st = torch.load(f, map_location="cpu", weights_only=False)
+            e._gen.set_state(st["generator"])
+            e._rng.setstate(st["python"])
+            e.weights_version = int(st.get("weights_version", e.weights_version))
+        except Exception as err:  # noqa: BLE001 - a state from another device type or torch version: sample afresh
+            logger.warning("resume: rollout sampling state in %s not restored (%s)", f, err)
 
     def _ensure_tp_exchange_group(self):
         """A group of its own (gloo: plain host objects) for handing rollouts round the TP group, so that the
@@ -283,6 +313,7 @@ class ColocateOrchestrator:
         self.start_iteration = max(0, done)
         self._skip_batches = max(0, int(st.get("batches_consumed", done)))
         self.weights_version = int(st.get("weights_version", 0))
+        self._resume_rng_from = path
         logger.info("resume: continuing at iteration %d of %d", self.start_iteration, self.config.total_iterations)
 
     def _next_batch(self) -> GRPOBatch:
@@ -768,6 +799,7 @@ class ColocateOrchestrator:
         for name in (tag, "latest"):
             d = os.path.join(base, name)
             self.train_engine.save_checkpoint(d)
+            self._save_rollout_rng(d)
             if self.train_engine.parallel_ctx.global_rank == 0:
                 self.train_engine._atomic_save({"iterations_completed": done, "batches_consumed": done,
                                                 "weights_version": self.weights_version},

@@ -796,3 +796,36 @@ def test_replacing_one_stage_leaves_the_native_default_stages_in_the_loop():
         assert o.weights_version == 1 and m is None
         await o.shutdown()
     asyncio.run(direct())
+
+
+def test_resumed_grpo_run_draws_the_samples_of_the_uninterrupted_one():
+    """GRPO with sampling (temperature 1): the checkpoint carries the rollout engine's sampling state, so iterations 2
+    and 3 of a run resumed from ``iter_2`` generate the same tokens, see the same rewards and reach the same losses
+    as the run that was never interrupted."""
+    with tempfile.TemporaryDirectory() as d:
+        common = dict(total_iterations=4, temperature=1.0, top_p=0.95, max_tokens=6, learning_rate=2e-3,
+                      synthetic_reward_dense_weight=1.0)          # a reward that depends on every sampled token
+        whole, _ = _run(_tiny_cfg(os.path.join(d, "a"), checkpoint_save_enabled=False, **common))
+        first_cfg = _tiny_cfg(os.path.join(d, "b"), checkpoint_save_interval=2, **common)
+        first = ColocateOrchestrator(first_cfg)
+
+        async def two_then_stop():
+            await first.initialize()
+            real = first._save_checkpoint
+
+            def stop_after(tag, done=None):
+                real(tag, done)
+                if tag == "iter_2":
+                    raise KeyboardInterrupt
+            first._save_checkpoint = stop_after
+            await first.run()
+        with pytest.raises(KeyboardInterrupt):
+            asyncio.run(two_then_stop())
+        ck = os.path.join(first_cfg.checkpoint_save_dir, "iter_2")
+        assert os.path.exists(os.path.join(ck, "rollout_rng_rank0.pt"))
+        resumed, _ = _run(_tiny_cfg(os.path.join(d, "c"), resume_from=ck, checkpoint_save_enabled=False, **common))
+        assert [m.iteration for m in resumed.metrics] == [2, 3]
+        for a, b in zip(whole.metrics[2:], resumed.metrics):
+            assert a.tokens_generated == b.tokens_generated and a.avg_reward == pytest.approx(b.avg_reward, abs=1e-7)
+            assert a.train_metrics.loss == pytest.approx(b.train_metrics.loss, rel=1e-5, abs=1e-7)
+        assert len({m.avg_reward for m in whole.metrics}) > 1          # the rewards did vary: the comparison means something
