@@ -106,6 +106,8 @@ class ColocateOrchestrator:
         self._batches = None
         self.start_iteration = 0        # > 0 after a resume from a checkpoint that recorded its iteration
         self._resume_rng_from: Optional[str] = None
+        self._stop_requested = False
+        self.stopped_early = False      # the loop ended on request_stop() before total_iterations
         self._skip_batches = 0          # batches the resumed run's completed iterations had consumed
         self._pool = ThreadPoolExecutor(max_workers=1)
         self._rollout_stream = None
@@ -545,18 +547,46 @@ class ColocateOrchestrator:
                 self._save_checkpoint(f"iter_{it + 1}", it + 1)
             if cfg.memory_profile_interval > 0 and (it + 1) % cfg.memory_profile_interval == 0:
                 self.memory.snapshot(f"iter_{it + 1}")
+            if it + 1 < cfg.total_iterations and self._stop_agreed():
+                # a stop was asked for (SIGTERM from a scheduler about to take the node, an operator): leave at an
+                # iteration boundary, with a checkpoint that ``resume_from`` continues from
+                logger.info("stop requested: leaving after iteration %d of %d", it + 1, cfg.total_iterations)
+                self.stopped_early = True
+                if cfg.checkpoint_save_enabled and self._last_checkpoint_path != os.path.join(
+                        cfg.checkpoint_save_dir, f"iter_{it + 1}"):
+                    self._save_checkpoint(f"iter_{it + 1}", it + 1)
+                break
         if pending is not None:
             try:
                 await pending
             except Exception:  # noqa: BLE001
                 pass
-        if cfg.eval_num_prompts > 0:
-            self._do_eval("after")
-        if cfg.checkpoint_save_enabled:
-            self._save_checkpoint("final", max(self.start_iteration, cfg.total_iterations))
+        if not self.stopped_early:
+            if cfg.eval_num_prompts > 0:
+                self._do_eval("after")
+            if cfg.checkpoint_save_enabled:
+                self._save_checkpoint("final", max(self.start_iteration, cfg.total_iterations))
         self._set_state(OrchestratorState.DONE)
         self._write_final_artifacts()
         return self.metrics
+
+    def request_stop(self):
+        """Ask the loop to end at the next iteration boundary (safe to call from a signal handler or another thread).
+        The run then saves ``iter_N`` (when checkpoints are enabled), skips the final evaluation and the ``final``
+        checkpoint, writes its artefacts and returns; ``resume_from`` that checkpoint continues the run."""
+        self._stop_requested = True
+
+    def _stop_agreed(self) -> bool:
+        """True when any rank was asked to stop: signals reach the ranks at different moments, and all of them must
+        leave after the same iteration (one small all-reduce per iteration, between the iteration's own collectives)."""
+        flag = self._stop_requested
+        ctx = self.train_engine.parallel_ctx
+        import torch.distributed as dist
+        if ctx.world_size > 1 and dist.is_initialized():
+            t = torch.tensor([int(flag)], dtype=torch.int32, device=self.train_engine.device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            flag = bool(int(t.item()))
+        return flag
 
     # ---- stage methods under the reference's names (src/orchestrator/colocate_orchestrator.py:886-1060,
     # 1644-1740): its loop and its tests address the stages as _do_* coroutines --------------------------------

@@ -65,6 +65,16 @@ def main(argv=None):
     async def go():
         orch = ColocateOrchestrator(cfg)
         await orch.initialize()
+        # SIGTERM (a scheduler reclaiming the node) and the first Ctrl-C end the run at the next iteration boundary
+        # with a checkpoint to resume from; a second Ctrl-C interrupts as usual
+        import signal
+
+        def stop(signum, _frame):
+            orch.request_stop()
+            signal.signal(signal.SIGINT, signal.default_int_handler)
+            print(f"[run_colocate] signal {signum}: stopping after the current iteration", file=sys.stderr, flush=True)
+        for sig in (signal.SIGTERM, signal.SIGINT):
+            signal.signal(sig, stop)
         await orch.run()
         summary = orch.get_summary()
         await orch.shutdown()

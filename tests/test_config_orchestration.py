@@ -829,3 +829,79 @@ def test_resumed_grpo_run_draws_the_samples_of_the_uninterrupted_one():
             assert a.tokens_generated == b.tokens_generated and a.avg_reward == pytest.approx(b.avg_reward, abs=1e-7)
             assert a.train_metrics.loss == pytest.approx(b.train_metrics.loss, rel=1e-5, abs=1e-7)
         assert len({m.avg_reward for m in whole.metrics}) > 1          # the rewards did vary: the comparison means something
+
+
+def test_a_stop_request_ends_the_run_at_an_iteration_boundary_with_a_resumable_checkpoint():
+    """``request_stop()`` (what the script's SIGTERM handler calls) during iteration 1: the loop finishes that
+    iteration, saves ``iter_2``, skips the final checkpoint, and a run resumed from there completes iterations 2 and 3
+    with the losses of a run that was never stopped."""
+    with tempfile.TemporaryDirectory() as d:
+        common = dict(training_mode="sft", total_iterations=4, max_tokens=6, batch_size=2, inference_preview_enabled=False,
+                      learning_rate=2e-3)
+        whole, _ = _run(_tiny_cfg(os.path.join(d, "a"), checkpoint_save_enabled=False, **common))
+        cfg = _tiny_cfg(os.path.join(d, "b"), **common)
+        o = ColocateOrchestrator(cfg)
+
+        async def go():
+            await o.initialize()
+            real = o._train_sft
+
+            def train(batch):
+                if len(o.metrics) == 1:
+                    o.request_stop()                  # arrives in the middle of iteration 1
+                return real(batch)
+            o._train_sft = train
+            await o.run()
+            await o.shutdown()
+        asyncio.run(go())
+        assert o.stopped_early and [m.iteration for m in o.metrics] == [0, 1] and o.state == OrchestratorState.DONE
+        saved = set(os.listdir(cfg.checkpoint_save_dir))
+        assert "iter_2" in saved and "final" not in saved
+        assert os.path.exists(os.path.join(cfg.output_dir, "run_summary.json"))
+        ck = os.path.join(cfg.checkpoint_save_dir, "iter_2")
+        resumed, _ = _run(_tiny_cfg(os.path.join(d, "c"), resume_from=ck, checkpoint_save_enabled=False, **common))
+        assert not resumed.stopped_early and [m.iteration for m in resumed.metrics] == [2, 3]
+        assert [m.train_metrics.loss for m in resumed.metrics] == pytest.approx(
+            [m.train_metrics.loss for m in whole.metrics[2:]], rel=1e-6)
+        # a request during the last iteration changes nothing: the run is complete anyway
+        last = ColocateOrchestrator(_tiny_cfg(os.path.join(d, "e"), **{**common, "total_iterations": 1}))
+
+        async def one():
+            await last.initialize()
+            last.request_stop()
+            await last.run()
+            await last.shutdown()
+        asyncio.run(one())
+        assert not last.stopped_early and "final" in os.listdir(last.config.checkpoint_save_dir)
+
+
+def _dp_stop_worker(rank, world, tmp):
+    """Only rank 1 is asked to stop, in the middle of iteration 0."""
+    cfg = _tiny_cfg(os.path.join(tmp, "shared"), dp_size=world, zero_stage=1, total_iterations=4, batch_size=4,
+                    num_samples_per_prompt=2, output_dir=os.path.join(tmp, f"out{rank}"))
+    o = ColocateOrchestrator(cfg)
+
+    async def go():
+        await o.initialize()
+        if rank == 1:
+            real = o._rewards
+
+            def rewards(ro):
+                o.request_stop()
+                return real(ro)
+            o._rewards = rewards
+        await o.run()
+        await o.shutdown()
+    asyncio.run(go())
+    ck = os.path.join(cfg.checkpoint_save_dir, "iter_1")
+    return o.stopped_early, [m.iteration for m in o.metrics], sorted(os.listdir(ck))
+
+
+def test_a_stop_request_on_one_rank_stops_every_rank_after_the_same_iteration():
+    from _dist_util import run_ranks
+    with tempfile.TemporaryDirectory() as d:
+        res = run_ranks(_dp_stop_worker, 2, d, timeout=600)
+    for stopped, its, files in res:
+        assert stopped and its == [0]
+        assert {"optimizer_state_rank0.pt", "optimizer_state_rank1.pt", "orchestrator_state.json", "trainer_state.json",
+                "rollout_rng_rank0.pt", "rollout_rng_rank1.pt"} <= set(files), files
