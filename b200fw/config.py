@@ -98,6 +98,8 @@ class ColocateConfig:
     reward_format: float = -0.5            # reward.format_reward: wrong or missing answer, well-formed response
     reward_wrong: float = -1.0             # reward.wrong_reward: wrong or missing answer, no recognisable format
     deterministic: bool = False            # fixed seeds, deterministic torch algorithms, no split-K atomics in the GEMM
+    heartbeat_interval_s: float = 0.0      # > 0: ranks watch each other over the rendezvous store; a step is refused
+    heartbeat_timeout_s: float = 10.0      # (PeerLostError ends the run) once a peer has been silent this long
     icepop_enabled: bool = False
     icepop_divergence_threshold: float = 0.5
     icepop_max_mask_ratio: float = 0.5
@@ -133,6 +135,7 @@ _YAML_MAP: List[Tuple[str, str]] = [
     ("runtime.tp_size", "tp_size"), ("runtime.dp_size", "dp_size"), ("runtime.precision", "amp_dtype"),
     ("runtime.inference_backend", "inference_backend"), ("runtime.enable_comm_overlap", "enable_comm_overlap"),
     ("runtime.sequence_parallel", "sequence_parallel"), ("runtime.seed", "seed"), ("runtime.deterministic", "deterministic"),
+    ("runtime.heartbeat_interval_s", "heartbeat_interval_s"), ("runtime.heartbeat_timeout_s", "heartbeat_timeout_s"),
     ("reward.correct_reward", "reward_correct"), ("reward.format_reward", "reward_format"),
     ("reward.wrong_reward", "reward_wrong"),
     ("distributed.pp_size", "pp_size"), ("distributed.num_micro_batches", "num_micro_batches"),

@@ -28,6 +28,7 @@ from typing import Dict, List, Optional
 import torch
 
 from ..config import ColocateConfig, config_snapshot
+from ..dist.heartbeat import PeerLostError
 from ..data import GRPOBatch, GSM8KDataPipeline, SyntheticTokenPipeline
 from ..infer import InferenceConfig, InferenceEngine
 from ..obs import (ArtifactWriter, CommProfiler, ComputeProfiler, EvalMetrics, MemoryProfiler, MetricsCollector,
@@ -138,7 +139,8 @@ class ColocateOrchestrator:
                 lr_scheduler_type=cfg.lr_scheduler_type, warmup_steps=cfg.warmup_steps, min_lr_ratio=cfg.min_lr_ratio,
                 total_training_steps=total_steps, icepop_enabled=cfg.icepop_enabled,
                 icepop_divergence_threshold=cfg.icepop_divergence_threshold,
-                icepop_max_mask_ratio=cfg.icepop_max_mask_ratio, sequence_parallel=cfg.sequence_parallel, seed=cfg.seed)
+                icepop_max_mask_ratio=cfg.icepop_max_mask_ratio, sequence_parallel=cfg.sequence_parallel, seed=cfg.seed,
+                heartbeat_interval_s=cfg.heartbeat_interval_s, heartbeat_timeout_s=cfg.heartbeat_timeout_s)
             self.train_engine = TrainEngine(tc).initialize()
         eng = self.train_engine
         eng.metrics_collector = self.collector
@@ -539,6 +541,8 @@ class ColocateOrchestrator:
                         await self._wake_with_retries()
                 im.weights_version = self.weights_version
             except Exception as e:  # noqa: BLE001 - an iteration may fail; the loop continues
+                if isinstance(e, PeerLostError):
+                    raise           # a rank is gone: no later iteration can complete its collectives
                 await self._handle_error(it, e, im)
             im.total_time = time.perf_counter() - t_iter
             self.metrics.append(im)
@@ -706,6 +710,8 @@ class ColocateOrchestrator:
                     await self._wake_with_retries()
                 im.weights_version = self.weights_version
             except Exception as e:  # noqa: BLE001 - an iteration may fail; the loop continues
+                if isinstance(e, PeerLostError):
+                    raise           # a rank is gone: no later iteration can complete its collectives
                 await self._handle_error(it, e, im)
             im.total_time = time.perf_counter() - t_iter
             self.metrics.append(im)

@@ -88,6 +88,8 @@ class TrainConfig:
     zero3_prefetch: bool = True                 # ZeRO-3: overlap the per-bucket parameter gathers with the forward
     build_ref_model: Optional[bool] = None      # default: grpo_beta > 0, as in the reference
     backend: Optional[str] = None               # nccl / gloo (default by device)
+    heartbeat_interval_s: float = 0.0           # > 0: watch the other ranks over the rendezvous store and refuse to
+    heartbeat_timeout_s: float = 10.0           # launch a step once one of them is gone (b200fw.dist.heartbeat)
 
 
 @dataclass
@@ -117,6 +119,7 @@ class TrainEngine:
         self.pp_context: Optional[PipelineParallelContext] = None
         self.pipeline_scheduler: Optional[PipelineScheduler] = None
         self.icepop: Optional[IcePopFilter] = None
+        self.heartbeat = None                       # b200fw.dist.heartbeat.RankHeartbeat when enabled
         self._prev_lora_snapshot: Optional[Dict[str, torch.Tensor]] = None
         self.memory_profiler = MemoryProfiler()
         self.device = torch.device("cpu")
@@ -213,6 +216,12 @@ class TrainEngine:
                                        cfg.total_training_steps, cfg.min_lr_ratio)
         self.optimizer.param_groups[0]["lr"] = self.lr_scheduler.lr_at(0)
         ctx.on_destroy(self.release_graphs)
+        if cfg.heartbeat_interval_s > 0:
+            from ..dist.heartbeat import RankHeartbeat
+            self.heartbeat = RankHeartbeat.from_default_group(cfg.heartbeat_interval_s, cfg.heartbeat_timeout_s)
+            if self.heartbeat is not None:
+                self.heartbeat.start()
+                ctx.on_destroy(self.heartbeat.announce_leave)      # leaving on purpose is not a failure
         if cfg.pp_size > 1:
             self.pipeline_scheduler = PipelineScheduler(self.model, self.pp_context, cfg.num_micro_batches)
         if cfg.icepop_enabled:
@@ -240,6 +249,12 @@ class TrainEngine:
             buf = torch.empty(max(numel, 1), dtype=torch.long, pin_memory=True)
             self._pinned[name] = buf
         return buf[:numel]
+
+    def _check_peers(self):
+        """Before anything of a step is launched: if the heartbeat watcher has found a rank gone, raise
+        ``PeerLostError`` here instead of entering collectives (or peer-memory kernels) that rank will never join."""
+        if self.heartbeat is not None:
+            self.heartbeat.check()
 
     def _check_host_batch(self, input_ids: Optional[torch.Tensor], labels: Optional[torch.Tensor] = None):
         """Refuse token ids and labels outside the vocabulary, and rows longer than the position table, while the
@@ -392,6 +407,7 @@ class TrainEngine:
         """SFT step on ready ``[B,S]`` tensors (host tensors are copied to the device asynchronously).
         ``sync=False`` returns ``(loss_tensor, grad_norm_tensor_or_None)`` without a host sync."""
         valid_idx = None
+        self._check_peers()
         self._check_host_batch(input_ids, labels)
         if input_ids.device != self.device:
             if labels.device.type == "cpu" and self.device.type == "cuda":
@@ -644,6 +660,7 @@ class TrainEngine:
         ``close_window`` makes this backward the last of the accumulation window whatever the count says
         (C3PO++ packs a batch into a variable number of chunks and closes the window on the last one)."""
         assert self.pp_context is None or self.pp_context.pp_size == 1, "GRPO needs pp_size == 1"
+        self._check_peers()
         cfg, opt = self.config, self.optimizer
         if reset_behavior_baseline:
             self._old_log_probs_buffer = None

@@ -175,3 +175,70 @@ def _biased_tp_layers(rank, world):
 def test_tp_layers_with_bias_and_unsplit_input():
     for err in run_ranks(_biased_tp_layers, 2):
         assert max(err) < 1e-5, err
+
+
+def test_heartbeat_watcher_finds_a_silent_peer_and_an_announced_leave():
+    """Three watchers on one in-process store, driven by hand with a made-up clock: beats keep everybody alive; a
+    peer whose counter stands still longer than the limit is reported with its rank; an announced leave is reported at
+    the next look, with the reason; ``check()`` is quiet until then and raises the same error ever after."""
+    import pytest
+    import torch.distributed as dist
+    from b200fw.dist import PeerLostError, RankHeartbeat
+    store = dist.HashStore()
+    hb = [RankHeartbeat(store, r, 3, interval_s=1.0, timeout_s=5.0) for r in range(3)]
+    t = 100.0
+    for step in range(8):                       # everyone beats: nobody is lost
+        for h in hb:
+            h.beat()
+        for h in hb:
+            h.poll(now=t)
+            h.check()
+        t += 1.0
+    for step in range(7):                       # rank 2 goes silent
+        hb[0].beat()
+        hb[1].beat()
+        hb[0].poll(now=t)
+        hb[1].poll(now=t)
+        t += 1.0
+    for h in hb[:2]:
+        with pytest.raises(PeerLostError) as e:
+            h.check()
+        assert e.value.rank == 2 and "no heartbeat" in e.value.reason
+        with pytest.raises(PeerLostError):
+            h.check()                           # and it stays raised
+    # an announced leave is seen at once, whatever the clock says
+    store2 = dist.HashStore()
+    a, b = RankHeartbeat(store2, 0, 2, 1.0, 5.0), RankHeartbeat(store2, 1, 2, 1.0, 5.0)
+    a.beat(); b.beat(); a.poll(now=0.0); a.check()
+    b.announce_leave("out of memory on this rank")
+    a.poll(now=0.1)
+    with pytest.raises(PeerLostError, match="announced its leave: out of memory"):
+        a.check()
+    # a peer that never wrote a beat counts from the first look (a rank that died before its first beat)
+    store3 = dist.HashStore()
+    c = RankHeartbeat(store3, 0, 2, 1.0, 5.0)
+    c.poll(now=0.0)
+    c.poll(now=4.0)
+    c.check()
+    c.poll(now=6.0)
+    with pytest.raises(PeerLostError):
+        c.check()
+
+
+def test_heartbeat_thread_beats_polls_and_stops():
+    import time
+    import torch.distributed as dist
+    from b200fw.dist import RankHeartbeat
+    store = dist.HashStore()
+    a = RankHeartbeat(store, 0, 2, interval_s=0.02, timeout_s=0.2).start()
+    b = RankHeartbeat(store, 1, 2, interval_s=0.02, timeout_s=0.2).start()
+    time.sleep(0.3)
+    a.check(); b.check()
+    assert a.beats > 5 and b.beats > 5
+    b.stop()                                    # b goes silent without a word
+    deadline = time.time() + 3
+    while a.lost is None and time.time() < deadline:
+        time.sleep(0.02)
+    assert a.lost is not None and a.lost.rank == 1
+    a.stop()
+    assert a._thread is None

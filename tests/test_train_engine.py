@@ -466,3 +466,44 @@ def test_pipeline_1f1b_other_stage_and_micro_batch_counts(world, num_micro):
             assert abs(r[0] - total) < 1e-5
             for k, g in r[1].items():
                 assert (torch.tensor(g) - ref.layers[k].mlp.down_proj.weight.grad).abs().max() < 1e-6
+
+
+def _heartbeat_worker(rank, world, silent):
+    """Two data-parallel ranks train two steps; then rank 1 leaves between steps (with a word, or silently: its
+    heartbeat just stops).  Rank 0's next step must raise before it launches anything."""
+    import time
+    from b200fw.dist import PeerLostError
+    cfg = TrainConfig(model_config=SMALL, dp_size=world, lora_rank=0, grpo_beta=0.0, learning_rate=1e-3,
+                      gradient_accumulation_steps=1, zero_stage=1, use_amp=False, amp_dtype="fp32", warmup_steps=0,
+                      max_seq_len=32, backend="gloo", bucket_mb=0.02, heartbeat_interval_s=0.05, heartbeat_timeout_s=1.0)
+    eng = TrainEngine(cfg).initialize()
+    assert eng.heartbeat is not None
+    ids, labels = _tiny_batch(0, rank, 2, 16, SMALL.vocab_size)
+    for _ in range(2):
+        eng.sft_step_tensors(ids, labels)
+    if rank == 1:
+        if silent:
+            eng.heartbeat.stop()
+        else:
+            eng.heartbeat.announce_leave("made up by the test")
+        time.sleep(3.0)                  # stays around (its process group alive) while rank 0 notices
+        return "left"
+    deadline = time.time() + 10
+    while eng.heartbeat.lost is None and time.time() < deadline:
+        time.sleep(0.02)
+    t0 = time.time()
+    try:
+        eng.sft_step_tensors(ids, labels)
+    except PeerLostError as e:
+        return ("raised", e.rank, e.reason, time.time() - t0, eng.step_count)
+    return ("trained", None, None, time.time() - t0, eng.step_count)
+
+
+@pytest.mark.parametrize("silent", [False, True])
+def test_a_step_is_refused_once_the_heartbeat_has_lost_a_peer(silent):
+    res = run_ranks(_heartbeat_worker, 2, silent, timeout=120)
+    kind, who, reason, took, steps = res[0]
+    assert kind == "raised" and who == 1 and steps == 2
+    assert ("no heartbeat" in reason) if silent else ("made up by the test" in reason)
+    assert took < 0.5                    # refused on the host at once: nothing was launched, nothing timed out
+    assert res[1] == "left"
