@@ -644,6 +644,25 @@ class InferenceEngine:
         self.finished[r.request_id] = r
         self.requests.pop(r.request_id, None)
 
+    def abort_request(self, request_id: str) -> bool:
+        """Take one request out of the engine (its client went away): the tokens it has are settled (a launch in
+        flight is read first, so no placeholder is left behind), its blocks go back to the pool (a finished prompt is
+        still published to the prefix cache), and it is handed over in ``finished`` with what it produced.  Returns
+        False when no such request is in flight.  The reference has no cancellation: a request runs to its token
+        limit (src/inference/engine.py:478-497)."""
+        r = self.requests.get(request_id)
+        if r is None:
+            return False
+        self._resolve_inflight()
+        if self.PLACEHOLDER in r.output_tokens:      # defensive: nothing unread may leave the engine
+            cut = r.output_tokens.index(self.PLACEHOLDER)
+            del r.output_tokens[cut:]
+            del r.output_logprobs[cut:]
+        r.max_tokens = r.num_generated_tokens
+        self.stats["aborted_requests"] = self.stats.get("aborted_requests", 0) + 1
+        self._finish(r)
+        return True
+
     def _fail(self, r: Request, err: Exception):
         logger.warning("request %s failed: %s", r.request_id, err)
         self.stats["request_errors"] += 1

@@ -124,9 +124,9 @@ WORKLOAD = st.lists(st.tuples(st.integers(1, 70), st.integers(1, 24), st.boolean
 @settings(max_examples=40, deadline=None, suppress_health_check=[HealthCheck.too_slow, HealthCheck.function_scoped_fixture])
 @given(WORKLOAD, st.integers(0, 3), st.sampled_from([8, 16, 48]), st.sampled_from(["none", "hash", "radix"]), st.booleans(),
        st.sampled_from([2, 3, 256]), st.sampled_from([0, 0, 2, 4]), st.sets(st.integers(1, 60), max_size=3),
-       st.sampled_from([100, 100, 1, 0]))
+       st.sampled_from([100, 100, 1, 0]), st.dictionaries(st.integers(1, 40), st.integers(0, 9), max_size=2))
 def test_paged_engine_equals_eager_oracle_under_memory_pressure(model, workload, slack, chunk, cache, late, max_seqs, spec_k,
-                                                                update_at, staleness):
+                                                                update_at, staleness, abort_at):
     """Random prompts (some sharing a 32-token prefix), a block pool barely larger than the largest single request
     (so running sequences get preempted and recomputed), small prefill chunks, no / hash / radix prefix cache, read-back one
     step late or not, greedy speculative decoding with a one-layer draft or none: outputs must equal the eager full-recompute oracle, and every block must come back."""
@@ -149,12 +149,18 @@ def test_paged_engine_equals_eager_oracle_under_memory_pressure(model, workload,
                   speculative_draft_layers=1, max_weight_staleness=staleness)
     for i, (p, o) in enumerate(zip(prompts, outs)):
         eng.add_request(f"r{i}", p, o)
-    steps = 0
+    steps = cancelled = 0
     while eng.has_pending():
         eng.step()
         steps += 1
         if steps in update_at:
             eng.on_weights_updated()
+        if steps in abort_at:
+            rid = f"r{abort_at[steps] % len(prompts)}"
+            was_live = rid in eng.requests
+            assert eng.abort_request(rid) == was_live
+            cancelled += int(was_live)
+            assert rid not in eng.requests and rid in eng.finished and not eng.abort_request(rid)
         assert steps < 5000, "the engine stopped making progress"
     dropped = eng.stats.get("aborted_stale", 0)
     assert dropped == 0 or staleness < 100
@@ -167,7 +173,7 @@ def test_paged_engine_equals_eager_oracle_under_memory_pressure(model, workload,
             assert list(a) == list(b[:len(a)]), (i, a, b)
         else:
             assert list(a) == list(b), (i, prompts[i][:6], a, b)
-    assert short <= dropped
+    assert short <= dropped + cancelled
     # every block is back in the pool except those the prefix cache still references; evicting them frees the rest
     if eng.prefix_cache is not None:
         eng.prefix_cache.evict_lru(blocks)
