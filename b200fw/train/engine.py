@@ -401,14 +401,15 @@ class TrainEngine:
         # on a GPU the batch stays in pinned host memory until sft_step_tensors ships it together with the
         # supervised-row indices (known on the host, so the LM head needs no device -> host count)
         ids, labels = self._build_batch(prompts_tokens, response_tokens, on_host=self.device.type == "cuda")
-        return self.sft_step_tensors(ids, labels)
+        return self.sft_step_tensors(ids, labels, _checked=True)        # _build_batch has looked at the values
 
-    def sft_step_tensors(self, input_ids: torch.Tensor, labels: torch.Tensor, sync: bool = True):
+    def sft_step_tensors(self, input_ids: torch.Tensor, labels: torch.Tensor, sync: bool = True, _checked: bool = False):
         """SFT step on ready ``[B,S]`` tensors (host tensors are copied to the device asynchronously).
         ``sync=False`` returns ``(loss_tensor, grad_norm_tensor_or_None)`` without a host sync."""
         valid_idx = None
         self._check_peers()
-        self._check_host_batch(input_ids, labels)
+        if not _checked:
+            self._check_host_batch(input_ids, labels)
         if input_ids.device != self.device:
             if labels.device.type == "cpu" and self.device.type == "cuda":
                 # the supervised rows (label of the next token is not -100) are known on the host before the
