@@ -18,6 +18,10 @@ import random
 from dataclasses import dataclass
 from typing import Dict, Iterator, List, Optional
 
+from ..obs.logging import get_logger
+
+logger = get_logger("data.pipeline")
+
 PROMPT_TEMPLATES: Dict[str, str] = {
     "qwen3_math": ("<|im_start|>system\nYou are a helpful math assistant. Solve the problem step by step and give "
                    "the final answer after '####'.<|im_end|>\n<|im_start|>user\n{prompt}<|im_end|>\n"
@@ -91,7 +95,14 @@ class GSM8KDataPipeline:
         recs = records if records is not None else _load_records(dataset_name, dataset_config, split)
         if max_samples:
             recs = recs[:max_samples]
-        self.records = recs[dp_rank::max(1, dp_size)]
+        # a record without a prompt would become an empty request; drop it here, before the shards are cut, so that
+        # every rank drops the same ones
+        usable = [r for r in recs if isinstance(r, dict) and str(r.get(prompt_field) if r.get(prompt_field) is not None
+                                                                   else "").strip()]
+        if len(usable) < len(recs):
+            logger.warning("%d of %d records have no %r field (or an empty one) and are left out",
+                           len(recs) - len(usable), len(recs), prompt_field)
+        self.records = usable[dp_rank::max(1, dp_size)]
         self.template = PROMPT_TEMPLATES.get(prompt_template, prompt_template)
         self.prompt_field, self.input_field = prompt_field, input_field
         self.response_field, self.answer_field = response_field, answer_field

@@ -125,3 +125,20 @@ def test_synthetic_pipeline_is_seeded_and_shares_prefixes():
     assert bt.ground_truths == bt.prompt_indices == [1, 3, 5, 7] and len(bt.prompt_tokens[0]) == 8
     tok = SimpleTokenizer()
     assert tok.decode(tok.encode("héllo #### 7")) == "héllo #### 7" and tok.encode("a", add_special_tokens=True)[0] == 1
+
+
+def test_records_without_a_prompt_are_left_out_before_sharding():
+    """A record whose prompt field is missing, ``None`` or blank would become an empty request: it is dropped when the
+    pipeline is built, before the data-parallel shards are cut (so both ranks drop the same records and the shards
+    still partition what is left)."""
+    from b200fw.data.pipeline import GSM8KDataPipeline
+    recs = [{"question": f"{i}+1?", "answer": f"#### {i + 1}"} for i in range(6)]
+    recs[1] = {"answer": "#### 9"}
+    recs[3] = {"question": "   ", "answer": "#### 9"}
+    recs[4] = {"question": None, "answer": "#### 9"}
+    whole = GSM8KDataPipeline(records=recs, prompt_template="plain")
+    assert len(whole) == 3
+    shards = [GSM8KDataPipeline(records=recs, prompt_template="plain", dp_rank=r, dp_size=2) for r in range(2)]
+    got = sorted(b.prompts[0] for s in shards for b in s.get_batches(1))
+    assert got == sorted(b.prompts[0] for b in whole.get_batches(1)) and len(got) == 3
+    assert all(len(t) > 0 for s in shards for b in s.get_batches(1) for t in b.prompt_tokens)
