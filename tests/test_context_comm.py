@@ -230,13 +230,13 @@ def test_heartbeat_thread_beats_polls_and_stops():
     import torch.distributed as dist
     from b200fw.dist import RankHeartbeat
     store = dist.HashStore()
-    a = RankHeartbeat(store, 0, 2, interval_s=0.02, timeout_s=0.2).start()
-    b = RankHeartbeat(store, 1, 2, interval_s=0.02, timeout_s=0.2).start()
+    a = RankHeartbeat(store, 0, 2, interval_s=0.02, timeout_s=1.0).start()       # generous limit: a loaded test box
+    b = RankHeartbeat(store, 1, 2, interval_s=0.02, timeout_s=1.0).start()       # may starve a thread for a while
     time.sleep(0.3)
     a.check(); b.check()
     assert a.beats > 5 and b.beats > 5
     b.stop()                                    # b goes silent without a word
-    deadline = time.time() + 3
+    deadline = time.time() + 10
     while a.lost is None and time.time() < deadline:
         time.sleep(0.02)
     assert a.lost is not None and a.lost.rank == 1

@@ -475,7 +475,7 @@ def _heartbeat_worker(rank, world, silent):
     from b200fw.dist import PeerLostError
     cfg = TrainConfig(model_config=SMALL, dp_size=world, lora_rank=0, grpo_beta=0.0, learning_rate=1e-3,
                       gradient_accumulation_steps=1, zero_stage=1, use_amp=False, amp_dtype="fp32", warmup_steps=0,
-                      max_seq_len=32, backend="gloo", bucket_mb=0.02, heartbeat_interval_s=0.05, heartbeat_timeout_s=1.0)
+                      max_seq_len=32, backend="gloo", bucket_mb=0.02, heartbeat_interval_s=0.05, heartbeat_timeout_s=2.0)
     eng = TrainEngine(cfg).initialize()
     assert eng.heartbeat is not None
     ids, labels = _tiny_batch(0, rank, 2, 16, SMALL.vocab_size)
@@ -486,9 +486,9 @@ def _heartbeat_worker(rank, world, silent):
             eng.heartbeat.stop()
         else:
             eng.heartbeat.announce_leave("made up by the test")
-        time.sleep(3.0)                  # stays around (its process group alive) while rank 0 notices
+        time.sleep(6.0)                  # stays around (its process group alive) while rank 0 notices
         return "left"
-    deadline = time.time() + 10
+    deadline = time.time() + 20
     while eng.heartbeat.lost is None and time.time() < deadline:
         time.sleep(0.02)
     t0 = time.time()
