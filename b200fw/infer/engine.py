@@ -10,7 +10,9 @@ returned); a CUDA out-of-memory error clears caches and graphs and reports ``Non
 """
 from __future__ import annotations
 
+import functools
 import random
+import threading
 import time
 from typing import Dict, List, Optional
 
@@ -27,6 +29,18 @@ from .radix_cache import RadixAttentionCache
 from .runner import ModelRunner
 from .scheduler import ContinuousBatchingScheduler, Request, SchedulerOutput
 from .spec import SpeculativeDecoder
+
+def _locked(fn):
+    """Run a public entry point under the engine's lock.  A rollout runs on a worker thread while the trainer's thread
+    publishes new weights (``load_weights`` / ``on_weights_updated``), and a server thread may add or cancel requests:
+    each of these mutates the scheduler queues, the block tables and the launch in flight, so they take turns, one
+    engine step at a time.  Re-entrant (``load_weights`` calls ``on_weights_updated``); uncontended cost ~0.1 us."""
+    @functools.wraps(fn)
+    def inner(self, *a, **k):
+        with self._lock:
+            return fn(self, *a, **k)
+    return inner
+
 
 logger = get_logger("infer.engine")
 
@@ -55,6 +69,7 @@ class InferenceEngine:
         self.stats = {"steps": 0, "prefill_tokens": 0, "decode_tokens": 0, "cached_prefix_tokens": 0,
                       "oom_recoveries": 0, "request_errors": 0, "graph_replays": 0, "spec_rounds": 0}
         self._rng = random.Random(config.seed)
+        self._lock = threading.RLock()
         self._gen: Optional[torch.Generator] = None
         self.device = torch.device("cpu")
 
@@ -149,6 +164,7 @@ class InferenceEngine:
         self.spec = SpeculativeDecoder(self.runner, self.draft_runner, self.config.speculative_num_tokens)
 
     # =================================================================================================
+    @_locked
     def add_request(self, request_id: str, prompt_tokens: List[int], max_tokens: int = 512,
                     temperature: Optional[float] = None, top_p: Optional[float] = None) -> Request:
         assert self.initialized, "call initialize() first"
@@ -199,6 +215,7 @@ class InferenceEngine:
         return self.scheduler.has_pending_requests()
 
     # ---- one engine step ----------------------------------------------------------------------------------
+    @_locked
     def step(self) -> Dict[str, List[int]]:
         """Schedule, run prefill chunks and one decode token for every running sequence.  Returns the
         tokens produced in this step per request id."""
@@ -644,6 +661,7 @@ class InferenceEngine:
         self.finished[r.request_id] = r
         self.requests.pop(r.request_id, None)
 
+    @_locked
     def abort_request(self, request_id: str) -> bool:
         """Take one request out of the engine (its client went away): the tokens it has are settled (a launch in
         flight is read first, so no placeholder is left behind), its blocks go back to the pool (a finished prompt is
@@ -746,6 +764,7 @@ class InferenceEngine:
         return outs
 
     # ---- weight updates --------------------------------------------------------------------------------------------
+    @_locked
     @torch.no_grad()
     def load_weights(self, named_tensors) -> int:
         """Copy HF-named tensors into the live model *in place* (captured graphs keep working)."""
@@ -759,6 +778,7 @@ class InferenceEngine:
         self.on_weights_updated()
         return n
 
+    @_locked
     def on_weights_updated(self, abort_running: Optional[bool] = None):
         """The live weights changed (in place, so captured graphs stay valid).  Running requests keep decoding:
         the K/V of their earlier tokens came from the previous version, which is bounded staleness, not an error.

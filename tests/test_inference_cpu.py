@@ -390,3 +390,37 @@ def test_out_of_memory_in_a_step_drops_the_batch_and_leaves_a_clean_engine(model
         assert dp.num_free_blocks == dp.num_blocks and not eng.draft_runner.mgr.tables
     eng.runner.forward = real
     assert eng.generate(PROMPTS, max_tokens=10) == oracle
+
+
+def test_weight_updates_and_cancellations_from_another_thread_take_turns_with_the_steps(model, oracle):
+    """A rollout (``generate``) runs on a worker thread while this thread announces weight updates (same weights, so the
+    oracle holds), adds a request and cancels it again, hundreds of times: the engine's entry points take turns under
+    its lock, the rollout's outputs equal the oracle's and the pool comes back whole."""
+    import threading
+    eng = _engine(model, async_decode="force", enable_prefix_caching=True, max_weight_staleness=10 ** 9)
+    out, err = {}, []
+
+    def rollout():
+        try:
+            for i in range(6):
+                out[i] = eng.generate(PROMPTS, max_tokens=10)
+        except Exception as e:  # noqa: BLE001
+            err.append(e)
+    t = threading.Thread(target=rollout)
+    t.start()
+    n = 0
+    while t.is_alive():
+        eng.on_weights_updated()
+        eng.add_request(f"extra{n}", [7, 8, 9], 50)
+        # cancelled here, unless the rollout thread's steps already carried it to its end
+        assert eng.abort_request(f"extra{n}") or f"extra{n}" in eng.finished
+        assert -1 not in eng.finished[f"extra{n}"].output_tokens
+        n += 1
+    t.join()
+    assert not err, err
+    assert n >= 1 and all(out[i] == oracle for i in range(6))
+    for k in [k for k in eng.finished if k.startswith("extra")]:
+        del eng.finished[k]
+    if eng.prefix_cache is not None:
+        eng.prefix_cache.evict_lru(eng.pool.num_blocks)
+    assert eng.pool.num_free_blocks == eng.pool.num_blocks and not eng.kv.tables and not eng.requests
