@@ -171,6 +171,7 @@ class InferenceEngine:
         prompt_tokens, max_tokens = self._check_request(request_id, prompt_tokens, max_tokens)
         return self._enqueue(request_id, prompt_tokens, max_tokens, temperature, top_p)
 
+    @_locked
     def _enqueue(self, request_id, prompt_tokens, max_tokens, temperature, top_p) -> Request:
         t = float(self.config.temperature if temperature is None else temperature)
         p = float(self.config.top_p if top_p is None else top_p)
