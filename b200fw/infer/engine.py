@@ -10,6 +10,7 @@ returned); a CUDA out-of-memory error clears caches and graphs and reports ``Non
 """
 from __future__ import annotations
 
+import contextlib
 import functools
 import random
 import threading
@@ -765,6 +766,15 @@ class InferenceEngine:
         return outs
 
     # ---- weight updates --------------------------------------------------------------------------------------------
+    @contextlib.contextmanager
+    def paused(self):
+        """``with engine.paused():`` - no engine step runs inside the block, and the launch in flight (the one-step-late
+        decode) has been read, so nothing of this engine is executing on the device: the place to rewrite the live
+        weights in place from another thread.  Follow it with :meth:`on_weights_updated`."""
+        with self._lock:
+            self._resolve_inflight()
+            yield self
+
     @_locked
     @torch.no_grad()
     def load_weights(self, named_tensors) -> int:
@@ -772,6 +782,7 @@ class InferenceEngine:
         from ..model.hf_io import hf_named_tensors
         mine = dict(hf_named_tensors(self.model))
         n = 0
+        self._resolve_inflight()            # the launch in flight reads the weights: let it finish first
         for k, v in (named_tensors.items() if isinstance(named_tensors, dict) else named_tensors):
             if k in mine:
                 mine[k].copy_(v.to(mine[k].dtype))

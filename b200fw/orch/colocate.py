@@ -1110,12 +1110,13 @@ class _LoRAWorker:
         cat.index_copy_(0, plan["dst_new"], (new * plan["scale"]).to(dt))          # A_new and s * B_new
         if delta:
             cat.index_copy_(0, plan["dst_old"], (old * plan["scale_old"]).to(dt))   # A_old and -s * B_old
-        for bcat, acat, b_new, a_new, w, base_w in plan["jobs"]:
-            if delta:
-                # W += [s B_new | -s B_old] [A_new ; A_old]: one accumulate GEMM of contraction length 2R per module
-                ops.gemm(bcat, acat, b_mn=True, out=w, accumulate=True)
-            else:
-                ops.gemm(b_new, a_new, b_mn=True, out=w, residual=base_w)
-        plan["flat"] = new
-        self.applied = FlatState(plan["layout"], new)       # name -> view of the image, made when asked for
-        orch.infer_engine.on_weights_updated()
+        with orch.infer_engine.paused():        # a rollout on the worker thread waits at its next step boundary
+            for bcat, acat, b_new, a_new, w, base_w in plan["jobs"]:
+                if delta:
+                    # W += [s B_new | -s B_old] [A_new ; A_old]: one accumulate GEMM of contraction length 2R per module
+                    ops.gemm(bcat, acat, b_mn=True, out=w, accumulate=True)
+                else:
+                    ops.gemm(b_new, a_new, b_mn=True, out=w, residual=base_w)
+            plan["flat"] = new
+            self.applied = FlatState(plan["layout"], new)       # name -> view of the image, made when asked for
+            orch.infer_engine.on_weights_updated()
