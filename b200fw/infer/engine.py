@@ -71,6 +71,7 @@ class InferenceEngine:
                       "oom_recoveries": 0, "request_errors": 0, "graph_replays": 0, "spec_rounds": 0}
         self._rng = random.Random(config.seed)
         self._lock = threading.RLock()
+        self._weights_event = None                  # recorded after a weight rewrite; the next step waits for it
         self._gen: Optional[torch.Generator] = None
         self.device = torch.device("cpu")
 
@@ -221,6 +222,9 @@ class InferenceEngine:
     def step(self) -> Dict[str, List[int]]:
         """Schedule, run prefill chunks and one decode token for every running sequence.  Returns the
         tokens produced in this step per request id."""
+        ev, self._weights_event = self._weights_event, None
+        if ev is not None:
+            torch.cuda.current_stream().wait_event(ev)
         with nvtx.range("infer/schedule"):
             out = self.scheduler.schedule()
         self.stats["steps"] += 1
@@ -799,6 +803,11 @@ class InferenceEngine:
         computed under old weights."""
         self._resolve_inflight()
         self.weights_version += 1
+        if self.device.type == "cuda":
+            # the rewrite was queued on the caller's stream; the next step may run on another one (the rollout stream
+            # of a worker thread) and must not start before the new weights have landed
+            self._weights_event = torch.cuda.Event()
+            self._weights_event.record()
         limit = self.config.max_weight_staleness
         abort_all = abort_running if abort_running is not None else limit <= 0
         if self.scheduler is not None:
