@@ -208,3 +208,69 @@ def test_cpu_sampler_picks_inside_the_nucleus(row, temp, top_p, u):
     assert float(p[pick]) >= floor * (1 - 1e-5), (pick, float(p[pick]), floor)
     if top_p <= 0:
         assert float(p[pick]) >= float(sp[0]) * (1 - 1e-6)
+
+
+CACHE_OPS = st.lists(st.tuples(st.sampled_from(["insert", "match", "release", "evict", "clear"]),
+                               st.lists(st.integers(0, 2), min_size=0, max_size=14), st.integers(0, 5)),
+                     min_size=1, max_size=50)
+
+
+@settings(max_examples=150, deadline=None)
+@given(CACHE_OPS, st.sampled_from(["hash", "radix"]), st.integers(2, 8))
+def test_prefix_caches_agree_with_a_plain_model_of_them(ops, kind, capacity):
+    """Random insert / match / release / evict / clear sequences on the hash-chain and the radix cache (blocks of 2
+    tokens over a 3-letter alphabet, so prefixes collide all the time) against a dictionary model: a match returns the
+    block that was registered FIRST for each block-aligned prefix, whole blocks only and never past a gap; a block
+    leaves the cache exactly once (eviction callback), never while a match holds it; the cache never exceeds its
+    capacity."""
+    from b200fw.infer import PrefixCache, RadixAttentionCache
+    BSZ = 2
+    cache = PrefixCache(BSZ, capacity) if kind == "hash" else RadixAttentionCache(BSZ, capacity)
+    registered = {}          # prefix tuple (k whole blocks) -> block id in the cache
+    held = {}                # block id -> outstanding matches
+    gone = []
+    cache.on_evict = gone.append
+    next_block = [0]
+
+    def live_prefixes():
+        return {p: b for p, b in registered.items() if b not in gone}
+    for op, toks, n in ops:
+        nblocks = len(toks) // BSZ
+        if op == "insert":
+            ids = list(range(next_block[0], next_block[0] + nblocks))
+            next_block[0] += nblocks
+            new = cache.insert(toks, ids)
+            assert set(new) <= set(ids)
+            for i, bid in enumerate(ids):
+                if bid in new:
+                    p = tuple(toks[:(i + 1) * BSZ])
+                    assert p not in live_prefixes(), "a second block was cached for a prefix that is already there"
+                    registered[p] = bid
+        elif op == "match":
+            matched, ids = cache.match_prefix(toks)
+            assert matched == len(ids) * BSZ and matched <= nblocks * BSZ
+            live = live_prefixes()
+            for i, bid in enumerate(ids):
+                assert live.get(tuple(toks[:(i + 1) * BSZ])) == bid
+            if len(ids) < nblocks and kind == "radix":
+                assert tuple(toks[:(len(ids) + 1) * BSZ]) not in live      # the radix tree stops only at a real gap
+            for bid in ids:
+                held[bid] = held.get(bid, 0) + 1
+        elif op == "release" and held:
+            bid = sorted(held)[n % len(held)]
+            cache.release_blocks([bid])
+            held[bid] -= 1
+            if held[bid] == 0:
+                del held[bid]
+        elif op == "evict":
+            before = len(gone)
+            out = cache.evict_lru(n)
+            assert len(out) <= n and gone[before:] == out
+            assert not (set(out) & set(held)), "a block that a match still holds was evicted"
+        elif op == "clear" and n == 0 and not held:
+            cache.invalidate_all()
+            registered = {p: b for p, b in registered.items() if b in gone}
+        assert len(gone) == len(set(gone)), "a block left the cache twice"
+        size = len(cache.entries) if kind == "hash" else cache.size
+        assert size <= capacity
+        assert size == len(live_prefixes()), (size, live_prefixes())
