@@ -60,7 +60,9 @@ class RadixAttentionCache:
                 child = None
             if child is None:
                 if self.num_nodes >= self.max_nodes:
-                    self.evict_lru(1)
+                    # never the node the new block hangs under: as the deepest node of this path it is a leaf, and
+                    # evicting it would attach the new block to a detached node (unreachable, never evicted: a leak)
+                    self.evict_lru(1, protect=node)
                     if self.num_nodes >= self.max_nodes:
                         break
                 child = RadixNode(blk, bid, node)
@@ -88,10 +90,10 @@ class RadixAttentionCache:
             stack.extend(n.children.values())
         return out
 
-    def evict_lru(self, num_blocks: int = 1) -> List[int]:
+    def evict_lru(self, num_blocks: int = 1, protect: Optional[RadixNode] = None) -> List[int]:
         out = []
         for _ in range(num_blocks):
-            cands = [n for n in self._leaves() if n.ref_count == 0]
+            cands = [n for n in self._leaves() if n.ref_count == 0 and n is not protect]
             if not cands:
                 break
             victim = min(cands, key=lambda n: n.last_access)

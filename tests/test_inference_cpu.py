@@ -424,3 +424,25 @@ def test_weight_updates_and_cancellations_from_another_thread_take_turns_with_th
     if eng.prefix_cache is not None:
         eng.prefix_cache.evict_lru(eng.pool.num_blocks)
     assert eng.pool.num_free_blocks == eng.pool.num_blocks and not eng.kv.tables and not eng.requests
+
+
+def test_radix_cache_at_capacity_never_hangs_a_block_under_an_evicted_node():
+    """A path longer than the cache's capacity: making room for block i must not evict block i-1 (the only leaf), or
+    block i ends up under a detached node - counted, holding its pool reference, unreachable and never evicted."""
+    cache = RadixAttentionCache(2, 3)
+    gone = []
+    cache.on_evict = gone.append
+    toks = [0, 0, 0, 1, 0, 0, 0, 1]
+    new = cache.insert(toks, [10, 11, 12, 13])
+    assert new == [10, 11, 12] and not gone and cache.size == 3           # the fourth block does not fit: left out
+    assert cache.match_prefix(toks) == (6, [10, 11, 12])
+    cache.release_blocks([10, 11, 12])
+    assert cache.insert(toks, [20, 21, 22, 23]) == []                     # nothing new, nothing orphaned
+    assert sorted(cache.invalidate_all()) == [10, 11, 12] and sorted(gone) == [10, 11, 12]
+    # with another branch to give up, room is made from that branch
+    cache = RadixAttentionCache(2, 3)
+    cache.on_evict = gone.append
+    del gone[:]
+    cache.insert([5, 5], [1])
+    assert cache.insert([0, 0, 0, 1, 0, 0], [2, 3, 4]) == [2, 3, 4] and gone == [1]
+    assert cache.match_prefix([0, 0, 0, 1, 0, 0]) == (6, [2, 3, 4])
