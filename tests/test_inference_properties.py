@@ -274,3 +274,44 @@ def test_prefix_caches_agree_with_a_plain_model_of_them(ops, kind, capacity):
         size = len(cache.entries) if kind == "hash" else cache.size
         assert size <= capacity
         assert size == len(live_prefixes()), (size, live_prefixes())
+
+
+@settings(max_examples=100, deadline=None)
+@given(st.lists(st.tuples(st.integers(1, 300), st.integers(1, 40), st.integers(0, 30)), min_size=1, max_size=40),
+       st.sampled_from([16, 64, 256]), st.sampled_from([1, 2, 8, 64]), st.sampled_from([8, 32, 512]), st.booleans(),
+       st.booleans())
+def test_scheduler_budgets_hold_every_step_and_every_request_finishes(reqs, max_tokens, max_seqs, chunk, chunked, adaptive):
+    """The mock engine (scheduler and bookkeeping only, no model) over random arrivals: every step's batch respects the
+    token, prefill and sequence budgets, a prefill chunk never exceeds what is left of its prompt, decode requests are
+    scheduled before new prefills, and every request finishes with exactly ``max_tokens`` tokens."""
+    cfg = InferenceConfig(inference_mode="mock", num_blocks=8, max_num_batched_tokens=max_tokens, max_num_sequences=max_seqs,
+                          max_prefill_tokens=max(8, max_tokens // 2), chunk_size=chunk, enable_chunked_prefill=chunked,
+                          adaptive_chunking=adaptive, eos_token_id=None)
+    eng = InferenceEngine(cfg).initialize()
+    real = eng.scheduler.schedule
+
+    def checked():
+        out = real()
+        assert len(out.decode_requests) <= max_seqs
+        fresh = [r for r in out.prefill_requests if r not in out.decode_requests]
+        assert len(out.decode_requests) + len(fresh) <= max(max_seqs, len(out.decode_requests))
+        assert out.num_prefill_tokens <= cfg.max_prefill_tokens
+        assert out.total_tokens <= max(max_tokens, len(out.decode_requests) + 1)
+        for r in out.prefill_requests:
+            n = out.prefill_tokens[r.request_id]
+            assert 0 < n <= r.remaining_prefill_tokens
+        return out
+    eng.scheduler.schedule = checked
+    arrivals = sorted(((at, i, p, o) for i, (p, o, at) in enumerate(reqs)))
+    step, k = 0, 0
+    while k < len(arrivals) or eng.has_pending():
+        while k < len(arrivals) and arrivals[k][0] <= step:
+            _, i, p, o = arrivals[k]
+            eng.add_request(f"r{i}", [3 + (j % 90) for j in range(p)], o)
+            k += 1
+        eng.step()
+        step += 1
+        assert step < 20000, "the scheduler stopped making progress"
+    assert len(eng.finished) == len(reqs) and not eng.requests
+    for i, (p, o, _) in enumerate(reqs):
+        assert len(eng.finished[f"r{i}"].output_tokens) == o
