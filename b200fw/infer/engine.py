@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import contextlib
 import functools
+import operator
 import random
 import threading
 import time
@@ -194,6 +195,12 @@ class InferenceEngine:
         prompt = [int(t) for t in prompt_tokens]
         if not prompt:
             raise ValueError(f"request {request_id!r}: empty prompt")
+        try:
+            max_tokens = operator.index(max_tokens)         # int, numpy integer, 0-d integer tensor
+        except TypeError:
+            max_tokens = -1
+        if max_tokens < 0:
+            raise ValueError(f"request {request_id!r}: max_tokens must be a non-negative integer")
         if request_id in self.requests:
             raise ValueError(f"request id {request_id!r} is already in flight")
         mc = getattr(self.model, "cfg", None)

@@ -331,6 +331,8 @@ def test_bad_requests_are_refused_at_submission_and_leave_the_engine_serving(mod
                              ("l", [9] * MC.max_position_embeddings, "no room")]:
         with pytest.raises(ValueError, match=err):
             eng.add_request(rid, prompt, 4)
+    with pytest.raises(ValueError, match="max_tokens"):
+        eng.add_request("neg", [4, 5], -1)
     with pytest.raises(ValueError, match="empty prompt"):
         eng.generate([[4, 5], []], max_tokens=3)
     assert set(eng.requests) == {"good"}                       # the good half of that batch was not queued either
