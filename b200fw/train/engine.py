@@ -735,6 +735,7 @@ class TrainEngine:
         if top_p < 1.0:
             sp, si = probs.sort(dim=-1, descending=True)
             keep = (sp.cumsum(-1) - sp) < top_p      # keep the token that crosses the threshold
+            keep[..., 0] = True                      # top_p <= 0: the most likely token alone
             sp = sp * keep
             probs = torch.zeros_like(probs).scatter_(-1, si, sp)
             probs = probs / probs.sum(-1, keepdim=True)
@@ -748,7 +749,12 @@ class TrainEngine:
         :class:`b200fw.infer.InferenceEngine`.  Under TP, rank 0 of the TP group samples and broadcasts."""
         import torch.distributed as dist
         ctx = self.parallel_ctx
-        seq = list(prompt_tokens)
+        seq = [int(t) for t in prompt_tokens]
+        if not seq:
+            raise ValueError("generate(): empty prompt")
+        V = self.model_config.vocab_size
+        if min(seq) < 0 or max(seq) >= V:
+            raise ValueError(f"generate(): token id {min(seq) if min(seq) < 0 else max(seq)} is outside the vocabulary [0, {V})")
         out: List[int] = []
         with self.optimizer.eval_mode():
             was = self.model.training

@@ -199,7 +199,15 @@ def test_truncation_and_sampling_helpers():
     g = torch.Generator().manual_seed(0)
     picks = {int(TrainEngine.sample_next_token(logits, 1.0, 0.5, g)) for _ in range(50)}
     assert picks == {1}                                        # nucleus 0.5 keeps only the top token
+    assert int(TrainEngine.sample_next_token(logits, 1.0, 0.0, g)) == 1      # top_p 0: the top token, not a NaN draw
     assert math.isclose(sum(TrainEngine.group_advantages([1.0, 2.0, 3.0])), 0.0, abs_tol=1e-6)
+    full = TrainEngine(TrainConfig(model_config=SMALL, max_seq_len=32, lora_rank=0, grpo_beta=0.0, amp_dtype="fp32")).initialize()
+    import pytest as _pytest
+    with _pytest.raises(ValueError, match="empty prompt"):
+        full.generate([], 2)
+    with _pytest.raises(ValueError, match="outside the vocabulary"):
+        full.generate([3, SMALL.vocab_size], 2)
+    assert full.generate([3, 4], 0) == [] and len(full.generate([3, 4], 3, temperature=0.0)) == 3
 
 
 def test_export_weights_leaves_the_lora_base_bit_identical():
