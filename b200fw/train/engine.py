@@ -167,8 +167,10 @@ class TrainEngine:
             mc = read_hf_config(cfg.model_path)
         self.model_config = mc
         if cfg.max_seq_len > mc.max_position_embeddings:
-            raise ValueError(f"max_seq_len={cfg.max_seq_len} exceeds the model's max_position_embeddings="
-                             f"{mc.max_position_embeddings}")
+            # sequences are truncated to max_seq_len when batches are built: truncate to what the model can address
+            logger.warning("max_seq_len=%d exceeds the model's max_position_embeddings=%d: using %d", cfg.max_seq_len,
+                           mc.max_position_embeddings, mc.max_position_embeddings)
+            cfg.max_seq_len = mc.max_position_embeddings
         layer_range, first, last = None, True, True
         if cfg.pp_size > 1:
             if mc.num_layers < cfg.pp_size:
