@@ -119,3 +119,45 @@ def test_profile_memory_from_yaml(tmp_path):
                     "--batch-size", "2", "--seq-len", "64", "--device", "cpu", "--skip-backward", "--output", str(out)])
     d = json.load(open(out))
     assert set(d) >= {"breakdown", "phase_peaks", "optimizer_bytes"} and "forward" in d["phase_peaks"] and rep is not None
+
+
+def test_sigterm_stops_run_colocate_at_an_iteration_boundary_and_the_checkpoint_resumes(tmp_path):
+    """The whole path a preempted job takes: ``run_colocate.py`` gets SIGTERM while it trains, finishes the iteration,
+    writes ``iter_N`` / ``latest`` with the orchestrator's position and exits 0; a second launch with ``--resume-from``
+    continues at iteration N."""
+    import signal
+    import time
+    cfg = tmp_path / "cfg.yaml"
+    cfg.write_text(f"""
+model: {{preset: tiny128, max_seq_len: 64}}
+runtime: {{precision: fp32, inference_backend: native}}
+training: {{mode: sft, total_iterations: 1000000, batch_size: 2, gradient_accumulation_steps: 1, warmup_steps: 0}}
+lora: {{rank: 0}}
+checkpoint: {{save_dir: {tmp_path}/ckpt}}
+experiment: {{output_dir: {tmp_path}/out}}
+inference_preview: {{enabled: false, max_tokens: 4}}
+""")
+    cmd = [sys.executable, os.path.join(ROOT, "scripts", "run_colocate.py"), "--config", str(cfg), "--synthetic"]
+    p = subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    try:
+        metrics = tmp_path / "out" / "metrics_rank0.jsonl"
+        deadline = time.time() + 240
+        while time.time() < deadline and not (metrics.exists() and metrics.stat().st_size > 0):
+            assert p.poll() is None, p.stdout.read()
+            time.sleep(0.2)
+        assert metrics.exists(), "the run never recorded an iteration"
+        p.send_signal(signal.SIGTERM)            # the exact child started above
+        out, _ = p.communicate(timeout=120)
+    finally:
+        if p.poll() is None:
+            p.kill()
+    assert p.returncode == 0, out[-2000:]
+    assert "stopping after the current iteration" in out
+    state = json.load(open(tmp_path / "ckpt" / "latest" / "orchestrator_state.json"))
+    done = state["iterations_completed"]
+    assert done >= 1 and os.path.isdir(tmp_path / "ckpt" / f"iter_{done}") and not os.path.exists(tmp_path / "ckpt" / "final")
+    cfg.write_text(cfg.read_text().replace("total_iterations: 1000000", f"total_iterations: {done + 2}"))
+    r = subprocess.run(cmd + ["--resume-from", str(tmp_path / "ckpt" / "latest")], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, (r.stdout + r.stderr)[-2000:]
+    assert f"continuing at iteration {done} of {done + 2}" in r.stdout + r.stderr
+    assert json.loads(r.stdout[r.stdout.index("{"):])["completed_iterations"] == 2
