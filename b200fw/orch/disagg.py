@@ -61,6 +61,8 @@ class DisaggConfig:
     inference_backend: str = "custom"    # rollout ranks run the native engine; a vLLM server is not driven from here
     async_weight_update: bool = True
     max_data_samples: int = 0
+    heartbeat_interval_s: float = 0.0    # > 0: ranks watch each other over the rendezvous store; an iteration is not
+    heartbeat_timeout_s: float = 10.0    # started once a peer is gone (PeerLostError instead of a hung collective)
 
     # The reference sizes its two groups by tensor-parallel degree and GPU lists and names the sync backend and the
     # overlap switch differently (src/orchestrator/disagg_orchestrator.py:40-70; its run_disaggregated.py passes
@@ -144,6 +146,12 @@ class DisaggOrchestrator:
     def initialize(self):
         cfg = self.config
         assert cfg.num_train_gpus + cfg.num_infer_gpus == self.world, "train + infer GPUs must equal WORLD_SIZE"
+        self.heartbeat = None
+        if cfg.heartbeat_interval_s > 0:
+            from ..dist.heartbeat import RankHeartbeat
+            self.heartbeat = RankHeartbeat.from_default_group(cfg.heartbeat_interval_s, cfg.heartbeat_timeout_s)
+            if self.heartbeat is not None:
+                self.heartbeat.start()
         tr = list(range(cfg.num_train_gpus))
         inf = list(range(cfg.num_train_gpus, self.world))
         self.train_group = dist.new_group(tr)
@@ -278,6 +286,8 @@ class DisaggOrchestrator:
         cfg = self.config
         prev = None     # (prompts, samples) generated in the previous iteration, trained in this one
         for it in range(cfg.total_iterations + (1 if cfg.mode == "pipeline" else 0)):
+            if getattr(self, "heartbeat", None) is not None:
+                self.heartbeat.check()           # a peer is gone: do not walk into this iteration's collectives
             t_iter = time.perf_counter()
             m = DisaggIterationMetrics(it)
             prompts = self._prompts(it)
@@ -351,4 +361,6 @@ class DisaggOrchestrator:
                 "weights_version": self.weights_version}
 
     def shutdown(self):
-        pass
+        hb = getattr(self, "heartbeat", None)
+        if hb is not None:
+            hb.announce_leave("shutdown")

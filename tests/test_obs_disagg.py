@@ -187,7 +187,8 @@ def _disagg_worker(rank, world, mode):
     cfg = DisaggConfig(num_train_gpus=2, num_infer_gpus=2, total_iterations=2, batch_size=4, num_samples_per_prompt=2,
                        prompt_len=8, max_tokens=5, mode=mode, kv_num_blocks=64,
                        # without CUDA peer memory the peer-write request falls back to the collective broadcast
-                       transfer_backend="peer_write" if mode == "sequential" else "nccl")
+                       transfer_backend="peer_write" if mode == "sequential" else "nccl",
+                       heartbeat_interval_s=0.05 if mode_arg.endswith("+leave") else 0.0, heartbeat_timeout_s=2.0)
 
     def trainer(group, n, r):
         ctx = ParallelContext(1, n, 1, r, n, r, "gloo")
@@ -209,6 +210,26 @@ def _disagg_worker(rank, world, mode):
         recs = [{"question": f"{i}+1?", "answer": f"#### {i + 1}"} for i in range(16)]
         data = GSM8KDataPipeline(records=recs, prompt_template="plain", max_prompt_tokens=8)
     o = DisaggOrchestrator(cfg, trainer, engine, data=data).initialize()
+    if mode_arg.endswith("+leave"):
+        # one iteration together; then the last rank shuts down between iterations and the others, once their
+        # watcher has seen it, refuse to start the next iteration
+        import time
+        from b200fw.dist import PeerLostError
+        assert o.heartbeat is not None
+        o.run()
+        if rank == world - 1:
+            o.shutdown()
+            time.sleep(4.0)
+            return {"left": True}
+        deadline = time.time() + 20
+        while o.heartbeat.lost is None and time.time() < deadline:
+            time.sleep(0.02)
+        t0 = time.time()
+        try:
+            o.run()
+        except PeerLostError as e:
+            return {"lost": e.rank, "reason": e.reason, "took": time.time() - t0, "iterations": len(o.metrics)}
+        return {"lost": None}
     if mode_arg.endswith("+fail"):
         # the last rank's engine breaks in the second iteration: every rank must leave the loop with that error
         if rank == world - 1:
@@ -359,3 +380,11 @@ def test_compute_profiler_layer_timing_and_memory_manager_thresholds(monkeypatch
     assert ref_form.get_stats() == {} and ref_form.check_memory_pressure()["utilization"] == 0
     ref_form.reserve_buffer(1)
     ref_form.release_buffer()
+
+
+def test_disaggregated_ranks_do_not_start_an_iteration_once_a_peer_has_left():
+    from _dist_util import run_ranks
+    res = run_ranks(_disagg_worker, 4, "sequential+leave", timeout=300)
+    assert res[3] == {"left": True}
+    for r in res[:3]:
+        assert r["lost"] == 3 and "shutdown" in r["reason"] and r["took"] < 0.5, r
