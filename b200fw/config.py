@@ -51,6 +51,7 @@ class ColocateConfig:
     checkpoint_save_dir: str = "checkpoints"
     checkpoint_save_interval: int = 0
     checkpoint_save_enabled: bool = True
+    checkpoint_keep_last: int = 0           # > 0: only the newest N ``iter_*`` directories are kept (``latest`` / ``final`` always)
     resume_from: Optional[str] = None
     train_steps_per_iteration: int = 1
     total_iterations: int = 10
@@ -160,6 +161,7 @@ _YAML_MAP: List[Tuple[str, str]] = [
     ("eval.max_tokens", "eval_max_tokens"), ("eval.num_prompts", "eval_num_prompts"),
     ("checkpoint.save_dir", "checkpoint_save_dir"), ("checkpoint.save_interval", "checkpoint_save_interval"),
     ("checkpoint.save_enabled", "checkpoint_save_enabled"), ("checkpoint.resume_from", "resume_from"),
+    ("checkpoint.keep_last", "checkpoint_keep_last"),
     ("experiment.output_dir", "output_dir"),
     ("profiling.enabled", "enable_profiling"), ("profiling.interval", "profile_interval"),
     ("icepop.enabled", "icepop_enabled"), ("icepop.divergence_threshold", "icepop_divergence_threshold"),

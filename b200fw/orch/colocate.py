@@ -842,6 +842,21 @@ class ColocateOrchestrator:
                                                os.path.join(d, "orchestrator_state.json"), as_json=True)
         self.train_engine.parallel_ctx.barrier()
         self._last_checkpoint_path = os.path.join(base, tag)
+        self._prune_checkpoints(base)
+
+    def _prune_checkpoints(self, base: str):
+        """``checkpoint.keep_last = N`` keeps the newest N ``iter_*`` directories (by iteration number) and deletes the
+        older ones, on rank 0, after the new checkpoint is complete; ``latest`` and ``final`` are never touched, nor
+        anything that is not an ``iter_<number>`` directory."""
+        keep = self.config.checkpoint_keep_last
+        if keep <= 0 or self.train_engine.parallel_ctx.global_rank != 0:
+            return
+        import re
+        import shutil
+        found = sorted((int(m.group(1)), name) for name in os.listdir(base)
+                       for m in [re.fullmatch(r"iter_(\d+)", name)] if m and os.path.isdir(os.path.join(base, name)))
+        for _, name in found[:-keep]:
+            shutil.rmtree(os.path.join(base, name), ignore_errors=True)
 
     @property
     def metrics_history(self) -> List[IterationMetrics]:

@@ -905,3 +905,14 @@ def test_a_stop_request_on_one_rank_stops_every_rank_after_the_same_iteration():
         assert stopped and its == [0]
         assert {"optimizer_state_rank0.pt", "optimizer_state_rank1.pt", "orchestrator_state.json", "trainer_state.json",
                 "rollout_rng_rank0.pt", "rollout_rng_rank1.pt"} <= set(files), files
+
+
+def test_checkpoint_retention_keeps_the_newest_iteration_directories():
+    with tempfile.TemporaryDirectory() as d:
+        cfg = _tiny_cfg(d, training_mode="sft", inference_preview_enabled=False, total_iterations=5,
+                        checkpoint_save_interval=1, checkpoint_keep_last=2)
+        os.makedirs(os.path.join(cfg.checkpoint_save_dir, "iter_notes"))          # not ours: left alone
+        _run(cfg)
+        assert sorted(os.listdir(cfg.checkpoint_save_dir)) == ["final", "iter_4", "iter_5", "iter_notes", "latest"]
+        st = json.load(open(os.path.join(cfg.checkpoint_save_dir, "iter_5", "orchestrator_state.json")))
+        assert st["iterations_completed"] == 5
