@@ -127,6 +127,15 @@ def generate_text(eng, tok, prompts, a, max_tokens, vocab):
     for s in range(0, len(prompts), step):
         chunk = prompts[s:s + step]
         toks = [[min(t, vocab - 1) for t in tok.encode(p)] for p in chunk]
+        empty = [p for p, t in zip(chunk, toks) if not t]
+        if empty:       # a prompt that encodes to nothing cannot be served: report it and go on with the others
+            print(f"[run_inference] {len(empty)} empty prompt(s) skipped", file=sys.stderr)
+            for p in empty:
+                results.append({"prompt": p, "sample_idx": 0, "output": "", "num_tokens": 0, "time_s": 0.0,
+                                "tokens_per_s": 0.0, "error": "empty prompt"})
+            chunk, toks = [p for p, t in zip(chunk, toks) if t], [t for t in toks if t]
+            if not chunk:
+                continue
         batch = [t for t in toks for _ in range(a.num_samples)]
         _sync()
         t0 = time.perf_counter()
