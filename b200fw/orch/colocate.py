@@ -165,6 +165,17 @@ class ColocateOrchestrator:
                     prompt_field=cfg.prompt_field, input_field=cfg.input_field or "input",
                     response_field=cfg.response_field, answer_field=cfg.answer_field or "answer",
                     dp_rank=ctx.dp_rank, dp_size=ctx.dp_size)
+        if isinstance(self.data, GSM8KDataPipeline):
+            tok = self.data.tokenizer
+            try:
+                tok_vocab = len(tok)
+            except TypeError:
+                tok_vocab = int(getattr(tok, "vocab_size", 0) or 0)
+            if tok_vocab > eng.model_config.vocab_size:
+                # fail here, once, with the reason - not in every iteration when a prompt's id is refused
+                raise ValueError(f"the tokenizer has {tok_vocab} ids but the model's vocabulary is "
+                                 f"{eng.model_config.vocab_size}: its prompts cannot be embedded (wrong model / "
+                                 "tokenizer pair, or a preset too small for text data)")
         if self.reward_fn is None:
             self.reward_fn = SyntheticTokenReward(eng.model_config.vocab_size, cfg.seed,
                                                   dense_weight=cfg.synthetic_reward_dense_weight) if cfg.synthetic_data \

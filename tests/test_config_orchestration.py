@@ -916,3 +916,26 @@ def test_checkpoint_retention_keeps_the_newest_iteration_directories():
         assert sorted(os.listdir(cfg.checkpoint_save_dir)) == ["final", "iter_4", "iter_5", "iter_notes", "latest"]
         st = json.load(open(os.path.join(cfg.checkpoint_save_dir, "iter_5", "orchestrator_state.json")))
         assert st["iterations_completed"] == 5
+
+
+def test_a_tokenizer_larger_than_the_model_vocabulary_is_refused_at_initialize():
+    from b200fw.data.pipeline import GSM8KDataPipeline, SimpleTokenizer
+
+    class Big(SimpleTokenizer):
+        vocab_size = 10 ** 6
+
+        def __len__(self):
+            return self.vocab_size
+    recs = [{"question": f"{i}+1?", "answer": f"#### {i + 1}"} for i in range(8)]
+    with tempfile.TemporaryDirectory() as d:
+        cfg = _tiny_cfg(d, synthetic_data=False, checkpoint_save_enabled=False)
+        data = GSM8KDataPipeline(records=recs, prompt_template="plain", tokenizer=Big())
+
+        async def go():
+            o = ColocateOrchestrator(cfg, data=data)
+            try:
+                await o.initialize()
+            finally:
+                await o.shutdown()
+        with pytest.raises(ValueError, match="tokenizer has 1000000 ids"):
+            asyncio.run(go())
