@@ -185,6 +185,17 @@ class DisaggOrchestrator:
                 self.transfer = WeightTransferManager("peer_write", peer_sync=peer)
             else:
                 self.transfer = WeightTransferManager("nccl", self.sync_group, src_rank=0)
+        if self.data is not None:
+            # every rank reads the same pipeline, so every rank refuses the same mismatch here, once, with the reason
+            tok = self.data.tokenizer
+            try:
+                tok_vocab = len(tok)
+            except TypeError:
+                tok_vocab = int(getattr(tok, "vocab_size", 0) or 0)
+            vocab = (self.train_engine.model_config.vocab_size if self.is_trainer else self.infer_engine.config.vocab_size)
+            if tok_vocab > vocab:
+                raise ValueError(f"the tokenizer has {tok_vocab} ids but the model's vocabulary is {vocab}: its prompts "
+                                 "cannot be embedded (wrong model / tokenizer pair)")
         if self.reward_fn is None and self.data is not None:
             from ..reward import GSM8KRewardFunction
             self.reward_fn = GSM8KRewardFunction()
