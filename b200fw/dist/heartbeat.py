@@ -76,7 +76,7 @@ class RankHeartbeat:
             try:
                 self.beat()
                 self.poll()
-            except Exception as e:  # noqa: BLE001 - the store itself is gone: the rank that hosts it (0) is
+            except Exception as e:  # noqa: BLE001 - the store no longer answers: rank 0, which hosts it, is gone
                 if self.lost is None and not self._stop.is_set():
                     self.lost = PeerLostError(0, f"the rendezvous store stopped answering ({type(e).__name__}: {e})")
                 return
